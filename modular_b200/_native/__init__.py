@@ -1,0 +1,57 @@
+"""Loader for the in-tree native library (``modular_b200/_C.so``).
+
+``lib()`` returns the extension module. On a machine with a CUDA device a missing or
+unloadable library is an error (ops must never fall back silently to eager PyTorch on a
+GPU); on a CPU-only machine ``lib(required=False)`` returns ``None`` and callers use the
+PyTorch reference implementations.
+"""
+
+from __future__ import annotations
+
+import importlib.util
+import os
+import threading
+from pathlib import Path
+
+_LOCK = threading.Lock()
+_MOD = None
+_TRIED = False
+_ERR: Exception | None = None
+SO_PATH = Path(__file__).resolve().parent.parent / "_C.so"
+
+
+def _load():
+    global _MOD, _TRIED, _ERR
+    with _LOCK:
+        if _TRIED:
+            return _MOD
+        _TRIED = True
+        try:
+            if not SO_PATH.exists() and os.environ.get("MB200_NO_BUILD") != "1":
+                from .build import build
+
+                build()
+            import torch  # noqa: F401  (libtorch must be loaded first)
+
+            spec = importlib.util.spec_from_file_location("modular_b200._C", str(SO_PATH))
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            _MOD = mod
+        except Exception as e:  # noqa: BLE001
+            _ERR = e
+            _MOD = None
+        return _MOD
+
+
+def lib(required: bool = True):
+    mod = _load()
+    if mod is None and required:
+        raise RuntimeError(
+            f"modular_b200 native library could not be loaded from {SO_PATH}: {_ERR!r}. "
+            "Run `python -m modular_b200._native.build`."
+        )
+    return mod
+
+
+def available() -> bool:
+    return _load() is not None

@@ -1,0 +1,333 @@
+// Python bindings: torch tensors in, raw pointers + current CUDA stream out.
+// No kernel is defined here; every op forwards to the C ABI in common/api.h or to the
+// native executor, so the same entry points serve Python, the C++ engine and C callers.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "common/api.h"
+#include "engine/decoder_executor.h"
+#include "runtime/runtime.h"
+
+namespace py = pybind11;
+using torch::Tensor;
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_rc(int rc, const char* what) {
+  if (rc == MB_OK) return;
+  const char* msg = "unknown";
+  switch (rc) {
+    case MB_ERR_SHAPE: msg = "unsupported shape"; break;
+    case MB_ERR_ALIGN: msg = "pointer not 16-byte aligned"; break;
+    case MB_ERR_DRIVER: msg = "driver entry point unavailable"; break;
+    case MB_ERR_TMAP: msg = "tensor-map encode failed"; break;
+    case MB_ERR_LAUNCH: msg = "kernel launch failed"; break;
+    case MB_ERR_TOO_LARGE: msg = "size beyond the supported maximum"; break;
+  }
+  throw std::runtime_error(std::string(what) + ": " + msg + " (" + std::to_string(rc) + ")");
+}
+
+void need_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+}
+const void* optptr(const c10::optional<Tensor>& t) {
+  return t.has_value() && t->defined() ? t->data_ptr() : nullptr;
+}
+
+// One error word per process (one process per GPU): kernels with bounded waits set it.
+int* error_flag() {
+  static int* flag = nullptr;
+  if (!flag) {
+    TORCH_CHECK(cudaMalloc(&flag, sizeof(int)) == cudaSuccess, "cudaMalloc(error flag)");
+    cudaMemset(flag, 0, sizeof(int));
+  }
+  return flag;
+}
+int read_error_flag(bool reset) {
+  int v = 0;
+  cudaMemcpy(&v, error_flag(), sizeof(int), cudaMemcpyDeviceToHost);
+  if (reset && v) cudaMemset(error_flag(), 0, sizeof(int));
+  return v;
+}
+
+int num_sms() {
+  static int n = 0;
+  if (!n) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  return n;
+}
+
+// y = x @ w.T with optional fusions; see mb_gemm_bf16.
+void gemm_bf16(const Tensor& x, const Tensor& w, Tensor& y, const c10::optional<Tensor>& residual,
+               bool dual, const c10::optional<Tensor>& workspace, int bn, int splits, int stages) {
+  need_cuda(x, "x"); need_cuda(w, "w"); need_cuda(y, "y");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2, "gemm_bf16: 2-D tensors expected");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "bf16 inputs");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1, "row-major operands");
+  const int M = x.size(0), K = x.size(1);
+  const int N = dual ? w.size(0) / 2 : w.size(0);
+  TORCH_CHECK(w.size(1) == K && y.size(0) == M && y.size(1) == N, "gemm_bf16: shape mismatch");
+  const bool f32 = y.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || y.scalar_type() == at::kBFloat16, "output must be bf16 or fp32");
+  int flags = (dual ? 1 : 0) | (residual.has_value() && residual->defined() ? 2 : 0) | (f32 ? 4 : 0);
+  void* ws = nullptr;
+  if (workspace.has_value() && workspace->defined()) {
+    ws = workspace->data_ptr();
+    if (splits <= 0) {
+      int pbn, psp, pst;
+      mb_gemm_bf16_plan(M, N, K, dual, num_sms(), &pbn, &psp, &pst);
+      splits = psp;
+    }
+    if (static_cast<size_t>(splits) * M * N * 4 > static_cast<size_t>(workspace->nbytes())) splits = 1;
+  } else {
+    splits = 1;
+  }
+  int ldr = 0;
+  if (flags & 2) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->stride(1) == 1, "residual");
+    ldr = residual->stride(0);
+  }
+  check_rc(mb_gemm_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), optptr(residual), M, N, K,
+                        x.stride(0), w.stride(0), y.stride(0), ldr, flags, bn, splits, stages, ws,
+                        error_flag(), num_sms(), cur_stream()),
+           "gemm_bf16");
+}
+
+py::tuple gemm_plan(int M, int N, int K, bool dual) {
+  int bn, sp, st;
+  mb_gemm_bf16_plan(M, N, K, dual, num_sms(), &bn, &sp, &st);
+  return py::make_tuple(bn, sp, st);
+}
+
+void rmsnorm(const Tensor& x, const Tensor& w, Tensor& out, double eps, double w_off, bool mbc) {
+  need_cuda(x, "x");
+  check_rc(mb_rmsnorm(x.data_ptr(), w.data_ptr(), out.data_ptr(), x.size(0), x.size(1),
+                      x.stride(0), out.stride(0), eps, w_off, mbc, cur_stream()),
+           "rmsnorm");
+}
+void add_rmsnorm(const Tensor& x, Tensor& residual, const Tensor& w, Tensor& out, double eps,
+                 double w_off, bool mbc) {
+  need_cuda(x, "x");
+  TORCH_CHECK(x.is_contiguous() && residual.is_contiguous() && out.is_contiguous(), "contiguous");
+  check_rc(mb_add_rmsnorm(x.data_ptr(), residual.data_ptr(), w.data_ptr(), out.data_ptr(),
+                          x.size(0), x.size(1), eps, w_off, mbc, cur_stream()),
+           "add_rmsnorm");
+}
+void silu_mul(const Tensor& gu, Tensor& out) {
+  need_cuda(gu, "gate_up");
+  TORCH_CHECK(gu.is_contiguous() && out.is_contiguous(), "contiguous");
+  check_rc(mb_silu_mul(gu.data_ptr(), out.data_ptr(), gu.size(0), gu.size(1) / 2, cur_stream()),
+           "silu_mul");
+}
+void embedding(const Tensor& ids, const Tensor& table, Tensor& out, int vocab_start) {
+  need_cuda(ids, "ids");
+  TORCH_CHECK(ids.scalar_type() == at::kLong && table.is_contiguous() && out.is_contiguous(), "embedding");
+  check_rc(mb_embedding(ids.data_ptr<int64_t>(), table.data_ptr(), out.data_ptr(), ids.numel(),
+                        table.size(1), table.size(0), vocab_start, cur_stream()),
+           "embedding");
+}
+void gather_rows(const Tensor& src, const Tensor& idx, Tensor& dst) {
+  need_cuda(src, "src");
+  TORCH_CHECK(idx.scalar_type() == at::kInt && dst.is_contiguous() && src.stride(1) == 1, "gather_rows");
+  check_rc(mb_gather_rows(src.data_ptr(), idx.data_ptr<int32_t>(), dst.data_ptr(), idx.numel(),
+                          src.size(1) * src.element_size(), src.stride(0) * src.element_size(),
+                          cur_stream()),
+           "gather_rows");
+}
+
+// k_cache / v_cache: views [pages, n_kv, page_size, head_dim] of one layer (any page stride).
+void rope_kv_store(Tensor& qkv, const Tensor& positions, const Tensor& slots, const Tensor& cos_sin,
+                   Tensor& k_cache, Tensor& v_cache, int n_q, int n_kv, int head_dim,
+                   bool interleaved) {
+  need_cuda(qkv, "qkv");
+  TORCH_CHECK(qkv.is_contiguous() && positions.scalar_type() == at::kInt &&
+                  slots.scalar_type() == at::kLong && cos_sin.scalar_type() == at::kFloat,
+              "rope_kv_store: dtypes");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.stride(3) == 1 && k_cache.stride(2) == head_dim, "cache layout");
+  TORCH_CHECK(v_cache.stride(0) == k_cache.stride(0) && v_cache.stride(1) == k_cache.stride(1), "k/v strides");
+  check_rc(mb_rope_kv_store(qkv.data_ptr(), positions.data_ptr<int32_t>(), slots.data_ptr<int64_t>(),
+                            cos_sin.data_ptr<float>(), k_cache.data_ptr(), v_cache.data_ptr(),
+                            qkv.size(0), n_q, n_kv, head_dim, k_cache.size(2), k_cache.stride(0),
+                            k_cache.stride(1), interleaved, cur_stream()),
+           "rope_kv_store");
+}
+
+void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_cache, const Tensor& v_cache,
+                     const Tensor& block_table, const Tensor& q_start, const Tensor& q_len,
+                     const Tensor& kv_len, const c10::optional<Tensor>& tile_seq,
+                     const c10::optional<Tensor>& tile_q0, const c10::optional<Tensor>& decode_seq,
+                     int n_q, int n_kv, int head_dim, double scale) {
+  need_cuda(q, "q");
+  TORCH_CHECK(q.dim() == 2 && out.dim() == 2 && q.stride(1) == 1 && out.stride(1) == 1, "q/out 2-D");
+  TORCH_CHECK(block_table.scalar_type() == at::kInt && block_table.dim() == 2, "block_table int32 2-D");
+  const int n_tiles = tile_seq.has_value() && tile_seq->defined() ? tile_seq->numel() : 0;
+  const int n_dec = decode_seq.has_value() && decode_seq->defined() ? decode_seq->numel() : 0;
+  check_rc(mb_paged_attention(
+               q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(),
+               v_cache.data_ptr(), block_table.data_ptr<int32_t>(), block_table.stride(0),
+               q_start.data_ptr<int32_t>(), q_len.data_ptr<int32_t>(), kv_len.data_ptr<int32_t>(),
+               static_cast<const int32_t*>(optptr(tile_seq)),
+               static_cast<const int32_t*>(optptr(tile_q0)), n_tiles, n_dec,
+               static_cast<const int32_t*>(optptr(decode_seq)), n_q, n_kv, head_dim,
+               k_cache.size(2), k_cache.stride(0), k_cache.stride(1), scale, cur_stream()),
+           "paged_attention");
+}
+
+void argmax(const Tensor& logits, Tensor& out) {
+  need_cuda(logits, "logits");
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && out.scalar_type() == at::kLong, "argmax dtypes");
+  check_rc(mb_argmax(logits.data_ptr<float>(), out.data_ptr<int64_t>(), logits.size(0),
+                     logits.size(1), logits.stride(0), cur_stream()),
+           "argmax");
+}
+void sample(const Tensor& logits, Tensor& out, const c10::optional<Tensor>& temperature,
+            const c10::optional<Tensor>& top_k, const c10::optional<Tensor>& top_p,
+            const c10::optional<Tensor>& min_p, const c10::optional<Tensor>& seeds, int64_t step) {
+  need_cuda(logits, "logits");
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && out.scalar_type() == at::kLong, "sample dtypes");
+  check_rc(mb_sample_topk_topp(logits.data_ptr<float>(), out.data_ptr<int64_t>(), logits.size(0),
+                               logits.size(1), logits.stride(0),
+                               static_cast<const float*>(optptr(temperature)),
+                               static_cast<const int32_t*>(optptr(top_k)),
+                               static_cast<const float*>(optptr(top_p)),
+                               static_cast<const float*>(optptr(min_p)),
+                               static_cast<const uint64_t*>(optptr(seeds)),
+                               static_cast<uint64_t>(step), cur_stream()),
+           "sample");
+}
+void apply_penalties(Tensor& logits, const Tensor& tok, const Tensor& cnt, const Tensor& offsets,
+                     const c10::optional<Tensor>& freq, const c10::optional<Tensor>& pres,
+                     const c10::optional<Tensor>& rep) {
+  need_cuda(logits, "logits");
+  check_rc(mb_apply_penalties(logits.data_ptr<float>(), logits.size(0), logits.size(1),
+                              logits.stride(0), tok.data_ptr<int32_t>(), cnt.data_ptr<int32_t>(),
+                              offsets.data_ptr<int32_t>(), static_cast<const float*>(optptr(freq)),
+                              static_cast<const float*>(optptr(pres)),
+                              static_cast<const float*>(optptr(rep)), cur_stream()),
+           "apply_penalties");
+}
+
+// ------------------------------------------------------------------ executor wrapper
+class PyDecoderExecutor {
+ public:
+  mb::DecoderExecutor ex;
+  std::vector<Tensor> keep;  // keeps every tensor whose pointer the executor holds alive
+
+  PyDecoderExecutor(py::dict cfg) {
+    auto& c = ex.cfg;
+    c.n_layers = cfg["n_layers"].cast<int>();
+    c.hidden = cfg["hidden"].cast<int>();
+    c.n_q = cfg["n_q"].cast<int>();
+    c.n_kv = cfg["n_kv"].cast<int>();
+    c.head_dim = cfg["head_dim"].cast<int>();
+    c.inter = cfg["inter"].cast<int>();
+    c.vocab = cfg["vocab"].cast<int>();
+    c.eps = cfg["eps"].cast<float>();
+    c.norm_weight_offset = cfg.contains("norm_weight_offset") ? cfg["norm_weight_offset"].cast<float>() : 0.f;
+    c.multiply_before_cast = cfg.contains("multiply_before_cast") ? cfg["multiply_before_cast"].cast<int>() : 0;
+    c.rope_interleaved = cfg.contains("rope_interleaved") ? cfg["rope_interleaved"].cast<int>() : 0;
+    c.page_size = cfg["page_size"].cast<int>();
+    c.attn_scale = cfg["attn_scale"].cast<float>();
+    c.logits_scale = 1.f;
+    c.fuse_swiglu = cfg.contains("fuse_swiglu") ? cfg["fuse_swiglu"].cast<int>() : 1;
+    c.num_sms = num_sms();
+    ex.buf.err = error_flag();
+  }
+  const void* hold(const Tensor& t) {
+    TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "executor tensors must be contiguous CUDA tensors");
+    keep.push_back(t);
+    return t.data_ptr();
+  }
+  void set_globals(const Tensor& embed, const Tensor& final_norm, const Tensor& lm_head,
+                   const Tensor& cos_sin) {
+    ex.embed = hold(embed);
+    ex.final_norm = hold(final_norm);
+    ex.lm_head = hold(lm_head);
+    ex.cos_sin = static_cast<const float*>(hold(cos_sin));
+  }
+  void add_layer(const Tensor& attn_norm, const Tensor& wqkv, const Tensor& wo,
+                 const Tensor& mlp_norm, const Tensor& wgu, const Tensor& wd) {
+    mb::DecoderLayerWeights w;
+    w.attn_norm = hold(attn_norm); w.wqkv = hold(wqkv); w.wo = hold(wo);
+    w.mlp_norm = hold(mlp_norm); w.wgu = hold(wgu); w.wd = hold(wd);
+    ex.layers.push_back(w);
+  }
+  // kv: [pages, 2, n_layers, n_kv, page_size, head_dim]
+  void set_kv_cache(const Tensor& kv) {
+    TORCH_CHECK(kv.dim() == 6 && kv.is_contiguous(), "kv cache must be 6-D contiguous");
+    ex.kv.base = const_cast<void*>(hold(kv));
+    ex.kv.page_stride = kv.stride(0);
+    ex.kv.kv_stride = kv.stride(1);
+    ex.kv.layer_stride = kv.stride(2);
+    ex.kv.head_stride = kv.stride(3);
+  }
+  void set_buffers(const Tensor& h, const Tensor& xn, const Tensor& qkv, const Tensor& attn,
+                   const Tensor& act, const c10::optional<Tensor>& gu, const Tensor& last_h,
+                   const Tensor& last_xn, const Tensor& logits, const Tensor& workspace) {
+    auto& b = ex.buf;
+    b.h = const_cast<void*>(hold(h)); b.xn = const_cast<void*>(hold(xn));
+    b.qkv = const_cast<void*>(hold(qkv)); b.attn = const_cast<void*>(hold(attn));
+    b.act = const_cast<void*>(hold(act));
+    b.gu = gu.has_value() && gu->defined() ? const_cast<void*>(hold(*gu)) : nullptr;
+    b.last_h = const_cast<void*>(hold(last_h)); b.last_xn = const_cast<void*>(hold(last_xn));
+    b.logits = static_cast<float*>(const_cast<void*>(hold(logits)));
+    b.workspace = const_cast<void*>(hold(workspace));
+    b.workspace_bytes = workspace.nbytes();
+  }
+  // meta: one int32 device tensor holding every per-step array; offsets are in int32 units
+  // (tokens and slots are int64 and 8-byte aligned inside it).
+  void forward(const Tensor& meta, py::dict off, int T, int B, int bt_stride, int n_tiles,
+               int n_decode, int n_logits) {
+    const int32_t* base = meta.data_ptr<int32_t>();
+    auto at32 = [&](const char* k) { return base + off[k].cast<int64_t>(); };
+    mb::StepInputs in;
+    in.tokens = reinterpret_cast<const int64_t*>(at32("tokens"));
+    in.slots = reinterpret_cast<const int64_t*>(at32("slots"));
+    in.positions = at32("positions");
+    in.block_table = at32("block_table");
+    in.q_start = at32("q_start"); in.q_len = at32("q_len"); in.kv_len = at32("kv_len");
+    in.tile_seq = at32("tile_seq"); in.tile_q0 = at32("tile_q0");
+    in.decode_seq = at32("decode_seq"); in.logit_rows = at32("logit_rows");
+    in.T = T; in.B = B; in.bt_stride = bt_stride; in.n_tiles = n_tiles; in.n_decode = n_decode;
+    in.n_logits = n_logits;
+    check_rc(ex.forward(in, cur_stream()), "DecoderExecutor.forward");
+  }
+  long launches() const { return ex.launches; }
+};
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "modular_b200 native kernels and runtime (sm_100a)";
+  m.def("gemm_bf16", &gemm_bf16, py::arg("x"), py::arg("w"), py::arg("y"),
+        py::arg("residual") = py::none(), py::arg("dual") = false,
+        py::arg("workspace") = py::none(), py::arg("bn") = 0, py::arg("splits") = 0,
+        py::arg("stages") = 0);
+  m.def("gemm_plan", &gemm_plan);
+  m.def("rmsnorm", &rmsnorm);
+  m.def("add_rmsnorm", &add_rmsnorm);
+  m.def("silu_mul", &silu_mul);
+  m.def("embedding", &embedding);
+  m.def("gather_rows", &gather_rows);
+  m.def("rope_kv_store", &rope_kv_store);
+  m.def("paged_attention", &paged_attention);
+  m.def("argmax", &argmax);
+  m.def("sample", &sample);
+  m.def("apply_penalties", &apply_penalties);
+  m.def("read_error_flag", &read_error_flag, py::arg("reset") = true);
+  m.def("num_sms", &num_sms);
+  py::class_<PyDecoderExecutor>(m, "DecoderExecutor")
+      .def(py::init<py::dict>())
+      .def("set_globals", &PyDecoderExecutor::set_globals)
+      .def("add_layer", &PyDecoderExecutor::add_layer)
+      .def("set_kv_cache", &PyDecoderExecutor::set_kv_cache)
+      .def("set_buffers", &PyDecoderExecutor::set_buffers)
+      .def("forward", &PyDecoderExecutor::forward)
+      .def("launches", &PyDecoderExecutor::launches);
+  mb::bind_runtime(m);
+}

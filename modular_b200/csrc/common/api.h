@@ -1,0 +1,72 @@
+// C ABI of the kernel library. Every launcher takes raw device pointers and a stream,
+// returns MB_OK or a negative error code, allocates nothing and never synchronises.
+// Kernels that wait on barriers or flags report a timed-out wait through `err`
+// (a device int that stays 0 on success).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MB_OK 0
+#define MB_ERR_SHAPE -1
+#define MB_ERR_ALIGN -2
+#define MB_ERR_DRIVER -3
+#define MB_ERR_TMAP -4
+#define MB_ERR_LAUNCH -5
+#define MB_ERR_TOO_LARGE -6
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- GEMM (gemm_tcgen05.cu) -------------------------------------------------------------
+void mb_gemm_bf16_plan(int M, int N, int K, int dual, int num_sms, int* bn, int* splits,
+                       int* stages);
+int mb_gemm_bf16(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,
+                 int ldx, int ldw, int ldy, int ldr, int flags, int bn, int splits, int stages,
+                 void* workspace, int* err, int num_sms, cudaStream_t stream);
+
+// ---- block-scaled fp8 (gemm_fp8_blockscaled.cu, quant_fp8.cu) ----------------------------
+int mb_quant_fp8_group128(const void* x_bf16, void* q_fp8, float* scales, int M, int K, int ldx,
+                          int scale_ld, int scales_k_major, cudaStream_t stream);
+int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const void* Wq, const float* Ws,
+                            void* Y, const void* R, int M, int N, int K, int flags, int bn,
+                            int stages, int* err, cudaStream_t stream);
+
+// ---- elementwise / normalisation / rope (elementwise.cu) ---------------------------------
+int mb_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, int ldx, int ldo,
+               float eps, float weight_offset, int multiply_before_cast, cudaStream_t stream);
+int mb_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int rows, int cols,
+                   float eps, float weight_offset, int multiply_before_cast, cudaStream_t stream);
+int mb_silu_mul(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream);
+int mb_embedding(const int64_t* ids, const void* table, void* out, int n, int hidden, int vocab,
+                 int vocab_start, cudaStream_t stream);
+// RoPE on Q and K (in place in the fused QKV buffer) + K/V scatter into the paged cache.
+int mb_rope_kv_store(void* qkv, const int32_t* positions, const int64_t* slots,
+                     const float* cos_sin, void* k_cache, void* v_cache, int T, int n_q, int n_kv,
+                     int head_dim, int page_size, int64_t page_stride, int64_t head_stride,
+                     int interleaved, cudaStream_t stream);
+int mb_gather_rows(const void* src, const int32_t* idx, void* dst, int n, int row_bytes, int ld_src,
+                   cudaStream_t stream);
+
+// ---- attention (attention.cu) --------------------------------------------------------------
+int mb_paged_attention(const void* q, int ldq, void* out, int ldo, const void* k_cache,
+                       const void* v_cache, const int32_t* block_table, int bt_stride,
+                       const int32_t* q_start, const int32_t* q_len, const int32_t* kv_len,
+                       const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles,
+                       int n_decode, const int32_t* decode_seq, int n_q, int n_kv, int head_dim,
+                       int page_size, int64_t page_stride, int64_t head_stride, float scale,
+                       cudaStream_t stream);
+
+// ---- sampling (sampling.cu) ----------------------------------------------------------------
+int mb_argmax(const float* logits, int64_t* out, int rows, int vocab, int ld, cudaStream_t stream);
+int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, int vocab, int ld,
+                        const float* temperature, const int32_t* top_k, const float* top_p,
+                        const float* min_p, const uint64_t* seeds, uint64_t step,
+                        cudaStream_t stream);
+int mb_apply_penalties(float* logits, int rows, int vocab, int ld, const int32_t* tok,
+                       const int32_t* cnt, const int32_t* offsets, const float* freq_pen,
+                       const float* pres_pen, const float* rep_pen, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,95 @@
+// Native forward executor for Llama-family decoder stacks.
+//
+// The Python pipeline hands over raw device pointers once (weights, KV cache, scratch
+// activations) and then calls `forward` once per scheduler step; the executor issues
+// every kernel of the step on the caller's stream without touching the Python
+// interpreter, allocating, or synchronising. This plays the role the reference gives to
+// its compiled graph (`Model.execute`, max/python/max/engine/api.py:120): one host call
+// per step, replayable under CUDA graph capture because every buffer address is fixed.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <vector>
+
+namespace mb {
+
+struct DecoderLayerWeights {
+  const void* attn_norm;  // [hidden]
+  const void* wqkv;       // [(n_q + 2 n_kv) * head_dim, hidden]
+  const void* wo;         // [hidden, n_q * head_dim]
+  const void* mlp_norm;   // [hidden]
+  const void* wgu;        // [2 * inter, hidden]  (gate rows then up rows)
+  const void* wd;         // [hidden, inter]
+};
+
+struct DecoderConfig {
+  int n_layers, hidden, n_q, n_kv, head_dim, inter, vocab;
+  float eps;
+  float norm_weight_offset;   // 0 for Llama, 1 for Gemma-style (1 + w)
+  int multiply_before_cast;   // RMSNorm rounding order
+  int rope_interleaved;
+  int page_size;
+  float attn_scale;
+  float logits_scale;
+  int fuse_swiglu;            // gate/up GEMM with SwiGLU epilogue
+  int num_sms;
+};
+
+struct DecoderBuffers {
+  void* h;        // [max_tokens, hidden] residual stream
+  void* xn;       // [max_tokens, hidden]
+  void* qkv;      // [max_tokens, (n_q + 2 n_kv) * head_dim]
+  void* attn;     // [max_tokens, n_q * head_dim]
+  void* act;      // [max_tokens, inter] (or [max_tokens, 2*inter] + act when not fused)
+  void* gu;       // [max_tokens, 2*inter] only when !fuse_swiglu
+  void* last_h;   // [max_seqs, hidden]
+  void* last_xn;  // [max_seqs, hidden]
+  float* logits;  // [max_seqs, vocab]
+  void* workspace;  // split-K partials
+  size_t workspace_bytes;
+  int* err;
+};
+
+struct KVCacheView {
+  void* base;            // bf16
+  int64_t page_stride;   // elements between consecutive pages
+  int64_t kv_stride;     // elements between the K and V planes of a page
+  int64_t layer_stride;  // elements between layers inside a page
+  int64_t head_stride;   // elements between KV heads (= page_size * head_dim)
+};
+
+// Device-resident per-step metadata (one packed H2D copy per step).
+struct StepInputs {
+  const int64_t* tokens;      // [T]
+  const int32_t* positions;   // [T]
+  const int64_t* slots;       // [T] flat KV slot (page * page_size + offset), -1 = skip
+  const int32_t* block_table; // [B, bt_stride]
+  const int32_t* q_start;     // [B]
+  const int32_t* q_len;       // [B]
+  const int32_t* kv_len;      // [B]
+  const int32_t* tile_seq;    // [n_tiles]
+  const int32_t* tile_q0;     // [n_tiles]
+  const int32_t* decode_seq;  // [n_decode]
+  const int32_t* logit_rows;  // [n_logits] token rows whose logits are wanted
+  int T, B, bt_stride, n_tiles, n_decode, n_logits;
+};
+
+class DecoderExecutor {
+ public:
+  DecoderConfig cfg;
+  DecoderBuffers buf;
+  KVCacheView kv;
+  const void* embed = nullptr;
+  const void* final_norm = nullptr;
+  const void* lm_head = nullptr;
+  const float* cos_sin = nullptr;
+  std::vector<DecoderLayerWeights> layers;
+  long launches = 0;  // kernels launched since construction (for accounting)
+
+  // Runs embedding -> layers -> final norm -> LM head on `stream`. Returns MB_OK or the
+  // first launcher error.
+  int forward(const StepInputs& in, cudaStream_t stream);
+};
+
+}  // namespace mb

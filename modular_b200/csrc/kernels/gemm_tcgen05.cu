@@ -1,0 +1,457 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   Y[M, N] = X[M, K] · W[N, K]^T            (nn.Linear layout, both operands K-major)
+//
+// The weight matrix always sits on the UMMA "M" side (128 weight rows per CTA tile)
+// and the activations on the UMMA "N" side (BN tokens, any multiple of 16 up to 256,
+// chosen at run time). Serving batches are ragged in the token count, so putting the
+// tokens on the side with 16-granularity keeps the tensor cores full at M = 64..600
+// where a 128-row token tile would waste up to half of every instruction.
+//
+// One CTA = 6 warps:
+//   warp 0     TMA producer   (cp.async.bulk.tensor 2-D, 128B swizzle, no multicast)
+//   warp 1     MMA issuer     (tcgen05.mma kind::f16, fp32 accumulators in TMEM)
+//   warps 2-5  epilogue       (tcgen05.ld -> registers -> smem transpose -> 16-byte stores)
+//
+// Fused epilogues: bf16 store, bf16 store with residual add, fp32 store (split-K
+// partials / logits), and a "dual" mode where two weight tiles (gate, up) feed two
+// accumulators and the epilogue writes silu(gate) * up.
+//
+// Behavioural counterpart in the reference: the warp-specialised sm100 matmul
+// (max/kernels/src/linalg/matmul/gpu/sm100_structured/default/matmul_kernels.mojo:348)
+// and its fused SwiGLU variant (sm100_structured/fused_swiglu/matmul_swiglu_kernels.mojo).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "../common/ptx.cuh"
+#include "../common/api.h"
+
+namespace mb {
+
+constexpr int kBM = 128;          // weight rows per tile (UMMA M)
+constexpr int kBK = 64;           // bf16 elements per 128-byte swizzle row
+constexpr int kUmmaK = 16;        // K of one tcgen05.mma kind::f16
+constexpr int kATileBytes = kBM * kBK * 2;  // 16 KiB
+constexpr int kStageWarpBytes = 32 * 32 * 2;  // per-epilogue-warp transpose buffer
+constexpr int kGemmThreads = 192;
+
+enum GemmEpi { EPI_BF16 = 0, EPI_BF16_RESIDUAL = 1, EPI_F32 = 2 };
+
+struct GemmSmemTail {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full;
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+template <bool DUAL, int EPI>
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+               void* __restrict__ Yv, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
+               int ldy, int ldr, int dual_rows, int k_per_split, int BN, int stages,
+               uint32_t tmem_cols, int* err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int a_bytes = kATileBytes * (DUAL ? 2 : 1);
+  const int b_bytes = BN * kBK * 2;
+  const int stage_bytes = a_bytes + b_bytes;
+  uint8_t* stage_buf = smem + stages * stage_bytes;  // 4 * 2 KiB epilogue transpose buffers
+  GemmSmemTail* tail = reinterpret_cast<GemmSmemTail*>(stage_buf + 4 * kStageWarpBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tile = blockIdx.x;  // token tile (fast index: CTAs sharing a weight tile co-run)
+  const int n_tile = blockIdx.y;  // weight-row tile
+  const int split = blockIdx.z;
+  const int n0 = n_tile * kBM;
+  const int t0 = m_tile * BN;
+  const int k_begin = split * k_per_split;
+  const int k_end = min(K, k_begin + k_per_split);
+  const int k_iters = (k_end - k_begin + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 1);
+    }
+    mbar_init(&tail->tmem_full, 1);
+    tail->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tail->tmem_base, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tail->tmem_base;
+  volatile int* abort_word = &tail->abort_word;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int it = 0; it < k_iters; ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1;
+        if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, err, 101)) break;
+        uint8_t* sa = smem + s * stage_bytes;
+        uint8_t* sb = sa + a_bytes;
+        mbar_arrive_expect_tx(&tail->full[s], stage_bytes);
+        const int kc = k_begin + it * kBK;
+        tma_load_2d(sa, &tmW, &tail->full[s], kc, n0);
+        if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, &tail->full[s], kc, dual_rows + n0);
+        tma_load_2d(sb, &tmX, &tail->full[s], kc, t0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(kBM, BN, 1, 1);
+      bool ok = true;
+      for (int it = 0; it < k_iters && ok; ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1;
+        ok = mbar_wait(&tail->full[s], ph, abort_word, err, 102);
+        if (!ok) break;
+        tc_fence_after();
+        uint8_t* sa = smem + s * stage_bytes;
+        const uint64_t da0 = umma_desc_sw128(sa);
+        const uint64_t da1 = umma_desc_sw128(sa + kATileBytes);
+        const uint64_t db = umma_desc_sw128(sa + a_bytes);
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+          const uint64_t koff = static_cast<uint64_t>(k * kUmmaK * 2 >> 4);
+          umma_bf16(tmem_base, da0 + koff, db + koff, idesc, acc);
+          if (DUAL) umma_bf16(tmem_base + BN, da1 + koff, db + koff, idesc, acc);
+        }
+        tc_commit(&tail->empty[s]);  // frees the smem stage when these MMAs retire
+      }
+      tc_commit(&tail->tmem_full);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const bool ok = mbar_wait(&tail->tmem_full, 0, abort_word, err, 103);
+    tc_fence_after();
+    if (ok && k_iters > 0) {
+      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(stage_buf + quad * kStageWarpBytes);
+      const int n_row = n0 + quad * 32 + lane;  // weight row (= output column) of this thread
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (t0 + c0 >= M) break;  // warp-uniform
+        uint32_t g[16];
+        tmem_ld_32x16(lane_addr + c0, g);
+        float v[16];
+        if (DUAL) {
+          uint32_t u[16];
+          tmem_ld_32x16(lane_addr + BN + c0, u);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+        } else {
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(g[j]);
+        }
+        if (EPI == EPI_F32) {
+          float* Y = reinterpret_cast<float*>(Yv) + static_cast<size_t>(split) * M * ldy;
+          if (n_row < N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c0 + j;
+              if (t < M) Y[static_cast<size_t>(t) * ldy + n_row] = v[j];
+            }
+          }
+        } else {
+          __nv_bfloat16* Y = reinterpret_cast<__nv_bfloat16*>(Yv);
+          // transpose through this warp's private buffer: stg[token j][weight row lane]
+#pragma unroll
+          for (int j = 0; j < 16; ++j) stg[j * 32 + lane] = __float2bfloat16(v[j]);
+          __syncwarp();
+          // 16 tokens x 64 bytes: 4 lanes cover one token row, 8 tokens per pass
+#pragma unroll
+          for (int pass = 0; pass < 2; ++pass) {
+            const int j = pass * 8 + (lane >> 2);
+            const int seg = lane & 3;
+            const int t = t0 + c0 + j;
+            const int n = n0 + quad * 32 + seg * 8;
+            if (t < M && n < N) {
+              uint4 val = *reinterpret_cast<const uint4*>(stg + j * 32 + seg * 8);
+              if (EPI == EPI_BF16_RESIDUAL) {
+                const uint4 rv =
+                    *reinterpret_cast<const uint4*>(R + static_cast<size_t>(t) * ldr + n);
+                __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&val);
+                const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float2 fa = __bfloat1622float2(a[q]);
+                  const float2 fb = __bfloat1622float2(b[q]);
+                  a[q] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+                }
+              }
+              *reinterpret_cast<uint4*>(Y + static_cast<size_t>(t) * ldy + n) = val;
+            }
+          }
+          __syncwarp();
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// Sum split-K fp32 partials [splits, M, N] -> bf16 Y (+ optional residual).
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, const __nv_bfloat16* __restrict__ R,
+                                     __nv_bfloat16* __restrict__ Y, int M, int N, int splits,
+                                     int ldy, int ldr) {
+  const size_t idx = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  const size_t total = static_cast<size_t>(M) * N;
+  if (idx >= total) return;
+  const int t = static_cast<int>(idx / N);
+  const int n = static_cast<int>(idx % N);
+  float4 acc = *reinterpret_cast<const float4*>(part + idx);
+  for (int s = 1; s < splits; ++s) {
+    const float4 p = *reinterpret_cast<const float4*>(part + s * total + idx);
+    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+  }
+  __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+  __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+  if (R != nullptr) {
+    const uint2 rv = *reinterpret_cast<const uint2*>(R + static_cast<size_t>(t) * ldr + n);
+    const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rv);
+    float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(rb[0]);
+    lo = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+    a = __bfloat1622float2(hi); b = __bfloat1622float2(rb[1]);
+    hi = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+  }
+  uint2 out;
+  out.x = *reinterpret_cast<uint32_t*>(&lo);
+  out.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(Y + static_cast<size_t>(t) * ldy + n) = out;
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D row-major [rows, cols] tensor of `elt_bytes` elements; box = [box_rows, 128 bytes].
+int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_rows, int elt_bytes) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return MB_ERR_DRIVER;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elt_bytes)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elt_bytes), box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt =
+      elt_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MB_OK : MB_ERR_TMAP;
+}
+
+struct TmapKey {
+  const void* p;
+  uint64_t rows, cols, ld;
+  uint32_t box;
+  bool operator==(const TmapKey& o) const {
+    return p == o.p && rows == o.rows && cols == o.cols && ld == o.ld && box == o.box;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.p);
+    h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= k.cols * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+    h ^= (k.ld * 31 + k.box) + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+// Descriptors are pure functions of (pointer, shape, box): cache them so the steady
+// state of a serving loop encodes nothing on the host.
+static int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                       uint64_t ld, uint32_t box_rows, int elt_bytes) {
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  static std::mutex mu;
+  TmapKey key{base, rows, cols, ld, box_rows * 4 + static_cast<uint32_t>(elt_bytes)};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return MB_OK;
+  }
+  int rc = make_tmap_2d(out, base, rows, cols, ld, box_rows, elt_bytes);
+  if (rc == MB_OK) {
+    if (cache.size() > 65536) cache.clear();
+    cache.emplace(key, *out);
+  }
+  return rc;
+}
+
+static uint32_t pow2_cols(int c) {
+  uint32_t p = 32;
+  while (static_cast<int>(p) < c) p <<= 1;
+  return p;
+}
+
+template <bool DUAL, int EPI>
+static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, const void* R, int M,
+                      int N, int K, int ldy, int ldr, int dual_rows, int k_per_split, int splits,
+                      int BN, int stages, int* err, cudaStream_t stream) {
+  const int stage_bytes = kATileBytes * (DUAL ? 2 : 1) + BN * kBK * 2;
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes +
+                      sizeof(GemmSmemTail) + 1024;
+  auto kern = gemm_wx_kernel<DUAL, EPI>;
+  static size_t configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+        cudaSuccess)
+      return MB_ERR_LAUNCH;
+    configured = 227 * 1024;
+  }
+  dim3 grid((M + BN - 1) / BN, (N + kBM - 1) / kBM, splits);
+  const uint32_t tmem_cols = pow2_cols(DUAL ? 2 * BN : BN);
+  kern<<<grid, kGemmThreads, smem, stream>>>(tw, tx, Y, static_cast<const __nv_bfloat16*>(R), M, N,
+                                             K, ldy, ldr, dual_rows, k_per_split, BN, stages,
+                                             tmem_cols, err);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+// Tile-shape heuristic: the token tile is the smallest multiple of 16 that covers M in
+// ceil(M/256) passes; split-K only when the grid would leave most SMs idle.
+extern "C" void mb_gemm_bf16_plan(int M, int N, int K, int dual, int num_sms, int* bn_out,
+                                  int* splits_out, int* stages_out) {
+  const int max_bn = dual ? 128 : 256;
+  const int m_tiles = (M + max_bn - 1) / max_bn;
+  int bn = ((M + m_tiles - 1) / m_tiles + 15) / 16 * 16;
+  if (bn < 16) bn = 16;
+  const int n_tiles = (N + kBM - 1) / kBM;
+  int splits = 1;
+  const int ctas = n_tiles * m_tiles;
+  if (!dual && ctas * 2 <= num_sms) {
+    splits = num_sms / ctas;
+    const int k_blocks = (K + kBK - 1) / kBK;
+    if (splits > k_blocks / 8) splits = k_blocks / 8 > 0 ? k_blocks / 8 : 1;
+    if (splits > 8) splits = 8;
+  }
+  const int stage_bytes = kATileBytes * (dual ? 2 : 1) + bn * kBK * 2;
+  const int tmem_need = dual ? 2 * bn : bn;
+  // Two CTAs per SM when both the pipeline and the accumulators fit twice.
+  int budget = (tmem_need <= 256 && stage_bytes * 4 + 12 * 1024 <= 112 * 1024) ? 100 * 1024
+                                                                               : 212 * 1024;
+  int stages = budget / stage_bytes;
+  if (stages > 8) stages = 8;
+  if (stages < 2) stages = 2;
+  *bn_out = bn;
+  *splits_out = splits;
+  *stages_out = stages;
+}
+
+// Y = X · W^T with optional fusions. flags: bit0 dual (SwiGLU over W = [gate; up]),
+// bit1 residual add, bit2 fp32 output. `bn`/`splits`/`stages` <= 0 selects the plan above.
+// Split-K needs `workspace` of splits*M*N floats.
+extern "C" int mb_gemm_bf16(const void* X, const void* W, void* Y, const void* R, int M, int N,
+                            int K, int ldx, int ldw, int ldy, int ldr, int flags, int bn,
+                            int splits, int stages, void* workspace, int* err, int num_sms,
+                            cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return MB_OK;
+  const bool dual = flags & 1, resid = flags & 2, f32 = flags & 4;
+  if (K % 8 || ldx % 8 || ldw % 8 || N % 8 || (!f32 && ldy % 8) || (resid && ldr % 8))
+    return MB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) |
+       reinterpret_cast<uintptr_t>(Y) | reinterpret_cast<uintptr_t>(R)) & 15)
+    return MB_ERR_ALIGN;
+  int pbn, psp, pst;
+  mb_gemm_bf16_plan(M, N, K, dual, num_sms > 0 ? num_sms : 148, &pbn, &psp, &pst);
+  if (bn <= 0) bn = pbn;
+  if (splits <= 0) splits = psp;
+  if (bn % 16 || bn > 256 || (dual && bn > 256)) return MB_ERR_SHAPE;
+  if (dual && f32) return MB_ERR_SHAPE;
+  if (splits > 1 && (workspace == nullptr || dual || f32)) splits = 1;
+  {
+    const int stage_bytes = kATileBytes * (dual ? 2 : 1) + bn * kBK * 2;
+    const int max_stages = (227 * 1024 - 1024 - 4 * kStageWarpBytes - 512) / stage_bytes;
+    if (stages <= 0) stages = pst;
+    if (stages > max_stages) stages = max_stages;
+    if (stages > 8) stages = 8;
+    if (stages < 1) return MB_ERR_SHAPE;
+  }
+  const int w_rows = dual ? 2 * N : N;
+  CUtensorMap tw, tx;
+  int rc = cached_tmap(&tw, W, w_rows, K, ldw, kBM, 2);
+  if (rc != MB_OK) return rc;
+  rc = cached_tmap(&tx, X, M, K, ldx, bn, 2);
+  if (rc != MB_OK) return rc;
+
+  int k_per_split = K;
+  if (splits > 1) {
+    const int k_blocks = (K + kBK - 1) / kBK;
+    k_per_split = ((k_blocks + splits - 1) / splits) * kBK;
+    splits = (K + k_per_split - 1) / k_per_split;
+  }
+  if (splits > 1) {
+    rc = launch_cfg<false, EPI_F32>(tw, tx, workspace, nullptr, M, N, K, N, 0, 0, k_per_split,
+                                    splits, bn, stages, err, stream);
+    if (rc != MB_OK) return rc;
+    if (f32) return MB_ERR_SHAPE;  // fp32 output is never split
+    const size_t total4 = (static_cast<size_t>(M) * N + 3) / 4;
+    splitk_reduce_kernel<<<static_cast<unsigned>((total4 + 255) / 256), 256, 0, stream>>>(
+        static_cast<const float*>(workspace), resid ? static_cast<const __nv_bfloat16*>(R) : nullptr,
+        static_cast<__nv_bfloat16*>(Y), M, N, splits, ldy, ldr);
+    return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+  }
+  if (dual)
+    return launch_cfg<true, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, N, K, 1, bn, stages, err,
+                                      stream);
+  if (f32)
+    return launch_cfg<false, EPI_F32>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err,
+                                      stream);
+  if (resid)
+    return launch_cfg<false, EPI_BF16_RESIDUAL>(tw, tx, Y, R, M, N, K, ldy, ldr, 0, K, 1, bn,
+                                                stages, err, stream);
+  return launch_cfg<false, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err,
+                                     stream);
+}

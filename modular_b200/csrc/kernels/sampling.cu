@@ -1,0 +1,274 @@
+// Token sampling on the device: greedy argmax, temperature / top-k / top-p / min-p
+// sampling with per-request seeds, and frequency / presence / repetition penalties.
+//
+// One CTA of 1024 threads owns one batch row. Top-k and top-p cut-offs are found by
+// bisection on the order-preserving integer image of the fp32 logits, so no sort and
+// no scratch memory is needed; pure temperature sampling takes the one-pass Gumbel-max
+// route. Behavioural counterparts in the reference: max/kernels/src/nn/topk.mojo
+// (fused token sampling :2037, Gumbel argmax :2369), nn/sampling/topk_fi.mojo,
+// nn/sampling/sampling.mojo:31 (penalties).
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "../common/api.h"
+
+namespace mb {
+
+constexpr int kSampThreads = 1024;
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+__device__ __forceinline__ float uniform01(uint64_t seed, uint64_t step, uint64_t idx) {
+  const uint64_t h = mix64(mix64(seed ^ (step * 0xD1342543DE82EF95ull)) + idx);
+  return (static_cast<float>(h >> 40) + 0.5f) * (1.0f / 16777216.0f);  // (0,1)
+}
+// Monotone map fp32 -> uint32 (larger float <=> larger key).
+__device__ __forceinline__ uint32_t fkey(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float fkey_inv(uint32_t k) {
+  const uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(u);
+}
+
+struct ArgMax {
+  float v;
+  int i;
+};
+__device__ __forceinline__ ArgMax amax2(ArgMax a, ArgMax b) {
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+__device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax b;
+    b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+    b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    a = amax2(a, b);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) sh[warp] = a;
+  __syncthreads();
+  ArgMax r = lane < (blockDim.x >> 5) ? sh[lane] : ArgMax{-FLT_MAX, 0x7fffffff};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax b;
+    b.v = __shfl_xor_sync(0xffffffffu, r.v, o);
+    b.i = __shfl_xor_sync(0xffffffffu, r.i, o);
+    r = amax2(r, b);
+  }
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ float block_sum_f(float v, float* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float r = lane < (blockDim.x >> 5) ? sh[lane] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  __syncthreads();
+  return r;
+}
+
+__global__ void __launch_bounds__(kSampThreads)
+argmax_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int vocab, int ld) {
+  __shared__ ArgMax sh[32];
+  const float* row = logits + static_cast<size_t>(blockIdx.x) * ld;
+  ArgMax a{-FLT_MAX, 0x7fffffff};
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) a = amax2(a, ArgMax{row[i], i});
+  a = block_argmax(a, sh);
+  if (threadIdx.x == 0) out[blockIdx.x] = a.i;
+}
+
+__global__ void __launch_bounds__(kSampThreads)
+sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int vocab, int ld,
+              const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
+              const float* __restrict__ top_p, const float* __restrict__ min_p,
+              const uint64_t* __restrict__ seeds, uint64_t step) {
+  __shared__ ArgMax sh_am[32];
+  __shared__ float sh_f[32];
+  __shared__ float sh_scan[kSampThreads / 32];
+  __shared__ int sh_pick;
+  const int rowi = blockIdx.x;
+  const float* row = logits + static_cast<size_t>(rowi) * ld;
+  const float T = temperature ? temperature[rowi] : 1.f;
+  const int k = top_k ? top_k[rowi] : 0;
+  const float tp = top_p ? top_p[rowi] : 1.f;
+  const float mp = min_p ? min_p[rowi] : 0.f;
+  const uint64_t seed = seeds ? seeds[rowi] : 0x1234ull + rowi;
+
+  // greedy
+  if (T <= 0.f || k == 1) {
+    ArgMax a{-FLT_MAX, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) a = amax2(a, ArgMax{row[i], i});
+    a = block_argmax(a, sh_am);
+    if (threadIdx.x == 0) out[rowi] = a.i;
+    return;
+  }
+  const float invT = 1.f / T;
+  const bool use_k = k > 0 && k < vocab, use_p = tp < 1.f, use_m = mp > 0.f;
+  if (!use_k && !use_p && !use_m) {
+    // Gumbel-max: argmax(x/T + g), g = -log(-log u)
+    ArgMax a{-FLT_MAX, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float u = uniform01(seed, step, i);
+      a = amax2(a, ArgMax{row[i] * invT - __logf(-__logf(u)), i});
+    }
+    a = block_argmax(a, sh_am);
+    if (threadIdx.x == 0) out[rowi] = a.i;
+    return;
+  }
+  // max of scaled logits
+  ArgMax a{-FLT_MAX, 0x7fffffff};
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) a = amax2(a, ArgMax{row[i] * invT, i});
+  a = block_argmax(a, sh_am);
+  const float mx = a.v;
+  uint32_t thr_key = 0;  // keep x with fkey(x*invT) >= thr_key
+  if (use_k) {
+    // largest key t with count(key >= t) >= k
+    uint32_t lo = 0, hi = fkey(mx);
+    while (lo < hi) {
+      const uint32_t mid = lo + ((hi - lo + 1) >> 1);
+      float c = 0.f;
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) c += fkey(row[i] * invT) >= mid ? 1.f : 0.f;
+      c = block_sum_f(c, sh_f);
+      if (c >= static_cast<float>(k)) lo = mid; else hi = mid - 1;
+    }
+    thr_key = lo;
+  }
+  if (use_m) {
+    const uint32_t km = fkey(mx + __logf(mp));
+    thr_key = max(thr_key, km);
+  }
+  float Z = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float x = row[i] * invT;
+    Z += fkey(x) >= thr_key ? __expf(x - mx) : 0.f;
+  }
+  Z = block_sum_f(Z, sh_f);
+  if (use_p) {
+    // largest key t (>= thr_key) with mass(key >= t) >= tp * Z
+    const float target = tp * Z;
+    uint32_t lo = thr_key, hi = fkey(mx);
+    while (lo < hi) {
+      const uint32_t mid = lo + ((hi - lo + 1) >> 1);
+      float c = 0.f;
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float x = row[i] * invT;
+        c += fkey(x) >= mid ? __expf(x - mx) : 0.f;
+      }
+      c = block_sum_f(c, sh_f);
+      if (c >= target) lo = mid; else hi = mid - 1;
+    }
+    thr_key = lo;
+    Z = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float x = row[i] * invT;
+      Z += fkey(x) >= thr_key ? __expf(x - mx) : 0.f;
+    }
+    Z = block_sum_f(Z, sh_f);
+  }
+  // inverse-CDF draw over the kept set, in index order
+  const float target = uniform01(seed, step, 0xffffffffull) * Z;
+  if (threadIdx.x == 0) sh_pick = -1;
+  __syncthreads();
+  float base = 0.f;
+  int last_kept = -1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c0 = 0; c0 < vocab; c0 += kSampThreads) {
+    const int i = c0 + threadIdx.x;
+    float w = 0.f;
+    if (i < vocab) {
+      const float x = row[i] * invT;
+      if (fkey(x) >= thr_key) w = __expf(x - mx);
+    }
+    float incl = w;  // warp inclusive scan
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) sh_scan[warp] = incl;
+    __syncthreads();
+    float woff = 0.f, total = 0.f;
+    for (int q = 0; q < kSampThreads / 32; ++q) {
+      const float t = sh_scan[q];
+      if (q < warp) woff += t;
+      total += t;
+    }
+    const float cum = base + woff + incl;
+    if (w > 0.f && cum >= target && cum - w < target) atomicMax(&sh_pick, i);
+    if (w > 0.f) last_kept = i;
+    base += total;
+    __syncthreads();
+    if (sh_pick >= 0) break;
+  }
+  if (sh_pick < 0) {
+    // rounding left the target just above the total mass: take the last kept index
+    ArgMax b{static_cast<float>(last_kept), last_kept < 0 ? 0x7fffffff : -last_kept};
+    b = block_argmax(b, sh_am);
+    if (threadIdx.x == 0) out[rowi] = b.v >= 0.f ? static_cast<int64_t>(b.v) : a.i;
+  } else if (threadIdx.x == 0) {
+    out[rowi] = sh_pick;
+  }
+}
+
+// One thread per (row, distinct history token). counts > 0 are output-token counts for
+// frequency/presence; repetition applies to every listed token.
+__global__ void penalties_kernel(float* __restrict__ logits, int rows, int vocab, int ld,
+                                 const int32_t* __restrict__ tok, const int32_t* __restrict__ cnt,
+                                 const int32_t* __restrict__ offsets, const float* __restrict__ freq,
+                                 const float* __restrict__ pres, const float* __restrict__ rep) {
+  const int row = blockIdx.y;
+  const int beg = offsets[row], end = offsets[row + 1];
+  for (int j = beg + blockIdx.x * blockDim.x + threadIdx.x; j < end; j += gridDim.x * blockDim.x) {
+    const int t = tok[j];
+    if (t < 0 || t >= vocab) continue;
+    float x = logits[static_cast<size_t>(row) * ld + t];
+    const float r = rep ? rep[row] : 1.f;
+    if (r != 1.f) x = x > 0.f ? x / r : x * r;
+    const int c = cnt[j];
+    if (c > 0) x -= (freq ? freq[row] : 0.f) * c + (pres ? pres[row] : 0.f);
+    logits[static_cast<size_t>(row) * ld + t] = x;
+  }
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+extern "C" int mb_argmax(const float* logits, int64_t* out, int rows, int vocab, int ld,
+                         cudaStream_t stream) {
+  if (rows <= 0) return MB_OK;
+  argmax_kernel<<<rows, kSampThreads, 0, stream>>>(logits, out, vocab, ld);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+extern "C" int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, int vocab, int ld,
+                                   const float* temperature, const int32_t* top_k,
+                                   const float* top_p, const float* min_p, const uint64_t* seeds,
+                                   uint64_t step, cudaStream_t stream) {
+  if (rows <= 0) return MB_OK;
+  sample_kernel<<<rows, kSampThreads, 0, stream>>>(logits, out, vocab, ld, temperature, top_k,
+                                                   top_p, min_p, seeds, step);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+extern "C" int mb_apply_penalties(float* logits, int rows, int vocab, int ld, const int32_t* tok,
+                                  const int32_t* cnt, const int32_t* offsets, const float* freq,
+                                  const float* pres, const float* rep, cudaStream_t stream) {
+  if (rows <= 0) return MB_OK;
+  penalties_kernel<<<dim3(8, rows), 256, 0, stream>>>(logits, rows, vocab, ld, tok, cnt, offsets,
+                                                      freq, pres, rep);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}

@@ -1,0 +1,190 @@
+"""Op layer: one Python function per kernel.
+
+CUDA tensors go to the hand-written sm_100a kernels in ``modular_b200/_C.so``; CPU tensors
+go to the PyTorch reference in :mod:`modular_b200.ops.reference`. A CUDA tensor with no
+loadable native library raises - there is no eager-PyTorch fallback on a GPU.
+
+The set mirrors the custom-op wrappers the reference's layers call
+(max/python/max/nn/kernels.py: fused_qkv_ragged_matmul, rope_split_store_ragged,
+flash_attention_ragged, rms_norm, topk_fused_sampling, apply_penalties_to_logits, ...).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .._native import lib as _lib
+from . import reference as ref
+
+__all__ = [
+    "linear", "linear_swiglu", "rms_norm", "add_rms_norm", "silu_mul", "embedding",
+    "rope_kv_store", "paged_attention", "build_attention_plan", "argmax", "sample",
+    "apply_penalties", "gemm_workspace", "check_device_error",
+]
+
+_WORKSPACES: dict[int, torch.Tensor] = {}
+_WORKSPACE_BYTES = 64 << 20
+
+
+def gemm_workspace(device) -> torch.Tensor:
+    """Per-device fp32 scratch for split-K partial sums (allocated once, 64 MiB)."""
+    idx = torch.device(device).index or 0
+    ws = _WORKSPACES.get(idx)
+    if ws is None:
+        ws = torch.empty(_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
+        _WORKSPACES[idx] = ws
+    return ws
+
+
+def check_device_error() -> None:
+    """Raises if a kernel reported a timed-out wait (reads and clears the error word)."""
+    code = _lib().read_error_flag(True)
+    if code:
+        raise RuntimeError(f"modular_b200 kernel reported a bounded-wait timeout (code {code})")
+
+
+def linear(x, w, residual=None, out=None, out_dtype=None, bn=0, splits=0, stages=0):
+    """``x @ w.T`` (+ residual). x: [M, K] bf16, w: [N, K] bf16."""
+    if not x.is_cuda:
+        y = ref.linear(x, w, residual, out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty(x.shape[0], w.shape[0], dtype=out_dtype or x.dtype, device=x.device)
+    _lib().gemm_bf16(x, w, out, residual, False, gemm_workspace(x.device), bn, splits, stages)
+    return out
+
+
+def linear_swiglu(x, w_gate_up, out=None, bn=0, stages=0):
+    """``silu(x @ w_gate.T) * (x @ w_up.T)`` with ``w_gate_up = [w_gate; w_up]`` stacked on rows."""
+    if not x.is_cuda:
+        y = ref.linear_swiglu(x, w_gate_up)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
+    _lib().gemm_bf16(x, w_gate_up, out, None, True, None, bn, 1, stages)
+    return out
+
+
+def rms_norm(x, w, eps, weight_offset=0.0, multiply_before_cast=False, out=None):
+    if not x.is_cuda or x.dtype != torch.bfloat16:
+        y = ref.rms_norm(x, w, eps, weight_offset, multiply_before_cast)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty_like(x)
+    _lib().rmsnorm(x, w, out, eps, weight_offset, multiply_before_cast)
+    return out
+
+
+def add_rms_norm(x, residual, w, eps, weight_offset=0.0, multiply_before_cast=False, out=None):
+    """residual <- x + residual (in place); returns (rms_norm(residual), residual)."""
+    if not x.is_cuda or x.dtype != torch.bfloat16:
+        y, h = ref.add_rms_norm(x, residual, w, eps, weight_offset, multiply_before_cast)
+        residual.copy_(h)
+        return y, residual
+    if out is None:
+        out = torch.empty_like(x)
+    _lib().add_rmsnorm(x, residual, w, out, eps, weight_offset, multiply_before_cast)
+    return out, residual
+
+
+def silu_mul(gate_up, out=None):
+    if not gate_up.is_cuda or gate_up.dtype != torch.bfloat16:
+        return ref.silu_mul(gate_up)
+    if out is None:
+        out = torch.empty(gate_up.shape[0], gate_up.shape[1] // 2, dtype=gate_up.dtype,
+                          device=gate_up.device)
+    _lib().silu_mul(gate_up, out)
+    return out
+
+
+def embedding(ids, table, vocab_start=0, out=None):
+    if not table.is_cuda or table.dtype != torch.bfloat16:
+        return ref.embedding(ids, table, vocab_start)
+    if out is None:
+        out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    _lib().embedding(ids, table, out, vocab_start)
+    return out
+
+
+def rope_kv_store(qkv, positions, slots, cos_sin, k_cache, v_cache, n_q, n_kv, head_dim,
+                  interleaved=False):
+    if not qkv.is_cuda or qkv.dtype != torch.bfloat16:
+        return ref.rope_kv_store(qkv, positions, slots, cos_sin, k_cache, v_cache, n_q, n_kv,
+                                 head_dim, interleaved)
+    _lib().rope_kv_store(qkv, positions, slots, cos_sin, k_cache, v_cache, n_q, n_kv, head_dim,
+                         interleaved)
+
+
+def build_attention_plan(q_lens, n_q: int, n_kv: int):
+    """Host-side split of a ragged batch into decode CTAs and prefill tiles.
+
+    Returns (tile_seq, tile_q0, decode_seq) as int32 numpy arrays. A sequence whose new
+    tokens times the GQA group size fit one 16-row MMA tile takes the decode kernel.
+    """
+    G = n_q // n_kv
+    tok_per_tile = max(1, 64 // G)
+    tile_seq, tile_q0, decode_seq = [], [], []
+    for s, ql in enumerate(q_lens):
+        ql = int(ql)
+        if ql <= 0:
+            continue
+        if ql * G <= 16:
+            decode_seq.append(s)
+        else:
+            for t0 in range(0, ql, tok_per_tile):
+                tile_seq.append(s)
+                tile_q0.append(t0)
+    return (np.asarray(tile_seq, dtype=np.int32), np.asarray(tile_q0, dtype=np.int32),
+            np.asarray(decode_seq, dtype=np.int32))
+
+
+def paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, n_q, n_kv,
+                    head_dim, scale, plan=None, out=None):
+    """Ragged causal attention. q: [T, ld] with the n_q*head_dim query columns first."""
+    if not q.is_cuda or q.dtype != torch.bfloat16:
+        return ref.paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, kv_len,
+                                   n_q, n_kv, head_dim, scale)
+    if plan is None:
+        ts, t0, ds = build_attention_plan(q_len.cpu().numpy(), n_q, n_kv)
+        plan = tuple(torch.from_numpy(a).to(q.device) if a.size else None for a in (ts, t0, ds))
+    if out is None:
+        out = torch.empty(q.shape[0], n_q * head_dim, dtype=q.dtype, device=q.device)
+    _lib().paged_attention(q, out, k_cache, v_cache, block_table, q_start, q_len, kv_len,
+                           plan[0], plan[1], plan[2], n_q, n_kv, head_dim, scale)
+    return out
+
+
+def argmax(logits, out=None):
+    if not logits.is_cuda:
+        return ref.argmax(logits)
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.long, device=logits.device)
+    _lib().argmax(logits.float() if logits.dtype != torch.float32 else logits, out)
+    return out
+
+
+def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, seeds=None, step=0,
+           out=None, generator=None):
+    if not logits.is_cuda:
+        return ref.sample(logits, temperature, top_k, top_p, min_p, generator)
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.long, device=logits.device)
+    _lib().sample(logits, out, temperature, top_k, top_p, min_p, seeds, int(step))
+    return out
+
+
+def apply_penalties(logits, tok, cnt, offsets, freq=None, pres=None, rep=None):
+    if not logits.is_cuda:
+        return ref.apply_penalties(logits, tok, cnt, offsets, freq, pres, rep)
+    _lib().apply_penalties(logits, tok, cnt, offsets, freq, pres, rep)
+    return logits

@@ -1,0 +1,177 @@
+"""Plain PyTorch implementations of every op in :mod:`modular_b200.ops`.
+
+They define the semantics the CUDA kernels are tested against (fp32 math, the same
+rounding points) and are the execution path on CPU-only machines.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def linear(x, w, residual=None, out_dtype=None):
+    y = (x.float() @ w.float().t()).to(out_dtype or x.dtype)
+    if residual is not None:
+        y = (y.float() + residual.float()).to(y.dtype)
+    return y
+
+
+def linear_swiglu(x, w_gate_up):
+    inter = w_gate_up.shape[0] // 2
+    g = x.float() @ w_gate_up[:inter].float().t()
+    u = x.float() @ w_gate_up[inter:].float().t()
+    return (F.silu(g) * u).to(x.dtype)
+
+
+def rms_norm(x, w, eps, weight_offset=0.0, multiply_before_cast=False):
+    xf = x.float()
+    n = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    wf = w.float() + weight_offset
+    if multiply_before_cast:
+        return (n * wf).to(x.dtype)
+    return (n.to(x.dtype).float() * wf).to(x.dtype)
+
+
+def add_rms_norm(x, residual, w, eps, weight_offset=0.0, multiply_before_cast=False):
+    h = (x.float() + residual.float()).to(x.dtype)
+    return rms_norm(h, w, eps, weight_offset, multiply_before_cast), h
+
+
+def silu_mul(gate_up):
+    inter = gate_up.shape[-1] // 2
+    g, u = gate_up[..., :inter].float(), gate_up[..., inter:].float()
+    return (F.silu(g) * u).to(gate_up.dtype)
+
+
+def embedding(ids, table, vocab_start=0):
+    local = ids - vocab_start
+    ok = (local >= 0) & (local < table.shape[0])
+    out = table[local.clamp(0, table.shape[0] - 1)]
+    return out * ok.unsqueeze(-1).to(out.dtype)
+
+
+def apply_rope(x, cos, sin, interleaved=False):
+    """x: [T, H, D]; cos/sin: [T, D/2]."""
+    xf = x.float()
+    c, s = cos.unsqueeze(1).float(), sin.unsqueeze(1).float()
+    if interleaved:
+        a, b = xf[..., 0::2], xf[..., 1::2]
+        out = torch.stack((a * c - b * s, b * c + a * s), dim=-1).flatten(-2)
+    else:
+        half = x.shape[-1] // 2
+        a, b = xf[..., :half], xf[..., half:]
+        out = torch.cat((a * c - b * s, b * c + a * s), dim=-1)
+    return out.to(x.dtype)
+
+
+def rope_kv_store(qkv, positions, slots, cos_sin, k_cache, v_cache, n_q, n_kv, head_dim,
+                  interleaved=False):
+    """In place: rotates Q (and K) inside ``qkv`` and scatters K/V into the paged cache.
+
+    k_cache / v_cache: [pages, n_kv, page_size, head_dim] views of one layer.
+    """
+    T = qkv.shape[0]
+    half = head_dim // 2
+    cs = cos_sin[positions.long()]
+    cos, sin = cs[:, :half], cs[:, half:]
+    q = qkv[:, : n_q * head_dim].view(T, n_q, head_dim)
+    k = qkv[:, n_q * head_dim : (n_q + n_kv) * head_dim].view(T, n_kv, head_dim)
+    v = qkv[:, (n_q + n_kv) * head_dim :].view(T, n_kv, head_dim)
+    q.copy_(apply_rope(q, cos, sin, interleaved))
+    k_rot = apply_rope(k, cos, sin, interleaved)
+    page_size = k_cache.shape[2]
+    ok = slots >= 0
+    pg = torch.div(slots.clamp(min=0), page_size, rounding_mode="floor")
+    off = slots.clamp(min=0) % page_size
+    k_cache[pg[ok], :, off[ok]] = k_rot[ok].to(k_cache.dtype)
+    v_cache[pg[ok], :, off[ok]] = v[ok].to(v_cache.dtype)
+
+
+def paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, n_q, n_kv,
+                    head_dim, scale):
+    """Ragged causal attention over a paged cache. q: [T, >= n_q*head_dim] (row stride free)."""
+    T = q.shape[0]
+    out = torch.zeros(T, n_q * head_dim, dtype=q.dtype, device=q.device)
+    G = n_q // n_kv
+    page_size = k_cache.shape[2]
+    for b in range(block_table.shape[0]):
+        qs, ql, kl = int(q_start[b]), int(q_len[b]), int(kv_len[b])
+        if ql == 0:
+            continue
+        n_pages = (kl + page_size - 1) // page_size
+        pages = block_table[b, :n_pages].long()
+        k = k_cache[pages].permute(1, 0, 2, 3).reshape(n_kv, -1, head_dim)[:, :kl].float()
+        v = v_cache[pages].permute(1, 0, 2, 3).reshape(n_kv, -1, head_dim)[:, :kl].float()
+        qq = q[qs : qs + ql, : n_q * head_dim].view(ql, n_q, head_dim).float()
+        k = k.repeat_interleave(G, dim=0)
+        v = v.repeat_interleave(G, dim=0)
+        s = torch.einsum("qhd,hkd->hqk", qq, k) * scale
+        qi = torch.arange(ql, device=q.device).unsqueeze(1) + (kl - ql)
+        ki = torch.arange(kl, device=q.device).unsqueeze(0)
+        s = s.masked_fill(ki > qi, float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        o = torch.einsum("hqk,hkd->qhd", p, v)
+        out[qs : qs + ql] = o.reshape(ql, -1).to(q.dtype)
+    return out
+
+
+def argmax(logits):
+    return logits.argmax(dim=-1)
+
+
+def apply_penalties(logits, tok, cnt, offsets, freq=None, pres=None, rep=None):
+    for r in range(logits.shape[0]):
+        b, e = int(offsets[r]), int(offsets[r + 1])
+        if e <= b:
+            continue
+        t = tok[b:e].long()
+        c = cnt[b:e].float()
+        x = logits[r, t]
+        if rep is not None and float(rep[r]) != 1.0:
+            x = torch.where(x > 0, x / rep[r], x * rep[r])
+        f = freq[r] if freq is not None else 0.0
+        p = pres[r] if pres is not None else 0.0
+        x = x - (c > 0).float() * (f * c + p)
+        logits[r, t] = x
+    return logits
+
+
+def filtered_probs(logits, temperature, top_k, top_p, min_p):
+    """Probability vector the device sampler draws from (used by distribution tests)."""
+    x = logits.float() / temperature
+    mx = x.max()
+    keep = torch.ones_like(x, dtype=torch.bool)
+    if top_k and 0 < top_k < x.numel():
+        kth = torch.topk(x, top_k).values[-1]
+        keep &= x >= kth
+    if min_p and min_p > 0:
+        keep &= x >= mx + math.log(min_p)
+    w = torch.where(keep, torch.exp(x - mx), torch.zeros_like(x))
+    if top_p is not None and top_p < 1.0:
+        order = torch.argsort(x, descending=True)
+        ws = w[order]
+        csum = torch.cumsum(ws, 0)
+        target = top_p * ws.sum()
+        # smallest prefix whose mass reaches the target (ties at the cut stay in)
+        n_keep = int((csum < target).sum().item()) + 1
+        thr = x[order[min(n_keep, x.numel()) - 1]]
+        keep &= x >= thr
+        w = torch.where(keep, w, torch.zeros_like(w))
+    return w / w.sum()
+
+
+def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, generator=None):
+    out = torch.empty(logits.shape[0], dtype=torch.long, device=logits.device)
+    for r in range(logits.shape[0]):
+        T = float(temperature[r]) if temperature is not None else 1.0
+        k = int(top_k[r]) if top_k is not None else 0
+        if T <= 0 or k == 1:
+            out[r] = logits[r].argmax()
+            continue
+        p = filtered_probs(logits[r], T, k, float(top_p[r]) if top_p is not None else 1.0,
+                           float(min_p[r]) if min_p is not None else 0.0)
+        out[r] = torch.multinomial(p, 1, generator=generator)[0]
+    return out

@@ -1,0 +1,196 @@
+"""Numerics of every CUDA kernel against the fp32 PyTorch reference of the same op."""
+
+import math
+
+import pytest
+import torch
+
+from modular_b200 import ops
+from modular_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-6)).item()
+
+
+@pytest.fixture(autouse=True)
+def _no_device_error():
+    yield
+    torch.cuda.synchronize()
+    ops.check_device_error()
+
+
+@pytest.mark.parametrize(
+    "M,N,K",
+    [(1, 128, 64), (16, 256, 128), (64, 4096, 4096), (100, 384, 520), (320, 6144, 4096),
+     (257, 1000, 1024), (1024, 4096, 14336), (2048, 2048, 512)],
+)
+def test_gemm_bf16(M, N, K):
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    y = ops.linear(x, w)
+    yr = ref.linear(x, w)
+    assert _rel_err(y, yr) < 1e-2
+    assert (y.float() - yr.float()).abs().max() <= 0.02 * yr.float().abs().max() + 1e-2
+
+
+@pytest.mark.parametrize("bn,stages,splits", [(16, 2, 1), (32, 4, 1), (64, 8, 1), (128, 4, 2), (256, 3, 4), (160, 4, 1)])
+def test_gemm_tile_configs(bn, stages, splits):
+    torch.manual_seed(1)
+    M, N, K = 300, 512, 2048
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    y = ops.linear(x, w, bn=bn, stages=stages, splits=splits)
+    assert _rel_err(y, ref.linear(x, w)) < 1e-2
+
+
+def test_gemm_residual_and_fp32_out():
+    torch.manual_seed(2)
+    M, N, K = 200, 4096, 1024
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    r = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    y = ops.linear(x, w, residual=r)
+    assert _rel_err(y, ref.linear(x, w, r)) < 1e-2
+    # in-place residual (output aliases the residual)
+    h = r.clone()
+    ops.linear(x, w, residual=h, out=h)
+    assert _rel_err(h, ref.linear(x, w, r)) < 1e-2
+    # split-K with residual
+    y2 = ops.linear(x, w, residual=r, splits=4, bn=64)
+    assert _rel_err(y2, ref.linear(x, w, r)) < 1e-2
+    yf = ops.linear(x, w, out_dtype=torch.float32)
+    assert yf.dtype == torch.float32
+    assert _rel_err(yf, x.float() @ w.float().t()) < 2e-3
+
+
+@pytest.mark.parametrize("M", [1, 48, 130, 512])
+def test_gemm_swiglu(M):
+    torch.manual_seed(3)
+    K, I = 1024, 1408
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(2 * I, K, device=DEV) * 0.05).to(torch.bfloat16)
+    y = ops.linear_swiglu(x, w)
+    assert _rel_err(y, ref.linear_swiglu(x, w)) < 1.5e-2
+
+
+@pytest.mark.parametrize("mbc", [False, True])
+def test_rmsnorm(mbc):
+    torch.manual_seed(4)
+    x = torch.randn(77, 4096, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(4096, device=DEV, dtype=torch.bfloat16)
+    y = ops.rms_norm(x, w, 1e-5, 0.0, mbc)
+    assert _rel_err(y, ref.rms_norm(x, w, 1e-5, 0.0, mbc)) < 4e-3
+    r = torch.randn_like(x)
+    r2 = r.clone()
+    y2, h = ops.add_rms_norm(x, r2, w, 1e-5, 0.0, mbc)
+    yr, hr = ref.add_rms_norm(x, r, w, 1e-5, 0.0, mbc)
+    assert torch.equal(h, hr)
+    assert _rel_err(y2, yr) < 4e-3
+
+
+def test_silu_mul_and_embedding():
+    torch.manual_seed(5)
+    gu = torch.randn(33, 2 * 1408, device=DEV, dtype=torch.bfloat16)
+    assert _rel_err(ops.silu_mul(gu), ref.silu_mul(gu)) < 4e-3
+    table = torch.randn(1000, 256, device=DEV, dtype=torch.bfloat16)
+    ids = torch.randint(0, 1200, (50,), device=DEV)
+    assert torch.equal(ops.embedding(ids, table, 100), ref.embedding(ids, table, 100))
+
+
+def _make_cache(pages, n_layers, n_kv, page_size, hd):
+    return torch.zeros(pages, 2, n_layers, n_kv, page_size, hd, device=DEV, dtype=torch.bfloat16)
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_rope_kv_store(interleaved, hd):
+    torch.manual_seed(6)
+    n_q, n_kv, T, ps = 8, 2, 37, 16
+    kv = _make_cache(12, 2, n_kv, ps, hd)
+    kv_ref = kv.clone()
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, device=DEV, dtype=torch.bfloat16)
+    qkv_ref = qkv.clone()
+    pos = torch.randint(0, 500, (T,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(12 * ps, device=DEV)[:T].long()
+    slots[3] = -1
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device=DEV).float() / hd))
+    ang = torch.arange(512, device=DEV).float()[:, None] * inv[None]
+    cos_sin = torch.cat([ang.cos(), ang.sin()], dim=1).contiguous()
+    ops.rope_kv_store(qkv, pos, slots, cos_sin, kv[:, 0, 1], kv[:, 1, 1], n_q, n_kv, hd, interleaved)
+    ref.rope_kv_store(qkv_ref, pos, slots, cos_sin, kv_ref[:, 0, 1], kv_ref[:, 1, 1], n_q, n_kv, hd, interleaved)
+    assert _rel_err(qkv[:, : n_q * hd], qkv_ref[:, : n_q * hd]) < 4e-3
+    assert _rel_err(kv, kv_ref) < 4e-3
+    assert torch.equal(kv[:, :, 0], kv_ref[:, :, 0])
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,ps", [(32, 8, 128, 128), (4, 2, 64, 16), (8, 8, 128, 64), (16, 1, 64, 32)])
+def test_paged_attention_mixed_batch(n_q, n_kv, hd, ps):
+    torch.manual_seed(7)
+    q_lens = [1, 70, 1, 200, 33, 1]
+    kv_lens = [513, 70, 64, 456, 161, 1]
+    B = len(q_lens)
+    max_pages = max((k + ps - 1) // ps for k in kv_lens)
+    n_pages = B * max_pages + 3
+    kv = (torch.randn(n_pages, 2, 1, n_kv, ps, hd, device=DEV) * 0.5).to(torch.bfloat16)
+    perm = torch.randperm(n_pages, device=DEV)[: B * max_pages].int().view(B, max_pages)
+    T = sum(q_lens)
+    ld = (n_q + 2 * n_kv) * hd
+    q = torch.randn(T, ld, device=DEV, dtype=torch.bfloat16)
+    qs = torch.tensor([sum(q_lens[:i]) for i in range(B)], device=DEV, dtype=torch.int32)
+    ql = torch.tensor(q_lens, device=DEV, dtype=torch.int32)
+    kl = torch.tensor(kv_lens, device=DEV, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(hd)
+    o = ops.paged_attention(q, kv[:, 0, 0], kv[:, 1, 0], perm, qs, ql, kl, n_q, n_kv, hd, scale)
+    o_ref = ref.paged_attention(q, kv[:, 0, 0], kv[:, 1, 0], perm, qs, ql, kl, n_q, n_kv, hd, scale)
+    assert torch.isfinite(o.float()).all()
+    assert _rel_err(o, o_ref) < 1e-2
+    assert (o.float() - o_ref.float()).abs().max() < 3e-2
+
+
+def test_argmax_and_sampling():
+    torch.manual_seed(8)
+    logits = torch.randn(9, 128256, device=DEV)
+    assert torch.equal(ops.argmax(logits), logits.argmax(-1))
+    # greedy through the sampler
+    t0 = torch.zeros(9, device=DEV)
+    assert torch.equal(ops.sample(logits, temperature=t0), logits.argmax(-1))
+    # distribution check on a small vocab
+    V = 50
+    lg = torch.randn(1, V, device=DEV) * 2
+    rows = lg.repeat(4096, 1).contiguous()
+    seeds = torch.arange(4096, device=DEV, dtype=torch.int64) * 7919 + 11
+    for kw in (dict(), dict(top_k=5), dict(top_p=0.7), dict(top_k=20, top_p=0.9, min_p=0.02)):
+        temperature = torch.full((4096,), 0.8, device=DEV)
+        args = dict(temperature=temperature, seeds=seeds, step=3)
+        if "top_k" in kw:
+            args["top_k"] = torch.full((4096,), kw["top_k"], device=DEV, dtype=torch.int32)
+        if "top_p" in kw:
+            args["top_p"] = torch.full((4096,), kw["top_p"], device=DEV)
+        if "min_p" in kw:
+            args["min_p"] = torch.full((4096,), kw["min_p"], device=DEV)
+        s = ops.sample(rows, **args)
+        emp = torch.bincount(s, minlength=V).float() / 4096
+        p = ref.filtered_probs(lg[0], 0.8, kw.get("top_k", 0), kw.get("top_p", 1.0), kw.get("min_p", 0.0))
+        assert (emp[p == 0] == 0).all(), kw
+        assert (emp - p).abs().max() < 0.04, kw
+
+
+def test_penalties():
+    torch.manual_seed(9)
+    logits = torch.randn(3, 1000, device=DEV)
+    lr = logits.clone()
+    tok = torch.tensor([1, 5, 9, 2, 7], device=DEV, dtype=torch.int32)
+    cnt = torch.tensor([2, 0, 1, 3, 0], device=DEV, dtype=torch.int32)
+    off = torch.tensor([0, 3, 3, 5], device=DEV, dtype=torch.int32)
+    f = torch.tensor([0.5, 0.1, 0.2], device=DEV)
+    p = torch.tensor([0.3, 0.0, 0.1], device=DEV)
+    r = torch.tensor([1.2, 1.0, 1.5], device=DEV)
+    ops.apply_penalties(logits, tok, cnt, off, f, p, r)
+    ref.apply_penalties(lr, tok, cnt, off, f, p, r)
+    assert torch.allclose(logits, lr, atol=1e-5)
