@@ -1,0 +1,222 @@
+#!/usr/bin/env python
+"""Headline serving benchmark: output tokens/s at fixed concurrency, with p50 TTFT / TPOT.
+
+Workload (the reference's serving benchmark shape): Llama-3.1-8B architecture, bf16,
+random-init weights, synthetic uniform-random prompts of 1024 tokens, 256 forced output
+tokens (EOS ignored, greedy), closed-loop concurrency 64, 128-token KV pages.
+
+A *step* is one concurrency-width of requests (64) served to completion, so the default
+``--steps 16`` is the full 1024-request run. ``--warmup W`` first serves W x 64 requests
+untimed (this also captures the CUDA graphs). The timed region is bracketed by a barrier
+and ``torch.cuda.synchronize()`` on both sides.
+
+Two numbers come out:
+* ``value``  - output tokens / GPU-busy time, from CUDA events recorded around every
+  scheduler step's device work (max over ranks);
+* ``e2e``    - output tokens / wall time of the same run through ``LLM.generate`` (the public
+  API): every step copies its packed inputs from pinned host memory (H2D) and reads the
+  sampled tokens back (D2H); byte counts are taken from those copies.
+
+Launch for N > 1: ``python -m torch.distributed.run --nnodes=1 --nproc-per-node N
+--master-addr 127.0.0.1 --master-port P bench.py --gpus N ...`` (tensor parallel over NCCL
+bootstrap; one rank per GPU).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+
+def _reference_arm(args) -> int:
+    """The reference (modular/modular) needs Bazel, a Mojo toolchain and a prebuilt engine
+    wheel fetched from the network; none can be installed offline, so there is nothing to run."""
+    marker = os.path.join(REPO, "baseline", "reference_install.json")
+    why = "reference needs bazel + mojo toolchain + closed engine wheel (network); pip install from source fails offline"
+    try:
+        with open(marker) as f:
+            why = json.load(f).get("unavailable", why)
+    except Exception:  # noqa: BLE001
+        pass
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--input-len", type=int, default=1024)
+    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--concurrency", type=int, default=64)
+    ap.add_argument("--max-batch-input-tokens", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return _reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.models.llama3 import Llama3Config
+    from modular_b200.pipelines.context import SamplingParams
+
+    cfg = Llama3Config.llama31_8b()
+    if args.layers:
+        cfg.num_hidden_layers = args.layers
+    conc = args.concurrency
+    max_len = args.input_len + args.output_len + 8
+    llm = LLM(cfg, device=f"cuda:{local_rank}", dtype=torch.bfloat16, max_length=max_len,
+              max_batch_size=conc, max_batch_input_tokens=args.max_batch_input_tokens, page_size=128,
+              enable_prefix_caching=True, enable_chunked_prefill=True, enable_in_flight_batching=True,
+              enable_overlap_scheduler=True, device_graph_capture=True, graph_batch_sizes=[conc],
+              tp_size=world, tp_rank=rank, seed=0)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=args.output_len, ignore_eos=True)
+    rng = np.random.default_rng(1234)
+
+    def prompts(n):
+        return [rng.integers(0, cfg.vocab_size, size=args.input_len, dtype=np.int64) for _ in range(n)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # warm-up: W steps of `conc` requests (graph capture happened in the constructor)
+    llm.generate(prompts(args.warmup * conc), sp, max_concurrency=conc)
+    barrier()
+    st = llm.pipeline.stats
+    st0 = (st.steps, st.h2d_bytes, st.d2h_bytes, st.tokens_out, llm.pipeline.gpu_launches())
+    llm.pipeline.reset_gpu_time()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    timed_prompts = prompts(args.steps * conc)
+    barrier()
+    t0 = time.perf_counter()
+    recs = llm.generate(timed_prompts, sp, max_concurrency=conc)
+    barrier()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    gpu_busy = llm.pipeline.gpu_time_s()
+    out_tokens = sum(len(r.tokens) for r in recs)
+    assert out_tokens == args.steps * conc * args.output_len, (out_tokens,)
+    times = torch.tensor([gpu_busy, wall], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    gpu_busy, wall = times.tolist()
+    if rank == 0:
+        ttft = sorted(r.ttft for r in recs)
+        tpot = sorted(r.tpot for r in recs)
+        p = lambda a, q: a[min(len(a) - 1, int(q * len(a)))]
+        n_sched = st.steps - st0[0]
+        value = out_tokens / gpu_busy
+        e2e = out_tokens / wall
+        line = {
+            "metric": "output_tokens_per_s_at_concurrency_64", "value": value, "unit": "tok/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": gpu_busy / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic uniform-random token ids; random-init N(0,0.02) weights",
+            "impl": "ours",
+            "config": {"model": "Llama-3.1-8B architecture (32L, h4096, 32q/8kv, ffn 14336, vocab 128256)"
+                       + (f" DEBUG {args.layers} layers" if args.layers else ""),
+                       "global_batch": conc, "seq_len": args.input_len + args.output_len,
+                       "input_len": args.input_len, "output_len": args.output_len,
+                       "num_requests": args.steps * conc, "concurrency": conc,
+                       "parallelism": f"tp{world}", "kv_page_tokens": 128,
+                       "max_batch_input_tokens": args.max_batch_input_tokens,
+                       "step_definition": f"{conc} requests served to completion (closed loop)",
+                       "l2_policy": "inputs larger than L2 (16 GB of weights streamed every scheduler iteration)"},
+            "p50_ttft_ms": p(ttft, 0.5) * 1e3, "p99_ttft_ms": p(ttft, 0.99) * 1e3,
+            "p50_tpot_ms": p(tpot, 0.5) * 1e3, "p99_tpot_ms": p(tpot, 0.99) * 1e3,
+            "total_tokens_per_s": (out_tokens + args.steps * conc * args.input_len) / wall,
+            "scheduler_iterations": n_sched, "graph_replays": st.graph_replays,
+            "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "tok/s", "wall_s": wall,
+                    "h2d_bytes_per_step": (st.h2d_bytes - st0[1]) / args.steps,
+                    "d2h_bytes_per_step": (st.d2h_bytes - st0[2]) / args.steps},
+            "gpu_launches": llm.pipeline.gpu_launches() - st0[4],
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

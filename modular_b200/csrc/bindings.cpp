@@ -268,7 +268,8 @@ class PyDecoderExecutor {
   }
   void set_buffers(const Tensor& h, const Tensor& xn, const Tensor& qkv, const Tensor& attn,
                    const Tensor& act, const c10::optional<Tensor>& gu, const Tensor& last_h,
-                   const Tensor& last_xn, const Tensor& logits, const Tensor& workspace) {
+                   const Tensor& last_xn, const Tensor& logits, const Tensor& sampled,
+                   const Tensor& workspace) {
     auto& b = ex.buf;
     b.h = const_cast<void*>(hold(h)); b.xn = const_cast<void*>(hold(xn));
     b.qkv = const_cast<void*>(hold(qkv)); b.attn = const_cast<void*>(hold(attn));
@@ -276,13 +277,15 @@ class PyDecoderExecutor {
     b.gu = gu.has_value() && gu->defined() ? const_cast<void*>(hold(*gu)) : nullptr;
     b.last_h = const_cast<void*>(hold(last_h)); b.last_xn = const_cast<void*>(hold(last_xn));
     b.logits = static_cast<float*>(const_cast<void*>(hold(logits)));
+    TORCH_CHECK(sampled.scalar_type() == at::kLong, "sampled must be int64");
+    b.sampled = static_cast<int64_t*>(const_cast<void*>(hold(sampled)));
     b.workspace = const_cast<void*>(hold(workspace));
     b.workspace_bytes = workspace.nbytes();
   }
   // meta: one int32 device tensor holding every per-step array; offsets are in int32 units
   // (tokens and slots are int64 and 8-byte aligned inside it).
   void forward(const Tensor& meta, py::dict off, int T, int B, int bt_stride, int n_tiles,
-               int n_decode, int n_logits) {
+               int n_decode, int n_logits, bool has_future, bool do_sample, int64_t sample_step) {
     const int32_t* base = meta.data_ptr<int32_t>();
     auto at32 = [&](const char* k) { return base + off[k].cast<int64_t>(); };
     mb::StepInputs in;
@@ -295,6 +298,14 @@ class PyDecoderExecutor {
     in.decode_seq = at32("decode_seq"); in.logit_rows = at32("logit_rows");
     in.T = T; in.B = B; in.bt_stride = bt_stride; in.n_tiles = n_tiles; in.n_decode = n_decode;
     in.n_logits = n_logits;
+    in.future_src = has_future ? at32("future_src") : nullptr;
+    in.temperature = reinterpret_cast<const float*>(at32("temperature"));
+    in.top_k = at32("top_k");
+    in.top_p = reinterpret_cast<const float*>(at32("top_p"));
+    in.min_p = reinterpret_cast<const float*>(at32("min_p"));
+    in.seeds = reinterpret_cast<const uint64_t*>(at32("seeds"));
+    in.sample_step = static_cast<uint64_t>(sample_step);
+    in.do_sample = do_sample ? 1 : 0;
     check_rc(ex.forward(in, cur_stream()), "DecoderExecutor.forward");
   }
   long launches() const { return ex.launches; }

@@ -45,6 +45,8 @@ int mb_rope_kv_store(void* qkv, const int32_t* positions, const int64_t* slots,
                      const float* cos_sin, void* k_cache, void* v_cache, int T, int n_q, int n_kv,
                      int head_dim, int page_size, int64_t page_stride, int64_t head_stride,
                      int interleaved, cudaStream_t stream);
+int mb_realize_future_tokens(int64_t* tokens, const int32_t* src, const int64_t* prev, int n,
+                             cudaStream_t stream);
 int mb_gather_rows(const void* src, const int32_t* idx, void* dst, int n, int row_bytes, int ld_src,
                    cudaStream_t stream);
 

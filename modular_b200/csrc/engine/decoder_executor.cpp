@@ -26,6 +26,11 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
                         buf.workspace, buf.err, c.num_sms, stream);
   };
 
+  if (in.future_src != nullptr) {
+    MB_TRY(mb_realize_future_tokens(const_cast<int64_t*>(in.tokens), in.future_src, buf.sampled, T,
+                                    stream));
+    launches += 1;
+  }
   MB_TRY(mb_embedding(in.tokens, embed, buf.h, T, c.hidden, c.vocab, 0, stream));
   launches += 1;
   for (int l = 0; l < c.n_layers; ++l) {
@@ -67,6 +72,12 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
     MB_TRY(gemm(buf.last_xn, lm_head, buf.logits, nullptr, in.n_logits, c.vocab, c.hidden,
                 c.hidden, c.vocab, 4));
     launches += 2;
+    if (in.do_sample) {
+      MB_TRY(mb_sample_topk_topp(buf.logits, buf.sampled, in.n_logits, c.vocab, c.vocab,
+                                 in.temperature, in.top_k, in.top_p, in.min_p, in.seeds,
+                                 in.sample_step, stream));
+      launches += 1;
+    }
   }
   return MB_OK;
 }

@@ -46,6 +46,7 @@ struct DecoderBuffers {
   void* last_h;   // [max_seqs, hidden]
   void* last_xn;  // [max_seqs, hidden]
   float* logits;  // [max_seqs, vocab]
+  int64_t* sampled;  // [max_seqs] tokens sampled by the latest step (also next step's source)
   void* workspace;  // split-K partials
   size_t workspace_bytes;
   int* err;
@@ -72,6 +73,16 @@ struct StepInputs {
   const int32_t* tile_q0;     // [n_tiles]
   const int32_t* decode_seq;  // [n_decode]
   const int32_t* logit_rows;  // [n_logits] token rows whose logits are wanted
+  // optional: rows whose token id is still on the device (index into `prev_sampled`, or -1)
+  const int32_t* future_src;  // [T] or nullptr
+  // optional fused sampling of the logit rows (all arrays [n_logits])
+  const float* temperature;
+  const int32_t* top_k;
+  const float* top_p;
+  const float* min_p;
+  const uint64_t* seeds;
+  uint64_t sample_step;
+  int do_sample;
   int T, B, bt_stride, n_tiles, n_decode, n_logits;
 };
 

@@ -227,9 +227,24 @@ __global__ void rope_kv_store_kernel(bf16* __restrict__ qkv, const int32_t* __re
   }
 }
 
+// tokens[i] <- prev_sampled[src[i]] where src[i] >= 0: fills in ids that were sampled on the
+// device by the previous step and never visited the host.
+__global__ void realize_future_kernel(int64_t* __restrict__ tokens, const int32_t* __restrict__ src,
+                                      const int64_t* __restrict__ prev, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && src[i] >= 0) tokens[i] = prev[src[i]];
+}
+
 }  // namespace mb
 
 using namespace mb;
+
+extern "C" int mb_realize_future_tokens(int64_t* tokens, const int32_t* src, const int64_t* prev,
+                                        int n, cudaStream_t stream) {
+  if (n <= 0) return MB_OK;
+  realize_future_kernel<<<(n + 255) / 256, 256, 0, stream>>>(tokens, src, prev, n);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
 
 static inline unsigned blocks_for(size_t n, int threads) {
   return static_cast<unsigned>((n + threads - 1) / threads);

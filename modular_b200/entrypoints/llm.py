@@ -1,0 +1,171 @@
+"""Offline inference entry point.
+
+``LLM`` builds model + KV cache + pipeline + scheduler in-process and exposes
+
+* ``generate(prompts, sampling_params, max_concurrency=...)`` - run a set of requests to
+  completion with closed-loop admission (at most ``max_concurrency`` in flight) and return
+  per-request token ids and latency records;
+* ``add_request`` / ``step`` / ``has_unfinished`` - the engine loop for callers that drive
+  it themselves.
+
+Reference: the offline ``LLM`` class (max/python/max/_entrypoints/llm.py:74) and
+``GenerateMixin.generate`` (max/python/max/pipelines/lib/interfaces/generate.py:44).
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..kv_cache import KVCacheParams, PagedKVCacheManager
+from ..pipelines.context import SamplingParams, TextContext
+from ..pipelines.text_generation import TextGenerationPipeline
+from ..serve.scheduler import TokenGenerationScheduler, TokenGenerationSchedulerConfig
+
+
+@dataclass
+class RequestRecord:
+    request_id: str
+    prompt_len: int
+    tokens: list = field(default_factory=list)
+    arrival: float = 0.0
+    first_token: Optional[float] = None
+    last_token: Optional[float] = None
+    finished: bool = False
+
+    @property
+    def ttft(self) -> Optional[float]:
+        return None if self.first_token is None else self.first_token - self.arrival
+
+    @property
+    def tpot(self) -> Optional[float]:
+        n = len(self.tokens)
+        if n < 2 or self.first_token is None:
+            return None
+        return (self.last_token - self.first_token) / (n - 1)
+
+
+class LLM:
+    def __init__(self, model_config, weights=None, *, device: Optional[str] = None,
+                 dtype: Optional[torch.dtype] = None, max_length: int = 4096, max_batch_size: int = 256,
+                 max_batch_input_tokens: int = 8192, page_size: int = 128,
+                 device_memory_utilization: float = 0.9, num_kv_pages: Optional[int] = None,
+                 enable_prefix_caching: bool = True, enable_chunked_prefill: bool = True,
+                 enable_in_flight_batching: bool = False, enable_overlap_scheduler: Optional[bool] = None,
+                 device_graph_capture: bool = True, graph_batch_sizes: Optional[Sequence[int]] = None,
+                 eos_token_ids: Sequence[int] = (), seed: int = 0, tp_size: int = 1,
+                 tp_rank: int = 0):
+        from ..models.llama3 import Llama3Config, Llama3Model, Llama3Weights
+
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        on_gpu = self.device.type == "cuda"
+        if dtype is None:
+            dtype = torch.bfloat16 if on_gpu else torch.float32
+        self.cfg = model_config
+        if tp_size != 1:
+            raise NotImplementedError("tensor parallel LLM construction goes through modular_b200.parallel")
+        if weights is None:
+            weights = Llama3Weights.random_init(model_config, self.device, dtype, seed=seed)
+        self.weights = weights
+        self.max_length = max_length
+        kvp = KVCacheParams(model_config.num_hidden_layers, model_config.num_key_value_heads,
+                            model_config.head_dim, page_size, dtype, False, enable_prefix_caching)
+        if num_kv_pages is None:
+            if on_gpu:
+                free, total = torch.cuda.mem_get_info(self.device)
+                act = max_batch_input_tokens * (3 * model_config.hidden_size + 2 * model_config.q_dim
+                                                + 3 * model_config.intermediate_size) * 2
+                act += max_batch_size * model_config.vocab_size * 4 + (256 << 20)
+                budget = int(free - (1.0 - device_memory_utilization) * total - act)
+                num_kv_pages = kvp.compute_num_device_blocks(budget, max_batch_size * 4, max_length)
+            else:
+                num_kv_pages = kvp.compute_num_device_blocks(1 << 62, max_batch_size, max_length)
+        self.kv = PagedKVCacheManager(kvp, num_kv_pages, self.device, max_seq_len=max_length)
+        self.model = Llama3Model(model_config, weights, self.kv.kv, max_tokens=max_batch_input_tokens,
+                                 max_seqs=max_batch_size, max_position=max_length)
+        overlap = on_gpu if enable_overlap_scheduler is None else enable_overlap_scheduler
+        if graph_batch_sizes is None:
+            graph_batch_sizes = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch_size]
+        self.pipeline = TextGenerationPipeline(
+            self.model, self.kv, max_batch_input_tokens, max_batch_size, overlap=overlap,
+            graph_batch_sizes=graph_batch_sizes if (device_graph_capture and on_gpu) else (),
+            eos_token_ids=eos_token_ids)
+        if device_graph_capture and on_gpu:
+            self.pipeline.warmup_graph_capture()
+        self.sched_config = TokenGenerationSchedulerConfig(
+            max_batch_size=max_batch_size, target_tokens_per_batch_ce=max_batch_input_tokens,
+            max_seq_len=max_length, enable_chunked_prefill=enable_chunked_prefill,
+            enable_in_flight_batching=enable_in_flight_batching,
+            kv_lookahead_tokens=1 if overlap else 0)
+        self.scheduler = TokenGenerationScheduler(self.sched_config, self.pipeline, self.kv)
+        self.eos_token_ids = tuple(eos_token_ids)
+        self._records: dict[str, RequestRecord] = {}
+        self._n = 0
+
+    # ------------------------------------------------------------ engine loop
+    def add_request(self, prompt_ids, sampling_params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None) -> str:
+        self._n += 1
+        rid = request_id or f"llm-{self._n}"
+        ctx = TextContext.from_prompt(prompt_ids, self.max_length, rid, sampling_params,
+                                      self.eos_token_ids)
+        self._records[rid] = RequestRecord(rid, ctx.tokens.prompt_len, arrival=ctx.arrival_time)
+        self.scheduler.add_request(ctx)
+        return rid
+
+    def step(self) -> list[RequestRecord]:
+        """One scheduler iteration; returns the records of requests that finished in it."""
+        self.scheduler.run_iteration()
+        finished = []
+        q = self.scheduler.response_queue
+        while not q.empty():
+            for rid, out in q.get_nowait().items():
+                rec = self._records.get(rid)
+                if rec is None:
+                    continue
+                if out.tokens:
+                    now = time.perf_counter()
+                    if rec.first_token is None:
+                        rec.first_token = now
+                    rec.last_token = now
+                    rec.tokens.extend(out.tokens)
+                if out.is_done:
+                    rec.finished = True
+                    finished.append(rec)
+        return finished
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work() or not self.scheduler.request_queue.empty()
+
+    # ------------------------------------------------------------ batch API
+    def generate(self, prompts: Sequence[Union[Sequence[int], np.ndarray]],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 max_concurrency: Optional[int] = None) -> list[RequestRecord]:
+        """Run every prompt (token ids) to completion. With ``max_concurrency`` a new request is
+        admitted only when one finishes (closed loop), as a serving benchmark client would."""
+        n = len(prompts)
+        if isinstance(sampling_params, SamplingParams) or sampling_params is None:
+            sps = [sampling_params] * n
+        else:
+            sps = list(sampling_params)
+        conc = n if not max_concurrency else min(max_concurrency, n)
+        order, nxt, inflight = [], 0, 0
+        while nxt < conc:
+            order.append(self.add_request(prompts[nxt], sps[nxt]))
+            nxt += 1
+            inflight += 1
+        while inflight > 0:
+            for _ in self.step():
+                inflight -= 1
+                if nxt < n:
+                    order.append(self.add_request(prompts[nxt], sps[nxt]))
+                    nxt += 1
+                    inflight += 1
+        recs = [self._records.pop(rid) for rid in order]
+        return recs

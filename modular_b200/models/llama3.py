@@ -1,0 +1,291 @@
+"""Llama-3 family decoder (GQA attention, SwiGLU MLP, RMSNorm, RoPE) over a paged KV cache.
+
+The model owns *fused* weights (``wqkv`` = [q; k; v] rows, ``wgu`` = [gate; up] rows) built
+from an HF-layout state dict by :func:`adapt_hf_state_dict`, and runs one ragged batch
+(``StepBatch``) per call:
+
+* on CUDA the whole stack is issued by the native ``DecoderExecutor`` (one host call per
+  step: embedding, per layer RMSNorm -> QKV GEMM -> RoPE + KV store -> paged attention ->
+  O GEMM (+residual) -> RMSNorm -> gate/up GEMM with SwiGLU epilogue -> down GEMM
+  (+residual), final norm, LM head on the requested rows);
+* on CPU the same sequence runs op by op through the PyTorch reference ops in fp32/bf16.
+
+Reference counterparts: max/python/max/pipelines/architectures/llama3/llama3.py:73,
+model_config.py, weight_adapters.py:33; layer wiring max/python/max/nn/attention/
+attention_with_rope.py:498-557 and nn/linear.py:1037-1084.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from .. import ops
+from .._native import lib as _lib
+from ..nn.rotary_embedding import RopeScaling, cos_sin_table
+
+
+@dataclass
+class Llama3Config:
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: Optional[int] = None
+    vocab_size: int = 128256
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    rope_scaling: Optional[dict] = None
+    max_position_embeddings: int = 131072
+    tie_word_embeddings: bool = False
+    attention_multiplier: Optional[float] = None
+    logits_scaling: float = 1.0
+    architectures: tuple = ("LlamaForCausalLM",)
+
+    def __post_init__(self):
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "Llama3Config":
+        keys = set(cls.__dataclass_fields__)
+        kw = {k: v for k, v in d.items() if k in keys}
+        if "architectures" in kw:
+            kw["architectures"] = tuple(kw["architectures"])
+        return cls(**kw)
+
+    def to_hf(self) -> dict:
+        d = {k: getattr(self, k) for k in self.__dataclass_fields__}
+        d["architectures"] = list(self.architectures)
+        d["model_type"] = "llama"
+        return d
+
+    @property
+    def q_dim(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def param_count(self) -> int:
+        per_layer = (self.hidden_size * (self.q_dim + 2 * self.kv_dim) + self.q_dim * self.hidden_size
+                     + 3 * self.hidden_size * self.intermediate_size + 2 * self.hidden_size)
+        emb = self.vocab_size * self.hidden_size
+        return self.num_hidden_layers * per_layer + emb * (1 if self.tie_word_embeddings else 2) + self.hidden_size
+
+    # named presets used by benchmarks and tests
+    @classmethod
+    def llama31_8b(cls) -> "Llama3Config":
+        return cls(rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                 "high_freq_factor": 4.0, "original_max_position_embeddings": 8192})
+
+    @classmethod
+    def llama33_70b(cls) -> "Llama3Config":
+        return cls(hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
+                   num_attention_heads=64, num_key_value_heads=8,
+                   rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                 "high_freq_factor": 4.0, "original_max_position_embeddings": 8192})
+
+    @classmethod
+    def tiny(cls) -> "Llama3Config":
+        return cls(hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                   num_key_value_heads=2, head_dim=64, vocab_size=4096, rms_norm_eps=1e-5,
+                   rope_theta=500000.0, max_position_embeddings=2048, tie_word_embeddings=True)
+
+
+@dataclass
+class LayerWeights:
+    attn_norm: torch.Tensor
+    wqkv: torch.Tensor
+    wo: torch.Tensor
+    mlp_norm: torch.Tensor
+    wgu: torch.Tensor
+    wd: torch.Tensor
+
+
+@dataclass
+class Llama3Weights:
+    embed: torch.Tensor
+    layers: list
+    final_norm: torch.Tensor
+    lm_head: torch.Tensor
+
+    @classmethod
+    def random_init(cls, cfg: Llama3Config, device="cpu", dtype=torch.bfloat16, seed: int = 0,
+                    std: float = 0.02) -> "Llama3Weights":
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        dev = torch.device(device)
+
+        def rnd(*shape):
+            if dev.type == "cuda" and math.prod(shape) > (1 << 22):
+                # large tensors: generate on the device (seeded per tensor)
+                gd = torch.Generator(device=dev).manual_seed(int(torch.randint(0, 2**31, (1,), generator=g)))
+                return (torch.randn(*shape, device=dev, dtype=torch.float32, generator=gd) * std).to(dtype)
+            return (torch.randn(*shape, generator=g) * std).to(dtype).to(dev)
+
+        embed = rnd(cfg.vocab_size, cfg.hidden_size)
+        layers = []
+        for _ in range(cfg.num_hidden_layers):
+            layers.append(LayerWeights(
+                attn_norm=torch.ones(cfg.hidden_size, dtype=dtype, device=dev),
+                wqkv=rnd(cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden_size),
+                wo=rnd(cfg.hidden_size, cfg.q_dim),
+                mlp_norm=torch.ones(cfg.hidden_size, dtype=dtype, device=dev),
+                wgu=rnd(2 * cfg.intermediate_size, cfg.hidden_size),
+                wd=rnd(cfg.hidden_size, cfg.intermediate_size)))
+        final_norm = torch.ones(cfg.hidden_size, dtype=dtype, device=dev)
+        lm_head = embed if cfg.tie_word_embeddings else rnd(cfg.vocab_size, cfg.hidden_size)
+        return cls(embed, layers, final_norm, lm_head)
+
+    @classmethod
+    def from_state_dict(cls, cfg: Llama3Config, sd: dict, device="cpu", dtype=torch.bfloat16):
+        sd = adapt_hf_state_dict(sd)
+        dev = torch.device(device)
+
+        def get(name):
+            return sd[name].to(device=dev, dtype=dtype).contiguous()
+
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"layers.{i}."
+            wqkv = torch.cat([sd[p + "self_attn.q_proj.weight"], sd[p + "self_attn.k_proj.weight"],
+                              sd[p + "self_attn.v_proj.weight"]], dim=0)
+            wgu = torch.cat([sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]], dim=0)
+            layers.append(LayerWeights(
+                attn_norm=get(p + "input_layernorm.weight"),
+                wqkv=wqkv.to(device=dev, dtype=dtype).contiguous(),
+                wo=get(p + "self_attn.o_proj.weight"),
+                mlp_norm=get(p + "post_attention_layernorm.weight"),
+                wgu=wgu.to(device=dev, dtype=dtype).contiguous(),
+                wd=get(p + "mlp.down_proj.weight")))
+        embed = get("embed_tokens.weight")
+        lm_head = embed if (cfg.tie_word_embeddings or "lm_head.weight" not in sd) else get("lm_head.weight")
+        return cls(embed, layers, get("norm.weight"), lm_head)
+
+    def to_hf_state_dict(self, cfg: Llama3Config) -> dict:
+        """Inverse of :meth:`from_state_dict` (used to write checkpoints in tests and tools)."""
+        sd = {"model.embed_tokens.weight": self.embed, "model.norm.weight": self.final_norm}
+        if not cfg.tie_word_embeddings:
+            sd["lm_head.weight"] = self.lm_head
+        for i, l in enumerate(self.layers):
+            p = f"model.layers.{i}."
+            q, k, v = torch.split(l.wqkv, [cfg.q_dim, cfg.kv_dim, cfg.kv_dim], dim=0)
+            g, u = torch.split(l.wgu, cfg.intermediate_size, dim=0)
+            sd.update({p + "input_layernorm.weight": l.attn_norm, p + "self_attn.q_proj.weight": q,
+                       p + "self_attn.k_proj.weight": k, p + "self_attn.v_proj.weight": v,
+                       p + "self_attn.o_proj.weight": l.wo,
+                       p + "post_attention_layernorm.weight": l.mlp_norm,
+                       p + "mlp.gate_proj.weight": g, p + "mlp.up_proj.weight": u,
+                       p + "mlp.down_proj.weight": l.wd})
+        return {k: v.contiguous() for k, v in sd.items()}
+
+
+def adapt_hf_state_dict(sd: dict) -> dict:
+    """HF checkpoint names -> internal names: strips the ``model.`` prefix, keeps ``lm_head``."""
+    out = {}
+    for k, v in sd.items():
+        if k.startswith("model."):
+            k = k[len("model."):]
+        out[k] = v
+    return out
+
+
+class Llama3Model:
+    """Runs ragged batches of a Llama-3 decoder against a paged KV cache."""
+
+    def __init__(self, cfg: Llama3Config, weights: Llama3Weights, kv_cache: torch.Tensor,
+                 max_tokens: int = 8192, max_seqs: int = 256, max_position: Optional[int] = None,
+                 use_executor: Optional[bool] = None, fuse_swiglu: bool = True):
+        self.cfg = cfg
+        self.w = weights
+        self.kv = kv_cache
+        self.device = weights.embed.device
+        self.dtype = weights.embed.dtype
+        self.max_tokens = max_tokens
+        self.max_seqs = max_seqs
+        self.page_size = kv_cache.shape[4]
+        self.scale = cfg.attention_multiplier or 1.0 / math.sqrt(cfg.head_dim)
+        max_position = max_position or cfg.max_position_embeddings
+        self.cos_sin = cos_sin_table(cfg.head_dim, max_position, cfg.rope_theta,
+                                     RopeScaling.from_hf(cfg.rope_scaling), self.device)
+        on_gpu = self.device.type == "cuda"
+        self.use_executor = on_gpu and self.dtype == torch.bfloat16 if use_executor is None else use_executor
+        self.fuse_swiglu = fuse_swiglu
+        self.executor = None
+        self.logits_buf = None
+        if self.use_executor:
+            self._build_executor()
+
+    # ------------------------------------------------------------ native path
+    def _build_executor(self) -> None:
+        c, dev, dt = self.cfg, self.device, self.dtype
+        L = _lib()
+        ex = L.DecoderExecutor(dict(
+            n_layers=c.num_hidden_layers, hidden=c.hidden_size, n_q=c.num_attention_heads,
+            n_kv=c.num_key_value_heads, head_dim=c.head_dim, inter=c.intermediate_size,
+            vocab=c.vocab_size, eps=c.rms_norm_eps, page_size=self.page_size,
+            attn_scale=self.scale, fuse_swiglu=int(self.fuse_swiglu)))
+        ex.set_globals(self.w.embed, self.w.final_norm, self.w.lm_head, self.cos_sin)
+        for l in self.w.layers:
+            ex.add_layer(l.attn_norm, l.wqkv, l.wo, l.mlp_norm, l.wgu, l.wd)
+        ex.set_kv_cache(self.kv)
+        T, B = self.max_tokens, self.max_seqs
+        mk = lambda *s, dtype=dt: torch.empty(*s, dtype=dtype, device=dev)
+        self.logits_buf = mk(B, c.vocab_size, dtype=torch.float32)
+        self.sampled = torch.zeros(B, dtype=torch.long, device=dev)
+        self._bufs = dict(
+            h=mk(T, c.hidden_size), xn=mk(T, c.hidden_size), qkv=mk(T, c.q_dim + 2 * c.kv_dim),
+            attn=mk(T, c.q_dim), act=mk(T, c.intermediate_size),
+            gu=None if self.fuse_swiglu else mk(T, 2 * c.intermediate_size),
+            last_h=mk(B, c.hidden_size), last_xn=mk(B, c.hidden_size))
+        b = self._bufs
+        ex.set_buffers(b["h"], b["xn"], b["qkv"], b["attn"], b["act"], b["gu"], b["last_h"],
+                       b["last_xn"], self.logits_buf, self.sampled, ops.gemm_workspace(dev))
+        self.executor = ex
+
+    def forward_packed(self, meta: torch.Tensor, offsets: dict, T: int, B: int, bt_stride: int,
+                       n_tiles: int, n_decode: int, n_logits: int, has_future: bool = False,
+                       do_sample: bool = False, sample_step: int = 0) -> torch.Tensor:
+        """Native step from a packed device metadata buffer. Returns fp32 logits
+        ``[n_logits, vocab]`` (a view of a persistent buffer, valid until the next call). With
+        ``do_sample`` the sampled ids land in ``self.sampled[:n_logits]``; with ``has_future``
+        token ids flagged in the batch are first taken from the previous step's ``sampled``."""
+        if T > self.max_tokens or n_logits > self.max_seqs:
+            raise ValueError(f"batch of {T} tokens / {n_logits} logit rows exceeds the executor's "
+                             f"buffers ({self.max_tokens}, {self.max_seqs})")
+        self.executor.forward(meta, offsets, T, B, bt_stride, n_tiles, n_decode, n_logits,
+                              has_future, do_sample, sample_step)
+        return self.logits_buf[:n_logits]
+
+    # ------------------------------------------------------------ op-by-op path
+    def forward_tensors(self, tokens, positions, slots, block_table, q_start, q_len, kv_len,
+                        logit_rows, plan=None) -> torch.Tensor:
+        """Same computation through :mod:`modular_b200.ops` one op at a time (CPU, and the
+        cross-check for the executor on GPU). Returns fp32 logits [len(logit_rows), vocab]."""
+        c = self.cfg
+        h = ops.embedding(tokens, self.w.embed)
+        for li, l in enumerate(self.w.layers):
+            kc, vc = self.kv[:, 0, li], self.kv[:, 1, li]
+            x = ops.rms_norm(h, l.attn_norm, c.rms_norm_eps)
+            qkv = ops.linear(x, l.wqkv)
+            ops.rope_kv_store(qkv, positions, slots, self.cos_sin, kc, vc, c.num_attention_heads,
+                              c.num_key_value_heads, c.head_dim, False)
+            a = ops.paged_attention(qkv, kc, vc, block_table, q_start, q_len, kv_len,
+                                    c.num_attention_heads, c.num_key_value_heads, c.head_dim,
+                                    self.scale, plan=plan)
+            h = ops.linear(a, l.wo, residual=h)
+            x = ops.rms_norm(h, l.mlp_norm, c.rms_norm_eps)
+            if self.fuse_swiglu:
+                act = ops.linear_swiglu(x, l.wgu)
+            else:
+                act = ops.silu_mul(ops.linear(x, l.wgu))
+            h = ops.linear(act, l.wd, residual=h)
+        last = h[logit_rows.long()]
+        xn = ops.rms_norm(last, self.w.final_norm, c.rms_norm_eps)
+        logits = ops.linear(xn, self.w.lm_head, out_dtype=torch.float32)
+        return logits.float()

@@ -190,6 +190,7 @@ class TextContext:
     # bookkeeping owned by the engine
     pending_future: int = 0          # tokens sampled on device whose values are still in flight
     emitted: int = 0                 # generated tokens already handed to the caller
+    sample_slot: int = -1            # row of this request in the previous step's sampled-token buffer
     dp_replica: int = 0
     lora_name: Optional[str] = None
     json_schema: Optional[str] = None

@@ -1,0 +1,286 @@
+"""Text-generation pipelines: one forward + sample per ``execute`` call.
+
+``TextGenerationPipeline.execute(batch)`` runs a ragged batch of contexts (each contributes
+its active window), samples one token for every context whose window reaches its last
+token, updates the contexts and the KV manager, and returns ``{request_id:
+TextGenerationOutput}``. (Reference: max/python/max/pipelines/lib/pipeline_variants/
+text_generation.py:135, ``execute`` :498.)
+
+With ``overlap=True`` the pipeline behaves like the reference's
+``OverlapTextGenerationPipeline`` (overlap_text_generation.py:14-60, :3899): ``execute``
+enqueues step N and returns the outputs of step N-1, so the host prepares the next batch
+while the GPU runs the current one. Token ids sampled by step N stay on the device; step
+N+1 picks them up there (``FUTURE_TOKEN`` placeholders in the context until the readback
+lands). Decode-only steps of a captured batch size replay as CUDA graphs.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..kv_cache import PagedKVCacheManager
+from .batch import BatchPacker, StepBatch, meta_layout
+from .context import FUTURE_TOKEN, GenerationStatus, TextContext, TextGenerationOutput
+
+
+@dataclass
+class _InFlight:
+    batch: StepBatch
+    event: Optional[torch.cuda.Event]
+    host_tokens: Optional[torch.Tensor]   # pinned int64 [n_logits] (GPU) or plain tensor (CPU)
+    launched_at: float = 0.0
+
+
+@dataclass
+class PipelineStats:
+    steps: int = 0
+    graph_replays: int = 0
+    tokens_in: int = 0
+    tokens_out: int = 0
+    h2d_bytes: int = 0
+    d2h_bytes: int = 0
+    gpu_launches_at_start: int = 0
+
+
+class TextGenerationPipeline:
+    def __init__(self, model, kv_manager: PagedKVCacheManager, max_batch_tokens: int = 8192,
+                 max_batch_size: int = 256, overlap: bool = False, graph_batch_sizes: Sequence[int] = (),
+                 eos_token_ids: Sequence[int] = ()):
+        self.model = model
+        self.kv = kv_manager
+        self.device = model.device
+        self.on_gpu = self.device.type == "cuda"
+        self.overlap = overlap and self.on_gpu
+        self.eos_token_ids = frozenset(eos_token_ids)
+        cfg = model.cfg
+        self.packer = BatchPacker(cfg.num_attention_heads, cfg.num_key_value_heads, kv_manager.page_size,
+                                  max_batch_tokens, max_batch_size, kv_manager.max_pages_per_seq,
+                                  device=self.device)
+        self.stats = PipelineStats()
+        self._pending: Optional[_InFlight] = None
+        self._step = 0
+        self._graphs: dict[int, tuple] = {}
+        self._d2h = [torch.empty(max_batch_size, dtype=torch.long, pin_memory=self.on_gpu) for _ in range(4)]
+        self._d2h_i = 0
+        self.graph_batch_sizes = tuple(sorted(set(int(b) for b in graph_batch_sizes)))
+        self._cpu_gen = torch.Generator().manual_seed(0)
+        self._gpu_events: list = []
+        self._graph_launches: dict[int, int] = {}
+        self._replayed_launches = 0
+        self.record_gpu_time = self.on_gpu
+
+    # ------------------------------------------------------------ CUDA graphs
+    def warmup_graph_capture(self) -> None:
+        """Capture one decode graph per configured batch size (layout pinned per size)."""
+        if not (self.on_gpu and self.model.use_executor):
+            return
+        for B in self.graph_batch_sizes:
+            if B in self._graphs or B > self.packer.max_seqs:
+                continue
+            fixed = (B, B, self.kv.max_pages_per_seq, 1)
+            off, words = meta_layout(*fixed)
+            meta = self.packer.meta_dev
+            # a harmless all-dummy batch for the capture run
+            host = np.zeros(words, dtype=np.int32)
+            host[off["q_len"] : off["q_len"] + B] = 1
+            host[off["kv_len"] : off["kv_len"] + B] = 1
+            host[off["q_start"] : off["q_start"] + B] = np.arange(B)
+            host[off["decode_seq"] : off["decode_seq"] + B] = np.arange(B)
+            host[off["logit_rows"] : off["logit_rows"] + B] = np.arange(B)
+            host[off["future_src"] : off["future_src"] + B] = -1
+            host.view(np.int64)[off["slots"] // 2 : off["slots"] // 2 + B] = -1
+            host.view(np.float32)[off["top_p"] : off["top_p"] + B] = 1.0
+            meta[:words].copy_(torch.from_numpy(host))
+            args = (meta, off, B, B, fixed[2], 0, B, B, True, True, 0)
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(2):
+                    self.model.forward_packed(*args)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            n0 = self.model.executor.launches()
+            with torch.cuda.graph(g):
+                self.model.forward_packed(*args)
+            self._graph_launches[B] = self.model.executor.launches() - n0
+            self._graphs[B] = (g, fixed, off, words)
+        torch.cuda.synchronize()
+
+    def _graph_bucket(self, batch: Sequence[TextContext]) -> int:
+        if not self._graphs:
+            return 0
+        n = len(batch)
+        for B in self.graph_batch_sizes:
+            if B >= n and B in self._graphs:
+                if all(c.tokens.active_length == 1 and c.sampling_params.is_greedy for c in batch):
+                    return B
+                return 0
+        return 0
+
+    # ------------------------------------------------------------ one step
+    def _launch(self, batch: Sequence[TextContext]) -> _InFlight:
+        self._step += 1
+        self.stats.steps += 1
+        model = self.model
+        if self.on_gpu and model.use_executor:
+            if self.record_gpu_time:
+                ev0 = torch.cuda.Event(enable_timing=True)
+                ev0.record()
+            B_graph = self._graph_bucket(batch)
+            if B_graph:
+                g, fixed, off, words = self._graphs[B_graph]
+                sb = self.packer.pack(batch, self.kv, fixed=fixed, pad_to=B_graph)
+                self.packer.upload(sb)
+                g.replay()
+                self.stats.graph_replays += 1
+                self._replayed_launches += self._graph_launches[B_graph]
+            else:
+                sb = self.packer.pack(batch, self.kv)
+                meta = self.packer.upload(sb)
+                needs_pen = any(c.sampling_params.needs_penalties for c in sb.logit_ctx)
+                model.forward_packed(meta, sb.offsets, sb.T, sb.B, sb.bt_stride, sb.n_tiles,
+                                     sb.n_decode, sb.n_logits, sb.has_future, not needs_pen, self._step)
+                if needs_pen:
+                    self._penalties_and_sample(sb, meta)
+            self.stats.h2d_bytes += sb.words * 4
+            host = self._d2h[self._d2h_i]
+            self._d2h_i = (self._d2h_i + 1) % len(self._d2h)
+            host[: sb.n_logits].copy_(model.sampled[: sb.n_logits], non_blocking=True)
+            ev = torch.cuda.Event(enable_timing=self.record_gpu_time)
+            ev.record()
+            if self.record_gpu_time:
+                self._gpu_events.append((ev0, ev))
+            self.stats.d2h_bytes += sb.n_logits * 8
+            inflight = _InFlight(sb, ev, host, time.perf_counter())
+        else:
+            sb = self.packer.pack(batch, self.kv)
+            t = BatchPacker.tensors(sb, self.device)
+            toks = t["tokens"]
+            if sb.has_future:
+                raise RuntimeError("future tokens require the overlap (GPU) pipeline")
+            logits = model.forward_tensors(toks, t["positions"], t["slots"], t["block_table"],
+                                           t["q_start"], t["q_len"], t["kv_len"], t["logit_rows"])
+            sampled = self._sample_host(sb, t, logits)
+            inflight = _InFlight(sb, None, sampled.cpu(), time.perf_counter())
+            self.last_logits = logits
+        self.stats.tokens_in += sb.T
+        # bookkeeping that does not need the token values
+        for i, c in enumerate(sb.logit_ctx):
+            c.sample_slot = i
+        for c in sb.ctxs:
+            c.tokens.advance_processed()
+        for c in sb.logit_ctx:
+            c.update_with_future_token()
+        return inflight
+
+    def _penalties_and_sample(self, sb: StepBatch, meta: torch.Tensor) -> None:
+        n, off = sb.n_logits, sb.offsets
+        logits = self.model.logits_buf[:n]
+        tok, cnt, offs = [], [], [0]
+        freq = np.zeros(n, np.float32)
+        pres = np.zeros(n, np.float32)
+        rep = np.ones(n, np.float32)
+        for i, c in enumerate(sb.logit_ctx):
+            sp = c.sampling_params
+            if sp.needs_penalties:
+                allt = c.tokens.all
+                allt = allt[allt >= 0]
+                gen_start = c.tokens.prompt_len
+                u, _ = np.unique(allt, return_counts=True)
+                gen = c.tokens.all[gen_start:]
+                gen = gen[gen >= 0]
+                gu, gc = np.unique(gen, return_counts=True)
+                counts = dict(zip(gu.tolist(), gc.tolist()))
+                tok.extend(u.tolist())
+                cnt.extend(counts.get(int(x), 0) for x in u.tolist())
+                freq[i], pres[i], rep[i] = sp.frequency_penalty, sp.presence_penalty, sp.repetition_penalty
+            offs.append(len(tok))
+        dev = self.device
+        mk = lambda a, dt: torch.tensor(a, dtype=dt, device=dev)
+        ops.apply_penalties(logits, mk(tok or [0], torch.int32), mk(cnt or [0], torch.int32),
+                            mk(offs, torch.int32), mk(freq, torch.float32), mk(pres, torch.float32),
+                            mk(rep, torch.float32))
+        f32 = lambda name: meta[off[name] : off[name] + n].view(torch.float32)
+        ops.sample(logits, f32("temperature"), meta[off["top_k"] : off["top_k"] + n], f32("top_p"),
+                   f32("min_p"), meta[off["seeds"] : off["seeds"] + 2 * n].view(torch.int64),
+                   self._step, out=self.model.sampled[:n])
+
+    def _sample_host(self, sb: StepBatch, t: dict, logits: torch.Tensor) -> torch.Tensor:
+        if any(c.sampling_params.needs_penalties for c in sb.logit_ctx):
+            tok, cnt, offs = [], [], [0]
+            for c in sb.logit_ctx:
+                if c.sampling_params.needs_penalties:
+                    u = np.unique(c.tokens.all)
+                    gu, gc = np.unique(c.tokens.generated, return_counts=True)
+                    counts = dict(zip(gu.tolist(), gc.tolist()))
+                    tok.extend(u.tolist())
+                    cnt.extend(counts.get(int(x), 0) for x in u.tolist())
+                offs.append(len(tok))
+            sp = [c.sampling_params for c in sb.logit_ctx]
+            ops.apply_penalties(logits, torch.tensor(tok or [0], dtype=torch.int32),
+                                torch.tensor(cnt or [0], dtype=torch.int32), torch.tensor(offs, dtype=torch.int32),
+                                torch.tensor([s.frequency_penalty for s in sp]),
+                                torch.tensor([s.presence_penalty for s in sp]),
+                                torch.tensor([s.repetition_penalty for s in sp]))
+        if sb.all_greedy:
+            return ops.argmax(logits)
+        return ops.sample(logits, t["temperature"], t["top_k"], t["top_p"], t["min_p"],
+                          generator=self._cpu_gen)
+
+    def _collect(self, inflight: Optional[_InFlight]) -> dict:
+        """Wait for a launched step's tokens, fold them into the contexts, build outputs."""
+        out: dict[str, TextGenerationOutput] = {}
+        if inflight is None:
+            return out
+        if inflight.event is not None:
+            inflight.event.synchronize()
+        sb = inflight.batch
+        vals = inflight.host_tokens[: sb.n_logits].numpy()
+        for i, c in enumerate(sb.logit_ctx):
+            c.realize_future_token(int(vals[i]))
+            self.stats.tokens_out += 1
+        for c in sb.ctxs:
+            if self.kv.contains(c.request_id):
+                self.kv.step(c)
+        for c in sb.logit_ctx:
+            out[c.request_id] = c.to_generation_output()
+        return out
+
+    def execute(self, batch: Sequence[TextContext]) -> dict:
+        """Run one step. Synchronous mode returns this step's outputs; overlap mode returns the
+        previous step's (call with an empty batch to drain)."""
+        if not self.overlap:
+            return self._collect(self._launch(batch)) if batch else {}
+        new = self._launch(batch) if batch else None
+        out = self._collect(self._pending)
+        self._pending = new
+        return out
+
+    # ------------------------------------------------------------ accounting
+    def gpu_launches(self) -> int:
+        """Kernels of this library launched so far (direct launches + launches inside replayed
+        graphs)."""
+        ex = getattr(self.model, "executor", None)
+        direct = ex.launches() if ex is not None else 0
+        return direct - sum(self._graph_launches.values()) + self._replayed_launches
+
+    def reset_gpu_time(self) -> None:
+        self._gpu_events.clear()
+
+    def gpu_time_s(self) -> float:
+        """Device time between the first and last operation of every recorded step, summed."""
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in self._gpu_events) * 1e-3
+
+    def has_pending(self) -> bool:
+        return self._pending is not None
+
+    def release(self, request_id: str) -> None:
+        self.kv.release(request_id)

@@ -1,0 +1,136 @@
+"""Token-generation scheduler: the loop body of the model worker.
+
+One ``run_iteration``: drain the request queue (bounded by ``max_pending_requests``),
+construct a batch, execute it on the pipeline, move requests between queues, release
+finished ones, push responses, service cancellations, record batch metrics.
+Reference: max/python/max/serve/scheduler/text_generation_scheduler.py:86
+(``run_iteration`` :197, ``_schedule`` :291).
+"""
+
+from __future__ import annotations
+
+import enum
+import queue
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+from ...pipelines.context import GenerationStatus, TextContext, TextGenerationOutput
+from .batch_constructor import BatchType, SchedulerBatch, TextBatchConstructor
+from .config import TokenGenerationSchedulerConfig
+
+
+class SchedulerProgress(enum.Enum):
+    MADE_PROGRESS = "made_progress"
+    NO_PROGRESS = "no_progress"
+
+
+@dataclass
+class BatchMetrics:
+    batch_type: str = "empty"
+    batch_size: int = 0
+    num_ce: int = 0
+    num_tg: int = 0
+    input_tokens: int = 0
+    output_tokens: int = 0
+    batch_time_s: float = 0.0
+    kv_used_pct: float = 0.0
+    cache_hit_rate: float = 0.0
+    preemptions: int = 0
+    pending_requests: int = 0
+
+    @property
+    def prompt_throughput(self) -> float:
+        return self.input_tokens / self.batch_time_s if self.batch_time_s > 0 else 0.0
+
+    @property
+    def generation_throughput(self) -> float:
+        return self.output_tokens / self.batch_time_s if self.batch_time_s > 0 else 0.0
+
+
+class TokenGenerationScheduler:
+    def __init__(self, config: TokenGenerationSchedulerConfig, pipeline, kv=None,
+                 request_queue=None, response_queue=None, cancel_queue=None,
+                 metrics_sink: Optional[Callable[[BatchMetrics], None]] = None):
+        self.config = config
+        self.pipeline = pipeline
+        self.kv = kv if kv is not None else getattr(pipeline, "kv", None)
+        self.batch_constructor = TextBatchConstructor(config, self.kv)
+        self.request_queue = request_queue if request_queue is not None else queue.SimpleQueue()
+        self.response_queue = response_queue if response_queue is not None else queue.SimpleQueue()
+        self.cancel_queue = cancel_queue if cancel_queue is not None else queue.SimpleQueue()
+        self.metrics_sink = metrics_sink
+        self.last_metrics = BatchMetrics()
+        self._contexts: dict[str, TextContext] = {}
+        self.total_steps = 0
+
+    # ------------------------------------------------------------ queue plumbing
+    def _drain_requests(self) -> int:
+        n, limit = 0, self.config.max_pending_requests
+        while limit <= 0 or n < limit:
+            try:
+                ctx = self.request_queue.get_nowait()
+            except queue.Empty:
+                break
+            except Exception:  # noqa: BLE001  (zmq queues raise their own Empty)
+                break
+            self._contexts[ctx.request_id] = ctx
+            self.batch_constructor.enqueue_new_request(ctx)
+            n += 1
+        return n
+
+    def _handle_cancels(self) -> None:
+        while True:
+            try:
+                rid = self.cancel_queue.get_nowait()
+            except Exception:  # noqa: BLE001
+                break
+            ctx = self._contexts.pop(rid, None)
+            if ctx is None:
+                continue
+            ctx.status = GenerationStatus.CANCELLED
+            self.batch_constructor.release_request(rid)
+            self.response_queue.put_nowait({rid: TextGenerationOutput(rid, [], GenerationStatus.CANCELLED)})
+
+    def add_request(self, ctx: TextContext) -> None:
+        self.request_queue.put_nowait(ctx)
+
+    def has_work(self) -> bool:
+        return (self.batch_constructor.num_requests() > 0 or bool(self.batch_constructor.draining)
+                or self.pipeline.has_pending())
+
+    # ------------------------------------------------------------ one iteration
+    def _finish(self, outputs: dict) -> None:
+        done = [rid for rid, o in outputs.items() if o.is_done]
+        for rid in done:
+            if rid in self._contexts:
+                self.batch_constructor.release_request(rid)
+                del self._contexts[rid]
+        # outputs for requests already gone (cancelled, or extra speculative step) are dropped
+        live = {rid: o for rid, o in outputs.items() if o.tokens or o.is_done}
+        if live:
+            self.response_queue.put_nowait(live)
+
+    def run_iteration(self) -> SchedulerProgress:
+        self._drain_requests()
+        t0 = time.perf_counter()
+        batch = self.batch_constructor.construct_batch()
+        if not batch.contexts and not self.pipeline.has_pending():
+            self._handle_cancels()
+            return SchedulerProgress.NO_PROGRESS
+        outputs = self.pipeline.execute(batch.contexts)
+        self.batch_constructor.advance_requests(batch)
+        self.total_steps += 1
+        outputs = {rid: o for rid, o in outputs.items() if rid in self._contexts}
+        self._finish(outputs)
+        self._handle_cancels()
+        dt = time.perf_counter() - t0
+        m = BatchMetrics(batch.batch_type.value, len(batch), batch.num_ce, batch.num_tg,
+                         batch.input_tokens, sum(len(o.tokens) for o in outputs.values()), dt,
+                         self.kv.used_blocks_pct if self.kv is not None else 0.0,
+                         self.kv.cache_hit_rate if self.kv is not None else 0.0,
+                         batch.preempted, self.batch_constructor.num_requests())
+        self.last_metrics = m
+        if self.metrics_sink is not None:
+            self.metrics_sink(m)
+        return SchedulerProgress.MADE_PROGRESS
