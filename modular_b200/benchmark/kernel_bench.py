@@ -61,10 +61,14 @@ def bench_gemm(shapes, results, configs=None):
             lib = lambda: torch.matmul(x, w.t(), out=out)
         t_ours = time_fn(ours)
         t_lib = time_fn(lib)
+        if mode == "swiglu":
+            t_tiled = time_fn(lambda: ops.linear_swiglu(x, w, impl="tiled"))
+        else:
+            t_tiled = time_fn(lambda: ops.linear(x, w, out=out, impl="tiled"))
         t_roof = max(flops / (peaks["bf16_tflops"] * 1e12), bytes_ / (peaks["hbm_gbs"] * 1e9))
         rec = dict(kernel="gemm_bf16", name=name, M=M, N=N, K=K, mode=mode,
                    plan=list(ops._lib().gemm_plan(M, N, K, mode == "swiglu")),
-                   us=t_ours * 1e6, lib_us=t_lib * 1e6, tflops=flops / t_ours / 1e12,
+                   us=t_ours * 1e6, lib_us=t_lib * 1e6, tiled_us=t_tiled * 1e6, tflops=flops / t_ours / 1e12,
                    gbs=bytes_ / t_ours / 1e9, frac_of_measured_roofline=t_roof / t_ours,
                    speedup_vs_lib=t_lib / t_ours)
         if configs:
@@ -139,6 +143,7 @@ def main(argv=None):
     ap.add_argument("--what", default="gemm,attn")
     ap.add_argument("--out", default=None)
     ap.add_argument("--sweep", action="store_true", help="also sweep tile configs per shape")
+    ap.add_argument("--only", default=None, help="comma-separated GEMM shape names to run")
     args = ap.parse_args(argv)
     results = []
     what = set(args.what.split(","))
@@ -147,7 +152,11 @@ def main(argv=None):
         if args.sweep:
             cfgs = [(bn, st, sp) for bn in (16, 32, 64, 96, 128, 160, 192, 256) for st in (3, 4, 6, 8)
                     for sp in (1, 2, 4)]
-        bench_gemm(LLAMA8B_SHAPES, results, cfgs)
+        shapes = LLAMA8B_SHAPES
+        if args.only:
+            keep = set(args.only.split(","))
+            shapes = [s for s in shapes if s[0] in keep]
+        bench_gemm(shapes, results, cfgs)
     if "attn" in what:
         bench_attention(results)
     if args.out:

@@ -98,6 +98,36 @@ void gemm_bf16(const Tensor& x, const Tensor& w, Tensor& y, const c10::optional<
            "gemm_bf16");
 }
 
+// Persistent stream-K variant. `ws` = (float workspace, int32 zeroed counters).
+void gemm_bf16_persistent(const Tensor& x, const Tensor& w, Tensor& y,
+                          const c10::optional<Tensor>& residual, bool dual, const Tensor& ws,
+                          const Tensor& counters, int bn, int stages, int mode, bool pdl) {
+  need_cuda(x, "x"); need_cuda(w, "w"); need_cuda(y, "y");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2, "gemm: 2-D tensors expected");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "bf16 inputs");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1, "row-major operands");
+  const int M = x.size(0), K = x.size(1);
+  const int N = dual ? w.size(0) / 2 : w.size(0);
+  TORCH_CHECK(w.size(1) == K && y.size(0) == M && y.size(1) == N, "gemm: shape mismatch");
+  const bool f32 = y.scalar_type() == at::kFloat;
+  const bool resid = residual.has_value() && residual->defined();
+  TORCH_CHECK(static_cast<size_t>(ws.nbytes()) >= mb_gemm_persistent_workspace_bytes(num_sms()) &&
+                  static_cast<size_t>(counters.numel()) >= mb_gemm_persistent_counter_ints(num_sms()) &&
+                  counters.scalar_type() == at::kInt,
+              "gemm: workspace too small");
+  int flags = (dual ? 1 : 0) | (resid ? 2 : 0) | (f32 ? 4 : 0) | (pdl ? 8 : 0);
+  check_rc(mb_gemm_bf16_persistent(x.data_ptr(), w.data_ptr(), y.data_ptr(), optptr(residual), M, N, K,
+                                   x.stride(0), w.stride(0), y.stride(0),
+                                   resid ? residual->stride(0) : 0, flags, bn, stages, mode,
+                                   ws.data_ptr(), counters.data_ptr<int>(), error_flag(), num_sms(),
+                                   cur_stream()),
+           "gemm_bf16_persistent");
+}
+py::tuple gemm_persistent_sizes() {
+  return py::make_tuple(mb_gemm_persistent_workspace_bytes(num_sms()),
+                        mb_gemm_persistent_counter_ints(num_sms()));
+}
+
 py::tuple gemm_plan(int M, int N, int K, bool dual) {
   int bn, sp, st;
   mb_gemm_bf16_plan(M, N, K, dual, num_sms(), &bn, &sp, &st);
@@ -320,6 +350,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("workspace") = py::none(), py::arg("bn") = 0, py::arg("splits") = 0,
         py::arg("stages") = 0);
   m.def("gemm_plan", &gemm_plan);
+  m.def("gemm_bf16_persistent", &gemm_bf16_persistent, py::arg("x"), py::arg("w"), py::arg("y"),
+        py::arg("residual") = py::none(), py::arg("dual") = false, py::arg("ws"), py::arg("counters"),
+        py::arg("bn") = 0, py::arg("stages") = 0, py::arg("mode") = -1, py::arg("pdl") = false);
+  m.def("gemm_persistent_sizes", &gemm_persistent_sizes);
   m.def("rmsnorm", &rmsnorm);
   m.def("add_rmsnorm", &add_rmsnorm);
   m.def("silu_mul", &silu_mul);

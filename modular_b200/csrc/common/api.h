@@ -25,6 +25,13 @@ int mb_gemm_bf16(const void* X, const void* W, void* Y, const void* R, int M, in
                  int ldx, int ldw, int ldy, int ldr, int flags, int bn, int splits, int stages,
                  void* workspace, int* err, int num_sms, cudaStream_t stream);
 
+size_t mb_gemm_persistent_workspace_bytes(int num_sms);
+size_t mb_gemm_persistent_counter_ints(int num_sms);
+int mb_gemm_bf16_persistent(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,
+                            int ldx, int ldw, int ldy, int ldr, int flags, int bn, int stages,
+                            int force_mode, void* ws, int* counters, int* err, int num_sms,
+                            cudaStream_t stream);
+
 // ---- block-scaled fp8 (gemm_fp8_blockscaled.cu, quant_fp8.cu) ----------------------------
 int mb_quant_fp8_group128(const void* x_bf16, void* q_fp8, float* scales, int M, int K, int ldx,
                           int scale_ld, int scales_k_major, cudaStream_t stream);

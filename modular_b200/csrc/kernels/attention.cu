@@ -475,6 +475,7 @@ extern "C" int mb_paged_attention(const void* q, int ldq, void* out, int ldo, co
   MB_ATTN_CASE(128, 1) MB_ATTN_CASE(128, 2) MB_ATTN_CASE(128, 4) MB_ATTN_CASE(128, 8)
   MB_ATTN_CASE(128, 16)
   MB_ATTN_CASE(64, 1) MB_ATTN_CASE(64, 2) MB_ATTN_CASE(64, 4) MB_ATTN_CASE(64, 8)
+  MB_ATTN_CASE(64, 16)
 #undef MB_ATTN_CASE
   return MB_ERR_SHAPE;
 }

@@ -30,6 +30,7 @@
 
 #include "../common/ptx.cuh"
 #include "../common/api.h"
+#include "gemm_common.h"
 
 namespace mb {
 
@@ -308,7 +309,7 @@ struct TmapKeyHash {
 
 // Descriptors are pure functions of (pointer, shape, box): cache them so the steady
 // state of a serving loop encodes nothing on the host.
-static int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                        uint64_t ld, uint32_t box_rows, int elt_bytes) {
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
   static std::mutex mu;

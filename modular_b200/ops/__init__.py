@@ -11,6 +11,8 @@ flash_attention_ragged, rms_norm, topk_fused_sampling, apply_penalties_to_logits
 
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -44,7 +46,27 @@ def check_device_error() -> None:
         raise RuntimeError(f"modular_b200 kernel reported a bounded-wait timeout (code {code})")
 
 
-def linear(x, w, residual=None, out=None, out_dtype=None, bn=0, splits=0, stages=0):
+_PERSISTENT_WS: dict[int, tuple] = {}
+# "persistent": one CTA per SM with stream-K work split (default);
+# "tiled": one CTA per output tile with optional split-K through a workspace.
+GEMM_IMPL = os.environ.get("MB200_GEMM", "persistent")
+
+
+def persistent_gemm_workspace(device):
+    """(fp32 partial-tile slots, zeroed int32 tile counters) of the persistent GEMM; one pair
+    per device, to be used from one stream at a time."""
+    idx = torch.device(device).index or 0
+    ws = _PERSISTENT_WS.get(idx)
+    if ws is None:
+        nbytes, nints = _lib().gemm_persistent_sizes()
+        ws = (torch.empty(nbytes // 4, dtype=torch.float32, device=device),
+              torch.zeros(nints, dtype=torch.int32, device=device))
+        _PERSISTENT_WS[idx] = ws
+    return ws
+
+
+def linear(x, w, residual=None, out=None, out_dtype=None, bn=0, splits=0, stages=0, impl=None,
+           mode=-1, pdl=False):
     """``x @ w.T`` (+ residual). x: [M, K] bf16, w: [N, K] bf16."""
     if not x.is_cuda:
         y = ref.linear(x, w, residual, out_dtype)
@@ -54,11 +76,15 @@ def linear(x, w, residual=None, out=None, out_dtype=None, bn=0, splits=0, stages
         return y
     if out is None:
         out = torch.empty(x.shape[0], w.shape[0], dtype=out_dtype or x.dtype, device=x.device)
-    _lib().gemm_bf16(x, w, out, residual, False, gemm_workspace(x.device), bn, splits, stages)
+    if (impl or GEMM_IMPL) == "persistent":
+        ws, counters = persistent_gemm_workspace(x.device)
+        _lib().gemm_bf16_persistent(x, w, out, residual, False, ws, counters, bn, stages, mode, pdl)
+    else:
+        _lib().gemm_bf16(x, w, out, residual, False, gemm_workspace(x.device), bn, splits, stages)
     return out
 
 
-def linear_swiglu(x, w_gate_up, out=None, bn=0, stages=0):
+def linear_swiglu(x, w_gate_up, out=None, bn=0, stages=0, impl=None, mode=-1, pdl=False):
     """``silu(x @ w_gate.T) * (x @ w_up.T)`` with ``w_gate_up = [w_gate; w_up]`` stacked on rows."""
     if not x.is_cuda:
         y = ref.linear_swiglu(x, w_gate_up)
@@ -68,7 +94,11 @@ def linear_swiglu(x, w_gate_up, out=None, bn=0, stages=0):
         return y
     if out is None:
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
-    _lib().gemm_bf16(x, w_gate_up, out, None, True, None, bn, 1, stages)
+    if (impl or GEMM_IMPL) == "persistent":
+        ws, counters = persistent_gemm_workspace(x.device)
+        _lib().gemm_bf16_persistent(x, w_gate_up, out, None, True, ws, counters, bn, stages, mode, pdl)
+    else:
+        _lib().gemm_bf16(x, w_gate_up, out, None, True, None, bn, 1, stages)
     return out
 
 

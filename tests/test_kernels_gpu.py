@@ -29,11 +29,12 @@ def _no_device_error():
     [(1, 128, 64), (16, 256, 128), (64, 4096, 4096), (100, 384, 520), (320, 6144, 4096),
      (257, 1000, 1024), (1024, 4096, 14336), (2048, 2048, 512)],
 )
-def test_gemm_bf16(M, N, K):
+@pytest.mark.parametrize("impl", ["tiled", "persistent"])
+def test_gemm_bf16(M, N, K, impl):
     torch.manual_seed(0)
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
-    y = ops.linear(x, w)
+    y = ops.linear(x, w, impl=impl)
     yr = ref.linear(x, w)
     assert _rel_err(y, yr) < 1e-2
     assert (y.float() - yr.float()).abs().max() <= 0.02 * yr.float().abs().max() + 1e-2
@@ -45,8 +46,24 @@ def test_gemm_tile_configs(bn, stages, splits):
     M, N, K = 300, 512, 2048
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
-    y = ops.linear(x, w, bn=bn, stages=stages, splits=splits)
+    y = ops.linear(x, w, bn=bn, stages=stages, splits=splits, impl="tiled")
     assert _rel_err(y, ref.linear(x, w)) < 1e-2
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("M,N,K,bn,stages", [(300, 512, 2048, 160, 4), (64, 4096, 4096, 64, 8),
+                                              (1, 256, 8192, 16, 3), (700, 1024, 1024, 256, 4),
+                                              (320, 6144, 4096, 0, 0), (48, 128, 16384, 48, 6)])
+def test_gemm_persistent_modes(M, N, K, bn, stages, mode):
+    torch.manual_seed(11)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    r = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(3):  # repeated launches reuse the counters the kernel resets itself
+        y = ops.linear(x, w, residual=r, bn=bn, stages=stages, impl="persistent", mode=mode)
+    assert _rel_err(y, ref.linear(x, w, r)) < 1e-2
+    y2 = ops.linear(x, w, residual=r, bn=bn, stages=stages, impl="persistent", mode=mode)
+    assert torch.equal(y, y2)  # deterministic reduction order
 
 
 def test_gemm_residual_and_fp32_out():
@@ -55,27 +72,29 @@ def test_gemm_residual_and_fp32_out():
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
     r = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
-    y = ops.linear(x, w, residual=r)
-    assert _rel_err(y, ref.linear(x, w, r)) < 1e-2
-    # in-place residual (output aliases the residual)
-    h = r.clone()
-    ops.linear(x, w, residual=h, out=h)
-    assert _rel_err(h, ref.linear(x, w, r)) < 1e-2
+    for impl in ("tiled", "persistent"):
+        y = ops.linear(x, w, residual=r, impl=impl)
+        assert _rel_err(y, ref.linear(x, w, r)) < 1e-2
+        # in-place residual (output aliases the residual)
+        h = r.clone()
+        ops.linear(x, w, residual=h, out=h, impl=impl)
+        assert _rel_err(h, ref.linear(x, w, r)) < 1e-2
+        yf = ops.linear(x, w, out_dtype=torch.float32, impl=impl)
+        assert yf.dtype == torch.float32
+        assert _rel_err(yf, x.float() @ w.float().t()) < 2e-3
     # split-K with residual
-    y2 = ops.linear(x, w, residual=r, splits=4, bn=64)
+    y2 = ops.linear(x, w, residual=r, splits=4, bn=64, impl="tiled")
     assert _rel_err(y2, ref.linear(x, w, r)) < 1e-2
-    yf = ops.linear(x, w, out_dtype=torch.float32)
-    assert yf.dtype == torch.float32
-    assert _rel_err(yf, x.float() @ w.float().t()) < 2e-3
 
 
+@pytest.mark.parametrize("impl,mode", [("tiled", -1), ("persistent", 0), ("persistent", 1)])
 @pytest.mark.parametrize("M", [1, 48, 130, 512])
-def test_gemm_swiglu(M):
+def test_gemm_swiglu(M, impl, mode):
     torch.manual_seed(3)
     K, I = 1024, 1408
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     w = (torch.randn(2 * I, K, device=DEV) * 0.05).to(torch.bfloat16)
-    y = ops.linear_swiglu(x, w)
+    y = ops.linear_swiglu(x, w, impl=impl, mode=mode)
     assert _rel_err(y, ref.linear_swiglu(x, w)) < 1.5e-2
 
 
