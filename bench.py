@@ -112,7 +112,7 @@ def main() -> int:
     ap.add_argument("--input-len", type=int, default=1024)
     ap.add_argument("--output-len", type=int, default=256)
     ap.add_argument("--concurrency", type=int, default=64)
-    ap.add_argument("--max-batch-input-tokens", type=int, default=512)
+    ap.add_argument("--max-batch-input-tokens", type=int, default=2176)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -116,12 +116,15 @@ def bench_attention(results):
         plan = tuple(torch.from_numpy(a).cuda() if a.size else None for a in (ts, t0, ds))
         out = torch.empty(T, n_q * hd, device="cuda", dtype=torch.bfloat16)
         fn = lambda: ops.paged_attention(q, kv[:, 0, 0], kv[:, 1, 0], bt, qs, ql, kl, n_q, n_kv,
-                                         hd, 1 / math.sqrt(hd), plan=plan, out=out)
+                                         hd, 1 / math.sqrt(hd), plan=plan, out=out, kv=kv, layer=0)
+        fn_old = lambda: ops.paged_attention(q, kv[:, 0, 0], kv[:, 1, 0], bt, qs, ql, kl, n_q, n_kv,
+                                             hd, 1 / math.sqrt(hd), plan=plan, out=out)
         t = time_fn(fn)
+        t_old = time_fn(fn_old)
         kv_bytes = sum(kv_lens) * n_kv * hd * 2 * 2
         flops = sum(4.0 * n_q * hd * q_ * (k_ - q_ / 2) for q_, k_ in zip(q_lens, kv_lens))
         t_roof = max(flops / (peaks["bf16_tflops"] * 1e12), kv_bytes / (peaks["hbm_gbs"] * 1e9))
-        rec = dict(kernel="paged_attention", name=name, us=t * 1e6, kv_gbs=kv_bytes / t / 1e9,
+        rec = dict(kernel="paged_attention", name=name, us=t * 1e6, cp_async_us=t_old * 1e6, kv_gbs=kv_bytes / t / 1e9,
                    tflops=flops / t / 1e12, frac_of_measured_roofline=t_roof / t)
         results.append(rec)
         print(json.dumps(rec), flush=True)

@@ -1,0 +1,111 @@
+"""Time one scheduler step of a Llama-shaped model in isolation.
+
+    python -m modular_b200.benchmark.step_profile --layers 32 --decode 64 --ctx 1152 \
+        --prefill 256 --prefill-offset 512 --iters 20
+
+Builds the model with random weights, fabricates a batch in a given state (``--decode``
+single-token sequences with ``--ctx`` tokens of context plus one prefill chunk of
+``--prefill`` tokens that already has ``--prefill-offset`` tokens cached) and replays that
+exact step, so kernel work can be timed (CUDA events) or listed (ncu with
+``--metrics gpu__time_duration.sum``) without a serving loop around it. KV contents are
+whatever the allocator left - only the shapes matter here.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+
+import numpy as np
+import torch
+
+from ..kv_cache import KVCacheParams, PagedKVCacheManager
+from ..models.llama3 import Llama3Config, Llama3Model, Llama3Weights
+from ..pipelines.batch import BatchPacker
+from ..pipelines.context import TextContext
+from .. import ops
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--decode", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=1152)
+    ap.add_argument("--prefill", type=int, default=256)
+    ap.add_argument("--prefill-offset", type=int, default=512)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph")
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args(argv)
+
+    dev = torch.device("cuda")
+    cfg = Llama3Config.llama31_8b()
+    cfg.num_hidden_layers = args.layers
+    w = Llama3Weights.random_init(cfg, dev, torch.bfloat16, seed=0)
+    page = 128
+    n_seq = args.decode + (1 if args.prefill else 0)
+    pages_per_seq = (max(args.ctx, args.prefill_offset + args.prefill) + page) // page + 1
+    kvp = KVCacheParams(cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.head_dim, page,
+                        torch.bfloat16, False, False)
+    kv = PagedKVCacheManager(kvp, n_seq * pages_per_seq + 2, dev, max_seq_len=pages_per_seq * page)
+    T = args.decode + args.prefill
+    model = Llama3Model(cfg, w, kv.kv, max_tokens=max(T, 16), max_seqs=max(n_seq, 1),
+                        max_position=pages_per_seq * page)
+    packer = BatchPacker(cfg.num_attention_heads, cfg.num_key_value_heads, page, max(T, 16),
+                         max(n_seq, 1), kv.max_pages_per_seq, device=dev)
+    rng = np.random.default_rng(0)
+    ctxs = []
+    for i in range(args.decode):
+        c = TextContext.from_prompt(rng.integers(0, cfg.vocab_size, size=args.ctx), 1 << 20, f"d{i}")
+        kv.claim(c)
+        kv.alloc(c)
+        c.tokens.processed = args.ctx - 1
+        ctxs.append(c)
+    if args.prefill:
+        n = args.prefill_offset + args.prefill
+        c = TextContext.from_prompt(rng.integers(0, cfg.vocab_size, size=n + 1), 1 << 20, "p0")
+        kv.claim(c)
+        kv.alloc(c)
+        c.tokens.processed = args.prefill_offset
+        c.tokens.active_end = n
+        ctxs.append(c)
+    sb = packer.pack(ctxs, kv)
+    meta = packer.upload(sb)
+    call = lambda: model.forward_packed(meta, sb.offsets, sb.T, sb.B, sb.bt_stride, sb.n_tiles,
+                                        sb.n_decode, sb.n_logits, False, True, 1)
+    for _ in range(args.warmup):
+        call()
+    torch.cuda.synchronize()
+    if args.graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            call()
+        run = g.replay
+    else:
+        run = call
+    times = []
+    n0 = model.executor.launches()
+    for _ in range(args.iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        run()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    ops.check_device_error()
+    rec = dict(layers=args.layers, decode=args.decode, ctx=args.ctx, prefill=args.prefill,
+               tokens=sb.T, graph=args.graph, ms_median=statistics.median(times), ms_min=min(times),
+               launches_per_step=(model.executor.launches() - n0) // max(1, args.iters) if not args.graph else None,
+               gemm_impl=ops.GEMM_IMPL)
+    print(json.dumps(rec), flush=True)
+    if args.out:
+        with open(args.out, "a") as f:
+            f.write(json.dumps(rec) + "\n")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -208,6 +208,30 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_cache, const 
            "paged_attention");
 }
 
+// TMA-fed attention over the whole cache tensor kv: [pages, 2, layers, n_kv, page_size, head_dim].
+void paged_attention_tma(const Tensor& q, Tensor& out, const Tensor& kv, int layer,
+                         const Tensor& block_table, const Tensor& q_start, const Tensor& q_len,
+                         const Tensor& kv_len, const c10::optional<Tensor>& tile_seq,
+                         const c10::optional<Tensor>& tile_q0, const c10::optional<Tensor>& decode_seq,
+                         int n_q, int n_kv, int head_dim, double scale) {
+  need_cuda(q, "q");
+  TORCH_CHECK(kv.dim() == 6 && kv.is_contiguous() && kv.size(1) == 2 && kv.size(5) == head_dim,
+              "kv must be the contiguous 6-D cache tensor");
+  TORCH_CHECK(block_table.scalar_type() == at::kInt && block_table.dim() == 2, "block_table int32 2-D");
+  const int n_tiles = tile_seq.has_value() && tile_seq->defined() ? tile_seq->numel() : 0;
+  const int n_dec = decode_seq.has_value() && decode_seq->defined() ? decode_seq->numel() : 0;
+  const long long hd = head_dim;
+  check_rc(mb_paged_attention_tma(
+               q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv.data_ptr(), kv.numel() / hd,
+               layer * kv.stride(2) / hd, (layer * kv.stride(2) + kv.stride(1)) / hd, kv.stride(0) / hd,
+               block_table.data_ptr<int32_t>(), block_table.stride(0), q_start.data_ptr<int32_t>(),
+               q_len.data_ptr<int32_t>(), kv_len.data_ptr<int32_t>(),
+               static_cast<const int32_t*>(optptr(tile_seq)), static_cast<const int32_t*>(optptr(tile_q0)),
+               n_tiles, n_dec, static_cast<const int32_t*>(optptr(decode_seq)), n_q, n_kv, head_dim,
+               kv.size(4), scale, error_flag(), cur_stream()),
+           "paged_attention_tma");
+}
+
 void argmax(const Tensor& logits, Tensor& out) {
   need_cuda(logits, "logits");
   TORCH_CHECK(logits.scalar_type() == at::kFloat && out.scalar_type() == at::kLong, "argmax dtypes");
@@ -265,6 +289,11 @@ class PyDecoderExecutor {
     c.attn_scale = cfg["attn_scale"].cast<float>();
     c.logits_scale = 1.f;
     c.fuse_swiglu = cfg.contains("fuse_swiglu") ? cfg["fuse_swiglu"].cast<int>() : 1;
+    c.gemm_impl = cfg.contains("gemm_impl") ? cfg["gemm_impl"].cast<int>() : 0;
+    c.use_pdl = cfg.contains("use_pdl") ? cfg["use_pdl"].cast<int>() : 0;
+    c.attn_impl = cfg.contains("attn_impl") ? cfg["attn_impl"].cast<int>() : 1;
+    ex.buf.p_ws = nullptr;
+    ex.buf.p_counters = nullptr;
     c.num_sms = num_sms();
     ex.buf.err = error_flag();
   }
@@ -295,11 +324,13 @@ class PyDecoderExecutor {
     ex.kv.kv_stride = kv.stride(1);
     ex.kv.layer_stride = kv.stride(2);
     ex.kv.head_stride = kv.stride(3);
+    ex.kv.total_elems = kv.numel();
   }
   void set_buffers(const Tensor& h, const Tensor& xn, const Tensor& qkv, const Tensor& attn,
                    const Tensor& act, const c10::optional<Tensor>& gu, const Tensor& last_h,
                    const Tensor& last_xn, const Tensor& logits, const Tensor& sampled,
-                   const Tensor& workspace) {
+                   const Tensor& workspace, const c10::optional<Tensor>& p_ws,
+                   const c10::optional<Tensor>& p_counters) {
     auto& b = ex.buf;
     b.h = const_cast<void*>(hold(h)); b.xn = const_cast<void*>(hold(xn));
     b.qkv = const_cast<void*>(hold(qkv)); b.attn = const_cast<void*>(hold(attn));
@@ -311,6 +342,13 @@ class PyDecoderExecutor {
     b.sampled = static_cast<int64_t*>(const_cast<void*>(hold(sampled)));
     b.workspace = const_cast<void*>(hold(workspace));
     b.workspace_bytes = workspace.nbytes();
+    if (p_ws.has_value() && p_ws->defined() && p_counters.has_value() && p_counters->defined()) {
+      TORCH_CHECK(static_cast<size_t>(p_ws->nbytes()) >= mb_gemm_persistent_workspace_bytes(num_sms()) &&
+                      static_cast<size_t>(p_counters->numel()) >= mb_gemm_persistent_counter_ints(num_sms()),
+                  "persistent GEMM workspace too small");
+      b.p_ws = const_cast<void*>(hold(*p_ws));
+      b.p_counters = static_cast<int*>(const_cast<void*>(hold(*p_counters)));
+    }
   }
   // meta: one int32 device tensor holding every per-step array; offsets are in int32 units
   // (tokens and slots are int64 and 8-byte aligned inside it).
@@ -361,6 +399,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gather_rows", &gather_rows);
   m.def("rope_kv_store", &rope_kv_store);
   m.def("paged_attention", &paged_attention);
+  m.def("paged_attention_tma", &paged_attention_tma);
   m.def("argmax", &argmax);
   m.def("sample", &sample);
   m.def("apply_penalties", &apply_penalties);

@@ -66,6 +66,15 @@ int mb_paged_attention(const void* q, int ldq, void* out, int ldo, const void* k
                        int page_size, int64_t page_stride, int64_t head_stride, float scale,
                        cudaStream_t stream);
 
+// TMA-fed variant (attention_tma.cu): the KV allocation is addressed as [total_rows, head_dim].
+int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo, const void* kv_base,
+                           long long total_rows, long long k_off_rows, long long v_off_rows,
+                           long long page_rows, const int32_t* block_table, int bt_stride,
+                           const int32_t* q_start, const int32_t* q_len, const int32_t* kv_len,
+                           const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, int n_decode,
+                           const int32_t* decode_seq, int n_q, int n_kv, int head_dim, int page_size,
+                           float scale, int* err, cudaStream_t stream);
+
 // ---- sampling (sampling.cu) ----------------------------------------------------------------
 int mb_argmax(const float* logits, int64_t* out, int rows, int vocab, int ld, cudaStream_t stream);
 int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, int vocab, int ld,

@@ -18,6 +18,11 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
   const int q_dim = c.n_q * c.head_dim;
   auto gemm = [&](const void* X, const void* W, void* Y, const void* R, int M, int N, int K,
                   int ldx, int ldy, int flags) {
+    if (c.gemm_impl == 1 && buf.p_ws != nullptr) {
+      launches += 1;
+      return mb_gemm_bf16_persistent(X, W, Y, R, M, N, K, ldx, K, ldy, ldy, flags | (c.use_pdl ? 8 : 0),
+                                     0, 0, -1, buf.p_ws, buf.p_counters, buf.err, c.num_sms, stream);
+    }
     int bn, splits, stages;
     mb_gemm_bf16_plan(M, N, K, flags & 1, c.num_sms, &bn, &splits, &stages);
     if (static_cast<size_t>(splits) * M * N * sizeof(float) > buf.workspace_bytes) splits = 1;
@@ -44,12 +49,24 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
     MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kc, vc, T, c.n_q, c.n_kv,
                             c.head_dim, c.page_size, kv.page_stride, kv.head_stride,
                             c.rope_interleaved, stream));
-    MB_TRY(mb_paged_attention(buf.qkv, qkv_dim, buf.attn, q_dim, kc, vc, in.block_table,
-                              in.bt_stride, in.q_start, in.q_len, in.kv_len, in.tile_seq,
-                              in.tile_q0, in.n_tiles, in.n_decode, in.decode_seq, c.n_q, c.n_kv,
-                              c.head_dim, c.page_size, kv.page_stride, kv.head_stride,
-                              c.attn_scale, stream));
-    launches += 2 + (in.n_tiles > 0) + (in.n_decode > 0);
+    if (c.attn_impl == 1 && c.page_size % 64 == 0) {
+      const long long hd = c.head_dim;
+      MB_TRY(mb_paged_attention_tma(
+          buf.qkv, qkv_dim, buf.attn, q_dim, kv.base, kv.total_elems / hd,
+          static_cast<long long>(l) * kv.layer_stride / hd,
+          (static_cast<long long>(l) * kv.layer_stride + kv.kv_stride) / hd, kv.page_stride / hd,
+          in.block_table, in.bt_stride, in.q_start, in.q_len, in.kv_len, in.tile_seq, in.tile_q0,
+          in.n_tiles, in.n_decode, in.decode_seq, c.n_q, c.n_kv, c.head_dim, c.page_size,
+          c.attn_scale, buf.err, stream));
+      launches += 3;
+    } else {
+      MB_TRY(mb_paged_attention(buf.qkv, qkv_dim, buf.attn, q_dim, kc, vc, in.block_table,
+                                in.bt_stride, in.q_start, in.q_len, in.kv_len, in.tile_seq,
+                                in.tile_q0, in.n_tiles, in.n_decode, in.decode_seq, c.n_q, c.n_kv,
+                                c.head_dim, c.page_size, kv.page_stride, kv.head_stride,
+                                c.attn_scale, stream));
+      launches += 2 + (in.n_tiles > 0) + (in.n_decode > 0);
+    }
     MB_TRY(gemm(buf.attn, w.wo, buf.h, buf.h, T, c.hidden, q_dim, q_dim, c.hidden, 2));
     MB_TRY(mb_rmsnorm(buf.h, w.mlp_norm, buf.xn, T, c.hidden, c.hidden, c.hidden, c.eps,
                       c.norm_weight_offset, c.multiply_before_cast, stream));

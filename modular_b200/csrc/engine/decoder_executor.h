@@ -33,6 +33,9 @@ struct DecoderConfig {
   float attn_scale;
   float logits_scale;
   int fuse_swiglu;            // gate/up GEMM with SwiGLU epilogue
+  int gemm_impl;              // 0 = one CTA per tile (+split-K), 1 = persistent stream-K
+  int use_pdl;                // launch persistent GEMMs with programmatic dependent launch
+  int attn_impl;              // 0 = cp.async kernels, 1 = TMA-fed single-launch kernel (page_size % 64 == 0)
   int num_sms;
 };
 
@@ -49,6 +52,8 @@ struct DecoderBuffers {
   int64_t* sampled;  // [max_seqs] tokens sampled by the latest step (also next step's source)
   void* workspace;  // split-K partials
   size_t workspace_bytes;
+  void* p_ws;       // persistent GEMM partial-tile slots
+  int* p_counters;  // persistent GEMM tile counters (zeroed)
   int* err;
 };
 
@@ -58,6 +63,7 @@ struct KVCacheView {
   int64_t kv_stride;     // elements between the K and V planes of a page
   int64_t layer_stride;  // elements between layers inside a page
   int64_t head_stride;   // elements between KV heads (= page_size * head_dim)
+  int64_t total_elems;   // elements in the whole allocation
 };
 
 // Device-resident per-step metadata (one packed H2D copy per step).

@@ -1,0 +1,406 @@
+// Paged GQA flash attention fed by TMA, one launch for a whole ragged batch.
+//
+// Differences from attention.cu (which stays as the path for page sizes that are not a
+// multiple of 64):
+//   * K/V tiles (64 tokens) arrive through cp.async.bulk.tensor from a single 2-D tensor map
+//     laid over the whole KV allocation ([rows, head_dim], a (page, plane, layer, head) slice
+//     being `page_size` consecutive rows), 128-byte swizzled, into a 3-stage ring guarded by
+//     full/empty mbarriers. A dedicated producer warp walks the block table; the four
+//     compute warps never compute a global address for K or V and never hit a CTA barrier
+//     inside the loop.
+//   * prefill tiles and decode sequences are CTAs of the same grid (prefill first), so the
+//     compute-bound and the bandwidth-bound part of a mixed step overlap on the machine.
+//
+// Rows of the last tile that lie beyond kv_len are whatever the cache holds; they are masked
+// to -inf before the softmax. The cache is zero-initialised and only ever holds finite
+// values, which keeps 0 * garbage finite in the PV product.
+//
+// Reference counterpart: flash_attention_ragged over PagedKVCache
+// (max/kernels/src/nn/attention/gpu/nvidia/sm100/attention.mojo:62, load_warp.mojo).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../common/api.h"
+#include "../common/ptx.cuh"
+#include "gemm_common.h"
+
+namespace mb {
+namespace at2 {
+
+typedef __nv_bfloat16 bf16;
+constexpr int kStages = 3;
+constexpr int kThreads = 160;  // 4 compute warps + 1 producer warp
+
+struct Params {
+  const bf16* q;
+  bf16* out;
+  const int32_t* block_table;
+  const int32_t* q_start;
+  const int32_t* q_len;
+  const int32_t* kv_len;
+  const int32_t* tile_seq;
+  const int32_t* tile_q0;
+  const int32_t* decode_seq;
+  int* err;
+  int ldq, ldo, bt_stride, page_size, n_tiles;
+  long long k_off_rows, v_off_rows, page_rows;
+  float scale_log2;
+};
+
+struct Bars {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  int abort_word;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Q tile layout: [rows][HD] with 16-byte chunks XOR-swizzled by the low row bits.
+template <int HD>
+__device__ __forceinline__ int qswz(int row, int chunk) {
+  return row * HD + ((chunk ^ (row & 7)) << 3);
+}
+// K/V tile layout as written by TMA: HD/64 sub-tiles of [64 rows][64 dims], 128B swizzle.
+__device__ __forceinline__ int kvswz(int row, int chunk) {
+  return (chunk >> 3) * (64 * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+}
+
+// One online-softmax step of 16 packed query rows against NP*16 tokens starting at row
+// `tok_in_tile` of the K/V tile (global KV index kv0).
+template <int HD, int NP>
+__device__ __forceinline__ void process_block(const bf16* tK, const bf16* tV, int tok_in_tile, int kv0,
+                                              const uint32_t (&qf)[HD / 16][4], float (&o)[HD / 8][4],
+                                              float (&m)[2], float (&l)[2], const int (&limit)[2],
+                                              float scale_log2, int lane) {
+  constexpr int KS = HD / 16, DT = HD / 8;
+  const int mi = lane >> 3;
+  float sc[2 * NP][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NP; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+    for (int np = 0; np < NP; ++np) {
+      uint32_t b[4];
+      ldsm_x4(b, tK + kvswz(tok_in_tile + np * 16 + (mi >> 1) * 8 + (lane & 7), 2 * ks + (mi & 1)));
+      mma_bf16(sc[2 * np], qf[ks], b[0], b[1]);
+      mma_bf16(sc[2 * np + 1], qf[ks], b[2], b[3]);
+    }
+  }
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < 2 * NP; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int col = kv0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+      const int h = e >> 1;
+      const float v = col <= limit[h] ? sc[nt][e] * scale_log2 : -INFINITY;
+      sc[nt][e] = v;
+      mx[h] = fmaxf(mx[h], v);
+    }
+  }
+  float alpha[2], msafe[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    const float mn = fmaxf(m[h], mx[h]);
+    msafe[h] = mn == -INFINITY ? 0.f : mn;
+    alpha[h] = exp2f(m[h] - msafe[h]);
+    m[h] = mn;
+    l[h] *= alpha[h];
+  }
+#pragma unroll
+  for (int nt = 0; nt < 2 * NP; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float pv = exp2f(sc[nt][e] - msafe[e >> 1]);
+      sc[nt][e] = pv;
+      l[e >> 1] += pv;
+    }
+  }
+#pragma unroll
+  for (int dt = 0; dt < DT; ++dt) {
+    o[dt][0] *= alpha[0]; o[dt][1] *= alpha[0];
+    o[dt][2] *= alpha[1]; o[dt][3] *= alpha[1];
+  }
+#pragma unroll
+  for (int kk = 0; kk < NP; ++kk) {
+    uint32_t a[4];
+    a[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+    a[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+    a[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+    a[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+    for (int dp = 0; dp < DT / 2; ++dp) {
+      uint32_t b[4];
+      ldsm_x4_t(b, tV + kvswz(tok_in_tile + kk * 16 + (mi & 1) * 8 + (lane & 7), 2 * dp + (mi >> 1)));
+      mma_bf16(o[2 * dp], a, b[0], b[1]);
+      mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(kThreads)
+attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
+  constexpr int CH = HD / 8, KS = HD / 16, DT = HD / 8;
+  constexpr int kTileElems = 64 * HD;          // one K (or V) tile
+  constexpr uint32_t kStageBytes = 2 * kTileElems * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  bf16* sKV = reinterpret_cast<bf16*>(smem);                       // [stages][K tile | V tile]
+  bf16* sQ = sKV + kStages * 2 * kTileElems;                        // [64][HD]
+  Bars* bars = reinterpret_cast<Bars*>(sQ + 64 * HD);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kvh = blockIdx.y;
+  const bool is_prefill = static_cast<int>(blockIdx.x) < p.n_tiles;
+  const int seq = is_prefill ? p.tile_seq[blockIdx.x] : p.decode_seq[blockIdx.x - p.n_tiles];
+  const int tq0 = is_prefill ? p.tile_q0[blockIdx.x] : 0;
+  const int qs = p.q_start[seq], ql = p.q_len[seq], kl = p.kv_len[seq];
+  const int32_t* bt = p.block_table + static_cast<int64_t>(seq) * p.bt_stride;
+  int kv_hi = kl;
+  if (is_prefill) {
+    int last_tq = tq0 + 64 / G;
+    if (last_tq > ql) last_tq = ql;
+    kv_hi = kl - ql + last_tq;
+  }
+  const int ntiles = (kv_hi + 63) / 64;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 4);
+    }
+    bars->abort_word = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  volatile int* abort_word = &bars->abort_word;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmKV);
+      for (int t = 0; t < ntiles; ++t) {
+        const int s = t % kStages;
+        const uint32_t ph = (t / kStages) & 1;
+        if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_word, p.err, 301)) break;
+        const int tok0 = t * 64;
+        const long long row = static_cast<long long>(bt[tok0 / p.page_size]) * p.page_rows +
+                              static_cast<long long>(kvh) * p.page_size + (tok0 % p.page_size);
+        bf16* dK = sKV + s * 2 * kTileElems;
+        bf16* dV = dK + kTileElems;
+        mbar_arrive_expect_tx(&bars->full[s], kStageBytes);
+#pragma unroll
+        for (int sub = 0; sub < HD / 64; ++sub) {
+          tma_load_2d(dK + sub * 64 * 64, &tmKV, &bars->full[s], sub * 64,
+                      static_cast<int32_t>(p.k_off_rows + row));
+          tma_load_2d(dV + sub * 64 * 64, &tmKV, &bars->full[s], sub * 64,
+                      static_cast<int32_t>(p.v_off_rows + row));
+        }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------ compute warps
+  const int q_rows = is_prefill ? 64 : 16;
+  for (int idx = tid; idx < q_rows * CH; idx += 128) {
+    const int row = idx / CH, chunk = idx % CH;
+    const int tq = tq0 + row / G, head = kvh * G + row % G;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tq < ql)
+      v = *reinterpret_cast<const uint4*>(p.q + static_cast<int64_t>(qs + tq) * p.ldq + head * HD + chunk * 8);
+    *reinterpret_cast<uint4*>(sQ + qswz<HD>(row, chunk)) = v;
+  }
+  consumer_sync();
+  const int row_base = is_prefill ? warp * 16 : 0;   // this warp's 16 packed rows
+  uint32_t qf[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks)
+    ldsm_x4(qf[ks], sQ + qswz<HD>(row_base + (lane & 15), 2 * ks + (lane >> 4)));
+
+  float o[DT][4];
+#pragma unroll
+  for (int i = 0; i < DT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  int limit[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = row_base + (lane >> 2) + h * 8;
+    const int tq = tq0 + r / G;
+    limit[h] = tq < ql ? kl - ql + tq : -1;
+  }
+  for (int t = 0; t < ntiles; ++t) {
+    const int s = t % kStages;
+    const uint32_t ph = (t / kStages) & 1;
+    if (!mbar_wait(&bars->full[s], ph, abort_word, p.err, 302)) break;
+    const bf16* tK = sKV + s * 2 * kTileElems;
+    const bf16* tV = tK + kTileElems;
+    if (is_prefill) {
+      // every warp runs its 16 rows against all 64 tokens of the tile
+      process_block<HD, 4>(tK, tV, 0, t * 64, qf, o, m, l, limit, p.scale_log2, lane);
+    } else if (t * 64 + warp * 16 < kv_hi) {
+      // the 16 packed rows are shared; each warp takes 16 tokens of the tile
+      process_block<HD, 1>(tK, tV, warp * 16, t * 64 + warp * 16, qf, o, m, l, limit, p.scale_log2, lane);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bars->empty[s]);
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+  if (is_prefill) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+      const int r = row_base + (lane >> 2) + h * 8;
+      const int tq = tq0 + r / G, head = kvh * G + r % G;
+      if (tq < ql) {
+        bf16* orow = p.out + static_cast<int64_t>(qs + tq) * p.ldo + head * HD + 2 * (lane & 3);
+#pragma unroll
+        for (int dt = 0; dt < DT; ++dt)
+          *reinterpret_cast<uint32_t*>(orow + dt * 8) = pack_bf16(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
+      }
+    }
+    return;
+  }
+  // ---- decode: merge the four warps' partial states through shared memory
+  consumer_sync();  // every warp is done reading the K/V ring
+  float* mO = reinterpret_cast<float*>(sKV);   // [4][16][HD]
+  float* mM = mO + 4 * 16 * HD;                // [4][16]
+  float* mL = mM + 64;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = (lane >> 2) + h * 8;
+    if ((lane & 3) == 0) {
+      mM[warp * 16 + r] = m[h];
+      mL[warp * 16 + r] = l[h];
+    }
+#pragma unroll
+    for (int dt = 0; dt < DT; ++dt)
+      *reinterpret_cast<float2*>(mO + (warp * 16 + r) * HD + dt * 8 + 2 * (lane & 3)) =
+          make_float2(o[dt][2 * h], o[dt][2 * h + 1]);
+  }
+  consumer_sync();
+  {
+    const int r = tid >> 3;
+    const int tq = r / G, head = kvh * G + r % G;
+    if (tq < ql) {
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, mM[w * 16 + r]);
+      float wgt[4], L = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = mM[w * 16 + r];
+        wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+        L += wgt[w] * mL[w * 16 + r];
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* orow = p.out + static_cast<int64_t>(qs + tq) * p.ldo + head * HD;
+      constexpr int PER = HD / 8;
+      const int d0 = (tid & 7) * PER;
+#pragma unroll
+      for (int d = 0; d < PER; d += 2) {
+        float a = 0.f, b = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float2 v = *reinterpret_cast<const float2*>(mO + (w * 16 + r) * HD + d0 + d);
+          a += wgt[w] * v.x;
+          b += wgt[w] * v.y;
+        }
+        *reinterpret_cast<uint32_t*>(orow + d0 + d) = pack_bf16(a * inv, b * inv);
+      }
+    }
+  }
+}
+
+template <int HD, int G>
+static int launch(const CUtensorMap& tm, const Params& p, int n_ctas, int n_kv, cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(kStages) * 2 * 64 * HD * 2 + 64 * HD * 2 + sizeof(Bars) + 1024;
+  auto kern = attn_tma_kernel<HD, G>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess)
+      return MB_ERR_LAUNCH;
+    configured = true;
+  }
+  kern<<<dim3(n_ctas, n_kv), kThreads, smem, stream>>>(tm, p);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+}  // namespace at2
+}  // namespace mb
+
+using namespace mb;
+
+// kv_base: start of the KV allocation, viewed as [total_rows, head_dim] bf16. A token of page
+// `pg`, KV head `h`, offset `o` lives at row  k_off_rows (or v_off_rows) + pg*page_rows +
+// h*page_size + o. Requires page_size % 64 == 0.
+extern "C" int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo, const void* kv_base,
+                                      long long total_rows, long long k_off_rows, long long v_off_rows,
+                                      long long page_rows, const int32_t* block_table, int bt_stride,
+                                      const int32_t* q_start, const int32_t* q_len,
+                                      const int32_t* kv_len, const int32_t* tile_seq,
+                                      const int32_t* tile_q0, int n_tiles, int n_decode,
+                                      const int32_t* decode_seq, int n_q, int n_kv, int head_dim,
+                                      int page_size, float scale, int* err, cudaStream_t stream) {
+  using namespace mb::at2;
+  if (n_tiles <= 0 && n_decode <= 0) return MB_OK;
+  if (n_kv <= 0 || n_q % n_kv || page_size % 64 || total_rows >= (1ll << 31)) return MB_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(kv_base) & 15) return MB_ERR_ALIGN;
+  Params p;
+  p.q = static_cast<const bf16*>(q);
+  p.out = static_cast<bf16*>(out);
+  p.block_table = block_table;
+  p.q_start = q_start; p.q_len = q_len; p.kv_len = kv_len;
+  p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.decode_seq = decode_seq;
+  p.err = err;
+  p.ldq = ldq; p.ldo = ldo; p.bt_stride = bt_stride; p.page_size = page_size;
+  p.n_tiles = n_tiles < 0 ? 0 : n_tiles;
+  p.k_off_rows = k_off_rows; p.v_off_rows = v_off_rows; p.page_rows = page_rows;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  CUtensorMap tm;
+  const int rc = cached_tmap(&tm, kv_base, static_cast<uint64_t>(total_rows), head_dim, head_dim, 64, 2);
+  if (rc != MB_OK) return rc;
+  const int n_ctas = p.n_tiles + (n_decode < 0 ? 0 : n_decode);
+  const int G = n_q / n_kv;
+#define MB_ATTN2_CASE(HD_, G_) \
+  if (head_dim == HD_ && G == G_) return launch<HD_, G_>(tm, p, n_ctas, n_kv, stream);
+  MB_ATTN2_CASE(128, 1) MB_ATTN2_CASE(128, 2) MB_ATTN2_CASE(128, 4) MB_ATTN2_CASE(128, 8)
+  MB_ATTN2_CASE(128, 16)
+  MB_ATTN2_CASE(64, 1) MB_ATTN2_CASE(64, 2) MB_ATTN2_CASE(64, 4) MB_ATTN2_CASE(64, 8)
+  MB_ATTN2_CASE(64, 16)
+#undef MB_ATTN2_CASE
+  return MB_ERR_SHAPE;
+}

@@ -5,16 +5,19 @@
 //
 // Work is counted in units of one 64-wide K block of one 128(weight rows) x BN(tokens) tile.
 //
-//   mode 0 (round robin): CTA g owns whole tiles g, g+G, ... Concurrent CTAs then work on
-//       neighbouring tiles and share weight/activation tiles in L2. Used when there are
-//       many tiles per SM.
-//   mode 1 (stream-K): the unit range [0, tiles*kb) is cut into G equal contiguous shares,
-//       so every SM streams the same number of weight bytes no matter how the tile count
-//       divides the SM count - this is what keeps decode-sized GEMMs (a few dozen tiles)
-//       at HBM speed. A tile cut across CTAs is finished by whichever contributor arrives
-//       last: every contributor writes its fp32 partial to a private workspace slot, bumps
-//       a per-(tile, lane-quadrant) counter, and the last one sums the slots in CTA order
-//       (deterministic) and runs the fused epilogue. Nobody waits on anybody.
+// The schedule has two phases:
+//   phase 1 (round robin): the first `tiles_dp` tiles - a whole number of waves - go to CTAs
+//       as whole tiles g, g+G, ... Concurrent CTAs then work on neighbouring tiles and share
+//       weight/activation tiles in L2, and no tile needs a fix-up.
+//   phase 2 (stream-K): the K-block range of the remaining tiles (less than one wave) is cut
+//       into equal contiguous shares, so every SM streams the same number of weight bytes no
+//       matter how the tile count divides the SM count - this is what keeps decode-sized
+//       GEMMs (a few dozen tiles) busy on all 148 SMs. A tile cut across CTAs is finished by
+//       whichever contributor arrives last: every contributor writes its fp32 partial to a
+//       private workspace slot, bumps a per-(tile, lane-quadrant) counter, and the last one
+//       sums the slots in CTA order (deterministic) and runs the fused epilogue. Nobody
+//       waits on anybody.
+//   mode 0 = phase 1 only, mode 1 = phase 2 only, mode 2 = both (default).
 //
 // Warp roles: warp 0 TMA producer, warp 1 MMA issuer (tcgen05.mma, fp32 accumulate in
 // TMEM), warps 2-5 epilogue. Two accumulator buffers in TMEM let the epilogue of one
@@ -54,10 +57,13 @@ struct Params {
   int* counters;
   int* err;
   int M, N, K, ldy, ldr, dual_rows;
-  int BN, stages, acc_cols;
+  int BN, stages, acc_cols, nbufs;
   uint32_t tmem_cols;
-  int m_tiles, tiles, kb, mode;
-  long long units;
+  int m_tiles, tiles, kb;
+  int tiles_dp;      // tiles handled round-robin as whole tiles
+  int G2;            // CTAs taking part in the stream-K phase
+  int dbg;           // measurement aid: bit0 skip the fix-up reduction, bit1 skip the partial store too
+  long long units2;  // K blocks in the stream-K phase = (tiles - tiles_dp) * kb
 };
 
 struct Tail {
@@ -71,30 +77,37 @@ struct Tail {
 
 struct Seg {
   int tile, kb0, kb1, idx;
+  int slot;  // workspace slot (0/1) of this CTA when the segment is a partial tile
 };
 
 // Enumerates this CTA's segments; identical in every warp role.
 struct SegIter {
-  int mode, G, g, tiles, kb, idx, next_tile;
+  int G, g, kb, idx, next_tile, tiles_dp;
+  bool sk_first;
   long long u, u1;
   __device__ SegIter(const Params& p, int g_, int G_)
-      : mode(p.mode), G(G_), g(g_), tiles(p.tiles), kb(p.kb), idx(0), next_tile(g_) {
-    u = p.units * g_ / G_;
-    u1 = p.units * (g_ + 1) / G_;
+      : G(G_), g(g_), kb(p.kb), idx(0), next_tile(g_), tiles_dp(p.tiles_dp), sk_first(true) {
+    if (g_ < p.G2) {
+      u = p.units2 * g_ / p.G2;
+      u1 = p.units2 * (g_ + 1) / p.G2;
+    } else {
+      u = u1 = 0;
+    }
   }
   __device__ bool next(Seg& s) {
-    if (mode == 0) {
-      if (next_tile >= tiles) return false;
-      s.tile = next_tile; s.kb0 = 0; s.kb1 = kb; s.idx = idx++;
+    if (next_tile < tiles_dp) {
+      s.tile = next_tile; s.kb0 = 0; s.kb1 = kb; s.idx = idx++; s.slot = 0;
       next_tile += G;
       return true;
     }
     if (u >= u1) return false;
-    const int tile = static_cast<int>(u / kb);
-    const int kb0 = static_cast<int>(u - static_cast<long long>(tile) * kb);
+    const int rel = static_cast<int>(u / kb);
+    const int kb0 = static_cast<int>(u - static_cast<long long>(rel) * kb);
     long long len = kb - kb0;
     if (len > u1 - u) len = u1 - u;
-    s.tile = tile; s.kb0 = kb0; s.kb1 = kb0 + static_cast<int>(len); s.idx = idx++;
+    s.tile = tiles_dp + rel; s.kb0 = kb0; s.kb1 = kb0 + static_cast<int>(len); s.idx = idx++;
+    s.slot = sk_first ? 0 : 1;
+    sk_first = false;
     u += len;
     return true;
   }
@@ -220,8 +233,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
       int n = 0;
       bool ok = true;
       while (ok && it.next(s)) {
-        const int buf = s.idx & 1;
-        const uint32_t bph = (s.idx >> 1) & 1;
+        const int buf = s.idx % p.nbufs;
+        const uint32_t bph = (s.idx / p.nbufs) & 1;
         if (!mbar_wait(&tail->tmem_empty[buf], bph ^ 1, abort_word, p.err, 202)) break;
         tc_fence_after();
         const uint32_t acc = tmem_base + buf * p.acc_cols;
@@ -255,8 +268,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
     SegIter it(p, g, G);
     Seg s;
     while (it.next(s)) {
-      const int buf = s.idx & 1;
-      const uint32_t bph = (s.idx >> 1) & 1;
+      const int buf = s.idx % p.nbufs;
+      const uint32_t bph = (s.idx / p.nbufs) & 1;
       if (!mbar_wait(&tail->tmem_full[buf], bph, abort_word, p.err, 204)) break;
       tc_fence_after();
       const int n0 = (s.tile / p.m_tiles) * kBM;
@@ -290,7 +303,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
       }
       // ---- partial tile: publish, then maybe reduce
       const int row = quad * 32 + lane;
-      float* mine = p.ws + (static_cast<size_t>(g) * 2 + (s.idx == 0 ? 0 : 1)) * slot_floats;
+      if (p.dbg & 2) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
+        continue;
+      }
+      float* mine = p.ws + (static_cast<size_t>(g) * 2 + s.slot) * slot_floats;
       for (int c0 = 0; c0 < p.BN; c0 += 16) {
         if (t0 + c0 >= p.M) break;
         uint32_t a[16];
@@ -309,39 +328,100 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
-      const long long first_unit = static_cast<long long>(s.tile) * p.kb;
-      const int g_first = static_cast<int>(((first_unit + 1) * G - 1) / p.units);
-      const int g_last = static_cast<int>(((first_unit + p.kb) * G - 1) / p.units);
+      const long long first_unit = static_cast<long long>(s.tile - p.tiles_dp) * p.kb;
+      const int g_first = static_cast<int>(((first_unit + 1) * p.G2 - 1) / p.units2);
+      const int g_last = static_cast<int>(((first_unit + p.kb) * p.G2 - 1) / p.units2);
       __threadfence();
       __syncwarp();
       int old = 0;
-      if (lane == 0) old = atomicAdd(&p.counters[s.tile * 4 + quad], 1);
+      if (lane == 0) old = atomicAdd(&p.counters[(s.tile - p.tiles_dp) * 4 + quad], 1);
       old = __shfl_sync(0xffffffffu, old, 0);
       if (old != g_last - g_first) continue;  // someone else finishes this tile
+      if (p.dbg & 1) {
+        if (lane == 0) p.counters[(s.tile - p.tiles_dp) * 4 + quad] = 0;
+        continue;
+      }
       __threadfence();
-      for (int c0 = 0; c0 < p.BN; c0 += 16) {
-        if (t0 + c0 >= p.M) break;
-        float v[16], w[16];
+      // Vectorised reduction of this warp's 32 rows: a lane owns 4 consecutive rows (one float4
+      // per partial) and the warp covers 4 tokens per step, 16 per unrolled iteration, so the
+      // slots stream in with many independent 16-byte loads in flight.
+      {
+        const int rq = lane & 7;          // row quad inside the 32-row quadrant
+        const int tsub = lane >> 3;       // token inside a 4-token step
+        const int n = n_base + rq * 4;
+        const int n_contrib = g_last - g_first + 1;
+        const float* slots[8];
+        int nc = n_contrib < 8 ? n_contrib : 8;
+        for (int i = 0; i < nc; ++i) {
+          const int gc = g_first + i;
+          const long long b0 = p.units2 * gc / p.G2;
+          slots[i] = p.ws + (static_cast<size_t>(gc) * 2 + (b0 >= first_unit ? 0 : 1)) * slot_floats +
+                     quad * 32 + rq * 4;
+        }
+        int t_hi = p.M - t0;
+        if (t_hi > p.BN) t_hi = p.BN;
+        for (int tb = 0; tb < t_hi; tb += 16) {
+          float4 acc[4], acc2[4];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) { v[j] = 0.f; w[j] = 0.f; }
-        for (int gc = g_first; gc <= g_last; ++gc) {
-          const long long b0 = p.units * gc / G;
-          const float* src = p.ws + (static_cast<size_t>(gc) * 2 + (b0 >= first_unit ? 0 : 1)) * slot_floats;
+          for (int u = 0; u < 4; ++u) {
+            acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            acc2[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+          for (int i = 0; i < n_contrib; ++i) {
+            const float* src;
+            if (i < 8) {
+              src = slots[i];
+            } else {
+              const int gc = g_first + i;
+              const long long b0 = p.units2 * gc / p.G2;
+              src = p.ws + (static_cast<size_t>(gc) * 2 + (b0 >= first_unit ? 0 : 1)) * slot_floats +
+                    quad * 32 + rq * 4;
+            }
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + static_cast<size_t>(c0 + j) * kBM + row);
-          if (DUAL) {
+            for (int u = 0; u < 4; ++u) {
+              const int tl = tb + u * 4 + tsub;
+              if (tl < t_hi) {
+                const float4 x = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(tl) * kBM));
+                acc[u].x += x.x; acc[u].y += x.y; acc[u].z += x.z; acc[u].w += x.w;
+                if (DUAL) {
+                  const float4 y = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(p.BN + tl) * kBM));
+                  acc2[u].x += y.x; acc2[u].y += y.y; acc2[u].z += y.z; acc2[u].w += y.w;
+                }
+              }
+            }
+          }
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              w[j] += __ldcg(src + static_cast<size_t>(p.BN + c0 + j) * kBM + row);
+          for (int u = 0; u < 4; ++u) {
+            const int tl = tb + u * 4 + tsub;
+            const int t = t0 + tl;
+            if (tl >= t_hi || n >= p.N) continue;
+            float4 r = acc[u];
+            if (DUAL) {
+              r.x = silu_f(r.x) * acc2[u].x; r.y = silu_f(r.y) * acc2[u].y;
+              r.z = silu_f(r.z) * acc2[u].z; r.w = silu_f(r.w) * acc2[u].w;
+            }
+            if (EPI == EPI_F32) {
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.Y) + static_cast<size_t>(t) * p.ldy + n) = r;
+            } else {
+              __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+              if (EPI == EPI_RESID) {
+                const uint2 rv = *reinterpret_cast<const uint2*>(p.R + static_cast<size_t>(t) * p.ldr + n);
+                const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rv);
+                float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(rb[0]);
+                lo = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+                a = __bfloat1622float2(hi); b = __bfloat1622float2(rb[1]);
+                hi = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+              }
+              uint2 o2;
+              o2.x = *reinterpret_cast<uint32_t*>(&lo);
+              o2.y = *reinterpret_cast<uint32_t*>(&hi);
+              *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.Y) + static_cast<size_t>(t) * p.ldy + n) = o2;
+            }
           }
         }
-        if (DUAL) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = silu_f(v[j]) * w[j];
-        }
-        store_chunk<EPI>(v, p, t0, c0, n_base, lane, stg);
       }
-      if (lane == 0) p.counters[s.tile * 4 + quad] = 0;  // ready for the next launch
+      __syncwarp();
+      if (lane == 0) p.counters[(s.tile - p.tiles_dp) * 4 + quad] = 0;  // ready for the next launch
     }
   }
 
@@ -412,7 +492,7 @@ extern "C" int mb_gemm_bf16_persistent(const void* X, const void* W, void* Y, co
     return MB_ERR_ALIGN;
   if (dual && f32) return MB_ERR_SHAPE;
   if (num_sms <= 0) num_sms = 148;
-  const int max_bn = dual ? 128 : 256;
+  const int max_bn = 256;
   if (bn <= 0) {
     const int mt = (M + max_bn - 1) / max_bn;
     bn = ((M + mt - 1) / mt + 15) / 16 * 16;
@@ -424,7 +504,8 @@ extern "C" int mb_gemm_bf16_persistent(const void* X, const void* W, void* Y, co
   p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.ldr = ldr; p.dual_rows = N;
   p.BN = bn;
   p.acc_cols = bn * (dual ? 2 : 1);
-  p.tmem_cols = pow2_cols(2 * p.acc_cols);
+  p.nbufs = 2 * p.acc_cols <= 512 ? 2 : 1;  // double-buffer the accumulators when TMEM allows
+  p.tmem_cols = pow2_cols(p.nbufs * p.acc_cols);
   if (p.tmem_cols > 512) return MB_ERR_SHAPE;
   const int stage_bytes = kATile * (dual ? 2 : 1) + bn * kBK * 2;
   const int max_stages = (227 * 1024 - 1024 - 4 * kStgWarp - 512) / stage_bytes;
@@ -436,20 +517,31 @@ extern "C" int mb_gemm_bf16_persistent(const void* X, const void* W, void* Y, co
   const int n_tiles = (N + kBM - 1) / kBM;
   p.tiles = p.m_tiles * n_tiles;
   p.kb = (K + kBK - 1) / kBK;
-  p.units = static_cast<long long>(p.tiles) * p.kb;
-  int mode = p.tiles >= 4 * num_sms ? 0 : 1;
-  if (force_mode == 0 || force_mode == 1) mode = force_mode;
-  if (mode == 1 && (ws == nullptr || counters == nullptr || p.tiles * 4 > static_cast<int>(mb_gemm_persistent_counter_ints(num_sms))))
-    mode = 0;
-  p.mode = mode;
-  int grid;
+  // mode 2: whole waves round robin, the remainder stream-K; with many waves the remainder is
+  // not worth a fix-up pass.
+  int mode = p.tiles >= 8 * num_sms ? 0 : 2;
+  p.dbg = force_mode >= 0 ? (force_mode >> 4) & 3 : 0;
+  if (force_mode >= 0 && (force_mode & 15) <= 2) mode = force_mode & 15;
+  const bool sk_ok = ws != nullptr && counters != nullptr;
+  if (!sk_ok) mode = 0;
+  int grid = num_sms;
   if (mode == 0) {
-    grid = p.tiles < num_sms ? p.tiles : num_sms;
+    p.tiles_dp = p.tiles;
+  } else if (mode == 1) {
+    p.tiles_dp = 0;
   } else {
-    long long g = p.units / 4;  // at least four K blocks per CTA
-    if (g < 1) g = 1;
-    grid = g < num_sms ? static_cast<int>(g) : num_sms;
+    p.tiles_dp = p.tiles / num_sms * num_sms;
   }
+  const int rest = p.tiles - p.tiles_dp;
+  if (rest * 4 > static_cast<int>(mb_gemm_persistent_counter_ints(num_sms))) return MB_ERR_TOO_LARGE;
+  p.units2 = static_cast<long long>(rest) * p.kb;
+  long long g2 = p.units2 / 4;  // at least four K blocks per stream-K share
+  if (g2 > num_sms) g2 = num_sms;
+  if (rest > 0 && g2 < 1) g2 = 1;
+  p.G2 = static_cast<int>(g2);
+  if (p.tiles_dp == 0) grid = p.G2;
+  else if (p.tiles < num_sms) grid = p.tiles;
+  if (grid < 1) grid = 1;
   CUtensorMap tw, tx;
   int rc = cached_tmap(&tw, W, dual ? 2 * N : N, K, ldw, kBM, 2);
   if (rc != MB_OK) return rc;

@@ -18,6 +18,7 @@ attention_with_rope.py:498-557 and nn/linear.py:1037-1084.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -229,7 +230,10 @@ class Llama3Model:
             n_layers=c.num_hidden_layers, hidden=c.hidden_size, n_q=c.num_attention_heads,
             n_kv=c.num_key_value_heads, head_dim=c.head_dim, inter=c.intermediate_size,
             vocab=c.vocab_size, eps=c.rms_norm_eps, page_size=self.page_size,
-            attn_scale=self.scale, fuse_swiglu=int(self.fuse_swiglu)))
+            attn_scale=self.scale, fuse_swiglu=int(self.fuse_swiglu),
+            gemm_impl=1 if ops.GEMM_IMPL == "persistent" else 0,
+            use_pdl=int(os.environ.get("MB200_PDL", "0")),
+            attn_impl=int(os.environ.get("MB200_ATTN_TMA", "1"))))
         ex.set_globals(self.w.embed, self.w.final_norm, self.w.lm_head, self.cos_sin)
         for l in self.w.layers:
             ex.add_layer(l.attn_norm, l.wqkv, l.wo, l.mlp_norm, l.wgu, l.wd)
@@ -245,7 +249,8 @@ class Llama3Model:
             last_h=mk(B, c.hidden_size), last_xn=mk(B, c.hidden_size))
         b = self._bufs
         ex.set_buffers(b["h"], b["xn"], b["qkv"], b["attn"], b["act"], b["gu"], b["last_h"],
-                       b["last_xn"], self.logits_buf, self.sampled, ops.gemm_workspace(dev))
+                       b["last_xn"], self.logits_buf, self.sampled, ops.gemm_workspace(dev),
+                       *ops.persistent_gemm_workspace(dev))
         self.executor = ex
 
     def forward_packed(self, meta: torch.Tensor, offsets: dict, T: int, B: int, bt_stride: int,

@@ -179,8 +179,13 @@ def build_attention_plan(q_lens, n_q: int, n_kv: int):
 
 
 def paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, n_q, n_kv,
-                    head_dim, scale, plan=None, out=None):
-    """Ragged causal attention. q: [T, ld] with the n_q*head_dim query columns first."""
+                    head_dim, scale, plan=None, out=None, kv=None, layer=0):
+    """Ragged causal attention. q: [T, ld] with the n_q*head_dim query columns first.
+
+    ``k_cache`` / ``v_cache`` are one layer's views ``[pages, n_kv, page, head_dim]``. When the
+    whole cache tensor ``kv`` (6-D) and ``layer`` are given and the page size is a multiple of
+    64, the TMA-fed single-launch kernel runs; otherwise the cp.async kernels.
+    """
     if not q.is_cuda or q.dtype != torch.bfloat16:
         return ref.paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, kv_len,
                                    n_q, n_kv, head_dim, scale)
@@ -189,8 +194,12 @@ def paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, n_
         plan = tuple(torch.from_numpy(a).to(q.device) if a.size else None for a in (ts, t0, ds))
     if out is None:
         out = torch.empty(q.shape[0], n_q * head_dim, dtype=q.dtype, device=q.device)
-    _lib().paged_attention(q, out, k_cache, v_cache, block_table, q_start, q_len, kv_len,
-                           plan[0], plan[1], plan[2], n_q, n_kv, head_dim, scale)
+    if kv is not None and kv.shape[4] % 64 == 0 and os.environ.get("MB200_ATTN_TMA", "1") == "1":
+        _lib().paged_attention_tma(q, out, kv, layer, block_table, q_start, q_len, kv_len,
+                                   plan[0], plan[1], plan[2], n_q, n_kv, head_dim, scale)
+    else:
+        _lib().paged_attention(q, out, k_cache, v_cache, block_table, q_start, q_len, kv_len,
+                               plan[0], plan[1], plan[2], n_q, n_kv, head_dim, scale)
     return out
 
 

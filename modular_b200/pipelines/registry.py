@@ -1,0 +1,175 @@
+"""Architecture registry and pipeline factory.
+
+``PIPELINE_REGISTRY.retrieve_factory(pipeline_config)`` returns ``(tokenizer, factory)`` where
+``factory()`` builds the ready-to-run pipeline (weights loaded, KV cache allocated, graphs
+captured). Building is deferred so the API process can construct the tokenizer while the
+model worker process runs the factory. Reference: max/python/max/pipelines/lib/registry.py:330
+(``retrieve_factory`` :649, memory plan :731, factory :901) and lib/arch_lookup.py:70
+``SupportedArchitecture``.
+"""
+
+from __future__ import annotations
+
+import functools
+from dataclasses import dataclass, field
+from typing import Any, Callable, Optional
+
+import torch
+
+from .config import PipelineConfig
+from .memory_estimation import MemoryEstimator, MemoryPlan
+from .tokenizer import PipelineTokenizer, load_tokenizer
+from .weights import load_hf_config, load_state_dict, parse_quant_config
+
+
+@dataclass
+class SupportedArchitecture:
+    name: str                                  # HF architecture string, e.g. "LlamaForCausalLM"
+    config_class: Any
+    weights_class: Any
+    model_class: Any
+    default_encoding: str = "bfloat16"
+    supported_encodings: tuple = ("bfloat16", "float32")
+    example_repo_ids: tuple = ()
+    task: str = "text_generation"
+    preset_configs: dict = field(default_factory=dict)   # name -> callable returning a config
+
+
+class PipelineRegistry:
+    def __init__(self):
+        self.architectures: dict[str, SupportedArchitecture] = {}
+        self._lazy: list[Callable[[], None]] = []
+
+    def register(self, arch: SupportedArchitecture, allow_override: bool = False) -> None:
+        if arch.name in self.architectures and not allow_override:
+            raise ValueError(f"architecture {arch.name} is already registered")
+        self.architectures[arch.name] = arch
+
+    def register_lazy(self, fn: Callable[[], None]) -> None:
+        self._lazy.append(fn)
+
+    def _materialise(self) -> None:
+        while self._lazy:
+            self._lazy.pop(0)()
+
+    def list_architectures(self) -> list[SupportedArchitecture]:
+        self._materialise()
+        return sorted(self.architectures.values(), key=lambda a: a.name)
+
+    def retrieve_architecture(self, hf_config: dict) -> SupportedArchitecture:
+        self._materialise()
+        for name in hf_config.get("architectures", []):
+            if name in self.architectures:
+                return self.architectures[name]
+        raise ValueError(f"no registered architecture among {hf_config.get('architectures')}; "
+                         f"known: {sorted(self.architectures)}")
+
+    # ------------------------------------------------------------ config resolution
+    def resolve_model(self, pc: PipelineConfig):
+        """Returns (arch, model config object, hf config dict)."""
+        self._materialise()
+        m = pc.model
+        if m.model_path.startswith("preset:"):
+            preset = m.model_path.split(":", 1)[1]
+            for arch in self.architectures.values():
+                if preset in arch.preset_configs:
+                    cfg = arch.preset_configs[preset]()
+                    return arch, cfg, cfg.to_hf()
+            raise ValueError(f"unknown preset {preset!r}")
+        hf = load_hf_config(m.model_path)
+        arch = self.retrieve_architecture(hf)
+        return arch, arch.config_class.from_hf(hf), hf
+
+    def retrieve_tokenizer(self, pc: PipelineConfig, vocab_size: int = 258) -> PipelineTokenizer:
+        path = "" if pc.model.model_path.startswith("preset:") else pc.model.model_path
+        return load_tokenizer(path, vocab_size, pc.model.trust_remote_code)
+
+    def plan_memory(self, pc: PipelineConfig, cfg, device: torch.device) -> Optional[MemoryPlan]:
+        if device.type != "cuda":
+            return None
+        from ..kv_cache import KVCacheParams
+
+        dtype_bytes = 2
+        kvp = KVCacheParams(cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.head_dim,
+                            pc.model.kv_cache.kv_cache_page_size)
+        free, total = torch.cuda.mem_get_info(device)
+        act = MemoryEstimator.activation_bytes(cfg.hidden_size, cfg.q_dim, cfg.kv_dim, cfg.intermediate_size,
+                                               cfg.vocab_size, pc.runtime.max_batch_input_tokens,
+                                               pc.runtime.max_batch_size or 256, dtype_bytes)
+        return MemoryEstimator.plan_from_sizes(
+            free, total, cfg.param_count() * dtype_bytes, act, kvp.bytes_per_page, kvp.page_size,
+            pc.model.kv_cache.device_memory_utilization, 0, pc.runtime.max_batch_size,
+            pc.model.max_length, cfg.max_position_embeddings)
+
+    # ------------------------------------------------------------ factory
+    def retrieve_factory(self, pc: PipelineConfig):
+        pc.resolve()
+        arch, cfg, hf = self.resolve_model(pc)
+        tokenizer = self.retrieve_tokenizer(pc, cfg.vocab_size)
+        factory = functools.partial(self._build, pc, arch, cfg, hf, tokenizer)
+        return tokenizer, factory
+
+    def retrieve(self, pc: PipelineConfig):
+        tokenizer, factory = self.retrieve_factory(pc)
+        return tokenizer, factory()
+
+    def _build(self, pc: PipelineConfig, arch: SupportedArchitecture, cfg, hf: dict, tokenizer):
+        from ..entrypoints.llm import LLM
+
+        m, rt = pc.model, pc.runtime
+        on_gpu = m.uses_gpu and torch.cuda.is_available()
+        device = torch.device(f"cuda:{m.device_ids[0]}" if on_gpu else "cpu")
+        enc = m.quantization_encoding or (arch.default_encoding if on_gpu else "float32")
+        dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}.get(enc)
+        if dtype is None:
+            raise ValueError(f"encoding {enc!r} is not supported by {arch.name} (supported: {arch.supported_encodings})")
+        quant = parse_quant_config(hf)
+        if quant is not None and not quant.is_blockscaled_fp8:
+            raise ValueError(f"quantisation format {quant.format!r} is not supported yet")
+        if m.random_weights or m.model_path.startswith("preset:"):
+            weights = None
+        else:
+            sd = load_state_dict(m.model_path, m.weight_path)
+            weights = arch.weights_class.from_state_dict(cfg, sd.to_dict(), device, dtype)
+        plan = self.plan_memory(pc, cfg, device) if on_gpu else None
+        max_length = min(m.max_length or cfg.max_position_embeddings, cfg.max_position_embeddings)
+        if plan is not None:
+            max_length = min(max_length, plan.max_length)
+        max_bs = rt.max_batch_size or (plan.max_batch_size if plan else 8)
+        llm = LLM(cfg, weights, device=str(device), dtype=dtype, max_length=max_length,
+                  max_batch_size=max_bs, max_batch_input_tokens=rt.max_batch_input_tokens,
+                  page_size=m.kv_cache.kv_cache_page_size,
+                  device_memory_utilization=m.kv_cache.device_memory_utilization,
+                  num_kv_pages=None if on_gpu else max(64, max_bs * ((max_length + m.kv_cache.kv_cache_page_size - 1)
+                                                                     // m.kv_cache.kv_cache_page_size) + 1),
+                  enable_prefix_caching=m.kv_cache.enable_prefix_caching,
+                  enable_chunked_prefill=rt.enable_chunked_prefill,
+                  enable_in_flight_batching=rt.enable_in_flight_batching,
+                  enable_overlap_scheduler=rt.enable_overlap_scheduler,
+                  device_graph_capture=bool(rt.device_graph_capture),
+                  graph_batch_sizes=[b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256)
+                                     if b <= min(max_bs, rt.max_graph_capture_batch_size)],
+                  eos_token_ids=tokenizer.eos_token_ids)
+        llm.tokenizer = tokenizer
+        llm.pipeline_config = pc
+        llm.memory_plan = plan
+        return llm
+
+
+PIPELINE_REGISTRY = PipelineRegistry()
+
+
+def _register_builtin() -> None:
+    from ..models.llama3 import Llama3Config, Llama3Model, Llama3Weights
+
+    llama = SupportedArchitecture(
+        name="LlamaForCausalLM", config_class=Llama3Config, weights_class=Llama3Weights,
+        model_class=Llama3Model, default_encoding="bfloat16",
+        supported_encodings=("bfloat16", "float32", "float8_e4m3fn"),
+        example_repo_ids=("meta-llama/Llama-3.1-8B-Instruct", "meta-llama/Llama-3.3-70B-Instruct"),
+        preset_configs={"llama3.1-8b": Llama3Config.llama31_8b, "llama3.3-70b": Llama3Config.llama33_70b,
+                        "tiny-llama": Llama3Config.tiny})
+    PIPELINE_REGISTRY.register(llama, allow_override=True)
+
+
+PIPELINE_REGISTRY.register_lazy(_register_builtin)

@@ -1,0 +1,189 @@
+"""FastAPI application and its lifespan.
+
+``fastapi_app(settings, pipeline_config, tokenizer, factory)`` builds the app; its lifespan
+starts the model worker process (``subprocess_manager``), wires the ZMQ queues into a
+``ModelWorkerProxy`` and a ``TokenGeneratorPipeline`` and tears everything down on exit. A
+worker that dies takes the server down with it (the watcher task is awaited next to uvicorn).
+Reference: max/python/max/serve/api_server.py:110 (lifespan), :330 (``fastapi_app``), :389
+(``/reset_prefix_cache``), :307 (``RequestQueueFull`` -> 429).
+"""
+
+from __future__ import annotations
+
+import asyncio
+import contextlib
+import logging
+import queue
+import time
+import uuid
+from typing import Callable, Optional
+
+from fastapi import FastAPI, Request
+from fastapi.exceptions import RequestValidationError
+from fastapi.responses import JSONResponse, Response
+from starlette.exceptions import HTTPException as StarletteHTTPException
+
+from .. import __version__
+from .config import Settings
+from .model_worker import model_worker_main
+from .pipelines.llm import TokenGeneratorPipeline
+from .process_control import SubprocessExit, subprocess_manager
+from .router import openai_routes
+from .router.openai_routes import error_response
+from .telemetry.metrics import METRICS, configure_metrics
+from .worker_interface import ModelWorkerProxy, RequestQueueFull, WorkerQueues, ZmqQueueSpec
+
+logger = logging.getLogger("modular_b200.serve")
+
+
+class _Rpc:
+    """API-side end of the worker side channel."""
+
+    def __init__(self, req: ZmqQueueSpec, resp: ZmqQueueSpec):
+        self.req = req.push(bind=False)
+        self.resp = resp.pull(bind=True)
+        self.lock = asyncio.Lock()
+
+    async def call(self, name: str, arg=None, timeout_s: float = 10.0):
+        async with self.lock:
+            self.req.put_nowait((name, arg))
+            t0 = time.monotonic()
+            while time.monotonic() - t0 < timeout_s:
+                try:
+                    got, ok, val = self.resp.get_nowait()
+                except queue.Empty:
+                    await asyncio.sleep(0.005)
+                    continue
+                if got == name:
+                    if not ok:
+                        raise RuntimeError(val)
+                    return val
+            raise TimeoutError(f"worker RPC {name} timed out")
+
+
+def make_lifespan(settings: Settings, pipeline_config, tokenizer, factory: Callable, model_name: str,
+                  max_length: int):
+    @contextlib.asynccontextmanager
+    async def lifespan(app: FastAPI):
+        specs = {k: ZmqQueueSpec.create(k) for k in ("request", "response", "cancel", "rpc_req", "rpc_resp")}
+        response_pull = specs["response"].pull(bind=True)
+        rpc_resp_pull_spec = specs["rpc_resp"]
+        async with subprocess_manager(
+                "model-worker", model_worker_main, (factory, pipeline_config, specs, settings),
+                ready_timeout_s=settings.mw_timeout_s, use_heartbeat=settings.use_heartbeat,
+                health_fail_s=settings.mw_health_fail_s) as (pm, watcher):
+            queues = WorkerQueues(request=specs["request"].push(bind=False), response=response_pull,
+                                  cancel=specs["cancel"].push(bind=False))
+            proxy = ModelWorkerProxy(queues, settings.max_queue_size)
+            proxy.start()
+            app.state.pipeline = TokenGeneratorPipeline(model_name, tokenizer, proxy, max_length,
+                                                        settings.stream_min_chunk_tokens)
+            app.state.rpc = _Rpc(specs["rpc_req"], rpc_resp_pull_spec)
+            app.state.worker_watcher = watcher
+            app.state.proxy = proxy
+            logger.info("server ready: model %s", model_name)
+            try:
+                yield
+            finally:
+                await proxy.stop()
+                app.state.pipeline = None
+    return lifespan
+
+
+def fastapi_app(settings: Settings, pipeline_config=None, tokenizer=None, factory: Optional[Callable] = None,
+                model_name: str = "model", max_length: int = 4096, lifespan=None) -> FastAPI:
+    configure_metrics(settings.metric_recording.value)
+    if lifespan is None:
+        lifespan = make_lifespan(settings, pipeline_config, tokenizer, factory, model_name, max_length)
+    app = FastAPI(title="modular_b200 serve", version=__version__, lifespan=lifespan)
+    app.state.pipeline = None
+    app.state.model_names = {model_name}
+    app.state.structured_output = bool(pipeline_config and pipeline_config.sampling.enable_structured_output)
+    app.state.settings = settings
+
+    @app.middleware("http")
+    async def request_id_middleware(request: Request, call_next):
+        rid = request.headers.get("x-request-id") or uuid.uuid4().hex
+        request.state.request_id = rid
+        resp = await call_next(request)
+        resp.headers["x-request-id"] = rid
+        return resp
+
+    @app.exception_handler(RequestQueueFull)
+    async def _queue_full(_r: Request, exc: RequestQueueFull):
+        return error_response(429, str(exc), "rate_limit_error")
+
+    @app.exception_handler(StarletteHTTPException)
+    async def _http_exc(_r: Request, exc: StarletteHTTPException):
+        kind = {404: "not_found_error", 429: "rate_limit_error", 503: "service_unavailable"}.get(exc.status_code, "invalid_request_error")
+        return error_response(exc.status_code, str(exc.detail), kind)
+
+    @app.exception_handler(RequestValidationError)
+    async def _validation(_r: Request, exc: RequestValidationError):
+        first = exc.errors()[0] if exc.errors() else {}
+        loc = ".".join(str(x) for x in first.get("loc", []) if x != "body")
+        return error_response(400, f"{loc}: {first.get('msg', 'invalid request')}" if loc else str(exc))
+
+    @app.exception_handler(Exception)
+    async def _unhandled(_r: Request, exc: Exception):
+        METRICS.request_errors.inc()
+        logger.exception("unhandled error")
+        return error_response(500, f"{type(exc).__name__}: {exc}", "server_error")
+
+    @app.get("/health")
+    async def health():
+        if app.state.pipeline is None:
+            return JSONResponse(status_code=503, content={"status": "starting"})
+        return {"status": "ok"}
+
+    @app.get("/version")
+    async def version():
+        return {"version": __version__}
+
+    @app.get("/metrics")
+    async def metrics():
+        return Response(METRICS.render(), media_type="text/plain; version=0.0.4")
+
+    @app.post("/reset_prefix_cache")
+    async def reset_prefix_cache():
+        ok = await app.state.rpc.call("reset_prefix_cache")
+        return {"success": bool(ok)}
+
+    @app.get("/max_internal/worker_stats")
+    async def worker_stats():
+        return await app.state.rpc.call("stats")
+
+    app.include_router(openai_routes.router)
+    return app
+
+
+async def serve_until_done(app: FastAPI, settings: Settings) -> None:
+    """Run uvicorn; if the worker watcher fails first, stop the server and re-raise."""
+    import uvicorn
+
+    config = uvicorn.Config(app, host=settings.host, port=settings.port, log_level=settings.log_level.lower(),
+                            lifespan="on")
+    server = uvicorn.Server(config)
+    serve_task = asyncio.create_task(server.serve())
+
+    async def watch():
+        while getattr(app.state, "worker_watcher", None) is None and not serve_task.done():
+            await asyncio.sleep(0.1)
+        w = getattr(app.state, "worker_watcher", None)
+        if w is not None:
+            try:
+                await w
+            except asyncio.CancelledError:
+                return
+            except SubprocessExit:
+                server.should_exit = True
+                raise
+
+    watch_task = asyncio.create_task(watch())
+    done, _ = await asyncio.wait({serve_task, watch_task}, return_when=asyncio.FIRST_COMPLETED)
+    server.should_exit = True
+    await serve_task
+    watch_task.cancel()
+    for t in done:
+        if t is watch_task and t.exception() is not None:
+            raise t.exception()

@@ -1,0 +1,100 @@
+"""Model worker: the process that owns the GPU and runs the scheduler loop.
+
+Start-up: configure logging, run the pipeline factory (weights, KV cache, CUDA graphs), build
+the scheduler on ZMQ queues, freeze the GC, signal readiness; then ``run_iteration`` forever,
+beating a heartbeat every loop and backing off while idle. Reference:
+max/python/max/serve/pipelines/model_worker.py:213 (factory :306, warm-up :351, scheduler :407,
+gc freeze :472, loop :497-524), ``start_model_worker`` :579.
+"""
+
+from __future__ import annotations
+
+import gc
+import logging
+import os
+import time
+import traceback
+from typing import Callable, Optional
+
+from .scheduler import SchedulerProgress, TokenGenerationScheduler, TokenGenerationSchedulerConfig
+from .worker_interface import WorkerQueues, ZmqQueueSpec
+
+logger = logging.getLogger("modular_b200.serve.model_worker")
+
+
+class _SideChannel:
+    """Small request/response RPC served once per loop (reset prefix cache, stats)."""
+
+    def __init__(self, req_spec: ZmqQueueSpec, resp_spec: ZmqQueueSpec):
+        self.req = req_spec.pull(bind=True)
+        self.resp = resp_spec.push(bind=False)
+
+    def service(self, handlers: dict) -> None:
+        import queue
+
+        while True:
+            try:
+                name, arg = self.req.get_nowait()
+            except queue.Empty:
+                return
+            try:
+                self.resp.put_nowait((name, True, handlers[name](arg)))
+            except Exception as e:  # noqa: BLE001
+                self.resp.put_nowait((name, False, repr(e)))
+
+
+def scheduler_config_from(pipeline_config, llm) -> TokenGenerationSchedulerConfig:
+    rt = pipeline_config.runtime
+    return TokenGenerationSchedulerConfig(
+        max_batch_size=llm.sched_config.max_batch_size if llm is not None else (rt.max_batch_size or 64),
+        target_tokens_per_batch_ce=rt.max_batch_input_tokens,
+        max_seq_len=llm.max_length if llm is not None else 1 << 20,
+        enable_chunked_prefill=rt.enable_chunked_prefill,
+        enable_in_flight_batching=rt.enable_in_flight_batching,
+        kv_lookahead_tokens=1 if rt.enable_overlap_scheduler else 0)
+
+
+def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, settings,
+                      ready_event, alive_event, stop_event) -> None:
+    """Entry point of the spawned process."""
+    logging.basicConfig(level=getattr(logging, str(settings.log_level).upper(), logging.INFO),
+                        format=f"%(asctime)s {settings.log_prefix or 'worker'} %(levelname)s %(name)s: %(message)s")
+    try:
+        t0 = time.perf_counter()
+        built = factory()
+        llm = None
+        if hasattr(built, "pipeline"):          # an LLM facade from the registry
+            llm, pipeline, kv = built, built.pipeline, built.kv
+        else:                                    # a bare pipeline (echo)
+            pipeline, kv = built, getattr(built, "kv", None)
+        queues = WorkerQueues(request=queue_specs["request"].pull(bind=True),
+                              response=queue_specs["response"].push(bind=False),
+                              cancel=queue_specs["cancel"].pull(bind=True))
+        side = _SideChannel(queue_specs["rpc_req"], queue_specs["rpc_resp"])
+        cfg = scheduler_config_from(pipeline_config, llm)
+        sched = TokenGenerationScheduler(cfg, pipeline, kv, queues.request, queues.response, queues.cancel)
+        handlers = {
+            "reset_prefix_cache": lambda _a: bool(kv.reset_prefix_cache()) if kv is not None else False,
+            "stats": lambda _a: {
+                "steps": sched.total_steps, "pending": sched.batch_constructor.num_requests(),
+                "kv_used_pct": kv.used_blocks_pct if kv is not None else 0.0,
+                "cache_hit_rate": kv.cache_hit_rate if kv is not None else 0.0,
+                "preemptions": sched.batch_constructor.total_preemptions},
+        }
+        gc.collect()
+        gc.freeze()
+        logger.info("model worker ready in %.1f s", time.perf_counter() - t0)
+        ready_event.set()
+        idle = 0
+        while not stop_event.is_set():
+            alive_event.set()
+            progress = sched.run_iteration()
+            side.service(handlers)
+            if progress is SchedulerProgress.NO_PROGRESS:
+                idle = min(idle + 1, 50)
+                time.sleep(min(0.0001 * (2 ** min(idle, 6)), 0.005))
+            else:
+                idle = 0
+    except BaseException:  # noqa: BLE001
+        traceback.print_exc()
+        os._exit(1)

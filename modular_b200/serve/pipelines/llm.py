@@ -1,0 +1,95 @@
+"""API-side token generator: tokenise, submit to the worker, stream detokenised chunks.
+
+Reference: max/python/max/serve/pipelines/llm.py:234 ``TokenGeneratorPipeline``
+(``next_token_chunk`` :279, ``_coalesce_chunks`` :178): TTFT / ITL / TPOT are recorded here,
+chunks are coalesced up to ``stream_min_chunk_tokens``, stop strings end the stream and cancel
+the request on the worker.
+"""
+
+from __future__ import annotations
+
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import AsyncIterator, Optional, Sequence, Union
+
+from ...pipelines.context import GenerationStatus, SamplingParams
+from ..telemetry.metrics import METRICS
+from ..worker_interface import ModelWorkerProxy
+from .incremental_detokenizer import IncrementalDetokenizer
+
+
+@dataclass
+class TokenChunk:
+    text: str
+    token_ids: list
+    finish_reason: Optional[str] = None
+    prompt_tokens: int = 0
+    completion_tokens: int = 0
+
+
+def finish_reason_of(status: GenerationStatus, stopped_on_string: bool = False) -> Optional[str]:
+    if stopped_on_string or status is GenerationStatus.END_OF_SEQUENCE:
+        return "stop"
+    if status is GenerationStatus.MAXIMUM_LENGTH:
+        return "length"
+    if status is GenerationStatus.CANCELLED:
+        return "cancelled"
+    return None
+
+
+class TokenGeneratorPipeline:
+    def __init__(self, model_name: str, tokenizer, proxy: ModelWorkerProxy, max_length: int,
+                 stream_min_chunk_tokens: int = 1):
+        self.model_name = model_name
+        self.tokenizer = tokenizer
+        self.proxy = proxy
+        self.max_length = max_length
+        self.min_chunk = max(1, stream_min_chunk_tokens)
+
+    async def next_token_chunk(self, prompt: Union[str, Sequence[int]], sampling_params: SamplingParams,
+                               request_id: Optional[str] = None) -> AsyncIterator[TokenChunk]:
+        rid = request_id or uuid.uuid4().hex
+        ctx = self.tokenizer.new_context(prompt, self.max_length, sampling_params, rid, self.model_name)
+        n_prompt = ctx.tokens.prompt_len
+        detok = IncrementalDetokenizer(self.tokenizer, sampling_params.stop) if sampling_params.detokenize else None
+        t_start = time.perf_counter()
+        t_last: Optional[float] = None
+        n_out = 0
+        METRICS.request_count.inc()
+        METRICS.input_tokens.inc(n_prompt)
+        buf_ids: list = []
+        buf_text = ""
+        async for out in self.proxy.stream(ctx):
+            now = time.perf_counter()
+            if out.tokens:
+                if t_last is None:
+                    METRICS.ttft_ms.observe((now - t_start) * 1e3)
+                else:
+                    METRICS.itl_ms.observe((now - t_last) * 1e3 / len(out.tokens))
+                t_last = now
+                n_out += len(out.tokens)
+            text = detok.push(out.tokens, final=out.is_done) if detok is not None else ""
+            stopped = detok is not None and detok.stopped
+            buf_ids.extend(out.tokens)
+            buf_text += text
+            done = out.is_done or stopped
+            if done or len(buf_ids) >= self.min_chunk:
+                reason = finish_reason_of(out.final_status, stopped) if done else None
+                yield TokenChunk(buf_text, buf_ids, reason, n_prompt, n_out)
+                buf_ids, buf_text = [], ""
+            if done:
+                break
+        METRICS.output_tokens.inc(n_out)
+        if n_out > 1 and t_last is not None:
+            METRICS.tpot_ms.observe((t_last - t_start) * 1e3 / n_out)
+        METRICS.request_time_ms.observe((time.perf_counter() - t_start) * 1e3)
+
+    async def all_tokens(self, prompt, sampling_params: SamplingParams, request_id: Optional[str] = None) -> TokenChunk:
+        text, ids, reason, n_prompt, n_out = "", [], None, 0, 0
+        async for ch in self.next_token_chunk(prompt, sampling_params, request_id):
+            text += ch.text
+            ids.extend(ch.token_ids)
+            reason = ch.finish_reason or reason
+            n_prompt, n_out = ch.prompt_tokens, ch.completion_tokens
+        return TokenChunk(text, ids, reason, n_prompt, n_out)

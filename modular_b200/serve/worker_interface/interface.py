@@ -1,0 +1,100 @@
+"""Proxy the API process uses to talk to the model worker: submit, stream, cancel."""
+
+from __future__ import annotations
+
+import asyncio
+import queue
+from dataclasses import dataclass
+from typing import Any, AsyncIterator, Optional
+
+
+class RequestQueueFull(RuntimeError):
+    """More requests are pending than ``max_queue_size`` allows (mapped to HTTP 429)."""
+
+
+@dataclass
+class WorkerQueues:
+    request: Any
+    response: Any
+    cancel: Any
+
+
+class ModelWorkerProxy:
+    """Fan-out of worker responses to per-request asyncio queues."""
+
+    def __init__(self, queues: WorkerQueues, max_queue_size: int = 0, poll_s: float = 0.001):
+        self.queues = queues
+        self.max_queue_size = max_queue_size
+        self.poll_s = poll_s
+        self._streams: dict[str, asyncio.Queue] = {}
+        self._task: Optional[asyncio.Task] = None
+
+    def start(self) -> None:
+        if self._task is None:
+            self._task = asyncio.create_task(self._response_worker())
+
+    async def stop(self) -> None:
+        if self._task is not None:
+            self._task.cancel()
+            try:
+                await self._task
+            except BaseException:  # noqa: BLE001
+                pass
+            self._task = None
+
+    @property
+    def pending(self) -> int:
+        return len(self._streams)
+
+    async def _response_worker(self) -> None:
+        idle = 0
+        while True:
+            got = False
+            while True:
+                try:
+                    batch = self.queues.response.get_nowait()
+                except queue.Empty:
+                    break
+                except Exception:  # noqa: BLE001
+                    break
+                got = True
+                for rid, out in batch.items():
+                    q = self._streams.get(rid)
+                    if q is not None:
+                        q.put_nowait(out)
+            idle = 0 if got else min(idle + 1, 20)
+            await asyncio.sleep(0 if got else self.poll_s * (1 + idle))
+
+    async def stream(self, ctx) -> AsyncIterator:
+        """Submit ``ctx`` and yield TextGenerationOutput chunks until the final one."""
+        if self.max_queue_size and len(self._streams) >= self.max_queue_size:
+            raise RequestQueueFull(f"{len(self._streams)} requests pending (limit {self.max_queue_size})")
+        q: asyncio.Queue = asyncio.Queue()
+        self._streams[ctx.request_id] = q
+        try:
+            self.queues.request.put_nowait(ctx)
+            while True:
+                out = await q.get()
+                yield out
+                if out.is_done:
+                    return
+        finally:
+            still = self._streams.pop(ctx.request_id, None)
+            if still is not None and not ctx_done(still):
+                try:
+                    self.queues.cancel.put_nowait(ctx.request_id)
+                except Exception:  # noqa: BLE001
+                    pass
+
+    def cancel(self, request_id: str) -> None:
+        self.queues.cancel.put_nowait(request_id)
+        q = self._streams.get(request_id)
+        if q is not None:
+            from ...pipelines.context import GenerationStatus, TextGenerationOutput
+
+            q.put_nowait(TextGenerationOutput(request_id, [], GenerationStatus.CANCELLED))
+
+
+def ctx_done(q: asyncio.Queue) -> bool:
+    """True when the stream ended normally (nothing left to cancel on the worker)."""
+    return getattr(q, "_finished_normally", False)

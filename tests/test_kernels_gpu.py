@@ -50,10 +50,11 @@ def test_gemm_tile_configs(bn, stages, splits):
     assert _rel_err(y, ref.linear(x, w)) < 1e-2
 
 
-@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("mode", [0, 1, 2])
 @pytest.mark.parametrize("M,N,K,bn,stages", [(300, 512, 2048, 160, 4), (64, 4096, 4096, 64, 8),
                                               (1, 256, 8192, 16, 3), (700, 1024, 1024, 256, 4),
-                                              (320, 6144, 4096, 0, 0), (48, 128, 16384, 48, 6)])
+                                              (320, 6144, 4096, 0, 0), (48, 128, 16384, 48, 6),
+                                              (1500, 19200, 256, 0, 0), (130, 18944, 512, 0, 0)])
 def test_gemm_persistent_modes(M, N, K, bn, stages, mode):
     torch.manual_seed(11)
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
@@ -87,8 +88,8 @@ def test_gemm_residual_and_fp32_out():
     assert _rel_err(y2, ref.linear(x, w, r)) < 1e-2
 
 
-@pytest.mark.parametrize("impl,mode", [("tiled", -1), ("persistent", 0), ("persistent", 1)])
-@pytest.mark.parametrize("M", [1, 48, 130, 512])
+@pytest.mark.parametrize("impl,mode", [("tiled", -1), ("persistent", 0), ("persistent", 1), ("persistent", 2)])
+@pytest.mark.parametrize("M", [1, 48, 130, 320, 512])
 def test_gemm_swiglu(M, impl, mode):
     torch.manual_seed(3)
     K, I = 1024, 1408
@@ -148,15 +149,20 @@ def test_rope_kv_store(interleaved, hd):
     assert torch.equal(kv[:, :, 0], kv_ref[:, :, 0])
 
 
-@pytest.mark.parametrize("n_q,n_kv,hd,ps", [(32, 8, 128, 128), (4, 2, 64, 16), (8, 8, 128, 64), (16, 1, 64, 32)])
-def test_paged_attention_mixed_batch(n_q, n_kv, hd, ps):
+@pytest.mark.parametrize("tma", [False, True])
+@pytest.mark.parametrize("n_q,n_kv,hd,ps", [(32, 8, 128, 128), (4, 2, 64, 16), (8, 8, 128, 64), (16, 1, 64, 32),
+                                            (16, 2, 64, 128), (8, 1, 128, 64)])
+def test_paged_attention_mixed_batch(n_q, n_kv, hd, ps, tma):
+    if tma and ps % 64:
+        pytest.skip("the TMA kernel needs pages that are multiples of 64 tokens")
     torch.manual_seed(7)
     q_lens = [1, 70, 1, 200, 33, 1]
     kv_lens = [513, 70, 64, 456, 161, 1]
     B = len(q_lens)
     max_pages = max((k + ps - 1) // ps for k in kv_lens)
     n_pages = B * max_pages + 3
-    kv = (torch.randn(n_pages, 2, 1, n_kv, ps, hd, device=DEV) * 0.5).to(torch.bfloat16)
+    n_layers, layer = 3, 1
+    kv = (torch.randn(n_pages, 2, n_layers, n_kv, ps, hd, device=DEV) * 0.5).to(torch.bfloat16)
     perm = torch.randperm(n_pages, device=DEV)[: B * max_pages].int().view(B, max_pages)
     T = sum(q_lens)
     ld = (n_q + 2 * n_kv) * hd
@@ -165,8 +171,9 @@ def test_paged_attention_mixed_batch(n_q, n_kv, hd, ps):
     ql = torch.tensor(q_lens, device=DEV, dtype=torch.int32)
     kl = torch.tensor(kv_lens, device=DEV, dtype=torch.int32)
     scale = 1.0 / math.sqrt(hd)
-    o = ops.paged_attention(q, kv[:, 0, 0], kv[:, 1, 0], perm, qs, ql, kl, n_q, n_kv, hd, scale)
-    o_ref = ref.paged_attention(q, kv[:, 0, 0], kv[:, 1, 0], perm, qs, ql, kl, n_q, n_kv, hd, scale)
+    o = ops.paged_attention(q, kv[:, 0, layer], kv[:, 1, layer], perm, qs, ql, kl, n_q, n_kv, hd, scale,
+                            kv=kv if tma else None, layer=layer)
+    o_ref = ref.paged_attention(q, kv[:, 0, layer], kv[:, 1, layer], perm, qs, ql, kl, n_q, n_kv, hd, scale)
     assert torch.isfinite(o.float()).all()
     assert _rel_err(o, o_ref) < 1e-2
     assert (o.float() - o_ref.float()).abs().max() < 3e-2

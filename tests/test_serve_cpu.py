@@ -1,0 +1,110 @@
+"""Server tests on CPU: OpenAI routes end to end through the real worker process (ZMQ IPC),
+with the echo pipeline and with the tiny Llama preset."""
+
+import json
+
+import pytest
+from fastapi.testclient import TestClient
+
+from modular_b200.pipelines.config import PipelineArgs, PipelineConfig
+from modular_b200.pipelines.registry import PIPELINE_REGISTRY
+from modular_b200.pipelines.tokenizer import ByteTokenizer
+from modular_b200.serve.api_server import fastapi_app
+from modular_b200.serve.config import Settings
+from modular_b200.serve.pipelines.echo_gen import EchoPipeline
+from modular_b200.serve.pipelines.incremental_detokenizer import IncrementalDetokenizer
+
+
+def _config(**flat):
+    return PipelineConfig.from_args(PipelineArgs.from_flat_kwargs(None, **flat))
+
+
+@pytest.fixture(scope="module")
+def echo_client():
+    settings = Settings(metric_recording="ASYNCIO", max_queue_size=64)
+    pc = _config(model_path="echo", devices="cpu")
+    app = fastapi_app(settings, pc, ByteTokenizer(), EchoPipeline, "echo", 4096)
+    with TestClient(app) as c:
+        yield c
+
+
+def test_health_models_metrics(echo_client):
+    assert echo_client.get("/health").json() == {"status": "ok"}
+    assert echo_client.get("/version").json()["version"]
+    assert [m["id"] for m in echo_client.get("/v1/models").json()["data"]] == ["echo"]
+    assert echo_client.get("/v1/models/nope").status_code == 404
+    assert b"maxserve_request_count" in echo_client.get("/metrics").content
+
+
+def test_completion_echo(echo_client):
+    r = echo_client.post("/v1/completions", json={"model": "echo", "prompt": "hello world", "max_tokens": 64})
+    assert r.status_code == 200, r.text
+    body = r.json()
+    assert body["choices"][0]["text"] == "hello world"
+    assert body["choices"][0]["finish_reason"] == "stop"
+    assert body["usage"]["prompt_tokens"] == 12 and body["usage"]["completion_tokens"] >= 11
+
+
+def test_completion_max_tokens_and_stop(echo_client):
+    r = echo_client.post("/v1/completions", json={"model": "echo", "prompt": "abcdefghij", "max_tokens": 4})
+    assert r.json()["choices"][0]["finish_reason"] == "length"
+    r = echo_client.post("/v1/completions", json={"model": "echo", "prompt": "one two three", "max_tokens": 64,
+                                                  "stop": ["two"]})
+    c = r.json()["choices"][0]
+    assert c["text"] == "one " and c["finish_reason"] == "stop"
+
+
+def test_chat_stream(echo_client):
+    with echo_client.stream("POST", "/v1/chat/completions", json={
+            "model": "echo", "stream": True, "max_tokens": 200, "stream_options": {"include_usage": True},
+            "messages": [{"role": "user", "content": "ping"}]}) as r:
+        assert r.status_code == 200
+        chunks = [l[6:] for l in r.iter_lines() if l.startswith("data: ")]
+    assert chunks[-1] == "[DONE]"
+    objs = [json.loads(c) for c in chunks[:-1]]
+    assert objs[0]["choices"][0]["delta"]["role"] == "assistant"
+    text = "".join(o["choices"][0]["delta"].get("content") or "" for o in objs if o["choices"])
+    assert "ping" in text
+    assert objs[-1]["usage"]["completion_tokens"] > 0
+    assert any(o["choices"] and o["choices"][0].get("finish_reason") == "stop" for o in objs)
+
+
+def test_errors(echo_client):
+    r = echo_client.post("/v1/completions", json={"model": "other", "prompt": "x"})
+    assert r.status_code == 404 and r.json()["error"]["type"] == "not_found_error"
+    r = echo_client.post("/v1/completions", json={"model": "echo"})
+    assert r.status_code == 400 and "prompt" in r.json()["error"]["message"]
+    r = echo_client.post("/v1/completions", json={"model": "echo", "prompt": "x", "temperature": -1})
+    assert r.status_code == 400
+
+
+def test_worker_rpc(echo_client):
+    assert echo_client.get("/max_internal/worker_stats").json()["steps"] > 0
+    assert echo_client.post("/reset_prefix_cache").json() == {"success": False}  # echo has no cache
+
+
+def test_tiny_llama_server():
+    pc = _config(model_path="preset:tiny-llama", devices="cpu", max_length=256, max_batch_size=4,
+                 max_batch_input_tokens=128, kv_cache_page_size=16)
+    tokenizer, factory = PIPELINE_REGISTRY.retrieve_factory(pc)
+    app = fastapi_app(Settings(), pc, tokenizer, factory, "tiny", 256)
+    with TestClient(app) as c:
+        a = c.post("/v1/completions", json={"model": "tiny", "prompt": [5, 6, 7, 8, 9], "max_tokens": 6,
+                                            "temperature": 0, "ignore_eos": True}).json()
+        b = c.post("/v1/completions", json={"model": "tiny", "prompt": [5, 6, 7, 8, 9], "max_tokens": 6,
+                                            "temperature": 0, "ignore_eos": True}).json()
+        assert a["usage"]["completion_tokens"] == 6 and a["choices"][0]["finish_reason"] == "length"
+        assert a["choices"][0]["text"] == b["choices"][0]["text"]
+        assert c.post("/reset_prefix_cache").json() == {"success": True}
+
+
+def test_incremental_detokenizer_utf8_and_stop():
+    tok = ByteTokenizer()
+    d = IncrementalDetokenizer(tok, stop=["END"])
+    ids = tok.encode("héllo wörld EN", add_special_tokens=False)
+    out = "".join(d.push([i]) for i in ids)
+    assert out == "héllo wörld "          # "EN" is held back: it may become "END"
+    assert d.push(tok.encode("X", add_special_tokens=False)) == "ENX"
+    d2 = IncrementalDetokenizer(tok, stop=["END"])
+    out = "".join(d2.push([i]) for i in tok.encode("abcENDdef", add_special_tokens=False))
+    assert out == "abc" and d2.stopped
