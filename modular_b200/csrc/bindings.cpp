@@ -376,6 +376,26 @@ class PyDecoderExecutor {
     in.do_sample = do_sample ? 1 : 0;
     check_rc(ex.forward(in, cur_stream()), "DecoderExecutor.forward");
   }
+  // peer pointers are integers (device addresses valid in this process: symmetric memory)
+  void set_tp(int world, int rank, const std::vector<int64_t>& partial, const std::vector<int64_t>& xn,
+              const std::vector<int64_t>& logits, const std::vector<int64_t>& flags, const Tensor& h_local,
+              const Tensor& logits_local, int vocab_local) {
+    TORCH_CHECK(world >= 1 && world <= 8 && static_cast<int>(partial.size()) == world &&
+                    static_cast<int>(xn.size()) == world && static_cast<int>(logits.size()) == world &&
+                    static_cast<int>(flags.size()) == world,
+                "set_tp: one pointer per rank expected");
+    ex.tp.world = world;
+    ex.tp.rank = rank;
+    for (int i = 0; i < world; ++i) {
+      ex.tp.partial[i] = reinterpret_cast<void*>(partial[i]);
+      ex.tp.xn[i] = reinterpret_cast<void*>(xn[i]);
+      ex.tp.logits[i] = reinterpret_cast<void*>(logits[i]);
+      ex.tp.flags[i] = reinterpret_cast<int*>(flags[i]);
+    }
+    ex.tp.h_local = const_cast<void*>(hold(h_local));
+    ex.tp.logits_local = static_cast<float*>(const_cast<void*>(hold(logits_local)));
+    ex.tp.vocab_local = vocab_local;
+  }
   long launches() const { return ex.launches; }
 };
 
@@ -405,12 +425,34 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("apply_penalties", &apply_penalties);
   m.def("read_error_flag", &read_error_flag, py::arg("reset") = true);
   m.def("num_sms", &num_sms);
+  m.def("tp_flag_ints", []() { return mb_tp_flag_ints(); });
+  m.def("tp_barrier", [](int world, int rank, const std::vector<int64_t>& flags) {
+    int* f[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) f[i] = reinterpret_cast<int*>(flags[i]);
+    check_rc(mb_tp_barrier(world, rank, f, error_flag(), cur_stream()), "tp_barrier");
+  });
+  m.def("tp_rs_norm_ag", [](int world, int rank, const std::vector<int64_t>& partial,
+                            const std::vector<int64_t>& xn, const std::vector<int64_t>& flags,
+                            Tensor& h_local, const Tensor& gamma, int M, int rows_per_rank, double eps,
+                            bool has_partials) {
+    void* a[8] = {}; void* b[8] = {}; int* f[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) {
+      a[i] = reinterpret_cast<void*>(partial[i]);
+      b[i] = reinterpret_cast<void*>(xn[i]);
+      f[i] = reinterpret_cast<int*>(flags[i]);
+    }
+    check_rc(mb_tp_rs_norm_ag(world, rank, a, b, f, h_local.data_ptr(), gamma.data_ptr(), M,
+                              h_local.size(1), rows_per_rank, eps, 0.f, 0, has_partials ? 1 : 0,
+                              error_flag(), cur_stream()),
+             "tp_rs_norm_ag");
+  });
   py::class_<PyDecoderExecutor>(m, "DecoderExecutor")
       .def(py::init<py::dict>())
       .def("set_globals", &PyDecoderExecutor::set_globals)
       .def("add_layer", &PyDecoderExecutor::add_layer)
       .def("set_kv_cache", &PyDecoderExecutor::set_kv_cache)
       .def("set_buffers", &PyDecoderExecutor::set_buffers)
+      .def("set_tp", &PyDecoderExecutor::set_tp)
       .def("forward", &PyDecoderExecutor::forward)
       .def("launches", &PyDecoderExecutor::launches);
   mb::bind_runtime(m);

@@ -75,6 +75,17 @@ int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo, const voi
                            const int32_t* decode_seq, int n_q, int n_kv, int head_dim, int page_size,
                            float scale, int* err, cudaStream_t stream);
 
+// ---- tensor-parallel communication over peer memory (comm.cu) ------------------------------
+int mb_tp_flag_ints(void);
+int mb_tp_barrier(int world, int rank, int* const* flags, int* err, cudaStream_t stream);
+int mb_tp_rs_norm_ag(int world, int rank, void* const* partial_bufs, void* const* xn_bufs,
+                     int* const* flags, void* h_local, const void* gamma, int M, int H,
+                     int rows_per_rank, float eps, float w_off, int mbc, int has_partials, int* err,
+                     cudaStream_t stream);
+int mb_tp_allgather(int world, int rank, void* const* dst_bufs, int* const* flags, const void* src,
+                    int rows, int row_bytes, int ld_src, int ld_dst, long long col_off, int* err,
+                    cudaStream_t stream);
+
 // ---- sampling (sampling.cu) ----------------------------------------------------------------
 int mb_argmax(const float* logits, int64_t* out, int rows, int vocab, int ld, cudaStream_t stream);
 int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, int vocab, int ld,

@@ -11,6 +11,7 @@ namespace mb {
   } while (0)
 
 int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
+  if (tp.world > 1) return forward_tp(in, stream);
   const DecoderConfig& c = cfg;
   const int T = in.T;
   if (T <= 0) return MB_OK;
@@ -18,10 +19,22 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
   const int q_dim = c.n_q * c.head_dim;
   auto gemm = [&](const void* X, const void* W, void* Y, const void* R, int M, int N, int K,
                   int ldx, int ldy, int flags) {
-    if (c.gemm_impl == 1 && buf.p_ws != nullptr) {
+    // gemm_impl: 0 = one CTA per tile, 1 = persistent (hybrid stream-K), 2 = per-shape choice
+    // from measurements on B200: the persistent kernel in whole-tile mode wins for the fused
+    // SwiGLU GEMM (wider token tiles, epilogue overlapped by the second TMEM buffer) and once
+    // there are several waves of tiles; small single-wave GEMMs stay on the tiled kernel with
+    // split-K, whose separate reduction pass is cheaper than an in-kernel fix-up.
+    bool persistent = c.gemm_impl == 1;
+    int mode = -1;
+    if (c.gemm_impl == 2) {
+      const int tiles = ((N + 127) / 128) * ((M + 255) / 256);
+      persistent = (flags & 1) || tiles >= 4 * c.num_sms;
+      mode = 0;
+    }
+    if (persistent && buf.p_ws != nullptr) {
       launches += 1;
       return mb_gemm_bf16_persistent(X, W, Y, R, M, N, K, ldx, K, ldy, ldy, flags | (c.use_pdl ? 8 : 0),
-                                     0, 0, -1, buf.p_ws, buf.p_counters, buf.err, c.num_sms, stream);
+                                     0, 0, mode, buf.p_ws, buf.p_counters, buf.err, c.num_sms, stream);
     }
     int bn, splits, stages;
     mb_gemm_bf16_plan(M, N, K, flags & 1, c.num_sms, &bn, &splits, &stages);
@@ -92,6 +105,107 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
     if (in.do_sample) {
       MB_TRY(mb_sample_topk_topp(buf.logits, buf.sampled, in.n_logits, c.vocab, c.vocab,
                                  in.temperature, in.top_k, in.top_p, in.min_p, in.seeds,
+                                 in.sample_step, stream));
+      launches += 1;
+    }
+  }
+  return MB_OK;
+}
+
+// Tensor-parallel step. Config sizes (n_q, n_kv, inter) are this rank's shard; hidden and vocab
+// are global. Column-parallel GEMMs (QKV, gate/up, LM head) read the gathered activations;
+// row-parallel GEMMs (O, down) write partial sums into the symmetric `partial` buffer, and one
+// fused kernel per GEMM does reduce-scatter + residual + RMSNorm + all-gather over NVLink.
+int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
+  const DecoderConfig& c = cfg;
+  const int T = in.T;
+  if (T <= 0) return MB_OK;
+  const int W = tp.world, R = tp.rank;
+  const int qkv_dim = (c.n_q + 2 * c.n_kv) * c.head_dim;
+  const int q_dim = c.n_q * c.head_dim;
+  const int rows_per_rank = (T + W - 1) / W;
+  void* xn = tp.xn[R];
+  void* partial = tp.partial[R];
+  auto gemm = [&](const void* X, const void* Wt, void* Y, int M, int N, int K, int ldx, int ldy, int flags) {
+    if ((flags & 1) && buf.p_ws != nullptr) {
+      launches += 1;
+      return mb_gemm_bf16_persistent(X, Wt, Y, nullptr, M, N, K, ldx, K, ldy, ldy, flags, 0, 0, 0,
+                                     buf.p_ws, buf.p_counters, buf.err, c.num_sms, stream);
+    }
+    int bn, splits, stages;
+    mb_gemm_bf16_plan(M, N, K, flags & 1, c.num_sms, &bn, &splits, &stages);
+    if (static_cast<size_t>(splits) * M * N * sizeof(float) > buf.workspace_bytes) splits = 1;
+    launches += splits > 1 ? 2 : 1;
+    return mb_gemm_bf16(X, Wt, Y, nullptr, M, N, K, ldx, K, ldy, ldy, flags, bn, splits, stages,
+                        buf.workspace, buf.err, c.num_sms, stream);
+  };
+  auto reduce_norm = [&](const void* gamma) {
+    launches += 1;
+    return mb_tp_rs_norm_ag(W, R, tp.partial, tp.xn, tp.flags, tp.h_local, gamma, T, c.hidden,
+                            rows_per_rank, c.eps, c.norm_weight_offset, c.multiply_before_cast, 1,
+                            buf.err, stream);
+  };
+
+  if (in.future_src != nullptr) {
+    MB_TRY(mb_realize_future_tokens(const_cast<int64_t*>(in.tokens), in.future_src, buf.sampled, T, stream));
+    launches += 1;
+  }
+  // embedding on every rank (replicated table); keep this rank's rows as its residual slice
+  MB_TRY(mb_embedding(in.tokens, embed, buf.h, T, c.hidden, c.vocab, 0, stream));
+  {
+    const int row0 = R * rows_per_rank;
+    int n = T - row0;
+    if (n > rows_per_rank) n = rows_per_rank;
+    if (n > 0 &&
+        cudaMemcpyAsync(tp.h_local, static_cast<const char*>(buf.h) + static_cast<size_t>(row0) * c.hidden * 2,
+                        static_cast<size_t>(n) * c.hidden * 2, cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+      return MB_ERR_LAUNCH;
+  }
+  MB_TRY(mb_rmsnorm(buf.h, layers[0].attn_norm, xn, T, c.hidden, c.hidden, c.hidden, c.eps,
+                    c.norm_weight_offset, c.multiply_before_cast, stream));
+  launches += 3;
+  for (int l = 0; l < c.n_layers; ++l) {
+    const DecoderLayerWeights& w = layers[l];
+    const long long hd = c.head_dim;
+    MB_TRY(gemm(xn, w.wqkv, buf.qkv, T, qkv_dim, c.hidden, c.hidden, qkv_dim, 0));
+    char* kbase = static_cast<char*>(kv.base) + 2 * (static_cast<int64_t>(l) * kv.layer_stride);
+    MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, T,
+                            c.n_q, c.n_kv, c.head_dim, c.page_size, kv.page_stride, kv.head_stride,
+                            c.rope_interleaved, stream));
+    if (c.attn_impl == 1 && c.page_size % 64 == 0) {
+      MB_TRY(mb_paged_attention_tma(
+          buf.qkv, qkv_dim, buf.attn, q_dim, kv.base, kv.total_elems / hd,
+          static_cast<long long>(l) * kv.layer_stride / hd,
+          (static_cast<long long>(l) * kv.layer_stride + kv.kv_stride) / hd, kv.page_stride / hd,
+          in.block_table, in.bt_stride, in.q_start, in.q_len, in.kv_len, in.tile_seq, in.tile_q0,
+          in.n_tiles, in.n_decode, in.decode_seq, c.n_q, c.n_kv, c.head_dim, c.page_size,
+          c.attn_scale, buf.err, stream));
+    } else {
+      MB_TRY(mb_paged_attention(buf.qkv, qkv_dim, buf.attn, q_dim, kbase, kbase + 2 * kv.kv_stride,
+                                in.block_table, in.bt_stride, in.q_start, in.q_len, in.kv_len,
+                                in.tile_seq, in.tile_q0, in.n_tiles, in.n_decode, in.decode_seq, c.n_q,
+                                c.n_kv, c.head_dim, c.page_size, kv.page_stride, kv.head_stride,
+                                c.attn_scale, stream));
+    }
+    launches += 2;
+    MB_TRY(gemm(buf.attn, w.wo, partial, T, c.hidden, q_dim, q_dim, c.hidden, 0));
+    MB_TRY(reduce_norm(w.mlp_norm));
+    MB_TRY(gemm(xn, w.wgu, buf.act, T, c.inter, c.hidden, c.hidden, c.inter, 1));
+    MB_TRY(gemm(buf.act, w.wd, partial, T, c.hidden, c.inter, c.inter, c.hidden, 0));
+    MB_TRY(reduce_norm(l + 1 < c.n_layers ? layers[l + 1].attn_norm : final_norm));
+  }
+  if (in.n_logits > 0) {
+    // xn already holds the final-normalised rows of every token on every rank
+    MB_TRY(mb_gather_rows(xn, in.logit_rows, buf.last_xn, in.n_logits, c.hidden * 2, c.hidden * 2, stream));
+    MB_TRY(gemm(buf.last_xn, lm_head, tp.logits_local, in.n_logits, tp.vocab_local, c.hidden, c.hidden,
+                tp.vocab_local, 4));
+    MB_TRY(mb_tp_allgather(W, R, tp.logits, tp.flags, tp.logits_local, in.n_logits, tp.vocab_local * 4,
+                           tp.vocab_local * 4, c.vocab * 4, static_cast<long long>(R) * tp.vocab_local * 4,
+                           buf.err, stream));
+    launches += 2;
+    if (in.do_sample) {
+      MB_TRY(mb_sample_topk_topp(static_cast<const float*>(tp.logits[R]), buf.sampled, in.n_logits, c.vocab,
+                                 c.vocab, in.temperature, in.top_k, in.top_p, in.min_p, in.seeds,
                                  in.sample_step, stream));
       launches += 1;
     }

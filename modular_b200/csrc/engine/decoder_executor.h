@@ -92,8 +92,21 @@ struct StepInputs {
   int T, B, bt_stride, n_tiles, n_decode, n_logits;
 };
 
+// Tensor-parallel state: peer addresses of the symmetric buffers (index = rank).
+struct TpState {
+  int world = 1, rank = 0;
+  void* partial[8] = {};   // [max_tokens, hidden] bf16: row-parallel GEMM partial sums
+  void* xn[8] = {};        // [max_tokens, hidden] bf16: gathered normalised activations
+  void* logits[8] = {};    // [max_seqs, vocab] fp32: gathered logits
+  int* flags[8] = {};      // barrier flag words
+  void* h_local = nullptr;       // [ceil(max_tokens / world), hidden] bf16 residual slice
+  float* logits_local = nullptr; // [max_seqs, vocab / world] fp32
+  int vocab_local = 0;
+};
+
 class DecoderExecutor {
  public:
+  TpState tp;
   DecoderConfig cfg;
   DecoderBuffers buf;
   KVCacheView kv;
@@ -107,6 +120,9 @@ class DecoderExecutor {
   // Runs embedding -> layers -> final norm -> LM head on `stream`. Returns MB_OK or the
   // first launcher error.
   int forward(const StepInputs& in, cudaStream_t stream);
+
+ private:
+  int forward_tp(const StepInputs& in, cudaStream_t stream);
 };
 
 }  // namespace mb

@@ -1,0 +1,278 @@
+// Tensor-parallel communication kernels over NVLink peer memory (one process per GPU).
+//
+// Every rank owns a set of *symmetric* buffers (same size and role on every rank) whose peer
+// addresses are known to all ranks. Kernels read and write peers' buffers directly with
+// 16-byte loads/stores and synchronise through flag words in peer memory (release/acquire at
+// system scope); NVSwitch gives every pair of GPUs full bandwidth, so the algorithms are
+// all-to-all in one or two shots, never rings.
+//
+//   tp_rs_norm_ag    row-parallel GEMM partials -> reduce-scatter (each rank sums the rows it
+//                    owns over all ranks' partials, pulled from peer memory) + residual add +
+//                    RMSNorm -> all-gather (the normalised rows are pushed into every rank's
+//                    activation buffer). The residual stream stays sharded by rows
+//                    (sequence-parallel layout), so only normalised activations cross NVLink.
+//   tp_allgather     push a local [rows, cols] block into a column slot of every peer's buffer.
+//   tp_barrier       all-rank barrier (used between phases that are not fused).
+//
+// Flags: each rank has an int array in symmetric memory. Word layout: [slot][src_rank] where a
+// rank writes its current epoch into word [slot][my_rank] of every peer; EPOCH lives in the
+// rank's own array and is advanced by the kernels themselves, so captured CUDA graphs replay
+// with fresh epochs. All waits are bounded (1 s); a timeout sets the error word and the kernel
+// carries on, leaving the context usable.
+//
+// Reference counterparts: max/kernels/src/comm/sync.mojo:336 (_multi_gpu_barrier),
+// comm/reducescatter_rmsnorm.mojo:390, comm/allgather_rmsnorm.mojo:288, comm/allgather.mojo:167.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../common/api.h"
+#include "../common/ptx.cuh"
+
+namespace mb {
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+constexpr int kMaxRanks = 8;
+constexpr int kFlagSlots = 4;             // independent barrier slots
+constexpr int kEpochWord = kFlagSlots * kMaxRanks;  // index of the epoch counter
+constexpr int kDoneWord = kEpochWord + 1;           // CTAs of the running kernel that finished their part
+
+struct TpPeers {
+  int world, rank;
+  void* a[kMaxRanks];    // buffer A on every rank (meaning depends on the kernel)
+  void* b[kMaxRanks];    // buffer B on every rank
+  int* flags[kMaxRanks]; // flag arrays
+};
+
+// Barrier across ranks, executed by every CTA: CTA 0 publishes `epoch` to all peers, every CTA
+// waits until all peers have published it. `slot` selects an independent set of words.
+__device__ __forceinline__ void tp_barrier_dev(const TpPeers& p, int slot, int epoch, int* err) {
+  if (blockIdx.x == 0 && threadIdx.x < p.world) {
+    __threadfence_system();
+    st_release_sys(p.flags[threadIdx.x] + slot * kMaxRanks + p.rank, epoch);
+  }
+  if (threadIdx.x < p.world)
+    wait_flag_ge(p.flags[p.rank] + slot * kMaxRanks + threadIdx.x, epoch, err, 400 + slot);
+  __syncthreads();
+}
+
+// Closing barrier of a multi-CTA kernel: the last CTA of this rank to finish publishes `epoch`
+// to all peers (so a peer sees it only when *all* of this rank's remote reads and writes are
+// done), waits for every peer's epoch, then advances the epoch word. Other CTAs just leave.
+__device__ __forceinline__ void tp_finish_barrier(const TpPeers& p, int slot, int epoch, int* err) {
+  __shared__ int is_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(p.flags[p.rank] + kDoneWord, 1);
+    is_last = prev == static_cast<int>(gridDim.x) - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  if (threadIdx.x < p.world) {
+    __threadfence_system();
+    st_release_sys(p.flags[threadIdx.x] + slot * kMaxRanks + p.rank, epoch);
+    wait_flag_ge(p.flags[p.rank] + slot * kMaxRanks + threadIdx.x, epoch, err, 400 + slot);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    p.flags[p.rank][kDoneWord] = 0;
+    p.flags[p.rank][kEpochWord] = epoch;
+  }
+}
+
+__global__ void tp_barrier_kernel(TpPeers p, int* err) {
+  const int epoch = ld_volatile(p.flags[p.rank] + kEpochWord) + 1;
+  __syncthreads();
+  tp_barrier_dev(p, 0, epoch, err);
+  if (threadIdx.x == 0) p.flags[p.rank][kEpochWord] = epoch;
+}
+
+// a[r] = partial sums [M, H] of rank r;  b[r] = gathered normalised activations [M, H] of rank r.
+// h_local = this rank's slice of the residual stream, rows [row0, row0 + n_rows).
+// has_partials = 0 skips the reduction (h_local is used as is): layer-0 entry.
+__global__ void __launch_bounds__(256)
+tp_rs_norm_ag_kernel(TpPeers p, bf16* __restrict__ h_local, const bf16* __restrict__ gamma, int M,
+                     int H, int rows_per_rank, float eps, float w_off, int mbc, int has_partials,
+                     int* err) {
+  __shared__ float red[32];
+  extern __shared__ uint4 row_cache[];
+  const int epoch = ld_volatile(p.flags[p.rank] + kEpochWord) + 1;
+  __syncthreads();
+  // all ranks' GEMMs have written their partials
+  tp_barrier_dev(p, 0, epoch, err);
+
+  const int row0 = p.rank * rows_per_rank;
+  int n_rows = M - row0;
+  if (n_rows > rows_per_rank) n_rows = rows_per_rank;
+  const int nvec = H >> 3;
+  for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
+    const int t = row0 + r;
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float acc[8];
+      {
+        const uint4 hv = *reinterpret_cast<const uint4*>(h_local + static_cast<size_t>(r) * H + v * 8);
+        const bf162* hp = reinterpret_cast<const bf162*>(&hv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(hp[i]);
+          acc[2 * i] = f.x; acc[2 * i + 1] = f.y;
+        }
+      }
+      if (has_partials) {
+        uint4 pv[kMaxRanks];
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; ++s) {
+          if (s < p.world) {
+            // start with the next rank so that the eight GPUs do not all pull from rank 0 first
+            const int src = (p.rank + 1 + s) % p.world;
+            pv[s] = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.a[src]) +
+                                                    static_cast<size_t>(t) * H + v * 8);
+          }
+        }
+        // a row is reduced by exactly one rank, always in the same order: deterministic
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; ++s) {
+          if (s < p.world) {
+            const bf162* pp = reinterpret_cast<const bf162*>(&pv[s]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(pp[i]);
+              acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+            }
+          }
+        }
+      }
+      uint4 out;
+      bf162* op = reinterpret_cast<bf162*>(&out);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        op[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        const float2 f = __bfloat1622float2(op[i]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+      *reinterpret_cast<uint4*>(h_local + static_cast<size_t>(r) * H + v * 8) = out;
+      row_cache[v] = out;
+    }
+    // block reduction of the sum of squares
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = (threadIdx.x & 31) < (blockDim.x >> 5) ? red[threadIdx.x & 31] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    __syncthreads();
+    const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      uint4 a = row_cache[v];
+      const uint4 wv = *reinterpret_cast<const uint4*>(gamma + v * 8);
+      bf162* ap = reinterpret_cast<bf162*>(&a);
+      const bf162* wp = reinterpret_cast<const bf162*>(&wv);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(ap[i]);
+        const float2 g = __bfloat1622float2(wp[i]);
+        if (mbc) {
+          ap[i] = __floats2bfloat162_rn(f.x * inv * (g.x + w_off), f.y * inv * (g.y + w_off));
+        } else {
+          const bf162 n = __floats2bfloat162_rn(f.x * inv, f.y * inv);
+          const float2 nf = __bfloat1622float2(n);
+          ap[i] = __floats2bfloat162_rn(nf.x * (g.x + w_off), nf.y * (g.y + w_off));
+        }
+      }
+      // all-gather: push the normalised row into every rank's activation buffer
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s) {
+        if (s < p.world) {
+          const int dst = (p.rank + s) % p.world;
+          *reinterpret_cast<uint4*>(static_cast<bf16*>(p.b[dst]) + static_cast<size_t>(t) * H + v * 8) = a;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // every rank's pushes have landed (and every rank is done pulling) before anyone continues
+  tp_finish_barrier(p, 1, epoch, err);
+}
+
+// Push local block src[rows, cols] (row stride ld_src bytes) to a[dst] + col_off bytes on every
+// rank (row stride ld_dst bytes), then barrier.
+__global__ void __launch_bounds__(256)
+tp_allgather_kernel(TpPeers p, const uint8_t* __restrict__ src, int rows, int row_bytes, int ld_src,
+                    int ld_dst, long long col_off, int* err) {
+  const int epoch = ld_volatile(p.flags[p.rank] + kEpochWord) + 1;
+  __syncthreads();
+  const int per_row = row_bytes >> 4;
+  const long long total = static_cast<long long>(rows) * per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / per_row), c = static_cast<int>(i % per_row) * 16;
+    const uint4 v = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * ld_src + c);
+#pragma unroll
+    for (int s = 0; s < kMaxRanks; ++s) {
+      if (s < p.world) {
+        const int dst = (p.rank + s) % p.world;
+        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.a[dst]) + static_cast<size_t>(r) * ld_dst +
+                                  col_off + c) = v;
+      }
+    }
+  }
+  tp_finish_barrier(p, 2, epoch, err);
+}
+
+static TpPeers make_peers(int world, int rank, void* const* a, void* const* b, int* const* flags) {
+  TpPeers p;
+  p.world = world; p.rank = rank;
+  for (int i = 0; i < kMaxRanks; ++i) {
+    p.a[i] = i < world && a ? a[i] : nullptr;
+    p.b[i] = i < world && b ? b[i] : nullptr;
+    p.flags[i] = i < world ? flags[i] : nullptr;
+  }
+  return p;
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+extern "C" int mb_tp_flag_ints(void) { return kEpochWord + 8; }
+
+extern "C" int mb_tp_barrier(int world, int rank, int* const* flags, int* err, cudaStream_t stream) {
+  if (world < 1 || world > kMaxRanks) return MB_ERR_SHAPE;
+  tp_barrier_kernel<<<1, 32, 0, stream>>>(make_peers(world, rank, nullptr, nullptr, flags), err);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+extern "C" int mb_tp_rs_norm_ag(int world, int rank, void* const* partial_bufs, void* const* xn_bufs,
+                                int* const* flags, void* h_local, const void* gamma, int M, int H,
+                                int rows_per_rank, float eps, float w_off, int mbc, int has_partials,
+                                int* err, cudaStream_t stream) {
+  if (world < 1 || world > kMaxRanks || H % 8 || H > 32768) return MB_ERR_SHAPE;
+  if (M <= 0) return MB_OK;
+  int grid = rows_per_rank < 1 ? 1 : rows_per_rank;
+  if (grid > 592) grid = 592;
+  tp_rs_norm_ag_kernel<<<grid, 256, H * 2, stream>>>(
+      make_peers(world, rank, partial_bufs, xn_bufs, flags), static_cast<bf16*>(h_local),
+      static_cast<const bf16*>(gamma), M, H, rows_per_rank, eps, w_off, mbc, has_partials, err);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+extern "C" int mb_tp_allgather(int world, int rank, void* const* dst_bufs, int* const* flags,
+                               const void* src, int rows, int row_bytes, int ld_src, int ld_dst,
+                               long long col_off, int* err, cudaStream_t stream) {
+  if (world < 1 || world > kMaxRanks || row_bytes % 16 || ld_src % 16 || ld_dst % 16 || col_off % 16)
+    return MB_ERR_SHAPE;
+  if (rows <= 0) return MB_OK;
+  long long work = static_cast<long long>(rows) * (row_bytes / 16);
+  int grid = static_cast<int>((work + 255) / 256);
+  if (grid > 296) grid = 296;
+  if (grid < 1) grid = 1;
+  tp_allgather_kernel<<<grid, 256, 0, stream>>>(make_peers(world, rank, dst_bufs, nullptr, flags),
+                                                static_cast<const uint8_t*>(src), rows, row_bytes,
+                                                ld_src, ld_dst, col_off, err);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}

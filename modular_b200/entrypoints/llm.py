@@ -68,9 +68,23 @@ class LLM:
         if dtype is None:
             dtype = torch.bfloat16 if on_gpu else torch.float32
         self.cfg = model_config
-        if tp_size != 1:
-            raise NotImplementedError("tensor parallel LLM construction goes through modular_b200.parallel")
-        if weights is None:
+        self.tp = None
+        if tp_size > 1:
+            # one process per GPU; every rank runs the same scheduler on the same requests
+            from ..parallel.tp import TPContext, shard_llama_config, shard_llama_weights
+
+            if not on_gpu:
+                raise ValueError("tensor parallelism needs CUDA devices")
+            self.tp = TPContext(device=self.device)
+            if self.tp.world != tp_size or self.tp.rank != tp_rank:
+                raise ValueError("tp_size / tp_rank do not match the initialised process group")
+            full_cfg = model_config
+            if weights is None:
+                weights = Llama3Weights.random_init(full_cfg, self.device, dtype, seed=seed)
+            weights = shard_llama_weights(full_cfg, weights, tp_rank, tp_size)
+            model_config = shard_llama_config(full_cfg, tp_size)
+            torch.cuda.empty_cache()
+        elif weights is None:
             weights = Llama3Weights.random_init(model_config, self.device, dtype, seed=seed)
         self.weights = weights
         self.max_length = max_length
@@ -88,7 +102,7 @@ class LLM:
                 num_kv_pages = kvp.compute_num_device_blocks(1 << 62, max_batch_size, max_length)
         self.kv = PagedKVCacheManager(kvp, num_kv_pages, self.device, max_seq_len=max_length)
         self.model = Llama3Model(model_config, weights, self.kv.kv, max_tokens=max_batch_input_tokens,
-                                 max_seqs=max_batch_size, max_position=max_length)
+                                 max_seqs=max_batch_size, max_position=max_length, tp=self.tp)
         overlap = on_gpu if enable_overlap_scheduler is None else enable_overlap_scheduler
         if graph_batch_sizes is None:
             graph_batch_sizes = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch_size]

@@ -201,8 +201,11 @@ class Llama3Model:
 
     def __init__(self, cfg: Llama3Config, weights: Llama3Weights, kv_cache: torch.Tensor,
                  max_tokens: int = 8192, max_seqs: int = 256, max_position: Optional[int] = None,
-                 use_executor: Optional[bool] = None, fuse_swiglu: bool = True):
+                 use_executor: Optional[bool] = None, fuse_swiglu: bool = True, tp=None):
+        # under tensor parallelism `cfg` and `weights` are this rank's shard (heads, FFN and
+        # LM-head rows divided by the TP degree; hidden and vocab sizes stay global)
         self.cfg = cfg
+        self.tp = tp
         self.w = weights
         self.kv = kv_cache
         self.device = weights.embed.device
@@ -231,7 +234,7 @@ class Llama3Model:
             n_kv=c.num_key_value_heads, head_dim=c.head_dim, inter=c.intermediate_size,
             vocab=c.vocab_size, eps=c.rms_norm_eps, page_size=self.page_size,
             attn_scale=self.scale, fuse_swiglu=int(self.fuse_swiglu),
-            gemm_impl=1 if ops.GEMM_IMPL == "persistent" else 0,
+            gemm_impl={"tiled": 0, "persistent": 1}.get(ops.GEMM_IMPL, 2),
             use_pdl=int(os.environ.get("MB200_PDL", "0")),
             attn_impl=int(os.environ.get("MB200_ATTN_TMA", "1"))))
         ex.set_globals(self.w.embed, self.w.final_norm, self.w.lm_head, self.cos_sin)
@@ -251,6 +254,21 @@ class Llama3Model:
         ex.set_buffers(b["h"], b["xn"], b["qkv"], b["attn"], b["act"], b["gu"], b["last_h"],
                        b["last_xn"], self.logits_buf, self.sampled, ops.gemm_workspace(dev),
                        *ops.persistent_gemm_workspace(dev))
+        if self.tp is not None and self.tp.world > 1:
+            # symmetric buffers for the fused reduce-scatter + norm + all-gather and the logits
+            tp, W = self.tp, self.tp.world
+            vocab_local = self.w.lm_head.shape[0]
+            sym_partial = tp.alloc_symmetric(T * c.hidden_size, dt)
+            sym_xn = tp.alloc_symmetric(T * c.hidden_size, dt)
+            sym_logits = tp.alloc_symmetric(B * c.vocab_size, torch.float32)
+            sym_flags = tp.alloc_symmetric(max(64, L.tp_flag_ints()), torch.int32, zero=True)
+            self._tp_bufs = (sym_partial, sym_xn, sym_logits, sym_flags)
+            h_local = mk((T + W - 1) // W, c.hidden_size)
+            logits_local = mk(B, vocab_local, dtype=torch.float32)
+            self.logits_buf = sym_logits.tensor.view(B, c.vocab_size)
+            tp.barrier()  # flags are zeroed everywhere before any kernel can touch them
+            ex.set_tp(W, tp.rank, sym_partial.peer_ptrs, sym_xn.peer_ptrs, sym_logits.peer_ptrs,
+                      sym_flags.peer_ptrs, h_local, logits_local, vocab_local)
         self.executor = ex
 
     def forward_packed(self, meta: torch.Tensor, offsets: dict, T: int, B: int, bt_stride: int,

@@ -47,9 +47,9 @@ def check_device_error() -> None:
 
 
 _PERSISTENT_WS: dict[int, tuple] = {}
-# "persistent": one CTA per SM with stream-K work split (default);
+# "auto" (default): per-shape choice; "persistent": one CTA per SM with stream-K work split;
 # "tiled": one CTA per output tile with optional split-K through a workspace.
-GEMM_IMPL = os.environ.get("MB200_GEMM", "persistent")
+GEMM_IMPL = os.environ.get("MB200_GEMM", "auto")
 
 
 def persistent_gemm_workspace(device):
@@ -94,8 +94,11 @@ def linear_swiglu(x, w_gate_up, out=None, bn=0, stages=0, impl=None, mode=-1, pd
         return y
     if out is None:
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
-    if (impl or GEMM_IMPL) == "persistent":
+    sel = impl or GEMM_IMPL
+    if sel in ("persistent", "auto"):
         ws, counters = persistent_gemm_workspace(x.device)
+        if sel == "auto" and mode < 0:
+            mode = 0  # whole tiles, no stream-K fix-up: the measured best for the fused SwiGLU GEMM
         _lib().gemm_bf16_persistent(x, w_gate_up, out, None, True, ws, counters, bn, stages, mode, pdl)
     else:
         _lib().gemm_bf16(x, w_gate_up, out, None, True, None, bn, 1, stages)
