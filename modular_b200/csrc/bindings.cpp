@@ -128,6 +128,101 @@ py::tuple gemm_persistent_sizes() {
                         mb_gemm_persistent_counter_ints(num_sms()));
 }
 
+// Per-token-group (1 x 128) dynamic fp8 quantisation. q: [M, K] float8_e4m3fn; scales fp32
+// [ceil(K/128), M] when k_major (the layout the fp8 GEMM reads) else [M, ceil(K/128)].
+void quant_fp8_group128(const Tensor& x, Tensor& q, Tensor& scales, bool k_major) {
+  need_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kBFloat16, "x: bf16 [M, K]");
+  TORCH_CHECK(q.is_contiguous() && q.element_size() == 1 && scales.scalar_type() == at::kFloat, "q / scales");
+  check_rc(mb_quant_fp8_group128(x.data_ptr(), q.data_ptr(), scales.data_ptr<float>(), x.size(0),
+                                 x.size(1), x.stride(0), 0, k_major ? 1 : 0, cur_stream()),
+           "quant_fp8_group128");
+}
+// y = (xq * xs) @ (wq * ws).T with 128x128 weight blocks and 1x128 activation groups.
+void gemm_fp8_blockscaled(const Tensor& xq, const Tensor& xs, const Tensor& wq, const Tensor& ws,
+                          Tensor& y, const c10::optional<Tensor>& residual, int bn, int stages) {
+  need_cuda(xq, "xq");
+  TORCH_CHECK(xq.is_contiguous() && wq.is_contiguous() && y.is_contiguous() && xs.is_contiguous() &&
+                  ws.is_contiguous() && xq.element_size() == 1 && wq.element_size() == 1 &&
+                  y.scalar_type() == at::kBFloat16,
+              "gemm_fp8: contiguous fp8 operands, bf16 output");
+  const int M = xq.size(0), K = xq.size(1), N = wq.size(0);
+  TORCH_CHECK(wq.size(1) == K && y.size(0) == M && y.size(1) == N, "gemm_fp8: shape mismatch");
+  TORCH_CHECK(xs.numel() == static_cast<int64_t>((K + 127) / 128) * M &&
+                  ws.numel() == static_cast<int64_t>((N + 127) / 128) * ((K + 127) / 128),
+              "gemm_fp8: scale shapes");
+  const bool resid = residual.has_value() && residual->defined();
+  if (resid) TORCH_CHECK(residual->is_contiguous() && residual->scalar_type() == at::kBFloat16, "residual");
+  check_rc(mb_gemm_fp8_blockscaled(xq.data_ptr(), xs.data_ptr<float>(), wq.data_ptr(), ws.data_ptr<float>(),
+                                   y.data_ptr(), optptr(residual), M, N, K, resid ? 2 : 0, bn, stages,
+                                   error_flag(), cur_stream()),
+           "gemm_fp8_blockscaled");
+}
+
+// ---- mixture of experts
+void moe_router_group_limited(const Tensor& logits, const c10::optional<Tensor>& bias, Tensor& ids,
+                              Tensor& w, int n_group, int topk_group, bool norm_topk, double scaling) {
+  need_cuda(logits, "logits");
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1 && ids.scalar_type() == at::kInt &&
+                  w.scalar_type() == at::kFloat && ids.is_contiguous() && w.is_contiguous(),
+              "router dtypes");
+  check_rc(mb_moe_router_group_limited(logits.data_ptr<float>(), static_cast<const float*>(optptr(bias)),
+                                       ids.data_ptr<int32_t>(), w.data_ptr<float>(), logits.size(0),
+                                       logits.size(1), n_group, topk_group, ids.size(1), norm_topk, scaling,
+                                       logits.stride(0), cur_stream()),
+           "moe_router_group_limited");
+}
+void moe_router_softmax_topk(const Tensor& logits, Tensor& ids, Tensor& w, bool norm_topk) {
+  need_cuda(logits, "logits");
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1 && ids.is_contiguous() && w.is_contiguous(), "router");
+  check_rc(mb_moe_router_softmax_topk(logits.data_ptr<float>(), ids.data_ptr<int32_t>(), w.data_ptr<float>(),
+                                      logits.size(0), logits.size(1), ids.size(1), norm_topk,
+                                      logits.stride(0), cur_stream()),
+           "moe_router_softmax_topk");
+}
+// scratch: int32 [2 * E_local] zeroed once (counts | cursor); offsets int32 [E_local + 1].
+void moe_create_indices(const Tensor& ids, int e_begin, int e_end, Tensor& scratch, Tensor& offsets,
+                        Tensor& order, Tensor& inverse) {
+  need_cuda(ids, "topk_ids");
+  const int E = e_end - e_begin;
+  TORCH_CHECK(ids.is_contiguous() && ids.scalar_type() == at::kInt && scratch.numel() >= 2 * E &&
+                  offsets.numel() >= E + 1 && order.numel() >= ids.numel() && inverse.numel() >= ids.numel(),
+              "moe_create_indices buffers");
+  check_rc(mb_moe_create_indices(ids.data_ptr<int32_t>(), ids.numel(), e_begin, e_end,
+                                 scratch.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(),
+                                 scratch.data_ptr<int32_t>() + E, order.data_ptr<int32_t>(),
+                                 inverse.data_ptr<int32_t>(), cur_stream()),
+           "moe_create_indices");
+}
+void moe_permute_rows(const Tensor& src, const Tensor& order, const c10::optional<Tensor>& n_rows,
+                      Tensor& dst, int top_k) {
+  need_cuda(src, "src");
+  TORCH_CHECK(src.is_contiguous() && dst.is_contiguous(), "contiguous");
+  check_rc(mb_moe_permute_rows(src.data_ptr(), order.data_ptr<int32_t>(),
+                               static_cast<const int32_t*>(optptr(n_rows)), dst.data_ptr(), dst.size(0),
+                               src.size(1) * src.element_size(), top_k, cur_stream()),
+           "moe_permute_rows");
+}
+void moe_combine(const Tensor& expert_out, const Tensor& inverse, const Tensor& w,
+                 const c10::optional<Tensor>& shared, Tensor& y, int top_k) {
+  need_cuda(expert_out, "expert_out");
+  TORCH_CHECK(expert_out.is_contiguous() && y.is_contiguous() && w.is_contiguous(), "contiguous");
+  check_rc(mb_moe_combine(expert_out.data_ptr(), inverse.data_ptr<int32_t>(), w.data_ptr<float>(),
+                          optptr(shared), y.data_ptr(), y.size(0), y.size(1), top_k, cur_stream()),
+           "moe_combine");
+}
+// x: [rows, K] tokens in expert order; w: [E, N or 2N, K]; offsets int32 [E + 1] on device.
+void grouped_gemm_bf16(const Tensor& x, const Tensor& w, Tensor& y, const Tensor& offsets, int max_rows,
+                       bool dual, int bn) {
+  need_cuda(x, "x");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous() && y.is_contiguous() && w.dim() == 3, "grouped_gemm layout");
+  const int E = w.size(0), K = w.size(2), N = dual ? w.size(1) / 2 : w.size(1);
+  TORCH_CHECK(x.size(1) == K && y.size(1) == N && y.size(0) == x.size(0) && offsets.numel() >= E + 1, "grouped_gemm shapes");
+  check_rc(mb_grouped_gemm_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), offsets.data_ptr<int32_t>(), E,
+                                x.size(0), max_rows, N, K, dual ? 1 : 0, bn, error_flag(), cur_stream()),
+           "grouped_gemm_bf16");
+}
+
 py::tuple gemm_plan(int M, int N, int K, bool dual) {
   int bn, sp, st;
   mb_gemm_bf16_plan(M, N, K, dual, num_sms(), &bn, &sp, &st);
@@ -408,6 +503,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("workspace") = py::none(), py::arg("bn") = 0, py::arg("splits") = 0,
         py::arg("stages") = 0);
   m.def("gemm_plan", &gemm_plan);
+  m.def("moe_router_group_limited", &moe_router_group_limited);
+  m.def("moe_router_softmax_topk", &moe_router_softmax_topk);
+  m.def("moe_create_indices", &moe_create_indices);
+  m.def("moe_permute_rows", &moe_permute_rows);
+  m.def("moe_combine", &moe_combine);
+  m.def("grouped_gemm_bf16", &grouped_gemm_bf16);
+  m.def("quant_fp8_group128", &quant_fp8_group128);
+  m.def("gemm_fp8_blockscaled", &gemm_fp8_blockscaled, py::arg("xq"), py::arg("xs"), py::arg("wq"),
+        py::arg("ws"), py::arg("y"), py::arg("residual") = py::none(), py::arg("bn") = 0,
+        py::arg("stages") = 0);
   m.def("gemm_bf16_persistent", &gemm_bf16_persistent, py::arg("x"), py::arg("w"), py::arg("y"),
         py::arg("residual") = py::none(), py::arg("dual") = false, py::arg("ws"), py::arg("counters"),
         py::arg("bn") = 0, py::arg("stages") = 0, py::arg("mode") = -1, py::arg("pdl") = false);

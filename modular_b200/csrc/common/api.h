@@ -75,6 +75,23 @@ int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo, const voi
                            const int32_t* decode_seq, int n_q, int n_kv, int head_dim, int page_size,
                            float scale, int* err, cudaStream_t stream);
 
+// ---- mixture of experts (moe.cu, grouped mode of gemm_tcgen05.cu) ---------------------------
+int mb_moe_router_group_limited(const float* logits, const float* bias, int32_t* topk_ids, float* topk_w,
+                                int T, int E, int n_group, int topk_group, int top_k, int norm_topk,
+                                float scaling, int ld, cudaStream_t stream);
+int mb_moe_router_softmax_topk(const float* logits, int32_t* topk_ids, float* topk_w, int T, int E,
+                               int top_k, int norm_topk, int ld, cudaStream_t stream);
+int mb_moe_create_indices(const int32_t* topk_ids, int n_pairs, int e_begin, int e_end, int32_t* counts,
+                          int32_t* offsets, int32_t* cursor, int32_t* order, int32_t* inverse,
+                          cudaStream_t stream);
+int mb_moe_permute_rows(const void* src, const int32_t* order, const int32_t* n_rows_dev, void* dst,
+                        int max_rows, int row_bytes, int top_k, cudaStream_t stream);
+int mb_moe_combine(const void* expert_out, const int32_t* inverse, const float* w, const void* shared,
+                   void* y, int T, int H, int top_k, cudaStream_t stream);
+int mb_grouped_gemm_bf16(const void* X, const void* W, void* Y, const int32_t* expert_offsets,
+                         int n_experts, int total_rows, int max_rows, int N, int K, int flags, int bn,
+                         int* err, cudaStream_t stream);
+
 // ---- tensor-parallel communication over peer memory (comm.cu) ------------------------------
 int mb_tp_flag_ints(void);
 int mb_tp_barrier(int world, int rank, int* const* flags, int* err, cudaStream_t stream);

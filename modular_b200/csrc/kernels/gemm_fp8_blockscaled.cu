@@ -1,0 +1,313 @@
+// Block-scaled fp8 (e4m3) GEMM for sm_100a and the matching activation quantiser.
+//
+//   Y[M, N] = (Xq ⊙ sx)[M, K] · (Wq ⊙ sw)[N, K]^T
+//
+//   Wq  e4m3 [N, K], sw fp32 [ceil(N/128), ceil(K/128)]   one scale per 128x128 weight block
+//   Xq  e4m3 [M, K], sx fp32 [ceil(K/128), M]             one scale per token per 128-wide K group
+//                                                          (stored K-group-major so that a tile's
+//                                                          tokens are contiguous)
+//
+// tcgen05.mma kind::f8f6f4 accumulates 128 K (four K=32 instructions) into one of two TMEM
+// buffers; two epilogue warpgroups then "promote" that partial: read it back with tcgen05.ld,
+// multiply by sw * sx and add it into fp32 register accumulators while the tensor core already
+// works on the next K group in the other buffer. For decode-sized token counts the promotion
+// hides completely under the weight stream; for large token counts it bounds the kernel at
+// roughly the bf16 rate, which is the price of arbitrary (non power-of-two) fp32 scales.
+//
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 promote token
+// columns [0, BN/2), warps 6-9 columns [BN/2, BN). Weights sit on the UMMA M side (128 rows),
+// tokens on the N side (BN = 32..128, multiple of 32).
+//
+// Reference counterparts: max/kernels/src/linalg/matmul/gpu/sm100/
+// warp_specialized_blockwise_fp8.mojo:898 (promote_accumulators :520) and
+// linalg/fp8_quantization.mojo:369 (per-token-group dynamic quantisation).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../common/api.h"
+#include "../common/ptx.cuh"
+#include "gemm_common.h"
+
+namespace mb {
+namespace f8 {
+
+constexpr int kBM = 128;
+constexpr int kBKBytes = 128;     // one swizzle row = 128 fp8 elements
+constexpr int kThreads = 320;
+constexpr int kATile = kBM * kBKBytes;
+constexpr int kStgWarp = 16 * 32 * 2;
+
+struct Params {
+  __nv_bfloat16* Y;
+  const __nv_bfloat16* R;
+  const float* sw;
+  const float* sx;
+  int* err;
+  int M, N, K, ldy, ldr, sw_ld, BN, stages;
+};
+
+struct Tail {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+template <bool RESID>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int stage_bytes = kATile + p.BN * kBKBytes;
+  uint8_t* stg_base = smem + p.stages * stage_bytes;
+  Tail* tail = reinterpret_cast<Tail*>(stg_base + 8 * kStgWarp);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.y * kBM, t0 = blockIdx.x * p.BN;
+  const int kb_total = (p.K + 127) / 128;
+  const uint32_t tmem_cols = p.BN * 2 <= 32 ? 32 : (p.BN * 2 <= 64 ? 64 : (p.BN * 2 <= 128 ? 128 : 256));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tail->acc_full[b], 1);
+      mbar_init(&tail->acc_empty[b], 8);
+    }
+    tail->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tail->tmem_base, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tail->tmem_base;
+  volatile int* abort_word = &tail->abort_word;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < kb_total; ++kb) {
+        const int s = kb % p.stages;
+        const uint32_t ph = (kb / p.stages) & 1;
+        if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, p.err, 501)) break;
+        uint8_t* sa = smem + s * stage_bytes;
+        mbar_arrive_expect_tx(&tail->full[s], stage_bytes);
+        tma_load_2d(sa, &tmW, &tail->full[s], kb * 128, n0);
+        tma_load_2d(sa + kATile, &tmX, &tail->full[s], kb * 128, t0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(kBM, p.BN, 0, 0);  // e4m3 x e4m3 -> fp32
+      for (int kb = 0; kb < kb_total; ++kb) {
+        const int s = kb % p.stages;
+        const uint32_t ph = (kb / p.stages) & 1;
+        const int buf = kb & 1;
+        const uint32_t bph = (kb >> 1) & 1;
+        if (!mbar_wait(&tail->acc_empty[buf], bph ^ 1, abort_word, p.err, 502)) break;
+        if (!mbar_wait(&tail->full[s], ph, abort_word, p.err, 503)) break;
+        tc_fence_after();
+        uint8_t* sa = smem + s * stage_bytes;
+        const uint64_t da = umma_desc_sw128(sa);
+        const uint64_t db = umma_desc_sw128(sa + kATile);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t koff = static_cast<uint64_t>(k * 32 >> 4);  // 32 bytes per K=32 step
+          umma_fp8(tmem_base + buf * p.BN, da + koff, db + koff, idesc, k > 0 ? 1u : 0u);
+        }
+        tc_commit(&tail->empty[s]);
+        tc_commit(&tail->acc_full[buf]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- promotion + epilogue
+    const int ew = warp - 2;            // 0..7
+    const int quad = warp & 3;          // TMEM lane quadrant
+    const int half = ew >> 2;           // which half of the token columns
+    const int cols = p.BN >> 1;         // columns handled by this warpgroup (multiple of 16)
+    const int c_base = half * cols;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+    const float* sw_row = p.sw + static_cast<size_t>(blockIdx.y) * p.sw_ld;
+    bool ok = true;
+    for (int kb = 0; kb < kb_total && ok; ++kb) {
+      const int buf = kb & 1;
+      const uint32_t bph = (kb >> 1) & 1;
+      ok = mbar_wait(&tail->acc_full[buf], bph, abort_word, p.err, 504);
+      if (!ok) break;
+      tc_fence_after();
+      const float w_scale = sw_row[kb];
+      const float* sx_row = p.sx + static_cast<size_t>(kb) * p.M + t0 + c_base;
+#pragma unroll
+      for (int c = 0; c < 64; c += 16) {
+        if (c < cols) {
+          uint32_t v[16];
+          tmem_ld_32x16(lane_addr + buf * p.BN + c_base + c, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c_base + c + j;
+            const float s = t < p.M ? sx_row[c + j] * w_scale : 0.f;
+            acc[c + j] = fmaf(__uint_as_float(v[j]), s, acc[c + j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tail->acc_empty[buf]);
+    }
+    if (ok) {
+      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(stg_base + ew * kStgWarp);
+      const int n_base = n0 + quad * 32;
+#pragma unroll
+      for (int c = 0; c < 64; c += 16) {
+        if (c < cols && t0 + c_base + c < p.M) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) stg[j * 32 + lane] = __float2bfloat16(acc[c + j]);
+          __syncwarp();
+#pragma unroll
+          for (int pass = 0; pass < 2; ++pass) {
+            const int j = pass * 8 + (lane >> 2);
+            const int seg = lane & 3;
+            const int t = t0 + c_base + c + j;
+            const int n = n_base + seg * 8;
+            if (t < p.M && n < p.N) {
+              uint4 val = *reinterpret_cast<const uint4*>(stg + j * 32 + seg * 8);
+              if (RESID) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(p.R + static_cast<size_t>(t) * p.ldr + n);
+                __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&val);
+                const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float2 fa = __bfloat1622float2(a[q]);
+                  const float2 fb = __bfloat1622float2(b[q]);
+                  a[q] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+                }
+              }
+              *reinterpret_cast<uint4*>(p.Y + static_cast<size_t>(t) * p.ldy + n) = val;
+            }
+          }
+          __syncwarp();
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// One warp per (token, 128-wide K group): amax -> scale = amax / 448, q = x / scale.
+__global__ void quant_fp8_group128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
+                                          float* __restrict__ scales, int M, int K, int ldx,
+                                          int k_major) {
+  const int groups = (K + 127) / 128;
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= static_cast<long long>(M) * groups) return;
+  const int t = static_cast<int>(wid / groups), g = static_cast<int>(wid % groups);
+  const int k0 = g * 128 + lane * 4;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (k0 < K) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t) * ldx + k0);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(b[0]), c = __bfloat1622float2(b[1]);
+    v[0] = a.x; v[1] = a.y; v[2] = c.x; v[3] = c.y;
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float scale = fmaxf(amax, 1e-12f) / 448.0f;
+  const float inv = 1.0f / scale;
+  if (k0 < K) {
+    const __nv_fp8x4_e4m3 packed(make_float4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv));
+    *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(t) * K + k0) = packed.__x;
+  }
+  if (lane == 0) scales[k_major ? static_cast<size_t>(g) * M + t : static_cast<size_t>(t) * groups + g] = scale;
+}
+
+}  // namespace f8
+}  // namespace mb
+
+using namespace mb;
+
+extern "C" int mb_quant_fp8_group128(const void* x_bf16, void* q_fp8, float* scales, int M, int K,
+                                     int ldx, int scale_ld, int scales_k_major, cudaStream_t stream) {
+  (void)scale_ld;
+  if (M <= 0) return MB_OK;
+  if (K % 4 || ldx % 4) return MB_ERR_SHAPE;
+  const long long warps = static_cast<long long>(M) * ((K + 127) / 128);
+  const int threads = 256;
+  const long long blocks = (warps * 32 + threads - 1) / threads;
+  f8::quant_fp8_group128_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q_fp8), scales, M, K, ldx,
+      scales_k_major);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+// flags: bit1 residual add. Xs is K-group-major [ceil(K/128), M]; Ws is [ceil(N/128), ceil(K/128)].
+extern "C" int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const void* Wq, const float* Ws,
+                                       void* Y, const void* R, int M, int N, int K, int flags, int bn,
+                                       int stages, int* err, cudaStream_t stream) {
+  using namespace mb::f8;
+  if (M <= 0 || N <= 0) return MB_OK;
+  if (K % 16 || N % 8) return MB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(Xq) | reinterpret_cast<uintptr_t>(Wq) | reinterpret_cast<uintptr_t>(Y) |
+       reinterpret_cast<uintptr_t>(R)) & 15)
+    return MB_ERR_ALIGN;
+  if (bn <= 0) {
+    const int mt = (M + 127) / 128;
+    bn = ((M + mt - 1) / mt + 31) / 32 * 32;
+  }
+  if (bn % 32 || bn < 32 || bn > 128) return MB_ERR_SHAPE;
+  Params p;
+  p.Y = static_cast<__nv_bfloat16*>(Y);
+  p.R = static_cast<const __nv_bfloat16*>(R);
+  p.sw = Ws; p.sx = Xs; p.err = err;
+  p.M = M; p.N = N; p.K = K; p.ldy = N; p.ldr = N; p.sw_ld = (K + 127) / 128; p.BN = bn;
+  const int stage_bytes = kATile + bn * kBKBytes;
+  const int max_stages = (227 * 1024 - 1024 - 8 * kStgWarp - 512) / stage_bytes;
+  if (stages <= 0 || stages > max_stages) stages = max_stages;
+  if (stages > 8) stages = 8;
+  p.stages = stages;
+  CUtensorMap tw, tx;
+  int rc = cached_tmap(&tw, Wq, N, K, K, kBM, 1);
+  if (rc != MB_OK) return rc;
+  rc = cached_tmap(&tx, Xq, M, K, K, bn, 1);
+  if (rc != MB_OK) return rc;
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + 8 * kStgWarp + sizeof(Tail) + 1024;
+  dim3 grid((M + bn - 1) / bn, (N + kBM - 1) / kBM);
+  const bool resid = flags & 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(gemm_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    configured = true;
+  }
+  if (resid)
+    gemm_fp8_kernel<true><<<grid, kThreads, smem, stream>>>(tw, tx, p);
+  else
+    gemm_fp8_kernel<false><<<grid, kThreads, smem, stream>>>(tw, tx, p);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}

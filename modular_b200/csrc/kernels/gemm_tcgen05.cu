@@ -58,7 +58,8 @@ __global__ void __launch_bounds__(kGemmThreads)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                void* __restrict__ Yv, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
                int ldy, int ldr, int dual_rows, int k_per_split, int BN, int stages,
-               uint32_t tmem_cols, int* err) {
+               uint32_t tmem_cols, int* err, const int32_t* __restrict__ expert_offsets,
+               int w_rows_per_expert) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -72,9 +73,22 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const int m_tile = blockIdx.x;  // token tile (fast index: CTAs sharing a weight tile co-run)
   const int n_tile = blockIdx.y;  // weight-row tile
-  const int split = blockIdx.z;
+  // Grouped (mixture-of-experts) mode: blockIdx.z is the expert, its token rows are
+  // [expert_offsets[e], expert_offsets[e+1]) of X / Y and its weights start at row
+  // e * w_rows_per_expert of W. CTAs beyond an expert's rows leave before touching TMEM.
+  int split = blockIdx.z;
   const int n0 = n_tile * kBM;
-  const int t0 = m_tile * BN;
+  int t0 = m_tile * BN;
+  int Mlim = M, w_row0 = 0;
+  if (expert_offsets != nullptr) {
+    const int e = blockIdx.z;
+    const int row_begin = expert_offsets[e], row_end = expert_offsets[e + 1];
+    t0 = row_begin + m_tile * BN;
+    if (t0 >= row_end) return;
+    Mlim = row_end;
+    w_row0 = e * w_rows_per_expert;
+    split = 0;
+  }
   const int k_begin = split * k_per_split;
   const int k_end = min(K, k_begin + k_per_split);
   const int k_iters = (k_end - k_begin + kBK - 1) / kBK;
@@ -113,8 +127,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         uint8_t* sb = sa + a_bytes;
         mbar_arrive_expect_tx(&tail->full[s], stage_bytes);
         const int kc = k_begin + it * kBK;
-        tma_load_2d(sa, &tmW, &tail->full[s], kc, n0);
-        if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, &tail->full[s], kc, dual_rows + n0);
+        tma_load_2d(sa, &tmW, &tail->full[s], kc, w_row0 + n0);
+        if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, &tail->full[s], kc, w_row0 + dual_rows + n0);
         tma_load_2d(sb, &tmX, &tail->full[s], kc, t0);
       }
     }
@@ -154,7 +168,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const int n_row = n0 + quad * 32 + lane;  // weight row (= output column) of this thread
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
       for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (t0 + c0 >= M) break;  // warp-uniform
+        if (t0 + c0 >= Mlim) break;  // warp-uniform
         uint32_t g[16];
         tmem_ld_32x16(lane_addr + c0, g);
         float v[16];
@@ -175,7 +189,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int t = t0 + c0 + j;
-              if (t < M) Y[static_cast<size_t>(t) * ldy + n_row] = v[j];
+              if (t < Mlim) Y[static_cast<size_t>(t) * ldy + n_row] = v[j];
             }
           }
         } else {
@@ -191,7 +205,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const int seg = lane & 3;
             const int t = t0 + c0 + j;
             const int n = n0 + quad * 32 + seg * 8;
-            if (t < M && n < N) {
+            if (t < Mlim && n < N) {
               uint4 val = *reinterpret_cast<const uint4*>(stg + j * 32 + seg * 8);
               if (EPI == EPI_BF16_RESIDUAL) {
                 const uint4 rv =
@@ -337,7 +351,9 @@ static uint32_t pow2_cols(int c) {
 template <bool DUAL, int EPI>
 static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, const void* R, int M,
                       int N, int K, int ldy, int ldr, int dual_rows, int k_per_split, int splits,
-                      int BN, int stages, int* err, cudaStream_t stream) {
+                      int BN, int stages, int* err, cudaStream_t stream,
+                      const int32_t* expert_offsets = nullptr, int n_experts = 0,
+                      int w_rows_per_expert = 0) {
   const int stage_bytes = kATileBytes * (DUAL ? 2 : 1) + BN * kBK * 2;
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes +
                       sizeof(GemmSmemTail) + 1024;
@@ -349,11 +365,11 @@ static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, con
       return MB_ERR_LAUNCH;
     configured = 227 * 1024;
   }
-  dim3 grid((M + BN - 1) / BN, (N + kBM - 1) / kBM, splits);
+  dim3 grid((M + BN - 1) / BN, (N + kBM - 1) / kBM, expert_offsets ? n_experts : splits);
   const uint32_t tmem_cols = pow2_cols(DUAL ? 2 * BN : BN);
   kern<<<grid, kGemmThreads, smem, stream>>>(tw, tx, Y, static_cast<const __nv_bfloat16*>(R), M, N,
                                              K, ldy, ldr, dual_rows, k_per_split, BN, stages,
-                                             tmem_cols, err);
+                                             tmem_cols, err, expert_offsets, w_rows_per_expert);
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
@@ -455,4 +471,38 @@ extern "C" int mb_gemm_bf16(const void* X, const void* W, void* Y, const void* R
                                                 stages, err, stream);
   return launch_cfg<false, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err,
                                      stream);
+}
+
+// Grouped GEMM for mixture-of-experts layers: rows [offsets[e], offsets[e+1]) of X (tokens in
+// expert order) are multiplied by expert e's weights W[e] ([N, K], or [2N, K] = [gate; up] with
+// the SwiGLU epilogue when flags bit0 is set). `max_rows` bounds the rows any expert can have
+// (the grid is sized for it; CTAs past an expert's rows exit at once).
+// Reference: max/kernels/src/linalg/grouped_matmul_sm100.mojo (grouped_matmul_ragged).
+extern "C" int mb_grouped_gemm_bf16(const void* X, const void* W, void* Y, const int32_t* expert_offsets,
+                                    int n_experts, int total_rows, int max_rows, int N, int K, int flags,
+                                    int bn, int* err, cudaStream_t stream) {
+  if (n_experts <= 0 || total_rows <= 0 || max_rows <= 0) return MB_OK;
+  const bool dual = flags & 1;
+  if (K % 8 || N % 8) return MB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(Y)) & 15)
+    return MB_ERR_ALIGN;
+  if (bn <= 0) {
+    bn = max_rows >= 128 ? 128 : (max_rows + 15) / 16 * 16;
+    if (bn < 16) bn = 16;
+  }
+  if (bn % 16 || bn > (dual ? 128 : 256)) return MB_ERR_SHAPE;
+  const int w_rows = dual ? 2 * N : N;
+  const int stage_bytes = kATileBytes * (dual ? 2 : 1) + bn * kBK * 2;
+  int stages = (212 * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  CUtensorMap tw, tx;
+  int rc = cached_tmap(&tw, W, static_cast<uint64_t>(w_rows) * n_experts, K, K, kBM, 2);
+  if (rc != MB_OK) return rc;
+  rc = cached_tmap(&tx, X, total_rows, K, K, bn, 2);
+  if (rc != MB_OK) return rc;
+  if (dual)
+    return launch_cfg<true, EPI_BF16>(tw, tx, Y, nullptr, max_rows, N, K, N, 0, N, K, 1, bn, stages, err,
+                                      stream, expert_offsets, n_experts, w_rows);
+  return launch_cfg<false, EPI_BF16>(tw, tx, Y, nullptr, max_rows, N, K, N, 0, 0, K, 1, bn, stages, err,
+                                     stream, expert_offsets, n_experts, w_rows);
 }

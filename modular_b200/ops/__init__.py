@@ -230,3 +230,32 @@ def apply_penalties(logits, tok, cnt, offsets, freq=None, pres=None, rep=None):
         return ref.apply_penalties(logits, tok, cnt, offsets, freq, pres, rep)
     _lib().apply_penalties(logits, tok, cnt, offsets, freq, pres, rep)
     return logits
+
+
+# ------------------------------------------------------------------ block-scaled fp8
+def quant_fp8_group128(x):
+    """Dynamic per-token-group (1 x 128) fp8 quantisation of activations.
+    Returns (q [M, K] float8_e4m3fn, scales fp32 [ceil(K/128), M])."""
+    if not x.is_cuda:
+        return ref.quant_fp8_group128(x)
+    M, K = x.shape
+    q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((K + 127) // 128, M, dtype=torch.float32, device=x.device)
+    _lib().quant_fp8_group128(x, q, s, True)
+    return q, s
+
+
+def linear_fp8_blockscaled(xq, xs, wq, ws, residual=None, out=None, bn=0, stages=0):
+    """``(xq * xs) @ (wq * ws).T`` with 128x128 weight-block scales and 1x128 activation scales."""
+    if not xq.is_cuda:
+        return ref.linear_fp8_blockscaled(xq, xs, wq, ws, residual)
+    if out is None:
+        out = torch.empty(xq.shape[0], wq.shape[0], dtype=torch.bfloat16, device=xq.device)
+    _lib().gemm_fp8_blockscaled(xq, xs, wq, ws, out, residual, bn, stages)
+    return out
+
+
+def linear_fp8(x, wq, ws, residual=None, out=None):
+    """bf16 activations in: quantise per token group, then the block-scaled fp8 GEMM."""
+    xq, xs = quant_fp8_group128(x)
+    return linear_fp8_blockscaled(xq, xs, wq, ws, residual, out)

@@ -175,3 +175,57 @@ def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, generat
                            float(min_p[r]) if min_p is not None else 0.0)
         out[r] = torch.multinomial(p, 1, generator=generator)[0]
     return out
+
+
+# ------------------------------------------------------------------ block-scaled fp8
+FP8_MAX = 448.0
+
+
+def quant_fp8_group128(x):
+    """Per-token-group (1 x 128) dynamic quantisation. Returns (q float8_e4m3fn [M, K],
+    scales fp32 [ceil(K/128), M])."""
+    M, K = x.shape
+    G = (K + 127) // 128
+    xf = torch.zeros(M, G * 128, dtype=torch.float32, device=x.device)
+    xf[:, :K] = x.float()
+    xg = xf.view(M, G, 128)
+    scale = xg.abs().amax(-1).clamp_min(1e-12) / FP8_MAX
+    q = (xg / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).view(M, G * 128)[:, :K]
+    return q.to(torch.float8_e4m3fn), scale.t().contiguous()
+
+
+def quant_fp8_weight_block128(w):
+    """128x128 block quantisation of a weight [N, K]. Returns (q float8_e4m3fn, scales
+    [ceil(N/128), ceil(K/128)]) with scale = amax / 448 (the checkpoint's ``weight_scale_inv``)."""
+    N, K = w.shape
+    nb, kb = (N + 127) // 128, (K + 127) // 128
+    wf = torch.zeros(nb * 128, kb * 128, dtype=torch.float32, device=w.device)
+    wf[:N, :K] = w.float()
+    blocks = wf.view(nb, 128, kb, 128)
+    scale = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-12) / FP8_MAX
+    q = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).view(nb * 128, kb * 128)[:N, :K]
+    return q.to(torch.float8_e4m3fn).contiguous(), scale.contiguous()
+
+
+def dequant_fp8_weight_block128(q, scale):
+    N, K = q.shape
+    s = scale.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+    return q.float() * s
+
+
+def linear_fp8_blockscaled(xq, xs, wq, ws, residual=None, out_dtype=torch.bfloat16):
+    """fp32 emulation of the block-scaled GEMM: partial sums per 128-wide K group, scaled, added."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    G = (K + 127) // 128
+    xf, wf = xq.float(), wq.float()
+    y = torch.zeros(M, N, dtype=torch.float32, device=xq.device)
+    wsn = ws.repeat_interleave(128, 0)[:N]                      # [N, G]
+    for g in range(G):
+        k0, k1 = g * 128, min(K, (g + 1) * 128)
+        part = xf[:, k0:k1] @ wf[:, k0:k1].t()
+        y += part * xs[g].unsqueeze(1) * wsn[:, g].unsqueeze(0)
+    y = y.to(out_dtype)
+    if residual is not None:
+        y = (y.float() + residual.float()).to(out_dtype)
+    return y

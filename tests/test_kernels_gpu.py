@@ -220,3 +220,32 @@ def test_penalties():
     ops.apply_penalties(logits, tok, cnt, off, f, p, r)
     ref.apply_penalties(lr, tok, cnt, off, f, p, r)
     assert torch.allclose(logits, lr, atol=1e-5)
+
+
+def test_quant_fp8_group128():
+    torch.manual_seed(20)
+    x = (torch.randn(70, 1000, device=DEV) * 3).to(torch.bfloat16)
+    q, s = ops.quant_fp8_group128(x)
+    qr, sr = ref.quant_fp8_group128(x)
+    assert torch.allclose(s, sr, rtol=1e-6, atol=0)
+    # same scale -> identical codes except where the division rounds differently at a tie
+    assert (q.float() != qr.float()).float().mean() < 1e-3
+    deq = q.float().view(70, -1) * s.t().repeat_interleave(128, 1)[:, :1000]
+    assert _rel_err(deq, x) < 0.04
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 512), (64, 4096, 4096), (130, 1024, 7168), (400, 2048, 1536),
+                                   (96, 512, 2000)])
+def test_gemm_fp8_blockscaled(M, N, K):
+    torch.manual_seed(21)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    wq, ws = ref.quant_fp8_weight_block128(w)
+    xq, xs = ops.quant_fp8_group128(x)
+    r = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    y = ops.linear_fp8_blockscaled(xq, xs, wq, ws)
+    y_ref = ref.linear_fp8_blockscaled(xq, xs, wq, ws)
+    assert _rel_err(y, y_ref) < 5e-3          # same quantised operands: only summation order differs
+    assert _rel_err(y, ref.linear(x, w)) < 0.06   # against the unquantised product
+    y2 = ops.linear_fp8_blockscaled(xq, xs, wq, ws, residual=r)
+    assert _rel_err(y2, ref.linear_fp8_blockscaled(xq, xs, wq, ws, r)) < 5e-3
