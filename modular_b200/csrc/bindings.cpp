@@ -551,6 +551,73 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                               error_flag(), cur_stream()),
              "tp_rs_norm_ag");
   });
+  m.def("tp_allgather", [](int world, int rank, const std::vector<int64_t>& dst, const std::vector<int64_t>& flags,
+                           const Tensor& src, int rows, int row_bytes, int ld_src, int ld_dst, int64_t col_off) {
+    void* d[8] = {}; int* f[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) {
+      d[i] = reinterpret_cast<void*>(dst[i]);
+      f[i] = reinterpret_cast<int*>(flags[i]);
+    }
+    check_rc(mb_tp_allgather(world, rank, d, f, src.data_ptr(), rows, row_bytes, ld_src, ld_dst, col_off,
+                             error_flag(), cur_stream()),
+             "tp_allgather");
+  });
+  // ---- expert parallelism ----
+  m.def("ep_flag_ints", []() { return mb_ep_flag_ints(); });
+  m.def("ep_dispatch", [](int world, int rank, const std::vector<int64_t>& recv_x,
+                          const std::vector<int64_t>& recv_meta, const std::vector<int64_t>& flags,
+                          const Tensor& x, const Tensor& topk_ids, Tensor& send_pos, int e_local, int cap,
+                          bool fp8) {
+    need_cuda(x, "x");
+    TORCH_CHECK(x.is_contiguous() && topk_ids.is_contiguous() && topk_ids.scalar_type() == at::kInt &&
+                    send_pos.numel() >= topk_ids.numel(), "ep_dispatch layout");
+    void* a[8] = {}; void* b[8] = {}; int* f[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) {
+      a[i] = reinterpret_cast<void*>(recv_x[i]);
+      b[i] = reinterpret_cast<void*>(recv_meta[i]);
+      f[i] = reinterpret_cast<int*>(flags[i]);
+    }
+    check_rc(mb_ep_dispatch(world, rank, a, b, f, x.data_ptr(), topk_ids.data_ptr<int32_t>(),
+                            send_pos.data_ptr<int32_t>(), x.size(0), x.size(1), topk_ids.size(1), e_local,
+                            cap, fp8 ? 1 : 0, error_flag(), cur_stream()),
+             "ep_dispatch");
+  });
+  m.def("ep_gather_ids", [](const Tensor& recv_meta, const Tensor& flags, Tensor& ids, int world, int cap) {
+    need_cuda(recv_meta, "recv_meta");
+    TORCH_CHECK(ids.numel() >= static_cast<int64_t>(world) * cap, "ids too small");
+    check_rc(mb_ep_gather_ids(recv_meta.data_ptr<int32_t>(), flags.data_ptr<int32_t>(), ids.data_ptr<int32_t>(),
+                              world, cap, cur_stream()),
+             "ep_gather_ids");
+  });
+  m.def("ep_combine_send", [](int world, int rank, const std::vector<int64_t>& ret_x,
+                              const std::vector<int64_t>& flags, const Tensor& out_sorted, const Tensor& order,
+                              const Tensor& n_rows, int cap) {
+    need_cuda(out_sorted, "out_sorted");
+    TORCH_CHECK(out_sorted.is_contiguous(), "contiguous");
+    void* a[8] = {}; int* f[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) {
+      a[i] = reinterpret_cast<void*>(ret_x[i]);
+      f[i] = reinterpret_cast<int*>(flags[i]);
+    }
+    check_rc(mb_ep_combine_send(world, rank, a, f, out_sorted.data_ptr(), order.data_ptr<int32_t>(),
+                                n_rows.data_ptr<int32_t>(), out_sorted.size(0), out_sorted.size(1), cap,
+                                error_flag(), cur_stream()),
+             "ep_combine_send");
+  });
+  m.def("ep_combine_reduce", [](const Tensor& ret_x, const Tensor& topk_ids, const Tensor& send_pos,
+                                const Tensor& w, const c10::optional<Tensor>& shared, Tensor& y, int e_local,
+                                int cap) {
+    need_cuda(ret_x, "ret_x");
+    TORCH_CHECK(y.is_contiguous() && w.is_contiguous() && w.scalar_type() == at::kFloat, "ep_combine_reduce layout");
+    check_rc(mb_ep_combine_reduce(ret_x.data_ptr(), topk_ids.data_ptr<int32_t>(), send_pos.data_ptr<int32_t>(),
+                                  w.data_ptr<float>(), optptr(shared), y.data_ptr(), y.size(0), y.size(1),
+                                  topk_ids.size(1), e_local, cap, cur_stream()),
+             "ep_combine_reduce");
+  });
+  m.def("ep_dequant_rows", [](const Tensor& src, Tensor& dst, int n) {
+    need_cuda(src, "src");
+    check_rc(mb_ep_dequant_rows(src.data_ptr(), dst.data_ptr(), n, dst.size(1), cur_stream()), "ep_dequant_rows");
+  });
   py::class_<PyDecoderExecutor>(m, "DecoderExecutor")
       .def(py::init<py::dict>())
       .def("set_globals", &PyDecoderExecutor::set_globals)

@@ -103,6 +103,21 @@ int mb_tp_allgather(int world, int rank, void* const* dst_bufs, int* const* flag
                     int rows, int row_bytes, int ld_src, int ld_dst, long long col_off, int* err,
                     cudaStream_t stream);
 
+// ---- expert-parallel dispatch / combine over peer memory (comm_ep.cu) -----------------------
+int mb_ep_flag_ints(void);
+int mb_ep_dispatch(int world, int rank, void* const* recv_x, void* const* recv_meta, int* const* flags,
+                   const void* x, const int32_t* topk_ids, int32_t* send_pos, int T, int H, int top_k,
+                   int e_local, int cap, int fp8, int* err, cudaStream_t stream);
+int mb_ep_gather_ids(const int32_t* recv_meta, const int* flags, int32_t* ids, int world, int cap,
+                     cudaStream_t stream);
+int mb_ep_combine_send(int world, int rank, void* const* ret_x, int* const* flags, const void* out_sorted,
+                       const int32_t* order, const int32_t* n_rows_dev, int max_rows, int H, int cap,
+                       int* err, cudaStream_t stream);
+int mb_ep_combine_reduce(const void* ret_x, const int32_t* topk_ids, const int32_t* send_pos, const float* w,
+                         const void* shared, void* y, int T, int H, int top_k, int e_local, int cap,
+                         cudaStream_t stream);
+int mb_ep_dequant_rows(const void* src, void* dst, int n, int H, cudaStream_t stream);
+
 // ---- sampling (sampling.cu) ----------------------------------------------------------------
 int mb_argmax(const float* logits, int64_t* out, int rows, int vocab, int ld, cudaStream_t stream);
 int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, int vocab, int ld,

@@ -1,0 +1,65 @@
+"""Child process of test_ep.py: one rank of an expert-parallel MoE layer (launched by torchrun).
+
+Backend ``gloo`` runs the host exchange on CPU; ``nccl`` runs the peer-memory kernels on one GPU
+per rank. Every rank builds the same full MoE from a seed, keeps its expert slice, runs its own
+token batch through the EP layer several times and compares with the full single-rank layer.
+"""
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    backend = sys.argv[1]
+    fp8 = len(sys.argv) > 2 and sys.argv[2] == "fp8"
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    from modular_b200.nn.moe import MoE, MoEConfig
+    from modular_b200.parallel.ep import EPContext, EPMoE, shard_moe
+
+    if backend == "nccl":
+        local = int(os.environ["LOCAL_RANK"])
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
+    cfg = MoEConfig(hidden_size=512, moe_intermediate_size=256, n_routed_experts=16, num_experts_per_tok=4,
+                    n_shared_experts=1, n_group=4, topk_group=2, routed_scaling_factor=2.5)
+    full = MoE.random_init(cfg, dev, torch.bfloat16, seed=3, std=0.05)
+    mine = shard_moe(full, rank, world)
+    ep = None
+    if backend == "nccl":
+        from modular_b200.parallel.tp import TPContext
+        ep = EPContext(TPContext(device=dev), cfg.hidden_size, cfg.n_routed_experts, cfg.num_experts_per_tok,
+                       max_tokens=96, fp8_dispatch=fp8)
+    layer = EPMoE(mine, ep)
+    errs, drops = [], 0
+    for it, T in enumerate((64, 96, 1, 33)):
+        g = torch.Generator().manual_seed(100 * it + rank)
+        x = (torch.randn(T, cfg.hidden_size, generator=g)).to(torch.bfloat16).to(dev)
+        y = layer(x)
+        ref = full(x)
+        errs.append(float((y.float() - ref.float()).abs().max() / ref.float().abs().max()))
+        drops += layer.dropped
+    if backend == "nccl":
+        torch.cuda.synchronize()
+        from modular_b200 import ops
+        ops.check_device_error()
+    out = {"rank": rank, "errs": errs, "dropped": drops}
+    gathered = [None] * world
+    dist.all_gather_object(gathered, out)
+    if rank == 0:
+        print("EP_RESULT " + json.dumps(gathered), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
