@@ -474,7 +474,7 @@ class PyDecoderExecutor {
   // peer pointers are integers (device addresses valid in this process: symmetric memory)
   void set_tp(int world, int rank, const std::vector<int64_t>& partial, const std::vector<int64_t>& xn,
               const std::vector<int64_t>& logits, const std::vector<int64_t>& flags, const Tensor& h_local,
-              const Tensor& logits_local, int vocab_local) {
+              const Tensor& logits_local, int vocab_local, bool fused, int64_t partial_rows) {
     TORCH_CHECK(world >= 1 && world <= 8 && static_cast<int>(partial.size()) == world &&
                     static_cast<int>(xn.size()) == world && static_cast<int>(logits.size()) == world &&
                     static_cast<int>(flags.size()) == world,
@@ -490,6 +490,8 @@ class PyDecoderExecutor {
     ex.tp.h_local = const_cast<void*>(hold(h_local));
     ex.tp.logits_local = static_cast<float*>(const_cast<void*>(hold(logits_local)));
     ex.tp.vocab_local = vocab_local;
+    ex.tp.fused = fused ? 1 : 0;
+    ex.tp.partial_rows = partial_rows;
   }
   long launches() const { return ex.launches; }
 };
@@ -550,6 +552,45 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                               h_local.size(1), rows_per_rank, eps, 0.f, 0, has_partials ? 1 : 0,
                               error_flag(), cur_stream()),
              "tp_rs_norm_ag");
+  });
+  // mode bit0: pushed partials (n_slots, expected); bit1: close with ready flags instead of a barrier
+  m.def("tp_rs_norm_ag_ex", [](int world, int rank, const std::vector<int64_t>& partial,
+                               const std::vector<int64_t>& xn, const std::vector<int64_t>& flags,
+                               Tensor& h_local, const Tensor& gamma, int M, int rows_per_rank, double eps,
+                               bool has_partials, int mode, int n_slots, int expected) {
+    void* a[8] = {}; void* b[8] = {}; int* f[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) {
+      a[i] = reinterpret_cast<void*>(partial[i]);
+      b[i] = reinterpret_cast<void*>(xn[i]);
+      f[i] = reinterpret_cast<int*>(flags[i]);
+    }
+    check_rc(mb_tp_rs_norm_ag_ex(world, rank, a, b, f, h_local.data_ptr(), gamma.data_ptr(), M,
+                                 h_local.size(1), rows_per_rank, eps, 0.f, 0, has_partials ? 1 : 0, mode,
+                                 n_slots, expected, error_flag(), cur_stream()),
+             "tp_rs_norm_ag_ex");
+  });
+  // GEMM fused with its collective; returns (expected counter increments on this rank, splits used)
+  m.def("gemm_bf16_comm", [](const Tensor& x, const Tensor& w, const c10::optional<Tensor>& y, int M, bool dual,
+                             bool wait_ready, bool push, int bn, int splits, int world, int rank,
+                             int rows_per_rank, const std::vector<int64_t>& flags,
+                             const std::vector<int64_t>& partial, int max_slots) {
+    need_cuda(x, "x");
+    TORCH_CHECK(x.stride(1) == 1 && w.is_contiguous(), "gemm_bf16_comm layout");
+    int* f[8] = {}; void* a[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) {
+      f[i] = reinterpret_cast<int*>(flags[i]);
+      if (push) a[i] = reinterpret_cast<void*>(partial[i]);
+    }
+    const int K = x.size(1), N = dual ? w.size(0) / 2 : w.size(0);
+    int expected = 0, used = 1;
+    void* yp = y.has_value() ? y->data_ptr() : a[rank];
+    check_rc(mb_gemm_bf16_comm(x.data_ptr(), w.data_ptr(), yp, M, N, K, x.stride(0), K,
+                               y.has_value() ? static_cast<int>(y->stride(0)) : N,
+                               (dual ? 1 : 0) | (wait_ready ? 16 : 0) | (push ? 32 : 0), bn, splits, world, rank,
+                               rows_per_rank, f, push ? a : nullptr, max_slots, &expected, &used, error_flag(),
+                               num_sms(), cur_stream()),
+             "gemm_bf16_comm");
+    return py::make_tuple(expected, used);
   });
   m.def("tp_allgather", [](int world, int rank, const std::vector<int64_t>& dst, const std::vector<int64_t>& flags,
                            const Tensor& src, int rows, int row_bytes, int ld_src, int ld_dst, int64_t col_off) {

@@ -99,6 +99,18 @@ int mb_tp_rs_norm_ag(int world, int rank, void* const* partial_bufs, void* const
                      int* const* flags, void* h_local, const void* gamma, int M, int H,
                      int rows_per_rank, float eps, float w_off, int mbc, int has_partials, int* err,
                      cudaStream_t stream);
+// mode bit0: partials were pushed by mb_gemm_bf16_comm into partial_bufs[rank] (n_slots slots of
+// [rows_per_rank, H]); wait for `expected` counter increments instead of a barrier + pull.
+// mode bit1: close with per-source ready flags (for a flag-gated mb_gemm_bf16_comm) instead of a barrier.
+int mb_tp_rs_norm_ag_ex(int world, int rank, void* const* partial_bufs, void* const* xn_bufs,
+                        int* const* flags, void* h_local, const void* gamma, int M, int H,
+                        int rows_per_rank, float eps, float w_off, int mbc, int has_partials, int mode,
+                        int n_slots, int expected, int* err, cudaStream_t stream);
+// GEMM fused with the neighbouring tensor-parallel collective (gemm_comm.cu).
+int mb_gemm_bf16_comm(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
+                      int ldy, int flags, int bn, int splits, int world, int rank, int rows_per_rank,
+                      int* const* flags_all, void* const* partial_all, int max_slots,
+                      int* expected_out, int* splits_out, int* err, int num_sms, cudaStream_t stream);
 int mb_tp_allgather(int world, int rank, void* const* dst_bufs, int* const* flags, const void* src,
                     int rows, int row_bytes, int ld_src, int ld_dst, long long col_off, int* err,
                     cudaStream_t stream);

@@ -145,6 +145,25 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
                             rows_per_rank, c.eps, c.norm_weight_offset, c.multiply_before_cast, 1,
                             buf.err, stream);
   };
+  // Fused path: GEMM -> reduce-scatter by epilogue pushes, all-gather -> GEMM by flag-gated tiles.
+  const bool fused = tp.fused != 0 && tp.partial_rows >= static_cast<long long>(W) * rows_per_rank;
+  const int max_slots = fused ? static_cast<int>(tp.partial_rows / rows_per_rank) : 0;
+  auto gemm_gathered = [&](const void* Wt, void* Y, int N, int ldy, int flags, bool wait) {
+    launches += 1;
+    return mb_gemm_bf16_comm(xn, Wt, Y, T, N, c.hidden, c.hidden, c.hidden, ldy, flags | (wait ? 16 : 0), 0, 1,
+                             W, R, rows_per_rank, tp.flags, nullptr, 0, nullptr, nullptr, buf.err, c.num_sms,
+                             stream);
+  };
+  // row-parallel GEMM whose partial tiles go straight to the owners, then reduce + norm (+ gather)
+  auto gemm_push_reduce_norm = [&](const void* X, const void* Wt, int K, const void* gamma, bool last) {
+    int expected = 0, splits = 1;
+    MB_TRY(mb_gemm_bf16_comm(X, Wt, partial, T, c.hidden, K, K, K, c.hidden, 32, 0, 0, W, R, rows_per_rank,
+                             tp.flags, tp.partial, max_slots, &expected, &splits, buf.err, c.num_sms, stream));
+    launches += 2;
+    return mb_tp_rs_norm_ag_ex(W, R, tp.partial, tp.xn, tp.flags, tp.h_local, gamma, T, c.hidden, rows_per_rank,
+                               c.eps, c.norm_weight_offset, c.multiply_before_cast, 1, last ? 1 : 3, W * splits,
+                               expected, buf.err, stream);
+  };
 
   if (in.future_src != nullptr) {
     MB_TRY(mb_realize_future_tokens(const_cast<int64_t*>(in.tokens), in.future_src, buf.sampled, T, stream));
@@ -167,7 +186,11 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
   for (int l = 0; l < c.n_layers; ++l) {
     const DecoderLayerWeights& w = layers[l];
     const long long hd = c.head_dim;
-    MB_TRY(gemm(xn, w.wqkv, buf.qkv, T, qkv_dim, c.hidden, c.hidden, qkv_dim, 0));
+    if (fused) {
+      MB_TRY(gemm_gathered(w.wqkv, buf.qkv, qkv_dim, qkv_dim, 0, l > 0));
+    } else {
+      MB_TRY(gemm(xn, w.wqkv, buf.qkv, T, qkv_dim, c.hidden, c.hidden, qkv_dim, 0));
+    }
     char* kbase = static_cast<char*>(kv.base) + 2 * (static_cast<int64_t>(l) * kv.layer_stride);
     MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, T,
                             c.n_q, c.n_kv, c.head_dim, c.page_size, kv.page_stride, kv.head_stride,
@@ -188,11 +211,19 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
                                 c.attn_scale, stream));
     }
     launches += 2;
-    MB_TRY(gemm(buf.attn, w.wo, partial, T, c.hidden, q_dim, q_dim, c.hidden, 0));
-    MB_TRY(reduce_norm(w.mlp_norm));
-    MB_TRY(gemm(xn, w.wgu, buf.act, T, c.inter, c.hidden, c.hidden, c.inter, 1));
-    MB_TRY(gemm(buf.act, w.wd, partial, T, c.hidden, c.inter, c.inter, c.hidden, 0));
-    MB_TRY(reduce_norm(l + 1 < c.n_layers ? layers[l + 1].attn_norm : final_norm));
+    const void* next_norm = l + 1 < c.n_layers ? layers[l + 1].attn_norm : final_norm;
+    if (fused) {
+      MB_TRY(gemm_push_reduce_norm(buf.attn, w.wo, q_dim, w.mlp_norm, false));
+      MB_TRY(gemm_gathered(w.wgu, buf.act, c.inter, c.inter, 1, true));
+      // the last reduce of the step closes with a barrier: the logits path reads every row of xn
+      MB_TRY(gemm_push_reduce_norm(buf.act, w.wd, c.inter, next_norm, l + 1 == c.n_layers));
+    } else {
+      MB_TRY(gemm(buf.attn, w.wo, partial, T, c.hidden, q_dim, q_dim, c.hidden, 0));
+      MB_TRY(reduce_norm(w.mlp_norm));
+      MB_TRY(gemm(xn, w.wgu, buf.act, T, c.inter, c.hidden, c.hidden, c.inter, 1));
+      MB_TRY(gemm(buf.act, w.wd, partial, T, c.hidden, c.inter, c.inter, c.hidden, 0));
+      MB_TRY(reduce_norm(next_norm));
+    }
   }
   if (in.n_logits > 0) {
     // xn already holds the final-normalised rows of every token on every rank

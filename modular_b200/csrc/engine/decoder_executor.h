@@ -102,6 +102,11 @@ struct TpState {
   void* h_local = nullptr;       // [ceil(max_tokens / world), hidden] bf16 residual slice
   float* logits_local = nullptr; // [max_seqs, vocab / world] fp32
   int vocab_local = 0;
+  // fused = 1: row-parallel GEMMs push their partial tiles into the owners' slots and
+  // column-parallel GEMMs wait per source on ready flags (no barrier between GEMM and collective).
+  // `partial` then holds [slots][rows_per_rank][hidden] and must have room for partial_rows rows.
+  int fused = 0;
+  long long partial_rows = 0;
 };
 
 class DecoderExecutor {

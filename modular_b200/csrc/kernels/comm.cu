@@ -28,16 +28,12 @@
 
 #include "../common/api.h"
 #include "../common/ptx.cuh"
+#include "comm_flags.h"
 
 namespace mb {
 
 typedef __nv_bfloat16 bf16;
 typedef __nv_bfloat162 bf162;
-
-constexpr int kMaxRanks = 8;
-constexpr int kFlagSlots = 4;             // independent barrier slots
-constexpr int kEpochWord = kFlagSlots * kMaxRanks;  // index of the epoch counter
-constexpr int kDoneWord = kEpochWord + 1;           // CTAs of the running kernel that finished their part
 
 struct TpPeers {
   int world, rank;
@@ -61,7 +57,8 @@ __device__ __forceinline__ void tp_barrier_dev(const TpPeers& p, int slot, int e
 // Closing barrier of a multi-CTA kernel: the last CTA of this rank to finish publishes `epoch`
 // to all peers (so a peer sees it only when *all* of this rank's remote reads and writes are
 // done), waits for every peer's epoch, then advances the epoch word. Other CTAs just leave.
-__device__ __forceinline__ void tp_finish_barrier(const TpPeers& p, int slot, int epoch, int* err) {
+__device__ __forceinline__ void tp_finish_barrier(const TpPeers& p, int slot, int epoch, int* err,
+                                                  int push_target = -1) {
   __shared__ int is_last;
   __threadfence_system();
   __syncthreads();
@@ -80,6 +77,7 @@ __device__ __forceinline__ void tp_finish_barrier(const TpPeers& p, int slot, in
   if (threadIdx.x == 0) {
     p.flags[p.rank][kDoneWord] = 0;
     p.flags[p.rank][kEpochWord] = epoch;
+    if (push_target >= 0) p.flags[p.rank][kPushTarget] = push_target;
   }
 }
 
@@ -90,19 +88,58 @@ __global__ void tp_barrier_kernel(TpPeers p, int* err) {
   if (threadIdx.x == 0) p.flags[p.rank][kEpochWord] = epoch;
 }
 
-// a[r] = partial sums [M, H] of rank r;  b[r] = gathered normalised activations [M, H] of rank r.
+// Closing step without a barrier: the last CTA of this rank to finish tells every peer that this
+// rank's rows have landed in the peer's activation buffer (ready epoch) and leaves. The consumer
+// (the TMA producer of the next GEMM) does the waiting, tile by tile.
+__device__ __forceinline__ void tp_finish_signal(const TpPeers& p, int ready_epoch, int push_target) {
+  __shared__ int is_last_s;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(p.flags[p.rank] + kDoneWord, 1);
+    is_last_s = prev == static_cast<int>(gridDim.x) - 1;
+  }
+  __syncthreads();
+  if (!is_last_s) return;
+  if (threadIdx.x < p.world) {
+    __threadfence_system();
+    st_release_sys(p.flags[threadIdx.x] + kReady + p.rank, ready_epoch);
+  }
+  if (threadIdx.x == 0) {
+    // written by the last CTA only: every CTA has read these words at its start
+    p.flags[p.rank][kDoneWord] = 0;
+    p.flags[p.rank][kPushTarget] = push_target;
+    p.flags[p.rank][kReadyEpoch] = ready_epoch;
+  }
+}
+
+// b[r] = gathered normalised activations [M, H] of rank r.
 // h_local = this rank's slice of the residual stream, rows [row0, row0 + n_rows).
 // has_partials = 0 skips the reduction (h_local is used as is): layer-0 entry.
+// mode bit0 = 0: a[r] = partial sums [M, H] of rank r, pulled from peers after a barrier.
+// mode bit0 = 1: the GEMMs pushed their partials into a[rank] = [n_slots][rows_per_rank][H]; the
+//                kernel waits until the push counter has grown by `expected` and sums local slots.
+// mode bit1 = 0: closing barrier (every rank's rows have landed everywhere when the kernel ends).
+// mode bit1 = 1: closing signal only (per-source ready flags for a flag-gated consumer GEMM).
 __global__ void __launch_bounds__(256)
 tp_rs_norm_ag_kernel(TpPeers p, bf16* __restrict__ h_local, const bf16* __restrict__ gamma, int M,
                      int H, int rows_per_rank, float eps, float w_off, int mbc, int has_partials,
-                     int* err) {
+                     int mode, int n_slots, int expected, int* err) {
   __shared__ float red[32];
   extern __shared__ uint4 row_cache[];
-  const int epoch = ld_volatile(p.flags[p.rank] + kEpochWord) + 1;
+  int* my = p.flags[p.rank];
+  const int epoch = ld_volatile(my + kEpochWord) + 1;
+  const int ready_epoch = ld_volatile(my + kReadyEpoch) + 1;
+  const int push_target = ld_volatile(my + kPushTarget) + ((mode & 1) ? expected : 0);
   __syncthreads();
-  // all ranks' GEMMs have written their partials
-  tp_barrier_dev(p, 0, epoch, err);
+  if (mode & 1) {
+    // every partial tile destined for this rank has landed
+    if (threadIdx.x == 0) wait_flag_ge(my + kPushCount, push_target, err, 410);
+    __syncthreads();
+  } else {
+    // all ranks' GEMMs have written their partials
+    tp_barrier_dev(p, 0, epoch, err);
+  }
 
   const int row0 = p.rank * rows_per_rank;
   int n_rows = M - row0;
@@ -122,7 +159,27 @@ tp_rs_norm_ag_kernel(TpPeers p, bf16* __restrict__ h_local, const bf16* __restri
           acc[2 * i] = f.x; acc[2 * i + 1] = f.y;
         }
       }
-      if (has_partials) {
+      if (has_partials && (mode & 1)) {
+        const bf16* base = static_cast<const bf16*>(p.a[p.rank]) + static_cast<size_t>(r) * H + v * 8;
+        const size_t slot_stride = static_cast<size_t>(rows_per_rank) * H;
+        for (int s0 = 0; s0 < n_slots; s0 += 4) {
+          uint4 pv[4];
+#pragma unroll
+          for (int s = 0; s < 4; ++s)
+            if (s0 + s < n_slots) pv[s] = *reinterpret_cast<const uint4*>(base + (s0 + s) * slot_stride);
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            if (s0 + s < n_slots) {
+              const bf162* pp = reinterpret_cast<const bf162*>(&pv[s]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(pp[i]);
+                acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+              }
+            }
+          }
+        }
+      } else if (has_partials) {
         uint4 pv[kMaxRanks];
 #pragma unroll
         for (int s = 0; s < kMaxRanks; ++s) {
@@ -195,8 +252,12 @@ tp_rs_norm_ag_kernel(TpPeers p, bf16* __restrict__ h_local, const bf16* __restri
     }
     __syncthreads();
   }
+  if (mode & 2) {
+    tp_finish_signal(p, ready_epoch, push_target);
+    return;
+  }
   // every rank's pushes have landed (and every rank is done pulling) before anyone continues
-  tp_finish_barrier(p, 1, epoch, err);
+  tp_finish_barrier(p, 1, epoch, err, push_target);
 }
 
 // Push local block src[rows, cols] (row stride ld_src bytes) to a[dst] + col_off bytes on every
@@ -239,7 +300,7 @@ static TpPeers make_peers(int world, int rank, void* const* a, void* const* b, i
 
 using namespace mb;
 
-extern "C" int mb_tp_flag_ints(void) { return kEpochWord + 8; }
+extern "C" int mb_tp_flag_ints(void) { return kTpFlagInts; }
 
 extern "C" int mb_tp_barrier(int world, int rank, int* const* flags, int* err, cudaStream_t stream) {
   if (world < 1 || world > kMaxRanks) return MB_ERR_SHAPE;
@@ -251,13 +312,22 @@ extern "C" int mb_tp_rs_norm_ag(int world, int rank, void* const* partial_bufs, 
                                 int* const* flags, void* h_local, const void* gamma, int M, int H,
                                 int rows_per_rank, float eps, float w_off, int mbc, int has_partials,
                                 int* err, cudaStream_t stream) {
+  return mb_tp_rs_norm_ag_ex(world, rank, partial_bufs, xn_bufs, flags, h_local, gamma, M, H, rows_per_rank,
+                             eps, w_off, mbc, has_partials, 0, 0, 0, err, stream);
+}
+
+extern "C" int mb_tp_rs_norm_ag_ex(int world, int rank, void* const* partial_bufs, void* const* xn_bufs,
+                                   int* const* flags, void* h_local, const void* gamma, int M, int H,
+                                   int rows_per_rank, float eps, float w_off, int mbc, int has_partials,
+                                   int mode, int n_slots, int expected, int* err, cudaStream_t stream) {
   if (world < 1 || world > kMaxRanks || H % 8 || H > 32768) return MB_ERR_SHAPE;
   if (M <= 0) return MB_OK;
   int grid = rows_per_rank < 1 ? 1 : rows_per_rank;
   if (grid > 592) grid = 592;
   tp_rs_norm_ag_kernel<<<grid, 256, H * 2, stream>>>(
       make_peers(world, rank, partial_bufs, xn_bufs, flags), static_cast<bf16*>(h_local),
-      static_cast<const bf16*>(gamma), M, H, rows_per_rank, eps, w_off, mbc, has_partials, err);
+      static_cast<const bf16*>(gamma), M, H, rows_per_rank, eps, w_off, mbc, has_partials, mode, n_slots,
+      expected, err);
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 

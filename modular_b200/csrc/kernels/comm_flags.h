@@ -1,0 +1,27 @@
+// Word layout of a rank's tensor-parallel flag array (int32, symmetric memory, zeroed once).
+// Shared by the communication kernels (comm.cu) and the GEMMs that are fused with a collective
+// (gemm_comm.cu).
+//
+//   [slot * 8 + src]  slot 0..3   barrier words: rank `src` writes its epoch here on every peer
+//   kEpochWord        barrier epoch of this rank (advanced by the kernels themselves, so captured
+//                     CUDA graphs replay with fresh epochs)
+//   kDoneWord         CTAs of the running communication kernel that finished their part
+//   kReady + src      "rows of rank src have landed in your activation buffer" epoch (remote write)
+//   kReadyEpoch       how many signalling reduce+norm kernels this rank has run (local)
+//   kPushTarget       value kPushCount reaches once all partial tiles of the current GEMM landed
+//   kPushCount        incremented (remote atomics) by every GEMM CTA that pushed a partial tile here
+#pragma once
+
+namespace mb {
+
+constexpr int kMaxRanks = 8;
+constexpr int kFlagSlots = 4;
+constexpr int kEpochWord = kFlagSlots * kMaxRanks;  // 32
+constexpr int kDoneWord = kEpochWord + 1;           // 33
+constexpr int kReady = 40;                          // 40..47
+constexpr int kReadyEpoch = 48;
+constexpr int kPushTarget = 49;
+constexpr int kPushCount = 64;                      // on a cache line of its own
+constexpr int kTpFlagInts = 96;
+
+}  // namespace mb

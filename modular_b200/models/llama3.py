@@ -258,7 +258,11 @@ class Llama3Model:
             # symmetric buffers for the fused reduce-scatter + norm + all-gather and the logits
             tp, W = self.tp, self.tp.world
             vocab_local = self.w.lm_head.shape[0]
-            sym_partial = tp.alloc_symmetric(T * c.hidden_size, dt)
+            # fused GEMM+collective path: partial slots [slot][rows_per_rank][hidden]; W * rows_per_rank
+            # can exceed T by W - 1 rows
+            fused = os.environ.get("MB200_TP_FUSED", "1") != "0"
+            partial_rows = T + W
+            sym_partial = tp.alloc_symmetric(partial_rows * c.hidden_size, dt)
             sym_xn = tp.alloc_symmetric(T * c.hidden_size, dt)
             sym_logits = tp.alloc_symmetric(B * c.vocab_size, torch.float32)
             sym_flags = tp.alloc_symmetric(max(64, L.tp_flag_ints()), torch.int32, zero=True)
@@ -268,7 +272,7 @@ class Llama3Model:
             self.logits_buf = sym_logits.tensor.view(B, c.vocab_size)
             tp.barrier()  # flags are zeroed everywhere before any kernel can touch them
             ex.set_tp(W, tp.rank, sym_partial.peer_ptrs, sym_xn.peer_ptrs, sym_logits.peer_ptrs,
-                      sym_flags.peer_ptrs, h_local, logits_local, vocab_local)
+                      sym_flags.peer_ptrs, h_local, logits_local, vocab_local, fused, partial_rows)
         self.executor = ex
 
     def forward_packed(self, meta: torch.Tensor, offsets: dict, T: int, B: int, bt_stride: int,

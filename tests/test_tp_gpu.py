@@ -13,21 +13,33 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(world: int):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+def _run(world: int, worker: str = "tp_worker.py", tag: str = "TP_RESULT ", extra_env=None):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), os.path.join(HERE, "tp_worker.py")]
+           "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), os.path.join(HERE, worker)]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
-    line = [l for l in p.stdout.splitlines() if l.startswith("TP_RESULT ")][-1]
-    return json.loads(line[len("TP_RESULT "):])
+    line = [l for l in p.stdout.splitlines() if l.startswith(tag)][-1]
+    return json.loads(line[len(tag):])
 
 
 @pytest.mark.parametrize("world", [2, 4])
-def test_tp_matches_single_gpu(world):
+def test_fused_gemm_collectives(world):
+    """GEMM -> reduce-scatter pushes, reduce+norm with ready flags, flag-gated all-gather -> GEMM."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    res = _run(world)
+    res = _run(world, "tp_fused_worker.py", "TPF_RESULT ")
+    for r in res:
+        for T, splits, e_h, e_xn, e_y in r["errs"]:
+            assert e_h < 0.2 and e_xn < 0.03 and e_y < 0.03, (r["rank"], T, splits, e_h, e_xn, e_y)
+    assert any(e[1] > 1 for e in res[0]["errs"]), "no case exercised split-K pushes"
+
+
+@pytest.mark.parametrize("world,fused", [(2, "1"), (2, "0"), (4, "1")])
+def test_tp_matches_single_gpu(world, fused):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    res = _run(world, extra_env={"MB200_TP_FUSED": fused})
     toks = [r["tokens"] for r in res]
     assert all(t == toks[0] for t in toks), "ranks disagree"
     ref = res[0]["ref"]
