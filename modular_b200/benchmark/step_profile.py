@@ -39,12 +39,29 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--breakdown", action="store_true",
+                    help="also time every kernel group of the step with events (eager launches)")
     args = ap.parse_args(argv)
 
-    dev = torch.device("cuda")
+    import os
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
     cfg = Llama3Config.llama31_8b()
     cfg.num_hidden_layers = args.layers
     w = Llama3Weights.random_init(cfg, dev, torch.bfloat16, seed=0)
+    tp = None
+    if world > 1:
+        # launched with torch.distributed.run: one tensor-parallel rank per process
+        import torch.distributed as dist
+        from ..parallel.tp import TPContext, shard_llama_config, shard_llama_weights
+        dist.init_process_group("nccl", device_id=dev)
+        tp = TPContext(device=dev)
+        full_cfg = cfg
+        w = shard_llama_weights(full_cfg, w, rank, world)
+        cfg = shard_llama_config(full_cfg, world)
+        torch.cuda.empty_cache()
     page = 128
     n_seq = args.decode + (1 if args.prefill else 0)
     pages_per_seq = (max(args.ctx, args.prefill_offset + args.prefill) + page) // page + 1
@@ -52,8 +69,8 @@ def main(argv=None) -> int:
                         torch.bfloat16, False, False)
     kv = PagedKVCacheManager(kvp, n_seq * pages_per_seq + 2, dev, max_seq_len=pages_per_seq * page)
     T = args.decode + args.prefill
-    model = Llama3Model(cfg, w, kv.kv, max_tokens=max(T, 16), max_seqs=max(n_seq, 1),
-                        max_position=pages_per_seq * page)
+    model = Llama3Model(cfg, w, kv.kv, max_tokens=max(T, 2176), max_seqs=max(n_seq, 1),
+                        max_position=pages_per_seq * page, tp=tp)
     packer = BatchPacker(cfg.num_attention_heads, cfg.num_key_value_heads, page, max(T, 16),
                          max(n_seq, 1), kv.max_pages_per_seq, device=dev)
     rng = np.random.default_rng(0)
@@ -96,12 +113,29 @@ def main(argv=None) -> int:
         torch.cuda.synchronize()
         times.append(s.elapsed_time(e))
     ops.check_device_error()
-    rec = dict(layers=args.layers, decode=args.decode, ctx=args.ctx, prefill=args.prefill,
+    breakdown = None
+    if args.breakdown:
+        model.executor.set_profiling(True)
+        for _ in range(3):
+            if tp is not None:
+                tp.barrier()
+            call()
+        torch.cuda.synchronize()
+        breakdown = {name: dict(calls_per_step=n // 3, us_per_call=round(ms * 1e3 / n, 2),
+                                ms_per_step=round(ms / 3, 3))
+                     for name, n, ms in model.executor.profile()}
+        model.executor.set_profiling(False)
+    rec = dict(world=world, rank=rank, breakdown=breakdown, layers=args.layers, decode=args.decode, ctx=args.ctx, prefill=args.prefill,
                tokens=sb.T, graph=args.graph, ms_median=statistics.median(times), ms_min=min(times),
                launches_per_step=(model.executor.launches() - n0) // max(1, args.iters) if not args.graph else None,
                gemm_impl=ops.GEMM_IMPL)
-    print(json.dumps(rec), flush=True)
-    if args.out:
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    if tp is not None:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    if args.out and rank == 0:
         with open(args.out, "a") as f:
             f.write(json.dumps(rec) + "\n")
     return 0

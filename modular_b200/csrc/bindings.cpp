@@ -64,7 +64,8 @@ int num_sms() {
 
 // y = x @ w.T with optional fusions; see mb_gemm_bf16.
 void gemm_bf16(const Tensor& x, const Tensor& w, Tensor& y, const c10::optional<Tensor>& residual,
-               bool dual, const c10::optional<Tensor>& workspace, int bn, int splits, int stages) {
+               bool dual, const c10::optional<Tensor>& workspace, int bn, int splits, int stages,
+               bool packed) {
   need_cuda(x, "x"); need_cuda(w, "w"); need_cuda(y, "y");
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2, "gemm_bf16: 2-D tensors expected");
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "bf16 inputs");
@@ -74,7 +75,8 @@ void gemm_bf16(const Tensor& x, const Tensor& w, Tensor& y, const c10::optional<
   TORCH_CHECK(w.size(1) == K && y.size(0) == M && y.size(1) == N, "gemm_bf16: shape mismatch");
   const bool f32 = y.scalar_type() == at::kFloat;
   TORCH_CHECK(f32 || y.scalar_type() == at::kBFloat16, "output must be bf16 or fp32");
-  int flags = (dual ? 1 : 0) | (residual.has_value() && residual->defined() ? 2 : 0) | (f32 ? 4 : 0);
+  int flags = (dual ? 1 : 0) | (residual.has_value() && residual->defined() ? 2 : 0) | (f32 ? 4 : 0) |
+              (packed ? 64 : 0);
   void* ws = nullptr;
   if (workspace.has_value() && workspace->defined()) {
     ws = workspace->data_ptr();
@@ -101,7 +103,7 @@ void gemm_bf16(const Tensor& x, const Tensor& w, Tensor& y, const c10::optional<
 // Persistent stream-K variant. `ws` = (float workspace, int32 zeroed counters).
 void gemm_bf16_persistent(const Tensor& x, const Tensor& w, Tensor& y,
                           const c10::optional<Tensor>& residual, bool dual, const Tensor& ws,
-                          const Tensor& counters, int bn, int stages, int mode, bool pdl) {
+                          const Tensor& counters, int bn, int stages, int mode, bool pdl, bool packed) {
   need_cuda(x, "x"); need_cuda(w, "w"); need_cuda(y, "y");
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2, "gemm: 2-D tensors expected");
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "bf16 inputs");
@@ -115,7 +117,7 @@ void gemm_bf16_persistent(const Tensor& x, const Tensor& w, Tensor& y,
                   static_cast<size_t>(counters.numel()) >= mb_gemm_persistent_counter_ints(num_sms()) &&
                   counters.scalar_type() == at::kInt,
               "gemm: workspace too small");
-  int flags = (dual ? 1 : 0) | (resid ? 2 : 0) | (f32 ? 4 : 0) | (pdl ? 8 : 0);
+  int flags = (dual ? 1 : 0) | (resid ? 2 : 0) | (f32 ? 4 : 0) | (pdl ? 8 : 0) | (packed ? 64 : 0);
   check_rc(mb_gemm_bf16_persistent(x.data_ptr(), w.data_ptr(), y.data_ptr(), optptr(residual), M, N, K,
                                    x.stride(0), w.stride(0), y.stride(0),
                                    resid ? residual->stride(0) : 0, flags, bn, stages, mode,
@@ -474,7 +476,7 @@ class PyDecoderExecutor {
   // peer pointers are integers (device addresses valid in this process: symmetric memory)
   void set_tp(int world, int rank, const std::vector<int64_t>& partial, const std::vector<int64_t>& xn,
               const std::vector<int64_t>& logits, const std::vector<int64_t>& flags, const Tensor& h_local,
-              const Tensor& logits_local, int vocab_local, bool fused, int64_t partial_rows) {
+              const Tensor& logits_local, int vocab_local, int fused, int64_t partial_rows) {
     TORCH_CHECK(world >= 1 && world <= 8 && static_cast<int>(partial.size()) == world &&
                     static_cast<int>(xn.size()) == world && static_cast<int>(logits.size()) == world &&
                     static_cast<int>(flags.size()) == world,
@@ -490,10 +492,16 @@ class PyDecoderExecutor {
     ex.tp.h_local = const_cast<void*>(hold(h_local));
     ex.tp.logits_local = static_cast<float*>(const_cast<void*>(hold(logits_local)));
     ex.tp.vocab_local = vocab_local;
-    ex.tp.fused = fused ? 1 : 0;
+    ex.tp.fused = fused;
     ex.tp.partial_rows = partial_rows;
   }
   long launches() const { return ex.launches; }
+  void set_profiling(bool on) { ex.profiling = on; }
+  py::list profile() {
+    py::list out;
+    for (auto& e : ex.profile_ms()) out.append(py::make_tuple(std::get<0>(e), std::get<1>(e), std::get<2>(e)));
+    return out;
+  }
 };
 
 }  // namespace
@@ -503,7 +511,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16", &gemm_bf16, py::arg("x"), py::arg("w"), py::arg("y"),
         py::arg("residual") = py::none(), py::arg("dual") = false,
         py::arg("workspace") = py::none(), py::arg("bn") = 0, py::arg("splits") = 0,
-        py::arg("stages") = 0);
+        py::arg("stages") = 0, py::arg("packed") = false);
   m.def("gemm_plan", &gemm_plan);
   m.def("moe_router_group_limited", &moe_router_group_limited);
   m.def("moe_router_softmax_topk", &moe_router_softmax_topk);
@@ -517,7 +525,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("stages") = 0);
   m.def("gemm_bf16_persistent", &gemm_bf16_persistent, py::arg("x"), py::arg("w"), py::arg("y"),
         py::arg("residual") = py::none(), py::arg("dual") = false, py::arg("ws"), py::arg("counters"),
-        py::arg("bn") = 0, py::arg("stages") = 0, py::arg("mode") = -1, py::arg("pdl") = false);
+        py::arg("bn") = 0, py::arg("stages") = 0, py::arg("mode") = -1, py::arg("pdl") = false,
+        py::arg("packed") = false);
   m.def("gemm_persistent_sizes", &gemm_persistent_sizes);
   m.def("rmsnorm", &rmsnorm);
   m.def("add_rmsnorm", &add_rmsnorm);
@@ -667,6 +676,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_buffers", &PyDecoderExecutor::set_buffers)
       .def("set_tp", &PyDecoderExecutor::set_tp)
       .def("forward", &PyDecoderExecutor::forward)
-      .def("launches", &PyDecoderExecutor::launches);
+      .def("launches", &PyDecoderExecutor::launches)
+      .def("set_profiling", &PyDecoderExecutor::set_profiling)
+      .def("profile", &PyDecoderExecutor::profile);
   mb::bind_runtime(m);
 }

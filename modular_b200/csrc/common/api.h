@@ -25,6 +25,17 @@ int mb_gemm_bf16(const void* X, const void* W, void* Y, const void* R, int M, in
                  int ldx, int ldw, int ldy, int ldr, int flags, int bn, int splits, int stages,
                  void* workspace, int* err, int num_sms, cudaStream_t stream);
 
+// Gated variants: token tiles wait for the tensor-parallel ready flags (comm_flags.h) of the ranks
+// whose rows they read, so the GEMM overlaps the all-gather that fills X. gate_flags = nullptr: off.
+int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,
+                       int ldx, int ldw, int ldy, int ldr, int flags, int bn, int splits, int stages,
+                       void* workspace, int* err, int num_sms, const int* gate_flags, int gate_rpr,
+                       int gate_world, cudaStream_t stream);
+int mb_gemm_bf16_persistent_gated(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,
+                                  int ldx, int ldw, int ldy, int ldr, int flags, int bn, int stages,
+                                  int force_mode, void* ws, int* counters, int* err, int num_sms,
+                                  const int* gate_flags, int gate_rpr, int gate_world, cudaStream_t stream);
+
 size_t mb_gemm_persistent_workspace_bytes(int num_sms);
 size_t mb_gemm_persistent_counter_ints(int num_sms);
 int mb_gemm_bf16_persistent(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,

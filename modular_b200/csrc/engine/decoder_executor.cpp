@@ -1,5 +1,7 @@
 #include "decoder_executor.h"
 
+#include <string>
+
 #include "../common/api.h"
 
 namespace mb {
@@ -9,6 +11,32 @@ namespace mb {
     int rc__ = (expr);          \
     if (rc__ != MB_OK) return rc__; \
   } while (0)
+
+void DecoderExecutor::mark(const char* label, cudaStream_t stream) {
+  if (!profiling) return;
+  cudaEvent_t ev;
+  if (cudaEventCreate(&ev) != cudaSuccess) return;
+  cudaEventRecord(ev, stream);
+  marks_.emplace_back(label, ev);
+}
+
+std::vector<std::tuple<std::string, int, double>> DecoderExecutor::profile_ms() {
+  std::vector<std::tuple<std::string, int, double>> out;
+  if (marks_.empty()) return out;
+  cudaEventSynchronize(marks_.back().second);
+  for (size_t i = 1; i < marks_.size(); ++i) {
+    if (std::string(marks_[i].first) == "begin") continue;  // gap between two steps
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, marks_[i - 1].second, marks_[i].second);
+    bool found = false;
+    for (auto& e : out)
+      if (std::get<0>(e) == marks_[i].first) { std::get<1>(e) += 1; std::get<2>(e) += ms; found = true; break; }
+    if (!found) out.emplace_back(marks_[i].first, 1, ms);
+  }
+  for (auto& m : marks_) cudaEventDestroy(m.second);
+  marks_.clear();
+  return out;
+}
 
 int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
   if (tp.world > 1) return forward_tp(in, stream);
@@ -44,6 +72,7 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
                         buf.workspace, buf.err, c.num_sms, stream);
   };
 
+  mark("begin", stream);
   if (in.future_src != nullptr) {
     MB_TRY(mb_realize_future_tokens(const_cast<int64_t*>(in.tokens), in.future_src, buf.sampled, T,
                                     stream));
@@ -51,6 +80,7 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
   }
   MB_TRY(mb_embedding(in.tokens, embed, buf.h, T, c.hidden, c.vocab, 0, stream));
   launches += 1;
+  mark("embed", stream);
   for (int l = 0; l < c.n_layers; ++l) {
     const DecoderLayerWeights& w = layers[l];
     char* kbase = static_cast<char*>(kv.base) + 2 * (static_cast<int64_t>(l) * kv.layer_stride);
@@ -58,10 +88,13 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
     void* vc = kbase + 2 * kv.kv_stride;
     MB_TRY(mb_rmsnorm(buf.h, w.attn_norm, buf.xn, T, c.hidden, c.hidden, c.hidden, c.eps,
                       c.norm_weight_offset, c.multiply_before_cast, stream));
+    mark("rmsnorm", stream);
     MB_TRY(gemm(buf.xn, w.wqkv, buf.qkv, nullptr, T, qkv_dim, c.hidden, c.hidden, qkv_dim, 0));
+    mark("gemm_qkv", stream);
     MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kc, vc, T, c.n_q, c.n_kv,
                             c.head_dim, c.page_size, kv.page_stride, kv.head_stride,
                             c.rope_interleaved, stream));
+    mark("rope_kv_store", stream);
     if (c.attn_impl == 1 && c.page_size % 64 == 0) {
       const long long hd = c.head_dim;
       MB_TRY(mb_paged_attention_tma(
@@ -80,10 +113,13 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
                                 c.attn_scale, stream));
       launches += 2 + (in.n_tiles > 0) + (in.n_decode > 0);
     }
+    mark("attention", stream);
     MB_TRY(gemm(buf.attn, w.wo, buf.h, buf.h, T, c.hidden, q_dim, q_dim, c.hidden, 2));
+    mark("gemm_o", stream);
     MB_TRY(mb_rmsnorm(buf.h, w.mlp_norm, buf.xn, T, c.hidden, c.hidden, c.hidden, c.eps,
                       c.norm_weight_offset, c.multiply_before_cast, stream));
     launches += 1;
+    mark("rmsnorm", stream);
     if (c.fuse_swiglu) {
       MB_TRY(gemm(buf.xn, w.wgu, buf.act, nullptr, T, c.inter, c.hidden, c.hidden, c.inter, 1));
     } else {
@@ -92,7 +128,9 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
       MB_TRY(mb_silu_mul(buf.gu, buf.act, T, c.inter, stream));
       launches += 1;
     }
+    mark("gemm_gate_up", stream);
     MB_TRY(gemm(buf.act, w.wd, buf.h, buf.h, T, c.hidden, c.inter, c.inter, c.hidden, 2));
+    mark("gemm_down", stream);
   }
   if (in.n_logits > 0) {
     MB_TRY(mb_gather_rows(buf.h, in.logit_rows, buf.last_h, in.n_logits, c.hidden * 2,
@@ -102,11 +140,13 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
     MB_TRY(gemm(buf.last_xn, lm_head, buf.logits, nullptr, in.n_logits, c.vocab, c.hidden,
                 c.hidden, c.vocab, 4));
     launches += 2;
+    mark("lm_head", stream);
     if (in.do_sample) {
       MB_TRY(mb_sample_topk_topp(buf.logits, buf.sampled, in.n_logits, c.vocab, c.vocab,
                                  in.temperature, in.top_k, in.top_p, in.min_p, in.seeds,
                                  in.sample_step, stream));
       launches += 1;
+      mark("sample", stream);
     }
   }
   return MB_OK;
@@ -139,32 +179,50 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
     return mb_gemm_bf16(X, Wt, Y, nullptr, M, N, K, ldx, K, ldy, ldy, flags, bn, splits, stages,
                         buf.workspace, buf.err, c.num_sms, stream);
   };
-  auto reduce_norm = [&](const void* gamma) {
-    launches += 1;
-    return mb_tp_rs_norm_ag(W, R, tp.partial, tp.xn, tp.flags, tp.h_local, gamma, T, c.hidden,
-                            rows_per_rank, c.eps, c.norm_weight_offset, c.multiply_before_cast, 1,
-                            buf.err, stream);
-  };
-  // Fused path: GEMM -> reduce-scatter by epilogue pushes, all-gather -> GEMM by flag-gated tiles.
-  const bool fused = tp.fused != 0 && tp.partial_rows >= static_cast<long long>(W) * rows_per_rank;
-  const int max_slots = fused ? static_cast<int>(tp.partial_rows / rows_per_rank) : 0;
+  // Fused paths (tp.fused bit0 / bit1, independent):
+  //   push: row-parallel GEMMs store their tiles into the owners' partial slots (GEMM -> reduce-scatter)
+  //   gate: reduce+norm closes with ready flags and the next column-parallel GEMM waits per token
+  //         tile for the sources it reads (all-gather -> GEMM), instead of a closing barrier
+  const bool push = (tp.fused & 1) && tp.partial_rows >= static_cast<long long>(W) * rows_per_rank;
+  const bool gate_on = (tp.fused & 2) != 0;
+  const int max_slots = push ? static_cast<int>(tp.partial_rows / rows_per_rank) : 0;
+  // column-parallel GEMM on the gathered activations; its token tiles wait for the ready flags of
+  // the ranks that push their rows (same kernel choice as the single-GPU path)
   auto gemm_gathered = [&](const void* Wt, void* Y, int N, int ldy, int flags, bool wait) {
-    launches += 1;
-    return mb_gemm_bf16_comm(xn, Wt, Y, T, N, c.hidden, c.hidden, c.hidden, ldy, flags | (wait ? 16 : 0), 0, 1,
-                             W, R, rows_per_rank, tp.flags, nullptr, 0, nullptr, nullptr, buf.err, c.num_sms,
-                             stream);
+    const int* gate = wait ? tp.flags[R] : nullptr;
+    if ((flags & 1) && buf.p_ws != nullptr) {
+      launches += 1;
+      return mb_gemm_bf16_persistent_gated(xn, Wt, Y, nullptr, T, N, c.hidden, c.hidden, c.hidden, ldy, ldy,
+                                           flags, 0, 0, 0, buf.p_ws, buf.p_counters, buf.err, c.num_sms, gate,
+                                           rows_per_rank, W, stream);
+    }
+    int bn, splits, stages;
+    mb_gemm_bf16_plan(T, N, c.hidden, flags & 1, c.num_sms, &bn, &splits, &stages);
+    if (static_cast<size_t>(splits) * T * N * sizeof(float) > buf.workspace_bytes) splits = 1;
+    launches += splits > 1 ? 2 : 1;
+    return mb_gemm_bf16_gated(xn, Wt, Y, nullptr, T, N, c.hidden, c.hidden, c.hidden, ldy, ldy, flags, bn,
+                              splits, stages, buf.workspace, buf.err, c.num_sms, gate, rows_per_rank, W, stream);
   };
-  // row-parallel GEMM whose partial tiles go straight to the owners, then reduce + norm (+ gather)
-  auto gemm_push_reduce_norm = [&](const void* X, const void* Wt, int K, const void* gamma, bool last) {
-    int expected = 0, splits = 1;
-    MB_TRY(mb_gemm_bf16_comm(X, Wt, partial, T, c.hidden, K, K, K, c.hidden, 32, 0, 0, W, R, rows_per_rank,
-                             tp.flags, tp.partial, max_slots, &expected, &splits, buf.err, c.num_sms, stream));
-    launches += 2;
+  // row-parallel GEMM, then reduce-scatter + residual + norm + gather of the normalised rows
+  auto row_parallel_reduce_norm = [&](const void* X, const void* Wt, int K, const void* gamma, bool last) {
+    int expected = 0, splits = 1, mode = 0;
+    if (push) {
+      MB_TRY(mb_gemm_bf16_comm(X, Wt, partial, T, c.hidden, K, K, K, c.hidden, 32, 0, 0, W, R, rows_per_rank,
+                               tp.flags, tp.partial, max_slots, &expected, &splits, buf.err, c.num_sms, stream));
+      launches += 1;
+      mode |= 1;
+    } else {
+      MB_TRY(gemm(X, Wt, partial, T, c.hidden, K, K, c.hidden, 0));
+    }
+    // the last reduce of the step closes with a barrier: the logits path reads every row of xn
+    if (gate_on && !last) mode |= 2;
+    launches += 1;
     return mb_tp_rs_norm_ag_ex(W, R, tp.partial, tp.xn, tp.flags, tp.h_local, gamma, T, c.hidden, rows_per_rank,
-                               c.eps, c.norm_weight_offset, c.multiply_before_cast, 1, last ? 1 : 3, W * splits,
+                               c.eps, c.norm_weight_offset, c.multiply_before_cast, 1, mode, W * splits,
                                expected, buf.err, stream);
   };
 
+  mark("begin", stream);
   if (in.future_src != nullptr) {
     MB_TRY(mb_realize_future_tokens(const_cast<int64_t*>(in.tokens), in.future_src, buf.sampled, T, stream));
     launches += 1;
@@ -183,18 +241,17 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
   MB_TRY(mb_rmsnorm(buf.h, layers[0].attn_norm, xn, T, c.hidden, c.hidden, c.hidden, c.eps,
                     c.norm_weight_offset, c.multiply_before_cast, stream));
   launches += 3;
+  mark("embed", stream);
   for (int l = 0; l < c.n_layers; ++l) {
     const DecoderLayerWeights& w = layers[l];
     const long long hd = c.head_dim;
-    if (fused) {
-      MB_TRY(gemm_gathered(w.wqkv, buf.qkv, qkv_dim, qkv_dim, 0, l > 0));
-    } else {
-      MB_TRY(gemm(xn, w.wqkv, buf.qkv, T, qkv_dim, c.hidden, c.hidden, qkv_dim, 0));
-    }
+    MB_TRY(gemm_gathered(w.wqkv, buf.qkv, qkv_dim, qkv_dim, 0, gate_on && l > 0));
+    mark("gemm_qkv", stream);
     char* kbase = static_cast<char*>(kv.base) + 2 * (static_cast<int64_t>(l) * kv.layer_stride);
     MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, T,
                             c.n_q, c.n_kv, c.head_dim, c.page_size, kv.page_stride, kv.head_stride,
                             c.rope_interleaved, stream));
+    mark("rope_kv_store", stream);
     if (c.attn_impl == 1 && c.page_size % 64 == 0) {
       MB_TRY(mb_paged_attention_tma(
           buf.qkv, qkv_dim, buf.attn, q_dim, kv.base, kv.total_elems / hd,
@@ -211,19 +268,14 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
                                 c.attn_scale, stream));
     }
     launches += 2;
+    mark("attention", stream);
     const void* next_norm = l + 1 < c.n_layers ? layers[l + 1].attn_norm : final_norm;
-    if (fused) {
-      MB_TRY(gemm_push_reduce_norm(buf.attn, w.wo, q_dim, w.mlp_norm, false));
-      MB_TRY(gemm_gathered(w.wgu, buf.act, c.inter, c.inter, 1, true));
-      // the last reduce of the step closes with a barrier: the logits path reads every row of xn
-      MB_TRY(gemm_push_reduce_norm(buf.act, w.wd, c.inter, next_norm, l + 1 == c.n_layers));
-    } else {
-      MB_TRY(gemm(buf.attn, w.wo, partial, T, c.hidden, q_dim, q_dim, c.hidden, 0));
-      MB_TRY(reduce_norm(w.mlp_norm));
-      MB_TRY(gemm(xn, w.wgu, buf.act, T, c.inter, c.hidden, c.hidden, c.inter, 1));
-      MB_TRY(gemm(buf.act, w.wd, partial, T, c.hidden, c.inter, c.inter, c.hidden, 0));
-      MB_TRY(reduce_norm(next_norm));
-    }
+    MB_TRY(row_parallel_reduce_norm(buf.attn, w.wo, q_dim, w.mlp_norm, false));
+    mark("gemm_o+rs_norm_ag", stream);
+    MB_TRY(gemm_gathered(w.wgu, buf.act, c.inter, c.inter, 1, gate_on));
+    mark("gemm_gate_up", stream);
+    MB_TRY(row_parallel_reduce_norm(buf.act, w.wd, c.inter, next_norm, l + 1 == c.n_layers));
+    mark("gemm_down+rs_norm_ag", stream);
   }
   if (in.n_logits > 0) {
     // xn already holds the final-normalised rows of every token on every rank
@@ -234,11 +286,13 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
                            tp.vocab_local * 4, c.vocab * 4, static_cast<long long>(R) * tp.vocab_local * 4,
                            buf.err, stream));
     launches += 2;
+    mark("lm_head+allgather", stream);
     if (in.do_sample) {
       MB_TRY(mb_sample_topk_topp(static_cast<const float*>(tp.logits[R]), buf.sampled, in.n_logits, c.vocab,
                                  c.vocab, in.temperature, in.top_k, in.top_p, in.min_p, in.seeds,
                                  in.sample_step, stream));
       launches += 1;
+      mark("sample", stream);
     }
   }
   return MB_OK;

@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <string>
+#include <tuple>
 #include <vector>
 
 namespace mb {
@@ -102,9 +104,9 @@ struct TpState {
   void* h_local = nullptr;       // [ceil(max_tokens / world), hidden] bf16 residual slice
   float* logits_local = nullptr; // [max_seqs, vocab / world] fp32
   int vocab_local = 0;
-  // fused = 1: row-parallel GEMMs push their partial tiles into the owners' slots and
-  // column-parallel GEMMs wait per source on ready flags (no barrier between GEMM and collective).
-  // `partial` then holds [slots][rows_per_rank][hidden] and must have room for partial_rows rows.
+  // fused bit0: row-parallel GEMMs push their partial tiles into the owners' slots (`partial` then
+  // holds [slots][rows_per_rank][hidden] and must have room for partial_rows rows).
+  // fused bit1: column-parallel GEMMs wait per source on ready flags instead of a closing barrier.
   int fused = 0;
   long long partial_rows = 0;
 };
@@ -126,8 +128,16 @@ class DecoderExecutor {
   // first launcher error.
   int forward(const StepInputs& in, cudaStream_t stream);
 
+  // Per-kernel timing of eager (not graph-captured) steps: when `profiling` is set, an event is
+  // recorded after every launch group; profile_ms() synchronises and returns, per label, the
+  // number of intervals and their summed duration since the last call.
+  bool profiling = false;
+  void mark(const char* label, cudaStream_t stream);
+  std::vector<std::tuple<std::string, int, double>> profile_ms();
+
  private:
   int forward_tp(const StepInputs& in, cudaStream_t stream);
+  std::vector<std::pair<const char*, cudaEvent_t>> marks_;
 };
 
 }  // namespace mb

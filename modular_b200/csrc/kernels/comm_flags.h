@@ -9,7 +9,8 @@
 //   kReady + src      "rows of rank src have landed in your activation buffer" epoch (remote write)
 //   kReadyEpoch       how many signalling reduce+norm kernels this rank has run (local)
 //   kPushTarget       value kPushCount reaches once all partial tiles of the current GEMM landed
-//   kPushCount        incremented (remote atomics) by every GEMM CTA that pushed a partial tile here
+//   kPushCount        partial tiles that have landed here (one remote add per source rank and GEMM)
+//   kPushLocal + o    local count of this rank's GEMM CTAs that finished a tile destined for owner o
 #pragma once
 
 namespace mb {
@@ -22,6 +23,7 @@ constexpr int kReady = 40;                          // 40..47
 constexpr int kReadyEpoch = 48;
 constexpr int kPushTarget = 49;
 constexpr int kPushCount = 64;                      // on a cache line of its own
+constexpr int kPushLocal = 72;                      // 72..79: tiles of the running GEMM finished per owner
 constexpr int kTpFlagInts = 96;
 
 }  // namespace mb

@@ -9,10 +9,11 @@
 //
 //   GEMM -> reduce-scatter   (row-parallel linear: attention output, MLP down)
 //       The epilogue stores every output row straight into the partial-sum slot of the rank that
-//       owns the row (16-byte stores over NVLink, 256 contiguous bytes per row and tile), then
-//       the CTA bumps a counter on each owner it touched. The owner's reduce+norm kernel waits
-//       for the counter, so the transfer of tile i overlaps the math of tile i+1 and nothing is
-//       ever staged in a local partial buffer. With split-K every split owns a slot.
+//       owns the row (16-byte stores over NVLink, 256 contiguous bytes per row and tile). CTAs
+//       count their finished tiles per owner on a local word; the last one forwards the count to
+//       the owner with one remote add. The owner's reduce+norm kernel waits for that counter, so
+//       the transfer of tile i overlaps the math of tile i+1 and nothing is ever staged in a
+//       local partial buffer. With split-K every split owns a slot.
 //
 // Tile structure is that of gemm_tcgen05.cu: weights on the UMMA M side (128 rows per CTA),
 // tokens on the N side (runtime BN), warp 0 = TMA, warp 1 = MMA issue, warps 2-5 = epilogue.
@@ -217,11 +218,21 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     tmem_dealloc(tmem_base, tmem_cols);
   }
   if (ca.push && warp == 2 && k_iters > 0 && *abort_word == 0) {
-    // one count per (CTA, owner touched); the owner knows how many to expect
+    // Tell each owner this CTA touched that its tile has landed. Remote atomics on one word are
+    // slow (they serialise over NVLink), so CTAs count on a local word per owner and only the last
+    // one of this GEMM forwards the whole count with a single remote add.
     const int o_lo = t0 / ca.rows_per_rank, o_hi = t_last / ca.rows_per_rank;
     if (lane >= o_lo && lane <= o_hi && lane < ca.world) {
-      __threadfence_system();
-      red_release_sys_add(ca.peer_flags[lane] + kPushCount, 1);
+      const int lo = lane * ca.rows_per_rank;
+      const int hi = min(lo + ca.rows_per_rank, M) - 1;
+      const int total = (hi / BN - lo / BN + 1) * static_cast<int>(gridDim.y * gridDim.z);
+      __threadfence_system();  // this CTA's remote stores are visible before it is counted
+      const int prev = atomicAdd(ca.flags_local + kPushLocal + lane, 1);
+      if (prev == total - 1) {
+        ca.flags_local[kPushLocal + lane] = 0;  // every CTA of this GEMM has arrived: reset for the next
+        __threadfence_system();
+        red_release_sys_add(ca.peer_flags[lane] + kPushCount, total);
+      }
     }
   }
 }

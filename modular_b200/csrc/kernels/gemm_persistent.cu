@@ -35,6 +35,7 @@
 
 #include "../common/api.h"
 #include "../common/ptx.cuh"
+#include "comm_flags.h"
 #include "gemm_common.h"
 
 namespace mb {
@@ -64,6 +65,11 @@ struct Params {
   int G2;            // CTAs taking part in the stream-K phase
   int dbg;           // measurement aid: bit0 skip the fix-up reduction, bit1 skip the partial store too
   long long units2;  // K blocks in the stream-K phase = (tiles - tiles_dp) * kb
+  // Tensor-parallel all-gather -> GEMM gating (nullptr = off): token rows [s*rpr, (s+1)*rpr) are
+  // pushed into X by rank s, which then raises flag kReady+s of this rank's flag array.
+  const int* gate_flags;
+  int gate_rpr, gate_world;
+  int packed_kb;     // > 0: W is pre-tiled [rows/128][K/64][128][64]; value = K/64
 };
 
 struct Tail {
@@ -212,6 +218,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
       while (ok && it.next(s)) {
         const int n0 = (s.tile / p.m_tiles) * kBM;
         const int t0 = (s.tile % p.m_tiles) * p.BN;
+        if (p.gate_flags != nullptr) {
+          const int t_last = min(t0 + p.BN, p.M) - 1;
+          const int want = ld_volatile(p.gate_flags + kReadyEpoch);
+          for (int src = t0 / p.gate_rpr; src <= t_last / p.gate_rpr && src < p.gate_world; ++src)
+            ok = ok && wait_flag_ge(p.gate_flags + kReady + src, want, p.err, 205);
+          asm volatile("fence.proxy.async;" ::: "memory");  // TMA reads after the acquire
+          if (!ok) { *abort_word = 205; break; }
+        }
         for (int kbi = s.kb0; kbi < s.kb1; ++kbi, ++n) {
           const int st = n % p.stages;
           const uint32_t ph = (n / p.stages) & 1;
@@ -219,8 +233,15 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
           uint8_t* sa = smem + st * stage_bytes;
           mbar_arrive_expect_tx(&tail->full[st], stage_bytes);
           const int kc = kbi * kBK;
-          tma_load_2d(sa, &tmW, &tail->full[st], kc, n0);
-          if (DUAL) tma_load_2d(sa + kATile, &tmW, &tail->full[st], kc, p.dual_rows + n0);
+          if (p.packed_kb > 0) {
+            tma_load_2d(sa, &tmW, &tail->full[st], 0, ((n0 >> 7) * p.packed_kb + kbi) << 7);
+            if (DUAL)
+              tma_load_2d(sa + kATile, &tmW, &tail->full[st], 0,
+                          (((p.dual_rows + n0) >> 7) * p.packed_kb + kbi) << 7);
+          } else {
+            tma_load_2d(sa, &tmW, &tail->full[st], kc, n0);
+            if (DUAL) tma_load_2d(sa + kATile, &tmW, &tail->full[st], kc, p.dual_rows + n0);
+          }
           tma_load_2d(sa + a_bytes, &tmX, &tail->full[st], kc, t0);
         }
       }
@@ -483,9 +504,21 @@ extern "C" int mb_gemm_bf16_persistent(const void* X, const void* W, void* Y, co
                                        int N, int K, int ldx, int ldw, int ldy, int ldr, int flags,
                                        int bn, int stages, int force_mode, void* ws, int* counters,
                                        int* err, int num_sms, cudaStream_t stream) {
+  return mb_gemm_bf16_persistent_gated(X, W, Y, R, M, N, K, ldx, ldw, ldy, ldr, flags, bn, stages, force_mode,
+                                       ws, counters, err, num_sms, nullptr, 1, 0, stream);
+}
+
+// Same kernel with tensor-parallel gating of the token tiles (see Params::gate_flags).
+extern "C" int mb_gemm_bf16_persistent_gated(const void* X, const void* W, void* Y, const void* R, int M,
+                                             int N, int K, int ldx, int ldw, int ldy, int ldr, int flags,
+                                             int bn, int stages, int force_mode, void* ws, int* counters,
+                                             int* err, int num_sms, const int* gate_flags, int gate_rpr,
+                                             int gate_world, cudaStream_t stream) {
   using namespace mb::pg;
+  if (gate_flags != nullptr && (gate_rpr < 1 || gate_world < 1 || gate_world > mb::kMaxRanks)) return MB_ERR_SHAPE;
   if (M <= 0 || N <= 0) return MB_OK;
-  const bool dual = flags & 1, resid = flags & 2, f32 = flags & 4, pdl = flags & 8;
+  const bool dual = flags & 1, resid = flags & 2, f32 = flags & 4, pdl = flags & 8, packed = flags & 64;
+  if (packed && (K % kBK || N % kBM || ldw != K)) return MB_ERR_SHAPE;
   if (K % 8 || ldx % 8 || ldw % 8 || N % 8 || (!f32 && ldy % 8) || (resid && ldr % 8)) return MB_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(Y) |
        reinterpret_cast<uintptr_t>(R)) & 15)
@@ -499,6 +532,8 @@ extern "C" int mb_gemm_bf16_persistent(const void* X, const void* W, void* Y, co
   }
   if (bn % 16 || bn < 16 || bn > max_bn) return MB_ERR_SHAPE;
   Params p;
+  p.gate_flags = gate_flags; p.gate_rpr = gate_rpr; p.gate_world = gate_world;
+  p.packed_kb = packed ? K / kBK : 0;
   p.Y = Y; p.R = static_cast<const __nv_bfloat16*>(R);
   p.ws = static_cast<float*>(ws); p.counters = counters; p.err = err;
   p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.ldr = ldr; p.dual_rows = N;
@@ -543,7 +578,8 @@ extern "C" int mb_gemm_bf16_persistent(const void* X, const void* W, void* Y, co
   else if (p.tiles < num_sms) grid = p.tiles;
   if (grid < 1) grid = 1;
   CUtensorMap tw, tx;
-  int rc = cached_tmap(&tw, W, dual ? 2 * N : N, K, ldw, kBM, 2);
+  int rc = packed ? cached_tmap(&tw, W, static_cast<uint64_t>(dual ? 2 * N : N) * p.packed_kb, kBK, kBK, kBM, 2)
+                  : cached_tmap(&tw, W, dual ? 2 * N : N, K, ldw, kBM, 2);
   if (rc != MB_OK) return rc;
   rc = cached_tmap(&tx, X, M, K, ldx, bn, 2);
   if (rc != MB_OK) return rc;

@@ -30,6 +30,7 @@
 
 #include "../common/ptx.cuh"
 #include "../common/api.h"
+#include "comm_flags.h"
 #include "gemm_common.h"
 
 namespace mb {
@@ -59,7 +60,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                void* __restrict__ Yv, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
                int ldy, int ldr, int dual_rows, int k_per_split, int BN, int stages,
                uint32_t tmem_cols, int* err, const int32_t* __restrict__ expert_offsets,
-               int w_rows_per_expert) {
+               int w_rows_per_expert, const int* gate_flags, int gate_rpr, int gate_world,
+               int packed_kb) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -118,7 +120,21 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    bool ready = true;
+    if (gate_flags != nullptr) {
+      // Tensor-parallel all-gather -> GEMM: token rows [s*rpr, (s+1)*rpr) are pushed into X by rank
+      // s, which then raises flag kReady+s; wait only for the sources this token tile covers.
+      const int t_last = min(t0 + BN, M) - 1;
+      const int s_lo = t0 / gate_rpr, s_hi = t_last / gate_rpr;
+      const int want = ld_volatile(gate_flags + kReadyEpoch);
+      bool mine = true;
+      if (lane >= s_lo && lane <= s_hi && lane < gate_world)
+        mine = wait_flag_ge(gate_flags + kReady + lane, want, err, 105);
+      ready = __all_sync(0xffffffffu, mine);
+      asm volatile("fence.proxy.async;" ::: "memory");  // TMA reads after the acquire
+      if (!ready && lane == 0) *abort_word = 105;
+    }
+    if (lane == 0 && ready) {
       for (int it = 0; it < k_iters; ++it) {
         const int s = it % stages;
         const uint32_t ph = (it / stages) & 1;
@@ -127,8 +143,18 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         uint8_t* sb = sa + a_bytes;
         mbar_arrive_expect_tx(&tail->full[s], stage_bytes);
         const int kc = k_begin + it * kBK;
-        tma_load_2d(sa, &tmW, &tail->full[s], kc, w_row0 + n0);
-        if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, &tail->full[s], kc, w_row0 + dual_rows + n0);
+        if (packed_kb > 0) {
+          // pre-tiled weights: tile (row block, K block) is one contiguous 16 KiB run in memory,
+          // addressed as 128 rows of the [tiles * 128, 64] view
+          const int kb = kc / kBK;
+          tma_load_2d(sa, &tmW, &tail->full[s], 0, (((w_row0 + n0) >> 7) * packed_kb + kb) << 7);
+          if (DUAL)
+            tma_load_2d(sa + kATileBytes, &tmW, &tail->full[s], 0,
+                        (((w_row0 + dual_rows + n0) >> 7) * packed_kb + kb) << 7);
+        } else {
+          tma_load_2d(sa, &tmW, &tail->full[s], kc, w_row0 + n0);
+          if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, &tail->full[s], kc, w_row0 + dual_rows + n0);
+        }
         tma_load_2d(sb, &tmX, &tail->full[s], kc, t0);
       }
     }
@@ -353,7 +379,8 @@ static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, con
                       int N, int K, int ldy, int ldr, int dual_rows, int k_per_split, int splits,
                       int BN, int stages, int* err, cudaStream_t stream,
                       const int32_t* expert_offsets = nullptr, int n_experts = 0,
-                      int w_rows_per_expert = 0) {
+                      int w_rows_per_expert = 0, const int* gate_flags = nullptr, int gate_rpr = 1,
+                      int gate_world = 0, int packed_kb = 0) {
   const int stage_bytes = kATileBytes * (DUAL ? 2 : 1) + BN * kBK * 2;
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes +
                       sizeof(GemmSmemTail) + 1024;
@@ -369,7 +396,8 @@ static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, con
   const uint32_t tmem_cols = pow2_cols(DUAL ? 2 * BN : BN);
   kern<<<grid, kGemmThreads, smem, stream>>>(tw, tx, Y, static_cast<const __nv_bfloat16*>(R), M, N,
                                              K, ldy, ldr, dual_rows, k_per_split, BN, stages,
-                                             tmem_cols, err, expert_offsets, w_rows_per_expert);
+                                             tmem_cols, err, expert_offsets, w_rows_per_expert, gate_flags,
+                                             gate_rpr, gate_world, packed_kb);
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
@@ -414,8 +442,23 @@ extern "C" int mb_gemm_bf16(const void* X, const void* W, void* Y, const void* R
                             int K, int ldx, int ldw, int ldy, int ldr, int flags, int bn,
                             int splits, int stages, void* workspace, int* err, int num_sms,
                             cudaStream_t stream) {
+  return mb_gemm_bf16_gated(X, W, Y, R, M, N, K, ldx, ldw, ldy, ldr, flags, bn, splits, stages, workspace, err,
+                            num_sms, nullptr, 1, 0, stream);
+}
+
+// Same GEMM whose token tiles wait for the tensor-parallel ready flags of the ranks that push the
+// rows of X (`gate_flags` = this rank's flag array; nullptr = no gating).
+extern "C" int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const void* R, int M, int N,
+                                  int K, int ldx, int ldw, int ldy, int ldr, int flags, int bn,
+                                  int splits, int stages, void* workspace, int* err, int num_sms,
+                                  const int* gate_flags, int gate_rpr, int gate_world,
+                                  cudaStream_t stream) {
   if (M <= 0 || N <= 0) return MB_OK;
-  const bool dual = flags & 1, resid = flags & 2, f32 = flags & 4;
+  if (gate_flags != nullptr && (gate_rpr < 1 || gate_world < 1 || gate_world > kMaxRanks)) return MB_ERR_SHAPE;
+  const bool dual = flags & 1, resid = flags & 2, f32 = flags & 4, packed = flags & 64;
+  // bit6: W is pre-tiled as [rows/128][K/64][128][64] (mb_pack_weight_tiles layout)
+  if (packed && (K % kBK || N % kBM || ldw != K)) return MB_ERR_SHAPE;
+  const int packed_kb = packed ? K / kBK : 0;
   if (K % 8 || ldx % 8 || ldw % 8 || N % 8 || (!f32 && ldy % 8) || (resid && ldr % 8))
     return MB_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) |
@@ -438,7 +481,8 @@ extern "C" int mb_gemm_bf16(const void* X, const void* W, void* Y, const void* R
   }
   const int w_rows = dual ? 2 * N : N;
   CUtensorMap tw, tx;
-  int rc = cached_tmap(&tw, W, w_rows, K, ldw, kBM, 2);
+  int rc = packed ? cached_tmap(&tw, W, static_cast<uint64_t>(w_rows) * packed_kb, kBK, kBK, kBM, 2)
+                  : cached_tmap(&tw, W, w_rows, K, ldw, kBM, 2);
   if (rc != MB_OK) return rc;
   rc = cached_tmap(&tx, X, M, K, ldx, bn, 2);
   if (rc != MB_OK) return rc;
@@ -451,7 +495,8 @@ extern "C" int mb_gemm_bf16(const void* X, const void* W, void* Y, const void* R
   }
   if (splits > 1) {
     rc = launch_cfg<false, EPI_F32>(tw, tx, workspace, nullptr, M, N, K, N, 0, 0, k_per_split,
-                                    splits, bn, stages, err, stream);
+                                    splits, bn, stages, err, stream, nullptr, 0, 0, gate_flags, gate_rpr,
+                                    gate_world, packed_kb);
     if (rc != MB_OK) return rc;
     if (f32) return MB_ERR_SHAPE;  // fp32 output is never split
     const size_t total4 = (static_cast<size_t>(M) * N + 3) / 4;
@@ -462,15 +507,16 @@ extern "C" int mb_gemm_bf16(const void* X, const void* W, void* Y, const void* R
   }
   if (dual)
     return launch_cfg<true, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, N, K, 1, bn, stages, err,
-                                      stream);
+                                      stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb);
   if (f32)
     return launch_cfg<false, EPI_F32>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err,
-                                      stream);
+                                      stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb);
   if (resid)
     return launch_cfg<false, EPI_BF16_RESIDUAL>(tw, tx, Y, R, M, N, K, ldy, ldr, 0, K, 1, bn,
-                                                stages, err, stream);
+                                                stages, err, stream, nullptr, 0, 0, gate_flags, gate_rpr,
+                                                gate_world, packed_kb);
   return launch_cfg<false, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err,
-                                     stream);
+                                     stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb);
 }
 
 // Grouped GEMM for mixture-of-experts layers: rows [offsets[e], offsets[e+1]) of X (tokens in

@@ -260,7 +260,8 @@ class Llama3Model:
             vocab_local = self.w.lm_head.shape[0]
             # fused GEMM+collective path: partial slots [slot][rows_per_rank][hidden]; W * rows_per_rank
             # can exceed T by W - 1 rows
-            fused = os.environ.get("MB200_TP_FUSED", "1") != "0"
+            # bit0: GEMM -> reduce-scatter pushes, bit1: flag-gated all-gather -> GEMM
+            fused = int(os.environ.get("MB200_TP_FUSED", "2"))
             partial_rows = T + W
             sym_partial = tp.alloc_symmetric(partial_rows * c.hidden_size, dt)
             sym_xn = tp.alloc_symmetric(T * c.hidden_size, dt)

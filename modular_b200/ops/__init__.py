@@ -259,3 +259,46 @@ def linear_fp8(x, wq, ws, residual=None, out=None):
     """bf16 activations in: quantise per token group, then the block-scaled fp8 GEMM."""
     xq, xs = quant_fp8_group128(x)
     return linear_fp8_blockscaled(xq, xs, wq, ws, residual, out)
+
+
+# ---------------------------------------------------------------------- multi-head latent attention
+def batched_linear(x, w, out=None):
+    """Per-batch ``x[b] @ w[b].T``. x: [B, M, K], w: [B, N, K] -> [B, M, N].
+
+    On CUDA this is the grouped tcgen05 GEMM with one group per batch entry (used for the MLA
+    weight absorption, where the batch is the attention head).
+    """
+    if not x.is_cuda or x.dtype != torch.bfloat16:
+        return ref.batched_linear(x, w)
+    B, M, K = x.shape
+    N = w.shape[1]
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty(B, M, N, dtype=x.dtype, device=x.device)
+    key = (x.device.index or 0, B, M)
+    offs = _BATCH_OFFSETS.get(key)
+    if offs is None:
+        offs = (torch.arange(B + 1, dtype=torch.int32) * M).to(x.device)
+        _BATCH_OFFSETS[key] = offs
+    _lib().grouped_gemm_bf16(x.view(B * M, K), w.contiguous(), out.view(B * M, N), offs, M, False, 0)
+    return out
+
+
+_BATCH_OFFSETS: dict = {}
+
+
+def mla_kv_store(c_kv, k_rope, slots, cache):
+    """cache[slot] = [c_kv | k_rope] for every token with slot >= 0 (one latent row per token)."""
+    if c_kv.is_cuda and c_kv.dtype == torch.bfloat16 and hasattr(_lib(), "mla_kv_store"):
+        _lib().mla_kv_store(c_kv, k_rope, slots, cache)
+        return
+    ref.mla_kv_store(c_kv, k_rope, slots, cache)
+
+
+def mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, scale, plan=None):
+    """Absorbed-form multi-head latent attention over a paged latent cache; returns [T, h, R]."""
+    if q_lat.is_cuda and q_lat.dtype == torch.bfloat16 and hasattr(_lib(), "mla_paged_attention"):
+        out = torch.empty_like(q_lat)
+        _lib().mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, out, scale)
+        return out
+    return ref.mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, scale)

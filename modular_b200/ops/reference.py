@@ -229,3 +229,48 @@ def linear_fp8_blockscaled(xq, xs, wq, ws, residual=None, out_dtype=torch.bfloat
     if residual is not None:
         y = (y.float() + residual.float()).to(out_dtype)
     return y
+
+
+# ---------------------------------------------------------------------- multi-head latent attention
+def mla_kv_store(c_kv, k_rope, slots, cache):
+    """Scatter one latent row per token: cache[page, offset] = [c_kv (kv_lora_rank) | k_rope].
+
+    cache: [pages, page_size, kv_lora_rank + rope_dim] view of one layer; slots < 0 are skipped.
+    """
+    page_size = cache.shape[1]
+    ok = slots >= 0
+    pg = torch.div(slots.clamp(min=0), page_size, rounding_mode="floor")
+    off = slots.clamp(min=0) % page_size
+    row = torch.cat((c_kv, k_rope), dim=-1).to(cache.dtype)
+    cache[pg[ok], off[ok]] = row[ok]
+
+
+def mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, scale):
+    """Absorbed-form MLA over the latent cache (one shared "KV head" for all query heads).
+
+    q_lat: [T, h, R] queries already multiplied by W_uk; q_rope: [T, h, Dr] rotated;
+    cache: [pages, page_size, R + Dr]. Returns the attention output in latent space [T, h, R]
+    (the caller multiplies by W_uv).
+    """
+    T, h, R = q_lat.shape
+    out = torch.zeros(T, h, R, dtype=q_lat.dtype, device=q_lat.device)
+    page_size = cache.shape[1]
+    for b in range(block_table.shape[0]):
+        qs, ql, kl = int(q_start[b]), int(q_len[b]), int(kv_len[b])
+        if ql == 0:
+            continue
+        n_pages = (kl + page_size - 1) // page_size
+        kv = cache[block_table[b, :n_pages].long()].reshape(-1, cache.shape[-1])[:kl].float()
+        c, kr = kv[:, :R], kv[:, R:]
+        s = (torch.einsum("qhr,kr->hqk", q_lat[qs:qs + ql].float(), c) +
+             torch.einsum("qhd,kd->hqk", q_rope[qs:qs + ql].float(), kr)) * scale
+        qi = torch.arange(ql, device=s.device).unsqueeze(1) + (kl - ql)
+        ki = torch.arange(kl, device=s.device).unsqueeze(0)
+        p = torch.softmax(s.masked_fill(ki > qi, float("-inf")), dim=-1)
+        out[qs:qs + ql] = torch.einsum("hqk,kr->qhr", p, c).to(out.dtype)
+    return out
+
+
+def batched_linear(x, w):
+    """x: [B, M, K], w: [B, N, K] -> [B, M, N] (per-batch ``x @ w.T``)."""
+    return torch.einsum("bmk,bnk->bmn", x.float(), w.float()).to(x.dtype)

@@ -35,7 +35,7 @@ def test_fused_gemm_collectives(world):
     assert any(e[1] > 1 for e in res[0]["errs"]), "no case exercised split-K pushes"
 
 
-@pytest.mark.parametrize("world,fused", [(2, "1"), (2, "0"), (4, "1")])
+@pytest.mark.parametrize("world,fused", [(2, "3"), (2, "0"), (2, "1"), (2, "2"), (4, "3")])
 def test_tp_matches_single_gpu(world, fused):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
