@@ -612,6 +612,34 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                              error_flag(), cur_stream()),
              "tp_allgather");
   });
+  // ---- multi-head latent attention ----
+  // cache: [pages, page_size, R + 64] view of one layer (page stride free, rows contiguous)
+  m.def("mla_kv_store", [](const Tensor& c_kv, const Tensor& k_rope, const Tensor& slots, Tensor& cache) {
+    need_cuda(c_kv, "c_kv");
+    TORCH_CHECK(c_kv.stride(1) == 1 && k_rope.stride(1) == 1 && k_rope.size(1) == 64 &&
+                    cache.stride(2) == 1 && cache.stride(1) == cache.size(2) &&
+                    cache.size(2) == c_kv.size(1) + 64 && slots.scalar_type() == at::kLong,
+                "mla_kv_store layout");
+    check_rc(mb_mla_kv_store(c_kv.data_ptr(), k_rope.data_ptr(), slots.data_ptr<int64_t>(), cache.data_ptr(),
+                             c_kv.size(0), c_kv.size(1), c_kv.stride(0), k_rope.stride(0), cache.size(1),
+                             cache.stride(0), cur_stream()),
+             "mla_kv_store");
+  });
+  m.def("mla_paged_attention", [](const Tensor& q_lat, const Tensor& q_rope, const Tensor& cache,
+                                  const Tensor& block_table, const Tensor& q_start, const Tensor& q_len,
+                                  const Tensor& kv_len, Tensor& out, double scale) {
+    need_cuda(q_lat, "q_lat");
+    TORCH_CHECK(q_lat.is_contiguous() && q_rope.is_contiguous() && out.is_contiguous() && q_rope.size(2) == 64 &&
+                    cache.stride(2) == 1 && cache.stride(1) == cache.size(2) &&
+                    cache.size(2) == q_lat.size(2) + 64 && block_table.stride(1) == 1,
+                "mla_paged_attention layout");
+    check_rc(mb_mla_paged_attention(q_lat.data_ptr(), q_rope.data_ptr(), out.data_ptr(), cache.data_ptr(),
+                                    cache.stride(0), block_table.data_ptr<int32_t>(), block_table.stride(0),
+                                    q_start.data_ptr<int32_t>(), q_len.data_ptr<int32_t>(),
+                                    kv_len.data_ptr<int32_t>(), q_lat.size(0), block_table.size(0),
+                                    q_lat.size(1), q_lat.size(2), cache.size(1), scale, cur_stream()),
+             "mla_paged_attention");
+  });
   // ---- expert parallelism ----
   m.def("ep_flag_ints", []() { return mb_ep_flag_ints(); });
   m.def("ep_dispatch", [](int world, int rank, const std::vector<int64_t>& recv_x,

@@ -86,6 +86,14 @@ int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo, const voi
                            const int32_t* decode_seq, int n_q, int n_kv, int head_dim, int page_size,
                            float scale, int* err, cudaStream_t stream);
 
+// ---- multi-head latent attention over a paged latent cache (mla.cu) ------------------------
+int mb_mla_paged_attention(const void* q_lat, const void* q_rope, void* out, const void* cache,
+                           long long page_stride, const int32_t* block_table, int bt_stride,
+                           const int32_t* q_start, const int32_t* q_len, const int32_t* kv_len, int T,
+                           int B, int n_heads, int R, int page_size, float scale, cudaStream_t stream);
+int mb_mla_kv_store(const void* c_kv, const void* k_rope, const int64_t* slots, void* cache, int T, int R,
+                    int ld_c, int ld_r, int page_size, long long page_stride, cudaStream_t stream);
+
 // ---- mixture of experts (moe.cu, grouped mode of gemm_tcgen05.cu) ---------------------------
 int mb_moe_router_group_limited(const float* logits, const float* bias, int32_t* topk_ids, float* topk_w,
                                 int T, int E, int n_group, int topk_group, int top_k, int norm_topk,

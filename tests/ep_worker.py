@@ -30,6 +30,8 @@ def main():
     else:
         dev = torch.device("cpu")
         dist.init_process_group("gloo")
+    if len(sys.argv) > 2 and sys.argv[2] == "deepseek":
+        return deepseek_model(rank, world, dev)
     cfg = MoEConfig(hidden_size=512, moe_intermediate_size=256, n_routed_experts=16, num_experts_per_tok=4,
                     n_shared_experts=1, n_group=4, topk_group=2, routed_scaling_factor=2.5)
     full = MoE.random_init(cfg, dev, torch.bfloat16, seed=3, std=0.05)
@@ -55,6 +57,43 @@ def main():
     out = {"rank": rank, "errs": errs, "dropped": drops}
     gathered = [None] * world
     dist.all_gather_object(gathered, out)
+    if rank == 0:
+        print("EP_RESULT " + json.dumps(gathered), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def deepseek_model(rank, world, dev):
+    """A tiny DeepSeek-V3 with expert-parallel MoE layers (data-parallel attention: every rank runs
+    its own sequence) against the same model with all experts local."""
+    from modular_b200 import ops
+    from modular_b200.models.deepseek_v3 import DeepseekV3Config, DeepseekV3Model, DeepseekV3Weights
+    from modular_b200.parallel.ep import EPContext
+    from modular_b200.parallel.tp import TPContext
+
+    cfg = DeepseekV3Config.tiny(hidden_size=512, moe_intermediate_size=256, intermediate_size=1024,
+                                kv_lora_rank=128, q_lora_rank=256, num_attention_heads=8)
+    full = DeepseekV3Weights.random_init(cfg, dev, torch.bfloat16, seed=11, std=0.05)
+    El = cfg.n_routed_experts // world
+    mine = DeepseekV3Weights.random_init(cfg, dev, torch.bfloat16, seed=11, std=0.05,
+                                         e_begin=rank * El, e_end=(rank + 1) * El)
+    page, T = 16, 40 + 3 * rank
+    ep = EPContext(TPContext(device=dev), cfg.hidden_size, cfg.n_routed_experts, cfg.num_experts_per_tok,
+                   max_tokens=64)
+    kv = lambda: torch.zeros(8, 1, cfg.num_hidden_layers, 1, page, cfg.latent_dim, dtype=torch.bfloat16, device=dev)
+    m_ep, m_full = DeepseekV3Model(cfg, mine, kv(), ep=ep), DeepseekV3Model(cfg, full, kv())
+    tok = torch.randint(0, cfg.vocab_size, (T,), generator=torch.Generator().manual_seed(rank)).to(dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    slots = torch.arange(T, dtype=torch.long, device=dev) + page
+    bt = torch.tensor([[1, 2, 3, 0]], dtype=torch.int32, device=dev)
+    i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=dev)
+    args = (tok, pos, slots, bt, i32(0), i32(T), i32(T), torch.arange(T, dtype=torch.int32, device=dev))
+    got, want = m_ep.forward_tensors(*args), m_full.forward_tensors(*args)
+    torch.cuda.synchronize()
+    ops.check_device_error()
+    err = float((got - want).abs().max() / want.abs().max())
+    gathered = [None] * world
+    dist.all_gather_object(gathered, {"rank": rank, "errs": [err], "dropped": 0})
     if rank == 0:
         print("EP_RESULT " + json.dumps(gathered), flush=True)
     dist.barrier()
