@@ -59,8 +59,9 @@ class LLM:
                  device_graph_capture: bool = True, graph_batch_sizes: Optional[Sequence[int]] = None,
                  eos_token_ids: Sequence[int] = (), seed: int = 0, tp_size: int = 1,
                  tp_rank: int = 0):
-        from ..models.llama3 import Llama3Config, Llama3Model, Llama3Weights
+        from ..models import family_for
 
+        fam = family_for(model_config)
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -75,34 +76,34 @@ class LLM:
 
             if not on_gpu:
                 raise ValueError("tensor parallelism needs CUDA devices")
+            if not fam.supports_tp:
+                raise ValueError(f"tensor parallelism is not implemented for the {fam.name} family")
             self.tp = TPContext(device=self.device)
             if self.tp.world != tp_size or self.tp.rank != tp_rank:
                 raise ValueError("tp_size / tp_rank do not match the initialised process group")
             full_cfg = model_config
             if weights is None:
-                weights = Llama3Weights.random_init(full_cfg, self.device, dtype, seed=seed)
+                weights = fam.weights_class.random_init(full_cfg, self.device, dtype, seed=seed)
             weights = shard_llama_weights(full_cfg, weights, tp_rank, tp_size)
             model_config = shard_llama_config(full_cfg, tp_size)
             torch.cuda.empty_cache()
         elif weights is None:
-            weights = Llama3Weights.random_init(model_config, self.device, dtype, seed=seed)
+            weights = fam.weights_class.random_init(model_config, self.device, dtype, seed=seed)
         self.weights = weights
         self.max_length = max_length
-        kvp = KVCacheParams(model_config.num_hidden_layers, model_config.num_key_value_heads,
-                            model_config.head_dim, page_size, dtype, False, enable_prefix_caching)
+        kvp = fam.kv_params(model_config, page_size, dtype, enable_prefix_caching)
         if num_kv_pages is None:
             if on_gpu:
                 free, total = torch.cuda.mem_get_info(self.device)
-                act = max_batch_input_tokens * (3 * model_config.hidden_size + 2 * model_config.q_dim
-                                                + 3 * model_config.intermediate_size) * 2
-                act += max_batch_size * model_config.vocab_size * 4 + (256 << 20)
+                act = fam.activation_bytes(model_config, max_batch_input_tokens, max_batch_size)
                 budget = int(free - (1.0 - device_memory_utilization) * total - act)
                 num_kv_pages = kvp.compute_num_device_blocks(budget, max_batch_size * 4, max_length)
             else:
                 num_kv_pages = kvp.compute_num_device_blocks(1 << 62, max_batch_size, max_length)
         self.kv = PagedKVCacheManager(kvp, num_kv_pages, self.device, max_seq_len=max_length)
-        self.model = Llama3Model(model_config, weights, self.kv.kv, max_tokens=max_batch_input_tokens,
-                                 max_seqs=max_batch_size, max_position=max_length, tp=self.tp)
+        extra = {"tp": self.tp} if fam.supports_tp else {}
+        self.model = fam.model_class(model_config, weights, self.kv.kv, max_tokens=max_batch_input_tokens,
+                                     max_seqs=max_batch_size, max_position=max_length, **extra)
         overlap = on_gpu if enable_overlap_scheduler is None else enable_overlap_scheduler
         if graph_batch_sizes is None:
             graph_batch_sizes = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch_size]

@@ -71,6 +71,33 @@ class DeepseekV3Config:
     def latent_dim(self) -> int:
         return self.kv_lora_rank + self.qk_rope_head_dim
 
+    # what the generic engine code asks of any config
+    architectures = ("DeepseekV3ForCausalLM",)
+
+    @property
+    def num_key_value_heads(self) -> int:
+        return 1          # one shared latent row per token
+
+    @property
+    def head_dim(self) -> int:
+        return self.latent_dim
+
+    def to_hf(self) -> dict:
+        d = {k: getattr(self, k) for k in self.__dataclass_fields__}
+        d["architectures"] = list(self.architectures)
+        d["model_type"] = "deepseek_v3"
+        return d
+
+    def param_count(self) -> int:
+        H, h = self.hidden_size, self.num_attention_heads
+        attn = (H * (self.q_lora_rank or 0) + (self.q_lora_rank or H) * h * self.qk_head_dim + H * self.latent_dim
+                + self.kv_lora_rank * h * (self.qk_nope_head_dim + self.v_head_dim) + h * self.v_head_dim * H)
+        dense = 3 * H * self.intermediate_size
+        moe = 3 * H * self.moe_intermediate_size * (self.n_routed_experts + self.n_shared_experts) + H * self.n_routed_experts
+        n_moe = sum(self.is_moe_layer(i) for i in range(self.num_hidden_layers))
+        return (self.num_hidden_layers * attn + n_moe * moe + (self.num_hidden_layers - n_moe) * dense
+                + 2 * self.vocab_size * H)
+
     def is_moe_layer(self, i: int) -> bool:
         return (self.n_routed_experts > 0 and i >= self.first_k_dense_replace
                 and i % self.moe_layer_freq == 0)

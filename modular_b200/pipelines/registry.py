@@ -87,15 +87,13 @@ class PipelineRegistry:
     def plan_memory(self, pc: PipelineConfig, cfg, device: torch.device) -> Optional[MemoryPlan]:
         if device.type != "cuda":
             return None
-        from ..kv_cache import KVCacheParams
+        from ..models import family_for
 
         dtype_bytes = 2
-        kvp = KVCacheParams(cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.head_dim,
-                            pc.model.kv_cache.kv_cache_page_size)
+        fam = family_for(cfg)
+        kvp = fam.kv_params(cfg, pc.model.kv_cache.kv_cache_page_size, torch.bfloat16, True)
         free, total = torch.cuda.mem_get_info(device)
-        act = MemoryEstimator.activation_bytes(cfg.hidden_size, cfg.q_dim, cfg.kv_dim, cfg.intermediate_size,
-                                               cfg.vocab_size, pc.runtime.max_batch_input_tokens,
-                                               pc.runtime.max_batch_size or 256, dtype_bytes)
+        act = fam.activation_bytes(cfg, pc.runtime.max_batch_input_tokens, pc.runtime.max_batch_size or 256)
         return MemoryEstimator.plan_from_sizes(
             free, total, cfg.param_count() * dtype_bytes, act, kvp.bytes_per_page, kvp.page_size,
             pc.model.kv_cache.device_memory_utilization, 0, pc.runtime.max_batch_size,
@@ -170,6 +168,16 @@ def _register_builtin() -> None:
         preset_configs={"llama3.1-8b": Llama3Config.llama31_8b, "llama3.3-70b": Llama3Config.llama33_70b,
                         "tiny-llama": Llama3Config.tiny})
     PIPELINE_REGISTRY.register(llama, allow_override=True)
+
+    from ..models.deepseek_v3 import DeepseekV3Config, DeepseekV3Model, DeepseekV3Weights
+
+    deepseek = SupportedArchitecture(
+        name="DeepseekV3ForCausalLM", config_class=DeepseekV3Config, weights_class=DeepseekV3Weights,
+        model_class=DeepseekV3Model, default_encoding="bfloat16",
+        supported_encodings=("bfloat16", "float32", "float8_e4m3fn"),
+        example_repo_ids=("deepseek-ai/DeepSeek-V3", "deepseek-ai/DeepSeek-R1"),
+        preset_configs={"deepseek-v3": DeepseekV3Config.deepseek_v3, "tiny-deepseek": DeepseekV3Config.tiny})
+    PIPELINE_REGISTRY.register(deepseek, allow_override=True)
 
 
 PIPELINE_REGISTRY.register_lazy(_register_builtin)
