@@ -612,6 +612,30 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                              error_flag(), cur_stream()),
              "tp_allgather");
   });
+  // all-reduce of symmetric bf16 buffers; algo 0 auto / 1 one-shot / 2 two-shot / 3 multimem
+  m.def("tp_allreduce", [](int world, int rank, const std::vector<int64_t>& in_bufs,
+                           const std::vector<int64_t>& out_bufs, Tensor& out, int64_t mc_in,
+                           const std::vector<int64_t>& flags, int64_t n, int algo) {
+    void* a[8] = {}; void* b[8] = {}; int* f[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) {
+      a[i] = reinterpret_cast<void*>(in_bufs[i]);
+      if (!out_bufs.empty()) b[i] = reinterpret_cast<void*>(out_bufs[i]);
+      f[i] = reinterpret_cast<int*>(flags[i]);
+    }
+    check_rc(mb_tp_allreduce(world, rank, a, out_bufs.empty() ? nullptr : b, out.data_ptr(),
+                             reinterpret_cast<const void*>(mc_in), f, n, algo, error_flag(), cur_stream()),
+             "tp_allreduce");
+  });
+  m.def("tp_broadcast", [](int world, int rank, int root, const std::vector<int64_t>& in_bufs, Tensor& out,
+                           const std::vector<int64_t>& flags, int64_t nbytes) {
+    void* a[8] = {}; int* f[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) {
+      a[i] = reinterpret_cast<void*>(in_bufs[i]);
+      f[i] = reinterpret_cast<int*>(flags[i]);
+    }
+    check_rc(mb_tp_broadcast(world, rank, root, a, out.data_ptr(), f, nbytes, error_flag(), cur_stream()),
+             "tp_broadcast");
+  });
   // ---- multi-head latent attention ----
   // cache: [pages, page_size, R + 64] view of one layer (page stride free, rows contiguous)
   m.def("mla_kv_store", [](const Tensor& c_kv, const Tensor& k_rope, const Tensor& slots, Tensor& cache) {

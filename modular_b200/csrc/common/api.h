@@ -134,6 +134,12 @@ int mb_tp_allgather(int world, int rank, void* const* dst_bufs, int* const* flag
                     int rows, int row_bytes, int ld_src, int ld_dst, long long col_off, int* err,
                     cudaStream_t stream);
 
+int mb_tp_allreduce(int world, int rank, void* const* in_bufs, void* const* out_bufs, void* out,
+                    const void* mc_in, int* const* flags, long long n, int algo, int* err,
+                    cudaStream_t stream);
+int mb_tp_broadcast(int world, int rank, int root, void* const* in_bufs, void* out, int* const* flags,
+                    long long nbytes, int* err, cudaStream_t stream);
+
 // ---- expert-parallel dispatch / combine over peer memory (comm_ep.cu) -----------------------
 int mb_ep_flag_ints(void);
 int mb_ep_dispatch(int world, int rank, void* const* recv_x, void* const* recv_meta, int* const* flags,

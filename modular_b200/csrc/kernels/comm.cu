@@ -12,6 +12,8 @@
 //                    activation buffer). The residual stream stays sharded by rows
 //                    (sequence-parallel layout), so only normalised activations cross NVLink.
 //   tp_allgather     push a local [rows, cols] block into a column slot of every peer's buffer.
+//   tp_allreduce     one-shot (small), two-shot (large) and in-switch multimem.ld_reduce variants.
+//   tp_broadcast     pull from the root's buffer.
 //   tp_barrier       all-rank barrier (used between phases that are not fused).
 //
 // Flags: each rank has an int array in symmetric memory. Word layout: [slot][src_rank] where a
@@ -285,6 +287,112 @@ tp_allgather_kernel(TpPeers p, const uint8_t* __restrict__ src, int rows, int ro
   tp_finish_barrier(p, 2, epoch, err);
 }
 
+// ---------------------------------------------------------------------------- all-reduce
+// Sum of every rank's symmetric input buffer a[r] (bf16, n elements, n % 8 == 0) into out (local).
+// One-shot: after a barrier every rank reads all ranks' data itself (W reads of n over NVLink per
+// rank; best for small n). All ranks add in rank order in fp32, so results are bit-identical.
+__device__ __forceinline__ void accum8(float (&acc)[8], const uint4& v) {
+  const bf162* p = reinterpret_cast<const bf162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(p[i]);
+    acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&acc)[8]) {
+  uint4 o;
+  bf162* p = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  return o;
+}
+
+__global__ void __launch_bounds__(256)
+tp_allreduce_1shot_kernel(TpPeers p, bf16* __restrict__ out, long long n, int* err) {
+  const int epoch = ld_volatile(p.flags[p.rank] + kEpochWord) + 1;
+  __syncthreads();
+  tp_barrier_dev(p, 0, epoch, err);  // every rank's input is complete
+  const long long nvec = n >> 3;
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 in[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < p.world) in[r] = reinterpret_cast<const uint4*>(p.a[r])[v];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < p.world) accum8(acc, in[r]);
+    reinterpret_cast<uint4*>(out)[v] = pack8(acc);
+  }
+  tp_finish_barrier(p, 1, epoch, err);  // nobody overwrites its input while a peer still reads it
+}
+
+// Two-shot: each rank reduces the 1/W slice it owns (pulling that slice from every peer), then
+// pushes the reduced slice into every rank's output buffer b[r] (symmetric). 2(W-1)/W * n bytes per
+// rank over NVLink instead of (W-1) * n: the choice for large n.
+__global__ void __launch_bounds__(256)
+tp_allreduce_2shot_kernel(TpPeers p, long long n, int* err) {
+  const int epoch = ld_volatile(p.flags[p.rank] + kEpochWord) + 1;
+  __syncthreads();
+  tp_barrier_dev(p, 0, epoch, err);
+  const long long nvec = n >> 3;
+  const long long per = (nvec + p.world - 1) / p.world;
+  const long long v0 = per * p.rank;
+  const long long v1 = v0 + per < nvec ? v0 + per : nvec;
+  for (long long v = v0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < v1;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 in[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < p.world) in[r] = reinterpret_cast<const uint4*>(p.a[r])[v];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < p.world) accum8(acc, in[r]);
+    const uint4 o = pack8(acc);
+#pragma unroll
+    for (int s = 0; s < kMaxRanks; ++s)
+      if (s < p.world) reinterpret_cast<uint4*>(p.b[(p.rank + s) % p.world])[v] = o;
+  }
+  tp_finish_barrier(p, 1, epoch, err);  // every slice has landed everywhere
+}
+
+// One-shot through the NVSwitch: `mc_in` is the multicast address of the symmetric input, one
+// multimem.ld_reduce returns the sum over all ranks computed inside the switch.
+__global__ void __launch_bounds__(256)
+tp_allreduce_multimem_kernel(TpPeers p, const bf16* __restrict__ mc_in, bf16* __restrict__ out, long long n,
+                             int* err) {
+  const int epoch = ld_volatile(p.flags[p.rank] + kEpochWord) + 1;
+  __syncthreads();
+  tp_barrier_dev(p, 0, epoch, err);
+  const long long nvec = n >> 3;
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 o;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
+                 : "l"(mc_in + v * 8)
+                 : "memory");
+    reinterpret_cast<uint4*>(out)[v] = o;
+  }
+  tp_finish_barrier(p, 1, epoch, err);
+}
+
+// Broadcast n bytes (n % 16 == 0) of root's symmetric buffer a[root] into out on every rank (pull).
+__global__ void __launch_bounds__(256)
+tp_broadcast_kernel(TpPeers p, int root, uint8_t* __restrict__ out, long long n, int* err) {
+  const int epoch = ld_volatile(p.flags[p.rank] + kEpochWord) + 1;
+  __syncthreads();
+  tp_barrier_dev(p, 0, epoch, err);
+  const long long nvec = n >> 4;
+  const uint4* src = reinterpret_cast<const uint4*>(p.a[root]);
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x)
+    reinterpret_cast<uint4*>(out)[v] = src[v];
+  tp_finish_barrier(p, 1, epoch, err);
+}
+
 static TpPeers make_peers(int world, int rank, void* const* a, void* const* b, int* const* flags) {
   TpPeers p;
   p.world = world; p.rank = rank;
@@ -344,5 +452,46 @@ extern "C" int mb_tp_allgather(int world, int rank, void* const* dst_bufs, int* 
   tp_allgather_kernel<<<grid, 256, 0, stream>>>(make_peers(world, rank, dst_bufs, nullptr, flags),
                                                 static_cast<const uint8_t*>(src), rows, row_bytes,
                                                 ld_src, ld_dst, col_off, err);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+// algo: 0 = choose by size (one-shot up to 512 KiB, two-shot above), 1 = one-shot, 2 = two-shot,
+// 3 = multimem one-shot (needs `mc_in`). Two-shot writes the result into out_bufs[rank] (symmetric);
+// the others write `out` (local). n = bf16 elements, multiple of 8.
+extern "C" int mb_tp_allreduce(int world, int rank, void* const* in_bufs, void* const* out_bufs, void* out,
+                               const void* mc_in, int* const* flags, long long n, int algo, int* err,
+                               cudaStream_t stream) {
+  if (world < 1 || world > kMaxRanks || n % 8) return MB_ERR_SHAPE;
+  if (n <= 0) return MB_OK;
+  if (algo == 0) algo = n * 2 <= (512 << 10) || out_bufs == nullptr ? 1 : 2;
+  if (algo == 3 && mc_in == nullptr) return MB_ERR_SHAPE;
+  if (algo == 2 && out_bufs == nullptr) return MB_ERR_SHAPE;
+  const long long nvec = n >> 3;
+  long long work = algo == 2 ? (nvec + world - 1) / world : nvec;
+  int grid = static_cast<int>((work + 255) / 256);
+  if (grid > 592) grid = 592;
+  if (grid < 1) grid = 1;
+  TpPeers p = make_peers(world, rank, in_bufs, out_bufs, flags);
+  if (algo == 1)
+    tp_allreduce_1shot_kernel<<<grid, 256, 0, stream>>>(p, static_cast<bf16*>(out), n, err);
+  else if (algo == 2)
+    tp_allreduce_2shot_kernel<<<grid, 256, 0, stream>>>(p, n, err);
+  else if (algo == 3)
+    tp_allreduce_multimem_kernel<<<grid, 256, 0, stream>>>(p, static_cast<const bf16*>(mc_in),
+                                                           static_cast<bf16*>(out), n, err);
+  else
+    return MB_ERR_SHAPE;
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+extern "C" int mb_tp_broadcast(int world, int rank, int root, void* const* in_bufs, void* out, int* const* flags,
+                               long long nbytes, int* err, cudaStream_t stream) {
+  if (world < 1 || world > kMaxRanks || nbytes % 16 || root < 0 || root >= world) return MB_ERR_SHAPE;
+  if (nbytes <= 0) return MB_OK;
+  int grid = static_cast<int>(((nbytes >> 4) + 255) / 256);
+  if (grid > 592) grid = 592;
+  if (grid < 1) grid = 1;
+  tp_broadcast_kernel<<<grid, 256, 0, stream>>>(make_peers(world, rank, in_bufs, nullptr, flags), root,
+                                                static_cast<uint8_t*>(out), nbytes, err);
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }

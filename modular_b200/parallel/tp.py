@@ -68,6 +68,75 @@ class TPContext:
         torch.cuda.synchronize()
         dist.barrier(self.group)
 
+    def collectives(self, max_bytes: int = 64 << 20) -> "Collectives":
+        """Stand-alone collectives on this context (lazily built, one staging area per context)."""
+        if getattr(self, "_coll", None) is None or self._coll.max_bytes < max_bytes:
+            self._coll = Collectives(self, max_bytes)
+        return self._coll
+
+
+class Collectives:
+    """All-reduce / all-gather / broadcast over peer memory with this package's kernels.
+
+    Inputs are staged into a symmetric buffer (one device-to-device copy) unless they already live
+    in one. Results are bit-identical on every rank (fixed summation order). Reference:
+    max/kernels/src/comm/allreduce.mojo:257-468 (1-stage / 2-stage dispatch by size),
+    comm/allgather.mojo:167, comm/broadcast.mojo:173; nn/comm/allreduce.py:40 (``Allreduce`` layer).
+    """
+
+    def __init__(self, ctx: TPContext, max_bytes: int = 64 << 20):
+        from .._native import lib
+
+        self.ctx, self.max_bytes, self.L = ctx, max_bytes, lib()
+        self.inp = ctx.alloc_symmetric(max_bytes // 2, torch.bfloat16)
+        self.out = ctx.alloc_symmetric(max_bytes // 2, torch.bfloat16)
+        self.flags = ctx.alloc_symmetric(self.L.tp_flag_ints(), torch.int32, zero=True)
+        self.multicast_ptr = int(getattr(self.inp.handle, "multicast_ptr", 0) or 0)
+        ctx.barrier()
+
+    def all_reduce(self, x: torch.Tensor, algo: str = "auto") -> torch.Tensor:
+        """Sum of ``x`` (bf16, numel % 8 == 0) over all ranks. algo: auto | one_shot | two_shot | multimem."""
+        n = x.numel()
+        if x.dtype != torch.bfloat16 or n % 8 or n * 2 > self.max_bytes:
+            raise ValueError("all_reduce: bf16 tensors with numel % 8 == 0 up to the staging size")
+        code = {"auto": 0, "one_shot": 1, "two_shot": 2, "multimem": 3}[algo]
+        if code == 3 and not self.multicast_ptr:
+            raise RuntimeError("this symmetric allocation has no NVLink multicast mapping")
+        c = self.ctx
+        self.inp.tensor[:n].copy_(x.reshape(-1))
+        res = torch.empty_like(x)
+        two_shot = code == 2 or (code == 0 and n * 2 > (512 << 10))
+        self.L.tp_allreduce(c.world, c.rank, self.inp.peer_ptrs, self.out.peer_ptrs, res, self.multicast_ptr,
+                            self.flags.peer_ptrs, n, 2 if two_shot else (code or 1))
+        if two_shot:
+            res.copy_(self.out.tensor[:n].view_as(x))
+        return res
+
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """Concatenation of every rank's ``x`` along dim 0 (bf16 or fp32 rows of 16-byte multiples)."""
+        c = self.ctx
+        x2 = x.reshape(x.shape[0], -1).contiguous()
+        rows, row_bytes = x2.shape[0], x2.shape[1] * x2.element_size()
+        if row_bytes % 16 or c.world * rows * row_bytes > self.max_bytes:
+            raise ValueError("all_gather: rows must be multiples of 16 bytes and fit the staging size")
+        # every rank's block lands at row offset rank * rows of every rank's `out` buffer
+        dst = [p + c.rank * rows * row_bytes for p in self.out.peer_ptrs]
+        self.L.tp_allgather(c.world, c.rank, dst, self.flags.peer_ptrs, x2, rows, row_bytes, row_bytes,
+                            row_bytes, 0)
+        n = c.world * rows * x2.shape[1]
+        return self.out.tensor.view(x.dtype)[:n].view(c.world * x.shape[0], *x.shape[1:]).clone()
+
+    def broadcast(self, x: torch.Tensor, root: int = 0) -> torch.Tensor:
+        c = self.ctx
+        nbytes = x.numel() * x.element_size()
+        if nbytes % 16 or nbytes > self.max_bytes // 2:
+            raise ValueError("broadcast: size must be a multiple of 16 bytes and fit the staging size")
+        if c.rank == root:
+            self.inp.tensor.view(torch.uint8)[:nbytes].copy_(x.reshape(-1).view(torch.uint8))
+        res = torch.empty_like(x)
+        self.L.tp_broadcast(c.world, c.rank, root, self.inp.peer_ptrs, res, self.flags.peer_ptrs, nbytes)
+        return res
+
 
 def shard_llama_config(cfg, world: int):
     if cfg.num_attention_heads % world or cfg.num_key_value_heads % world:

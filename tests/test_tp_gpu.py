@@ -35,6 +35,17 @@ def test_fused_gemm_collectives(world):
     assert any(e[1] > 1 for e in res[0]["errs"]), "no case exercised split-K pushes"
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_standalone_collectives_match_nccl(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    res = _run(world, "coll_worker.py", "COLL_RESULT ", extra_env={"MB200_TEST_MULTIMEM": "1"})
+    for r in res:
+        for kind, algo, n, err, same in r["cases"]:
+            assert same, (kind, algo, n)
+            assert err < (2e-2 if kind == "allreduce" else 1e-6), (kind, algo, n, err)
+
+
 @pytest.mark.parametrize("world,fused", [(2, "3"), (2, "0"), (2, "1"), (2, "2"), (4, "3")])
 def test_tp_matches_single_gpu(world, fused):
     if torch.cuda.device_count() < world:
