@@ -216,3 +216,23 @@ def benchmark(base_url, model, num_prompts, max_concurrency, input_len, output_l
 
 if __name__ == "__main__":
     main()
+
+
+@main.command("replay-recording")
+@click.argument("recording", type=click.Path(exists=True))
+@click.option("--base-url", default="http://127.0.0.1:8000")
+@click.option("--concurrency", default=8, type=int)
+@click.option("--preserve-timing", is_flag=True, help="keep the recorded gaps between requests")
+@click.option("--speedup", default=1.0, type=float)
+@click.option("--limit", default=None, type=int)
+def replay_recording_cmd(recording, base_url, concurrency, preserve_timing, speedup, limit):
+    """Replay a JSONL transaction recording (see MAX_SERVE_TRANSACTION_RECORDING_FILE) against a server."""
+    import asyncio
+    import json
+
+    from ..serve.recordreplay import replay_recording
+
+    res = asyncio.run(replay_recording(recording, base_url, concurrency, preserve_timing, speedup, limit=limit))
+    click.echo(json.dumps(res.summary()))
+    if res.failures:
+        raise SystemExit(1)

@@ -28,7 +28,7 @@ from .config import Settings
 from .model_worker import model_worker_main
 from .pipelines.llm import TokenGeneratorPipeline
 from .process_control import SubprocessExit, subprocess_manager
-from .router import openai_routes
+from .router import extra_routes, openai_routes
 from .router.openai_routes import error_response
 from .telemetry.metrics import METRICS, configure_metrics
 from .worker_interface import ModelWorkerProxy, RequestQueueFull, WorkerQueues, ZmqQueueSpec
@@ -153,7 +153,20 @@ def fastapi_app(settings: Settings, pipeline_config=None, tokenizer=None, factor
     async def worker_stats():
         return await app.state.rpc.call("stats")
 
-    app.include_router(openai_routes.router)
+    api_types = {getattr(t, "value", t) for t in settings.api_types}
+    if "openai" in api_types:
+        app.include_router(openai_routes.router)
+        app.include_router(extra_routes.responses_router)
+    if "kserve" in api_types:
+        app.include_router(extra_routes.kserve_router)
+    if "sagemaker" in api_types:
+        if "openai" not in api_types:      # /invocations dispatches to the OpenAI handlers
+            app.include_router(openai_routes.router)
+        app.include_router(extra_routes.sagemaker_router)
+    if settings.transaction_recording_file:
+        from .recordreplay import RecordingMiddleware
+        app.add_middleware(RecordingMiddleware, path=settings.transaction_recording_file,
+                           include_responses=settings.transaction_recording_include_responses)
     return app
 
 

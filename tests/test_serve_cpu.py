@@ -108,3 +108,80 @@ def test_incremental_detokenizer_utf8_and_stop():
     d2 = IncrementalDetokenizer(tok, stop=["END"])
     out = "".join(d2.push([i]) for i in tok.encode("abcENDdef", add_special_tokens=False))
     assert out == "abc" and d2.stopped
+
+
+# ------------------------------------------------------------------ other API front ends
+@pytest.fixture(scope="module")
+def multi_api_client(tmp_path_factory):
+    rec = tmp_path_factory.mktemp("rec") / "transactions.jsonl"
+    settings = Settings(api_types=["openai", "kserve", "sagemaker"], transaction_recording_file=str(rec),
+                        transaction_recording_include_responses=True)
+    pc = _config(model_path="echo", devices="cpu")
+    app = fastapi_app(settings, pc, ByteTokenizer(), EchoPipeline, "echo", 4096)
+    with TestClient(app) as c:
+        c.recording = rec
+        c.asgi_app = app
+        yield c
+
+
+def test_kserve_routes(multi_api_client):
+    c = multi_api_client
+    assert c.get("/v2/health/live").json() == {"live": True}
+    assert c.get("/v2/health/ready").json() == {"ready": True}
+    assert c.get("/v2/models/echo").json()["inputs"][0]["name"] == "text_input"
+    assert c.get("/v2/models/nope").status_code == 404
+    r = c.post("/v2/models/echo/infer", json={"inputs": [{"name": "text_input", "datatype": "BYTES", "shape": [2],
+                                                           "data": ["hello", "abc"]}],
+                                               "parameters": {"max_tokens": 32}})
+    assert r.status_code == 200, r.text
+    out = r.json()["outputs"][0]
+    assert out["name"] == "text_output" and out["shape"] == [2] and out["data"][0] == "hello"
+    bad = c.post("/v2/models/echo/infer", json={"inputs": [{"name": "x", "datatype": "FP32", "data": [1.0]}]})
+    assert bad.status_code == 400
+
+
+def test_sagemaker_routes(multi_api_client):
+    c = multi_api_client
+    assert c.get("/ping").status_code == 200
+    r = c.post("/invocations", json={"prompt": "sage", "max_tokens": 16})
+    assert r.status_code == 200 and r.json()["choices"][0]["text"] == "sage"
+    r = c.post("/invocations", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 64})
+    assert r.status_code == 200 and r.json()["choices"][0]["message"]["role"] == "assistant"
+    assert c.post("/invocations", content=b"not json").status_code == 400
+
+
+def test_openresponses_route(multi_api_client):
+    c = multi_api_client
+    r = c.post("/v1/responses", json={"model": "echo", "input": "ping", "max_output_tokens": 64})
+    body = r.json()
+    assert r.status_code == 200 and body["object"] == "response" and body["status"] == "completed"
+    assert "ping" in body["output"][0]["content"][0]["text"] and body["usage"]["output_tokens"] > 0
+    with c.stream("POST", "/v1/responses", json={"model": "echo", "stream": True, "max_output_tokens": 64,
+                                                  "input": [{"role": "user", "content": [{"type": "input_text", "text": "xy"}]}]}) as s:
+        events = [l for l in s.iter_lines() if l.startswith("event:")]
+    assert events[0] == "event: response.created" and events[-1] == "event: response.completed"
+    assert any(e == "event: response.output_text.delta" for e in events)
+
+
+def test_record_and_replay(multi_api_client):
+    import asyncio
+
+    from modular_b200.serve.recordreplay import read_jsonl, replay_recording
+
+    c = multi_api_client
+    c.post("/v1/completions", json={"model": "echo", "prompt": "recorded", "max_tokens": 16},
+           headers={"authorization": "Bearer secret"})
+    c.post("/v1/completions", json={"model": "missing", "prompt": "x"})
+    recs = list(read_jsonl(str(c.recording)))
+    mine = [r for r in recs if "recorded" in r["body"]]
+    assert mine and mine[-1]["status"] == 200 and "recorded" in mine[-1]["response"]
+    assert all("authorization" not in r["headers"] for r in recs)
+    assert any(r["status"] == 404 for r in recs)
+
+    class Adapter:      # the app lives on the TestClient's event loop: drive it through the sync client
+        async def request(self, method, url, content=None, headers=None):
+            return await asyncio.to_thread(c.request, method, url.replace("http://test", ""), content=content,
+                                           headers=headers)
+
+    res = asyncio.run(replay_recording(str(c.recording), "http://test", concurrency=4, client=Adapter()))
+    assert res.sent == len(recs) and res.status_match == res.sent, res.failures
