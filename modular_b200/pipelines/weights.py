@@ -65,6 +65,14 @@ def parse_quant_config(hf_config: dict) -> Optional[QuantConfig]:
 
 
 def load_hf_config(model_path: str) -> dict:
+    g = _gguf_file(model_path)
+    if g is not None and not (os.path.isdir(model_path) and (Path(model_path) / "config.json").exists()):
+        from .gguf import GGUFReader
+        return GGUFReader(g).hf_config()
+    return _load_hf_config_json(model_path)
+
+
+def _load_hf_config_json(model_path: str) -> dict:
     p = Path(model_path) / "config.json"
     if not p.exists():
         raise FileNotFoundError(f"{p} not found: model_path must be a local HF-layout directory "
@@ -115,7 +123,42 @@ class SafetensorWeights:
         return {k: self[k] for k in self._where}
 
 
-def load_state_dict(model_path: str, weight_path=()) -> SafetensorWeights:
+class GGUFWeights:
+    """A ``.gguf`` file presented like :class:`SafetensorWeights` (HF names, tensors dequantised on access)."""
+
+    def __init__(self, path: str, dtype: torch.dtype = torch.bfloat16):
+        from .gguf import GGUFReader, hf_name
+
+        self.reader, self.dtype = GGUFReader(path), dtype
+        self._names = {hf_name(n): n for n in self.reader.tensors if hf_name(n)}
+
+    def keys(self):
+        return self._names.keys()
+
+    def __contains__(self, k):
+        return k in self._names
+
+    def to_dict(self) -> dict:
+        return self.reader.to_hf_state_dict(self.dtype)
+
+    def __getitem__(self, k) -> torch.Tensor:
+        return self.to_dict()[k] if ("q_proj" in k or "k_proj" in k) else self.reader.get(self._names[k], self.dtype)
+
+
+def _gguf_file(model_path: str, weight_path=()) -> Optional[str]:
+    cands = [str(w) for w in weight_path if str(w).endswith(".gguf")]
+    if model_path.endswith(".gguf"):
+        cands.append(model_path)
+    elif os.path.isdir(model_path) and not any(Path(model_path).glob("*.safetensors")):
+        cands += sorted(str(p) for p in Path(model_path).glob("*.gguf"))
+    return cands[0] if cands else None
+
+
+def load_state_dict(model_path: str, weight_path=()):
+    """Safetensors directory (HF layout) or a GGUF file."""
+    g = _gguf_file(model_path, weight_path)
+    if g is not None:
+        return GGUFWeights(g)
     return SafetensorWeights(find_weight_files(model_path, weight_path))
 
 
