@@ -36,6 +36,9 @@ def _load():
             spec = importlib.util.spec_from_file_location("modular_b200._C", str(SO_PATH))
             mod = importlib.util.module_from_spec(spec)
             spec.loader.exec_module(mod)
+            # step kernels launch as programmatic dependents unless MB200_PDL=0 (see csrc/common/launch.h)
+            if os.environ.get("MB200_PDL", "1") not in ("", "0") and hasattr(mod, "set_pdl"):
+                mod.set_pdl(True)
             _MOD = mod
         except Exception as e:  # noqa: BLE001
             _ERR = e

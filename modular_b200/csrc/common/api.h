@@ -18,6 +18,10 @@
 extern "C" {
 #endif
 
+// Programmatic dependent launch for the step kernels (process-wide; see common/launch.h).
+void mb_set_pdl(int on);
+int mb_get_pdl(void);
+
 // ---- GEMM (gemm_tcgen05.cu) -------------------------------------------------------------
 void mb_gemm_bf16_plan(int M, int N, int K, int dual, int num_sms, int* bn, int* splits,
                        int* stages);

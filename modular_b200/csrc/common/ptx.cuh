@@ -248,6 +248,12 @@ __device__ __forceinline__ int ld_volatile(const int* p) {
 __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Programmatic dependent launch: returns when every kernel this one depends on has completed and
+// its memory is visible (no-op when the kernel was launched normally). Call before the first
+// access to global memory; pdl_trigger() lets the next kernel on the stream start its prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Bounded spin until *p >= target (acquire, system scope). Returns false on timeout.
 __device__ __forceinline__ bool wait_flag_ge(const int* p, int target, int* err, int code,
                                              uint64_t timeout_ns = 1000000000ull) {

@@ -23,6 +23,7 @@
 #include <stdint.h>
 
 #include "../common/api.h"
+#include "../common/launch.h"
 #include "../common/ptx.cuh"
 #include "gemm_common.h"
 
@@ -178,6 +179,8 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
   Bars* bars = reinterpret_cast<Bars*>(sQ + 64 * HD);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kvh = blockIdx.y;
+  pdl_wait();      // Q, the KV pages of this step and the batch metadata come from earlier work on the stream
+  pdl_trigger();
   const bool is_prefill = static_cast<int>(blockIdx.x) < p.n_tiles;
   const int seq = is_prefill ? p.tile_seq[blockIdx.x] : p.decode_seq[blockIdx.x - p.n_tiles];
   const int tq0 = is_prefill ? p.tile_q0[blockIdx.x] : 0;
@@ -355,7 +358,7 @@ static int launch(const CUtensorMap& tm, const Params& p, int n_ctas, int n_kv, 
       return MB_ERR_LAUNCH;
     configured = true;
   }
-  kern<<<dim3(n_ctas, n_kv), kThreads, smem, stream>>>(tm, p);
+  if (launch_k(kern, dim3(n_ctas, n_kv), dim3(kThreads), smem, stream, tm, p) != cudaSuccess) return MB_ERR_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 

@@ -10,6 +10,8 @@
 #include <stdint.h>
 
 #include "../common/api.h"
+#include "../common/launch.h"
+#include "../common/ptx.cuh"
 
 namespace mb {
 
@@ -43,6 +45,8 @@ rmsnorm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf
                int mbc) {
   __shared__ float scratch[32];
   extern __shared__ uint4 row_cache[];  // cols/8 packed values (the summed row)
+  pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x;
   const bf16* xr = x + static_cast<size_t>(row) * ldx;
   bf16* rr = ADD ? residual + static_cast<size_t>(row) * cols : nullptr;
@@ -118,6 +122,8 @@ __global__ void silu_mul_kernel(const bf16* __restrict__ gu, bf16* __restrict__ 
 __global__ void embedding_kernel(const int64_t* __restrict__ ids, const bf16* __restrict__ table,
                                  bf16* __restrict__ out, int n, int hidden, int vocab,
                                  int vocab_start) {
+  pdl_wait();
+  pdl_trigger();
   const int per_row = hidden >> 3;
   const size_t vec = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (vec >= static_cast<size_t>(n) * per_row) return;
@@ -130,6 +136,8 @@ __global__ void embedding_kernel(const int64_t* __restrict__ ids, const bf16* __
 
 __global__ void gather_rows_kernel(const uint8_t* __restrict__ src, const int32_t* __restrict__ idx,
                                    uint8_t* __restrict__ dst, int n, int row_bytes, int ld_src) {
+  pdl_wait();
+  pdl_trigger();
   const int per_row = row_bytes >> 4;
   const size_t vec = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (vec >= static_cast<size_t>(n) * per_row) return;
@@ -148,6 +156,8 @@ __global__ void rope_kv_store_kernel(bf16* __restrict__ qkv, const int32_t* __re
                                      bf16* __restrict__ v_cache, int T, int n_q, int n_kv,
                                      int head_dim, int page_size, int64_t page_stride,
                                      int64_t head_stride, int interleaved) {
+  pdl_wait();
+  pdl_trigger();
   const int half = head_dim >> 1;
   const int vec_per_head = half >> 3;           // threads per (token, head) for q/k
   const int heads_rot = n_q + n_kv;             // heads that get rotated
@@ -231,18 +241,29 @@ __global__ void rope_kv_store_kernel(bf16* __restrict__ qkv, const int32_t* __re
 // device by the previous step and never visited the host.
 __global__ void realize_future_kernel(int64_t* __restrict__ tokens, const int32_t* __restrict__ src,
                                       const int64_t* __restrict__ prev, int n) {
+  pdl_wait();
+  pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n && src[i] >= 0) tokens[i] = prev[src[i]];
 }
 
 }  // namespace mb
 
+namespace mb {
+static bool g_pdl = false;
+bool pdl_enabled() { return g_pdl; }
+}  // namespace mb
+
 using namespace mb;
+
+// Process-wide switch for programmatic dependent launch of the step kernels (see common/launch.h).
+extern "C" void mb_set_pdl(int on) { mb::g_pdl = on != 0; }
+extern "C" int mb_get_pdl(void) { return mb::g_pdl ? 1 : 0; }
 
 extern "C" int mb_realize_future_tokens(int64_t* tokens, const int32_t* src, const int64_t* prev,
                                         int n, cudaStream_t stream) {
   if (n <= 0) return MB_OK;
-  realize_future_kernel<<<(n + 255) / 256, 256, 0, stream>>>(tokens, src, prev, n);
+  launch_k(realize_future_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, tokens, src, prev, n);
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
@@ -255,9 +276,9 @@ extern "C" int mb_rmsnorm(const void* x, const void* w, void* out, int rows, int
                           int ldo, float eps, float weight_offset, int mbc, cudaStream_t stream) {
   if (rows <= 0) return MB_OK;
   if (cols % 8 || ldx % 8 || ldo % 8 || cols > 32768) return MB_ERR_SHAPE;
-  rmsnorm_kernel<false><<<rows, 256, cols * 2, stream>>>(
-      static_cast<const bf16*>(x), nullptr, static_cast<const bf16*>(w), static_cast<bf16*>(out),
-      cols, ldx, ldo, eps, weight_offset, mbc);
+  launch_k(rmsnorm_kernel<false>, dim3(rows), dim3(256), cols * 2, stream, static_cast<const bf16*>(x),
+           static_cast<bf16*>(nullptr), static_cast<const bf16*>(w), static_cast<bf16*>(out), cols, ldx, ldo, eps,
+           weight_offset, mbc);
   return MB_LAUNCH_OK();
 }
 
@@ -266,9 +287,9 @@ extern "C" int mb_add_rmsnorm(const void* x, void* residual, const void* w, void
                               cudaStream_t stream) {
   if (rows <= 0) return MB_OK;
   if (cols % 8 || cols > 32768) return MB_ERR_SHAPE;
-  rmsnorm_kernel<true><<<rows, 256, cols * 2, stream>>>(
-      static_cast<const bf16*>(x), static_cast<bf16*>(residual), static_cast<const bf16*>(w),
-      static_cast<bf16*>(out), cols, cols, cols, eps, weight_offset, mbc);
+  launch_k(rmsnorm_kernel<true>, dim3(rows), dim3(256), cols * 2, stream, static_cast<const bf16*>(x),
+           static_cast<bf16*>(residual), static_cast<const bf16*>(w), static_cast<bf16*>(out), cols, cols, cols,
+           eps, weight_offset, mbc);
   return MB_LAUNCH_OK();
 }
 
@@ -287,8 +308,8 @@ extern "C" int mb_embedding(const int64_t* ids, const void* table, void* out, in
   if (n <= 0) return MB_OK;
   if (hidden % 8) return MB_ERR_SHAPE;
   const size_t work = static_cast<size_t>(n) * (hidden / 8);
-  embedding_kernel<<<blocks_for(work, 256), 256, 0, stream>>>(
-      ids, static_cast<const bf16*>(table), static_cast<bf16*>(out), n, hidden, vocab, vocab_start);
+  launch_k(embedding_kernel, dim3(blocks_for(work, 256)), dim3(256), 0, stream, ids,
+           static_cast<const bf16*>(table), static_cast<bf16*>(out), n, hidden, vocab, vocab_start);
   return MB_LAUNCH_OK();
 }
 
@@ -297,8 +318,8 @@ extern "C" int mb_gather_rows(const void* src, const int32_t* idx, void* dst, in
   if (n <= 0) return MB_OK;
   if (row_bytes % 16 || ld_src % 16) return MB_ERR_SHAPE;
   const size_t work = static_cast<size_t>(n) * (row_bytes / 16);
-  gather_rows_kernel<<<blocks_for(work, 256), 256, 0, stream>>>(
-      static_cast<const uint8_t*>(src), idx, static_cast<uint8_t*>(dst), n, row_bytes, ld_src);
+  launch_k(gather_rows_kernel, dim3(blocks_for(work, 256)), dim3(256), 0, stream,
+           static_cast<const uint8_t*>(src), idx, static_cast<uint8_t*>(dst), n, row_bytes, ld_src);
   return MB_LAUNCH_OK();
 }
 
@@ -310,9 +331,8 @@ extern "C" int mb_rope_kv_store(void* qkv, const int32_t* positions, const int64
   if (head_dim % 16) return MB_ERR_SHAPE;
   const int work_per_tok = (n_q + n_kv) * (head_dim / 16) + n_kv * (head_dim / 8);
   const size_t work = static_cast<size_t>(T) * work_per_tok;
-  rope_kv_store_kernel<<<blocks_for(work, 256), 256, 0, stream>>>(
-      static_cast<bf16*>(qkv), positions, slots, cos_sin, static_cast<bf16*>(k_cache),
-      static_cast<bf16*>(v_cache), T, n_q, n_kv, head_dim, page_size, page_stride, head_stride,
-      interleaved);
+  launch_k(rope_kv_store_kernel, dim3(blocks_for(work, 256)), dim3(256), 0, stream, static_cast<bf16*>(qkv),
+           positions, slots, cos_sin, static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), T, n_q, n_kv,
+           head_dim, page_size, page_stride, head_stride, interleaved);
   return MB_LAUNCH_OK();
 }

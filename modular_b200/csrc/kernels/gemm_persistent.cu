@@ -34,6 +34,7 @@
 #include <stdint.h>
 
 #include "../common/api.h"
+#include "../common/launch.h"
 #include "../common/ptx.cuh"
 #include "comm_flags.h"
 #include "gemm_common.h"
@@ -517,7 +518,7 @@ extern "C" int mb_gemm_bf16_persistent_gated(const void* X, const void* W, void*
   using namespace mb::pg;
   if (gate_flags != nullptr && (gate_rpr < 1 || gate_world < 1 || gate_world > mb::kMaxRanks)) return MB_ERR_SHAPE;
   if (M <= 0 || N <= 0) return MB_OK;
-  const bool dual = flags & 1, resid = flags & 2, f32 = flags & 4, pdl = flags & 8, packed = flags & 64;
+  const bool dual = flags & 1, resid = flags & 2, f32 = flags & 4, pdl = (flags & 8) || mb::pdl_enabled(), packed = flags & 64;
   if (packed && (K % kBK || N % kBM || ldw != K)) return MB_ERR_SHAPE;
   if (K % 8 || ldx % 8 || ldw % 8 || N % 8 || (!f32 && ldy % 8) || (resid && ldr % 8)) return MB_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(Y) |

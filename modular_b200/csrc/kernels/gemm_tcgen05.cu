@@ -28,6 +28,7 @@
 #include <mutex>
 #include <unordered_map>
 
+#include "../common/launch.h"
 #include "../common/ptx.cuh"
 #include "../common/api.h"
 #include "comm_flags.h"
@@ -83,6 +84,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   int t0 = m_tile * BN;
   int Mlim = M, w_row0 = 0;
   if (expert_offsets != nullptr) {
+    pdl_wait();  // the offsets are produced by the routing kernels
     const int e = blockIdx.z;
     const int row_begin = expert_offsets[e], row_end = expert_offsets[e + 1];
     t0 = row_begin + m_tile * BN;
@@ -117,6 +119,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = tail->tmem_base;
   volatile int* abort_word = &tail->abort_word;
+  // everything above touched only this CTA's own resources; the operands are produced by earlier
+  // kernels on the stream (no-op unless launched as a programmatic dependent)
+  pdl_wait();
+  pdl_trigger();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -266,6 +272,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, const __nv_bfloat16* __restrict__ R,
                                      __nv_bfloat16* __restrict__ Y, int M, int N, int splits,
                                      int ldy, int ldr) {
+  pdl_wait();
+  pdl_trigger();
   const size_t idx = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
   const size_t total = static_cast<size_t>(M) * N;
   if (idx >= total) return;
@@ -394,11 +402,11 @@ static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, con
   }
   dim3 grid((M + BN - 1) / BN, (N + kBM - 1) / kBM, expert_offsets ? n_experts : splits);
   const uint32_t tmem_cols = pow2_cols(DUAL ? 2 * BN : BN);
-  kern<<<grid, kGemmThreads, smem, stream>>>(tw, tx, Y, static_cast<const __nv_bfloat16*>(R), M, N,
-                                             K, ldy, ldr, dual_rows, k_per_split, BN, stages,
-                                             tmem_cols, err, expert_offsets, w_rows_per_expert, gate_flags,
-                                             gate_rpr, gate_world, packed_kb);
-  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+  const cudaError_t e = launch_k(kern, grid, dim3(kGemmThreads), smem, stream, tw, tx, Y,
+                                 static_cast<const __nv_bfloat16*>(R), M, N, K, ldy, ldr, dual_rows, k_per_split,
+                                 BN, stages, tmem_cols, err, expert_offsets, w_rows_per_expert, gate_flags,
+                                 gate_rpr, gate_world, packed_kb);
+  return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
 }  // namespace mb
@@ -424,9 +432,12 @@ extern "C" void mb_gemm_bf16_plan(int M, int N, int K, int dual, int num_sms, in
   }
   const int stage_bytes = kATileBytes * (dual ? 2 : 1) + bn * kBK * 2;
   const int tmem_need = dual ? 2 * bn : bn;
-  // Two CTAs per SM when both the pipeline and the accumulators fit twice.
-  int budget = (tmem_need <= 256 && stage_bytes * 4 + 12 * 1024 <= 112 * 1024) ? 100 * 1024
-                                                                               : 212 * 1024;
+  // Two CTAs per SM when both the pipeline and the accumulators fit twice - but only when the grid
+  // has more CTAs than SMs: a single-wave grid (the decode GEMMs) runs one CTA per SM, and then a
+  // deeper pipeline (more bytes in flight per SM) is what brings the weight stream up to HBM speed.
+  const bool one_wave = ctas * splits <= num_sms;
+  int budget = (!one_wave && tmem_need <= 256 && stage_bytes * 4 + 12 * 1024 <= 112 * 1024) ? 100 * 1024
+                                                                                           : 212 * 1024;
   int stages = budget / stage_bytes;
   if (stages > 8) stages = 8;
   if (stages < 2) stages = 2;
@@ -500,10 +511,11 @@ extern "C" int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const v
     if (rc != MB_OK) return rc;
     if (f32) return MB_ERR_SHAPE;  // fp32 output is never split
     const size_t total4 = (static_cast<size_t>(M) * N + 3) / 4;
-    splitk_reduce_kernel<<<static_cast<unsigned>((total4 + 255) / 256), 256, 0, stream>>>(
+    const cudaError_t e = launch_k(
+        splitk_reduce_kernel, dim3(static_cast<unsigned>((total4 + 255) / 256)), dim3(256), 0, stream,
         static_cast<const float*>(workspace), resid ? static_cast<const __nv_bfloat16*>(R) : nullptr,
         static_cast<__nv_bfloat16*>(Y), M, N, splits, ldy, ldr);
-    return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+    return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
   }
   if (dual)
     return launch_cfg<true, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, N, K, 1, bn, stages, err,

@@ -12,6 +12,8 @@
 #include <stdint.h>
 
 #include "../common/api.h"
+#include "../common/launch.h"
+#include "../common/ptx.cuh"
 
 namespace mb {
 
@@ -99,6 +101,8 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   __shared__ float sh_f[32];
   __shared__ float sh_scan[kSampThreads / 32];
   __shared__ int sh_pick;
+  pdl_wait();
+  pdl_trigger();
   const int rowi = blockIdx.x;
   const float* row = logits + static_cast<size_t>(rowi) * ld;
   const float T = temperature ? temperature[rowi] : 1.f;
@@ -259,9 +263,8 @@ extern "C" int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, 
                                    const float* top_p, const float* min_p, const uint64_t* seeds,
                                    uint64_t step, cudaStream_t stream) {
   if (rows <= 0) return MB_OK;
-  sample_kernel<<<rows, kSampThreads, 0, stream>>>(logits, out, vocab, ld, temperature, top_k,
-                                                   top_p, min_p, seeds, step);
-  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+  return launch_k(sample_kernel, dim3(rows), dim3(kSampThreads), 0, stream, logits, out, vocab, ld, temperature,
+                  top_k, top_p, min_p, seeds, step) == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
 extern "C" int mb_apply_penalties(float* logits, int rows, int vocab, int ld, const int32_t* tok,

@@ -105,6 +105,7 @@ class LLM:
         self.model = fam.model_class(model_config, weights, self.kv.kv, max_tokens=max_batch_input_tokens,
                                      max_seqs=max_batch_size, max_position=max_length, **extra)
         overlap = on_gpu if enable_overlap_scheduler is None else enable_overlap_scheduler
+        overlap = overlap and bool(getattr(self.model, "use_executor", False))
         if graph_batch_sizes is None:
             graph_batch_sizes = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch_size]
         self.pipeline = TextGenerationPipeline(

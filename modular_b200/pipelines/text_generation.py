@@ -56,7 +56,8 @@ class TextGenerationPipeline:
         self.kv = kv_manager
         self.device = model.device
         self.on_gpu = self.device.type == "cuda"
-        self.overlap = overlap and self.on_gpu
+        # overlap scheduling needs the native step (future tokens are realised on the device)
+        self.overlap = overlap and self.on_gpu and bool(getattr(model, "use_executor", False))
         self.eos_token_ids = frozenset(eos_token_ids)
         cfg = model.cfg
         self.packer = BatchPacker(cfg.num_attention_heads, cfg.num_key_value_heads, kv_manager.page_size,
