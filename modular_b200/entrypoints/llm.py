@@ -159,6 +159,12 @@ class LLM:
     def has_unfinished(self) -> bool:
         return self.scheduler.has_work() or not self.scheduler.request_queue.empty()
 
+    def encode(self, prompts: Sequence[Sequence[int]], pooling: str = "last") -> torch.Tensor:
+        """Pooled, L2-normalised embeddings of token-id prompts: fp32 [n, hidden]."""
+        if not hasattr(self.model, "encode"):
+            raise NotImplementedError(f"{type(self.model).__name__} does not produce embeddings")
+        return self.model.encode([list(p) for p in prompts], pooling)
+
     # ------------------------------------------------------------ batch API
     def generate(self, prompts: Sequence[Union[Sequence[int], np.ndarray]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,

@@ -295,10 +295,20 @@ class Llama3Model:
                         logit_rows, plan=None) -> torch.Tensor:
         """Same computation through :mod:`modular_b200.ops` one op at a time (CPU, and the
         cross-check for the executor on GPU). Returns fp32 logits [len(logit_rows), vocab]."""
+        h = self.forward_hidden(tokens, positions, slots, block_table, q_start, q_len, kv_len, plan=plan)
+        last = h[logit_rows.long()]
+        xn = ops.rms_norm(last, self.w.final_norm, self.cfg.rms_norm_eps)
+        logits = ops.linear(xn, self.w.lm_head, out_dtype=torch.float32)
+        return logits.float()
+
+    def forward_hidden(self, tokens, positions, slots, block_table, q_start, q_len, kv_len, plan=None,
+                       kv=None) -> torch.Tensor:
+        """Residual stream after the last layer, before the final norm: [T, hidden]."""
         c = self.cfg
+        kv = self.kv if kv is None else kv
         h = ops.embedding(tokens, self.w.embed)
         for li, l in enumerate(self.w.layers):
-            kc, vc = self.kv[:, 0, li], self.kv[:, 1, li]
+            kc, vc = kv[:, 0, li], kv[:, 1, li]
             x = ops.rms_norm(h, l.attn_norm, c.rms_norm_eps)
             qkv = ops.linear(x, l.wqkv)
             ops.rope_kv_store(qkv, positions, slots, self.cos_sin, kc, vc, c.num_attention_heads,
@@ -313,7 +323,35 @@ class Llama3Model:
             else:
                 act = ops.silu_mul(ops.linear(x, l.wgu))
             h = ops.linear(act, l.wd, residual=h)
-        last = h[logit_rows.long()]
-        xn = ops.rms_norm(last, self.w.final_norm, c.rms_norm_eps)
-        logits = ops.linear(xn, self.w.lm_head, out_dtype=torch.float32)
-        return logits.float()
+        return h
+
+    def encode(self, token_lists, pooling: str = "last", normalize: bool = True) -> torch.Tensor:
+        """Sentence embeddings: run the prompts as one ragged prefill over a private scratch cache and
+        pool the final-normed hidden states (``last`` token or ``mean``). Returns fp32 [n, hidden].
+        Reference: max/python/max/pipelines/lib/embeddings_pipeline.py."""
+        c, dev, page = self.cfg, self.device, self.page_size
+        lens = [len(t) for t in token_lists]
+        if not lens or min(lens) < 1:
+            raise ValueError("encode needs non-empty token lists")
+        pages_per = [(n + page - 1) // page for n in lens]
+        kv = torch.zeros(sum(pages_per) + 1, 2, c.num_hidden_layers, c.num_key_value_heads, page, c.head_dim,
+                         dtype=self.dtype, device=dev)
+        bt = torch.zeros(len(lens), max(pages_per), dtype=torch.int32)
+        slots, positions, nxt = [], [], 1
+        for i, (n, pp) in enumerate(zip(lens, pages_per)):
+            bt[i, :pp] = torch.arange(nxt, nxt + pp)
+            slots.append(torch.arange(n) + nxt * page)
+            positions.append(torch.arange(n))
+            nxt += pp
+        q_len = torch.tensor(lens, dtype=torch.int32)
+        q_start = torch.cumsum(q_len, 0, dtype=torch.int32) - q_len
+        tokens = torch.tensor([t for tl in token_lists for t in tl], dtype=torch.long, device=dev)
+        h = self.forward_hidden(tokens, torch.cat(positions).int().to(dev), torch.cat(slots).to(dev), bt.to(dev),
+                                q_start.to(dev), q_len.to(dev), q_len.to(dev), kv=kv)
+        hn = ops.rms_norm(h, self.w.final_norm, c.rms_norm_eps).float()
+        out = torch.empty(len(lens), c.hidden_size, dtype=torch.float32, device=dev)
+        for i, (s0, n) in enumerate(zip(q_start.tolist(), lens)):
+            out[i] = hn[s0 + n - 1] if pooling == "last" else hn[s0:s0 + n].mean(0)
+        if normalize:
+            out = out / out.norm(dim=-1, keepdim=True).clamp_min(1e-12)
+        return out

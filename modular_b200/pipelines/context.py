@@ -170,6 +170,20 @@ class TextGenerationOutput:
         return self.final_status.is_done
 
 
+@dataclass
+class EmbeddingsOutput:
+    """Final (and only) answer to an embeddings request."""
+    request_id: str
+    embedding: list
+    prompt_tokens: int = 0
+    final_status: GenerationStatus = GenerationStatus.END_OF_SEQUENCE
+    tokens: tuple = ()
+
+    @property
+    def is_done(self) -> bool:
+        return True
+
+
 _req_counter = itertools.count()
 
 
@@ -185,6 +199,8 @@ class TextContext:
     model_name: str = ""
     status: GenerationStatus = GenerationStatus.ACTIVE
     arrival_time: float = field(default_factory=time.perf_counter)
+    task: str = "generate"          # "generate" | "embed" (answered by the embeddings scheduler)
+    pooling: str = "last"
     first_token_time: Optional[float] = None
     last_token_time: Optional[float] = None
     # bookkeeping owned by the engine

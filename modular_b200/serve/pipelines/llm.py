@@ -93,3 +93,17 @@ class TokenGeneratorPipeline:
             reason = ch.finish_reason or reason
             n_prompt, n_out = ch.prompt_tokens, ch.completion_tokens
         return TokenChunk(text, ids, reason, n_prompt, n_out)
+
+    async def embed(self, prompt: Union[str, Sequence[int]], pooling: str = "last",
+                    request_id: Optional[str] = None):
+        """One pooled embedding; returns (vector, prompt_tokens)."""
+        rid = request_id or uuid.uuid4().hex
+        ctx = self.tokenizer.new_context(prompt, self.max_length, SamplingParams(max_new_tokens=1), rid, self.model_name)
+        ctx.task, ctx.pooling = "embed", pooling
+        METRICS.request_count.inc()
+        METRICS.input_tokens.inc(ctx.tokens.prompt_len)
+        async for out in self.proxy.stream(ctx):
+            if hasattr(out, "embedding"):
+                return out.embedding, out.prompt_tokens
+            raise ValueError("this model worker cannot produce embeddings")
+        raise RuntimeError("embeddings request ended without an answer")

@@ -20,7 +20,7 @@ from ...pipelines.context import SamplingParams
 from ..schemas.openai import (ChatChoice, ChatChoiceMessage, ChatChunkChoice, ChatCompletionChunk,
                               ChatCompletionRequest, ChatCompletionResponse, ChatDelta, CompletionChoice,
                               CompletionRequest, CompletionResponse, ErrorBody, ErrorResponse, ModelCard,
-                              ModelList, Usage)
+                              ModelList, Usage, EmbeddingData, EmbeddingsRequest, EmbeddingsResponse)
 from ..telemetry.metrics import METRICS
 from ..worker_interface import RequestQueueFull
 
@@ -201,3 +201,39 @@ async def create_chat_completion(req: ChatCompletionRequest, request: Request):
         return error_response(429, str(e), "rate_limit_error")
     except ValueError as e:
         return error_response(400, str(e))
+
+
+# ------------------------------------------------------------------ embeddings
+@router.post("/v1/embeddings")
+async def create_embeddings(req: EmbeddingsRequest, request: Request):
+    import base64
+    import struct
+
+    pipeline = _pipeline(request)
+    _check_model(request, req.model)
+    inp = req.input
+    if isinstance(inp, str) or (isinstance(inp, list) and inp and isinstance(inp[0], int)):
+        inputs = [inp]
+    else:
+        inputs = list(inp)
+    if not inputs:
+        return error_response(400, "input must not be empty")
+    if req.encoding_format not in ("float", "base64"):
+        return error_response(400, "encoding_format must be float or base64")
+    rid = getattr(request.state, "request_id", uuid.uuid4().hex)
+    data, n_tok = [], 0
+    try:
+        for i, item in enumerate(inputs):
+            vec, n = await pipeline.embed(item, req.pooling or "last", f"{rid}-{i}")
+            if req.dimensions:
+                vec = vec[: req.dimensions]
+                norm = sum(v * v for v in vec) ** 0.5 or 1.0
+                vec = [v / norm for v in vec]
+            n_tok += n
+            emb = vec if req.encoding_format == "float" else base64.b64encode(struct.pack(f"<{len(vec)}f", *vec)).decode()
+            data.append(EmbeddingData(index=i, embedding=emb))
+    except RequestQueueFull as e:
+        return error_response(429, str(e), "rate_limit_error")
+    except ValueError as e:
+        return error_response(400, str(e))
+    return EmbeddingsResponse(data=data, model=req.model, usage=Usage(prompt_tokens=n_tok, total_tokens=n_tok))

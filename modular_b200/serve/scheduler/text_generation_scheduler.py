@@ -63,6 +63,13 @@ class TokenGenerationScheduler:
         self.last_metrics = BatchMetrics()
         self._contexts: dict[str, TextContext] = {}
         self.total_steps = 0
+        # requests with task == "embed" are answered by an embeddings scheduler when the model can encode
+        self.embeddings = None
+        model = getattr(pipeline, "model", None)
+        if model is not None and hasattr(model, "encode"):
+            from .embeddings_scheduler import EmbeddingsScheduler
+            self.embeddings = EmbeddingsScheduler(model.encode, self.response_queue,
+                                                  config.target_tokens_per_batch_ce, config.max_batch_size)
 
     # ------------------------------------------------------------ queue plumbing
     def _drain_requests(self) -> int:
@@ -74,6 +81,14 @@ class TokenGenerationScheduler:
                 break
             except Exception:  # noqa: BLE001  (zmq queues raise their own Empty)
                 break
+            if getattr(ctx, "task", "generate") == "embed":
+                if self.embeddings is None:
+                    self.response_queue.put_nowait({ctx.request_id: TextGenerationOutput(
+                        ctx.request_id, [], GenerationStatus.CANCELLED)})
+                else:
+                    self.embeddings.enqueue(ctx)
+                n += 1
+                continue
             self._contexts[ctx.request_id] = ctx
             self.batch_constructor.enqueue_new_request(ctx)
             n += 1
@@ -87,6 +102,8 @@ class TokenGenerationScheduler:
                 break
             ctx = self._contexts.pop(rid, None)
             if ctx is None:
+                if self.embeddings is not None:
+                    self.embeddings.cancel(rid)
                 continue
             ctx.status = GenerationStatus.CANCELLED
             self.batch_constructor.release_request(rid)
@@ -97,7 +114,7 @@ class TokenGenerationScheduler:
 
     def has_work(self) -> bool:
         return (self.batch_constructor.num_requests() > 0 or bool(self.batch_constructor.draining)
-                or self.pipeline.has_pending())
+                or self.pipeline.has_pending() or bool(self.embeddings is not None and self.embeddings.pending))
 
     # ------------------------------------------------------------ one iteration
     def _finish(self, outputs: dict) -> None:
@@ -114,10 +131,11 @@ class TokenGenerationScheduler:
     def run_iteration(self) -> SchedulerProgress:
         self._drain_requests()
         t0 = time.perf_counter()
+        embedded = self.embeddings.run_iteration() if self.embeddings is not None else 0
         batch = self.batch_constructor.construct_batch()
         if not batch.contexts and not self.pipeline.has_pending():
             self._handle_cancels()
-            return SchedulerProgress.NO_PROGRESS
+            return SchedulerProgress.MADE_PROGRESS if embedded else SchedulerProgress.NO_PROGRESS
         outputs = self.pipeline.execute(batch.contexts)
         self.batch_constructor.advance_requests(batch)
         self.total_steps += 1

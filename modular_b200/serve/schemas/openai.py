@@ -165,3 +165,25 @@ class ErrorBody(BaseModel):
 
 class ErrorResponse(BaseModel):
     error: ErrorBody
+
+
+class EmbeddingsRequest(BaseModel):
+    model: str
+    input: Union[str, list[str], list[int], list[list[int]]]
+    encoding_format: str = "float"
+    dimensions: Optional[int] = None
+    pooling: Optional[str] = None      # extension: "last" (default) | "mean"
+    user: Optional[str] = None
+
+
+class EmbeddingData(BaseModel):
+    object: str = "embedding"
+    index: int = 0
+    embedding: Union[list[float], str]
+
+
+class EmbeddingsResponse(BaseModel):
+    object: str = "list"
+    data: list[EmbeddingData]
+    model: str
+    usage: Usage

@@ -78,6 +78,11 @@ def test_errors(echo_client):
     assert r.status_code == 400
 
 
+def test_embeddings_unavailable_on_echo(echo_client):
+    r = echo_client.post("/v1/embeddings", json={"model": "echo", "input": "x"})
+    assert r.status_code == 400 and "embeddings" in r.json()["error"]["message"]
+
+
 def test_worker_rpc(echo_client):
     assert echo_client.get("/max_internal/worker_stats").json()["steps"] > 0
     assert echo_client.post("/reset_prefix_cache").json() == {"success": False}  # echo has no cache
@@ -96,6 +101,15 @@ def test_tiny_llama_server():
         assert a["usage"]["completion_tokens"] == 6 and a["choices"][0]["finish_reason"] == "length"
         assert a["choices"][0]["text"] == b["choices"][0]["text"]
         assert c.post("/reset_prefix_cache").json() == {"success": True}
+        # embeddings from the same worker: unit vectors, deterministic, pooled per input
+        e = c.post("/v1/embeddings", json={"model": "tiny", "input": [[5, 6, 7], [9, 9], [5, 6, 7]]}).json()
+        v = [d["embedding"] for d in e["data"]]
+        assert len(v) == 3 and e["usage"]["prompt_tokens"] == 8
+        assert abs(sum(x * x for x in v[0]) - 1.0) < 1e-4 and v[0] == v[2] and v[0] != v[1]
+        m = c.post("/v1/embeddings", json={"model": "tiny", "input": "hello", "pooling": "mean",
+                                           "encoding_format": "base64", "dimensions": 16}).json()
+        import base64
+        assert len(base64.b64decode(m["data"][0]["embedding"])) == 64
 
 
 def test_incremental_detokenizer_utf8_and_stop():
