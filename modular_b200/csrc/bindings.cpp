@@ -539,6 +539,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("argmax", &argmax);
   m.def("sample", &sample);
   m.def("apply_penalties", &apply_penalties);
+  m.def("apply_token_bitmask", [](Tensor& logits, const Tensor& bitmask) {
+    need_cuda(logits, "logits");
+    TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1 && bitmask.is_contiguous() &&
+                    bitmask.scalar_type() == at::kInt && bitmask.size(0) >= logits.size(0) &&
+                    bitmask.size(1) == (logits.size(1) + 31) / 32,
+                "apply_token_bitmask: fp32 logits [rows, vocab], int32 bitmask [rows, ceil(vocab/32)]");
+    check_rc(mb_apply_token_bitmask(logits.data_ptr<float>(), bitmask.data_ptr<int32_t>(), logits.size(0),
+                                    logits.size(1), logits.stride(0), cur_stream()),
+             "apply_token_bitmask");
+  });
   m.def("read_error_flag", &read_error_flag, py::arg("reset") = true);
   m.def("num_sms", &num_sms);
   m.def("set_pdl", [](bool on) { mb_set_pdl(on ? 1 : 0); });

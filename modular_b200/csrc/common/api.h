@@ -165,6 +165,8 @@ int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, int vocab, 
                         const float* temperature, const int32_t* top_k, const float* top_p,
                         const float* min_p, const uint64_t* seeds, uint64_t step,
                         cudaStream_t stream);
+int mb_apply_token_bitmask(float* logits, const int32_t* bitmask, int rows, int vocab, int ld,
+                           cudaStream_t stream);
 int mb_apply_penalties(float* logits, int rows, int vocab, int ld, const int32_t* tok,
                        const int32_t* cnt, const int32_t* offsets, const float* freq_pen,
                        const float* pres_pen, const float* rep_pen, cudaStream_t stream);

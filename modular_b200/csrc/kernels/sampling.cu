@@ -267,6 +267,22 @@ extern "C" int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, 
                   top_k, top_p, min_p, seeds, step) == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
+// logits[r, v] = -inf where bit (v % 32) of bitmask[r, v / 32] is clear (grammar-constrained decoding)
+__global__ void token_bitmask_kernel(float* __restrict__ logits, const int32_t* __restrict__ bitmask, int vocab,
+                                     int ld, int words) {
+  const int r = blockIdx.y;
+  for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < vocab; v += gridDim.x * blockDim.x)
+    if (!((static_cast<uint32_t>(bitmask[static_cast<size_t>(r) * words + (v >> 5)]) >> (v & 31)) & 1u))
+      logits[static_cast<size_t>(r) * ld + v] = -INFINITY;
+}
+
+extern "C" int mb_apply_token_bitmask(float* logits, const int32_t* bitmask, int rows, int vocab, int ld,
+                                      cudaStream_t stream) {
+  if (rows <= 0) return MB_OK;
+  token_bitmask_kernel<<<dim3(16, rows), 256, 0, stream>>>(logits, bitmask, vocab, ld, (vocab + 31) / 32);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
 extern "C" int mb_apply_penalties(float* logits, int rows, int vocab, int ld, const int32_t* tok,
                                   const int32_t* cnt, const int32_t* offsets, const float* freq,
                                   const float* pres, const float* rep, cudaStream_t stream) {

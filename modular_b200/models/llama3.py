@@ -93,10 +93,12 @@ class Llama3Config:
                                  "high_freq_factor": 4.0, "original_max_position_embeddings": 8192})
 
     @classmethod
-    def tiny(cls) -> "Llama3Config":
-        return cls(hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
-                   num_key_value_heads=2, head_dim=64, vocab_size=4096, rms_norm_eps=1e-5,
-                   rope_theta=500000.0, max_position_embeddings=2048, tie_word_embeddings=True)
+    def tiny(cls, **overrides) -> "Llama3Config":
+        base = dict(hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, head_dim=64, vocab_size=4096, rms_norm_eps=1e-5,
+                    rope_theta=500000.0, max_position_embeddings=2048, tie_word_embeddings=True)
+        base.update(overrides)
+        return cls(**base)
 
 
 @dataclass

@@ -302,3 +302,13 @@ def mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_le
         _lib().mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, out, scale)
         return out
     return ref.mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, scale)
+
+
+def apply_token_bitmask(logits, bitmask):
+    """In place: mask out tokens whose bit is clear in ``bitmask`` (int32 [rows, ceil(vocab/32)])."""
+    if logits.is_cuda:
+        _lib().apply_token_bitmask(logits, bitmask.to(logits.device, non_blocking=True).contiguous())
+    else:
+        from ..pipelines.structured_output import apply_token_bitmask_reference
+        apply_token_bitmask_reference(logits, bitmask)
+    return logits

@@ -216,9 +216,8 @@ class PipelineConfig(ConfigFileModel):
             m.tensor_parallel_degree = max(1, n // max(1, m.data_parallel_degree))
         if rt.max_batch_size is None:
             rt.max_batch_size = 256 if gpu else 8
-        if self.sampling.enable_structured_output and rt.enable_overlap_scheduler:
-            # grammar masks need the token value before the next step is launched
-            rt.enable_overlap_scheduler = False
+        # structured output keeps overlap scheduling: the pipeline reads back the previous token only for
+        # batches that contain a grammar-constrained request
         if rt.pipeline_role is not PipelineRole.PREFILL_AND_DECODE:
             rt.enable_in_flight_batching = False
 

@@ -53,6 +53,8 @@ class SamplingParams:
     detokenize: bool = True
     seed: int = 0
     logprobs: int = 0
+    # grammar spec for constrained decoding: {"type": "json_object" | "json_schema" | "regex" | "ebnf", ...}
+    response_format: Optional[dict] = None
 
     def __post_init__(self):
         if self.temperature < 0:
@@ -201,6 +203,7 @@ class TextContext:
     arrival_time: float = field(default_factory=time.perf_counter)
     task: str = "generate"          # "generate" | "embed" (answered by the embeddings scheduler)
     pooling: str = "last"
+    grammar_state: Any = None       # matcher of a grammar-constrained request (built inside the worker)
     first_token_time: Optional[float] = None
     last_token_time: Optional[float] = None
     # bookkeeping owned by the engine

@@ -149,6 +149,8 @@ class PipelineRegistry:
                                      if b <= min(max_bs, rt.max_graph_capture_batch_size)],
                   eos_token_ids=tokenizer.eos_token_ids)
         llm.tokenizer = tokenizer
+        if pc.sampling.enable_structured_output:
+            llm.pipeline.enable_structured_output(tokenizer)
         llm.pipeline_config = pc
         llm.memory_plan = plan
         return llm

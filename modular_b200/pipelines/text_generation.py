@@ -75,6 +75,34 @@ class TextGenerationPipeline:
         self._graph_launches: dict[int, int] = {}
         self._replayed_launches = 0
         self.record_gpu_time = self.on_gpu
+        self.structured = None      # StructuredOutputBackend, see enable_structured_output
+
+    # ------------------------------------------------------------ grammar-constrained decoding
+    def enable_structured_output(self, tokenizer) -> None:
+        from .structured_output import StructuredOutputBackend
+        self.structured = StructuredOutputBackend(tokenizer, self.model.cfg.vocab_size)
+
+    def _prepare_grammars(self, batch: Sequence[TextContext]) -> bool:
+        """Compile grammars of new requests; True when any request of the batch is constrained."""
+        any_grammar = False
+        for c in batch:
+            spec = c.sampling_params.response_format
+            if spec is None:
+                continue
+            if self.structured is None:
+                raise RuntimeError("a request asked for structured output but the pipeline was built without it")
+            if c.grammar_state is None:
+                c.grammar_state = self.structured.compile(spec)
+                # tokens generated before a preemption are replayed into the fresh matcher
+                for t in c.tokens.generated:
+                    if t >= 0:
+                        c.grammar_state.accept(int(t))
+            any_grammar = True
+        return any_grammar
+
+    def _grammar_bitmask(self, sb: StepBatch):
+        states = [c.grammar_state for c in sb.logit_ctx]
+        return self.structured.bitmask_for(states) if any(s is not None for s in states) else None
 
     # ------------------------------------------------------------ CUDA graphs
     def warmup_graph_capture(self) -> None:
@@ -120,7 +148,8 @@ class TextGenerationPipeline:
         n = len(batch)
         for B in self.graph_batch_sizes:
             if B >= n and B in self._graphs:
-                if all(c.tokens.active_length == 1 and c.sampling_params.is_greedy for c in batch):
+                if all(c.tokens.active_length == 1 and c.sampling_params.is_greedy
+                       and c.sampling_params.response_format is None for c in batch):
                     return B
                 return 0
         return 0
@@ -146,9 +175,13 @@ class TextGenerationPipeline:
                 sb = self.packer.pack(batch, self.kv)
                 meta = self.packer.upload(sb)
                 needs_pen = any(c.sampling_params.needs_penalties for c in sb.logit_ctx)
+                mask = self._grammar_bitmask(sb) if self.structured is not None else None
+                host_sample = needs_pen or mask is not None
                 model.forward_packed(meta, sb.offsets, sb.T, sb.B, sb.bt_stride, sb.n_tiles,
-                                     sb.n_decode, sb.n_logits, sb.has_future, not needs_pen, self._step)
-                if needs_pen:
+                                     sb.n_decode, sb.n_logits, sb.has_future, not host_sample, self._step)
+                if mask is not None:
+                    ops.apply_token_bitmask(model.logits_buf[: sb.n_logits], mask)
+                if host_sample:
                     self._penalties_and_sample(sb, meta)
             self.stats.h2d_bytes += sb.words * 4
             host = self._d2h[self._d2h_i]
@@ -168,6 +201,9 @@ class TextGenerationPipeline:
                 raise RuntimeError("future tokens require the overlap (GPU) pipeline")
             logits = model.forward_tensors(toks, t["positions"], t["slots"], t["block_table"],
                                            t["q_start"], t["q_len"], t["kv_len"], t["logit_rows"])
+            mask = self._grammar_bitmask(sb) if self.structured is not None else None
+            if mask is not None:
+                ops.apply_token_bitmask(logits, mask)
             sampled = self._sample_host(sb, t, logits)
             inflight = _InFlight(sb, None, sampled.cpu(), time.perf_counter())
             self.last_logits = logits
@@ -246,6 +282,8 @@ class TextGenerationPipeline:
         vals = inflight.host_tokens[: sb.n_logits].numpy()
         for i, c in enumerate(sb.logit_ctx):
             c.realize_future_token(int(vals[i]))
+            if c.grammar_state is not None:
+                c.grammar_state.accept(int(vals[i]))
             self.stats.tokens_out += 1
         for c in sb.ctxs:
             if self.kv.contains(c.request_id):
@@ -257,8 +295,14 @@ class TextGenerationPipeline:
     def execute(self, batch: Sequence[TextContext]) -> dict:
         """Run one step. Synchronous mode returns this step's outputs; overlap mode returns the
         previous step's (call with an empty batch to drain)."""
+        constrained = self._prepare_grammars(batch) if batch else False
         if not self.overlap:
             return self._collect(self._launch(batch)) if batch else {}
+        if constrained and self._pending is not None:
+            # the mask of a constrained request depends on its previous token: read that back first
+            out = self._collect(self._pending)
+            self._pending = self._launch(batch)
+            return out
         new = self._launch(batch) if batch else None
         out = self._collect(self._pending)
         self._pending = new

@@ -65,6 +65,11 @@ class ByteTokenizer(PipelineTokenizer):
 
     BOS, EOS = 256, 257
 
+    def vocab_bytes(self, vocab_size: int) -> list:
+        """Byte string of every token id (for grammar compilers)."""
+        return [bytes([i]) if i < 256 else (b"<s>" if i == self.BOS else b"</s>" if i == self.EOS else b"")
+                for i in range(vocab_size)]
+
     def __init__(self, vocab_size: int = 258):
         self.vocab_size = max(vocab_size, 258)
         self.eos_token_ids = (self.EOS,)

@@ -37,8 +37,11 @@ def sampling_from_request(req, default_max_tokens: Optional[int]) -> SamplingPar
     max_tokens = req.max_tokens
     if max_tokens is None and getattr(req, "max_completion_tokens", None) is not None:
         max_tokens = req.max_completion_tokens
+    from ...pipelines.structured_output import response_format_to_spec
     try:
+        spec = response_format_to_spec(getattr(req, "response_format", None))
         return SamplingParams(
+            response_format=spec,
             top_k=req.top_k if req.top_k not in (None, 0) else -1,
             top_p=req.top_p if req.top_p is not None else 1.0,
             min_p=req.min_p or 0.0,
