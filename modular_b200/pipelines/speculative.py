@@ -1,0 +1,193 @@
+"""Speculative decoding: propose several tokens cheaply, verify them with one target-model step.
+
+Two proposers:
+* ``NgramProposer`` (prompt lookup): continue the longest recent n-gram match in the request's own
+  history; no second model.
+* ``DraftModelProposer``: a smaller model with its own paged cache decodes ``k`` tokens greedily
+  (or by sampling, returning its probabilities for rejection sampling).
+
+``SpeculativeDecoder.generate`` runs one sequence: each iteration feeds ``[last, d1..dk]`` to the
+target as a k+1-token ragged step (logits on every row), accepts the longest valid prefix and one
+bonus token, and rewinds the cache length past rejected drafts (their slots are simply overwritten by
+the next step). Acceptance rules: exact match for greedy requests (output is identical to plain
+greedy decoding) and the residual-distribution rejection sampler otherwise, which preserves the
+target distribution.
+
+Reference: max/python/max/pipelines/speculative/ (config, ragged token merger), the rejection
+samplers in max/python/max/pipelines/sampling/sampling.py:433-1018 (greedy / residual acceptance).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from .. import ops
+
+
+@dataclass
+class SpeculativeConfig:
+    method: str = "ngram"            # "ngram" | "draft_model"
+    num_speculative_tokens: int = 4
+    ngram_max: int = 4               # longest n-gram to match
+    ngram_min: int = 1
+
+
+@dataclass
+class SpecStats:
+    steps: int = 0
+    proposed: int = 0
+    accepted: int = 0
+    emitted: int = 0
+
+    @property
+    def acceptance_rate(self) -> float:
+        return self.accepted / self.proposed if self.proposed else 0.0
+
+    @property
+    def tokens_per_step(self) -> float:
+        return self.emitted / self.steps if self.steps else 0.0
+
+
+class NgramProposer:
+    def __init__(self, cfg: SpeculativeConfig):
+        self.cfg = cfg
+
+    def propose(self, history: Sequence[int], k: int):
+        """Draft tokens (possibly fewer than k, possibly none) and None for their probabilities."""
+        h = list(history)
+        for n in range(min(self.cfg.ngram_max, len(h) - 1), self.cfg.ngram_min - 1, -1):
+            tail = h[-n:]
+            for start in range(len(h) - n - 1, -1, -1):     # most recent earlier occurrence
+                if h[start:start + n] == tail:
+                    cont = h[start + n:start + n + k]
+                    if cont:
+                        return cont, None
+        return [], None
+
+    def observe(self, accepted_len: int) -> None:       # nothing to roll back
+        pass
+
+
+class _SeqCache:
+    """One sequence's pages in a private cache tensor + the tensors of a ragged single-sequence step."""
+
+    def __init__(self, model, max_len: int):
+        c, page = model.cfg, model.page_size
+        n_pages = (max_len + page - 1) // page
+        self.model, self.page, self.len = model, page, 0
+        shape = list(model.kv.shape)
+        shape[0] = n_pages + 1
+        self.kv = torch.zeros(shape, dtype=model.kv.dtype, device=model.device)
+        self.bt = torch.arange(1, n_pages + 1, dtype=torch.int32, device=model.device).unsqueeze(0)
+
+    def step(self, tokens: Sequence[int], all_logits: bool) -> torch.Tensor:
+        """Append ``tokens`` at the current length; fp32 logits of every row (or the last)."""
+        dev, n = self.model.device, len(tokens)
+        pos = torch.arange(self.len, self.len + n, dtype=torch.int32, device=dev)
+        i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=dev)
+        rows = torch.arange(n, dtype=torch.int32, device=dev) if all_logits else i32(n - 1)
+        old_kv, self.model.kv = self.model.kv, self.kv
+        try:
+            logits = self.model.forward_tensors(torch.tensor(list(tokens), dtype=torch.long, device=dev), pos,
+                                                (pos.long() + self.page), self.bt, i32(0), i32(n), i32(self.len + n), rows)
+        finally:
+            self.model.kv = old_kv
+        self.len += n
+        return logits
+
+    def rewind(self, new_len: int) -> None:
+        self.len = new_len
+
+
+class DraftModelProposer:
+    def __init__(self, draft_model, max_len: int, temperature: float = 0.0, generator=None):
+        self.cache = _SeqCache(draft_model, max_len)
+        self.temperature, self.gen = temperature, generator
+        self._fed = 0          # how many tokens of the history the draft cache has consumed
+
+    def propose(self, history: Sequence[int], k: int):
+        self.cache.rewind(min(self._fed, len(history) - 1))
+        pending = list(history[self.cache.len:])
+        drafts, probs = [], []
+        for _ in range(k):
+            logits = self.cache.step(pending, all_logits=False)[0]
+            if self.temperature == 0.0:
+                t = int(torch.argmax(logits))
+                probs.append(None)
+            else:
+                p = torch.softmax(logits / self.temperature, -1)
+                t = int(torch.multinomial(p.cpu(), 1, generator=self.gen))
+                probs.append(p.cpu())
+            drafts.append(t)
+            pending = [t]
+        self._fed = len(history)       # the drafts after it are speculative
+        return drafts, (probs if self.temperature > 0.0 else None)
+
+    def observe(self, accepted_len: int) -> None:
+        pass
+
+
+class SpeculativeDecoder:
+    def __init__(self, target_model, cfg: SpeculativeConfig = SpeculativeConfig(), draft_model=None,
+                 max_len: int = 2048):
+        self.target, self.cfg, self.draft, self.max_len = target_model, cfg, draft_model, max_len
+        self.stats = SpecStats()
+        if cfg.method == "draft_model" and draft_model is None:
+            raise ValueError("method draft_model needs a draft model")
+
+    def generate(self, prompt: Sequence[int], max_new_tokens: int, temperature: float = 0.0,
+                 eos_token_ids: Sequence[int] = (), seed: int = 0) -> list:
+        gen = torch.Generator().manual_seed(seed)
+        k = self.cfg.num_speculative_tokens
+        proposer = (DraftModelProposer(self.draft, self.max_len, temperature, gen) if self.cfg.method == "draft_model"
+                    else NgramProposer(self.cfg))
+        cache = _SeqCache(self.target, self.max_len)
+        history = list(prompt)
+        out: list = []
+        # prefill everything but the last prompt token; each iteration then feeds [last] + drafts
+        if len(history) > 1:
+            cache.step(history[:-1], all_logits=False)
+        while len(out) < max_new_tokens:
+            budget = min(k, max_new_tokens - len(out) - 1, self.max_len - len(history) - 1)
+            drafts, q = proposer.propose(history, budget) if budget > 0 else ([], None)
+            base = cache.len
+            logits = cache.step([history[-1]] + list(drafts), all_logits=True)      # [len(drafts) + 1, V]
+            accepted, bonus = self._verify(logits, drafts, q, temperature, gen)
+            self.stats.steps += 1
+            self.stats.proposed += len(drafts)
+            self.stats.accepted += accepted
+            new = list(drafts[:accepted]) + [bonus]
+            cache.rewind(base + 1 + accepted)        # rows of rejected drafts are overwritten next step
+            for t in new:
+                out.append(t)
+                history.append(t)
+                self.stats.emitted += 1
+                if t in eos_token_ids or len(out) >= max_new_tokens:
+                    return out
+        return out
+
+    @staticmethod
+    def _verify(logits, drafts, q, temperature, gen):
+        """Returns (number of accepted drafts, the token that follows them)."""
+        if temperature == 0.0:
+            top = ops.argmax(logits).tolist()
+            a = 0
+            while a < len(drafts) and top[a] == drafts[a]:
+                a += 1
+            return a, int(top[a])
+        p = torch.softmax(logits.float().cpu() / temperature, -1)
+        for i, d in enumerate(drafts):
+            qi = q[i][d] if q is not None else 1.0        # n-gram drafts are a point mass
+            if torch.rand((), generator=gen) < torch.clamp(p[i, d] / qi, max=1.0):
+                continue
+            resid = p[i].clone()
+            if q is not None:
+                resid = torch.clamp(resid - q[i], min=0.0)
+            else:
+                resid[d] = 0.0
+            resid = resid / resid.sum().clamp_min(1e-20)
+            return i, int(torch.multinomial(resid, 1, generator=gen))
+        return len(drafts), int(torch.multinomial(p[len(drafts)], 1, generator=gen))
