@@ -125,12 +125,30 @@ class LLM:
         self._n = 0
 
     # ------------------------------------------------------------ engine loop
+    # ------------------------------------------------------------ LoRA
+    def load_lora(self, name: str, state_dict: dict, alpha: Optional[float] = None, max_loras: int = 8) -> None:
+        """Make a PEFT-layout adapter available to requests (``add_request(..., lora_name=name)``)."""
+        from ..pipelines.lora import LoRAAdapter, LoRAManager
+        if self.pipeline.lora_manager is None:
+            self.pipeline.lora_manager = LoRAManager(max_loras)
+        dtype = self.weights.embed.dtype
+        self.pipeline.lora_manager.load(LoRAAdapter.from_state_dict(name, state_dict, alpha=alpha,
+                                                                    device=self.device, dtype=dtype))
+
+    def unload_lora(self, name: str) -> bool:
+        return self.pipeline.lora_manager is not None and self.pipeline.lora_manager.unload(name)
+
     def add_request(self, prompt_ids, sampling_params: Optional[SamplingParams] = None,
-                    request_id: Optional[str] = None) -> str:
+                    request_id: Optional[str] = None, lora_name: Optional[str] = None) -> str:
         self._n += 1
         rid = request_id or f"llm-{self._n}"
         ctx = TextContext.from_prompt(prompt_ids, self.max_length, rid, sampling_params,
                                       self.eos_token_ids)
+        if lora_name:
+            if self.pipeline.lora_manager is None:
+                raise KeyError(f"LoRA adapter {lora_name!r} is not loaded")
+            self.pipeline.lora_manager.slot_of(lora_name)      # raises when unknown
+            ctx.lora_name = lora_name
         self._records[rid] = RequestRecord(rid, ctx.tokens.prompt_len, arrival=ctx.arrival_time)
         self.scheduler.add_request(ctx)
         return rid

@@ -294,19 +294,25 @@ class Llama3Model:
 
     # ------------------------------------------------------------ op-by-op path
     def forward_tensors(self, tokens, positions, slots, block_table, q_start, q_len, kv_len,
-                        logit_rows, plan=None) -> torch.Tensor:
+                        logit_rows, plan=None, lora=None) -> torch.Tensor:
         """Same computation through :mod:`modular_b200.ops` one op at a time (CPU, and the
         cross-check for the executor on GPU). Returns fp32 logits [len(logit_rows), vocab]."""
-        h = self.forward_hidden(tokens, positions, slots, block_table, q_start, q_len, kv_len, plan=plan)
+        h = self.forward_hidden(tokens, positions, slots, block_table, q_start, q_len, kv_len, plan=plan, lora=lora)
         last = h[logit_rows.long()]
         xn = ops.rms_norm(last, self.w.final_norm, self.cfg.rms_norm_eps)
         logits = ops.linear(xn, self.w.lm_head, out_dtype=torch.float32)
         return logits.float()
 
     def forward_hidden(self, tokens, positions, slots, block_table, q_start, q_len, kv_len, plan=None,
-                       kv=None) -> torch.Tensor:
-        """Residual stream after the last layer, before the final norm: [T, hidden]."""
+                       kv=None, lora=None) -> torch.Tensor:
+        """Residual stream after the last layer, before the final norm: [T, hidden]. ``lora`` is a
+        :class:`modular_b200.pipelines.lora.LoRABatch`; its per-module deltas are added to the base outputs."""
         c = self.cfg
+        if lora is not None and not lora.active:
+            lora = None
+        if lora is not None:
+            return self._forward_hidden_lora(tokens, positions, slots, block_table, q_start, q_len, kv_len, plan,
+                                             self.kv if kv is None else kv, lora)
         kv = self.kv if kv is None else kv
         h = ops.embedding(tokens, self.w.embed)
         for li, l in enumerate(self.w.layers):
@@ -325,6 +331,41 @@ class Llama3Model:
             else:
                 act = ops.silu_mul(ops.linear(x, l.wgu))
             h = ops.linear(act, l.wd, residual=h)
+        return h
+
+    def _forward_hidden_lora(self, tokens, positions, slots, block_table, q_start, q_len, kv_len, plan, kv, lora):
+        """Same network with LoRA deltas on the seven projection modules (separate gate/up products so the
+        deltas enter before the activation)."""
+        c = self.cfg
+        I = c.intermediate_size
+
+        def add(y, delta, lo=None, hi=None):
+            if delta is not None:
+                if lo is None:
+                    y += delta
+                else:
+                    y[:, lo:hi] += delta
+            return y
+
+        h = ops.embedding(tokens, self.w.embed)
+        for li, l in enumerate(self.w.layers):
+            kc, vc = kv[:, 0, li], kv[:, 1, li]
+            x = ops.rms_norm(h, l.attn_norm, c.rms_norm_eps)
+            qkv = ops.linear(x, l.wqkv)
+            add(qkv, lora.delta(li, "q_proj", x), 0, c.q_dim)
+            add(qkv, lora.delta(li, "k_proj", x), c.q_dim, c.q_dim + c.kv_dim)
+            add(qkv, lora.delta(li, "v_proj", x), c.q_dim + c.kv_dim, c.q_dim + 2 * c.kv_dim)
+            ops.rope_kv_store(qkv, positions, slots, self.cos_sin, kc, vc, c.num_attention_heads,
+                              c.num_key_value_heads, c.head_dim, False)
+            a = ops.paged_attention(qkv, kc, vc, block_table, q_start, q_len, kv_len, c.num_attention_heads,
+                                    c.num_key_value_heads, c.head_dim, self.scale, plan=plan)
+            h = add(ops.linear(a, l.wo, residual=h), lora.delta(li, "o_proj", a))
+            x = ops.rms_norm(h, l.mlp_norm, c.rms_norm_eps)
+            gu = ops.linear(x, l.wgu)
+            add(gu, lora.delta(li, "gate_proj", x), 0, I)
+            add(gu, lora.delta(li, "up_proj", x), I, 2 * I)
+            act = ops.silu_mul(gu)
+            h = add(ops.linear(act, l.wd, residual=h), lora.delta(li, "down_proj", act))
         return h
 
     def encode(self, token_lists, pooling: str = "last", normalize: bool = True) -> torch.Tensor:

@@ -204,6 +204,7 @@ class TextContext:
     task: str = "generate"          # "generate" | "embed" (answered by the embeddings scheduler)
     pooling: str = "last"
     grammar_state: Any = None       # matcher of a grammar-constrained request (built inside the worker)
+    lora_name: Optional[str] = None  # adapter applied to this request (None = base model)
     first_token_time: Optional[float] = None
     last_token_time: Optional[float] = None
     # bookkeeping owned by the engine

@@ -76,6 +76,7 @@ class TextGenerationPipeline:
         self._replayed_launches = 0
         self.record_gpu_time = self.on_gpu
         self.structured = None      # StructuredOutputBackend, see enable_structured_output
+        self.lora_manager = None    # pipelines.lora.LoRAManager when adapters are enabled
 
     # ------------------------------------------------------------ grammar-constrained decoding
     def enable_structured_output(self, tokenizer) -> None:
@@ -159,7 +160,8 @@ class TextGenerationPipeline:
         self._step += 1
         self.stats.steps += 1
         model = self.model
-        if self.on_gpu and model.use_executor:
+        uses_lora = self.lora_manager is not None and any(c.lora_name for c in batch)
+        if self.on_gpu and model.use_executor and not uses_lora:
             if self.record_gpu_time:
                 ev0 = torch.cuda.Event(enable_timing=True)
                 ev0.record()
@@ -199,8 +201,15 @@ class TextGenerationPipeline:
             toks = t["tokens"]
             if sb.has_future:
                 raise RuntimeError("future tokens require the overlap (GPU) pipeline")
+            extra = {}
+            if uses_lora:
+                # steps that touch an adapter run op by op: base GEMMs plus grouped shrink/expand GEMMs
+                from .lora import LoRABatch, token_slots_for
+                extra["lora"] = LoRABatch(self.lora_manager, token_slots_for(
+                    self.lora_manager, [c.tokens.active_length for c in sb.ctxs], [c.lora_name for c in sb.ctxs],
+                    self.device))
             logits = model.forward_tensors(toks, t["positions"], t["slots"], t["block_table"],
-                                           t["q_start"], t["q_len"], t["kv_len"], t["logit_rows"])
+                                           t["q_start"], t["q_len"], t["kv_len"], t["logit_rows"], **extra)
             mask = self._grammar_bitmask(sb) if self.structured is not None else None
             if mask is not None:
                 ops.apply_token_bitmask(logits, mask)
@@ -296,6 +305,8 @@ class TextGenerationPipeline:
         """Run one step. Synchronous mode returns this step's outputs; overlap mode returns the
         previous step's (call with an empty batch to drain)."""
         constrained = self._prepare_grammars(batch) if batch else False
+        if batch and self.lora_manager is not None and any(c.lora_name for c in batch):
+            constrained = True      # adapter steps run synchronously on real token values
         if not self.overlap:
             return self._collect(self._launch(batch)) if batch else {}
         if constrained and self._pending is not None:
