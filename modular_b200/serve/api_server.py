@@ -31,7 +31,7 @@ from .process_control import SubprocessExit, subprocess_manager
 from .router import extra_routes, openai_routes
 from .router.openai_routes import error_response
 from .telemetry.metrics import METRICS, configure_metrics
-from .worker_interface import ModelWorkerProxy, RequestQueueFull, WorkerQueues, ZmqQueueSpec
+from .worker_interface import ModelWorkerProxy, ReplicaRouter, RequestQueueFull, WorkerQueues, ZmqQueueSpec
 
 logger = logging.getLogger("modular_b200.serve")
 
@@ -61,27 +61,75 @@ class _Rpc:
             raise TimeoutError(f"worker RPC {name} timed out")
 
 
+def _replica_config(pipeline_config, replica: int, n_replicas: int):
+    """The pipeline config of one data-parallel replica: its share of the configured devices."""
+    if n_replicas <= 1 or pipeline_config is None:
+        return pipeline_config
+    import copy
+    pc = copy.deepcopy(pipeline_config)
+    m = pc.model
+    if m.uses_gpu:
+        ids = m.device_ids
+        per = max(1, len(ids) // n_replicas)
+        mine = ids[replica * per:(replica + 1) * per] or [ids[replica % len(ids)]]
+        m.devices = "gpu:" + ",".join(str(i) for i in mine)
+    m.data_parallel_degree = 1
+    return pc
+
+
+class _MultiRpc:
+    """Side-channel calls fan out to every replica; results come back as a list (one replica: the value)."""
+
+    def __init__(self, rpcs):
+        self.rpcs = rpcs
+
+    async def call(self, name: str, arg=None, timeout_s: float = 10.0):
+        vals = [await r.call(name, arg, timeout_s) for r in self.rpcs]
+        if len(vals) == 1:
+            return vals[0]
+        if name == "reset_prefix_cache":
+            return all(vals)
+        return {"replicas": vals}
+
+
 def make_lifespan(settings: Settings, pipeline_config, tokenizer, factory: Callable, model_name: str,
-                  max_length: int):
+                  max_length: int, factories: Optional[list] = None):
+    """``factories``: one pipeline factory per data-parallel replica (default: ``factory`` for each of
+    ``pipeline_config.model.data_parallel_degree`` replicas)."""
+    n_rep = len(factories) if factories else max(1, getattr(getattr(pipeline_config, "model", None),
+                                                            "data_parallel_degree", 1) or 1)
+    factories = factories or [factory] * n_rep
+
     @contextlib.asynccontextmanager
     async def lifespan(app: FastAPI):
-        specs = {k: ZmqQueueSpec.create(k) for k in ("request", "response", "cancel", "rpc_req", "rpc_resp")}
-        response_pull = specs["response"].pull(bind=True)
-        rpc_resp_pull_spec = specs["rpc_resp"]
-        async with subprocess_manager(
-                "model-worker", model_worker_main, (factory, pipeline_config, specs, settings),
-                ready_timeout_s=settings.mw_timeout_s, use_heartbeat=settings.use_heartbeat,
-                health_fail_s=settings.mw_health_fail_s) as (pm, watcher):
-            queues = WorkerQueues(request=specs["request"].push(bind=False), response=response_pull,
-                                  cancel=specs["cancel"].push(bind=False))
-            proxy = ModelWorkerProxy(queues, settings.max_queue_size)
+        async with contextlib.AsyncExitStack() as stack:
+            proxies, rpcs, watchers = [], [], []
+            for i in range(n_rep):
+                specs = {k: ZmqQueueSpec.create(f"{k}{i}") for k in ("request", "response", "cancel", "rpc_req", "rpc_resp")}
+                response_pull = specs["response"].pull(bind=True)
+                _pm, watcher = await stack.enter_async_context(subprocess_manager(
+                    f"model-worker-{i}", model_worker_main,
+                    (factories[i], _replica_config(pipeline_config, i, n_rep), specs, settings),
+                    ready_timeout_s=settings.mw_timeout_s, use_heartbeat=settings.use_heartbeat,
+                    health_fail_s=settings.mw_health_fail_s))
+                queues = WorkerQueues(request=specs["request"].push(bind=False), response=response_pull,
+                                      cancel=specs["cancel"].push(bind=False))
+                proxies.append(ModelWorkerProxy(queues, settings.max_queue_size))
+                rpcs.append(_Rpc(specs["rpc_req"], specs["rpc_resp"]))
+                watchers.append(watcher)
+            proxy = proxies[0] if n_rep == 1 else ReplicaRouter(proxies)
             proxy.start()
             app.state.pipeline = TokenGeneratorPipeline(model_name, tokenizer, proxy, max_length,
                                                         settings.stream_min_chunk_tokens)
-            app.state.rpc = _Rpc(specs["rpc_req"], rpc_resp_pull_spec)
-            app.state.worker_watcher = watcher
+            app.state.rpc = _MultiRpc(rpcs)
+            async def first_failure():
+                done, _ = await asyncio.wait(watchers, return_when=asyncio.FIRST_COMPLETED)
+                for t in done:
+                    t.result()          # re-raises SubprocessExit of the replica that died
+
+            app.state.worker_watcher = watchers[0] if n_rep == 1 else asyncio.ensure_future(first_failure())
             app.state.proxy = proxy
-            logger.info("server ready: model %s", model_name)
+            logger.info("server ready: model %s on %d replica(s)", model_name, n_rep)
             try:
                 yield
             finally:

@@ -98,3 +98,49 @@ class ModelWorkerProxy:
 def ctx_done(q: asyncio.Queue) -> bool:
     """True when the stream ended normally (nothing left to cancel on the worker)."""
     return getattr(q, "_finished_normally", False)
+
+
+class ReplicaRouter:
+    """Data-parallel replicas behind one proxy interface: every replica is a full model worker (own
+    GPU, own scheduler and KV cache); a request goes to the replica with the fewest requests in
+    flight, ties broken round-robin, and stays there (its KV cache lives on that replica).
+
+    Reference: max/python/max/serve/scheduler/batch_constructor/text_batch_constructor.py:566-594
+    (least-loaded replica assignment) and the data_parallel_degree setting of the model config.
+    """
+
+    def __init__(self, proxies):
+        if not proxies:
+            raise ValueError("at least one replica is needed")
+        self.proxies = list(proxies)
+        self._rr = 0
+        self.assigned = [0] * len(self.proxies)      # requests ever routed to each replica
+
+    def start(self) -> None:
+        for p in self.proxies:
+            p.start()
+
+    async def stop(self) -> None:
+        for p in self.proxies:
+            await p.stop()
+
+    @property
+    def pending(self) -> int:
+        return sum(p.pending for p in self.proxies)
+
+    def pick(self) -> int:
+        n = len(self.proxies)
+        best = min(range(n), key=lambda i: (self.proxies[i].pending, (i - self._rr) % n))
+        self._rr = (best + 1) % n
+        return best
+
+    async def stream(self, ctx):
+        i = self.pick()
+        self.assigned[i] += 1
+        async for out in self.proxies[i].stream(ctx):
+            yield out
+
+    def cancel(self, request_id: str) -> None:
+        for p in self.proxies:
+            if request_id in p._streams:
+                p.cancel(request_id)

@@ -199,3 +199,16 @@ def test_record_and_replay(multi_api_client):
 
     res = asyncio.run(replay_recording(str(c.recording), "http://test", concurrency=4, client=Adapter()))
     assert res.sent == len(recs) and res.status_match == res.sent, res.failures
+
+
+def test_data_parallel_replicas_share_the_load():
+    pc = _config(model_path="echo", devices="cpu", data_parallel_degree=2)
+    app = fastapi_app(Settings(), pc, ByteTokenizer(), EchoPipeline, "echo", 4096)
+    with TestClient(app) as c:
+        for i in range(6):
+            r = c.post("/v1/completions", json={"model": "echo", "prompt": f"req {i}", "max_tokens": 16})
+            assert r.status_code == 200 and r.json()["choices"][0]["text"] == f"req {i}"
+        stats = c.get("/max_internal/worker_stats").json()["replicas"]
+        assert len(stats) == 2 and all(s["steps"] > 0 for s in stats)
+        assert c.app.state.proxy.assigned == [3, 3]
+        assert c.post("/reset_prefix_cache").json() == {"success": False}
