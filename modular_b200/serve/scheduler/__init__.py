@@ -12,8 +12,9 @@ __all__ = ["BatchType", "SchedulerBatch", "TextBatchConstructor", "TokenGenerati
 
 def load_scheduler(pipeline, config: TokenGenerationSchedulerConfig, pipeline_role: str = "prefill_and_decode",
                    **queues):
-    """Pick the scheduler for a pipeline and role."""
-    if pipeline_role != "prefill_and_decode":
-        raise NotImplementedError(
-            f"pipeline_role={pipeline_role!r}: disaggregated prefill/decode scheduling is not built yet")
+    """Pick the scheduler for a pipeline and role. ``prefill_only`` / ``decode_only`` engines are driven by
+    :class:`disaggregated.PrefillNode` / :class:`disaggregated.DecodeNode`, which wrap an engine built with
+    the ordinary scheduler (the role changes who feeds it and where finished prefills go)."""
+    if pipeline_role not in ("prefill_and_decode", "prefill_only", "decode_only"):
+        raise ValueError(f"unknown pipeline_role {pipeline_role!r}")
     return TokenGenerationScheduler(config, pipeline, **queues)

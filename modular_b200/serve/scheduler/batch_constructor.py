@@ -78,12 +78,26 @@ class TextBatchConstructor:
         return (request_id in self.ce_reqs or request_id in self.tg_reqs
                 or request_id in self.draining)
 
-    def release_request(self, request_id: str) -> None:
+    # optional hook ``on_release(request_id, n_tokens_with_kv)`` called just before a request's pages
+    # are freed (a prefill-only engine exports them to the decode engine there)
+    on_release = None
+
+    def release_request(self, request_id: str, ctx: Optional[TextContext] = None) -> None:
+        ctx = self.ce_reqs.pop(request_id, None) or self.tg_reqs.pop(request_id, None) or ctx
+        ctx = self.draining.pop(request_id, None) or ctx
         self.ce_reqs.pop(request_id, None)
         self.tg_reqs.pop(request_id, None)
-        self.draining.pop(request_id, None)
         if self.kv is not None:
+            if self.on_release is not None and ctx is not None and self.kv.contains(request_id):
+                self.on_release(request_id, ctx.tokens.processed)
             self.kv.release(request_id)
+
+    def enqueue_prefilled_request(self, ctx: TextContext) -> None:
+        """A request whose prompt KV is already in this engine's cache (disaggregated decode): it joins
+        the token-generation queue directly. Its pages must have been claimed and filled."""
+        if ctx.request_id in self.ce_reqs or ctx.request_id in self.tg_reqs:
+            raise ValueError(f"duplicate request id {ctx.request_id}")
+        self.tg_reqs[ctx.request_id] = ctx
 
     # ------------------------------------------------------------ policy pieces
     def _identify_priority(self) -> BatchType:

@@ -121,7 +121,7 @@ class TokenGenerationScheduler:
         done = [rid for rid, o in outputs.items() if o.is_done]
         for rid in done:
             if rid in self._contexts:
-                self.batch_constructor.release_request(rid)
+                self.batch_constructor.release_request(rid, self._contexts[rid])
                 del self._contexts[rid]
         # outputs for requests already gone (cancelled, or extra speculative step) are dropped
         live = {rid: o for rid, o in outputs.items() if o.tokens or o.is_done}
