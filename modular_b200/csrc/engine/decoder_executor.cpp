@@ -104,7 +104,7 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
           in.block_table, in.bt_stride, in.q_start, in.q_len, in.kv_len, in.tile_seq, in.tile_q0,
           in.n_tiles, in.n_decode, in.decode_seq, c.n_q, c.n_kv, c.head_dim, c.page_size,
           c.attn_scale, buf.err, stream));
-      launches += 3;
+      launches += 3;   // rmsnorm, rope+store, attention
     } else {
       MB_TRY(mb_paged_attention(buf.qkv, qkv_dim, buf.attn, q_dim, kc, vc, in.block_table,
                                 in.bt_stride, in.q_start, in.q_len, in.kv_len, in.tile_seq,

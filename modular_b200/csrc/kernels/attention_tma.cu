@@ -48,6 +48,7 @@ struct Params {
   int ldq, ldo, bt_stride, page_size, n_tiles;
   long long k_off_rows, v_off_rows, page_rows;
   float scale_log2;
+  int q_rows_alloc;      // rows of shared memory reserved for Q (64, or 16 in a decode-only launch)
 };
 
 struct Bars {
@@ -176,7 +177,7 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
                                              ~static_cast<uintptr_t>(1023));
   bf16* sKV = reinterpret_cast<bf16*>(smem);                       // [stages][K tile | V tile]
   bf16* sQ = sKV + kStages * 2 * kTileElems;                        // [64][HD]
-  Bars* bars = reinterpret_cast<Bars*>(sQ + 64 * HD);
+  Bars* bars = reinterpret_cast<Bars*>(sQ + p.q_rows_alloc * HD);   // Q region: 64 rows (prefill) or 16 (decode-only launch)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kvh = blockIdx.y;
   pdl_wait();      // Q, the KV pages of this step and the batch metadata come from earlier work on the stream
@@ -348,18 +349,31 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
 }
 
 template <int HD, int G>
-static int launch(const CUtensorMap& tm, const Params& p, int n_ctas, int n_kv, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(kStages) * 2 * 64 * HD * 2 + 64 * HD * 2 + sizeof(Bars) + 1024;
+static int launch_one(const CUtensorMap& tm, Params p, int n_ctas, int n_kv, int q_rows, cudaStream_t stream) {
+  const size_t smem_max = static_cast<size_t>(kStages) * 2 * 64 * HD * 2 + 64 * HD * 2 + sizeof(Bars) + 1024;
+  const size_t smem = static_cast<size_t>(kStages) * 2 * 64 * HD * 2 + static_cast<size_t>(q_rows) * HD * 2 +
+                      sizeof(Bars) + 1024;
   auto kern = attn_tma_kernel<HD, G>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_max)) !=
         cudaSuccess)
       return MB_ERR_LAUNCH;
     configured = true;
   }
+  p.q_rows_alloc = q_rows;
   if (launch_k(kern, dim3(n_ctas, n_kv), dim3(kThreads), smem, stream, tm, p) != cudaSuccess) return MB_ERR_LAUNCH;
-  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+  return MB_OK;
+}
+
+// One launch covers prefill tiles and decode sequences. A decode-only step (the common serving case)
+// reserves shared memory for 16 query rows instead of 64, which lets two CTAs share an SM.
+template <int HD, int G>
+static int launch(const CUtensorMap& tm, const Params& p, int n_decode, int n_kv, const int32_t* decode_seq,
+                  cudaStream_t stream) {
+  (void)decode_seq;
+  const int nd = n_decode < 0 ? 0 : n_decode;
+  return launch_one<HD, G>(tm, p, p.n_tiles + nd, n_kv, p.n_tiles > 0 ? 64 : 16, stream);
 }
 
 }  // namespace at2
@@ -396,10 +410,9 @@ extern "C" int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo
   CUtensorMap tm;
   const int rc = cached_tmap(&tm, kv_base, static_cast<uint64_t>(total_rows), head_dim, head_dim, 64, 2);
   if (rc != MB_OK) return rc;
-  const int n_ctas = p.n_tiles + (n_decode < 0 ? 0 : n_decode);
   const int G = n_q / n_kv;
 #define MB_ATTN2_CASE(HD_, G_) \
-  if (head_dim == HD_ && G == G_) return launch<HD_, G_>(tm, p, n_ctas, n_kv, stream);
+  if (head_dim == HD_ && G == G_) return launch<HD_, G_>(tm, p, n_decode, n_kv, decode_seq, stream);
   MB_ATTN2_CASE(128, 1) MB_ATTN2_CASE(128, 2) MB_ATTN2_CASE(128, 4) MB_ATTN2_CASE(128, 8)
   MB_ATTN2_CASE(128, 16)
   MB_ATTN2_CASE(64, 1) MB_ATTN2_CASE(64, 2) MB_ATTN2_CASE(64, 4) MB_ATTN2_CASE(64, 8)
