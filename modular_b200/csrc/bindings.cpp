@@ -638,6 +638,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                              reinterpret_cast<const void*>(mc_in), f, n, algo, error_flag(), cur_stream()),
              "tp_allreduce");
   });
+  m.def("tp_wait_flag", [](const Tensor& flag, int target, int timeout_ms, int code, Tensor& ok_out) {
+    need_cuda(flag, "flag");
+    check_rc(mb_tp_wait_flag(flag.data_ptr<int32_t>(), target, timeout_ms, code, error_flag(),
+                             ok_out.data_ptr<int32_t>(), cur_stream()),
+             "tp_wait_flag");
+  });
   m.def("tp_broadcast", [](int world, int rank, int root, const std::vector<int64_t>& in_bufs, Tensor& out,
                            const std::vector<int64_t>& flags, int64_t nbytes) {
     void* a[8] = {}; int* f[8] = {};

@@ -141,6 +141,9 @@ int mb_tp_allgather(int world, int rank, void* const* dst_bufs, int* const* flag
 int mb_tp_allreduce(int world, int rank, void* const* in_bufs, void* const* out_bufs, void* out,
                     const void* mc_in, int* const* flags, long long n, int algo, int* err,
                     cudaStream_t stream);
+// Bounded wait on a flag word (at most 5 s): *ok_out = 1 when reached, else `code` goes to the error word.
+int mb_tp_wait_flag(const int* flag, int target, unsigned timeout_ms, int code, int* err, int* ok_out,
+                    cudaStream_t stream);
 int mb_tp_broadcast(int world, int rank, int root, void* const* in_bufs, void* out, int* const* flags,
                     long long nbytes, int* err, cudaStream_t stream);
 

@@ -393,6 +393,15 @@ tp_broadcast_kernel(TpPeers p, int root, uint8_t* __restrict__ out, long long n,
   tp_finish_barrier(p, 1, epoch, err);
 }
 
+// Waits (bounded) until *flag >= target; on timeout the error word receives `code` and the kernel
+// returns normally, so the context stays usable. Used to probe a peer's progress flag from the host
+// side of failure detection without ever blocking a GPU.
+__global__ void tp_wait_flag_kernel(const int* flag, int target, unsigned long long timeout_ns, int code,
+                                    int* err, int* ok_out) {
+  const bool ok = wait_flag_ge(flag, target, err, code, timeout_ns);
+  if (ok_out) *ok_out = ok ? 1 : 0;
+}
+
 static TpPeers make_peers(int world, int rank, void* const* a, void* const* b, int* const* flags) {
   TpPeers p;
   p.world = world; p.rank = rank;
@@ -493,5 +502,13 @@ extern "C" int mb_tp_broadcast(int world, int rank, int root, void* const* in_bu
   if (grid < 1) grid = 1;
   tp_broadcast_kernel<<<grid, 256, 0, stream>>>(make_peers(world, rank, in_bufs, nullptr, flags), root,
                                                 static_cast<uint8_t*>(out), nbytes, err);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+extern "C" int mb_tp_wait_flag(const int* flag, int target, unsigned timeout_ms, int code, int* err, int* ok_out,
+                               cudaStream_t stream) {
+  if (timeout_ms > 5000) timeout_ms = 5000;  // a wait in a kernel never exceeds a few seconds
+  tp_wait_flag_kernel<<<1, 1, 0, stream>>>(flag, target, static_cast<unsigned long long>(timeout_ms) * 1000000ull,
+                                           code, err, ok_out);
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
