@@ -734,9 +734,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                   topk_ids.size(1), e_local, cap, cur_stream()),
              "ep_combine_reduce");
   });
-  m.def("ep_dequant_rows", [](const Tensor& src, Tensor& dst, int n) {
+  m.def("ep_dequant_rows", [](const Tensor& src, Tensor& dst, int n, const c10::optional<Tensor>& n_rows) {
     need_cuda(src, "src");
-    check_rc(mb_ep_dequant_rows(src.data_ptr(), dst.data_ptr(), n, dst.size(1), cur_stream()), "ep_dequant_rows");
+    check_rc(mb_ep_dequant_rows(src.data_ptr(), dst.data_ptr(), n, dst.size(1),
+                                static_cast<const int32_t*>(optptr(n_rows)), cur_stream()),
+             "ep_dequant_rows");
   });
   py::class_<PyDecoderExecutor>(m, "DecoderExecutor")
       .def(py::init<py::dict>())

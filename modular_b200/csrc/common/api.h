@@ -160,7 +160,7 @@ int mb_ep_combine_send(int world, int rank, void* const* ret_x, int* const* flag
 int mb_ep_combine_reduce(const void* ret_x, const int32_t* topk_ids, const int32_t* send_pos, const float* w,
                          const void* shared, void* y, int T, int H, int top_k, int e_local, int cap,
                          cudaStream_t stream);
-int mb_ep_dequant_rows(const void* src, void* dst, int n, int H, cudaStream_t stream);
+int mb_ep_dequant_rows(const void* src, void* dst, int n, int H, const int32_t* n_rows_dev, cudaStream_t stream);
 
 // ---- sampling (sampling.cu) ----------------------------------------------------------------
 int mb_argmax(const float* logits, int64_t* out, int rows, int vocab, int ld, cudaStream_t stream);

@@ -197,9 +197,10 @@ __global__ void ep_combine_reduce_kernel(const uint8_t* __restrict__ ret_x, cons
 
 // fp8 rows [n, H + H/128*4] -> bf16 rows (used after dispatch when the experts run in bf16)
 __global__ void ep_dequant_rows_kernel(const uint8_t* __restrict__ src, bf16* __restrict__ dst, int n, int H,
-                                       int row_bytes) {
+                                       int row_bytes, const int32_t* __restrict__ n_rows_dev) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int per_row = H >> 2;
+  if (n_rows_dev != nullptr && *n_rows_dev < n) n = *n_rows_dev;   // only the rows that were received
   if (i >= static_cast<long long>(n) * per_row) return;
   const int r = static_cast<int>(i / per_row), c = static_cast<int>(i % per_row) * 4;
   const uint8_t* row = src + static_cast<size_t>(r) * row_bytes;
@@ -283,10 +284,11 @@ extern "C" int mb_ep_combine_reduce(const void* ret_x, const int32_t* topk_ids, 
   return EP_LAUNCH_OK();
 }
 
-extern "C" int mb_ep_dequant_rows(const void* src, void* dst, int n, int H, cudaStream_t stream) {
+extern "C" int mb_ep_dequant_rows(const void* src, void* dst, int n, int H, const int32_t* n_rows_dev,
+                                  cudaStream_t stream) {
   if (n <= 0) return MB_OK;
   const long long work = static_cast<long long>(n) * (H / 4);
   ep::ep_dequant_rows_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
-      static_cast<const uint8_t*>(src), static_cast<ep::bf16*>(dst), n, H, H + (H / 128) * 4);
+      static_cast<const uint8_t*>(src), static_cast<ep::bf16*>(dst), n, H, H + (H / 128) * 4, n_rows_dev);
   return EP_LAUNCH_OK();
 }

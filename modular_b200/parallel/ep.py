@@ -80,7 +80,7 @@ class EPContext:
         if self.fp8:
             L.moe_permute_rows(self.recv_x.tensor.view(W * self.cap, self.row_bytes), self.order, n_rows,
                                self.xq, 1)
-            L.ep_dequant_rows(self.xq, self.xp, W * self.cap)
+            L.ep_dequant_rows(self.xq, self.xp, W * self.cap, n_rows)
         else:
             L.moe_permute_rows(self.recv_x.tensor.view(torch.bfloat16).view(W * self.cap, self.hidden),
                                self.order, n_rows, self.xp, 1)
