@@ -39,6 +39,9 @@ def _load():
             # step kernels launch as programmatic dependents unless MB200_PDL=0 (see csrc/common/launch.h)
             if os.environ.get("MB200_PDL", "1") not in ("", "0") and hasattr(mod, "set_pdl"):
                 mod.set_pdl(True)
+            # MB200_ATTN_TC=1: prefill attention tiles on the tcgen05 kernel (head_dim 128)
+            if os.environ.get("MB200_ATTN_TC", "0") not in ("", "0") and hasattr(mod, "set_attn_tc"):
+                mod.set_attn_tc(True)
             _MOD = mod
         except Exception as e:  # noqa: BLE001
             _ERR = e

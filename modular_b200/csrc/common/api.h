@@ -90,6 +90,18 @@ int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo, const voi
                            const int32_t* decode_seq, int n_q, int n_kv, int head_dim, int page_size,
                            float scale, int* err, cudaStream_t stream);
 
+// tcgen05 prefill attention (attention_tc.cu): same addressing as mb_paged_attention_tma, head_dim 128 only.
+int mb_paged_attention_prefill_tc(const void* q, int ldq, void* out, int ldo, const void* kv_base,
+                                  long long total_rows, long long k_off_rows, long long v_off_rows,
+                                  long long page_rows, const int32_t* block_table, int bt_stride,
+                                  const int32_t* q_start, const int32_t* q_len, const int32_t* kv_len,
+                                  const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, int n_q,
+                                  int n_kv, int head_dim, int page_size, float scale, int* err,
+                                  cudaStream_t stream);
+// Route the prefill tiles of mb_paged_attention_tma through the tcgen05 kernel (process-wide switch).
+void mb_set_attn_tc(int on);
+int mb_get_attn_tc(void);
+
 // ---- multi-head latent attention over a paged latent cache (mla.cu) ------------------------
 int mb_mla_paged_attention(const void* q_lat, const void* q_rope, void* out, const void* cache,
                            long long page_stride, const int32_t* block_table, int bt_stride,

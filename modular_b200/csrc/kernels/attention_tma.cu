@@ -381,6 +381,10 @@ static int launch(const CUtensorMap& tm, const Params& p, int n_decode, int n_kv
 
 using namespace mb;
 
+static bool g_attn_tc = false;
+extern "C" void mb_set_attn_tc(int on) { g_attn_tc = on != 0; }
+extern "C" int mb_get_attn_tc(void) { return g_attn_tc ? 1 : 0; }
+
 // kv_base: start of the KV allocation, viewed as [total_rows, head_dim] bf16. A token of page
 // `pg`, KV head `h`, offset `o` lives at row  k_off_rows (or v_off_rows) + pg*page_rows +
 // h*page_size + o. Requires page_size % 64 == 0.
@@ -411,6 +415,16 @@ extern "C" int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo
   const int rc = cached_tmap(&tm, kv_base, static_cast<uint64_t>(total_rows), head_dim, head_dim, 64, 2);
   if (rc != MB_OK) return rc;
   const int G = n_q / n_kv;
+  if (g_attn_tc && head_dim == 128 && p.n_tiles > 0 && G <= 16 && (G & (G - 1)) == 0) {
+    // prefill tiles on the tcgen05 kernel, decode sequences (if any) on this file's kernel
+    const int rc2 = mb_paged_attention_prefill_tc(q, ldq, out, ldo, kv_base, total_rows, k_off_rows, v_off_rows,
+                                                  page_rows, block_table, bt_stride, q_start, q_len, kv_len, tile_seq,
+                                                  tile_q0, p.n_tiles, n_q, n_kv, head_dim, page_size, scale, err,
+                                                  stream);
+    if (rc2 != MB_OK) return rc2;
+    if (n_decode <= 0) return MB_OK;
+    p.n_tiles = 0;
+  }
 #define MB_ATTN2_CASE(HD_, G_) \
   if (head_dim == HD_ && G == G_) return launch<HD_, G_>(tm, p, n_decode, n_kv, decode_seq, stream);
   MB_ATTN2_CASE(128, 1) MB_ATTN2_CASE(128, 2) MB_ATTN2_CASE(128, 4) MB_ATTN2_CASE(128, 8)

@@ -205,6 +205,10 @@ class TextContext:
     pooling: str = "last"
     grammar_state: Any = None       # matcher of a grammar-constrained request (built inside the worker)
     lora_name: Optional[str] = None  # adapter applied to this request (None = base model)
+    # one entry per generated token when sampling_params.logprobs > 0:
+    # {"token": id, "logprob": float, "top": [(id, logprob), ...]}
+    logprob_entries: list = field(default_factory=list)
+    logprobs_emitted: int = 0
     first_token_time: Optional[float] = None
     last_token_time: Optional[float] = None
     # bookkeeping owned by the engine
@@ -314,7 +318,14 @@ class TextContext:
                 ):
                     toks = toks[: i + 1]
                     break
+        lps = None
+        if self.sampling_params.logprobs and toks:
+            lps = self.logprob_entries[self.logprobs_emitted:self.logprobs_emitted + len(toks)]
+            self.logprobs_emitted += len(toks)
         self.emitted += len(toks)
         done = self.is_done and self.pending_future == 0
+        if lps is not None:
+            return TextGenerationOutput(self.request_id, toks,
+                                        self.status if done else GenerationStatus.ACTIVE, lps)
         return TextGenerationOutput(self.request_id, toks,
                                     self.status if done else GenerationStatus.ACTIVE)

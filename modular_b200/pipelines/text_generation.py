@@ -35,6 +35,7 @@ class _InFlight:
     event: Optional[torch.cuda.Event]
     host_tokens: Optional[torch.Tensor]   # pinned int64 [n_logits] (GPU) or plain tensor (CPU)
     launched_at: float = 0.0
+    logprobs: Optional[tuple] = None      # (chosen [n], top values [n, k], top ids [n, k]) when a request asked
 
 
 @dataclass
@@ -150,7 +151,8 @@ class TextGenerationPipeline:
         for B in self.graph_batch_sizes:
             if B >= n and B in self._graphs:
                 if all(c.tokens.active_length == 1 and c.sampling_params.is_greedy
-                       and c.sampling_params.response_format is None for c in batch):
+                       and c.sampling_params.response_format is None and not c.sampling_params.logprobs
+                       for c in batch):
                     return B
                 return 0
         return 0
@@ -165,6 +167,7 @@ class TextGenerationPipeline:
             if self.record_gpu_time:
                 ev0 = torch.cuda.Event(enable_timing=True)
                 ev0.record()
+            step_logprobs = None
             B_graph = self._graph_bucket(batch)
             if B_graph:
                 g, fixed, off, words = self._graphs[B_graph]
@@ -178,13 +181,16 @@ class TextGenerationPipeline:
                 meta = self.packer.upload(sb)
                 needs_pen = any(c.sampling_params.needs_penalties for c in sb.logit_ctx)
                 mask = self._grammar_bitmask(sb) if self.structured is not None else None
-                host_sample = needs_pen or mask is not None
+                wants_lp = any(c.sampling_params.logprobs for c in sb.logit_ctx)
+                host_sample = needs_pen or mask is not None or wants_lp
                 model.forward_packed(meta, sb.offsets, sb.T, sb.B, sb.bt_stride, sb.n_tiles,
                                      sb.n_decode, sb.n_logits, sb.has_future, not host_sample, self._step)
                 if mask is not None:
                     ops.apply_token_bitmask(model.logits_buf[: sb.n_logits], mask)
                 if host_sample:
                     self._penalties_and_sample(sb, meta)
+                if wants_lp:
+                    step_logprobs = self._logprobs_of(sb, model.logits_buf, model.sampled)
             self.stats.h2d_bytes += sb.words * 4
             host = self._d2h[self._d2h_i]
             self._d2h_i = (self._d2h_i + 1) % len(self._d2h)
@@ -194,7 +200,7 @@ class TextGenerationPipeline:
             if self.record_gpu_time:
                 self._gpu_events.append((ev0, ev))
             self.stats.d2h_bytes += sb.n_logits * 8
-            inflight = _InFlight(sb, ev, host, time.perf_counter())
+            inflight = _InFlight(sb, ev, host, time.perf_counter(), step_logprobs)
         else:
             sb = self.packer.pack(batch, self.kv)
             t = BatchPacker.tensors(sb, self.device)
@@ -214,7 +220,7 @@ class TextGenerationPipeline:
             if mask is not None:
                 ops.apply_token_bitmask(logits, mask)
             sampled = self._sample_host(sb, t, logits)
-            inflight = _InFlight(sb, None, sampled.cpu(), time.perf_counter())
+            inflight = _InFlight(sb, None, sampled.cpu(), time.perf_counter(), self._logprobs_of(sb, logits, sampled))
             self.last_logits = logits
         self.stats.tokens_in += sb.T
         # bookkeeping that does not need the token values
@@ -258,6 +264,17 @@ class TextGenerationPipeline:
                    f32("min_p"), meta[off["seeds"] : off["seeds"] + 2 * n].view(torch.int64),
                    self._step, out=self.model.sampled[:n])
 
+    @staticmethod
+    def _logprobs_of(sb: StepBatch, logits: torch.Tensor, sampled: torch.Tensor) -> Optional[tuple]:
+        """Log-probabilities of the sampled tokens and the top-k alternatives (k = the largest request)."""
+        k = max(((c.sampling_params.logprobs or 0) for c in sb.logit_ctx), default=0)
+        if k <= 0:
+            return None
+        lp = torch.log_softmax(logits[: sb.n_logits].float(), dim=-1)
+        chosen = lp.gather(1, sampled[: sb.n_logits].view(-1, 1).long()).squeeze(1)
+        top_v, top_i = lp.topk(min(int(k), lp.shape[1]), dim=-1)
+        return chosen.cpu(), top_v.cpu(), top_i.cpu()
+
     def _sample_host(self, sb: StepBatch, t: dict, logits: torch.Tensor) -> torch.Tensor:
         if any(c.sampling_params.needs_penalties for c in sb.logit_ctx):
             tok, cnt, offs = [], [], [0]
@@ -293,6 +310,11 @@ class TextGenerationPipeline:
             c.realize_future_token(int(vals[i]))
             if c.grammar_state is not None:
                 c.grammar_state.accept(int(vals[i]))
+            if inflight.logprobs is not None and c.sampling_params.logprobs:
+                chosen, top_v, top_i = inflight.logprobs
+                k = int(c.sampling_params.logprobs)
+                c.logprob_entries.append({"token": int(vals[i]), "logprob": float(chosen[i]),
+                                          "top": [(int(a), float(b)) for a, b in zip(top_i[i, :k], top_v[i, :k])]})
             self.stats.tokens_out += 1
         for c in sb.ctxs:
             if self.kv.contains(c.request_id):

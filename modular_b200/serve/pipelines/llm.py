@@ -26,6 +26,7 @@ class TokenChunk:
     finish_reason: Optional[str] = None
     prompt_tokens: int = 0
     completion_tokens: int = 0
+    logprobs: Optional[list] = None     # entries {"token", "logprob", "top"} aligned with token_ids
 
 
 def finish_reason_of(status: GenerationStatus, stopped_on_string: bool = False) -> Optional[str]:
@@ -59,6 +60,7 @@ class TokenGeneratorPipeline:
         METRICS.request_count.inc()
         METRICS.input_tokens.inc(n_prompt)
         buf_ids: list = []
+        buf_lps: list = []
         buf_text = ""
         async for out in self.proxy.stream(ctx):
             now = time.perf_counter()
@@ -72,12 +74,14 @@ class TokenGeneratorPipeline:
             text = detok.push(out.tokens, final=out.is_done) if detok is not None else ""
             stopped = detok is not None and detok.stopped
             buf_ids.extend(out.tokens)
+            if getattr(out, "log_probabilities", None):
+                buf_lps.extend(out.log_probabilities)
             buf_text += text
             done = out.is_done or stopped
             if done or len(buf_ids) >= self.min_chunk:
                 reason = finish_reason_of(out.final_status, stopped) if done else None
-                yield TokenChunk(buf_text, buf_ids, reason, n_prompt, n_out)
-                buf_ids, buf_text = [], ""
+                yield TokenChunk(buf_text, buf_ids, reason, n_prompt, n_out, buf_lps or None)
+                buf_ids, buf_lps, buf_text = [], [], ""
             if done:
                 break
         METRICS.output_tokens.inc(n_out)
@@ -86,13 +90,14 @@ class TokenGeneratorPipeline:
         METRICS.request_time_ms.observe((time.perf_counter() - t_start) * 1e3)
 
     async def all_tokens(self, prompt, sampling_params: SamplingParams, request_id: Optional[str] = None) -> TokenChunk:
-        text, ids, reason, n_prompt, n_out = "", [], None, 0, 0
+        text, ids, reason, n_prompt, n_out, lps = "", [], None, 0, 0, []
         async for ch in self.next_token_chunk(prompt, sampling_params, request_id):
             text += ch.text
             ids.extend(ch.token_ids)
+            lps.extend(ch.logprobs or [])
             reason = ch.finish_reason or reason
             n_prompt, n_out = ch.prompt_tokens, ch.completion_tokens
-        return TokenChunk(text, ids, reason, n_prompt, n_out)
+        return TokenChunk(text, ids, reason, n_prompt, n_out, lps or None)
 
     async def embed(self, prompt: Union[str, Sequence[int]], pooling: str = "last",
                     request_id: Optional[str] = None):

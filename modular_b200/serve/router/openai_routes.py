@@ -51,9 +51,38 @@ def sampling_from_request(req, default_max_tokens: Optional[int]) -> SamplingPar
             repetition_penalty=req.repetition_penalty or 1.0,
             max_new_tokens=max_tokens if max_tokens is not None else default_max_tokens,
             min_new_tokens=req.min_tokens or 0, ignore_eos=req.ignore_eos, stop=stop,
-            stop_token_ids=req.stop_token_ids, seed=req.seed or 0)
+            stop_token_ids=req.stop_token_ids, seed=req.seed or 0, logprobs=_logprobs_requested(req))
     except ValueError as e:
         raise HTTPException(status_code=400, detail=str(e)) from e
+
+
+def _logprobs_requested(req) -> int:
+    """Number of alternatives per token (0 = off). Completions: ``logprobs: N``; chat: ``logprobs: true`` +
+    ``top_logprobs: N``."""
+    lp = getattr(req, "logprobs", None)
+    if lp is None or lp is False:
+        return 0
+    if lp is True:
+        return max(1, int(getattr(req, "top_logprobs", None) or 1))
+    return max(1, int(lp))
+
+
+def _completion_logprobs(pipeline, ch) -> Optional[dict]:
+    if not ch.logprobs:
+        return None
+    dec = lambda t: pipeline.tokenizer.decode([t])
+    return {"tokens": [dec(e["token"]) for e in ch.logprobs],
+            "token_logprobs": [e["logprob"] for e in ch.logprobs],
+            "top_logprobs": [{dec(t): lp for t, lp in e["top"]} for e in ch.logprobs]}
+
+
+def _chat_logprobs(pipeline, ch) -> Optional[dict]:
+    if not ch.logprobs:
+        return None
+    dec = lambda t: pipeline.tokenizer.decode([t])
+    return {"content": [{"token": dec(e["token"]), "logprob": e["logprob"],
+                         "top_logprobs": [{"token": dec(t), "logprob": lp} for t, lp in e["top"]]}
+                        for e in ch.logprobs]}
 
 
 def _pipeline(request: Request):
@@ -142,7 +171,8 @@ async def create_completion(req: CompletionRequest, request: Request):
             text = ch.text
             if req.echo and isinstance(p, str):
                 text = p + text
-            choices.append(CompletionChoice(index=i, text=text, finish_reason=ch.finish_reason))
+            choices.append(CompletionChoice(index=i, text=text, finish_reason=ch.finish_reason,
+                                            logprobs=_completion_logprobs(pipeline, ch)))
             usage.prompt_tokens += ch.prompt_tokens
             usage.completion_tokens += ch.completion_tokens
         usage.total_tokens = usage.prompt_tokens + usage.completion_tokens
@@ -199,7 +229,8 @@ async def create_chat_completion(req: ChatCompletionRequest, request: Request):
         usage = Usage(prompt_tokens=ch.prompt_tokens, completion_tokens=ch.completion_tokens,
                       total_tokens=ch.prompt_tokens + ch.completion_tokens)
         return ChatCompletionResponse(id=cid, model=req.model, usage=usage, choices=[
-            ChatChoice(message=ChatChoiceMessage(content=ch.text), finish_reason=ch.finish_reason)])
+            ChatChoice(message=ChatChoiceMessage(content=ch.text), finish_reason=ch.finish_reason,
+                       logprobs=_chat_logprobs(pipeline, ch))])
     except RequestQueueFull as e:
         return error_response(429, str(e), "rate_limit_error")
     except ValueError as e:

@@ -44,6 +44,7 @@ class _SamplingMixin(_Req):
     stream: bool = False
     stream_options: Optional[StreamOptions] = None
     logprobs: Optional[Union[bool, int]] = None
+    top_logprobs: Optional[int] = None
     user: Optional[str] = None
 
 

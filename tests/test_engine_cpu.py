@@ -142,3 +142,27 @@ def test_eos_and_sampling(tiny):
     r = llm.generate([prompt], SamplingParams(temperature=0.9, top_k=50, top_p=0.9, max_new_tokens=5,
                                               ignore_eos=True))[0]
     assert len(r.tokens) == 5 and all(0 <= t < cfg.vocab_size for t in r.tokens)
+
+
+def test_logprobs_follow_the_sampled_tokens():
+    import math
+
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.models.llama3 import Llama3Config
+    from modular_b200.pipelines.context import SamplingParams, TextContext
+
+    cfg = Llama3Config.tiny()
+    llm = LLM(cfg, device="cpu", dtype=torch.float32, max_length=128, max_batch_size=4, max_batch_input_tokens=64,
+              page_size=16, num_kv_pages=32)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=5, ignore_eos=True, logprobs=4)
+    ctx = TextContext.from_prompt([5, 6, 7, 8, 9], 128, "lp", sp, ())
+    llm.scheduler.add_request(ctx)
+    plain = llm.add_request([5, 6, 7, 8, 9], SamplingParams(temperature=0.0, max_new_tokens=5, ignore_eos=True))
+    while llm.has_unfinished():
+        llm.step()
+    ents = ctx.logprob_entries
+    assert [e["token"] for e in ents] == [int(t) for t in ctx.tokens.generated]
+    for e in ents:      # greedy: the sampled token is the most likely one; the alternatives are sorted
+        assert e["top"][0][0] == e["token"] and abs(e["top"][0][1] - e["logprob"]) < 1e-6
+        assert len(e["top"]) == 4 and all(a[1] >= b[1] for a, b in zip(e["top"], e["top"][1:]))
+        assert e["logprob"] <= 0 and math.isfinite(e["logprob"])

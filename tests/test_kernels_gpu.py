@@ -149,12 +149,14 @@ def test_rope_kv_store(interleaved, hd):
     assert torch.equal(kv[:, :, 0], kv_ref[:, :, 0])
 
 
-@pytest.mark.parametrize("tma", [False, True])
+@pytest.mark.parametrize("tma", [False, True, "tc"])
 @pytest.mark.parametrize("n_q,n_kv,hd,ps", [(32, 8, 128, 128), (4, 2, 64, 16), (8, 8, 128, 64), (16, 1, 64, 32),
-                                            (16, 2, 64, 128), (8, 1, 128, 64)])
+                                            (16, 2, 64, 128), (8, 1, 128, 64), (16, 1, 128, 128), (4, 2, 128, 64)])
 def test_paged_attention_mixed_batch(n_q, n_kv, hd, ps, tma):
     if tma and ps % 64:
         pytest.skip("the TMA kernel needs pages that are multiples of 64 tokens")
+    if tma == "tc" and hd != 128:
+        pytest.skip("the tcgen05 prefill kernel is built for head_dim 128")
     torch.manual_seed(7)
     q_lens = [1, 70, 1, 200, 33, 1]
     kv_lens = [513, 70, 64, 456, 161, 1]
@@ -166,13 +168,23 @@ def test_paged_attention_mixed_batch(n_q, n_kv, hd, ps, tma):
     perm = torch.randperm(n_pages, device=DEV)[: B * max_pages].int().view(B, max_pages)
     T = sum(q_lens)
     ld = (n_q + 2 * n_kv) * hd
-    q = torch.randn(T, ld, device=DEV, dtype=torch.bfloat16)
+    # large queries for the tcgen05 path: scores spread over many powers of two, which exercises the
+    # lazy rescaling of the accumulator
+    q = (torch.randn(T, ld, device=DEV) * (6.0 if tma == "tc" and n_kv == 8 else 1.0)).to(torch.bfloat16)
     qs = torch.tensor([sum(q_lens[:i]) for i in range(B)], device=DEV, dtype=torch.int32)
     ql = torch.tensor(q_lens, device=DEV, dtype=torch.int32)
     kl = torch.tensor(kv_lens, device=DEV, dtype=torch.int32)
     scale = 1.0 / math.sqrt(hd)
-    o = ops.paged_attention(q, kv[:, 0, layer], kv[:, 1, layer], perm, qs, ql, kl, n_q, n_kv, hd, scale,
-                            kv=kv if tma else None, layer=layer)
+    from modular_b200._native import lib
+    was = lib().get_attn_tc()
+    lib().set_attn_tc(tma == "tc")      # prefill tiles on the tcgen05 kernel, decode rows on the mma.sync kernel
+    try:
+        o = ops.paged_attention(q, kv[:, 0, layer], kv[:, 1, layer], perm, qs, ql, kl, n_q, n_kv, hd, scale,
+                                kv=kv if tma else None, layer=layer)
+        torch.cuda.synchronize()
+    finally:
+        lib().set_attn_tc(was)
+    ops.check_device_error()
     o_ref = ref.paged_attention(q, kv[:, 0, layer], kv[:, 1, layer], perm, qs, ql, kl, n_q, n_kv, hd, scale)
     assert torch.isfinite(o.float()).all()
     assert _rel_err(o, o_ref) < 1e-2

@@ -101,6 +101,16 @@ def test_tiny_llama_server():
         assert a["usage"]["completion_tokens"] == 6 and a["choices"][0]["finish_reason"] == "length"
         assert a["choices"][0]["text"] == b["choices"][0]["text"]
         assert c.post("/reset_prefix_cache").json() == {"success": True}
+        # log-probabilities: greedy token is the most likely alternative, values are valid log-probs
+        lp = c.post("/v1/completions", json={"model": "tiny", "prompt": [5, 6, 7, 8, 9], "max_tokens": 4,
+                                             "temperature": 0, "ignore_eos": True, "logprobs": 3}).json()
+        info = lp["choices"][0]["logprobs"]
+        assert len(info["token_logprobs"]) == 4 and all(v <= 0 for v in info["token_logprobs"])
+        assert all(1 <= len(t) <= 3 for t in info["top_logprobs"])      # byte tokenizer: ids above 255 share a text
+        assert lp["choices"][0]["text"] == a["choices"][0]["text"][: len(lp["choices"][0]["text"])]
+        ch = c.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "hi"}],
+                                                   "max_tokens": 3, "logprobs": True, "top_logprobs": 2}).json()
+        assert len(ch["choices"][0]["logprobs"]["content"]) == ch["usage"]["completion_tokens"]
         # embeddings from the same worker: unit vectors, deterministic, pooled per input
         e = c.post("/v1/embeddings", json={"model": "tiny", "input": [[5, 6, 7], [9, 9], [5, 6, 7]]}).json()
         v = [d["embedding"] for d in e["data"]]
