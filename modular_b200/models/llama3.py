@@ -150,15 +150,26 @@ class Llama3Weights:
         sd = adapt_hf_state_dict(sd)
         dev = torch.device(device)
 
+        def raw(name):
+            """Checkpoint tensor in floating point: fp8 tensors (block-scaled ``<name>_scale_inv`` [N/128, K/128],
+            or per-tensor ``weight_scale``) are expanded with their scales; the GEMMs then run in ``dtype``."""
+            w = sd[name]
+            if w.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+                if name + "_scale_inv" in sd:
+                    return ops.reference.dequant_fp8_weight_block128(w, sd[name + "_scale_inv"].float())
+                scale = sd.get(name.replace(".weight", ".weight_scale"))
+                return w.float() * (scale.float() if scale is not None else 1.0)
+            return w
+
         def get(name):
-            return sd[name].to(device=dev, dtype=dtype).contiguous()
+            return raw(name).to(device=dev, dtype=dtype).contiguous()
 
         layers = []
         for i in range(cfg.num_hidden_layers):
             p = f"layers.{i}."
-            wqkv = torch.cat([sd[p + "self_attn.q_proj.weight"], sd[p + "self_attn.k_proj.weight"],
-                              sd[p + "self_attn.v_proj.weight"]], dim=0)
-            wgu = torch.cat([sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]], dim=0)
+            wqkv = torch.cat([raw(p + "self_attn.q_proj.weight"), raw(p + "self_attn.k_proj.weight"),
+                              raw(p + "self_attn.v_proj.weight")], dim=0)
+            wgu = torch.cat([raw(p + "mlp.gate_proj.weight"), raw(p + "mlp.up_proj.weight")], dim=0)
             layers.append(LayerWeights(
                 attn_norm=get(p + "input_layernorm.weight"),
                 wqkv=wqkv.to(device=dev, dtype=dtype).contiguous(),
