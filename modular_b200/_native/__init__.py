@@ -39,9 +39,10 @@ def _load():
             # step kernels launch as programmatic dependents unless MB200_PDL=0 (see csrc/common/launch.h)
             if os.environ.get("MB200_PDL", "1") not in ("", "0") and hasattr(mod, "set_pdl"):
                 mod.set_pdl(True)
-            # MB200_ATTN_TC=1: prefill attention tiles on the tcgen05 kernel (head_dim 128)
-            if os.environ.get("MB200_ATTN_TC", "0") not in ("", "0") and hasattr(mod, "set_attn_tc"):
-                mod.set_attn_tc(True)
+            # prefill attention on the tcgen05 kernel (head_dim 128) for steps with at least MB200_ATTN_TC
+            # 64-row tiles (default 32; 0 turns it off, 1 always uses it)
+            if hasattr(mod, "set_attn_tc"):
+                mod.set_attn_tc(int(os.environ.get("MB200_ATTN_TC", "32") or 0))
             _MOD = mod
         except Exception as e:  # noqa: BLE001
             _ERR = e

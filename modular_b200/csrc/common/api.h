@@ -98,8 +98,9 @@ int mb_paged_attention_prefill_tc(const void* q, int ldq, void* out, int ldo, co
                                   const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, int n_q,
                                   int n_kv, int head_dim, int page_size, float scale, int* err,
                                   cudaStream_t stream);
-// Route the prefill tiles of mb_paged_attention_tma through the tcgen05 kernel (process-wide switch).
-void mb_set_attn_tc(int on);
+// Route the prefill tiles of mb_paged_attention_tma through the tcgen05 kernel when a step has at least
+// `min_tiles` 64-row tiles (process-wide; 0 = never).
+void mb_set_attn_tc(int min_tiles);
 int mb_get_attn_tc(void);
 
 // ---- multi-head latent attention over a paged latent cache (mla.cu) ------------------------

@@ -5,12 +5,15 @@
 // sequence's KV pages 64 tokens at a time:
 //
 //   warp 0      TMA producer: K tile and V tile of 64 tokens (two 64-column boxes each, 128B swizzle)
-//               into a 2-stage ring
+//               into a 4-stage ring
 //   warp 1      MMA issuer:   S = Q . K^T   (M=128, N=64, K=128; fp32 in TMEM, two S buffers so the
 //               next tile's scores are computed while the softmax warps work on this one)
 //                             O  += P . V   (M=128, N=128, K=64; V is read as an MN-major operand
 //               straight from the row-major KV page, no transpose pass)
-//   warps 2-5   one query row per thread (TMEM lane = row): read S, mask, running max / sum, write
+//   warps 2-9   two softmax groups of four warps; group g owns the KV tiles g, g+2, ... with its own
+//               accumulator and P buffer, so two score -> probability -> P.V chains are in flight; the
+//               partial results are merged at the end. Inside a group:
+//               one query row per thread (TMEM lane = row): read S, mask, running max / sum, write
 //               P (bf16) into shared memory in the swizzled K-major layout the MMA reads. The output
 //               accumulates in TMEM across tiles; it is rescaled only when a row's maximum has grown by
 //               more than 2^8 since the reference maximum was taken (exact after the final 1/l
@@ -37,13 +40,13 @@ namespace atc {
 
 typedef __nv_bfloat16 bf16;
 constexpr int HD = 128;
-constexpr int kStages = 2;
-constexpr int kThreads = 192;
+constexpr int kStages = 4;     // K/V tiles are prefetched three ahead
+constexpr int kThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2-5 softmax group 0, warps 6-9 softmax group 1
 constexpr int kQBytes = 2 * 128 * 128;        // two 64-column chunks of 128 rows x 128 B
 constexpr int kTileBytes = 2 * 64 * 128;      // K (or V) tile: two chunks of 64 rows x 128 B
 constexpr int kStageBytes = 2 * kTileBytes;   // K + V
-constexpr int kPBytes = 128 * 128;            // P: 128 rows x 64 bf16
-constexpr uint32_t kTmemCols = 256;           // S0 | S1 (64 each) | O tile (128)
+constexpr int kPBytes = 128 * 128;            // P of one group: 128 rows x 64 bf16
+constexpr uint32_t kTmemCols = 512;           // S0 | S1 (64 each) | O group 0 (128) | O group 1 (128)
 
 struct Params {
   const bf16* q;
@@ -65,10 +68,12 @@ struct Bars {
   uint64_t kv_empty[kStages];
   uint64_t s_full[2];
   uint64_t s_free[2];
-  uint64_t p_full;
-  uint64_t pv_full;
+  uint64_t p_full[2];
+  uint64_t pv_full[2];
   uint32_t tmem_base;
   int abort_word;
+  float merge_m[128];   // group 1's reference maximum and sum per row, for the final merge
+  float merge_l[128];
 };
 
 // MN-major operand with 128B swizzle: rows of 64 contiguous MN elements (128 B), 8 consecutive K rows
@@ -85,11 +90,11 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(const void* smem_tile, ui
   return d;
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
-  // No alignment slack: 2 x (112 KiB + barriers) is what lets two CTAs share an SM. The dynamic shared
-  // memory window starts 1024-byte aligned (there is no static shared memory in this kernel); should a
-  // future toolchain place it elsewhere the kernel reports it instead of computing garbage.
+  // No alignment slack (208 KiB of tiles + barriers per CTA). The dynamic shared memory window starts
+  // 1024-byte aligned (there is no static shared memory in this kernel); should a future toolchain place
+  // it elsewhere the kernel reports it instead of computing garbage.
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem_raw) & 1023u) {
@@ -98,8 +103,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
   }
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + kQBytes;                     // [stage][K chunk0 | K chunk1 | V chunk0 | V chunk1]
-  uint8_t* sP = sKV + kStages * kStageBytes;
-  Bars* bars = reinterpret_cast<Bars*>(sP + kPBytes);
+  uint8_t* sP = sKV + kStages * kStageBytes;        // [group][128 rows x 128 B]
+  Bars* bars = reinterpret_cast<Bars*>(sP + 2 * kPBytes);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kvh = blockIdx.y;
   const int G = p.G;
@@ -125,9 +130,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->s_full[b], 1);
       mbar_init(&bars->s_free[b], 4);
+      mbar_init(&bars->p_full[b], 4);
+      mbar_init(&bars->pv_full[b], 1);
     }
-    mbar_init(&bars->p_full, 4);
-    mbar_init(&bars->pv_full, 1);
     bars->abort_word = 0;
     fence_mbar_init();
   }
@@ -136,16 +141,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
     tmem_relinquish();
   }
   if (warp >= 2) {
-    // Q rows of this CTA into shared memory, K-major with 128B swizzle (row r, 16 B piece c)
+    // Q rows of this CTA into shared memory, K-major with 128B swizzle (row r, 16 B piece c); each softmax
+    // group copies one of the two 64-column chunks
+    const int grp = (warp - 2) >> 2;
     const int r = (warp & 3) * 32 + lane;
     const int tq = tq0 + r / G, head = kvh * G + r % G;
     const bool valid = tq < ql;
-    const bf16* src = p.q + static_cast<int64_t>(qs + (valid ? tq : 0)) * p.ldq + head * HD;
+    const bf16* src = p.q + static_cast<int64_t>(qs + (valid ? tq : 0)) * p.ldq + head * HD + grp * 64;
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
+    for (int c = 0; c < 8; ++c) {
       uint4 v = make_uint4(0, 0, 0, 0);
       if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
-      *reinterpret_cast<uint4*>(sQ + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+      *reinterpret_cast<uint4*>(sQ + grp * 16384 + r * 128 + ((c ^ (r & 7)) << 4)) = v;
     }
     fence_proxy_async_smem();
   }
@@ -199,60 +206,74 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
       if (ntiles > 0) issue_s(0);
       for (int t = 0; t < ntiles && ok; ++t) {
         if (t + 1 < ntiles) issue_s(t + 1);
-        ok = ok && mbar_wait(&bars->p_full, t & 1, abort_word, p.err, 704);
+        const int g = t & 1, u = t >> 1;       // tile t belongs to softmax group g, its u-th tile
+        ok = ok && mbar_wait(&bars->p_full[g], u & 1, abort_word, p.err, 704);
         if (!ok) break;
         tc_fence_after();
         const int s = t % kStages;
         const uint8_t* sV = sKV + s * kStageBytes + kTileBytes;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint64_t da = umma_desc_sw128(sP) + static_cast<uint64_t>(k * 2);
+          const uint64_t da = umma_desc_sw128(sP + g * kPBytes) + static_cast<uint64_t>(k * 2);
           const uint64_t db = umma_desc_mn_sw128(sV + k * 2048, 8192, 1024);
-          umma_bf16(tmem_base + 128, da, db, idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
+          umma_bf16(tmem_base + 128 + g * 128, da, db, idesc_pv, (u > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(&bars->pv_full);
+        tc_commit(&bars->pv_full[g]);
         tc_commit(&bars->kv_empty[s]);
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax + accumulation
+    // ---------------------------------------------------------------- softmax groups
+    // Group g takes the KV tiles t = g, g+2, ... of the same 128 query rows, with its own reference
+    // maximum, sum and TMEM accumulator; the two partial results are merged at the end. Two groups keep
+    // two dependent chains (scores -> probabilities -> P.V) in flight per CTA.
+    const int grp = (warp - 2) >> 2;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const int tq = tq0 + r / G, head = kvh * G + r % G;
     const int limit = tq < ql ? kl - ql + tq : -1;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const uint32_t o_addr = lane_addr + 128 + grp * 128;
+    uint8_t* myP = sP + grp * kPBytes;
     float m_ref = 0.f, l = 0.f;       // P and l are relative to m_ref (a lagging running maximum)
     bool ok = true;
-    for (int t = 0; t < ntiles && ok; ++t) {
-      const int b = t & 1;
-      ok = mbar_wait(&bars->s_full[b], (t >> 1) & 1, abort_word, p.err, 706);
+    const int n_mine = (ntiles - grp + 1) / 2;
+    for (int u = 0; u < n_mine && ok; ++u) {
+      const int t = 2 * u + grp;
+      ok = mbar_wait(&bars->s_full[grp], u & 1, abort_word, p.err, 706);
       if (!ok) break;
       tc_fence_after();
       uint32_t sr[2][32];
-      tmem_ld_32x32(lane_addr + b * 64, sr[0]);
-      tmem_ld_32x32(lane_addr + b * 64 + 32, sr[1]);
+      tmem_ld_32x32(lane_addr + grp * 64, sr[0]);
+      tmem_ld_32x32(lane_addr + grp * 64 + 32, sr[1]);
       tc_wait_ld();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_free[b]);
+      if (lane == 0) mbar_arrive(&bars->s_free[grp]);
       const int kv0 = t * 64;
-      float mx = -INFINITY;
+      // row maximum of the raw scores (four independent chains); only tiles that touch the causal
+      // diagonal or the end of the sequence need the mask
+      float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (kv0 + 63 <= limit) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
+        for (int c = 0; c < 64; ++c) mxa[c & 3] = fmaxf(mxa[c & 3], __uint_as_float(sr[c >> 5][c & 31]));
+      } else {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float v = (kv0 + h * 32 + c) <= limit ? __uint_as_float(sr[h][c]) * p.scale_log2 : -INFINITY;
-          sr[h][c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+        for (int c = 0; c < 64; ++c) {
+          const float v = (kv0 + c) <= limit ? __uint_as_float(sr[c >> 5][c & 31]) : -INFINITY;
+          sr[c >> 5][c & 31] = __float_as_uint(v);
+          mxa[c & 3] = fmaxf(mxa[c & 3], v);
         }
-      // the previous tile's P . V has retired: P's buffer is free and the accumulator is quiescent
-      if (t > 0) {
-        ok = mbar_wait(&bars->pv_full, (t - 1) & 1, abort_word, p.err, 707);
+      }
+      const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])) * p.scale_log2;   // scale > 0
+      // this group's previous P . V has retired: its P buffer is free and its accumulator is quiescent
+      if (u > 0) {
+        ok = mbar_wait(&bars->pv_full[grp], (u - 1) & 1, abort_word, p.err, 707);
         if (!ok) break;
         tc_fence_after();
       }
       bool grow = false;
-      if (t == 0) {
+      if (u == 0) {
         m_ref = mx == -INFINITY ? 0.f : mx;
       } else {
         grow = mx - m_ref > 8.0f;      // probabilities would exceed 2^8: move the reference
@@ -264,42 +285,63 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           uint32_t tr[32];
-          tmem_ld_32x32(lane_addr + 128 + q4 * 32, tr);
+          tmem_ld_32x32(o_addr + q4 * 32, tr);
           tc_wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; ++c) tr[c] = __float_as_uint(__uint_as_float(tr[c]) * factor);
-          tmem_st_32x32(lane_addr + 128 + q4 * 32, tr);
+          tmem_st_32x32(o_addr + q4 * 32, tr);
         }
         tc_wait_st();
       }
+      float la[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c8 = 0; c8 < 8; ++c8) {
         uint32_t pk[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int c = c8 * 8 + 2 * j;
-          const float p0 = exp2f(__uint_as_float(sr[c >> 5][c & 31]) - m_ref);
-          const float p1 = exp2f(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]) - m_ref);
-          l += p0 + p1;
+          const float p0 = exp2f(fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale_log2, -m_ref));
+          const float p1 = exp2f(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), p.scale_log2, -m_ref));
+          la[j] += p0 + p1;
           __nv_bfloat162 v2 = __floats2bfloat162_rn(p0, p1);
           pk[j] = *reinterpret_cast<uint32_t*>(&v2);
         }
-        *reinterpret_cast<uint4*>(sP + r * 128 + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(myP + r * 128 + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
+      l += (la[0] + la[1]) + (la[2] + la[3]);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full);
+      if (lane == 0) mbar_arrive(&bars->p_full[grp]);
     }
-    if (ok && ntiles > 0) ok = mbar_wait(&bars->pv_full, (ntiles - 1) & 1, abort_word, p.err, 708);
-    if (ok && ntiles > 0) {
-      tc_fence_after();
+    if (ok && n_mine > 0) ok = mbar_wait(&bars->pv_full[grp], (n_mine - 1) & 1, abort_word, p.err, 708);
+    // ---- merge the two groups' partial results (group 1 publishes, group 0 combines and stores)
+    const bool has_b = ntiles >= 2;      // CTA-uniform: group 1 worked on at least one tile
+    if (grp == 1) {
+      bars->merge_m[r] = m_ref;
+      bars->merge_l[r] = n_mine > 0 ? l : 0.f;
+    }
+    tc_fence_before();
+    asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight softmax warps
+    tc_fence_after();
+    if (grp == 0 && ok && n_mine > 0 && *abort_word == 0) {
+      float wa = 1.f, wb = 0.f;
+      if (has_b) {
+        const float mb_ = bars->merge_m[r], lb = bars->merge_l[r];
+        const float mm = fmaxf(m_ref, mb_);
+        wa = exp2f(m_ref - mm);
+        wb = lb > 0.f ? exp2f(mb_ - mm) : 0.f;
+        l = l * wa + lb * wb;
+      }
       const float inv = l > 0.f ? 1.f / l : 0.f;
+      wa *= inv;
+      wb *= inv;
       bf16* orow = p.out + static_cast<int64_t>(qs + (tq < ql ? tq : 0)) * p.ldo + head * HD;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
-        uint32_t tr[32];
-        tmem_ld_32x32(lane_addr + 128 + q4 * 32, tr);   // warp-collective: every lane takes part
+        uint32_t ta[32], tb[32];
+        tmem_ld_32x32(lane_addr + 128 + q4 * 32, ta);          // warp-collective: every lane takes part
+        if (has_b) tmem_ld_32x32(lane_addr + 256 + q4 * 32, tb);
         tc_wait_ld();
         if (tq < ql) {
 #pragma unroll
@@ -307,8 +349,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
             uint32_t pk[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(tr[c * 8 + 2 * j]) * inv,
-                                                        __uint_as_float(tr[c * 8 + 2 * j + 1]) * inv);
+              float x0 = __uint_as_float(ta[c * 8 + 2 * j]) * wa, x1 = __uint_as_float(ta[c * 8 + 2 * j + 1]) * wa;
+              if (has_b) {
+                x0 = fmaf(__uint_as_float(tb[c * 8 + 2 * j]), wb, x0);
+                x1 = fmaf(__uint_as_float(tb[c * 8 + 2 * j + 1]), wb, x1);
+              }
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(x0, x1);
               pk[j] = *reinterpret_cast<uint32_t*>(&v2);
             }
             *reinterpret_cast<uint4*>(orow + q4 * 32 + c * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -360,7 +406,7 @@ extern "C" int mb_paged_attention_prefill_tc(const void* q, int ldq, void* out, 
   CUtensorMap tm;
   const int rc = cached_tmap(&tm, kv_base, static_cast<uint64_t>(total_rows), head_dim, head_dim, 64, 2);
   if (rc != MB_OK) return rc;
-  const size_t smem = kQBytes + kStages * kStageBytes + kPBytes + sizeof(Bars);
+  const size_t smem = kQBytes + kStages * kStageBytes + 2 * kPBytes + sizeof(Bars);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=

@@ -381,9 +381,12 @@ static int launch(const CUtensorMap& tm, const Params& p, int n_decode, int n_kv
 
 using namespace mb;
 
-static bool g_attn_tc = false;
-extern "C" void mb_set_attn_tc(int on) { g_attn_tc = on != 0; }
-extern "C" int mb_get_attn_tc(void) { return g_attn_tc ? 1 : 0; }
+// Prefill tiles go to the tcgen05 kernel (attention_tc.cu) when a step has at least this many 64-row
+// tiles (0 = never). Small prefill chunks next to many decode rows are cheaper in this file's single
+// combined launch; measured crossover on B200: about 32 tiles (512 tokens at 4 query heads per KV head).
+static int g_attn_tc_min_tiles = 0;
+extern "C" void mb_set_attn_tc(int min_tiles) { g_attn_tc_min_tiles = min_tiles < 0 ? 0 : min_tiles; }
+extern "C" int mb_get_attn_tc(void) { return g_attn_tc_min_tiles; }
 
 // kv_base: start of the KV allocation, viewed as [total_rows, head_dim] bf16. A token of page
 // `pg`, KV head `h`, offset `o` lives at row  k_off_rows (or v_off_rows) + pg*page_rows +
@@ -415,7 +418,8 @@ extern "C" int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo
   const int rc = cached_tmap(&tm, kv_base, static_cast<uint64_t>(total_rows), head_dim, head_dim, 64, 2);
   if (rc != MB_OK) return rc;
   const int G = n_q / n_kv;
-  if (g_attn_tc && head_dim == 128 && p.n_tiles > 0 && G <= 16 && (G & (G - 1)) == 0) {
+  if (g_attn_tc_min_tiles > 0 && p.n_tiles >= g_attn_tc_min_tiles && head_dim == 128 && G <= 16 &&
+      (G & (G - 1)) == 0) {
     // prefill tiles on the tcgen05 kernel, decode sequences (if any) on this file's kernel
     const int rc2 = mb_paged_attention_prefill_tc(q, ldq, out, ldo, kv_base, total_rows, k_off_rows, v_off_rows,
                                                   page_rows, block_table, bt_stride, q_start, q_len, kv_len, tile_seq,

@@ -177,7 +177,7 @@ def test_paged_attention_mixed_batch(n_q, n_kv, hd, ps, tma):
     scale = 1.0 / math.sqrt(hd)
     from modular_b200._native import lib
     was = lib().get_attn_tc()
-    lib().set_attn_tc(tma == "tc")      # prefill tiles on the tcgen05 kernel, decode rows on the mma.sync kernel
+    lib().set_attn_tc(1 if tma == "tc" else 0)   # prefill tiles on the tcgen05 kernel, decode rows on the mma.sync kernel
     try:
         o = ops.paged_attention(q, kv[:, 0, layer], kv[:, 1, layer], perm, qs, ql, kl, n_q, n_kv, hd, scale,
                                 kv=kv if tma else None, layer=layer)
