@@ -130,6 +130,100 @@ def bench_attention(results):
         print(json.dumps(rec), flush=True)
 
 
+def bench_misc(results):
+    """The remaining hot kernels on DeepSeek-V3 / Llama shapes: block-scaled fp8 GEMM, grouped (MoE) GEMM,
+    MLA decode attention, router, RMSNorm, RoPE + KV store, SwiGLU, sampling. Roofline = bytes (or FLOPs)
+    over the measured peaks."""
+    from ..nn.moe import MoEConfig, route
+    peaks = measured_peaks()
+    dev = "cuda"
+    bw, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+
+    def rec(name, t, nbytes, flops=0.0, **kw):
+        roof = max(nbytes / bw, flops / tf)
+        r = dict(kernel=name, us=t * 1e6, gbs=nbytes / t / 1e9, tflops=flops / t / 1e12,
+                 frac_of_measured_roofline=roof / t, **kw)
+        results.append(r)
+        print(json.dumps(r), flush=True)
+
+    # block-scaled fp8 GEMM (DeepSeek-V3 o_proj-like: K = 7168, N = 7168)
+    for M in (64, 512):
+        N, K = 7168, 7168
+        w = torch.randn(N, K, device=dev) * 0.02
+        wq, ws = ops.reference.quant_fp8_weight_block128(w)
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        xq, xs = ops.quant_fp8_group128(x)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        t = time_fn(lambda: ops.linear_fp8_blockscaled(xq, xs, wq, ws, out=out))
+        # compute roofline uses the bf16 peak measured here (fp8 peak is not in the measured file)
+        rec("gemm_fp8_blockscaled", t, N * K + M * K + 2 * M * N, 2.0 * M * N * K, M=M, N=N, K=K)
+        tq = time_fn(lambda: ops.quant_fp8_group128(x))
+        rec("quant_fp8_group128", tq, M * K * 3, M=M, K=K)
+    # grouped GEMM: 32 local experts (EP8 of 256), moe_inter 2048, hidden 7168, 512 tokens x top-8 / 8 ranks
+    E, H, I, rows = 32, 7168, 2048, 512
+    offs = (torch.arange(E + 1, dtype=torch.int32) * (rows // E)).to(dev)
+    xg = torch.randn(rows, H, device=dev, dtype=torch.bfloat16)
+    wgu = (torch.randn(E, 2 * I, H, device=dev) * 0.02).to(torch.bfloat16)
+    wd = (torch.randn(E, H, I, device=dev) * 0.02).to(torch.bfloat16)
+    act = torch.empty(rows, I, device=dev, dtype=torch.bfloat16)
+    yo = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)
+    L = ops._lib()
+    t = time_fn(lambda: L.grouped_gemm_bf16(xg, wgu, act, offs, rows // E, True, 0))
+    rec("grouped_gemm_gate_up_swiglu", t, wgu.numel() * 2 + xg.numel() * 2, 2.0 * rows * 2 * I * H, experts=E, rows=rows)
+    t = time_fn(lambda: L.grouped_gemm_bf16(act, wd, yo, offs, rows // E, False, 0))
+    rec("grouped_gemm_down", t, wd.numel() * 2 + act.numel() * 2, 2.0 * rows * I * H, experts=E, rows=rows)
+    del wgu, wd
+    # MLA decode attention: 64 sequences x 1152 tokens of latent cache, 128 heads, kv_lora 512 + rope 64
+    B, ctx, h, R, page = 64, 1152, 128, 512, 128
+    ppseq = ctx // page
+    cache = (torch.randn(B * ppseq + 1, page, R + 64, device=dev) * 0.3).to(torch.bfloat16)
+    bt = (torch.randperm(B * ppseq, device=dev) + 1).int().view(B, ppseq)
+    q_lat = (torch.randn(B, h, R, device=dev) * 0.2).to(torch.bfloat16)
+    q_rope = (torch.randn(B, h, 64, device=dev) * 0.2).to(torch.bfloat16)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    qs, ql, kl = i32(list(range(B))), i32([1] * B), i32([ctx] * B)
+    t = time_fn(lambda: ops.mla_paged_attention(q_lat, q_rope, cache, bt, qs, ql, kl, 0.1))
+    rec("mla_decode", t, B * ctx * (R + 64) * 2, 2.0 * B * h * ctx * (2 * R + 64), batch=B, ctx=ctx, heads=h)
+    # router (DeepSeek-V3: 256 experts, 8 groups, top-4 groups, top-8 experts)
+    cfg = MoEConfig(7168, 2048, 256, 8, 1, 8, 4, True, 2.5, "sigmoid")
+    logits = torch.randn(512, 256, device=dev)
+    bias = torch.randn(256, device=dev) * 0.1
+    t = time_fn(lambda: route(logits, bias, cfg))
+    rec("moe_router_group_limited", t, logits.numel() * 4, tokens=512)
+    # elementwise kernels at a mixed-step size (320 tokens of Llama-3.1-8B)
+    T, Hd = 320, 4096
+    xe = torch.randn(T, Hd, device=dev, dtype=torch.bfloat16)
+    g = torch.ones(Hd, device=dev, dtype=torch.bfloat16)
+    oe = torch.empty_like(xe)
+    t = time_fn(lambda: ops.rms_norm(xe, g, 1e-5, out=oe))
+    rec("rmsnorm", t, 2 * xe.numel() * 2, rows=T, cols=Hd)
+    gu = torch.randn(T, 2 * 14336, device=dev, dtype=torch.bfloat16)
+    t = time_fn(lambda: ops.silu_mul(gu))
+    rec("silu_mul", t, gu.numel() * 2 * 1.5, rows=T)
+    n_q, n_kv, hd, ps = 32, 8, 128, 128
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, device=dev, dtype=torch.bfloat16)
+    kvc = torch.zeros(8, 2, 1, n_kv, ps, hd, device=dev, dtype=torch.bfloat16)
+    pos = torch.arange(T, device=dev, dtype=torch.int32)
+    slots = torch.arange(T, device=dev, dtype=torch.long) + ps
+    inv = 1.0 / (500000.0 ** (torch.arange(0, hd, 2, device=dev).float() / hd))
+    ang = torch.arange(4096, device=dev).float()[:, None] * inv[None]
+    cs = torch.cat([ang.cos(), ang.sin()], dim=1).contiguous()
+    t = time_fn(lambda: ops.rope_kv_store(qkv, pos, slots, cs, kvc[:, 0, 0], kvc[:, 1, 0], n_q, n_kv, hd, False))
+    rec("rope_kv_store", t, qkv.numel() * 2 * 2, tokens=T)
+    lg = torch.randn(64, 128256, device=dev)
+    temp = torch.full((64,), 0.8, device=dev)
+    tk = torch.full((64,), 50, device=dev, dtype=torch.int32)
+    tp_ = torch.full((64,), 0.9, device=dev)
+    mp = torch.zeros(64, device=dev)
+    seeds = torch.arange(64, device=dev, dtype=torch.int64)
+    t = time_fn(lambda: ops.sample(lg, temp, tk, tp_, mp, seeds, 1))
+    rec("sample_topk_topp", t, lg.numel() * 4, rows=64, vocab=128256)
+    t = time_fn(lambda: ops.argmax(lg))
+    rec("argmax", t, lg.numel() * 4, rows=64, vocab=128256)
+    torch.cuda.synchronize()
+    ops.check_device_error()
+
+
 LLAMA8B_SHAPES = []
 for _m in (16, 64, 128, 320, 512, 1024, 4096):
     LLAMA8B_SHAPES += [
@@ -162,6 +256,8 @@ def main(argv=None):
         bench_gemm(shapes, results, cfgs)
     if "attn" in what:
         bench_attention(results)
+    if "misc" in what:
+        bench_misc(results)
     if args.out:
         with open(args.out, "w") as f:
             json.dump(results, f, indent=1)

@@ -65,7 +65,7 @@ int num_sms() {
 // y = x @ w.T with optional fusions; see mb_gemm_bf16.
 void gemm_bf16(const Tensor& x, const Tensor& w, Tensor& y, const c10::optional<Tensor>& residual,
                bool dual, const c10::optional<Tensor>& workspace, int bn, int splits, int stages,
-               bool packed) {
+               bool packed, bool pair) {
   need_cuda(x, "x"); need_cuda(w, "w"); need_cuda(y, "y");
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2, "gemm_bf16: 2-D tensors expected");
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "bf16 inputs");
@@ -80,12 +80,16 @@ void gemm_bf16(const Tensor& x, const Tensor& w, Tensor& y, const c10::optional<
   void* ws = nullptr;
   if (workspace.has_value() && workspace->defined()) {
     ws = workspace->data_ptr();
-    if (splits <= 0) {
+    if (pair) {
+      // the pair kernel picks its own split count (at most 8)
+      const size_t need = static_cast<size_t>(splits > 0 ? splits : 8) * M * N * 4;
+      if (need > static_cast<size_t>(workspace->nbytes())) { ws = nullptr; splits = 1; }
+    } else if (splits <= 0) {
       int pbn, psp, pst;
       mb_gemm_bf16_plan(M, N, K, dual, num_sms(), &pbn, &psp, &pst);
       splits = psp;
     }
-    if (static_cast<size_t>(splits) * M * N * 4 > static_cast<size_t>(workspace->nbytes())) splits = 1;
+    if (!pair && static_cast<size_t>(splits) * M * N * 4 > static_cast<size_t>(workspace->nbytes())) splits = 1;
   } else {
     splits = 1;
   }
@@ -93,6 +97,13 @@ void gemm_bf16(const Tensor& x, const Tensor& w, Tensor& y, const c10::optional<
   if (flags & 2) {
     TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->stride(1) == 1, "residual");
     ldr = residual->stride(0);
+  }
+  if (pair) {
+    check_rc(mb_gemm_bf16_pair(x.data_ptr(), w.data_ptr(), y.data_ptr(), optptr(residual), M, N, K,
+                               x.stride(0), w.stride(0), y.stride(0), ldr, flags, bn, splits, stages, ws,
+                               error_flag(), num_sms(), nullptr, 1, 0, cur_stream()),
+             "gemm_bf16_pair");
+    return;
   }
   check_rc(mb_gemm_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), optptr(residual), M, N, K,
                         x.stride(0), w.stride(0), y.stride(0), ldr, flags, bn, splits, stages, ws,
@@ -142,7 +153,8 @@ void quant_fp8_group128(const Tensor& x, Tensor& q, Tensor& scales, bool k_major
 }
 // y = (xq * xs) @ (wq * ws).T with 128x128 weight blocks and 1x128 activation groups.
 void gemm_fp8_blockscaled(const Tensor& xq, const Tensor& xs, const Tensor& wq, const Tensor& ws,
-                          Tensor& y, const c10::optional<Tensor>& residual, int bn, int stages) {
+                          Tensor& y, const c10::optional<Tensor>& residual, int bn, int stages, int splits,
+                          const c10::optional<Tensor>& workspace) {
   need_cuda(xq, "xq");
   TORCH_CHECK(xq.is_contiguous() && wq.is_contiguous() && y.is_contiguous() && xs.is_contiguous() &&
                   ws.is_contiguous() && xq.element_size() == 1 && wq.element_size() == 1 &&
@@ -155,8 +167,12 @@ void gemm_fp8_blockscaled(const Tensor& xq, const Tensor& xs, const Tensor& wq, 
               "gemm_fp8: scale shapes");
   const bool resid = residual.has_value() && residual->defined();
   if (resid) TORCH_CHECK(residual->is_contiguous() && residual->scalar_type() == at::kBFloat16, "residual");
+  const bool has_ws = workspace.has_value() && workspace->defined();
+  if (has_ws) TORCH_CHECK(workspace->is_cuda() && workspace->is_contiguous(), "gemm_fp8: workspace");
   check_rc(mb_gemm_fp8_blockscaled(xq.data_ptr(), xs.data_ptr<float>(), wq.data_ptr(), ws.data_ptr<float>(),
-                                   y.data_ptr(), optptr(residual), M, N, K, resid ? 2 : 0, bn, stages,
+                                   y.data_ptr(), optptr(residual), M, N, K, resid ? 2 : 0, bn, stages, splits,
+                                   has_ws ? workspace->data_ptr() : nullptr,
+                                   has_ws ? static_cast<size_t>(workspace->nbytes()) : 0, num_sms(),
                                    error_flag(), cur_stream()),
            "gemm_fp8_blockscaled");
 }
@@ -511,7 +527,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16", &gemm_bf16, py::arg("x"), py::arg("w"), py::arg("y"),
         py::arg("residual") = py::none(), py::arg("dual") = false,
         py::arg("workspace") = py::none(), py::arg("bn") = 0, py::arg("splits") = 0,
-        py::arg("stages") = 0, py::arg("packed") = false);
+        py::arg("stages") = 0, py::arg("packed") = false, py::arg("pair") = false);
   m.def("gemm_plan", &gemm_plan);
   m.def("moe_router_group_limited", &moe_router_group_limited);
   m.def("moe_router_softmax_topk", &moe_router_softmax_topk);
@@ -522,7 +538,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("quant_fp8_group128", &quant_fp8_group128);
   m.def("gemm_fp8_blockscaled", &gemm_fp8_blockscaled, py::arg("xq"), py::arg("xs"), py::arg("wq"),
         py::arg("ws"), py::arg("y"), py::arg("residual") = py::none(), py::arg("bn") = 0,
-        py::arg("stages") = 0);
+        py::arg("stages") = 0, py::arg("splits") = 0, py::arg("workspace") = py::none());
   m.def("gemm_bf16_persistent", &gemm_bf16_persistent, py::arg("x"), py::arg("w"), py::arg("y"),
         py::arg("residual") = py::none(), py::arg("dual") = false, py::arg("ws"), py::arg("counters"),
         py::arg("bn") = 0, py::arg("stages") = 0, py::arg("mode") = -1, py::arg("pdl") = false,

@@ -35,6 +35,11 @@ int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const void* R, int
                        int ldx, int ldw, int ldy, int ldr, int flags, int bn, int splits, int stages,
                        void* workspace, int* err, int num_sms, const int* gate_flags, int gate_rpr,
                        int gate_world, cudaStream_t stream);
+// CTA-pair (cta_group::2, cluster of two) variant of the tiled GEMM; same contract as mb_gemm_bf16_gated.
+int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const void* R, int M, int N, int K, int ldx,
+                      int ldw, int ldy, int ldr, int flags, int bn, int splits, int stages, void* workspace,
+                      int* err, int num_sms, const int* gate_flags, int gate_rpr, int gate_world,
+                      cudaStream_t stream);
 int mb_gemm_bf16_persistent_gated(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,
                                   int ldx, int ldw, int ldy, int ldr, int flags, int bn, int stages,
                                   int force_mode, void* ws, int* counters, int* err, int num_sms,
@@ -50,9 +55,10 @@ int mb_gemm_bf16_persistent(const void* X, const void* W, void* Y, const void* R
 // ---- block-scaled fp8 (gemm_fp8_blockscaled.cu, quant_fp8.cu) ----------------------------
 int mb_quant_fp8_group128(const void* x_bf16, void* q_fp8, float* scales, int M, int K, int ldx,
                           int scale_ld, int scales_k_major, cudaStream_t stream);
-int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const void* Wq, const float* Ws,
-                            void* Y, const void* R, int M, int N, int K, int flags, int bn,
-                            int stages, int* err, cudaStream_t stream);
+int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const void* Wq, const float* Ws, void* Y,
+                            const void* R, int M, int N, int K, int flags, int bn, int stages, int splits,
+                            void* workspace, size_t workspace_bytes, int num_sms, int* err,
+                            cudaStream_t stream);
 
 // ---- elementwise / normalisation / rope (elementwise.cu) ---------------------------------
 int mb_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, int ldx, int ldo,

@@ -7,10 +7,13 @@
 //                                                          (stored K-group-major so that a tile's
 //                                                          tokens are contiguous)
 //
-// tcgen05.mma kind::f8f6f4 accumulates 128 K (four K=32 instructions) into one of two TMEM
+// tcgen05.mma kind::f8f6f4 accumulates 128 K (four K=32 instructions) into one of four TMEM
 // buffers; two epilogue warpgroups then "promote" that partial: read it back with tcgen05.ld,
 // multiply by sw * sx and add it into fp32 register accumulators while the tensor core already
-// works on the next K group in the other buffer. For decode-sized token counts the promotion
+// works on the next K groups in the other buffers. The combined scales of a K group are fetched
+// one group ahead and staged per warp in shared memory, so no global load sits between the
+// accumulator barrier and the promotion. Token counts that give fewer CTAs than SMs split K
+// over grid.z: every split writes fp32 partials that a small kernel sums (and adds the residual). For decode-sized token counts the promotion
 // hides completely under the weight stream; for large token counts it bounds the kernel at
 // roughly the bf16 rate, which is the price of arbitrary (non power-of-two) fp32 scales.
 //
@@ -47,15 +50,20 @@ struct Params {
   const float* sx;
   int* err;
   int M, N, K, ldy, ldr, sw_ld, BN, stages;
+  int splits, kb_per_split;
+  float* partial;   // [splits, M, N] fp32 when splits > 1
 };
+
+constexpr int kAccBufs = 4;
 
 struct Tail {
   uint64_t full[8];
   uint64_t empty[8];
-  uint64_t acc_full[2];
-  uint64_t acc_empty[2];
+  uint64_t acc_full[kAccBufs];
+  uint64_t acc_empty[kAccBufs];
   uint32_t tmem_base;
   int abort_word;
+  alignas(16) float scales[8][2][64];   // per promotion warp, double-buffered: sw * sx of its token columns
 };
 
 template <bool RESID>
@@ -70,15 +78,19 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   Tail* tail = reinterpret_cast<Tail*>(stg_base + 8 * kStgWarp);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.y * kBM, t0 = blockIdx.x * p.BN;
-  const int kb_total = (p.K + 127) / 128;
-  const uint32_t tmem_cols = p.BN * 2 <= 32 ? 32 : (p.BN * 2 <= 64 ? 64 : (p.BN * 2 <= 128 ? 128 : 256));
+  const int kb_all = (p.K + 127) / 128;
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kb_end = kb_begin + p.kb_per_split < kb_all ? kb_begin + p.kb_per_split : kb_all;
+  const int kb_total = kb_end - kb_begin;          // K groups of this split
+  const uint32_t want_cols = p.BN * kAccBufs;
+  const uint32_t tmem_cols = want_cols <= 128 ? 128 : (want_cols <= 256 ? 256 : 512);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&tail->full[s], 1);
       mbar_init(&tail->empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kAccBufs; ++b) {
       mbar_init(&tail->acc_full[b], 1);
       mbar_init(&tail->acc_empty[b], 8);
     }
@@ -107,8 +119,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, p.err, 501)) break;
         uint8_t* sa = smem + s * stage_bytes;
         mbar_arrive_expect_tx(&tail->full[s], stage_bytes);
-        tma_load_2d(sa, &tmW, &tail->full[s], kb * 128, n0);
-        tma_load_2d(sa + kATile, &tmX, &tail->full[s], kb * 128, t0);
+        tma_load_2d(sa, &tmW, &tail->full[s], (kb_begin + kb) * 128, n0);
+        tma_load_2d(sa + kATile, &tmX, &tail->full[s], (kb_begin + kb) * 128, t0);
       }
     }
   } else if (warp == 1) {
@@ -117,8 +129,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       for (int kb = 0; kb < kb_total; ++kb) {
         const int s = kb % p.stages;
         const uint32_t ph = (kb / p.stages) & 1;
-        const int buf = kb & 1;
-        const uint32_t bph = (kb >> 1) & 1;
+        const int buf = kb % kAccBufs;
+        const uint32_t bph = (kb / kAccBufs) & 1;
         if (!mbar_wait(&tail->acc_empty[buf], bph ^ 1, abort_word, p.err, 502)) break;
         if (!mbar_wait(&tail->full[s], ph, abort_word, p.err, 503)) break;
         tc_fence_after();
@@ -145,33 +157,71 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     float acc[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) acc[i] = 0.f;
-    const float* sw_row = p.sw + static_cast<size_t>(blockIdx.y) * p.sw_ld;
+    const float* sw_row = p.sw + static_cast<size_t>(blockIdx.y) * p.sw_ld + kb_begin;
+    const float* sx_base = p.sx + static_cast<size_t>(kb_begin) * p.M + t0 + c_base;
+    float* sc = &tail->scales[ew][0][0];
+    // lane l owns the scales of token columns l and l + 32 of this warpgroup's half
+    const bool in0 = lane < cols && t0 + c_base + lane < p.M;
+    const bool in1 = lane + 32 < cols && t0 + c_base + lane + 32 < p.M;
+    float s0 = 0.f, s1 = 0.f;
+    if (kb_total > 0) {
+      const float w = sw_row[0];
+      s0 = in0 ? sx_base[lane] * w : 0.f;
+      s1 = in1 ? sx_base[lane + 32] * w : 0.f;
+    }
+    sc[lane] = s0;
+    sc[lane + 32] = s1;
+    __syncwarp();
     bool ok = true;
     for (int kb = 0; kb < kb_total && ok; ++kb) {
-      const int buf = kb & 1;
-      const uint32_t bph = (kb >> 1) & 1;
+      const int buf = kb % kAccBufs;
+      const uint32_t bph = (kb / kAccBufs) & 1;
+      // next group's scales: in flight while this group's accumulator is awaited and promoted
+      if (kb + 1 < kb_total) {
+        const float w = sw_row[kb + 1];
+        const float* sx_row = sx_base + static_cast<size_t>(kb + 1) * p.M;
+        s0 = in0 ? sx_row[lane] * w : 0.f;
+        s1 = in1 ? sx_row[lane + 32] * w : 0.f;
+      }
       ok = mbar_wait(&tail->acc_full[buf], bph, abort_word, p.err, 504);
       if (!ok) break;
       tc_fence_after();
-      const float w_scale = sw_row[kb];
-      const float* sx_row = p.sx + static_cast<size_t>(kb) * p.M + t0 + c_base;
+      const float* scur = sc + (kb & 1) * 64;
 #pragma unroll
       for (int c = 0; c < 64; c += 16) {
         if (c < cols) {
           uint32_t v[16];
           tmem_ld_32x16(lane_addr + buf * p.BN + c_base + c, v);
+          float4 sv[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) sv[q] = *reinterpret_cast<const float4*>(scur + c + q * 4);
           tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c_base + c + j;
-            const float s = t < p.M ? sx_row[c + j] * w_scale : 0.f;
-            acc[c + j] = fmaf(__uint_as_float(v[j]), s, acc[c + j]);
+          for (int q = 0; q < 4; ++q) {
+            acc[c + q * 4 + 0] = fmaf(__uint_as_float(v[q * 4 + 0]), sv[q].x, acc[c + q * 4 + 0]);
+            acc[c + q * 4 + 1] = fmaf(__uint_as_float(v[q * 4 + 1]), sv[q].y, acc[c + q * 4 + 1]);
+            acc[c + q * 4 + 2] = fmaf(__uint_as_float(v[q * 4 + 2]), sv[q].z, acc[c + q * 4 + 2]);
+            acc[c + q * 4 + 3] = fmaf(__uint_as_float(v[q * 4 + 3]), sv[q].w, acc[c + q * 4 + 3]);
           }
         }
       }
       tc_fence_before();
+      float* snext = sc + ((kb + 1) & 1) * 64;
+      snext[lane] = s0;
+      snext[lane + 32] = s1;
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->acc_empty[buf]);
+    }
+    if (ok && p.splits > 1) {
+      // fp32 partials of this split: lane = weight row, so each token's 32 floats are contiguous
+      const int n = n0 + quad * 32 + lane;
+      float* dst = p.partial + static_cast<size_t>(blockIdx.z) * p.M * p.N;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const int t = t0 + c_base + c;
+        if (c < cols && t < p.M && n < p.N) dst[static_cast<size_t>(t) * p.N + n] = acc[c];
+      }
+      ok = false;   // nothing left for the bf16 epilogue
     }
     if (ok) {
       __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(stg_base + ew * kStgWarp);
@@ -216,6 +266,30 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
   }
+}
+
+// Sum of the split-K partials [splits, M, N] (+ residual) -> bf16 Y; N % 4 == 0.
+__global__ void fp8_splitk_reduce_kernel(const float* __restrict__ part, const __nv_bfloat16* __restrict__ R,
+                                         __nv_bfloat16* __restrict__ Y, int M, int N, int splits) {
+  const size_t idx = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  const size_t total = static_cast<size_t>(M) * N;
+  if (idx >= total) return;
+  float4 a = *reinterpret_cast<const float4*>(part + idx);
+  for (int s = 1; s < splits; ++s) {
+    const float4 b = *reinterpret_cast<const float4*>(part + s * total + idx);
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  }
+  if (R != nullptr) {
+    const uint2 rv = *reinterpret_cast<const uint2*>(R + idx);
+    const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rv);
+    const float2 r0 = __bfloat1622float2(rb[0]), r1 = __bfloat1622float2(rb[1]);
+    a.x += r0.x; a.y += r0.y; a.z += r1.x; a.w += r1.y;
+  }
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+  uint2 out;
+  out.x = *reinterpret_cast<const uint32_t*>(&lo);
+  out.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(Y + idx) = out;
 }
 
 // One warp per (token, 128-wide K group): amax -> scale = amax / 448, q = x / scale.
@@ -266,10 +340,27 @@ extern "C" int mb_quant_fp8_group128(const void* x_bf16, void* q_fp8, float* sca
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
+// Number of K splits for a grid of `ctas` output tiles: the split count (<= 8, at least four K groups
+// each) that fills whole waves of SMs best, with a small bias towards fewer splits.
+static int fp8_pick_splits(int ctas, int kb_total, int num_sms) {
+  if (ctas >= num_sms || num_sms <= 0) return 1;
+  int best = 1;
+  float best_score = -1.f;
+  for (int s = 1; s <= 8 && kb_total / s >= 4; ++s) {
+    const int total = ctas * s;
+    const int waves = (total + num_sms - 1) / num_sms;
+    const float score = static_cast<float>(total) / (waves * num_sms) - 0.02f * s;
+    if (score > best_score) { best_score = score; best = s; }
+  }
+  return best;
+}
+
 // flags: bit1 residual add. Xs is K-group-major [ceil(K/128), M]; Ws is [ceil(N/128), ceil(K/128)].
+// splits <= 0: chosen here (1 without a workspace of splits*M*N floats); num_sms is used for that choice.
 extern "C" int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const void* Wq, const float* Ws,
                                        void* Y, const void* R, int M, int N, int K, int flags, int bn,
-                                       int stages, int* err, cudaStream_t stream) {
+                                       int stages, int splits, void* workspace, size_t workspace_bytes,
+                                       int num_sms, int* err, cudaStream_t stream) {
   using namespace mb::f8;
   if (M <= 0 || N <= 0) return MB_OK;
   if (K % 16 || N % 8) return MB_ERR_SHAPE;
@@ -287,7 +378,7 @@ extern "C" int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const vo
   p.sw = Ws; p.sx = Xs; p.err = err;
   p.M = M; p.N = N; p.K = K; p.ldy = N; p.ldr = N; p.sw_ld = (K + 127) / 128; p.BN = bn;
   const int stage_bytes = kATile + bn * kBKBytes;
-  const int max_stages = (227 * 1024 - 1024 - 8 * kStgWarp - 512) / stage_bytes;
+  const int max_stages = (227 * 1024 - 1024 - 8 * kStgWarp - static_cast<int>(sizeof(Tail)) - 256) / stage_bytes;
   if (stages <= 0 || stages > max_stages) stages = max_stages;
   if (stages > 8) stages = 8;
   p.stages = stages;
@@ -297,8 +388,19 @@ extern "C" int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const vo
   rc = cached_tmap(&tx, Xq, M, K, K, bn, 1);
   if (rc != MB_OK) return rc;
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 8 * kStgWarp + sizeof(Tail) + 1024;
-  dim3 grid((M + bn - 1) / bn, (N + kBM - 1) / kBM);
-  const bool resid = flags & 2;
+  const int kb_all = (K + 127) / 128;
+  const int tiles = ((M + bn - 1) / bn) * ((N + kBM - 1) / kBM);
+  if (splits <= 0) splits = fp8_pick_splits(tiles, kb_all, num_sms);
+  if (splits > kb_all) splits = kb_all;
+  if (workspace == nullptr || N % 4 ||
+      static_cast<size_t>(splits) * M * N * sizeof(float) > workspace_bytes)
+    splits = 1;
+  p.kb_per_split = (kb_all + splits - 1) / splits;
+  splits = (kb_all + p.kb_per_split - 1) / p.kb_per_split;
+  p.splits = splits;
+  p.partial = static_cast<float*>(workspace);
+  dim3 grid((M + bn - 1) / bn, (N + kBM - 1) / kBM, splits);
+  const bool resid = (flags & 2) && splits == 1;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -309,5 +411,10 @@ extern "C" int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const vo
     gemm_fp8_kernel<true><<<grid, kThreads, smem, stream>>>(tw, tx, p);
   else
     gemm_fp8_kernel<false><<<grid, kThreads, smem, stream>>>(tw, tx, p);
+  if (splits > 1) {
+    const size_t total4 = static_cast<size_t>(M) * N / 4;
+    fp8_splitk_reduce_kernel<<<static_cast<unsigned>((total4 + 255) / 256), 256, 0, stream>>>(
+        p.partial, (flags & 2) ? p.R : nullptr, p.Y, M, N, splits);
+  }
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }

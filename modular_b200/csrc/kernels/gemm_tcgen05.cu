@@ -55,6 +55,76 @@ struct GemmSmemTail {
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
+// Epilogue of one accumulator tile by one warp: TMEM lanes [quad*32, +32) = weight rows
+// n0 + quad*32 + lane, columns [0, BN) = tokens t0.. (DUAL: gate at column 0, up at column BN).
+template <bool DUAL, int EPI>
+__device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, uint8_t* stage_buf, int quad, int lane,
+                                              void* __restrict__ Yv, const __nv_bfloat16* __restrict__ R,
+                                              int M, int N, int ldy, int ldr, int BN, int n0, int t0,
+                                              int Mlim, int split) {
+    __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(stage_buf + quad * kStageWarpBytes);
+    const int n_row = n0 + quad * 32 + lane;  // weight row (= output column) of this thread
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+      if (t0 + c0 >= Mlim) break;  // warp-uniform
+      uint32_t g[16];
+      tmem_ld_32x16(lane_addr + c0, g);
+      float v[16];
+      if (DUAL) {
+        uint32_t u[16];
+        tmem_ld_32x16(lane_addr + BN + c0, u);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+      } else {
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(g[j]);
+      }
+      if (EPI == EPI_F32) {
+        float* Y = reinterpret_cast<float*>(Yv) + static_cast<size_t>(split) * M * ldy;
+        if (n_row < N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c0 + j;
+            if (t < Mlim) Y[static_cast<size_t>(t) * ldy + n_row] = v[j];
+          }
+        }
+      } else {
+        __nv_bfloat16* Y = reinterpret_cast<__nv_bfloat16*>(Yv);
+        // transpose through this warp's private buffer: stg[token j][weight row lane]
+#pragma unroll
+        for (int j = 0; j < 16; ++j) stg[j * 32 + lane] = __float2bfloat16(v[j]);
+        __syncwarp();
+        // 16 tokens x 64 bytes: 4 lanes cover one token row, 8 tokens per pass
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+          const int j = pass * 8 + (lane >> 2);
+          const int seg = lane & 3;
+          const int t = t0 + c0 + j;
+          const int n = n0 + quad * 32 + seg * 8;
+          if (t < Mlim && n < N) {
+            uint4 val = *reinterpret_cast<const uint4*>(stg + j * 32 + seg * 8);
+            if (EPI == EPI_BF16_RESIDUAL) {
+              const uint4 rv =
+                  *reinterpret_cast<const uint4*>(R + static_cast<size_t>(t) * ldr + n);
+              __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&val);
+              const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float2 fa = __bfloat1622float2(a[q]);
+                const float2 fb = __bfloat1622float2(b[q]);
+                a[q] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+              }
+            }
+            *reinterpret_cast<uint4*>(Y + static_cast<size_t>(t) * ldy + n) = val;
+          }
+        }
+        __syncwarp();
+      }
+    }
+}
+
 template <bool DUAL, int EPI>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
@@ -195,69 +265,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     const bool ok = mbar_wait(&tail->tmem_full, 0, abort_word, err, 103);
     tc_fence_after();
-    if (ok && k_iters > 0) {
-      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(stage_buf + quad * kStageWarpBytes);
-      const int n_row = n0 + quad * 32 + lane;  // weight row (= output column) of this thread
-      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (t0 + c0 >= Mlim) break;  // warp-uniform
-        uint32_t g[16];
-        tmem_ld_32x16(lane_addr + c0, g);
-        float v[16];
-        if (DUAL) {
-          uint32_t u[16];
-          tmem_ld_32x16(lane_addr + BN + c0, u);
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
-        } else {
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(g[j]);
-        }
-        if (EPI == EPI_F32) {
-          float* Y = reinterpret_cast<float*>(Yv) + static_cast<size_t>(split) * M * ldy;
-          if (n_row < N) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int t = t0 + c0 + j;
-              if (t < Mlim) Y[static_cast<size_t>(t) * ldy + n_row] = v[j];
-            }
-          }
-        } else {
-          __nv_bfloat16* Y = reinterpret_cast<__nv_bfloat16*>(Yv);
-          // transpose through this warp's private buffer: stg[token j][weight row lane]
-#pragma unroll
-          for (int j = 0; j < 16; ++j) stg[j * 32 + lane] = __float2bfloat16(v[j]);
-          __syncwarp();
-          // 16 tokens x 64 bytes: 4 lanes cover one token row, 8 tokens per pass
-#pragma unroll
-          for (int pass = 0; pass < 2; ++pass) {
-            const int j = pass * 8 + (lane >> 2);
-            const int seg = lane & 3;
-            const int t = t0 + c0 + j;
-            const int n = n0 + quad * 32 + seg * 8;
-            if (t < Mlim && n < N) {
-              uint4 val = *reinterpret_cast<const uint4*>(stg + j * 32 + seg * 8);
-              if (EPI == EPI_BF16_RESIDUAL) {
-                const uint4 rv =
-                    *reinterpret_cast<const uint4*>(R + static_cast<size_t>(t) * ldr + n);
-                __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&val);
-                const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&rv);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const float2 fa = __bfloat1622float2(a[q]);
-                  const float2 fb = __bfloat1622float2(b[q]);
-                  a[q] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
-                }
-              }
-              *reinterpret_cast<uint4*>(Y + static_cast<size_t>(t) * ldy + n) = val;
-            }
-          }
-          __syncwarp();
-        }
-      }
-    }
+    if (ok && k_iters > 0)
+      epilogue_tile<DUAL, EPI>(tmem_base, stage_buf, quad, lane, Yv, R, M, N, ldy, ldr, BN, n0, t0, Mlim, split);
   }
 
   tc_fence_before();
@@ -265,6 +274,157 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// ------------------------------------------------------------------ CTA-pair variant
+// Same GEMM with cta_group::2 MMAs: a cluster of two CTAs owns 256 weight rows x BN tokens. Each CTA
+// loads its own 128 weight rows and HALF of the token tile; the leader (even) CTA issues
+// 256 x BN x 16 MMAs that read both halves, and each CTA's TMEM receives the accumulator of its own
+// weight rows. Per CTA and K step the shared-memory traffic is 128 + BN/2 rows instead of
+// 128 + BN, which is what lifts the tensor pipe past the one-CTA shared-memory bound.
+//   full[s]   lives in the leader: its producer posts the byte count of both CTAs' loads, and both
+//             CTAs' TMA loads complete on it.
+//   empty[s]  one per CTA, released by the leader's commits (one commit per CTA).
+//   tmem_full one per CTA, likewise.
+// grid = (2 * token tiles, weight-row pairs, K splits), cluster = (2, 1, 1).
+template <bool DUAL, int EPI>
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                 void* __restrict__ Yv, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
+                 int ldy, int ldr, int dual_rows, int k_per_split, int BN, int stages,
+                 uint32_t tmem_cols, int* err, const int* gate_flags, int gate_rpr, int gate_world,
+                 int packed_kb) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int half = BN >> 1;
+  const int a_bytes = kATileBytes * (DUAL ? 2 : 1);
+  const int b_bytes = half * kBK * 2;
+  const int stage_bytes = a_bytes + b_bytes;
+  uint8_t* stage_buf = smem + stages * stage_bytes;
+  GemmSmemTail* tail = reinterpret_cast<GemmSmemTail*>(stage_buf + 4 * kStageWarpBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  const int m_tile = blockIdx.x >> 1;
+  const int n0 = blockIdx.y * (2 * kBM) + static_cast<int>(rank) * kBM;   // this CTA's weight rows
+  const int t0 = m_tile * BN;                                              // the pair's token tile
+  const int tb0 = t0 + static_cast<int>(rank) * half;                      // this CTA's half of it
+  const int split = blockIdx.z;
+  const int k_begin = split * k_per_split;
+  const int k_end = min(K, k_begin + k_per_split);
+  const int k_iters = (k_end - k_begin + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 1);
+    }
+    mbar_init(&tail->tmem_full, 1);
+    tail->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tail->tmem_base, tmem_cols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t tmem_base = tail->tmem_base;
+  volatile int* abort_word = &tail->abort_word;
+  pdl_wait();
+  pdl_trigger();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    bool ready = true;
+    if (gate_flags != nullptr) {
+      const int t_last = min(tb0 + half, M) - 1;
+      const int s_lo = tb0 / gate_rpr, s_hi = t_last / gate_rpr;   // empty range when tb0 >= M
+      const int want = ld_volatile(gate_flags + kReadyEpoch);
+      bool mine = true;
+      if (lane >= s_lo && lane <= s_hi && lane < gate_world)
+        mine = wait_flag_ge(gate_flags + kReady + lane, want, err, 115);
+      ready = __all_sync(0xffffffffu, mine);
+      asm volatile("fence.proxy.async;" ::: "memory");
+      if (!ready && lane == 0) *abort_word = 115;
+    }
+    if (lane == 0 && ready) {
+      for (int it = 0; it < k_iters; ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1;
+        if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, err, 111)) break;
+        uint8_t* sa = smem + s * stage_bytes;
+        uint8_t* sb = sa + a_bytes;
+        if (rank == 0) mbar_arrive_expect_tx(&tail->full[s], 2 * stage_bytes);
+        const uint32_t full_leader = mapa_shared(&tail->full[s], 0);
+        const int kc = k_begin + it * kBK;
+        if (packed_kb > 0) {
+          const int kb = kc / kBK;
+          tma_load_2d_pair(sa, &tmW, full_leader, 0, ((n0 >> 7) * packed_kb + kb) << 7);
+          if (DUAL)
+            tma_load_2d_pair(sa + kATileBytes, &tmW, full_leader, 0,
+                             (((dual_rows + n0) >> 7) * packed_kb + kb) << 7);
+        } else {
+          tma_load_2d_pair(sa, &tmW, full_leader, kc, n0);
+          if (DUAL) tma_load_2d_pair(sa + kATileBytes, &tmW, full_leader, kc, dual_rows + n0);
+        }
+        tma_load_2d_pair(sb, &tmX, full_leader, kc, tb0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc(2 * kBM, BN, 1, 1);
+      bool ok = true;
+      for (int it = 0; it < k_iters && ok; ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1;
+        ok = mbar_wait(&tail->full[s], ph, abort_word, err, 112);
+        if (!ok) break;
+        tc_fence_after();
+        uint8_t* sa = smem + s * stage_bytes;
+        const uint64_t da0 = umma_desc_sw128(sa);
+        const uint64_t da1 = umma_desc_sw128(sa + kATileBytes);
+        const uint64_t db = umma_desc_sw128(sa + a_bytes);
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+          const uint64_t koff = static_cast<uint64_t>(k * kUmmaK * 2 >> 4);
+          umma_bf16_pair(tmem_base, da0 + koff, db + koff, idesc, acc);
+          if (DUAL) umma_bf16_pair(tmem_base + BN, da1 + koff, db + koff, idesc, acc);
+        }
+        tc_commit_pair(mapa_shared(&tail->empty[s], 0));
+        tc_commit_pair(mapa_shared(&tail->empty[s], 1));
+      }
+      tc_commit_pair(mapa_shared(&tail->tmem_full, 0));
+      tc_commit_pair(mapa_shared(&tail->tmem_full, 1));
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    const bool ok = mbar_wait(&tail->tmem_full, 0, abort_word, err, 113);
+    tc_fence_after();
+    if (ok && k_iters > 0)
+      epilogue_tile<DUAL, EPI>(tmem_base, stage_buf, quad, lane, Yv, R, M, N, ldy, ldr, BN, n0, t0, M, split);
+  }
+
+  // neither CTA may leave (or free TMEM) while the other can still read its shared memory, signal
+  // its barriers or run MMAs into its TMEM
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, tmem_cols);
   }
 }
 
@@ -409,6 +569,45 @@ static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, con
   return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
+template <bool DUAL, int EPI>
+static int launch_pair_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, const void* R, int M, int N,
+                           int K, int ldy, int ldr, int dual_rows, int k_per_split, int splits, int BN,
+                           int stages, int* err, cudaStream_t stream, const int* gate_flags, int gate_rpr,
+                           int gate_world, int packed_kb) {
+  const int stage_bytes = kATileBytes * (DUAL ? 2 : 1) + (BN / 2) * kBK * 2;
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes +
+                      sizeof(GemmSmemTail) + 1024;
+  auto kern = gemm_pair_kernel<DUAL, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+      return MB_ERR_LAUNCH;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * ((M + BN - 1) / BN), (N + 2 * kBM - 1) / (2 * kBM), splits);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.numAttrs = 1;
+  if (pdl_enabled()) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  cfg.attrs = attr;
+  const uint32_t tmem_cols = pow2_cols(DUAL ? 2 * BN : BN);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, Y, static_cast<const __nv_bfloat16*>(R), M, N, K,
+                                           ldy, ldr, dual_rows, k_per_split, BN, stages, tmem_cols, err,
+                                           gate_flags, gate_rpr, gate_world, packed_kb);
+  return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -529,6 +728,82 @@ extern "C" int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const v
                                                 gate_world, packed_kb);
   return launch_cfg<false, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err,
                                      stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb);
+}
+
+// CTA-pair (cta_group::2) GEMM: same contract and flags as mb_gemm_bf16_gated. The token tile is a
+// multiple of 32 (each CTA of a pair loads half of it).
+extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,
+                                 int ldx, int ldw, int ldy, int ldr, int flags, int bn, int splits,
+                                 int stages, void* workspace, int* err, int num_sms, const int* gate_flags,
+                                 int gate_rpr, int gate_world, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return MB_OK;
+  if (gate_flags != nullptr && (gate_rpr < 1 || gate_world < 1 || gate_world > kMaxRanks)) return MB_ERR_SHAPE;
+  const bool dual = flags & 1, resid = flags & 2, f32 = flags & 4, packed = flags & 64;
+  if (packed && (K % kBK || N % kBM || ldw != K)) return MB_ERR_SHAPE;
+  const int packed_kb = packed ? K / kBK : 0;
+  if (K % 8 || ldx % 8 || ldw % 8 || N % 8 || (!f32 && ldy % 8) || (resid && ldr % 8)) return MB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(Y) |
+       reinterpret_cast<uintptr_t>(R)) & 15)
+    return MB_ERR_ALIGN;
+  if (dual && f32) return MB_ERR_SHAPE;
+  if (num_sms <= 0) num_sms = 148;
+  if (bn <= 0) {
+    const int mt = (M + 255) / 256;
+    bn = ((M + mt - 1) / mt + 31) / 32 * 32;
+  }
+  if (bn % 32 || bn < 32 || bn > 256) return MB_ERR_SHAPE;
+  const int m_tiles = (M + bn - 1) / bn;
+  const int pairs = (N + 2 * kBM - 1) / (2 * kBM);
+  const int k_blocks = (K + kBK - 1) / kBK;
+  if (splits <= 0) {
+    splits = 1;
+    const int ctas = 2 * m_tiles * pairs;
+    if (!dual && !f32 && ctas * 2 <= num_sms) {
+      splits = num_sms / ctas;
+      if (splits > k_blocks / 8) splits = k_blocks / 8 > 0 ? k_blocks / 8 : 1;
+      if (splits > 8) splits = 8;
+    }
+  }
+  if (splits > 1 && (workspace == nullptr || dual || f32)) splits = 1;
+  const int stage_bytes = kATileBytes * (dual ? 2 : 1) + (bn / 2) * kBK * 2;
+  const int max_stages = (227 * 1024 - 1024 - 4 * kStageWarpBytes - 512) / stage_bytes;
+  if (stages <= 0 || stages > max_stages) stages = max_stages;
+  if (stages > 8) stages = 8;
+  if (stages < 2) return MB_ERR_SHAPE;
+  const int w_rows = dual ? 2 * N : N;
+  CUtensorMap tw, tx;
+  int rc = packed ? cached_tmap(&tw, W, static_cast<uint64_t>(w_rows) * packed_kb, kBK, kBK, kBM, 2)
+                  : cached_tmap(&tw, W, w_rows, K, ldw, kBM, 2);
+  if (rc != MB_OK) return rc;
+  rc = cached_tmap(&tx, X, M, K, ldx, bn / 2, 2);
+  if (rc != MB_OK) return rc;
+  int k_per_split = K;
+  if (splits > 1) {
+    k_per_split = ((k_blocks + splits - 1) / splits) * kBK;
+    splits = (K + k_per_split - 1) / k_per_split;
+  }
+  if (splits > 1) {
+    rc = launch_pair_cfg<false, EPI_F32>(tw, tx, workspace, nullptr, M, N, K, N, 0, 0, k_per_split, splits, bn,
+                                         stages, err, stream, gate_flags, gate_rpr, gate_world, packed_kb);
+    if (rc != MB_OK) return rc;
+    const size_t total4 = (static_cast<size_t>(M) * N + 3) / 4;
+    const cudaError_t e = launch_k(
+        splitk_reduce_kernel, dim3(static_cast<unsigned>((total4 + 255) / 256)), dim3(256), 0, stream,
+        static_cast<const float*>(workspace), resid ? static_cast<const __nv_bfloat16*>(R) : nullptr,
+        static_cast<__nv_bfloat16*>(Y), M, N, splits, ldy, ldr);
+    return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+  }
+  if (dual)
+    return launch_pair_cfg<true, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, N, K, 1, bn, stages, err, stream,
+                                           gate_flags, gate_rpr, gate_world, packed_kb);
+  if (f32)
+    return launch_pair_cfg<false, EPI_F32>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err, stream,
+                                           gate_flags, gate_rpr, gate_world, packed_kb);
+  if (resid)
+    return launch_pair_cfg<false, EPI_BF16_RESIDUAL>(tw, tx, Y, R, M, N, K, ldy, ldr, 0, K, 1, bn, stages, err,
+                                                     stream, gate_flags, gate_rpr, gate_world, packed_kb);
+  return launch_pair_cfg<false, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err, stream,
+                                          gate_flags, gate_rpr, gate_world, packed_kb);
 }
 
 // Grouped GEMM for mixture-of-experts layers: rows [offsets[e], offsets[e+1]) of X (tokens in

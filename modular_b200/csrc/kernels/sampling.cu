@@ -92,7 +92,56 @@ argmax_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   if (threadIdx.x == 0) out[blockIdx.x] = a.i;
 }
 
-__global__ void __launch_bounds__(kSampThreads)
+// Largest key t in [lo, hi] with measure{ i : fkey(x_i) >= t } >= target, where the measure is a count
+// (MASS = false) or the softmax mass exp(x_i - mx) (MASS = true). Sixteen-way search: every pass over the row
+// evaluates fifteen thresholds at once (per-thread bucket accumulators, one block reduction), so the 32-bit
+// key space is resolved in eight passes instead of thirty-two. Requires measure(key >= lo) >= target.
+template <bool MASS>
+__device__ uint32_t multiway_threshold(const float* __restrict__ row, int vocab, float invT, float mx,
+                                       uint32_t lo, uint32_t hi, float target, float* sh_acc /* [32][16] */) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  while (lo < hi) {
+    const uint32_t width = (hi - lo) / 16u + 1u;   // bucket j = [lo + j*width, lo + (j+1)*width); 16 cover [lo, hi]
+    float acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float x = row[i] * invT;
+      const uint32_t key = fkey(x);
+      if (key < lo) continue;
+      const uint32_t bq = (key - lo) / width;
+      const int b = bq > 15u ? 15 : static_cast<int>(bq);               // keys above hi count for every threshold
+      const float w = MASS ? __expf(x - mx) : 1.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] += (b == j) ? w : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+      if (lane == 0) sh_acc[warp * 16 + j] = acc[j];
+    }
+    __syncthreads();
+    // every thread derives the same decision: suffix sums over buckets, from the top
+    float suffix = 0.f;
+    int best = 0;            // bucket 0 always qualifies (its threshold is lo itself)
+    bool found = false;
+    for (int j = 15; j >= 0; --j) {
+      float t = 0.f;
+      for (int q = 0; q < (blockDim.x >> 5); ++q) t += sh_acc[q * 16 + j];
+      suffix += t;
+      if (!found && suffix >= target) { best = j; found = true; }
+    }
+    __syncthreads();
+    // a qualifying bucket holds a key, so lo + best * width cannot wrap; the bucket's upper end can
+    lo += static_cast<uint32_t>(best) * width;
+    const uint64_t new_hi = static_cast<uint64_t>(lo) + width - 1;
+    hi = new_hi < hi ? static_cast<uint32_t>(new_hi) : hi;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(kSampThreads, 1)
 sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int vocab, int ld,
               const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ min_p,
@@ -100,6 +149,7 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   __shared__ ArgMax sh_am[32];
   __shared__ float sh_f[32];
   __shared__ float sh_scan[kSampThreads / 32];
+  __shared__ float sh_acc[(kSampThreads / 32) * 16];
   __shared__ int sh_pick;
   pdl_wait();
   pdl_trigger();
@@ -140,14 +190,7 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   uint32_t thr_key = 0;  // keep x with fkey(x*invT) >= thr_key
   if (use_k) {
     // largest key t with count(key >= t) >= k
-    uint32_t lo = 0, hi = fkey(mx);
-    while (lo < hi) {
-      const uint32_t mid = lo + ((hi - lo + 1) >> 1);
-      float c = 0.f;
-      for (int i = threadIdx.x; i < vocab; i += blockDim.x) c += fkey(row[i] * invT) >= mid ? 1.f : 0.f;
-      c = block_sum_f(c, sh_f);
-      if (c >= static_cast<float>(k)) lo = mid; else hi = mid - 1;
-    }
+    const uint32_t lo = multiway_threshold<false>(row, vocab, invT, mx, 0u, fkey(mx), static_cast<float>(k), sh_acc);
     thr_key = lo;
   }
   if (use_m) {
@@ -163,17 +206,7 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   if (use_p) {
     // largest key t (>= thr_key) with mass(key >= t) >= tp * Z
     const float target = tp * Z;
-    uint32_t lo = thr_key, hi = fkey(mx);
-    while (lo < hi) {
-      const uint32_t mid = lo + ((hi - lo + 1) >> 1);
-      float c = 0.f;
-      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float x = row[i] * invT;
-        c += fkey(x) >= mid ? __expf(x - mx) : 0.f;
-      }
-      c = block_sum_f(c, sh_f);
-      if (c >= target) lo = mid; else hi = mid - 1;
-    }
+    const uint32_t lo = multiway_threshold<true>(row, vocab, invT, mx, thr_key, fkey(mx), target, sh_acc);
     thr_key = lo;
     Z = 0.f;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {

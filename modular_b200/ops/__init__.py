@@ -48,7 +48,8 @@ def check_device_error() -> None:
 
 _PERSISTENT_WS: dict[int, tuple] = {}
 # "auto" (default): per-shape choice; "persistent": one CTA per SM with stream-K work split;
-# "tiled": one CTA per output tile with optional split-K through a workspace.
+# "tiled": one CTA per output tile with optional split-K through a workspace;
+# "pair": the tiled kernel on clusters of two CTAs (cta_group::2 MMAs, 256 weight rows per pair).
 GEMM_IMPL = os.environ.get("MB200_GEMM", "auto")
 
 
@@ -79,6 +80,8 @@ def linear(x, w, residual=None, out=None, out_dtype=None, bn=0, splits=0, stages
     if (impl or GEMM_IMPL) == "persistent":
         ws, counters = persistent_gemm_workspace(x.device)
         _lib().gemm_bf16_persistent(x, w, out, residual, False, ws, counters, bn, stages, mode, pdl)
+    elif (impl or GEMM_IMPL) == "pair":
+        _lib().gemm_bf16(x, w, out, residual, False, gemm_workspace(x.device), bn, splits, stages, False, True)
     else:
         _lib().gemm_bf16(x, w, out, residual, False, gemm_workspace(x.device), bn, splits, stages)
     return out
@@ -95,7 +98,9 @@ def linear_swiglu(x, w_gate_up, out=None, bn=0, stages=0, impl=None, mode=-1, pd
     if out is None:
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
     sel = impl or GEMM_IMPL
-    if sel in ("persistent", "auto"):
+    if sel == "pair":
+        _lib().gemm_bf16(x, w_gate_up, out, None, True, None, bn, 1, stages, False, True)
+    elif sel in ("persistent", "auto"):
         ws, counters = persistent_gemm_workspace(x.device)
         if sel == "auto" and mode < 0:
             mode = 0  # whole tiles, no stream-K fix-up: the measured best for the fused SwiGLU GEMM
@@ -245,13 +250,14 @@ def quant_fp8_group128(x):
     return q, s
 
 
-def linear_fp8_blockscaled(xq, xs, wq, ws, residual=None, out=None, bn=0, stages=0):
-    """``(xq * xs) @ (wq * ws).T`` with 128x128 weight-block scales and 1x128 activation scales."""
+def linear_fp8_blockscaled(xq, xs, wq, ws, residual=None, out=None, bn=0, stages=0, splits=0):
+    """``(xq * xs) @ (wq * ws).T`` with 128x128 weight-block scales and 1x128 activation scales.
+    ``splits``: K splits (0 = chosen by the kernel from the tile count and the SM count)."""
     if not xq.is_cuda:
         return ref.linear_fp8_blockscaled(xq, xs, wq, ws, residual)
     if out is None:
         out = torch.empty(xq.shape[0], wq.shape[0], dtype=torch.bfloat16, device=xq.device)
-    _lib().gemm_fp8_blockscaled(xq, xs, wq, ws, out, residual, bn, stages)
+    _lib().gemm_fp8_blockscaled(xq, xs, wq, ws, out, residual, bn, stages, splits, gemm_workspace(xq.device))
     return out
 
 

@@ -217,6 +217,20 @@ def test_argmax_and_sampling():
         p = ref.filtered_probs(lg[0], 0.8, kw.get("top_k", 0), kw.get("top_p", 1.0), kw.get("min_p", 0.0))
         assert (emp[p == 0] == 0).all(), kw
         assert (emp - p).abs().max() < 0.04, kw
+    # full-size vocabulary: the samples stay inside the filtered support
+    big = (torch.randn(1, 128256, device=DEV) * 3).repeat(512, 1).contiguous()
+    sd = torch.arange(512, device=DEV, dtype=torch.int64) * 104729 + 5
+    t1 = torch.ones(512, device=DEV)
+    for kw in (dict(top_k=50), dict(top_p=0.6), dict(top_k=1000, top_p=0.95)):
+        args = dict(temperature=t1, seeds=sd, step=1)
+        if "top_k" in kw:
+            args["top_k"] = torch.full((512,), kw["top_k"], device=DEV, dtype=torch.int32)
+        if "top_p" in kw:
+            args["top_p"] = torch.full((512,), kw["top_p"], device=DEV)
+        s = ops.sample(big, **args)
+        p = ref.filtered_probs(big[0], 1.0, kw.get("top_k", 0), kw.get("top_p", 1.0), 0.0)
+        assert (p[s] > 0).all(), kw
+        assert s.unique().numel() > 8, kw
 
 
 def test_penalties():
@@ -261,3 +275,18 @@ def test_gemm_fp8_blockscaled(M, N, K):
     assert _rel_err(y, ref.linear(x, w)) < 0.06   # against the unquantised product
     y2 = ops.linear_fp8_blockscaled(xq, xs, wq, ws, residual=r)
     assert _rel_err(y2, ref.linear_fp8_blockscaled(xq, xs, wq, ws, r)) < 5e-3
+
+
+def test_gemm_fp8_blockscaled_split_k_matches_single_pass():
+    torch.manual_seed(22)
+    M, N, K = 70, 1024, 3712          # 29 K groups: uneven splits
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    wq, ws = ref.quant_fp8_weight_block128(w)
+    xq, xs = ops.quant_fp8_group128(x)
+    r = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    y1 = ops.linear_fp8_blockscaled(xq, xs, wq, ws, residual=r, splits=1)
+    for splits in (2, 3, 8):
+        ys = ops.linear_fp8_blockscaled(xq, xs, wq, ws, residual=r, splits=splits)
+        assert _rel_err(ys, y1) < 3e-3, splits
+    assert _rel_err(y1, ref.linear_fp8_blockscaled(xq, xs, wq, ws, r)) < 5e-3
