@@ -43,6 +43,11 @@ def _load():
             # 64-row tiles (default 32; 0 turns it off, 1 always uses it)
             if hasattr(mod, "set_attn_tc"):
                 mod.set_attn_tc(int(os.environ.get("MB200_ATTN_TC", "32") or 0))
+            # GEMMs on CTA pairs (cta_group::2): MB200_GEMM_PAIR="<min tokens, plain>,<min tokens, SwiGLU>",
+            # 0 = never for that kind
+            if hasattr(mod, "set_gemm_pair"):
+                plain, _, dual = os.environ.get("MB200_GEMM_PAIR", "0,0").partition(",")
+                mod.set_gemm_pair(int(plain or 0), int(dual or 0))
             _MOD = mod
         except Exception as e:  # noqa: BLE001
             _ERR = e

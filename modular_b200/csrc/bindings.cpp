@@ -569,6 +569,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("num_sms", &num_sms);
   m.def("set_attn_tc", [](int min_tiles) { mb_set_attn_tc(min_tiles); });
   m.def("get_attn_tc", []() { return mb_get_attn_tc(); });
+  m.def("set_gemm_pair", [](int min_m_plain, int min_m_dual) { mb_set_gemm_pair(min_m_plain, min_m_dual); },
+        py::arg("min_m_plain"), py::arg("min_m_dual"));
   m.def("set_pdl", [](bool on) { mb_set_pdl(on ? 1 : 0); });
   m.def("get_pdl", []() { return mb_get_pdl() != 0; });
   m.def("tp_flag_ints", []() { return mb_tp_flag_ints(); });

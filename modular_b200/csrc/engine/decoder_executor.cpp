@@ -59,6 +59,12 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
       persistent = (flags & 1) || tiles >= 4 * c.num_sms;
       mode = 0;
     }
+    if (mb_gemm_pair_wanted(M, flags & 1)) {
+      const bool ws_ok = static_cast<size_t>(8) * M * N * sizeof(float) <= buf.workspace_bytes;
+      launches += 1;
+      return mb_gemm_bf16_pair(X, W, Y, R, M, N, K, ldx, K, ldy, ldy, flags, 0, ws_ok ? 0 : 1, 0,
+                               ws_ok ? buf.workspace : nullptr, buf.err, c.num_sms, nullptr, 1, 0, stream);
+    }
     if (persistent && buf.p_ws != nullptr) {
       launches += 1;
       return mb_gemm_bf16_persistent(X, W, Y, R, M, N, K, ldx, K, ldy, ldy, flags | (c.use_pdl ? 8 : 0),

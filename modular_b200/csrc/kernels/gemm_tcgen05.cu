@@ -730,6 +730,18 @@ extern "C" int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const v
                                      stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb);
 }
 
+// Process-wide choice of the CTA-pair kernel by token count: plain (and residual) GEMMs with
+// M >= min_m_plain and fused SwiGLU GEMMs with M >= min_m_dual use it; 0 = never.
+static int g_pair_min_m[2] = {0, 0};
+extern "C" void mb_set_gemm_pair(int min_m_plain, int min_m_dual) {
+  g_pair_min_m[0] = min_m_plain;
+  g_pair_min_m[1] = min_m_dual;
+}
+extern "C" int mb_gemm_pair_wanted(int M, int dual) {
+  const int m = g_pair_min_m[dual ? 1 : 0];
+  return m > 0 && M >= m;
+}
+
 // CTA-pair (cta_group::2) GEMM: same contract and flags as mb_gemm_bf16_gated. The token tile is a
 // multiple of 32 (each CTA of a pair loads half of it).
 extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,

@@ -58,7 +58,8 @@ class LLM:
                  enable_in_flight_batching: bool = False, enable_overlap_scheduler: Optional[bool] = None,
                  device_graph_capture: bool = True, graph_batch_sizes: Optional[Sequence[int]] = None,
                  eos_token_ids: Sequence[int] = (), seed: int = 0, tp_size: int = 1,
-                 tp_rank: int = 0):
+                 tp_rank: int = 0, host_kvcache_swap_space_gb: float = 0.0,
+                 disk_kvcache_dir: Optional[str] = None, disk_kvcache_space_gb: float = 0.0):
         from ..models import family_for
 
         fam = family_for(model_config)
@@ -100,7 +101,11 @@ class LLM:
                 num_kv_pages = kvp.compute_num_device_blocks(budget, max_batch_size * 4, max_length)
             else:
                 num_kv_pages = kvp.compute_num_device_blocks(1 << 62, max_batch_size, max_length)
-        self.kv = PagedKVCacheManager(kvp, num_kv_pages, self.device, max_seq_len=max_length)
+        # evicted prefix pages fall back to pinned host memory and then to a file (kv_cache/tiers.py)
+        host_pages = int(host_kvcache_swap_space_gb * (1 << 30) // kvp.bytes_per_page)
+        disk_pages = int(disk_kvcache_space_gb * (1 << 30) // kvp.bytes_per_page) if disk_kvcache_dir else 0
+        self.kv = PagedKVCacheManager(kvp, num_kv_pages, self.device, max_seq_len=max_length,
+                                      host_pages=host_pages, disk_pages=disk_pages, disk_dir=disk_kvcache_dir)
         extra = {"tp": self.tp} if fam.supports_tp else {}
         self.model = fam.model_class(model_config, weights, self.kv.kv, max_tokens=max_batch_input_tokens,
                                      max_seqs=max_batch_size, max_position=max_length, **extra)

@@ -43,6 +43,9 @@ class BlockPool:
         self._free: "OrderedDict[int, None]" = OrderedDict((i, None) for i in range(first, num_blocks))
         self._by_hash: dict[int, int] = {}
         self.evictions = 0
+        # called as on_evict(block_id, block_hash, parent_hash) just before a cached page's content is
+        # given up (the lower cache tiers copy the page out here)
+        self.on_evict = None
 
     # ---- introspection
     @property
@@ -73,6 +76,8 @@ class BlockPool:
                 # evict the cached content
                 if self._by_hash.get(blk.block_hash) == bid:
                     del self._by_hash[blk.block_hash]
+                    if self.on_evict is not None:
+                        self.on_evict(bid, blk.block_hash, blk.parent_hash)
                 blk.block_hash = None
                 blk.parent_hash = None
                 self.evictions += 1

@@ -104,7 +104,8 @@ class _ReqState:
 
 class PagedKVCacheManager:
     def __init__(self, params: KVCacheParams, num_pages: int, device="cpu", max_seq_len: int = 0,
-                 allocate: bool = True):
+                 allocate: bool = True, host_pages: int = 0, disk_pages: int = 0,
+                 disk_dir: Optional[str] = None):
         self.params = params
         self.page_size = params.page_size
         self.num_pages = num_pages
@@ -115,9 +116,16 @@ class PagedKVCacheManager:
         self.kv = (torch.zeros(params.shape(num_pages), dtype=params.dtype, device=self.device)
                    if allocate else None)
         self._req: dict[str, _ReqState] = {}
+        # lower tiers for evicted prefix pages (pinned host memory, then a file); see tiers.py
+        self.tiers = None
+        if allocate and params.enable_prefix_caching and host_pages > 0:
+            from .tiers import TieredKVStore
+            self.tiers = TieredKVStore(params.shape(1)[1:], params.dtype, host_pages, disk_pages, disk_dir)
+            self.pool.on_evict = self._offload_page
         # metrics
         self.prefix_query_tokens = 0
         self.prefix_hit_tokens = 0
+        self.tier_hit_tokens = 0       # part of prefix_hit_tokens that came back from host memory or disk
         self.preemptions = 0
 
     # ------------------------------------------------------------ bookkeeping
@@ -138,7 +146,24 @@ class PagedKVCacheManager:
             self.pool.release(bid)
 
     def reset_prefix_cache(self) -> bool:
+        if self.tiers is not None:
+            self.tiers.clear()
         return self.pool.reset_prefix_cache()
+
+    def _offload_page(self, bid: int, block_hash: int, parent_hash) -> None:
+        self.tiers.offload(self.kv[bid], block_hash, parent_hash)
+
+    def _onload_page(self, block_hash: int, parent_hash) -> Optional[int]:
+        """Bring a page of a lower tier back into a fresh device page; None if it cannot be placed."""
+        try:
+            bid = self.pool.allocate(1)[0]
+        except InsufficientBlocksError:
+            return None
+        if self.tiers.onload(block_hash, self.kv[bid]) is None:   # evicted from the tier by that allocation
+            self.pool.release(bid)
+            return None
+        self.pool.commit(bid, block_hash, parent_hash)
+        return bid
 
     @property
     def free_blocks(self) -> int:
@@ -171,8 +196,14 @@ class PagedKVCacheManager:
         for h in hashes:
             bid = self.pool.lookup(h)
             if bid is None:
-                break
-            self.pool.acquire_cached(bid)
+                if self.tiers is None or h not in self.tiers:
+                    break
+                bid = self._onload_page(h, parent)
+                if bid is None:
+                    break
+                self.tier_hit_tokens += self.page_size
+            else:
+                self.pool.acquire_cached(bid)
             st.blocks.append(bid)
             st.hashes.append(h)
             parent = h

@@ -73,7 +73,9 @@ class KVCacheConfig(ConfigFileModel):
     enable_prefix_caching: bool = True
     device_memory_utilization: float = 0.9
     kv_cache_format: Optional[str] = None          # None = model dtype, "float8_e4m3fn" = fp8 KV
-    host_kvcache_swap_space_gb: float = 0.0
+    host_kvcache_swap_space_gb: float = 0.0        # pinned host memory for evicted prefix pages
+    disk_kvcache_dir: Optional[str] = None         # file tier below the host tier
+    disk_kvcache_space_gb: float = 0.0
     kv_block_hash_algorithm: str = "native64"       # native64 | sha256
     enable_kv_head_replication: bool = False        # TP degree > kv heads
 

@@ -147,7 +147,10 @@ class PipelineRegistry:
                   device_graph_capture=bool(rt.device_graph_capture),
                   graph_batch_sizes=[b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256)
                                      if b <= min(max_bs, rt.max_graph_capture_batch_size)],
-                  eos_token_ids=tokenizer.eos_token_ids)
+                  eos_token_ids=tokenizer.eos_token_ids,
+                  host_kvcache_swap_space_gb=m.kv_cache.host_kvcache_swap_space_gb,
+                  disk_kvcache_dir=m.kv_cache.disk_kvcache_dir,
+                  disk_kvcache_space_gb=m.kv_cache.disk_kvcache_space_gb)
         llm.tokenizer = tokenizer
         if pc.sampling.enable_structured_output:
             llm.pipeline.enable_structured_output(tokenizer)
