@@ -555,6 +555,69 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("argmax", &argmax);
   m.def("sample", &sample);
   m.def("apply_penalties", &apply_penalties);
+  // state-space layers
+  m.def("causal_conv1d_varlen", [](const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, Tensor& y,
+                                   const c10::optional<Tensor>& conv_state, const Tensor& cu_seqlens,
+                                   const c10::optional<Tensor>& state_idx, const c10::optional<Tensor>& has_init,
+                                   bool silu) {
+    need_cuda(x, "x");
+    TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && y.stride(1) == 1 && x.scalar_type() == at::kBFloat16 &&
+                    w.is_contiguous() && w.scalar_type() == at::kBFloat16 && w.size(0) == x.size(1),
+                "causal_conv1d: x [T, D] bf16, w [D, W] bf16");
+    TORCH_CHECK(cu_seqlens.scalar_type() == at::kInt, "cu_seqlens int32");
+    check_rc(mb_causal_conv1d_varlen(x.data_ptr(), w.data_ptr(), optptr(bias), y.data_ptr(),
+                                     conv_state.has_value() ? conv_state->data_ptr<float>() : nullptr,
+                                     cu_seqlens.data_ptr<int>(),
+                                     state_idx.has_value() ? state_idx->data_ptr<int>() : nullptr,
+                                     has_init.has_value() ? has_init->data_ptr<int>() : nullptr,
+                                     cu_seqlens.numel() - 1, x.size(1), w.size(1), x.stride(0), y.stride(0),
+                                     silu ? 1 : 0, cur_stream()),
+             "causal_conv1d_varlen");
+  });
+  m.def("selective_scan_varlen", [](const Tensor& u, const Tensor& delta, const Tensor& A, const Tensor& B,
+                                    const Tensor& C, const c10::optional<Tensor>& D, const c10::optional<Tensor>& z,
+                                    const c10::optional<Tensor>& dt_bias, Tensor& y,
+                                    const c10::optional<Tensor>& ssm_state, const Tensor& cu_seqlens,
+                                    const c10::optional<Tensor>& state_idx, const c10::optional<Tensor>& has_init,
+                                    bool dt_softplus) {
+    need_cuda(u, "u");
+    TORCH_CHECK(u.is_contiguous() && delta.is_contiguous() && y.is_contiguous() && B.is_contiguous() &&
+                    C.is_contiguous() && A.is_contiguous() && A.scalar_type() == at::kFloat &&
+                    u.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
+                "selective_scan: contiguous bf16 u/delta/B/C, fp32 A");
+    TORCH_CHECK(!z.has_value() || z->is_contiguous(), "selective_scan: z contiguous");
+    check_rc(mb_selective_scan_varlen(u.data_ptr(), delta.data_ptr(), A.data_ptr<float>(), B.data_ptr(),
+                                      C.data_ptr(), D.has_value() ? D->data_ptr<float>() : nullptr, optptr(z),
+                                      dt_bias.has_value() ? dt_bias->data_ptr<float>() : nullptr, y.data_ptr(),
+                                      ssm_state.has_value() ? ssm_state->data_ptr<float>() : nullptr,
+                                      cu_seqlens.data_ptr<int>(),
+                                      state_idx.has_value() ? state_idx->data_ptr<int>() : nullptr,
+                                      has_init.has_value() ? has_init->data_ptr<int>() : nullptr,
+                                      cu_seqlens.numel() - 1, u.size(1), A.size(1), u.size(1), B.size(1),
+                                      dt_softplus ? 1 : 0, cur_stream()),
+             "selective_scan_varlen");
+  });
+  m.def("ssd_scan_varlen", [](const Tensor& x, const Tensor& dt, const Tensor& A, const Tensor& B, const Tensor& C,
+                              const c10::optional<Tensor>& D, const c10::optional<Tensor>& dt_bias, Tensor& y,
+                              const c10::optional<Tensor>& ssm_state, const Tensor& cu_seqlens,
+                              const c10::optional<Tensor>& state_idx, const c10::optional<Tensor>& has_init,
+                              bool dt_softplus) {
+    need_cuda(x, "x");
+    TORCH_CHECK(x.dim() == 3 && x.is_contiguous() && dt.is_contiguous() && B.dim() == 3 && B.is_contiguous() &&
+                    C.is_contiguous() && y.is_contiguous() && A.scalar_type() == at::kFloat &&
+                    x.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
+                "ssd_scan: x [T, H, P], dt [T, H], B/C [T, G, N] contiguous bf16, A fp32 [H]");
+    check_rc(mb_ssd_scan_varlen(x.data_ptr(), dt.data_ptr(), A.data_ptr<float>(), B.data_ptr(), C.data_ptr(),
+                                D.has_value() ? D->data_ptr<float>() : nullptr,
+                                dt_bias.has_value() ? dt_bias->data_ptr<float>() : nullptr, y.data_ptr(),
+                                ssm_state.has_value() ? ssm_state->data_ptr<float>() : nullptr,
+                                cu_seqlens.data_ptr<int>(),
+                                state_idx.has_value() ? state_idx->data_ptr<int>() : nullptr,
+                                has_init.has_value() ? has_init->data_ptr<int>() : nullptr,
+                                cu_seqlens.numel() - 1, x.size(1), x.size(2), B.size(2), B.size(1),
+                                dt_softplus ? 1 : 0, cur_stream()),
+             "ssd_scan_varlen");
+  });
   m.def("apply_token_bitmask", [](Tensor& logits, const Tensor& bitmask) {
     need_cuda(logits, "logits");
     TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1 && bitmask.is_contiguous() &&

@@ -189,6 +189,18 @@ int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, int vocab, 
                         const float* temperature, const int32_t* top_k, const float* top_p,
                         const float* min_p, const uint64_t* seeds, uint64_t step,
                         cudaStream_t stream);
+// ---- state-space layers (state_space.cu): ragged batches, per-sequence state slots (-1 = none)
+int mb_causal_conv1d_varlen(const void* x, const void* w, const void* bias, void* y, float* conv_state,
+                            const int* cu_seqlens, const int* state_idx, const int* has_init, int n_seqs,
+                            int D, int width, int ldx, int ldy, int act, cudaStream_t stream);
+int mb_selective_scan_varlen(const void* u, const void* delta, const float* A, const void* B, const void* C,
+                             const float* Dskip, const void* z, const float* dt_bias, void* y, float* ssm_state,
+                             const int* cu_seqlens, const int* state_idx, const int* has_init, int n_seqs,
+                             int D, int N, int ld_u, int ld_bc, int dt_softplus, cudaStream_t stream);
+int mb_ssd_scan_varlen(const void* x, const void* dt, const float* A, const void* B, const void* C,
+                       const float* Dskip, const float* dt_bias, void* y, float* ssm_state,
+                       const int* cu_seqlens, const int* state_idx, const int* has_init, int n_seqs, int H,
+                       int P, int N, int G, int dt_softplus, cudaStream_t stream);
 int mb_apply_token_bitmask(float* logits, const int32_t* bitmask, int rows, int vocab, int ld,
                            cudaStream_t stream);
 int mb_apply_penalties(float* logits, int rows, int vocab, int ld, const int32_t* tok,
