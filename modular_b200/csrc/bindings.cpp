@@ -618,6 +618,28 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                 dt_softplus ? 1 : 0, cur_stream()),
              "ssd_scan_varlen");
   });
+  // grouped block-scaled fp8 GEMM: xq [rows, K] e4m3 (tokens in expert order), xs fp32 [ceil(K/128), rows],
+  // wq [E, N, K] e4m3, ws fp32 [E, N/128, ceil(K/128)], offsets int32 [E + 1]
+  m.def("grouped_gemm_fp8", [](const Tensor& xq, const Tensor& xs, const Tensor& wq, const Tensor& ws, Tensor& y,
+                               const Tensor& offsets, int max_rows, int bn) {
+    need_cuda(xq, "xq");
+    TORCH_CHECK(xq.dim() == 2 && wq.dim() == 3 && xq.stride(1) == 1 && wq.is_contiguous() && xs.is_contiguous() &&
+                    ws.is_contiguous() && y.is_contiguous() && xq.element_size() == 1 && wq.element_size() == 1 &&
+                    y.scalar_type() == at::kBFloat16 && offsets.scalar_type() == at::kInt,
+                "grouped_gemm_fp8: contiguous fp8 operands, bf16 output, int32 offsets");
+    const int rows = xq.size(0), K = xq.size(1), E = wq.size(0), N = wq.size(1);
+    TORCH_CHECK(wq.size(2) == K && y.size(0) == rows && y.size(1) == N && offsets.numel() >= E + 1,
+                "grouped_gemm_fp8: shape mismatch");
+    TORCH_CHECK(xs.numel() == static_cast<int64_t>((K + 127) / 128) * rows &&
+                    ws.numel() == static_cast<int64_t>(E) * (N / 128) * ((K + 127) / 128),
+                "grouped_gemm_fp8: scale shapes");
+    check_rc(mb_grouped_gemm_fp8_blockscaled(xq.data_ptr(), xs.data_ptr<float>(), wq.data_ptr(),
+                                             ws.data_ptr<float>(), y.data_ptr(), offsets.data_ptr<int>(), E, rows,
+                                             max_rows, N, K, static_cast<int>(xq.stride(0)), bn, 0, error_flag(),
+                                             cur_stream()),
+             "grouped_gemm_fp8");
+  }, py::arg("xq"), py::arg("xs"), py::arg("wq"), py::arg("ws"), py::arg("y"), py::arg("offsets"),
+     py::arg("max_rows") = 0, py::arg("bn") = 0);
   m.def("apply_token_bitmask", [](Tensor& logits, const Tensor& bitmask) {
     need_cuda(logits, "logits");
     TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1 && bitmask.is_contiguous() &&

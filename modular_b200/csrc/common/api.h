@@ -61,6 +61,9 @@ int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const void* Wq, con
                             const void* R, int M, int N, int K, int flags, int bn, int stages, int splits,
                             void* workspace, size_t workspace_bytes, int num_sms, int* err,
                             cudaStream_t stream);
+int mb_grouped_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const void* Wq, const float* Ws, void* Y,
+                                    const int32_t* expert_offsets, int n_experts, int total_rows, int max_rows,
+                                    int N, int K, int ldx, int bn, int stages, int* err, cudaStream_t stream);
 
 // ---- elementwise / normalisation / rope (elementwise.cu) ---------------------------------
 int mb_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, int ldx, int ldo,

@@ -52,6 +52,10 @@ struct Params {
   int M, N, K, ldy, ldr, sw_ld, BN, stages;
   int splits, kb_per_split;
   float* partial;   // [splits, M, N] fp32 when splits > 1
+  // grouped (mixture-of-experts) mode: blockIdx.z = expert, token rows [offsets[e], offsets[e+1]),
+  // weights / weight scales of expert e start at row e * w_rows / e * sw_rows
+  const int* expert_offsets;
+  int w_rows, sw_rows;
 };
 
 constexpr int kAccBufs = 4;
@@ -77,9 +81,21 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   uint8_t* stg_base = smem + p.stages * stage_bytes;
   Tail* tail = reinterpret_cast<Tail*>(stg_base + 8 * kStgWarp);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.y * kBM, t0 = blockIdx.x * p.BN;
+  const int n0 = blockIdx.y * kBM;
+  int t0 = blockIdx.x * p.BN;
+  int Mlim = p.M, w_row0 = 0, sw_row0 = 0, zsplit = blockIdx.z;
+  if (p.expert_offsets != nullptr) {
+    const int e = blockIdx.z;
+    const int row_begin = p.expert_offsets[e], row_end = p.expert_offsets[e + 1];
+    t0 = row_begin + blockIdx.x * p.BN;
+    if (t0 >= row_end) return;      // whole CTA, before any barrier or TMEM allocation
+    Mlim = row_end;
+    w_row0 = e * p.w_rows;
+    sw_row0 = e * p.sw_rows;
+    zsplit = 0;
+  }
   const int kb_all = (p.K + 127) / 128;
-  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kb_begin = zsplit * p.kb_per_split;
   const int kb_end = kb_begin + p.kb_per_split < kb_all ? kb_begin + p.kb_per_split : kb_all;
   const int kb_total = kb_end - kb_begin;          // K groups of this split
   const uint32_t want_cols = p.BN * kAccBufs;
@@ -119,7 +135,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, p.err, 501)) break;
         uint8_t* sa = smem + s * stage_bytes;
         mbar_arrive_expect_tx(&tail->full[s], stage_bytes);
-        tma_load_2d(sa, &tmW, &tail->full[s], (kb_begin + kb) * 128, n0);
+        tma_load_2d(sa, &tmW, &tail->full[s], (kb_begin + kb) * 128, w_row0 + n0);
         tma_load_2d(sa + kATile, &tmX, &tail->full[s], (kb_begin + kb) * 128, t0);
       }
     }
@@ -157,12 +173,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     float acc[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) acc[i] = 0.f;
-    const float* sw_row = p.sw + static_cast<size_t>(blockIdx.y) * p.sw_ld + kb_begin;
+    const float* sw_row = p.sw + static_cast<size_t>(sw_row0 + blockIdx.y) * p.sw_ld + kb_begin;
     const float* sx_base = p.sx + static_cast<size_t>(kb_begin) * p.M + t0 + c_base;
     float* sc = &tail->scales[ew][0][0];
     // lane l owns the scales of token columns l and l + 32 of this warpgroup's half
-    const bool in0 = lane < cols && t0 + c_base + lane < p.M;
-    const bool in1 = lane + 32 < cols && t0 + c_base + lane + 32 < p.M;
+    const bool in0 = lane < cols && t0 + c_base + lane < Mlim;
+    const bool in1 = lane + 32 < cols && t0 + c_base + lane + 32 < Mlim;
     float s0 = 0.f, s1 = 0.f;
     if (kb_total > 0) {
       const float w = sw_row[0];
@@ -215,11 +231,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     if (ok && p.splits > 1) {
       // fp32 partials of this split: lane = weight row, so each token's 32 floats are contiguous
       const int n = n0 + quad * 32 + lane;
-      float* dst = p.partial + static_cast<size_t>(blockIdx.z) * p.M * p.N;
+      float* dst = p.partial + static_cast<size_t>(zsplit) * p.M * p.N;
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
         const int t = t0 + c_base + c;
-        if (c < cols && t < p.M && n < p.N) dst[static_cast<size_t>(t) * p.N + n] = acc[c];
+        if (c < cols && t < Mlim && n < p.N) dst[static_cast<size_t>(t) * p.N + n] = acc[c];
       }
       ok = false;   // nothing left for the bf16 epilogue
     }
@@ -228,7 +244,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       const int n_base = n0 + quad * 32;
 #pragma unroll
       for (int c = 0; c < 64; c += 16) {
-        if (c < cols && t0 + c_base + c < p.M) {
+        if (c < cols && t0 + c_base + c < Mlim) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) stg[j * 32 + lane] = __float2bfloat16(acc[c + j]);
           __syncwarp();
@@ -238,7 +254,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const int seg = lane & 3;
             const int t = t0 + c_base + c + j;
             const int n = n_base + seg * 8;
-            if (t < p.M && n < p.N) {
+            if (t < Mlim && n < p.N) {
               uint4 val = *reinterpret_cast<const uint4*>(stg + j * 32 + seg * 8);
               if (RESID) {
                 const uint4 rv = *reinterpret_cast<const uint4*>(p.R + static_cast<size_t>(t) * p.ldr + n);
@@ -399,6 +415,7 @@ extern "C" int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const vo
   splits = (kb_all + p.kb_per_split - 1) / p.kb_per_split;
   p.splits = splits;
   p.partial = static_cast<float*>(workspace);
+  p.expert_offsets = nullptr; p.w_rows = 0; p.sw_rows = 0;
   dim3 grid((M + bn - 1) / bn, (N + kBM - 1) / kBM, splits);
   const bool resid = (flags & 2) && splits == 1;
   static bool configured = false;
@@ -416,5 +433,61 @@ extern "C" int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const vo
     fp8_splitk_reduce_kernel<<<static_cast<unsigned>((total4 + 255) / 256), 256, 0, stream>>>(
         p.partial, (flags & 2) ? p.R : nullptr, p.Y, M, N, splits);
   }
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+// Grouped block-scaled fp8 GEMM for mixture-of-experts layers: rows [offsets[e], offsets[e+1]) of Xq
+// (tokens in expert order, scales Xs K-group-major over all `total_rows`) times expert e's weights
+// Wq[e] ([N, K] e4m3 with 128x128 block scales Ws[e]). N % 128 == 0. `max_rows` bounds the rows of any
+// expert (the grid is sized for it; CTAs past an expert's rows exit at once). `ldx` = byte stride of
+// Xq rows (0 = K).
+// Reference: max/python/max/nn/moe/moe_fp8.py:48 (MoEQuantized, fp8-blockwise strategy) over
+// max/kernels/src/linalg/grouped_matmul_sm100_blockwise_fp8.mojo.
+extern "C" int mb_grouped_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const void* Wq, const float* Ws,
+                                               void* Y, const int32_t* expert_offsets, int n_experts,
+                                               int total_rows, int max_rows, int N, int K, int ldx, int bn,
+                                               int stages, int* err, cudaStream_t stream) {
+  using namespace mb::f8;
+  if (total_rows <= 0 || N <= 0 || n_experts <= 0) return MB_OK;
+  if (ldx <= 0) ldx = K;            // row stride of Xq in bytes (rows may carry trailing scale bytes)
+  if (K % 16 || N % 128 || ldx % 16 || ldx < K) return MB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(Xq) | reinterpret_cast<uintptr_t>(Wq) | reinterpret_cast<uintptr_t>(Y)) & 15)
+    return MB_ERR_ALIGN;
+  if (max_rows <= 0 || max_rows > total_rows) max_rows = total_rows;
+  if (bn <= 0) {
+    // expected rows per expert decide the token tile: small tiles when experts see few tokens
+    const int avg = (total_rows + n_experts - 1) / n_experts;
+    bn = avg <= 32 ? 32 : (avg <= 64 ? 64 : 128);
+  }
+  if (bn % 32 || bn < 32 || bn > 128) return MB_ERR_SHAPE;
+  Params p;
+  p.Y = static_cast<__nv_bfloat16*>(Y);
+  p.R = nullptr;
+  p.sw = Ws; p.sx = Xs; p.err = err;
+  p.M = total_rows; p.N = N; p.K = K; p.ldy = N; p.ldr = N; p.sw_ld = (K + 127) / 128; p.BN = bn;
+  const int stage_bytes = kATile + bn * kBKBytes;
+  const int max_stages = (227 * 1024 - 1024 - 8 * kStgWarp - static_cast<int>(sizeof(Tail)) - 256) / stage_bytes;
+  if (stages <= 0 || stages > max_stages) stages = max_stages;
+  if (stages > 8) stages = 8;
+  p.stages = stages;
+  p.splits = 1;
+  p.kb_per_split = (K + 127) / 128;
+  p.partial = nullptr;
+  p.expert_offsets = expert_offsets;
+  p.w_rows = N;
+  p.sw_rows = N / 128;
+  CUtensorMap tw, tx;
+  int rc = cached_tmap(&tw, Wq, static_cast<uint64_t>(n_experts) * N, K, K, kBM, 1);
+  if (rc != MB_OK) return rc;
+  rc = cached_tmap(&tx, Xq, total_rows, K, ldx, bn, 1);
+  if (rc != MB_OK) return rc;
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + 8 * kStgWarp + sizeof(Tail) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    configured = true;
+  }
+  dim3 grid((max_rows + bn - 1) / bn, N / kBM, n_experts);
+  gemm_fp8_kernel<false><<<grid, kThreads, smem, stream>>>(tw, tx, p);
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }

@@ -92,51 +92,118 @@ argmax_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   if (threadIdx.x == 0) out[blockIdx.x] = a.i;
 }
 
-// Largest key t in [lo, hi] with measure{ i : fkey(x_i) >= t } >= target, where the measure is a count
-// (MASS = false) or the softmax mass exp(x_i - mx) (MASS = true). Sixteen-way search: every pass over the row
-// evaluates fifteen thresholds at once (per-thread bucket accumulators, one block reduction), so the 32-bit
-// key space is resolved in eight passes instead of thirty-two. Requires measure(key >= lo) >= target.
-template <bool MASS>
-__device__ uint32_t multiway_threshold(const float* __restrict__ row, int vocab, float invT, float mx,
-                                       uint32_t lo, uint32_t hi, float target, float* sh_acc /* [32][16] */) {
+// ---- threshold search for the top-k / top-p filters
+// Wanted: the largest key t with measure{ i : fkey(x_i) >= t } >= target, where the measure is a count
+// (MASS = false) or the softmax mass exp(x_i - mx) (MASS = true). The search keeps an interval [lo, hi]
+// that holds t and `above` = measure{ key > hi }. One sixteen-way pass evaluates fifteen thresholds at
+// once (per-thread bucket accumulators, one block reduction) and shrinks the interval sixteen-fold. A pass
+// over the whole row costs about 70 instructions per element, so before every such pass the elements that
+// still lie inside [lo, hi] are collected into shared memory; as soon as they fit (they do after one or
+// two passes for any peaked distribution) the rest of the search runs on that list alone.
+constexpr int kListPerWarp = 256;
+
+struct SearchSmem {
+  float list[(kSampThreads / 32) * kListPerWarp];   // per warp, in index order: x_i / T of the candidates
+  float acc[(kSampThreads / 32) * 16];
+  int wcnt[kSampThreads / 32];
+  int over;
+};
+
+// Per warp (warp w scans its own contiguous share of the row): x / T of the elements with key in [lo, hi].
+// Returns false if some warp found more than it can hold.
+__device__ bool compact_range(const float* __restrict__ row, int vocab, float invT, uint32_t lo, uint32_t hi,
+                              SearchSmem* sm) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  while (lo < hi) {
-    const uint32_t width = (hi - lo) / 16u + 1u;   // bucket j = [lo + j*width, lo + (j+1)*width); 16 cover [lo, hi]
-    float acc[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      const float x = row[i] * invT;
+  if (threadIdx.x == 0) sm->over = 0;
+  __syncthreads();
+  const int seg = (((vocab + 31) / 32) + 31) & ~31;
+  const int beg = warp * seg;
+  const int end = beg + seg < vocab ? beg + seg : vocab;
+  int cnt = 0;   // warp-uniform
+  for (int i0 = beg; i0 < end && cnt <= kListPerWarp; i0 += 32) {
+    const int i = i0 + lane;
+    bool in = false;
+    float x = 0.f;
+    if (i < end) {
+      x = row[i] * invT;
       const uint32_t key = fkey(x);
-      if (key < lo) continue;
-      const uint32_t bq = (key - lo) / width;
-      const int b = bq > 15u ? 15 : static_cast<int>(bq);               // keys above hi count for every threshold
-      const float w = MASS ? __expf(x - mx) : 1.f;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] += (b == j) ? w : 0.f;
+      in = key >= lo && key <= hi;
     }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
-      if (lane == 0) sh_acc[warp * 16 + j] = acc[j];
+    const uint32_t m = __ballot_sync(0xffffffffu, in);
+    if (in) {
+      const int pos = cnt + __popc(m & ((1u << lane) - 1u));
+      if (pos < kListPerWarp) sm->list[warp * kListPerWarp + pos] = x;
     }
-    __syncthreads();
-    // every thread derives the same decision: suffix sums over buckets, from the top
-    float suffix = 0.f;
-    int best = 0;            // bucket 0 always qualifies (its threshold is lo itself)
-    bool found = false;
-    for (int j = 15; j >= 0; --j) {
-      float t = 0.f;
-      for (int q = 0; q < (blockDim.x >> 5); ++q) t += sh_acc[q * 16 + j];
-      suffix += t;
-      if (!found && suffix >= target) { best = j; found = true; }
+    cnt += __popc(m);
+  }
+  if (lane == 0) {
+    sm->wcnt[warp] = cnt < kListPerWarp ? cnt : kListPerWarp;
+    if (cnt > kListPerWarp) sm->over = 1;
+  }
+  __syncthreads();
+  return sm->over == 0;
+}
+
+// One sixteen-way pass over the row (LIST = false) or over the collected candidates (LIST = true).
+template <bool MASS, bool LIST>
+__device__ void multiway_pass(const float* __restrict__ row, int vocab, float invT, float mx, SearchSmem* sm,
+                              uint32_t& lo, uint32_t& hi, float target, float& above) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t width = (hi - lo) / 16u + 1u;   // bucket j = [lo + j*width, lo + (j+1)*width); 16 cover [lo, hi]
+  float acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+  auto visit = [&](float x) {
+    const uint32_t key = fkey(x);
+    if (key < lo || key > hi) return;
+    const int b = static_cast<int>((key - lo) / width);
+    const float w = MASS ? __expf(x - mx) : 1.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] += (b == j) ? w : 0.f;
+  };
+  if (LIST) {
+    const int n = sm->wcnt[warp];
+    for (int q = lane; q < n; q += 32) visit(sm->list[warp * kListPerWarp + q]);
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) visit(row[i] * invT);
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    if (lane == 0) sm->acc[warp * 16 + j] = acc[j];
+  }
+  __syncthreads();
+  // every thread derives the same decision: the highest bucket whose suffix measure reaches the target
+  float run = above, above_new = 0.f;
+  int best = 0;
+  bool found = false;
+  for (int j = 15; j >= 1; --j) {
+    float t = 0.f;
+    for (int q = 0; q < (kSampThreads / 32); ++q) t += sm->acc[q * 16 + j];
+    if (!found && run + t >= target) { best = j; found = true; above_new = run; }
+    run += t;
+  }
+  if (!found) above_new = run;   // bucket 0 (its lower end is lo itself, which qualifies by the invariant)
+  __syncthreads();
+  // a qualifying bucket holds a key, so lo + best * width cannot wrap; the bucket's upper end can
+  lo += static_cast<uint32_t>(best) * width;
+  const uint64_t new_hi = static_cast<uint64_t>(lo) + width - 1;
+  hi = new_hi < hi ? static_cast<uint32_t>(new_hi) : hi;
+  above = above_new;
+}
+
+// Requires measure{ key >= lo } >= target and measure{ key > hi } == 0 on entry.
+template <bool MASS>
+__device__ uint32_t find_threshold(const float* __restrict__ row, int vocab, float invT, float mx, uint32_t lo,
+                                   uint32_t hi, float target, SearchSmem* sm) {
+  float above = 0.f;
+  while (lo < hi) {
+    if (compact_range(row, vocab, invT, lo, hi, sm)) {
+      while (lo < hi) multiway_pass<MASS, true>(row, vocab, invT, mx, sm, lo, hi, target, above);
+      return lo;
     }
-    __syncthreads();
-    // a qualifying bucket holds a key, so lo + best * width cannot wrap; the bucket's upper end can
-    lo += static_cast<uint32_t>(best) * width;
-    const uint64_t new_hi = static_cast<uint64_t>(lo) + width - 1;
-    hi = new_hi < hi ? static_cast<uint32_t>(new_hi) : hi;
+    multiway_pass<MASS, false>(row, vocab, invT, mx, sm, lo, hi, target, above);
   }
   return lo;
 }
@@ -149,7 +216,7 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   __shared__ ArgMax sh_am[32];
   __shared__ float sh_f[32];
   __shared__ float sh_scan[kSampThreads / 32];
-  __shared__ float sh_acc[(kSampThreads / 32) * 16];
+  __shared__ SearchSmem sh_search;
   __shared__ int sh_pick;
   pdl_wait();
   pdl_trigger();
@@ -190,7 +257,7 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   uint32_t thr_key = 0;  // keep x with fkey(x*invT) >= thr_key
   if (use_k) {
     // largest key t with count(key >= t) >= k
-    const uint32_t lo = multiway_threshold<false>(row, vocab, invT, mx, 0u, fkey(mx), static_cast<float>(k), sh_acc);
+    const uint32_t lo = find_threshold<false>(row, vocab, invT, mx, 0u, fkey(mx), static_cast<float>(k), &sh_search);
     thr_key = lo;
   }
   if (use_m) {
@@ -206,7 +273,7 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   if (use_p) {
     // largest key t (>= thr_key) with mass(key >= t) >= tp * Z
     const float target = tp * Z;
-    const uint32_t lo = multiway_threshold<true>(row, vocab, invT, mx, thr_key, fkey(mx), target, sh_acc);
+    const uint32_t lo = find_threshold<true>(row, vocab, invT, mx, thr_key, fkey(mx), target, &sh_search);
     thr_key = lo;
     Z = 0.f;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {

@@ -28,7 +28,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from ..nn.moe import MoE, MoEConfig
+from ..nn.moe import Fp8ExpertWeights, MoE, MoEConfig
 from ..nn.rotary_embedding import RopeScaling, cos_sin_table
 
 
@@ -249,9 +249,20 @@ class DeepseekV3Weights:
             m = p + "mlp."
             if cfg.is_moe_layer(i):
                 cat = lambda x, y: torch.cat((x, y), dim=0).contiguous()
-                gu = torch.stack([cat(W(f"{m}experts.{e}.gate_proj", False), W(f"{m}experts.{e}.up_proj", False))
-                                  for e in range(e_begin, e_end)])
-                dn = torch.stack([W(f"{m}experts.{e}.down_proj", False) for e in range(e_begin, e_end)])
+                # routed experts stay in block-scaled fp8 when the checkpoint has them so and the row counts
+                # are whole 128-row scale blocks (gate and up then stack without re-blocking)
+                ex_fp8 = (keep_fp8 and f"{m}experts.{e_begin}.gate_proj.weight_scale_inv" in sd
+                          and cfg.moe_intermediate_size % 128 == 0 and cfg.hidden_size % 128 == 0)
+                if ex_fp8:
+                    def stack8(names):
+                        parts = [[W(f"{m}experts.{e}.{n}") for n in names] for e in range(e_begin, e_end)]
+                        return Fp8ExpertWeights(torch.stack([torch.cat([p.q for p in ps]) for ps in parts]),
+                                                torch.stack([torch.cat([p.scale for p in ps]) for ps in parts]))
+                    gu, dn = stack8(("gate_proj", "up_proj")), stack8(("down_proj",))
+                else:
+                    gu = torch.stack([cat(W(f"{m}experts.{e}.gate_proj", False), W(f"{m}experts.{e}.up_proj", False))
+                                      for e in range(e_begin, e_end)])
+                    dn = torch.stack([W(f"{m}experts.{e}.down_proj", False) for e in range(e_begin, e_end)])
                 sh_gu = sh_d = None
                 if cfg.n_shared_experts:
                     sh_gu = cat(W(m + "shared_experts.gate_proj", False), W(m + "shared_experts.up_proj", False))

@@ -83,9 +83,37 @@ def route(logits, bias, cfg: MoEConfig):
     return ids, w
 
 
+class Fp8ExpertWeights:
+    """Block-scaled fp8 weights of a stack of experts: ``q`` [E, N, K] float8_e4m3fn and ``scale`` fp32
+    [E, N/128, ceil(K/128)] (the checkpoint's ``weight_scale_inv`` per 128x128 block); N % 128 == 0.
+    Reference: max/python/max/nn/moe/moe_fp8.py:48 with the fp8-blockwise strategy of quant_strategy.py."""
+
+    def __init__(self, q: torch.Tensor, scale: torch.Tensor):
+        self.q, self.scale = q.contiguous(), scale.float().contiguous()
+
+    @classmethod
+    def quantize(cls, w: torch.Tensor) -> "Fp8ExpertWeights":
+        qs = [ops.reference.quant_fp8_weight_block128(w[e]) for e in range(w.shape[0])]
+        return cls(torch.stack([q for q, _ in qs]), torch.stack([s for _, s in qs]))
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    def __getitem__(self, e):
+        """Integer: dequantised weight of expert ``e`` (reference paths). Slice: that range of experts."""
+        if isinstance(e, slice):
+            return Fp8ExpertWeights(self.q[e], self.scale[e])
+        return ops.reference.dequant_fp8_weight_block128(self.q[e], self.scale[e])
+
+    def contiguous(self):
+        return self
+
+
 class MoE:
-    """Weights: ``gate`` [E, H] router, ``w_gate_up`` [E_local, 2I, H], ``w_down`` [E_local, H, I],
-    optional shared experts fused as one MLP (``shared_gate_up`` [2 I_s, H], ``shared_down`` [H, I_s])."""
+    """Weights: ``gate`` [E, H] router, ``w_gate_up`` [E_local, 2I, H], ``w_down`` [E_local, H, I] (bf16
+    tensors or :class:`Fp8ExpertWeights`), optional shared experts fused as one MLP (``shared_gate_up``
+    [2 I_s, H], ``shared_down`` [H, I_s])."""
 
     def __init__(self, cfg: MoEConfig, gate, w_gate_up, w_down, e_score_bias=None, shared_gate_up=None,
                  shared_down=None, e_begin: int = 0, e_end: Optional[int] = None):
@@ -133,13 +161,37 @@ class MoE:
         n_local = offsets[E:E + 1]
         xp = torch.empty(T * k, cfg.hidden_size, dtype=x.dtype, device=dev)
         L.moe_permute_rows(x, order, n_local, xp, k)
-        act = torch.empty(T * k, cfg.moe_intermediate_size, dtype=x.dtype, device=dev)
-        L.grouped_gemm_bf16(xp, self.w_gate_up, act, offsets, T * k, True, 0)
-        out = torch.empty(T * k, cfg.hidden_size, dtype=x.dtype, device=dev)
-        L.grouped_gemm_bf16(act, self.w_down, out, offsets, T * k, False, 0)
+        out = self.local_gemms(xp, offsets)
         y = torch.empty(T, cfg.hidden_size, dtype=x.dtype, device=dev)
         L.moe_combine(out, inverse, w, shared_out, y, k)
         return y
+
+    def local_gemms(self, xp, offsets, act=None, out=None):
+        """Both grouped GEMMs of the local experts on rows already in expert order (``offsets`` int32
+        [E_local + 1]). ``xp``: bf16 rows, or ``(xq, xs)`` = e4m3 rows [n, H] (any row stride) with fp32
+        scales [H/128, n] for fp8 experts that receive quantised rows. Returns bf16 [n, H]."""
+        cfg, L = self.cfg, _lib()
+        fp8_in = isinstance(xp, tuple)
+        n = (xp[0] if fp8_in else xp).shape[0]
+        dev = (xp[0] if fp8_in else xp).device
+        if out is None:
+            out = torch.empty(n, cfg.hidden_size, dtype=torch.bfloat16, device=dev)
+        if isinstance(self.w_gate_up, Fp8ExpertWeights):
+            # quantise per 1x128 group, grouped block-scaled GEMM, SwiGLU, quantise again, second grouped
+            # GEMM (rows past the local count hold garbage that is never read back)
+            xq, xs = xp if fp8_in else ops.quant_fp8_group128(xp)
+            gu = torch.empty(n, 2 * cfg.moe_intermediate_size, dtype=torch.bfloat16, device=dev)
+            L.grouped_gemm_fp8(xq, xs, self.w_gate_up.q, self.w_gate_up.scale, gu, offsets, n, 0)
+            aq, a_s = ops.quant_fp8_group128(ops.silu_mul(gu))
+            L.grouped_gemm_fp8(aq, a_s, self.w_down.q, self.w_down.scale, out, offsets, n, 0)
+            return out
+        if fp8_in:
+            raise ValueError("quantised rows need fp8 expert weights")
+        if act is None:
+            act = torch.empty(n, cfg.moe_intermediate_size, dtype=xp.dtype, device=dev)
+        L.grouped_gemm_bf16(xp, self.w_gate_up, act, offsets, n, True, 0)
+        L.grouped_gemm_bf16(act, self.w_down, out, offsets, n, False, 0)
+        return out
 
     def _experts_ref(self, x, ids, w, shared_out=None):
         cfg = self.cfg

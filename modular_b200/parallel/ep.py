@@ -25,7 +25,7 @@ import torch
 import torch.distributed as dist
 
 from .._native import lib as _lib
-from ..nn.moe import MoE, MoEConfig, route
+from ..nn.moe import Fp8ExpertWeights, MoE, MoEConfig, route
 from .tp import TPContext
 
 
@@ -64,8 +64,10 @@ class EPContext:
         ctx.barrier()   # flags are zero everywhere before the first kernel signals a peer
 
     # ------------------------------------------------------------------ stages
-    def dispatch(self, x: torch.Tensor, ids: torch.Tensor):
-        """Push rows to their owners. Returns (rows in local-expert order, offsets [E_local+1])."""
+    def dispatch(self, x: torch.Tensor, ids: torch.Tensor, keep_fp8: bool = False):
+        """Push rows to their owners. Returns (rows in local-expert order, offsets [E_local+1], send_pos).
+        With fp8 dispatch and ``keep_fp8`` the rows stay quantised: ``(xq e4m3 [n, H] strided, xs fp32
+        [H/128, n])``, the operand form of the block-scaled grouped GEMM."""
         L, W = _lib(), self.world
         T = x.shape[0]
         assert T <= self.max_tokens and ids.shape[1] == self.top_k
@@ -80,6 +82,10 @@ class EPContext:
         if self.fp8:
             L.moe_permute_rows(self.recv_x.tensor.view(W * self.cap, self.row_bytes), self.order, n_rows,
                                self.xq, 1)
+            if keep_fp8:
+                xq = self.xq[:, : self.hidden].view(torch.float8_e4m3fn)
+                xs = self.xq[:, self.hidden:].view(torch.float32).t().contiguous()
+                return (xq, xs), self.offsets, send_pos
             L.ep_dequant_rows(self.xq, self.xp, W * self.cap, n_rows)
         else:
             L.moe_permute_rows(self.recv_x.tensor.view(torch.bfloat16).view(W * self.cap, self.hidden),
@@ -125,13 +131,14 @@ class EPMoE:
         if not x.is_cuda:
             return self._forward_host(x, ids, w, shared)
         ep, L = self.ep, _lib()
-        xp, offsets, send_pos = ep.dispatch(x, ids)
-        n = xp.shape[0]
-        if self._act is None:
-            self._act = torch.empty(n, cfg.moe_intermediate_size, dtype=x.dtype, device=x.device)
+        fp8_experts = isinstance(moe.w_gate_up, Fp8ExpertWeights)
+        xp, offsets, send_pos = ep.dispatch(x, ids, keep_fp8=fp8_experts)
+        n = (xp[0] if isinstance(xp, tuple) else xp).shape[0]
+        if self._out is None:
+            self._act = (None if fp8_experts else
+                         torch.empty(n, cfg.moe_intermediate_size, dtype=x.dtype, device=x.device))
             self._out = torch.empty(n, cfg.hidden_size, dtype=x.dtype, device=x.device)
-        L.grouped_gemm_bf16(xp, moe.w_gate_up, self._act, offsets, n, True, 0)
-        L.grouped_gemm_bf16(self._act, moe.w_down, self._out, offsets, n, False, 0)
+        moe.local_gemms(xp, offsets, self._act, self._out)
         return ep.combine(self._out, ids, send_pos, w.contiguous(), shared)
 
     __call__ = forward

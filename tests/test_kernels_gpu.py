@@ -290,3 +290,39 @@ def test_gemm_fp8_blockscaled_split_k_matches_single_pass():
         ys = ops.linear_fp8_blockscaled(xq, xs, wq, ws, residual=r, splits=splits)
         assert _rel_err(ys, y1) < 3e-3, splits
     assert _rel_err(y1, ref.linear_fp8_blockscaled(xq, xs, wq, ws, r)) < 5e-3
+
+
+def test_grouped_gemm_fp8_and_fp8_experts():
+    """Grouped block-scaled fp8 GEMM against per-expert references, and a MoE layer with fp8 expert weights
+    against the same layer with those weights dequantised to bf16."""
+    from modular_b200._native import lib
+    from modular_b200.nn.moe import Fp8ExpertWeights, MoE, MoEConfig
+
+    torch.manual_seed(23)
+    E, N, K = 5, 256, 512
+    counts = [40, 0, 130, 1, 64]
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    rows = sum(counts)
+    x = torch.randn(rows + 7, K, device=DEV, dtype=torch.bfloat16)        # trailing rows belong to no expert
+    w = (torch.randn(E, N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    fw = Fp8ExpertWeights.quantize(w)
+    xq, xs = ops.quant_fp8_group128(x)
+    y = torch.zeros(rows + 7, N, device=DEV, dtype=torch.bfloat16)
+    lib().grouped_gemm_fp8(xq, xs, fw.q, fw.scale, y, offsets, rows + 7, 0)
+    for e in range(E):
+        a, b = int(offsets[e]), int(offsets[e + 1])
+        if b > a:
+            # same quantised operands: xs is K-group-major over all rows
+            yr = ref.linear_fp8_blockscaled(xq[a:b], xs[:, a:b].contiguous(), fw.q[e], fw.scale[e])
+            assert _rel_err(y[a:b], yr) < 5e-3, e
+    assert torch.all(y[rows:] == 0)
+
+    cfg = MoEConfig(hidden_size=512, moe_intermediate_size=256, n_routed_experts=8, num_experts_per_tok=2,
+                    n_shared_experts=1, n_group=4, topk_group=2, routed_scaling_factor=2.5)
+    moe = MoE.random_init(cfg, DEV, torch.bfloat16, seed=5, std=0.05)
+    gu8, dn8 = Fp8ExpertWeights.quantize(moe.w_gate_up), Fp8ExpertWeights.quantize(moe.w_down)
+    deq = lambda f: torch.stack([f[e] for e in range(f.shape[0])]).to(torch.bfloat16)
+    moe_bf16 = MoE(cfg, moe.gate, deq(gu8), deq(dn8), moe.bias, moe.shared_gate_up, moe.shared_down)
+    moe_fp8 = MoE(cfg, moe.gate, gu8, dn8, moe.bias, moe.shared_gate_up, moe.shared_down)
+    xt = torch.randn(77, 512, device=DEV, dtype=torch.bfloat16)
+    assert _rel_err(moe_fp8(xt), moe_bf16(xt)) < 4e-2      # activations are quantised to fp8 on the fp8 path
