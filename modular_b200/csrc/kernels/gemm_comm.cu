@@ -121,39 +121,42 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       if (!ready && lane == 0) *abort_word = 301;
     }
     if (lane == 0 && ready) {
+      int s = 0;       // stage and phase are carried: no division on the pipeline's latency path
+      uint32_t ph = 0;
       for (int it = 0; it < k_iters; ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
         if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, err, 302)) break;
         uint8_t* sa = smem + s * stage_bytes;
-        mbar_arrive_expect_tx(&tail->full[s], stage_bytes);
+        uint64_t* full_s = &tail->full[s];
+        mbar_arrive_expect_tx(full_s, stage_bytes);
         const int kc = k_begin + it * kBK;
-        tma_load_2d(sa, &tmW, &tail->full[s], kc, n0);
-        if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, &tail->full[s], kc, dual_rows + n0);
-        tma_load_2d(sa + a_bytes, &tmX, &tail->full[s], kc, t0);
+        tma_load_2d(sa, &tmW, full_s, kc, n0);
+        if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, full_s, kc, dual_rows + n0);
+        tma_load_2d(sa + a_bytes, &tmX, full_s, kc, t0);
+        if (++s == stages) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(kBM, BN, 1, 1);
+      const uint64_t da0_first = umma_desc_sw128(smem);
+      const uint64_t d_a1 = static_cast<uint64_t>(kATileBytes >> 4), d_b = static_cast<uint64_t>(a_bytes >> 4);
+      const uint64_t d_stage = static_cast<uint64_t>(stage_bytes >> 4);
+      uint64_t da0 = da0_first;
+      int s = 0;
+      uint32_t ph = 0;
       for (int it = 0; it < k_iters; ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
         if (!mbar_wait(&tail->full[s], ph, abort_word, err, 303)) break;
         tc_fence_after();
-        uint8_t* sa = smem + s * stage_bytes;
-        const uint64_t da0 = umma_desc_sw128(sa);
-        const uint64_t da1 = umma_desc_sw128(sa + kATileBytes);
-        const uint64_t db = umma_desc_sw128(sa + a_bytes);
 #pragma unroll
         for (int k = 0; k < kBK / kUmmaK; ++k) {
           const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
           const uint64_t koff = static_cast<uint64_t>(k * kUmmaK * 2 >> 4);
-          umma_bf16(tmem_base, da0 + koff, db + koff, idesc, acc);
-          if (DUAL) umma_bf16(tmem_base + BN, da1 + koff, db + koff, idesc, acc);
+          umma_bf16(tmem_base, da0 + koff, da0 + d_b + koff, idesc, acc);
+          if (DUAL) umma_bf16(tmem_base + BN, da0 + d_a1 + koff, da0 + d_b + koff, idesc, acc);
         }
         tc_commit(&tail->empty[s]);
+        if (++s == stages) { s = 0; ph ^= 1; da0 = da0_first; } else { da0 += d_stage; }
       }
       tc_commit(&tail->tmem_full);
     }

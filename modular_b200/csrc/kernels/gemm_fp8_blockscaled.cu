@@ -129,9 +129,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < kb_total; ++kb) {
-        const int s = kb % p.stages;
-        const uint32_t ph = (kb / p.stages) & 1;
+      int s = 0;       // stage and phase are carried: no division on the pipeline's latency path
+      uint32_t ph = 0;
+      for (int kb = 0; kb < kb_total; ++kb, s = (s + 1 == p.stages ? 0 : s + 1), ph ^= (s == 0)) {
         if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, p.err, 501)) break;
         uint8_t* sa = smem + s * stage_bytes;
         mbar_arrive_expect_tx(&tail->full[s], stage_bytes);
@@ -142,9 +142,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(kBM, p.BN, 0, 0);  // e4m3 x e4m3 -> fp32
-      for (int kb = 0; kb < kb_total; ++kb) {
-        const int s = kb % p.stages;
-        const uint32_t ph = (kb / p.stages) & 1;
+      int s = 0;
+      uint32_t ph = 0;
+      for (int kb = 0; kb < kb_total; ++kb, s = (s + 1 == p.stages ? 0 : s + 1), ph ^= (s == 0)) {
         const int buf = kb % kAccBufs;
         const uint32_t bph = (kb / kAccBufs) & 1;
         if (!mbar_wait(&tail->acc_empty[buf], bph ^ 1, abort_word, p.err, 502)) break;

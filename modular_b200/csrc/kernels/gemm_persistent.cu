@@ -214,7 +214,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
     if (lane == 0) {
       SegIter it(p, g, G);
       Seg s;
-      int n = 0;
+      // stage index and phase are carried (no division per K block): this loop and the MMA loop are on the
+      // latency path of the pipeline
+      int st = 0;
+      uint32_t ph = 0;
       bool ok = true;
       while (ok && it.next(s)) {
         const int n0 = (s.tile / p.m_tiles) * kBM;
@@ -227,23 +230,23 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
           asm volatile("fence.proxy.async;" ::: "memory");  // TMA reads after the acquire
           if (!ok) { *abort_word = 205; break; }
         }
-        for (int kbi = s.kb0; kbi < s.kb1; ++kbi, ++n) {
-          const int st = n % p.stages;
-          const uint32_t ph = (n / p.stages) & 1;
+        for (int kbi = s.kb0; kbi < s.kb1; ++kbi) {
           if (!mbar_wait(&tail->empty[st], ph ^ 1, abort_word, p.err, 201)) { ok = false; break; }
           uint8_t* sa = smem + st * stage_bytes;
-          mbar_arrive_expect_tx(&tail->full[st], stage_bytes);
+          uint64_t* full_st = &tail->full[st];
+          mbar_arrive_expect_tx(full_st, stage_bytes);
           const int kc = kbi * kBK;
+          if (++st == p.stages) { st = 0; ph ^= 1; }
           if (p.packed_kb > 0) {
-            tma_load_2d(sa, &tmW, &tail->full[st], 0, ((n0 >> 7) * p.packed_kb + kbi) << 7);
+            tma_load_2d(sa, &tmW, full_st, 0, ((n0 >> 7) * p.packed_kb + kbi) << 7);
             if (DUAL)
-              tma_load_2d(sa + kATile, &tmW, &tail->full[st], 0,
+              tma_load_2d(sa + kATile, &tmW, full_st, 0,
                           (((p.dual_rows + n0) >> 7) * p.packed_kb + kbi) << 7);
           } else {
-            tma_load_2d(sa, &tmW, &tail->full[st], kc, n0);
-            if (DUAL) tma_load_2d(sa + kATile, &tmW, &tail->full[st], kc, p.dual_rows + n0);
+            tma_load_2d(sa, &tmW, full_st, kc, n0);
+            if (DUAL) tma_load_2d(sa + kATile, &tmW, full_st, kc, p.dual_rows + n0);
           }
-          tma_load_2d(sa + a_bytes, &tmX, &tail->full[st], kc, t0);
+          tma_load_2d(sa + a_bytes, &tmX, full_st, kc, t0);
         }
       }
     }
@@ -252,7 +255,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
       const uint32_t idesc = umma_idesc(kBM, p.BN, 1, 1);
       SegIter it(p, g, G);
       Seg s;
-      int n = 0;
+      // descriptors advance by one stage per K block (the address field counts 16-byte units)
+      const uint64_t da0_first = umma_desc_sw128(smem);
+      const uint64_t d_a1 = static_cast<uint64_t>(kATile >> 4), d_b = static_cast<uint64_t>(a_bytes >> 4);
+      const uint64_t d_stage = static_cast<uint64_t>(stage_bytes >> 4);
+      uint64_t da0 = da0_first;
+      int st = 0;
+      uint32_t ph = 0;
       bool ok = true;
       while (ok && it.next(s)) {
         const int buf = s.idx % p.nbufs;
@@ -260,23 +269,18 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
         if (!mbar_wait(&tail->tmem_empty[buf], bph ^ 1, abort_word, p.err, 202)) break;
         tc_fence_after();
         const uint32_t acc = tmem_base + buf * p.acc_cols;
-        for (int kbi = s.kb0; kbi < s.kb1; ++kbi, ++n) {
-          const int st = n % p.stages;
-          const uint32_t ph = (n / p.stages) & 1;
+        for (int kbi = s.kb0; kbi < s.kb1; ++kbi) {
           if (!mbar_wait(&tail->full[st], ph, abort_word, p.err, 203)) { ok = false; break; }
           tc_fence_after();
-          uint8_t* sa = smem + st * stage_bytes;
-          const uint64_t da0 = umma_desc_sw128(sa);
-          const uint64_t da1 = umma_desc_sw128(sa + kATile);
-          const uint64_t db = umma_desc_sw128(sa + a_bytes);
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             const uint32_t accum = (kbi > s.kb0 || k > 0) ? 1u : 0u;
             const uint64_t koff = static_cast<uint64_t>(k * kUmmaK * 2 >> 4);
-            umma_bf16(acc, da0 + koff, db + koff, idesc, accum);
-            if (DUAL) umma_bf16(acc + p.BN, da1 + koff, db + koff, idesc, accum);
+            umma_bf16(acc, da0 + koff, da0 + d_b + koff, idesc, accum);
+            if (DUAL) umma_bf16(acc + p.BN, da0 + d_a1 + koff, da0 + d_b + koff, idesc, accum);
           }
           tc_commit(&tail->empty[st]);
+          if (++st == p.stages) { st = 0; ph ^= 1; da0 = da0_first; } else { da0 += d_stage; }
         }
         if (ok) tc_commit(&tail->tmem_full[buf]);
       }

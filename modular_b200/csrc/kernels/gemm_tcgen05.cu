@@ -211,27 +211,31 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       if (!ready && lane == 0) *abort_word = 105;
     }
     if (lane == 0 && ready) {
+      // the stage index and phase are carried, not divided out of `it`: this loop and the MMA loop below sit
+      // on the latency path of the pipeline (a stage is refilled only after both have turned around)
+      int s = 0;
+      uint32_t ph = 0;
       for (int it = 0; it < k_iters; ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
         if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, err, 101)) break;
         uint8_t* sa = smem + s * stage_bytes;
         uint8_t* sb = sa + a_bytes;
-        mbar_arrive_expect_tx(&tail->full[s], stage_bytes);
+        uint64_t* full_s = &tail->full[s];
+        mbar_arrive_expect_tx(full_s, stage_bytes);
         const int kc = k_begin + it * kBK;
+        if (++s == stages) { s = 0; ph ^= 1; }
         if (packed_kb > 0) {
           // pre-tiled weights: tile (row block, K block) is one contiguous 16 KiB run in memory,
           // addressed as 128 rows of the [tiles * 128, 64] view
           const int kb = kc / kBK;
-          tma_load_2d(sa, &tmW, &tail->full[s], 0, (((w_row0 + n0) >> 7) * packed_kb + kb) << 7);
+          tma_load_2d(sa, &tmW, full_s, 0, (((w_row0 + n0) >> 7) * packed_kb + kb) << 7);
           if (DUAL)
-            tma_load_2d(sa + kATileBytes, &tmW, &tail->full[s], 0,
+            tma_load_2d(sa + kATileBytes, &tmW, full_s, 0,
                         (((w_row0 + dual_rows + n0) >> 7) * packed_kb + kb) << 7);
         } else {
-          tma_load_2d(sa, &tmW, &tail->full[s], kc, w_row0 + n0);
-          if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, &tail->full[s], kc, w_row0 + dual_rows + n0);
+          tma_load_2d(sa, &tmW, full_s, kc, w_row0 + n0);
+          if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, full_s, kc, w_row0 + dual_rows + n0);
         }
-        tma_load_2d(sb, &tmX, &tail->full[s], kc, t0);
+        tma_load_2d(sb, &tmX, full_s, kc, t0);
       }
     }
   } else if (warp == 1) {
@@ -239,24 +243,26 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(kBM, BN, 1, 1);
       bool ok = true;
+      // descriptors advance by one stage per iteration (the address field counts 16-byte units)
+      const uint64_t da0_first = umma_desc_sw128(smem);
+      const uint64_t d_a1 = static_cast<uint64_t>(kATileBytes >> 4), d_b = static_cast<uint64_t>(a_bytes >> 4);
+      const uint64_t d_stage = static_cast<uint64_t>(stage_bytes >> 4);
+      uint64_t da0 = da0_first;
+      int s = 0;
+      uint32_t ph = 0;
       for (int it = 0; it < k_iters && ok; ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
         ok = mbar_wait(&tail->full[s], ph, abort_word, err, 102);
         if (!ok) break;
         tc_fence_after();
-        uint8_t* sa = smem + s * stage_bytes;
-        const uint64_t da0 = umma_desc_sw128(sa);
-        const uint64_t da1 = umma_desc_sw128(sa + kATileBytes);
-        const uint64_t db = umma_desc_sw128(sa + a_bytes);
 #pragma unroll
         for (int k = 0; k < kBK / kUmmaK; ++k) {
           const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
           const uint64_t koff = static_cast<uint64_t>(k * kUmmaK * 2 >> 4);
-          umma_bf16(tmem_base, da0 + koff, db + koff, idesc, acc);
-          if (DUAL) umma_bf16(tmem_base + BN, da1 + koff, db + koff, idesc, acc);
+          umma_bf16(tmem_base, da0 + koff, da0 + d_b + koff, idesc, acc);
+          if (DUAL) umma_bf16(tmem_base + BN, da0 + d_a1 + koff, da0 + d_b + koff, idesc, acc);
         }
         tc_commit(&tail->empty[s]);  // frees the smem stage when these MMAs retire
+        if (++s == stages) { s = 0; ph ^= 1; da0 = da0_first; } else { da0 += d_stage; }
       }
       tc_commit(&tail->tmem_full);
     }
@@ -358,15 +364,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       if (!ready && lane == 0) *abort_word = 115;
     }
     if (lane == 0 && ready) {
+      int s = 0;
+      uint32_t ph = 0;
       for (int it = 0; it < k_iters; ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
         if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, err, 111)) break;
         uint8_t* sa = smem + s * stage_bytes;
         uint8_t* sb = sa + a_bytes;
         if (rank == 0) mbar_arrive_expect_tx(&tail->full[s], 2 * stage_bytes);
         const uint32_t full_leader = mapa_shared(&tail->full[s], 0);
         const int kc = k_begin + it * kBK;
+        if (++s == stages) { s = 0; ph ^= 1; }
         if (packed_kb > 0) {
           const int kb = kc / kBK;
           tma_load_2d_pair(sa, &tmW, full_leader, 0, ((n0 >> 7) * packed_kb + kb) << 7);
@@ -385,25 +392,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc(2 * kBM, BN, 1, 1);
       bool ok = true;
+      const uint64_t da0_first = umma_desc_sw128(smem);
+      const uint64_t d_a1 = static_cast<uint64_t>(kATileBytes >> 4), d_b = static_cast<uint64_t>(a_bytes >> 4);
+      const uint64_t d_stage = static_cast<uint64_t>(stage_bytes >> 4);
+      const uint32_t empty0 = mapa_shared(&tail->empty[0], 0), empty1 = mapa_shared(&tail->empty[0], 1);
+      uint64_t da0 = da0_first;
+      int s = 0;
+      uint32_t ph = 0;
       for (int it = 0; it < k_iters && ok; ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
         ok = mbar_wait(&tail->full[s], ph, abort_word, err, 112);
         if (!ok) break;
         tc_fence_after();
-        uint8_t* sa = smem + s * stage_bytes;
-        const uint64_t da0 = umma_desc_sw128(sa);
-        const uint64_t da1 = umma_desc_sw128(sa + kATileBytes);
-        const uint64_t db = umma_desc_sw128(sa + a_bytes);
 #pragma unroll
         for (int k = 0; k < kBK / kUmmaK; ++k) {
           const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
           const uint64_t koff = static_cast<uint64_t>(k * kUmmaK * 2 >> 4);
-          umma_bf16_pair(tmem_base, da0 + koff, db + koff, idesc, acc);
-          if (DUAL) umma_bf16_pair(tmem_base + BN, da1 + koff, db + koff, idesc, acc);
+          umma_bf16_pair(tmem_base, da0 + koff, da0 + d_b + koff, idesc, acc);
+          if (DUAL) umma_bf16_pair(tmem_base + BN, da0 + d_a1 + koff, da0 + d_b + koff, idesc, acc);
         }
-        tc_commit_pair(mapa_shared(&tail->empty[s], 0));
-        tc_commit_pair(mapa_shared(&tail->empty[s], 1));
+        tc_commit_pair(empty0 + 8u * s);   // mbarriers are 8 bytes apart, at the same offset in both CTAs
+        tc_commit_pair(empty1 + 8u * s);
+        if (++s == stages) { s = 0; ph ^= 1; da0 = da0_first; } else { da0 += d_stage; }
       }
       tc_commit_pair(mapa_shared(&tail->tmem_full, 0));
       tc_commit_pair(mapa_shared(&tail->tmem_full, 1));

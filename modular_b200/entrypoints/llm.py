@@ -59,7 +59,8 @@ class LLM:
                  device_graph_capture: bool = True, graph_batch_sizes: Optional[Sequence[int]] = None,
                  eos_token_ids: Sequence[int] = (), seed: int = 0, tp_size: int = 1,
                  tp_rank: int = 0, host_kvcache_swap_space_gb: float = 0.0,
-                 disk_kvcache_dir: Optional[str] = None, disk_kvcache_space_gb: float = 0.0):
+                 disk_kvcache_dir: Optional[str] = None, disk_kvcache_space_gb: float = 0.0,
+                 step_token_alignment: Optional[int] = None):
         from ..models import family_for
 
         fam = family_for(model_config)
@@ -123,7 +124,10 @@ class LLM:
             max_batch_size=max_batch_size, target_tokens_per_batch_ce=max_batch_input_tokens,
             max_seq_len=max_length, enable_chunked_prefill=enable_chunked_prefill,
             enable_in_flight_batching=enable_in_flight_batching,
-            kv_lookahead_tokens=1 if overlap else 0)
+            kv_lookahead_tokens=1 if overlap else 0,
+            # on the GPU, steps that would overshoot a multiple of 1024 tokens by a few are trimmed to it (whole
+            # waves of GEMM tiles, see ActiveTokenBudget)
+            step_token_alignment=(1024 if on_gpu else 0) if step_token_alignment is None else step_token_alignment)
         self.scheduler = TokenGenerationScheduler(self.sched_config, self.pipeline, self.kv)
         self.eos_token_ids = tuple(eos_token_ids)
         self._records: dict[str, RequestRecord] = {}

@@ -206,7 +206,7 @@ class TextBatchConstructor:
         cfg = self.config
         batch = SchedulerBatch()
         budget = ActiveTokenBudget(cfg.target_tokens_per_batch_ce, cfg.enable_chunked_prefill,
-                                   cfg.chunked_prefill_min_chunk_size)
+                                   cfg.chunked_prefill_min_chunk_size, cfg.step_token_alignment)
         total = TotalContextTokenBudget(cfg.max_batch_total_tokens,
                                         self.kv.page_size if self.kv is not None else 1)
         if cfg.enable_in_flight_batching:

@@ -13,6 +13,7 @@ class TokenGenerationSchedulerConfig:
     max_batch_total_tokens: int = 0            # cap on resident context tokens (0 = unlimited)
     enable_chunked_prefill: bool = True
     chunked_prefill_min_chunk_size: int = 16
+    step_token_alignment: int = 0              # trim prompt chunks so steps land on multiples of this (0 = off)
     enable_in_flight_batching: bool = False    # mix CE chunks into TG steps
     max_pending_requests: int = 0              # requests drained from the queue per iteration (0 = all)
     tg_priority_kv_percentage: float = 0.90    # above this KV usage decode goes first

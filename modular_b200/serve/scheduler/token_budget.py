@@ -18,11 +18,19 @@ class BudgetStatus(enum.Enum):
 
 
 class ActiveTokenBudget:
-    def __init__(self, capacity: int, allow_chunking: bool = True, min_chunk: int = 1):
+    """``align`` > 0 makes steps land on whole multiples of ``align`` tokens when they would otherwise
+    overshoot one by less than ``align // 4``: a prompt chunk that would bring a step to 1088 tokens is cut
+    so the step has 1024 and the 64 left over ride along with the next step. The GEMMs tile tokens in
+    blocks of up to 256 and weight rows in blocks of 128; with 32 weight-row blocks (N = 4096) a step of
+    1024 tokens is 128 CTAs - one wave on 148 SMs - while 1088 tokens need 160 CTAs and a second, almost
+    empty wave that nearly doubles the time of those GEMMs."""
+
+    def __init__(self, capacity: int, allow_chunking: bool = True, min_chunk: int = 1, align: int = 0):
         self.capacity = capacity
         self.used = 0
         self.allow_chunking = allow_chunking
         self.min_chunk = max(1, min_chunk)
+        self.align = max(0, align)
 
     @property
     def remaining(self) -> int:
@@ -35,6 +43,14 @@ class ActiveTokenBudget:
         if rem <= 0:
             return BudgetStatus.BUDGET_EXHAUSTED
         if n <= rem:
+            if self.align and self.allow_chunking:
+                total = self.used + n
+                over = total % self.align
+                keep = n - over                      # lands the step on a multiple of `align`
+                if total > self.align and 0 < over < self.align // 4 and keep >= self.min_chunk:
+                    ctx.tokens.chunk(keep)
+                    self.used += ctx.tokens.active_length
+                    return BudgetStatus.BUDGET_REACHED
             self.used += n
             return BudgetStatus.BUDGET_REACHED if self.used == self.capacity else BudgetStatus.BUDGET_AVAILABLE
         if not self.allow_chunking or rem < min(self.min_chunk, n):

@@ -222,3 +222,34 @@ def test_data_parallel_replicas_share_the_load():
         assert len(stats) == 2 and all(s["steps"] > 0 for s in stats)
         assert c.app.state.proxy.assigned == [3, 3]
         assert c.post("/reset_prefix_cache").json() == {"success": False}
+
+
+def test_step_token_alignment_trims_overshoot():
+    """A prompt chunk that would push a step slightly past a multiple of the alignment is cut to land on it."""
+    import numpy as np
+    from modular_b200.pipelines.context import SamplingParams, TextContext
+    from modular_b200.serve.scheduler.token_budget import ActiveTokenBudget, BudgetStatus
+
+    def ctx(n):
+        return TextContext.from_prompt(np.arange(n, dtype=np.int64) % 100, 8192, f"r{n}", SamplingParams(), ())
+
+    b = ActiveTokenBudget(2176, True, 16, align=1024)
+    b.used = 64                                   # decode tokens already in the step
+    c = ctx(1024)
+    assert b.status_after_context(c) is BudgetStatus.BUDGET_REACHED
+    assert c.tokens.active_length == 960 and b.used == 1024
+    # far from a boundary: untouched
+    b2 = ActiveTokenBudget(2176, True, 16, align=1024)
+    b2.used = 64
+    c2 = ctx(500)
+    assert b2.status_after_context(c2) is BudgetStatus.BUDGET_AVAILABLE and c2.tokens.active_length == 500
+    # large overshoot (more than a quarter of the alignment): untouched
+    b3 = ActiveTokenBudget(4096, True, 16, align=1024)
+    b3.used = 64
+    c3 = ctx(1400)
+    assert b3.status_after_context(c3) is BudgetStatus.BUDGET_AVAILABLE and c3.tokens.active_length == 1400
+    # alignment off
+    b4 = ActiveTokenBudget(2176, True, 16)
+    b4.used = 64
+    c4 = ctx(1024)
+    assert b4.status_after_context(c4) is BudgetStatus.BUDGET_AVAILABLE and c4.tokens.active_length == 1024
