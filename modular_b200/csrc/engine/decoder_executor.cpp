@@ -57,7 +57,7 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
     if (c.gemm_impl == 2) {
       const int tiles = ((N + 127) / 128) * ((M + 255) / 256);
       persistent = (flags & 1) || tiles >= 4 * c.num_sms;
-      mode = 0;
+      mode = -1;   // the kernel picks whole tiles or whole tiles + a stream-K remainder
     }
     if (mb_gemm_pair_wanted(M, flags & 1)) {
       const bool ws_ok = static_cast<size_t>(8) * M * N * sizeof(float) <= buf.workspace_bytes;
@@ -199,7 +199,7 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
     if ((flags & 1) && buf.p_ws != nullptr) {
       launches += 1;
       return mb_gemm_bf16_persistent_gated(xn, Wt, Y, nullptr, T, N, c.hidden, c.hidden, c.hidden, ldy, ldy,
-                                           flags, 0, 0, 0, buf.p_ws, buf.p_counters, buf.err, c.num_sms, gate,
+                                           flags, 0, 0, -1, buf.p_ws, buf.p_counters, buf.err, c.num_sms, gate,
                                            rows_per_rank, W, stream);
     }
     int bn, splits, stages;

@@ -532,7 +532,23 @@ extern "C" int mb_gemm_bf16_persistent_gated(const void* X, const void* W, void*
   if (num_sms <= 0) num_sms = 148;
   const int max_bn = 256;
   if (bn <= 0) {
-    const int mt = (M + max_bn - 1) / max_bn;
+    int mt = (M + max_bn - 1) / max_bn;
+    if (dual) {
+      // Token-tile count for the fused SwiGLU GEMM in whole-tile rounds: every CTA runs ceil(tiles / SMs)
+      // tiles, and a tile of `b` tokens costs about (89 + b) units on B200 (fit to 61 us at b = 256 and
+      // 55.5 us at b = 224 with K = 4096), so a slightly narrower tile wins when it saves nothing in rounds
+      // but shortens each one (1024 tokens: 5 x 208 instead of 4 x 256, both four rounds on 148 SMs).
+      const int n_t = (N + kBM - 1) / kBM;
+      long best_cost = -1;
+      int best_mt = mt;
+      for (int c = mt; c <= mt + 2; ++c) {
+        const int b = ((M + c - 1) / c + 15) / 16 * 16;
+        const long rounds = (static_cast<long>(c) * n_t + num_sms - 1) / num_sms;
+        const long cost = rounds * (89 + b);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_mt = c; }
+      }
+      mt = best_mt;
+    }
     bn = ((M + mt - 1) / mt + 15) / 16 * 16;
   }
   if (bn % 16 || bn < 16 || bn > max_bn) return MB_ERR_SHAPE;
@@ -557,12 +573,15 @@ extern "C" int mb_gemm_bf16_persistent_gated(const void* X, const void* W, void*
   const int n_tiles = (N + kBM - 1) / kBM;
   p.tiles = p.m_tiles * n_tiles;
   p.kb = (K + kBK - 1) / kBK;
-  // mode 2: whole waves round robin, the remainder stream-K; with many waves the remainder is
-  // not worth a fix-up pass.
-  int mode = p.tiles >= 8 * num_sms ? 0 : 2;
+  // Default schedule: whole tiles round robin (mode 0). The stream-K remainder (mode 2) and pure stream-K
+  // (mode 1) measured slower on B200 for every Llama shape, small remainders included (M = 1024 SwiGLU:
+  // 245 us in whole tiles, 365 us with the 4 left-over tiles cut stream-K), so they run only when forced.
+  int mode = 0;
   p.dbg = force_mode >= 0 ? (force_mode >> 4) & 3 : 0;
   if (force_mode >= 0 && (force_mode & 15) <= 2) mode = force_mode & 15;
-  const bool sk_ok = ws != nullptr && counters != nullptr;
+  // the workspace holds two 256-column fp32 slots per CTA: wider accumulators (SwiGLU with more than 128
+  // tokens per tile) cannot take part in a stream-K fix-up
+  const bool sk_ok = ws != nullptr && counters != nullptr && p.acc_cols <= 256;
   if (!sk_ok) mode = 0;
   int grid = num_sms;
   if (mode == 0) {

@@ -626,10 +626,25 @@ using namespace mb;
 extern "C" void mb_gemm_bf16_plan(int M, int N, int K, int dual, int num_sms, int* bn_out,
                                   int* splits_out, int* stages_out) {
   const int max_bn = dual ? 128 : 256;
-  const int m_tiles = (M + max_bn - 1) / max_bn;
+  const int n_tiles = (N + kBM - 1) / kBM;
+  int m_tiles = (M + max_bn - 1) / max_bn;
+  if (!dual && n_tiles * m_tiles > num_sms) {
+    // More CTAs than SMs: every SM runs ceil(CTAs / SMs) tiles one after the other, and a tile of `b`
+    // tokens costs about (128 + b) units (its bytes per K block). A narrower tile that needs no extra round
+    // is cheaper: 1024 tokens x 48 weight tiles run as 6 x 176 (288 CTAs, two rounds) instead of 4 x 256
+    // (192 CTAs, also two rounds).
+    long best_cost = -1;
+    int best = m_tiles;
+    for (int c = m_tiles; c <= m_tiles + 2; ++c) {
+      const int b = ((M + c - 1) / c + 15) / 16 * 16;
+      const long rounds = (static_cast<long>(c) * n_tiles + num_sms - 1) / num_sms;
+      const long cost = rounds * (128 + b);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = c; }
+    }
+    m_tiles = best;
+  }
   int bn = ((M + m_tiles - 1) / m_tiles + 15) / 16 * 16;
   if (bn < 16) bn = 16;
-  const int n_tiles = (N + kBM - 1) / kBM;
   int splits = 1;
   const int ctas = n_tiles * m_tiles;
   if (!dual && ctas * 2 <= num_sms) {
@@ -769,7 +784,19 @@ extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const vo
   if (dual && f32) return MB_ERR_SHAPE;
   if (num_sms <= 0) num_sms = 148;
   if (bn <= 0) {
-    const int mt = (M + 255) / 256;
+    int mt = (M + 255) / 256;
+    const int pairs0 = (N + 2 * kBM - 1) / (2 * kBM);
+    if (!dual && 2 * pairs0 * mt > num_sms) {   // same rounds x tile-cost choice as the one-CTA plan
+      long best_cost = -1;
+      int best = mt;
+      for (int c = mt; c <= mt + 2; ++c) {
+        const int b = ((M + c - 1) / c + 31) / 32 * 32;
+        const long rounds = (2L * c * pairs0 + num_sms - 1) / num_sms;
+        const long cost = rounds * (128 + b / 2);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = c; }
+      }
+      mt = best;
+    }
     bn = ((M + mt - 1) / mt + 31) / 32 * 32;
   }
   if (bn % 32 || bn < 32 || bn > 256) return MB_ERR_SHAPE;

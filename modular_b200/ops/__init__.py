@@ -102,8 +102,6 @@ def linear_swiglu(x, w_gate_up, out=None, bn=0, stages=0, impl=None, mode=-1, pd
         _lib().gemm_bf16(x, w_gate_up, out, None, True, None, bn, 1, stages, False, True)
     elif sel in ("persistent", "auto"):
         ws, counters = persistent_gemm_workspace(x.device)
-        if sel == "auto" and mode < 0:
-            mode = 0  # whole tiles, no stream-K fix-up: the measured best for the fused SwiGLU GEMM
         _lib().gemm_bf16_persistent(x, w_gate_up, out, None, True, ws, counters, bn, stages, mode, pdl)
     else:
         _lib().gemm_bf16(x, w_gate_up, out, None, True, None, bn, 1, stages)

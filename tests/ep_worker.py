@@ -17,7 +17,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def main():
     backend = sys.argv[1]
-    fp8 = len(sys.argv) > 2 and sys.argv[2] == "fp8"
+    fp8 = len(sys.argv) > 2 and sys.argv[2] in ("fp8", "fp8experts")
+    fp8_experts = len(sys.argv) > 2 and sys.argv[2] == "fp8experts"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     from modular_b200.nn.moe import MoE, MoEConfig
     from modular_b200.parallel.ep import EPContext, EPMoE, shard_moe
@@ -35,6 +36,11 @@ def main():
     cfg = MoEConfig(hidden_size=512, moe_intermediate_size=256, n_routed_experts=16, num_experts_per_tok=4,
                     n_shared_experts=1, n_group=4, topk_group=2, routed_scaling_factor=2.5)
     full = MoE.random_init(cfg, dev, torch.bfloat16, seed=3, std=0.05)
+    if fp8_experts:
+        # block-scaled fp8 expert weights: the dispatched rows stay quantised and feed the grouped fp8 GEMM
+        from modular_b200.nn.moe import Fp8ExpertWeights
+        full = MoE(cfg, full.gate, Fp8ExpertWeights.quantize(full.w_gate_up), Fp8ExpertWeights.quantize(full.w_down),
+                   full.bias, full.shared_gate_up, full.shared_down)
     mine = shard_moe(full, rank, world)
     ep = None
     if backend == "nccl":

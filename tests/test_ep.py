@@ -33,12 +33,12 @@ def test_ep_host_exchange_matches_full_layer():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("world,mode", [(2, "bf16"), (2, "fp8"), (4, "bf16"), (2, "deepseek")])
+@pytest.mark.parametrize("world,mode", [(2, "bf16"), (2, "fp8"), (2, "fp8experts"), (4, "bf16"), (2, "deepseek")])
 def test_ep_kernels_match_full_layer(world, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     res = _run(world, "nccl", *([mode] if mode != "bf16" else []), port=29620 + world)
-    tol = 6e-2 if mode == "fp8" else 3e-2
+    tol = 6e-2 if mode in ("fp8", "fp8experts") else 3e-2
     for r in res:
         assert r["dropped"] == 0
         assert max(r["errs"]) < tol, r
