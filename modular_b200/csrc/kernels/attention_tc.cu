@@ -166,13 +166,19 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmKV);
+      // pages are walked (no division) and the next block-table entry is loaded ahead of the wait for a free
+      // stage: this loop is on the latency path of the KV ring
+      int page_i = 0, page_off = 0;
+      int32_t page_next = ntiles > 0 ? bt[0] : 0;
+      const long long head_row = static_cast<long long>(kvh) * p.page_size;
       for (int t = 0; t < ntiles; ++t) {
         const int s = t % kStages;
         const uint32_t ph = (t / kStages) & 1;
+        const long long row = static_cast<long long>(page_next) * p.page_rows + head_row + page_off;
+        page_off += 64;
+        if (page_off == p.page_size) { page_off = 0; ++page_i; }
+        if (t + 1 < ntiles && page_off == 0) page_next = bt[page_i];
         if (!mbar_wait(&bars->kv_empty[s], ph ^ 1, abort_word, p.err, 701)) break;
-        const int tok0 = t * 64;
-        const long long row = static_cast<long long>(bt[tok0 / p.page_size]) * p.page_rows +
-                              static_cast<long long>(kvh) * p.page_size + (tok0 % p.page_size);
         uint8_t* dK = sKV + s * kStageBytes;
         uint8_t* dV = dK + kTileBytes;
         mbar_arrive_expect_tx(&bars->kv_full[s], kStageBytes);

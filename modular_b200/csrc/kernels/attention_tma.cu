@@ -31,7 +31,8 @@ namespace mb {
 namespace at2 {
 
 typedef __nv_bfloat16 bf16;
-constexpr int kStages = 3;
+constexpr int kStages = 3;          // ring depth of the mixed launch (and the size of the barrier arrays)
+constexpr int kStagesDecode = 2;    // decode-only launch: 2 stages and <= 136 registers, three CTAs per SM
 constexpr int kThreads = 160;  // 4 compute warps + 1 producer warp
 
 struct Params {
@@ -166,8 +167,10 @@ __device__ __forceinline__ void process_block(const bf16* tK, const bf16* tV, in
   }
 }
 
-template <int HD, int G>
-__global__ void __launch_bounds__(kThreads)
+// STAGES / MINB: ring depth and CTAs per SM the kernel is compiled for. The decode path is bound by the latency
+// of each warp's ldmatrix -> mma -> softmax -> mma chain, so more resident warps matter more than ring depth.
+template <int HD, int G, int STAGES, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
 attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
   constexpr int CH = HD / 8, KS = HD / 16, DT = HD / 8;
   constexpr int kTileElems = 64 * HD;          // one K (or V) tile
@@ -176,7 +179,7 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   bf16* sKV = reinterpret_cast<bf16*>(smem);                       // [stages][K tile | V tile]
-  bf16* sQ = sKV + kStages * 2 * kTileElems;                        // [64][HD]
+  bf16* sQ = sKV + STAGES * 2 * kTileElems;                         // [64][HD]
   Bars* bars = reinterpret_cast<Bars*>(sQ + p.q_rows_alloc * HD);   // Q region: 64 rows (prefill) or 16 (decode-only launch)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kvh = blockIdx.y;
@@ -196,7 +199,7 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
   const int ntiles = (kv_hi + 63) / 64;
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 4);
     }
@@ -210,13 +213,19 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       tma_prefetch_desc(&tmKV);
-      for (int t = 0; t < ntiles; ++t) {
-        const int s = t % kStages;
-        const uint32_t ph = (t / kStages) & 1;
+      // This loop is on the latency path of the ring: the page index is walked (no division) and the block
+      // table entry of the next tile is loaded before the wait for a free stage, so its latency hides there.
+      int s = 0;
+      uint32_t ph = 0;
+      int page_i = 0, page_off = 0;
+      int32_t page_next = ntiles > 0 ? bt[0] : 0;
+      const long long head_row = static_cast<long long>(kvh) * p.page_size;
+      for (int t = 0; t < ntiles; ++t, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
+        const long long row = static_cast<long long>(page_next) * p.page_rows + head_row + page_off;
+        page_off += 64;
+        if (page_off == p.page_size) { page_off = 0; ++page_i; }
+        if (t + 1 < ntiles && page_off == 0) page_next = bt[page_i];
         if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_word, p.err, 301)) break;
-        const int tok0 = t * 64;
-        const long long row = static_cast<long long>(bt[tok0 / p.page_size]) * p.page_rows +
-                              static_cast<long long>(kvh) * p.page_size + (tok0 % p.page_size);
         bf16* dK = sKV + s * 2 * kTileElems;
         bf16* dV = dK + kTileElems;
         mbar_arrive_expect_tx(&bars->full[s], kStageBytes);
@@ -260,9 +269,9 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
     const int tq = tq0 + r / G;
     limit[h] = tq < ql ? kl - ql + tq : -1;
   }
-  for (int t = 0; t < ntiles; ++t) {
-    const int s = t % kStages;
-    const uint32_t ph = (t / kStages) & 1;
+  int s = 0;
+  uint32_t ph = 0;
+  for (int t = 0; t < ntiles; ++t, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
     if (!mbar_wait(&bars->full[s], ph, abort_word, p.err, 302)) break;
     const bf16* tK = sKV + s * 2 * kTileElems;
     const bf16* tV = tK + kTileElems;
@@ -348,14 +357,14 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
   }
 }
 
-template <int HD, int G>
+template <int HD, int G, int STAGES, int MINB>
 static int launch_one(const CUtensorMap& tm, Params p, int n_ctas, int n_kv, int q_rows, cudaStream_t stream) {
-  const size_t smem_max = static_cast<size_t>(kStages) * 2 * 64 * HD * 2 + 64 * HD * 2 + sizeof(Bars) + 1024;
-  const size_t smem = static_cast<size_t>(kStages) * 2 * 64 * HD * 2 + static_cast<size_t>(q_rows) * HD * 2 +
+  const size_t smem = static_cast<size_t>(STAGES) * 2 * 64 * HD * 2 + static_cast<size_t>(q_rows) * HD * 2 +
                       sizeof(Bars) + 1024;
-  auto kern = attn_tma_kernel<HD, G>;
+  auto kern = attn_tma_kernel<HD, G, STAGES, MINB>;
   static bool configured = false;
   if (!configured) {
+    const size_t smem_max = static_cast<size_t>(STAGES) * 2 * 64 * HD * 2 + 64 * HD * 2 + sizeof(Bars) + 1024;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_max)) !=
         cudaSuccess)
       return MB_ERR_LAUNCH;
@@ -366,14 +375,21 @@ static int launch_one(const CUtensorMap& tm, Params p, int n_ctas, int n_kv, int
   return MB_OK;
 }
 
-// One launch covers prefill tiles and decode sequences. A decode-only step (the common serving case)
-// reserves shared memory for 16 query rows instead of 64, which lets two CTAs share an SM.
+// Decode-only launches may run the 2-stage / three-CTAs-per-SM build (switch below). Off by default: on B200
+// it measured 83 us against 70 us for the three-stage / two-CTAs-per-SM build (64 sequences x 1152 tokens) -
+// the depth of the TMA ring matters more than the number of resident warps.
+static int g_decode_dense = 0;
+
+// One launch covers prefill tiles and decode sequences. A decode-only step reserves shared memory for 16
+// query rows instead of 64, so two CTAs (eight compute warps, six 32 KiB stages in flight) share an SM.
 template <int HD, int G>
 static int launch(const CUtensorMap& tm, const Params& p, int n_decode, int n_kv, const int32_t* decode_seq,
                   cudaStream_t stream) {
   (void)decode_seq;
   const int nd = n_decode < 0 ? 0 : n_decode;
-  return launch_one<HD, G>(tm, p, p.n_tiles + nd, n_kv, p.n_tiles > 0 ? 64 : 16, stream);
+  if (p.n_tiles == 0 && g_decode_dense && HD == 128)
+    return launch_one<HD, G, kStagesDecode, 3>(tm, p, nd, n_kv, 16, stream);
+  return launch_one<HD, G, kStages, 2>(tm, p, p.n_tiles + nd, n_kv, p.n_tiles > 0 ? 64 : 16, stream);
 }
 
 }  // namespace at2
@@ -385,6 +401,8 @@ using namespace mb;
 // tiles (0 = never). Small prefill chunks next to many decode rows are cheaper in this file's single
 // combined launch; measured crossover on B200: about 32 tiles (512 tokens at 4 query heads per KV head).
 static int g_attn_tc_min_tiles = 0;
+// 1: decode-only launches use the denser build; 0 (default): the three-stage build for every launch
+extern "C" void mb_set_attn_decode_dense(int on) { mb::at2::g_decode_dense = on; }
 extern "C" void mb_set_attn_tc(int min_tiles) { g_attn_tc_min_tiles = min_tiles < 0 ? 0 : min_tiles; }
 extern "C" int mb_get_attn_tc(void) { return g_attn_tc_min_tiles; }
 
