@@ -184,6 +184,9 @@ def bench_misc(results):
     qs, ql, kl = i32(list(range(B))), i32([1] * B), i32([ctx] * B)
     t = time_fn(lambda: ops.mla_paged_attention(q_lat, q_rope, cache, bt, qs, ql, kl, 0.1))
     rec("mla_decode", t, B * ctx * (R + 64) * 2, 2.0 * B * h * ctx * (2 * R + 64), batch=B, ctx=ctx, heads=h)
+    t = time_fn(lambda: ops.mla_paged_attention(q_lat, q_rope, cache, bt, qs, ql, kl, 0.1, decode_only=False))
+    rec("mla_decode_mma_sync", t, B * ctx * (R + 64) * 2, 2.0 * B * h * ctx * (2 * R + 64), batch=B, ctx=ctx,
+        heads=h)
     # router (DeepSeek-V3: 256 experts, 8 groups, top-4 groups, top-8 experts)
     cfg = MoEConfig(7168, 2048, 256, 8, 1, 8, 4, True, 2.5, "sigmoid")
     logits = torch.randn(512, 256, device=dev)

@@ -775,19 +775,32 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("mla_paged_attention", [](const Tensor& q_lat, const Tensor& q_rope, const Tensor& cache,
                                   const Tensor& block_table, const Tensor& q_start, const Tensor& q_len,
-                                  const Tensor& kv_len, Tensor& out, double scale) {
+                                  const Tensor& kv_len, Tensor& out, double scale, bool decode_only) {
     need_cuda(q_lat, "q_lat");
     TORCH_CHECK(q_lat.is_contiguous() && q_rope.is_contiguous() && out.is_contiguous() && q_rope.size(2) == 64 &&
                     cache.stride(2) == 1 && cache.stride(1) == cache.size(2) &&
                     cache.size(2) == q_lat.size(2) + 64 && block_table.stride(1) == 1,
                 "mla_paged_attention layout");
+    // decode_only: the caller knows that every sequence has exactly one query token
+    if (decode_only && mb_mla_tc_usable(q_lat.size(0), block_table.size(0), q_lat.size(1), q_lat.size(2),
+                                        cache.size(1))) {
+      check_rc(mb_mla_decode_tc(q_lat.data_ptr(), q_rope.data_ptr(), out.data_ptr(), cache.data_ptr(),
+                                cache.stride(0), cache.size(0), block_table.data_ptr<int32_t>(),
+                                block_table.stride(0), q_start.data_ptr<int32_t>(), q_len.data_ptr<int32_t>(),
+                                kv_len.data_ptr<int32_t>(), q_lat.size(0), block_table.size(0), q_lat.size(1),
+                                cache.size(1), scale, error_flag(), cur_stream()),
+               "mla_decode_tc");
+      return;
+    }
     check_rc(mb_mla_paged_attention(q_lat.data_ptr(), q_rope.data_ptr(), out.data_ptr(), cache.data_ptr(),
                                     cache.stride(0), block_table.data_ptr<int32_t>(), block_table.stride(0),
                                     q_start.data_ptr<int32_t>(), q_len.data_ptr<int32_t>(),
                                     kv_len.data_ptr<int32_t>(), q_lat.size(0), block_table.size(0),
                                     q_lat.size(1), q_lat.size(2), cache.size(1), scale, cur_stream()),
              "mla_paged_attention");
-  });
+  }, py::arg("q_lat"), py::arg("q_rope"), py::arg("cache"), py::arg("block_table"), py::arg("q_start"),
+     py::arg("q_len"), py::arg("kv_len"), py::arg("out"), py::arg("scale"), py::arg("decode_only") = false);
+  m.def("set_mla_tc", [](bool on) { mb_set_mla_tc(on ? 1 : 0); }, py::arg("on"));
   // ---- expert parallelism ----
   m.def("ep_flag_ints", []() { return mb_ep_flag_ints(); });
   m.def("ep_dispatch", [](int world, int rank, const std::vector<int64_t>& recv_x,

@@ -116,6 +116,13 @@ void mb_set_attn_tc(int min_tiles);
 int mb_get_attn_tc(void);
 
 // ---- multi-head latent attention over a paged latent cache (mla.cu) ------------------------
+// Decode steps (one query token per sequence) of absorbed MLA on tcgen05 (mla_tc.cu).
+void mb_set_mla_tc(int on);
+int mb_mla_tc_usable(int T, int B, int n_heads, int R, int page_size);
+int mb_mla_decode_tc(const void* q_lat, const void* q_rope, void* out, const void* cache, long long page_stride,
+                     long long n_pages, const int32_t* block_table, int bt_stride, const int32_t* q_start,
+                     const int32_t* q_len, const int32_t* kv_len, int T, int B, int n_heads, int page_size,
+                     float scale, int* err, cudaStream_t stream);
 int mb_mla_paged_attention(const void* q_lat, const void* q_rope, void* out, const void* cache,
                            long long page_stride, const int32_t* block_table, int bt_stride,
                            const int32_t* q_start, const int32_t* q_len, const int32_t* kv_len, int T,

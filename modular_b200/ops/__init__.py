@@ -299,11 +299,19 @@ def mla_kv_store(c_kv, k_rope, slots, cache):
     ref.mla_kv_store(c_kv, k_rope, slots, cache)
 
 
-def mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, scale, plan=None):
-    """Absorbed-form multi-head latent attention over a paged latent cache; returns [T, h, R]."""
+def mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, scale, plan=None,
+                        decode_only=None):
+    """Absorbed-form multi-head latent attention over a paged latent cache; returns [T, h, R].
+
+    ``decode_only``: every sequence has exactly one query token (then 512-wide latents with a multiple of 128
+    heads run on the tcgen05 kernel). ``None`` infers it from ``T == number of sequences``: schedulers never
+    put a sequence without query tokens into a batch."""
     if q_lat.is_cuda and q_lat.dtype == torch.bfloat16 and hasattr(_lib(), "mla_paged_attention"):
         out = torch.empty_like(q_lat)
-        _lib().mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, out, scale)
+        if decode_only is None:
+            decode_only = q_lat.shape[0] == block_table.shape[0]
+        _lib().mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, out, scale,
+                                   bool(decode_only))
         return out
     return ref.mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, scale)
 

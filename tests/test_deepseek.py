@@ -203,3 +203,40 @@ def test_engine_serves_deepseek_on_gpu():
     # bf16 batches of different shapes may flip a late near-tie; the first tokens must agree
     assert all(a[:2] == b[:2] for a, b in zip(got, solo))
     ops.check_device_error()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("h,page,kv_lens", [(128, 64, [1, 64, 65, 130, 700]), (256, 128, [1152, 33, 1280]),
+                                            (128, 128, [3000])])
+def test_mla_decode_tcgen05_matches_reference(h, page, kv_lens):
+    """Decode step (one query token per sequence) on the tcgen05 kernel, against the fp32 reference and the
+    mma.sync kernel; queries scaled up so that the lazily rescaled accumulator path is exercised."""
+    dev = torch.device("cuda")
+    gen = torch.Generator().manual_seed(h + page)
+    R, B = 512, len(kv_lens)
+    n_pages_seq = [(k + page - 1) // page for k in kv_lens]
+    total_pages = sum(n_pages_seq) + 1
+    cache_full = torch.zeros(total_pages, 2, page, R + 64, dtype=torch.bfloat16, device=dev)
+    cache = cache_full[:, 1]
+    order = torch.randperm(total_pages - 1, generator=gen) + 1           # pages in random order
+    bt = torch.zeros(B, max(n_pages_seq), dtype=torch.int32, device=dev)
+    nxt = 0
+    for b, n in enumerate(n_pages_seq):
+        bt[b, :n] = order[nxt:nxt + n].to(torch.int32)
+        nxt += n
+    cache[1:] = (torch.randn(total_pages - 1, page, R + 64, generator=gen) * 0.5).to(torch.bfloat16).to(dev)
+    q_lat = (torch.randn(B, h, R, generator=gen) * 1.5).to(torch.bfloat16).to(dev)
+    q_rope = (torch.randn(B, h, 64, generator=gen) * 1.5).to(torch.bfloat16).to(dev)
+    q_start = torch.arange(B, dtype=torch.int32, device=dev)
+    q_len = torch.ones(B, dtype=torch.int32, device=dev)
+    kv_len = torch.tensor(kv_lens, dtype=torch.int32, device=dev)
+    args = (q_lat, q_rope, cache, bt, q_start, q_len, kv_len)
+    scale = 0.07
+    got = ops.mla_paged_attention(*args, scale)                          # T == B: tcgen05 kernel
+    torch.cuda.synchronize()
+    ops.check_device_error()
+    old = ops.mla_paged_attention(*args, scale, decode_only=False)       # mma.sync kernel
+    want = ops.reference.mla_paged_attention(*[a.float() if a.is_floating_point() else a for a in args], scale)
+    assert (old.float() - want).abs().max() / want.abs().max() < 2e-2
+    err = (got.float() - want).abs().max() / want.abs().max()
+    assert err < 2e-2, err
