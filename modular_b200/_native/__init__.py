@@ -51,6 +51,8 @@ def _load():
                 mod.set_gemm_pair(int(plain or 0), int(dual or 0))
             if hasattr(mod, "set_attn_decode_dense"):
                 mod.set_attn_decode_dense(os.environ.get("MB200_ATTN_DECODE_DENSE", "0") not in ("", "0"))
+            if hasattr(mod, "set_attn_fork"):
+                mod.set_attn_fork(os.environ.get("MB200_ATTN_FORK", "1") not in ("", "0"))
             if hasattr(mod, "set_mla_tc"):
                 mod.set_mla_tc(os.environ.get("MB200_MLA_TC", "1") not in ("", "0"))
             _MOD = mod

@@ -657,6 +657,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_gemm_pair", [](int min_m_plain, int min_m_dual) { mb_set_gemm_pair(min_m_plain, min_m_dual); },
         py::arg("min_m_plain"), py::arg("min_m_dual"));
   m.def("set_attn_decode_dense", [](bool on) { mb_set_attn_decode_dense(on ? 1 : 0); }, py::arg("on"));
+  m.def("set_attn_fork", [](bool on) { mb_set_attn_fork(on ? 1 : 0); }, py::arg("on"));
   m.def("set_pdl", [](bool on) { mb_set_pdl(on ? 1 : 0); });
   m.def("get_pdl", []() { return mb_get_pdl() != 0; });
   m.def("tp_flag_ints", []() { return mb_tp_flag_ints(); });

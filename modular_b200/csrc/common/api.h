@@ -21,6 +21,7 @@ extern "C" {
 // Programmatic dependent launch for the step kernels (process-wide; see common/launch.h).
 void mb_set_pdl(int on);
 void mb_set_attn_decode_dense(int on);
+void mb_set_attn_fork(int on);
 int mb_get_pdl(void);
 
 // ---- GEMM (gemm_tcgen05.cu) -------------------------------------------------------------

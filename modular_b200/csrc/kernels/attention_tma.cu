@@ -401,6 +401,9 @@ using namespace mb;
 // tiles (0 = never). Small prefill chunks next to many decode rows are cheaper in this file's single
 // combined launch; measured crossover on B200: about 32 tiles (512 tokens at 4 query heads per KV head).
 static int g_attn_tc_min_tiles = 0;
+static int g_attn_fork = 1;                 // decode launch on a side stream next to the tcgen05 prefill launch
+static cudaEvent_t g_fork_join = nullptr;
+extern "C" void mb_set_attn_fork(int on) { g_attn_fork = on; }
 // 1: decode-only launches use the denser build; 0 (default): the three-stage build for every launch
 extern "C" void mb_set_attn_decode_dense(int on) { mb::at2::g_decode_dense = on; }
 extern "C" void mb_set_attn_tc(int min_tiles) { g_attn_tc_min_tiles = min_tiles < 0 ? 0 : min_tiles; }
@@ -436,23 +439,57 @@ extern "C" int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo
   const int rc = cached_tmap(&tm, kv_base, static_cast<uint64_t>(total_rows), head_dim, head_dim, 64, 2);
   if (rc != MB_OK) return rc;
   const int G = n_q / n_kv;
+  cudaStream_t dstream = stream;   // stream of the decode launch
+  bool forked = false;
   if (g_attn_tc_min_tiles > 0 && p.n_tiles >= g_attn_tc_min_tiles && head_dim == 128 && G <= 16 &&
       (G & (G - 1)) == 0) {
-    // prefill tiles on the tcgen05 kernel, decode sequences (if any) on this file's kernel
+    // Prefill tiles on the tcgen05 kernel, decode sequences (if any) on this file's kernel. The prefill
+    // kernel takes one SM per CTA and a step's prompt chunk rarely gives it 148 CTAs, so the decode launch
+    // goes to a side stream and fills the remaining SMs at the same time (fork / join with two events; not
+    // while the stream is being captured into a graph).
+    if (n_decode > 0 && g_attn_fork) {
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
+        static cudaStream_t side = nullptr;
+        static cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+        if (side == nullptr) {
+          if (cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess ||
+              cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+              cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming) != cudaSuccess)
+            side = nullptr;
+        }
+        if (side != nullptr && cudaEventRecord(ev_fork, stream) == cudaSuccess &&
+            cudaStreamWaitEvent(side, ev_fork, 0) == cudaSuccess) {
+          dstream = side;
+          forked = true;
+          g_fork_join = ev_join;
+        }
+      }
+    }
     const int rc2 = mb_paged_attention_prefill_tc(q, ldq, out, ldo, kv_base, total_rows, k_off_rows, v_off_rows,
                                                   page_rows, block_table, bt_stride, q_start, q_len, kv_len, tile_seq,
                                                   tile_q0, p.n_tiles, n_q, n_kv, head_dim, page_size, scale, err,
                                                   stream);
-    if (rc2 != MB_OK) return rc2;
-    if (n_decode <= 0) return MB_OK;
+    if (rc2 != MB_OK && !forked) return rc2;
+    if (n_decode <= 0) return rc2;
     p.n_tiles = 0;
+    if (rc2 != MB_OK) {   // still join the side stream before reporting
+      cudaEventRecord(g_fork_join, dstream);
+      cudaStreamWaitEvent(stream, g_fork_join, 0);
+      return rc2;
+    }
   }
+  int rc3 = MB_ERR_SHAPE;
 #define MB_ATTN2_CASE(HD_, G_) \
-  if (head_dim == HD_ && G == G_) return launch<HD_, G_>(tm, p, n_decode, n_kv, decode_seq, stream);
+  if (head_dim == HD_ && G == G_) rc3 = launch<HD_, G_>(tm, p, n_decode, n_kv, decode_seq, dstream);
   MB_ATTN2_CASE(128, 1) MB_ATTN2_CASE(128, 2) MB_ATTN2_CASE(128, 4) MB_ATTN2_CASE(128, 8)
   MB_ATTN2_CASE(128, 16)
   MB_ATTN2_CASE(64, 1) MB_ATTN2_CASE(64, 2) MB_ATTN2_CASE(64, 4) MB_ATTN2_CASE(64, 8)
   MB_ATTN2_CASE(64, 16)
 #undef MB_ATTN2_CASE
-  return MB_ERR_SHAPE;
+  if (forked) {
+    if (cudaEventRecord(g_fork_join, dstream) != cudaSuccess || cudaStreamWaitEvent(stream, g_fork_join, 0) != cudaSuccess)
+      return MB_ERR_LAUNCH;
+  }
+  return rc3;
 }
