@@ -29,7 +29,7 @@ def _no_device_error():
     [(1, 128, 64), (16, 256, 128), (64, 4096, 4096), (100, 384, 520), (320, 6144, 4096),
      (257, 1000, 1024), (1024, 4096, 14336), (2048, 2048, 512)],
 )
-@pytest.mark.parametrize("impl", ["tiled", "persistent"])
+@pytest.mark.parametrize("impl", ["tiled", "persistent", "pair"])
 def test_gemm_bf16(M, N, K, impl):
     torch.manual_seed(0)
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
@@ -73,7 +73,7 @@ def test_gemm_residual_and_fp32_out():
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
     r = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
-    for impl in ("tiled", "persistent"):
+    for impl in ("tiled", "persistent", "pair"):
         y = ops.linear(x, w, residual=r, impl=impl)
         assert _rel_err(y, ref.linear(x, w, r)) < 1e-2
         # in-place residual (output aliases the residual)
@@ -88,7 +88,8 @@ def test_gemm_residual_and_fp32_out():
     assert _rel_err(y2, ref.linear(x, w, r)) < 1e-2
 
 
-@pytest.mark.parametrize("impl,mode", [("tiled", -1), ("persistent", 0), ("persistent", 1), ("persistent", 2)])
+@pytest.mark.parametrize("impl,mode", [("tiled", -1), ("persistent", 0), ("persistent", 1), ("persistent", 2),
+                                       ("pair", -1)])
 @pytest.mark.parametrize("M", [1, 48, 130, 320, 512])
 def test_gemm_swiglu(M, impl, mode):
     torch.manual_seed(3)
