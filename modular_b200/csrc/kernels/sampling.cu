@@ -82,12 +82,40 @@ __device__ __forceinline__ float block_sum_f(float v, float* sh) {
   return r;
 }
 
+// Visit every element of a row as f(value, index). Rows that start on a 16-byte boundary are read as float4 with
+// two loads in flight per thread: with one scalar load per iteration a pass over 128 k logits is bound by
+// the latency of its 125 dependent round trips (about 60 us per pass on B200), not by bandwidth.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ row, int vocab, F&& f) {
+  if ((reinterpret_cast<uintptr_t>(row) & 15) != 0) {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) f(row[i], i);
+    return;
+  }
+  const int n4 = vocab >> 2;
+  const float4* __restrict__ r4 = reinterpret_cast<const float4*>(row);
+  const int step = blockDim.x;
+  int i = threadIdx.x;
+  for (; i + step < n4; i += 2 * step) {
+    const float4 a = r4[i];
+    const float4 b = r4[i + step];
+    const int ia = i << 2, ib = (i + step) << 2;
+    f(a.x, ia); f(a.y, ia + 1); f(a.z, ia + 2); f(a.w, ia + 3);
+    f(b.x, ib); f(b.y, ib + 1); f(b.z, ib + 2); f(b.w, ib + 3);
+  }
+  for (; i < n4; i += step) {
+    const float4 a = r4[i];
+    const int ia = i << 2;
+    f(a.x, ia); f(a.y, ia + 1); f(a.z, ia + 2); f(a.w, ia + 3);
+  }
+  for (int t = (n4 << 2) + threadIdx.x; t < vocab; t += blockDim.x) f(row[t], t);
+}
+
 __global__ void __launch_bounds__(kSampThreads)
 argmax_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int vocab, int ld) {
   __shared__ ArgMax sh[32];
   const float* row = logits + static_cast<size_t>(blockIdx.x) * ld;
   ArgMax a{-FLT_MAX, 0x7fffffff};
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) a = amax2(a, ArgMax{row[i], i});
+  for_each_logit(row, vocab, [&](float v, int i) { a = amax2(a, ArgMax{v, i}); });
   a = block_argmax(a, sh);
   if (threadIdx.x == 0) out[blockIdx.x] = a.i;
 }
@@ -116,25 +144,36 @@ __device__ bool compact_range(const float* __restrict__ row, int vocab, float in
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) sm->over = 0;
   __syncthreads();
-  const int seg = (((vocab + 31) / 32) + 31) & ~31;
+  // each warp owns a contiguous share of the row (a multiple of 128 elements, so float4 loads stay aligned);
+  // candidates are appended in a fixed order (element slot of the float4, then lane), which keeps the list -
+  // and with it every later floating-point sum - the same from run to run
+  const int seg = (((vocab + 31) / 32) + 127) & ~127;
   const int beg = warp * seg;
   const int end = beg + seg < vocab ? beg + seg : vocab;
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
   int cnt = 0;   // warp-uniform
-  for (int i0 = beg; i0 < end && cnt <= kListPerWarp; i0 += 32) {
-    const int i = i0 + lane;
-    bool in = false;
-    float x = 0.f;
-    if (i < end) {
-      x = row[i] * invT;
+  for (int i0 = beg; i0 < end && cnt <= kListPerWarp; i0 += 128) {
+    const int i = i0 + 4 * lane;
+    float xv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec && i + 3 < end) {
+      const float4 q = *reinterpret_cast<const float4*>(row + i);
+      xv[0] = q.x; xv[1] = q.y; xv[2] = q.z; xv[3] = q.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) xv[e] = i + e < end ? row[i + e] : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float x = xv[e] * invT;
       const uint32_t key = fkey(x);
-      in = key >= lo && key <= hi;
+      const bool in = i + e < end && key >= lo && key <= hi;
+      const uint32_t m = __ballot_sync(0xffffffffu, in);
+      if (in) {
+        const int pos = cnt + __popc(m & ((1u << lane) - 1u));
+        if (pos < kListPerWarp) sm->list[warp * kListPerWarp + pos] = x;
+      }
+      cnt += __popc(m);
     }
-    const uint32_t m = __ballot_sync(0xffffffffu, in);
-    if (in) {
-      const int pos = cnt + __popc(m & ((1u << lane) - 1u));
-      if (pos < kListPerWarp) sm->list[warp * kListPerWarp + pos] = x;
-    }
-    cnt += __popc(m);
   }
   if (lane == 0) {
     sm->wcnt[warp] = cnt < kListPerWarp ? cnt : kListPerWarp;
@@ -169,7 +208,7 @@ __device__ void multiway_pass(const float* __restrict__ row, int vocab, float in
     const int n = sm->wcnt[warp];
     for (int q = lane; q < n; q += 32) visit(sm->list[warp * kListPerWarp + q]);
   } else {
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) visit(row[i] * invT);
+    for_each_logit(row, vocab, [&](float v, int) { visit(v * invT); });
   }
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
@@ -197,11 +236,48 @@ __device__ void multiway_pass(const float* __restrict__ row, int vocab, float in
   above = above_new;
 }
 
-// Requires measure{ key >= lo } >= target and measure{ key > hi } == 0 on entry.
+// Count (or softmax mass) of the collected candidates; every thread gets the same value.
+template <bool MASS>
+__device__ float list_measure(SearchSmem* sm, float mx) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float v = 0.f;
+  if (MASS) {
+    const int n = sm->wcnt[warp];
+    for (int q = lane; q < n; q += 32) v += __expf(sm->list[warp * kListPerWarp + q] - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  } else {
+    v = static_cast<float>(sm->wcnt[warp]);
+  }
+  __syncthreads();
+  if (lane == 0) sm->acc[warp] = v;
+  __syncthreads();
+  float tot = 0.f;
+  for (int q = 0; q < kSampThreads / 32; ++q) tot += sm->acc[q];
+  __syncthreads();
+  return tot;
+}
+
+// Requires measure{ key >= lo } >= target and measure{ key > hi } == 0 on entry (hi = key of the maximum).
 template <bool MASS>
 __device__ uint32_t find_threshold(const float* __restrict__ row, int vocab, float invT, float mx, uint32_t lo,
                                    uint32_t hi, float target, SearchSmem* sm) {
   float above = 0.f;
+  // Shortcut for the usual case that the wanted set sits within a few units below the maximum: collect the
+  // elements of a window under the maximum in one cheap pass; if they fit and already reach the target, the
+  // whole search runs on that list. Windows that hold too much (flat distributions) or too little fall
+  // through to the general search.
+  for (int wi = 0; wi < 3 && lo < hi; ++wi) {
+    const float window = wi == 0 ? 2.f : (wi == 1 ? 6.f : 12.f);
+    const uint32_t wlo = fkey(mx - window);
+    if (wlo <= lo) break;                                   // the window is the whole remaining range
+    if (!compact_range(row, vocab, invT, wlo, hi, sm)) break;   // too many candidates
+    if (list_measure<MASS>(sm, mx) >= target) {
+      lo = wlo;
+      while (lo < hi) multiway_pass<MASS, true>(row, vocab, invT, mx, sm, lo, hi, target, above);
+      return lo;
+    }
+  }
   while (lo < hi) {
     if (compact_range(row, vocab, invT, lo, hi, sm)) {
       while (lo < hi) multiway_pass<MASS, true>(row, vocab, invT, mx, sm, lo, hi, target, above);
@@ -235,7 +311,7 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   // greedy
   if (T <= 0.f || k == 1) {
     ArgMax a{-FLT_MAX, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) a = amax2(a, ArgMax{row[i], i});
+    for_each_logit(row, vocab, [&](float v, int i) { a = amax2(a, ArgMax{v, i}); });
     a = block_argmax(a, sh_am);
     if (threadIdx.x == 0) out[rowi] = a.i;
     return;
@@ -245,17 +321,17 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   if (!use_k && !use_p && !use_m) {
     // Gumbel-max: argmax(x/T + g), g = -log(-log u)
     ArgMax a{-FLT_MAX, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for_each_logit(row, vocab, [&](float v, int i) {
       const float u = uniform01(seed, step, i);
-      a = amax2(a, ArgMax{row[i] * invT - __logf(-__logf(u)), i});
-    }
+      a = amax2(a, ArgMax{v * invT - __logf(-__logf(u)), i});
+    });
     a = block_argmax(a, sh_am);
     if (threadIdx.x == 0) out[rowi] = a.i;
     return;
   }
   // max of scaled logits
   ArgMax a{-FLT_MAX, 0x7fffffff};
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) a = amax2(a, ArgMax{row[i] * invT, i});
+  for_each_logit(row, vocab, [&](float v, int i) { a = amax2(a, ArgMax{v * invT, i}); });
   a = block_argmax(a, sh_am);
   const float mx = a.v;
   uint32_t thr_key = 0;  // keep x with fkey(x*invT) >= thr_key
@@ -269,10 +345,10 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
     thr_key = max(thr_key, km);
   }
   float Z = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float x = row[i] * invT;
+  for_each_logit(row, vocab, [&](float v, int) {
+    const float x = v * invT;
     Z += fkey(x) >= thr_key ? __expf(x - mx) : 0.f;
-  }
+  });
   Z = block_sum_f(Z, sh_f);
   if (use_p) {
     // largest key t (>= thr_key) with mass(key >= t) >= tp * Z
@@ -280,10 +356,10 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
     const uint32_t lo = find_threshold<true>(row, vocab, invT, mx, thr_key, fkey(mx), target, &sh_search);
     thr_key = lo;
     Z = 0.f;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      const float x = row[i] * invT;
+    for_each_logit(row, vocab, [&](float v, int) {
+      const float x = v * invT;
       Z += fkey(x) >= thr_key ? __expf(x - mx) : 0.f;
-    }
+    });
     Z = block_sum_f(Z, sh_f);
   }
   // inverse-CDF draw over the kept set, in index order
@@ -293,14 +369,27 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
   float base = 0.f;
   int last_kept = -1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int c0 = 0; c0 < vocab; c0 += kSampThreads) {
-    const int i = c0 + threadIdx.x;
-    float w = 0.f;
-    if (i < vocab) {
-      const float x = row[i] * invT;
-      if (fkey(x) >= thr_key) w = __expf(x - mx);
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+  for (int c0 = 0; c0 < vocab; c0 += 4 * kSampThreads) {
+    // four consecutive elements per thread and iteration
+    const int i = c0 + 4 * threadIdx.x;
+    float xv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec && i + 3 < vocab) {
+      const float4 q = *reinterpret_cast<const float4*>(row + i);
+      xv[0] = q.x; xv[1] = q.y; xv[2] = q.z; xv[3] = q.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) xv[e] = i + e < vocab ? row[i + e] : 0.f;
     }
-    float incl = w;  // warp inclusive scan
+    float w[4];
+    float mine = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float x = xv[e] * invT;
+      w[e] = (i + e < vocab && fkey(x) >= thr_key) ? __expf(x - mx) : 0.f;
+      mine += w[e];
+    }
+    float incl = mine;  // warp inclusive scan of the per-thread sums
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const float t = __shfl_up_sync(0xffffffffu, incl, o);
@@ -314,9 +403,15 @@ sample_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int v
       if (q < warp) woff += t;
       total += t;
     }
-    const float cum = base + woff + incl;
-    if (w > 0.f && cum >= target && cum - w < target) atomicMax(&sh_pick, i);
-    if (w > 0.f) last_kept = i;
+    float cum = base + woff + incl - mine;   // mass before this thread's first element
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (w[e] > 0.f) {
+        if (cum + w[e] >= target && cum < target) atomicMax(&sh_pick, i + e);
+        last_kept = i + e;
+      }
+      cum += w[e];
+    }
     base += total;
     __syncthreads();
     if (sh_pick >= 0) break;
