@@ -83,7 +83,7 @@ __device__ __forceinline__ float block_sum_f(float v, float* sh) {
 }
 
 // Visit every element of a row as f(value, index). Rows that start on a 16-byte boundary are read as float4 with
-// two loads in flight per thread: with one scalar load per iteration a pass over 128 k logits is bound by
+// four loads in flight per thread: with one scalar load per iteration a pass over 128 k logits is bound by
 // the latency of its 125 dependent round trips (about 60 us per pass on B200), not by bandwidth.
 template <typename F>
 __device__ __forceinline__ void for_each_logit(const float* __restrict__ row, int vocab, F&& f) {
@@ -95,12 +95,16 @@ __device__ __forceinline__ void for_each_logit(const float* __restrict__ row, in
   const float4* __restrict__ r4 = reinterpret_cast<const float4*>(row);
   const int step = blockDim.x;
   int i = threadIdx.x;
-  for (; i + step < n4; i += 2 * step) {
+  for (; i + 3 * step < n4; i += 4 * step) {
     const float4 a = r4[i];
     const float4 b = r4[i + step];
-    const int ia = i << 2, ib = (i + step) << 2;
+    const float4 c = r4[i + 2 * step];
+    const float4 d = r4[i + 3 * step];
+    const int ia = i << 2, ib = (i + step) << 2, ic = (i + 2 * step) << 2, id = (i + 3 * step) << 2;
     f(a.x, ia); f(a.y, ia + 1); f(a.z, ia + 2); f(a.w, ia + 3);
     f(b.x, ib); f(b.y, ib + 1); f(b.z, ib + 2); f(b.w, ib + 3);
+    f(c.x, ic); f(c.y, ic + 1); f(c.z, ic + 2); f(c.w, ic + 3);
+    f(d.x, id); f(d.y, id + 1); f(d.z, id + 2); f(d.w, id + 3);
   }
   for (; i < n4; i += step) {
     const float4 a = r4[i];
