@@ -81,8 +81,13 @@ void gemm_bf16(const Tensor& x, const Tensor& w, Tensor& y, const c10::optional<
   if (workspace.has_value() && workspace->defined()) {
     ws = workspace->data_ptr();
     if (pair) {
-      // the pair kernel picks its own split count (at most 8)
-      const size_t need = static_cast<size_t>(splits > 0 ? splits : 8) * M * N * 4;
+      if (splits <= 0 && bn <= 0) {
+        int pbn;
+        mb_gemm_bf16_pair_plan(M, N, K, (dual || f32) ? 1 : 0, num_sms(), &pbn, &splits);
+      } else if (splits <= 0) {
+        splits = 1;   // explicit tile width: no automatic split
+      }
+      const size_t need = static_cast<size_t>(splits > 0 ? splits : 1) * M * N * 4;
       if (need > static_cast<size_t>(workspace->nbytes())) { ws = nullptr; splits = 1; }
     } else if (splits <= 0) {
       int pbn, psp, pst;

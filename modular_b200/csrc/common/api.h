@@ -42,6 +42,7 @@ int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const void* R, int 
                       int ldw, int ldy, int ldr, int flags, int bn, int splits, int stages, void* workspace,
                       int* err, int num_sms, const int* gate_flags, int gate_rpr, int gate_world,
                       cudaStream_t stream);
+void mb_gemm_bf16_pair_plan(int M, int N, int K, int no_split, int num_sms, int* bn_out, int* splits_out);
 void mb_set_gemm_pair(int min_m_plain, int min_m_dual);
 int mb_gemm_pair_wanted(int M, int dual);
 int mb_gemm_bf16_persistent_gated(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,

@@ -60,10 +60,12 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
       mode = -1;   // the kernel picks whole tiles or whole tiles + a stream-K remainder
     }
     if (mb_gemm_pair_wanted(M, flags & 1)) {
-      const bool ws_ok = static_cast<size_t>(8) * M * N * sizeof(float) <= buf.workspace_bytes;
-      launches += 1;
-      return mb_gemm_bf16_pair(X, W, Y, R, M, N, K, ldx, K, ldy, ldy, flags, 0, ws_ok ? 0 : 1, 0,
-                               ws_ok ? buf.workspace : nullptr, buf.err, c.num_sms, nullptr, 1, 0, stream);
+      int pbn, psp;
+      mb_gemm_bf16_pair_plan(M, N, K, (flags & 5) ? 1 : 0, c.num_sms, &pbn, &psp);
+      if (static_cast<size_t>(psp) * M * N * sizeof(float) > buf.workspace_bytes) psp = 1;
+      launches += psp > 1 ? 2 : 1;
+      return mb_gemm_bf16_pair(X, W, Y, R, M, N, K, ldx, K, ldy, ldy, flags, pbn, psp, 0, buf.workspace, buf.err,
+                               c.num_sms, nullptr, 1, 0, stream);
     }
     if (persistent && buf.p_ws != nullptr) {
       launches += 1;

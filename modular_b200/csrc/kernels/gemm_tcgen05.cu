@@ -766,6 +766,38 @@ extern "C" int mb_gemm_pair_wanted(int M, int dual) {
   return m > 0 && M >= m;
 }
 
+// Token-tile width and K splits the pair kernel picks by itself (no_split: fused SwiGLU or fp32 output).
+// Callers use it to check that their workspace holds splits * M * N floats.
+extern "C" void mb_gemm_bf16_pair_plan(int M, int N, int K, int no_split, int num_sms, int* bn_out,
+                                       int* splits_out) {
+  if (num_sms <= 0) num_sms = 148;
+  int mt = (M + 255) / 256;
+  const int pairs = (N + 2 * kBM - 1) / (2 * kBM);
+  if (!no_split && 2 * pairs * mt > num_sms) {   // same rounds x tile-cost choice as the one-CTA plan
+    long best_cost = -1;
+    int best = mt;
+    for (int c = mt; c <= mt + 2; ++c) {
+      const int b = ((M + c - 1) / c + 31) / 32 * 32;
+      const long rounds = (2L * c * pairs + num_sms - 1) / num_sms;
+      const long cost = rounds * (128 + b / 2);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = c; }
+    }
+    mt = best;
+  }
+  const int bn = ((M + mt - 1) / mt + 31) / 32 * 32;
+  const int m_tiles = (M + bn - 1) / bn;
+  const int k_blocks = (K + kBK - 1) / kBK;
+  int splits = 1;
+  const int ctas = 2 * m_tiles * pairs;
+  if (!no_split && ctas * 2 <= num_sms) {
+    splits = num_sms / ctas;
+    if (splits > k_blocks / 8) splits = k_blocks / 8 > 0 ? k_blocks / 8 : 1;
+    if (splits > 8) splits = 8;
+  }
+  *bn_out = bn;
+  *splits_out = splits;
+}
+
 // CTA-pair (cta_group::2) GEMM: same contract and flags as mb_gemm_bf16_gated. The token tile is a
 // multiple of 32 (each CTA of a pair loads half of it).
 extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,
@@ -783,35 +815,14 @@ extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const vo
     return MB_ERR_ALIGN;
   if (dual && f32) return MB_ERR_SHAPE;
   if (num_sms <= 0) num_sms = 148;
-  if (bn <= 0) {
-    int mt = (M + 255) / 256;
-    const int pairs0 = (N + 2 * kBM - 1) / (2 * kBM);
-    if (!dual && 2 * pairs0 * mt > num_sms) {   // same rounds x tile-cost choice as the one-CTA plan
-      long best_cost = -1;
-      int best = mt;
-      for (int c = mt; c <= mt + 2; ++c) {
-        const int b = ((M + c - 1) / c + 31) / 32 * 32;
-        const long rounds = (2L * c * pairs0 + num_sms - 1) / num_sms;
-        const long cost = rounds * (128 + b / 2);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = c; }
-      }
-      mt = best;
-    }
-    bn = ((M + mt - 1) / mt + 31) / 32 * 32;
+  {
+    int pbn, psp;
+    mb_gemm_bf16_pair_plan(M, N, K, (dual || f32) ? 1 : 0, num_sms, &pbn, &psp);
+    if (bn <= 0) bn = pbn;
+    if (splits <= 0) splits = (bn == pbn) ? psp : 1;
   }
   if (bn % 32 || bn < 32 || bn > 256) return MB_ERR_SHAPE;
-  const int m_tiles = (M + bn - 1) / bn;
-  const int pairs = (N + 2 * kBM - 1) / (2 * kBM);
   const int k_blocks = (K + kBK - 1) / kBK;
-  if (splits <= 0) {
-    splits = 1;
-    const int ctas = 2 * m_tiles * pairs;
-    if (!dual && !f32 && ctas * 2 <= num_sms) {
-      splits = num_sms / ctas;
-      if (splits > k_blocks / 8) splits = k_blocks / 8 > 0 ? k_blocks / 8 : 1;
-      if (splits > 8) splits = 8;
-    }
-  }
   if (splits > 1 && (workspace == nullptr || dual || f32)) splits = 1;
   const int stage_bytes = kATileBytes * (dual ? 2 : 1) + (bn / 2) * kBK * 2;
   const int max_stages = (227 * 1024 - 1024 - 4 * kStageWarpBytes - 512) / stage_bytes;
