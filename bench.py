@@ -175,8 +175,19 @@ def main() -> int:
     out_tokens = sum(len(r.tokens) for r in recs)
     assert out_tokens == args.steps * conc * args.output_len, (out_tokens,)
     times = torch.tensor([gpu_busy, wall], dtype=torch.float64, device="cuda")
+    ranks_agree = True
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        # every rank samples from the same gathered logits: the generated ids must be identical everywhere
+        import hashlib
+
+        h = hashlib.sha256()
+        for r in recs:
+            h.update(np.asarray(r.tokens, dtype=np.int64).tobytes())
+        digests = [None] * world
+        dist.all_gather_object(digests, h.hexdigest())
+        ranks_agree = all(d == digests[0] for d in digests)
+        assert ranks_agree, f"tensor-parallel ranks generated different tokens: {digests}"
     gpu_busy, wall = times.tolist()
     if rank == 0:
         ttft = sorted(r.ttft for r in recs)
@@ -210,6 +221,7 @@ def main() -> int:
                     "h2d_bytes_per_step": (st.h2d_bytes - st0[1]) / args.steps,
                     "d2h_bytes_per_step": (st.d2h_bytes - st0[2]) / args.steps},
             "gpu_launches": llm.pipeline.gpu_launches() - st0[4],
+            "ranks_agree": ranks_agree,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -92,16 +92,107 @@ def bench_gemm(shapes, results, configs=None):
     ops.check_device_error()
 
 
-def bench_attention(results):
+def bench_decode_gemm(results, tp_degrees=(1, 8)):
+    """Decode-step GEMMs (gemm_decode.cu) against the tiled kernels + stand-alone RMSNorm and against cuBLAS, per
+    shape (L2 flushed) and as the GEMM chain of a run of layers with distinct weights (weights cold, launches
+    back to back, which is what a decode step does). Shapes: Llama-3.1-8B, whole and the shard of each TP degree."""
     peaks = measured_peaks()
-    n_q, n_kv, hd, ps = 32, 8, 128, 128
-    for name, q_lens, kv_lens in [
-        ("decode_b64_ctx1152", [1] * 64, [1152] * 64),
-        ("decode_b256_ctx1152", [1] * 256, [1152] * 256),
-        ("prefill_1x1024", [1024], [1024]),
-        ("prefill_8x1024", [1024] * 8, [1024] * 8),
-        ("mixed_64dec_256pf", [1] * 64 + [256], [1152] * 64 + [768]),
+    bw = peaks["hbm_gbs"] * 1e9
+    H, I, QKV, QD = 4096, 14336, 6144, 4096
+    dev = "cuda"
+    for tp in tp_degrees:
+        shapes = [("qkv", QKV // tp, H, "plain"), ("o", H, QD // tp, "add_norm"),
+                  ("gate_up", I // tp, H, "swiglu"), ("down", H, I // tp, "add_norm")]
+        for M in (1, 16, 64, 128, 256):
+            for name, N, K, mode in shapes:
+                rows = 2 * N if mode == "swiglu" else N
+                x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+                w = (torch.randn(rows, K, device=dev) * 0.02).to(torch.bfloat16)
+                h = torch.randn(M, H, device=dev, dtype=torch.bfloat16)
+                g = torch.ones(H, device=dev, dtype=torch.bfloat16)
+                out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+                xn = torch.empty(M, H, device=dev, dtype=torch.bfloat16)
+                if mode == "plain":
+                    new = lambda: ops.linear_decode(x, w, out=out)
+                    old = lambda: ops.linear(x, w, out=out)
+                    lib = lambda: torch.matmul(x, w.t(), out=out)
+                elif mode == "swiglu":
+                    new = lambda: ops.linear_decode(x, w, mode="swiglu", out=out)
+                    old = lambda: ops.linear_swiglu(x, w, out=out)
+                    lib = lambda: ops.reference.silu_mul(x @ w.t())
+                else:
+                    new = lambda: ops.linear_decode(x, w, mode="add_norm", h=h, gamma=g, xn=xn)
+                    old = lambda: (ops.linear(x, w, residual=h, out=h), ops.rms_norm(h, g, 1e-5, out=xn))
+                    lib = lambda: (torch.addmm(h, x, w.t(), out=h), ops.rms_norm(h, g, 1e-5, out=xn))
+                t_new, t_old, t_lib = time_fn(new), time_fn(old), time_fn(lib)
+                nbytes = 2.0 * (rows * K + M * K + M * N)
+                rec = dict(kernel="gemm_decode", name=f"{name}_m{M}_tp{tp}", M=M, N=N, K=K, mode=mode, us=t_new * 1e6,
+                           tiled_us=t_old * 1e6, lib_us=t_lib * 1e6, gbs=nbytes / t_new / 1e9,
+                           frac_of_measured_roofline=nbytes / bw / t_new, speedup_vs_tiled=t_old / t_new,
+                           speedup_vs_lib=t_lib / t_new)
+                results.append(rec)
+                print(json.dumps(rec), flush=True)
+        # chain of 8 layers' GEMMs (no attention): us per layer
+        n_layers = 8
+        ws = [[(torch.randn(r, k, device=dev) * 0.02).to(torch.bfloat16)
+               for (r, k) in ((QKV // tp, H), (H, QD // tp), (2 * I // tp, H), (H, I // tp))] for _ in range(n_layers)]
+        g = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        for M in (16, 64, 128):
+            h = torch.randn(M, H, device=dev, dtype=torch.bfloat16) * 0.1
+            xn = torch.randn(M, H, device=dev, dtype=torch.bfloat16)
+            qkv = torch.empty(M, QKV // tp, device=dev, dtype=torch.bfloat16)
+            act = torch.empty(M, I // tp, device=dev, dtype=torch.bfloat16)
+
+            def chain_new():
+                for wq, wo, wg, wd in ws:
+                    ops.linear_decode(xn, wq, out=qkv)
+                    ops.linear_decode(qkv[:, :QD // tp], wo, mode="add_norm", h=h, gamma=g, xn=xn)
+                    ops.linear_decode(xn, wg, mode="swiglu", out=act)
+                    ops.linear_decode(act, wd, mode="add_norm", h=h, gamma=g, xn=xn)
+
+            def chain_old():
+                for wq, wo, wg, wd in ws:
+                    ops.rms_norm(h, g, 1e-5, out=xn)
+                    ops.linear(xn, wq, out=qkv)
+                    ops.linear(qkv[:, :QD // tp], wo, residual=h, out=h)
+                    ops.rms_norm(h, g, 1e-5, out=xn)
+                    ops.linear_swiglu(xn, wg, out=act)
+                    ops.linear(act, wd, residual=h, out=h)
+
+            res = {}
+            for label, fn in (("decode", chain_new), ("tiled", chain_old)):
+                gr = torch.cuda.CUDAGraph()
+                fn()
+                torch.cuda.synchronize()
+                with torch.cuda.graph(gr):
+                    fn()
+                res[label] = time_fn(gr.replay, flush=False) / n_layers
+            wbytes = sum(w.numel() * 2 for w in ws[0])
+            rec = dict(kernel="gemm_decode_chain", name=f"layer_gemms_m{M}_tp{tp}", M=M, us_per_layer=res["decode"] * 1e6,
+                       tiled_us_per_layer=res["tiled"] * 1e6, weight_mb=wbytes / 1e6,
+                       frac_of_measured_roofline=wbytes / bw / res["decode"], speedup_vs_tiled=res["tiled"] / res["decode"])
+            results.append(rec)
+            print(json.dumps(rec), flush=True)
+        del ws
+    torch.cuda.synchronize()
+    ops.check_device_error()
+
+
+def bench_attention(results, only=None):
+    peaks = measured_peaks()
+    hd, ps = 128, 128
+    ops.ensure_attention_split_workspace("cuda")
+    for name, q_lens, kv_lens, n_q, n_kv in [
+        ("decode_b64_ctx1152", [1] * 64, [1152] * 64, 32, 8),
+        ("decode_b64_ctx1152_tp8shard", [1] * 64, [1152] * 64, 4, 1),
+        ("decode_b256_ctx1152", [1] * 256, [1152] * 256, 32, 8),
+        ("decode_b16_ctx8192", [1] * 16, [8192] * 16, 32, 8),
+        ("prefill_1x1024", [1024], [1024], 32, 8),
+        ("prefill_8x1024", [1024] * 8, [1024] * 8, 32, 8),
+        ("mixed_64dec_256pf", [1] * 64 + [256], [1152] * 64 + [768], 32, 8),
     ]:
+        if only and name not in only:
+            continue
         B = len(q_lens)
         max_pages = max((k + ps - 1) // ps for k in kv_lens)
         n_pages = B * max_pages
@@ -121,11 +212,20 @@ def bench_attention(results):
                                              hd, 1 / math.sqrt(hd), plan=plan, out=out)
         t = time_fn(fn)
         t_old = time_fn(fn_old)
+        t_nosplit = None
+        if name.startswith("decode"):
+            ops._lib().set_attn_split(0)
+            t_nosplit = time_fn(fn)
+            ops._lib().set_attn_split(2)
+            t = time_fn(fn)
+            ops._lib().set_attn_split(1)
         kv_bytes = sum(kv_lens) * n_kv * hd * 2 * 2
         flops = sum(4.0 * n_q * hd * q_ * (k_ - q_ / 2) for q_, k_ in zip(q_lens, kv_lens))
         t_roof = max(flops / (peaks["bf16_tflops"] * 1e12), kv_bytes / (peaks["hbm_gbs"] * 1e9))
         rec = dict(kernel="paged_attention", name=name, us=t * 1e6, cp_async_us=t_old * 1e6, kv_gbs=kv_bytes / t / 1e9,
                    tflops=flops / t / 1e12, frac_of_measured_roofline=t_roof / t)
+        if t_nosplit is not None:
+            rec["one_cta_per_seq_us"] = t_nosplit * 1e6   # `us` is the split-KV kernel for the decode rows
         results.append(rec)
         print(json.dumps(rec), flush=True)
 
@@ -257,8 +357,10 @@ def main(argv=None):
             keep = set(args.only.split(","))
             shapes = [s for s in shapes if s[0] in keep]
         bench_gemm(shapes, results, cfgs)
+    if "dec" in what:
+        bench_decode_gemm(results)
     if "attn" in what:
-        bench_attention(results)
+        bench_attention(results, set(args.only.split(",")) if args.only else None)
     if "misc" in what:
         bench_misc(results)
     if args.out:

@@ -410,6 +410,8 @@ class PyDecoderExecutor {
     c.gemm_impl = cfg.contains("gemm_impl") ? cfg["gemm_impl"].cast<int>() : 0;
     c.use_pdl = cfg.contains("use_pdl") ? cfg["use_pdl"].cast<int>() : 0;
     c.attn_impl = cfg.contains("attn_impl") ? cfg["attn_impl"].cast<int>() : 1;
+    c.dec_max_tokens = cfg.contains("dec_max_tokens") ? cfg["dec_max_tokens"].cast<int>() : 0;
+    if (c.dec_max_tokens > mb_gemm_dec_max_tokens()) c.dec_max_tokens = mb_gemm_dec_max_tokens();
     ex.buf.p_ws = nullptr;
     ex.buf.p_counters = nullptr;
     c.num_sms = num_sms();
@@ -516,6 +518,20 @@ class PyDecoderExecutor {
     ex.tp.fused = fused;
     ex.tp.partial_rows = partial_rows;
   }
+  // workspace (fp32) and zeroed state words of the decode-step GEMMs
+  void set_dec(const Tensor& ws, const Tensor& state) {
+    TORCH_CHECK(state.scalar_type() == at::kInt && state.numel() >= mb_gemm_dec_state_ints(), "dec state too small");
+    ex.buf.dec_ws = const_cast<void*>(hold(ws));
+    ex.buf.dec_ws_bytes = ws.nbytes();
+    ex.buf.dec_state = static_cast<int*>(const_cast<void*>(hold(state)));
+  }
+  // receive buffers of the fused all-reduce on every rank (symmetric memory, filled with bf16 -0.0)
+  void set_tp_lamport(const std::vector<int64_t>& lam, int lam_rows) {
+    TORCH_CHECK(static_cast<int>(lam.size()) == ex.tp.world, "set_tp_lamport: one pointer per rank expected");
+    for (int i = 0; i < ex.tp.world; ++i) ex.tp.lam[i] = reinterpret_cast<void*>(lam[i]);
+    ex.tp.lam_rows = lam_rows;
+  }
+  bool dec_usable(int T) const { return ex.dec_usable(T); }
   long launches() const { return ex.launches; }
   void set_profiling(bool on) { ex.profiling = on; }
   py::list profile() {
@@ -549,6 +565,55 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("bn") = 0, py::arg("stages") = 0, py::arg("mode") = -1, py::arg("pdl") = false,
         py::arg("packed") = false);
   m.def("gemm_persistent_sizes", &gemm_persistent_sizes);
+  m.def("gemm_dec_sizes", []() {
+    return py::make_tuple(static_cast<int64_t>(mb_gemm_dec_workspace_bytes(num_sms())), mb_gemm_dec_state_ints(),
+                          mb_gemm_dec_max_tokens());
+  });
+  m.def("gemm_dec_lamport_elems", [](int world, int rows, int N) {
+    return static_cast<int64_t>(mb_gemm_dec_lamport_elems(world, rows, N));
+  });
+  m.def("set_gemm_dec_smem_kb", [](int kb) { mb_set_gemm_dec_smem_kb(kb); });
+  m.def("set_gemm_dec_trace", [](const c10::optional<Tensor>& buf) {
+    TORCH_CHECK(!buf.has_value() || (buf->is_cuda() && buf->nbytes() >= static_cast<size_t>(num_sms()) * 64), "trace buffer");
+    mb_set_gemm_dec_trace(buf.has_value() ? buf->data_ptr() : nullptr);
+  });
+  m.def("gemm_dec_plan", [](int M, int N, int K, int mode, int64_t ws_bytes) {
+    return mb_gemm_dec_plan(M, N, K, mode, static_cast<size_t>(ws_bytes), num_sms()) == MB_OK;
+  });
+  // Decode-step GEMM; see mb_gemm_dec. mode 0/1: `y` is the output; mode 2: `h` (in place) and `xn`.
+  m.def("gemm_dec", [](const Tensor& x, const Tensor& w, int mode, const c10::optional<Tensor>& y,
+                       const c10::optional<Tensor>& h, const c10::optional<Tensor>& xn,
+                       const c10::optional<Tensor>& gamma, double eps, double w_off, bool mbc, int world, int rank,
+                       const std::vector<int64_t>& lam, int lam_rows, const Tensor& ws, Tensor& state) {
+    need_cuda(x, "x"); need_cuda(w, "w");
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "gemm_dec: row-major 2-D operands");
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "gemm_dec: bf16 inputs");
+    const int M = x.size(0), K = x.size(1), N = w.size(0);
+    TORCH_CHECK(w.size(1) == K, "gemm_dec: shape mismatch");
+    TORCH_CHECK(state.scalar_type() == at::kInt && state.numel() >= mb_gemm_dec_state_ints(), "gemm_dec: state");
+    void* yp = nullptr;
+    int ldy = 0;
+    if (mode == 2) {
+      TORCH_CHECK(h.has_value() && xn.has_value() && gamma.has_value(), "gemm_dec mode 2 needs h, xn, gamma");
+      TORCH_CHECK(h->is_contiguous() && xn->is_contiguous() && h->size(0) >= M && h->size(1) == N &&
+                      xn->size(0) >= M && xn->size(1) == N && gamma->numel() == N,
+                  "gemm_dec mode 2: h / xn must be contiguous [>=M, N]");
+      TORCH_CHECK(world == 1 || static_cast<int>(lam.size()) == world, "gemm_dec: one receive buffer per rank");
+    } else {
+      TORCH_CHECK(y.has_value() && y->stride(1) == 1 && y->size(0) >= M && y->size(1) == (mode == 1 ? N / 2 : N) &&
+                      y->scalar_type() == at::kBFloat16,
+                  "gemm_dec: output shape");
+      yp = y->data_ptr();
+      ldy = y->stride(0);
+    }
+    void* lamp[8] = {};
+    for (size_t i = 0; i < lam.size() && i < 8; ++i) lamp[i] = reinterpret_cast<void*>(lam[i]);
+    check_rc(mb_gemm_dec(x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), mode, yp, ldy,
+                         const_cast<void*>(optptr(h)), const_cast<void*>(optptr(xn)), optptr(gamma),
+                         static_cast<float>(eps), static_cast<float>(w_off), mbc ? 1 : 0, world, rank, lamp, lam_rows,
+                         ws.data_ptr(), ws.nbytes(), state.data_ptr<int>(), error_flag(), num_sms(), cur_stream()),
+             "gemm_dec");
+  });
   m.def("rmsnorm", &rmsnorm);
   m.def("add_rmsnorm", &add_rmsnorm);
   m.def("silu_mul", &silu_mul);
@@ -657,6 +722,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("read_error_flag", &read_error_flag, py::arg("reset") = true);
   m.def("num_sms", &num_sms);
+  m.def("attn_split_workspace_bytes", []() { return static_cast<int64_t>(mb_attn_split_workspace_bytes(num_sms())); });
+  // partial-state workspace (fp32) and zeroed int32 counters of the split-KV decode attention; the caller keeps
+  // both tensors alive for the life of the process
+  m.def("set_attn_split_workspace", [](const Tensor& ws, const Tensor& counters) {
+    need_cuda(ws, "ws"); need_cuda(counters, "counters");
+    TORCH_CHECK(counters.scalar_type() == at::kInt && ws.is_contiguous() && counters.is_contiguous(), "workspace types");
+    mb_set_attn_split_workspace(ws.data_ptr(), ws.nbytes(), counters.data_ptr<int>(), static_cast<int>(counters.numel()));
+  });
+  // 0 = never, 1 = by the partition heuristic (few sequences x KV heads), 2 = every decode-only step
+  m.def("set_attn_split", [](int mode) { mb_set_attn_split(mode); });
   m.def("set_attn_tc", [](int min_tiles) { mb_set_attn_tc(min_tiles); });
   m.def("get_attn_tc", []() { return mb_get_attn_tc(); });
   m.def("set_gemm_pair", [](int min_m_plain, int min_m_dual) { mb_set_gemm_pair(min_m_plain, min_m_dual); },
@@ -872,6 +947,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_kv_cache", &PyDecoderExecutor::set_kv_cache)
       .def("set_buffers", &PyDecoderExecutor::set_buffers)
       .def("set_tp", &PyDecoderExecutor::set_tp)
+      .def("set_dec", &PyDecoderExecutor::set_dec)
+      .def("set_tp_lamport", &PyDecoderExecutor::set_tp_lamport)
+      .def("dec_usable", &PyDecoderExecutor::dec_usable)
       .def("forward", &PyDecoderExecutor::forward)
       .def("launches", &PyDecoderExecutor::launches)
       .def("set_profiling", &PyDecoderExecutor::set_profiling)

@@ -57,6 +57,22 @@ int mb_gemm_bf16_persistent(const void* X, const void* W, void* Y, const void* R
                             int force_mode, void* ws, int* counters, int* err, int num_sms,
                             cudaStream_t stream);
 
+// Decode-step GEMM (gemm_decode.cu): M <= 256 tokens, equal K-block shares on every SM, epilogue over the
+// whole output after one grid-wide meeting point. mode 0 bf16 store, 1 SwiGLU over W = [gate; up],
+// 2 all-reduce over `world` ranks (sentinel-polled receive buffers `lam`) + residual `h` + RMSNorm -> `xn`.
+int mb_gemm_dec_max_tokens(void);
+int mb_gemm_dec_state_ints(void);
+size_t mb_gemm_dec_workspace_bytes(int num_sms);
+size_t mb_gemm_dec_lamport_elems(int world, int rows, int N);
+void mb_set_gemm_dec_smem_kb(int kb);
+void mb_set_gemm_dec_trace(void* buf);
+// MB_OK when mb_gemm_dec takes the shape with a workspace of `ws_bytes`
+int mb_gemm_dec_plan(int M, int N, int K, int mode, size_t ws_bytes, int num_sms);
+int mb_gemm_dec(const void* X, const void* W, int M, int N, int K, int ldx, int ldw, int mode, void* Y, int ldy,
+                void* h, void* xn, const void* gamma, float eps, float w_off, int mbc, int world, int rank,
+                void* const* lam, int lam_rows, void* ws, size_t ws_bytes, int* state, int* err, int num_sms,
+                cudaStream_t stream);
+
 // ---- block-scaled fp8 (gemm_fp8_blockscaled.cu, quant_fp8.cu) ----------------------------
 int mb_quant_fp8_group128(const void* x_bf16, void* q_fp8, float* scales, int M, int K, int ldx,
                           int scale_ld, int scales_k_major, cudaStream_t stream);
@@ -103,6 +119,12 @@ int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo, const voi
                            const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, int n_decode,
                            const int32_t* decode_seq, int n_q, int n_kv, int head_dim, int page_size,
                            float scale, int* err, cudaStream_t stream);
+
+// Split-KV decode (attention_tma.cu): decode-only steps cut the KV tiles of all sequences into equal shares per
+// CTA once this process-wide workspace is set (partials + zeroed counters, one per KV head and sequence).
+size_t mb_attn_split_workspace_bytes(int num_sms);
+void mb_set_attn_split_workspace(void* ws, size_t ws_bytes, int* counters, int counter_ints);
+void mb_set_attn_split(int on);
 
 // tcgen05 prefill attention (attention_tc.cu): same addressing as mb_paged_attention_tma, head_dim 128 only.
 int mb_paged_attention_prefill_tc(const void* q, int ldq, void* out, int ldo, const void* kv_base,

@@ -11,6 +11,19 @@
 
 namespace mb {
 
+// Function attributes such as the dynamic shared-memory opt-in are per device. A launcher keeps one of these in
+// a function-local static and sets the attribute the first time it runs on each device of the process
+// (setting it twice is harmless, so no lock is taken).
+struct PerDeviceOnce {
+  bool seen[64] = {};
+  int dev = -1;
+  bool needed() {
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { dev = -1; return true; }
+    return !seen[dev];
+  }
+  void done() { if (dev >= 0) seen[dev] = true; }
+};
+
 // process-wide switch (set once by the engine; see mb_set_pdl in elementwise.cu)
 bool pdl_enabled();
 

@@ -38,7 +38,117 @@ std::vector<std::tuple<std::string, int, double>> DecoderExecutor::profile_ms() 
   return out;
 }
 
+bool DecoderExecutor::dec_usable(int T) const {
+  const DecoderConfig& c = cfg;
+  if (T <= 0 || T > c.dec_max_tokens || buf.dec_ws == nullptr || buf.dec_state == nullptr) return false;
+  if (tp.world > 1 && (tp.lam[0] == nullptr || T > tp.lam_rows)) return false;
+  const int qkv_dim = (c.n_q + 2 * c.n_kv) * c.head_dim;
+  const int q_dim = c.n_q * c.head_dim;
+  const size_t wsb = buf.dec_ws_bytes;
+  return mb_gemm_dec_plan(T, qkv_dim, c.hidden, 0, wsb, c.num_sms) == MB_OK &&
+         mb_gemm_dec_plan(T, c.hidden, q_dim, 2, wsb, c.num_sms) == MB_OK &&
+         mb_gemm_dec_plan(T, 2 * c.inter, c.hidden, c.fuse_swiglu ? 1 : 0, wsb, c.num_sms) == MB_OK &&
+         mb_gemm_dec_plan(T, c.hidden, c.inter, 2, wsb, c.num_sms) == MB_OK;
+}
+
+int DecoderExecutor::forward_dec(const StepInputs& in, cudaStream_t stream) {
+  const DecoderConfig& c = cfg;
+  const int T = in.T;
+  const int W = tp.world, R = tp.rank;
+  const int qkv_dim = (c.n_q + 2 * c.n_kv) * c.head_dim;
+  const int q_dim = c.n_q * c.head_dim;
+  auto dec = [&](const void* X, const void* Wt, int N, int K, int mode, void* Y, int ldy, const void* gamma) {
+    launches += 1;
+    return mb_gemm_dec(X, Wt, T, N, K, K, K, mode, Y, ldy, buf.h, buf.xn, gamma, c.eps, c.norm_weight_offset,
+                       c.multiply_before_cast, W, R, tp.lam, tp.lam_rows, buf.dec_ws, buf.dec_ws_bytes,
+                       buf.dec_state, buf.err, c.num_sms, stream);
+  };
+  mark("begin", stream);
+  if (in.future_src != nullptr) {
+    MB_TRY(mb_realize_future_tokens(const_cast<int64_t*>(in.tokens), in.future_src, buf.sampled, T, stream));
+    launches += 1;
+  }
+  MB_TRY(mb_embedding(in.tokens, embed, buf.h, T, c.hidden, c.vocab, 0, stream));
+  MB_TRY(mb_rmsnorm(buf.h, layers[0].attn_norm, buf.xn, T, c.hidden, c.hidden, c.hidden, c.eps,
+                    c.norm_weight_offset, c.multiply_before_cast, stream));
+  launches += 2;
+  mark("embed", stream);
+  for (int l = 0; l < c.n_layers; ++l) {
+    const DecoderLayerWeights& w = layers[l];
+    const long long hd = c.head_dim;
+    char* kbase = static_cast<char*>(kv.base) + 2 * (static_cast<int64_t>(l) * kv.layer_stride);
+    MB_TRY(dec(buf.xn, w.wqkv, qkv_dim, c.hidden, 0, buf.qkv, qkv_dim, nullptr));
+    mark("gemm_qkv", stream);
+    MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, T, c.n_q,
+                            c.n_kv, c.head_dim, c.page_size, kv.page_stride, kv.head_stride, c.rope_interleaved,
+                            stream));
+    mark("rope_kv_store", stream);
+    if (c.attn_impl == 1 && c.page_size % 64 == 0) {
+      MB_TRY(mb_paged_attention_tma(
+          buf.qkv, qkv_dim, buf.attn, q_dim, kv.base, kv.total_elems / hd,
+          static_cast<long long>(l) * kv.layer_stride / hd,
+          (static_cast<long long>(l) * kv.layer_stride + kv.kv_stride) / hd, kv.page_stride / hd, in.block_table,
+          in.bt_stride, in.q_start, in.q_len, in.kv_len, in.tile_seq, in.tile_q0, in.n_tiles, in.n_decode,
+          in.decode_seq, c.n_q, c.n_kv, c.head_dim, c.page_size, c.attn_scale, buf.err, stream));
+    } else {
+      MB_TRY(mb_paged_attention(buf.qkv, qkv_dim, buf.attn, q_dim, kbase, kbase + 2 * kv.kv_stride, in.block_table,
+                                in.bt_stride, in.q_start, in.q_len, in.kv_len, in.tile_seq, in.tile_q0, in.n_tiles,
+                                in.n_decode, in.decode_seq, c.n_q, c.n_kv, c.head_dim, c.page_size, kv.page_stride,
+                                kv.head_stride, c.attn_scale, stream));
+    }
+    launches += 2;
+    mark("attention", stream);
+    MB_TRY(dec(buf.attn, w.wo, c.hidden, q_dim, 2, nullptr, 0, w.mlp_norm));
+    mark("gemm_o+ar+norm", stream);
+    if (c.fuse_swiglu) {
+      MB_TRY(dec(buf.xn, w.wgu, 2 * c.inter, c.hidden, 1, buf.act, c.inter, nullptr));
+    } else {
+      MB_TRY(dec(buf.xn, w.wgu, 2 * c.inter, c.hidden, 0, buf.gu, 2 * c.inter, nullptr));
+      MB_TRY(mb_silu_mul(buf.gu, buf.act, T, c.inter, stream));
+      launches += 1;
+    }
+    mark("gemm_gate_up", stream);
+    const void* next_norm = l + 1 < c.n_layers ? layers[l + 1].attn_norm : final_norm;
+    MB_TRY(dec(buf.act, w.wd, c.hidden, c.inter, 2, nullptr, 0, next_norm));
+    mark("gemm_down+ar+norm", stream);
+  }
+  if (in.n_logits > 0) {
+    // xn holds the final-normalised rows of every token (on every rank)
+    MB_TRY(mb_gather_rows(buf.xn, in.logit_rows, buf.last_xn, in.n_logits, c.hidden * 2, c.hidden * 2, stream));
+    launches += 1;
+    const float* logits = buf.logits;
+    if (W > 1) {
+      int bn, splits, stages;
+      mb_gemm_bf16_plan(in.n_logits, tp.vocab_local, c.hidden, 0, c.num_sms, &bn, &splits, &stages);
+      MB_TRY(mb_gemm_bf16(buf.last_xn, lm_head, tp.logits_local, nullptr, in.n_logits, tp.vocab_local, c.hidden,
+                          c.hidden, c.hidden, tp.vocab_local, tp.vocab_local, 4, bn, 1, stages, buf.workspace,
+                          buf.err, c.num_sms, stream));
+      MB_TRY(mb_tp_allgather(W, R, tp.logits, tp.flags, tp.logits_local, in.n_logits, tp.vocab_local * 4,
+                             tp.vocab_local * 4, c.vocab * 4, static_cast<long long>(R) * tp.vocab_local * 4,
+                             buf.err, stream));
+      launches += 2;
+      logits = static_cast<const float*>(tp.logits[R]);
+      mark("lm_head+allgather", stream);
+    } else {
+      int bn, splits, stages;
+      mb_gemm_bf16_plan(in.n_logits, c.vocab, c.hidden, 0, c.num_sms, &bn, &splits, &stages);
+      MB_TRY(mb_gemm_bf16(buf.last_xn, lm_head, buf.logits, nullptr, in.n_logits, c.vocab, c.hidden, c.hidden,
+                          c.hidden, c.vocab, c.vocab, 4, bn, 1, stages, buf.workspace, buf.err, c.num_sms, stream));
+      launches += 1;
+      mark("lm_head", stream);
+    }
+    if (in.do_sample) {
+      MB_TRY(mb_sample_topk_topp(logits, buf.sampled, in.n_logits, c.vocab, c.vocab, in.temperature, in.top_k,
+                                 in.top_p, in.min_p, in.seeds, in.sample_step, stream));
+      launches += 1;
+      mark("sample", stream);
+    }
+  }
+  return MB_OK;
+}
+
 int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
+  if (dec_usable(in.T)) return forward_dec(in, stream);
   if (tp.world > 1) return forward_tp(in, stream);
   const DecoderConfig& c = cfg;
   const int T = in.T;

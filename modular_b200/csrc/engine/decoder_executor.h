@@ -39,6 +39,7 @@ struct DecoderConfig {
   int use_pdl;                // launch persistent GEMMs with programmatic dependent launch
   int attn_impl;              // 0 = cp.async kernels, 1 = TMA-fed single-launch kernel (page_size % 64 == 0)
   int num_sms;
+  int dec_max_tokens;         // steps of up to this many tokens run the decode-step GEMMs (0 = never)
 };
 
 struct DecoderBuffers {
@@ -57,6 +58,9 @@ struct DecoderBuffers {
   void* p_ws;       // persistent GEMM partial-tile slots
   int* p_counters;  // persistent GEMM tile counters (zeroed)
   int* err;
+  void* dec_ws = nullptr;       // decode-step GEMM partial tiles
+  size_t dec_ws_bytes = 0;
+  int* dec_state = nullptr;     // decode-step GEMM counters / all-reduce generation (zeroed once)
 };
 
 struct KVCacheView {
@@ -109,6 +113,10 @@ struct TpState {
   // fused bit1: column-parallel GEMMs wait per source on ready flags instead of a closing barrier.
   int fused = 0;
   long long partial_rows = 0;
+  // decode steps: receive buffers of the GEMM + all-reduce + norm kernel on every rank
+  // ([3][world][lam_rows][hidden] bf16, filled with -0.0 once); the residual stream is then replicated
+  void* lam[8] = {};
+  int lam_rows = 0;
 };
 
 class DecoderExecutor {
@@ -128,6 +136,9 @@ class DecoderExecutor {
   // first launcher error.
   int forward(const StepInputs& in, cudaStream_t stream);
 
+  // True when a step of T tokens takes the decode-step path (forward_dec).
+  bool dec_usable(int T) const;
+
   // Per-kernel timing of eager (not graph-captured) steps: when `profiling` is set, an event is
   // recorded after every launch group; profile_ms() synchronises and returns, per label, the
   // number of intervals and their summed duration since the last call.
@@ -137,6 +148,10 @@ class DecoderExecutor {
 
  private:
   int forward_tp(const StepInputs& in, cudaStream_t stream);
+  // Small steps (T <= cfg.dec_max_tokens), one GPU or tensor parallel: four decode-step GEMMs per layer,
+  // the row-parallel ones fused with all-reduce + residual + RMSNorm; no other collective, no stand-alone
+  // norm after the first one.
+  int forward_dec(const StepInputs& in, cudaStream_t stream);
   std::vector<std::pair<const char*, cudaEvent_t>> marks_;
 };
 

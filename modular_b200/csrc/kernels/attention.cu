@@ -18,6 +18,7 @@
 #include <stdint.h>
 
 #include "../common/api.h"
+#include "../common/launch.h"
 
 namespace mb {
 
@@ -427,13 +428,13 @@ static int launch_attn(const AttnParams& p, int n_tiles, int n_decode, int n_kv,
                        cudaStream_t stream) {
   const size_t smem_pf = (64 + 4 * 64) * HD * 2;
   const size_t smem_dc = (16 + 4 * 64) * HD * 2;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     cudaFuncSetAttribute(attn_prefill_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(smem_pf));
     cudaFuncSetAttribute(attn_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(smem_dc));
-    configured = true;
+    configured.done();
   }
   if (n_tiles > 0)
     attn_prefill_kernel<HD, G><<<dim3(n_tiles, n_kv), 128, smem_pf, stream>>>(p);

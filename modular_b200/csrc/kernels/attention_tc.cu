@@ -413,12 +413,12 @@ extern "C" int mb_paged_attention_prefill_tc(const void* q, int ldq, void* out, 
   const int rc = cached_tmap(&tm, kv_base, static_cast<uint64_t>(total_rows), head_dim, head_dim, 64, 2);
   if (rc != MB_OK) return rc;
   const size_t smem = kQBytes + kStages * kStageBytes + 2 * kPBytes + sizeof(Bars);
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
         cudaSuccess)
       return MB_ERR_LAUNCH;
-    configured = true;
+    configured.done();
   }
   return launch_k(attn_tc_kernel, dim3(n_tiles, n_kv), dim3(kThreads), smem, stream, tm, p) == cudaSuccess
              ? MB_OK

@@ -357,18 +357,365 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p) {
   }
 }
 
+// ---------------------------------------------------------------------------- split-KV decode
+// Decode-only steps: the 64-token KV tiles of all decode sequences of one KV head form one list of
+// work units that is cut into equal contiguous shares, one per CTA (grid = CTAs per head x KV heads,
+// two CTAs per SM), so every SM streams the same number of KV bytes whatever the batch size, the
+// context lengths or the number of KV heads on this rank (one head at tensor-parallel degree 8).
+// A CTA that holds a whole sequence writes its output; a sequence cut across CTAs is combined by
+// whichever contributor arrives last: each writes its running maximum, sum and unnormalised output
+// (fp32, in MMA fragment order) to a workspace slot and bumps a per-(sequence, head) counter, and the
+// last one merges the slots in CTA order (deterministic) and stores the rows. Nobody waits.
+//
+// Reference counterparts: max/kernels/src/nn/attention/gpu/mha_decode_partition_heuristic.mojo (how
+// many partitions), nn/attention/gpu/nvidia/sm100/fa4_splitk_combine.mojo (the combine step).
+struct SplitParams {
+  float* ws;         // [n_kv][GX][2][part_floats]
+  int* counters;     // [n_kv][n_decode], zero between launches
+  int n_decode, GX;
+};
+
+constexpr int kMaxSplitDecode = 1024;
+
+template <int HD>
+struct PartLayout {
+  static constexpr int DT = HD / 8;
+  static constexpr int kFloats = (DT * 4 + 4) * 32;
+};
+
+template <int DT>
+__device__ __forceinline__ void store_state(const float (&o)[DT][4], const float (&m)[2], const float (&l)[2],
+                                            float* dst, int lane, bool hi) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (h == 1 && !hi) break;
+    dst[(DT * 4 + h) * 32 + lane] = m[h];
+    dst[(DT * 4 + 2 + h) * 32 + lane] = l[h];
+#pragma unroll
+    for (int dt = 0; dt < DT; ++dt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) dst[((h * DT + dt) * 2 + e) * 32 + lane] = o[dt][2 * h + e];
+    }
+  }
+}
+
+template <int HD, int G, int STAGES>
+__global__ void __launch_bounds__(kThreads, 2)
+attn_decode_split_kernel(const __grid_constant__ CUtensorMap tmKV, const Params p, const SplitParams sp) {
+  constexpr int CH = HD / 8, KS = HD / 16, DT = HD / 8;
+  constexpr int kTileElems = 64 * HD;
+  constexpr uint32_t kStageBytes = 2 * kTileElems * 2;
+  constexpr int kPart = PartLayout<HD>::kFloats;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  bf16* sKV = reinterpret_cast<bf16*>(smem);
+  bf16* sQ = sKV + STAGES * 2 * kTileElems;                 // [16][HD]
+  float* sM = reinterpret_cast<float*>(sQ + 16 * HD);       // two merge slots, one row half each
+  constexpr int kMergeFloats = (DT * 2 + 4) * 32;           // o of one row half + m, l of both
+  Bars* bars = reinterpret_cast<Bars*>(sM + 2 * kMergeFloats);
+  int* prefix = reinterpret_cast<int*>(bars + 1);           // [n_decode + 1] tile prefix sums
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kvh = blockIdx.y, gx = blockIdx.x;
+  const int nd = sp.n_decode;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 4);
+    }
+    bars->abort_word = 0;
+    fence_mbar_init();
+  }
+  pdl_wait();
+  pdl_trigger();
+  // tile counts of the decode sequences (one round of loads by all threads), then their prefix sums
+  // (warp 0: lanes own consecutive chunks of the shared-memory array)
+  for (int i = tid; i < nd; i += kThreads) prefix[i + 1] = (p.kv_len[p.decode_seq[i]] + 63) >> 6;
+  __syncthreads();
+  if (warp == 0) {
+    const int per = (nd + 31) / 32;
+    const int i0 = lane * per;
+    int sum = 0;
+    for (int i = i0; i < i0 + per && i < nd; ++i) sum += prefix[i + 1];
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int run = incl - sum;
+    if (lane == 0) prefix[0] = 0;
+    for (int i = i0; i < i0 + per && i < nd; ++i) {
+      run += prefix[i + 1];
+      prefix[i + 1] = run;
+    }
+  }
+  __syncthreads();
+  volatile int* abort_word = &bars->abort_word;
+  const long long U = prefix[nd];
+  // never more shares than tiles: every CTA that stays has at least one tile, so the contributors of a
+  // sequence are consecutive CTAs;
+  // and no share shorter than four tiles (256 tokens): below that the per-share costs outweigh the balance
+  const long long gmax = U >= 8 ? U / 4 : 1;
+  const int GX = gmax < sp.GX ? static_cast<int>(gmax) : sp.GX;
+  if (gx >= GX) return;
+  const int u0 = static_cast<int>(U * gx / GX), u1 = static_cast<int>(U * (gx + 1) / GX);
+  // first sequence of this CTA's share: largest i with prefix[i] <= u0
+  int i_first;
+  {
+    int lo = 0, hi = nd - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (prefix[mid] <= u0) lo = mid; else hi = mid - 1;
+    }
+    i_first = lo;
+  }
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmKV);
+      int s = 0;
+      uint32_t ph = 0;
+      const long long head_row = static_cast<long long>(kvh) * p.page_size;
+      bool ok = true;
+      for (int i = i_first, u = u0; ok && u < u1; ++i) {
+        const int fu = prefix[i], nt = prefix[i + 1] - fu;
+        const int t0 = u - fu;
+        int t1 = nt;
+        if (fu + t1 > u1) t1 = u1 - fu;
+        u = fu + t1;
+        if (t1 <= t0) continue;   // a sequence without tiles
+        const int32_t* bt = p.block_table + static_cast<int64_t>(p.decode_seq[i]) * p.bt_stride;
+        int page_i = (t0 * 64) / p.page_size, page_off = (t0 * 64) % p.page_size;
+        int32_t page_next = bt[page_i];
+        for (int t = t0; t < t1; ++t) {
+          const long long row = static_cast<long long>(page_next) * p.page_rows + head_row + page_off;
+          page_off += 64;
+          if (page_off == p.page_size) { page_off = 0; ++page_i; }
+          if (t + 1 < t1 && page_off == 0) page_next = bt[page_i];
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_word, p.err, 311)) { ok = false; break; }
+          bf16* dK = sKV + s * 2 * kTileElems;
+          bf16* dV = dK + kTileElems;
+          mbar_arrive_expect_tx(&bars->full[s], kStageBytes);
+#pragma unroll
+          for (int sub = 0; sub < HD / 64; ++sub) {
+            tma_load_2d(dK + sub * 64 * 64, &tmKV, &bars->full[s], sub * 64, static_cast<int32_t>(p.k_off_rows + row));
+            tma_load_2d(dV + sub * 64 * 64, &tmKV, &bars->full[s], sub * 64, static_cast<int32_t>(p.v_off_rows + row));
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------ compute warps
+  int s = 0;
+  uint32_t ph = 0;
+  bool ok = true;
+  for (int i = i_first, u = u0; u < u1; ++i) {
+    const int fu = prefix[i], nt = prefix[i + 1] - fu;
+    const int t0 = u - fu;
+    int t1 = nt;
+    if (fu + t1 > u1) t1 = u1 - fu;
+    u = fu + t1;
+    if (t1 <= t0) continue;
+    const int seq = p.decode_seq[i];
+    const int qs = p.q_start[seq], ql = p.q_len[seq], kl = p.kv_len[seq];
+    const bool hi = ql * G > 8;   // rows 8..15 of the packed query tile are in use
+    consumer_sync();              // the previous segment no longer reads sQ or the merge slots
+    for (int idx = tid; idx < 16 * CH; idx += 128) {
+      const int row = idx / CH, chunk = idx % CH;
+      const int tq = row / G, head = kvh * G + row % G;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (tq < ql)
+        v = *reinterpret_cast<const uint4*>(p.q + static_cast<int64_t>(qs + tq) * p.ldq + head * HD + chunk * 8);
+      *reinterpret_cast<uint4*>(sQ + qswz<HD>(row, chunk)) = v;
+    }
+    consumer_sync();
+    uint32_t qf[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) ldsm_x4(qf[ks], sQ + qswz<HD>(lane & 15, 2 * ks + (lane >> 4)));
+    float o[DT][4];
+#pragma unroll
+    for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    int limit[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int tq = ((lane >> 2) + h * 8) / G;
+      limit[h] = tq < ql ? kl - ql + tq : -1;
+    }
+    for (int t = t0; t < t1 && ok; ++t) {
+      // after a failed wait this warp skips the remaining tiles but keeps meeting the other warps at
+      // every barrier below (a warp that left early would leave them waiting)
+      if (!mbar_wait(&bars->full[s], ph, abort_word, p.err, 312)) { ok = false; break; }
+      const bf16* tK = sKV + s * 2 * kTileElems;
+      const bf16* tV = tK + kTileElems;
+      if (t * 64 + warp * 16 < kl)
+        process_block<HD, 1>(tK, tV, warp * 16, t * 64 + warp * 16, qf, o, m, l, limit, p.scale_log2, lane);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->empty[s]);
+      if (++s == STAGES) { s = 0; ph ^= 1; }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    // tree merge of the four warps' states, one row half at a time through two small slots:
+    // warps 2,3 -> slots; warps 0,1 fold them in; warp 1 -> slot 0; warp 0 folds it in
+    for (int half = 0; half < (hi ? 2 : 1); ++half) {
+      float* slot = sM + (warp & 1) * kMergeFloats;
+      auto put = [&]() {
+        slot[(DT * 2 + 0) * 32 + lane] = m[half];
+        slot[(DT * 2 + 1) * 32 + lane] = l[half];
+#pragma unroll
+        for (int dt = 0; dt < DT; ++dt) {
+          slot[(dt * 2 + 0) * 32 + lane] = o[dt][2 * half];
+          slot[(dt * 2 + 1) * 32 + lane] = o[dt][2 * half + 1];
+        }
+      };
+      auto fold = [&]() {
+        const float m2 = slot[(DT * 2 + 0) * 32 + lane], l2 = slot[(DT * 2 + 1) * 32 + lane];
+        const float mn = fmaxf(m[half], m2);
+        const float a = m[half] == -INFINITY ? 0.f : exp2f(m[half] - mn);
+        const float b = m2 == -INFINITY ? 0.f : exp2f(m2 - mn);
+        m[half] = mn;
+        l[half] = a * l[half] + b * l2;
+#pragma unroll
+        for (int dt = 0; dt < DT; ++dt) {
+          o[dt][2 * half] = a * o[dt][2 * half] + b * slot[(dt * 2 + 0) * 32 + lane];
+          o[dt][2 * half + 1] = a * o[dt][2 * half + 1] + b * slot[(dt * 2 + 1) * 32 + lane];
+        }
+      };
+      if (warp >= 2) put();
+      consumer_sync();
+      if (warp < 2) fold();
+      consumer_sync();
+      if (warp == 1) put();     // (warp & 1) == 1: slot 1
+      consumer_sync();
+      if (warp == 0) {
+        slot = sM + kMergeFloats;
+        fold();
+      }
+      if (half == 0 && hi) consumer_sync();   // slot 1 is read before the second half overwrites it
+    }
+    if (warp != 0 || *abort_word != 0) continue;
+    // ---- warp 0 holds the state of this segment
+    const bool whole = t0 == 0 && t1 == nt;
+    bool finish = whole;
+    if (!whole) {
+      const int g_first = static_cast<int>(((static_cast<long long>(fu) + 1) * GX - 1) / U);
+      const int g_last = static_cast<int>(((static_cast<long long>(fu) + nt) * GX - 1) / U);
+      float* base = sp.ws + static_cast<size_t>(kvh) * sp.GX * 2 * kPart;
+      float* mine = base + (static_cast<size_t>(gx) * 2 + (fu <= u0 ? 0 : 1)) * kPart;
+      store_state<DT>(o, m, l, mine, lane, hi);
+      __threadfence();
+      __syncwarp();
+      int old = 0;
+      int* cnt = sp.counters + static_cast<size_t>(kvh) * nd + i;
+      if (lane == 0) old = atomicAdd(cnt, 1);
+      old = __shfl_sync(0xffffffffu, old, 0);
+      if (old == g_last - g_first) {
+        __threadfence();
+        // merge every contributor's slot in CTA order, starting from an empty state
+#pragma unroll
+        for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+        for (int gc = g_first; gc <= g_last; ++gc) {
+          const int c0 = static_cast<int>(U * gc / GX);
+          const float* src = base + (static_cast<size_t>(gc) * 2 + (fu <= c0 ? 0 : 1)) * kPart;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (h == 1 && !hi) break;
+            const float m2 = __ldcg(src + (DT * 4 + h) * 32 + lane);
+            const float l2 = __ldcg(src + (DT * 4 + 2 + h) * 32 + lane);
+            float v[DT][2];
+#pragma unroll
+            for (int dt = 0; dt < DT; ++dt) {
+              v[dt][0] = __ldcg(src + ((h * DT + dt) * 2 + 0) * 32 + lane);
+              v[dt][1] = __ldcg(src + ((h * DT + dt) * 2 + 1) * 32 + lane);
+            }
+            const float mn = fmaxf(m[h], m2);
+            const float a = m[h] == -INFINITY ? 0.f : exp2f(m[h] - mn);
+            const float b = m2 == -INFINITY ? 0.f : exp2f(m2 - mn);
+            m[h] = mn;
+            l[h] = a * l[h] + b * l2;
+#pragma unroll
+            for (int dt = 0; dt < DT; ++dt) {
+              o[dt][2 * h] = a * o[dt][2 * h] + b * v[dt][0];
+              o[dt][2 * h + 1] = a * o[dt][2 * h + 1] + b * v[dt][1];
+            }
+          }
+        }
+        if (lane == 0) *cnt = 0;   // ready for the next launch
+        finish = true;
+      }
+    }
+    if (finish) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+        const int r = (lane >> 2) + h * 8;
+        const int tq = r / G, head = kvh * G + r % G;
+        if (tq < ql) {
+          bf16* orow = p.out + static_cast<int64_t>(qs + tq) * p.ldo + head * HD + 2 * (lane & 3);
+#pragma unroll
+          for (int dt = 0; dt < DT; ++dt)
+            *reinterpret_cast<uint32_t*>(orow + dt * 8) = pack_bf16(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
+        }
+      }
+    }
+  }
+}
+
+static float* g_split_ws = nullptr;
+static size_t g_split_ws_bytes = 0;
+static int* g_split_counters = nullptr;
+static int g_split_counter_ints = 0;
+static int g_split_on = 1;
+
+template <int HD, int G>
+static int launch_split(const CUtensorMap& tm, const Params& p, int n_decode, int n_kv, int num_sms,
+                        cudaStream_t stream) {
+  constexpr int STAGES = kStages;
+  constexpr int kPart = PartLayout<HD>::kFloats;
+  int GX = 2 * num_sms / n_kv;
+  if (GX < 1) GX = 1;
+  const size_t need = static_cast<size_t>(n_kv) * GX * 2 * kPart * sizeof(float);
+  if (need > g_split_ws_bytes || static_cast<long long>(n_kv) * n_decode > g_split_counter_ints) return MB_ERR_TOO_LARGE;
+  SplitParams sp;
+  sp.ws = g_split_ws; sp.counters = g_split_counters; sp.n_decode = n_decode; sp.GX = GX;
+  constexpr int kMergeFloats = (HD / 8 * 2 + 4) * 32;
+  const size_t smem = static_cast<size_t>(STAGES) * 2 * 64 * HD * 2 + 16 * HD * 2 + 2 * kMergeFloats * sizeof(float) +
+                      sizeof(Bars) + (static_cast<size_t>(n_decode) + 1) * sizeof(int) + 1024;
+  auto kern = attn_decode_split_kernel<HD, G, STAGES>;
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
+      return MB_ERR_LAUNCH;
+    configured.done();
+  }
+  if (launch_k(kern, dim3(GX, n_kv), dim3(kThreads), smem, stream, tm, p, sp) != cudaSuccess) return MB_ERR_LAUNCH;
+  return MB_OK;
+}
+
 template <int HD, int G, int STAGES, int MINB>
 static int launch_one(const CUtensorMap& tm, Params p, int n_ctas, int n_kv, int q_rows, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(STAGES) * 2 * 64 * HD * 2 + static_cast<size_t>(q_rows) * HD * 2 +
                       sizeof(Bars) + 1024;
   auto kern = attn_tma_kernel<HD, G, STAGES, MINB>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     const size_t smem_max = static_cast<size_t>(STAGES) * 2 * 64 * HD * 2 + 64 * HD * 2 + sizeof(Bars) + 1024;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_max)) !=
         cudaSuccess)
       return MB_ERR_LAUNCH;
-    configured = true;
+    configured.done();
   }
   p.q_rows_alloc = q_rows;
   if (launch_k(kern, dim3(n_ctas, n_kv), dim3(kThreads), smem, stream, tm, p) != cudaSuccess) return MB_ERR_LAUNCH;
@@ -406,6 +753,20 @@ static cudaEvent_t g_fork_join = nullptr;
 extern "C" void mb_set_attn_fork(int on) { g_attn_fork = on; }
 // 1: decode-only launches use the denser build; 0 (default): the three-stage build for every launch
 extern "C" void mb_set_attn_decode_dense(int on) { mb::at2::g_decode_dense = on; }
+// Workspace of the split-KV decode kernel: `ws` holds partial states (mb_attn_split_workspace_bytes), `counters`
+// zeroed ints, one per (KV head, decode sequence) of the largest batch. Process-wide (one process per GPU);
+// without it, or with mb_set_attn_split(0), decode-only steps run one CTA per (sequence, KV head).
+extern "C" size_t mb_attn_split_workspace_bytes(int num_sms) {
+  // at most 2 * num_sms CTAs in all, two slots each, head_dim 128
+  return static_cast<size_t>(2 * (num_sms > 0 ? num_sms : 148) + 16) * 2 * mb::at2::PartLayout<128>::kFloats * sizeof(float);
+}
+extern "C" void mb_set_attn_split_workspace(void* ws, size_t ws_bytes, int* counters, int counter_ints) {
+  mb::at2::g_split_ws = static_cast<float*>(ws);
+  mb::at2::g_split_ws_bytes = ws_bytes;
+  mb::at2::g_split_counters = counters;
+  mb::at2::g_split_counter_ints = counter_ints;
+}
+extern "C" void mb_set_attn_split(int on) { mb::at2::g_split_on = on; }
 extern "C" void mb_set_attn_tc(int min_tiles) { g_attn_tc_min_tiles = min_tiles < 0 ? 0 : min_tiles; }
 extern "C" int mb_get_attn_tc(void) { return g_attn_tc_min_tiles; }
 
@@ -478,6 +839,35 @@ extern "C" int mb_paged_attention_tma(const void* q, int ldq, void* out, int ldo
       cudaStreamWaitEvent(stream, g_fork_join, 0);
       return rc2;
     }
+  }
+  int sms = 0;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    static int sm_count[64] = {};
+    if (dev >= 0 && dev < 64) {
+      if (sm_count[dev] == 0) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+      sms = sm_count[dev];
+    }
+    if (sms <= 0) sms = 148;
+  }
+  // Partition heuristic, measured on B200 under graph replay (64 sequences x 1152 tokens, 8 / 4 / 2 / 1 KV heads:
+  // one CTA per (sequence, head) 52.9 / 29.1 / 17.3 / 15.0 us, split 54.2 / 32.3 / 22.7 / 17.3 us; one sequence
+  // of 8192 tokens: 76.1 against 28.6 us): with at least one CTA per (sequence, head) for every second SM the
+  // unsplit kernel already streams at 0.85-0.99 of the copy bandwidth and the split costs ~2 us of fixed work;
+  // below that a long context would be read by a handful of CTAs, so the KV tiles are shared out.
+  // g_split_on = 2 forces the split kernel for every decode-only step.
+  const bool want_split = g_split_on == 2 || (g_split_on == 1 && static_cast<long long>(n_decode) * n_kv * 2 <= sms);
+  if (p.n_tiles == 0 && n_decode > 0 && n_decode <= kMaxSplitDecode && want_split && g_split_ws != nullptr && !forked) {
+    // decode-only step: equal KV shares per CTA with an in-kernel combine
+    int rcs = MB_ERR_SHAPE;
+#define MB_ATTN_SPLIT_CASE(HD_, G_) \
+  if (head_dim == HD_ && G == G_) rcs = launch_split<HD_, G_>(tm, p, n_decode, n_kv, sms, stream);
+    MB_ATTN_SPLIT_CASE(128, 1) MB_ATTN_SPLIT_CASE(128, 2) MB_ATTN_SPLIT_CASE(128, 4) MB_ATTN_SPLIT_CASE(128, 8)
+    MB_ATTN_SPLIT_CASE(128, 16)
+    MB_ATTN_SPLIT_CASE(64, 1) MB_ATTN_SPLIT_CASE(64, 2) MB_ATTN_SPLIT_CASE(64, 4) MB_ATTN_SPLIT_CASE(64, 8)
+#undef MB_ATTN_SPLIT_CASE
+    if (rcs == MB_OK || rcs == MB_ERR_LAUNCH) return rcs;   // other codes: the one-CTA-per-sequence kernel below
   }
   int rc3 = MB_ERR_SHAPE;
 #define MB_ATTN2_CASE(HD_, G_) \

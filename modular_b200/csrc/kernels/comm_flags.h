@@ -26,4 +26,15 @@ constexpr int kPushCount = 64;                      // on a cache line of its ow
 constexpr int kPushLocal = 72;                      // 72..79: tiles of the running GEMM finished per owner
 constexpr int kTpFlagInts = 96;
 
+// State words of the decode GEMM (gemm_decode.cu), local device memory, zeroed once:
+//   kDecArrive        CTAs of the running kernel whose partial tiles are written
+//   kDecDepart        CTAs that have left; the last one clears both counters
+//   kDecGen           all-reduce generation (advanced by the kernel, so graph replays stay in step)
+//   kDecGenRows + i   token rows written into receive-buffer generation i the last time it was used
+constexpr int kDecArrive = 0;
+constexpr int kDecDepart = 1;
+constexpr int kDecGen = 2;
+constexpr int kDecGenRows = 3;                      // 3..5
+constexpr int kDecStateInts = 8;
+
 }  // namespace mb

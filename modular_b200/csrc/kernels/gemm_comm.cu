@@ -28,6 +28,7 @@
 #include <stdint.h>
 
 #include "../common/api.h"
+#include "../common/launch.h"
 #include "../common/ptx.cuh"
 #include "comm_flags.h"
 #include "gemm_common.h"
@@ -247,11 +248,11 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, int M, 
   const int stage_bytes = kATileBytes * (DUAL ? 2 : 1) + BN * kBK * 2;
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes + sizeof(SmemTail) + 1024;
   auto kern = gemm_comm_kernel<DUAL>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
       return MB_ERR_LAUNCH;
-    configured = true;
+    configured.done();
   }
   uint32_t tmem_cols = 32;
   while (static_cast<int>(tmem_cols) < (DUAL ? 2 * BN : BN)) tmem_cols <<= 1;

@@ -31,6 +31,7 @@
 #include <stdint.h>
 
 #include "../common/api.h"
+#include "../common/launch.h"
 #include "../common/ptx.cuh"
 #include "gemm_common.h"
 
@@ -418,11 +419,11 @@ extern "C" int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const vo
   p.expert_offsets = nullptr; p.w_rows = 0; p.sw_rows = 0;
   dim3 grid((M + bn - 1) / bn, (N + kBM - 1) / kBM, splits);
   const bool resid = (flags & 2) && splits == 1;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     cudaFuncSetAttribute(gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(gemm_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    configured = true;
+    configured.done();
   }
   if (resid)
     gemm_fp8_kernel<true><<<grid, kThreads, smem, stream>>>(tw, tx, p);
@@ -482,10 +483,10 @@ extern "C" int mb_grouped_gemm_fp8_blockscaled(const void* Xq, const float* Xs, 
   rc = cached_tmap(&tx, Xq, total_rows, K, ldx, bn, 1);
   if (rc != MB_OK) return rc;
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 8 * kStgWarp + sizeof(Tail) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     cudaFuncSetAttribute(gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    configured = true;
+    configured.done();
   }
   dim3 grid((max_rows + bn - 1) / bn, N / kBM, n_experts);
   gemm_fp8_kernel<false><<<grid, kThreads, smem, stream>>>(tw, tx, p);

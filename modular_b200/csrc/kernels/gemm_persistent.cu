@@ -471,11 +471,11 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, const Params& p,
   const int stage_bytes = kATile * (DUAL ? 2 : 1) + p.BN * kBK * 2;
   const size_t smem = static_cast<size_t>(p.stages) * stage_bytes + 4 * kStgWarp + sizeof(Tail) + 1024;
   auto kern = gemm_persistent_kernel<DUAL, EPI>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
       return MB_ERR_LAUNCH;
-    configured = true;
+    configured.done();
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);

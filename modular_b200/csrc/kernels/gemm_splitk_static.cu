@@ -34,7 +34,10 @@ int setup_current_device(DeviceSlots** out) {
     p = nullptr;
     if (cudaGetSymbolAddress(&p, g_splitk_err) != cudaSuccess || p == nullptr) return MB_ERR_DRIVER;
     s.err = static_cast<int*>(p);
-    if (cudaMemset(s.err, 0, sizeof(int)) != cudaSuccess) return MB_ERR_DRIVER;
+    // the clear must have landed before a first GEMM on any stream (a non-blocking stream does not wait for
+    // the legacy stream the memset runs on), hence the one device-wide synchronisation of the set-up
+    if (cudaMemset(s.err, 0, sizeof(int)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess)
+      return MB_ERR_DRIVER;
     s.ready = true;
   }
   *out = &s;
@@ -61,8 +64,12 @@ extern "C" int mb_gemm_bf16_splitk_static(const void* X, const void* W, void* Y,
 extern "C" int mb_gemm_bf16_splitk_static_error(void) {
   DeviceSlots* s = nullptr;
   if (setup_current_device(&s) != MB_OK) return MB_ERR_DRIVER;
+  // wait for every stream of the device, non-blocking ones included: a plain cudaMemcpy alone would only
+  // order itself after the legacy stream and could read the word before a GEMM on another stream has finished
+  if (cudaDeviceSynchronize() != cudaSuccess) return MB_ERR_DRIVER;
   int v = 0;
   if (cudaMemcpy(&v, s->err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return MB_ERR_DRIVER;
-  if (v != 0) cudaMemset(s->err, 0, sizeof(int));
+  if (v != 0 && (cudaMemset(s->err, 0, sizeof(int)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess))
+    return MB_ERR_DRIVER;
   return v;
 }

@@ -31,8 +31,9 @@ extern "C" {
 //
 // Rules for callers:
 //   * The first call on each device resolves the device address of the scratch array (with
-//     that device current) and clears the library's error word. Make that first call early,
-//     outside any stream capture.
+//     that device current), clears the library's error word and waits once for the whole device
+//     (cudaDeviceSynchronize) so that the clear is ordered before GEMMs on any stream. Make
+//     that first call early, outside any stream capture.
 //   * No cudaMalloc, cudaFree or allocating library routine is called, on the first call or
 //     later.
 //   * All calls on one device share the one scratch array. Calls that may overlap on the GPU
@@ -46,7 +47,9 @@ int mb_gemm_bf16_splitk_static(const void* X, const void* W, void* Y, const void
                                cudaStream_t stream);
 
 // Reads (and clears) the error word the static entry point hands to its kernels: non-zero means
-// a bounded barrier wait inside a kernel timed out. Synchronises the device.
+// a bounded barrier wait inside a kernel timed out. Calls cudaDeviceSynchronize() first, so work on
+// every stream of the device (non-blocking streams too) has finished when the word is read; do not
+// call it from a thread that must not block, nor during stream capture.
 int mb_gemm_bf16_splitk_static_error(void);
 
 #ifdef __cplusplus

@@ -562,12 +562,12 @@ static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, con
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes +
                       sizeof(GemmSmemTail) + 1024;
   auto kern = gemm_wx_kernel<DUAL, EPI>;
-  static size_t configured = 0;
-  if (smem > configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
         cudaSuccess)
       return MB_ERR_LAUNCH;
-    configured = 227 * 1024;
+    configured.done();
   }
   dim3 grid((M + BN - 1) / BN, (N + kBM - 1) / kBM, expert_offsets ? n_experts : splits);
   const uint32_t tmem_cols = pow2_cols(DUAL ? 2 * BN : BN);
@@ -587,11 +587,11 @@ static int launch_pair_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes +
                       sizeof(GemmSmemTail) + 1024;
   auto kern = gemm_pair_kernel<DUAL, EPI>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
       return MB_ERR_LAUNCH;
-    configured = true;
+    configured.done();
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * ((M + BN - 1) / BN), (N + 2 * kBM - 1) / (2 * kBM), splits);

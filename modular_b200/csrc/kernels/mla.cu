@@ -22,6 +22,7 @@
 #include <stdint.h>
 
 #include "../common/api.h"
+#include "../common/launch.h"
 
 namespace mb {
 namespace mla {
@@ -276,11 +277,11 @@ static int launch(const Params& p, int grid_x, cudaStream_t stream) {
   constexpr int LD = R + DR;
   const size_t smem = static_cast<size_t>(3) * 64 * LD * sizeof(bf16);
   auto kern = mla_kernel<R>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return MB_ERR_LAUNCH;
-    configured = true;
+    configured.done();
   }
   dim3 grid(grid_x, p.n_heads / p.HB);
   kern<<<grid, 256, smem, stream>>>(p);

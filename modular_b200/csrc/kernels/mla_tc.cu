@@ -374,12 +374,12 @@ extern "C" int mb_mla_decode_tc(const void* q_lat, const void* q_rope, void* out
   rc = cached_tmap(&tkv, cache, static_cast<uint64_t>(total_rows), LD, LD, 64, 2);
   if (rc != MB_OK) return rc;
   const size_t smem = kQBlocks * kQBlockBytes + kSlots * kSlotBytes + kPBytes + sizeof(Bars);
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(mla_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
         cudaSuccess)
       return MB_ERR_LAUNCH;
-    configured = true;
+    configured.done();
   }
   return launch_k(mla_tc_kernel, dim3(B, n_heads / 128, 2), dim3(kThreads), smem, stream, tql, tqr, tkv, p) ==
                  cudaSuccess

@@ -249,7 +249,9 @@ class Llama3Model:
             attn_scale=self.scale, fuse_swiglu=int(self.fuse_swiglu),
             gemm_impl={"tiled": 0, "persistent": 1}.get(ops.GEMM_IMPL, 2),
             use_pdl=int(os.environ.get("MB200_PDL", "0")),
-            attn_impl=int(os.environ.get("MB200_ATTN_TMA", "1"))))
+            attn_impl=int(os.environ.get("MB200_ATTN_TMA", "1")),
+            # steps of up to this many tokens run the decode-step GEMMs (fused all-reduce + residual + norm)
+            dec_max_tokens=self._dec_tokens()))
         ex.set_globals(self.w.embed, self.w.final_norm, self.w.lm_head, self.cos_sin)
         for l in self.w.layers:
             ex.add_layer(l.attn_norm, l.wqkv, l.wo, l.mlp_norm, l.wgu, l.wd)
@@ -267,6 +269,8 @@ class Llama3Model:
         ex.set_buffers(b["h"], b["xn"], b["qkv"], b["attn"], b["act"], b["gu"], b["last_h"],
                        b["last_xn"], self.logits_buf, self.sampled, ops.gemm_workspace(dev),
                        *ops.persistent_gemm_workspace(dev))
+        ex.set_dec(*ops.decode_gemm_workspace(dev))
+        ops.ensure_attention_split_workspace(dev)
         if self.tp is not None and self.tp.world > 1:
             # symmetric buffers for the fused reduce-scatter + norm + all-gather and the logits
             tp, W = self.tp, self.tp.world
@@ -287,7 +291,26 @@ class Llama3Model:
             tp.barrier()  # flags are zeroed everywhere before any kernel can touch them
             ex.set_tp(W, tp.rank, sym_partial.peer_ptrs, sym_xn.peer_ptrs, sym_logits.peer_ptrs,
                       sym_flags.peer_ptrs, h_local, logits_local, vocab_local, fused, partial_rows)
+            # decode steps: receive buffers of the fused GEMM + all-reduce + norm, every word a bf16 -0.0
+            # ("nothing has arrived"); the kernels restore that state themselves after each use
+            lam_rows = min(T, self._dec_tokens(), L.gemm_dec_sizes()[2])
+            if lam_rows > 0:
+                sym_lam = tp.alloc_symmetric(L.gemm_dec_lamport_elems(W, lam_rows, c.hidden_size), dt)
+                sym_lam.tensor.view(torch.int16).fill_(-32768)
+                self._tp_bufs += (sym_lam,)
+                tp.barrier()
+                ex.set_tp_lamport(sym_lam.peer_ptrs, lam_rows)
         self.executor = ex
+
+    def _dec_tokens(self) -> int:
+        """Largest step (tokens) that takes the decode-step GEMM path. Under tensor parallelism it replaces two
+        collective launches per layer and wins at every decode size; on one GPU the tiled kernels with
+        split-K measured faster (106 against 117 us per layer of GEMMs at 64 tokens), so it is off there.
+        ``MB200_DEC_TOKENS`` overrides."""
+        env = os.environ.get("MB200_DEC_TOKENS")
+        if env is not None:
+            return int(env)
+        return 256 if (self.tp is not None and self.tp.world > 1) else 0
 
     def forward_packed(self, meta: torch.Tensor, offsets: dict, T: int, B: int, bt_stride: int,
                        n_tiles: int, n_decode: int, n_logits: int, has_future: bool = False,

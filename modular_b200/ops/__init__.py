@@ -22,7 +22,7 @@ from . import reference as ref
 __all__ = [
     "linear", "linear_swiglu", "rms_norm", "add_rms_norm", "silu_mul", "embedding",
     "rope_kv_store", "paged_attention", "build_attention_plan", "argmax", "sample",
-    "apply_penalties", "gemm_workspace", "check_device_error",
+    "apply_penalties", "gemm_workspace", "check_device_error", "linear_decode", "decode_gemm_workspace",
 ]
 
 _WORKSPACES: dict[int, torch.Tensor] = {}
@@ -64,6 +64,56 @@ def persistent_gemm_workspace(device):
               torch.zeros(nints, dtype=torch.int32, device=device))
         _PERSISTENT_WS[idx] = ws
     return ws
+
+
+_DEC_WS: dict[int, tuple] = {}
+
+
+def decode_gemm_workspace(device):
+    """(fp32 partial-tile workspace, zeroed int32 state words) of the decode-step GEMM; one pair per
+    device, used from one stream at a time. The state words carry the all-reduce generation, so they
+    live as long as the receive buffers they are used with."""
+    idx = torch.device(device).index or 0
+    ws = _DEC_WS.get(idx)
+    if ws is None:
+        nbytes, nints, _ = _lib().gemm_dec_sizes()
+        ws = (torch.empty(nbytes // 4, dtype=torch.float32, device=device),
+              torch.zeros(nints, dtype=torch.int32, device=device))
+        _DEC_WS[idx] = ws
+    return ws
+
+
+def linear_decode(x, w, mode="plain", out=None, h=None, gamma=None, eps=1e-5, weight_offset=0.0,
+                  multiply_before_cast=False, xn=None, tp=None):
+    """Decode-step GEMM (at most 256 token rows) with its fused tail.
+
+    mode ``plain``: ``x @ w.T``; ``swiglu``: ``silu(x @ wg.T) * (x @ wu.T)`` with ``w = [wg; wu]``;
+    ``add_norm``: ``h += x @ w.T`` summed over the tensor-parallel ranks of ``tp`` (a dict with world, rank,
+    lam (peer addresses of the receive buffers), lam_rows, state) or this GPU alone, in place, and returns
+    ``(rms_norm(h) * gamma, h)``. CPU tensors take the PyTorch reference."""
+    code = {"plain": 0, "swiglu": 1, "add_norm": 2}[mode]
+    if not x.is_cuda:
+        if code == 0:
+            return ref.linear(x, w)
+        if code == 1:
+            return ref.linear_swiglu(x, w)
+        y, hh = ref.add_rms_norm(ref.linear(x, w), h, gamma, eps, weight_offset, multiply_before_cast)
+        h.copy_(hh)
+        return y, h
+    ws, state = decode_gemm_workspace(x.device)
+    if code == 2:
+        if xn is None:
+            xn = torch.empty_like(h)
+        t = tp or {}
+        _lib().gemm_dec(x, w, 2, None, h, xn, gamma, eps, weight_offset, multiply_before_cast,
+                        t.get("world", 1), t.get("rank", 0), t.get("lam", []), t.get("lam_rows", 0), ws,
+                        t.get("state", state))
+        return xn, h
+    if out is None:
+        n = w.shape[0] // 2 if code == 1 else w.shape[0]
+        out = torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
+    _lib().gemm_dec(x, w, code, out, None, None, None, 0.0, 0.0, False, 1, 0, [], 0, ws, state)
+    return out
 
 
 def linear(x, w, residual=None, out=None, out_dtype=None, bn=0, splits=0, stages=0, impl=None,
@@ -184,6 +234,25 @@ def build_attention_plan(q_lens, n_q: int, n_kv: int):
             np.asarray(decode_seq, dtype=np.int32))
 
 
+_ATTN_SPLIT_WS: dict[int, tuple] = {}
+
+
+def ensure_attention_split_workspace(device) -> None:
+    """Registers the workspace of the split-KV decode attention for this process (one GPU per process):
+    partial states plus one zeroed counter per (KV head, decode sequence) of up to 1024 sequences x 64 heads.
+    ``MB200_ATTN_SPLIT``: 0 keeps decode steps on the one-CTA-per-sequence kernel, 1 (default) splits when
+    there are few (sequence, KV head) pairs, 2 always splits."""
+    idx = torch.device(device).index or 0
+    if idx in _ATTN_SPLIT_WS:
+        return
+    L = _lib()
+    ws = torch.empty(L.attn_split_workspace_bytes() // 4, dtype=torch.float32, device=device)
+    counters = torch.zeros(1024 * 64, dtype=torch.int32, device=device)
+    _ATTN_SPLIT_WS[idx] = (ws, counters)
+    L.set_attn_split_workspace(ws, counters)
+    L.set_attn_split(int(os.environ.get("MB200_ATTN_SPLIT", "1")))
+
+
 def paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, n_q, n_kv,
                     head_dim, scale, plan=None, out=None, kv=None, layer=0):
     """Ragged causal attention. q: [T, ld] with the n_q*head_dim query columns first.
@@ -201,6 +270,7 @@ def paged_attention(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, n_
     if out is None:
         out = torch.empty(q.shape[0], n_q * head_dim, dtype=q.dtype, device=q.device)
     if kv is not None and kv.shape[4] % 64 == 0 and os.environ.get("MB200_ATTN_TMA", "1") == "1":
+        ensure_attention_split_workspace(q.device)
         _lib().paged_attention_tma(q, out, kv, layer, block_table, q_start, q_len, kv_len,
                                    plan[0], plan[1], plan[2], n_q, n_kv, head_dim, scale)
     else:

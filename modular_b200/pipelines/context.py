@@ -216,7 +216,9 @@ class TextContext:
     emitted: int = 0                 # generated tokens already handed to the caller
     sample_slot: int = -1            # row of this request in the previous step's sampled-token buffer
     dp_replica: int = 0
-    lora_name: Optional[str] = None
+    # salt of this request's prefix-cache hashes: the caller's own salt (requests with different salts never
+    # share pages); the scheduler folds the adapter identity in before the first claim
+    cache_salt: int = 0
     json_schema: Optional[str] = None
     matcher: Any = None
     seq: int = field(default_factory=lambda: next(_req_counter))

@@ -67,6 +67,17 @@ class LoRAManager:
         self._slots: "OrderedDict[str, int]" = OrderedDict()
         self.adapters: dict[int, LoRAAdapter] = {}
         self._pinned: dict[str, int] = {}
+        self._generation: dict[str, int] = {}   # how many times a name has been loaded
+
+    def cache_salt(self, name: Optional[str]) -> int:
+        """Prefix-cache salt of requests that run on adapter ``name`` (0 for the base model). Adapters change
+        the k/v projections, so KV pages written under one adapter must never be reused under another or under
+        the base model; the load count makes a re-loaded adapter of the same name miss as well."""
+        if not name:
+            return 0
+        import hashlib
+        d = hashlib.blake2b(f"{name}\0{self._generation.get(name, 0)}".encode(), digest_size=8).digest()
+        return (int.from_bytes(d, "little") & 0x7FFFFFFFFFFFFFFF) or 1
 
     def load(self, adapter: LoRAAdapter) -> int:
         if adapter.rank > self.max_rank or adapter.rank % 8:
@@ -84,6 +95,7 @@ class LoRAManager:
         self._slots[adapter.name] = slot
         self._slots.move_to_end(adapter.name)
         self.adapters[slot] = adapter
+        self._generation[adapter.name] = self._generation.get(adapter.name, 0) + 1
         return slot
 
     def unload(self, name: str) -> bool:

@@ -78,6 +78,7 @@ class _SeqCache:
         c, page = model.cfg, model.page_size
         n_pages = (max_len + page - 1) // page
         self.model, self.page, self.len = model, page, 0
+        self.capacity = n_pages * page          # token slots of the private cache
         shape = list(model.kv.shape)
         shape[0] = n_pages + 1
         self.kv = torch.zeros(shape, dtype=model.kv.dtype, device=model.device)
@@ -86,6 +87,9 @@ class _SeqCache:
     def step(self, tokens: Sequence[int], all_logits: bool) -> torch.Tensor:
         """Append ``tokens`` at the current length; fp32 logits of every row (or the last)."""
         dev, n = self.model.device, len(tokens)
+        if n < 1 or self.len + n > self.capacity:
+            # slots past the private cache would be written by the KV-store kernel and read through the block table
+            raise ValueError(f"sequence of {self.len} + {n} tokens exceeds the cache capacity of {self.capacity}")
         pos = torch.arange(self.len, self.len + n, dtype=torch.int32, device=dev)
         i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=dev)
         rows = torch.arange(n, dtype=torch.int32, device=dev) if all_logits else i32(n - 1)
@@ -112,6 +116,8 @@ class DraftModelProposer:
         self.cache.rewind(min(self._fed, len(history) - 1))
         pending = list(history[self.cache.len:])
         drafts, probs = [], []
+        # every draft step appends to the draft cache: stop where it would run out
+        k = max(0, min(k, self.cache.capacity - self.cache.len - len(pending) + 1))
         for _ in range(k):
             logits = self.cache.step(pending, all_logits=False)[0]
             if self.temperature == 0.0:
@@ -140,6 +146,8 @@ class SpeculativeDecoder:
 
     def generate(self, prompt: Sequence[int], max_new_tokens: int, temperature: float = 0.0,
                  eos_token_ids: Sequence[int] = (), seed: int = 0) -> list:
+        if len(prompt) < 1 or len(prompt) >= self.max_len:
+            raise ValueError(f"prompt of {len(prompt)} tokens does not fit max_len {self.max_len} with room to generate")
         gen = torch.Generator().manual_seed(seed)
         k = self.cfg.num_speculative_tokens
         proposer = (DraftModelProposer(self.draft, self.max_len, temperature, gen) if self.cfg.method == "draft_model"
@@ -151,6 +159,8 @@ class SpeculativeDecoder:
         if len(history) > 1:
             cache.step(history[:-1], all_logits=False)
         while len(out) < max_new_tokens:
+            if len(history) >= self.max_len:
+                return out          # length finish: the next step would not fit the cache
             budget = min(k, max_new_tokens - len(out) - 1, self.max_len - len(history) - 1)
             drafts, q = proposer.propose(history, budget) if budget > 0 else ([], None)
             base = cache.len

@@ -150,8 +150,11 @@ class TextGenerationPipeline:
         n = len(batch)
         for B in self.graph_batch_sizes:
             if B >= n and B in self._graphs:
+                # the captured graph samples inside the step: anything the replay cannot apply per request
+                # (penalties, grammar masks, log-probabilities, adapters) keeps the batch on the eager path
                 if all(c.tokens.active_length == 1 and c.sampling_params.is_greedy
                        and c.sampling_params.response_format is None and not c.sampling_params.logprobs
+                       and not c.sampling_params.needs_penalties and not c.lora_name
                        for c in batch):
                     return B
                 return 0
@@ -164,21 +167,24 @@ class TextGenerationPipeline:
         model = self.model
         uses_lora = self.lora_manager is not None and any(c.lora_name for c in batch)
         if self.on_gpu and model.use_executor and not uses_lora:
-            if self.record_gpu_time:
-                ev0 = torch.cuda.Event(enable_timing=True)
-                ev0.record()
+            # device time of a step = from after the metadata upload to after the sampled-token copy is queued
+            ev0 = torch.cuda.Event(enable_timing=True) if self.record_gpu_time else None
             step_logprobs = None
             B_graph = self._graph_bucket(batch)
             if B_graph:
                 g, fixed, off, words = self._graphs[B_graph]
                 sb = self.packer.pack(batch, self.kv, fixed=fixed, pad_to=B_graph)
                 self.packer.upload(sb)
+                if ev0 is not None:
+                    ev0.record()
                 g.replay()
                 self.stats.graph_replays += 1
                 self._replayed_launches += self._graph_launches[B_graph]
             else:
                 sb = self.packer.pack(batch, self.kv)
                 meta = self.packer.upload(sb)
+                if ev0 is not None:
+                    ev0.record()
                 needs_pen = any(c.sampling_params.needs_penalties for c in sb.logit_ctx)
                 mask = self._grammar_bitmask(sb) if self.structured is not None else None
                 wants_lp = any(c.sampling_params.logprobs for c in sb.logit_ctx)

@@ -53,13 +53,27 @@ class SchedulerBatch:
 
 
 class TextBatchConstructor:
-    def __init__(self, config: TokenGenerationSchedulerConfig, kv: Optional[PagedKVCacheManager]):
+    def __init__(self, config: TokenGenerationSchedulerConfig, kv: Optional[PagedKVCacheManager],
+                 lora_manager=None):
         self.config = config
         self.kv = kv
+        # a callable returning the pipeline's LoRA manager (it may be created after the scheduler), or None
+        self.lora_manager = lora_manager
         self.ce_reqs: "OrderedDict[str, TextContext]" = OrderedDict()
         self.tg_reqs: "OrderedDict[str, TextContext]" = OrderedDict()
         self.draining: dict[str, TextContext] = {}   # finished, last token still in flight
         self.total_preemptions = 0
+
+    def _kv_salt(self, ctx: TextContext) -> int:
+        """Salt of the request's page hashes: the caller's ``cache_salt`` combined with the identity of the
+        adapter the request runs on (reference: block_manager.py:134 passes ``ctx.cache_salt``)."""
+        salt = int(ctx.cache_salt)
+        if ctx.lora_name:
+            mgr = self.lora_manager() if callable(self.lora_manager) else self.lora_manager
+            if mgr is None:
+                raise KeyError(f"request {ctx.request_id} names LoRA adapter {ctx.lora_name!r} but none is loaded")
+            salt ^= mgr.cache_salt(ctx.lora_name)
+        return salt & 0x7FFFFFFFFFFFFFFF
 
     # ------------------------------------------------------------ queue management
     def enqueue_new_request(self, ctx: TextContext) -> None:
@@ -178,7 +192,8 @@ class TextBatchConstructor:
                 continue
             if self.kv is not None:
                 if not self.kv.contains(rid):
-                    self.kv.claim(ctx)
+                    # also the path of a re-claim after preemption: the salt is recomputed from the request
+                    self.kv.claim(ctx, salt=self._kv_salt(ctx))
                 # prefix-cache lookup on the whole prompt first: it moves the window start
                 self.kv.lookup_prefix(ctx)
             st = budget.status_after_context(ctx)       # may chunk the window

@@ -55,7 +55,7 @@ class TokenGenerationScheduler:
         self.config = config
         self.pipeline = pipeline
         self.kv = kv if kv is not None else getattr(pipeline, "kv", None)
-        self.batch_constructor = TextBatchConstructor(config, self.kv)
+        self.batch_constructor = TextBatchConstructor(config, self.kv, lambda: getattr(self.pipeline, "lora_manager", None))
         self.request_queue = request_queue if request_queue is not None else queue.SimpleQueue()
         self.response_queue = response_queue if response_queue is not None else queue.SimpleQueue()
         self.cancel_queue = cancel_queue if cancel_queue is not None else queue.SimpleQueue()

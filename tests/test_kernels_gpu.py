@@ -327,3 +327,132 @@ def test_grouped_gemm_fp8_and_fp8_experts():
     moe_fp8 = MoE(cfg, moe.gate, gu8, dn8, moe.bias, moe.shared_gate_up, moe.shared_down)
     xt = torch.randn(77, 512, device=DEV, dtype=torch.bfloat16)
     assert _rel_err(moe_fp8(xt), moe_bf16(xt)) < 4e-2      # activations are quantised to fp8 on the fp8 path
+
+
+# ---------------------------------------------------------------------------- decode-step GEMM
+@pytest.mark.parametrize("M,N,K", [(64, 6144, 4096), (64, 4096, 4096), (64, 4096, 14336), (1, 8192, 8192),
+                                   (16, 1024, 1024), (100, 4096, 512), (256, 4096, 1792), (33, 1536, 4160),
+                                   (8, 128, 64), (129, 768, 2048)])
+def test_gemm_decode_plain(M, N, K):
+    torch.manual_seed(3)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    for _ in range(2):   # the second call reuses the counters the first one left behind
+        y = ops.linear_decode(x, w)
+        yr = ref.linear(x, w)
+        assert _rel_err(y, yr) < 1e-2
+        assert (y.float() - yr.float()).abs().max() <= 0.02 * yr.float().abs().max() + 1e-2
+
+
+@pytest.mark.parametrize("M,I,K", [(64, 14336, 4096), (64, 1792, 4096), (17, 688, 256), (200, 3584, 1024)])
+def test_gemm_decode_swiglu(M, I, K):
+    torch.manual_seed(4)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(2 * I, K, device=DEV) * 0.03).to(torch.bfloat16)
+    y = ops.linear_decode(x, w, mode="swiglu")
+    yr = ref.linear_swiglu(x, w)
+    assert _rel_err(y, yr) < 1.5e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (64, 4096, 14336), (1, 4096, 512), (130, 8192, 1024),
+                                   (256, 1024, 1792), (48, 256, 688)])
+@pytest.mark.parametrize("mbc", [False, True])
+def test_gemm_decode_add_norm(M, N, K, mbc):
+    """One rank: h += x @ w.T, xn = rms_norm(h) * gamma, against the fp32 composition."""
+    torch.manual_seed(5)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.03).to(torch.bfloat16)
+    h0 = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn(N, device=DEV)).to(torch.bfloat16)
+    for it in range(2):
+        h = h0.clone()
+        xn, h = ops.linear_decode(x, w, mode="add_norm", h=h, gamma=gamma, eps=1e-5, multiply_before_cast=mbc)
+        hr = (h0.float() + x.float() @ w.float().t()).to(torch.bfloat16)
+        xr = ref.rms_norm(hr, gamma, 1e-5, 0.0, mbc)
+        assert (h.float() - hr.float()).abs().max() <= 0.02 * hr.float().abs().max() + 1e-2
+        assert _rel_err(xn, xr) < 1e-2
+
+
+def test_gemm_decode_chain_matches_layer_ops():
+    """qkv-like, add+norm, SwiGLU, add+norm back to back on one stream (each kernel starts before its
+    predecessor has finished when dependent launch is on) against the same chain from the tiled kernels."""
+    torch.manual_seed(6)
+    T, H, I = 64, 1024, 2816
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    h0 = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    w1 = (torch.randn(H, H, device=DEV) * 0.03).to(torch.bfloat16)
+    w2 = (torch.randn(2 * I, H, device=DEV) * 0.03).to(torch.bfloat16)
+    w3 = (torch.randn(H, I, device=DEV) * 0.03).to(torch.bfloat16)
+    g1 = torch.ones(H, device=DEV, dtype=torch.bfloat16)
+    for _ in range(3):
+        h = h0.clone()
+        a = ops.linear_decode(x, w1)
+        xn, h = ops.linear_decode(a, w1, mode="add_norm", h=h, gamma=g1)
+        act = ops.linear_decode(xn, w2, mode="swiglu")
+        xn2, h = ops.linear_decode(act, w3, mode="add_norm", h=h, gamma=g1)
+    hr = h0.clone()
+    ar = ops.linear(x, w1)
+    hr = ops.linear(ar, w1, residual=hr)
+    xr = ops.rms_norm(hr, g1, 1e-5)
+    actr = ops.linear_swiglu(xr, w2)
+    hr = ops.linear(actr, w3, residual=hr)
+    xr2 = ops.rms_norm(hr, g1, 1e-5)
+    assert _rel_err(h, hr) < 1e-2 and _rel_err(xn2, xr2) < 1e-2
+
+
+# ---------------------------------------------------------------------------- split-KV decode attention
+@pytest.mark.parametrize("n_q,n_kv,hd,ps", [(32, 8, 128, 128), (4, 1, 128, 128), (8, 8, 128, 64), (16, 2, 64, 64),
+                                            (16, 1, 128, 128)])
+@pytest.mark.parametrize("case", ["uniform", "ragged", "tiny", "spec"])
+@pytest.mark.parametrize("split", [True, False])
+def test_paged_attention_decode_split(n_q, n_kv, hd, ps, case, split):
+    """Decode-only batches through the split-KV kernel (equal KV shares per CTA, combine by the last
+    contributor) and through the one-CTA-per-sequence kernel, against the fp32 reference. Covers sequences
+    shorter than one share, one-token contexts, a single sequence spread over every CTA, and (spec) several
+    query tokens per sequence, which fill the upper half of the packed query tile."""
+    torch.manual_seed(9)
+    G = n_q // n_kv
+    if case == "uniform":
+        kv_lens, q_lens = [1152] * 64, [1] * 64
+    elif case == "ragged":
+        kv_lens = [1, 63, 64, 65, 513, 2000, 17, 129, 4096, 300, 1, 777]
+        q_lens = [1] * len(kv_lens)
+    elif case == "tiny":
+        kv_lens, q_lens = [700], [1]
+    else:
+        per = max(1, 16 // G)
+        kv_lens = [900, 70, 300, 1500]
+        q_lens = [min(per, 3), 1, min(per, 2), min(per, 4)]
+    B = len(kv_lens)
+    max_pages = max((k + ps - 1) // ps for k in kv_lens)
+    n_pages = sum((k + ps - 1) // ps for k in kv_lens) + 3
+    kv = (torch.randn(n_pages, 2, 2, n_kv, ps, hd, device=DEV) * 0.5).to(torch.bfloat16)
+    perm = torch.randperm(n_pages, device=DEV).int()
+    bt = torch.zeros(B, max_pages, dtype=torch.int32, device=DEV)
+    nxt = 0
+    for i, k in enumerate(kv_lens):
+        n = (k + ps - 1) // ps
+        bt[i, :n] = perm[nxt:nxt + n]
+        nxt += n
+    T = sum(q_lens)
+    q = torch.randn(T, (n_q + 2 * n_kv) * hd, device=DEV).to(torch.bfloat16)
+    qs = torch.tensor([sum(q_lens[:i]) for i in range(B)], device=DEV, dtype=torch.int32)
+    ql = torch.tensor(q_lens, device=DEV, dtype=torch.int32)
+    kl = torch.tensor(kv_lens, device=DEV, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(hd)
+    from modular_b200._native import lib
+    ops.ensure_attention_split_workspace(q.device)
+    lib().set_attn_split(2 if split else 0)
+    try:
+        outs = [ops.paged_attention(q, kv[:, 0, 1], kv[:, 1, 1], bt, qs, ql, kl, n_q, n_kv, hd, scale, kv=kv, layer=1)
+                for _ in range(2)]   # the second launch finds the counters the first one reset
+        torch.cuda.synchronize()
+    finally:
+        lib().set_attn_split(1)
+    ops.check_device_error()
+    o_ref = ref.paged_attention(q, kv[:, 0, 1], kv[:, 1, 1], bt, qs, ql, kl, n_q, n_kv, hd, scale)
+    for o in outs:
+        assert torch.isfinite(o.float()).all()
+        assert _rel_err(o, o_ref) < 1e-2
+        assert (o.float() - o_ref.float()).abs().max() < 3e-2
+    assert torch.equal(outs[0], outs[1]), "the combine order must not depend on arrival order"

@@ -132,3 +132,44 @@ def test_engine_applies_adapter_per_request():
     assert done[r_lora] == merged and done[r_base] == plain and merged != plain
     with pytest.raises(KeyError):
         llm.add_request(prompt, sp, lora_name="nope")
+
+
+def test_prefix_cache_never_crosses_adapters():
+    """A prompt of several pages run on the base model and then on an adapter (and the other way round, and
+    after the adapter was loaded again under the same name) must not reuse the other run's KV pages: adapters
+    change the k/v projections, so the page hashes carry the adapter identity."""
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.pipelines.context import SamplingParams
+
+    cfg = Llama3Config.tiny()
+    w = Llama3Weights.random_init(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    a1, sd1 = _adapter(cfg, "a1", 1, alpha=64.0)
+    a2, sd2 = _adapter(cfg, "a1", 2, alpha=64.0)       # different weights, same name
+    mk = lambda weights: LLM(cfg, weights, device="cpu", dtype=torch.float32, max_length=128, max_batch_size=4,
+                             max_batch_input_tokens=64, page_size=16, num_kv_pages=64)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True)
+    prompt = [int(t) for t in torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(1))]
+    merged1 = mk(_merged(cfg, w, sd1, a1.scale)).generate([prompt], sp)[0].tokens
+    merged2 = mk(_merged(cfg, w, sd2, a2.scale)).generate([prompt], sp)[0].tokens
+    plain = mk(w).generate([prompt], sp)[0].tokens
+
+    def run(llm, lora_name=None):
+        rid = llm.add_request(prompt, sp, lora_name=lora_name)
+        out = None
+        while llm.has_unfinished():
+            for rec in llm.step():
+                if rec.request_id == rid:
+                    out = rec.tokens
+        return out
+
+    llm = mk(w)
+    llm.load_lora("a1", sd1, alpha=64.0)
+    assert run(llm) == plain                       # base first: fills the prefix cache
+    assert run(llm, "a1") == merged1               # adapter after base
+    assert run(llm) == plain                       # base after adapter
+    hits_before = llm.kv.stats.hit_tokens if hasattr(llm.kv, "stats") else None
+    assert run(llm, "a1") == merged1               # same adapter again may hit its own pages
+    llm.unload_lora("a1")
+    llm.load_lora("a1", sd2, alpha=64.0)           # re-loaded under the same name with other weights
+    assert run(llm, "a1") == merged2
+    del hits_before

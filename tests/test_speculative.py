@@ -48,3 +48,24 @@ def test_rejection_sampling_runs_and_respects_eos():
     cut = SpeculativeDecoder(target, SpeculativeConfig("ngram", 3), max_len=256).generate(
         [3, 4, 5, 3, 4], 20, eos_token_ids=(eos,))
     assert cut == greedy[: greedy.index(eos) + 1]
+
+
+def test_generation_stops_at_the_cache_capacity():
+    """The private caches hold ceil(max_len / page) pages: prompts that do not fit are refused, generation ends
+    with a length finish before a step would write past them, and the draft cache is bounded the same way."""
+    import pytest
+
+    target = _model(0)
+    with pytest.raises(ValueError):
+        SpeculativeDecoder(target, SpeculativeConfig("ngram", 4), max_len=32).generate(list(range(32)), 4)
+    prompt = [3, 4, 5, 3, 4, 5, 3, 4]
+    want = _plain_greedy(target, prompt, 24)
+    for method, draft in (("ngram", None), ("draft_model", _model(0))):
+        dec = SpeculativeDecoder(target, SpeculativeConfig(method, 4), draft_model=draft, max_len=20)
+        out = dec.generate(prompt, 64)
+        assert len(prompt) + len(out) <= 20 and out == want[: len(out)] and len(out) >= 11
+    from modular_b200.pipelines.speculative import _SeqCache
+    cache = _SeqCache(target, 16)
+    cache.step(list(range(16)), all_logits=False)
+    with pytest.raises(ValueError):
+        cache.step([1], all_logits=False)

@@ -36,6 +36,18 @@ def test_fused_gemm_collectives(world):
 
 
 @pytest.mark.parametrize("world", [2, 4])
+def test_decode_gemm_allreduce_norm(world):
+    """Decode-step GEMM + sentinel-polled all-reduce + residual + RMSNorm: ranks agree bit for bit."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    res = _run(world, "tp_dec_worker.py", "TPD_RESULT ")
+    for r in res:
+        for (T, e_h, e_x, digest), (_, _, _, digest0) in zip(r["errs"], res[0]["errs"]):
+            assert e_h < 0.02 and e_x < 0.03, (r["rank"], T, e_h, e_x)
+            assert digest == digest0, (r["rank"], T, "ranks hold different bits")
+
+
+@pytest.mark.parametrize("world", [2, 4])
 def test_standalone_collectives_match_nccl(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -46,11 +58,14 @@ def test_standalone_collectives_match_nccl(world):
             assert err < (2e-2 if kind == "allreduce" else 1e-6), (kind, algo, n, err)
 
 
-@pytest.mark.parametrize("world,fused", [(2, "3"), (2, "0"), (2, "1"), (2, "2"), (4, "3")])
-def test_tp_matches_single_gpu(world, fused):
+@pytest.mark.parametrize("world,fused,dec", [(2, "3", "256"), (2, "0", "0"), (2, "1", "0"), (2, "2", "0"),
+                                             (2, "2", "256"), (4, "3", "256"), (4, "2", "0")])
+def test_tp_matches_single_gpu(world, fused, dec):
+    """`dec` = largest step that takes the decode-step GEMMs with the fused all-reduce (0: every step runs
+    the reduce-scatter / all-gather path)."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    res = _run(world, extra_env={"MB200_TP_FUSED": fused})
+    res = _run(world, extra_env={"MB200_TP_FUSED": fused, "MB200_DEC_TOKENS": dec})
     toks = [r["tokens"] for r in res]
     assert all(t == toks[0] for t in toks), "ranks disagree"
     ref = res[0]["ref"]

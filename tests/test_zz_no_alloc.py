@@ -57,6 +57,28 @@ def test_static_scratch_gemm_matches_regular_entry_point():
         rel = ((y.float() - expect.float()).norm() / expect.float().norm()).item()
         assert rel < 1e-2, rel
         assert torch.equal(y, expect)  # same kernels, same split: bit-identical
+        # and against the plain fp32 product, so that a fault shared by both entry points cannot hide
+        want = x.float() @ w.float().t() + (r.float() if r is not None else 0.0)
+        assert ((y.float() - want).norm() / want.norm()).item() < 1e-2
+        assert (y.float() - want).abs().max() <= 0.02 * want.abs().max() + 1e-2
+
+
+def test_static_scratch_gemm_on_a_non_blocking_stream():
+    """A C caller's own stream does not synchronise with the legacy stream: the error reader must still see
+    the finished GEMM, and the result must match the fp32 product."""
+    fn, err = _entry()
+    torch.manual_seed(1)
+    M, N, K, splits = 64, 2048, 8192, 4
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    y = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()      # torch creates its streams non-blocking
+    rc = fn(x.data_ptr(), w.data_ptr(), y.data_ptr(), None, M, N, K, K, K, N, 0, splits, 0, s.cuda_stream)
+    assert rc == 0
+    assert err() == 0            # synchronises the device, the side stream included
+    want = x.float() @ w.float().t()
+    assert ((y.float() - want).norm() / want.norm()).item() < 1e-2
 
 
 def test_static_scratch_gemm_rejects_oversize():
