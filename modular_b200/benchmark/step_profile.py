@@ -113,6 +113,12 @@ def main(argv=None) -> int:
         torch.cuda.synchronize()
         times.append(s.elapsed_time(e))
     ops.check_device_error()
+    if tp is not None:
+        # a multi-GPU step lasts as long as its slowest rank
+        import torch.distributed as dist
+        tt = torch.tensor(times, dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        times = tt.tolist()
     breakdown = None
     if args.breakdown:
         model.executor.set_profiling(True)

@@ -347,15 +347,15 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
     }
-    __threadfence();   // this thread's partials are visible device-wide before the arrival below
   }
 
   // ------------------------------------------------------------------ grid-wide meeting point
+  // The CTA barrier orders every thread's partial-tile stores before thread 0's release below, and a
+  // release is cumulative: one fence per CTA, then a fire-and-forget add, then acquire polls.
   __syncthreads();
   MB_DEC_STAMP(3);
   if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(p.state + kDecArrive, 1);
+    asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.state + kDecArrive) : "memory");
     bool ok = *abort_word == 0;
     if (ok && ld_acquire_gpu(p.state + kDecArrive) < p.G) {
       const uint64_t t_start = globaltimer_ns();

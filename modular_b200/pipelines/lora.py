@@ -59,6 +59,26 @@ class LoRAAdapter:
         return cls(name, r, (alpha if alpha is not None else r) / r, weights)
 
 
+def load_peft_adapter_files(path: str) -> tuple:
+    """Reads a PEFT adapter from a directory (``adapter_model.safetensors`` + ``adapter_config.json``) or from
+    one ``.safetensors`` file. Returns (state dict, lora_alpha or None)."""
+    import json
+    import os
+
+    from safetensors.torch import load_file
+
+    alpha = None
+    if os.path.isdir(path):
+        cfg = os.path.join(path, "adapter_config.json")
+        if os.path.exists(cfg):
+            with open(cfg) as f:
+                alpha = json.load(f).get("lora_alpha")
+        path = os.path.join(path, "adapter_model.safetensors")
+    if not os.path.exists(path):
+        raise FileNotFoundError(path)
+    return load_file(path), alpha
+
+
 class LoRAManager:
     """Keeps up to ``max_loras`` adapters resident in slots (LRU eviction of inactive ones)."""
 

@@ -147,6 +147,10 @@ def fastapi_app(settings: Settings, pipeline_config=None, tokenizer=None, factor
     app.state.pipeline = None
     app.state.model_names = {model_name}
     app.state.structured_output = bool(pipeline_config and pipeline_config.sampling.enable_structured_output)
+    app.state.lora_names = set()
+    rt = getattr(pipeline_config, "runtime", None)
+    app.state.tool_parser = getattr(rt, "tool_parser", None)
+    app.state.reasoning_parser = getattr(rt, "reasoning_parser", None)
     app.state.settings = settings
 
     @app.middleware("http")

@@ -73,7 +73,24 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
         side = _SideChannel(queue_specs["rpc_req"], queue_specs["rpc_resp"])
         cfg = scheduler_config_from(pipeline_config, llm)
         sched = TokenGenerationScheduler(cfg, pipeline, kv, queues.request, queues.response, queues.cancel)
+        def load_lora(arg):
+            if llm is None:
+                raise RuntimeError("this pipeline does not take LoRA adapters")
+            from ..pipelines.lora import load_peft_adapter_files
+            sd, alpha = load_peft_adapter_files(arg["path"])
+            llm.load_lora(arg["name"], sd, alpha=arg.get("alpha") or alpha)
+            return sorted(llm.pipeline.lora_manager.names())
+
+        def unload_lora(arg):
+            if llm is None or not llm.unload_lora(arg["name"]):
+                raise RuntimeError(f"adapter {arg['name']!r} is not loaded")
+            return sorted(llm.pipeline.lora_manager.names())
+
         handlers = {
+            "load_lora": load_lora,
+            "unload_lora": unload_lora,
+            "list_loras": lambda _a: sorted(llm.pipeline.lora_manager.names())
+            if llm is not None and llm.pipeline.lora_manager is not None else [],
             "reset_prefix_cache": lambda _a: bool(kv.reset_prefix_cache()) if kv is not None else False,
             "stats": lambda _a: {
                 "steps": sched.total_steps, "pending": sched.batch_constructor.num_requests(),

@@ -49,9 +49,12 @@ class TokenGeneratorPipeline:
         self.min_chunk = max(1, stream_min_chunk_tokens)
 
     async def next_token_chunk(self, prompt: Union[str, Sequence[int]], sampling_params: SamplingParams,
-                               request_id: Optional[str] = None) -> AsyncIterator[TokenChunk]:
+                               request_id: Optional[str] = None, lora_name: Optional[str] = None,
+                               cache_salt: int = 0) -> AsyncIterator[TokenChunk]:
         rid = request_id or uuid.uuid4().hex
         ctx = self.tokenizer.new_context(prompt, self.max_length, sampling_params, rid, self.model_name)
+        ctx.lora_name = lora_name
+        ctx.cache_salt = cache_salt
         n_prompt = ctx.tokens.prompt_len
         detok = IncrementalDetokenizer(self.tokenizer, sampling_params.stop) if sampling_params.detokenize else None
         t_start = time.perf_counter()
@@ -89,9 +92,10 @@ class TokenGeneratorPipeline:
             METRICS.tpot_ms.observe((t_last - t_start) * 1e3 / n_out)
         METRICS.request_time_ms.observe((time.perf_counter() - t_start) * 1e3)
 
-    async def all_tokens(self, prompt, sampling_params: SamplingParams, request_id: Optional[str] = None) -> TokenChunk:
+    async def all_tokens(self, prompt, sampling_params: SamplingParams, request_id: Optional[str] = None,
+                         lora_name: Optional[str] = None, cache_salt: int = 0) -> TokenChunk:
         text, ids, reason, n_prompt, n_out, lps = "", [], None, 0, 0, []
-        async for ch in self.next_token_chunk(prompt, sampling_params, request_id):
+        async for ch in self.next_token_chunk(prompt, sampling_params, request_id, lora_name, cache_salt):
             text += ch.text
             ids.extend(ch.token_ids)
             lps.extend(ch.logprobs or [])

@@ -17,10 +17,15 @@ from fastapi import APIRouter, HTTPException, Request
 from fastapi.responses import JSONResponse, StreamingResponse
 
 from ...pipelines.context import SamplingParams
+import asyncio
+import hashlib
+
+from ..parser import ReasoningSplitter, get_tool_parser, split_reasoning
 from ..schemas.openai import (ChatChoice, ChatChoiceMessage, ChatChunkChoice, ChatCompletionChunk,
                               ChatCompletionRequest, ChatCompletionResponse, ChatDelta, CompletionChoice,
                               CompletionRequest, CompletionResponse, ErrorBody, ErrorResponse, ModelCard,
-                              ModelList, Usage, EmbeddingData, EmbeddingsRequest, EmbeddingsResponse)
+                              ModelList, Usage, EmbeddingData, EmbeddingsRequest, EmbeddingsResponse,
+                              LoadLoraRequest, UnloadLoraRequest)
 from ..telemetry.metrics import METRICS
 from ..worker_interface import RequestQueueFull
 
@@ -92,10 +97,61 @@ def _pipeline(request: Request):
     return p
 
 
-def _check_model(request: Request, name: str) -> None:
+def _check_model(request: Request, name: str) -> Optional[str]:
+    """Validates the ``model`` field; returns the LoRA adapter it names (requests address an adapter by using its
+    name as the model, reference: openai_routes.py LoRA handling) or None for the base model."""
     served = request.app.state.model_names
-    if name not in served:
-        raise HTTPException(status_code=404, detail=f"model {name!r} is not served here (available: {sorted(served)})")
+    if name in served:
+        return None
+    if name in getattr(request.app.state, "lora_names", ()):
+        return name
+    raise HTTPException(status_code=404, detail=f"model {name!r} is not served here (available: "
+                                                f"{sorted(served | set(getattr(request.app.state, 'lora_names', ())))})")
+
+
+def _salt_of(req) -> int:
+    s = getattr(req, "cache_salt", None)
+    if not s:
+        return 0
+    return int.from_bytes(hashlib.blake2b(str(s).encode(), digest_size=8).digest(), "little") & 0x7FFFFFFFFFFFFFFF
+
+
+def _with_seed(sp: SamplingParams, i: int) -> SamplingParams:
+    """The i-th of ``n`` samples of one request: same parameters, its own seed."""
+    if i == 0:
+        return sp
+    import dataclasses
+    return dataclasses.replace(sp, seed=(sp.seed or 0) + i)
+
+
+async def _merge_streams(gens: list):
+    """Yields (index, item) from several async generators as items arrive."""
+    q: asyncio.Queue = asyncio.Queue()
+    done = object()
+
+    async def pump(i, g):
+        try:
+            async for item in g:
+                await q.put((i, item))
+        except Exception as e:  # noqa: BLE001
+            await q.put((i, e))
+        finally:
+            await q.put((i, done))
+
+    tasks = [asyncio.ensure_future(pump(i, g)) for i, g in enumerate(gens)]
+    left = len(tasks)
+    try:
+        while left:
+            i, item = await q.get()
+            if item is done:
+                left -= 1
+            elif isinstance(item, Exception):
+                raise item
+            else:
+                yield i, item
+    finally:
+        for t in tasks:
+            t.cancel()
 
 
 def _sse(obj) -> bytes:
@@ -107,14 +163,49 @@ def _sse(obj) -> bytes:
 # ------------------------------------------------------------------ models / health
 @router.get("/v1/models")
 async def list_models(request: Request) -> ModelList:
-    return ModelList(data=[ModelCard(id=n) for n in sorted(request.app.state.model_names)])
+    names = set(request.app.state.model_names) | set(getattr(request.app.state, "lora_names", ()))
+    return ModelList(data=[ModelCard(id=n) for n in sorted(names)])
 
 
 @router.get("/v1/models/{model_id:path}")
 async def get_model(model_id: str, request: Request):
-    if model_id not in request.app.state.model_names:
+    if model_id not in request.app.state.model_names and model_id not in getattr(request.app.state, "lora_names", ()):
         return error_response(404, f"model {model_id!r} not found", "not_found_error")
     return ModelCard(id=model_id)
+
+
+# ------------------------------------------------------------------ LoRA administration
+@router.post("/v1/load_lora_adapter")
+async def load_lora_adapter(req: LoadLoraRequest, request: Request):
+    """Loads a PEFT-layout adapter directory (or .safetensors file) into the model worker; requests then select it
+    with ``model = lora_name``. Reference: max/python/max/serve/router/openai_routes.py:3217."""
+    rpc = getattr(request.app.state, "rpc", None)
+    if rpc is None:
+        return error_response(503, "model worker is not ready", "service_unavailable")
+    if req.lora_name in request.app.state.model_names:
+        return error_response(400, f"{req.lora_name!r} is the name of the base model")
+    try:
+        await rpc.call("load_lora", {"name": req.lora_name, "path": req.lora_path, "alpha": req.alpha}, timeout_s=120.0)
+    except (RuntimeError, TimeoutError) as e:
+        return error_response(400, f"could not load adapter {req.lora_name!r}: {e}")
+    request.app.state.lora_names = set(getattr(request.app.state, "lora_names", ())) | {req.lora_name}
+    return {"status": "success", "message": f"LoRA adapter {req.lora_name!r} loaded"}
+
+
+@router.post("/v1/unload_lora_adapter")
+async def unload_lora_adapter(req: UnloadLoraRequest, request: Request):
+    """Reference: max/python/max/serve/router/openai_routes.py:3295."""
+    rpc = getattr(request.app.state, "rpc", None)
+    if rpc is None:
+        return error_response(503, "model worker is not ready", "service_unavailable")
+    if req.lora_name not in getattr(request.app.state, "lora_names", ()):
+        return error_response(404, f"LoRA adapter {req.lora_name!r} is not loaded", "not_found_error")
+    try:
+        await rpc.call("unload_lora", {"name": req.lora_name}, timeout_s=30.0)
+    except (RuntimeError, TimeoutError) as e:
+        return error_response(400, f"could not unload adapter {req.lora_name!r}: {e}")
+    request.app.state.lora_names = set(request.app.state.lora_names) - {req.lora_name}
+    return {"status": "success", "message": f"LoRA adapter {req.lora_name!r} unloaded"}
 
 
 @router.get("/v1/health")
@@ -137,11 +228,12 @@ def _prompts_of(req: CompletionRequest) -> list:
 @router.post("/v1/completions")
 async def create_completion(req: CompletionRequest, request: Request):
     pipeline = _pipeline(request)
-    _check_model(request, req.model)
-    if req.n != 1:
-        return error_response(400, "n > 1 is not supported")
+    lora = _check_model(request, req.model)
+    if req.n < 1 or req.n > 16:
+        return error_response(400, "n must be between 1 and 16")
     prompts = _prompts_of(req)
     sp = sampling_from_request(req, None)
+    salt = _salt_of(req)
     rid = getattr(request.state, "request_id", uuid.uuid4().hex)
     cid = f"cmpl-{rid}"
     try:
@@ -150,30 +242,37 @@ async def create_completion(req: CompletionRequest, request: Request):
                 return error_response(400, "streaming supports a single prompt")
 
             async def gen() -> AsyncIterator[bytes]:
-                usage = Usage()
+                usages = [Usage() for _ in range(req.n)]
                 try:
-                    async for ch in pipeline.next_token_chunk(prompts[0], sp, rid):
-                        usage = Usage(prompt_tokens=ch.prompt_tokens, completion_tokens=ch.completion_tokens,
-                                      total_tokens=ch.prompt_tokens + ch.completion_tokens)
+                    streams = [pipeline.next_token_chunk(prompts[0], _with_seed(sp, i), f"{rid}-{i}" if req.n > 1 else rid,
+                                                         lora, salt) for i in range(req.n)]
+                    async for i, ch in _merge_streams(streams):
+                        usages[i] = Usage(prompt_tokens=ch.prompt_tokens, completion_tokens=ch.completion_tokens)
                         yield _sse(CompletionResponse(id=cid, model=req.model, choices=[
-                            CompletionChoice(text=ch.text, finish_reason=ch.finish_reason)]))
+                            CompletionChoice(index=i, text=ch.text, finish_reason=ch.finish_reason)]))
                     if req.stream_options and req.stream_options.include_usage:
-                        yield _sse(CompletionResponse(id=cid, model=req.model, choices=[], usage=usage))
+                        u = Usage(prompt_tokens=usages[0].prompt_tokens,
+                                  completion_tokens=sum(x.completion_tokens for x in usages))
+                        u.total_tokens = u.prompt_tokens + u.completion_tokens
+                        yield _sse(CompletionResponse(id=cid, model=req.model, choices=[], usage=u))
                 except Exception as e:  # noqa: BLE001
                     METRICS.request_errors.inc()
                     yield _sse(json.dumps(ErrorResponse(error=ErrorBody(message=str(e), type="server_error")).model_dump()))
                 yield _sse("[DONE]")
 
             return StreamingResponse(gen(), media_type="text/event-stream")
+        jobs = [(pi, si) for pi in range(len(prompts)) for si in range(req.n)]
+        results = await asyncio.gather(*[
+            pipeline.all_tokens(prompts[pi], _with_seed(sp, si), f"{rid}-{pi}-{si}", lora, salt) for pi, si in jobs])
         choices, usage = [], Usage()
-        for i, p in enumerate(prompts):
-            ch = await pipeline.all_tokens(p, sp, f"{rid}-{i}")
+        for k, ((pi, si), ch) in enumerate(zip(jobs, results)):
             text = ch.text
-            if req.echo and isinstance(p, str):
-                text = p + text
-            choices.append(CompletionChoice(index=i, text=text, finish_reason=ch.finish_reason,
+            if req.echo and isinstance(prompts[pi], str):
+                text = prompts[pi] + text
+            choices.append(CompletionChoice(index=k, text=text, finish_reason=ch.finish_reason,
                                             logprobs=_completion_logprobs(pipeline, ch)))
-            usage.prompt_tokens += ch.prompt_tokens
+            if si == 0:
+                usage.prompt_tokens += ch.prompt_tokens
             usage.completion_tokens += ch.completion_tokens
         usage.total_tokens = usage.prompt_tokens + usage.completion_tokens
         return CompletionResponse(id=cid, model=req.model, choices=choices, usage=usage)
@@ -191,46 +290,107 @@ def _chat_prompt(pipeline, req: ChatCompletionRequest) -> str:
     return pipeline.tokenizer.apply_chat_template(msgs, tools=req.tools, add_generation_prompt=True)
 
 
+def _tool_parser_for(request: Request, req: ChatCompletionRequest):
+    """A fresh tool-call parser when the request offers tools and does not forbid their use."""
+    if not req.tools or req.tool_choice == "none":
+        return None
+    return get_tool_parser(getattr(request.app.state, "tool_parser", None) or "llama")
+
+
+def _finish_message(text: str, parser, reasoning_on: bool):
+    """(message, finish_reason override) of a complete answer."""
+    reasoning = None
+    if reasoning_on:
+        reasoning, text = split_reasoning(text)
+    if parser is not None:
+        try:
+            parsed = parser.parse_complete(text)
+        except ValueError:
+            parsed = None
+        if parsed is not None and parsed.tool_calls:
+            return ChatChoiceMessage(content=parsed.content, reasoning_content=reasoning,
+                                     tool_calls=[c.to_openai() for c in parsed.tool_calls]), "tool_calls"
+    return ChatChoiceMessage(content=text, reasoning_content=reasoning), None
+
+
 @router.post("/v1/chat/completions")
 async def create_chat_completion(req: ChatCompletionRequest, request: Request):
     pipeline = _pipeline(request)
-    _check_model(request, req.model)
-    if req.n != 1:
-        return error_response(400, "n > 1 is not supported")
+    lora = _check_model(request, req.model)
+    if req.n < 1 or req.n > 16:
+        return error_response(400, "n must be between 1 and 16")
     if req.response_format is not None and req.response_format.type != "text":
         if not request.app.state.structured_output:
             return error_response(400, "response_format requires the server to run with --enable-structured-output")
     sp = sampling_from_request(req, None)
+    salt = _salt_of(req)
     prompt = _chat_prompt(pipeline, req)
+    reasoning_on = bool(getattr(request.app.state, "reasoning_parser", None))
+    try:
+        _tool_parser_for(request, req)
+    except ValueError as e:
+        return error_response(400, str(e))
     rid = getattr(request.state, "request_id", uuid.uuid4().hex)
     cid = f"chatcmpl-{rid}"
     try:
         if req.stream:
             async def gen() -> AsyncIterator[bytes]:
-                usage = Usage()
-                yield _sse(ChatCompletionChunk(id=cid, model=req.model,
-                                               choices=[ChatChunkChoice(delta=ChatDelta(role="assistant", content=""))]))
+                n = req.n
+                usages = [Usage() for _ in range(n)]
+                parsers = [_tool_parser_for(request, req) for _ in range(n)]
+                splitters = [ReasoningSplitter() if reasoning_on else None for _ in range(n)]
+                n_calls = [0] * n
+                for i in range(n):
+                    yield _sse(ChatCompletionChunk(id=cid, model=req.model, choices=[
+                        ChatChunkChoice(index=i, delta=ChatDelta(role="assistant", content=""))]))
                 try:
-                    async for ch in pipeline.next_token_chunk(prompt, sp, rid):
-                        usage = Usage(prompt_tokens=ch.prompt_tokens, completion_tokens=ch.completion_tokens,
-                                      total_tokens=ch.prompt_tokens + ch.completion_tokens)
-                        if ch.text or ch.finish_reason:
+                    streams = [pipeline.next_token_chunk(prompt, _with_seed(sp, i), f"{rid}-{i}" if n > 1 else rid, lora, salt)
+                               for i in range(n)]
+                    async for i, ch in _merge_streams(streams):
+                        usages[i] = Usage(prompt_tokens=ch.prompt_tokens, completion_tokens=ch.completion_tokens)
+                        final = ch.finish_reason is not None
+                        text, reasoning = ch.text, ""
+                        if splitters[i] is not None:
+                            reasoning, text = splitters[i].push(text, final)
+                        calls = []
+                        if parsers[i] is not None:
+                            text, calls = parsers[i].parse_delta(text, final)
+                        if reasoning:
                             yield _sse(ChatCompletionChunk(id=cid, model=req.model, choices=[ChatChunkChoice(
-                                delta=ChatDelta(content=ch.text or None), finish_reason=ch.finish_reason)]))
+                                index=i, delta=ChatDelta(reasoning_content=reasoning))]))
+                        for c in calls:
+                            yield _sse(ChatCompletionChunk(id=cid, model=req.model, choices=[ChatChunkChoice(
+                                index=i, delta=ChatDelta(tool_calls=[c.to_openai(index=n_calls[i])]))]))
+                            n_calls[i] += 1
+                        reason = ch.finish_reason
+                        if final and n_calls[i] and reason == "stop":
+                            reason = "tool_calls"
+                        if text or reason:
+                            yield _sse(ChatCompletionChunk(id=cid, model=req.model, choices=[ChatChunkChoice(
+                                index=i, delta=ChatDelta(content=text or None), finish_reason=reason)]))
                     if req.stream_options and req.stream_options.include_usage:
-                        yield _sse(ChatCompletionChunk(id=cid, model=req.model, choices=[], usage=usage))
+                        u = Usage(prompt_tokens=usages[0].prompt_tokens,
+                                  completion_tokens=sum(x.completion_tokens for x in usages))
+                        u.total_tokens = u.prompt_tokens + u.completion_tokens
+                        yield _sse(ChatCompletionChunk(id=cid, model=req.model, choices=[], usage=u))
                 except Exception as e:  # noqa: BLE001
                     METRICS.request_errors.inc()
                     yield _sse(json.dumps(ErrorResponse(error=ErrorBody(message=str(e), type="server_error")).model_dump()))
                 yield _sse("[DONE]")
 
             return StreamingResponse(gen(), media_type="text/event-stream")
-        ch = await pipeline.all_tokens(prompt, sp, rid)
-        usage = Usage(prompt_tokens=ch.prompt_tokens, completion_tokens=ch.completion_tokens,
-                      total_tokens=ch.prompt_tokens + ch.completion_tokens)
-        return ChatCompletionResponse(id=cid, model=req.model, usage=usage, choices=[
-            ChatChoice(message=ChatChoiceMessage(content=ch.text), finish_reason=ch.finish_reason,
-                       logprobs=_chat_logprobs(pipeline, ch))])
+        results = await asyncio.gather(*[
+            pipeline.all_tokens(prompt, _with_seed(sp, i), f"{rid}-{i}" if req.n > 1 else rid, lora, salt)
+            for i in range(req.n)])
+        usage = Usage(prompt_tokens=results[0].prompt_tokens,
+                      completion_tokens=sum(r.completion_tokens for r in results))
+        usage.total_tokens = usage.prompt_tokens + usage.completion_tokens
+        choices = []
+        for i, ch in enumerate(results):
+            msg, reason = _finish_message(ch.text, _tool_parser_for(request, req), reasoning_on)
+            choices.append(ChatChoice(index=i, message=msg, logprobs=_chat_logprobs(pipeline, ch),
+                                      finish_reason=reason if (reason and ch.finish_reason == "stop") else ch.finish_reason))
+        return ChatCompletionResponse(id=cid, model=req.model, usage=usage, choices=choices)
     except RequestQueueFull as e:
         return error_response(429, str(e), "rate_limit_error")
     except ValueError as e:

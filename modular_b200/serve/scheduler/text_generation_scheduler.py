@@ -89,6 +89,15 @@ class TokenGenerationScheduler:
                     self.embeddings.enqueue(ctx)
                 n += 1
                 continue
+            if ctx.lora_name:
+                # a request that names an adapter which is not (or no longer) loaded is refused here: it must
+                # neither run on the base weights nor take the worker down
+                mgr = getattr(self.pipeline, "lora_manager", None)
+                if mgr is None or ctx.lora_name not in mgr.names():
+                    self.response_queue.put_nowait({ctx.request_id: TextGenerationOutput(
+                        ctx.request_id, [], GenerationStatus.CANCELLED)})
+                    n += 1
+                    continue
             self._contexts[ctx.request_id] = ctx
             self.batch_constructor.enqueue_new_request(ctx)
             n += 1

@@ -46,6 +46,7 @@ class _SamplingMixin(_Req):
     logprobs: Optional[Union[bool, int]] = None
     top_logprobs: Optional[int] = None
     user: Optional[str] = None
+    cache_salt: Optional[str] = None    # requests with different salts never share prefix-cache pages
 
 
 class CompletionRequest(_SamplingMixin):
@@ -155,6 +156,16 @@ class ModelCard(BaseModel):
 class ModelList(BaseModel):
     object: str = "list"
     data: list[ModelCard] = Field(default_factory=list)
+
+
+class LoadLoraRequest(_Req):
+    lora_name: str
+    lora_path: str
+    alpha: Optional[float] = None
+
+
+class UnloadLoraRequest(_Req):
+    lora_name: str
 
 
 class ErrorBody(BaseModel):

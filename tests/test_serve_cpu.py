@@ -253,3 +253,115 @@ def test_step_token_alignment_trims_overshoot():
     b4.used = 64
     c4 = ctx(1024)
     assert b4.status_after_context(c4) is BudgetStatus.BUDGET_AVAILABLE and c4.tokens.active_length == 1024
+
+
+# ---------------------------------------------------------------------------- tool calls, reasoning, n > 1, LoRA admin
+def test_tool_and_reasoning_parsers():
+    from modular_b200.serve.parser import (ReasoningSplitter, get_tool_parser, parse_json_objects, split_reasoning)
+
+    assert parse_json_objects('x {"a": "}{"} y {"b": {"c": 1}} {bad') == [{"a": "}{"}, {"b": {"c": 1}}]
+    p = get_tool_parser("llama")
+    r = p.parse_complete('<|python_tag|>{"name": "get_weather", "parameters": {"city": "Paris"}}; '
+                         '{"name": "f", "parameters": {}}')
+    assert [c.name for c in r.tool_calls] == ["get_weather", "f"] and r.content is None
+    assert json.loads(r.tool_calls[0].arguments) == {"city": "Paris"} and r.tool_calls[0].id.startswith("call_")
+    assert p.parse_complete("plain answer").tool_calls == []
+    with pytest.raises(ValueError):
+        p.parse_complete('{"name": "no_parameters"}')
+    # streaming: nothing leaks while the JSON is open, the call comes out when it closes, plain text passes through
+    p.reset()
+    outs = [p.parse_delta(c) for c in ['{"name": "g', 'et", "param', 'eters": {"a": 1}}']] + [p.parse_delta("", True)]
+    assert all(t == "" for t, _ in outs) and sum(len(c) for _, c in outs) == 1 and outs[2][1][0].name == "get"
+    p.reset()
+    assert [p.parse_delta(c)[0] for c in ["Hel", "lo {", "}"]] == ["Hel", "lo {", "}"]
+    h = get_tool_parser("hermes")
+    r = h.parse_complete('ok <tool_call>{"name": "a", "arguments": {"x": 1}}</tool_call> done')
+    assert r.content == "ok  done" and r.tool_calls[0].to_openai()["function"] == {"name": "a", "arguments": '{"x": 1}'}
+    with pytest.raises(ValueError):
+        get_tool_parser("nope")
+    assert split_reasoning("<think>abc</think>\nanswer") == ("abc", "answer")
+    assert split_reasoning("no tags") == (None, "no tags")
+    s = ReasoningSplitter()
+    parts = [s.push(c) for c in ["<th", "ink>rea", "son</th", "ink>\nvis", "ible"]] + [s.push("", True)]
+    assert "".join(a for a, _ in parts) == "reason" and "".join(b for _, b in parts) == "visible"
+
+
+def test_chat_tool_calls_and_n(echo_client):
+    echo_client.app.state.tool_parser = "hermes"
+    tools = [{"type": "function", "function": {"name": "lookup", "parameters": {"type": "object"}}}]
+    call = '<tool_call>{"name": "lookup", "arguments": {"q": "x"}}</tool_call>'
+    body = {"model": "echo", "max_tokens": 400, "tools": tools, "messages": [{"role": "user", "content": call}]}
+    r = echo_client.post("/v1/chat/completions", json=body).json()
+    ch = r["choices"][0]
+    assert ch["finish_reason"] == "tool_calls" and ch["message"]["tool_calls"][0]["function"]["name"] == "lookup"
+    assert json.loads(ch["message"]["tool_calls"][0]["function"]["arguments"]) == {"q": "x"}
+    # without tools in the request the same text stays content
+    plain = echo_client.post("/v1/chat/completions", json={k: v for k, v in body.items() if k != "tools"}).json()
+    assert plain["choices"][0]["message"].get("tool_calls") is None and "<tool_call>" in plain["choices"][0]["message"]["content"]
+    # streaming: the call arrives as a tool_calls delta, the stream ends with finish_reason tool_calls
+    calls, reasons, text = [], [], ""
+    with echo_client.stream("POST", "/v1/chat/completions", json=dict(body, stream=True)) as resp:
+        for line in resp.iter_lines():
+            if not line.startswith("data: ") or line == "data: [DONE]":
+                continue
+            for c in json.loads(line[6:])["choices"]:
+                calls += c["delta"].get("tool_calls") or []
+                text += c["delta"].get("content") or ""
+                if c.get("finish_reason"):
+                    reasons.append(c["finish_reason"])
+    assert len(calls) == 1 and calls[0]["index"] == 0 and calls[0]["function"]["name"] == "lookup"
+    assert reasons == ["tool_calls"] and "<tool_call>" not in text
+    # n > 1: one choice per sample, usage counts the prompt once
+    r = echo_client.post("/v1/completions", json={"model": "echo", "prompt": "abc", "max_tokens": 16, "n": 3}).json()
+    assert [c["index"] for c in r["choices"]] == [0, 1, 2] and all(c["text"] == "abc" for c in r["choices"])
+    assert r["usage"]["prompt_tokens"] == 4 and r["usage"]["completion_tokens"] >= 9
+    r = echo_client.post("/v1/chat/completions", json={"model": "echo", "n": 2, "max_tokens": 64,
+                                                       "messages": [{"role": "user", "content": "hi"}]}).json()
+    assert len(r["choices"]) == 2 and r["choices"][0]["message"]["content"] == r["choices"][1]["message"]["content"]
+    seen = set()
+    with echo_client.stream("POST", "/v1/completions", json={"model": "echo", "prompt": "abcd", "max_tokens": 16,
+                                                             "n": 2, "stream": True}) as resp:
+        for line in resp.iter_lines():
+            if line.startswith("data: {"):
+                seen |= {c["index"] for c in json.loads(line[6:])["choices"]}
+    assert seen == {0, 1}
+    assert echo_client.post("/v1/completions", json={"model": "echo", "prompt": "a", "n": 0}).status_code == 400
+
+
+def test_lora_admin_routes(tmp_path):
+    """Load an adapter over HTTP, address it with ``model = <adapter name>``, unload it again."""
+    import torch
+    from safetensors.torch import save_file
+
+    from modular_b200.models.llama3 import Llama3Config
+
+    cfg = Llama3Config.tiny()
+    g = torch.Generator().manual_seed(3)
+    sd = {}
+    for i in range(cfg.num_hidden_layers):
+        sd[f"base_model.model.model.layers.{i}.self_attn.q_proj.lora_A.weight"] = torch.randn(8, cfg.hidden_size, generator=g) * 0.3
+        sd[f"base_model.model.model.layers.{i}.self_attn.q_proj.lora_B.weight"] = torch.randn(cfg.q_dim, 8, generator=g) * 0.3
+    (tmp_path / "ad").mkdir()
+    save_file(sd, str(tmp_path / "ad" / "adapter_model.safetensors"))
+    (tmp_path / "ad" / "adapter_config.json").write_text(json.dumps({"r": 8, "lora_alpha": 64}))
+    pc = _config(model_path="preset:tiny-llama", devices="cpu", max_length=256, max_batch_size=4,
+                 max_batch_input_tokens=128, kv_cache_page_size=16)
+    tokenizer, factory = PIPELINE_REGISTRY.retrieve_factory(pc)
+    app = fastapi_app(Settings(), pc, tokenizer, factory, "tiny", 256)
+    # the byte tokenizer renders ids above 255 alike, so outputs are compared through their log-probabilities
+    req = {"prompt": [5, 6, 7, 8, 9, 10, 11, 12], "max_tokens": 8, "temperature": 0, "ignore_eos": True, "logprobs": 1}
+    lps = lambda r: [round(v, 4) for v in r.json()["choices"][0]["logprobs"]["token_logprobs"]]
+    with TestClient(app) as c:
+        assert c.post("/v1/completions", json=dict(req, model="ad1")).status_code == 404
+        bad = c.post("/v1/load_lora_adapter", json={"lora_name": "ad1", "lora_path": str(tmp_path / "missing")})
+        assert bad.status_code == 400
+        ok = c.post("/v1/load_lora_adapter", json={"lora_name": "ad1", "lora_path": str(tmp_path / "ad")})
+        assert ok.status_code == 200, ok.text
+        assert "ad1" in [m["id"] for m in c.get("/v1/models").json()["data"]]
+        base = lps(c.post("/v1/completions", json=dict(req, model="tiny")))
+        tuned = lps(c.post("/v1/completions", json=dict(req, model="ad1")))
+        again = lps(c.post("/v1/completions", json=dict(req, model="tiny")))
+        assert tuned != base and again == base          # the adapter changes the output; the base model is untouched
+        assert c.post("/v1/unload_lora_adapter", json={"lora_name": "ad1"}).status_code == 200
+        assert c.post("/v1/unload_lora_adapter", json={"lora_name": "ad1"}).status_code == 404
+        assert c.post("/v1/completions", json=dict(req, model="ad1")).status_code == 404
