@@ -30,7 +30,7 @@ from .pipelines.llm import TokenGeneratorPipeline
 from .process_control import SubprocessExit, subprocess_manager
 from .router import extra_routes, openai_routes
 from .router.openai_routes import error_response
-from .telemetry.metrics import METRICS, configure_metrics
+from .telemetry.metrics import METRICS, configure_metrics, record_batch_metrics
 from .worker_interface import ModelWorkerProxy, ReplicaRouter, RequestQueueFull, WorkerQueues, ZmqQueueSpec
 
 logger = logging.getLogger("modular_b200.serve")
@@ -102,11 +102,14 @@ def make_lifespan(settings: Settings, pipeline_config, tokenizer, factory: Calla
 
     @contextlib.asynccontextmanager
     async def lifespan(app: FastAPI):
+        t_start = time.monotonic()
         async with contextlib.AsyncExitStack() as stack:
-            proxies, rpcs, watchers = [], [], []
+            proxies, rpcs, watchers, metric_pulls = [], [], [], []
             for i in range(n_rep):
-                specs = {k: ZmqQueueSpec.create(f"{k}{i}") for k in ("request", "response", "cancel", "rpc_req", "rpc_resp")}
+                specs = {k: ZmqQueueSpec.create(f"{k}{i}")
+                         for k in ("request", "response", "cancel", "rpc_req", "rpc_resp", "metrics")}
                 response_pull = specs["response"].pull(bind=True)
+                metric_pulls.append(specs["metrics"].pull(bind=True))
                 _pm, watcher = await stack.enter_async_context(subprocess_manager(
                     f"model-worker-{i}", model_worker_main,
                     (factories[i], _replica_config(pipeline_config, i, n_rep), specs, settings),
@@ -129,10 +132,29 @@ def make_lifespan(settings: Settings, pipeline_config, tokenizer, factory: Calla
 
             app.state.worker_watcher = watchers[0] if n_rep == 1 else asyncio.ensure_future(first_failure())
             app.state.proxy = proxy
+            METRICS.pipeline_load.inc(n_rep)
+            METRICS.model_load_time_ms.set((time.monotonic() - t_start) * 1e3)
+
+            async def consume_worker_metrics():
+                """Replays the workers' per-step metrics into this process's instruments."""
+                while True:
+                    idle = True
+                    for q_ in metric_pulls:
+                        for _ in range(256):
+                            try:
+                                record_batch_metrics(q_.get_nowait())
+                                idle = False
+                            except queue.Empty:
+                                break
+                    METRICS.queue_depth.set(getattr(proxy, "pending", 0) or 0)
+                    await asyncio.sleep(0.05 if idle else 0.0)
+
+            metrics_task = asyncio.ensure_future(consume_worker_metrics())
             logger.info("server ready: model %s on %d replica(s)", model_name, n_rep)
             try:
                 yield
             finally:
+                metrics_task.cancel()
                 await proxy.stop()
                 app.state.pipeline = None
     return lifespan

@@ -72,7 +72,18 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
                               cancel=queue_specs["cancel"].pull(bind=True))
         side = _SideChannel(queue_specs["rpc_req"], queue_specs["rpc_resp"])
         cfg = scheduler_config_from(pipeline_config, llm)
-        sched = TokenGenerationScheduler(cfg, pipeline, kv, queues.request, queues.response, queues.cancel)
+        # per-step metrics travel to the API process, which owns the Prometheus registry; a full queue drops them
+        sink = None
+        if "metrics" in queue_specs and str(getattr(settings.metric_recording, "value", settings.metric_recording)).upper() != "NOOP":
+            mq = queue_specs["metrics"].push(bind=False)
+
+            def sink(m):
+                try:
+                    mq.put_nowait(m.to_dict())
+                except Exception:  # noqa: BLE001
+                    pass
+        sched = TokenGenerationScheduler(cfg, pipeline, kv, queues.request, queues.response, queues.cancel,
+                                         metrics_sink=sink)
         def load_lora(arg):
             if llm is None:
                 raise RuntimeError("this pipeline does not take LoRA adapters")

@@ -52,10 +52,15 @@ class TokenGeneratorPipeline:
                                request_id: Optional[str] = None, lora_name: Optional[str] = None,
                                cache_salt: int = 0) -> AsyncIterator[TokenChunk]:
         rid = request_id or uuid.uuid4().hex
+        t_in = time.perf_counter()
         ctx = self.tokenizer.new_context(prompt, self.max_length, sampling_params, rid, self.model_name)
         ctx.lora_name = lora_name
         ctx.cache_salt = cache_salt
         n_prompt = ctx.tokens.prompt_len
+        METRICS.input_processing_ms.observe((time.perf_counter() - t_in) * 1e3)
+        METRICS.input_tokens_per_request.observe(n_prompt)
+        if isinstance(prompt, str):
+            METRICS.input_characters.inc(len(prompt))
         detok = IncrementalDetokenizer(self.tokenizer, sampling_params.stop) if sampling_params.detokenize else None
         t_start = time.perf_counter()
         t_last: Optional[float] = None
@@ -75,6 +80,7 @@ class TokenGeneratorPipeline:
                 t_last = now
                 n_out += len(out.tokens)
             text = detok.push(out.tokens, final=out.is_done) if detok is not None else ""
+            METRICS.output_processing_ms.observe((time.perf_counter() - now) * 1e3)
             stopped = detok is not None and detok.stopped
             buf_ids.extend(out.tokens)
             if getattr(out, "log_probabilities", None):
@@ -88,6 +94,7 @@ class TokenGeneratorPipeline:
             if done:
                 break
         METRICS.output_tokens.inc(n_out)
+        METRICS.output_tokens_per_request.observe(n_out)
         if n_out > 1 and t_last is not None:
             METRICS.tpot_ms.observe((t_last - t_start) * 1e3 / n_out)
         METRICS.request_time_ms.observe((time.perf_counter() - t_start) * 1e3)

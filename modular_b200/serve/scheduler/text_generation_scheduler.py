@@ -38,6 +38,23 @@ class BatchMetrics:
     cache_hit_rate: float = 0.0
     preemptions: int = 0
     pending_requests: int = 0
+    batch_creation_s: float = 0.0
+    context_tokens: int = 0          # resident context of the step's sequences (cached + new tokens)
+    terminated: int = 0              # requests that finished in this step
+    total_blocks: int = 0
+    used_blocks: int = 0
+    cache_hit_tokens: int = 0        # prompt tokens served from the prefix cache since the previous step
+    cache_miss_tokens: int = 0
+    used_host_kv_pct: float = 0.0
+    used_disk_kv_pct: float = 0.0
+
+    def to_dict(self) -> dict:
+        """Flat form for the telemetry queue (keys as :func:`serve.telemetry.metrics.record_batch_metrics` reads them)."""
+        import dataclasses
+        d = dataclasses.asdict(self)
+        d["used_kv_pct"] = d.pop("kv_used_pct")
+        d["preempted"] = d.pop("preemptions")
+        return d
 
     @property
     def prompt_throughput(self) -> float:
@@ -63,6 +80,7 @@ class TokenGenerationScheduler:
         self.last_metrics = BatchMetrics()
         self._contexts: dict[str, TextContext] = {}
         self.total_steps = 0
+        self._cache_seen = (0, 0)        # (hit tokens, queried tokens) already reported
         # requests with task == "embed" are answered by an embeddings scheduler when the model can encode
         self.embeddings = None
         model = getattr(pipeline, "model", None)
@@ -142,6 +160,7 @@ class TokenGenerationScheduler:
         t0 = time.perf_counter()
         embedded = self.embeddings.run_iteration() if self.embeddings is not None else 0
         batch = self.batch_constructor.construct_batch()
+        t_built = time.perf_counter()
         if not batch.contexts and not self.pipeline.has_pending():
             self._handle_cancels()
             return SchedulerProgress.MADE_PROGRESS if embedded else SchedulerProgress.NO_PROGRESS
@@ -152,11 +171,25 @@ class TokenGenerationScheduler:
         self._finish(outputs)
         self._handle_cancels()
         dt = time.perf_counter() - t0
+        kv = self.kv
         m = BatchMetrics(batch.batch_type.value, len(batch), batch.num_ce, batch.num_tg,
                          batch.input_tokens, sum(len(o.tokens) for o in outputs.values()), dt,
-                         self.kv.used_blocks_pct if self.kv is not None else 0.0,
-                         self.kv.cache_hit_rate if self.kv is not None else 0.0,
-                         batch.preempted, self.batch_constructor.num_requests())
+                         kv.used_blocks_pct if kv is not None else 0.0,
+                         kv.cache_hit_rate if kv is not None else 0.0,
+                         batch.preempted, self.batch_constructor.num_requests(),
+                         batch_creation_s=t_built - t0,
+                         context_tokens=sum(c.tokens.processed for c in batch.contexts),
+                         terminated=sum(1 for o in outputs.values() if o.is_done))
+        if kv is not None:
+            hit, asked = kv.prefix_hit_tokens, kv.prefix_query_tokens
+            m.cache_hit_tokens = hit - self._cache_seen[0]
+            m.cache_miss_tokens = (asked - self._cache_seen[1]) - m.cache_hit_tokens
+            self._cache_seen = (hit, asked)
+            m.total_blocks, m.used_blocks = kv.pool.usable_blocks, kv.pool.used_blocks
+            tiers = getattr(kv, "tiers", None)
+            if tiers is not None:
+                m.used_host_kv_pct = getattr(tiers, "host_used_pct", 0.0)
+                m.used_disk_kv_pct = getattr(tiers, "disk_used_pct", 0.0)
         self.last_metrics = m
         if self.metrics_sink is not None:
             self.metrics_sink(m)

@@ -1,15 +1,17 @@
-"""ZMQ PUSH/PULL queues with a ``queue.Queue``-like API (``put_nowait`` / ``get_nowait``)."""
+"""ZMQ PUSH/PULL queues with a ``queue.Queue``-like API (``put_nowait`` / ``get_nowait``); frames are msgpack
+(see ``codec.py``), never pickle."""
 
 from __future__ import annotations
 
 import os
-import pickle
 import queue
 import tempfile
 import uuid
 from dataclasses import dataclass
 
 import zmq
+
+from . import codec
 
 
 def generate_ipc_path(tag: str = "q") -> str:
@@ -56,7 +58,7 @@ class ZmqPushSocket(_Base):
 
     def put_nowait(self, obj) -> None:
         try:
-            self.sock.send(pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL), flags=zmq.NOBLOCK)
+            self.sock.send(codec.encode(obj), flags=zmq.NOBLOCK)
         except zmq.Again as e:
             raise queue.Full() from e
 
@@ -69,14 +71,14 @@ class ZmqPullSocket(_Base):
 
     def get_nowait(self):
         try:
-            return pickle.loads(self.sock.recv(flags=zmq.NOBLOCK))
+            return codec.decode(self.sock.recv(flags=zmq.NOBLOCK))
         except zmq.Again as e:
             raise queue.Empty() from e
 
     def get(self, timeout_s: float = None):
         if timeout_s is not None and not self.sock.poll(int(timeout_s * 1000)):
             raise queue.Empty()
-        return pickle.loads(self.sock.recv())
+        return codec.decode(self.sock.recv())
 
     def empty(self) -> bool:
         return not self.sock.poll(0)

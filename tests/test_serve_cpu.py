@@ -85,6 +85,17 @@ def test_embeddings_unavailable_on_echo(echo_client):
 
 def test_worker_rpc(echo_client):
     assert echo_client.get("/max_internal/worker_stats").json()["steps"] > 0
+    # the worker's per-step metrics reach the API process's registry
+    import time
+    for _ in range(50):
+        body = echo_client.get("/metrics").content
+        if b"maxserve_batch_size_count 0.0" not in body:
+            break
+        time.sleep(0.1)
+    assert b"maxserve_batch_size_count" in body and b"maxserve_batch_size_count 0.0" not in body
+    for name in (b"maxserve_batch_execution_time_ms", b"maxserve_cache_used_kv_pct", b"maxserve_batch_pending_reqs",
+                 b"maxserve_batch_generation_throughput", b"maxserve_cache_preemption_count"):
+        assert name in body
     assert echo_client.post("/reset_prefix_cache").json() == {"success": False}  # echo has no cache
 
 
@@ -365,3 +376,33 @@ def test_lora_admin_routes(tmp_path):
         assert c.post("/v1/unload_lora_adapter", json={"lora_name": "ad1"}).status_code == 200
         assert c.post("/v1/unload_lora_adapter", json={"lora_name": "ad1"}).status_code == 404
         assert c.post("/v1/completions", json=dict(req, model="ad1")).status_code == 404
+
+
+def test_worker_hop_codec_roundtrip():
+    """Requests, step outputs (with log-probabilities), embeddings, cancels and RPC frames survive the msgpack hop."""
+    import numpy as np
+
+    from modular_b200.pipelines.context import (EmbeddingsOutput, GenerationStatus, SamplingParams, TextContext,
+                                                TextGenerationOutput)
+    from modular_b200.serve.worker_interface import codec
+
+    sp = SamplingParams(temperature=0.5, top_k=7, stop=["x"], stop_token_ids=[3], seed=9, logprobs=2,
+                        response_format={"type": "json_object"})
+    ctx = TextContext.from_prompt(np.arange(5, 40), 128, "r1", sp, eos_token_ids=(2, 9), model_name="m")
+    ctx.lora_name, ctx.cache_salt, ctx.task, ctx.pooling = "ad", 12345678901234, "generate", "mean"
+    got = codec.decode(codec.encode(ctx))
+    assert got.request_id == "r1" and got.tokens.prompt.tolist() == list(range(5, 40)) and got.max_length == 128
+    assert got.sampling_params == sp and got.eos_token_ids == frozenset((2, 9)) and got.model_name == "m"
+    assert (got.lora_name, got.cache_salt, got.pooling) == ("ad", 12345678901234, "mean")
+    outs = {"a": TextGenerationOutput("a", [np.int64(4), 5], GenerationStatus.ACTIVE,
+                                      [{"token": 4, "logprob": np.float32(-0.5), "top": [(4, -0.5), (7, -1.5)]}]),
+            "b": TextGenerationOutput("b", [], GenerationStatus.MAXIMUM_LENGTH)}
+    back = codec.decode(codec.encode(outs))
+    assert back["a"].tokens == [4, 5] and back["a"].log_probabilities[0]["top"] == [(4, -0.5), (7, -1.5)]
+    assert back["b"].is_done and back["b"].final_status is GenerationStatus.MAXIMUM_LENGTH
+    emb = codec.decode(codec.encode({"e": EmbeddingsOutput("e", [0.5, 0.25], 3)}))["e"]
+    assert emb.embedding == [0.5, 0.25] and emb.prompt_tokens == 3
+    assert codec.decode(codec.encode("rid-7")) == "rid-7"
+    assert codec.decode(codec.encode(("stats", None))) == ("stats", None)
+    with pytest.raises(Exception):
+        codec.decode(b"\\x80\\x04garbage")
