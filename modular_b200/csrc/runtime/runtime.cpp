@@ -419,9 +419,23 @@ void bind_runtime(py::module_& m) {
       .def("submit", [](ThreadPool& p, py::function fn) {
         auto holder = std::make_shared<py::function>(std::move(fn));
         return p.submit([holder] {
-          py::gil_scoped_acquire acq;
-          (*holder)();
-          holder->release().dec_ref();
+          // A Python exception must be turned into a plain C++ one while the GIL is still held: its message
+          // and its destructor both touch Python objects, and the pool's catch block runs without the GIL.
+          std::string failure;
+          bool failed = false;
+          {
+            py::gil_scoped_acquire acq;
+            try {
+              (*holder)();
+            } catch (py::error_already_set& e) {
+              failure = e.what();
+              failed = true;
+              e.restore();
+              PyErr_Clear();
+            }
+            holder->release().dec_ref();
+          }
+          if (failed) throw std::runtime_error(failure);
         });
       })
       // dst/src are raw addresses (e.g. tensor.data_ptr()); copies run without the GIL.
