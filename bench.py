@@ -114,7 +114,21 @@ def main() -> int:
     ap.add_argument("--concurrency", type=int, default=64)
     ap.add_argument("--max-batch-input-tokens", type=int, default=2176)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
+    ap.add_argument("--model", default="llama8b", choices=["llama8b", "llama70b-fp8"],
+                    help="llama8b: the headline config (bf16, any --gpus); llama70b-fp8: Llama-3.3-70B shapes with "
+                         "block-scaled fp8 weights, tensor parallel over --gpus (input 2048 / output 512 / "
+                         "concurrency 128 unless given)")
     args = ap.parse_args()
+    if args.model == "llama70b-fp8":
+        defaults = ap.parse_args([])
+        if args.input_len == defaults.input_len:
+            args.input_len = 2048
+        if args.output_len == defaults.output_len:
+            args.output_len = 512
+        if args.concurrency == defaults.concurrency:
+            args.concurrency = 128
+        if args.max_batch_input_tokens == defaults.max_batch_input_tokens:
+            args.max_batch_input_tokens = 4224
     if args.impl == "reference":
         return _reference_arm(args)
     if args.warmup < 3:
@@ -135,16 +149,23 @@ def main() -> int:
     from modular_b200.models.llama3 import Llama3Config
     from modular_b200.pipelines.context import SamplingParams
 
-    cfg = Llama3Config.llama31_8b()
+    fp8 = args.model == "llama70b-fp8"
+    cfg = Llama3Config.llama33_70b() if fp8 else Llama3Config.llama31_8b()
     if args.layers:
         cfg.num_hidden_layers = args.layers
     conc = args.concurrency
     max_len = args.input_len + args.output_len + 8
-    llm = LLM(cfg, device=f"cuda:{local_rank}", dtype=torch.bfloat16, max_length=max_len,
+    weights, sharded = None, False
+    if fp8:
+        # 70 GB of e4m3 weights: every rank creates its own shard, quantised layer by layer
+        from modular_b200.models.llama3 import Llama3Weights
+        weights = Llama3Weights.random_init_shard(cfg, rank, world, f"cuda:{local_rank}", torch.bfloat16, seed=0, fp8=True)
+        sharded = world > 1
+    llm = LLM(cfg, weights, device=f"cuda:{local_rank}", dtype=torch.bfloat16, max_length=max_len,
               max_batch_size=conc, max_batch_input_tokens=args.max_batch_input_tokens, page_size=128,
               enable_prefix_caching=True, enable_chunked_prefill=True, enable_in_flight_batching=True,
               enable_overlap_scheduler=True, device_graph_capture=True, graph_batch_sizes=[conc],
-              tp_size=world, tp_rank=rank, seed=0)
+              tp_size=world, tp_rank=rank, seed=0, weights_are_sharded=sharded)
     sp = SamplingParams(temperature=0.0, max_new_tokens=args.output_len, ignore_eos=True)
     rng = np.random.default_rng(1234)
 
@@ -197,13 +218,14 @@ def main() -> int:
         value = out_tokens / gpu_busy
         e2e = out_tokens / wall
         line = {
-            "metric": "output_tokens_per_s_at_concurrency_64", "value": value, "unit": "tok/s",
+            "metric": f"output_tokens_per_s_at_concurrency_{conc}", "value": value, "unit": "tok/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": gpu_busy / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16",
+            "vs_baseline": None, "dtype": "fp8 e4m3 weights (128x128 block scales) + per-token-group fp8 activations, bf16 elsewhere" if fp8 else "bf16",
             "data": "synthetic uniform-random token ids; random-init N(0,0.02) weights",
             "impl": "ours",
-            "config": {"model": "Llama-3.1-8B architecture (32L, h4096, 32q/8kv, ffn 14336, vocab 128256)"
+            "config": {"model": ("Llama-3.3-70B architecture (80L, h8192, 64q/8kv, ffn 28672, vocab 128256), fp8 block-scaled"
+                                 if fp8 else "Llama-3.1-8B architecture (32L, h4096, 32q/8kv, ffn 14336, vocab 128256)")
                        + (f" DEBUG {args.layers} layers" if args.layers else ""),
                        "global_batch": conc, "seq_len": args.input_len + args.output_len,
                        "input_len": args.input_len, "output_len": args.output_len,
@@ -211,7 +233,7 @@ def main() -> int:
                        "parallelism": f"tp{world}", "kv_page_tokens": 128,
                        "max_batch_input_tokens": args.max_batch_input_tokens,
                        "step_definition": f"{conc} requests served to completion (closed loop)",
-                       "l2_policy": "inputs larger than L2 (16 GB of weights streamed every scheduler iteration)"},
+                       "l2_policy": "inputs larger than L2 (the rank's whole weight shard, GBs, is streamed every scheduler iteration)"},
             "p50_ttft_ms": p(ttft, 0.5) * 1e3, "p99_ttft_ms": p(ttft, 0.99) * 1e3,
             "p50_tpot_ms": p(tpot, 0.5) * 1e3, "p99_tpot_ms": p(tpot, 0.99) * 1e3,
             "total_tokens_per_s": (out_tokens + args.steps * conc * args.input_len) / wall,

@@ -10,6 +10,8 @@ Run one process per GPU:
               flags -> flag-gated column-parallel GEMM                      (3 launches, 0 barriers)
     baseline  the same tcgen05 GEMMs, NCCL reduce_scatter_tensor, add+RMSNorm kernel, NCCL
               all_gather_into_tensor                                       (5 launches)
+``sweep``: N = K = 8192 sharded over the ranks, M in {1 ... 8192}: GEMM -> reduce (one fused kernel up to 256
+    rows) and all-gather -> GEMM, each against NCCL + separate kernels (see ``bench_sweep``)
 ``ep``: MoE dispatch + combine of DeepSeek-V3 shapes (hidden 7168, top-8, 256 experts)
     fused     peer-memory dispatch / combine kernels (bf16 and fp8 payload)
     baseline  NCCL all_to_all_single of the same rows, both directions
@@ -134,6 +136,128 @@ def bench_tp(args, ctx, L, peaks, flush, out):
         ops.check_device_error()
 
 
+def bench_sweep(args, ctx, L, peaks, flush, out):
+    """Square sweep N = K = 8192 (K or N sharded over the ranks), M in --sweep-tokens:
+
+    gemm_reduce   row-parallel GEMM whose partial sums are reduced over the ranks.
+                  M <= 256: ONE kernel, the decode-step GEMM with sentinel-polled all-reduce + residual + RMSNorm
+                  (every rank ends with all rows); baseline: GEMM, NCCL all_reduce, add+RMSNorm kernel.
+                  M > 256: GEMM with reduce-scatter pushes, then reduce + residual + RMSNorm + all-gather pushes;
+                  baseline: GEMM, NCCL reduce_scatter, add+RMSNorm kernel, NCCL all_gather.
+    ag_gemm       rows sharded over the ranks -> all-gather -> column-parallel GEMM: norm + pushes with ready
+                  flags, GEMM tiles gated on the flags; baseline: RMSNorm kernel, NCCL all_gather, GEMM.
+    """
+    from .. import ops
+    world, rank, dev = ctx.world, ctx.rank, ctx.device
+    N = K = 8192
+    if K % world:
+        return
+    T_max = max(args.sweep_tokens)
+    partial_rows = T_max + world
+    sym_partial = ctx.alloc_symmetric(partial_rows * N, torch.bfloat16)
+    sym_xn = ctx.alloc_symmetric(T_max * N, torch.bfloat16)
+    sym_flags = ctx.alloc_symmetric(L.tp_flag_ints(), torch.int32, zero=True)
+    dec_rows = L.gemm_dec_sizes()[2]
+    sym_lam = ctx.alloc_symmetric(L.gemm_dec_lamport_elems(world, dec_rows, N), torch.bfloat16)
+    sym_lam.tensor.view(torch.int16).fill_(-32768)
+    _, dec_state = ops.decode_gemm_workspace(dev)
+    tp = dict(world=world, rank=rank, lam=sym_lam.peer_ptrs, lam_rows=dec_rows, state=dec_state)
+    ctx.barrier()
+    g = torch.Generator().manual_seed(2)
+    mk = lambda *s_, std=0.02: (torch.randn(*s_, generator=g) * std).to(torch.bfloat16).to(dev)
+    gamma = torch.ones(N, dtype=torch.bfloat16, device=dev)
+    w_row = mk(N, K // world)              # row-parallel weight shard
+    w_col = mk(N // world, K)              # column-parallel weight shard
+    ws = ops.gemm_workspace(dev)
+    for T in args.sweep_tokens:
+        rpr = (T + world - 1) // world
+        Tp = rpr * world
+        x = mk(T, K // world, std=1.0)
+        link_rs_ag = (world - 1) / world * T * N * 2 * 2
+        # ---------------- GEMM -> reduce
+        if T <= dec_rows:
+            h = mk(T, N, std=1.0)
+            xn = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+
+            def fused():
+                ops.linear_decode(x, w_row, mode="add_norm", h=h, gamma=gamma, xn=xn, tp=tp)
+
+            part = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+
+            def baseline():
+                L.gemm_bf16(x, w_row, part, None, False, ws, 0, 0, 0)
+                dist.all_reduce(part)
+                L.add_rmsnorm(part, h, gamma, xn, 1e-5, 0.0, False)
+
+            link = (world - 1) * T * N * 2           # one-shot: every rank sends its partial to every peer
+            variant = "one kernel: GEMM + all-reduce + residual + RMSNorm"
+        else:
+            h_local = mk(rpr, N, std=1.0)
+            max_slots = partial_rows // rpr
+
+            def fused():
+                e, s_ = L.gemm_bf16_comm(x, w_row, None, T, False, False, True, 0, 0, world, rank, rpr,
+                                         sym_flags.peer_ptrs, sym_partial.peer_ptrs, max_slots)
+                L.tp_rs_norm_ag_ex(world, rank, sym_partial.peer_ptrs, sym_xn.peer_ptrs, sym_flags.peer_ptrs,
+                                   h_local, gamma, T, rpr, 1e-5, True, 1, world * s_, e)
+
+            part = torch.zeros(Tp, N, dtype=torch.bfloat16, device=dev)
+            mine = torch.empty(rpr, N, dtype=torch.bfloat16, device=dev)
+            xn_loc = torch.empty(rpr, N, dtype=torch.bfloat16, device=dev)
+            xn_all = torch.empty(Tp, N, dtype=torch.bfloat16, device=dev)
+
+            def baseline():
+                L.gemm_bf16(x, w_row, part[:T], None, False, ws, 0, 0, 0)
+                dist.reduce_scatter_tensor(mine, part)
+                L.add_rmsnorm(mine, h_local, gamma, xn_loc, 1e-5, 0.0, False)
+                dist.all_gather_into_tensor(xn_all, xn_loc)
+
+            link = link_rs_ag
+            variant = "GEMM with reduce-scatter pushes + reduce/norm/all-gather kernel"
+        t_f = _time(fused, args.iters, flush)
+        t_b = _time(baseline, args.iters, flush)
+        flops = 2.0 * T * N * (K // world)
+        bound = max(flops / (peaks["bf16_tflops"] * 1e12), link / 770e9, (N * (K // world) * 2) / (peaks["hbm_gbs"] * 1e9)) * 1e6
+        rec = dict(kind="sweep", case="gemm_reduce", variant=variant, world=world, M=T, N=N, K=K, fused_us=round(t_f, 1),
+                   nccl_us=round(t_b, 1), speedup=round(t_b / t_f, 2), roofline_us=round(bound, 1),
+                   frac_of_measured_roofline=round(bound / t_f, 3))
+        out.append(rec)
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
+        # ---------------- all-gather -> GEMM
+        h_rows = mk(rpr, N, std=1.0)
+        y = torch.empty(T, N // world, dtype=torch.bfloat16, device=dev)
+        xn_view = sym_xn.tensor[: T * N].view(T, N)
+
+        def fused_ag():
+            # has_partials = 0: normalise this rank's rows, push them to every rank, raise the ready flags
+            L.tp_rs_norm_ag_ex(world, rank, sym_partial.peer_ptrs, sym_xn.peer_ptrs, sym_flags.peer_ptrs,
+                               h_rows, gamma, T, rpr, 1e-5, False, 2, 0, 0)
+            L.gemm_bf16_comm(xn_view, w_col, y, T, False, True, False, 0, 1, world, rank, rpr,
+                             sym_flags.peer_ptrs, [], 0)
+
+        xl = torch.empty(rpr, N, dtype=torch.bfloat16, device=dev)
+        xa = torch.empty(Tp, N, dtype=torch.bfloat16, device=dev)
+
+        def baseline_ag():
+            L.rmsnorm(h_rows, gamma, xl, 1e-5, 0.0, False)
+            dist.all_gather_into_tensor(xa, xl)
+            L.gemm_bf16(xa[:T], w_col, y, None, False, ws, 0, 0, 0)
+
+        t_f = _time(fused_ag, args.iters, flush)
+        t_b = _time(baseline_ag, args.iters, flush)
+        flops = 2.0 * T * (N // world) * K
+        link = (world - 1) / world * T * K * 2
+        bound = max(flops / (peaks["bf16_tflops"] * 1e12), link / 770e9, ((N // world) * K * 2) / (peaks["hbm_gbs"] * 1e9)) * 1e6
+        rec = dict(kind="sweep", case="ag_gemm", world=world, M=T, N=N, K=K, fused_us=round(t_f, 1),
+                   nccl_us=round(t_b, 1), speedup=round(t_b / t_f, 2), roofline_us=round(bound, 1),
+                   frac_of_measured_roofline=round(bound / t_f, 3))
+        out.append(rec)
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
+    ops.check_device_error()
+
+
 def bench_ep(args, ctx, L, peaks, flush, out):
     from .. import ops
     from ..parallel.ep import EPContext
@@ -189,7 +313,8 @@ def bench_ep(args, ctx, L, peaks, flush, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="all", choices=["tp", "ep", "all"])
+    ap.add_argument("--what", default="all", choices=["tp", "ep", "sweep", "all"])
+    ap.add_argument("--sweep-tokens", type=int, nargs="+", default=[1, 16, 64, 256, 1024, 4096, 8192])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tokens", type=int, nargs="+", default=[64, 256, 1024, 2048])
     ap.add_argument("--ep-tokens", type=int, nargs="+", default=[64, 512])
@@ -210,6 +335,8 @@ def main():
     out = []
     if args.what in ("tp", "all"):
         bench_tp(args, ctx, L, peaks, flush, out)
+    if args.what == "sweep":
+        bench_sweep(args, ctx, L, peaks, flush, out)
     if args.what in ("ep", "all"):
         bench_ep(args, ctx, L, peaks, flush, out)
     if ctx.rank == 0 and args.out:

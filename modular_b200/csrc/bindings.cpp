@@ -429,12 +429,33 @@ class PyDecoderExecutor {
     ex.lm_head = hold(lm_head);
     ex.cos_sin = static_cast<const float*>(hold(cos_sin));
   }
+  // scales: the four block-scale tensors of an fp8 layer (all or none)
   void add_layer(const Tensor& attn_norm, const Tensor& wqkv, const Tensor& wo,
-                 const Tensor& mlp_norm, const Tensor& wgu, const Tensor& wd) {
+                 const Tensor& mlp_norm, const Tensor& wgu, const Tensor& wd,
+                 const c10::optional<std::vector<Tensor>>& scales) {
     mb::DecoderLayerWeights w;
     w.attn_norm = hold(attn_norm); w.wqkv = hold(wqkv); w.wo = hold(wo);
     w.mlp_norm = hold(mlp_norm); w.wgu = hold(wgu); w.wd = hold(wd);
+    if (scales.has_value()) {
+      TORCH_CHECK(scales->size() == 4, "add_layer: four scale tensors (qkv, o, gate_up, down) expected");
+      const Tensor* ws[4] = {&wqkv, &wo, &wgu, &wd};
+      const float* ptr[4];
+      for (int i = 0; i < 4; ++i) {
+        const Tensor& s = (*scales)[i];
+        TORCH_CHECK(s.scalar_type() == at::kFloat && s.dim() == 2 && ws[i]->element_size() == 1 &&
+                        s.size(0) == (ws[i]->size(0) + 127) / 128 && s.size(1) == (ws[i]->size(1) + 127) / 128,
+                    "add_layer: scales must be fp32 [ceil(N/128), ceil(K/128)] of an 8-bit weight");
+        ptr[i] = static_cast<const float*>(hold(s));
+      }
+      w.wqkv_s = ptr[0]; w.wo_s = ptr[1]; w.wgu_s = ptr[2]; w.wd_s = ptr[3];
+    }
     ex.layers.push_back(w);
+  }
+  void set_fp8_buffers(const Tensor& xq, const Tensor& xs, const Tensor& gu) {
+    ex.buf.xq = const_cast<void*>(hold(xq));
+    TORCH_CHECK(xs.scalar_type() == at::kFloat, "xs must be fp32");
+    ex.buf.xs = static_cast<float*>(const_cast<void*>(hold(xs)));
+    ex.buf.gu = const_cast<void*>(hold(gu));
   }
   // kv: [pages, 2, n_layers, n_kv, page_size, head_dim]
   void set_kv_cache(const Tensor& kv) {
@@ -943,7 +964,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<PyDecoderExecutor>(m, "DecoderExecutor")
       .def(py::init<py::dict>())
       .def("set_globals", &PyDecoderExecutor::set_globals)
-      .def("add_layer", &PyDecoderExecutor::add_layer)
+      .def("add_layer", &PyDecoderExecutor::add_layer, py::arg("attn_norm"), py::arg("wqkv"), py::arg("wo"),
+           py::arg("mlp_norm"), py::arg("wgu"), py::arg("wd"), py::arg("scales") = py::none())
+      .def("set_fp8_buffers", &PyDecoderExecutor::set_fp8_buffers)
       .def("set_kv_cache", &PyDecoderExecutor::set_kv_cache)
       .def("set_buffers", &PyDecoderExecutor::set_buffers)
       .def("set_tp", &PyDecoderExecutor::set_tp)

@@ -38,8 +38,22 @@ std::vector<std::tuple<std::string, int, double>> DecoderExecutor::profile_ms() 
   return out;
 }
 
+// Y[M, N] (bf16, contiguous) = X[M, K] · W^T for a block-scaled fp8 weight: quantise X per token and
+// 128-wide K group, then the fp8 GEMM (optionally + residual R).
+static int linear_fp8(const DecoderBuffers& buf, const DecoderConfig& c, const void* X, int ldx, const void* Wq,
+                      const float* Ws, void* Y, const void* R, int M, int N, int K, long* launches,
+                      cudaStream_t stream) {
+  if (buf.xq == nullptr || buf.xs == nullptr) return MB_ERR_SHAPE;
+  MB_TRY(mb_quant_fp8_group128(X, buf.xq, buf.xs, M, K, ldx, M, 1, stream));
+  MB_TRY(mb_gemm_fp8_blockscaled(buf.xq, buf.xs, Wq, Ws, Y, R, M, N, K, R != nullptr ? 2 : 0, 0, 0, 0,
+                                 buf.workspace, buf.workspace_bytes, c.num_sms, buf.err, stream));
+  *launches += 2;
+  return MB_OK;
+}
+
 bool DecoderExecutor::dec_usable(int T) const {
   const DecoderConfig& c = cfg;
+  if (!layers.empty() && layers[0].wqkv_s != nullptr) return false;   // fp8 layers run the general path
   if (T <= 0 || T > c.dec_max_tokens || buf.dec_ws == nullptr || buf.dec_state == nullptr) return false;
   if (tp.world > 1 && (tp.lam[0] == nullptr || T > tp.lam_rows)) return false;
   const int qkv_dim = (c.n_q + 2 * c.n_kv) * c.head_dim;
@@ -207,7 +221,12 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
     MB_TRY(mb_rmsnorm(buf.h, w.attn_norm, buf.xn, T, c.hidden, c.hidden, c.hidden, c.eps,
                       c.norm_weight_offset, c.multiply_before_cast, stream));
     mark("rmsnorm", stream);
-    MB_TRY(gemm(buf.xn, w.wqkv, buf.qkv, nullptr, T, qkv_dim, c.hidden, c.hidden, qkv_dim, 0));
+    if (w.wqkv_s != nullptr) {
+      MB_TRY(linear_fp8(buf, c, buf.xn, c.hidden, w.wqkv, w.wqkv_s, buf.qkv, nullptr, T, qkv_dim, c.hidden,
+                        &launches, stream));
+    } else {
+      MB_TRY(gemm(buf.xn, w.wqkv, buf.qkv, nullptr, T, qkv_dim, c.hidden, c.hidden, qkv_dim, 0));
+    }
     mark("gemm_qkv", stream);
     MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kc, vc, T, c.n_q, c.n_kv,
                             c.head_dim, c.page_size, kv.page_stride, kv.head_stride,
@@ -232,13 +251,23 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
       launches += 2 + (in.n_tiles > 0) + (in.n_decode > 0);
     }
     mark("attention", stream);
-    MB_TRY(gemm(buf.attn, w.wo, buf.h, buf.h, T, c.hidden, q_dim, q_dim, c.hidden, 2));
+    if (w.wo_s != nullptr) {
+      MB_TRY(linear_fp8(buf, c, buf.attn, q_dim, w.wo, w.wo_s, buf.h, buf.h, T, c.hidden, q_dim, &launches, stream));
+    } else {
+      MB_TRY(gemm(buf.attn, w.wo, buf.h, buf.h, T, c.hidden, q_dim, q_dim, c.hidden, 2));
+    }
     mark("gemm_o", stream);
     MB_TRY(mb_rmsnorm(buf.h, w.mlp_norm, buf.xn, T, c.hidden, c.hidden, c.hidden, c.eps,
                       c.norm_weight_offset, c.multiply_before_cast, stream));
     launches += 1;
     mark("rmsnorm", stream);
-    if (c.fuse_swiglu) {
+    if (w.wgu_s != nullptr) {
+      if (buf.gu == nullptr) return MB_ERR_SHAPE;
+      MB_TRY(linear_fp8(buf, c, buf.xn, c.hidden, w.wgu, w.wgu_s, buf.gu, nullptr, T, 2 * c.inter, c.hidden,
+                        &launches, stream));
+      MB_TRY(mb_silu_mul(buf.gu, buf.act, T, c.inter, stream));
+      launches += 1;
+    } else if (c.fuse_swiglu) {
       MB_TRY(gemm(buf.xn, w.wgu, buf.act, nullptr, T, c.inter, c.hidden, c.hidden, c.inter, 1));
     } else {
       MB_TRY(gemm(buf.xn, w.wgu, buf.gu, nullptr, T, 2 * c.inter, c.hidden, c.hidden, 2 * c.inter,
@@ -247,7 +276,11 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
       launches += 1;
     }
     mark("gemm_gate_up", stream);
-    MB_TRY(gemm(buf.act, w.wd, buf.h, buf.h, T, c.hidden, c.inter, c.inter, c.hidden, 2));
+    if (w.wd_s != nullptr) {
+      MB_TRY(linear_fp8(buf, c, buf.act, c.inter, w.wd, w.wd_s, buf.h, buf.h, T, c.hidden, c.inter, &launches, stream));
+    } else {
+      MB_TRY(gemm(buf.act, w.wd, buf.h, buf.h, T, c.hidden, c.inter, c.inter, c.hidden, 2));
+    }
     mark("gemm_down", stream);
   }
   if (in.n_logits > 0) {
@@ -301,12 +334,26 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
   //   push: row-parallel GEMMs store their tiles into the owners' partial slots (GEMM -> reduce-scatter)
   //   gate: reduce+norm closes with ready flags and the next column-parallel GEMM waits per token
   //         tile for the sources it reads (all-gather -> GEMM), instead of a closing barrier
-  const bool push = (tp.fused & 1) && tp.partial_rows >= static_cast<long long>(W) * rows_per_rank;
-  const bool gate_on = (tp.fused & 2) != 0;
+  // fp8 layers: the fp8 GEMM neither pushes its tiles nor waits on ready flags, so the exchange kernel opens
+  // and closes with barriers and the GEMMs run on complete inputs
+  const bool fp8 = !layers.empty() && layers[0].wqkv_s != nullptr;
+  const bool push = !fp8 && (tp.fused & 1) && tp.partial_rows >= static_cast<long long>(W) * rows_per_rank;
+  const bool gate_on = !fp8 && (tp.fused & 2) != 0;
   const int max_slots = push ? static_cast<int>(tp.partial_rows / rows_per_rank) : 0;
   // column-parallel GEMM on the gathered activations; its token tiles wait for the ready flags of
   // the ranks that push their rows (same kernel choice as the single-GPU path)
-  auto gemm_gathered = [&](const void* Wt, void* Y, int N, int ldy, int flags, bool wait) {
+  auto gemm_gathered = [&](const void* Wt, const float* Ws, void* Y, int N, int ldy, int flags, bool wait) {
+    if (Ws != nullptr) {
+      // column-parallel fp8 GEMM on the gathered activations; SwiGLU (flags bit0: W = [gate; up], N = inter) as a
+      // separate pass over the [T, 2 inter] product
+      if (flags & 1) {
+        if (buf.gu == nullptr) return static_cast<int>(MB_ERR_SHAPE);
+        MB_TRY(linear_fp8(buf, c, xn, c.hidden, Wt, Ws, buf.gu, nullptr, T, 2 * N, c.hidden, &launches, stream));
+        launches += 1;
+        return mb_silu_mul(buf.gu, Y, T, N, stream);
+      }
+      return linear_fp8(buf, c, xn, c.hidden, Wt, Ws, Y, nullptr, T, N, c.hidden, &launches, stream);
+    }
     const int* gate = wait ? tp.flags[R] : nullptr;
     if ((flags & 1) && buf.p_ws != nullptr) {
       launches += 1;
@@ -322,9 +369,12 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
                               splits, stages, buf.workspace, buf.err, c.num_sms, gate, rows_per_rank, W, stream);
   };
   // row-parallel GEMM, then reduce-scatter + residual + norm + gather of the normalised rows
-  auto row_parallel_reduce_norm = [&](const void* X, const void* Wt, int K, const void* gamma, bool last) {
+  auto row_parallel_reduce_norm = [&](const void* X, const void* Wt, const float* Ws, int K, const void* gamma,
+                                      bool last) {
     int expected = 0, splits = 1, mode = 0;
-    if (push) {
+    if (Ws != nullptr) {
+      MB_TRY(linear_fp8(buf, c, X, K, Wt, Ws, partial, nullptr, T, c.hidden, K, &launches, stream));
+    } else if (push) {
       MB_TRY(mb_gemm_bf16_comm(X, Wt, partial, T, c.hidden, K, K, K, c.hidden, 32, 0, 0, W, R, rows_per_rank,
                                tp.flags, tp.partial, max_slots, &expected, &splits, buf.err, c.num_sms, stream));
       launches += 1;
@@ -363,7 +413,7 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
   for (int l = 0; l < c.n_layers; ++l) {
     const DecoderLayerWeights& w = layers[l];
     const long long hd = c.head_dim;
-    MB_TRY(gemm_gathered(w.wqkv, buf.qkv, qkv_dim, qkv_dim, 0, gate_on && l > 0));
+    MB_TRY(gemm_gathered(w.wqkv, w.wqkv_s, buf.qkv, qkv_dim, qkv_dim, 0, gate_on && l > 0));
     mark("gemm_qkv", stream);
     char* kbase = static_cast<char*>(kv.base) + 2 * (static_cast<int64_t>(l) * kv.layer_stride);
     MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, T,
@@ -388,11 +438,11 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
     launches += 2;
     mark("attention", stream);
     const void* next_norm = l + 1 < c.n_layers ? layers[l + 1].attn_norm : final_norm;
-    MB_TRY(row_parallel_reduce_norm(buf.attn, w.wo, q_dim, w.mlp_norm, false));
+    MB_TRY(row_parallel_reduce_norm(buf.attn, w.wo, w.wo_s, q_dim, w.mlp_norm, false));
     mark("gemm_o+rs_norm_ag", stream);
-    MB_TRY(gemm_gathered(w.wgu, buf.act, c.inter, c.inter, 1, gate_on));
+    MB_TRY(gemm_gathered(w.wgu, w.wgu_s, buf.act, c.inter, c.inter, 1, gate_on));
     mark("gemm_gate_up", stream);
-    MB_TRY(row_parallel_reduce_norm(buf.act, w.wd, c.inter, next_norm, l + 1 == c.n_layers));
+    MB_TRY(row_parallel_reduce_norm(buf.act, w.wd, w.wd_s, c.inter, next_norm, l + 1 == c.n_layers));
     mark("gemm_down+rs_norm_ag", stream);
   }
   if (in.n_logits > 0) {

@@ -23,6 +23,12 @@ struct DecoderLayerWeights {
   const void* mlp_norm;   // [hidden]
   const void* wgu;        // [2 * inter, hidden]  (gate rows then up rows)
   const void* wd;         // [hidden, inter]
+  // Block-scaled fp8 layers: the four matrices above are e4m3 and these are their fp32 scales, one per
+  // 128 x 128 block ([ceil(rows/128), ceil(cols/128)]); nullptr = bf16 weights.
+  const float* wqkv_s = nullptr;
+  const float* wo_s = nullptr;
+  const float* wgu_s = nullptr;
+  const float* wd_s = nullptr;
 };
 
 struct DecoderConfig {
@@ -58,6 +64,9 @@ struct DecoderBuffers {
   void* p_ws;       // persistent GEMM partial-tile slots
   int* p_counters;  // persistent GEMM tile counters (zeroed)
   int* err;
+  // fp8 layers: activations quantised per token and 128-wide K group before every GEMM
+  void* xq = nullptr;           // e4m3 [max_tokens, max K]
+  float* xs = nullptr;          // fp32 [ceil(max K / 128), max_tokens]
   void* dec_ws = nullptr;       // decode-step GEMM partial tiles
   size_t dec_ws_bytes = 0;
   int* dec_state = nullptr;     // decode-step GEMM counters / all-reduce generation (zeroed once)

@@ -60,7 +60,7 @@ class LLM:
                  eos_token_ids: Sequence[int] = (), seed: int = 0, tp_size: int = 1,
                  tp_rank: int = 0, host_kvcache_swap_space_gb: float = 0.0,
                  disk_kvcache_dir: Optional[str] = None, disk_kvcache_space_gb: float = 0.0,
-                 step_token_alignment: Optional[int] = None):
+                 step_token_alignment: Optional[int] = None, weights_are_sharded: bool = False):
         from ..models import family_for
 
         fam = family_for(model_config)
@@ -86,7 +86,8 @@ class LLM:
             full_cfg = model_config
             if weights is None:
                 weights = fam.weights_class.random_init(full_cfg, self.device, dtype, seed=seed)
-            weights = shard_llama_weights(full_cfg, weights, tp_rank, tp_size)
+            if not weights_are_sharded:      # ``weights`` may already be this rank's shard (random_init_shard)
+                weights = shard_llama_weights(full_cfg, weights, tp_rank, tp_size)
             model_config = shard_llama_config(full_cfg, tp_size)
             torch.cuda.empty_cache()
         elif weights is None:

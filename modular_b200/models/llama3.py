@@ -109,6 +109,19 @@ class LayerWeights:
     mlp_norm: torch.Tensor
     wgu: torch.Tensor
     wd: torch.Tensor
+    # block-scaled fp8 layers: the four matrices are float8_e4m3fn and these hold one fp32 scale per
+    # 128 x 128 block ([ceil(N/128), ceil(K/128)], the checkpoint's ``weight_scale_inv``); None = bf16
+    wqkv_s: Optional[torch.Tensor] = None
+    wo_s: Optional[torch.Tensor] = None
+    wgu_s: Optional[torch.Tensor] = None
+    wd_s: Optional[torch.Tensor] = None
+
+    @property
+    def is_fp8(self) -> bool:
+        return self.wqkv_s is not None
+
+    def scales(self):
+        return [self.wqkv_s, self.wo_s, self.wgu_s, self.wd_s] if self.is_fp8 else None
 
 
 @dataclass
@@ -146,9 +159,78 @@ class Llama3Weights:
         return cls(embed, layers, final_norm, lm_head)
 
     @classmethod
-    def from_state_dict(cls, cfg: Llama3Config, sd: dict, device="cpu", dtype=torch.bfloat16):
+    def random_init_shard(cls, cfg: Llama3Config, rank: int, world: int, device="cuda", dtype=torch.bfloat16,
+                          seed: int = 0, std: float = 0.02, fp8: bool = False) -> "Llama3Weights":
+        """Random weights of ONE tensor-parallel rank, created at shard size (a 70B model never exists whole
+        on a GPU). Replicated tensors (embedding, norms) come from ``seed`` alone and are identical on every
+        rank; sharded ones mix in the rank. ``fp8`` quantises each layer as it is made, so the peak footprint
+        is one bf16 layer shard. The values are not a sharding of ``random_init(cfg, seed)``: this is for
+        synthetic-weight benchmarks, where only shapes and dtypes matter."""
+        from ..parallel.tp import shard_llama_config
+
+        local = shard_llama_config(cfg, world) if world > 1 else cfg
+        dev = torch.device(device)
+        g_shared = torch.Generator(device=dev).manual_seed(seed)
+        g_rank = torch.Generator(device=dev).manual_seed(seed * 1000003 + rank + 1)
+        rnd = lambda g, *shape: (torch.randn(*shape, device=dev, dtype=torch.float32, generator=g) * std).to(dtype)
+        embed = rnd(g_shared, cfg.vocab_size, cfg.hidden_size)
+        ones = lambda: torch.ones(cfg.hidden_size, dtype=dtype, device=dev)
+        layers = []
+        for _ in range(cfg.num_hidden_layers):
+            l = LayerWeights(ones(), rnd(g_rank, local.q_dim + 2 * local.kv_dim, cfg.hidden_size),
+                             rnd(g_rank, cfg.hidden_size, local.q_dim), ones(),
+                             rnd(g_rank, 2 * local.intermediate_size, cfg.hidden_size),
+                             rnd(g_rank, cfg.hidden_size, local.intermediate_size))
+            if fp8:
+                l = cls(embed, [l], ones(), embed).quantize_fp8().layers[0]
+            layers.append(l)
+        v_local = cfg.vocab_size // world
+        lm_head = rnd(g_rank, v_local, cfg.hidden_size) if (world > 1 or not cfg.tie_word_embeddings) else embed
+        return cls(embed, layers, ones(), lm_head)
+
+    def quantize_fp8(self) -> "Llama3Weights":
+        """Block-scaled fp8 copy of these weights: every projection becomes e4m3 with 128 x 128 scales
+        (amax / 448); embeddings, norms and the LM head keep their dtype. Reference:
+        max/python/max/pipelines/weights/quantize_checkpoint.py, quant config weights/quant.py:581."""
+        def q(w):
+            return ops.reference.quant_fp8_weight_block128(w)
+
+        layers = []
+        for l in self.layers:
+            if l.is_fp8:
+                layers.append(l)
+                continue
+            (a, a_s), (b, b_s), (c_, c_s), (d, d_s) = q(l.wqkv), q(l.wo), q(l.wgu), q(l.wd)
+            layers.append(LayerWeights(l.attn_norm, a, b, l.mlp_norm, c_, d, a_s, b_s, c_s, d_s))
+        return Llama3Weights(self.embed, layers, self.final_norm, self.lm_head)
+
+    def dequantize(self, dtype=torch.bfloat16) -> "Llama3Weights":
+        """The same weights with fp8 layers expanded to ``dtype`` (what the fp8 kernels compute, up to the
+        activation quantisation)."""
+        d = lambda w, s: ops.reference.dequant_fp8_weight_block128(w, s).to(dtype)
+        layers = [LayerWeights(l.attn_norm, d(l.wqkv, l.wqkv_s), d(l.wo, l.wo_s), l.mlp_norm, d(l.wgu, l.wgu_s),
+                               d(l.wd, l.wd_s)) if l.is_fp8 else l for l in self.layers]
+        return Llama3Weights(self.embed, layers, self.final_norm, self.lm_head)
+
+    @classmethod
+    def from_state_dict(cls, cfg: Llama3Config, sd: dict, device="cpu", dtype=torch.bfloat16, keep_fp8: bool = True):
+        """``keep_fp8``: block-scaled fp8 projections (``<name>`` e4m3 + ``<name>_scale_inv``) stay fp8 when the
+        fused row blocks line up with the 128-row scale blocks; otherwise they are expanded to ``dtype``."""
         sd = adapt_hf_state_dict(sd)
         dev = torch.device(device)
+        fp8_names = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+                     "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")
+
+        def layer_is_fp8(p):
+            return keep_fp8 and all(
+                sd[p + n + ".weight"].dtype == torch.float8_e4m3fn and (p + n + ".weight_scale_inv") in sd
+                and (n in ("self_attn.o_proj", "mlp.down_proj") or sd[p + n + ".weight"].shape[0] % 128 == 0)
+                for n in fp8_names)
+
+        def fp8_cat(p, names):
+            w = torch.cat([sd[p + n + ".weight"] for n in names], dim=0).to(dev).contiguous()
+            s_ = torch.cat([sd[p + n + ".weight_scale_inv"].float() for n in names], dim=0).to(dev).contiguous()
+            return w, s_
 
         def raw(name):
             """Checkpoint tensor in floating point: fp8 tensors (block-scaled ``<name>_scale_inv`` [N/128, K/128],
@@ -167,6 +249,14 @@ class Llama3Weights:
         layers = []
         for i in range(cfg.num_hidden_layers):
             p = f"layers.{i}."
+            if layer_is_fp8(p):
+                a, a_s = fp8_cat(p, ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"))
+                b, b_s = fp8_cat(p, ("self_attn.o_proj",))
+                c_, c_s = fp8_cat(p, ("mlp.gate_proj", "mlp.up_proj"))
+                d, d_s = fp8_cat(p, ("mlp.down_proj",))
+                layers.append(LayerWeights(get(p + "input_layernorm.weight"), a, b,
+                                           get(p + "post_attention_layernorm.weight"), c_, d, a_s, b_s, c_s, d_s))
+                continue
             wqkv = torch.cat([raw(p + "self_attn.q_proj.weight"), raw(p + "self_attn.k_proj.weight"),
                               raw(p + "self_attn.v_proj.weight")], dim=0)
             wgu = torch.cat([raw(p + "mlp.gate_proj.weight"), raw(p + "mlp.up_proj.weight")], dim=0)
@@ -188,6 +278,21 @@ class Llama3Weights:
             sd["lm_head.weight"] = self.lm_head
         for i, l in enumerate(self.layers):
             p = f"model.layers.{i}."
+            if l.is_fp8:
+                # e4m3 tensors cannot be split by torch.split on every build: slice through the byte view
+                rows = lambda w, a, b: w.view(torch.uint8)[a:b].view(torch.float8_e4m3fn)
+                qd, kd, I = cfg.q_dim, cfg.kv_dim, cfg.intermediate_size
+                parts = {"self_attn.q_proj": (l.wqkv, l.wqkv_s, 0, qd), "self_attn.k_proj": (l.wqkv, l.wqkv_s, qd, qd + kd),
+                         "self_attn.v_proj": (l.wqkv, l.wqkv_s, qd + kd, qd + 2 * kd),
+                         "self_attn.o_proj": (l.wo, l.wo_s, 0, l.wo.shape[0]),
+                         "mlp.gate_proj": (l.wgu, l.wgu_s, 0, I), "mlp.up_proj": (l.wgu, l.wgu_s, I, 2 * I),
+                         "mlp.down_proj": (l.wd, l.wd_s, 0, l.wd.shape[0])}
+                for n, (w, s_, a, b) in parts.items():
+                    sd[p + n + ".weight"] = rows(w, a, b)
+                    sd[p + n + ".weight_scale_inv"] = s_[a // 128:(b + 127) // 128]
+                sd[p + "input_layernorm.weight"] = l.attn_norm
+                sd[p + "post_attention_layernorm.weight"] = l.mlp_norm
+                continue
             q, k, v = torch.split(l.wqkv, [cfg.q_dim, cfg.kv_dim, cfg.kv_dim], dim=0)
             g, u = torch.split(l.wgu, cfg.intermediate_size, dim=0)
             sd.update({p + "input_layernorm.weight": l.attn_norm, p + "self_attn.q_proj.weight": q,
@@ -253,8 +358,11 @@ class Llama3Model:
             # steps of up to this many tokens run the decode-step GEMMs (fused all-reduce + residual + norm)
             dec_max_tokens=self._dec_tokens()))
         ex.set_globals(self.w.embed, self.w.final_norm, self.w.lm_head, self.cos_sin)
+        self.is_fp8 = any(l.is_fp8 for l in self.w.layers)
+        if self.is_fp8 and not all(l.is_fp8 for l in self.w.layers):
+            raise ValueError("mixed fp8 / bf16 layers are not supported by the executor")
         for l in self.w.layers:
-            ex.add_layer(l.attn_norm, l.wqkv, l.wo, l.mlp_norm, l.wgu, l.wd)
+            ex.add_layer(l.attn_norm, l.wqkv, l.wo, l.mlp_norm, l.wgu, l.wd, l.scales())
         ex.set_kv_cache(self.kv)
         T, B = self.max_tokens, self.max_seqs
         mk = lambda *s, dtype=dt: torch.empty(*s, dtype=dtype, device=dev)
@@ -269,6 +377,14 @@ class Llama3Model:
         ex.set_buffers(b["h"], b["xn"], b["qkv"], b["attn"], b["act"], b["gu"], b["last_h"],
                        b["last_xn"], self.logits_buf, self.sampled, ops.gemm_workspace(dev),
                        *ops.persistent_gemm_workspace(dev))
+        if self.is_fp8:
+            # quantised activations (e4m3 + one fp32 scale per token and 128-wide K group) and the unfused
+            # gate/up product
+            kmax = max(c.hidden_size, c.intermediate_size, c.q_dim)
+            self._fp8_bufs = (torch.empty(T, kmax, dtype=torch.uint8, device=dev),
+                              torch.empty((kmax + 127) // 128, T, dtype=torch.float32, device=dev),
+                              b["gu"] if b["gu"] is not None else mk(T, 2 * c.intermediate_size))
+            ex.set_fp8_buffers(*self._fp8_bufs)
         ex.set_dec(*ops.decode_gemm_workspace(dev))
         ops.ensure_attention_split_workspace(dev)
         if self.tp is not None and self.tp.world > 1:
@@ -352,6 +468,18 @@ class Llama3Model:
         for li, l in enumerate(self.w.layers):
             kc, vc = kv[:, 0, li], kv[:, 1, li]
             x = ops.rms_norm(h, l.attn_norm, c.rms_norm_eps)
+            if l.is_fp8:
+                # block-scaled fp8 projections: activations quantised per token group in front of every GEMM
+                qkv = ops.linear_fp8(x, l.wqkv, l.wqkv_s)
+                ops.rope_kv_store(qkv, positions, slots, self.cos_sin, kc, vc, c.num_attention_heads,
+                                  c.num_key_value_heads, c.head_dim, False)
+                a = ops.paged_attention(qkv, kc, vc, block_table, q_start, q_len, kv_len, c.num_attention_heads,
+                                        c.num_key_value_heads, c.head_dim, self.scale, plan=plan)
+                h = ops.linear_fp8(a, l.wo, l.wo_s, residual=h)
+                x = ops.rms_norm(h, l.mlp_norm, c.rms_norm_eps)
+                act = ops.silu_mul(ops.linear_fp8(x, l.wgu, l.wgu_s))
+                h = ops.linear_fp8(act, l.wd, l.wd_s, residual=h)
+                continue
             qkv = ops.linear(x, l.wqkv)
             ops.rope_kv_store(qkv, positions, slots, self.cos_sin, kc, vc, c.num_attention_heads,
                               c.num_key_value_heads, c.head_dim, False)

@@ -151,6 +151,39 @@ def shard_llama_config(cfg, world: int):
     return local
 
 
+def _shard_fp8_layer(cfg, l, rank: int, world: int):
+    """Shard of a block-scaled fp8 layer: weights are cut on 128-element boundaries so that every scale block
+    stays whole (the shard sizes of the supported models are multiples of 128)."""
+    from ..models.llama3 import LayerWeights
+
+    hd = cfg.head_dim
+    nq, nkv = cfg.num_attention_heads // world, cfg.num_key_value_heads // world
+    qd, kd, I = cfg.q_dim, cfg.kv_dim, cfg.intermediate_size
+    Il = I // world
+    if (nq * hd) % 128 or (nkv * hd) % 128 or Il % 128:
+        raise ValueError("fp8 tensor parallelism needs per-rank head and FFN sizes that are multiples of 128")
+    u8 = lambda w: w.view(torch.uint8)
+    f8 = lambda w: w.contiguous().view(torch.float8_e4m3fn)
+
+    def rows(w, s, a, n):          # rows [a, a + n) of weight and scales
+        return u8(w)[a:a + n], s[a // 128:(a + n) // 128]
+
+    def cols(w, s, a, n):
+        return u8(w)[:, a:a + n], s[:, a // 128:(a + n) // 128]
+
+    parts = [rows(l.wqkv, l.wqkv_s, rank * nq * hd, nq * hd), rows(l.wqkv, l.wqkv_s, qd + rank * nkv * hd, nkv * hd),
+             rows(l.wqkv, l.wqkv_s, qd + kd + rank * nkv * hd, nkv * hd)]
+    wqkv = f8(torch.cat([p[0] for p in parts], 0))
+    wqkv_s = torch.cat([p[1] for p in parts], 0).contiguous()
+    wo, wo_s = cols(l.wo, l.wo_s, rank * nq * hd, nq * hd)
+    gu = [rows(l.wgu, l.wgu_s, rank * Il, Il), rows(l.wgu, l.wgu_s, I + rank * Il, Il)]
+    wgu = f8(torch.cat([p[0] for p in gu], 0))
+    wgu_s = torch.cat([p[1] for p in gu], 0).contiguous()
+    wd, wd_s = cols(l.wd, l.wd_s, rank * Il, Il)
+    return LayerWeights(l.attn_norm, wqkv, f8(wo), l.mlp_norm, wgu, f8(wd), wqkv_s, wo_s.contiguous(), wgu_s,
+                        wd_s.contiguous())
+
+
 def shard_llama_weights(cfg, weights, rank: int, world: int):
     """Slice full weights into this rank's shard (see the module docstring for the layout)."""
     from ..models.llama3 import LayerWeights, Llama3Weights
@@ -162,6 +195,9 @@ def shard_llama_weights(cfg, weights, rank: int, world: int):
     Il = I // world
     layers = []
     for l in weights.layers:
+        if l.is_fp8:
+            layers.append(_shard_fp8_layer(cfg, l, rank, world))
+            continue
         q, k, v = torch.split(l.wqkv, [cfg.q_dim, cfg.kv_dim, cfg.kv_dim], dim=0)
         wqkv = torch.cat([q[q0:q0 + nq * hd], k[k0:k0 + nkv * hd], v[k0:k0 + nkv * hd]], dim=0).contiguous()
         wo = l.wo[:, q0:q0 + nq * hd].contiguous()

@@ -103,3 +103,76 @@ def test_sampling_and_penalties_on_gpu(small):
     torch.cuda.synchronize()
     ops.check_device_error()
     assert all(len(r.tokens) == 10 and all(0 <= t < cfg.vocab_size for t in r.tokens) for r in recs)
+
+
+# ---------------------------------------------------------------------------- block-scaled fp8 weights
+@pytest.fixture(scope="module")
+def fp8_model():
+    cfg = Llama3Config(hidden_size=1024, intermediate_size=2816, num_hidden_layers=4, num_attention_heads=8,
+                       num_key_value_heads=2, head_dim=128, vocab_size=4096, max_position_embeddings=2048)
+    w = Llama3Weights.random_init(cfg, "cuda", torch.bfloat16, seed=0, std=0.05).quantize_fp8()
+    return cfg, w
+
+
+def test_fp8_executor_matches_op_by_op_and_dequantised_model(fp8_model):
+    """fp8 layers through the native executor (activation quantiser + block-scaled fp8 GEMM per projection):
+    same tokens as the same kernels launched op by op, and agreement with the model whose fp8 weights were
+    expanded to bf16 (what differs is only the 1 x 128 activation quantisation)."""
+    cfg, w = fp8_model
+    assert w.layers[0].is_fp8 and w.layers[0].wqkv.dtype == torch.float8_e4m3fn
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (150, 40, 300, 17)]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True)
+    # 16-token pages: the executor and the op-by-op path then run the same attention kernel, so the two must
+    # agree bit for bit
+    kw = dict(enable_overlap_scheduler=False, device_graph_capture=False)
+    a = _mk(cfg, w, **kw).generate(prompts, sp)
+    llm_b = _mk(cfg, w, **kw)
+    llm_b.model.use_executor = False
+    b = llm_b.generate(prompts, sp)
+    torch.cuda.synchronize()
+    ops.check_device_error()
+    assert [r.tokens for r in a] == [r.tokens for r in b]
+    # against the model whose weights were expanded to bf16: random weights give flat logits, so argmax ties
+    # flip under the activation quantisation noise; compare the logits themselves
+    one = SamplingParams(temperature=0.0, max_new_tokens=1, ignore_eos=True)
+    q8 = _mk(cfg, w, **kw)
+    q8.generate([prompts[0]], one)
+    got = q8.model.logits_buf[0].float().clone()
+    bf = _mk(cfg, w.dequantize(), **kw)
+    bf.generate([prompts[0]], one)
+    want = bf.model.logits_buf[0].float()
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=0).item()
+    assert cos > 0.9, cos       # e4m3 activations add a few percent of noise per projection
+    # and against the fp32 emulation of the very same fp8 arithmetic (PyTorch ops on CPU, same quantisers)
+    from modular_b200.models.llama3 import LayerWeights
+    cpu = lambda t: None if t is None else t.cpu()
+    w_cpu = Llama3Weights(w.embed.cpu(), [LayerWeights(*(cpu(getattr(l, f)) for f in (
+        "attn_norm", "wqkv", "wo", "mlp_norm", "wgu", "wd", "wqkv_s", "wo_s", "wgu_s", "wd_s"))) for l in w.layers],
+        w.final_norm.cpu(), w.lm_head.cpu())
+    emu = LLM(cfg, w_cpu, device="cpu", dtype=torch.bfloat16, max_length=1024, max_batch_size=8,
+              max_batch_input_tokens=512, page_size=16, num_kv_pages=400)
+    emu.generate([prompts[0]], one)
+    want_emu = emu.pipeline.last_logits[0].float()
+    # not bit-comparable: a last-bit difference in a bf16 activation can move an e4m3 value to its neighbour
+    # (a 6 % step), and four layers of random weights amplify that
+    cos = torch.nn.functional.cosine_similarity(got.cpu(), want_emu, dim=0).item()
+    assert cos > 0.98, cos
+    # with graphs and the overlap scheduler
+    c = _mk(cfg, w, graph_batch_sizes=[4]).generate(prompts, sp)
+    assert all(x.tokens[:2] == y.tokens[:2] for x, y in zip(a, c))
+
+
+def test_fp8_checkpoint_roundtrip_keeps_fp8(fp8_model, tmp_path):
+    from safetensors.torch import load_file, save_file
+
+    cfg, w = fp8_model
+    sd = {k: v.cpu() for k, v in w.to_hf_state_dict(cfg).items()}
+    save_file(sd, str(tmp_path / "m.safetensors"))
+    w2 = Llama3Weights.from_state_dict(cfg, load_file(str(tmp_path / "m.safetensors")), "cuda", torch.bfloat16)
+    assert all(l.is_fp8 for l in w2.layers)
+    assert torch.equal(w2.layers[1].wgu.view(torch.uint8), w.layers[1].wgu.view(torch.uint8))
+    assert torch.equal(w2.layers[1].wo_s, w.layers[1].wo_s)
+    w3 = Llama3Weights.from_state_dict(cfg, load_file(str(tmp_path / "m.safetensors")), "cuda", torch.bfloat16,
+                                       keep_fp8=False)
+    assert not w3.layers[0].is_fp8 and w3.layers[0].wqkv.dtype == torch.bfloat16
