@@ -51,6 +51,79 @@ def _reference_arm(args) -> int:
     return 0
 
 
+def _server_arm(args, world: int, model_name: str) -> dict:
+    """The same metric measured at the serving endpoint: starts ``serve`` (HTTP server + model worker, tensor
+    parallel over ``world`` GPUs) as a child process and drives it with the serving benchmark client at the same
+    concurrency, so HTTP, the ZMQ hop between the API and worker processes, detokenisation and SSE streaming are
+    all inside the timed region."""
+    import asyncio
+    import socket
+    import urllib.request
+
+    from modular_b200.benchmark.benchmark_serving import run_benchmark
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s_:
+        s_.bind(("127.0.0.1", 0))
+        port = s_.getsockname()[1]
+    preset = "preset:llama3.3-70b" if args.model == "llama70b-fp8" else "preset:llama3.1-8b"
+    cmd = [sys.executable, "-m", "modular_b200.entrypoints", "serve", "--model-path", preset, "--served-model-name", model_name,
+           "--devices", "gpu:" + ",".join(str(i) for i in range(world)), "--max-length", str(args.input_len + args.output_len + 8),
+           "--max-batch-size", str(args.concurrency), "--max-batch-input-tokens", str(args.max_batch_input_tokens),
+           "--enable-in-flight-batching", "--port", str(port), "--host", "127.0.0.1"]
+    if args.model == "llama70b-fp8":
+        cmd += ["--quantization-encoding", "float8_e4m3fn"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "0"))
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT", "TORCHELASTIC_RUN_ID", "GROUP_RANK",
+              "LOCAL_WORLD_SIZE", "ROLE_RANK", "ROLE_WORLD_SIZE"):
+        env.pop(k, None)           # the server starts its own ranks
+    import tempfile
+
+    log = tempfile.NamedTemporaryFile("w+", suffix=".log", prefix="bench_server_", delete=False)
+
+    def log_tail() -> str:
+        try:
+            log.flush()
+            with open(log.name) as f:
+                return " | ".join(f.read().strip().splitlines()[-3:])[-400:]
+        except Exception:  # noqa: BLE001
+            return ""
+
+    proc = subprocess.Popen(cmd, cwd=REPO, env=env, stdout=log, stderr=subprocess.STDOUT)
+    base = f"http://127.0.0.1:{port}"
+    try:
+        deadline = time.time() + 900
+        while True:
+            if proc.poll() is not None:
+                return {"unavailable": f"server exited with code {proc.returncode} before it was ready: {log_tail()}"}
+            try:
+                with urllib.request.urlopen(base + "/health", timeout=2) as r:
+                    if r.status == 200:
+                        break
+            except Exception:  # noqa: BLE001
+                pass
+            if time.time() > deadline:
+                return {"unavailable": "server was not ready within 15 minutes"}
+            time.sleep(1.0)
+        conc = args.concurrency
+        run = lambda n, seed: asyncio.run(run_benchmark(base, model_name, n, conc, args.input_len, args.output_len,
+                                                        vocab_size=128256, seed=seed))
+        run(args.warmup * conc, 1)
+        res = run(args.steps * conc, 2)
+        if res["failed"]:
+            return {"unavailable": f"{res['failed']} requests failed: {res['errors']}"}
+        return {"value": res["output_token_throughput"], "unit": "tok/s", "p50_ttft_ms": res["p50_ttft_ms"],
+                "p50_tpot_ms": res["p50_tpot_ms"], "p99_ttft_ms": res["p99_ttft_ms"], "p99_tpot_ms": res["p99_tpot_ms"],
+                "duration_s": res["duration_s"], "completed": res["completed"],
+                "path": "HTTP /v1/completions (SSE) -> API process -> ZMQ -> model worker(s)"}
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=30)
+        except Exception:  # noqa: BLE001
+            proc.kill()
+        log.close()
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -114,6 +187,8 @@ def main() -> int:
     ap.add_argument("--concurrency", type=int, default=64)
     ap.add_argument("--max-batch-input-tokens", type=int, default=2176)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
+    ap.add_argument("--no-server", action="store_true",
+                    help="skip the second measurement through the HTTP serving endpoint")
     ap.add_argument("--model", default="llama8b", choices=["llama8b", "llama70b-fp8"],
                     help="llama8b: the headline config (bf16, any --gpus); llama70b-fp8: Llama-3.3-70B shapes with "
                          "block-scaled fp8 weights, tensor parallel over --gpus (input 2048 / output 512 / "
@@ -210,11 +285,33 @@ def main() -> int:
         ranks_agree = all(d == digests[0] for d in digests)
         assert ranks_agree, f"tensor-parallel ranks generated different tokens: {digests}"
     gpu_busy, wall = times.tolist()
+    n_sched_steps = st.steps - st0[0]
+    counters = dict(h2d=st.h2d_bytes - st0[1], d2h=st.d2h_bytes - st0[2], graph_replays=st.graph_replays,
+                    launches=llm.pipeline.gpu_launches() - st0[4])
+    # the serving-endpoint measurement needs the GPUs: leave the process group, drop the engine, then rank 0
+    # alone starts the server (which brings up its own ranks)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    server = None
+    if not args.no_server:
+        import gc
+
+        del llm
+        gc.collect()
+        torch.cuda.empty_cache()
+        if rank == 0:
+            if world > 1:
+                time.sleep(5.0)      # the other ranks' processes are exiting and returning their memory
+            try:
+                server = _server_arm(args, world, "bench-model")
+            except Exception as e:  # noqa: BLE001
+                server = {"unavailable": f"{type(e).__name__}: {e}"}
     if rank == 0:
         ttft = sorted(r.ttft for r in recs)
         tpot = sorted(r.tpot for r in recs)
         p = lambda a, q: a[min(len(a) - 1, int(q * len(a)))]
-        n_sched = st.steps - st0[0]
+        n_sched = n_sched_steps
         value = out_tokens / gpu_busy
         e2e = out_tokens / wall
         line = {
@@ -237,18 +334,16 @@ def main() -> int:
             "p50_ttft_ms": p(ttft, 0.5) * 1e3, "p99_ttft_ms": p(ttft, 0.99) * 1e3,
             "p50_tpot_ms": p(tpot, 0.5) * 1e3, "p99_tpot_ms": p(tpot, 0.99) * 1e3,
             "total_tokens_per_s": (out_tokens + args.steps * conc * args.input_len) / wall,
-            "scheduler_iterations": n_sched, "graph_replays": st.graph_replays,
+            "scheduler_iterations": n_sched, "graph_replays": counters["graph_replays"],
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tok/s", "wall_s": wall,
-                    "h2d_bytes_per_step": (st.h2d_bytes - st0[1]) / args.steps,
-                    "d2h_bytes_per_step": (st.d2h_bytes - st0[2]) / args.steps},
-            "gpu_launches": llm.pipeline.gpu_launches() - st0[4],
+                    "h2d_bytes_per_step": counters["h2d"] / args.steps,
+                    "d2h_bytes_per_step": counters["d2h"] / args.steps},
+            "server": server,
+            "gpu_launches": counters["launches"],
             "ranks_agree": ranks_agree,
         }
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
     return 0
 
 

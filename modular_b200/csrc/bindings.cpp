@@ -846,6 +846,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                              reinterpret_cast<const void*>(mc_in), f, n, algo, error_flag(), cur_stream()),
              "tp_allreduce");
   });
+  m.def("tp_allreduce_lamport", [](int world, int rank, const std::vector<int64_t>& lam, const Tensor& x, Tensor& out,
+                                   int64_t cap, Tensor& state, const c10::optional<Tensor>& residual,
+                                   const c10::optional<Tensor>& gamma, double eps) {
+    need_cuda(x, "x");
+    TORCH_CHECK(x.is_contiguous() && out.is_contiguous() && x.scalar_type() == at::kBFloat16 && state.numel() >= 8 &&
+                    state.scalar_type() == at::kInt && static_cast<int>(lam.size()) == world,
+                "tp_allreduce_lamport: contiguous bf16 tensors, 8 state ints, one buffer per rank");
+    void* a[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) a[i] = reinterpret_cast<void*>(lam[i]);
+    const bool norm = gamma.has_value() && gamma->defined();
+    check_rc(mb_tp_allreduce_lamport(world, rank, a, x.data_ptr(), out.data_ptr(), x.numel(), cap, state.data_ptr<int>(),
+                                     norm ? const_cast<void*>(optptr(residual)) : nullptr, norm ? optptr(gamma) : nullptr,
+                                     norm ? static_cast<int>(x.size(-1)) : 0, static_cast<float>(eps), 0.f, 0,
+                                     error_flag(), cur_stream()),
+             "tp_allreduce_lamport");
+  });
   m.def("tp_wait_flag", [](const Tensor& flag, int target, int timeout_ms, int code, Tensor& ok_out) {
     need_cuda(flag, "flag");
     check_rc(mb_tp_wait_flag(flag.data_ptr<int32_t>(), target, timeout_ms, code, error_flag(),

@@ -197,6 +197,11 @@ int mb_tp_allgather(int world, int rank, void* const* dst_bufs, int* const* flag
 int mb_tp_allreduce(int world, int rank, void* const* in_bufs, void* const* out_bufs, void* out,
                     const void* mc_in, int* const* flags, long long n, int algo, int* err,
                     cudaStream_t stream);
+// Barrier-free one-shot all-reduce (sentinel-polled receive buffers, three generations), optionally with the
+// residual add + RMSNorm epilogue. lam_bufs[r]: [3][world][cap] bf16 on rank r, filled with -0.0 once.
+int mb_tp_allreduce_lamport(int world, int rank, void* const* lam_bufs, const void* x, void* out, long long n,
+                            long long cap, int* state, void* residual, const void* gamma, int cols, float eps,
+                            float w_off, int mbc, int* err, cudaStream_t stream);
 // Bounded wait on a flag word (at most 5 s): *ok_out = 1 when reached, else `code` goes to the error word.
 int mb_tp_wait_flag(const int* flag, int target, unsigned timeout_ms, int code, int* err, int* ok_out,
                     cudaStream_t stream);

@@ -379,6 +379,156 @@ tp_allreduce_multimem_kernel(TpPeers p, const bf16* __restrict__ mc_in, bf16* __
   tp_finish_barrier(p, 1, epoch, err);
 }
 
+// ---------------------------------------------------------------------------- barrier-free all-reduce
+// One-shot all-reduce without any barrier or flag (sentinel protocol): every rank writes its 16-byte packs
+// straight into every peer's receive buffer lam[peer][generation][my rank] and then polls its own receive
+// buffer until no pack holds the sentinel bf16 -0.0 any more - the data is its own arrival signal. Inputs are
+// sanitised (a real -0.0 is sent as +0.0). Three generations rotate: while generation g is in use, peers that
+// run one call ahead already write g+1, and g+2 (read two calls ago) is reset to sentinels, so no rank ever
+// waits for another one to finish reading. All ranks add in rank order: results are bit-identical.
+// Optional epilogue per row of `cols` elements: residual += sum (in place), out = RMSNorm(residual) * gamma.
+//   lam[r]   receive buffer of rank r, [3][world][cap] bf16, every element -0.0 before the first call
+//   state    local ints (zeroed once): [0] generation, [1..3] elements written when a generation was last used,
+//            [4] CTAs that have left
+// Reference: max/kernels/src/comm/allreduce.mojo:1051 (_allreduce_lamport_kernel), comm/lamport.mojo,
+// comm/allreduce_lamport_rmsnorm.mojo:62.
+__device__ __forceinline__ bool lam_pending(const uint4& v) {
+  auto bad = [](uint32_t w) { return (w & 0xffffu) == 0x8000u || (w >> 16) == 0x8000u; };
+  return bad(v.x) || bad(v.y) || bad(v.z) || bad(v.w);
+}
+__device__ __forceinline__ uint32_t lam_clean(uint32_t w) {
+  if ((w & 0xffffu) == 0x8000u) w &= 0xffff0000u;
+  if ((w >> 16) == 0x8000u) w &= 0x0000ffffu;
+  return w;
+}
+__device__ __forceinline__ uint4 ld_volatile_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// Sum over ranks of pack `v` (this rank's contribution `mine` is pushed first). Returns fp32 sums in acc.
+__device__ __forceinline__ void lam_exchange(const TpPeers& p, long long v, long long cap_vec, int g3, uint4 mine,
+                                             float (&acc)[8], int* err) {
+  mine.x = lam_clean(mine.x); mine.y = lam_clean(mine.y); mine.z = lam_clean(mine.z); mine.w = lam_clean(mine.w);
+  const long long gen_off = static_cast<long long>(g3) * p.world * cap_vec;
+#pragma unroll
+  for (int s = 1; s < kMaxRanks; ++s) {
+    if (s < p.world) {
+      const int dst = (p.rank + s) % p.world;
+      reinterpret_cast<uint4*>(p.a[dst])[gen_off + static_cast<long long>(p.rank) * cap_vec + v] = mine;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  const uint4* inbox = reinterpret_cast<const uint4*>(p.a[p.rank]) + gen_off + v;
+  uint64_t t0 = 0;
+  for (int src = 0; src < p.world; ++src) {
+    if (src == p.rank) { accum8(acc, mine); continue; }
+    const uint4* a = inbox + static_cast<long long>(src) * cap_vec;
+    uint4 in = ld_volatile_u4(a);
+    uint32_t spins = 0;
+    while (lam_pending(in)) {
+      if (((++spins) & 0x3f) == 0) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > 1000000000ull) { if (err) atomicCAS(err, 0, 420); break; }
+      }
+      in = ld_volatile_u4(a);
+    }
+    accum8(acc, in);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+tp_allreduce_lamport_kernel(TpPeers p, const bf16* __restrict__ x, bf16* __restrict__ out, long long n, long long cap,
+                            int* state, bf16* __restrict__ residual, const bf16* __restrict__ gamma, int cols,
+                            float eps, float w_off, int mbc, int* err) {
+  __shared__ float red[8];
+  extern __shared__ uint4 lam_row[];
+  const int gen = ld_volatile(state + 0);
+  const int g3 = gen % 3, gclr = (gen + 2) % 3;
+  const long long old_vec = ld_volatile(state + 1 + gclr) >> 3;
+  const long long nvec = n >> 3, cap_vec = cap >> 3;
+  const uint4 sentinel = make_uint4(0x80008000u, 0x80008000u, 0x80008000u, 0x80008000u);
+  if (gamma == nullptr) {
+    for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec;
+         v += static_cast<long long>(gridDim.x) * blockDim.x) {
+      float acc[8];
+      lam_exchange(p, v, cap_vec, g3, reinterpret_cast<const uint4*>(x)[v], acc, err);
+      reinterpret_cast<uint4*>(out)[v] = pack8(acc);
+    }
+  } else {
+    const int rvec = cols >> 3;
+    const long long rows = nvec / rvec;
+    for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+      float ss = 0.f;
+      for (int c = threadIdx.x; c < rvec; c += blockDim.x) {
+        const long long v = r * rvec + c;
+        float acc[8];
+        const uint4 hv = reinterpret_cast<const uint4*>(residual)[v];
+        lam_exchange(p, v, cap_vec, g3, reinterpret_cast<const uint4*>(x)[v], acc, err);
+        accum8(acc, hv);
+        const uint4 o = pack8(acc);
+        const bf162* q = reinterpret_cast<const bf162*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(q[i]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+        reinterpret_cast<uint4*>(residual)[v] = o;
+        lam_row[c] = o;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tot += red[i];
+      const float inv = rsqrtf(tot / static_cast<float>(cols) + eps);
+      for (int c = threadIdx.x; c < rvec; c += blockDim.x) {
+        uint4 a = lam_row[c];
+        const uint4 wv = reinterpret_cast<const uint4*>(gamma)[c];
+        bf162* ap = reinterpret_cast<bf162*>(&a);
+        const bf162* wp = reinterpret_cast<const bf162*>(&wv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(ap[i]);
+          const float2 gm = __bfloat1622float2(wp[i]);
+          if (mbc) {
+            ap[i] = __floats2bfloat162_rn(f.x * inv * (gm.x + w_off), f.y * inv * (gm.y + w_off));
+          } else {
+            const bf162 nrm = __floats2bfloat162_rn(f.x * inv, f.y * inv);
+            const float2 nf = __bfloat1622float2(nrm);
+            ap[i] = __floats2bfloat162_rn(nf.x * (gm.x + w_off), nf.y * (gm.y + w_off));
+          }
+        }
+        reinterpret_cast<uint4*>(out)[r * rvec + c] = a;
+      }
+      __syncthreads();
+    }
+  }
+  // the generation read two calls ago becomes sentinels again
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < old_vec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    for (int src = 0; src < p.world; ++src)
+      if (src != p.rank)
+        reinterpret_cast<uint4*>(p.a[p.rank])[(static_cast<long long>(gclr) * p.world + src) * cap_vec + v] = sentinel;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(state + 4, 1);
+    if (prev == static_cast<int>(gridDim.x) - 1) {
+      state[4] = 0;
+      state[1 + g3] = static_cast<int>(n);
+      state[0] = gen + 1;
+    }
+  }
+}
+
 // Broadcast n bytes (n % 16 == 0) of root's symmetric buffer a[root] into out on every rank (pull).
 __global__ void __launch_bounds__(256)
 tp_broadcast_kernel(TpPeers p, int root, uint8_t* __restrict__ out, long long n, int* err) {
@@ -490,6 +640,33 @@ extern "C" int mb_tp_allreduce(int world, int rank, void* const* in_bufs, void* 
                                                            static_cast<bf16*>(out), n, err);
   else
     return MB_ERR_SHAPE;
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+// Barrier-free one-shot all-reduce of `x` (local bf16, n % 8 == 0, n <= cap) into `out` (local); see the kernel.
+// gamma != nullptr: rows of `cols` elements, residual += sum (in place), out = RMSNorm(residual) * (gamma + w_off).
+// `state` holds 8 zeroed ints that live as long as the receive buffers; every rank must issue the same calls.
+extern "C" int mb_tp_allreduce_lamport(int world, int rank, void* const* lam_bufs, const void* x, void* out,
+                                       long long n, long long cap, int* state, void* residual, const void* gamma,
+                                       int cols, float eps, float w_off, int mbc, int* err, cudaStream_t stream) {
+  if (world < 1 || world > kMaxRanks || n % 8 || cap % 8 || n > cap || n >= (1ll << 31)) return MB_ERR_SHAPE;
+  if (n <= 0) return MB_OK;
+  if (gamma != nullptr && (residual == nullptr || cols <= 0 || cols % 8 || n % cols || cols > 32768)) return MB_ERR_SHAPE;
+  TpPeers p = make_peers(world, rank, lam_bufs, nullptr, lam_bufs ? reinterpret_cast<int* const*>(lam_bufs) : nullptr);
+  for (int i = 0; i < kMaxRanks; ++i) p.flags[i] = nullptr;
+  int grid;
+  size_t smem = 0;
+  if (gamma != nullptr) {
+    grid = static_cast<int>(n / cols);
+    smem = static_cast<size_t>(cols) * 2;
+  } else {
+    grid = static_cast<int>(((n >> 3) + 255) / 256);
+  }
+  if (grid > 592) grid = 592;
+  if (grid < 1) grid = 1;
+  tp_allreduce_lamport_kernel<<<grid, 256, smem, stream>>>(
+      p, static_cast<const bf16*>(x), static_cast<bf16*>(out), n, cap, state, static_cast<bf16*>(residual),
+      static_cast<const bf16*>(gamma), cols, eps, w_off, mbc, err);
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 

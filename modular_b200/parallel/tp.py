@@ -84,6 +84,10 @@ class Collectives:
     comm/allgather.mojo:167, comm/broadcast.mojo:173; nn/comm/allreduce.py:40 (``Allreduce`` layer).
     """
 
+    # messages up to this size take the barrier-free path under ``auto`` (the reference selects its sentinel
+    # kernel for <= 1 MB on 2/4/8 B200, comm/allreduce.mojo:320-372)
+    LAMPORT_MAX_BYTES = 1 << 20
+
     def __init__(self, ctx: TPContext, max_bytes: int = 64 << 20):
         from .._native import lib
 
@@ -92,13 +96,27 @@ class Collectives:
         self.out = ctx.alloc_symmetric(max_bytes // 2, torch.bfloat16)
         self.flags = ctx.alloc_symmetric(self.L.tp_flag_ints(), torch.int32, zero=True)
         self.multicast_ptr = int(getattr(self.inp.handle, "multicast_ptr", 0) or 0)
+        # barrier-free small-message path: receive buffers [3 generations][world][cap] of bf16 -0.0 sentinels
+        self.lam_cap = min(self.LAMPORT_MAX_BYTES, max_bytes) // 2
+        self.lam = ctx.alloc_symmetric(3 * ctx.world * self.lam_cap, torch.bfloat16)
+        self.lam.tensor.view(torch.int16).fill_(-32768)
+        self.lam_state = torch.zeros(8, dtype=torch.int32, device=ctx.device)
         ctx.barrier()
 
     def all_reduce(self, x: torch.Tensor, algo: str = "auto") -> torch.Tensor:
-        """Sum of ``x`` (bf16, numel % 8 == 0) over all ranks. algo: auto | one_shot | two_shot | multimem."""
+        """Sum of ``x`` (bf16, numel % 8 == 0) over all ranks.
+        algo: auto | lamport (barrier-free, sentinel-polled; small messages) | one_shot | two_shot | multimem."""
         n = x.numel()
         if x.dtype != torch.bfloat16 or n % 8 or n * 2 > self.max_bytes:
             raise ValueError("all_reduce: bf16 tensors with numel % 8 == 0 up to the staging size")
+        if algo == "lamport" or (algo == "auto" and n <= self.lam_cap):
+            if n > self.lam_cap:
+                raise ValueError(f"lamport all-reduce takes at most {self.lam_cap} elements")
+            c = self.ctx
+            res = torch.empty_like(x)
+            self.L.tp_allreduce_lamport(c.world, c.rank, self.lam.peer_ptrs, x.contiguous(), res, self.lam_cap,
+                                        self.lam_state, None, None, 0.0)
+            return res
         code = {"auto": 0, "one_shot": 1, "two_shot": 2, "multimem": 3}[algo]
         if code == 3 and not self.multicast_ptr:
             raise RuntimeError("this symmetric allocation has no NVLink multicast mapping")
@@ -111,6 +129,17 @@ class Collectives:
         if two_shot:
             res.copy_(self.out.tensor[:n].view_as(x))
         return res
+
+    def all_reduce_add_rms_norm(self, x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float):
+        """``residual += all_reduce(x)`` (in place) and ``rms_norm(residual) * gamma`` in one barrier-free kernel.
+        x, residual: [rows, cols] bf16. Returns (normalised rows, residual)."""
+        if x.numel() > self.lam_cap or x.shape != residual.shape or x.shape[-1] % 8:
+            raise ValueError("all_reduce_add_rms_norm: rows of a multiple of 8 elements, within the receive buffer")
+        c = self.ctx
+        out = torch.empty_like(x)
+        self.L.tp_allreduce_lamport(c.world, c.rank, self.lam.peer_ptrs, x.contiguous(), out, self.lam_cap,
+                                    self.lam_state, residual, gamma, eps)
+        return out, residual
 
     def all_gather(self, x: torch.Tensor) -> torch.Tensor:
         """Concatenation of every rank's ``x`` along dim 0 (bf16 or fp32 rows of 16-byte multiples)."""

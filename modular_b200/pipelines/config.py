@@ -185,6 +185,20 @@ class PipelineConfig(ConfigFileModel):
     speculative: SpeculativeConfig = Field(default_factory=SpeculativeConfig)
     runtime: PipelineRuntimeConfig = Field(default_factory=PipelineRuntimeConfig)
     task: str = "text_generation"
+    # set by the model worker for each tensor-parallel rank it starts (not user options)
+    tp_size: int = 1
+    tp_rank: int = 0
+
+    @property
+    def tensor_parallel_degree(self) -> int:
+        """GPUs that share one model replica: the configured devices divided among the data-parallel replicas
+        (the reference shards a model over all devices it is given, nn/transformer/distributed_transformer.py)."""
+        m = self.model
+        if not m.uses_gpu:
+            return 1
+        if m.tensor_parallel_degree:
+            return max(1, min(int(m.tensor_parallel_degree), len(m.device_ids)))
+        return max(1, len(m.device_ids) // max(1, m.data_parallel_degree or 1))
 
     # ---- convenience accessors used across the code base
     @property

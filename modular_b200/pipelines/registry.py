@@ -116,19 +116,34 @@ class PipelineRegistry:
 
         m, rt = pc.model, pc.runtime
         on_gpu = m.uses_gpu and torch.cuda.is_available()
-        device = torch.device(f"cuda:{m.device_ids[0]}" if on_gpu else "cpu")
+        dev_i = int(getattr(pc, "tp_rank", 0) or 0) if int(getattr(pc, "tp_size", 1) or 1) > 1 else 0
+        device = torch.device(f"cuda:{m.device_ids[dev_i]}" if on_gpu else "cpu")
         enc = m.quantization_encoding or (arch.default_encoding if on_gpu else "float32")
-        dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}.get(enc)
+        # float8_e4m3fn: projections are quantised to block-scaled fp8 at load (checkpoints that already are
+        # block-scaled fp8 stay fp8 under every encoding); everything else runs in bf16
+        to_fp8 = enc in ("float8_e4m3fn", "fp8")
+        dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16,
+                 "float8_e4m3fn": torch.bfloat16, "fp8": torch.bfloat16}.get(enc)
         if dtype is None:
             raise ValueError(f"encoding {enc!r} is not supported by {arch.name} (supported: {arch.supported_encodings})")
         quant = parse_quant_config(hf)
         if quant is not None and not quant.is_blockscaled_fp8:
             raise ValueError(f"quantisation format {quant.format!r} is not supported yet")
+        tp_size, tp_rank = int(getattr(pc, "tp_size", 1) or 1), int(getattr(pc, "tp_rank", 0) or 0)
+        sharded = False
         if m.random_weights or m.model_path.startswith("preset:"):
             weights = None
+            # models too large to exist whole on one GPU (and fp8 ones) are created at shard size; small ones
+            # are created whole and sliced, so that every tensor-parallel degree serves the same weights
+            big = hasattr(cfg, "param_count") and cfg.param_count() > 30e9
+            if (to_fp8 or (tp_size > 1 and big)) and hasattr(arch.weights_class, "random_init_shard"):
+                weights = arch.weights_class.random_init_shard(cfg, tp_rank, tp_size, device, dtype, seed=0, fp8=to_fp8)
+                sharded = tp_size > 1
         else:
             sd = load_state_dict(m.model_path, m.weight_path)
             weights = arch.weights_class.from_state_dict(cfg, sd.to_dict(), device, dtype)
+            if to_fp8:
+                weights = weights.quantize_fp8()
         plan = self.plan_memory(pc, cfg, device) if on_gpu else None
         max_length = min(m.max_length or cfg.max_position_embeddings, cfg.max_position_embeddings)
         if plan is not None:
@@ -150,7 +165,8 @@ class PipelineRegistry:
                   eos_token_ids=tokenizer.eos_token_ids,
                   host_kvcache_swap_space_gb=m.kv_cache.host_kvcache_swap_space_gb,
                   disk_kvcache_dir=m.kv_cache.disk_kvcache_dir,
-                  disk_kvcache_space_gb=m.kv_cache.disk_kvcache_space_gb)
+                  disk_kvcache_space_gb=m.kv_cache.disk_kvcache_space_gb,
+                  tp_size=tp_size, tp_rank=tp_rank, weights_are_sharded=sharded)
         llm.tokenizer = tokenizer
         if pc.sampling.enable_structured_output:
             llm.pipeline.enable_structured_output(tokenizer)

@@ -54,6 +54,34 @@ def scheduler_config_from(pipeline_config, llm) -> TokenGenerationSchedulerConfi
         kv_lookahead_tokens=1 if rt.enable_overlap_scheduler else 0)
 
 
+def _drain(q, limit: int) -> list:
+    """Everything waiting on a worker queue (at most ``limit`` items when limit > 0)."""
+    import queue as _q
+
+    out = []
+    while limit <= 0 or len(out) < limit:
+        try:
+            out.append(q.get_nowait())
+        except (_q.Empty, Exception):  # noqa: BLE001  (zmq queues raise their own Empty)
+            break
+    return out
+
+
+class _PerRankFactory:
+    """``factory(pipeline_config)``: the registry's build function with the pipeline config replaced (picklable,
+    so that it can be handed to spawned ranks)."""
+
+    def __init__(self, partial):
+        self.func, self.args, self.kw = partial.func, partial.args, dict(partial.keywords or {})
+
+    def __call__(self, pc):
+        return self.func(pc, *self.args[1:], **self.kw)
+
+
+def _rebind_factory(factory):
+    return _PerRankFactory(factory)
+
+
 def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, settings,
                       ready_event, alive_event, stop_event) -> None:
     """Entry point of the spawned process."""
@@ -61,7 +89,20 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
                         format=f"%(asctime)s {settings.log_prefix or 'worker'} %(levelname)s %(name)s: %(message)s")
     try:
         t0 = time.perf_counter()
-        built = factory()
+        # tensor parallelism: this process is rank 0; the other ranks are started here and fed in lock step
+        tp_world = getattr(pipeline_config, "tensor_parallel_degree", 1) if pipeline_config is not None else 1
+        feed, followers = None, []
+        if tp_world > 1 and getattr(factory, "func", None) is not None:
+            from . import tp_worker
+            port = tp_worker.free_port()
+            per_rank = _rebind_factory(factory)
+            followers = tp_worker.start_followers(tp_world, port, per_rank, pipeline_config, settings)
+            pc0 = tp_worker.rank_config(pipeline_config, 0, tp_world)
+            ctl = tp_worker.init_distributed(0, tp_world, port, pc0.model.device_ids[0])
+            built = per_rank(pc0)
+            feed = tp_worker.LockstepFeed(ctl, 0)
+        else:
+            built = factory()
         llm = None
         if hasattr(built, "pipeline"):          # an LLM facade from the registry
             llm, pipeline, kv = built, built.pipeline, built.kv
@@ -82,8 +123,13 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
                     mq.put_nowait(m.to_dict())
                 except Exception:  # noqa: BLE001
                     pass
-        sched = TokenGenerationScheduler(cfg, pipeline, kv, queues.request, queues.response, queues.cancel,
-                                         metrics_sink=sink)
+        if feed is not None:
+            # the scheduler reads the replicated stream; rank 0 alone answers the API process
+            sched = TokenGenerationScheduler(cfg, pipeline, kv, feed.requests, queues.response, feed.cancels,
+                                             metrics_sink=sink)
+        else:
+            sched = TokenGenerationScheduler(cfg, pipeline, kv, queues.request, queues.response, queues.cancel,
+                                             metrics_sink=sink)
         def load_lora(arg):
             if llm is None:
                 raise RuntimeError("this pipeline does not take LoRA adapters")
@@ -116,6 +162,10 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
         idle = 0
         while not stop_event.is_set():
             alive_event.set()
+            if feed is not None:
+                if any(not p.is_alive() for p in followers):
+                    raise RuntimeError("a tensor-parallel rank died")
+                feed.exchange(_drain(queues.request, cfg.max_pending_requests), _drain(queues.cancel, 0))
             progress = sched.run_iteration()
             side.service(handlers)
             if progress is SchedulerProgress.NO_PROGRESS:
@@ -123,6 +173,8 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
                 time.sleep(min(0.0001 * (2 ** min(idle, 6)), 0.005))
             else:
                 idle = 0
+        if feed is not None:
+            feed.exchange(stop=True)
     except BaseException:  # noqa: BLE001
         traceback.print_exc()
         os._exit(1)

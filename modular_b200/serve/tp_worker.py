@@ -1,0 +1,115 @@
+"""Tensor-parallel model worker: one process per GPU behind one serving endpoint.
+
+The model worker that owns the ZMQ queues is rank 0. It starts ``world - 1`` follower processes; every rank
+builds its shard of the model and runs the *same* scheduler on the *same* requests, so all ranks construct
+identical batches and meet in the kernels' collectives without any per-step negotiation. The only thing that has
+to travel is the input: once per loop iteration rank 0 broadcasts the requests and cancellations it drained from
+the API process (as the msgpack frames of ``worker_interface/codec.py``, over a gloo group so the control plane
+never touches the GPUs' streams), and every rank enqueues them before its ``run_iteration``. Followers discard
+their outputs; rank 0 answers the API process.
+
+Reference: the reference drives all GPUs of a replica from one process and one compiled graph
+(max/python/max/serve/pipelines/model_worker.py:213, nn/transformer/distributed_transformer.py:297); with one
+process per GPU the lock-step scheduler plays that role.
+"""
+
+from __future__ import annotations
+
+import copy
+import os
+import queue
+import socket
+from typing import Optional
+
+from .worker_interface import codec
+
+
+def free_port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def rank_config(pipeline_config, rank: int, world: int):
+    pc = copy.deepcopy(pipeline_config)
+    pc.tp_size, pc.tp_rank = world, rank
+    return pc
+
+
+def init_distributed(rank: int, world: int, port: int, device_index: int):
+    """NCCL group for the kernels' bootstrap, gloo group for the control plane."""
+    import torch
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    torch.cuda.set_device(device_index)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", device_index), rank=rank, world_size=world)
+    return dist.new_group(backend="gloo")
+
+
+class LockstepFeed:
+    """Replicates rank 0's request stream on every rank (see the module docstring)."""
+
+    def __init__(self, ctl_group, rank: int):
+        self.group, self.rank = ctl_group, rank
+        self.requests: "queue.SimpleQueue" = queue.SimpleQueue()
+        self.cancels: "queue.SimpleQueue" = queue.SimpleQueue()
+
+    def exchange(self, new_ctxs=(), cancels=(), stop: bool = False) -> bool:
+        """Rank 0 passes what it drained; every rank returns with the same items in its local queues.
+        Returns False when rank 0 asked the group to stop."""
+        import torch.distributed as dist
+
+        box = [None]
+        if self.rank == 0:
+            box[0] = {"new": [codec.encode(c) for c in new_ctxs], "cancel": list(cancels), "stop": stop}
+        dist.broadcast_object_list(box, src=0, group=self.group)
+        msg = box[0]
+        for frame in msg["new"]:
+            self.requests.put_nowait(codec.decode(frame))
+        for rid in msg["cancel"]:
+            self.cancels.put_nowait(rid)
+        return not msg["stop"]
+
+
+class _NullQueue:
+    def put_nowait(self, _obj) -> None:
+        pass
+
+
+def follower_main(rank: int, world: int, port: int, factory, pipeline_config, settings) -> None:
+    """Entry point of ranks 1..world-1 (spawned by rank 0)."""
+    import logging
+    import traceback
+
+    from .model_worker import scheduler_config_from
+    from .scheduler import TokenGenerationScheduler
+
+    logging.basicConfig(level=getattr(logging, str(settings.log_level).upper(), logging.INFO),
+                        format=f"%(asctime)s tp-rank-{rank} %(levelname)s %(name)s: %(message)s")
+    try:
+        pc = rank_config(pipeline_config, rank, world)
+        ctl = init_distributed(rank, world, port, pc.model.device_ids[rank])
+        llm = factory(pc)
+        feed = LockstepFeed(ctl, rank)
+        sched = TokenGenerationScheduler(scheduler_config_from(pc, llm), llm.pipeline, llm.kv, feed.requests,
+                                         _NullQueue(), feed.cancels)
+        while feed.exchange():
+            sched.run_iteration()
+    except BaseException:  # noqa: BLE001
+        traceback.print_exc()
+        os._exit(1)
+
+
+def start_followers(world: int, port: int, factory, pipeline_config, settings) -> list:
+    import multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    procs = []
+    for r in range(1, world):
+        p = ctx.Process(target=follower_main, args=(r, world, port, factory, pipeline_config, settings), daemon=True,
+                        name=f"tp-rank-{r}")
+        p.start()
+        procs.append(p)
+    return procs

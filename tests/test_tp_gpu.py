@@ -73,3 +73,36 @@ def test_tp_matches_single_gpu(world, fused, dec):
     assert all(a[:3] == b[:3] for a, b in zip(toks[0], ref))
     assert sum(a == b for a, b in zip(toks[0], ref)) >= len(ref) - 2
     assert res[0]["graph_replays"] > 0
+
+
+def test_tensor_parallel_serving_matches_single_gpu():
+    """`serve` over two GPUs: the model worker starts a follower rank, both run the scheduler in lock step on
+    the replicated request stream; the HTTP answers equal those of a one-GPU server with the same weights."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from fastapi.testclient import TestClient
+
+    from modular_b200.pipelines.config import PipelineArgs, PipelineConfig
+    from modular_b200.pipelines.registry import PIPELINE_REGISTRY
+    from modular_b200.serve.api_server import fastapi_app
+    from modular_b200.serve.config import Settings
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    body = {"prompt": list(range(5, 45)), "max_tokens": 8, "temperature": 0, "ignore_eos": True, "logprobs": 1}
+    outs = {}
+    for devices in ("gpu:0", "gpu:0,1"):
+        pc = PipelineConfig.from_args(PipelineArgs.from_flat_kwargs(
+            None, model_path="preset:tiny-llama", devices=devices, max_length=256, max_batch_size=4,
+            max_batch_input_tokens=128, kv_cache_page_size=16))
+        assert pc.tensor_parallel_degree == len(devices.split(","))
+        tokenizer, factory = PIPELINE_REGISTRY.retrieve_factory(pc)
+        app = fastapi_app(Settings(), pc, tokenizer, factory, "tiny", 256)
+        with TestClient(app) as c:
+            rs = [c.post("/v1/completions", json=dict(body, model="tiny")) for _ in range(2)]
+            assert all(r.status_code == 200 for r in rs), rs[0].text
+            lp = [r.json()["choices"][0]["logprobs"] for r in rs]
+            assert lp[0]["tokens"] == lp[1]["tokens"]
+            outs[devices] = lp[0]
+    a, b = outs["gpu:0"], outs["gpu:0,1"]
+    assert a["tokens"][:3] == b["tokens"][:3]
+    assert max(abs(x - y) for x, y in zip(a["token_logprobs"][:3], b["token_logprobs"][:3])) < 0.1
