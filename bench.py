@@ -176,6 +176,119 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
+def _deepseek_arm(args, defaults) -> int:
+    """DeepSeek-V3 served expert-parallel: every rank holds E / N routed experts (block-scaled fp8) and a copy of
+    the attention, dense and shared-expert weights, and serves its own concurrency / N requests; the ranks meet
+    in the dispatch / combine kernels of every MoE layer. Device time is one pair of CUDA events around the
+    whole closed-loop run on every rank, maximum over ranks."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    if args.warmup < 3:
+        args.warmup = 3
+    conc_total = 256 if args.concurrency == defaults.concurrency else args.concurrency
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from modular_b200 import _native
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.models.deepseek_v3 import DeepseekV3Config, DeepseekV3Weights
+    from modular_b200.pipelines.context import SamplingParams
+
+    _native.count_calls(True)
+    cfg = DeepseekV3Config.deepseek_v3()
+    if args.layers:
+        cfg.num_hidden_layers = args.layers
+    conc = conc_total // world
+    max_len = args.input_len + args.output_len + 8
+    weights = DeepseekV3Weights.random_init_ep(cfg, rank, world, dev, torch.bfloat16, seed=0, fp8_experts=True)
+    pages = conc * (-(-max_len // 128) + 1) + 16
+    llm = LLM(cfg, weights, device=dev, dtype=torch.bfloat16, max_length=max_len, max_batch_size=conc,
+              max_batch_input_tokens=args.max_batch_input_tokens, page_size=128, num_kv_pages=pages,
+              enable_prefix_caching=False, enable_chunked_prefill=True, enable_in_flight_batching=False,
+              device_graph_capture=True, graph_batch_sizes=[conc], seed=0,
+              ep_size=world, ep_rank=rank, ep_fp8_dispatch=True)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=args.output_len, ignore_eos=True)
+    rng = np.random.default_rng(1234 + rank)
+
+    def prompts(n):
+        return [rng.integers(0, cfg.vocab_size, size=args.input_len, dtype=np.int64) for _ in range(n)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # every rank runs the same number of requests of the same lengths: the schedulers take the same steps
+    llm.generate(prompts(args.warmup * conc), sp, max_concurrency=conc)
+    barrier()
+    st = llm.pipeline.stats
+    steps0, calls0, rep0 = st.steps, _native.native_calls(), llm.model.replayed_calls
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    timed = prompts(args.steps * conc)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0 = time.perf_counter()
+    ev0.record()
+    recs = llm.generate(timed, sp, max_concurrency=conc)
+    ev1.record()
+    barrier()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    out_tokens = sum(len(r.tokens) for r in recs)
+    assert out_tokens == args.steps * conc * args.output_len, (out_tokens,)
+    from modular_b200 import ops
+
+    ops.check_device_error()
+    times = torch.tensor([ev0.elapsed_time(ev1) / 1e3, wall], dtype=torch.float64, device="cuda")
+    total = torch.tensor([out_tokens], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(total)
+    dev_s, wall = times.tolist()
+    total_out = float(total)
+    launches = (_native.native_calls() - calls0) + (llm.model.replayed_calls - rep0)
+    if rank == 0:
+        ttft = sorted(r.ttft for r in recs)
+        tpot = sorted(r.tpot for r in recs)
+        p = lambda a, q: a[min(len(a) - 1, int(q * len(a)))]
+        full = not args.layers
+        line = {
+            "metric": f"output_tokens_per_s_at_concurrency_{conc_total}", "value": total_out / dev_s, "unit": "tok/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_s / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp8 e4m3 routed experts (128x128 block scales) with fp8 dispatch, bf16 elsewhere",
+            "data": "synthetic uniform-random token ids; random-init N(0,0.02) weights", "impl": "ours",
+            "config": {"model": "DeepSeek-V3 architecture (61L, h7168, MLA 128 heads, 256 routed experts top-8 + 1 shared, "
+                                "vocab 129280)" + ("" if full else f" REDUCED TO {args.layers} LAYERS (not the named config)"),
+                       "global_batch": conc_total, "seq_len": args.input_len + args.output_len,
+                       "input_len": args.input_len, "output_len": args.output_len,
+                       "num_requests": args.steps * conc_total, "concurrency": conc_total,
+                       "parallelism": f"ep{world} + data-parallel attention ({conc} requests per rank)",
+                       "kv_page_tokens": 128, "max_batch_input_tokens": args.max_batch_input_tokens,
+                       "step_definition": f"{conc_total} requests served to completion (closed loop)",
+                       "l2_policy": "inputs larger than L2 (each rank streams GBs of weights every iteration)"},
+            "p50_ttft_ms": p(ttft, 0.5) * 1e3, "p99_ttft_ms": p(ttft, 0.99) * 1e3,
+            "p50_tpot_ms": p(tpot, 0.5) * 1e3, "p99_tpot_ms": p(tpot, 0.99) * 1e3,
+            "scheduler_iterations": st.steps - steps0, "graph_replays": llm.model.graph_replays,
+            "clocks": clocks,
+            # the device interval already contains the per-step uploads and token read-backs of the engine
+            "e2e": {"value": total_out / wall, "unit": "tok/s", "wall_s": wall,
+                    "note": "inputs are uploaded from host memory and sampled tokens read back every iteration"},
+            "gpu_launches": launches,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -189,11 +302,16 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
     ap.add_argument("--no-server", action="store_true",
                     help="skip the second measurement through the HTTP serving endpoint")
-    ap.add_argument("--model", default="llama8b", choices=["llama8b", "llama70b-fp8"],
+    ap.add_argument("--model", default="llama8b", choices=["llama8b", "llama70b-fp8", "deepseek-v3"],
                     help="llama8b: the headline config (bf16, any --gpus); llama70b-fp8: Llama-3.3-70B shapes with "
                          "block-scaled fp8 weights, tensor parallel over --gpus (input 2048 / output 512 / "
-                         "concurrency 128 unless given)")
+                         "concurrency 128 unless given); deepseek-v3: DeepSeek-V3 shapes, fp8 routed experts, "
+                         "expert parallel over --gpus with data-parallel attention (concurrency 256 over all ranks)")
     args = ap.parse_args()
+    if args.model == "deepseek-v3":
+        if args.impl == "reference":
+            return _reference_arm(args)
+        return _deepseek_arm(args, ap.parse_args([]))
     if args.model == "llama70b-fp8":
         defaults = ap.parse_args([])
         if args.input_len == defaults.input_len:

@@ -62,8 +62,45 @@ def _load():
         return _MOD
 
 
+class _CountingLib:
+    """The extension module with every function call counted (``native_calls()``): a lower bound of the kernels
+    launched by paths that are driven op by op from Python (some functions launch two or three kernels)."""
+
+    def __init__(self, mod):
+        self._mod, self._cache, self.calls = mod, {}, 0
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            target = getattr(self._mod, name)
+            if not callable(target):
+                return target
+
+            def fn(*a, __t=target, **k):
+                self.calls += 1
+                return __t(*a, **k)
+
+            self._cache[name] = fn
+        return fn
+
+
+_COUNTING: _CountingLib | None = None
+
+
+def count_calls(on: bool = True) -> None:
+    """Route ``lib()`` through a call counter (off by default: one Python frame per call)."""
+    global _COUNTING
+    _COUNTING = _CountingLib(_load()) if on and _load() is not None else None
+
+
+def native_calls() -> int:
+    return _COUNTING.calls if _COUNTING is not None else 0
+
+
 def lib(required: bool = True):
     mod = _load()
+    if _COUNTING is not None:
+        return _COUNTING
     if mod is None and required:
         raise RuntimeError(
             f"modular_b200 native library could not be loaded from {SO_PATH}: {_ERR!r}. "

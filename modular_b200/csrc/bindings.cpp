@@ -868,6 +868,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                              ok_out.data_ptr<int32_t>(), cur_stream()),
              "tp_wait_flag");
   });
+  m.def("tp_scatter", [](int world, int rank, int root, const std::vector<int64_t>& in_bufs, Tensor& out,
+                         const std::vector<int64_t>& flags, int64_t chunk_bytes) {
+    void* a[8] = {}; int* f[8] = {};
+    for (int i = 0; i < world && i < 8; ++i) {
+      a[i] = reinterpret_cast<void*>(in_bufs[i]);
+      f[i] = reinterpret_cast<int*>(flags[i]);
+    }
+    check_rc(mb_tp_scatter(world, rank, root, a, out.data_ptr(), f, chunk_bytes, error_flag(), cur_stream()),
+             "tp_scatter");
+  });
   m.def("tp_broadcast", [](int world, int rank, int root, const std::vector<int64_t>& in_bufs, Tensor& out,
                            const std::vector<int64_t>& flags, int64_t nbytes) {
     void* a[8] = {}; int* f[8] = {};
@@ -970,6 +980,50 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                   w.data_ptr<float>(), optptr(shared), y.data_ptr(), y.size(0), y.size(1),
                                   topk_ids.size(1), e_local, cap, cur_stream()),
              "ep_combine_reduce");
+  });
+  // receive buffers -> rows in expert order + offsets + order, one launch; fp8 rows are split into payload and
+  // group-major scales
+  m.def("ep_recv_compact", [](const Tensor& recv_x, const Tensor& recv_meta, const Tensor& flags, int world, int cap,
+                              int n_experts, int hidden, bool fp8, int rows_bound, Tensor& offsets, Tensor& order,
+                              Tensor& xq, const c10::optional<Tensor>& xs) {
+    need_cuda(recv_x, "recv_x");
+    TORCH_CHECK(recv_meta.scalar_type() == at::kInt && offsets.scalar_type() == at::kInt &&
+                    order.scalar_type() == at::kInt && offsets.numel() >= n_experts + 1 && xq.is_contiguous() &&
+                    xq.dim() == 2 && order.numel() >= xq.size(0) && xq.size(0) >= rows_bound &&
+                    xq.size(1) * xq.element_size() == (fp8 ? hidden : hidden * 2),
+                "ep_recv_compact layout");
+    TORCH_CHECK(!fp8 || (xs.has_value() && xs->is_contiguous() && xs->scalar_type() == at::kFloat && xs->dim() == 2 &&
+                         xs->size(0) == hidden / 128 && xs->size(1) >= rows_bound),
+                "ep_recv_compact: scales [hidden / 128, >= rows_bound]");
+    check_rc(mb_ep_recv_compact(recv_x.data_ptr(), recv_meta.data_ptr<int32_t>(), flags.data_ptr<int32_t>(), world,
+                                cap, n_experts, hidden, fp8 ? 1 : 0, rows_bound, offsets.data_ptr<int32_t>(),
+                                order.data_ptr<int32_t>(), xq.data_ptr(), xs ? xs->data_ptr<float>() : nullptr,
+                                xs ? static_cast<int>(xs->size(1)) : 0, num_sms(), cur_stream()),
+             "ep_recv_compact");
+  });
+  m.def("dequant_fp8_group128", [](const Tensor& q, const Tensor& scales, Tensor& out, const c10::optional<Tensor>& n_rows) {
+    need_cuda(q, "q");
+    TORCH_CHECK(q.is_contiguous() && q.element_size() == 1 && q.dim() == 2 && out.is_contiguous() &&
+                    out.scalar_type() == at::kBFloat16 && out.size(0) == q.size(0) && out.size(1) == q.size(1) &&
+                    scales.is_contiguous() && scales.scalar_type() == at::kFloat && scales.dim() == 2 &&
+                    scales.size(0) == q.size(1) / 128 && scales.size(1) >= q.size(0),
+                "dequant_fp8_group128 layout");
+    check_rc(mb_dequant_fp8_group128(q.data_ptr(), scales.data_ptr<float>(), out.data_ptr(), q.size(0), q.size(1),
+                                     static_cast<int>(scales.size(1)), n_rows ? n_rows->data_ptr<int32_t>() : nullptr,
+                                     cur_stream()),
+             "dequant_fp8_group128");
+  });
+  m.def("silu_mul_quant_fp8", [](const Tensor& gu, Tensor& q, Tensor& scales, const c10::optional<Tensor>& n_rows) {
+    need_cuda(gu, "gate_up");
+    const int M = gu.size(0), I = gu.size(1) / 2;
+    TORCH_CHECK(gu.is_contiguous() && gu.scalar_type() == at::kBFloat16 && q.is_contiguous() && q.element_size() == 1 &&
+                    q.size(0) == M && q.size(1) == I && scales.is_contiguous() && scales.scalar_type() == at::kFloat &&
+                    scales.dim() == 2 && scales.size(0) == I / 128 && scales.size(1) >= M,
+                "silu_mul_quant_fp8 layout");
+    check_rc(mb_silu_mul_quant_fp8(gu.data_ptr(), q.data_ptr(), scales.data_ptr<float>(), M, I,
+                                   static_cast<int>(scales.size(1)), n_rows ? n_rows->data_ptr<int32_t>() : nullptr,
+                                   cur_stream()),
+             "silu_mul_quant_fp8");
   });
   m.def("ep_dequant_rows", [](const Tensor& src, Tensor& dst, int n, const c10::optional<Tensor>& n_rows) {
     need_cuda(src, "src");

@@ -90,6 +90,13 @@ int mb_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, int 
 int mb_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int rows, int cols,
                    float eps, float weight_offset, int multiply_before_cast, cudaStream_t stream);
 int mb_silu_mul(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream);
+int mb_silu_mul_quant_fp8(const void* gate_up, void* q_fp8, float* scales, int M, int inter, int ld_s,
+                          const int32_t* n_rows_dev, cudaStream_t stream);
+int mb_dequant_fp8_group128(const void* q_fp8, const float* scales, void* out_bf16, int M, int K, int ld_s,
+                            const int32_t* n_rows_dev, cudaStream_t stream);
+int mb_ep_recv_compact(const void* recv_x, const int32_t* recv_meta, const int* flags, int world, int cap,
+                       int n_experts, int H, int fp8, int rows_bound, int32_t* offsets, int32_t* order, void* xq,
+                       float* xs, int ld_s, int num_sms, cudaStream_t stream);
 int mb_embedding(const int64_t* ids, const void* table, void* out, int n, int hidden, int vocab,
                  int vocab_start, cudaStream_t stream);
 // RoPE on Q and K (in place in the fused QKV buffer) + K/V scatter into the paged cache.
@@ -207,6 +214,9 @@ int mb_tp_wait_flag(const int* flag, int target, unsigned timeout_ms, int code, 
                     cudaStream_t stream);
 int mb_tp_broadcast(int world, int rank, int root, void* const* in_bufs, void* out, int* const* flags,
                     long long nbytes, int* err, cudaStream_t stream);
+// rank r receives bytes [r * chunk_bytes, (r + 1) * chunk_bytes) of the root's symmetric buffer
+int mb_tp_scatter(int world, int rank, int root, void* const* in_bufs, void* out, int* const* flags,
+                  long long chunk_bytes, int* err, cudaStream_t stream);
 
 // ---- expert-parallel dispatch / combine over peer memory (comm_ep.cu) -----------------------
 int mb_ep_flag_ints(void);

@@ -543,6 +543,21 @@ tp_broadcast_kernel(TpPeers p, int root, uint8_t* __restrict__ out, long long n,
   tp_finish_barrier(p, 1, epoch, err);
 }
 
+// Scatter: rank r pulls chunk r (n bytes, n % 16 == 0) of root's symmetric buffer a[root] into out.
+// Reference: max/kernels/src/comm/scatter.mojo:61 (pull scatter).
+__global__ void __launch_bounds__(256)
+tp_scatter_kernel(TpPeers p, int root, uint8_t* __restrict__ out, long long n, int* err) {
+  const int epoch = ld_volatile(p.flags[p.rank] + kEpochWord) + 1;
+  __syncthreads();
+  tp_barrier_dev(p, 0, epoch, err);
+  const long long nvec = n >> 4;
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.a[root]) + static_cast<long long>(p.rank) * n);
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x)
+    reinterpret_cast<uint4*>(out)[v] = src[v];
+  tp_finish_barrier(p, 1, epoch, err);   // the root may not overwrite its buffer while a peer still reads it
+}
+
 // Waits (bounded) until *flag >= target; on timeout the error word receives `code` and the kernel
 // returns normally, so the context stays usable. Used to probe a peer's progress flag from the host
 // side of failure detection without ever blocking a GPU.
@@ -679,6 +694,18 @@ extern "C" int mb_tp_broadcast(int world, int rank, int root, void* const* in_bu
   if (grid < 1) grid = 1;
   tp_broadcast_kernel<<<grid, 256, 0, stream>>>(make_peers(world, rank, in_bufs, nullptr, flags), root,
                                                 static_cast<uint8_t*>(out), nbytes, err);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+extern "C" int mb_tp_scatter(int world, int rank, int root, void* const* in_bufs, void* out, int* const* flags,
+                             long long chunk_bytes, int* err, cudaStream_t stream) {
+  if (world < 1 || world > kMaxRanks || chunk_bytes % 16 || root < 0 || root >= world) return MB_ERR_SHAPE;
+  if (chunk_bytes <= 0) return MB_OK;
+  int grid = static_cast<int>(((chunk_bytes >> 4) + 255) / 256);
+  if (grid > 592) grid = 592;
+  if (grid < 1) grid = 1;
+  tp_scatter_kernel<<<grid, 256, 0, stream>>>(make_peers(world, rank, in_bufs, nullptr, flags), root,
+                                              static_cast<uint8_t*>(out), chunk_bytes, err);
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 

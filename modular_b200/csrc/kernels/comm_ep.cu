@@ -11,6 +11,9 @@
 //                 for theirs, so when the kernel ends the rank knows how many rows it received.
 //   ep_gather_ids turns the received meta words into an expert-id array (or -1 for empty slots)
 //                 that the MoE index kernel sorts; the grouped GEMMs then run on local experts.
+//   ep_recv_compact   the same in one launch, and with the rows moved: per-expert offsets, the rows of the
+//                 receive buffer copied into expert order (fp8 payload and scales split into the operand
+//                 layout of the block-scaled grouped GEMM), and the order array that the combine needs.
 //   ep_combine_send   expert outputs go back to  ret_x[src][owner = me][pos]  on the source rank.
 //   ep_combine_reduce on the source: y[t] = shared[t] + sum_k w[t,k] * ret_x[owner(t,k)][pos(t,k)].
 //
@@ -25,6 +28,7 @@
 #include <stdint.h>
 
 #include "../common/api.h"
+#include "../common/launch.h"
 #include "../common/ptx.cuh"
 
 namespace mb {
@@ -124,6 +128,115 @@ __global__ void ep_gather_ids_kernel(const int32_t* __restrict__ recv_meta, cons
   if (i >= world * cap) return;
   const int src = i / cap, pos = i % cap;
   ids[i] = pos < flags[kCount + src] ? recv_meta[static_cast<size_t>(i) * 2] : -1;
+}
+
+// Received rows -> grouped-GEMM operands, one launch. Every CTA ranks ALL received rows (a counting sort
+// by local expert that keeps the order of (source, position), so the result does not depend on the grid),
+// then moves its own share of them.
+//   virtual row v in [0, total): source s with base[s] <= v < base[s + 1], position v - base[s]
+//   thread th owns the v of chunk th (ceil(total / 256) each); hist[e][th] counts them per expert
+//   rank of a row = offsets[e] + rows of expert e in earlier chunks + earlier rows of e in its own chunk
+// Outputs: offsets [E + 1]; order[pos] = s * cap + position; rows: fp8 -> xq [rows, H] e4m3 and
+// xs [H / 128, ld_s] fp32 (group-major), bf16 -> xq [rows, H] bf16. E <= 128 (uint16 histogram in 64 KB).
+constexpr int kCompactThreads = 256;
+constexpr int kCompactMaxExperts = 128;
+
+__global__ void __launch_bounds__(kCompactThreads)
+ep_recv_compact_kernel(const uint8_t* __restrict__ recv_x, const int32_t* __restrict__ recv_meta,
+                       const int* __restrict__ flags, int world, int cap, int E, int H, int row_bytes, int fp8,
+                       int share_cap, int32_t* __restrict__ offsets, int32_t* __restrict__ order,
+                       uint8_t* __restrict__ xq, float* __restrict__ xs, int ld_s) {
+  extern __shared__ uint8_t dyn[];
+  uint16_t* hist = reinterpret_cast<uint16_t*>(dyn);                               // [E][256]
+  int2* todo = reinterpret_cast<int2*>(dyn + static_cast<size_t>(E) * kCompactThreads * 2);  // [share_cap]
+  __shared__ int base[kMaxRanks + 1];
+  __shared__ int off_s[kCompactMaxExperts + 1];
+  const int th = threadIdx.x, lane = th & 31, warp = th >> 5;
+  if (th == 0) {
+    int acc = 0;
+    for (int s = 0; s < world; ++s) {
+      base[s] = acc;
+      int c = flags[kCount + s];
+      acc += c < cap ? (c < 0 ? 0 : c) : cap;
+    }
+    for (int s = world; s <= kMaxRanks; ++s) base[s] = acc;
+  }
+  for (int i = th; i < E * kCompactThreads; i += kCompactThreads) hist[i] = 0;
+  __syncthreads();
+  const int total = base[world];
+  const int chunk = (total + kCompactThreads - 1) / kCompactThreads;
+  const int v0 = th * chunk, v1 = min(total, v0 + chunk);
+  // pass 1: histogram of this thread's chunk
+  {
+    int s = 0;
+    for (int v = v0; v < v1; ++v) {
+      while (v >= base[s + 1]) ++s;
+      const int e = recv_meta[(static_cast<size_t>(s) * cap + (v - base[s])) * 2];
+      if (e >= 0 && e < E) hist[e * kCompactThreads + th] += 1;
+    }
+  }
+  __syncthreads();
+  // exclusive scan over the 256 chunks of every expert (one warp per expert, 8 entries per lane)
+  for (int e = warp; e < E; e += kCompactThreads / 32) {
+    uint16_t* h = hist + e * kCompactThreads + lane * 8;
+    int loc[8], sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { loc[j] = h[j]; sum += loc[j]; }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    int run = incl - sum;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { h[j] = static_cast<uint16_t>(run); run += loc[j]; }
+    if (lane == 31) off_s[e + 1] = incl;       // rows of expert e
+  }
+  __syncthreads();
+  if (th == 0) {
+    off_s[0] = 0;
+    for (int e = 0; e < E; ++e) off_s[e + 1] += off_s[e];
+  }
+  __syncthreads();
+  if (blockIdx.x == 0)
+    for (int e = th; e <= E; e += kCompactThreads) offsets[e] = off_s[e];
+  // pass 2: positions of the rows in this CTA's share [r0, r1) of the virtual rows
+  const int share = (total + gridDim.x - 1) / gridDim.x;
+  const int r0 = blockIdx.x * share, r1 = min(total, r0 + share);
+  if (v0 < r1 && v1 > r0) {
+    int s = 0;
+    for (int v = v0; v < v1; ++v) {
+      while (v >= base[s + 1]) ++s;
+      const int flat = s * cap + (v - base[s]);
+      const int e = recv_meta[static_cast<size_t>(flat) * 2];
+      const bool mine = v >= r0 && v < r1 && v - r0 < share_cap;
+      if (e < 0 || e >= E) {          // not an id the dispatch writes: the row gets no position
+        if (mine) todo[v - r0] = make_int2(-1, flat);
+        continue;
+      }
+      const int pos = off_s[e] + hist[e * kCompactThreads + th];
+      hist[e * kCompactThreads + th] += 1;
+      if (mine) todo[v - r0] = make_int2(pos, flat);
+    }
+  }
+  __syncthreads();
+  const int n_mine = max(0, min(r1 - r0, share_cap));
+  // move the rows: one warp per row, 16 bytes per lane and iteration
+  const int payload = fp8 ? H : H * 2;
+  for (int i = warp; i < n_mine; i += kCompactThreads / 32) {
+    const int2 pf = todo[i];
+    if (pf.x < 0) continue;
+    const uint8_t* src = recv_x + static_cast<size_t>(pf.y) * row_bytes;
+    uint8_t* dst = xq + static_cast<size_t>(pf.x) * payload;
+    for (int c = lane * 16; c < payload; c += 512)
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+    if (fp8) {
+      const float* sc = reinterpret_cast<const float*>(src + H);
+      for (int g = lane; g < (H >> 7); g += 32) xs[static_cast<size_t>(g) * ld_s + pf.x] = sc[g];
+    }
+    if (lane == 0) order[pf.x] = pf.y;
+  }
 }
 
 // out_sorted: [n_rows, H] expert outputs in expert order; order[p] = src*cap + pos.
@@ -257,6 +370,36 @@ extern "C" int mb_ep_gather_ids(const int32_t* recv_meta, const int* flags, int3
   const int n = world * cap;
   if (n <= 0) return MB_OK;
   ep::ep_gather_ids_kernel<<<(n + 255) / 256, 256, 0, stream>>>(recv_meta, flags, ids, world, cap);
+  return EP_LAUNCH_OK();
+}
+
+// One launch from receive buffers to grouped-GEMM operands (see ep_recv_compact_kernel). `rows_bound`: an upper
+// bound of the rows this rank can have received (<= world * cap); `ld_s` >= rows_bound.
+extern "C" int mb_ep_recv_compact(const void* recv_x, const int32_t* recv_meta, const int* flags, int world, int cap,
+                                  int n_experts, int H, int fp8, int rows_bound, int32_t* offsets, int32_t* order,
+                                  void* xq, float* xs, int ld_s, int num_sms, cudaStream_t stream) {
+  if (world < 1 || world > ep::kMaxRanks || H % 128 || n_experts < 1 || n_experts > ep::kCompactMaxExperts)
+    return MB_ERR_SHAPE;
+  if (rows_bound <= 0 || rows_bound > world * cap) rows_bound = world * cap;
+  if (fp8 && (xs == nullptr || ld_s < rows_bound)) return MB_ERR_SHAPE;
+  const int row_bytes = fp8 ? H + (H / 128) * 4 : H * 2;
+  // rows move as 16-byte vectors: the received rows (payload + scales) must keep that alignment
+  if (row_bytes % 16 || (reinterpret_cast<uintptr_t>(recv_x) | reinterpret_cast<uintptr_t>(xq)) & 15) return MB_ERR_ALIGN;
+  int grid = (rows_bound + 7) / 8;                  // at least a warp-load of rows per CTA
+  if (num_sms <= 0) num_sms = 148;
+  if (grid > num_sms) grid = num_sms;
+  if (grid < 1) grid = 1;
+  const int share_cap = (rows_bound + grid - 1) / grid;
+  const size_t smem = static_cast<size_t>(n_experts) * ep::kCompactThreads * 2 + static_cast<size_t>(share_cap) * 8;
+  if (smem > 200 * 1024) return MB_ERR_TOO_LARGE;
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
+    cudaFuncSetAttribute(ep::ep_recv_compact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    configured.done();
+  }
+  ep::ep_recv_compact_kernel<<<grid, ep::kCompactThreads, smem, stream>>>(
+      static_cast<const uint8_t*>(recv_x), recv_meta, flags, world, cap, n_experts, H, row_bytes, fp8, share_cap,
+      offsets, order, static_cast<uint8_t*>(xq), xs, ld_s);
   return EP_LAUNCH_OK();
 }
 

@@ -53,10 +53,11 @@ struct Params {
   int M, N, K, ldy, ldr, sw_ld, BN, stages;
   int splits, kb_per_split;
   float* partial;   // [splits, M, N] fp32 when splits > 1
-  // grouped (mixture-of-experts) mode: blockIdx.z = expert, token rows [offsets[e], offsets[e+1]),
-  // weights / weight scales of expert e start at row e * w_rows / e * sw_rows
+  // grouped (mixture-of-experts) mode: blockIdx.x walks the token tiles of all experts in expert order
+  // (expert e owns rows [offsets[e], offsets[e+1]) and ceil(rows / BN) tiles); weights / weight scales of
+  // expert e start at row e * w_rows / e * sw_rows
   const int* expert_offsets;
-  int w_rows, sw_rows;
+  int w_rows, sw_rows, n_experts;
 };
 
 constexpr int kAccBufs = 4;
@@ -86,10 +87,34 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   int t0 = blockIdx.x * p.BN;
   int Mlim = p.M, w_row0 = 0, sw_row0 = 0, zsplit = blockIdx.z;
   if (p.expert_offsets != nullptr) {
-    const int e = blockIdx.z;
-    const int row_begin = p.expert_offsets[e], row_end = p.expert_offsets[e + 1];
-    t0 = row_begin + blockIdx.x * p.BN;
-    if (t0 >= row_end) return;      // whole CTA, before any barrier or TMEM allocation
+    // every warp finds the expert of this CTA's tile: a prefix sum of the experts' tile counts, 32 experts
+    // per round. The grid is sized for the worst case, so CTAs past the last tile leave here, before any
+    // barrier or TMEM allocation.
+    const int tile = blockIdx.x;
+    int e = -1, row_end = 0, base = 0;
+    for (int c = 0; c < p.n_experts; c += 32) {
+      const int j = c + lane;
+      const int b = j < p.n_experts ? p.expert_offsets[j] : 0;
+      const int en = j < p.n_experts ? p.expert_offsets[j + 1] : 0;
+      const int nt = (en - b + p.BN - 1) / p.BN;
+      int incl = nt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      const int before = base + incl - nt;
+      const unsigned hit = __ballot_sync(0xffffffffu, tile >= before && tile < before + nt);
+      if (hit != 0) {
+        const int src = __ffs(hit) - 1;
+        e = c + src;
+        row_end = __shfl_sync(0xffffffffu, en, src);
+        t0 = __shfl_sync(0xffffffffu, b, src) + (tile - __shfl_sync(0xffffffffu, before, src)) * p.BN;
+        break;
+      }
+      base += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (e < 0) return;
     Mlim = row_end;
     w_row0 = e * p.w_rows;
     sw_row0 = e * p.sw_rows;
@@ -338,10 +363,95 @@ __global__ void quant_fp8_group128_kernel(const __nv_bfloat16* __restrict__ x, u
   if (lane == 0) scales[k_major ? static_cast<size_t>(g) * M + t : static_cast<size_t>(t) * groups + g] = scale;
 }
 
+// SwiGLU and the 1x128 quantisation of its result in one pass: gu [M, 2I] bf16 (gate | up) -> q [M, I] e4m3
+// and scales [I/128, ld_s] (group-major). The product is rounded to bf16 first, so the result equals the
+// two-pass form bit for bit. Rows at or past *n_rows_dev (when given) are skipped: grouped GEMMs whose row
+// count is only known on the device pay for the rows that exist. One warp per (row, group), grid-stride.
+__global__ void silu_mul_quant_fp8_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict__ q,
+                                          float* __restrict__ scales, int M, int I, int ld_s,
+                                          const int32_t* __restrict__ n_rows_dev) {
+  const int rows = n_rows_dev != nullptr ? min(M, *n_rows_dev) : M;
+  const int groups = I >> 7;
+  const long long total = static_cast<long long>(rows) * groups;
+  const long long stride = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; wid < total;
+       wid += stride) {
+    const int t = static_cast<int>(wid / groups), g = static_cast<int>(wid % groups);
+    const int k0 = g * 128 + lane * 4;
+    const __nv_bfloat16* row = gu + static_cast<size_t>(t) * 2 * I;
+    const uint2 graw = *reinterpret_cast<const uint2*>(row + k0);
+    const uint2 uraw = *reinterpret_cast<const uint2*>(row + I + k0);
+    const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&graw);
+    const __nv_bfloat162* ub = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    const float2 g0 = __bfloat1622float2(gb[0]), g1 = __bfloat1622float2(gb[1]);
+    const float2 u0 = __bfloat1622float2(ub[0]), u1 = __bfloat1622float2(ub[1]);
+    float v[4] = {g0.x / (1.f + __expf(-g0.x)) * u0.x, g0.y / (1.f + __expf(-g0.y)) * u0.y,
+                  g1.x / (1.f + __expf(-g1.x)) * u1.x, g1.y / (1.f + __expf(-g1.y)) * u1.y};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = fmaxf(amax, 1e-12f) / 448.0f;
+    const float inv = 1.0f / scale;
+    const __nv_fp8x4_e4m3 packed(make_float4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv));
+    *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(t) * I + k0) = packed.__x;
+    if (lane == 0) scales[static_cast<size_t>(g) * ld_s + t] = scale;
+  }
+}
+
+// The inverse of the 1x128 quantisation: q [M, K] e4m3 with group-major scales [K/128, ld_s] -> bf16 [M, K].
+// Rows at or past *n_rows_dev (when given) are skipped.
+__global__ void dequant_fp8_group128_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales,
+                                            __nv_bfloat16* __restrict__ out, int M, int K, int ld_s,
+                                            const int32_t* __restrict__ n_rows_dev) {
+  const int rows = n_rows_dev != nullptr ? min(M, *n_rows_dev) : M;
+  const int per_row = K >> 2;
+  const long long total = static_cast<long long>(rows) * per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int r = static_cast<int>(i / per_row), c = static_cast<int>(i % per_row) * 4;
+    const float scale = scales[static_cast<size_t>(c >> 7) * ld_s + r];
+    __nv_fp8x4_e4m3 v;
+    v.__x = *reinterpret_cast<const uint32_t*>(q + static_cast<size_t>(r) * K + c);
+    const float4 f = static_cast<float4>(v);
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(f.z * scale, f.w * scale);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&lo);
+    o.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + static_cast<size_t>(r) * K + c) = o;
+  }
+}
+
 }  // namespace f8
 }  // namespace mb
 
 using namespace mb;
+
+extern "C" int mb_dequant_fp8_group128(const void* q_fp8, const float* scales, void* out_bf16, int M, int K, int ld_s,
+                                       const int32_t* n_rows_dev, cudaStream_t stream) {
+  if (M <= 0) return MB_OK;
+  if (K % 128 || ld_s < M) return MB_ERR_SHAPE;
+  long long blocks = (static_cast<long long>(M) * (K / 4) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  f8::dequant_fp8_group128_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(q_fp8), scales, static_cast<__nv_bfloat16*>(out_bf16), M, K, ld_s, n_rows_dev);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+extern "C" int mb_silu_mul_quant_fp8(const void* gate_up, void* q_fp8, float* scales, int M, int inter, int ld_s,
+                                     const int32_t* n_rows_dev, cudaStream_t stream) {
+  if (M <= 0) return MB_OK;
+  if (inter % 128 || ld_s < M) return MB_ERR_SHAPE;
+  const long long warps = static_cast<long long>(M) * (inter / 128);
+  long long blocks = (warps + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  f8::silu_mul_quant_fp8_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), static_cast<uint8_t*>(q_fp8), scales, M, inter, ld_s, n_rows_dev);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
 
 extern "C" int mb_quant_fp8_group128(const void* x_bf16, void* q_fp8, float* scales, int M, int K,
                                      int ldx, int scale_ld, int scales_k_major, cudaStream_t stream) {
@@ -416,7 +526,7 @@ extern "C" int mb_gemm_fp8_blockscaled(const void* Xq, const float* Xs, const vo
   splits = (kb_all + p.kb_per_split - 1) / p.kb_per_split;
   p.splits = splits;
   p.partial = static_cast<float*>(workspace);
-  p.expert_offsets = nullptr; p.w_rows = 0; p.sw_rows = 0;
+  p.expert_offsets = nullptr; p.w_rows = 0; p.sw_rows = 0; p.n_experts = 0;
   dim3 grid((M + bn - 1) / bn, (N + kBM - 1) / kBM, splits);
   const bool resid = (flags & 2) && splits == 1;
   static PerDeviceOnce configured;
@@ -475,6 +585,7 @@ extern "C" int mb_grouped_gemm_fp8_blockscaled(const void* Xq, const float* Xs, 
   p.kb_per_split = (K + 127) / 128;
   p.partial = nullptr;
   p.expert_offsets = expert_offsets;
+  p.n_experts = n_experts;
   p.w_rows = N;
   p.sw_rows = N / 128;
   CUtensorMap tw, tx;
@@ -488,7 +599,12 @@ extern "C" int mb_grouped_gemm_fp8_blockscaled(const void* Xq, const float* Xs, 
     cudaFuncSetAttribute(gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     configured.done();
   }
-  dim3 grid((max_rows + bn - 1) / bn, N / kBM, n_experts);
+  // an upper bound of the number of token tiles: every expert wastes less than one tile, and no expert has
+  // more than max_rows rows
+  long long tiles = (total_rows + bn - 1) / bn + n_experts;
+  const long long by_expert = static_cast<long long>(n_experts) * ((max_rows + bn - 1) / bn);
+  if (by_expert < tiles) tiles = by_expert;
+  dim3 grid(static_cast<unsigned>(tiles), N / kBM, 1);
   gemm_fp8_kernel<false><<<grid, kThreads, smem, stream>>>(tw, tx, p);
   return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }

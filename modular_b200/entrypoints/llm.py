@@ -60,7 +60,8 @@ class LLM:
                  eos_token_ids: Sequence[int] = (), seed: int = 0, tp_size: int = 1,
                  tp_rank: int = 0, host_kvcache_swap_space_gb: float = 0.0,
                  disk_kvcache_dir: Optional[str] = None, disk_kvcache_space_gb: float = 0.0,
-                 step_token_alignment: Optional[int] = None, weights_are_sharded: bool = False):
+                 step_token_alignment: Optional[int] = None, weights_are_sharded: bool = False,
+                 ep_size: int = 1, ep_rank: int = 0, ep_fp8_dispatch: bool = False):
         from ..models import family_for
 
         fam = family_for(model_config)
@@ -90,6 +91,19 @@ class LLM:
                 weights = shard_llama_weights(full_cfg, weights, tp_rank, tp_size)
             model_config = shard_llama_config(full_cfg, tp_size)
             torch.cuda.empty_cache()
+        elif ep_size > 1:
+            # expert parallelism with data-parallel attention: one process per GPU, the routed experts are sharded,
+            # every rank serves its own requests and the ranks meet in the dispatch / combine kernels of every MoE
+            # layer, so all ranks must run the same sequence of steps (same batch shapes)
+            from ..parallel.tp import TPContext
+
+            if not on_gpu or not fam.supports_ep:
+                raise ValueError(f"expert parallelism needs CUDA devices and a MoE family (got {fam.name})")
+            self.tp = TPContext(device=self.device)
+            if self.tp.world != ep_size or self.tp.rank != ep_rank:
+                raise ValueError("ep_size / ep_rank do not match the initialised process group")
+            if weights is None:
+                weights = fam.weights_class.random_init_ep(model_config, ep_rank, ep_size, self.device, dtype, seed=seed)
         elif weights is None:
             weights = fam.weights_class.random_init(model_config, self.device, dtype, seed=seed)
         self.weights = weights
@@ -109,6 +123,19 @@ class LLM:
         self.kv = PagedKVCacheManager(kvp, num_kv_pages, self.device, max_seq_len=max_length,
                                       host_pages=host_pages, disk_pages=disk_pages, disk_dir=disk_kvcache_dir)
         extra = {"tp": self.tp} if fam.supports_tp else {}
+        if ep_size > 1:
+            from ..parallel.ep import EPContext
+
+            c = model_config
+            import datetime
+
+            import torch.distributed as dist
+
+            # the ranks agree on the token bound of every step over a host-side group (they serve different
+            # requests, so their batches differ)
+            extra["ep"] = EPContext(self.tp, c.hidden_size, c.n_routed_experts, c.num_experts_per_tok,
+                                    max_tokens=max_batch_input_tokens, fp8_dispatch=ep_fp8_dispatch,
+                                    host_group=dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=300)))
         self.model = fam.model_class(model_config, weights, self.kv.kv, max_tokens=max_batch_input_tokens,
                                      max_seqs=max_batch_size, max_position=max_length, **extra)
         overlap = on_gpu if enable_overlap_scheduler is None else enable_overlap_scheduler
@@ -121,6 +148,9 @@ class LLM:
             eos_token_ids=eos_token_ids)
         if device_graph_capture and on_gpu:
             self.pipeline.warmup_graph_capture()
+            if hasattr(self.model, "capture_decode_graphs"):
+                # models whose step is driven op by op capture their decode steps themselves
+                self.model.capture_decode_graphs(graph_batch_sizes)
         self.sched_config = TokenGenerationSchedulerConfig(
             max_batch_size=max_batch_size, target_tokens_per_batch_ce=max_batch_input_tokens,
             max_seq_len=max_length, enable_chunked_prefill=enable_chunked_prefill,

@@ -22,6 +22,7 @@ class ModelFamily:
     kv_params: Callable        # (cfg, page_size, dtype, prefix_caching) -> KVCacheParams
     activation_bytes: Callable  # (cfg, max_tokens, max_seqs) -> int
     supports_tp: bool = False
+    supports_ep: bool = False       # expert parallelism: routed experts sharded, every rank serves its own requests
 
 
 def _llama_family() -> ModelFamily:
@@ -51,7 +52,7 @@ def _deepseek_family() -> ModelFamily:
                    + 3 * max(cfg.intermediate_size, cfg.num_experts_per_tok * cfg.moe_intermediate_size))
         return T * per_tok * 2 + B * cfg.vocab_size * 4 + (256 << 20)
 
-    return ModelFamily("deepseek_v3", DeepseekV3Config, DeepseekV3Weights, DeepseekV3Model, kv, act)
+    return ModelFamily("deepseek_v3", DeepseekV3Config, DeepseekV3Weights, DeepseekV3Model, kv, act, supports_ep=True)
 
 
 def family_for(config) -> ModelFamily:

@@ -217,6 +217,50 @@ class DeepseekV3Weights:
         return cls(cfg, embed, layers, ones(H), embed if cfg.tie_word_embeddings else r(cfg.vocab_size, H))
 
     @classmethod
+    def random_init_ep(cls, cfg: DeepseekV3Config, rank: int, world: int, device="cuda", dtype=torch.bfloat16,
+                       seed: int = 0, std: float = 0.02, fp8_experts: bool = True) -> "DeepseekV3Weights":
+        """Random weights of ONE expert-parallel rank, generated on the device: attention, dense layers, router and
+        shared experts replicated (same seed on every rank), routed experts [rank * E/world, (rank + 1) * E/world)
+        only, quantised to block-scaled fp8 layer by layer when ``fp8_experts`` (the full model holds 671 B
+        parameters; a rank's slice is ~82 GB in fp8). For synthetic-weight benchmarks."""
+        from ..nn.moe import Fp8ExpertWeights
+
+        dev = torch.device(device)
+        g_all = torch.Generator(device=dev).manual_seed(seed)
+        g_rank = torch.Generator(device=dev).manual_seed(seed * 1000003 + rank + 1)
+        rnd = lambda g, *s: (torch.randn(*s, device=dev, dtype=torch.float32, generator=g) * std).to(dtype)
+        ones = lambda n: torch.ones(n, dtype=dtype, device=dev)
+        H, h = cfg.hidden_size, cfg.num_attention_heads
+        mc = cfg.moe_config()
+        E, I = cfg.n_routed_experts, cfg.moe_intermediate_size
+        El = E // world
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            kv_b = rnd(g_all, h * (cfg.qk_nope_head_dim + cfg.v_head_dim), cfg.kv_lora_rank)
+            w_uk, w_uv = cls.split_kv_b(cfg, kv_b)
+            if cfg.q_lora_rank:
+                q_a, q_a_norm, q_b = rnd(g_all, cfg.q_lora_rank, H), ones(cfg.q_lora_rank), rnd(g_all, h * cfg.qk_head_dim, cfg.q_lora_rank)
+            else:
+                q_a, q_a_norm, q_b = None, None, rnd(g_all, h * cfg.qk_head_dim, H)
+            lw = DSLayer(ones(H), q_a, q_a_norm, q_b, rnd(g_all, cfg.latent_dim, H), ones(cfg.kv_lora_rank), w_uk, w_uv,
+                         rnd(g_all, H, h * cfg.v_head_dim), ones(H))
+            if cfg.is_moe_layer(i):
+                gate = rnd(g_all, E, H).float()
+                bias = (torch.randn(E, device=dev, generator=g_all) * 0.1) if mc.scoring_func == "sigmoid" else None
+                shared = mc.n_shared_experts * I
+                sgu = rnd(g_all, 2 * shared, H) if shared else None
+                sd_ = rnd(g_all, H, shared) if shared else None
+                wgu, wd = rnd(g_rank, El, 2 * I, H), rnd(g_rank, El, H, I)
+                if fp8_experts:
+                    wgu, wd = Fp8ExpertWeights.quantize(wgu), Fp8ExpertWeights.quantize(wd)
+                lw.moe = MoE(mc, gate, wgu, wd, bias, sgu, sd_, e_begin=rank * El, e_end=(rank + 1) * El)
+            else:
+                lw.wgu, lw.wd = rnd(g_all, 2 * cfg.intermediate_size, H), rnd(g_all, H, cfg.intermediate_size)
+            layers.append(lw)
+        embed = rnd(g_all, cfg.vocab_size, H)
+        return cls(cfg, embed, layers, ones(H), embed if cfg.tie_word_embeddings else rnd(g_all, cfg.vocab_size, H))
+
+    @classmethod
     def from_state_dict(cls, cfg: DeepseekV3Config, sd: dict, device="cpu", dtype=torch.bfloat16,
                         e_begin: int = 0, e_end: Optional[int] = None, keep_fp8: bool = True):
         """HF ``DeepseekV3ForCausalLM`` names (with or without the ``model.`` prefix). fp8 tensors come
@@ -359,6 +403,84 @@ class DeepseekV3Model:
                 if l.moe is not None:
                     self._ep_layers[i] = EPMoE(l.moe, ep if self.device.type == "cuda" else None)
         self.sampled = torch.zeros(max_seqs, dtype=torch.long, device=self.device)
+        self._graphs: dict = {}             # decode batch size -> (graph, static inputs, static logits)
+        self._graph_calls: dict = {}        # native calls recorded in each graph (0 unless calls are counted)
+        self.graph_replays = 0
+        self.replayed_calls = 0
+
+    # ------------------------------------------------------------ CUDA graphs of decode steps
+    def capture_decode_graphs(self, batch_sizes: Sequence[int]) -> None:
+        """Capture one graph per decode batch size (one query token per sequence). The whole step, MoE exchange
+        included, is one replay: the exchange kernels keep their epochs in device memory. With expert
+        parallelism every rank must call this with the same sizes at the same point (the warm-up run of every
+        size exchanges rows)."""
+        if self.device.type != "cuda":
+            return
+        dev, pages = self.device, self.kv.shape[0]
+        max_pages = -(-min(self.cos_sin.shape[0], pages * self.page_size) // self.page_size)
+        for B in sorted(set(int(b) for b in batch_sizes)):
+            if B in self._graphs or B > self.max_seqs:
+                continue
+            i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
+            st = dict(tokens=torch.zeros(B, dtype=torch.long, device=dev), positions=i32(B),
+                      slots=torch.full((B,), -1, dtype=torch.long, device=dev), block_table=i32(B, max_pages),
+                      q_start=torch.arange(B, dtype=torch.int32, device=dev), q_len=i32(B) + 1, kv_len=i32(B) + 1,
+                      logit_rows=torch.arange(B, dtype=torch.int32, device=dev))
+            args = tuple(st[k] for k in ("tokens", "positions", "slots", "block_table", "q_start", "q_len",
+                                         "kv_len", "logit_rows"))
+            if self.ep is not None:
+                self.ep.set_step_tokens(B)
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._forward(*args)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            from .._native import native_calls
+
+            g = torch.cuda.CUDAGraph()
+            n0 = native_calls()
+            with torch.cuda.graph(g):
+                logits = self._forward(*args)
+            self._graph_calls[B] = native_calls() - n0
+            self._graphs[B] = (g, st, logits)
+        torch.cuda.synchronize()
+
+    def _graph_for(self, T: int, n_seqs: int, n_logits: int):
+        """The graph size for this step, or 0. Expert-parallel ranks first agree on the largest token count of
+        the step: all of them then address the exchange buffers with the same bound, whichever path each takes."""
+        sizes = sorted(self._graphs)
+        if self.ep is not None and self.device.type == "cuda":
+            if self.ep.host_group is None:
+                return 0        # no agreement between the ranks: every step runs eagerly with the full bound
+            bound = self.ep.set_step_tokens(T)
+            fit = next((b for b in sizes if b >= bound), 0)
+            self.ep.set_step_tokens_local(fit or bound)
+        else:
+            fit = next((b for b in sizes if b >= T), 0)
+        return fit if (fit and T == n_seqs == n_logits) else 0
+
+    def forward_tensors(self, tokens, positions, slots, block_table, q_start, q_len, kv_len,
+                        logit_rows, plan=None) -> torch.Tensor:
+        """One ragged step. Returns fp32 logits ``[len(logit_rows), vocab]``. Decode-only steps replay a captured
+        graph when one of a fitting size exists (sequences beyond the real ones are dummies that write no KV)."""
+        T, n = tokens.shape[0], q_len.shape[0]
+        B = self._graph_for(T, n, logit_rows.shape[0]) if (self._graphs or self.ep is not None) else 0
+        if not B:
+            return self._forward(tokens, positions, slots, block_table, q_start, q_len, kv_len, logit_rows)
+        g, st, logits = self._graphs[B]
+        st["tokens"][:n].copy_(tokens)
+        st["positions"][:n].copy_(positions)
+        st["slots"][:n].copy_(slots)
+        st["slots"][n:].fill_(-1)
+        st["kv_len"][:n].copy_(kv_len)
+        st["kv_len"][n:].fill_(1)
+        w = min(block_table.shape[1], st["block_table"].shape[1])
+        st["block_table"][:n, :w].copy_(block_table[:, :w])
+        g.replay()
+        self.graph_replays += 1
+        self.replayed_calls += self._graph_calls.get(B, 0)
+        return logits[:n]
 
     # ------------------------------------------------------------ attention
     def _attention(self, li: int, l: DSLayer, x, positions, slots, block_table, q_start, q_len, kv_len):
@@ -396,9 +518,7 @@ class DeepseekV3Model:
         return l.moe(x)
 
     # ------------------------------------------------------------ step
-    def forward_tensors(self, tokens, positions, slots, block_table, q_start, q_len, kv_len,
-                        logit_rows, plan=None) -> torch.Tensor:
-        """One ragged step. Returns fp32 logits ``[len(logit_rows), vocab]``."""
+    def _forward(self, tokens, positions, slots, block_table, q_start, q_len, kv_len, logit_rows) -> torch.Tensor:
         c = self.cfg
         h = ops.embedding(tokens, self.w.embed)
         for li, l in enumerate(self.w.layers):

@@ -138,6 +138,15 @@ class MoE:
                    r(2 * shared, H) if shared else None, r(H, shared) if shared else None, **kw)
 
     # ------------------------------------------------------------ pieces
+    def router_logits(self, x):
+        """fp32 router scores [T, E]. On the GPU the product runs on this package's GEMM with a bf16 copy of the
+        router matrix (checkpoints store it in bf16, so nothing is lost) and fp32 accumulation and output."""
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.gate.shape[0] % 64 == 0:
+            if getattr(self, "_gate_bf16", None) is None:
+                self._gate_bf16 = self.gate.to(torch.bfloat16).contiguous()
+            return ops.linear(x, self._gate_bf16, out_dtype=torch.float32)
+        return x.float() @ self.gate.float().t()
+
     def shared_forward(self, x):
         if self.shared_gate_up is None:
             return None
@@ -166,10 +175,12 @@ class MoE:
         L.moe_combine(out, inverse, w, shared_out, y, k)
         return y
 
-    def local_gemms(self, xp, offsets, act=None, out=None):
+    def local_gemms(self, xp, offsets, act=None, out=None, max_rows: int = 0, expected_rows: int = 0):
         """Both grouped GEMMs of the local experts on rows already in expert order (``offsets`` int32
         [E_local + 1]). ``xp``: bf16 rows, or ``(xq, xs)`` = e4m3 rows [n, H] (any row stride) with fp32
-        scales [H/128, n] for fp8 experts that receive quantised rows. Returns bf16 [n, H]."""
+        scales [H/128, n] for fp8 experts that receive quantised rows. Returns bf16 [n, H]. ``n`` may be an
+        upper bound of the rows (the true count is ``offsets[-1]`` on the device); ``max_rows`` bounds the rows
+        of one expert and ``expected_rows`` is the typical count per expert (it picks the token tile)."""
         cfg, L = self.cfg, _lib()
         fp8_in = isinstance(xp, tuple)
         n = (xp[0] if fp8_in else xp).shape[0]
@@ -180,10 +191,18 @@ class MoE:
             # quantise per 1x128 group, grouped block-scaled GEMM, SwiGLU, quantise again, second grouped
             # GEMM (rows past the local count hold garbage that is never read back)
             xq, xs = xp if fp8_in else ops.quant_fp8_group128(xp)
-            gu = torch.empty(n, 2 * cfg.moe_intermediate_size, dtype=torch.bfloat16, device=dev)
-            L.grouped_gemm_fp8(xq, xs, self.w_gate_up.q, self.w_gate_up.scale, gu, offsets, n, 0)
-            aq, a_s = ops.quant_fp8_group128(ops.silu_mul(gu))
-            L.grouped_gemm_fp8(aq, a_s, self.w_down.q, self.w_down.scale, out, offsets, n, 0)
+            I = cfg.moe_intermediate_size
+            E = self.e_end - self.e_begin
+            bn = 0
+            if expected_rows > 0:
+                bn = 32 if expected_rows <= 32 else (64 if expected_rows <= 64 else 128)
+            gu = torch.empty(n, 2 * I, dtype=torch.bfloat16, device=dev)
+            L.grouped_gemm_fp8(xq, xs, self.w_gate_up.q, self.w_gate_up.scale, gu, offsets, max_rows or n, bn)
+            # SwiGLU and the quantisation of its result in one pass over the rows that exist
+            aq = torch.empty(n, I, dtype=torch.float8_e4m3fn, device=dev)
+            a_s = torch.empty(I // 128, n, dtype=torch.float32, device=dev)
+            L.silu_mul_quant_fp8(gu, aq, a_s, offsets[E:E + 1])
+            L.grouped_gemm_fp8(aq, a_s, self.w_down.q, self.w_down.scale, out, offsets, max_rows or n, bn)
             return out
         if fp8_in:
             raise ValueError("quantised rows need fp8 expert weights")
@@ -211,8 +230,7 @@ class MoE:
         return y.to(x.dtype)
 
     def forward(self, x):
-        logits = x.float() @ self.gate.float().t()
-        ids, w = route(logits, self.bias, self.cfg)
+        ids, w = route(self.router_logits(x), self.bias, self.cfg)
         return self.experts_forward(x, ids, w, self.shared_forward(x))
 
     __call__ = forward

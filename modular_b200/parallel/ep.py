@@ -30,10 +30,14 @@ from .tp import TPContext
 
 
 class EPContext:
-    """Symmetric receive / return buffers for one MoE shape, shared by all layers."""
+    """Symmetric receive / return buffers for one MoE shape, shared by all layers.
+
+    Buffers are allocated for ``max_tokens`` tokens per rank; a step that is known to be smaller (every rank
+    calls :meth:`set_step_tokens` with the same bound) addresses them with a smaller per-pair capacity, so the
+    index kernels, the row moves and the GEMM grids of a decode step are sized for the decode step."""
 
     def __init__(self, ctx: TPContext, hidden: int, n_experts: int, top_k: int, max_tokens: int,
-                 cap: Optional[int] = None, fp8_dispatch: bool = False):
+                 cap: Optional[int] = None, fp8_dispatch: bool = False, host_group=None):
         if n_experts % ctx.world:
             raise ValueError(f"{n_experts} experts cannot be split over {ctx.world} ranks")
         if hidden % 128:
@@ -41,10 +45,17 @@ class EPContext:
         self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
         self.hidden, self.top_k = hidden, top_k
         self.e_local = n_experts // ctx.world
+        if self.e_local > 128:
+            raise ValueError("at most 128 experts per rank")
         self.cap = cap if cap is not None else max_tokens * top_k
+        self.step_cap = self.cap
+        self.step_tokens = max_tokens
         self.max_tokens = max_tokens
         self.fp8 = fp8_dispatch
+        self.host_group = host_group        # a gloo group of the same ranks: per-step agreement on the bound
         self.row_bytes = hidden + hidden // 128 * 4 if fp8_dispatch else hidden * 2
+        if self.row_bytes % 16:
+            raise ValueError("fp8 dispatch needs a hidden size that is a multiple of 512 (rows move as 16-byte vectors)")
         W, L = self.world, _lib()
         self.recv_x = ctx.alloc_symmetric(W * self.cap * self.row_bytes, torch.uint8)
         self.recv_meta = ctx.alloc_symmetric(W * self.cap * 2, torch.int32, zero=True)
@@ -52,54 +63,78 @@ class EPContext:
         self.flags = ctx.alloc_symmetric(L.ep_flag_ints(), torch.int32, zero=True)
         dev = ctx.device
         n = W * self.cap
-        self.ids_recv = torch.empty(n, dtype=torch.int32, device=dev)
         self.order = torch.empty(n, dtype=torch.int32, device=dev)
-        self.inverse = torch.empty(n, dtype=torch.int32, device=dev)
-        self.scratch = torch.zeros(2 * self.e_local, dtype=torch.int32, device=dev)
-        self.offsets = torch.empty(self.e_local + 1, dtype=torch.int32, device=dev)
-        self.xp = torch.empty(n, hidden, dtype=torch.bfloat16, device=dev)
-        self.xq = torch.empty(n, self.row_bytes, dtype=torch.uint8, device=dev) if fp8_dispatch else None
+        self.offsets = torch.zeros(self.e_local + 1, dtype=torch.int32, device=dev)
+        self.n_rows = self.offsets[self.e_local:self.e_local + 1]
+        # rows in expert order: bf16 [n, H], or e4m3 [n, H] with group-major scales [H / 128, n]
+        self.xrows = torch.empty(n * hidden * (1 if fp8_dispatch else 2), dtype=torch.uint8, device=dev)
+        self.xs = torch.empty(hidden // 128 * n, dtype=torch.float32, device=dev) if fp8_dispatch else None
+        self.xdq = None                      # bf16 rows for bf16 experts behind an fp8 dispatch (lazily)
+        self.out = torch.empty(n, hidden, dtype=torch.bfloat16, device=dev)    # expert outputs, all layers
         self.send_pos = torch.zeros(max_tokens * top_k, dtype=torch.int32, device=dev)
+        self.side = torch.cuda.Stream(device=dev)       # the shared experts run beside the exchange
         self.last_pairs = 0
         ctx.barrier()   # flags are zero everywhere before the first kernel signals a peer
+
+    # ------------------------------------------------------------------ per-step bound
+    def set_step_tokens(self, tokens: int) -> int:
+        """Bound of the tokens any rank brings to the MoE layers of the coming step. Must be the same on every
+        rank: with a host group the ranks agree on the maximum here, else the caller guarantees it."""
+        if self.host_group is not None:
+            t = torch.tensor([tokens], dtype=torch.int64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.host_group)
+            tokens = int(t)
+        return self.set_step_tokens_local(tokens)
+
+    def set_step_tokens_local(self, tokens: int) -> int:
+        """The same without the exchange: the caller already holds a bound that every rank shares."""
+        tokens = max(1, min(int(tokens), self.max_tokens))
+        self.step_tokens = tokens
+        self.step_cap = min(self.cap, tokens * self.top_k)
+        return tokens
+
+    @property
+    def step_rows(self) -> int:
+        """Upper bound of the rows this rank can receive in a step."""
+        return self.world * self.step_cap
 
     # ------------------------------------------------------------------ stages
     def dispatch(self, x: torch.Tensor, ids: torch.Tensor, keep_fp8: bool = False):
         """Push rows to their owners. Returns (rows in local-expert order, offsets [E_local+1], send_pos).
-        With fp8 dispatch and ``keep_fp8`` the rows stay quantised: ``(xq e4m3 [n, H] strided, xs fp32
-        [H/128, n])``, the operand form of the block-scaled grouped GEMM."""
-        L, W = _lib(), self.world
+        With fp8 dispatch and ``keep_fp8`` the rows stay quantised: ``(xq e4m3 [n, H], xs fp32 [H/128, n])``,
+        the operand form of the block-scaled grouped GEMM."""
+        L, W, cap, H = _lib(), self.world, self.step_cap, self.hidden
         T = x.shape[0]
-        assert T <= self.max_tokens and ids.shape[1] == self.top_k
+        assert T <= self.step_tokens and ids.shape[1] == self.top_k
         send_pos = self.send_pos[: T * self.top_k]
         self.last_pairs = T * self.top_k
         L.ep_dispatch(W, self.rank, self.recv_x.peer_ptrs, self.recv_meta.peer_ptrs, self.flags.peer_ptrs,
-                      x, ids, send_pos, self.e_local, self.cap, self.fp8)
-        L.ep_gather_ids(self.recv_meta.tensor, self.flags.tensor, self.ids_recv, W, self.cap)
-        L.moe_create_indices(self.ids_recv.view(-1, 1), 0, self.e_local, self.scratch, self.offsets,
-                             self.order, self.inverse)
-        n_rows = self.offsets[self.e_local:self.e_local + 1]
+                      x, ids, send_pos, self.e_local, cap, self.fp8)
+        n = W * cap
         if self.fp8:
-            L.moe_permute_rows(self.recv_x.tensor.view(W * self.cap, self.row_bytes), self.order, n_rows,
-                               self.xq, 1)
+            xq = self.xrows[: n * H].view(n, H)
+            xs = self.xs[: H // 128 * n].view(H // 128, n)
+            L.ep_recv_compact(self.recv_x.tensor, self.recv_meta.tensor, self.flags.tensor, W, cap, self.e_local, H,
+                              True, n, self.offsets, self.order, xq, xs)
             if keep_fp8:
-                xq = self.xq[:, : self.hidden].view(torch.float8_e4m3fn)
-                xs = self.xq[:, self.hidden:].view(torch.float32).t().contiguous()
-                return (xq, xs), self.offsets, send_pos
-            L.ep_dequant_rows(self.xq, self.xp, W * self.cap, n_rows)
-        else:
-            L.moe_permute_rows(self.recv_x.tensor.view(torch.bfloat16).view(W * self.cap, self.hidden),
-                               self.order, n_rows, self.xp, 1)
-        return self.xp, self.offsets, send_pos
+                return (xq.view(torch.float8_e4m3fn), xs), self.offsets, send_pos
+            if self.xdq is None:
+                self.xdq = torch.empty(W * self.cap, H, dtype=torch.bfloat16, device=x.device)
+            xp = self.xdq[:n]
+            L.dequant_fp8_group128(xq, xs, xp, self.n_rows)
+            return xp, self.offsets, send_pos
+        xp = self.xrows[: n * H * 2].view(torch.bfloat16).view(n, H)
+        L.ep_recv_compact(self.recv_x.tensor, self.recv_meta.tensor, self.flags.tensor, W, cap, self.e_local, H,
+                          False, n, self.offsets, self.order, xp, None)
+        return xp, self.offsets, send_pos
 
     def combine(self, out_sorted: torch.Tensor, ids: torch.Tensor, send_pos: torch.Tensor, w: torch.Tensor,
                 shared: Optional[torch.Tensor]) -> torch.Tensor:
         L, W = _lib(), self.world
-        n_rows = self.offsets[self.e_local:self.e_local + 1]
         L.ep_combine_send(W, self.rank, self.ret_x.peer_ptrs, self.flags.peer_ptrs, out_sorted, self.order,
-                          n_rows, self.cap)
+                          self.n_rows, self.step_cap)
         y = torch.empty(ids.shape[0], self.hidden, dtype=torch.bfloat16, device=out_sorted.device)
-        L.ep_combine_reduce(self.ret_x.tensor, ids, send_pos, w, shared, y, self.e_local, self.cap)
+        L.ep_combine_reduce(self.ret_x.tensor, ids, send_pos, w, shared, y, self.e_local, self.step_cap)
         return y
 
 
@@ -114,7 +149,6 @@ class EPMoE:
         self.e_local = moe.cfg.n_routed_experts // self.world
         assert moe.e_begin == self.rank * self.e_local and moe.e_end == moe.e_begin + self.e_local, \
             "the MoE must hold exactly this rank's expert slice"
-        self._act = self._out = None
 
     @property
     def dropped(self) -> int:
@@ -125,21 +159,29 @@ class EPMoE:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         moe, cfg = self.moe, self.moe.cfg
-        logits = x.float() @ moe.gate.float().t()
-        ids, w = route(logits, moe.bias, cfg)
-        shared = moe.shared_forward(x)
+        ids, w = route(moe.router_logits(x), moe.bias, cfg)
         if not x.is_cuda:
-            return self._forward_host(x, ids, w, shared)
-        ep, L = self.ep, _lib()
+            return self._forward_host(x, ids, w, moe.shared_forward(x))
+        ep = self.ep
+        # the shared experts need no exchange: they run on a side stream while the rows travel (reference:
+        # nn/moe/expert_parallel.py:247-300 issues the shared expert between dispatch and its wait)
+        shared = None
+        if moe.shared_gate_up is not None:
+            main = torch.cuda.current_stream()
+            ep.side.wait_stream(main)
+            with torch.cuda.stream(ep.side):
+                shared = moe.shared_forward(x)
+            shared.record_stream(main)
         fp8_experts = isinstance(moe.w_gate_up, Fp8ExpertWeights)
         xp, offsets, send_pos = ep.dispatch(x, ids, keep_fp8=fp8_experts)
-        n = (xp[0] if isinstance(xp, tuple) else xp).shape[0]
-        if self._out is None:
-            self._act = (None if fp8_experts else
-                         torch.empty(n, cfg.moe_intermediate_size, dtype=x.dtype, device=x.device))
-            self._out = torch.empty(n, cfg.hidden_size, dtype=x.dtype, device=x.device)
-        moe.local_gemms(xp, offsets, self._act, self._out)
-        return ep.combine(self._out, ids, send_pos, w.contiguous(), shared)
+        n = ep.step_rows
+        out = ep.out[:n]
+        # rows per expert: no more than one per token of any rank; a balanced router gives pairs / experts
+        moe.local_gemms(xp, offsets, None, out, max_rows=min(n, self.world * ep.step_tokens),
+                        expected_rows=ep.step_tokens * cfg.num_experts_per_tok // self.e_local + 1)
+        if shared is not None:
+            torch.cuda.current_stream().wait_stream(ep.side)
+        return ep.combine(out, ids, send_pos, w.contiguous(), shared)
 
     __call__ = forward
 

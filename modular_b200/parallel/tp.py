@@ -155,6 +155,21 @@ class Collectives:
         n = c.world * rows * x2.shape[1]
         return self.out.tensor.view(x.dtype)[:n].view(c.world * x.shape[0], *x.shape[1:]).clone()
 
+    def scatter(self, x: Optional[torch.Tensor], like: torch.Tensor, root: int = 0) -> torch.Tensor:
+        """Rank r receives ``x[r]`` of the root's ``x`` ([world, ...]); ``like`` gives the chunk's shape and dtype on
+        every rank (``x`` is only read on the root)."""
+        c = self.ctx
+        nbytes = like.numel() * like.element_size()
+        if nbytes % 16 or nbytes * c.world > self.max_bytes // 2:
+            raise ValueError("scatter: chunks must be multiples of 16 bytes and fit the staging size")
+        if c.rank == root:
+            if x is None or x.shape[0] != c.world or x[0].numel() != like.numel():
+                raise ValueError("scatter: the root passes a tensor of world chunks")
+            self.inp.tensor.view(torch.uint8)[: nbytes * c.world].copy_(x.contiguous().reshape(-1).view(torch.uint8))
+        res = torch.empty_like(like)
+        self.L.tp_scatter(c.world, c.rank, root, self.inp.peer_ptrs, res, self.flags.peer_ptrs, nbytes)
+        return res
+
     def broadcast(self, x: torch.Tensor, root: int = 0) -> torch.Tensor:
         c = self.ctx
         nbytes = x.numel() * x.element_size()

@@ -114,7 +114,9 @@ def make_lifespan(settings: Settings, pipeline_config, tokenizer, factory: Calla
                     f"model-worker-{i}", model_worker_main,
                     (factories[i], _replica_config(pipeline_config, i, n_rep), specs, settings),
                     ready_timeout_s=settings.mw_timeout_s, use_heartbeat=settings.use_heartbeat,
-                    health_fail_s=settings.mw_health_fail_s))
+                    health_fail_s=settings.mw_health_fail_s,
+                    # a tensor-parallel worker starts the other ranks itself
+                    daemon=(getattr(pipeline_config, "tensor_parallel_degree", 1) or 1) <= 1))
                 queues = WorkerQueues(request=specs["request"].push(bind=False), response=response_pull,
                                       cancel=specs["cancel"].push(bind=False))
                 proxies.append(ModelWorkerProxy(queues, settings.max_queue_size))

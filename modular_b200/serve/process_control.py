@@ -18,14 +18,20 @@ class SubprocessExit(RuntimeError):
 
 
 class ProcessManager:
-    def __init__(self, name: str, target: Callable, args: tuple = (), ctx=None):
+    def __init__(self, name: str, target: Callable, args: tuple = (), ctx=None, daemon: bool = True):
+        """``daemon=False`` for a child that starts processes of its own (a daemonic process may not); such a
+        child is stopped by :meth:`shutdown`, also at interpreter exit."""
         self.name = name
         self.ctx = ctx or mp.get_context("spawn")
         self.ready_event = self.ctx.Event()
         self.alive_event = self.ctx.Event()
         self.stop_event = self.ctx.Event()
-        self.process = self.ctx.Process(target=target, name=name, daemon=True,
+        self.process = self.ctx.Process(target=target, name=name, daemon=daemon,
                                         args=(*args, self.ready_event, self.alive_event, self.stop_event))
+        if not daemon:
+            import atexit
+
+            atexit.register(self.shutdown, 1.0)
 
     def start(self) -> None:
         self.process.start()
@@ -60,6 +66,8 @@ class ProcessManager:
 
     def shutdown(self, grace_s: float = 5.0) -> None:
         self.stop_event.set()
+        if self.process.pid is None:
+            return
         if self.process.is_alive():
             self.process.join(grace_s)
         if self.process.is_alive():
@@ -71,12 +79,12 @@ class ProcessManager:
 
 @contextlib.asynccontextmanager
 async def subprocess_manager(name: str, target: Callable, args: tuple = (), ready_timeout_s: float = 1200.0,
-                             use_heartbeat: bool = False, health_fail_s: float = 60.0):
+                             use_heartbeat: bool = False, health_fail_s: float = 60.0, daemon: bool = True):
     """Start ``target`` in a spawned process, wait until ready, yield (manager, watcher task).
 
     The watcher task fails with SubprocessExit if the child dies (or stops beating); callers
     await it alongside the server so a worker crash brings the server down."""
-    pm = ProcessManager(name, target, args)
+    pm = ProcessManager(name, target, args, daemon=daemon)
     pm.start()
     watcher: Optional[asyncio.Task] = None
     try:

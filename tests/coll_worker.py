@@ -62,6 +62,9 @@ def main():
     want = y.clone()
     dist.broadcast(want, world - 1)
     res["cases"].append(["broadcast", "", y.numel(), float((got - want).abs().max()), True])
+    full = torch.randn(world, 33, 16, generator=torch.Generator().manual_seed(7)).to(dev)
+    got = coll.scatter(full if rank == 1 % world else None, full[0], root=1 % world)
+    res["cases"].append(["scatter", "", full[0].numel(), float((got - full[rank]).abs().max()), True])
     torch.cuda.synchronize()
     ops.check_device_error()
     gathered = [None] * world

@@ -85,7 +85,7 @@ def deepseek_model(rank, world, dev):
                                          e_begin=rank * El, e_end=(rank + 1) * El)
     page, T = 16, 40 + 3 * rank
     ep = EPContext(TPContext(device=dev), cfg.hidden_size, cfg.n_routed_experts, cfg.num_experts_per_tok,
-                   max_tokens=64)
+                   max_tokens=64, fp8_dispatch=False, host_group=dist.new_group(backend="gloo"))
     kv = lambda: torch.zeros(8, 1, cfg.num_hidden_layers, 1, page, cfg.latent_dim, dtype=torch.bfloat16, device=dev)
     m_ep, m_full = DeepseekV3Model(cfg, mine, kv(), ep=ep), DeepseekV3Model(cfg, full, kv())
     tok = torch.randint(0, cfg.vocab_size, (T,), generator=torch.Generator().manual_seed(rank)).to(dev)
@@ -94,12 +94,22 @@ def deepseek_model(rank, world, dev):
     bt = torch.tensor([[1, 2, 3, 0]], dtype=torch.int32, device=dev)
     i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=dev)
     args = (tok, pos, slots, bt, i32(0), i32(T), i32(T), torch.arange(T, dtype=torch.int32, device=dev))
+    m_ep.capture_decode_graphs([4])          # every rank, same sizes: the warm-up run exchanges rows
     got, want = m_ep.forward_tensors(*args), m_full.forward_tensors(*args)
     torch.cuda.synchronize()
     ops.check_device_error()
     err = float((got - want).abs().max() / want.abs().max())
+    # one decode step on top of the prefill: the EP model replays its captured graph (one real sequence, three
+    # dummies), the reference model runs eagerly
+    nxt = want[-1].argmax().view(1)
+    dargs = (nxt, i32(T), torch.tensor([T + page], dtype=torch.long, device=dev), bt, i32(0), i32(1), i32(T + 1), i32(0))
+    got_d, want_d = m_ep.forward_tensors(*dargs), m_full.forward_tensors(*dargs)
+    torch.cuda.synchronize()
+    ops.check_device_error()
+    assert m_ep.graph_replays == 1, m_ep.graph_replays
+    err_d = float((got_d - want_d).abs().max() / want_d.abs().max())
     gathered = [None] * world
-    dist.all_gather_object(gathered, {"rank": rank, "errs": [err], "dropped": 0})
+    dist.all_gather_object(gathered, {"rank": rank, "errs": [err, err_d], "dropped": 0})
     if rank == 0:
         print("EP_RESULT " + json.dumps(gathered), flush=True)
     dist.barrier()

@@ -329,6 +329,99 @@ def test_grouped_gemm_fp8_and_fp8_experts():
     assert _rel_err(moe_fp8(xt), moe_bf16(xt)) < 4e-2      # activations are quantised to fp8 on the fp8 path
 
 
+def test_grouped_gemm_fp8_many_experts_with_row_bound():
+    """The tile list of the grouped GEMM: more experts than one round of the in-kernel prefix sum covers, empty
+    experts, a row count that is only an upper bound, and every token tile size."""
+    from modular_b200._native import lib
+    from modular_b200.nn.moe import Fp8ExpertWeights
+
+    torch.manual_seed(24)
+    E, N, K = 40, 128, 256
+    g = torch.Generator().manual_seed(1)
+    counts = torch.randint(0, 150, (E,), generator=g)
+    counts[[3, 17, 39]] = 0
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]).to(torch.int32).to(DEV)
+    rows, bound = int(counts.sum()), int(counts.sum()) + 300
+    x = torch.randn(bound, K, device=DEV, dtype=torch.bfloat16)
+    fw = Fp8ExpertWeights.quantize((torch.randn(E, N, K, device=DEV) * 0.05).to(torch.bfloat16))
+    xq, xs = ops.quant_fp8_group128(x)
+    for bn in (0, 32, 64, 128):
+        y = torch.zeros(bound, N, device=DEV, dtype=torch.bfloat16)
+        lib().grouped_gemm_fp8(xq, xs, fw.q, fw.scale, y, offsets, 150, bn)
+        for e in range(E):
+            a, b = int(offsets[e]), int(offsets[e + 1])
+            if b > a:
+                yr = ref.linear_fp8_blockscaled(xq[a:b], xs[:, a:b].contiguous(), fw.q[e], fw.scale[e])
+                assert _rel_err(y[a:b], yr) < 5e-3, (bn, e)
+        assert torch.all(y[rows:] == 0)
+
+
+def test_silu_mul_quant_fp8_equals_two_passes_and_respects_row_count():
+    from modular_b200._native import lib
+
+    torch.manual_seed(25)
+    M, I = 300, 512
+    gu = (torch.randn(M, 2 * I, device=DEV) * 2).to(torch.bfloat16)
+    q2, s2 = ops.quant_fp8_group128(ops.silu_mul(gu))
+    q = torch.zeros(M, I, dtype=torch.float8_e4m3fn, device=DEV)
+    s = torch.zeros(I // 128, M + 20, dtype=torch.float32, device=DEV)
+    lib().silu_mul_quant_fp8(gu, q, s, None)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s[:, :M], s2)
+    n_rows = torch.tensor([77], dtype=torch.int32, device=DEV)
+    q.view(torch.uint8).zero_()
+    s.zero_()
+    lib().silu_mul_quant_fp8(gu, q, s, n_rows)
+    assert torch.equal(q.view(torch.uint8)[:77], q2.view(torch.uint8)[:77]) and torch.all(q.view(torch.uint8)[77:] == 0)
+    assert torch.equal(s[:, :77], s2[:, :77]) and torch.all(s[:, 77:] == 0)
+    # and back: the dequantised rows are the bf16 activations to fp8 precision
+    out = torch.zeros(M, I, dtype=torch.bfloat16, device=DEV)
+    lib().dequant_fp8_group128(q2, s2, out, n_rows)
+    assert _rel_err(out[:77], ops.silu_mul(gu)[:77]) < 0.04 and torch.all(out[77:] == 0)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("world,cap,E,counts", [(4, 64, 8, [64, 0, 17, 33]), (2, 300, 32, [299, 150]),
+                                                (8, 16, 128, [1, 0, 0, 16, 5, 0, 9, 2]), (1, 2000, 5, [1777])])
+def test_ep_recv_compact_sorts_received_rows_by_expert(fp8, world, cap, E, counts):
+    """The receive side of the expert-parallel dispatch in one launch, checked against a stable sort of the same
+    receive buffers: offsets, the order array, the rows, and (fp8) the payload / scale split."""
+    from modular_b200._native import lib
+
+    torch.manual_seed(26)
+    H = 512            # fp8 rows carry H / 128 fp32 scales behind the payload and must stay 16-byte aligned
+    row_bytes = H + H // 128 * 4 if fp8 else 2 * H
+    recv_x = torch.randint(0, 255, (world * cap, row_bytes), dtype=torch.uint8, device=DEV)
+    meta = torch.zeros(world * cap, 2, dtype=torch.int32, device=DEV)
+    meta[:, 0] = torch.randint(0, E, (world * cap,), device=DEV).int()
+    flags = torch.zeros(lib().ep_flag_ints(), dtype=torch.int32, device=DEV)
+    flags[16:16 + world] = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    n = world * cap
+    offsets = torch.zeros(E + 1, dtype=torch.int32, device=DEV)
+    order = torch.full((n,), -1, dtype=torch.int32, device=DEV)
+    if fp8:
+        xq = torch.zeros(n, H, dtype=torch.uint8, device=DEV)
+        xs = torch.zeros(H // 128, n, dtype=torch.float32, device=DEV)
+    else:
+        xq, xs = torch.zeros(n, H, dtype=torch.bfloat16, device=DEV), None
+    lib().ep_recv_compact(recv_x, meta, flags, world, cap, E, H, fp8, n, offsets, order, xq, xs)
+    torch.cuda.synchronize()
+    flat = torch.cat([torch.arange(c) + s * cap for s, c in enumerate(counts)]).to(DEV)
+    ids = meta[flat, 0].long()
+    perm = torch.sort(ids, stable=True).indices
+    want_order = flat[perm].int()
+    total = len(flat)
+    want_off = torch.cat([torch.zeros(1, dtype=torch.long, device=DEV), torch.bincount(ids, minlength=E).cumsum(0)]).int()
+    assert torch.equal(offsets, want_off)
+    assert torch.equal(order[:total], want_order)
+    rows = recv_x[want_order.long()]
+    if fp8:
+        assert torch.equal(xq[:total], rows[:, :H])
+        want_s = rows[:, H:].contiguous().view(torch.float32)           # [total, H / 128]
+        assert torch.equal(xs[:, :total].view(torch.int32), want_s.t().contiguous().view(torch.int32))
+    else:
+        assert torch.equal(xq[:total].view(torch.uint8).view(total, -1), rows)
+
+
 # ---------------------------------------------------------------------------- decode-step GEMM
 @pytest.mark.parametrize("M,N,K", [(64, 6144, 4096), (64, 4096, 4096), (64, 4096, 14336), (1, 8192, 8192),
                                    (16, 1024, 1024), (100, 4096, 512), (256, 4096, 1792), (33, 1536, 4160),
