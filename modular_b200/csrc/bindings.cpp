@@ -928,6 +928,39 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              "mla_paged_attention");
   }, py::arg("q_lat"), py::arg("q_rope"), py::arg("cache"), py::arg("block_table"), py::arg("q_start"),
      py::arg("q_len"), py::arg("kv_len"), py::arg("out"), py::arg("scale"), py::arg("decode_only") = false);
+  // after the fused down-projections of an MLA layer: norms, key rotation and the latent-cache store in one launch
+  m.def("mla_post_down", [](const Tensor& qkv_a, int q_lora, const c10::optional<Tensor>& gamma_q, const Tensor& gamma_kv,
+                            double eps, const Tensor& positions, const Tensor& cos_sin, const Tensor& slots,
+                            const c10::optional<Tensor>& q_a_out, Tensor& cache) {
+    need_cuda(qkv_a, "qkv_a");
+    const int R = cache.size(2) - 64;
+    TORCH_CHECK(qkv_a.dim() == 2 && qkv_a.stride(1) == 1 && qkv_a.scalar_type() == at::kBFloat16 &&
+                    qkv_a.size(1) >= q_lora + R + 64 && positions.scalar_type() == at::kInt &&
+                    slots.scalar_type() == at::kLong && cos_sin.scalar_type() == at::kFloat && cos_sin.is_contiguous() &&
+                    cos_sin.size(1) == 64 && cache.stride(2) == 1 && cache.stride(1) == cache.size(2) &&
+                    gamma_kv.numel() == R && positions.numel() >= qkv_a.size(0) && slots.numel() >= qkv_a.size(0),
+                "mla_post_down layout");
+    TORCH_CHECK(q_lora == 0 || (gamma_q.has_value() && q_a_out.has_value() && gamma_q->numel() == q_lora &&
+                                q_a_out->is_contiguous() && q_a_out->size(0) >= qkv_a.size(0) && q_a_out->size(1) == q_lora),
+                "mla_post_down: q_a outputs");
+    check_rc(mb_mla_post_down(qkv_a.data_ptr(), qkv_a.stride(0), q_lora, R, q_lora ? gamma_q->data_ptr() : gamma_kv.data_ptr(),
+                              gamma_kv.data_ptr(), eps, positions.data_ptr<int32_t>(), cos_sin.data_ptr<float>(),
+                              slots.data_ptr<int64_t>(), q_lora ? q_a_out->data_ptr() : cache.data_ptr(), cache.data_ptr(),
+                              qkv_a.size(0), cache.size(1), cache.stride(0), cur_stream()),
+             "mla_post_down");
+  });
+  m.def("mla_q_rope", [](const Tensor& q, int n_heads, int nope, const Tensor& positions, const Tensor& cos_sin,
+                         Tensor& q_rope) {
+    need_cuda(q, "q");
+    TORCH_CHECK(q.is_contiguous() && q_rope.is_contiguous() && q.scalar_type() == at::kBFloat16 &&
+                    q.numel() == q.size(0) * static_cast<int64_t>(n_heads) * (nope + 64) &&
+                    q_rope.numel() >= q.size(0) * static_cast<int64_t>(n_heads) * 64 && positions.scalar_type() == at::kInt &&
+                    cos_sin.scalar_type() == at::kFloat && cos_sin.is_contiguous() && cos_sin.size(1) == 64,
+                "mla_q_rope layout");
+    check_rc(mb_mla_q_rope(q.data_ptr(), n_heads, nope, positions.data_ptr<int32_t>(), cos_sin.data_ptr<float>(),
+                           q_rope.data_ptr(), q.size(0), cur_stream()),
+             "mla_q_rope");
+  });
   m.def("set_mla_tc", [](bool on) { mb_set_mla_tc(on ? 1 : 0); }, py::arg("on"));
   // ---- expert parallelism ----
   m.def("ep_flag_ints", []() { return mb_ep_flag_ints(); });
@@ -973,14 +1006,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("ep_combine_reduce", [](const Tensor& ret_x, const Tensor& topk_ids, const Tensor& send_pos,
                                 const Tensor& w, const c10::optional<Tensor>& shared, Tensor& y, int e_local,
-                                int cap) {
+                                int cap, const c10::optional<Tensor>& residual) {
     need_cuda(ret_x, "ret_x");
-    TORCH_CHECK(y.is_contiguous() && w.is_contiguous() && w.scalar_type() == at::kFloat, "ep_combine_reduce layout");
+    TORCH_CHECK(y.is_contiguous() && w.is_contiguous() && w.scalar_type() == at::kFloat &&
+                    (!residual || (residual->is_contiguous() && residual->sizes() == y.sizes())) &&
+                    (!shared || (shared->is_contiguous() && shared->sizes() == y.sizes())),
+                "ep_combine_reduce layout");
     check_rc(mb_ep_combine_reduce(ret_x.data_ptr(), topk_ids.data_ptr<int32_t>(), send_pos.data_ptr<int32_t>(),
-                                  w.data_ptr<float>(), optptr(shared), y.data_ptr(), y.size(0), y.size(1),
-                                  topk_ids.size(1), e_local, cap, cur_stream()),
+                                  w.data_ptr<float>(), optptr(shared), optptr(residual), y.data_ptr(), y.size(0),
+                                  y.size(1), topk_ids.size(1), e_local, cap, cur_stream()),
              "ep_combine_reduce");
-  });
+  }, py::arg("ret_x"), py::arg("topk_ids"), py::arg("send_pos"), py::arg("w"), py::arg("shared"), py::arg("y"),
+     py::arg("e_local"), py::arg("cap"), py::arg("residual") = py::none());
   // receive buffers -> rows in expert order + offsets + order, one launch; fp8 rows are split into payload and
   // group-major scales
   m.def("ep_recv_compact", [](const Tensor& recv_x, const Tensor& recv_meta, const Tensor& flags, int world, int cap,
@@ -1000,6 +1037,36 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                 order.data_ptr<int32_t>(), xq.data_ptr(), xs ? xs->data_ptr<float>() : nullptr,
                                 xs ? static_cast<int>(xs->size(1)) : 0, num_sms(), cur_stream()),
              "ep_recv_compact");
+  });
+  // y[m, b * y_off + n] = sum_k x[m, b * x_off + k] * w[b, n, k]: per-head products on column blocks of x and y
+  m.def("batched_gemm_bf16", [](const Tensor& x, const Tensor& w, Tensor& y, int x_off, int y_off) {
+    need_cuda(x, "x");
+    TORCH_CHECK(x.dim() == 2 && y.dim() == 2 && w.dim() == 3 && x.stride(1) == 1 && y.stride(1) == 1 &&
+                    w.is_contiguous() && x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
+                    y.scalar_type() == at::kBFloat16 && y.size(0) == x.size(0),
+                "batched_gemm_bf16: bf16 x [M, *], w [B, N, K], y [M, *]");
+    const int B = w.size(0), N = w.size(1), K = w.size(2);
+    TORCH_CHECK(static_cast<int64_t>(B - 1) * x_off + K <= x.size(1) && static_cast<int64_t>(B - 1) * y_off + N <= y.size(1),
+                "batched_gemm_bf16: column blocks out of range");
+    check_rc(mb_batched_gemm_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), B, x.size(0), N, K, x.stride(0), x_off,
+                                  y.stride(0), y_off, x.size(1), 0, error_flag(), cur_stream()),
+             "batched_gemm_bf16");
+  });
+  // the same on the persistent decode-step GEMM (at most 256 rows, N % 128 == 0): one launch over all heads
+  m.def("gemm_dec_batched", [](const Tensor& x, const Tensor& w, Tensor& y, int x_off, int y_off, Tensor& ws,
+                               Tensor& state) {
+    need_cuda(x, "x");
+    TORCH_CHECK(x.dim() == 2 && y.dim() == 2 && w.dim() == 3 && x.stride(1) == 1 && y.stride(1) == 1 &&
+                    w.is_contiguous() && x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
+                    y.scalar_type() == at::kBFloat16 && y.size(0) == x.size(0) && state.scalar_type() == at::kInt,
+                "gemm_dec_batched: bf16 x [M, *], w [B, N, K], y [M, *]");
+    const int B = w.size(0), N = w.size(1), K = w.size(2);
+    TORCH_CHECK(static_cast<int64_t>(B - 1) * x_off + K <= x.size(1) && static_cast<int64_t>(B - 1) * y_off + N <= y.size(1),
+                "gemm_dec_batched: column blocks out of range");
+    check_rc(mb_gemm_dec_batched(x.data_ptr(), w.data_ptr(), y.data_ptr(), B, x.size(0), N, K, x.stride(0), x_off,
+                                 y.stride(0), y_off, x.size(1), ws.data_ptr(), ws.nbytes(), state.data_ptr<int>(),
+                                 error_flag(), num_sms(), cur_stream()),
+             "gemm_dec_batched");
   });
   m.def("dequant_fp8_group128", [](const Tensor& q, const Tensor& scales, Tensor& out, const c10::optional<Tensor>& n_rows) {
     need_cuda(q, "q");

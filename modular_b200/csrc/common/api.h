@@ -92,6 +92,16 @@ int mb_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int 
 int mb_silu_mul(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream);
 int mb_silu_mul_quant_fp8(const void* gate_up, void* q_fp8, float* scales, int M, int inter, int ld_s,
                           const int32_t* n_rows_dev, cudaStream_t stream);
+int mb_mla_post_down(const void* qkv_a, int ld, int q_lora, int R, const void* gamma_q, const void* gamma_kv, float eps,
+                     const int32_t* positions, const float* cos_sin, const int64_t* slots, void* q_a_out, void* cache,
+                     int T, int page_size, long long page_stride, cudaStream_t stream);
+int mb_mla_q_rope(const void* q, int n_heads, int nope, const int32_t* positions, const float* cos_sin, void* q_rope,
+                  int T, cudaStream_t stream);
+int mb_gemm_dec_batched(const void* X, const void* W, void* Y, int B, int M, int N, int K, int ldx, int x_off, int ldy,
+                        int y_off, int x_cols, void* ws, size_t ws_bytes, int* state, int* err, int num_sms,
+                        cudaStream_t stream);
+int mb_batched_gemm_bf16(const void* X, const void* W, void* Y, int B, int M, int N, int K, int ldx, int x_off,
+                         int ldy, int y_off, int x_cols, int bn, int* err, cudaStream_t stream);
 int mb_dequant_fp8_group128(const void* q_fp8, const float* scales, void* out_bf16, int M, int K, int ld_s,
                             const int32_t* n_rows_dev, cudaStream_t stream);
 int mb_ep_recv_compact(const void* recv_x, const int32_t* recv_meta, const int* flags, int world, int cap,
@@ -229,8 +239,8 @@ int mb_ep_combine_send(int world, int rank, void* const* ret_x, int* const* flag
                        const int32_t* order, const int32_t* n_rows_dev, int max_rows, int H, int cap,
                        int* err, cudaStream_t stream);
 int mb_ep_combine_reduce(const void* ret_x, const int32_t* topk_ids, const int32_t* send_pos, const float* w,
-                         const void* shared, void* y, int T, int H, int top_k, int e_local, int cap,
-                         cudaStream_t stream);
+                         const void* shared, const void* residual, void* y, int T, int H, int top_k, int e_local,
+                         int cap, cudaStream_t stream);
 int mb_ep_dequant_rows(const void* src, void* dst, int n, int H, const int32_t* n_rows_dev, cudaStream_t stream);
 
 // ---- sampling (sampling.cu) ----------------------------------------------------------------

@@ -266,10 +266,10 @@ ep_combine_send_kernel(Peers p, const bf16* __restrict__ out_sorted, const int32
   if (threadIdx.x == 0) { my[kDone] = 0; my[kEpoch] = epoch; }
 }
 
-// y[t] = shared[t] + sum_k w[t,k] * ret_x[owner][pos]   (all local reads)
+// y[t] = residual[t] + shared[t] + sum_k w[t,k] * ret_x[owner][pos]   (all local reads; y may alias residual)
 __global__ void ep_combine_reduce_kernel(const uint8_t* __restrict__ ret_x, const int32_t* __restrict__ topk_ids,
                                          const int32_t* __restrict__ send_pos, const float* __restrict__ w,
-                                         const bf16* __restrict__ shared, bf16* __restrict__ y, int T, int H,
+                                         const bf16* __restrict__ shared, const bf16* residual, bf16* y, int T, int H,
                                          int top_k, int e_local, int cap) {
   const int per_row = H >> 3;
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -284,6 +284,12 @@ __global__ void ep_combine_reduce_kernel(const uint8_t* __restrict__ ret_x, cons
   } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  }
+  if (residual) {
+    const uint4 rv = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * H + c);
+    const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(rp[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
   }
   for (int k = 0; k < top_k; ++k) {
     const int pair = t * top_k + k;
@@ -417,13 +423,13 @@ extern "C" int mb_ep_combine_send(int world, int rank, void* const* ret_x, int* 
 }
 
 extern "C" int mb_ep_combine_reduce(const void* ret_x, const int32_t* topk_ids, const int32_t* send_pos,
-                                    const float* w, const void* shared, void* y, int T, int H, int top_k,
-                                    int e_local, int cap, cudaStream_t stream) {
+                                    const float* w, const void* shared, const void* residual, void* y, int T, int H,
+                                    int top_k, int e_local, int cap, cudaStream_t stream) {
   if (T <= 0) return MB_OK;
   const long long work = static_cast<long long>(T) * (H / 8);
   ep::ep_combine_reduce_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
       static_cast<const uint8_t*>(ret_x), topk_ids, send_pos, w, static_cast<const ep::bf16*>(shared),
-      static_cast<ep::bf16*>(y), T, H, top_k, e_local, cap);
+      static_cast<const ep::bf16*>(residual), static_cast<ep::bf16*>(y), T, H, top_k, e_local, cap);
   return EP_LAUNCH_OK();
 }
 

@@ -69,6 +69,9 @@ struct Params {
   int mode;
   __nv_bfloat16* Y;        // mode 0/1 output
   int ldy;
+  // batched mode 0 (bN > 0): W stacks B matrices of bN rows; rows [b bN, (b + 1) bN) multiply the K columns of X
+  // that start at b * x_boff and produce the bN columns of Y that start at b * y_boff
+  int bN, x_boff, y_boff;
   int inter;               // mode 1: gate rows [0, inter), up rows [inter, 2 inter)
   __nv_bfloat16* h;        // mode 2: residual stream [M, N], updated in place
   __nv_bfloat16* xn;       // mode 2: normalised rows [M, N]
@@ -273,7 +276,7 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             mbar_arrive_expect_tx(full_st, stage_bytes);
             tma_load_2d(sa, &tmW, full_st, kbi * kBK, n0);
           }
-          tma_load_2d(sa + kATile, &tmX, full_st, kbi * kBK, t0);
+          tma_load_2d(sa + kATile, &tmX, full_st, (p.bN > 0 ? (n0 / p.bN) * p.x_boff : 0) + kbi * kBK, t0);
           ++issued;
           if (++st == p.stages) { st = 0; ph ^= 1; }
         }
@@ -390,7 +393,8 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = silu_f(v[i]) * u[i];
       }
-      *reinterpret_cast<uint4*>(p.Y + static_cast<size_t>(t) * p.ldy + n) = pack_bf16x8(v);
+      const int col = p.bN > 0 ? (n / p.bN) * p.y_boff + n % p.bN : n;
+      *reinterpret_cast<uint4*>(p.Y + static_cast<size_t>(t) * p.ldy + col) = pack_bf16x8(v);
     }
   } else if (run_epilogue) {
     // all ring stages are idle: reuse them as the row cache (N * 2 bytes)
@@ -603,10 +607,11 @@ extern "C" int mb_gemm_dec_plan(int M, int N, int K, int mode, size_t ws_bytes, 
 // All ranks must issue the same sequence of mode-2 calls. Launches that share `ws` / `state` must not
 // overlap on the device. Returns MB_ERR_SHAPE / MB_ERR_TOO_LARGE for shapes this kernel does not take
 // (see mb_gemm_dec_plan); the caller then uses the tiled kernels.
-extern "C" int mb_gemm_dec(const void* X, const void* W, int M, int N, int K, int ldx, int ldw, int mode,
-                           void* Y, int ldy, void* h, void* xn, const void* gamma, float eps, float w_off,
-                           int mbc, int world, int rank, void* const* lam, int lam_rows, void* ws,
-                           size_t ws_bytes, int* state, int* err, int num_sms, cudaStream_t stream) {
+static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int ldx, int ldw, int mode,
+                         void* Y, int ldy, void* h, void* xn, const void* gamma, float eps, float w_off,
+                         int mbc, int world, int rank, void* const* lam, int lam_rows, void* ws,
+                         size_t ws_bytes, int* state, int* err, int num_sms, cudaStream_t stream, int bN, int x_boff,
+                         int y_boff, int x_cols) {
   using namespace mb::dec;
   if (M <= 0 || N <= 0) return MB_OK;
   if (ldx % 8 || ldw % 8 || (mode != 2 && ldy % 8)) return MB_ERR_SHAPE;
@@ -625,6 +630,7 @@ extern "C" int mb_gemm_dec(const void* X, const void* W, int M, int N, int K, in
   p.trace = g_dec_trace;
   p.state = state; p.err = err; p.mode = mode;
   p.Y = static_cast<__nv_bfloat16*>(Y); p.ldy = ldy;
+  p.bN = bN; p.x_boff = x_boff; p.y_boff = y_boff;
   p.inter = mode == 1 ? N / 2 : 0;
   p.h = static_cast<__nv_bfloat16*>(h); p.xn = static_cast<__nv_bfloat16*>(xn);
   p.gamma = static_cast<const __nv_bfloat16*>(gamma);
@@ -635,7 +641,7 @@ extern "C" int mb_gemm_dec(const void* X, const void* W, int M, int N, int K, in
   CUtensorMap tw, tx;
   rc = cached_tmap(&tw, W, N, K, ldw, kBM, 2);
   if (rc != MB_OK) return rc;
-  rc = cached_tmap(&tx, X, M, K, ldx, p.BN, 2);
+  rc = cached_tmap(&tx, X, M, bN > 0 ? x_cols : K, ldx, p.BN, 2);
   if (rc != MB_OK) return rc;
   const int stage_bytes = kATile + p.BN * kBK * 2;
   const size_t smem = static_cast<size_t>(p.stages) * stage_bytes + sizeof(Tail) + 1024;
@@ -647,4 +653,24 @@ extern "C" int mb_gemm_dec(const void* X, const void* W, int M, int N, int K, in
   }
   const cudaError_t e = launch_k(gemm_dec_kernel, dim3(p.G), dim3(kThreads), smem, stream, tw, tx, p);
   return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+extern "C" int mb_gemm_dec(const void* X, const void* W, int M, int N, int K, int ldx, int ldw, int mode,
+                           void* Y, int ldy, void* h, void* xn, const void* gamma, float eps, float w_off,
+                           int mbc, int world, int rank, void* const* lam, int lam_rows, void* ws,
+                           size_t ws_bytes, int* state, int* err, int num_sms, cudaStream_t stream) {
+  return gemm_dec_impl(X, W, M, N, K, ldx, ldw, mode, Y, ldy, h, xn, gamma, eps, w_off, mbc, world, rank, lam, lam_rows,
+                       ws, ws_bytes, state, err, num_sms, stream, 0, 0, 0, 0);
+}
+
+// The decode-step GEMM over the column blocks of one activation matrix (per-head weight absorption with at most
+// 256 tokens): Y[m, b * y_off + n] = sum_k X[m, b * x_off + k] * W[b, n, k]. W: [B, N, K] contiguous with
+// N % 128 == 0 (a weight tile belongs to one head) and K % 64 == 0. One persistent launch over all heads.
+extern "C" int mb_gemm_dec_batched(const void* X, const void* W, void* Y, int B, int M, int N, int K, int ldx,
+                                   int x_off, int ldy, int y_off, int x_cols, void* ws, size_t ws_bytes, int* state,
+                                   int* err, int num_sms, cudaStream_t stream) {
+  if (B <= 0) return MB_OK;
+  if (N % mb::dec::kBM || K % mb::dec::kBK || x_off % 8 || y_off % 8 || x_off <= 0 || y_off < N) return MB_ERR_SHAPE;
+  return gemm_dec_impl(X, W, M, B * N, K, ldx, K, 0, Y, ldy, nullptr, nullptr, nullptr, 0.f, 0.f, 0, 1, 0, nullptr, 0, ws,
+                       ws_bytes, state, err, num_sms, stream, N, x_off, y_off, x_cols);
 }

@@ -132,7 +132,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                int ldy, int ldr, int dual_rows, int k_per_split, int BN, int stages,
                uint32_t tmem_cols, int* err, const int32_t* __restrict__ expert_offsets,
                int w_rows_per_expert, const int* gate_flags, int gate_rpr, int gate_world,
-               int packed_kb) {
+               int packed_kb, int x_batch_off, int y_batch_off) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -161,6 +161,16 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (t0 >= row_end) return;
     Mlim = row_end;
     w_row0 = e * w_rows_per_expert;
+    split = 0;
+  }
+  // Batched mode (x_batch_off > 0): blockIdx.z is the batch entry b (an attention head); it reads the K columns
+  // of X that start at b * x_batch_off, weights W[b] and writes the N columns of Y that start at b * y_batch_off.
+  int xk0 = 0;
+  if (x_batch_off > 0) {
+    const int b = blockIdx.z;
+    w_row0 = b * w_rows_per_expert;
+    xk0 = b * x_batch_off;
+    Yv = static_cast<__nv_bfloat16*>(Yv) + static_cast<size_t>(b) * y_batch_off;
     split = 0;
   }
   const int k_begin = split * k_per_split;
@@ -235,7 +245,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tma_load_2d(sa, &tmW, full_s, kc, w_row0 + n0);
           if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, full_s, kc, w_row0 + dual_rows + n0);
         }
-        tma_load_2d(sb, &tmX, full_s, kc, t0);
+        tma_load_2d(sb, &tmX, full_s, xk0 + kc, t0);
       }
     }
   } else if (warp == 1) {
@@ -557,7 +567,8 @@ static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, con
                       int BN, int stages, int* err, cudaStream_t stream,
                       const int32_t* expert_offsets = nullptr, int n_experts = 0,
                       int w_rows_per_expert = 0, const int* gate_flags = nullptr, int gate_rpr = 1,
-                      int gate_world = 0, int packed_kb = 0) {
+                      int gate_world = 0, int packed_kb = 0, int batch = 0, int x_batch_off = 0,
+                      int y_batch_off = 0) {
   const int stage_bytes = kATileBytes * (DUAL ? 2 : 1) + BN * kBK * 2;
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes +
                       sizeof(GemmSmemTail) + 1024;
@@ -569,12 +580,12 @@ static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, con
       return MB_ERR_LAUNCH;
     configured.done();
   }
-  dim3 grid((M + BN - 1) / BN, (N + kBM - 1) / kBM, expert_offsets ? n_experts : splits);
+  dim3 grid((M + BN - 1) / BN, (N + kBM - 1) / kBM, expert_offsets ? n_experts : (batch > 0 ? batch : splits));
   const uint32_t tmem_cols = pow2_cols(DUAL ? 2 * BN : BN);
   const cudaError_t e = launch_k(kern, grid, dim3(kGemmThreads), smem, stream, tw, tx, Y,
                                  static_cast<const __nv_bfloat16*>(R), M, N, K, ldy, ldr, dual_rows, k_per_split,
                                  BN, stages, tmem_cols, err, expert_offsets, w_rows_per_expert, gate_flags,
-                                 gate_rpr, gate_world, packed_kb);
+                                 gate_rpr, gate_world, packed_kb, x_batch_off, y_batch_off);
   return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
@@ -870,6 +881,34 @@ extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const vo
 // the SwiGLU epilogue when flags bit0 is set). `max_rows` bounds the rows any expert can have
 // (the grid is sized for it; CTAs past an expert's rows exit at once).
 // Reference: max/kernels/src/linalg/grouped_matmul_sm100.mojo (grouped_matmul_ragged).
+// Batched product over the column blocks of one activation matrix (the per-head weight absorption of multi-head
+// latent attention): Y[m, b * y_off + n] = sum_k X[m, b * x_off + k] * W[b, n, k] for b < B. X: [M, >= B * x_off]
+// with row stride ldx, W: [B, N, K] contiguous, Y row stride ldy. No operand is transposed or copied: the head
+// is a coordinate offset of the TMA loads and of the stores.
+extern "C" int mb_batched_gemm_bf16(const void* X, const void* W, void* Y, int B, int M, int N, int K, int ldx,
+                                    int x_off, int ldy, int y_off, int x_cols, int bn, int* err,
+                                    cudaStream_t stream) {
+  if (B <= 0 || M <= 0) return MB_OK;
+  if (K % kBK || N % 8 || ldx % 8 || ldy % 8 || x_off % 8 || y_off % 8 || x_off <= 0 || y_off < N) return MB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(Y)) & 15)
+    return MB_ERR_ALIGN;
+  if (bn <= 0) {
+    bn = M >= 256 ? 256 : (M + 15) / 16 * 16;
+    if (bn < 16) bn = 16;
+  }
+  if (bn % 16 || bn > 256) return MB_ERR_SHAPE;
+  const int stage_bytes = kATileBytes + bn * kBK * 2;
+  int stages = (212 * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  CUtensorMap tw, tx;
+  int rc = cached_tmap(&tw, W, static_cast<uint64_t>(N) * B, K, K, kBM, 2);
+  if (rc != MB_OK) return rc;
+  rc = cached_tmap(&tx, X, M, x_cols, ldx, bn, 2);
+  if (rc != MB_OK) return rc;
+  return launch_cfg<false, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err, stream, nullptr, 0,
+                                     N, nullptr, 1, 0, 0, B, x_off, y_off);
+}
+
 extern "C" int mb_grouped_gemm_bf16(const void* X, const void* W, void* Y, const int32_t* expert_offsets,
                                     int n_experts, int total_rows, int max_rows, int N, int K, int flags,
                                     int bn, int* err, cudaStream_t stream) {

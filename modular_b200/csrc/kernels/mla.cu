@@ -28,6 +28,7 @@ namespace mb {
 namespace mla {
 
 typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
 constexpr int DR = 64;  // rotary part of the key
 
 struct Params {
@@ -272,6 +273,100 @@ __global__ void mla_kv_store_kernel(const bf16* __restrict__ c_kv, const bf16* _
   }
 }
 
+// What follows the two down-projections of an MLA layer, in one pass over the fused projection output
+// qkv_a[t] = [q_a (QL) | c_kv (R) | k_rope (64)]:
+//   q_a_out[t] = rms_norm(q_a) * gamma_q              (input of the q_b projection; skipped when QL == 0)
+//   cache[slot[t]] = [rms_norm(c_kv) * gamma_kv | rope(k_rope, position[t])]   (interleaved pairs)
+// One CTA of 256 threads per token. The norm rounds to bf16 before the weight is applied, like rmsnorm_kernel.
+__device__ __forceinline__ float block_sum_256(float v, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = threadIdx.x < (blockDim.x >> 5) ? scratch[threadIdx.x] : 0.f;
+  if (threadIdx.x < 32) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) scratch[0] = t;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+
+__device__ __forceinline__ uint4 norm8(const uint4 raw, const uint4 wraw, float inv) {
+  uint4 o;
+  const bf162* xp = reinterpret_cast<const bf162*>(&raw);
+  const bf162* wp = reinterpret_cast<const bf162*>(&wraw);
+  bf162* op = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(xp[i]), g = __bfloat1622float2(wp[i]);
+    const float2 nf = __bfloat1622float2(__floats2bfloat162_rn(f.x * inv, f.y * inv));
+    op[i] = __floats2bfloat162_rn(nf.x * g.x, nf.y * g.y);
+  }
+  return o;
+}
+
+__global__ void __launch_bounds__(256)
+mla_post_down_kernel(const bf16* __restrict__ qkv_a, int ld, int QL, int R, const bf16* __restrict__ gamma_q,
+                     const bf16* __restrict__ gamma_kv, float eps, const int32_t* __restrict__ positions,
+                     const float* __restrict__ cos_sin, const int64_t* __restrict__ slots,
+                     bf16* __restrict__ q_a_out, bf16* __restrict__ cache, int page_size, int64_t page_stride) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const bf16* row = qkv_a + static_cast<int64_t>(t) * ld;
+  if (QL > 0) {
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < QL / 8; v += blockDim.x) {
+      const uint4 a = *reinterpret_cast<const uint4*>(row + v * 8);
+      const bf162* ap = reinterpret_cast<const bf162*>(&a);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(ap[i]); ss += f.x * f.x + f.y * f.y; }
+    }
+    const float inv = rsqrtf(block_sum_256(ss, scratch) / static_cast<float>(QL) + eps);
+    for (int v = threadIdx.x; v < QL / 8; v += blockDim.x)
+      *reinterpret_cast<uint4*>(q_a_out + static_cast<int64_t>(t) * QL + v * 8) =
+          norm8(*reinterpret_cast<const uint4*>(row + v * 8), *reinterpret_cast<const uint4*>(gamma_q + v * 8), inv);
+  }
+  const int64_t slot = slots[t];
+  if (slot < 0) return;            // a dummy row: nothing to store (uniform over the CTA)
+  const bf16* ckv = row + QL;
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < R / 8; v += blockDim.x) {
+    const uint4 a = *reinterpret_cast<const uint4*>(ckv + v * 8);
+    const bf162* ap = reinterpret_cast<const bf162*>(&a);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(ap[i]); ss += f.x * f.x + f.y * f.y; }
+  }
+  const float inv = rsqrtf(block_sum_256(ss, scratch) / static_cast<float>(R) + eps);
+  bf16* dst = cache + (slot / page_size) * page_stride + (slot % page_size) * (R + DR);
+  for (int v = threadIdx.x; v < R / 8; v += blockDim.x)
+    *reinterpret_cast<uint4*>(dst + v * 8) =
+        norm8(*reinterpret_cast<const uint4*>(ckv + v * 8), *reinterpret_cast<const uint4*>(gamma_kv + v * 8), inv);
+  if (threadIdx.x < DR / 2) {
+    const int i = threadIdx.x;
+    const float* cs = cos_sin + static_cast<int64_t>(positions[t]) * DR;
+    const float c = cs[i], sn = cs[DR / 2 + i];
+    const float2 ab = __bfloat1622float2(*reinterpret_cast<const bf162*>(ckv + R + 2 * i));
+    *reinterpret_cast<bf162*>(dst + R + 2 * i) = __floats2bfloat162_rn(ab.x * c - ab.y * sn, ab.y * c + ab.x * sn);
+  }
+}
+
+// q: [T, h, NOPE + 64] -> q_rope [T, h, 64] = rope(q[..., NOPE:], position) (interleaved pairs), contiguous.
+__global__ void mla_q_rope_kernel(const bf16* __restrict__ q, int n_heads, int nope, const int32_t* __restrict__ positions,
+                                  const float* __restrict__ cos_sin, bf16* __restrict__ q_rope, int T) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;   // one rotated pair per thread
+  if (i >= static_cast<int64_t>(T) * n_heads * (DR / 2)) return;
+  const int pr = static_cast<int>(i % (DR / 2));
+  const int64_t th = i / (DR / 2);
+  const int t = static_cast<int>(th / n_heads);
+  const float* cs = cos_sin + static_cast<int64_t>(positions[t]) * DR;
+  const float c = cs[pr], sn = cs[DR / 2 + pr];
+  const float2 ab = __bfloat1622float2(*reinterpret_cast<const bf162*>(q + th * (nope + DR) + nope + 2 * pr));
+  *reinterpret_cast<bf162*>(q_rope + th * DR + 2 * pr) = __floats2bfloat162_rn(ab.x * c - ab.y * sn, ab.y * c + ab.x * sn);
+}
+
 template <int R>
 static int launch(const Params& p, int grid_x, cudaStream_t stream) {
   constexpr int LD = R + DR;
@@ -292,6 +387,32 @@ static int launch(const Params& p, int grid_x, cudaStream_t stream) {
 }  // namespace mb
 
 using namespace mb;
+
+extern "C" int mb_mla_post_down(const void* qkv_a, int ld, int q_lora, int R, const void* gamma_q, const void* gamma_kv,
+                                float eps, const int32_t* positions, const float* cos_sin, const int64_t* slots,
+                                void* q_a_out, void* cache, int T, int page_size, long long page_stride,
+                                cudaStream_t stream) {
+  if (T <= 0) return MB_OK;
+  if (R % 8 || q_lora % 8 || ld % 8 || page_stride % 8) return MB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(qkv_a) | reinterpret_cast<uintptr_t>(q_a_out) | reinterpret_cast<uintptr_t>(cache) |
+       reinterpret_cast<uintptr_t>(gamma_q) | reinterpret_cast<uintptr_t>(gamma_kv)) & 15)
+    return MB_ERR_ALIGN;
+  mla::mla_post_down_kernel<<<T, 256, 0, stream>>>(
+      static_cast<const mla::bf16*>(qkv_a), ld, q_lora, R, static_cast<const mla::bf16*>(gamma_q),
+      static_cast<const mla::bf16*>(gamma_kv), eps, positions, cos_sin, slots, static_cast<mla::bf16*>(q_a_out),
+      static_cast<mla::bf16*>(cache), page_size, page_stride);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+extern "C" int mb_mla_q_rope(const void* q, int n_heads, int nope, const int32_t* positions, const float* cos_sin,
+                             void* q_rope, int T, cudaStream_t stream) {
+  if (T <= 0) return MB_OK;
+  if (nope % 2) return MB_ERR_SHAPE;
+  const long long work = static_cast<long long>(T) * n_heads * (mla::DR / 2);
+  mla::mla_q_rope_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+      static_cast<const mla::bf16*>(q), n_heads, nope, positions, cos_sin, static_cast<mla::bf16*>(q_rope), T);
+  return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
 
 // T = total query tokens, B = sequences. kv_lora_rank R in {128, 256, 512}; rope width 64.
 extern "C" int mb_mla_paged_attention(const void* q_lat, const void* q_rope, void* out, const void* cache,

@@ -172,6 +172,7 @@ class DSLayer:
     w_uv: torch.Tensor               # [h, v_dim, kv_lora]  applied to the latent output  (N=v_dim, K=kv_lora)
     wo: object                       # [H, h * v_dim]
     mlp_norm: torch.Tensor
+    w_a: Optional[torch.Tensor] = None   # [q_lora + kv_lora + rope, H]: q_a and kv_a stacked (bf16 weights only)
     wgu: Optional[object] = None     # dense layers: [2 * inter, H]
     wd: Optional[object] = None      # dense layers: [H, inter]
     moe: Optional[MoE] = None
@@ -395,6 +396,13 @@ class DeepseekV3Model:
         max_position = max_position or min(cfg.max_position_embeddings, 1 << 17)
         self.cos_sin = cos_sin_table(cfg.qk_rope_head_dim, max_position, cfg.rope_theta,
                                      RopeScaling.from_hf(rs) if rs else None, self.device)
+        # q_a and kv_a read the same input: one GEMM over their stacked rows (the layer keeps views of the stack)
+        for l in weights.layers:
+            if getattr(l, "w_a", None) is None and torch.is_tensor(l.kv_a) and (l.q_a is None or torch.is_tensor(l.q_a)):
+                l.w_a = torch.cat([l.q_a, l.kv_a]) if l.q_a is not None else l.kv_a
+                if l.q_a is not None:
+                    ql = l.q_a.shape[0]
+                    l.q_a, l.kv_a = l.w_a[:ql], l.w_a[ql:]
         self.ep = ep
         self._ep_layers = {}
         if ep is not None:
@@ -483,8 +491,36 @@ class DeepseekV3Model:
         return logits[:n]
 
     # ------------------------------------------------------------ attention
+    def _attention_fused(self, li: int, l: DSLayer, x, positions, slots, block_table, q_start, q_len, kv_len):
+        """The CUDA path for bf16 attention weights: one down-projection GEMM, one kernel for both norms, the key
+        rotation and the cache store, per-head absorption GEMMs that address the heads in place (no transposes)."""
+        from .._native import lib
+
+        c, L = self.cfg, lib()
+        T, h, R = x.shape[0], c.num_attention_heads, c.kv_lora_rank
+        lin = ops.linear_decode if T <= ops.DECODE_GEMM_MAX_TOKENS else ops.linear
+        dev = x.device
+        cache = self.kv[:, 0, li, 0]
+        ql = c.q_lora_rank or 0
+        qkv_a = lin(x, l.w_a)
+        q_a = torch.empty(T, ql, dtype=x.dtype, device=dev) if ql else None
+        L.mla_post_down(qkv_a, ql, l.q_a_norm, l.kv_a_norm, c.rms_norm_eps, positions, self.cos_sin, slots, q_a, cache)
+        q = lin(q_a if ql else x, l.q_b)                                      # [T, h * (nope + rope)]
+        q_rope = torch.empty(T, h, c.qk_rope_head_dim, dtype=x.dtype, device=dev)
+        L.mla_q_rope(q, h, c.qk_nope_head_dim, positions, self.cos_sin, q_rope)
+        q_lat = torch.empty(T, h * R, dtype=x.dtype, device=dev)
+        ops.batched_linear_heads(q, l.w_uk, q_lat, c.qk_head_dim, R)          # absorb W_uk per head
+        o_lat = ops.mla_paged_attention(q_lat.view(T, h, R), q_rope, cache, block_table, q_start, q_len, kv_len,
+                                        self.scale)
+        o = torch.empty(T, h * c.v_head_dim, dtype=x.dtype, device=dev)
+        ops.batched_linear_heads(o_lat.view(T, h * R), l.w_uv, o, R, c.v_head_dim)   # apply W_uv per head
+        return o
+
     def _attention(self, li: int, l: DSLayer, x, positions, slots, block_table, q_start, q_len, kv_len):
         c = self.cfg
+        if (x.is_cuda and x.dtype == torch.bfloat16 and l.w_a is not None and torch.is_tensor(l.q_b)
+                and c.qk_rope_head_dim == 64 and positions.dtype == torch.int32):
+            return self._attention_fused(li, l, x, positions, slots, block_table, q_start, q_len, kv_len)
         T, h = x.shape[0], c.num_attention_heads
         if l.q_a is not None:
             q = _linear(ops.rms_norm(_linear(x, l.q_a), l.q_a_norm, c.rms_norm_eps), l.q_b)
@@ -519,17 +555,31 @@ class DeepseekV3Model:
 
     # ------------------------------------------------------------ step
     def _forward(self, tokens, positions, slots, block_table, q_start, q_len, kv_len, logit_rows) -> torch.Tensor:
-        c = self.cfg
+        c, eps = self.cfg, self.cfg.rms_norm_eps
+        layers = self.w.layers
         h = ops.embedding(tokens, self.w.embed)
-        for li, l in enumerate(self.w.layers):
-            x = ops.rms_norm(h, l.attn_norm, c.rms_norm_eps)
+        # decode-sized steps on the GPU use the GEMM that carries the residual add and the next norm in its tail
+        small = h.is_cuda and h.dtype == torch.bfloat16 and h.shape[0] <= ops.DECODE_GEMM_MAX_TOKENS
+        x = ops.rms_norm(h, layers[0].attn_norm, eps)
+        for li, l in enumerate(layers):
             a = self._attention(li, l, x, positions, slots, block_table, q_start, q_len, kv_len)
-            h = _linear(a, l.wo, residual=h)
-            x = ops.rms_norm(h, l.mlp_norm, c.rms_norm_eps)
-            h = (h.float() + self._mlp(li, l, x).float()).to(h.dtype) if not h.is_cuda else h + self._mlp(li, l, x)
-        last = h[logit_rows.long()]
-        xn = ops.rms_norm(last, self.w.final_norm, c.rms_norm_eps)
-        return ops.linear(xn, self.w.lm_head, out_dtype=torch.float32).float()
+            if small and torch.is_tensor(l.wo):
+                x, h = ops.linear_decode(a, l.wo, "add_norm", h=h, gamma=l.mlp_norm, eps=eps)
+            else:
+                h = _linear(a, l.wo, residual=h)
+                x = ops.rms_norm(h, l.mlp_norm, eps)
+            gamma_next = layers[li + 1].attn_norm if li + 1 < len(layers) else self.w.final_norm
+            if l.moe is None and small and torch.is_tensor(l.wgu):
+                x, h = ops.linear_decode(ops.linear_decode(x, l.wgu, "swiglu"), l.wd, "add_norm", h=h, gamma=gamma_next,
+                                         eps=eps)
+                continue
+            if li in self._ep_layers and h.is_cuda:
+                h = self._ep_layers[li](x, residual=h)            # the combine adds the residual
+            else:
+                y = self._mlp(li, l, x)
+                h = (h.float() + y.float()).to(h.dtype) if not h.is_cuda else h + y
+            x = ops.rms_norm(h, gamma_next, eps)
+        return ops.linear(x[logit_rows.long()], self.w.lm_head, out_dtype=torch.float32).float()
 
 
 def hf_reference_forward(cfg: DeepseekV3Config, sd: dict, tokens: torch.Tensor) -> torch.Tensor:

@@ -150,6 +150,8 @@ class MoE:
     def shared_forward(self, x):
         if self.shared_gate_up is None:
             return None
+        if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[0] <= ops.DECODE_GEMM_MAX_TOKENS:
+            return ops.linear_decode(ops.linear_decode(x, self.shared_gate_up, "swiglu"), self.shared_down)
         return ops.linear(ops.linear_swiglu(x, self.shared_gate_up), self.shared_down)
 
     def experts_forward(self, x, ids, w, shared_out=None):

@@ -83,6 +83,9 @@ def decode_gemm_workspace(device):
     return ws
 
 
+DECODE_GEMM_MAX_TOKENS = 256      # the decode-step GEMM takes at most this many token rows
+
+
 def linear_decode(x, w, mode="plain", out=None, h=None, gamma=None, eps=1e-5, weight_offset=0.0,
                   multiply_before_cast=False, xn=None, tp=None):
     """Decode-step GEMM (at most 256 token rows) with its fused tail.
@@ -113,6 +116,23 @@ def linear_decode(x, w, mode="plain", out=None, h=None, gamma=None, eps=1e-5, we
         n = w.shape[0] // 2 if code == 1 else w.shape[0]
         out = torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
     _lib().gemm_dec(x, w, code, out, None, None, None, 0.0, 0.0, False, 1, 0, [], 0, ws, state)
+    return out
+
+
+def batched_linear_heads(x, w, out, x_off, y_off):
+    """``out[m, b * y_off + n] = sum_k x[m, b * x_off + k] * w[b, n, k]``: per-head products that address the heads
+    as column blocks of ``x`` and ``out`` (no transposes). At most 256 rows with N % 128 == 0 run as one persistent
+    launch of the decode-step GEMM, everything else on the tiled GEMM with the head as a grid dimension."""
+    if not x.is_cuda:
+        B, N, K = w.shape
+        for b in range(B):
+            out[:, b * y_off: b * y_off + N] = ref.linear(x[:, b * x_off: b * x_off + K], w[b])
+        return out
+    if x.shape[0] <= DECODE_GEMM_MAX_TOKENS and w.shape[1] % 128 == 0 and w.shape[2] % 64 == 0:
+        ws, state = decode_gemm_workspace(x.device)
+        _lib().gemm_dec_batched(x, w, out, x_off, y_off, ws, state)
+    else:
+        _lib().batched_gemm_bf16(x, w, out, x_off, y_off)
     return out
 
 

@@ -129,12 +129,15 @@ class EPContext:
         return xp, self.offsets, send_pos
 
     def combine(self, out_sorted: torch.Tensor, ids: torch.Tensor, send_pos: torch.Tensor, w: torch.Tensor,
-                shared: Optional[torch.Tensor]) -> torch.Tensor:
+                shared: Optional[torch.Tensor], residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Expert outputs back to their tokens and the weighted sum (+ shared experts, + ``residual``, which is
+        then also the output: the layer's residual add happens here)."""
         L, W = _lib(), self.world
         L.ep_combine_send(W, self.rank, self.ret_x.peer_ptrs, self.flags.peer_ptrs, out_sorted, self.order,
                           self.n_rows, self.step_cap)
-        y = torch.empty(ids.shape[0], self.hidden, dtype=torch.bfloat16, device=out_sorted.device)
-        L.ep_combine_reduce(self.ret_x.tensor, ids, send_pos, w, shared, y, self.e_local, self.step_cap)
+        y = residual if residual is not None else torch.empty(ids.shape[0], self.hidden, dtype=torch.bfloat16,
+                                                              device=out_sorted.device)
+        L.ep_combine_reduce(self.ret_x.tensor, ids, send_pos, w, shared, y, self.e_local, self.step_cap, residual)
         return y
 
 
@@ -157,11 +160,16 @@ class EPMoE:
             return 0
         return int((self.ep.send_pos[: self.ep.last_pairs] < 0).sum().item())
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``moe(x)``, or ``residual + moe(x)`` written into ``residual`` when one is given."""
         moe, cfg = self.moe, self.moe.cfg
         ids, w = route(moe.router_logits(x), moe.bias, cfg)
         if not x.is_cuda:
-            return self._forward_host(x, ids, w, moe.shared_forward(x))
+            y = self._forward_host(x, ids, w, moe.shared_forward(x))
+            if residual is None:
+                return y
+            residual.copy_((residual.float() + y.float()).to(residual.dtype))
+            return residual
         ep = self.ep
         # the shared experts need no exchange: they run on a side stream while the rows travel (reference:
         # nn/moe/expert_parallel.py:247-300 issues the shared expert between dispatch and its wait)
@@ -181,7 +189,7 @@ class EPMoE:
                         expected_rows=ep.step_tokens * cfg.num_experts_per_tok // self.e_local + 1)
         if shared is not None:
             torch.cuda.current_stream().wait_stream(ep.side)
-        return ep.combine(out, ids, send_pos, w.contiguous(), shared)
+        return ep.combine(out, ids, send_pos, w.contiguous(), shared, residual)
 
     __call__ = forward
 

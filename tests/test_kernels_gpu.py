@@ -422,6 +422,63 @@ def test_ep_recv_compact_sorts_received_rows_by_expert(fp8, world, cap, E, count
         assert torch.equal(xq[:total].view(torch.uint8).view(total, -1), rows)
 
 
+@pytest.mark.parametrize("T,B,N,K,x_off,y_off", [(40, 8, 512, 128, 192, 512), (300, 16, 128, 512, 512, 128),
+                                                 (1, 4, 64, 64, 64, 64), (2176, 4, 256, 128, 192, 300 - 300 % 8),
+                                                 (32, 128, 512, 128, 192, 512), (32, 128, 128, 512, 512, 128),
+                                                 (256, 16, 128, 64, 64, 136), (300, 128, 512, 128, 192, 512)])
+def test_batched_gemm_addresses_heads_in_place(T, B, N, K, x_off, y_off):
+    from modular_b200._native import lib
+
+    torch.manual_seed(27)
+    x = torch.randn(T, B * x_off + 8, device=DEV, dtype=torch.bfloat16)[:, : B * x_off]      # a strided view
+    w = (torch.randn(B, N, K, device=DEV) * 0.1).to(torch.bfloat16)
+    y = torch.full((T, B * y_off), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.batched_linear_heads(x, w, y, x_off, y_off)        # the decode-step GEMM up to 256 rows when N % 128 == 0
+    xs = torch.stack([x[:, b * x_off: b * x_off + K] for b in range(B)]).float()              # [B, T, K]
+    want = torch.einsum("btk,bnk->tbn", xs, w.float())
+    got = y.view(T, B, y_off)
+    assert _rel_err(got[:, :, :N], want) < 1e-2
+    if y_off > N:
+        assert torch.all(got[:, :, N:] == 7.0)            # columns between the heads' blocks are not touched
+
+
+@pytest.mark.parametrize("T,QL", [(37, 1536), (300, 0), (1, 256)])
+def test_mla_post_down_matches_composed_ops(T, QL):
+    """Norms of both down-projections, key rotation and the latent-cache store in one launch."""
+    from modular_b200._native import lib
+    from modular_b200.nn.rotary_embedding import cos_sin_table
+
+    torch.manual_seed(28)
+    R, page, pages = 512, 16, 40
+    qkv = torch.randn(T, QL + R + 64 + 8, device=DEV, dtype=torch.bfloat16)[:, : QL + R + 64]
+    gq = (1 + 0.1 * torch.randn(max(QL, 8), device=DEV)).to(torch.bfloat16)
+    gkv = (1 + 0.1 * torch.randn(R, device=DEV)).to(torch.bfloat16)
+    cs = cos_sin_table(64, 4096, 10000.0, None, DEV)
+    pos = torch.randint(0, 4096, (T,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(page * pages, device=DEV)[:T].long()
+    slots[T // 2] = -1
+    cache = torch.zeros(pages, page, R + 64, device=DEV, dtype=torch.bfloat16)
+    q_a = torch.zeros(T, QL, device=DEV, dtype=torch.bfloat16) if QL else None
+    lib().mla_post_down(qkv, QL, gq[:QL] if QL else None, gkv, 1e-6, pos, cs, slots, q_a, cache)
+    want = torch.zeros_like(cache)
+    c_kv = ops.rms_norm(qkv[:, QL:QL + R].contiguous(), gkv, 1e-6)
+    csp = cs[pos.long()]
+    k_rope = ref.apply_rope(qkv[:, QL + R:].unsqueeze(1), csp[:, :32], csp[:, 32:], True).squeeze(1)
+    ops.mla_kv_store(c_kv, k_rope, slots, want)
+    assert torch.equal(cache[..., :R], want[..., :R])
+    # the rotation contracts its multiply-adds differently from the op-by-op form: one bf16 ulp at most
+    assert torch.allclose(cache[..., R:].float(), want[..., R:].float(), rtol=8e-3, atol=1e-3)
+    if QL:
+        assert torch.equal(q_a, ops.rms_norm(qkv[:, :QL].contiguous(), gq[:QL], 1e-6))
+    # the query side: rotate the trailing 64 values of every head into a contiguous tensor
+    h, nope = 8, 128
+    q = torch.randn(T, h, nope + 64, device=DEV, dtype=torch.bfloat16)
+    q_rope = torch.zeros(T, h, 64, device=DEV, dtype=torch.bfloat16)
+    lib().mla_q_rope(q, h, nope, pos, cs, q_rope)
+    assert torch.allclose(q_rope.float(), ref.apply_rope(q[..., nope:], csp[:, :32], csp[:, 32:], True).float(),
+                          rtol=8e-3, atol=1e-3)
+
+
 # ---------------------------------------------------------------------------- decode-step GEMM
 @pytest.mark.parametrize("M,N,K", [(64, 6144, 4096), (64, 4096, 4096), (64, 4096, 14336), (1, 8192, 8192),
                                    (16, 1024, 1024), (100, 4096, 512), (256, 4096, 1792), (33, 1536, 4160),
