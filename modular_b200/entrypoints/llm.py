@@ -61,7 +61,9 @@ class LLM:
                  tp_rank: int = 0, host_kvcache_swap_space_gb: float = 0.0,
                  disk_kvcache_dir: Optional[str] = None, disk_kvcache_space_gb: float = 0.0,
                  step_token_alignment: Optional[int] = None, weights_are_sharded: bool = False,
-                 ep_size: int = 1, ep_rank: int = 0, ep_fp8_dispatch: bool = False):
+                 ep_size: int = 1, ep_rank: int = 0, ep_fp8_dispatch: bool = False, speculative=None):
+        """``speculative``: a :class:`pipelines.speculative.SpeculativeConfig`; decode steps of greedy requests
+        then verify n-gram proposals (several tokens per step, same output as plain greedy decoding)."""
         from ..models import family_for
 
         fam = family_for(model_config)
@@ -136,16 +138,18 @@ class LLM:
             extra["ep"] = EPContext(self.tp, c.hidden_size, c.n_routed_experts, c.num_experts_per_tok,
                                     max_tokens=max_batch_input_tokens, fp8_dispatch=ep_fp8_dispatch,
                                     host_group=dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=300)))
+        # verification asks for the logits of every draft position: size the model's logit rows for it
+        spec_rows = (speculative.num_speculative_tokens + 1) if speculative is not None else 1
         self.model = fam.model_class(model_config, weights, self.kv.kv, max_tokens=max_batch_input_tokens,
-                                     max_seqs=max_batch_size, max_position=max_length, **extra)
+                                     max_seqs=max_batch_size * spec_rows, max_position=max_length, **extra)
         overlap = on_gpu if enable_overlap_scheduler is None else enable_overlap_scheduler
-        overlap = overlap and bool(getattr(self.model, "use_executor", False))
+        overlap = overlap and bool(getattr(self.model, "use_executor", False)) and speculative is None
         if graph_batch_sizes is None:
             graph_batch_sizes = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch_size]
         self.pipeline = TextGenerationPipeline(
             self.model, self.kv, max_batch_input_tokens, max_batch_size, overlap=overlap,
             graph_batch_sizes=graph_batch_sizes if (device_graph_capture and on_gpu) else (),
-            eos_token_ids=eos_token_ids)
+            eos_token_ids=eos_token_ids, speculative=speculative)
         if device_graph_capture and on_gpu:
             self.pipeline.warmup_graph_capture()
             if hasattr(self.model, "capture_decode_graphs"):

@@ -119,16 +119,21 @@ def linear_decode(x, w, mode="plain", out=None, h=None, gamma=None, eps=1e-5, we
     return out
 
 
+HEADS_ON_DECODE_GEMM = False
+
+
 def batched_linear_heads(x, w, out, x_off, y_off):
     """``out[m, b * y_off + n] = sum_k x[m, b * x_off + k] * w[b, n, k]``: per-head products that address the heads
-    as column blocks of ``x`` and ``out`` (no transposes). At most 256 rows with N % 128 == 0 run as one persistent
-    launch of the decode-step GEMM, everything else on the tiled GEMM with the head as a grid dimension."""
+    as column blocks of ``x`` and ``out`` (no transposes). Runs on the tiled GEMM with the head as a grid dimension;
+    ``HEADS_ON_DECODE_GEMM`` moves steps of at most 256 rows (N % 128 == 0) to one persistent launch of the
+    decode-step GEMM instead (measured slower on B200 inside a CUDA graph: 14.8 vs 10.4 us for 128 heads of
+    [32, 128] x [128, 512], 9.8 vs 4.6 us for [32, 512] x [512, 128])."""
     if not x.is_cuda:
         B, N, K = w.shape
         for b in range(B):
             out[:, b * y_off: b * y_off + N] = ref.linear(x[:, b * x_off: b * x_off + K], w[b])
         return out
-    if x.shape[0] <= DECODE_GEMM_MAX_TOKENS and w.shape[1] % 128 == 0 and w.shape[2] % 64 == 0:
+    if HEADS_ON_DECODE_GEMM and x.shape[0] <= DECODE_GEMM_MAX_TOKENS and w.shape[1] % 128 == 0 and w.shape[2] % 64 == 0:
         ws, state = decode_gemm_workspace(x.device)
         _lib().gemm_dec_batched(x, w, out, x_off, y_off, ws, state)
     else:

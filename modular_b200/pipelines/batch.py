@@ -25,18 +25,19 @@ from .context import FUTURE_TOKEN, TextContext
 
 # arrays in the packed buffer; (name, words per element, per-"T" | per-"B" | per-"tile" | "bt")
 _FIELDS = [
-    ("tokens", 2, "T"), ("slots", 2, "T"), ("seeds", 2, "B"),
+    ("tokens", 2, "T"), ("slots", 2, "T"), ("seeds", 2, "R"),
     ("positions", 1, "T"), ("future_src", 1, "T"),
     ("q_start", 1, "B"), ("q_len", 1, "B"), ("kv_len", 1, "B"), ("decode_seq", 1, "B"),
-    ("logit_rows", 1, "B"), ("temperature", 1, "B"), ("top_k", 1, "B"), ("top_p", 1, "B"),
-    ("min_p", 1, "B"), ("tile_seq", 1, "tile"), ("tile_q0", 1, "tile"), ("block_table", 1, "bt"),
+    ("logit_rows", 1, "R"), ("temperature", 1, "R"), ("top_k", 1, "R"), ("top_p", 1, "R"),
+    ("min_p", 1, "R"), ("tile_seq", 1, "tile"), ("tile_q0", 1, "tile"), ("block_table", 1, "bt"),
 ]
 
 
-def meta_layout(T_cap: int, B_cap: int, bt_stride: int, tiles_cap: int):
-    """Offsets (in int32 words) of every array for the given capacities."""
+def meta_layout(T_cap: int, B_cap: int, bt_stride: int, tiles_cap: int, rows_cap: int = 0):
+    """Offsets (in int32 words) of every array for the given capacities. ``rows_cap``: rows that can ask for
+    logits (one per sequence unless draft tokens are verified, then one per token)."""
     sizes = {"T": max(T_cap, 1), "B": max(B_cap, 1), "tile": max(tiles_cap, 1),
-             "bt": max(B_cap, 1) * max(bt_stride, 1)}
+             "R": max(rows_cap, B_cap, 1), "bt": max(B_cap, 1) * max(bt_stride, 1)}
     off, cur = {}, 0
     for name, words, kind in _FIELDS:
         if words == 2 and cur % 2:
@@ -72,14 +73,15 @@ class StepBatch:
 
 class BatchPacker:
     def __init__(self, n_q: int, n_kv: int, page_size: int, max_tokens: int, max_seqs: int,
-                 max_pages_per_seq: int, device="cpu", n_staging: int = 4):
+                 max_pages_per_seq: int, device="cpu", n_staging: int = 4, max_logit_rows: int = 0):
         self.n_q, self.n_kv, self.page_size = n_q, n_kv, page_size
         self.max_tokens, self.max_seqs, self.max_pages = max_tokens, max_seqs, max_pages_per_seq
         self.device = torch.device(device)
         G = n_q // n_kv
         self.tok_per_tile = max(1, 64 // G)
         tiles_cap = max_tokens // self.tok_per_tile + max_seqs + 1
-        _, words = meta_layout(max_tokens, max_seqs, max_pages_per_seq, tiles_cap)
+        self.max_logit_rows = max(max_logit_rows, max_seqs)
+        _, words = meta_layout(max_tokens, max_seqs, max_pages_per_seq, tiles_cap, self.max_logit_rows)
         self.capacity_words = words
         pin = self.device.type == "cuda"
         self._staging = [torch.empty(words, dtype=torch.int32, pin_memory=pin) for _ in range(n_staging)]
@@ -97,11 +99,14 @@ class BatchPacker:
         return i
 
     def pack(self, ctxs: Sequence[TextContext], kv, fixed: Optional[tuple] = None,
-             pad_to: int = 0) -> StepBatch:
+             pad_to: int = 0, all_logits: bool = False) -> StepBatch:
         """Build the metadata for ``ctxs`` (each contributes its active window).
 
         ``fixed = (T_cap, B_cap, bt_stride, tiles_cap)`` pins the layout (CUDA-graph replay);
-        ``pad_to`` pads the batch with dummy single-token sequences on the null page.
+        ``pad_to`` pads the batch with dummy single-token sequences on the null page;
+        ``all_logits`` asks for the logits of every row of a window that reaches the last known token
+        (verification of draft tokens), not only of its last row: the per-row sampling arrays are then laid
+        out for one entry per token.
         """
         B_real = len(ctxs)
         B = max(B_real, pad_to)
@@ -115,7 +120,9 @@ class BatchPacker:
         tile_seq, tile_q0, decode_seq = build_attention_plan(q_lens, self.n_q, self.n_kv)
         if fixed is None:
             bt_stride = max([len(kv.blocks_of(c.request_id)) for c in ctxs] + [1])
-            off, words = meta_layout(T, B, bt_stride, len(tile_seq))
+            if all_logits and T > self.max_logit_rows:
+                raise ValueError(f"{T} rows ask for logits; the pipeline was built for {self.max_logit_rows}")
+            off, words = meta_layout(T, B, bt_stride, len(tile_seq), T if all_logits else 0)
         else:
             T_cap, B_cap, bt_stride, tiles_cap = fixed
             off, words = meta_layout(T_cap, B_cap, bt_stride, tiles_cap)
@@ -132,12 +139,13 @@ class BatchPacker:
         q_len = sb.arr("q_len", np.int32, B)
         kv_len = sb.arr("kv_len", np.int32, B)
         bt = sb.arr("block_table", np.int32, B * bt_stride).reshape(B, bt_stride)
-        logit_rows = sb.arr("logit_rows", np.int32, B)
-        temperature = sb.arr("temperature", np.float32, B)
-        top_k = sb.arr("top_k", np.int32, B)
-        top_p = sb.arr("top_p", np.float32, B)
-        min_p = sb.arr("min_p", np.float32, B)
-        seeds = sb.arr("seeds", np.int64, B)
+        n_rows_cap = max(B, T) if all_logits else B
+        logit_rows = sb.arr("logit_rows", np.int32, n_rows_cap)
+        temperature = sb.arr("temperature", np.float32, n_rows_cap)
+        top_k = sb.arr("top_k", np.int32, n_rows_cap)
+        top_p = sb.arr("top_p", np.float32, n_rows_cap)
+        min_p = sb.arr("min_p", np.float32, n_rows_cap)
+        seeds = sb.arr("seeds", np.int64, n_rows_cap)
 
         q_len[:] = q_lens
         q_start[0] = 0
@@ -169,16 +177,17 @@ class BatchPacker:
             if tb.active_end == len(tb):
                 # the window reaches the last known token: this pass produces a new token
                 sp = c.sampling_params
-                logit_rows[n_logits] = row + n - 1
-                temperature[n_logits] = 0.0 if sp.is_greedy else sp.temperature
-                top_k[n_logits] = sp.top_k if sp.top_k > 0 else 0
-                top_p[n_logits] = sp.top_p
-                min_p[n_logits] = sp.min_p
-                seeds[n_logits] = sp.seed * 1000003 + c.seq
+                for r in (range(row, row + n) if all_logits else (row + n - 1,)):
+                    logit_rows[n_logits] = r
+                    temperature[n_logits] = 0.0 if sp.is_greedy else sp.temperature
+                    top_k[n_logits] = sp.top_k if sp.top_k > 0 else 0
+                    top_p[n_logits] = sp.top_p
+                    min_p[n_logits] = sp.min_p
+                    seeds[n_logits] = sp.seed * 1000003 + c.seq
+                    sb.logit_ctx.append(c)
+                    n_logits += 1
                 if not sp.is_greedy:
                     sb.all_greedy = False
-                sb.logit_ctx.append(c)
-                n_logits += 1
             row += n
         # dummy padding sequences: one token each on the null page, logits wanted (graph shape)
         for i in range(B_real, B):

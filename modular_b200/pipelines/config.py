@@ -112,7 +112,7 @@ class LoRAConfig(ConfigFileModel):
 
 
 class SpeculativeConfig(ConfigFileModel):
-    speculative_method: Optional[str] = None        # eagle | mtp | standalone
+    speculative_method: Optional[str] = None        # ngram (served); eagle | mtp | standalone are accepted names only
     num_speculative_tokens: int = 0
     draft_model_path: Optional[str] = None
 

@@ -154,6 +154,14 @@ class TokenBuffer:
     def set_token(self, index: int, token: int) -> None:
         self._arr[index] = token
 
+    def truncate(self, length: int) -> None:
+        """Drop tokens past ``length`` (tentative draft tokens that were not accepted)."""
+        if length < self.prompt_len or length > self._len:
+            raise ValueError("truncate: length out of range")
+        self._len = length
+        self.active_end = min(self.active_end, length)
+        self.processed = min(self.processed, length)
+
     def reset(self) -> None:
         """Forget cache state (after preemption): everything becomes one prompt again."""
         self.processed = 0

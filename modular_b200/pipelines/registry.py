@@ -166,7 +166,8 @@ class PipelineRegistry:
                   host_kvcache_swap_space_gb=m.kv_cache.host_kvcache_swap_space_gb,
                   disk_kvcache_dir=m.kv_cache.disk_kvcache_dir,
                   disk_kvcache_space_gb=m.kv_cache.disk_kvcache_space_gb,
-                  tp_size=tp_size, tp_rank=tp_rank, weights_are_sharded=sharded)
+                  tp_size=tp_size, tp_rank=tp_rank, weights_are_sharded=sharded,
+                  speculative=_speculative_from(pc))
         llm.tokenizer = tokenizer
         if pc.sampling.enable_structured_output:
             llm.pipeline.enable_structured_output(tokenizer)
@@ -176,6 +177,20 @@ class PipelineRegistry:
 
 
 PIPELINE_REGISTRY = PipelineRegistry()
+
+
+def _speculative_from(pc):
+    """The engine's speculative-decoding settings from the pipeline config (``--speculative-method ngram``; the
+    reference's ``standalone`` / ``eagle`` / ``mtp`` draft-model methods are not served by this loop)."""
+    sc = pc.speculative
+    if not sc.speculative_method:
+        return None
+    if sc.speculative_method != "ngram":
+        raise ValueError(f"speculative method {sc.speculative_method!r} is not available in the serving loop "
+                         "(ngram is; draft models run through pipelines.speculative.SpeculativeDecoder)")
+    from .speculative import SpeculativeConfig as EngineSpec
+
+    return EngineSpec(method="ngram", num_speculative_tokens=sc.num_speculative_tokens or 4)
 
 
 def _register_builtin() -> None:

@@ -57,14 +57,21 @@ class NgramProposer:
 
     def propose(self, history: Sequence[int], k: int):
         """Draft tokens (possibly fewer than k, possibly none) and None for their probabilities."""
-        h = list(history)
+        import numpy as np
+
+        h = np.asarray(history, dtype=np.int64).reshape(-1)
+        if k <= 0:
+            return [], None
         for n in range(min(self.cfg.ngram_max, len(h) - 1), self.cfg.ngram_min - 1, -1):
-            tail = h[-n:]
-            for start in range(len(h) - n - 1, -1, -1):     # most recent earlier occurrence
-                if h[start:start + n] == tail:
-                    cont = h[start + n:start + n + k]
-                    if cont:
-                        return cont, None
+            # the most recent earlier occurrence of the last n tokens (vectorised: the serving loop calls this
+            # for every request of every decode step)
+            win = np.lib.stride_tricks.sliding_window_view(h[:-1], n)
+            hits = np.flatnonzero((win == h[-n:]).all(axis=1))
+            if hits.size:
+                start = int(hits[-1])
+                cont = h[start + n:start + n + k]
+                if cont.size:
+                    return [int(t) for t in cont], None
         return [], None
 
     def observe(self, accepted_len: int) -> None:       # nothing to roll back

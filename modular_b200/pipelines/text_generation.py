@@ -52,23 +52,38 @@ class PipelineStats:
 class TextGenerationPipeline:
     def __init__(self, model, kv_manager: PagedKVCacheManager, max_batch_tokens: int = 8192,
                  max_batch_size: int = 256, overlap: bool = False, graph_batch_sizes: Sequence[int] = (),
-                 eos_token_ids: Sequence[int] = ()):
+                 eos_token_ids: Sequence[int] = (), speculative=None):
+        """``speculative``: a :class:`speculative.SpeculativeConfig` turns decode steps of greedy requests into
+        propose-and-verify steps (the step runs synchronously: the proposals need the previous token values)."""
         self.model = model
         self.kv = kv_manager
         self.device = model.device
         self.on_gpu = self.device.type == "cuda"
         # overlap scheduling needs the native step (future tokens are realised on the device)
-        self.overlap = overlap and self.on_gpu and bool(getattr(model, "use_executor", False))
+        self.overlap = overlap and self.on_gpu and bool(getattr(model, "use_executor", False)) and speculative is None
         self.eos_token_ids = frozenset(eos_token_ids)
         cfg = model.cfg
+        self.spec = speculative
+        self.spec_stats = None
+        self.proposer = None
+        rows = max_batch_size
+        if speculative is not None:
+            from .speculative import NgramProposer, SpecStats
+
+            if speculative.method != "ngram":
+                raise ValueError("the serving loop verifies n-gram (prompt lookup) proposals; draft-model proposals "
+                                 "run through speculative.SpeculativeDecoder")
+            self.proposer = NgramProposer(speculative)
+            self.spec_stats = SpecStats()
+            rows = min(max_batch_size * (speculative.num_speculative_tokens + 1), getattr(model, "max_seqs", 1 << 30))
         self.packer = BatchPacker(cfg.num_attention_heads, cfg.num_key_value_heads, kv_manager.page_size,
                                   max_batch_tokens, max_batch_size, kv_manager.max_pages_per_seq,
-                                  device=self.device)
+                                  device=self.device, max_logit_rows=rows)
         self.stats = PipelineStats()
         self._pending: Optional[_InFlight] = None
         self._step = 0
         self._graphs: dict[int, tuple] = {}
-        self._d2h = [torch.empty(max_batch_size, dtype=torch.long, pin_memory=self.on_gpu) for _ in range(4)]
+        self._d2h = [torch.empty(rows, dtype=torch.long, pin_memory=self.on_gpu) for _ in range(4)]
         self._d2h_i = 0
         self.graph_batch_sizes = tuple(sorted(set(int(b) for b in graph_batch_sizes)))
         self._cpu_gen = torch.Generator().manual_seed(0)
@@ -329,9 +344,92 @@ class TextGenerationPipeline:
             out[c.request_id] = c.to_generation_output()
         return out
 
+    # ------------------------------------------------------------ speculative decoding
+    def _spec_eligible(self, batch: Sequence[TextContext]) -> bool:
+        """Propose-and-verify applies to decode-only steps whose requests are greedy and need nothing per token
+        that the verification pass does not provide (masks, penalties, log-probabilities, adapters)."""
+        for c in batch:
+            sp = c.sampling_params
+            if (c.tokens.active_length != 1 or c.needs_ce or c.pending_future or not sp.is_greedy
+                    or sp.response_format is not None or sp.logprobs or sp.needs_penalties or c.lora_name):
+                return False
+        return True
+
+    def _speculative_step(self, batch: Sequence[TextContext]) -> dict:
+        """One propose-and-verify step (reference: pipelines/lib/pipeline_variants/overlap_text_generation.py:306,
+        nn/sampling/rejection_sampler.py:121 greedy acceptance). Every request brings its last token plus up to k
+        draft tokens; the target model scores all of them in one ragged pass; the longest prefix of drafts that
+        equals the target's own greedy choice is accepted together with one more token. The output is exactly
+        that of plain greedy decoding."""
+        k = self.spec.num_speculative_tokens
+        budget = self.packer.max_tokens - len(batch)          # rows left for drafts in this step
+        rows_left = self.packer.max_logit_rows - len(batch)
+        base_len, drafts = [], []
+        for c in batch:
+            tb = c.tokens
+            room = min(k, c.max_new_tokens_effective - tb.generated_length - 1, c.max_length - len(tb) - 1,
+                       budget, rows_left)
+            d = self.proposer.propose(tb.all, room)[0] if room > 0 else []
+            while d and not self.kv.can_alloc(c, len(d)):
+                d = d[:-1]
+            base_len.append(len(tb))
+            drafts.append(d)
+            budget -= len(d)
+            rows_left -= len(d)
+            for t in d:                                        # tentative: rolled back below
+                tb.advance_with_token(int(t))
+            tb.active_end = len(tb)
+            self.kv.alloc(c)
+        self._step += 1
+        self.stats.steps += 1
+        sb = self.packer.pack(batch, self.kv, all_logits=True)
+        if self.on_gpu and self.model.use_executor:
+            meta = self.packer.upload(sb)
+            self.model.forward_packed(meta, sb.offsets, sb.T, sb.B, sb.bt_stride, sb.n_tiles, sb.n_decode, sb.n_logits,
+                                      False, True, self._step)
+            self.stats.h2d_bytes += sb.words * 4
+            self.stats.d2h_bytes += sb.n_logits * 8
+            vals = self.model.sampled[: sb.n_logits].cpu().numpy()
+        else:
+            t = BatchPacker.tensors(sb, self.device)
+            logits = self.model.forward_tensors(t["tokens"], t["positions"], t["slots"], t["block_table"], t["q_start"],
+                                                t["q_len"], t["kv_len"], t["logit_rows"])
+            vals = ops.argmax(logits).cpu().numpy()
+        self.stats.tokens_in += sb.T
+        out: dict[str, TextGenerationOutput] = {}
+        row = 0
+        st = self.spec_stats
+        for c, d, L in zip(batch, drafts, base_len):
+            n = len(d) + 1
+            target = vals[row: row + n]
+            row += n
+            acc = 0
+            while acc < len(d) and int(d[acc]) == int(target[acc]):
+                acc += 1
+            tb = c.tokens
+            tb.truncate(L)                                     # drop the drafts ...
+            for j in range(acc + 1):                           # ... and append what the target chose
+                c.update(int(target[j]))
+                self.stats.tokens_out += 1
+                st.emitted += 1
+                if c.is_done:
+                    break
+            # the cache holds the last token and the accepted drafts; the newest token is the next window
+            tb.processed = len(tb) - 1
+            tb.active_end = len(tb)
+            st.steps += 1
+            st.proposed += len(d)
+            st.accepted += acc
+            if self.kv.contains(c.request_id):
+                self.kv.step(c)
+            out[c.request_id] = c.to_generation_output()
+        return out
+
     def execute(self, batch: Sequence[TextContext]) -> dict:
         """Run one step. Synchronous mode returns this step's outputs; overlap mode returns the
         previous step's (call with an empty batch to drain)."""
+        if batch and self.spec is not None and self._spec_eligible(batch):
+            return self._speculative_step(batch)
         constrained = self._prepare_grammars(batch) if batch else False
         if batch and self.lora_manager is not None and any(c.lora_name for c in batch):
             constrained = True      # adapter steps run synchronously on real token values

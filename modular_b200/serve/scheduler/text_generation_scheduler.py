@@ -47,6 +47,10 @@ class BatchMetrics:
     cache_miss_tokens: int = 0
     used_host_kv_pct: float = 0.0
     used_disk_kv_pct: float = 0.0
+    spec_steps: int = 0              # propose-and-verify passes of this step (one per request)
+    spec_proposed: int = 0
+    spec_accepted: int = 0
+    spec_emitted: int = 0
 
     def to_dict(self) -> dict:
         """Flat form for the telemetry queue (keys as :func:`serve.telemetry.metrics.record_batch_metrics` reads them)."""
@@ -81,6 +85,7 @@ class TokenGenerationScheduler:
         self._contexts: dict[str, TextContext] = {}
         self.total_steps = 0
         self._cache_seen = (0, 0)        # (hit tokens, queried tokens) already reported
+        self._spec_seen = (0, 0, 0, 0)   # speculative-decoding counters already reported
         # requests with task == "embed" are answered by an embeddings scheduler when the model can encode
         self.embeddings = None
         model = getattr(pipeline, "model", None)
@@ -190,6 +195,11 @@ class TokenGenerationScheduler:
             if tiers is not None:
                 m.used_host_kv_pct = getattr(tiers, "host_used_pct", 0.0)
                 m.used_disk_kv_pct = getattr(tiers, "disk_used_pct", 0.0)
+        ss = getattr(self.pipeline, "spec_stats", None)
+        if ss is not None:
+            now = (ss.steps, ss.proposed, ss.accepted, ss.emitted)
+            m.spec_steps, m.spec_proposed, m.spec_accepted, m.spec_emitted = (a - b for a, b in zip(now, self._spec_seen))
+            self._spec_seen = now
         self.last_metrics = m
         if self.metrics_sink is not None:
             self.metrics_sink(m)

@@ -433,13 +433,22 @@ def test_batched_gemm_addresses_heads_in_place(T, B, N, K, x_off, y_off):
     x = torch.randn(T, B * x_off + 8, device=DEV, dtype=torch.bfloat16)[:, : B * x_off]      # a strided view
     w = (torch.randn(B, N, K, device=DEV) * 0.1).to(torch.bfloat16)
     y = torch.full((T, B * y_off), 7.0, device=DEV, dtype=torch.bfloat16)
-    ops.batched_linear_heads(x, w, y, x_off, y_off)        # the decode-step GEMM up to 256 rows when N % 128 == 0
+    ops.batched_linear_heads(x, w, y, x_off, y_off)
     xs = torch.stack([x[:, b * x_off: b * x_off + K] for b in range(B)]).float()              # [B, T, K]
     want = torch.einsum("btk,bnk->tbn", xs, w.float())
     got = y.view(T, B, y_off)
     assert _rel_err(got[:, :, :N], want) < 1e-2
     if y_off > N:
         assert torch.all(got[:, :, N:] == 7.0)            # columns between the heads' blocks are not touched
+    if T <= 256 and N % 128 == 0 and K % 64 == 0:
+        # the same product as one persistent launch of the decode-step GEMM
+        y2 = torch.full_like(y, 7.0)
+        ops.HEADS_ON_DECODE_GEMM = True
+        try:
+            ops.batched_linear_heads(x, w, y2, x_off, y_off)
+        finally:
+            ops.HEADS_ON_DECODE_GEMM = False
+        assert _rel_err(y2.view(T, B, y_off)[:, :, :N], want) < 1e-2
 
 
 @pytest.mark.parametrize("T,QL", [(37, 1536), (300, 0), (1, 256)])

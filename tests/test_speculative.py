@@ -69,3 +69,67 @@ def test_generation_stops_at_the_cache_capacity():
     cache.step(list(range(16)), all_logits=False)
     with pytest.raises(ValueError):
         cache.step([1], all_logits=False)
+
+
+def _engine_tokens(spec, prompts, n, device="cpu", **kw):
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.pipelines.context import SamplingParams
+
+    cfg = Llama3Config.tiny(num_hidden_layers=2, vocab_size=64)
+    dtype = torch.float32 if device == "cpu" else torch.bfloat16
+    llm = LLM(cfg, device=device, dtype=dtype, max_length=160, max_batch_size=4, max_batch_input_tokens=64, page_size=16,
+              num_kv_pages=64, seed=5, speculative=spec, **kw)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=n, ignore_eos=True)
+    recs = llm.generate(prompts, sp)
+    return [list(r.tokens) for r in recs], llm
+
+
+def test_serving_loop_verifies_ngram_proposals_and_matches_plain_greedy():
+    """The engine with speculation on emits exactly the tokens of the engine without it, in fewer steps, through
+    the scheduler (chunked prefill, several requests per step, requests finishing at different times)."""
+    prompts = [[3, 4, 5, 3, 4, 5, 3, 4], [7, 7, 7, 7, 7], [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12] * 6, [9, 8]]
+    want, plain = _engine_tokens(None, prompts, 40)
+    got, spec = _engine_tokens(SpeculativeConfig("ngram", 4), prompts, 40)
+    assert got == want
+    st = spec.pipeline.spec_stats
+    assert st.emitted == 4 * 40 - 4 and st.accepted > 0          # the first token of a request comes from its prefill
+    assert spec.pipeline.stats.steps < plain.pipeline.stats.steps
+    m = spec.scheduler.last_metrics
+    assert m.spec_steps >= 0 and "spec_accepted" in m.to_dict()
+
+
+def test_speculation_respects_token_limits_and_eos():
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.pipelines.context import SamplingParams
+
+    prompts = [[3, 4, 5, 3, 4, 5, 3, 4]]
+    want, _ = _engine_tokens(None, prompts, 23)
+    got, _ = _engine_tokens(SpeculativeConfig("ngram", 6), prompts, 23)
+    assert got == want and len(got[0]) == 23
+    eos = want[0][9]
+    cfg = Llama3Config.tiny(num_hidden_layers=2, vocab_size=64)
+    llm = LLM(cfg, device="cpu", dtype=torch.float32, max_length=160, max_batch_size=4, max_batch_input_tokens=64,
+              page_size=16, num_kv_pages=64, seed=5, speculative=SpeculativeConfig("ngram", 6), eos_token_ids=(eos,))
+    rec = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=23))[0]
+    assert list(rec.tokens) == want[0][: want[0].index(eos) + 1]
+
+
+import pytest
+
+
+@pytest.mark.gpu
+def test_serving_loop_speculation_on_gpu_follows_plain_greedy():
+    """On the GPU the verification pass scores k + 1 rows per request through the prefill kernels while plain
+    decoding uses the decode kernels: bf16 rounding can flip a near-tie, after which the two runs legitimately
+    differ. The common prefix must be long and speculation must accept drafts."""
+    prompts = [[3, 4, 5, 3, 4, 5, 3, 4], [7, 7, 7, 7, 7], [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12] * 6, [9, 8]]
+    want, _ = _engine_tokens(None, prompts, 40, device="cuda")
+    got, spec = _engine_tokens(SpeculativeConfig("ngram", 4), prompts, 40, device="cuda")
+    common = 0
+    for a, b in zip(want, got):
+        assert len(a) == len(b) == 40
+        n = next((i for i, (x, y) in enumerate(zip(a, b)) if x != y), 40)
+        common += n
+    assert common >= 0.6 * 160, (common, want, got)
+    st = spec.pipeline.spec_stats
+    assert st.accepted > 0 and st.emitted == 4 * 40 - 4
