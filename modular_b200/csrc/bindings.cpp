@@ -920,6 +920,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                "mla_decode_tc");
       return;
     }
+    // ragged steps with 512-wide latents and a multiple of 128 heads: the tensor-core kernel, one CTA pair per token
+    if (!decode_only && mb_mla_tc_usable(q_lat.size(0), q_lat.size(0), q_lat.size(1), q_lat.size(2), cache.size(1))) {
+      auto scratch = at::empty({2 * q_lat.size(0)}, q_start.options().dtype(at::kInt));
+      check_rc(mb_mla_prefill_tc(q_lat.data_ptr(), q_rope.data_ptr(), out.data_ptr(), cache.data_ptr(),
+                                 cache.stride(0), cache.size(0), block_table.data_ptr<int32_t>(),
+                                 block_table.stride(0), q_start.data_ptr<int32_t>(), q_len.data_ptr<int32_t>(),
+                                 kv_len.data_ptr<int32_t>(), q_lat.size(0), block_table.size(0), q_lat.size(1),
+                                 cache.size(1), scale, scratch.data_ptr<int32_t>(), error_flag(), cur_stream()),
+               "mla_prefill_tc");
+      return;
+    }
     check_rc(mb_mla_paged_attention(q_lat.data_ptr(), q_rope.data_ptr(), out.data_ptr(), cache.data_ptr(),
                                     cache.stride(0), block_table.data_ptr<int32_t>(), block_table.stride(0),
                                     q_start.data_ptr<int32_t>(), q_len.data_ptr<int32_t>(),

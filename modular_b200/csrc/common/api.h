@@ -92,6 +92,10 @@ int mb_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int 
 int mb_silu_mul(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream);
 int mb_silu_mul_quant_fp8(const void* gate_up, void* q_fp8, float* scales, int M, int inter, int ld_s,
                           const int32_t* n_rows_dev, cudaStream_t stream);
+int mb_mla_prefill_tc(const void* q_lat, const void* q_rope, void* out, const void* cache, long long page_stride,
+                      long long n_pages, const int32_t* block_table, int bt_stride, const int32_t* q_start,
+                      const int32_t* q_len, const int32_t* kv_len, int T, int B, int n_heads, int page_size, float scale,
+                      int32_t* tok_scratch, int* err, cudaStream_t stream);
 int mb_mla_post_down(const void* qkv_a, int ld, int q_lora, int R, const void* gamma_q, const void* gamma_kv, float eps,
                      const int32_t* positions, const float* cos_sin, const int64_t* slots, void* q_a_out, void* cache,
                      int T, int page_size, long long page_stride, cudaStream_t stream);

@@ -19,8 +19,9 @@
 //            K-major layout
 //
 // Every mbarrier wait is bounded; on a time-out the CTA raises the error word, drains and frees its TMEM.
-// Steps with more than one query token per sequence, other ranks or head counts stay on the mma.sync kernel
-// of mla.cu.
+// Steps with more than one query token per sequence run the same kernel in token mode (one CTA pair per query
+// token over the causal prefix of its sequence); other latent widths or head counts stay on the mma.sync kernel of
+// mla.cu.
 //
 // Reference counterpart: max/kernels/src/nn/attention/gpu/nvidia/sm100/mla_decode_*.mojo (absorbed MLA decode
 // with split-K partitions) behind nn/attention/multi_latent_attention.py:511.
@@ -54,6 +55,10 @@ struct Params {
   const int32_t* q_start;
   const int32_t* q_len;
   const int32_t* kv_len;
+  // token mode (prefill): grid x walks query tokens; token t belongs to sequence tok_seq[t] and sees the first
+  // tok_kvlen[t] cache rows of it (causal). nullptr: grid x walks sequences with one query token each.
+  const int32_t* tok_seq;
+  const int32_t* tok_kvlen;
   int* err;
   long long page_rows;             // rows of the [rows, 576] view between consecutive pages
   int bt_stride, n_heads, page_size;
@@ -95,11 +100,19 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_constant__ 
   uint8_t* sP = sRing + kSlots * kSlotBytes;
   Bars* bars = reinterpret_cast<Bars*>(sP + kPBytes);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int seq = blockIdx.x, hb = blockIdx.y, half = blockIdx.z;
+  const int hb = blockIdx.y, half = blockIdx.z;
 
   pdl_wait();
   pdl_trigger();
-  const int qs = p.q_start[seq], ql = p.q_len[seq], kl = p.kv_len[seq];
+  int seq = blockIdx.x, qs, ql, kl;
+  if (p.tok_seq != nullptr) {
+    qs = blockIdx.x;                    // one CTA pair per query token
+    seq = p.tok_seq[qs];
+    kl = p.tok_kvlen[qs];
+    ql = seq >= 0 ? 1 : 0;
+  } else {
+    qs = p.q_start[seq]; ql = p.q_len[seq]; kl = p.kv_len[seq];
+  }
   if (ql <= 0) return;   // whole CTA, before any barrier or TMEM allocation
   const int32_t* bt = p.block_table + static_cast<int64_t>(seq) * p.bt_stride;
   const int ntiles = (kl + 63) / 64;
@@ -332,6 +345,25 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_constant__ 
   }
 }
 
+// Per-token view of a ragged batch for the token mode: tok_seq[t] = sequence of query token t (-1 for rows
+// that belong to none), tok_kvlen[t] = cache rows it attends to = kv_len - q_len + (t - q_start) + 1.
+__global__ void mla_expand_tokens_kernel(const int32_t* __restrict__ q_start, const int32_t* __restrict__ q_len,
+                                         const int32_t* __restrict__ kv_len, int B, int T, int32_t* __restrict__ tok_seq,
+                                         int32_t* __restrict__ tok_kvlen) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  // sequences are laid out in order: binary search for the last q_start <= t
+  int lo = 0, hi = B - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (q_start[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  const int off = t - q_start[lo];
+  const bool in = off >= 0 && off < q_len[lo];
+  tok_seq[t] = in ? lo : -1;
+  tok_kvlen[t] = in ? kv_len[lo] - q_len[lo] + off + 1 : 0;
+}
+
 }  // namespace mlatc
 }  // namespace mb
 
@@ -347,10 +379,36 @@ extern "C" int mb_mla_tc_usable(int T, int B, int n_heads, int R, int page_size)
 // Decode-only absorbed MLA: T == B (one query token per sequence; sequences with q_len 0 are skipped),
 // R = 512, n_heads % 128 == 0, page_size % 64 == 0. `cache` is one layer's [pages, page_size, 576] view with
 // `page_stride` elements between pages (a multiple of 576); `n_pages` bounds the tensor map.
+static int mla_tc_launch(const void* q_lat, const void* q_rope, void* out, const void* cache, long long page_stride,
+                         long long n_pages, const int32_t* block_table, int bt_stride, const int32_t* q_start,
+                         const int32_t* q_len, const int32_t* kv_len, int T, int B, int n_heads, int page_size,
+                         float scale, int32_t* tok_scratch, int* err, cudaStream_t stream);
+
 extern "C" int mb_mla_decode_tc(const void* q_lat, const void* q_rope, void* out, const void* cache,
                                 long long page_stride, long long n_pages, const int32_t* block_table, int bt_stride,
                                 const int32_t* q_start, const int32_t* q_len, const int32_t* kv_len, int T, int B,
                                 int n_heads, int page_size, float scale, int* err, cudaStream_t stream) {
+  return mla_tc_launch(q_lat, q_rope, out, cache, page_stride, n_pages, block_table, bt_stride, q_start, q_len, kv_len,
+                       T, B, n_heads, page_size, scale, nullptr, err, stream);
+}
+
+// Any ragged batch (prefill, chunks, mixed steps) on the same tensor-core kernel: every query token is one CTA
+// pair that walks the causal prefix of its sequence. `tok_scratch`: 2 * T int32 of device scratch. The KV tiles of
+// a sequence are read once from HBM and again from L2 by the tokens that share them.
+extern "C" int mb_mla_prefill_tc(const void* q_lat, const void* q_rope, void* out, const void* cache,
+                                 long long page_stride, long long n_pages, const int32_t* block_table, int bt_stride,
+                                 const int32_t* q_start, const int32_t* q_len, const int32_t* kv_len, int T, int B,
+                                 int n_heads, int page_size, float scale, int32_t* tok_scratch, int* err,
+                                 cudaStream_t stream) {
+  if (tok_scratch == nullptr) return MB_ERR_SHAPE;
+  return mla_tc_launch(q_lat, q_rope, out, cache, page_stride, n_pages, block_table, bt_stride, q_start, q_len, kv_len,
+                       T, B, n_heads, page_size, scale, tok_scratch, err, stream);
+}
+
+static int mla_tc_launch(const void* q_lat, const void* q_rope, void* out, const void* cache, long long page_stride,
+                         long long n_pages, const int32_t* block_table, int bt_stride, const int32_t* q_start,
+                         const int32_t* q_len, const int32_t* kv_len, int T, int B, int n_heads, int page_size,
+                         float scale, int32_t* tok_scratch, int* err, cudaStream_t stream) {
   using namespace mb::mlatc;
   if (T <= 0 || B <= 0) return MB_OK;
   if (n_heads % 128 || page_size % 64 || page_stride % LD || n_pages <= 0) return MB_ERR_SHAPE;
@@ -363,6 +421,9 @@ extern "C" int mb_mla_decode_tc(const void* q_lat, const void* q_rope, void* out
   Params p;
   p.out = static_cast<bf16*>(out);
   p.block_table = block_table; p.q_start = q_start; p.q_len = q_len; p.kv_len = kv_len;
+  p.tok_seq = tok_scratch; p.tok_kvlen = tok_scratch ? tok_scratch + T : nullptr;
+  if (tok_scratch != nullptr)
+    mla_expand_tokens_kernel<<<(T + 255) / 256, 256, 0, stream>>>(q_start, q_len, kv_len, B, T, tok_scratch, tok_scratch + T);
   p.err = err;
   p.page_rows = page_rows; p.bt_stride = bt_stride; p.n_heads = n_heads; p.page_size = page_size;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -381,7 +442,8 @@ extern "C" int mb_mla_decode_tc(const void* q_lat, const void* q_rope, void* out
       return MB_ERR_LAUNCH;
     configured.done();
   }
-  return launch_k(mla_tc_kernel, dim3(B, n_heads / 128, 2), dim3(kThreads), smem, stream, tql, tqr, tkv, p) ==
+  return launch_k(mla_tc_kernel, dim3(tok_scratch ? T : B, n_heads / 128, 2), dim3(kThreads), smem, stream, tql, tqr,
+                  tkv, p) ==
                  cudaSuccess
              ? MB_OK
              : MB_ERR_LAUNCH;

@@ -140,6 +140,7 @@ class LLM:
                                     host_group=dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=300)))
         # verification asks for the logits of every draft position: size the model's logit rows for it
         spec_rows = (speculative.num_speculative_tokens + 1) if speculative is not None else 1
+        self._ep = extra.get("ep")
         self.model = fam.model_class(model_config, weights, self.kv.kv, max_tokens=max_batch_input_tokens,
                                      max_seqs=max_batch_size * spec_rows, max_position=max_length, **extra)
         overlap = on_gpu if enable_overlap_scheduler is None else enable_overlap_scheduler
@@ -198,8 +199,13 @@ class LLM:
         return rid
 
     def step(self) -> list[RequestRecord]:
-        """One scheduler iteration; returns the records of requests that finished in it."""
+        """One scheduler iteration; returns the records of requests that finished in it. Expert-parallel ranks
+        keep in step: a rank whose scheduler launched nothing runs an idle step, because every MoE layer of every
+        step is an exchange that all ranks take part in."""
+        fw0 = getattr(self.model, "forward_calls", 0)
         self.scheduler.run_iteration()
+        if self._ep and getattr(self.model, "forward_calls", 0) == fw0:
+            self.model.idle_step()
         finished = []
         q = self.scheduler.response_queue
         while not q.empty():
@@ -244,7 +250,7 @@ class LLM:
             order.append(self.add_request(prompts[nxt], sps[nxt]))
             nxt += 1
             inflight += 1
-        while inflight > 0:
+        while self._any_rank_busy(inflight > 0):
             for _ in self.step():
                 inflight -= 1
                 if nxt < n:
@@ -253,3 +259,14 @@ class LLM:
                     inflight += 1
         recs = [self._records.pop(rid) for rid in order]
         return recs
+
+    def _any_rank_busy(self, busy: bool) -> bool:
+        """``busy`` on one GPU; under expert parallelism whether ANY rank still has requests (the others keep
+        taking idle steps until all are done)."""
+        if not self._ep:
+            return busy
+        import torch.distributed as dist
+
+        t = torch.tensor([1 if busy else 0], dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self._ep.host_group)
+        return bool(int(t))

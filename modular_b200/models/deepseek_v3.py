@@ -412,6 +412,7 @@ class DeepseekV3Model:
                     self._ep_layers[i] = EPMoE(l.moe, ep if self.device.type == "cuda" else None)
         self.sampled = torch.zeros(max_seqs, dtype=torch.long, device=self.device)
         self._graphs: dict = {}             # decode batch size -> (graph, static inputs, static logits)
+        self.forward_calls = 0              # steps taken (eager or replayed)
         self._graph_calls: dict = {}        # native calls recorded in each graph (0 unless calls are counted)
         self.graph_replays = 0
         self.replayed_calls = 0
@@ -473,6 +474,7 @@ class DeepseekV3Model:
         """One ragged step. Returns fp32 logits ``[len(logit_rows), vocab]``. Decode-only steps replay a captured
         graph when one of a fitting size exists (sequences beyond the real ones are dummies that write no KV)."""
         T, n = tokens.shape[0], q_len.shape[0]
+        self.forward_calls += 1
         B = self._graph_for(T, n, logit_rows.shape[0]) if (self._graphs or self.ep is not None) else 0
         if not B:
             return self._forward(tokens, positions, slots, block_table, q_start, q_len, kv_len, logit_rows)
@@ -489,6 +491,15 @@ class DeepseekV3Model:
         self.graph_replays += 1
         self.replayed_calls += self._graph_calls.get(B, 0)
         return logits[:n]
+
+    def idle_step(self) -> None:
+        """A step with one dummy token that writes no cache entry: what an expert-parallel rank without requests
+        runs while other ranks work, so that it takes part in their exchanges (and serves its experts)."""
+        dev = self.device
+        i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=dev)
+        self.forward_tensors(torch.zeros(1, dtype=torch.long, device=dev), i32(0),
+                             torch.full((1,), -1, dtype=torch.long, device=dev),
+                             torch.zeros(1, 1, dtype=torch.int32, device=dev), i32(0), i32(1), i32(1), i32(0))
 
     # ------------------------------------------------------------ attention
     def _attention_fused(self, li: int, l: DSLayer, x, positions, slots, block_table, q_start, q_len, kv_len):

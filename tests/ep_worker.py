@@ -33,6 +33,8 @@ def main():
         dist.init_process_group("gloo")
     if len(sys.argv) > 2 and sys.argv[2] == "deepseek":
         return deepseek_model(rank, world, dev)
+    if len(sys.argv) > 2 and sys.argv[2] == "engine":
+        return deepseek_engine(rank, world, dev)
     cfg = MoEConfig(hidden_size=512, moe_intermediate_size=256, n_routed_experts=16, num_experts_per_tok=4,
                     n_shared_experts=1, n_group=4, topk_group=2, routed_scaling_factor=2.5)
     full = MoE.random_init(cfg, dev, torch.bfloat16, seed=3, std=0.05)
@@ -110,6 +112,42 @@ def deepseek_model(rank, world, dev):
     err_d = float((got_d - want_d).abs().max() / want_d.abs().max())
     gathered = [None] * world
     dist.all_gather_object(gathered, {"rank": rank, "errs": [err, err_d], "dropped": 0})
+    if rank == 0:
+        print("EP_RESULT " + json.dumps(gathered), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def deepseek_engine(rank, world, dev):
+    """The engine under expert parallelism with data-parallel attention: every rank serves its OWN requests
+    (different counts and lengths, so the ranks' schedulers take different numbers of steps; ranks that run out of
+    work keep taking idle steps), against the same requests on an engine that holds all experts."""
+    from modular_b200 import ops
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.models.deepseek_v3 import DeepseekV3Config, DeepseekV3Weights
+    from modular_b200.pipelines.context import SamplingParams
+
+    cfg = DeepseekV3Config.tiny(hidden_size=512, moe_intermediate_size=256, intermediate_size=1024,
+                                kv_lora_rank=128, q_lora_rank=256, num_attention_heads=8)
+    El = cfg.n_routed_experts // world
+    mine = DeepseekV3Weights.random_init(cfg, dev, torch.bfloat16, seed=11, std=0.05, e_begin=rank * El, e_end=(rank + 1) * El)
+    full = DeepseekV3Weights.random_init(cfg, dev, torch.bfloat16, seed=11, std=0.05)
+    kw = dict(device=str(dev), dtype=torch.bfloat16, max_length=128, max_batch_size=4, max_batch_input_tokens=64,
+              page_size=16, num_kv_pages=64, enable_prefix_caching=False, graph_batch_sizes=[4])
+    ep_llm = LLM(cfg, mine, ep_size=world, ep_rank=rank, **kw)
+    g = torch.Generator().manual_seed(50 + rank)
+    prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist() for n in (9 + 20 * rank, 70, 5)[: 2 + rank]]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=6 + 5 * rank, ignore_eos=True)
+    got = [list(r.tokens) for r in ep_llm.generate(prompts, sp)]
+    torch.cuda.synchronize()
+    ops.check_device_error()
+    ref_llm = LLM(cfg, full, **kw)
+    want = [list(r.tokens) for r in ref_llm.generate(prompts, sp)]
+    same_first = sum(a[0] == b[0] for a, b in zip(got, want))
+    ok = all(len(a) == 6 + 5 * rank for a in got) and same_first >= len(got) - 1 and ep_llm.model.graph_replays > 0
+    gathered = [None] * world
+    dist.all_gather_object(gathered, {"rank": rank, "errs": [0.0 if ok else 1.0], "dropped": 0,
+                                      "detail": [got, want, ep_llm.model.graph_replays]})
     if rank == 0:
         print("EP_RESULT " + json.dumps(gathered), flush=True)
     dist.barrier()

@@ -33,7 +33,8 @@ def test_ep_host_exchange_matches_full_layer():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("world,mode", [(2, "bf16"), (2, "fp8"), (2, "fp8experts"), (4, "bf16"), (2, "deepseek")])
+@pytest.mark.parametrize("world,mode", [(2, "bf16"), (2, "fp8"), (2, "fp8experts"), (4, "bf16"), (2, "deepseek"),
+                                        (2, "engine"), (4, "fp8experts")])
 def test_ep_kernels_match_full_layer(world, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
