@@ -235,7 +235,18 @@ def _deepseek_arm(args, defaults) -> int:
     barrier()
     t0 = time.perf_counter()
     ev0.record()
+    prof = None
+    if os.environ.get("MB200_HOST_PROFILE") and rank == 0:      # where the host spends the timed region
+        import cProfile
+
+        prof = cProfile.Profile()
+        prof.enable()
     recs = llm.generate(timed, sp, max_concurrency=conc)
+    if prof is not None:
+        import pstats
+
+        prof.disable()
+        pstats.Stats(prof, stream=sys.stderr).sort_stats("cumulative").print_stats(45)
     ev1.record()
     barrier()
     wall = time.perf_counter() - t0

@@ -274,10 +274,14 @@ def bench_ep(args, ctx, L, peaks, flush, out):
             ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).int().to(dev)
             w = torch.full((T, k), 1.0 / k, device=dev)
 
+            ep.set_step_tokens_local(T)          # every rank brings T tokens: buffers addressed for T * k pairs
+
             def fused():
-                # the received rows stand in for the expert outputs: same bytes on the wire
-                xp, offsets, send_pos = ep.dispatch(x, ids)
-                ep.combine(xp, ids, send_pos, w, None)
+                # dispatch + receive compaction (the grouped GEMM's operands), then the combine; a bf16 buffer of
+                # the same shape stands in for the expert outputs: same bytes on the wire
+                xp, offsets, send_pos = ep.dispatch(x, ids, keep_fp8=fp8)
+                rows = ep.out[: ep.step_rows] if fp8 else xp
+                ep.combine(rows, ids, send_pos, w, None)
 
             # NCCL baseline: the same rows as all_to_all_single with precomputed splits
             owner = (ids // (E // world)).flatten().cpu()

@@ -972,6 +972,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                            q_rope.data_ptr(), q.size(0), cur_stream()),
              "mla_q_rope");
   });
+  m.def("mla_split_workspace_bytes", []() { return static_cast<int64_t>(mb_mla_split_workspace_bytes(num_sms())); });
+  m.def("set_mla_split_workspace", [](const Tensor& ws, const Tensor& counters) {
+    need_cuda(ws, "ws"); need_cuda(counters, "counters");
+    TORCH_CHECK(counters.scalar_type() == at::kInt && ws.is_contiguous() && counters.is_contiguous(), "workspace types");
+    mb_set_mla_split_workspace(ws.data_ptr(), ws.nbytes(), counters.data_ptr<int>(), static_cast<int>(counters.numel()));
+  });
+  m.def("set_mla_split", [](int mode) { mb_set_mla_split(mode); }, py::arg("mode"));
   m.def("set_mla_tc", [](bool on) { mb_set_mla_tc(on ? 1 : 0); }, py::arg("on"));
   // ---- expert parallelism ----
   m.def("ep_flag_ints", []() { return mb_ep_flag_ints(); });

@@ -92,6 +92,9 @@ int mb_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int 
 int mb_silu_mul(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream);
 int mb_silu_mul_quant_fp8(const void* gate_up, void* q_fp8, float* scales, int M, int inter, int ld_s,
                           const int32_t* n_rows_dev, cudaStream_t stream);
+void mb_set_mla_split_workspace(void* ws, size_t ws_bytes, int* counters, int n_counters);
+void mb_set_mla_split(int mode);
+size_t mb_mla_split_workspace_bytes(int num_sms);
 int mb_mla_prefill_tc(const void* q_lat, const void* q_rope, void* out, const void* cache, long long page_stride,
                       long long n_pages, const int32_t* block_table, int bt_stride, const int32_t* q_start,
                       const int32_t* q_len, const int32_t* kv_len, int T, int B, int n_heads, int page_size, float scale,

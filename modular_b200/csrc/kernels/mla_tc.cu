@@ -48,6 +48,7 @@ constexpr int kPBytes = 128 * 128;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;           // S0 | S1 (64 each) | O half (256)
 constexpr int kVBlocks = 4;                   // 256 output columns = four 64-column blocks
+constexpr int kPartFloats = 256 * 128 + 2 * 128;   // one partial: O [256 columns][128 heads], m [128], l [128]
 
 struct Params {
   bf16* out;                       // [T, h, 512]
@@ -59,6 +60,12 @@ struct Params {
   // tok_kvlen[t] cache rows of it (causal). nullptr: grid x walks sequences with one query token each.
   const int32_t* tok_seq;
   const int32_t* tok_kvlen;
+  // KV split (decode with few sequences): grid x = sequence * nsplit + part; every part walks its share of the
+  // 64-token tiles and leaves an unnormalised partial (256 x 128 fp32 + running maximum and sum per head) in `ws`;
+  // the last part to arrive at the (sequence, head block, half) counter combines them. nsplit = 1: no workspace.
+  int nsplit;
+  float* ws;
+  int* counters;
   int* err;
   long long page_rows;             // rows of the [rows, 576] view between consecutive pages
   int bt_stride, n_heads, page_size;
@@ -75,6 +82,7 @@ struct Bars {
   uint64_t pv_full;
   uint32_t tmem_base;
   int abort_word;
+  int last_flag;
 };
 
 __device__ __forceinline__ uint64_t desc_mn_sw128(const void* smem_tile, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -105,6 +113,11 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_constant__ 
   pdl_wait();
   pdl_trigger();
   int seq = blockIdx.x, qs, ql, kl;
+  int part = 0;
+  if (p.nsplit > 1) {
+    part = seq % p.nsplit;
+    seq /= p.nsplit;
+  }
   if (p.tok_seq != nullptr) {
     qs = blockIdx.x;                    // one CTA pair per query token
     seq = p.tok_seq[qs];
@@ -115,7 +128,13 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_constant__ 
   }
   if (ql <= 0) return;   // whole CTA, before any barrier or TMEM allocation
   const int32_t* bt = p.block_table + static_cast<int64_t>(seq) * p.bt_stride;
-  const int ntiles = (kl + 63) / 64;
+  const int tiles_all = (kl + 63) / 64;
+  // this part's tiles [t_begin, t_begin + ntiles); parts are as even as possible and the trailing ones may be empty
+  const int tiles_per = p.nsplit > 1 ? (tiles_all + p.nsplit - 1) / p.nsplit : tiles_all;
+  const int t_begin = part * tiles_per;
+  const int ntiles = max(0, min(tiles_all, t_begin + tiles_per) - t_begin);
+  const int n_parts = tiles_per > 0 ? (tiles_all + tiles_per - 1) / tiles_per : 1;   // parts that have tiles
+  if (part > 0 && ntiles == 0) return;            // whole CTA, before any barrier or TMEM allocation
   const int q_row = qs * p.n_heads + hb * 128;   // row of the [T*h, .] views of q_lat / q_rope / out
 
   if (tid == 0) {
@@ -163,7 +182,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_constant__ 
         if (++slot == kSlots) { slot = 0; ph ^= 1; }
       };
       // pages are walked without divisions; row_prev is the tile whose P . V blocks follow the next S blocks
-      int page_i = 0, page_off = 0;
+      int page_i = (t_begin * 64) / p.page_size, page_off = (t_begin * 64) % p.page_size;
       long long row_prev = 0;
       for (int i = 0; i <= ntiles && ok; ++i) {
         long long row_cur = 0;
@@ -248,7 +267,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_free[b]);
-      const int kv0 = t * 64;
+      const int kv0 = (t_begin + t) * 64;
       float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (kv0 + 64 <= kl) {
 #pragma unroll
@@ -312,28 +331,83 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_constant__ 
     if (ok && ntiles > 0) ok = mbar_wait(&bars->pv_full, (ntiles - 1) & 1, abort_word, p.err, 809);
     tc_fence_after();
     // ---- epilogue: O / l -> bf16, 256 columns of this CTA's half
-    const float inv = (ok && ntiles > 0 && l > 0.f) ? 1.f / l : 0.f;
     bf16* orow = p.out + (static_cast<int64_t>(q_row) + r) * R + half * 256;
-    if (ntiles > 0 && ok) {
+    if (n_parts <= 1) {
+      const float inv = (ok && ntiles > 0 && l > 0.f) ? 1.f / l : 0.f;
+      if (ntiles > 0 && ok) {
+#pragma unroll 1
+        for (int q8 = 0; q8 < 8; ++q8) {
+          uint32_t ta[32];
+          tmem_ld_32x32(o_addr + q8 * 32, ta);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(ta[c * 8 + 2 * j]) * inv,
+                                                        __uint_as_float(ta[c * 8 + 2 * j + 1]) * inv);
+              pk[j] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+            *reinterpret_cast<uint4*>(orow + q8 * 32 + c * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+        }
+      } else if (ntiles == 0) {
+        for (int c = 0; c < 256; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
+      }
+    } else {
+      // ---- this part's partial goes to the workspace; the last part to arrive combines all of them
+      const int unit = (seq * (p.n_heads / 128) + hb) * 2 + half;
+      float* base = p.ws + static_cast<size_t>(unit) * p.nsplit * kPartFloats;
+      float* mine = base + static_cast<size_t>(part) * kPartFloats;
 #pragma unroll 1
       for (int q8 = 0; q8 < 8; ++q8) {
         uint32_t ta[32];
         tmem_ld_32x32(o_addr + q8 * 32, ta);
         tc_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 32; ++c) __stcg(mine + (q8 * 32 + c) * 128 + r, ok ? __uint_as_float(ta[c]) : 0.f);
+      }
+      __stcg(mine + 256 * 128 + r, m_ref);
+      __stcg(mine + 256 * 128 + 128 + r, ok ? l : 0.f);
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");           // the four softmax warps
+      if (r == 0) bars->last_flag = atomicAdd(p.counters + unit, 1) == n_parts - 1 ? 1 : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (bars->last_flag != 0) {
+        __threadfence();
+        float M = -INFINITY;
+        for (int q = 0; q < n_parts; ++q) {
+          const float* pp = base + static_cast<size_t>(q) * kPartFloats;
+          if (__ldcg(pp + 256 * 128 + 128 + r) > 0.f) M = fmaxf(M, __ldcg(pp + 256 * 128 + r));
+        }
+        float wq[16];                                         // nsplit <= 16
+        float L = 0.f;
+        for (int q = 0; q < n_parts; ++q) {
+          const float* pp = base + static_cast<size_t>(q) * kPartFloats;
+          const float lq = __ldcg(pp + 256 * 128 + 128 + r);
+          wq[q] = lq > 0.f ? exp2f(__ldcg(pp + 256 * 128 + r) - M) : 0.f;
+          L += lq * wq[q];
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll 1
+        for (int c8 = 0; c8 < 32; ++c8) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int q = 0; q < n_parts; ++q) {
+            const float* pp = base + static_cast<size_t>(q) * kPartFloats + (c8 * 8) * 128 + r;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = fmaf(__ldcg(pp + j * 128), wq[q], acc[j]);
+          }
           uint32_t pk[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(ta[c * 8 + 2 * j]) * inv,
-                                                      __uint_as_float(ta[c * 8 + 2 * j + 1]) * inv);
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(acc[2 * j] * inv, acc[2 * j + 1] * inv);
             pk[j] = *reinterpret_cast<uint32_t*>(&v2);
           }
-          *reinterpret_cast<uint4*>(orow + q8 * 32 + c * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(orow + c8 * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
+        if (r == 0) p.counters[unit] = 0;                     // ready for the next launch
       }
-    } else if (ntiles == 0) {
-      for (int c = 0; c < 256; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
     }
   }
 
@@ -368,6 +442,22 @@ __global__ void mla_expand_tokens_kernel(const int32_t* __restrict__ q_start, co
 }  // namespace mb
 
 using namespace mb;
+
+static float* g_mla_ws = nullptr;
+static size_t g_mla_ws_bytes = 0;
+static int* g_mla_counters = nullptr;
+static int g_mla_n_counters = 0;
+static int g_mla_split = 1;       // 0: never split the KV, 1: when the sequences leave SMs idle
+// Workspace of the KV-split decode path: `ws` fp32 scratch for the partials, `counters` zeroed int32 (one per
+// (sequence, 128-head block, output half)); both live as long as the process uses the kernel.
+extern "C" void mb_set_mla_split_workspace(void* ws, size_t ws_bytes, int* counters, int n_counters) {
+  g_mla_ws = static_cast<float*>(ws); g_mla_ws_bytes = ws_bytes; g_mla_counters = counters; g_mla_n_counters = n_counters;
+}
+extern "C" void mb_set_mla_split(int mode) { g_mla_split = mode; }
+extern "C" size_t mb_mla_split_workspace_bytes(int num_sms) {
+  // at most 2 * num_sms partials are in flight by construction of the split count
+  return static_cast<size_t>(2) * (num_sms > 0 ? num_sms : 148) * mb::mlatc::kPartFloats * sizeof(float);
+}
 
 static int g_mla_tc = 1;
 // 1 (default): decode steps with 512-wide latents and a multiple of 128 heads run on the tcgen05 kernel
@@ -422,6 +512,25 @@ static int mla_tc_launch(const void* q_lat, const void* q_rope, void* out, const
   p.out = static_cast<bf16*>(out);
   p.block_table = block_table; p.q_start = q_start; p.q_len = q_len; p.kv_len = kv_len;
   p.tok_seq = tok_scratch; p.tok_kvlen = tok_scratch ? tok_scratch + T : nullptr;
+  p.nsplit = 1; p.ws = nullptr; p.counters = nullptr;
+  const int units = B * (n_heads / 128) * 2;
+  if (tok_scratch == nullptr && g_mla_split && g_mla_ws != nullptr && g_mla_counters != nullptr) {
+    static int sms = 0;
+    if (sms == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    // as many parts as fill the SMs once, at least four tiles each (the block table bounds the tiles of a sequence)
+    const long long max_tiles = static_cast<long long>(bt_stride) * page_size / 64;
+    long long ns = sms / units;
+    if (ns > max_tiles / 4) ns = max_tiles / 4;
+    if (ns > 16) ns = 16;
+    while (ns > 1 && (static_cast<size_t>(units) * ns * kPartFloats * sizeof(float) > g_mla_ws_bytes)) --ns;
+    if (ns > 1 && units <= g_mla_n_counters) {
+      p.nsplit = static_cast<int>(ns); p.ws = g_mla_ws; p.counters = g_mla_counters;
+    }
+  }
   if (tok_scratch != nullptr)
     mla_expand_tokens_kernel<<<(T + 255) / 256, 256, 0, stream>>>(q_start, q_len, kv_len, B, T, tok_scratch, tok_scratch + T);
   p.err = err;
@@ -442,7 +551,7 @@ static int mla_tc_launch(const void* q_lat, const void* q_rope, void* out, const
       return MB_ERR_LAUNCH;
     configured.done();
   }
-  return launch_k(mla_tc_kernel, dim3(tok_scratch ? T : B, n_heads / 128, 2), dim3(kThreads), smem, stream, tql, tqr,
+  return launch_k(mla_tc_kernel, dim3(tok_scratch ? T : B * p.nsplit, n_heads / 128, 2), dim3(kThreads), smem, stream, tql, tqr,
                   tkv, p) ==
                  cudaSuccess
              ? MB_OK

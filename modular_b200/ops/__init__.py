@@ -394,6 +394,24 @@ def mla_kv_store(c_kv, k_rope, slots, cache):
     ref.mla_kv_store(c_kv, k_rope, slots, cache)
 
 
+_MLA_SPLIT_WS: dict = {}
+
+
+def ensure_mla_split_workspace(device) -> None:
+    """Registers the workspace of the KV-split MLA decode path for this process (one GPU per process): partial
+    outputs of up to one part per SM and one zeroed counter per (sequence, 128-head block, output half).
+    ``MB200_MLA_SPLIT=0`` keeps one CTA pair per sequence."""
+    idx = torch.device(device).index or 0
+    if idx in _MLA_SPLIT_WS:
+        return
+    L = _lib()
+    ws = torch.empty(L.mla_split_workspace_bytes() // 4, dtype=torch.float32, device=device)
+    counters = torch.zeros(4096, dtype=torch.int32, device=device)
+    _MLA_SPLIT_WS[idx] = (ws, counters)
+    L.set_mla_split_workspace(ws, counters)
+    L.set_mla_split(int(os.environ.get("MB200_MLA_SPLIT", "1")))
+
+
 def mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_len, scale, plan=None,
                         decode_only=None):
     """Absorbed-form multi-head latent attention over a paged latent cache; returns [T, h, R].
@@ -402,6 +420,7 @@ def mla_paged_attention(q_lat, q_rope, cache, block_table, q_start, q_len, kv_le
     heads run on the tcgen05 kernel). ``None`` infers it from ``T == number of sequences``: schedulers never
     put a sequence without query tokens into a batch."""
     if q_lat.is_cuda and q_lat.dtype == torch.bfloat16 and hasattr(_lib(), "mla_paged_attention"):
+        ensure_mla_split_workspace(q_lat.device)
         out = torch.empty_like(q_lat)
         if decode_only is None:
             decode_only = q_lat.shape[0] == block_table.shape[0]

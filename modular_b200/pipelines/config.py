@@ -188,13 +188,21 @@ class PipelineConfig(ConfigFileModel):
     # set by the model worker for each tensor-parallel rank it starts (not user options)
     tp_size: int = 1
     tp_rank: int = 0
+    # likewise for the ranks of an expert-parallel engine (runtime.ep_size of them)
+    ep_rank: int = 0
+
+    @property
+    def expert_parallel_degree(self) -> int:
+        """Ranks that share the routed experts (``--ep-size``; attention is then data parallel: every rank serves
+        its own requests. Reference: pipeline_runtime_config.py:96)."""
+        return max(1, int(self.runtime.ep_size or 1)) if self.model.uses_gpu else 1
 
     @property
     def tensor_parallel_degree(self) -> int:
         """GPUs that share one model replica: the configured devices divided among the data-parallel replicas
         (the reference shards a model over all devices it is given, nn/transformer/distributed_transformer.py)."""
         m = self.model
-        if not m.uses_gpu:
+        if not m.uses_gpu or self.expert_parallel_degree > 1:
             return 1
         if m.tensor_parallel_degree:
             return max(1, min(int(m.tensor_parallel_degree), len(m.device_ids)))

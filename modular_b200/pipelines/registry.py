@@ -116,7 +116,10 @@ class PipelineRegistry:
 
         m, rt = pc.model, pc.runtime
         on_gpu = m.uses_gpu and torch.cuda.is_available()
-        dev_i = int(getattr(pc, "tp_rank", 0) or 0) if int(getattr(pc, "tp_size", 1) or 1) > 1 else 0
+        ep_size, ep_rank = pc.expert_parallel_degree, int(getattr(pc, "ep_rank", 0) or 0)
+        if ep_size > 1 and not hasattr(arch.weights_class, "random_init_ep"):
+            raise ValueError(f"--ep-size needs a mixture-of-experts architecture ({arch.name} is not)")
+        dev_i = int(getattr(pc, "tp_rank", 0) or 0) if int(getattr(pc, "tp_size", 1) or 1) > 1 else (ep_rank if ep_size > 1 else 0)
         device = torch.device(f"cuda:{m.device_ids[dev_i]}" if on_gpu else "cpu")
         enc = m.quantization_encoding or (arch.default_encoding if on_gpu else "float32")
         # float8_e4m3fn: projections are quantised to block-scaled fp8 at load (checkpoints that already are
@@ -136,14 +139,26 @@ class PipelineRegistry:
             # models too large to exist whole on one GPU (and fp8 ones) are created at shard size; small ones
             # are created whole and sliced, so that every tensor-parallel degree serves the same weights
             big = hasattr(cfg, "param_count") and cfg.param_count() > 30e9
-            if (to_fp8 or (tp_size > 1 and big)) and hasattr(arch.weights_class, "random_init_shard"):
+            if ep_size > 1 and (big or to_fp8):
+                # this rank's experts only (block-scaled fp8 under the fp8 encoding), the rest replicated
+                weights = arch.weights_class.random_init_ep(cfg, ep_rank, ep_size, device, dtype, seed=0, fp8_experts=to_fp8)
+            elif ep_size > 1:
+                # small models: the weights every degree of parallelism serves, sliced to this rank's experts
+                el = cfg.n_routed_experts // ep_size
+                weights = arch.weights_class.random_init(cfg, device, dtype, seed=0, e_begin=ep_rank * el, e_end=(ep_rank + 1) * el)
+            elif (to_fp8 or (tp_size > 1 and big)) and hasattr(arch.weights_class, "random_init_shard"):
                 weights = arch.weights_class.random_init_shard(cfg, tp_rank, tp_size, device, dtype, seed=0, fp8=to_fp8)
                 sharded = tp_size > 1
         else:
             sd = load_state_dict(m.model_path, m.weight_path)
-            weights = arch.weights_class.from_state_dict(cfg, sd.to_dict(), device, dtype)
-            if to_fp8:
-                weights = weights.quantize_fp8()
+            if ep_size > 1:
+                el = cfg.n_routed_experts // ep_size
+                weights = arch.weights_class.from_state_dict(cfg, sd.to_dict(), device, dtype, e_begin=ep_rank * el,
+                                                             e_end=(ep_rank + 1) * el)
+            else:
+                weights = arch.weights_class.from_state_dict(cfg, sd.to_dict(), device, dtype)
+                if to_fp8:
+                    weights = weights.quantize_fp8()
         plan = self.plan_memory(pc, cfg, device) if on_gpu else None
         max_length = min(m.max_length or cfg.max_position_embeddings, cfg.max_position_embeddings)
         if plan is not None:
@@ -167,7 +182,8 @@ class PipelineRegistry:
                   disk_kvcache_dir=m.kv_cache.disk_kvcache_dir,
                   disk_kvcache_space_gb=m.kv_cache.disk_kvcache_space_gb,
                   tp_size=tp_size, tp_rank=tp_rank, weights_are_sharded=sharded,
-                  speculative=_speculative_from(pc))
+                  speculative=_speculative_from(pc), ep_size=ep_size, ep_rank=ep_rank,
+                  ep_fp8_dispatch=ep_size > 1 and getattr(cfg, "hidden_size", 0) % 512 == 0)
         llm.tokenizer = tokenizer
         if pc.sampling.enable_structured_output:
             llm.pipeline.enable_structured_output(tokenizer)

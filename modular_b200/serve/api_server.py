@@ -116,7 +116,8 @@ def make_lifespan(settings: Settings, pipeline_config, tokenizer, factory: Calla
                     ready_timeout_s=settings.mw_timeout_s, use_heartbeat=settings.use_heartbeat,
                     health_fail_s=settings.mw_health_fail_s,
                     # a tensor-parallel worker starts the other ranks itself
-                    daemon=(getattr(pipeline_config, "tensor_parallel_degree", 1) or 1) <= 1))
+                    daemon=max(getattr(pipeline_config, "tensor_parallel_degree", 1) or 1,
+                               getattr(pipeline_config, "expert_parallel_degree", 1) or 1) <= 1))
                 queues = WorkerQueues(request=specs["request"].push(bind=False), response=response_pull,
                                       cancel=specs["cancel"].push(bind=False))
                 proxies.append(ModelWorkerProxy(queues, settings.max_queue_size))

@@ -91,8 +91,21 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
         t0 = time.perf_counter()
         # tensor parallelism: this process is rank 0; the other ranks are started here and fed in lock step
         tp_world = getattr(pipeline_config, "tensor_parallel_degree", 1) if pipeline_config is not None else 1
-        feed, followers = None, []
-        if tp_world > 1 and getattr(factory, "func", None) is not None:
+        ep_world = getattr(pipeline_config, "expert_parallel_degree", 1) if pipeline_config is not None else 1
+        feed, followers, ep_feed = None, [], None
+        if ep_world > 1 and getattr(factory, "func", None) is not None:
+            # expert parallelism with data-parallel attention: this process is rank 0, it deals the requests to
+            # the ranks and forwards everybody's outputs
+            from . import tp_worker
+            port = tp_worker.free_port()
+            per_rank = _rebind_factory(factory)
+            followers = tp_worker.start_followers(ep_world, port, per_rank, pipeline_config, settings,
+                                                  main=tp_worker.ep_follower_main)
+            pc0 = tp_worker.rank_config(pipeline_config, 0, ep_world)
+            ctl = tp_worker.init_distributed(0, ep_world, port, pc0.model.device_ids[0])
+            built = per_rank(pc0)
+            ep_feed = tp_worker.ShardedFeed(ctl, 0, ep_world)
+        elif tp_world > 1 and getattr(factory, "func", None) is not None:
             from . import tp_worker
             port = tp_worker.free_port()
             per_rank = _rebind_factory(factory)
@@ -123,7 +136,14 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
                     mq.put_nowait(m.to_dict())
                 except Exception:  # noqa: BLE001
                     pass
-        if feed is not None:
+        ep_out = None
+        if ep_feed is not None:
+            import queue as _queue
+
+            ep_out = _queue.SimpleQueue()      # this rank's outputs join the other ranks' in ep_feed.gather
+            sched = TokenGenerationScheduler(cfg, pipeline, kv, ep_feed.requests, ep_out, ep_feed.cancels,
+                                             metrics_sink=sink)
+        elif feed is not None:
             # the scheduler reads the replicated stream; rank 0 alone answers the API process
             sched = TokenGenerationScheduler(cfg, pipeline, kv, feed.requests, queues.response, feed.cancels,
                                              metrics_sink=sink)
@@ -162,6 +182,22 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
         idle = 0
         while not stop_event.is_set():
             alive_event.set()
+            if ep_feed is not None:
+                from . import tp_worker
+                if any(not p.is_alive() for p in followers):
+                    raise RuntimeError("an expert-parallel rank died")
+                _, responses, active = tp_worker.ep_iteration(
+                    ep_feed, sched, llm.model, ep_out, _drain(queues.request, cfg.max_pending_requests),
+                    _drain(queues.cancel, 0))
+                for r in responses:
+                    queues.response.put_nowait(r)
+                side.service(handlers)
+                if not active:
+                    idle = min(idle + 1, 50)
+                    time.sleep(min(0.0001 * (2 ** min(idle, 6)), 0.005))
+                else:
+                    idle = 0
+                continue
             if feed is not None:
                 if any(not p.is_alive() for p in followers):
                     raise RuntimeError("a tensor-parallel rank died")
@@ -175,6 +211,8 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
                 idle = 0
         if feed is not None:
             feed.exchange(stop=True)
+        if ep_feed is not None:
+            ep_feed.exchange(stop=True)
     except BaseException:  # noqa: BLE001
         traceback.print_exc()
         os._exit(1)

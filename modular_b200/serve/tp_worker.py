@@ -32,7 +32,10 @@ def free_port() -> int:
 
 def rank_config(pipeline_config, rank: int, world: int):
     pc = copy.deepcopy(pipeline_config)
-    pc.tp_size, pc.tp_rank = world, rank
+    if pc.expert_parallel_degree > 1:
+        pc.ep_rank = rank
+    else:
+        pc.tp_size, pc.tp_rank = world, rank
     return pc
 
 
@@ -73,6 +76,112 @@ class LockstepFeed:
         return not msg["stop"]
 
 
+class ShardedFeed:
+    """Expert parallelism with data-parallel attention behind one endpoint: rank 0 deals the requests it drained to
+    the ranks in turn (every rank hears about every request, keeps its own), and after every iteration the ranks
+    exchange what they produced: rank 0 forwards all outputs to the API process, and every rank learns whether any
+    rank still has work, because a step is an exchange that all ranks must take part in (ranks without requests
+    run idle steps, see ``DeepseekV3Model.idle_step``).
+
+    Reference: the data-parallel replicas of one process in max/python/max/serve/scheduler/text_batch_constructor.py
+    (:1318 replica assignment) and dp_padding.py:45 (idle replicas run dummy batches)."""
+
+    def __init__(self, ctl_group, rank: int, world: int):
+        self.group, self.rank, self.world = ctl_group, rank, world
+        self.requests: "queue.SimpleQueue" = queue.SimpleQueue()
+        self.cancels: "queue.SimpleQueue" = queue.SimpleQueue()
+        self._next_owner = 0
+        self.any_busy = False
+        self.arrived = 0
+
+    def exchange(self, new_ctxs=(), cancels=(), stop: bool = False) -> bool:
+        import torch.distributed as dist
+
+        box = [None]
+        if self.rank == 0:
+            frames = []
+            for c in new_ctxs:
+                frames.append((self._next_owner, codec.encode(c)))
+                self._next_owner = (self._next_owner + 1) % self.world
+            box[0] = {"new": frames, "cancel": list(cancels), "stop": stop}
+        dist.broadcast_object_list(box, src=0, group=self.group)
+        msg = box[0]
+        for owner, frame in msg["new"]:
+            if owner == self.rank:
+                self.requests.put_nowait(codec.decode(frame))
+        for rid in msg["cancel"]:
+            self.cancels.put_nowait(rid)       # unknown ids are ignored by the scheduler
+        self.arrived = len(msg["new"])
+        return not msg["stop"]
+
+    def gather(self, outputs: list, busy: bool) -> list:
+        """Every rank contributes the response batches of its iteration; returns all of them on rank 0 (an empty
+        list elsewhere) and records whether any rank is still busy."""
+        import torch.distributed as dist
+
+        mine = {"out": [codec.encode(o) for o in outputs], "busy": bool(busy)}
+        got = [None] * self.world
+        dist.all_gather_object(got, mine, group=self.group)
+        self.any_busy = any(g["busy"] for g in got)
+        if self.rank != 0:
+            return []
+        return [codec.decode(f) for g in got for f in g["out"]]
+
+
+def _drain_simple(q) -> list:
+    out = []
+    while True:
+        try:
+            out.append(q.get_nowait())
+        except queue.Empty:
+            return out
+
+
+def ep_iteration(feed: ShardedFeed, sched, model, out_queue: "queue.SimpleQueue", new=(), cancels=(), stop=False):
+    """One loop iteration of an expert-parallel rank. Returns (keep going, response batches for the API process
+    (rank 0 only), whether this iteration did anything)."""
+    if not feed.exchange(new, cancels, stop):
+        return False, [], False
+    active = feed.any_busy or feed.arrived > 0
+    if active:
+        calls = getattr(model, "forward_calls", 0)
+        sched.run_iteration()
+        if getattr(model, "forward_calls", 0) == calls:
+            model.idle_step()
+    responses = feed.gather(_drain_simple(out_queue), sched.has_work() or not feed.requests.empty())
+    return True, responses, active
+
+
+def ep_follower_main(rank: int, world: int, port: int, factory, pipeline_config, settings) -> None:
+    """Entry point of ranks 1..world-1 of an expert-parallel engine (spawned by rank 0)."""
+    import logging
+    import time
+    import traceback
+
+    from .model_worker import scheduler_config_from
+    from .scheduler import TokenGenerationScheduler
+
+    logging.basicConfig(level=getattr(logging, str(settings.log_level).upper(), logging.INFO),
+                        format=f"%(asctime)s ep-rank-{rank} %(levelname)s %(name)s: %(message)s")
+    try:
+        pc = rank_config(pipeline_config, rank, world)
+        ctl = init_distributed(rank, world, port, pc.model.device_ids[rank])
+        llm = factory(pc)
+        feed = ShardedFeed(ctl, rank, world)
+        out_q: "queue.SimpleQueue" = queue.SimpleQueue()
+        sched = TokenGenerationScheduler(scheduler_config_from(pc, llm), llm.pipeline, llm.kv, feed.requests, out_q,
+                                         feed.cancels)
+        while True:
+            go, _, active = ep_iteration(feed, sched, llm.model, out_q)
+            if not go:
+                break
+            if not active:
+                time.sleep(0.001)
+    except BaseException:  # noqa: BLE001
+        traceback.print_exc()
+        os._exit(1)
+
+
 class _NullQueue:
     def put_nowait(self, _obj) -> None:
         pass
@@ -102,14 +211,14 @@ def follower_main(rank: int, world: int, port: int, factory, pipeline_config, se
         os._exit(1)
 
 
-def start_followers(world: int, port: int, factory, pipeline_config, settings) -> list:
+def start_followers(world: int, port: int, factory, pipeline_config, settings, main=None) -> list:
     import multiprocessing as mp
 
     ctx = mp.get_context("spawn")
     procs = []
     for r in range(1, world):
-        p = ctx.Process(target=follower_main, args=(r, world, port, factory, pipeline_config, settings), daemon=True,
-                        name=f"tp-rank-{r}")
+        p = ctx.Process(target=main or follower_main, args=(r, world, port, factory, pipeline_config, settings), daemon=True,
+                        name=f"rank-{r}")
         p.start()
         procs.append(p)
     return procs

@@ -207,7 +207,8 @@ def test_engine_serves_deepseek_on_gpu():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("h,page,kv_lens", [(128, 64, [1, 64, 65, 130, 700]), (256, 128, [1152, 33, 1280]),
-                                            (128, 128, [3000])])
+                                            (128, 128, [3000]), (128, 64, [1100] * 32), (128, 128, [257, 4000, 64, 1]),
+                                            (128, 64, [5000, 5000])])
 def test_mla_decode_tcgen05_matches_reference(h, page, kv_lens):
     """Decode step (one query token per sequence) on the tcgen05 kernel, against the fp32 reference and the
     mma.sync kernel; queries scaled up so that the lazily rescaled accumulator path is exercised."""
@@ -232,11 +233,20 @@ def test_mla_decode_tcgen05_matches_reference(h, page, kv_lens):
     kv_len = torch.tensor(kv_lens, dtype=torch.int32, device=dev)
     args = (q_lat, q_rope, cache, bt, q_start, q_len, kv_len)
     scale = 0.07
-    got = ops.mla_paged_attention(*args, scale)                          # T == B: tcgen05 kernel
+    got = ops.mla_paged_attention(*args, scale)                          # T == B: tcgen05 kernel (KV split when few)
     torch.cuda.synchronize()
     ops.check_device_error()
+    from modular_b200._native import lib
+    lib().set_mla_split(0)
+    try:
+        unsplit = ops.mla_paged_attention(*args, scale)                  # one CTA pair per sequence
+    finally:
+        lib().set_mla_split(1)
+    again = ops.mla_paged_attention(*args, scale)                        # counters were left at zero
+    assert torch.equal(again, got)
     old = ops.mla_paged_attention(*args, scale, decode_only=False)       # mma.sync kernel
     want = ops.reference.mla_paged_attention(*[a.float() if a.is_floating_point() else a for a in args], scale)
     assert (old.float() - want).abs().max() / want.abs().max() < 2e-2
+    assert (unsplit.float() - want).abs().max() / want.abs().max() < 2e-2
     err = (got.float() - want).abs().max() / want.abs().max()
     assert err < 2e-2, err

@@ -106,3 +106,43 @@ def test_tensor_parallel_serving_matches_single_gpu():
     a, b = outs["gpu:0"], outs["gpu:0,1"]
     assert a["tokens"][:3] == b["tokens"][:3]
     assert max(abs(x - y) for x, y in zip(a["token_logprobs"][:3], b["token_logprobs"][:3])) < 0.1
+
+
+def test_expert_parallel_serving_matches_single_gpu():
+    """`serve --ep-size 2`: rank 0 deals the requests to the ranks, every rank serves its own with data-parallel
+    attention and the ranks meet in the MoE exchange of every step (idle ranks take dummy steps); the HTTP answers
+    equal those of a one-GPU server with the same weights."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from concurrent.futures import ThreadPoolExecutor
+
+    from fastapi.testclient import TestClient
+
+    from modular_b200.pipelines.config import PipelineArgs, PipelineConfig
+    from modular_b200.pipelines.registry import PIPELINE_REGISTRY
+    from modular_b200.serve.api_server import fastapi_app
+    from modular_b200.serve.config import Settings
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    bodies = [{"prompt": list(range(5 + i, 45 + 3 * i)), "max_tokens": 6 + 2 * i, "temperature": 0, "ignore_eos": True,
+               "logprobs": 1, "model": "tiny"} for i in range(3)]
+    outs = {}
+    for devices, ep in (("gpu:0", 1), ("gpu:0,1", 2)):
+        pc = PipelineConfig.from_args(PipelineArgs.from_flat_kwargs(
+            None, model_path="preset:tiny-deepseek", devices=devices, max_length=256, max_batch_size=4,
+            max_batch_input_tokens=128, kv_cache_page_size=16, ep_size=ep, enable_prefix_caching=False))
+        assert pc.expert_parallel_degree == ep and pc.tensor_parallel_degree == 1
+        tokenizer, factory = PIPELINE_REGISTRY.retrieve_factory(pc)
+        app = fastapi_app(Settings(), pc, tokenizer, factory, "tiny", 256)
+        with TestClient(app) as c:
+            with ThreadPoolExecutor(3) as pool:      # three requests in flight: two ranks, unequal loads
+                rs = list(pool.map(lambda b: c.post("/v1/completions", json=b), bodies))
+            assert all(r.status_code == 200 for r in rs), rs[0].text
+            outs[devices] = [r.json()["choices"][0]["logprobs"] for r in rs]
+            # a second round on the warm engine (ranks idle in between)
+            r2 = c.post("/v1/completions", json=bodies[0])
+            assert r2.status_code == 200 and r2.json()["choices"][0]["logprobs"]["tokens"] == outs[devices][0]["tokens"]
+    for a, b, body in zip(outs["gpu:0"], outs["gpu:0,1"], bodies):
+        assert len(a["tokens"]) == len(b["tokens"]) == body["max_tokens"]
+        assert a["tokens"][:2] == b["tokens"][:2]
+        assert max(abs(x - y) for x, y in zip(a["token_logprobs"][:2], b["token_logprobs"][:2])) < 0.15
