@@ -178,11 +178,27 @@ def fastapi_app(settings: Settings, pipeline_config=None, tokenizer=None, factor
     app.state.reasoning_parser = getattr(rt, "reasoning_parser", None)
     app.state.settings = settings
 
+    from .telemetry import tracing
+
+    tracing.configure_tracing(settings)
+
     @app.middleware("http")
     async def request_id_middleware(request: Request, call_next):
         rid = request.headers.get("x-request-id") or uuid.uuid4().hex
         request.state.request_id = rid
-        resp = await call_next(request)
+        if not tracing.tracing_enabled():
+            resp = await call_next(request)
+            resp.headers["x-request-id"] = rid
+            return resp
+        # one server span per request, continuing the caller's trace when it sent a W3C traceparent
+        with tracing.span(f"{request.method} {request.url.path}", {"http.method": request.method,
+                          "http.target": request.url.path, "request.id": rid},
+                          traceparent=request.headers.get("traceparent"), kind="server") as sp:
+            resp = await call_next(request)
+            tracing.set_attributes(sp, **{"http.status_code": resp.status_code})
+            tp = tracing.current_traceparent()
+            if tp:
+                resp.headers["traceparent"] = tp
         resp.headers["x-request-id"] = rid
         return resp
 

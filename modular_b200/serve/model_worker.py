@@ -175,6 +175,23 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
                 "cache_hit_rate": kv.cache_hit_rate if kv is not None else 0.0,
                 "preemptions": sched.batch_constructor.total_preemptions},
         }
+        from .telemetry import tracing
+
+        tracing.configure_tracing(settings, service_name="modular_b200.model_worker")
+        if tracing.batch_spans_enabled():
+            # one span per scheduler iteration that ran a batch (kernel_trace_level >= 1)
+            run_plain = sched.run_iteration
+
+            def run_traced():
+                with tracing.span("max.batch") as sp:
+                    progress = run_plain()
+                    m = sched.last_metrics
+                    tracing.set_attributes(sp, **{"batch.type": m.batch_type, "batch.size": m.batch_size,
+                                                  "batch.input_tokens": m.input_tokens,
+                                                  "batch.output_tokens": m.output_tokens})
+                return progress
+
+            sched.run_iteration = run_traced
         gc.collect()
         gc.freeze()
         logger.info("model worker ready in %.1f s", time.perf_counter() - t0)

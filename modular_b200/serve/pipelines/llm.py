@@ -14,6 +14,7 @@ from dataclasses import dataclass, field
 from typing import AsyncIterator, Optional, Sequence, Union
 
 from ...pipelines.context import GenerationStatus, SamplingParams
+from ..telemetry import tracing
 from ..telemetry.metrics import METRICS
 from ..worker_interface import ModelWorkerProxy
 from .incremental_detokenizer import IncrementalDetokenizer
@@ -53,7 +54,8 @@ class TokenGeneratorPipeline:
                                cache_salt: int = 0) -> AsyncIterator[TokenChunk]:
         rid = request_id or uuid.uuid4().hex
         t_in = time.perf_counter()
-        ctx = self.tokenizer.new_context(prompt, self.max_length, sampling_params, rid, self.model_name)
+        with tracing.span("max.tokenize", {"request.id": rid}):
+            ctx = self.tokenizer.new_context(prompt, self.max_length, sampling_params, rid, self.model_name)
         ctx.lora_name = lora_name
         ctx.cache_salt = cache_salt
         n_prompt = ctx.tokens.prompt_len
@@ -93,6 +95,12 @@ class TokenGeneratorPipeline:
                 buf_ids, buf_lps, buf_text = [], [], ""
             if done:
                 break
+        if tracing.tracing_enabled():
+            # the generation as one finished span (the stream yields in between, so it is not a `with` block)
+            with tracing.span("max.generate", {"request.id": rid, "gen.prompt_tokens": n_prompt,
+                                               "gen.output_tokens": n_out,
+                                               "gen.duration_ms": (time.perf_counter() - t_start) * 1e3}):
+                pass
         METRICS.output_tokens.inc(n_out)
         METRICS.output_tokens_per_request.observe(n_out)
         if n_out > 1 and t_last is not None:

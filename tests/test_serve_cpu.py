@@ -2,6 +2,7 @@
 with the echo pipeline and with the tiny Llama preset."""
 
 import json
+import os
 
 import pytest
 from fastapi.testclient import TestClient
@@ -406,3 +407,44 @@ def test_worker_hop_codec_roundtrip():
     assert codec.decode(codec.encode(("stats", None))) == ("stats", None)
     with pytest.raises(Exception):
         codec.decode(b"\\x80\\x04garbage")
+
+
+def test_tracing_spans_for_requests_and_batches(tmp_path):
+    """With telemetry on and a destination configured, a request produces a server span that continues the caller's
+    trace, with tokenise / generate children; without a destination nothing is recorded."""
+    from opentelemetry.sdk.trace.export.in_memory_span_exporter import InMemorySpanExporter
+
+    from modular_b200.serve.config import Settings
+    from modular_b200.serve.telemetry import tracing
+
+    assert tracing.configure_tracing(Settings()) is False and not tracing.tracing_enabled()
+    with tracing.span("nothing") as s:
+        assert s is None
+    exp = InMemorySpanExporter()
+    assert tracing.configure_tracing(Settings(disable_telemetry=False, kernel_trace_level=1), exporter=exp)
+    assert tracing.batch_spans_enabled()
+    parent = "00-0af7651916cd43dd8448eb211c80319c-b7ad6b7169203331-01"
+    with tracing.span("POST /v1/completions", {"request.id": "r1"}, traceparent=parent, kind="server") as sp:
+        with tracing.span("max.tokenize"):
+            pass
+        tracing.set_attributes(sp, **{"http.status_code": 200})
+        assert tracing.current_traceparent().split("-")[1] == "0af7651916cd43dd8448eb211c80319c"
+    spans = {s.name: s for s in exp.get_finished_spans()}
+    assert set(spans) == {"POST /v1/completions", "max.tokenize"}
+    server = spans["POST /v1/completions"]
+    assert f"{server.get_span_context().trace_id:032x}" == "0af7651916cd43dd8448eb211c80319c"
+    assert spans["max.tokenize"].parent.span_id == server.get_span_context().span_id
+    assert server.attributes["http.status_code"] == 200
+    # the file destination writes one JSON object per span
+    tracing.shutdown_tracing()
+    path = tmp_path / "spans.jsonl"
+    os.environ["MAX_SERVE_TRACE_FILE"] = str(path)
+    try:
+        assert tracing.configure_tracing(Settings(disable_telemetry=False))
+        with tracing.span("max.batch", {"batch.size": 3}):
+            pass
+        tracing.shutdown_tracing()
+    finally:
+        del os.environ["MAX_SERVE_TRACE_FILE"]
+    rec = json.loads(path.read_text().splitlines()[0])
+    assert rec["name"] == "max.batch" and rec["attributes"]["batch.size"] == 3
