@@ -49,6 +49,23 @@ class RequestRecord:
         return (self.last_token - self.first_token) / (n - 1)
 
 
+def merge_expert_load(parts: Sequence, slots_per_rank: Optional[int] = None) -> Optional[dict]:
+    """Per-rank load slices [layers, experts per rank] -> the statistics the balancer works on."""
+    from ..pipelines.eplb import rebalance
+
+    if not parts or any(p is None for p in parts):
+        return None
+    load = np.concatenate([np.asarray(p) for p in parts], axis=1)            # [layers, experts]
+    world, e_local = len(parts), np.asarray(parts[0]).shape[1]
+    per_rank = load.reshape(load.shape[0], world, e_local).sum(-1).astype(np.float64)
+    imb = per_rank.max(-1) / np.maximum(per_rank.mean(-1), 1e-9)
+    worst = int(np.argmax(imb))
+    plan = rebalance(load[worst], world, slots_per_rank or e_local + 1)
+    return {"load": load.tolist(), "imbalance": imb.tolist(), "worst_layer": worst,
+            "plan": {"phy2log": plan.phy2log.tolist(), "replica_count": plan.replica_count.tolist(),
+                     "imbalance_after": float(plan.imbalance)}}
+
+
 class LLM:
     def __init__(self, model_config, weights=None, *, device: Optional[str] = None,
                  dtype: Optional[torch.dtype] = None, max_length: int = 4096, max_batch_size: int = 256,
@@ -136,7 +153,7 @@ class LLM:
             # the ranks agree on the token bound of every step over a host-side group (they serve different
             # requests, so their batches differ)
             extra["ep"] = EPContext(self.tp, c.hidden_size, c.n_routed_experts, c.num_experts_per_tok,
-                                    max_tokens=max_batch_input_tokens, fp8_dispatch=ep_fp8_dispatch,
+                                    max_tokens=max_batch_input_tokens, fp8_dispatch=ep_fp8_dispatch, collect_load=True,
                                     host_group=dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=300)))
         # verification asks for the logits of every draft position: size the model's logit rows for it
         spec_rows = (speculative.num_speculative_tokens + 1) if speculative is not None else 1
@@ -259,6 +276,19 @@ class LLM:
                     inflight += 1
         recs = [self._records.pop(rid) for rid in order]
         return recs
+
+    def eplb_stats(self, slots_per_rank: Optional[int] = None) -> Optional[dict]:
+        """Expert load of all ranks (collective: every rank calls it): tokens per (MoE layer, logical expert), the
+        per-layer imbalance max / mean over ranks, and for the most imbalanced layer the balancer's placement with
+        ``slots_per_rank`` physical slots per rank (default: experts per rank + 1)."""
+        if not self._ep:
+            return None
+        import torch.distributed as dist
+
+        mine = self.model.expert_load()
+        parts = [None] * self._ep.world
+        dist.all_gather_object(parts, mine, group=self._ep.host_group)
+        return merge_expert_load(parts, slots_per_rank)
 
     def _any_rank_busy(self, busy: bool) -> bool:
         """``busy`` on one GPU; under expert parallelism whether ANY rank still has requests (the others keep

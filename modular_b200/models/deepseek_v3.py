@@ -492,6 +492,15 @@ class DeepseekV3Model:
         self.replayed_calls += self._graph_calls.get(B, 0)
         return logits[:n]
 
+    def expert_load(self):
+        """Rows routed to each local expert of every MoE layer so far: int64 numpy [moe layers, experts per rank]
+        (None unless the expert-parallel context collects the load). Idle steps and graph warm-ups count too: one
+        dummy token each."""
+        layers = [self._ep_layers[i] for i in sorted(self._ep_layers)]
+        if not layers or layers[0].load is None:
+            return None
+        return torch.stack([l.load for l in layers]).cpu().numpy()
+
     def idle_step(self) -> None:
         """A step with one dummy token that writes no cache entry: what an expert-parallel rank without requests
         runs while other ranks work, so that it takes part in their exchanges (and serves its experts)."""

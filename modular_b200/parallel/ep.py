@@ -37,7 +37,7 @@ class EPContext:
     index kernels, the row moves and the GEMM grids of a decode step are sized for the decode step."""
 
     def __init__(self, ctx: TPContext, hidden: int, n_experts: int, top_k: int, max_tokens: int,
-                 cap: Optional[int] = None, fp8_dispatch: bool = False, host_group=None):
+                 cap: Optional[int] = None, fp8_dispatch: bool = False, host_group=None, collect_load: bool = False):
         if n_experts % ctx.world:
             raise ValueError(f"{n_experts} experts cannot be split over {ctx.world} ranks")
         if hidden % 128:
@@ -53,6 +53,7 @@ class EPContext:
         self.max_tokens = max_tokens
         self.fp8 = fp8_dispatch
         self.host_group = host_group        # a gloo group of the same ranks: per-step agreement on the bound
+        self.collect_load = collect_load    # every layer adds its received rows per expert to EPMoE.load (EPLB input)
         self.row_bytes = hidden + hidden // 128 * 4 if fp8_dispatch else hidden * 2
         if self.row_bytes % 16:
             raise ValueError("fp8 dispatch needs a hidden size that is a multiple of 512 (rows move as 16-byte vectors)")
@@ -152,6 +153,9 @@ class EPMoE:
         self.e_local = moe.cfg.n_routed_experts // self.world
         assert moe.e_begin == self.rank * self.e_local and moe.e_end == moe.e_begin + self.e_local, \
             "the MoE must hold exactly this rank's expert slice"
+        # rows received per local expert since the start (all ranks' tokens): the load statistic of the balancer
+        self.load = (torch.zeros(self.e_local, dtype=torch.int64, device=ep.ctx.device)
+                     if ep is not None and ep.collect_load else None)
 
     @property
     def dropped(self) -> int:
@@ -182,6 +186,8 @@ class EPMoE:
             shared.record_stream(main)
         fp8_experts = isinstance(moe.w_gate_up, Fp8ExpertWeights)
         xp, offsets, send_pos = ep.dispatch(x, ids, keep_fp8=fp8_experts)
+        if self.load is not None:
+            self.load.add_(offsets[1:self.e_local + 1] - offsets[: self.e_local])
         n = ep.step_rows
         out = ep.out[:n]
         # rows per expert: no more than one per token of any rank; a balanced router gives pairs / experts

@@ -246,6 +246,14 @@ def fastapi_app(settings: Settings, pipeline_config=None, tokenizer=None, factor
     async def worker_stats():
         return await app.state.rpc.call("stats")
 
+    @app.get("/max_internal/eplb_stats")
+    async def eplb_stats(slots_per_rank: Optional[int] = None):
+        """Expert load over all ranks of an expert-parallel engine and the balancer's plan for the worst layer."""
+        try:
+            return await app.state.rpc.call("eplb_stats", {"slots_per_rank": slots_per_rank})
+        except Exception as e:  # noqa: BLE001
+            return error_response(409, str(e), "invalid_request_error")
+
     api_types = {getattr(t, "value", t) for t in settings.api_types}
     if "openai" in api_types:
         app.include_router(openai_routes.router)

@@ -163,7 +163,19 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
                 raise RuntimeError(f"adapter {arg['name']!r} is not loaded")
             return sorted(llm.pipeline.lora_manager.names())
 
+        def eplb_stats(arg):
+            """Expert load per (MoE layer, expert) over all ranks, per-layer imbalance and the balancer's plan for
+            the worst layer (reference: serve/pipelines/eplb_stats_rpc.py)."""
+            from ..entrypoints.llm import merge_expert_load
+            if ep_feed is None:
+                raise RuntimeError("expert-load statistics need an expert-parallel engine (--ep-size)")
+            stats = merge_expert_load(ep_feed.rank_loads, (arg or {}).get("slots_per_rank"))
+            if stats is None:
+                raise RuntimeError("no expert-load snapshot yet")
+            return stats
+
         handlers = {
+            "eplb_stats": eplb_stats,
             "load_lora": load_lora,
             "unload_lora": unload_lora,
             "list_loras": lambda _a: sorted(llm.pipeline.lora_manager.names())

@@ -93,6 +93,8 @@ class ShardedFeed:
         self._next_owner = 0
         self.any_busy = False
         self.arrived = 0
+        self.iterations = 0
+        self.rank_loads: list = [None] * world     # latest expert-load slice of every rank (rank 0 keeps them)
 
     def exchange(self, new_ctxs=(), cancels=(), stop: bool = False) -> bool:
         import torch.distributed as dist
@@ -114,17 +116,23 @@ class ShardedFeed:
         self.arrived = len(msg["new"])
         return not msg["stop"]
 
-    def gather(self, outputs: list, busy: bool) -> list:
-        """Every rank contributes the response batches of its iteration; returns all of them on rank 0 (an empty
-        list elsewhere) and records whether any rank is still busy."""
+    LOAD_EVERY = 64        # iterations between expert-load snapshots
+
+    def gather(self, outputs: list, busy: bool, load=None) -> list:
+        """Every rank contributes the response batches of its iteration (and now and then its expert-load slice,
+        the input of the load balancer); returns all responses on rank 0 (an empty list elsewhere) and records
+        whether any rank is still busy."""
         import torch.distributed as dist
 
-        mine = {"out": [codec.encode(o) for o in outputs], "busy": bool(busy)}
+        mine = {"out": [codec.encode(o) for o in outputs], "busy": bool(busy), "load": load}
         got = [None] * self.world
         dist.all_gather_object(got, mine, group=self.group)
         self.any_busy = any(g["busy"] for g in got)
         if self.rank != 0:
             return []
+        for r, g in enumerate(got):
+            if g.get("load") is not None:
+                self.rank_loads[r] = g["load"]
         return [codec.decode(f) for g in got for f in g["out"]]
 
 
@@ -148,7 +156,12 @@ def ep_iteration(feed: ShardedFeed, sched, model, out_queue: "queue.SimpleQueue"
         sched.run_iteration()
         if getattr(model, "forward_calls", 0) == calls:
             model.idle_step()
-    responses = feed.gather(_drain_simple(out_queue), sched.has_work() or not feed.requests.empty())
+    load = None
+    if active:
+        feed.iterations += 1
+        if feed.iterations % feed.LOAD_EVERY == 1 and hasattr(model, "expert_load"):
+            load = model.expert_load()          # the same iterations on every rank: the counter advances in step
+    responses = feed.gather(_drain_simple(out_queue), sched.has_work() or not feed.requests.empty(), load)
     return True, responses, active
 
 

@@ -142,6 +142,15 @@ def test_expert_parallel_serving_matches_single_gpu():
             # a second round on the warm engine (ranks idle in between)
             r2 = c.post("/v1/completions", json=bodies[0])
             assert r2.status_code == 200 and r2.json()["choices"][0]["logprobs"]["tokens"] == outs[devices][0]["tokens"]
+            st = c.get("/max_internal/eplb_stats")
+            if ep > 1:
+                # expert load of both ranks, gathered with the first iteration's outputs
+                body = st.json()
+                assert st.status_code == 200, st.text
+                assert len(body["load"][0]) == 8 and sum(map(sum, body["load"])) > 0 and len(body["imbalance"]) == len(body["load"])
+                assert sorted(set(body["plan"]["phy2log"])) == list(range(8))
+            else:
+                assert st.status_code == 409
     for a, b, body in zip(outs["gpu:0"], outs["gpu:0,1"], bodies):
         assert len(a["tokens"]) == len(b["tokens"]) == body["max_tokens"]
         assert a["tokens"][:2] == b["tokens"][:2]
