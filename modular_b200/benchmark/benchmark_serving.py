@@ -1,8 +1,13 @@
-"""Serving benchmark client: random-token requests at fixed concurrency over HTTP.
+"""Serving benchmark client over HTTP.
+
+Load shapes: closed loop at a fixed concurrency, open loop at a request rate (Poisson arrivals, optionally
+capped by a concurrency), and sweeps over either. Datasets: ``random`` (uniform token ids of fixed lengths),
+``sharegpt`` (a ShareGPT-format JSON file: first human turn as the prompt, the length of the first answer as the
+output length) and ``jsonl`` (one ``{"prompt": text or ids, "output_len": n}`` per line).
 
 Metric definitions follow the reference's client (max/python/max/benchmark/
-benchmark_serving.py, benchmark_shared/metrics.py): TTFT = time to the first streamed chunk,
-TPOT = (latency - TTFT) / (output tokens - 1), ITL = gaps between chunks, request throughput
+benchmark_serving.py, benchmark_shared/metrics.py, benchmark_shared/datasets/): TTFT = time to the first
+streamed chunk, TPOT = (latency - TTFT) / (output tokens - 1), ITL = gaps between chunks, request throughput
 and output-token throughput over the wall time of the run.
 """
 
@@ -36,10 +41,55 @@ def percentile(xs, q):
     return xs[min(len(xs) - 1, int(q / 100.0 * len(xs)))]
 
 
-async def _one(session, url, model, prompt_ids, output_len) -> RequestResult:
-    body = {"model": model, "prompt": prompt_ids, "max_tokens": output_len, "temperature": 0.0,
+@dataclass
+class SampleRequest:
+    prompt: object          # token ids or text
+    output_len: int
+
+
+def load_dataset(name: str, num_prompts: int, path: Optional[str] = None, input_len: int = 128, output_len: int = 32,
+                 vocab_size: int = 256, seed: int = 0, max_output_len: int = 4096) -> list:
+    """``num_prompts`` requests of the named dataset (files are cycled when they hold fewer)."""
+    rng = np.random.default_rng(seed)
+    if name == "random":
+        return [SampleRequest(rng.integers(0, vocab_size, size=input_len).tolist(), output_len) for _ in range(num_prompts)]
+    if not path:
+        raise ValueError(f"dataset {name!r} needs a file")
+    items = []
+    if name == "sharegpt":
+        with open(path) as f:
+            for conv in json.load(f):
+                turns = conv.get("conversations") or conv.get("items") or []
+                human = next((t for t in turns if t.get("from") in ("human", "user")), None)
+                answer = next((t for t in turns if t.get("from") in ("gpt", "assistant", "chatgpt")), None)
+                if human is None or not human.get("value"):
+                    continue
+                # answer length in whitespace words x 4/3 as a token estimate (no tokenizer on the client side)
+                n_out = int(len(answer["value"].split()) * 4 / 3) if answer and answer.get("value") else output_len
+                items.append(SampleRequest(human["value"], max(1, min(n_out, max_output_len))))
+    elif name == "jsonl":
+        with open(path) as f:
+            for line in f:
+                if line.strip():
+                    o = json.loads(line)
+                    items.append(SampleRequest(o["prompt"], int(o.get("output_len", output_len))))
+    else:
+        raise ValueError(f"unknown dataset {name!r} (random | sharegpt | jsonl)")
+    if not items:
+        raise ValueError(f"{path} holds no usable request")
+    order = rng.permutation(len(items))
+    return [items[order[i % len(items)]] for i in range(num_prompts)]
+
+
+async def _one(session, url, model, prompt_ids, output_len, chat: bool = False) -> RequestResult:
+    body = {"model": model, "max_tokens": output_len, "temperature": 0.0,
             "ignore_eos": True, "stream": True, "stream_options": {"include_usage": True}}
-    r = RequestResult(prompt_tokens=len(prompt_ids))
+    if chat:
+        body["messages"] = [{"role": "user", "content": prompt_ids if isinstance(prompt_ids, str) else
+                             " ".join(map(str, prompt_ids))}]
+    else:
+        body["prompt"] = prompt_ids
+    r = RequestResult(prompt_tokens=len(prompt_ids) if not isinstance(prompt_ids, str) else 0)
     t0 = time.perf_counter()
     last = t0
     try:
@@ -58,6 +108,7 @@ async def _one(session, url, model, prompt_ids, output_len) -> RequestResult:
                 now = time.perf_counter()
                 if obj.get("usage"):
                     r.output_tokens = obj["usage"]["completion_tokens"]
+                    r.prompt_tokens = obj["usage"].get("prompt_tokens", r.prompt_tokens)
                 if obj.get("choices"):
                     if r.ttft == 0.0:
                         r.ttft = now - t0
@@ -72,21 +123,34 @@ async def _one(session, url, model, prompt_ids, output_len) -> RequestResult:
 
 
 async def run_benchmark(base_url: str, model: str, num_prompts: int, max_concurrency: int, input_len: int,
-                        output_len: int, vocab_size: int = 256, seed: int = 0) -> dict:
+                        output_len: int, vocab_size: int = 256, seed: int = 0, request_rate: float = 0.0,
+                        dataset: str = "random", dataset_path: Optional[str] = None, chat: bool = False) -> dict:
+    """One run. ``request_rate`` > 0: requests arrive as a Poisson process of that rate (requests / s) and
+    ``max_concurrency`` (0 = unbounded) only caps how many are in flight; otherwise a closed loop keeps
+    ``max_concurrency`` requests in flight."""
     import aiohttp
 
-    rng = np.random.default_rng(seed)
-    prompts = [rng.integers(0, vocab_size, size=input_len).tolist() for _ in range(num_prompts)]
-    sem = asyncio.Semaphore(max_concurrency)
-    url = base_url.rstrip("/") + "/v1/completions"
+    reqs = load_dataset(dataset, num_prompts, dataset_path, input_len, output_len, vocab_size, seed)
+    sem = asyncio.Semaphore(max_concurrency) if max_concurrency > 0 else None
+    url = base_url.rstrip("/") + ("/v1/chat/completions" if chat else "/v1/completions")
     timeout = aiohttp.ClientTimeout(total=6 * 3600)
+    gaps = np.random.default_rng(seed + 1).exponential(1.0 / request_rate, size=num_prompts) if request_rate > 0 else None
     async with aiohttp.ClientSession(timeout=timeout) as session:
-        async def guarded(p):
+        async def guarded(q):
+            if sem is None:
+                return await _one(session, url, model, q.prompt, q.output_len, chat)
             async with sem:
-                return await _one(session, url, model, p, output_len)
+                return await _one(session, url, model, q.prompt, q.output_len, chat)
 
         t0 = time.perf_counter()
-        results = await asyncio.gather(*(guarded(p) for p in prompts))
+        if gaps is None:
+            results = await asyncio.gather(*(guarded(q) for q in reqs))
+        else:
+            tasks = []
+            for q, gap in zip(reqs, gaps):
+                tasks.append(asyncio.create_task(guarded(q)))
+                await asyncio.sleep(float(gap))
+            results = await asyncio.gather(*tasks)
         wall = time.perf_counter() - t0
     ok = [r for r in results if r.ok]
     tpots = [(r.latency - r.ttft) / (r.output_tokens - 1) for r in ok if r.output_tokens > 1]
@@ -103,5 +167,19 @@ async def run_benchmark(base_url: str, model: str, num_prompts: int, max_concurr
         "p50_itl_ms": ms(percentile(itls, 50)), "p99_itl_ms": ms(percentile(itls, 99)),
         "errors": [r.error for r in results if r.error][:3],
         "config": {"num_prompts": num_prompts, "max_concurrency": max_concurrency, "input_len": input_len,
-                   "output_len": output_len},
+                   "output_len": output_len, "request_rate": request_rate, "dataset": dataset, "chat": chat},
     }
+
+
+async def run_sweep(base_url: str, model: str, num_prompts: int, concurrencies=(), request_rates=(), rate_cap: int = 0,
+                    **kw) -> list:
+    """The same workload at several concurrencies (closed loop) and / or request rates (open loop): one result per
+    point, in order, each tagged with its load."""
+    out = []
+    for c in concurrencies:
+        r = await run_benchmark(base_url, model, max(num_prompts, int(c)), int(c), **kw)
+        out.append(dict(r, load={"max_concurrency": int(c)}))
+    for rate in request_rates:
+        r = await run_benchmark(base_url, model, num_prompts, rate_cap, request_rate=float(rate), **kw)
+        out.append(dict(r, load={"request_rate": float(rate)}))
+    return out

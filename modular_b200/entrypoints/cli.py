@@ -205,13 +205,32 @@ def serve(config_file, port, host, max_queue_size, headless, pretty_print_config
 @click.option("--output-len", default=32, type=int)
 @click.option("--vocab-size", default=256, type=int)
 @click.option("--seed", default=0, type=int)
-def benchmark(base_url, model, num_prompts, max_concurrency, input_len, output_len, vocab_size, seed):
-    """Closed-loop serving benchmark against a running server (random-token dataset)."""
-    from ..benchmark.benchmark_serving import run_benchmark
+@click.option("--request-rate", default=0.0, type=float, help="open loop: Poisson arrivals at this rate (requests / s)")
+@click.option("--dataset-name", default="random", type=click.Choice(["random", "sharegpt", "jsonl"]))
+@click.option("--dataset-path", default=None, type=click.Path())
+@click.option("--chat", is_flag=True, help="send /v1/chat/completions requests")
+@click.option("--sweep-concurrency", default=None, help="comma-separated concurrencies: one closed-loop run each")
+@click.option("--sweep-request-rate", default=None, help="comma-separated request rates: one open-loop run each")
+@click.option("--result-file", default=None, type=click.Path(), help="also write the result JSON here")
+def benchmark(base_url, model, num_prompts, max_concurrency, input_len, output_len, vocab_size, seed, request_rate,
+              dataset_name, dataset_path, chat, sweep_concurrency, sweep_request_rate, result_file):
+    """Serving benchmark against a running server: closed loop (--max-concurrency), open loop (--request-rate) or
+    a sweep over either; random, ShareGPT-format or JSONL requests."""
+    from ..benchmark.benchmark_serving import run_benchmark, run_sweep
 
-    res = asyncio.run(run_benchmark(base_url, model, num_prompts, max_concurrency, input_len, output_len,
-                                    vocab_size, seed))
-    click.echo(json.dumps(res, indent=1))
+    common = dict(input_len=input_len, output_len=output_len, vocab_size=vocab_size, seed=seed, dataset=dataset_name,
+                  dataset_path=dataset_path, chat=chat)
+    if sweep_concurrency or sweep_request_rate:
+        cs = [int(x) for x in (sweep_concurrency or "").split(",") if x]
+        rs = [float(x) for x in (sweep_request_rate or "").split(",") if x]
+        res = asyncio.run(run_sweep(base_url, model, num_prompts, cs, rs, **common))
+    else:
+        res = asyncio.run(run_benchmark(base_url, model, num_prompts, max_concurrency, request_rate=request_rate, **common))
+    text = json.dumps(res, indent=1)
+    if result_file:
+        with open(result_file, "w") as f:
+            f.write(text)
+    click.echo(text)
 
 
 if __name__ == "__main__":

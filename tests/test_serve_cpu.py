@@ -448,3 +448,56 @@ def test_tracing_spans_for_requests_and_batches(tmp_path):
         del os.environ["MAX_SERVE_TRACE_FILE"]
     rec = json.loads(path.read_text().splitlines()[0])
     assert rec["name"] == "max.batch" and rec["attributes"]["batch.size"] == 3
+
+
+def test_benchmark_client_loads_datasets_and_sweeps(tmp_path):
+    """The benchmark client against a real HTTP server (echo model): closed loop, Poisson open loop, a concurrency
+    sweep, and the ShareGPT / JSONL dataset readers."""
+    import asyncio
+    import socket
+    import threading
+    import time
+
+    import uvicorn
+
+    from modular_b200.benchmark.benchmark_serving import load_dataset, run_benchmark, run_sweep
+
+    share = tmp_path / "share.json"
+    share.write_text(json.dumps([
+        {"conversations": [{"from": "human", "value": "tell me a story"}, {"from": "gpt", "value": "once upon a time " * 3}]},
+        {"conversations": [{"from": "gpt", "value": "no human turn"}]},
+        {"conversations": [{"from": "human", "value": "second prompt"}, {"from": "gpt", "value": "short"}]}]))
+    reqs = load_dataset("sharegpt", 5, str(share))
+    assert len(reqs) == 5 and {r.prompt for r in reqs} == {"tell me a story", "second prompt"}
+    assert {r.output_len for r in reqs} == {16, 1}
+    jl = tmp_path / "reqs.jsonl"
+    jl.write_text('{"prompt": [1, 2, 3], "output_len": 4}\n{"prompt": "text prompt"}\n')
+    assert [r.output_len for r in load_dataset("jsonl", 2, str(jl), output_len=7, seed=1)] in ([4, 7], [7, 4])
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    app = fastapi_app(Settings(max_queue_size=64), _config(model_path="echo", devices="cpu"), ByteTokenizer(),
+                      EchoPipeline, "echo", 4096)
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="warning"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    try:
+        for _ in range(200):
+            if server.started:
+                break
+            time.sleep(0.05)
+        assert server.started
+        base = f"http://127.0.0.1:{port}"
+        closed = asyncio.run(run_benchmark(base, "echo", 6, 3, 16, 4))
+        assert closed["completed"] == 6 and closed["failed"] == 0 and closed["output_token_throughput"] > 0
+        opened = asyncio.run(run_benchmark(base, "echo", 5, 0, 16, 4, request_rate=200.0))
+        assert opened["completed"] == 5 and opened["config"]["request_rate"] == 200.0
+        sweep = asyncio.run(run_sweep(base, "echo", 4, concurrencies=(1, 4), request_rates=(100.0,), input_len=8, output_len=3))
+        assert [p["load"] for p in sweep] == [{"max_concurrency": 1}, {"max_concurrency": 4}, {"request_rate": 100.0}]
+        assert all(p["completed"] >= 4 for p in sweep)
+        chat = asyncio.run(run_benchmark(base, "echo", 2, 2, 8, 3, dataset="jsonl", dataset_path=str(jl), chat=True))
+        assert chat["completed"] == 2, chat
+    finally:
+        server.should_exit = True
+        th.join(timeout=10)
