@@ -586,6 +586,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("bn") = 0, py::arg("stages") = 0, py::arg("mode") = -1, py::arg("pdl") = false,
         py::arg("packed") = false);
   m.def("gemm_persistent_sizes", &gemm_persistent_sizes);
+  m.def("set_gemm_dec_tile_epilogue", [](bool on) { mb_set_gemm_dec_tile_epilogue(on ? 1 : 0); }, py::arg("on"));
   m.def("gemm_dec_sizes", []() {
     return py::make_tuple(static_cast<int64_t>(mb_gemm_dec_workspace_bytes(num_sms())), mb_gemm_dec_state_ints(),
                           mb_gemm_dec_max_tokens());

@@ -35,6 +35,10 @@ constexpr int kDecArrive = 0;
 constexpr int kDecDepart = 1;
 constexpr int kDecGen = 2;
 constexpr int kDecGenRows = 3;                      // 3..5
-constexpr int kDecStateInts = 8;
+//   kDecTileCnt + j   contributors of output tile (or gate / up tile pair) j that have written their partial; the
+//                     one that completes the count runs the tile's epilogue and clears the word
+constexpr int kDecTileCnt = 8;
+constexpr int kDecTileCounters = 4096;
+constexpr int kDecStateInts = kDecTileCnt + kDecTileCounters;
 
 }  // namespace mb

@@ -73,6 +73,10 @@ struct Params {
   // that start at b * x_boff and produce the bN columns of Y that start at b * y_boff
   int bN, x_boff, y_boff;
   int inter;               // mode 1: gate rows [0, inter), up rows [inter, 2 inter)
+  // modes 0 / 1 without the grid-wide meeting point: the CTA whose partial completes an output tile (mode 1: a
+  // gate tile and its up tile) reduces and stores that tile; the other CTAs leave as soon as their partials are
+  // written
+  int tile_epi;
   __nv_bfloat16* h;        // mode 2: residual stream [M, N], updated in place
   __nv_bfloat16* xn;       // mode 2: normalised rows [M, N]
   const __nv_bfloat16* gamma;
@@ -91,6 +95,7 @@ struct Tail {
   uint32_t tmem_base;
   int abort_word;
   int flag;
+  int tile_last;
   float red[kThreads / 32];
 };
 
@@ -178,6 +183,14 @@ __device__ __forceinline__ void reduce8(const Params& p, int t, int n, float (&a
       acc[4] += b[j].x; acc[5] += b[j].y; acc[6] += b[j].z; acc[7] += b[j].w;
     }
   }
+}
+
+// CTAs whose shares touch `tile`
+__device__ __forceinline__ int tile_contributors(const Params& p, int tile) {
+  const uint32_t fu = static_cast<uint32_t>(tile) * p.kb;
+  const int g_first = static_cast<int>(((fu + 1u) * static_cast<uint32_t>(p.G) - 1u) / p.units);
+  const int g_last = static_cast<int>(((fu + static_cast<uint32_t>(p.kb)) * static_cast<uint32_t>(p.G) - 1u) / p.units);
+  return g_last - g_first + 1;
 }
 
 __device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
@@ -349,7 +362,56 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
+      if (p.tile_epi) {
+        // count this CTA's partial of the tile in; the four drain warps act as one group of 128 threads
+        const int tiles_inter = p.inter >> 7;
+        const int n_tile = s.tile;                       // m_tiles == 1
+        const int cnt_idx = (p.mode == 1 && n_tile >= tiles_inter) ? n_tile - tiles_inter : n_tile;
+        __threadfence();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          int want = tile_contributors(p, cnt_idx);
+          if (p.mode == 1) want += tile_contributors(p, cnt_idx + tiles_inter);
+          const int prev = atomicAdd(p.state + kDecTileCnt + cnt_idx, 1);
+          tail->tile_last = prev == want - 1 ? 1 : 0;
+          if (prev == want - 1) p.state[kDecTileCnt + cnt_idx] = 0;     // ready for the next launch
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (tail->tile_last != 0) {
+          __threadfence();
+          const int tid = (warp - 2) * 32 + lane;
+          const int n0 = cnt_idx << 7;
+          const int ncols = min(128, (p.mode == 1 ? p.inter : p.N) - n0);
+          const int chunks = ncols >> 3;
+          for (int c = tid; c < p.M * chunks; c += 128) {
+            const int t = c / chunks;
+            const int n = n0 + ((c - t * chunks) << 3);
+            float v[8];
+            reduce8(p, t, n, v);
+            if (p.mode == 1) {
+              float u[8];
+              reduce8(p, t, p.inter + n, u);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = silu_f(v[i]) * u[i];
+            }
+            const int col = p.bN > 0 ? (n / p.bN) * p.y_boff + n % p.bN : n;
+            *reinterpret_cast<uint4*>(p.Y + static_cast<size_t>(t) * p.ldy + col) = pack_bf16x8(v);
+          }
+        }
+      }
     }
+  }
+
+  if (p.tile_epi) {
+    // no meeting point: leave once every role of this CTA is done
+    tc_fence_before();
+    __syncthreads();
+    MB_DEC_STAMP(5);
+    if (warp == 1) {
+      tc_fence_after();
+      tmem_dealloc(tmem_base, p.tmem_cols);
+    }
+    return;
   }
 
   // ------------------------------------------------------------------ grid-wide meeting point
@@ -554,6 +616,8 @@ static unsigned long long* g_dec_trace = nullptr;
 // [0] start, [1] weight prefetch issued, [2] dependencies done, [3] partials written, [4] all CTAs arrived,
 // [5] epilogue done. nullptr turns it off.
 extern "C" void mb_set_gemm_dec_trace(void* buf) { g_dec_trace = static_cast<unsigned long long*>(buf); }
+static int g_dec_tile_epi = 1;    // modes 0 / 1: per-tile last-arriver epilogue instead of the grid-wide meeting point
+extern "C" void mb_set_gemm_dec_tile_epilogue(int on) { g_dec_tile_epi = on; }
 static int g_dec_smem_kb = 200;   // ring budget (measured on B200: chains of decode GEMMs run 8 % faster with 150-200 KB than with 100)
 extern "C" void mb_set_gemm_dec_smem_kb(int kb) { g_dec_smem_kb = kb < 40 ? 40 : (kb > 200 ? 200 : kb); }
 
@@ -632,6 +696,7 @@ static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int 
   p.Y = static_cast<__nv_bfloat16*>(Y); p.ldy = ldy;
   p.bN = bN; p.x_boff = x_boff; p.y_boff = y_boff;
   p.inter = mode == 1 ? N / 2 : 0;
+  p.tile_epi = (g_dec_tile_epi && mode != 2 && p.tiles <= kDecTileCounters && (mode == 0 || p.inter % kBM == 0)) ? 1 : 0;
   p.h = static_cast<__nv_bfloat16*>(h); p.xn = static_cast<__nv_bfloat16*>(xn);
   p.gamma = static_cast<const __nv_bfloat16*>(gamma);
   p.eps = eps; p.w_off = w_off; p.mbc = mbc;
