@@ -586,6 +586,29 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("bn") = 0, py::arg("stages") = 0, py::arg("mode") = -1, py::arg("pdl") = false,
         py::arg("packed") = false);
   m.def("gemm_persistent_sizes", &gemm_persistent_sizes);
+  // QKV projection + rotary embedding + KV-cache store of a decode step in one launch (head_dim 128, rotate-half)
+  m.def("gemm_dec_qkv_rope", [](const Tensor& x, const Tensor& w, Tensor& qkv, const Tensor& positions,
+                                const Tensor& slots, const Tensor& cos_sin, Tensor& k_cache, Tensor& v_cache, int n_q,
+                                int n_kv, Tensor& ws, Tensor& state) {
+    need_cuda(x, "x");
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && qkv.stride(1) == 1 &&
+                    x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && qkv.scalar_type() == at::kBFloat16 &&
+                    positions.scalar_type() == at::kInt && slots.scalar_type() == at::kLong &&
+                    cos_sin.scalar_type() == at::kFloat && cos_sin.is_contiguous() && cos_sin.size(1) == 128 &&
+                    w.size(0) == (n_q + 2 * n_kv) * 128 && qkv.size(1) == w.size(0) && qkv.size(0) >= x.size(0) &&
+                    positions.numel() >= x.size(0) && slots.numel() >= x.size(0),
+                "gemm_dec_qkv_rope: operands");
+    TORCH_CHECK(k_cache.dim() == 4 && k_cache.stride(3) == 1 && k_cache.stride(2) == 128 && k_cache.size(3) == 128 &&
+                    v_cache.stride(0) == k_cache.stride(0) && v_cache.stride(1) == k_cache.stride(1) &&
+                    state.scalar_type() == at::kInt && state.numel() >= mb_gemm_dec_state_ints(),
+                "gemm_dec_qkv_rope: cache layout / state");
+    check_rc(mb_gemm_dec_qkv_rope(x.data_ptr(), w.data_ptr(), x.size(0), x.size(1), x.stride(0), w.stride(0),
+                                  qkv.data_ptr(), qkv.stride(0), positions.data_ptr<int32_t>(), slots.data_ptr<int64_t>(),
+                                  cos_sin.data_ptr<float>(), k_cache.data_ptr(), v_cache.data_ptr(), n_q, n_kv, 128,
+                                  k_cache.size(2), k_cache.stride(0), k_cache.stride(1), ws.data_ptr(), ws.nbytes(),
+                                  state.data_ptr<int>(), error_flag(), num_sms(), cur_stream()),
+             "gemm_dec_qkv_rope");
+  });
   m.def("set_gemm_dec_tile_epilogue", [](bool on) { mb_set_gemm_dec_tile_epilogue(on ? 1 : 0); }, py::arg("on"));
   m.def("gemm_dec_sizes", []() {
     return py::make_tuple(static_cast<int64_t>(mb_gemm_dec_workspace_bytes(num_sms())), mb_gemm_dec_state_ints(),

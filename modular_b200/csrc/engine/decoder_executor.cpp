@@ -91,12 +91,27 @@ int DecoderExecutor::forward_dec(const StepInputs& in, cudaStream_t stream) {
     const DecoderLayerWeights& w = layers[l];
     const long long hd = c.head_dim;
     char* kbase = static_cast<char*>(kv.base) + 2 * (static_cast<int64_t>(l) * kv.layer_stride);
-    MB_TRY(dec(buf.xn, w.wqkv, qkv_dim, c.hidden, 0, buf.qkv, qkv_dim, nullptr));
-    mark("gemm_qkv", stream);
-    MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, T, c.n_q,
-                            c.n_kv, c.head_dim, c.page_size, kv.page_stride, kv.head_stride, c.rope_interleaved,
-                            stream));
-    mark("rope_kv_store", stream);
+    // one launch for the projection, the rotation and the cache store where the kernel takes the shape
+    int fused = MB_ERR_SHAPE;
+    if (!c.rope_interleaved)
+      fused = mb_gemm_dec_qkv_rope(buf.xn, w.wqkv, T, c.hidden, c.hidden, c.hidden, buf.qkv, qkv_dim, in.positions,
+                                   in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, c.n_q, c.n_kv, c.head_dim,
+                                   c.page_size, kv.page_stride, kv.head_stride, buf.dec_ws, buf.dec_ws_bytes,
+                                   buf.dec_state, buf.err, c.num_sms, stream);
+    if (fused == MB_OK) {
+      launches += 1;
+      mark("gemm_qkv+rope+store", stream);
+    } else if (fused != MB_ERR_SHAPE) {
+      return fused;
+    } else {
+      MB_TRY(dec(buf.xn, w.wqkv, qkv_dim, c.hidden, 0, buf.qkv, qkv_dim, nullptr));
+      mark("gemm_qkv", stream);
+      MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, T, c.n_q,
+                              c.n_kv, c.head_dim, c.page_size, kv.page_stride, kv.head_stride, c.rope_interleaved,
+                              stream));
+      launches += 1;
+      mark("rope_kv_store", stream);
+    }
     if (c.attn_impl == 1 && c.page_size % 64 == 0) {
       MB_TRY(mb_paged_attention_tma(
           buf.qkv, qkv_dim, buf.attn, q_dim, kv.base, kv.total_elems / hd,
@@ -110,7 +125,7 @@ int DecoderExecutor::forward_dec(const StepInputs& in, cudaStream_t stream) {
                                 in.n_decode, in.decode_seq, c.n_q, c.n_kv, c.head_dim, c.page_size, kv.page_stride,
                                 kv.head_stride, c.attn_scale, stream));
     }
-    launches += 2;
+    launches += 1;
     mark("attention", stream);
     MB_TRY(dec(buf.attn, w.wo, c.hidden, q_dim, 2, nullptr, 0, w.mlp_norm));
     mark("gemm_o+ar+norm", stream);

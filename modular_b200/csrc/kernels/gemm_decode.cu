@@ -77,6 +77,17 @@ struct Params {
   // gate tile and its up tile) reduces and stores that tile; the other CTAs leave as soon as their partials are
   // written
   int tile_epi;
+  // QKV projection with the rotation and the cache store in the tile epilogue (head_dim 128: an output tile is
+  // one head; rotate-half convention). rope = 1: tiles [0, n_q) are query heads (rotated, stored to Y), the next
+  // n_kv key heads (rotated, stored to Y and to the K cache at the token's slot), the last n_kv value heads
+  // (stored to Y and to the V cache). Values are rounded to bf16 before the rotation, like the stand-alone kernel.
+  int rope, n_q, n_kv, page_size;
+  long long page_stride, head_stride;
+  const int32_t* positions;
+  const int64_t* kv_slots; // cache slot of every token row (-1: none)
+  const float* cos_sin;    // [max_pos, 128]: 64 cos then 64 sin
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
   __nv_bfloat16* h;        // mode 2: residual stream [M, N], updated in place
   __nv_bfloat16* xn;       // mode 2: normalised rows [M, N]
   const __nv_bfloat16* gamma;
@@ -377,7 +388,53 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           if (prev == want - 1) p.state[kDecTileCnt + cnt_idx] = 0;     // ready for the next launch
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (tail->tile_last != 0) {
+        if (tail->tile_last != 0 && p.rope) {
+          __threadfence();
+          const int tid = (warp - 2) * 32 + lane;
+          const int head = cnt_idx, n0 = cnt_idx << 7;
+          if (head < p.n_q + p.n_kv) {
+            // rotate: a thread takes 8 dims of the first half and their partners 64 dims further on
+            for (int c = tid; c < p.M * 8; c += 128) {
+              const int t = c >> 3, d = (c & 7) << 3;
+              float lo[8], hi[8];
+              reduce8(p, t, n0 + d, lo);
+              reduce8(p, t, n0 + 64 + d, hi);
+              const float* cs = p.cos_sin + static_cast<size_t>(p.positions[t]) * 128;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float a = __bfloat162float(__float2bfloat16_rn(lo[i])), b = __bfloat162float(__float2bfloat16_rn(hi[i]));
+                const float cc = cs[d + i], sn = cs[64 + d + i];
+                lo[i] = a * cc - b * sn;
+                hi[i] = b * cc + a * sn;
+              }
+              const uint4 vlo = pack_bf16x8(lo), vhi = pack_bf16x8(hi);
+              __nv_bfloat16* y = p.Y + static_cast<size_t>(t) * p.ldy + n0;
+              *reinterpret_cast<uint4*>(y + d) = vlo;
+              *reinterpret_cast<uint4*>(y + 64 + d) = vhi;
+              if (head >= p.n_q) {
+                const int64_t slot = p.kv_slots[t];
+                if (slot >= 0) {
+                  __nv_bfloat16* kc = p.k_cache + (slot / p.page_size) * p.page_stride + (head - p.n_q) * p.head_stride +
+                                      (slot % p.page_size) * 128;
+                  *reinterpret_cast<uint4*>(kc + d) = vlo;
+                  *reinterpret_cast<uint4*>(kc + 64 + d) = vhi;
+                }
+              }
+            }
+          } else {
+            for (int c = tid; c < p.M * 16; c += 128) {
+              const int t = c >> 4, d = (c & 15) << 3;
+              float v[8];
+              reduce8(p, t, n0 + d, v);
+              const uint4 o = pack_bf16x8(v);
+              *reinterpret_cast<uint4*>(p.Y + static_cast<size_t>(t) * p.ldy + n0 + d) = o;
+              const int64_t slot = p.kv_slots[t];
+              if (slot >= 0)
+                *reinterpret_cast<uint4*>(p.v_cache + (slot / p.page_size) * p.page_stride +
+                                          (head - p.n_q - p.n_kv) * p.head_stride + (slot % p.page_size) * 128 + d) = o;
+            }
+          }
+        } else if (tail->tile_last != 0) {
           __threadfence();
           const int tid = (warp - 2) * 32 + lane;
           const int n0 = cnt_idx << 7;
@@ -671,11 +728,21 @@ extern "C" int mb_gemm_dec_plan(int M, int N, int K, int mode, size_t ws_bytes, 
 // All ranks must issue the same sequence of mode-2 calls. Launches that share `ws` / `state` must not
 // overlap on the device. Returns MB_ERR_SHAPE / MB_ERR_TOO_LARGE for shapes this kernel does not take
 // (see mb_gemm_dec_plan); the caller then uses the tiled kernels.
+struct DecRope {
+  int n_q, n_kv, page_size;
+  long long page_stride, head_stride;
+  const int32_t* positions;
+  const int64_t* slots;
+  const float* cos_sin;
+  void* k_cache;
+  void* v_cache;
+};
+
 static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int ldx, int ldw, int mode,
                          void* Y, int ldy, void* h, void* xn, const void* gamma, float eps, float w_off,
                          int mbc, int world, int rank, void* const* lam, int lam_rows, void* ws,
                          size_t ws_bytes, int* state, int* err, int num_sms, cudaStream_t stream, int bN, int x_boff,
-                         int y_boff, int x_cols) {
+                         int y_boff, int x_cols, const DecRope* rope = nullptr) {
   using namespace mb::dec;
   if (M <= 0 || N <= 0) return MB_OK;
   if (ldx % 8 || ldw % 8 || (mode != 2 && ldy % 8)) return MB_ERR_SHAPE;
@@ -697,6 +764,14 @@ static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int 
   p.bN = bN; p.x_boff = x_boff; p.y_boff = y_boff;
   p.inter = mode == 1 ? N / 2 : 0;
   p.tile_epi = (g_dec_tile_epi && mode != 2 && p.tiles <= kDecTileCounters && (mode == 0 || p.inter % kBM == 0)) ? 1 : 0;
+  p.rope = 0;
+  if (rope != nullptr) {
+    if (!p.tile_epi || mode != 0 || N != (rope->n_q + 2 * rope->n_kv) * 128) return MB_ERR_SHAPE;
+    p.rope = 1; p.n_q = rope->n_q; p.n_kv = rope->n_kv; p.page_size = rope->page_size;
+    p.page_stride = rope->page_stride; p.head_stride = rope->head_stride;
+    p.positions = rope->positions; p.kv_slots = rope->slots; p.cos_sin = rope->cos_sin;
+    p.k_cache = static_cast<__nv_bfloat16*>(rope->k_cache); p.v_cache = static_cast<__nv_bfloat16*>(rope->v_cache);
+  }
   p.h = static_cast<__nv_bfloat16*>(h); p.xn = static_cast<__nv_bfloat16*>(xn);
   p.gamma = static_cast<const __nv_bfloat16*>(gamma);
   p.eps = eps; p.w_off = w_off; p.mbc = mbc;
@@ -738,4 +813,19 @@ extern "C" int mb_gemm_dec_batched(const void* X, const void* W, void* Y, int B,
   if (N % mb::dec::kBM || K % mb::dec::kBK || x_off % 8 || y_off % 8 || x_off <= 0 || y_off < N) return MB_ERR_SHAPE;
   return gemm_dec_impl(X, W, M, B * N, K, ldx, K, 0, Y, ldy, nullptr, nullptr, nullptr, 0.f, 0.f, 0, 1, 0, nullptr, 0, ws,
                        ws_bytes, state, err, num_sms, stream, N, x_off, y_off, x_cols);
+}
+
+// QKV projection of a decode step with the rotary embedding and the KV-cache store in its tile epilogue
+// (head_dim 128, rotate-half convention): what mb_gemm_dec (mode 0) followed by mb_rope_kv_store computes, in
+// one launch. Returns MB_ERR_SHAPE when the per-tile epilogue is switched off or the shape does not fit; the
+// caller then runs the two kernels.
+extern "C" int mb_gemm_dec_qkv_rope(const void* X, const void* W, int M, int K, int ldx, int ldw, void* qkv, int ldy,
+                                    const int32_t* positions, const int64_t* slots, const float* cos_sin, void* k_cache,
+                                    void* v_cache, int n_q, int n_kv, int head_dim, int page_size,
+                                    long long page_stride, long long head_stride, void* ws, size_t ws_bytes, int* state,
+                                    int* err, int num_sms, cudaStream_t stream) {
+  if (head_dim != 128 || !g_dec_tile_epi) return MB_ERR_SHAPE;
+  DecRope r{n_q, n_kv, page_size, page_stride, head_stride, positions, slots, cos_sin, k_cache, v_cache};
+  return gemm_dec_impl(X, W, M, (n_q + 2 * n_kv) * 128, K, ldx, ldw, 0, qkv, ldy, nullptr, nullptr, nullptr, 0.f, 0.f, 0,
+                       1, 0, nullptr, 0, ws, ws_bytes, state, err, num_sms, stream, 0, 0, 0, 0, &r);
 }

@@ -489,6 +489,38 @@ def test_mla_post_down_matches_composed_ops(T, QL):
 
 
 # ---------------------------------------------------------------------------- decode-step GEMM
+@pytest.mark.parametrize("M,n_q,n_kv,K", [(64, 32, 8, 4096), (1, 4, 1, 4096), (37, 8, 2, 1024), (256, 16, 4, 512)])
+def test_gemm_decode_qkv_rope_store_equals_the_two_kernels(M, n_q, n_kv, K):
+    """QKV projection with rotation and cache store in its tile epilogue against decode GEMM + rope_kv_store."""
+    from modular_b200._native import lib
+    from modular_b200.nn.rotary_embedding import cos_sin_table
+
+    torch.manual_seed(40)
+    page, pages, hd = 16, 40, 128
+    N = (n_q + 2 * n_kv) * hd
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    cs = cos_sin_table(hd, 2048, 500000.0, None, DEV)
+    pos = torch.randint(0, 2048, (M,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(page * pages, device=DEV)[:M].long()
+    if M > 2:
+        slots[M // 2] = -1
+    mk = lambda: torch.zeros(pages, 2, n_kv, page, hd, device=DEV, dtype=torch.bfloat16)
+    kv_a, kv_b = mk(), mk()
+    want = ops.linear_decode(x, w)
+    ops.rope_kv_store(want, pos, slots, cs, kv_a[:, 0], kv_a[:, 1], n_q, n_kv, hd)
+    got = torch.zeros_like(want)
+    ws, state = ops.decode_gemm_workspace(DEV)
+    for _ in range(2):        # the second call finds the tile counters cleared
+        lib().gemm_dec_qkv_rope(x, w, got, pos, slots, cs, kv_b[:, 0], kv_b[:, 1], n_q, n_kv, ws, state)
+    torch.cuda.synchronize()
+    ops.check_device_error()
+    assert torch.equal(got[:, n_q * hd:], want[:, n_q * hd:]) or torch.allclose(got.float(), want.float(), rtol=8e-3, atol=2e-3)
+    assert torch.allclose(got.float(), want.float(), rtol=8e-3, atol=2e-3)
+    assert torch.allclose(kv_b.float(), kv_a.float(), rtol=8e-3, atol=2e-3)
+    assert torch.equal(kv_b[:, 1], kv_a[:, 1])            # values are copied, not rotated
+
+
 @pytest.mark.parametrize("M,N,K", [(64, 6144, 4096), (64, 4096, 4096), (64, 4096, 14336), (1, 8192, 8192),
                                    (16, 1024, 1024), (100, 4096, 512), (256, 4096, 1792), (33, 1536, 4160),
                                    (8, 128, 64), (129, 768, 2048)])
