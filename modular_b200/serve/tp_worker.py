@@ -90,7 +90,11 @@ class ShardedFeed:
         self.group, self.rank, self.world = ctl_group, rank, world
         self.requests: "queue.SimpleQueue" = queue.SimpleQueue()
         self.cancels: "queue.SimpleQueue" = queue.SimpleQueue()
-        self._next_owner = 0
+        # rank 0 deals every new request to the rank with the fewest outstanding tokens (prompt tokens not yet
+        # encoded weigh in full, a decoding request as one token per step), as the reference balances context
+        # encoding over its data-parallel replicas (scheduler/batch_constructor/text_batch_constructor.py:566-594)
+        self._outstanding = [0] * world
+        self._owner_cost: dict = {}
         self.any_busy = False
         self.arrived = 0
         self.iterations = 0
@@ -103,8 +107,11 @@ class ShardedFeed:
         if self.rank == 0:
             frames = []
             for c in new_ctxs:
-                frames.append((self._next_owner, codec.encode(c)))
-                self._next_owner = (self._next_owner + 1) % self.world
+                owner = min(range(self.world), key=lambda r: (self._outstanding[r], r))
+                cost = int(c.tokens.prompt_len) + int(c.max_new_tokens_effective)
+                self._outstanding[owner] += cost
+                self._owner_cost[c.request_id] = (owner, cost)
+                frames.append((owner, codec.encode(c)))
             box[0] = {"new": frames, "cancel": list(cancels), "stop": stop}
         dist.broadcast_object_list(box, src=0, group=self.group)
         msg = box[0]
@@ -133,7 +140,13 @@ class ShardedFeed:
         for r, g in enumerate(got):
             if g.get("load") is not None:
                 self.rank_loads[r] = g["load"]
-        return [codec.decode(f) for g in got for f in g["out"]]
+        responses = [codec.decode(f) for g in got for f in g["out"]]
+        for batch in responses:
+            for rid, o in batch.items():
+                if o.is_done and rid in self._owner_cost:
+                    owner, cost = self._owner_cost.pop(rid)
+                    self._outstanding[owner] -= cost
+        return responses
 
 
 def _drain_simple(q) -> list:
