@@ -412,6 +412,7 @@ class PyDecoderExecutor {
     c.attn_impl = cfg.contains("attn_impl") ? cfg["attn_impl"].cast<int>() : 1;
     c.dec_max_tokens = cfg.contains("dec_max_tokens") ? cfg["dec_max_tokens"].cast<int>() : 0;
     if (c.dec_max_tokens > mb_gemm_dec_max_tokens()) c.dec_max_tokens = mb_gemm_dec_max_tokens();
+    c.prefetch_weights = cfg.contains("prefetch_weights") ? cfg["prefetch_weights"].cast<int>() : 0;
     ex.buf.p_ws = nullptr;
     ex.buf.p_counters = nullptr;
     c.num_sms = num_sms();
@@ -609,6 +610,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                   state.data_ptr<int>(), error_flag(), num_sms(), cur_stream()),
              "gemm_dec_qkv_rope");
   });
+  m.def("set_gemm_dec_rope", [](bool on) { mb_set_gemm_dec_rope(on ? 1 : 0); }, py::arg("on"));
   m.def("set_gemm_dec_tile_epilogue", [](bool on) { mb_set_gemm_dec_tile_epilogue(on ? 1 : 0); }, py::arg("on"));
   m.def("gemm_dec_sizes", []() {
     return py::make_tuple(static_cast<int64_t>(mb_gemm_dec_workspace_bytes(num_sms())), mb_gemm_dec_state_ints(),

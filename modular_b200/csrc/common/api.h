@@ -105,6 +105,7 @@ int mb_mla_post_down(const void* qkv_a, int ld, int q_lora, int R, const void* g
 int mb_mla_q_rope(const void* q, int n_heads, int nope, const int32_t* positions, const float* cos_sin, void* q_rope,
                   int T, cudaStream_t stream);
 void mb_set_gemm_dec_tile_epilogue(int on);
+void mb_set_gemm_dec_rope(int on);
 int mb_gemm_dec_qkv_rope(const void* X, const void* W, int M, int K, int ldx, int ldw, void* qkv, int ldy,
                          const int32_t* positions, const int64_t* slots, const float* cos_sin, void* k_cache,
                          void* v_cache, int n_q, int n_kv, int head_dim, int page_size, long long page_stride,

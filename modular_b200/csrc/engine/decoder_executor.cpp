@@ -208,15 +208,17 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
     }
     if (persistent && buf.p_ws != nullptr) {
       launches += 1;
-      return mb_gemm_bf16_persistent(X, W, Y, R, M, N, K, ldx, K, ldy, ldy, flags | (c.use_pdl ? 8 : 0),
-                                     0, 0, mode, buf.p_ws, buf.p_counters, buf.err, c.num_sms, stream);
+      return mb_gemm_bf16_persistent(X, W, Y, R, M, N, K, ldx, K, ldy, ldy,
+                                     flags | (c.use_pdl ? 8 : 0) | (c.prefetch_weights ? 128 : 0), 0, 0, mode, buf.p_ws,
+                                     buf.p_counters, buf.err, c.num_sms, stream);
     }
     int bn, splits, stages;
     mb_gemm_bf16_plan(M, N, K, flags & 1, c.num_sms, &bn, &splits, &stages);
     if (static_cast<size_t>(splits) * M * N * sizeof(float) > buf.workspace_bytes) splits = 1;
     launches += splits > 1 ? 2 : 1;
-    return mb_gemm_bf16(X, W, Y, R, M, N, K, ldx, K, ldy, ldy, flags, bn, splits, stages,
-                        buf.workspace, buf.err, c.num_sms, stream);
+    // bit 7: the weights of the model are written by no kernel of the step
+    return mb_gemm_bf16(X, W, Y, R, M, N, K, ldx, K, ldy, ldy, flags | (c.prefetch_weights ? 128 : 0), bn, splits,
+                        stages, buf.workspace, buf.err, c.num_sms, stream);
   };
 
   mark("begin", stream);
@@ -335,14 +337,14 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
   auto gemm = [&](const void* X, const void* Wt, void* Y, int M, int N, int K, int ldx, int ldy, int flags) {
     if ((flags & 1) && buf.p_ws != nullptr) {
       launches += 1;
-      return mb_gemm_bf16_persistent(X, Wt, Y, nullptr, M, N, K, ldx, K, ldy, ldy, flags, 0, 0, 0,
+      return mb_gemm_bf16_persistent(X, Wt, Y, nullptr, M, N, K, ldx, K, ldy, ldy, flags | (c.prefetch_weights ? 128 : 0), 0, 0, 0,
                                      buf.p_ws, buf.p_counters, buf.err, c.num_sms, stream);
     }
     int bn, splits, stages;
     mb_gemm_bf16_plan(M, N, K, flags & 1, c.num_sms, &bn, &splits, &stages);
     if (static_cast<size_t>(splits) * M * N * sizeof(float) > buf.workspace_bytes) splits = 1;
     launches += splits > 1 ? 2 : 1;
-    return mb_gemm_bf16(X, Wt, Y, nullptr, M, N, K, ldx, K, ldy, ldy, flags, bn, splits, stages,
+    return mb_gemm_bf16(X, Wt, Y, nullptr, M, N, K, ldx, K, ldy, ldy, flags | (c.prefetch_weights ? 128 : 0), bn, splits, stages,
                         buf.workspace, buf.err, c.num_sms, stream);
   };
   // Fused paths (tp.fused bit0 / bit1, independent):

@@ -46,6 +46,7 @@ struct DecoderConfig {
   int attn_impl;              // 0 = cp.async kernels, 1 = TMA-fed single-launch kernel (page_size % 64 == 0)
   int num_sms;
   int dec_max_tokens;         // steps of up to this many tokens run the decode-step GEMMs (0 = never)
+  int prefetch_weights;       // tiled GEMMs request their first weight tiles before the programmatic-dependency wait
 };
 
 struct DecoderBuffers {

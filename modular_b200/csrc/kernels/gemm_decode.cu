@@ -220,6 +220,49 @@ __device__ __forceinline__ void unpack_add(const uint4& v, float (&acc)[8]) {
   }
 }
 
+// One work item of the QKV epilogue with rotation: token t, head `head`, dims [d, d + 8) and their partners 64
+// further on (rotate-half). Query heads go to Y, key heads to Y and the K cache.
+__device__ __forceinline__ void qkv_rotate_item(const Params& p, int t, int head, int d) {
+  const int n0 = head << 7;
+  float lo[8], hi[8];
+  reduce8(p, t, n0 + d, lo);
+  reduce8(p, t, n0 + 64 + d, hi);
+  const float* cs = p.cos_sin + static_cast<size_t>(p.positions[t]) * 128;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float a = __bfloat162float(__float2bfloat16_rn(lo[i])), b = __bfloat162float(__float2bfloat16_rn(hi[i]));
+    const float cc = cs[d + i], sn = cs[64 + d + i];
+    lo[i] = a * cc - b * sn;
+    hi[i] = b * cc + a * sn;
+  }
+  const uint4 vlo = pack_bf16x8(lo), vhi = pack_bf16x8(hi);
+  __nv_bfloat16* y = p.Y + static_cast<size_t>(t) * p.ldy + n0;
+  *reinterpret_cast<uint4*>(y + d) = vlo;
+  *reinterpret_cast<uint4*>(y + 64 + d) = vhi;
+  if (head >= p.n_q) {
+    const int64_t slot = p.kv_slots[t];
+    if (slot >= 0) {
+      __nv_bfloat16* kc = p.k_cache + (slot / p.page_size) * p.page_stride + (head - p.n_q) * p.head_stride +
+                          (slot % p.page_size) * 128;
+      *reinterpret_cast<uint4*>(kc + d) = vlo;
+      *reinterpret_cast<uint4*>(kc + 64 + d) = vhi;
+    }
+  }
+}
+
+// Value heads: token t, head `head` (>= n_q + n_kv), dims [d, d + 8): to Y and to the V cache.
+__device__ __forceinline__ void qkv_value_item(const Params& p, int t, int head, int d) {
+  const int n0 = head << 7;
+  float v[8];
+  reduce8(p, t, n0 + d, v);
+  const uint4 o = pack_bf16x8(v);
+  *reinterpret_cast<uint4*>(p.Y + static_cast<size_t>(t) * p.ldy + n0 + d) = o;
+  const int64_t slot = p.kv_slots[t];
+  if (slot >= 0)
+    *reinterpret_cast<uint4*>(p.v_cache + (slot / p.page_size) * p.page_stride + (head - p.n_q - p.n_kv) * p.head_stride +
+                              (slot % p.page_size) * 128 + d) = o;
+}
+
 __global__ void __launch_bounds__(kThreads)
 gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                 const Params p) {
@@ -391,48 +434,11 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         if (tail->tile_last != 0 && p.rope) {
           __threadfence();
           const int tid = (warp - 2) * 32 + lane;
-          const int head = cnt_idx, n0 = cnt_idx << 7;
+          const int head = cnt_idx;
           if (head < p.n_q + p.n_kv) {
-            // rotate: a thread takes 8 dims of the first half and their partners 64 dims further on
-            for (int c = tid; c < p.M * 8; c += 128) {
-              const int t = c >> 3, d = (c & 7) << 3;
-              float lo[8], hi[8];
-              reduce8(p, t, n0 + d, lo);
-              reduce8(p, t, n0 + 64 + d, hi);
-              const float* cs = p.cos_sin + static_cast<size_t>(p.positions[t]) * 128;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float a = __bfloat162float(__float2bfloat16_rn(lo[i])), b = __bfloat162float(__float2bfloat16_rn(hi[i]));
-                const float cc = cs[d + i], sn = cs[64 + d + i];
-                lo[i] = a * cc - b * sn;
-                hi[i] = b * cc + a * sn;
-              }
-              const uint4 vlo = pack_bf16x8(lo), vhi = pack_bf16x8(hi);
-              __nv_bfloat16* y = p.Y + static_cast<size_t>(t) * p.ldy + n0;
-              *reinterpret_cast<uint4*>(y + d) = vlo;
-              *reinterpret_cast<uint4*>(y + 64 + d) = vhi;
-              if (head >= p.n_q) {
-                const int64_t slot = p.kv_slots[t];
-                if (slot >= 0) {
-                  __nv_bfloat16* kc = p.k_cache + (slot / p.page_size) * p.page_stride + (head - p.n_q) * p.head_stride +
-                                      (slot % p.page_size) * 128;
-                  *reinterpret_cast<uint4*>(kc + d) = vlo;
-                  *reinterpret_cast<uint4*>(kc + 64 + d) = vhi;
-                }
-              }
-            }
+            for (int c = tid; c < p.M * 8; c += 128) qkv_rotate_item(p, c >> 3, head, (c & 7) << 3);
           } else {
-            for (int c = tid; c < p.M * 16; c += 128) {
-              const int t = c >> 4, d = (c & 15) << 3;
-              float v[8];
-              reduce8(p, t, n0 + d, v);
-              const uint4 o = pack_bf16x8(v);
-              *reinterpret_cast<uint4*>(p.Y + static_cast<size_t>(t) * p.ldy + n0 + d) = o;
-              const int64_t slot = p.kv_slots[t];
-              if (slot >= 0)
-                *reinterpret_cast<uint4*>(p.v_cache + (slot / p.page_size) * p.page_stride +
-                                          (head - p.n_q - p.n_kv) * p.head_stride + (slot % p.page_size) * 128 + d) = o;
-            }
+            for (int c = tid; c < p.M * 16; c += 128) qkv_value_item(p, c >> 4, head, (c & 15) << 3);
           }
         } else if (tail->tile_last != 0) {
           __threadfence();
@@ -497,7 +503,21 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   const bool run_epilogue = tail->flag != 0;
 
   // ------------------------------------------------------------------ epilogue over the output (phase B)
-  if (run_epilogue && p.mode != 2) {
+  if (run_epilogue && p.rope) {
+    // QKV projection with rotation and cache store: rotated items first (8 per token and head), then the values
+    const int rot = p.M * (p.n_q + p.n_kv) * 8;
+    const int total = rot + p.M * p.n_kv * 16;
+    for (int c = g * kThreads + threadIdx.x; c < total; c += p.G * kThreads) {
+      if (c < rot) {
+        const int t = c / ((p.n_q + p.n_kv) * 8), r = c - t * ((p.n_q + p.n_kv) * 8);
+        qkv_rotate_item(p, t, r >> 3, (r & 7) << 3);
+      } else {
+        const int c2 = c - rot;
+        const int t = c2 / (p.n_kv * 16), r = c2 - t * (p.n_kv * 16);
+        qkv_value_item(p, t, p.n_q + p.n_kv + (r >> 4), (r & 15) << 3);
+      }
+    }
+  } else if (run_epilogue && p.mode != 2) {
     const int ncols = p.mode == 1 ? p.inter : p.N;
     const int chunks_per_row = ncols >> 3;
     const int total = p.M * chunks_per_row;
@@ -673,8 +693,13 @@ static unsigned long long* g_dec_trace = nullptr;
 // [0] start, [1] weight prefetch issued, [2] dependencies done, [3] partials written, [4] all CTAs arrived,
 // [5] epilogue done. nullptr turns it off.
 extern "C" void mb_set_gemm_dec_trace(void* buf) { g_dec_trace = static_cast<unsigned long long*>(buf); }
-static int g_dec_tile_epi = 1;    // modes 0 / 1: per-tile last-arriver epilogue instead of the grid-wide meeting point
+static int g_dec_tile_epi = 0;    // modes 0 / 1: per-tile last-arriver epilogue instead of the grid-wide meeting point (off: measured
+                                  // slower on B200 from 64 tokens up, 103 vs 53 us per layer at TP8 shapes: one CTA's drain warps
+                                  // reduce a whole tile while the meeting point spreads that work over all threads of the grid)
 extern "C" void mb_set_gemm_dec_tile_epilogue(int on) { g_dec_tile_epi = on; }
+static int g_dec_rope = 0;        // QKV projection with rotation + cache store in its epilogue (mb_gemm_dec_qkv_rope); off:
+                                  // measured 2.5 % (TP2) to 9 % (TP1) slower per decode step than the two kernels under a graph
+extern "C" void mb_set_gemm_dec_rope(int on) { g_dec_rope = on; }
 static int g_dec_smem_kb = 200;   // ring budget (measured on B200: chains of decode GEMMs run 8 % faster with 150-200 KB than with 100)
 extern "C" void mb_set_gemm_dec_smem_kb(int kb) { g_dec_smem_kb = kb < 40 ? 40 : (kb > 200 ? 200 : kb); }
 
@@ -766,7 +791,7 @@ static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int 
   p.tile_epi = (g_dec_tile_epi && mode != 2 && p.tiles <= kDecTileCounters && (mode == 0 || p.inter % kBM == 0)) ? 1 : 0;
   p.rope = 0;
   if (rope != nullptr) {
-    if (!p.tile_epi || mode != 0 || N != (rope->n_q + 2 * rope->n_kv) * 128) return MB_ERR_SHAPE;
+    if (mode != 0 || N != (rope->n_q + 2 * rope->n_kv) * 128) return MB_ERR_SHAPE;
     p.rope = 1; p.n_q = rope->n_q; p.n_kv = rope->n_kv; p.page_size = rope->page_size;
     p.page_stride = rope->page_stride; p.head_stride = rope->head_stride;
     p.positions = rope->positions; p.kv_slots = rope->slots; p.cos_sin = rope->cos_sin;
@@ -817,14 +842,13 @@ extern "C" int mb_gemm_dec_batched(const void* X, const void* W, void* Y, int B,
 
 // QKV projection of a decode step with the rotary embedding and the KV-cache store in its tile epilogue
 // (head_dim 128, rotate-half convention): what mb_gemm_dec (mode 0) followed by mb_rope_kv_store computes, in
-// one launch. Returns MB_ERR_SHAPE when the per-tile epilogue is switched off or the shape does not fit; the
-// caller then runs the two kernels.
+// one launch. Returns MB_ERR_SHAPE when the shape does not fit; the caller then runs the two kernels.
 extern "C" int mb_gemm_dec_qkv_rope(const void* X, const void* W, int M, int K, int ldx, int ldw, void* qkv, int ldy,
                                     const int32_t* positions, const int64_t* slots, const float* cos_sin, void* k_cache,
                                     void* v_cache, int n_q, int n_kv, int head_dim, int page_size,
                                     long long page_stride, long long head_stride, void* ws, size_t ws_bytes, int* state,
                                     int* err, int num_sms, cudaStream_t stream) {
-  if (head_dim != 128 || !g_dec_tile_epi) return MB_ERR_SHAPE;
+  if (head_dim != 128 || !g_dec_rope) return MB_ERR_SHAPE;
   DecRope r{n_q, n_kv, page_size, page_stride, head_stride, positions, slots, cos_sin, k_cache, v_cache};
   return gemm_dec_impl(X, W, M, (n_q + 2 * n_kv) * 128, K, ldx, ldw, 0, qkv, ldy, nullptr, nullptr, nullptr, 0.f, 0.f, 0,
                        1, 0, nullptr, 0, ws, ws_bytes, state, err, num_sms, stream, 0, 0, 0, 0, &r);

@@ -71,6 +71,7 @@ struct Params {
   const int* gate_flags;
   int gate_rpr, gate_world;
   int packed_kb;     // > 0: W is pre-tiled [rows/128][K/64][128][64]; value = K/64
+  int w_static;      // W is written by no kernel of the stream: its first tiles are requested before the dependency wait
 };
 
 struct Tail {
@@ -206,7 +207,30 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
   tc_fence_after();
   const uint32_t tmem_base = tail->tmem_base;
   volatile int* abort_word = &tail->abort_word;
-  // Everything above touched only this CTA's resources; wait here for the producing kernels
+  // Static weights: fill the ring with this CTA's first weight tiles while the previous kernel drains; their
+  // activation tiles follow after the wait on the same barriers.
+  int pre = 0;
+  if (p.w_static && p.gate_flags == nullptr && warp == 0 && lane == 0) {
+    SegIter it(p, g, G);
+    Seg s;
+    int st = 0;
+    while (pre < p.stages && it.next(s)) {
+      const int n0 = (s.tile / p.m_tiles) * kBM;
+      for (int kbi = s.kb0; kbi < s.kb1 && pre < p.stages; ++kbi, ++st, ++pre) {
+        uint8_t* sa = smem + st * stage_bytes;
+        uint64_t* full_st = &tail->full[st];
+        mbar_arrive_expect_tx(full_st, stage_bytes);
+        if (p.packed_kb > 0) {
+          tma_load_2d(sa, &tmW, full_st, 0, ((n0 >> 7) * p.packed_kb + kbi) << 7);
+          if (DUAL) tma_load_2d(sa + kATile, &tmW, full_st, 0, (((p.dual_rows + n0) >> 7) * p.packed_kb + kbi) << 7);
+        } else {
+          tma_load_2d(sa, &tmW, full_st, kbi * kBK, n0);
+          if (DUAL) tma_load_2d(sa + kATile, &tmW, full_st, kbi * kBK, p.dual_rows + n0);
+        }
+      }
+    }
+  }
+  // Everything above touched only this CTA's resources and static weights; wait here for the producing kernels
   // when launched with programmatic dependent launch (no-op otherwise).
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
@@ -216,7 +240,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
       Seg s;
       // stage index and phase are carried (no division per K block): this loop and the MMA loop are on the
       // latency path of the pipeline
-      int st = 0;
+      int st = 0, issued = 0;
       uint32_t ph = 0;
       bool ok = true;
       while (ok && it.next(s)) {
@@ -231,11 +255,19 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
           if (!ok) { *abort_word = 205; break; }
         }
         for (int kbi = s.kb0; kbi < s.kb1; ++kbi) {
-          if (!mbar_wait(&tail->empty[st], ph ^ 1, abort_word, p.err, 201)) { ok = false; break; }
           uint8_t* sa = smem + st * stage_bytes;
           uint64_t* full_st = &tail->full[st];
-          mbar_arrive_expect_tx(full_st, stage_bytes);
           const int kc = kbi * kBK;
+          if (issued < pre) {
+            // armed, and its weight tile requested, before the wait
+            ++issued;
+            if (++st == p.stages) { st = 0; ph ^= 1; }
+            tma_load_2d(sa + a_bytes, &tmX, full_st, kc, t0);
+            continue;
+          }
+          ++issued;
+          if (!mbar_wait(&tail->empty[st], ph ^ 1, abort_word, p.err, 201)) { ok = false; break; }
+          mbar_arrive_expect_tx(full_st, stage_bytes);
           if (++st == p.stages) { st = 0; ph ^= 1; }
           if (p.packed_kb > 0) {
             tma_load_2d(sa, &tmW, full_st, 0, ((n0 >> 7) * p.packed_kb + kbi) << 7);
@@ -555,6 +587,7 @@ extern "C" int mb_gemm_bf16_persistent_gated(const void* X, const void* W, void*
   Params p;
   p.gate_flags = gate_flags; p.gate_rpr = gate_rpr; p.gate_world = gate_world;
   p.packed_kb = packed ? K / kBK : 0;
+  p.w_static = (flags & 128) ? 1 : 0;
   p.Y = Y; p.R = static_cast<const __nv_bfloat16*>(R);
   p.ws = static_cast<float*>(ws); p.counters = counters; p.err = err;
   p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.ldr = ldr; p.dual_rows = N;

@@ -132,7 +132,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                int ldy, int ldr, int dual_rows, int k_per_split, int BN, int stages,
                uint32_t tmem_cols, int* err, const int32_t* __restrict__ expert_offsets,
                int w_rows_per_expert, const int* gate_flags, int gate_rpr, int gate_world,
-               int packed_kb, int x_batch_off, int y_batch_off) {
+               int packed_kb, int x_batch_off, int y_batch_off, int w_static) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -199,8 +199,28 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = tail->tmem_base;
   volatile int* abort_word = &tail->abort_word;
-  // everything above touched only this CTA's own resources; the operands are produced by earlier
-  // kernels on the stream (no-op unless launched as a programmatic dependent)
+  // Weights that no kernel on the stream writes (w_static) are requested before the wait: the first ring stages
+  // fill while the previous kernel drains, the activation tiles follow after the wait on the same barriers.
+  int pre = 0;
+  if (w_static && expert_offsets == nullptr && gate_flags == nullptr && warp == 0 && lane == 0) {
+    pre = k_iters < stages ? k_iters : stages;
+    for (int it = 0; it < pre; ++it) {
+      uint8_t* sa = smem + it * stage_bytes;
+      uint64_t* full_s = &tail->full[it];
+      mbar_arrive_expect_tx(full_s, stage_bytes);
+      const int kc = k_begin + it * kBK;
+      if (packed_kb > 0) {
+        const int kb = kc / kBK;
+        tma_load_2d(sa, &tmW, full_s, 0, (((w_row0 + n0) >> 7) * packed_kb + kb) << 7);
+        if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, full_s, 0, (((w_row0 + dual_rows + n0) >> 7) * packed_kb + kb) << 7);
+      } else {
+        tma_load_2d(sa, &tmW, full_s, kc, w_row0 + n0);
+        if (DUAL) tma_load_2d(sa + kATileBytes, &tmW, full_s, kc, w_row0 + dual_rows + n0);
+      }
+    }
+  }
+  // everything above touched only this CTA's own resources and static weights; the other operands are produced
+  // by earlier kernels on the stream (no-op unless launched as a programmatic dependent)
   pdl_wait();
   pdl_trigger();
 
@@ -226,12 +246,18 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       for (int it = 0; it < k_iters; ++it) {
-        if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, err, 101)) break;
         uint8_t* sa = smem + s * stage_bytes;
         uint8_t* sb = sa + a_bytes;
         uint64_t* full_s = &tail->full[s];
-        mbar_arrive_expect_tx(full_s, stage_bytes);
         const int kc = k_begin + it * kBK;
+        if (it < pre) {
+          // the stage was armed and its weight tile requested before the wait
+          if (++s == stages) { s = 0; ph ^= 1; }
+          tma_load_2d(sb, &tmX, full_s, xk0 + kc, t0);
+          continue;
+        }
+        if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, err, 101)) break;
+        mbar_arrive_expect_tx(full_s, stage_bytes);
         if (++s == stages) { s = 0; ph ^= 1; }
         if (packed_kb > 0) {
           // pre-tiled weights: tile (row block, K block) is one contiguous 16 KiB run in memory,
@@ -568,7 +594,7 @@ static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, con
                       const int32_t* expert_offsets = nullptr, int n_experts = 0,
                       int w_rows_per_expert = 0, const int* gate_flags = nullptr, int gate_rpr = 1,
                       int gate_world = 0, int packed_kb = 0, int batch = 0, int x_batch_off = 0,
-                      int y_batch_off = 0) {
+                      int y_batch_off = 0, int w_static = 0) {
   const int stage_bytes = kATileBytes * (DUAL ? 2 : 1) + BN * kBK * 2;
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes +
                       sizeof(GemmSmemTail) + 1024;
@@ -585,7 +611,7 @@ static int launch_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, con
   const cudaError_t e = launch_k(kern, grid, dim3(kGemmThreads), smem, stream, tw, tx, Y,
                                  static_cast<const __nv_bfloat16*>(R), M, N, K, ldy, ldr, dual_rows, k_per_split,
                                  BN, stages, tmem_cols, err, expert_offsets, w_rows_per_expert, gate_flags,
-                                 gate_rpr, gate_world, packed_kb, x_batch_off, y_batch_off);
+                                 gate_rpr, gate_world, packed_kb, x_batch_off, y_batch_off, w_static);
   return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
@@ -702,6 +728,9 @@ extern "C" int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const v
   if (gate_flags != nullptr && (gate_rpr < 1 || gate_world < 1 || gate_world > kMaxRanks)) return MB_ERR_SHAPE;
   const bool dual = flags & 1, resid = flags & 2, f32 = flags & 4, packed = flags & 64;
   // bit6: W is pre-tiled as [rows/128][K/64][128][64] (mb_pack_weight_tiles layout)
+  // bit7: W is written by no kernel on this stream (model weights): its first tiles may be requested before the
+  //       programmatic-dependency wait
+  const int w_static = (flags & 128) ? 1 : 0;
   if (packed && (K % kBK || N % kBM || ldw != K)) return MB_ERR_SHAPE;
   const int packed_kb = packed ? K / kBK : 0;
   if (K % 8 || ldx % 8 || ldw % 8 || N % 8 || (!f32 && ldy % 8) || (resid && ldr % 8))
@@ -741,7 +770,7 @@ extern "C" int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const v
   if (splits > 1) {
     rc = launch_cfg<false, EPI_F32>(tw, tx, workspace, nullptr, M, N, K, N, 0, 0, k_per_split,
                                     splits, bn, stages, err, stream, nullptr, 0, 0, gate_flags, gate_rpr,
-                                    gate_world, packed_kb);
+                                    gate_world, packed_kb, 0, 0, 0, w_static);
     if (rc != MB_OK) return rc;
     if (f32) return MB_ERR_SHAPE;  // fp32 output is never split
     const size_t total4 = (static_cast<size_t>(M) * N + 3) / 4;
@@ -753,16 +782,16 @@ extern "C" int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const v
   }
   if (dual)
     return launch_cfg<true, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, N, K, 1, bn, stages, err,
-                                      stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb);
+                                      stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb, 0, 0, 0, w_static);
   if (f32)
     return launch_cfg<false, EPI_F32>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err,
-                                      stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb);
+                                      stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb, 0, 0, 0, w_static);
   if (resid)
     return launch_cfg<false, EPI_BF16_RESIDUAL>(tw, tx, Y, R, M, N, K, ldy, ldr, 0, K, 1, bn,
                                                 stages, err, stream, nullptr, 0, 0, gate_flags, gate_rpr,
-                                                gate_world, packed_kb);
+                                                gate_world, packed_kb, 0, 0, 0, w_static);
   return launch_cfg<false, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err,
-                                     stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb);
+                                     stream, nullptr, 0, 0, gate_flags, gate_rpr, gate_world, packed_kb, 0, 0, 0, w_static);
 }
 
 // Process-wide choice of the CTA-pair kernel by token count: plain (and residual) GEMMs with

@@ -356,7 +356,9 @@ class Llama3Model:
             use_pdl=int(os.environ.get("MB200_PDL", "0")),
             attn_impl=int(os.environ.get("MB200_ATTN_TMA", "1")),
             # steps of up to this many tokens run the decode-step GEMMs (fused all-reduce + residual + norm)
-            dec_max_tokens=self._dec_tokens()))
+            dec_max_tokens=self._dec_tokens(),
+            # weights are static: the tiled GEMMs may request their first tiles while the previous kernel drains
+            prefetch_weights=int(os.environ.get("MB200_PREFETCH_W", "1") not in ("", "0"))))
         ex.set_globals(self.w.embed, self.w.final_norm, self.w.lm_head, self.cos_sin)
         self.is_fp8 = any(l.is_fp8 for l in self.w.layers)
         if self.is_fp8 and not all(l.is_fp8 for l in self.w.layers):

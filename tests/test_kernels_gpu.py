@@ -511,14 +511,31 @@ def test_gemm_decode_qkv_rope_store_equals_the_two_kernels(M, n_q, n_kv, K):
     ops.rope_kv_store(want, pos, slots, cs, kv_a[:, 0], kv_a[:, 1], n_q, n_kv, hd)
     got = torch.zeros_like(want)
     ws, state = ops.decode_gemm_workspace(DEV)
-    for _ in range(2):        # the second call finds the tile counters cleared
-        lib().gemm_dec_qkv_rope(x, w, got, pos, slots, cs, kv_b[:, 0], kv_b[:, 1], n_q, n_kv, ws, state)
+    lib().set_gemm_dec_rope(True)          # an option (off by default: it measured slower than the two kernels)
+    try:
+        for _ in range(2):        # the second call finds the counters cleared
+            lib().gemm_dec_qkv_rope(x, w, got, pos, slots, cs, kv_b[:, 0], kv_b[:, 1], n_q, n_kv, ws, state)
+    finally:
+        lib().set_gemm_dec_rope(False)
     torch.cuda.synchronize()
     ops.check_device_error()
-    assert torch.equal(got[:, n_q * hd:], want[:, n_q * hd:]) or torch.allclose(got.float(), want.float(), rtol=8e-3, atol=2e-3)
-    assert torch.allclose(got.float(), want.float(), rtol=8e-3, atol=2e-3)
+    # rotated queries and the values in the qkv buffer (the stand-alone kernel leaves the keys of that buffer
+    # unrotated: attention reads keys from the cache), rotated keys and the values in the cache
+    assert torch.allclose(got[:, : n_q * hd].float(), want[:, : n_q * hd].float(), rtol=8e-3, atol=2e-3)
+    assert torch.equal(got[:, (n_q + n_kv) * hd:], want[:, (n_q + n_kv) * hd:])
     assert torch.allclose(kv_b.float(), kv_a.float(), rtol=8e-3, atol=2e-3)
     assert torch.equal(kv_b[:, 1], kv_a[:, 1])            # values are copied, not rotated
+    # the same through the per-tile epilogue
+    lib().set_gemm_dec_tile_epilogue(True)
+    lib().set_gemm_dec_rope(True)
+    try:
+        kv_c, got2 = mk(), torch.zeros_like(want)
+        lib().gemm_dec_qkv_rope(x, w, got2, pos, slots, cs, kv_c[:, 0], kv_c[:, 1], n_q, n_kv, ws, state)
+        y = ops.linear_decode(x, w)
+    finally:
+        lib().set_gemm_dec_tile_epilogue(False)
+        lib().set_gemm_dec_rope(False)
+    assert torch.equal(got2, got) and torch.equal(kv_c, kv_b) and torch.equal(y, ops.linear_decode(x, w))
 
 
 @pytest.mark.parametrize("M,N,K", [(64, 6144, 4096), (64, 4096, 4096), (64, 4096, 14336), (1, 8192, 8192),
