@@ -30,7 +30,9 @@ from .. import ops
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--layers", type=int, default=0, help="0 = the model's own count")
+    ap.add_argument("--model", default="llama8b", choices=["llama8b", "llama70b"])
+    ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 projection weights (shard-size random init)")
     ap.add_argument("--decode", type=int, default=64)
     ap.add_argument("--ctx", type=int, default=1152)
     ap.add_argument("--prefill", type=int, default=256)
@@ -48,9 +50,12 @@ def main(argv=None) -> int:
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    cfg = Llama3Config.llama31_8b()
-    cfg.num_hidden_layers = args.layers
-    w = Llama3Weights.random_init(cfg, dev, torch.bfloat16, seed=0)
+    cfg = Llama3Config.llama33_70b() if args.model == "llama70b" else Llama3Config.llama31_8b()
+    if args.layers:
+        cfg.num_hidden_layers = args.layers
+    shard_init = args.fp8 or args.model == "llama70b"      # too large (or fp8): created at shard size
+    if not shard_init:
+        w = Llama3Weights.random_init(cfg, dev, torch.bfloat16, seed=0)
     tp = None
     if world > 1:
         # launched with torch.distributed.run: one tensor-parallel rank per process
@@ -58,8 +63,12 @@ def main(argv=None) -> int:
         from ..parallel.tp import TPContext, shard_llama_config, shard_llama_weights
         dist.init_process_group("nccl", device_id=dev)
         tp = TPContext(device=dev)
+    if shard_init:
+        w = Llama3Weights.random_init_shard(cfg, rank, world, dev, torch.bfloat16, seed=0, fp8=args.fp8)
+    if world > 1:
         full_cfg = cfg
-        w = shard_llama_weights(full_cfg, w, rank, world)
+        if not shard_init:
+            w = shard_llama_weights(full_cfg, w, rank, world)
         cfg = shard_llama_config(full_cfg, world)
         torch.cuda.empty_cache()
     page = 128

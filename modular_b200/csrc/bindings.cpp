@@ -631,10 +631,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_dec", [](const Tensor& x, const Tensor& w, int mode, const c10::optional<Tensor>& y,
                        const c10::optional<Tensor>& h, const c10::optional<Tensor>& xn,
                        const c10::optional<Tensor>& gamma, double eps, double w_off, bool mbc, int world, int rank,
-                       const std::vector<int64_t>& lam, int lam_rows, const Tensor& ws, Tensor& state) {
+                       const std::vector<int64_t>& lam, int lam_rows, const Tensor& ws, Tensor& state,
+                       const c10::optional<Tensor>& w_scale) {
     need_cuda(x, "x"); need_cuda(w, "w");
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "gemm_dec: row-major 2-D operands");
-    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "gemm_dec: bf16 inputs");
+    // w_scale: block-scaled fp8 weights (e4m3 [N, K] contiguous, fp32 scales [N / 128, K / 128]); activations stay bf16
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 &&
+                    (w_scale ? (w.element_size() == 1 && w.is_contiguous() && w_scale->is_contiguous() &&
+                                w_scale->scalar_type() == at::kFloat &&
+                                w_scale->numel() == (w.size(0) / 128) * ((w.size(1) + 127) / 128))
+                             : w.scalar_type() == at::kBFloat16),
+                "gemm_dec: bf16 activations; bf16 weights or e4m3 weights with block scales");
     const int M = x.size(0), K = x.size(1), N = w.size(0);
     TORCH_CHECK(w.size(1) == K, "gemm_dec: shape mismatch");
     TORCH_CHECK(state.scalar_type() == at::kInt && state.numel() >= mb_gemm_dec_state_ints(), "gemm_dec: state");
@@ -655,12 +662,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     }
     void* lamp[8] = {};
     for (size_t i = 0; i < lam.size() && i < 8; ++i) lamp[i] = reinterpret_cast<void*>(lam[i]);
+    if (w_scale) {
+      check_rc(mb_gemm_dec_w8(x.data_ptr(), w.data_ptr(), w_scale->data_ptr<float>(), M, N, K, x.stride(0), mode, yp, ldy,
+                              const_cast<void*>(optptr(h)), const_cast<void*>(optptr(xn)), optptr(gamma),
+                              static_cast<float>(eps), static_cast<float>(w_off), mbc ? 1 : 0, world, rank, lamp,
+                              lam_rows, ws.data_ptr(), ws.nbytes(), state.data_ptr<int>(), error_flag(), num_sms(),
+                              cur_stream()),
+               "gemm_dec_w8");
+      return;
+    }
     check_rc(mb_gemm_dec(x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), mode, yp, ldy,
                          const_cast<void*>(optptr(h)), const_cast<void*>(optptr(xn)), optptr(gamma),
                          static_cast<float>(eps), static_cast<float>(w_off), mbc ? 1 : 0, world, rank, lamp, lam_rows,
                          ws.data_ptr(), ws.nbytes(), state.data_ptr<int>(), error_flag(), num_sms(), cur_stream()),
              "gemm_dec");
-  });
+  }, py::arg("x"), py::arg("w"), py::arg("mode"), py::arg("y"), py::arg("h"), py::arg("xn"), py::arg("gamma"),
+     py::arg("eps"), py::arg("w_off"), py::arg("mbc"), py::arg("world"), py::arg("rank"), py::arg("lam"),
+     py::arg("lam_rows"), py::arg("ws"), py::arg("state"), py::arg("w_scale") = py::none());
   m.def("rmsnorm", &rmsnorm);
   m.def("add_rmsnorm", &add_rmsnorm);
   m.def("silu_mul", &silu_mul);

@@ -104,6 +104,10 @@ int mb_mla_post_down(const void* qkv_a, int ld, int q_lora, int R, const void* g
                      int T, int page_size, long long page_stride, cudaStream_t stream);
 int mb_mla_q_rope(const void* q, int n_heads, int nope, const int32_t* positions, const float* cos_sin, void* q_rope,
                   int T, cudaStream_t stream);
+int mb_gemm_dec_w8(const void* X, const void* Wq, const float* Ws, int M, int N, int K, int ldx, int mode, void* Y, int ldy,
+                   void* h, void* xn, const void* gamma, float eps, float w_off, int mbc, int world, int rank,
+                   void* const* lam, int lam_rows, void* ws, size_t ws_bytes, int* state, int* err, int num_sms,
+                   cudaStream_t stream);
 void mb_set_gemm_dec_tile_epilogue(int on);
 void mb_set_gemm_dec_rope(int on);
 int mb_gemm_dec_qkv_rope(const void* X, const void* W, int M, int K, int ldx, int ldw, void* qkv, int ldy,

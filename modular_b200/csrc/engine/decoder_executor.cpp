@@ -53,12 +53,15 @@ static int linear_fp8(const DecoderBuffers& buf, const DecoderConfig& c, const v
 
 bool DecoderExecutor::dec_usable(int T) const {
   const DecoderConfig& c = cfg;
-  if (!layers.empty() && layers[0].wqkv_s != nullptr) return false;   // fp8 layers run the general path
   if (T <= 0 || T > c.dec_max_tokens || buf.dec_ws == nullptr || buf.dec_state == nullptr) return false;
   if (tp.world > 1 && (tp.lam[0] == nullptr || T > tp.lam_rows)) return false;
   const int qkv_dim = (c.n_q + 2 * c.n_kv) * c.head_dim;
   const int q_dim = c.n_q * c.head_dim;
   const size_t wsb = buf.dec_ws_bytes;
+  // block-scaled fp8 layers: weight tiles are converted per 128 x 128 scale block
+  if (!layers.empty() && layers[0].wqkv_s != nullptr &&
+      (qkv_dim % 128 || c.hidden % 128 || q_dim % 128 || c.inter % 128 || !c.fuse_swiglu))
+    return false;
   return mb_gemm_dec_plan(T, qkv_dim, c.hidden, 0, wsb, c.num_sms) == MB_OK &&
          mb_gemm_dec_plan(T, c.hidden, q_dim, 2, wsb, c.num_sms) == MB_OK &&
          mb_gemm_dec_plan(T, 2 * c.inter, c.hidden, c.fuse_swiglu ? 1 : 0, wsb, c.num_sms) == MB_OK &&
@@ -71,8 +74,13 @@ int DecoderExecutor::forward_dec(const StepInputs& in, cudaStream_t stream) {
   const int W = tp.world, R = tp.rank;
   const int qkv_dim = (c.n_q + 2 * c.n_kv) * c.head_dim;
   const int q_dim = c.n_q * c.head_dim;
-  auto dec = [&](const void* X, const void* Wt, int N, int K, int mode, void* Y, int ldy, const void* gamma) {
+  auto dec = [&](const void* X, const void* Wt, const float* Ws, int N, int K, int mode, void* Y, int ldy,
+                 const void* gamma) {
     launches += 1;
+    if (Ws != nullptr)      // block-scaled fp8 weights, bf16 activations
+      return mb_gemm_dec_w8(X, Wt, Ws, T, N, K, K, mode, Y, ldy, buf.h, buf.xn, gamma, c.eps, c.norm_weight_offset,
+                            c.multiply_before_cast, W, R, tp.lam, tp.lam_rows, buf.dec_ws, buf.dec_ws_bytes,
+                            buf.dec_state, buf.err, c.num_sms, stream);
     return mb_gemm_dec(X, Wt, T, N, K, K, K, mode, Y, ldy, buf.h, buf.xn, gamma, c.eps, c.norm_weight_offset,
                        c.multiply_before_cast, W, R, tp.lam, tp.lam_rows, buf.dec_ws, buf.dec_ws_bytes,
                        buf.dec_state, buf.err, c.num_sms, stream);
@@ -93,7 +101,7 @@ int DecoderExecutor::forward_dec(const StepInputs& in, cudaStream_t stream) {
     char* kbase = static_cast<char*>(kv.base) + 2 * (static_cast<int64_t>(l) * kv.layer_stride);
     // one launch for the projection, the rotation and the cache store where the kernel takes the shape
     int fused = MB_ERR_SHAPE;
-    if (!c.rope_interleaved)
+    if (!c.rope_interleaved && w.wqkv_s == nullptr)
       fused = mb_gemm_dec_qkv_rope(buf.xn, w.wqkv, T, c.hidden, c.hidden, c.hidden, buf.qkv, qkv_dim, in.positions,
                                    in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, c.n_q, c.n_kv, c.head_dim,
                                    c.page_size, kv.page_stride, kv.head_stride, buf.dec_ws, buf.dec_ws_bytes,
@@ -104,7 +112,7 @@ int DecoderExecutor::forward_dec(const StepInputs& in, cudaStream_t stream) {
     } else if (fused != MB_ERR_SHAPE) {
       return fused;
     } else {
-      MB_TRY(dec(buf.xn, w.wqkv, qkv_dim, c.hidden, 0, buf.qkv, qkv_dim, nullptr));
+      MB_TRY(dec(buf.xn, w.wqkv, w.wqkv_s, qkv_dim, c.hidden, 0, buf.qkv, qkv_dim, nullptr));
       mark("gemm_qkv", stream);
       MB_TRY(mb_rope_kv_store(buf.qkv, in.positions, in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, T, c.n_q,
                               c.n_kv, c.head_dim, c.page_size, kv.page_stride, kv.head_stride, c.rope_interleaved,
@@ -127,18 +135,18 @@ int DecoderExecutor::forward_dec(const StepInputs& in, cudaStream_t stream) {
     }
     launches += 1;
     mark("attention", stream);
-    MB_TRY(dec(buf.attn, w.wo, c.hidden, q_dim, 2, nullptr, 0, w.mlp_norm));
+    MB_TRY(dec(buf.attn, w.wo, w.wo_s, c.hidden, q_dim, 2, nullptr, 0, w.mlp_norm));
     mark("gemm_o+ar+norm", stream);
     if (c.fuse_swiglu) {
-      MB_TRY(dec(buf.xn, w.wgu, 2 * c.inter, c.hidden, 1, buf.act, c.inter, nullptr));
+      MB_TRY(dec(buf.xn, w.wgu, w.wgu_s, 2 * c.inter, c.hidden, 1, buf.act, c.inter, nullptr));
     } else {
-      MB_TRY(dec(buf.xn, w.wgu, 2 * c.inter, c.hidden, 0, buf.gu, 2 * c.inter, nullptr));
+      MB_TRY(dec(buf.xn, w.wgu, w.wgu_s, 2 * c.inter, c.hidden, 0, buf.gu, 2 * c.inter, nullptr));
       MB_TRY(mb_silu_mul(buf.gu, buf.act, T, c.inter, stream));
       launches += 1;
     }
     mark("gemm_gate_up", stream);
     const void* next_norm = l + 1 < c.n_layers ? layers[l + 1].attn_norm : final_norm;
-    MB_TRY(dec(buf.act, w.wd, c.hidden, c.inter, 2, nullptr, 0, next_norm));
+    MB_TRY(dec(buf.act, w.wd, w.wd_s, c.hidden, c.inter, 2, nullptr, 0, next_norm));
     mark("gemm_down+ar+norm", stream);
   }
   if (in.n_logits > 0) {

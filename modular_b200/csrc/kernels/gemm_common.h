@@ -10,4 +10,9 @@ namespace mb {
 int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                 uint32_t box_rows, int elt_bytes);
 
+// Unswizzled byte tiles: `box_bytes` bytes (a multiple of 16) x `box_rows` rows of a [rows, cols] byte matrix with row
+// pitch `ld` bytes.
+int cached_tmap_raw(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                    uint32_t box_bytes);
+
 }  // namespace mb

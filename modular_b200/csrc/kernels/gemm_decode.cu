@@ -36,6 +36,7 @@
 // nn/gemv_partial_norm.mojo:131 (GEMV fused with norm statistics).
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -54,6 +55,8 @@ constexpr int kUmmaK = 16;
 constexpr int kATile = kBM * kBK * 2;
 constexpr int kThreads = 512;     // warps 0-5 run the main loop, all sixteen run the epilogue
 constexpr int kSlots = 6;      // most workspace slots per CTA (segments of different tiles)
+constexpr int kRawTile = 128 * 64;   // fp8 weight tile of one K block: 128 rows x 64 bytes, unswizzled
+constexpr int kConvWarps = 8;        // warps 6..13 convert fp8 weight tiles
 constexpr uint32_t kSentinel2 = 0x80008000u;   // two bf16 -0.0
 
 struct Params {
@@ -77,6 +80,11 @@ struct Params {
   // gate tile and its up tile) reduces and stores that tile; the other CTAs leave as soon as their partials are
   // written
   int tile_epi;
+  // Block-scaled fp8 weights (e4m3, one fp32 scale per 128 x 128 block) with bf16 activations: the weight tile of a
+  // K block arrives as 128 rows x 64 bytes, eight converter warps write it as scaled bf16 into the operand layout,
+  // the accumulation then runs in bf16 x bf16 as for bf16 weights. w_scale = nullptr: bf16 weights.
+  const float* w_scale;    // [N / 128, sw_ld]
+  int sw_ld;
   // QKV projection with the rotation and the cache store in the tile epilogue (head_dim 128: an output tile is
   // one head; rotate-half convention). rope = 1: tiles [0, n_q) are query heads (rotated, stored to Y), the next
   // n_kv key heads (rotated, stored to Y and to the K cache at the token's slot), the last n_kv value heads
@@ -103,6 +111,7 @@ struct Tail {
   uint64_t empty[8];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t raw_full[8];    // fp8 weights: the raw tile (and the activation tile) of the stage has landed
   uint32_t tmem_base;
   int abort_word;
   int flag;
@@ -270,7 +279,8 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const int b_bytes = p.BN * kBK * 2;
-  const int stage_bytes = kATile + b_bytes;
+  const bool w8 = p.w_scale != nullptr;
+  const int stage_bytes = kATile + b_bytes + (w8 ? kRawTile : 0);
   Tail* tail = reinterpret_cast<Tail*>(smem + p.stages * stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.x;
@@ -279,8 +289,9 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->full[s], w8 ? kConvWarps : 1);
       mbar_init(&tail->empty[s], 1);
+      mbar_init(&tail->raw_full[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail->tmem_full[b], 1);
@@ -317,8 +328,14 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         while (pre < p.stages && it.next(s)) {
           const int n0 = (s.tile / p.m_tiles) * kBM;
           for (int kbi = s.kb0; kbi < s.kb1 && pre < p.stages; ++kbi) {
-            mbar_arrive_expect_tx(&tail->full[st], stage_bytes);
-            tma_load_2d(smem + st * stage_bytes, &tmW, &tail->full[st], kbi * kBK, n0);
+            if (w8) {
+              // fp8 weights: the raw tile goes behind the operand tiles of the stage and signals the converters
+              mbar_arrive_expect_tx(&tail->raw_full[st], kRawTile + b_bytes);
+              tma_load_2d(smem + st * stage_bytes + kATile + b_bytes, &tmW, &tail->raw_full[st], kbi * kBK, n0);
+            } else {
+              mbar_arrive_expect_tx(&tail->full[st], stage_bytes);
+              tma_load_2d(smem + st * stage_bytes, &tmW, &tail->full[st], kbi * kBK, n0);
+            }
             ++st; ++pre;
           }
         }
@@ -337,11 +354,16 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const int t0 = (s.tile % p.m_tiles) * p.BN;
         for (int kbi = s.kb0; kbi < s.kb1; ++kbi) {
           uint8_t* sa = smem + st * stage_bytes;
-          uint64_t* full_st = &tail->full[st];
+          uint64_t* full_st = w8 ? &tail->raw_full[st] : &tail->full[st];
           if (issued >= pre) {
             if (!mbar_wait(&tail->empty[st], ph ^ 1, abort_word, p.err, 301)) { ok = false; break; }
-            mbar_arrive_expect_tx(full_st, stage_bytes);
-            tma_load_2d(sa, &tmW, full_st, kbi * kBK, n0);
+            if (w8) {
+              mbar_arrive_expect_tx(full_st, kRawTile + b_bytes);
+              tma_load_2d(sa + kATile + b_bytes, &tmW, full_st, kbi * kBK, n0);
+            } else {
+              mbar_arrive_expect_tx(full_st, stage_bytes);
+              tma_load_2d(sa, &tmW, full_st, kbi * kBK, n0);
+            }
           }
           tma_load_2d(sa + kATile, &tmX, full_st, (p.bN > 0 ? (n0 / p.bN) * p.x_boff : 0) + kbi * kBK, t0);
           ++issued;
@@ -390,6 +412,46 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   } else if (warp >= 6) {
     pdl_wait();
     pdl_trigger();
+    if (w8 && warp < 6 + kConvWarps) {
+      // ---------------------------------------------------------------- fp8 weight tiles -> scaled bf16 operand tiles
+      // two threads per weight row: 32 e4m3 values each -> four 16-byte chunks of the 128-byte-swizzled K-major tile
+      const int tid = (warp - 6) * 32 + lane;
+      const int r = tid >> 1, half = tid & 1;
+      SegIter it(p, g);
+      Seg s;
+      int st = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      while (ok && it.next(s)) {
+        const int n_tile = s.tile / p.m_tiles;
+        const float* srow = p.w_scale + static_cast<size_t>(n_tile) * p.sw_ld;
+        for (int kbi = s.kb0; kbi < s.kb1; ++kbi) {
+          if (!mbar_wait(&tail->raw_full[st], ph, abort_word, p.err, 307)) { ok = false; break; }
+          const float sc = srow[kbi >> 1];                  // one scale per 128 K values = two K blocks of 64
+          uint8_t* sa = smem + st * stage_bytes;
+          const uint8_t* raw = sa + kATile + b_bytes + r * 64 + half * 32;
+          const uint4 q0 = *reinterpret_cast<const uint4*>(raw), q1 = *reinterpret_cast<const uint4*>(raw + 16);
+          const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              __nv_fp8x4_e4m3 q;
+              q.__x = qw[c * 2 + j];
+              const float4 f = static_cast<float4>(q);
+              v[4 * j] = f.x * sc; v[4 * j + 1] = f.y * sc; v[4 * j + 2] = f.z * sc; v[4 * j + 3] = f.w * sc;
+            }
+            const int chunk = half * 4 + c;
+            *reinterpret_cast<uint4*>(sa + r * 128 + ((chunk ^ (r & 7)) << 4)) = pack_bf16x8(v);
+          }
+          fence_proxy_async_smem();        // generic-proxy writes before the tensor core reads the tile
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tail->full[st]);
+          if (++st == p.stages) { st = 0; ph ^= 1; }
+        }
+      }
+    }
   } else {
     pdl_wait();
     pdl_trigger();
@@ -703,7 +765,7 @@ extern "C" void mb_set_gemm_dec_rope(int on) { g_dec_rope = on; }
 static int g_dec_smem_kb = 200;   // ring budget (measured on B200: chains of decode GEMMs run 8 % faster with 150-200 KB than with 100)
 extern "C" void mb_set_gemm_dec_smem_kb(int kb) { g_dec_smem_kb = kb < 40 ? 40 : (kb > 200 ? 200 : kb); }
 
-static int dec_plan(int M, int N, int K, int mode, size_t ws_bytes, int num_sms, dec::Params* out) {
+static int dec_plan(int M, int N, int K, int mode, size_t ws_bytes, int num_sms, dec::Params* out, bool w8 = false) {
   using namespace mb::dec;
   if (M <= 0 || N <= 0 || M > 256 || K % 8 || N % 8 || K < kBK) return MB_ERR_SHAPE;
   if (mode < 0 || mode > 2 || (mode == 1 && N % 16)) return MB_ERR_SHAPE;
@@ -714,7 +776,7 @@ static int dec_plan(int M, int N, int K, int mode, size_t ws_bytes, int num_sms,
   p.m_tiles = 1;
   p.nbufs = 2;
   p.tmem_cols = pow2_cols(2 * p.BN);
-  const int stage_bytes = kATile + p.BN * kBK * 2;
+  const int stage_bytes = kATile + p.BN * kBK * 2 + (w8 ? kRawTile : 0);
   const int budget = (p.BN <= 128 ? g_dec_smem_kb : 200) * 1024;
   int stages = budget / stage_bytes;
   if (stages > 8) stages = 8;
@@ -767,7 +829,7 @@ static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int 
                          void* Y, int ldy, void* h, void* xn, const void* gamma, float eps, float w_off,
                          int mbc, int world, int rank, void* const* lam, int lam_rows, void* ws,
                          size_t ws_bytes, int* state, int* err, int num_sms, cudaStream_t stream, int bN, int x_boff,
-                         int y_boff, int x_cols, const DecRope* rope = nullptr) {
+                         int y_boff, int x_cols, const DecRope* rope = nullptr, const float* w_scale = nullptr) {
   using namespace mb::dec;
   if (M <= 0 || N <= 0) return MB_OK;
   if (ldx % 8 || ldw % 8 || (mode != 2 && ldy % 8)) return MB_ERR_SHAPE;
@@ -780,8 +842,10 @@ static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int 
     return MB_ERR_ALIGN;
   if (num_sms <= 0) num_sms = 148;
   Params p;
-  int rc = dec_plan(M, N, K, mode, ws_bytes, num_sms, &p);
+  int rc = dec_plan(M, N, K, mode, ws_bytes, num_sms, &p, w_scale != nullptr);
   if (rc != MB_OK) return rc;
+  if (w_scale != nullptr && (N % 128 || K % 128 || bN > 0)) return MB_ERR_SHAPE;
+  p.w_scale = w_scale; p.sw_ld = (K + 127) / 128;
   p.ws = static_cast<float*>(ws);
   p.trace = g_dec_trace;
   p.state = state; p.err = err; p.mode = mode;
@@ -804,11 +868,12 @@ static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int 
   for (int i = 0; i < kMaxRanks; ++i)
     p.lam[i] = (mode == 2 && world > 1 && i < world) ? static_cast<__nv_bfloat16*>(lam[i]) : nullptr;
   CUtensorMap tw, tx;
-  rc = cached_tmap(&tw, W, N, K, ldw, kBM, 2);
+  // fp8 weights: 128 rows x 64 bytes per K block, unswizzled (the converter warps write the operand layout)
+  rc = w_scale != nullptr ? cached_tmap_raw(&tw, W, N, K, ldw, kBM, 64) : cached_tmap(&tw, W, N, K, ldw, kBM, 2);
   if (rc != MB_OK) return rc;
   rc = cached_tmap(&tx, X, M, bN > 0 ? x_cols : K, ldx, p.BN, 2);
   if (rc != MB_OK) return rc;
-  const int stage_bytes = kATile + p.BN * kBK * 2;
+  const int stage_bytes = kATile + p.BN * kBK * 2 + (w_scale != nullptr ? kRawTile : 0);
   const size_t smem = static_cast<size_t>(p.stages) * stage_bytes + sizeof(Tail) + 1024;
   static PerDeviceOnce configured;
   if (configured.needed()) {
@@ -852,4 +917,16 @@ extern "C" int mb_gemm_dec_qkv_rope(const void* X, const void* W, int M, int K, 
   DecRope r{n_q, n_kv, page_size, page_stride, head_stride, positions, slots, cos_sin, k_cache, v_cache};
   return gemm_dec_impl(X, W, M, (n_q + 2 * n_kv) * 128, K, ldx, ldw, 0, qkv, ldy, nullptr, nullptr, nullptr, 0.f, 0.f, 0,
                        1, 0, nullptr, 0, ws, ws_bytes, state, err, num_sms, stream, 0, 0, 0, 0, &r);
+}
+
+// The decode-step GEMM on block-scaled fp8 weights (e4m3 [N, K] with fp32 scales [N / 128, K / 128]) and bf16
+// activations: weight tiles are converted to scaled bf16 in shared memory, everything else (modes, tails,
+// all-reduce) is mb_gemm_dec. N % 128 == 0 and K % 128 == 0.
+extern "C" int mb_gemm_dec_w8(const void* X, const void* Wq, const float* Ws, int M, int N, int K, int ldx, int mode,
+                              void* Y, int ldy, void* h, void* xn, const void* gamma, float eps, float w_off, int mbc,
+                              int world, int rank, void* const* lam, int lam_rows, void* ws, size_t ws_bytes,
+                              int* state, int* err, int num_sms, cudaStream_t stream) {
+  if (Ws == nullptr) return MB_ERR_SHAPE;
+  return gemm_dec_impl(X, Wq, M, N, K, ldx, K, mode, Y, ldy, h, xn, gamma, eps, w_off, mbc, world, rank, lam, lam_rows,
+                       ws, ws_bytes, state, err, num_sms, stream, 0, 0, 0, 0, nullptr, Ws);
 }

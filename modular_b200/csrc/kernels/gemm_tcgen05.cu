@@ -581,6 +581,34 @@ int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
   return rc;
 }
 
+// Unswizzled byte tiles: `box_bytes` bytes (a multiple of 16) of `box_rows` rows of a [rows, cols] byte matrix with
+// row pitch `ld` bytes.
+int cached_tmap_raw(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                    uint32_t box_bytes) {
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  static std::mutex mu;
+  TmapKey key{base, rows, cols, ld, box_rows * 1024 + box_bytes};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return MB_OK;
+  }
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return MB_ERR_DRIVER;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {ld};
+  const cuuint32_t box[2] = {box_bytes, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return MB_ERR_TMAP;
+  if (cache.size() > 65536) cache.clear();
+  cache.emplace(key, *out);
+  return MB_OK;
+}
+
 static uint32_t pow2_cols(int c) {
   uint32_t p = 32;
   while (static_cast<int>(p) < c) p <<= 1;

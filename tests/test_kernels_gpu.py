@@ -489,6 +489,41 @@ def test_mla_post_down_matches_composed_ops(T, QL):
 
 
 # ---------------------------------------------------------------------------- decode-step GEMM
+@pytest.mark.parametrize("M,N,K", [(64, 1280, 8192), (128, 8192, 1024), (1, 256, 128), (200, 1024, 3584), (33, 384, 640)])
+def test_gemm_decode_fp8_weights_plain_and_add_norm(M, N, K):
+    """Decode-step GEMM on block-scaled fp8 weights with bf16 activations: the weight tiles are converted to scaled
+    bf16 in shared memory, so the result equals the product with the dequantised weights up to bf16 rounding of the
+    scaled weights."""
+    torch.manual_seed(41)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    wq, wsc = ref.quant_fp8_weight_block128(w)
+    wd = ref.dequant_fp8_weight_block128(wq, wsc).to(torch.bfloat16)
+    for _ in range(2):
+        y = ops.linear_decode(x, wq, w_scale=wsc)
+        assert _rel_err(y, ref.linear(x, wd)) < 1e-2
+    assert _rel_err(y, ref.linear(x, w)) < 0.05                 # against the unquantised product
+    h = (torch.randn(M, N, device=DEV) * 0.5).to(torch.bfloat16)
+    g = (1 + 0.1 * torch.randn(N, device=DEV)).to(torch.bfloat16)
+    h2 = h.clone()
+    xn, hh = ops.linear_decode(x, wq, mode="add_norm", h=h2, gamma=g, eps=1e-5, w_scale=wsc)
+    want_n, want_h = ref.add_rms_norm(ref.linear(x, wd), h, g, 1e-5)
+    assert _rel_err(hh, want_h) < 1e-2 and _rel_err(xn, want_n) < 2e-2
+    ops.check_device_error()
+
+
+@pytest.mark.parametrize("M,inter,K", [(64, 3584, 8192), (16, 256, 256), (130, 1792, 1024)])
+def test_gemm_decode_fp8_weights_swiglu(M, inter, K):
+    torch.manual_seed(42)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(2 * inter, K, device=DEV) * 0.03).to(torch.bfloat16)
+    wq, wsc = ref.quant_fp8_weight_block128(w)
+    wd = ref.dequant_fp8_weight_block128(wq, wsc).to(torch.bfloat16)
+    y = ops.linear_decode(x, wq, mode="swiglu", w_scale=wsc)
+    assert _rel_err(y, ref.linear_swiglu(x, wd)) < 2e-2
+    ops.check_device_error()
+
+
 @pytest.mark.parametrize("M,n_q,n_kv,K", [(64, 32, 8, 4096), (1, 4, 1, 4096), (37, 8, 2, 1024), (256, 16, 4, 512)])
 def test_gemm_decode_qkv_rope_store_equals_the_two_kernels(M, n_q, n_kv, K):
     """QKV projection with rotation and cache store in its tile epilogue against decode GEMM + rope_kv_store."""
