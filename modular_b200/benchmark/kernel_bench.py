@@ -92,10 +92,13 @@ def bench_gemm(shapes, results, configs=None):
     ops.check_device_error()
 
 
-def bench_decode_gemm(results, tp_degrees=(1, 8)):
+def bench_decode_gemm(results, tp_degrees=(1, 8), only=None):
     """Decode-step GEMMs (gemm_decode.cu) against the tiled kernels + stand-alone RMSNorm and against cuBLAS, per
     shape (L2 flushed) and as the GEMM chain of a run of layers with distinct weights (weights cold, launches
-    back to back, which is what a decode step does). Shapes: Llama-3.1-8B, whole and the shard of each TP degree."""
+    back to back, which is what a decode step does). Shapes: Llama-3.1-8B, whole and the shard of each TP degree.
+    ``only``: case names (``down_m64_tp1``; a ``_w8`` suffix runs the block-scaled fp8 weight form against the
+    activation quantiser + fp8 GEMM) to run alone, a few launches each, without the chains: what a profiler is
+    pointed at."""
     peaks = measured_peaks()
     bw = peaks["hbm_gbs"] * 1e9
     H, I, QKV, QD = 4096, 14336, 6144, 4096
@@ -105,7 +108,29 @@ def bench_decode_gemm(results, tp_degrees=(1, 8)):
                   ("gate_up", I // tp, H, "swiglu"), ("down", H, I // tp, "add_norm")]
         for M in (1, 16, 64, 128, 256):
             for name, N, K, mode in shapes:
+                case = f"{name}_m{M}_tp{tp}"
+                if only is not None and case not in only and case + "_w8" not in only:
+                    continue
                 rows = 2 * N if mode == "swiglu" else N
+                if only is not None and case + "_w8" in only:
+                    if rows % 128 or K % 128:
+                        continue
+                    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+                    wq, wsc = ops.reference.quant_fp8_weight_block128((torch.randn(rows, K, device=dev) * 0.02).to(torch.bfloat16))
+                    h = torch.randn(M, H, device=dev, dtype=torch.bfloat16)
+                    g = torch.ones(H, device=dev, dtype=torch.bfloat16)
+                    xn = torch.empty(M, H, device=dev, dtype=torch.bfloat16)
+                    kw = dict(h=h, gamma=g, xn=xn) if mode == "add_norm" else {}
+                    new = lambda: ops.linear_decode(x, wq, mode=mode, w_scale=wsc, **kw)
+                    old = lambda: ops.linear_fp8(x, wq, wsc)
+                    t_new, t_old = time_fn(new), time_fn(old)
+                    nbytes = rows * K + 2.0 * (M * K + M * N)
+                    rec = dict(kernel="gemm_decode_w8", name=case + "_w8", M=M, N=N, K=K, mode=mode, us=t_new * 1e6,
+                               quant_plus_fp8_gemm_us=t_old * 1e6, gbs=nbytes / t_new / 1e9,
+                               frac_of_measured_roofline=nbytes / bw / t_new)
+                    results.append(rec)
+                    print(json.dumps(rec), flush=True)
+                    continue
                 x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
                 w = (torch.randn(rows, K, device=dev) * 0.02).to(torch.bfloat16)
                 h = torch.randn(M, H, device=dev, dtype=torch.bfloat16)
@@ -132,6 +157,8 @@ def bench_decode_gemm(results, tp_degrees=(1, 8)):
                            speedup_vs_lib=t_lib / t_new)
                 results.append(rec)
                 print(json.dumps(rec), flush=True)
+        if only is not None:
+            continue
         # chain of 8 layers' GEMMs (no attention): us per layer
         n_layers = 8
         ws = [[(torch.randn(r, k, device=dev) * 0.02).to(torch.bfloat16)
@@ -358,7 +385,7 @@ def main(argv=None):
             shapes = [s for s in shapes if s[0] in keep]
         bench_gemm(shapes, results, cfgs)
     if "dec" in what:
-        bench_decode_gemm(results)
+        bench_decode_gemm(results, only=set(args.only.split(",")) if args.only else None)
     if "attn" in what:
         bench_attention(results, set(args.only.split(",")) if args.only else None)
     if "misc" in what:

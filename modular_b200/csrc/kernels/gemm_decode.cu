@@ -289,7 +289,7 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&tail->full[s], w8 ? kConvWarps : 1);
+      mbar_init(&tail->full[s], 1);      // the TMA transaction count, or the one converter warp of the stage
       mbar_init(&tail->empty[s], 1);
       mbar_init(&tail->raw_full[s], 1);
     }
@@ -414,9 +414,13 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     pdl_trigger();
     if (w8 && warp < 6 + kConvWarps) {
       // ---------------------------------------------------------------- fp8 weight tiles -> scaled bf16 operand tiles
-      // two threads per weight row: 32 e4m3 values each -> four 16-byte chunks of the 128-byte-swizzled K-major tile
-      const int tid = (warp - 6) * 32 + lane;
-      const int r = tid >> 1, half = tid & 1;
+      // Each converter warp owns ring stages (stage s belongs to warp s % kConvWarps) and converts every tile that
+      // lands there by itself, so one tile per stage is in conversion at once and the latency of one tile's
+      // load-convert-store chain is hidden behind the others'. A stage's barrier is always waited on by the same
+      // warp, phase after phase: a waiter that skipped phases could not tell them apart by parity. Per pass a warp reads 512 contiguous raw bytes
+      // (8 rows x 64): lane l holds 16 values of row l / 4 and writes two 16-byte chunks of the 128-byte-swizzled
+      // K-major tile.
+      const int cw = warp - 6;
       SegIter it(p, g);
       Seg s;
       int st = 0;
@@ -426,28 +430,34 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const int n_tile = s.tile / p.m_tiles;
         const float* srow = p.w_scale + static_cast<size_t>(n_tile) * p.sw_ld;
         for (int kbi = s.kb0; kbi < s.kb1; ++kbi) {
-          if (!mbar_wait(&tail->raw_full[st], ph, abort_word, p.err, 307)) { ok = false; break; }
-          const float sc = srow[kbi >> 1];                  // one scale per 128 K values = two K blocks of 64
-          uint8_t* sa = smem + st * stage_bytes;
-          const uint8_t* raw = sa + kATile + b_bytes + r * 64 + half * 32;
-          const uint4 q0 = *reinterpret_cast<const uint4*>(raw), q1 = *reinterpret_cast<const uint4*>(raw + 16);
-          const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+          if (st % kConvWarps == cw) {
+            if (!mbar_wait(&tail->raw_full[st], ph, abort_word, p.err, 307)) { ok = false; break; }
+            const float sc = srow[kbi >> 1];                  // one scale per 128 K values = two K blocks of 64
+            uint8_t* sa = smem + st * stage_bytes;
+            const uint8_t* raw = sa + kATile + b_bytes + lane * 16;
+#pragma unroll 4
+            for (int pass = 0; pass < 16; ++pass) {
+              const uint4 q = *reinterpret_cast<const uint4*>(raw + pass * 512);
+              const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+              const int r = pass * 8 + (lane >> 2);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            float v[8];
+              for (int c = 0; c < 2; ++c) {
+                float v[8];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              __nv_fp8x4_e4m3 q;
-              q.__x = qw[c * 2 + j];
-              const float4 f = static_cast<float4>(q);
-              v[4 * j] = f.x * sc; v[4 * j + 1] = f.y * sc; v[4 * j + 2] = f.z * sc; v[4 * j + 3] = f.w * sc;
+                for (int j = 0; j < 2; ++j) {
+                  __nv_fp8x4_e4m3 e;
+                  e.__x = qw[c * 2 + j];
+                  const float4 f = static_cast<float4>(e);
+                  v[4 * j] = f.x * sc; v[4 * j + 1] = f.y * sc; v[4 * j + 2] = f.z * sc; v[4 * j + 3] = f.w * sc;
+                }
+                const int chunk = (lane & 3) * 2 + c;
+                *reinterpret_cast<uint4*>(sa + r * 128 + ((chunk ^ (r & 7)) << 4)) = pack_bf16x8(v);
+              }
             }
-            const int chunk = half * 4 + c;
-            *reinterpret_cast<uint4*>(sa + r * 128 + ((chunk ^ (r & 7)) << 4)) = pack_bf16x8(v);
+            fence_proxy_async_smem();        // generic-proxy writes before the tensor core reads the tile
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tail->full[st]);
           }
-          fence_proxy_async_smem();        // generic-proxy writes before the tensor core reads the tile
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tail->full[st]);
           if (++st == p.stages) { st = 0; ph ^= 1; }
         }
       }

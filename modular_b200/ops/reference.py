@@ -213,6 +213,42 @@ def dequant_fp8_weight_block128(q, scale):
     return q.float() * s
 
 
+# ---------------------------------------------------------------------------- nvfp4 (e2m1 values, e4m3 block scales)
+_E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def quant_nvfp4_weight(w):
+    """NVFP4 quantisation of a weight [N, K] (K % 16 == 0): 4-bit e2m1 values, one e4m3 scale per 16 values along K
+    and one fp32 scale per tensor. Returns (packed uint8 [N, K / 2] with the even index in the low nibble, block
+    scales float8_e4m3fn [N, K / 16], global scale fp32 scalar tensor); ``w ~ e2m1 * block_scale * global_scale``.
+    Reference format: the reference's nvfp4 weights (max/python/max/nn/quant_config.py, kernels
+    linalg/matmul/gpu/sm100/block_scaled_matmul.mojo)."""
+    N, K = w.shape
+    assert K % 16 == 0
+    wf = w.float()
+    amax = wf.abs().amax().clamp_min(1e-12)
+    g = amax / (6.0 * FP8_MAX)                                  # block scales then fit e4m3
+    blocks = wf.view(N, K // 16, 16)
+    bs = (blocks.abs().amax(-1) / 6.0 / g).clamp(max=FP8_MAX).to(torch.float8_e4m3fn)
+    denom = (bs.float() * g).clamp_min(1e-30).unsqueeze(-1)
+    x = (blocks / denom).clamp(-6.0, 6.0)
+    grid = torch.tensor(_E2M1_VALUES, dtype=torch.float32, device=w.device)
+    idx = (x.abs().unsqueeze(-1) - grid).abs().argmin(-1)       # nearest representable magnitude
+    code = (idx | ((x < 0).long() << 3)).view(N, K).to(torch.uint8)
+    packed = (code[:, 0::2] | (code[:, 1::2] << 4)).contiguous()
+    return packed, bs.contiguous(), g.reshape(()).clone()
+
+
+def dequant_nvfp4_weight(packed, block_scale, global_scale):
+    N, K2 = packed.shape
+    grid = torch.tensor(_E2M1_VALUES, dtype=torch.float32, device=packed.device)
+    lo, hi = (packed & 0xF).long(), (packed >> 4).long()
+    code = torch.stack((lo, hi), dim=-1).view(N, K2 * 2)
+    val = grid[code & 7] * torch.where((code & 8) != 0, -1.0, 1.0)
+    s = block_scale.float().repeat_interleave(16, 1) * global_scale.float()
+    return val * s
+
+
 def linear_fp8_blockscaled(xq, xs, wq, ws, residual=None, out_dtype=torch.bfloat16):
     """fp32 emulation of the block-scaled GEMM: partial sums per 128-wide K group, scaled, added."""
     M, K = xq.shape
