@@ -56,7 +56,7 @@ constexpr int kATile = kBM * kBK * 2;
 constexpr int kThreads = 512;     // warps 0-5 run the main loop, all sixteen run the epilogue
 constexpr int kSlots = 6;      // most workspace slots per CTA (segments of different tiles)
 constexpr int kRawTile = 128 * 64;   // fp8 weight tile of one K block: 128 rows x 64 bytes, unswizzled
-constexpr int kConvWarps = 8;        // warps 6..13 convert fp8 weight tiles
+constexpr int kConvWarps = 10;       // warps 6..15 convert fp8 weight tiles: two per ring stage (at most 5 stages)
 constexpr uint32_t kSentinel2 = 0x80008000u;   // two bf16 -0.0
 
 struct Params {
@@ -289,7 +289,7 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&tail->full[s], 1);      // the TMA transaction count, or the one converter warp of the stage
+      mbar_init(&tail->full[s], w8 ? 2 : 1);   // the TMA transaction count, or the two converter warps of the stage
       mbar_init(&tail->empty[s], 1);
       mbar_init(&tail->raw_full[s], 1);
     }
@@ -414,10 +414,10 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     pdl_trigger();
     if (w8 && warp < 6 + kConvWarps) {
       // ---------------------------------------------------------------- fp8 weight tiles -> scaled bf16 operand tiles
-      // Each converter warp owns ring stages (stage s belongs to warp s % kConvWarps) and converts every tile that
-      // lands there by itself, so one tile per stage is in conversion at once and the latency of one tile's
+      // Two converter warps own each ring stage (warps 2s and 2s + 1 take the upper and lower 64 rows of every tile
+      // that lands in stage s), so one tile per stage is in conversion at once and the latency of one tile's
       // load-convert-store chain is hidden behind the others'. A stage's barrier is always waited on by the same
-      // warp, phase after phase: a waiter that skipped phases could not tell them apart by parity. Per pass a warp reads 512 contiguous raw bytes
+      // warps, phase after phase: a waiter that skipped phases could not tell them apart by parity. Per pass a warp reads 512 contiguous raw bytes
       // (8 rows x 64): lane l holds 16 values of row l / 4 and writes two 16-byte chunks of the 128-byte-swizzled
       // K-major tile.
       const int cw = warp - 6;
@@ -430,13 +430,13 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const int n_tile = s.tile / p.m_tiles;
         const float* srow = p.w_scale + static_cast<size_t>(n_tile) * p.sw_ld;
         for (int kbi = s.kb0; kbi < s.kb1; ++kbi) {
-          if (st % kConvWarps == cw) {
+          if (st == (cw >> 1)) {
             if (!mbar_wait(&tail->raw_full[st], ph, abort_word, p.err, 307)) { ok = false; break; }
             const float sc = srow[kbi >> 1];                  // one scale per 128 K values = two K blocks of 64
             uint8_t* sa = smem + st * stage_bytes;
             const uint8_t* raw = sa + kATile + b_bytes + lane * 16;
 #pragma unroll 4
-            for (int pass = 0; pass < 16; ++pass) {
+            for (int pass = (cw & 1) * 8; pass < (cw & 1) * 8 + 8; ++pass) {
               const uint4 q = *reinterpret_cast<const uint4*>(raw + pass * 512);
               const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
               const int r = pass * 8 + (lane >> 2);
@@ -790,6 +790,7 @@ static int dec_plan(int M, int N, int K, int mode, size_t ws_bytes, int num_sms,
   const int budget = (p.BN <= 128 ? g_dec_smem_kb : 200) * 1024;
   int stages = budget / stage_bytes;
   if (stages > 8) stages = 8;
+  if (w8 && stages > 5) stages = 5;     // two converter warps per stage, ten converter warps
   if (stages < 2) stages = 2;
   p.stages = stages;
   p.tiles = (N + kBM - 1) / kBM;
