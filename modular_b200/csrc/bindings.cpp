@@ -632,9 +632,40 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                        const c10::optional<Tensor>& h, const c10::optional<Tensor>& xn,
                        const c10::optional<Tensor>& gamma, double eps, double w_off, bool mbc, int world, int rank,
                        const std::vector<int64_t>& lam, int lam_rows, const Tensor& ws, Tensor& state,
-                       const c10::optional<Tensor>& w_scale) {
+                       const c10::optional<Tensor>& w_scale, int w_format, const c10::optional<Tensor>& w_block_scale,
+                       const c10::optional<Tensor>& w_global_scale) {
     need_cuda(x, "x"); need_cuda(w, "w");
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "gemm_dec: row-major 2-D operands");
+    if (w_format == 2 || w_format == 3) {
+      // weight-only NVFP4 (w: [N, K / 2] bytes) or MXFP8 (w: [N, K] e4m3) with per-block scale bytes
+      const int M = x.size(0), K = x.size(1), N = w.size(0);
+      TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.element_size() == 1 && w.is_contiguous() &&
+                      w.size(1) == (w_format == 2 ? K / 2 : K) && w_block_scale && w_block_scale->is_contiguous() &&
+                      w_block_scale->element_size() == 1 && w_block_scale->numel() == static_cast<int64_t>(N) * (K / (w_format == 2 ? 16 : 32)) &&
+                      (w_format == 3 || (w_global_scale && w_global_scale->scalar_type() == at::kFloat && w_global_scale->is_cuda())),
+                  "gemm_dec: quantised weight layout");
+      TORCH_CHECK(state.scalar_type() == at::kInt && state.numel() >= mb_gemm_dec_state_ints(), "gemm_dec: state");
+      void* yp = nullptr;
+      int ldy = 0;
+      if (mode == 2) {
+        TORCH_CHECK(h.has_value() && xn.has_value() && gamma.has_value() && h->is_contiguous() && xn->is_contiguous() &&
+                        h->size(1) == N && xn->size(1) == N && gamma->numel() == N, "gemm_dec mode 2: h / xn / gamma");
+      } else {
+        TORCH_CHECK(y.has_value() && y->stride(1) == 1 && y->size(0) >= M && y->size(1) == (mode == 1 ? N / 2 : N) &&
+                        y->scalar_type() == at::kBFloat16, "gemm_dec: output shape");
+        yp = y->data_ptr();
+        ldy = y->stride(0);
+      }
+      void* lamq[8] = {};
+      for (size_t i = 0; i < lam.size() && i < 8; ++i) lamq[i] = reinterpret_cast<void*>(lam[i]);
+      check_rc(mb_gemm_dec_wq(w_format, x.data_ptr(), w.data_ptr(), w_block_scale->data_ptr(),
+                              w_global_scale ? w_global_scale->data_ptr<float>() : nullptr, M, N, K, x.stride(0), mode, yp, ldy,
+                              const_cast<void*>(optptr(h)), const_cast<void*>(optptr(xn)), optptr(gamma),
+                              static_cast<float>(eps), static_cast<float>(w_off), mbc ? 1 : 0, world, rank, lamq, lam_rows,
+                              ws.data_ptr(), ws.nbytes(), state.data_ptr<int>(), error_flag(), num_sms(), cur_stream()),
+               "gemm_dec_wq");
+      return;
+    }
     // w_scale: block-scaled fp8 weights (e4m3 [N, K] contiguous, fp32 scales [N / 128, K / 128]); activations stay bf16
     TORCH_CHECK(x.scalar_type() == at::kBFloat16 &&
                     (w_scale ? (w.element_size() == 1 && w.is_contiguous() && w_scale->is_contiguous() &&
@@ -678,7 +709,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              "gemm_dec");
   }, py::arg("x"), py::arg("w"), py::arg("mode"), py::arg("y"), py::arg("h"), py::arg("xn"), py::arg("gamma"),
      py::arg("eps"), py::arg("w_off"), py::arg("mbc"), py::arg("world"), py::arg("rank"), py::arg("lam"),
-     py::arg("lam_rows"), py::arg("ws"), py::arg("state"), py::arg("w_scale") = py::none());
+     py::arg("lam_rows"), py::arg("ws"), py::arg("state"), py::arg("w_scale") = py::none(), py::arg("w_format") = 0,
+     py::arg("w_block_scale") = py::none(), py::arg("w_global_scale") = py::none());
   m.def("rmsnorm", &rmsnorm);
   m.def("add_rmsnorm", &add_rmsnorm);
   m.def("silu_mul", &silu_mul);

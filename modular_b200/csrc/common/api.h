@@ -108,6 +108,10 @@ int mb_gemm_dec_w8(const void* X, const void* Wq, const float* Ws, int M, int N,
                    void* h, void* xn, const void* gamma, float eps, float w_off, int mbc, int world, int rank,
                    void* const* lam, int lam_rows, void* ws, size_t ws_bytes, int* state, int* err, int num_sms,
                    cudaStream_t stream);
+int mb_gemm_dec_wq(int wfmt, const void* X, const void* Wq, const void* block_scales, const float* global_scale, int M,
+                   int N, int K, int ldx, int mode, void* Y, int ldy, void* h, void* xn, const void* gamma, float eps,
+                   float w_off, int mbc, int world, int rank, void* const* lam, int lam_rows, void* ws, size_t ws_bytes,
+                   int* state, int* err, int num_sms, cudaStream_t stream);
 void mb_set_gemm_dec_tile_epilogue(int on);
 void mb_set_gemm_dec_rope(int on);
 int mb_gemm_dec_qkv_rope(const void* X, const void* W, int M, int K, int ldx, int ldw, void* qkv, int ldy,

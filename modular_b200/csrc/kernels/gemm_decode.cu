@@ -85,6 +85,13 @@ struct Params {
   // the accumulation then runs in bf16 x bf16 as for bf16 weights. w_scale = nullptr: bf16 weights.
   const float* w_scale;    // [N / 128, sw_ld]
   int sw_ld;
+  // Other weight-only formats through the same converter warps (wfmt): 2 = NVFP4 (two e2m1 values per byte, one
+  // e4m3 scale per 16 values along K in w_bscale, one fp32 scale per tensor at *w_gscale), 3 = MXFP8 (e4m3 values,
+  // one power-of-two ue8m0 scale per 32 values in w_bscale). 0 = bf16 weights, 1 = e4m3 with 128 x 128 fp32 scales.
+  int wfmt;
+  const uint8_t* w_bscale;  // [N, bs_ld] bytes
+  int bs_ld;
+  const float* w_gscale;
   // QKV projection with the rotation and the cache store in the tile epilogue (head_dim 128: an output tile is
   // one head; rotate-half convention). rope = 1: tiles [0, n_q) are query heads (rotated, stored to Y), the next
   // n_kv key heads (rotated, stored to Y and to the K cache at the token's slot), the last n_kv value heads
@@ -279,7 +286,9 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const int b_bytes = p.BN * kBK * 2;
-  const bool w8 = p.w_scale != nullptr;
+  const bool w8 = p.wfmt != 0;
+  const int raw_row = p.wfmt == 2 ? 32 : 64;            // raw bytes of one weight row of a K block
+  const int raw_bytes = 128 * raw_row;
   const int stage_bytes = kATile + b_bytes + (w8 ? kRawTile : 0);
   Tail* tail = reinterpret_cast<Tail*>(smem + p.stages * stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -330,8 +339,8 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           for (int kbi = s.kb0; kbi < s.kb1 && pre < p.stages; ++kbi) {
             if (w8) {
               // fp8 weights: the raw tile goes behind the operand tiles of the stage and signals the converters
-              mbar_arrive_expect_tx(&tail->raw_full[st], kRawTile + b_bytes);
-              tma_load_2d(smem + st * stage_bytes + kATile + b_bytes, &tmW, &tail->raw_full[st], kbi * kBK, n0);
+              mbar_arrive_expect_tx(&tail->raw_full[st], raw_bytes + b_bytes);
+              tma_load_2d(smem + st * stage_bytes + kATile + b_bytes, &tmW, &tail->raw_full[st], kbi * raw_row, n0);
             } else {
               mbar_arrive_expect_tx(&tail->full[st], stage_bytes);
               tma_load_2d(smem + st * stage_bytes, &tmW, &tail->full[st], kbi * kBK, n0);
@@ -358,8 +367,8 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           if (issued >= pre) {
             if (!mbar_wait(&tail->empty[st], ph ^ 1, abort_word, p.err, 301)) { ok = false; break; }
             if (w8) {
-              mbar_arrive_expect_tx(full_st, kRawTile + b_bytes);
-              tma_load_2d(sa + kATile + b_bytes, &tmW, full_st, kbi * kBK, n0);
+              mbar_arrive_expect_tx(full_st, raw_bytes + b_bytes);
+              tma_load_2d(sa + kATile + b_bytes, &tmW, full_st, kbi * raw_row, n0);
             } else {
               mbar_arrive_expect_tx(full_st, stage_bytes);
               tma_load_2d(sa, &tmW, full_st, kbi * kBK, n0);
@@ -428,30 +437,68 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       bool ok = true;
       while (ok && it.next(s)) {
         const int n_tile = s.tile / p.m_tiles;
-        const float* srow = p.w_scale + static_cast<size_t>(n_tile) * p.sw_ld;
+        const float* srow = p.wfmt == 1 ? p.w_scale + static_cast<size_t>(n_tile) * p.sw_ld : nullptr;
         for (int kbi = s.kb0; kbi < s.kb1; ++kbi) {
           if (st == (cw >> 1)) {
             if (!mbar_wait(&tail->raw_full[st], ph, abort_word, p.err, 307)) { ok = false; break; }
-            const float sc = srow[kbi >> 1];                  // one scale per 128 K values = two K blocks of 64
             uint8_t* sa = smem + st * stage_bytes;
             const uint8_t* raw = sa + kATile + b_bytes + lane * 16;
-#pragma unroll 4
-            for (int pass = (cw & 1) * 8; pass < (cw & 1) * 8 + 8; ++pass) {
-              const uint4 q = *reinterpret_cast<const uint4*>(raw + pass * 512);
-              const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-              const int r = pass * 8 + (lane >> 2);
+            if (p.wfmt == 2) {
+              // NVFP4: 16 rows x 32 raw bytes per pass; lane l holds 32 values of row l / 2 (two scale blocks of 16)
+              const float gs = *p.w_gscale;
+#pragma unroll 2
+              for (int pass = (cw & 1) * 4; pass < (cw & 1) * 4 + 4; ++pass) {
+                const uint4 q = *reinterpret_cast<const uint4*>(raw + pass * 512);
+                const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+                const int r = pass * 16 + (lane >> 1);
+                const uint16_t sb = *reinterpret_cast<const uint16_t*>(
+                    p.w_bscale + static_cast<size_t>(n_tile * 128 + r) * p.bs_ld + kbi * 4 + (lane & 1) * 2);
+                __nv_fp8_e4m3 s0, s1;
+                s0.__x = static_cast<__nv_fp8_storage_t>(sb & 0xff);
+                s1.__x = static_cast<__nv_fp8_storage_t>(sb >> 8);
+                const float sc2[2] = {static_cast<float>(s0) * gs, static_cast<float>(s1) * gs};
 #pragma unroll
-              for (int c = 0; c < 2; ++c) {
-                float v[8];
+                for (int c = 0; c < 4; ++c) {
+                  float v[8];
+                  const uint32_t w4 = qw[c];
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                  __nv_fp8x4_e4m3 e;
-                  e.__x = qw[c * 2 + j];
-                  const float4 f = static_cast<float4>(e);
-                  v[4 * j] = f.x * sc; v[4 * j + 1] = f.y * sc; v[4 * j + 2] = f.z * sc; v[4 * j + 3] = f.w * sc;
+                  for (int j = 0; j < 8; ++j) {
+                    const uint32_t nib = (w4 >> (4 * j)) & 0xfu, m = nib & 7u;
+                    // e2m1 magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6} as bf16 bit patterns, widened to fp32
+                    const uint32_t bits = m >= 2u ? 0x3f80u + (m - 2u) * 0x40u : (m ? 0x3f00u : 0u);
+                    v[j] = __uint_as_float((bits | ((nib & 8u) << 12)) << 16) * sc2[c >> 1];
+                  }
+                  const int chunk = (lane & 1) * 4 + c;
+                  *reinterpret_cast<uint4*>(sa + r * 128 + ((chunk ^ (r & 7)) << 4)) = pack_bf16x8(v);
                 }
-                const int chunk = (lane & 3) * 2 + c;
-                *reinterpret_cast<uint4*>(sa + r * 128 + ((chunk ^ (r & 7)) << 4)) = pack_bf16x8(v);
+              }
+            } else {
+              // e4m3 values: 8 rows x 64 raw bytes per pass; lane l holds 16 values of row l / 4
+              const float sc128 = p.wfmt == 1 ? srow[kbi >> 1] : 0.f;   // one scale per 128 K values = two K blocks
+#pragma unroll 4
+              for (int pass = (cw & 1) * 8; pass < (cw & 1) * 8 + 8; ++pass) {
+                const uint4 q = *reinterpret_cast<const uint4*>(raw + pass * 512);
+                const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+                const int r = pass * 8 + (lane >> 2);
+                float sc = sc128;
+                if (p.wfmt == 3) {
+                  // MXFP8: a power-of-two scale per 32 values (ue8m0: 2^(e - 127))
+                  const uint32_t e = p.w_bscale[static_cast<size_t>(n_tile * 128 + r) * p.bs_ld + kbi * 2 + ((lane & 3) >> 1)];
+                  sc = __uint_as_float(e << 23);
+                }
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                  float v[8];
+#pragma unroll
+                  for (int j = 0; j < 2; ++j) {
+                    __nv_fp8x4_e4m3 e;
+                    e.__x = qw[c * 2 + j];
+                    const float4 f = static_cast<float4>(e);
+                    v[4 * j] = f.x * sc; v[4 * j + 1] = f.y * sc; v[4 * j + 2] = f.z * sc; v[4 * j + 3] = f.w * sc;
+                  }
+                  const int chunk = (lane & 3) * 2 + c;
+                  *reinterpret_cast<uint4*>(sa + r * 128 + ((chunk ^ (r & 7)) << 4)) = pack_bf16x8(v);
+                }
               }
             }
             fence_proxy_async_smem();        // generic-proxy writes before the tensor core reads the tile
@@ -840,7 +887,8 @@ static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int 
                          void* Y, int ldy, void* h, void* xn, const void* gamma, float eps, float w_off,
                          int mbc, int world, int rank, void* const* lam, int lam_rows, void* ws,
                          size_t ws_bytes, int* state, int* err, int num_sms, cudaStream_t stream, int bN, int x_boff,
-                         int y_boff, int x_cols, const DecRope* rope = nullptr, const float* w_scale = nullptr) {
+                         int y_boff, int x_cols, const DecRope* rope = nullptr, const float* w_scale = nullptr,
+                         int wfmt = 0, const uint8_t* w_bscale = nullptr, const float* w_gscale = nullptr) {
   using namespace mb::dec;
   if (M <= 0 || N <= 0) return MB_OK;
   if (ldx % 8 || ldw % 8 || (mode != 2 && ldy % 8)) return MB_ERR_SHAPE;
@@ -853,10 +901,15 @@ static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int 
     return MB_ERR_ALIGN;
   if (num_sms <= 0) num_sms = 148;
   Params p;
-  int rc = dec_plan(M, N, K, mode, ws_bytes, num_sms, &p, w_scale != nullptr);
+  if (w_scale != nullptr) wfmt = 1;
+  int rc = dec_plan(M, N, K, mode, ws_bytes, num_sms, &p, wfmt != 0);
   if (rc != MB_OK) return rc;
-  if (w_scale != nullptr && (N % 128 || K % 128 || bN > 0)) return MB_ERR_SHAPE;
+  if (wfmt != 0 && (N % 128 || K % 128 || bN > 0)) return MB_ERR_SHAPE;
+  if ((wfmt == 2 && (w_bscale == nullptr || w_gscale == nullptr)) || (wfmt == 3 && w_bscale == nullptr) || wfmt < 0 || wfmt > 3)
+    return MB_ERR_SHAPE;
   p.w_scale = w_scale; p.sw_ld = (K + 127) / 128;
+  p.wfmt = wfmt; p.w_bscale = w_bscale; p.w_gscale = w_gscale;
+  p.bs_ld = wfmt == 2 ? K / 16 : K / 32;
   p.ws = static_cast<float*>(ws);
   p.trace = g_dec_trace;
   p.state = state; p.err = err; p.mode = mode;
@@ -880,11 +933,14 @@ static int gemm_dec_impl(const void* X, const void* W, int M, int N, int K, int 
     p.lam[i] = (mode == 2 && world > 1 && i < world) ? static_cast<__nv_bfloat16*>(lam[i]) : nullptr;
   CUtensorMap tw, tx;
   // fp8 weights: 128 rows x 64 bytes per K block, unswizzled (the converter warps write the operand layout)
-  rc = w_scale != nullptr ? cached_tmap_raw(&tw, W, N, K, ldw, kBM, 64) : cached_tmap(&tw, W, N, K, ldw, kBM, 2);
+  // (NVFP4: two values per byte, so a K block of 64 values is 32 bytes of a [N, K / 2] byte matrix)
+  rc = wfmt == 2   ? cached_tmap_raw(&tw, W, N, K / 2, K / 2, kBM, 32)
+       : wfmt != 0 ? cached_tmap_raw(&tw, W, N, K, ldw, kBM, 64)
+                   : cached_tmap(&tw, W, N, K, ldw, kBM, 2);
   if (rc != MB_OK) return rc;
   rc = cached_tmap(&tx, X, M, bN > 0 ? x_cols : K, ldx, p.BN, 2);
   if (rc != MB_OK) return rc;
-  const int stage_bytes = kATile + p.BN * kBK * 2 + (w_scale != nullptr ? kRawTile : 0);
+  const int stage_bytes = kATile + p.BN * kBK * 2 + (wfmt != 0 ? kRawTile : 0);
   const size_t smem = static_cast<size_t>(p.stages) * stage_bytes + sizeof(Tail) + 1024;
   static PerDeviceOnce configured;
   if (configured.needed()) {
@@ -940,4 +996,19 @@ extern "C" int mb_gemm_dec_w8(const void* X, const void* Wq, const float* Ws, in
   if (Ws == nullptr) return MB_ERR_SHAPE;
   return gemm_dec_impl(X, Wq, M, N, K, ldx, K, mode, Y, ldy, h, xn, gamma, eps, w_off, mbc, world, rank, lam, lam_rows,
                        ws, ws_bytes, state, err, num_sms, stream, 0, 0, 0, 0, nullptr, Ws);
+}
+
+// The decode-step GEMM on NVFP4 (wfmt 2: Wq [N, K / 2] bytes, two e2m1 values per byte with the even index in the low
+// nibble; block_scales [N, K / 16] e4m3; *global_scale fp32 on the device) or MXFP8 (wfmt 3: Wq [N, K] e4m3;
+// block_scales [N, K / 32] ue8m0) weights with bf16 activations: weight-only quantisation, dequantised tile by tile
+// in shared memory. Plain and SwiGLU modes and the all-reduce tail as for the other formats.
+extern "C" int mb_gemm_dec_wq(int wfmt, const void* X, const void* Wq, const void* block_scales, const float* global_scale,
+                              int M, int N, int K, int ldx, int mode, void* Y, int ldy, void* h, void* xn,
+                              const void* gamma, float eps, float w_off, int mbc, int world, int rank, void* const* lam,
+                              int lam_rows, void* ws, size_t ws_bytes, int* state, int* err, int num_sms,
+                              cudaStream_t stream) {
+  if (wfmt != 2 && wfmt != 3) return MB_ERR_SHAPE;
+  return gemm_dec_impl(X, Wq, M, N, K, ldx, K, mode, Y, ldy, h, xn, gamma, eps, w_off, mbc, world, rank, lam, lam_rows,
+                       ws, ws_bytes, state, err, num_sms, stream, 0, 0, 0, 0, nullptr, nullptr, wfmt,
+                       static_cast<const uint8_t*>(block_scales), global_scale);
 }

@@ -35,13 +35,20 @@ def _rand(shape, std, dtype, device, gen):
 
 
 class Linear:
-    """``y = x @ W.T (+ b)``; W is [out, in] in bf16, or fp8 with 128x128 block scales."""
+    """``y = x @ W.T (+ b)``; W is [out, in] in bf16, fp8 with 128x128 block scales, or weight-only NVFP4 / MXFP8
+    (``weight_format``; reference: max/python/max/nn/linear.py:44 with the float8 / float4 configs of
+    nn/quant_config.py). NVFP4 / MXFP8 weights run on the decode-step GEMM up to 256 rows (tiles dequantised in
+    shared memory) and are expanded to bf16 for larger inputs."""
 
     def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  weight_scale: Optional[torch.Tensor] = None,
-                 strategy: ShardingStrategy = ShardingStrategy.REPLICATE, split_sizes: Sequence[int] = ()):
+                 strategy: ShardingStrategy = ShardingStrategy.REPLICATE, split_sizes: Sequence[int] = (),
+                 weight_format: Optional[str] = None, block_scale: Optional[torch.Tensor] = None,
+                 global_scale: Optional[torch.Tensor] = None):
         self.weight, self.bias, self.weight_scale = weight, bias, weight_scale
         self.strategy, self.split_sizes = strategy, tuple(split_sizes)
+        self.weight_format, self.block_scale, self.global_scale = weight_format, block_scale, global_scale
+        self._expanded = None
 
     @classmethod
     def random(cls, in_dim, out_dim, dtype=torch.bfloat16, device="cpu", bias=False, std=0.02, seed=0, **kw):
@@ -51,7 +58,7 @@ class Linear:
 
     @property
     def in_dim(self):
-        return self.weight.shape[1]
+        return self.weight.shape[1] * (2 if self.weight_format == "nvfp4" else 1)
 
     @property
     def out_dim(self):
@@ -61,10 +68,41 @@ class Linear:
         q, s = ops.reference.quant_fp8_weight_block128(self.weight.float())
         return Linear(q, self.bias, s, self.strategy, self.split_sizes)
 
+    def quantize_nvfp4(self) -> "Linear":
+        q, bs, gs = ops.reference.quant_nvfp4_weight(self.weight.float())
+        return Linear(q, self.bias, None, self.strategy, self.split_sizes, "nvfp4", bs, gs)
+
+    def quantize_mxfp8(self) -> "Linear":
+        q, bs = ops.reference.quant_mxfp8_weight(self.weight.float())
+        return Linear(q, self.bias, None, self.strategy, self.split_sizes, "mxfp8", bs)
+
+    def dequantized_weight(self) -> torch.Tensor:
+        """bf16 weights of a quantised layer (cached: the form that steps of more than 256 rows multiply with)."""
+        if self._expanded is None:
+            if self.weight_format == "nvfp4":
+                w = ops.reference.dequant_nvfp4_weight(self.weight, self.block_scale, self.global_scale)
+            elif self.weight_format == "mxfp8":
+                w = ops.reference.dequant_mxfp8_weight(self.weight, self.block_scale)
+            else:
+                w = ops.reference.dequant_fp8_weight_block128(self.weight, self.weight_scale)
+            self._expanded = w.to(torch.bfloat16 if self.weight.is_cuda else torch.float32)
+        return self._expanded
+
     def __call__(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
-        if self.weight_scale is not None:
+        if self.weight_format in ("nvfp4", "mxfp8"):
+            n, k = self.out_dim, self.in_dim
+            if (x2.is_cuda and x2.dtype == torch.bfloat16 and x2.shape[0] <= ops.DECODE_GEMM_MAX_TOKENS
+                    and n % 128 == 0 and k % 128 == 0):
+                y = ops.linear_decode(x2.contiguous(), self.weight, w_format=self.weight_format,
+                                      w_block_scale=self.block_scale, w_global_scale=self.global_scale)
+                if residual is not None:
+                    y = y + residual
+            else:
+                w = self.dequantized_weight().to(x2.dtype)
+                y = ops.linear(x2, w, residual=residual) if x2.is_cuda else ops.reference.linear(x2, w, residual)
+        elif self.weight_scale is not None:
             if x2.is_cuda:
                 y = ops.linear_fp8(x2, self.weight, self.weight_scale, residual=residual)
             else:

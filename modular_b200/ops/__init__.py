@@ -87,7 +87,8 @@ DECODE_GEMM_MAX_TOKENS = 256      # the decode-step GEMM takes at most this many
 
 
 def linear_decode(x, w, mode="plain", out=None, h=None, gamma=None, eps=1e-5, weight_offset=0.0,
-                  multiply_before_cast=False, xn=None, tp=None, w_scale=None):
+                  multiply_before_cast=False, xn=None, tp=None, w_scale=None, w_format=None, w_block_scale=None,
+                  w_global_scale=None):
     """Decode-step GEMM (at most 256 token rows) with its fused tail.
 
     mode ``plain``: ``x @ w.T``; ``swiglu``: ``silu(x @ wg.T) * (x @ wu.T)`` with ``w = [wg; wu]``;
@@ -95,11 +96,19 @@ def linear_decode(x, w, mode="plain", out=None, h=None, gamma=None, eps=1e-5, we
     lam (peer addresses of the receive buffers), lam_rows, state) or this GPU alone, in place, and returns
     ``(rms_norm(h) * gamma, h)``. ``w_scale``: ``w`` is block-scaled fp8 (e4m3 [N, K], fp32 scales
     [N / 128, K / 128]); the kernel converts weight tiles to scaled bf16 in shared memory and the activations stay
-    bf16. CPU tensors take the PyTorch reference."""
+    bf16. ``w_format``: ``"nvfp4"`` (``w`` [N, K / 2] bytes of e2m1 pairs, ``w_block_scale`` [N, K / 16] e4m3,
+    ``w_global_scale`` fp32 scalar tensor) or ``"mxfp8"`` (``w`` [N, K] e4m3, ``w_block_scale`` [N, K / 32] ue8m0
+    bytes): weight-only quantisation, dequantised tile by tile in shared memory. CPU tensors take the PyTorch
+    reference."""
     code = {"plain": 0, "swiglu": 1, "add_norm": 2}[mode]
+    fmt = {None: 0, "nvfp4": 2, "mxfp8": 3}[w_format]
     if not x.is_cuda:
         if w_scale is not None:
             w = ref.dequant_fp8_weight_block128(w, w_scale).to(x.dtype)
+        elif fmt == 2:
+            w = ref.dequant_nvfp4_weight(w, w_block_scale, w_global_scale).to(x.dtype)
+        elif fmt == 3:
+            w = ref.dequant_mxfp8_weight(w, w_block_scale).to(x.dtype)
         if code == 0:
             return ref.linear(x, w)
         if code == 1:
@@ -114,12 +123,13 @@ def linear_decode(x, w, mode="plain", out=None, h=None, gamma=None, eps=1e-5, we
         t = tp or {}
         _lib().gemm_dec(x, w, 2, None, h, xn, gamma, eps, weight_offset, multiply_before_cast,
                         t.get("world", 1), t.get("rank", 0), t.get("lam", []), t.get("lam_rows", 0), ws,
-                        t.get("state", state), w_scale)
+                        t.get("state", state), w_scale, fmt, w_block_scale, w_global_scale)
         return xn, h
     if out is None:
         n = w.shape[0] // 2 if code == 1 else w.shape[0]
         out = torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
-    _lib().gemm_dec(x, w, code, out, None, None, None, 0.0, 0.0, False, 1, 0, [], 0, ws, state, w_scale)
+    _lib().gemm_dec(x, w, code, out, None, None, None, 0.0, 0.0, False, 1, 0, [], 0, ws, state, w_scale, fmt,
+                    w_block_scale, w_global_scale)
     return out
 
 

@@ -249,6 +249,23 @@ def dequant_nvfp4_weight(packed, block_scale, global_scale):
     return val * s
 
 
+def quant_mxfp8_weight(w):
+    """MXFP8 quantisation of a weight [N, K] (K % 32 == 0): e4m3 values with one power-of-two scale per 32 values
+    along K. Returns (q float8_e4m3fn [N, K], scales uint8 [N, K / 32] in ue8m0: scale = 2^(byte - 127))."""
+    N, K = w.shape
+    assert K % 32 == 0
+    blocks = w.float().view(N, K // 32, 32)
+    amax = blocks.abs().amax(-1).clamp_min(2.0 ** -120)
+    e = torch.ceil(torch.log2(amax / FP8_MAX)).clamp(-127, 127)
+    q = (blocks / torch.exp2(e).unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).view(N, K).to(torch.float8_e4m3fn)
+    return q.contiguous(), (e + 127).to(torch.uint8).contiguous()
+
+
+def dequant_mxfp8_weight(q, scale_bytes):
+    s = torch.exp2(scale_bytes.float() - 127.0).repeat_interleave(32, 1)
+    return q.float() * s
+
+
 def linear_fp8_blockscaled(xq, xs, wq, ws, residual=None, out_dtype=torch.bfloat16):
     """fp32 emulation of the block-scaled GEMM: partial sums per 128-wide K group, scaled, added."""
     M, K = xq.shape

@@ -22,7 +22,7 @@ import torch
 class QuantConfig:
     """Weight/activation quantisation of a checkpoint."""
 
-    format: str = "none"                 # none | blockscaled_fp8 | tensor_fp8 | compressed_tensors_fp8
+    format: str = "none"                 # none | blockscaled_fp8 | tensor_fp8 | compressed_tensors_fp8 | nvfp4 | mxfp8
     weight_block_size: tuple = (128, 128)
     activation_scheme: str = "dynamic"   # dynamic per-token-group (1 x 128) | static
     activation_group: int = 128
@@ -61,6 +61,20 @@ def parse_quant_config(hf_config: dict) -> Optional[QuantConfig]:
                                    "dynamic" if g.get("input_activations", {}).get("dynamic", True) else "static",
                                    128, "float8_e4m3fn", "weight_scale", tuple(q.get("ignore") or ()))
         raise ValueError("compressed-tensors checkpoint without an 8-bit float weight group")
+    if method in ("modelopt", "nvfp4"):
+        # NVIDIA Model Optimizer checkpoints: NVFP4 = 4-bit e2m1 weights, e4m3 scale per 16 values, fp32 scale per
+        # tensor (reference: nn/quant_config.py float4 config, weight adapters of the nvfp4 checkpoints)
+        algo = str(q.get("quant_algo") or q.get("quantization", {}).get("quant_algo") or "NVFP4").upper()
+        if algo == "NVFP4":
+            return QuantConfig("nvfp4", (1, 16), "dynamic", 16, "uint8", "weight_scale",
+                               tuple(q.get("exclude_modules") or q.get("ignore") or ()))
+        if algo in ("MXFP8", "FP8_MX"):
+            return QuantConfig("mxfp8", (1, 32), "dynamic", 32, "float8_e4m3fn", "weight_scale",
+                               tuple(q.get("exclude_modules") or q.get("ignore") or ()))
+        raise ValueError(f"unsupported modelopt quant_algo {algo!r}")
+    if method == "mxfp8":
+        return QuantConfig("mxfp8", (1, 32), "dynamic", 32, "float8_e4m3fn", "weight_scale",
+                           tuple(q.get("modules_to_not_convert") or ()))
     raise ValueError(f"unsupported quantisation method {method!r}")
 
 

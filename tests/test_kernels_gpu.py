@@ -512,6 +512,42 @@ def test_gemm_decode_fp8_weights_plain_and_add_norm(M, N, K):
     ops.check_device_error()
 
 
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp8"])
+@pytest.mark.parametrize("M,N,K", [(64, 1280, 8192), (1, 256, 128), (200, 1024, 3584), (128, 8192, 1024)])
+def test_gemm_decode_nvfp4_and_mxfp8_weights(fmt, M, N, K):
+    """Weight-only NVFP4 (e2m1 values, e4m3 scale per 16, fp32 scale per tensor) and MXFP8 (e4m3 values, power-of-two
+    scale per 32) on the decode-step GEMM: the tiles are dequantised to bf16 in shared memory, so the result equals
+    the product with the dequantised weights up to the bf16 rounding of those."""
+    torch.manual_seed(43)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    if fmt == "nvfp4":
+        wq, bs, gs = ref.quant_nvfp4_weight(w)
+        wd = ref.dequant_nvfp4_weight(wq, bs, gs)
+        kw = dict(w_format="nvfp4", w_block_scale=bs, w_global_scale=gs)
+        tol_q = 0.15           # 4-bit values: about 10 % relative error of the weights
+    else:
+        wq, bs = ref.quant_mxfp8_weight(w)
+        wd = ref.dequant_mxfp8_weight(wq, bs)
+        kw = dict(w_format="mxfp8", w_block_scale=bs)
+        tol_q = 0.05
+    wd = wd.to(torch.bfloat16)
+    for _ in range(2):
+        y = ops.linear_decode(x, wq, **kw)
+        assert _rel_err(y, ref.linear(x, wd)) < 1e-2
+    assert _rel_err(y, ref.linear(x, w)) < tol_q
+    if N % 256 == 0:
+        ys = ops.linear_decode(x, wq, mode="swiglu", **kw)
+        assert _rel_err(ys, ref.linear_swiglu(x, wd)) < 2e-2
+    h = (torch.randn(M, N, device=DEV) * 0.5).to(torch.bfloat16)
+    g = (1 + 0.1 * torch.randn(N, device=DEV)).to(torch.bfloat16)
+    h2 = h.clone()
+    xn, hh = ops.linear_decode(x, wq, mode="add_norm", h=h2, gamma=g, eps=1e-5, **kw)
+    want_n, want_h = ref.add_rms_norm(ref.linear(x, wd), h, g, 1e-5)
+    assert _rel_err(hh, want_h) < 1e-2 and _rel_err(xn, want_n) < 2e-2
+    ops.check_device_error()
+
+
 @pytest.mark.parametrize("M,inter,K", [(64, 3584, 8192), (16, 256, 256), (130, 1792, 1024)])
 def test_gemm_decode_fp8_weights_swiglu(M, inter, K):
     torch.manual_seed(42)

@@ -57,3 +57,30 @@ def test_norms_fp8_linear_and_vocab_parallel_embedding():
     ids = torch.tensor([[0, 13, 49], [25, 24, 7]])
     shards = [VocabParallelEmbedding.from_full(table, r, 2) for r in range(2)]
     assert torch.equal(sum(s(ids) for s in shards), table[ids])
+
+
+def test_linear_with_nvfp4_and_mxfp8_weights_and_their_quant_configs():
+    """Weight-only 4-bit (NVFP4) and micro-scaled 8-bit (MXFP8) linear layers against their dequantised weights, and
+    the checkpoint quantisation configs that name them."""
+    import torch
+
+    from modular_b200.nn.layers import Linear
+    from modular_b200.ops import reference as ref
+    from modular_b200.pipelines.weights import parse_quant_config
+
+    lin = Linear.random(256, 128, dtype=torch.float32, std=0.05, seed=3)
+    x = torch.randn(5, 256)
+    full = lin(x)
+    for q, tol in ((lin.quantize_nvfp4(), 0.2), (lin.quantize_mxfp8(), 0.06)):
+        assert q.in_dim == 256 and q.out_dim == 128
+        y = q(x)
+        assert torch.allclose(y, x @ q.dequantized_weight().float().t(), atol=1e-4)
+        assert (y - full).norm() / full.norm() < tol
+    p, bs, gs = ref.quant_nvfp4_weight(lin.weight)
+    assert p.dtype == torch.uint8 and p.shape == (128, 128) and bs.dtype == torch.float8_e4m3fn and bs.shape == (128, 16)
+    # every dequantised value is a representable e2m1 magnitude times its block scale
+    d = ref.dequant_nvfp4_weight(p, bs, gs).view(128, 16, 16) / (bs.float() * gs).clamp_min(1e-30).unsqueeze(-1)
+    assert set(d.abs().unique().round(decimals=3).tolist()) <= {0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0}
+    qc = parse_quant_config({"quantization_config": {"quant_method": "modelopt", "quant_algo": "NVFP4"}})
+    assert qc.format == "nvfp4" and qc.activation_group == 16
+    assert parse_quant_config({"quantization_config": {"quant_method": "mxfp8"}}).format == "mxfp8"
