@@ -348,6 +348,12 @@ def bench_misc(results):
     seeds = torch.arange(64, device=dev, dtype=torch.int64)
     t = time_fn(lambda: ops.sample(lg, temp, tk, tp_, mp, seeds, 1))
     rec("sample_topk_topp", t, lg.numel() * 4, rows=64, vocab=128256)
+    ops.set_sample_cluster(False)
+    t = time_fn(lambda: ops.sample(lg, temp, tk, tp_, mp, seeds, 1))
+    rec("sample_topk_topp_one_cta_per_row", t, lg.numel() * 4, rows=64, vocab=128256)
+    ops.set_sample_cluster(True)
+    t = time_fn(lambda: ops.sample(lg, temp, None, tp_, None, seeds, 1))
+    rec("sample_topp_only", t, lg.numel() * 4, rows=64, vocab=128256)
     t = time_fn(lambda: ops.argmax(lg))
     rec("argmax", t, lg.numel() * 4, rows=64, vocab=128256)
     torch.cuda.synchronize()

@@ -611,6 +611,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              "gemm_dec_qkv_rope");
   });
   m.def("set_gemm_dec_rope", [](bool on) { mb_set_gemm_dec_rope(on ? 1 : 0); }, py::arg("on"));
+  m.def("set_sample_cluster", [](bool on) { mb_set_sample_cluster(on ? 1 : 0); }, py::arg("on"));
   m.def("set_gemm_dec_tile_epilogue", [](bool on) { mb_set_gemm_dec_tile_epilogue(on ? 1 : 0); }, py::arg("on"));
   m.def("gemm_dec_sizes", []() {
     return py::make_tuple(static_cast<int64_t>(mb_gemm_dec_workspace_bytes(num_sms())), mb_gemm_dec_state_ints(),

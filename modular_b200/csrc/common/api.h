@@ -271,6 +271,8 @@ int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, int vocab, 
                         const float* temperature, const int32_t* top_k, const float* top_p,
                         const float* min_p, const uint64_t* seeds, uint64_t step,
                         cudaStream_t stream);
+// 0: rows with a top-k / top-p / min-p filter are not spread over a cluster of CTAs first (default 1)
+void mb_set_sample_cluster(int on);
 // ---- state-space layers (state_space.cu): ragged batches, per-sequence state slots (-1 = none)
 int mb_causal_conv1d_varlen(const void* x, const void* w, const void* bias, void* y, float* conv_state,
                             const int* cu_seqlens, const int* state_idx, const int* has_init, int n_seqs,

@@ -337,6 +337,12 @@ def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, seeds=N
     return out
 
 
+def set_sample_cluster(on: bool) -> None:
+    """Whether rows with a top-k / top-p / min-p filter are first sampled by the kernel that spreads a row
+    over a cluster of eight CTAs (default on); off leaves every row to the one-CTA-per-row kernel."""
+    _lib().set_sample_cluster(bool(on))
+
+
 def apply_penalties(logits, tok, cnt, offsets, freq=None, pres=None, rep=None):
     if not logits.is_cuda:
         return ref.apply_penalties(logits, tok, cnt, offsets, freq, pres, rep)

@@ -234,6 +234,36 @@ def test_argmax_and_sampling():
         assert s.unique().numel() > 8, kw
 
 
+def test_cluster_sampler_matches_one_cta_sampler():
+    # the same seeds give the same uniform draw, and both kernels walk the kept set in index order: apart
+    # from rounding at a bucket edge the two pick the same token
+    torch.manual_seed(81)
+    R, V = 96, 128256
+    logits = torch.randn(R, V, device=DEV) * 2
+    hot = torch.randint(0, V, (R, 40), device=DEV)
+    logits.scatter_add_(1, hot, torch.rand(R, 40, device=DEV) * 9)      # a peaked head like a language model's
+    seeds = torch.arange(R, device=DEV, dtype=torch.int64) * 31 + 7
+    temp = torch.full((R,), 0.9, device=DEV)
+    temp[::7] = 0.0                                                      # greedy rows pass through
+    cases = [dict(top_k=torch.full((R,), 40, device=DEV, dtype=torch.int32)),
+             dict(top_p=torch.full((R,), 0.85, device=DEV)),
+             dict(min_p=torch.full((R,), 0.05, device=DEV)),
+             dict(top_k=torch.randint(0, 300, (R,), device=DEV, dtype=torch.int32),
+                  top_p=torch.rand(R, device=DEV) * 0.6 + 0.4, min_p=torch.rand(R, device=DEV) * 0.02),
+             dict(top_k=torch.full((R,), 20000, device=DEV, dtype=torch.int32))]   # too wide: left to the other kernel
+    for kw in cases:
+        for lg in (logits, logits[:, :50001]):                           # second view: rows off a 16-byte boundary
+            ops.set_sample_cluster(True)
+            a = ops.sample(lg, temperature=temp, seeds=seeds, step=5, **kw)
+            ops.set_sample_cluster(False)
+            b = ops.sample(lg, temperature=temp, seeds=seeds, step=5, **kw)
+            ops.set_sample_cluster(True)
+            assert (a >= 0).all() and (a < lg.shape[1]).all()
+            assert (a == b).float().mean() >= 0.97, (list(kw), (a != b).sum().item())
+            assert torch.equal(a[::7], lg[::7].argmax(-1))
+    ops.check_device_error()
+
+
 def test_penalties():
     torch.manual_seed(9)
     logits = torch.randn(3, 1000, device=DEV)
