@@ -49,6 +49,9 @@ def _load():
             if hasattr(mod, "set_gemm_pair"):
                 plain, _, dual = os.environ.get("MB200_GEMM_PAIR", "512,0").partition(",")
                 mod.set_gemm_pair(int(plain or 0), int(dual or 0))
+            # MB200_GEMM_PAIR_PERSIST=0: one launch-time pair per tile even when there are more tiles than SM pairs
+            if hasattr(mod, "set_gemm_pair_persistent"):
+                mod.set_gemm_pair_persistent(os.environ.get("MB200_GEMM_PAIR_PERSIST", "1") not in ("", "0"))
             if hasattr(mod, "set_attn_decode_dense"):
                 mod.set_attn_decode_dense(os.environ.get("MB200_ATTN_DECODE_DENSE", "0") not in ("", "0"))
             if hasattr(mod, "set_attn_fork"):

@@ -473,6 +473,170 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------ persistent CTA-pair variant
+// The pair kernel above spends a TMEM allocation, a cluster barrier, a cold TMA ring and an epilogue that no
+// MMA overlaps on every tile. Here one pair per two SMs walks over tiles t = cluster, cluster + clusters, ...
+// (token tile fastest, so the pairs running at the same time share weight panels in L2). The operand ring
+// keeps running across tiles, and the accumulator has two TMEM stages of 256 columns: while the epilogue
+// warps of both CTAs drain stage a, the leader's MMAs fill stage a ^ 1.
+//   tmem_full[a]   one per CTA, completed by the leader's commit after the tile's last MMA
+//   tmem_empty[a]  in the leader, one arrival per epilogue warp of either CTA (eight)
+struct PairPersistTail {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_word;
+};
+constexpr int kAccStageCols = 256;
+
+template <int EPI>
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                            void* __restrict__ Yv, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
+                            int ldy, int ldr, int BN, int stages, int m_tiles, int total_tiles, int* err,
+                            int packed_kb) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int half = BN >> 1;
+  const int a_bytes = kATileBytes;
+  const int b_bytes = half * kBK * 2;
+  const int stage_bytes = a_bytes + b_bytes;
+  uint8_t* stage_buf = smem + stages * stage_bytes;
+  PairPersistTail* tail = reinterpret_cast<PairPersistTail*>(stage_buf + 4 * kStageWarpBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  const int cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+  const int k_iters = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tail->tmem_full[a], 1);
+      mbar_init(&tail->tmem_empty[a], 8);
+    }
+    tail->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tail->tmem_base, 2 * kAccStageCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t tmem_base = tail->tmem_base;
+  volatile int* abort_word = &tail->abort_word;
+  pdl_wait();
+  pdl_trigger();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = cluster; t < total_tiles && ok; t += clusters) {
+        const int n0 = (t / m_tiles) * (2 * kBM) + static_cast<int>(rank) * kBM;
+        const int tb0 = (t % m_tiles) * BN + static_cast<int>(rank) * half;
+        for (int it = 0; it < k_iters; ++it) {
+          if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, err, 116)) { ok = false; break; }
+          uint8_t* sa = smem + s * stage_bytes;
+          if (rank == 0) mbar_arrive_expect_tx(&tail->full[s], 2 * stage_bytes);
+          const uint32_t full_leader = mapa_shared(&tail->full[s], 0);
+          const int kc = it * kBK;
+          if (++s == stages) { s = 0; ph ^= 1; }
+          if (packed_kb > 0)
+            tma_load_2d_pair(sa, &tmW, full_leader, 0, ((n0 >> 7) * packed_kb + (kc / kBK)) << 7);
+          else
+            tma_load_2d_pair(sa, &tmW, full_leader, kc, n0);
+          tma_load_2d_pair(sa + a_bytes, &tmX, full_leader, kc, tb0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc(2 * kBM, BN, 1, 1);
+      const uint64_t da0_first = umma_desc_sw128(smem);
+      const uint64_t d_b = static_cast<uint64_t>(a_bytes >> 4);
+      const uint64_t d_stage = static_cast<uint64_t>(stage_bytes >> 4);
+      const uint32_t empty0 = mapa_shared(&tail->empty[0], 0), empty1 = mapa_shared(&tail->empty[0], 1);
+      const uint32_t tfull0 = mapa_shared(&tail->tmem_full[0], 0), tfull1 = mapa_shared(&tail->tmem_full[0], 1);
+      uint64_t da0 = da0_first;
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int i = 0;   // tiles done by this pair
+      for (int t = cluster; t < total_tiles && ok; t += clusters, ++i) {
+        const int a = i & 1;
+        // the epilogues of the tile that used this accumulator stage two tiles ago have read it out
+        ok = mbar_wait(&tail->tmem_empty[a], ((i >> 1) & 1) ^ 1, abort_word, err, 117);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(a * kAccStageCols);
+        for (int it = 0; it < k_iters; ++it) {
+          ok = mbar_wait(&tail->full[s], ph, abort_word, err, 118);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+            const uint64_t koff = static_cast<uint64_t>(k * kUmmaK * 2 >> 4);
+            umma_bf16_pair(d_tmem, da0 + koff, da0 + d_b + koff, idesc, acc);
+          }
+          tc_commit_pair(empty0 + 8u * s);   // mbarriers are 8 bytes apart, at the same offset in both CTAs
+          tc_commit_pair(empty1 + 8u * s);
+          if (++s == stages) { s = 0; ph ^= 1; da0 = da0_first; } else { da0 += d_stage; }
+        }
+        if (!ok) break;
+        tc_commit_pair(tfull0 + 8u * a);
+        tc_commit_pair(tfull1 + 8u * a);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    const uint32_t tempty_leader = mapa_shared(&tail->tmem_empty[0], 0);
+    int i = 0;
+    for (int t = cluster; t < total_tiles; t += clusters, ++i) {
+      const int a = i & 1;
+      if (!mbar_wait(&tail->tmem_full[a], (i >> 1) & 1, abort_word, err, 119)) break;
+      tc_fence_after();
+      const int n0 = (t / m_tiles) * (2 * kBM) + static_cast<int>(rank) * kBM;
+      const int t0 = (t % m_tiles) * BN;
+      if (k_iters > 0)
+        epilogue_tile<false, EPI>(tmem_base + static_cast<uint32_t>(a * kAccStageCols), stage_buf, quad, lane, Yv, R,
+                                  M, N, ldy, ldr, BN, n0, t0, M, 0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader + 8u * a);
+    }
+  }
+
+  // neither CTA may leave (or free TMEM) while the other can still read its shared memory, signal
+  // its barriers or run MMAs into its TMEM
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 2 * kAccStageCols);
+  }
+}
+
 // Sum split-K fp32 partials [splits, M, N] -> bf16 Y (+ optional residual).
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, const __nv_bfloat16* __restrict__ R,
                                      __nv_bfloat16* __restrict__ Y, int M, int N, int splits,
@@ -682,6 +846,45 @@ static int launch_pair_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y
   return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
+template <int EPI>
+static int launch_pair_persistent(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, const void* R, int M, int N,
+                                  int K, int ldy, int ldr, int BN, int stages, int num_sms, int* err,
+                                  cudaStream_t stream, int packed_kb) {
+  const int stage_bytes = kATileBytes + (BN / 2) * kBK * 2;
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes +
+                      sizeof(PairPersistTail) + 1024;
+  auto kern = gemm_pair_persistent_kernel<EPI>;
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+      return MB_ERR_LAUNCH;
+    configured.done();
+  }
+  const int m_tiles = (M + BN - 1) / BN;
+  const int total = m_tiles * ((N + 2 * kBM - 1) / (2 * kBM));
+  const int clusters = total < num_sms / 2 ? total : num_sms / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.numAttrs = 1;
+  if (pdl_enabled()) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  cfg.attrs = attr;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, Y, static_cast<const __nv_bfloat16*>(R), M, N, K, ldy,
+                                           ldr, BN, stages, m_tiles, total, err, packed_kb);
+  return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -825,6 +1028,9 @@ extern "C" int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const v
 // Process-wide choice of the CTA-pair kernel by token count: plain (and residual) GEMMs with
 // M >= min_m_plain and fused SwiGLU GEMMs with M >= min_m_dual use it; 0 = never.
 static int g_pair_min_m[2] = {0, 0};
+static bool g_pair_persistent = true;
+// 0: the CTA-pair GEMM launches one pair per tile even when there are more tiles than pairs of SMs
+extern "C" void mb_set_gemm_pair_persistent(int on) { g_pair_persistent = on != 0; }
 extern "C" void mb_set_gemm_pair(int min_m_plain, int min_m_dual) {
   g_pair_min_m[0] = min_m_plain;
   g_pair_min_m[1] = min_m_dual;
@@ -926,6 +1132,16 @@ extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const vo
   if (f32)
     return launch_pair_cfg<false, EPI_F32>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err, stream,
                                            gate_flags, gate_rpr, gate_world, packed_kb);
+  // more tiles than pairs of SMs: persistent pairs with two accumulator stages (epilogue under the next tile)
+  if (g_pair_persistent && gate_flags == nullptr &&
+      ((M + bn - 1) / bn) * ((N + 2 * kBM - 1) / (2 * kBM)) > num_sms / 2) {
+    const int ps = stages;
+    if (resid)
+      return launch_pair_persistent<EPI_BF16_RESIDUAL>(tw, tx, Y, R, M, N, K, ldy, ldr, bn, ps, num_sms, err, stream,
+                                                       packed_kb);
+    return launch_pair_persistent<EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, bn, ps, num_sms, err, stream,
+                                            packed_kb);
+  }
   if (resid)
     return launch_pair_cfg<false, EPI_BF16_RESIDUAL>(tw, tx, Y, R, M, N, K, ldy, ldr, 0, K, 1, bn, stages, err,
                                                      stream, gate_flags, gate_rpr, gate_world, packed_kb);

@@ -337,6 +337,12 @@ def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, seeds=N
     return out
 
 
+def set_gemm_pair_persistent(on: bool) -> None:
+    """Whether the CTA-pair GEMM runs as persistent pairs with two accumulator stages when a problem has more
+    tiles than pairs of SMs (default on); off launches one pair per tile."""
+    _lib().set_gemm_pair_persistent(bool(on))
+
+
 def set_sample_cluster(on: bool) -> None:
     """Whether rows with a top-k / top-p / min-p filter are first sampled by the kernel that spreads a row
     over a cluster of eight CTAs (default on); off leaves every row to the one-CTA-per-row kernel."""

@@ -40,6 +40,27 @@ def test_gemm_bf16(M, N, K, impl):
     assert (y.float() - yr.float()).abs().max() <= 0.02 * yr.float().abs().max() + 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(2176, 6144, 1024), (1280, 3840, 512), (1000, 5000, 520), (4096, 4096, 256)])
+def test_gemm_pair_persistent(M, N, K):
+    # more tiles than pairs of SMs: the pair kernel walks over tiles with two accumulator stages
+    torch.manual_seed(5)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    r = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        y = ops.linear(x, w, impl="pair")
+        yr = ops.linear(x, w, residual=r, impl="pair")
+    assert _rel_err(y, ref.linear(x, w)) < 1e-2
+    assert _rel_err(yr, ref.linear(x, w, r)) < 1e-2
+    ops.set_gemm_pair_persistent(False)
+    try:
+        y0 = ops.linear(x, w, impl="pair")
+    finally:
+        ops.set_gemm_pair_persistent(True)
+    assert torch.equal(y, y0)          # same tiles, same K order: bit-identical to one launch per tile
+    ops.check_device_error()
+
+
 @pytest.mark.parametrize("bn,stages,splits", [(16, 2, 1), (32, 4, 1), (64, 8, 1), (128, 4, 2), (256, 3, 4), (160, 4, 1)])
 def test_gemm_tile_configs(bn, stages, splits):
     torch.manual_seed(1)
