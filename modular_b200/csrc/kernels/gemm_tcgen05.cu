@@ -65,6 +65,21 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, uint8_t* stage
     __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(stage_buf + quad * kStageWarpBytes);
     const int n_row = n0 + quad * 32 + lane;  // weight row (= output column) of this thread
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    // Residual rows are fetched one 16-token chunk ahead: a load issued only after the transpose would put a
+    // global round trip (two per chunk) on the epilogue's critical path, which is longer than the TMEM read,
+    // the transpose and the stores together.
+    uint4 rv[2];
+    auto fetch_residual = [&](int c0) {
+#pragma unroll
+      for (int pass = 0; pass < 2; ++pass) {
+        const int t = t0 + c0 + pass * 8 + (lane >> 2);
+        const int n = n0 + quad * 32 + (lane & 3) * 8;
+        rv[pass] = make_uint4(0u, 0u, 0u, 0u);
+        if (c0 < BN && t < Mlim && n < N)
+          rv[pass] = *reinterpret_cast<const uint4*>(R + static_cast<size_t>(t) * ldr + n);
+      }
+    };
+    if (EPI == EPI_BF16_RESIDUAL) fetch_residual(0);
     for (int c0 = 0; c0 < BN; c0 += 16) {
       if (t0 + c0 >= Mlim) break;  // warp-uniform
       uint32_t g[16];
@@ -96,6 +111,12 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, uint8_t* stage
 #pragma unroll
         for (int j = 0; j < 16; ++j) stg[j * 32 + lane] = __float2bfloat16(v[j]);
         __syncwarp();
+        uint4 cur[2];
+        if (EPI == EPI_BF16_RESIDUAL) {
+          cur[0] = rv[0];
+          cur[1] = rv[1];
+          fetch_residual(c0 + 16);   // in flight while this chunk is added up and stored
+        }
         // 16 tokens x 64 bytes: 4 lanes cover one token row, 8 tokens per pass
 #pragma unroll
         for (int pass = 0; pass < 2; ++pass) {
@@ -106,10 +127,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_base, uint8_t* stage
           if (t < Mlim && n < N) {
             uint4 val = *reinterpret_cast<const uint4*>(stg + j * 32 + seg * 8);
             if (EPI == EPI_BF16_RESIDUAL) {
-              const uint4 rv =
-                  *reinterpret_cast<const uint4*>(R + static_cast<size_t>(t) * ldr + n);
               __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&val);
-              const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&rv);
+              const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&cur[pass]);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 const float2 fa = __bfloat1622float2(a[q]);
@@ -491,17 +510,17 @@ struct PairPersistTail {
 };
 constexpr int kAccStageCols = 256;
 
-template <int EPI>
+template <bool DUAL, int EPI>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                             void* __restrict__ Yv, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
-                            int ldy, int ldr, int BN, int stages, int m_tiles, int total_tiles, int* err,
-                            int packed_kb) {
+                            int ldy, int ldr, int dual_rows, int BN, int stages, int m_tiles, int total_tiles,
+                            int* err, int packed_kb) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const int half = BN >> 1;
-  const int a_bytes = kATileBytes;
+  const int a_bytes = kATileBytes * (DUAL ? 2 : 1);
   const int b_bytes = half * kBK * 2;
   const int stage_bytes = a_bytes + b_bytes;
   uint8_t* stage_buf = smem + stages * stage_bytes;
@@ -558,10 +577,15 @@ gemm_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __gri
           const uint32_t full_leader = mapa_shared(&tail->full[s], 0);
           const int kc = it * kBK;
           if (++s == stages) { s = 0; ph ^= 1; }
-          if (packed_kb > 0)
+          if (packed_kb > 0) {
             tma_load_2d_pair(sa, &tmW, full_leader, 0, ((n0 >> 7) * packed_kb + (kc / kBK)) << 7);
-          else
+            if (DUAL)
+              tma_load_2d_pair(sa + kATileBytes, &tmW, full_leader, 0,
+                               (((dual_rows + n0) >> 7) * packed_kb + (kc / kBK)) << 7);
+          } else {
             tma_load_2d_pair(sa, &tmW, full_leader, kc, n0);
+            if (DUAL) tma_load_2d_pair(sa + kATileBytes, &tmW, full_leader, kc, dual_rows + n0);
+          }
           tma_load_2d_pair(sa + a_bytes, &tmX, full_leader, kc, tb0);
         }
       }
@@ -571,7 +595,7 @@ gemm_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __gri
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc(2 * kBM, BN, 1, 1);
       const uint64_t da0_first = umma_desc_sw128(smem);
-      const uint64_t d_b = static_cast<uint64_t>(a_bytes >> 4);
+      const uint64_t d_a1 = static_cast<uint64_t>(kATileBytes >> 4), d_b = static_cast<uint64_t>(a_bytes >> 4);
       const uint64_t d_stage = static_cast<uint64_t>(stage_bytes >> 4);
       const uint32_t empty0 = mapa_shared(&tail->empty[0], 0), empty1 = mapa_shared(&tail->empty[0], 1);
       const uint32_t tfull0 = mapa_shared(&tail->tmem_full[0], 0), tfull1 = mapa_shared(&tail->tmem_full[0], 1);
@@ -596,6 +620,7 @@ gemm_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __gri
             const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
             const uint64_t koff = static_cast<uint64_t>(k * kUmmaK * 2 >> 4);
             umma_bf16_pair(d_tmem, da0 + koff, da0 + d_b + koff, idesc, acc);
+            if (DUAL) umma_bf16_pair(d_tmem + BN, da0 + d_a1 + koff, da0 + d_b + koff, idesc, acc);
           }
           tc_commit_pair(empty0 + 8u * s);   // mbarriers are 8 bytes apart, at the same offset in both CTAs
           tc_commit_pair(empty1 + 8u * s);
@@ -618,7 +643,7 @@ gemm_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __gri
       const int n0 = (t / m_tiles) * (2 * kBM) + static_cast<int>(rank) * kBM;
       const int t0 = (t % m_tiles) * BN;
       if (k_iters > 0)
-        epilogue_tile<false, EPI>(tmem_base + static_cast<uint32_t>(a * kAccStageCols), stage_buf, quad, lane, Yv, R,
+        epilogue_tile<DUAL, EPI>(tmem_base + static_cast<uint32_t>(a * kAccStageCols), stage_buf, quad, lane, Yv, R,
                                   M, N, ldy, ldr, BN, n0, t0, M, 0);
       tc_fence_before();
       __syncwarp();
@@ -846,14 +871,14 @@ static int launch_pair_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* Y
   return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
-template <int EPI>
+template <bool DUAL, int EPI>
 static int launch_pair_persistent(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, const void* R, int M, int N,
-                                  int K, int ldy, int ldr, int BN, int stages, int num_sms, int* err,
+                                  int K, int ldy, int ldr, int dual_rows, int BN, int stages, int num_sms, int* err,
                                   cudaStream_t stream, int packed_kb) {
-  const int stage_bytes = kATileBytes + (BN / 2) * kBK * 2;
+  const int stage_bytes = kATileBytes * (DUAL ? 2 : 1) + (BN / 2) * kBK * 2;
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * kStageWarpBytes +
                       sizeof(PairPersistTail) + 1024;
-  auto kern = gemm_pair_persistent_kernel<EPI>;
+  auto kern = gemm_pair_persistent_kernel<DUAL, EPI>;
   static PerDeviceOnce configured;
   if (configured.needed()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
@@ -881,7 +906,7 @@ static int launch_pair_persistent(const CUtensorMap& tw, const CUtensorMap& tx, 
   }
   cfg.attrs = attr;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, Y, static_cast<const __nv_bfloat16*>(R), M, N, K, ldy,
-                                           ldr, BN, stages, m_tiles, total, err, packed_kb);
+                                           ldr, dual_rows, BN, stages, m_tiles, total, err, packed_kb);
   return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
@@ -1089,6 +1114,13 @@ extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const vo
     return MB_ERR_ALIGN;
   if (dual && f32) return MB_ERR_SHAPE;
   if (num_sms <= 0) num_sms = 148;
+  if (dual && bn <= 0 && g_pair_persistent && gate_flags == nullptr) {
+    // fused SwiGLU with many tiles: the persistent form needs gate and up side by side in one 256-column
+    // accumulator stage, i.e. token tiles of at most 128
+    const int mt = (M + 127) / 128;
+    const int b = ((M + mt - 1) / mt + 31) / 32 * 32;
+    if (((M + b - 1) / b) * ((N + 2 * kBM - 1) / (2 * kBM)) > num_sms / 2) bn = b;
+  }
   {
     int pbn, psp;
     mb_gemm_bf16_pair_plan(M, N, K, (dual || f32) ? 1 : 0, num_sms, &pbn, &psp);
@@ -1126,6 +1158,10 @@ extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const vo
         static_cast<__nv_bfloat16*>(Y), M, N, splits, ldy, ldr);
     return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
   }
+  const bool many_tiles = ((M + bn - 1) / bn) * ((N + 2 * kBM - 1) / (2 * kBM)) > num_sms / 2;
+  if (dual && g_pair_persistent && gate_flags == nullptr && many_tiles && bn <= 128)
+    return launch_pair_persistent<true, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, N, bn, stages, num_sms, err,
+                                                  stream, packed_kb);
   if (dual)
     return launch_pair_cfg<true, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, N, K, 1, bn, stages, err, stream,
                                            gate_flags, gate_rpr, gate_world, packed_kb);
@@ -1133,14 +1169,12 @@ extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const vo
     return launch_pair_cfg<false, EPI_F32>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, K, 1, bn, stages, err, stream,
                                            gate_flags, gate_rpr, gate_world, packed_kb);
   // more tiles than pairs of SMs: persistent pairs with two accumulator stages (epilogue under the next tile)
-  if (g_pair_persistent && gate_flags == nullptr &&
-      ((M + bn - 1) / bn) * ((N + 2 * kBM - 1) / (2 * kBM)) > num_sms / 2) {
-    const int ps = stages;
+  if (g_pair_persistent && gate_flags == nullptr && many_tiles) {
     if (resid)
-      return launch_pair_persistent<EPI_BF16_RESIDUAL>(tw, tx, Y, R, M, N, K, ldy, ldr, bn, ps, num_sms, err, stream,
-                                                       packed_kb);
-    return launch_pair_persistent<EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, bn, ps, num_sms, err, stream,
-                                            packed_kb);
+      return launch_pair_persistent<false, EPI_BF16_RESIDUAL>(tw, tx, Y, R, M, N, K, ldy, ldr, 0, bn, stages, num_sms,
+                                                              err, stream, packed_kb);
+    return launch_pair_persistent<false, EPI_BF16>(tw, tx, Y, nullptr, M, N, K, ldy, 0, 0, bn, stages, num_sms, err,
+                                                   stream, packed_kb);
   }
   if (resid)
     return launch_pair_cfg<false, EPI_BF16_RESIDUAL>(tw, tx, Y, R, M, N, K, ldy, ldr, 0, K, 1, bn, stages, err,

@@ -61,6 +61,22 @@ def test_gemm_pair_persistent(M, N, K):
     ops.check_device_error()
 
 
+def test_gemm_pair_persistent_swiglu():
+    torch.manual_seed(6)
+    M, K, I = 2176, 1024, 1536                    # 17 token tiles x 6 row pairs: more tiles than pairs of SMs
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(2 * I, K, device=DEV) * 0.05).to(torch.bfloat16)
+    y = ops.linear_swiglu(x, w, impl="pair")
+    assert _rel_err(y, ref.linear_swiglu(x, w)) < 1.5e-2
+    ops.set_gemm_pair_persistent(False)
+    try:
+        y0 = ops.linear_swiglu(x, w, impl="pair", bn=128)
+    finally:
+        ops.set_gemm_pair_persistent(True)
+    assert torch.equal(y, y0)
+    ops.check_device_error()
+
+
 @pytest.mark.parametrize("bn,stages,splits", [(16, 2, 1), (32, 4, 1), (64, 8, 1), (128, 4, 2), (256, 3, 4), (160, 4, 1)])
 def test_gemm_tile_configs(bn, stages, splits):
     torch.manual_seed(1)
