@@ -50,6 +50,10 @@ def _load():
                 plain, _, dual = os.environ.get("MB200_GEMM_PAIR", "512,0").partition(",")
                 mod.set_gemm_pair(int(plain or 0), int(dual or 0))
             # MB200_GEMM_PAIR_PERSIST=0: one launch-time pair per tile even when there are more tiles than SM pairs
+            # MB200_GEMM_PAIR_TM: which pair GEMMs with many tiles run with the tokens on the MMA's M side (bit 0 fused
+            # SwiGLU: gate and up rows in one 256-wide MMA, 1.15-1.35x the one-CTA persistent kernel; bit 1 plain)
+            if hasattr(mod, "set_gemm_pair_token_major"):
+                mod.set_gemm_pair_token_major(int(os.environ.get("MB200_GEMM_PAIR_TM", "3") or 0))
             if hasattr(mod, "set_gemm_pair_persistent"):
                 mod.set_gemm_pair_persistent(os.environ.get("MB200_GEMM_PAIR_PERSIST", "1") not in ("", "0"))
             if hasattr(mod, "set_attn_decode_dense"):

@@ -832,6 +832,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_attn_split", [](int mode) { mb_set_attn_split(mode); });
   m.def("set_attn_tc", [](int min_tiles) { mb_set_attn_tc(min_tiles); });
   m.def("get_attn_tc", []() { return mb_get_attn_tc(); });
+  m.def("set_gemm_pair_token_major", [](int mask) { mb_set_gemm_pair_token_major(mask); }, py::arg("mask"));
   m.def("set_gemm_pair_persistent", [](bool on) { mb_set_gemm_pair_persistent(on ? 1 : 0); }, py::arg("on"));
   m.def("set_gemm_pair", [](int min_m_plain, int min_m_dual) { mb_set_gemm_pair(min_m_plain, min_m_dual); },
         py::arg("min_m_plain"), py::arg("min_m_dual"));

@@ -45,7 +45,10 @@ int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const void* R, int 
 void mb_gemm_bf16_pair_plan(int M, int N, int K, int no_split, int num_sms, int* bn_out, int* splits_out);
 void mb_set_gemm_pair(int min_m_plain, int min_m_dual);
 // 0: never the persistent form of the CTA-pair GEMM (default 1: used when there are more tiles than SM pairs)
+int mb_gemm_pair_choice(int M, int N, int dual, int num_sms);
 void mb_set_gemm_pair_persistent(int on);
+// bit 0: fused SwiGLU, bit 1: plain GEMMs on the token-major persistent pair kernel (tokens on the MMA's M side)
+void mb_set_gemm_pair_token_major(int mask);
 int mb_gemm_pair_wanted(int M, int dual);
 int mb_gemm_bf16_persistent_gated(const void* X, const void* W, void* Y, const void* R, int M, int N, int K,
                                   int ldx, int ldw, int ldy, int ldr, int flags, int bn, int stages,

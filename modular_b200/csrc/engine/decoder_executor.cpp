@@ -206,7 +206,7 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
       persistent = (flags & 1) || tiles >= 4 * c.num_sms;
       mode = -1;   // the kernel picks whole tiles or whole tiles + a stream-K remainder
     }
-    if (mb_gemm_pair_wanted(M, flags & 1)) {
+    if (mb_gemm_pair_choice(M, N, flags & 1, c.num_sms)) {
       int pbn, psp;
       mb_gemm_bf16_pair_plan(M, N, K, (flags & 5) ? 1 : 0, c.num_sms, &pbn, &psp);
       if (static_cast<size_t>(psp) * M * N * sizeof(float) > buf.workspace_bytes) psp = 1;

@@ -662,6 +662,229 @@ gemm_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __gri
   }
 }
 
+// ------------------------------------------------------------------ persistent CTA pairs, tokens on the MMA's M side
+// Same schedule as gemm_pair_persistent_kernel with the operand roles swapped: the pair's A operand is 256 token
+// rows (128 per CTA) and its B operand 256 weight rows, half of them loaded by each CTA. For the fused SwiGLU
+// GEMM the leader loads 128 gate rows and the peer the matching 128 up rows, so ONE 256 x 256 x 16 MMA produces
+// gate (accumulator columns 0..127) and up (128..255) of 128 features for 256 tokens: per CTA and K block
+// that is 32 KB of operands for the FLOPs the weight-major form spends 40-48 KB (and two N = 128 MMAs, which
+// are bound by their shared-memory reads) on, and the accumulator still fits a 256-column stage, so the epilogue
+// runs under the next tile. TMEM lanes are token rows here: a thread owns one output row and stores 32-byte
+// runs of it, no transpose. Plain GEMMs: the peer loads weight rows n0 + 128.., 256 features per tile.
+template <bool DUAL, int EPI>
+__device__ __forceinline__ void epilogue_rows(uint32_t tmem_acc, int quad, int lane, __nv_bfloat16* __restrict__ Y,
+                                              const __nv_bfloat16* __restrict__ R, int M, int N, int ldy, int ldr,
+                                              int token, int n0) {
+  const uint32_t lane_addr = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16);
+  constexpr int kCols = DUAL ? 128 : 256;
+  const bool row_ok = token < M;
+  // The residual is fetched one 128-byte line (64 features) ahead. The output is usually written in place over
+  // the residual, and a load that follows a store of the same thread to the same line waits for that store to
+  // be acknowledged: with a look-ahead of one 16-feature chunk every chunk paid two round trips to L2 (139
+  // against 61 us for a 2112 x 4096 x 4096 GEMM); a whole line ahead, loads and stores in flight never share one.
+  uint4 nxt[8];
+  auto fetch_line = [&](int l0) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      nxt[q] = make_uint4(0u, 0u, 0u, 0u);
+      if (row_ok && l0 < kCols && n0 + l0 + 8 * q + 8 <= N)
+        nxt[q] = __ldcg(reinterpret_cast<const uint4*>(R + static_cast<size_t>(token) * ldr + n0 + l0 + 8 * q));
+    }
+  };
+  if (EPI == EPI_BF16_RESIDUAL) fetch_line(0);
+  for (int l0 = 0; l0 < kCols; l0 += 64) {
+    if (n0 + l0 >= N) break;   // warp-uniform
+    uint4 cur[8];
+    if (EPI == EPI_BF16_RESIDUAL) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) cur[q] = nxt[q];
+      fetch_line(l0 + 64);
+    }
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int c0 = l0 + cc * 16;
+      if (n0 + c0 >= N) break;   // warp-uniform
+      uint32_t g[16];
+      tmem_ld_32x16(lane_addr + c0, g);
+      float v[16];
+      if (DUAL) {
+        uint32_t u[16];
+        tmem_ld_32x16(lane_addr + 128 + c0, u);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+      } else {
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(g[j]);
+      }
+      uint4 o[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&o[h]);
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&cur[2 * cc + h]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float x0 = v[h * 8 + 2 * q], x1 = v[h * 8 + 2 * q + 1];
+          if (EPI == EPI_BF16_RESIDUAL) {
+            const float2 fb = __bfloat1622float2(b[q]);
+            // the weight-major kernels round the product to bf16 before the residual is added
+            x0 = __bfloat162float(__float2bfloat16(x0)) + fb.x;
+            x1 = __bfloat162float(__float2bfloat16(x1)) + fb.y;
+          }
+          a[q] = __floats2bfloat162_rn(x0, x1);
+        }
+      }
+      if (row_ok) {
+        __nv_bfloat16* y = Y + static_cast<size_t>(token) * ldy + n0 + c0;
+        if (n0 + c0 + 8 <= N) *reinterpret_cast<uint4*>(y) = o[0];
+        if (n0 + c0 + 16 <= N) *reinterpret_cast<uint4*>(y + 8) = o[1];
+      }
+    }
+  }
+}
+
+template <bool DUAL, int EPI>
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_pair_xw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                    __nv_bfloat16* __restrict__ Y, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
+                    int ldy, int ldr, int dual_rows, int stages, int m_tiles, int total_tiles, int* err,
+                    int packed_kb) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  constexpr int kStage = 2 * kATileBytes;           // 128 token rows + 128 weight rows of one 64-wide K block
+  constexpr int kTileN = DUAL ? kBM : 2 * kBM;      // output features per tile
+  PairPersistTail* tail = reinterpret_cast<PairPersistTail*>(smem + stages * kStage);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  const int cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+  const int k_iters = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tail->tmem_full[a], 1);
+      mbar_init(&tail->tmem_empty[a], 8);
+    }
+    tail->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tail->tmem_base, 2 * kAccStageCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t tmem_base = tail->tmem_base;
+  volatile int* abort_word = &tail->abort_word;
+  pdl_wait();
+  pdl_trigger();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = cluster; t < total_tiles && ok; t += clusters) {
+        const int n0 = (t / m_tiles) * kTileN;
+        const int w0 = DUAL ? (rank == 0 ? n0 : dual_rows + n0) : n0 + static_cast<int>(rank) * kBM;   // my weight rows
+        const int tk0 = (t % m_tiles) * (2 * kBM) + static_cast<int>(rank) * kBM;                     // my token rows
+        for (int it = 0; it < k_iters; ++it) {
+          if (!mbar_wait(&tail->empty[s], ph ^ 1, abort_word, err, 120)) { ok = false; break; }
+          uint8_t* sa = smem + s * kStage;
+          if (rank == 0) mbar_arrive_expect_tx(&tail->full[s], 2 * kStage);
+          const uint32_t full_leader = mapa_shared(&tail->full[s], 0);
+          const int kc = it * kBK;
+          if (++s == stages) { s = 0; ph ^= 1; }
+          tma_load_2d_pair(sa, &tmX, full_leader, kc, tk0);
+          if (packed_kb > 0)
+            tma_load_2d_pair(sa + kATileBytes, &tmW, full_leader, 0, ((w0 >> 7) * packed_kb + it) << 7);
+          else
+            tma_load_2d_pair(sa + kATileBytes, &tmW, full_leader, kc, w0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc(2 * kBM, 2 * kBM, 1, 1);
+      const uint64_t da0_first = umma_desc_sw128(smem);
+      const uint64_t d_b = static_cast<uint64_t>(kATileBytes >> 4);
+      const uint64_t d_stage = static_cast<uint64_t>(kStage >> 4);
+      const uint32_t empty0 = mapa_shared(&tail->empty[0], 0), empty1 = mapa_shared(&tail->empty[0], 1);
+      const uint32_t tfull0 = mapa_shared(&tail->tmem_full[0], 0), tfull1 = mapa_shared(&tail->tmem_full[0], 1);
+      uint64_t da0 = da0_first;
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int i = 0;
+      for (int t = cluster; t < total_tiles && ok; t += clusters, ++i) {
+        const int a = i & 1;
+        ok = mbar_wait(&tail->tmem_empty[a], ((i >> 1) & 1) ^ 1, abort_word, err, 121);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(a * kAccStageCols);
+        for (int it = 0; it < k_iters; ++it) {
+          ok = mbar_wait(&tail->full[s], ph, abort_word, err, 122);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+            const uint64_t koff = static_cast<uint64_t>(k * kUmmaK * 2 >> 4);
+            umma_bf16_pair(d_tmem, da0 + koff, da0 + d_b + koff, idesc, acc);
+          }
+          tc_commit_pair(empty0 + 8u * s);
+          tc_commit_pair(empty1 + 8u * s);
+          if (++s == stages) { s = 0; ph ^= 1; da0 = da0_first; } else { da0 += d_stage; }
+        }
+        if (!ok) break;
+        tc_commit_pair(tfull0 + 8u * a);
+        tc_commit_pair(tfull1 + 8u * a);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    const uint32_t tempty_leader = mapa_shared(&tail->tmem_empty[0], 0);
+    int i = 0;
+    for (int t = cluster; t < total_tiles; t += clusters, ++i) {
+      const int a = i & 1;
+      if (!mbar_wait(&tail->tmem_full[a], (i >> 1) & 1, abort_word, err, 123)) break;
+      tc_fence_after();
+      const int n0 = (t / m_tiles) * kTileN;
+      const int token = (t % m_tiles) * (2 * kBM) + static_cast<int>(rank) * kBM + quad * 32 + lane;
+      if (k_iters > 0)
+        epilogue_rows<DUAL, EPI>(tmem_base + static_cast<uint32_t>(a * kAccStageCols), quad, lane, Y, R, M, N, ldy,
+                                 ldr, token, n0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader + 8u * a);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 2 * kAccStageCols);
+  }
+}
+
 // Sum split-K fp32 partials [splits, M, N] -> bf16 Y (+ optional residual).
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, const __nv_bfloat16* __restrict__ R,
                                      __nv_bfloat16* __restrict__ Y, int M, int N, int splits,
@@ -910,6 +1133,47 @@ static int launch_pair_persistent(const CUtensorMap& tw, const CUtensorMap& tx, 
   return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }
 
+template <bool DUAL, int EPI>
+static int launch_pair_xw(const CUtensorMap& tw, const CUtensorMap& tx, void* Y, const void* R, int M, int N, int K,
+                          int ldy, int ldr, int dual_rows, int num_sms, int* err, cudaStream_t stream,
+                          int packed_kb) {
+  constexpr int kStage = 2 * kATileBytes;
+  const int stages = 6;
+  const size_t smem = static_cast<size_t>(stages) * kStage + sizeof(PairPersistTail) + 1024;
+  auto kern = gemm_pair_xw_kernel<DUAL, EPI>;
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+      return MB_ERR_LAUNCH;
+    configured.done();
+  }
+  const int tile_n = DUAL ? kBM : 2 * kBM;
+  const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
+  const int total = m_tiles * ((N + tile_n - 1) / tile_n);
+  const int clusters = total < num_sms / 2 ? total : num_sms / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.numAttrs = 1;
+  if (pdl_enabled()) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  cfg.attrs = attr;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, static_cast<__nv_bfloat16*>(Y),
+                                           static_cast<const __nv_bfloat16*>(R), M, N, K, ldy, ldr, dual_rows, stages,
+                                           m_tiles, total, err, packed_kb);
+  return e == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -1054,6 +1318,19 @@ extern "C" int mb_gemm_bf16_gated(const void* X, const void* W, void* Y, const v
 // M >= min_m_plain and fused SwiGLU GEMMs with M >= min_m_dual use it; 0 = never.
 static int g_pair_min_m[2] = {0, 0};
 static bool g_pair_persistent = true;
+static int g_pair_token_major = 3;
+// More tiles than pairs of SMs, and for plain GEMMs a last round that is not mostly idle (the weight-major
+// kernel picks its token-tile width by rounds x tile cost; this one has fixed 256 x 256 tiles).
+static bool pair_token_major_fits(int M, int N, bool dual, int num_sms) {
+  const int tile_n = dual ? kBM : 2 * kBM;
+  const int total = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + tile_n - 1) / tile_n);
+  const int clusters = num_sms / 2;
+  if (total <= clusters) return false;
+  const int rounds = (total + clusters - 1) / clusters;
+  return dual || 5 * total >= 4 * rounds * clusters;
+}
+// bit 0: fused SwiGLU GEMMs with more tiles than SM pairs run the token-major persistent pair kernel, bit 1: plain ones
+extern "C" void mb_set_gemm_pair_token_major(int mask) { g_pair_token_major = mask; }
 // 0: the CTA-pair GEMM launches one pair per tile even when there are more tiles than pairs of SMs
 extern "C" void mb_set_gemm_pair_persistent(int on) { g_pair_persistent = on != 0; }
 extern "C" void mb_set_gemm_pair(int min_m_plain, int min_m_dual) {
@@ -1063,6 +1340,14 @@ extern "C" void mb_set_gemm_pair(int min_m_plain, int min_m_dual) {
 extern "C" int mb_gemm_pair_wanted(int M, int dual) {
   const int m = g_pair_min_m[dual ? 1 : 0];
   return m > 0 && M >= m;
+}
+// The same question with the problem's width known: fused SwiGLU GEMMs also take the pair path from the plain
+// threshold up when the token-major persistent kernel would run them.
+extern "C" int mb_gemm_pair_choice(int M, int N, int dual, int num_sms) {
+  if (mb_gemm_pair_wanted(M, dual)) return 1;
+  if (num_sms <= 0) num_sms = 148;
+  return dual && g_pair_min_m[0] > 0 && M >= g_pair_min_m[0] && g_pair_persistent && (g_pair_token_major & 1) &&
+         pair_token_major_fits(M, N, true, num_sms);
 }
 
 // Token-tile width and K splits the pair kernel picks by itself (no_split: fused SwiGLU or fp32 output).
@@ -1114,6 +1399,25 @@ extern "C" int mb_gemm_bf16_pair(const void* X, const void* W, void* Y, const vo
     return MB_ERR_ALIGN;
   if (dual && f32) return MB_ERR_SHAPE;
   if (num_sms <= 0) num_sms = 148;
+  // token-major persistent pairs: bit 0 of the switch = fused SwiGLU GEMMs, bit 1 = plain ones
+  if (g_pair_persistent && gate_flags == nullptr && !f32 && splits <= 1 &&
+      (g_pair_token_major & (dual ? 1 : 2)) != 0) {
+    if (pair_token_major_fits(M, N, dual, num_sms)) {
+      const int w_rows_x = dual ? 2 * N : N;
+      CUtensorMap twx, txx;
+      int rcx = packed ? cached_tmap(&twx, W, static_cast<uint64_t>(w_rows_x) * packed_kb, kBK, kBK, kBM, 2)
+                       : cached_tmap(&twx, W, w_rows_x, K, ldw, kBM, 2);
+      if (rcx != MB_OK) return rcx;
+      rcx = cached_tmap(&txx, X, M, K, ldx, kBM, 2);
+      if (rcx != MB_OK) return rcx;
+      if (dual)
+        return launch_pair_xw<true, EPI_BF16>(twx, txx, Y, nullptr, M, N, K, ldy, 0, N, num_sms, err, stream, packed_kb);
+      if (resid)
+        return launch_pair_xw<false, EPI_BF16_RESIDUAL>(twx, txx, Y, R, M, N, K, ldy, ldr, 0, num_sms, err, stream,
+                                                        packed_kb);
+      return launch_pair_xw<false, EPI_BF16>(twx, txx, Y, nullptr, M, N, K, ldy, 0, 0, num_sms, err, stream, packed_kb);
+    }
+  }
   if (dual && bn <= 0 && g_pair_persistent && gate_flags == nullptr) {
     // fused SwiGLU with many tiles: the persistent form needs gate and up side by side in one 256-column
     // accumulator stage, i.e. token tiles of at most 128

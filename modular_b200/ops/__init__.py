@@ -343,6 +343,12 @@ def set_gemm_pair_persistent(on: bool) -> None:
     _lib().set_gemm_pair_persistent(bool(on))
 
 
+def set_gemm_pair_token_major(mask: int) -> None:
+    """Which CTA-pair GEMMs with more tiles than SM pairs run the token-major persistent kernel (tokens on the MMA's
+    M side, gate and up rows of a fused SwiGLU GEMM in one 256-wide MMA): bit 0 fused SwiGLU, bit 1 plain."""
+    _lib().set_gemm_pair_token_major(int(mask))
+
+
 def set_sample_cluster(on: bool) -> None:
     """Whether rows with a top-k / top-p / min-p filter are first sampled by the kernel that spreads a row
     over a cluster of eight CTAs (default on); off leaves every row to the one-CTA-per-row kernel."""

@@ -47,17 +47,49 @@ def test_gemm_pair_persistent(M, N, K):
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
     r = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
-    for _ in range(2):
-        y = ops.linear(x, w, impl="pair")
-        yr = ops.linear(x, w, residual=r, impl="pair")
-    assert _rel_err(y, ref.linear(x, w)) < 1e-2
-    assert _rel_err(yr, ref.linear(x, w, r)) < 1e-2
-    ops.set_gemm_pair_persistent(False)
+    ops.set_gemm_pair_token_major(0)               # the weight-major kernels are the ones under test here
     try:
+        for _ in range(2):
+            y = ops.linear(x, w, impl="pair")
+            yr = ops.linear(x, w, residual=r, impl="pair")
+        ops.set_gemm_pair_persistent(False)
         y0 = ops.linear(x, w, impl="pair")
     finally:
         ops.set_gemm_pair_persistent(True)
+        ops.set_gemm_pair_token_major(3)
+    assert _rel_err(y, ref.linear(x, w)) < 1e-2
+    assert _rel_err(yr, ref.linear(x, w, r)) < 1e-2
     assert torch.equal(y, y0)          # same tiles, same K order: bit-identical to one launch per tile
+    ops.check_device_error()
+
+
+@pytest.mark.parametrize("M,N,K", [(2176, 6144, 1024), (1000, 5000, 520), (4100, 4096, 256), (700, 28672, 128)])
+def test_gemm_pair_token_major(M, N, K):
+    # tokens on the MMA's M side: plain, residual (also in place) and fused SwiGLU, against fp32 references
+    torch.manual_seed(7)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    r = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.set_gemm_pair_token_major(3)
+    try:
+        for _ in range(2):
+            y = ops.linear(x, w, impl="pair")
+            yr = ops.linear(x, w, residual=r, impl="pair")
+        h = r.clone()
+        ops.linear(x, w, residual=h, out=h, impl="pair")
+        ys = ops.linear_swiglu(x, w[: N // 256 * 256], impl="pair")
+    finally:
+        ops.set_gemm_pair_token_major(0)
+    try:
+        y_wm = ops.linear(x, w, impl="pair")           # weight-major kernels: same K order, same rounding
+    finally:
+        ops.set_gemm_pair_token_major(3)
+    assert torch.equal(y, y_wm)
+    assert _rel_err(y, ref.linear(x, w)) < 1e-2
+    assert (y.float() - ref.linear(x, w).float()).abs().max() <= 0.02 * ref.linear(x, w).float().abs().max() + 1e-2
+    assert _rel_err(yr, ref.linear(x, w, r)) < 1e-2
+    assert torch.equal(h, yr)
+    assert _rel_err(ys, ref.linear_swiglu(x, w[: N // 256 * 256])) < 1.5e-2
     ops.check_device_error()
 
 
@@ -66,13 +98,15 @@ def test_gemm_pair_persistent_swiglu():
     M, K, I = 2176, 1024, 1536                    # 17 token tiles x 6 row pairs: more tiles than pairs of SMs
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     w = (torch.randn(2 * I, K, device=DEV) * 0.05).to(torch.bfloat16)
-    y = ops.linear_swiglu(x, w, impl="pair")
-    assert _rel_err(y, ref.linear_swiglu(x, w)) < 1.5e-2
-    ops.set_gemm_pair_persistent(False)
+    ops.set_gemm_pair_token_major(0)
     try:
+        y = ops.linear_swiglu(x, w, impl="pair")
+        ops.set_gemm_pair_persistent(False)
         y0 = ops.linear_swiglu(x, w, impl="pair", bn=128)
     finally:
         ops.set_gemm_pair_persistent(True)
+        ops.set_gemm_pair_token_major(3)
+    assert _rel_err(y, ref.linear_swiglu(x, w)) < 1.5e-2
     assert torch.equal(y, y0)
     ops.check_device_error()
 
