@@ -51,6 +51,7 @@ _PERSISTENT_WS: dict[int, tuple] = {}
 # "tiled": one CTA per output tile with optional split-K through a workspace;
 # "pair": the tiled kernel on clusters of two CTAs (cta_group::2 MMAs, 256 weight rows per pair).
 GEMM_IMPL = os.environ.get("MB200_GEMM", "auto")
+PAIR_MIN_TOKENS = 512   # "auto": plain and fused SwiGLU GEMMs of at least this many rows run on CTA pairs
 
 
 def persistent_gemm_workspace(device):
@@ -166,10 +167,13 @@ def linear(x, w, residual=None, out=None, out_dtype=None, bn=0, splits=0, stages
         return y
     if out is None:
         out = torch.empty(x.shape[0], w.shape[0], dtype=out_dtype or x.dtype, device=x.device)
-    if (impl or GEMM_IMPL) == "persistent":
+    sel = impl or GEMM_IMPL
+    if sel == "auto" and x.shape[0] >= PAIR_MIN_TOKENS and out.dtype == torch.bfloat16 and bn == 0 and splits == 0:
+        sel = "pair"        # same choice as the step executor: CTA pairs from 512 tokens up
+    if sel == "persistent":
         ws, counters = persistent_gemm_workspace(x.device)
         _lib().gemm_bf16_persistent(x, w, out, residual, False, ws, counters, bn, stages, mode, pdl)
-    elif (impl or GEMM_IMPL) == "pair":
+    elif sel == "pair":
         _lib().gemm_bf16(x, w, out, residual, False, gemm_workspace(x.device), bn, splits, stages, False, True)
     else:
         _lib().gemm_bf16(x, w, out, residual, False, gemm_workspace(x.device), bn, splits, stages)
@@ -187,6 +191,8 @@ def linear_swiglu(x, w_gate_up, out=None, bn=0, stages=0, impl=None, mode=-1, pd
     if out is None:
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
     sel = impl or GEMM_IMPL
+    if sel == "auto" and x.shape[0] >= PAIR_MIN_TOKENS and bn == 0 and w_gate_up.shape[0] >= 2 * 128 * 40:
+        sel = "pair"        # token-major persistent pairs once there are more tiles than pairs of SMs
     if sel == "pair":
         _lib().gemm_bf16(x, w_gate_up, out, None, True, None, bn, 1, stages, False, True)
     elif sel in ("persistent", "auto"):
