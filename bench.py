@@ -91,7 +91,7 @@ def _server_arm(args, world: int, model_name: str) -> dict:
     proc = subprocess.Popen(cmd, cwd=REPO, env=env, stdout=log, stderr=subprocess.STDOUT)
     base = f"http://127.0.0.1:{port}"
     try:
-        deadline = time.time() + 900
+        deadline = time.time() + 420
         while True:
             if proc.poll() is not None:
                 return {"unavailable": f"server exited with code {proc.returncode} before it was ready: {log_tail()}"}
@@ -102,13 +102,18 @@ def _server_arm(args, world: int, model_name: str) -> dict:
             except Exception:  # noqa: BLE001
                 pass
             if time.time() > deadline:
-                return {"unavailable": "server was not ready within 15 minutes"}
+                return {"unavailable": "server was not ready within 7 minutes"}
             time.sleep(1.0)
         conc = args.concurrency
-        run = lambda n, seed: asyncio.run(run_benchmark(base, model_name, n, conc, args.input_len, args.output_len,
-                                                        vocab_size=128256, seed=seed))
-        run(args.warmup * conc, 1)
-        res = run(args.steps * conc, 2)
+        # every client run has a time limit: a stalled endpoint must not take the in-process numbers with it
+        run = lambda n, seed: asyncio.run(asyncio.wait_for(
+            run_benchmark(base, model_name, n, conc, args.input_len, args.output_len, vocab_size=128256, seed=seed),
+            timeout=600))
+        try:
+            run(args.warmup * conc, 1)
+            res = run(args.steps * conc, 2)
+        except asyncio.TimeoutError:
+            return {"unavailable": f"the endpoint did not finish a client run within 10 minutes: {log_tail()}"}
         if res["failed"]:
             return {"unavailable": f"{res['failed']} requests failed: {res['errors']}"}
         return {"value": res["output_token_throughput"], "unit": "tok/s", "p50_ttft_ms": res["p50_ttft_ms"],
@@ -313,6 +318,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
     ap.add_argument("--no-server", action="store_true",
                     help="skip the second measurement through the HTTP serving endpoint")
+    ap.add_argument("--server", action="store_true",
+                    help="measure through the HTTP serving endpoint on more than one GPU too (by default only "
+                         "one-GPU runs do: on N GPUs the endpoint needs a second bring-up of all ranks)")
     ap.add_argument("--model", default="llama8b", choices=["llama8b", "llama70b-fp8", "deepseek-v3"],
                     help="llama8b: the headline config (bf16, any --gpus); llama70b-fp8: Llama-3.3-70B shapes with "
                          "block-scaled fp8 weights, tensor parallel over --gpus (input 2048 / output 512 / "
@@ -423,7 +431,9 @@ def main() -> int:
         dist.barrier()
         dist.destroy_process_group()
     server = None
-    if not args.no_server:
+    if world > 1 and not args.server and not args.no_server:
+        server = {"skipped": "multi-GPU runs measure the endpoint only with --server"}
+    elif not args.no_server:
         import gc
 
         del llm
