@@ -67,6 +67,14 @@ def merge_expert_load(parts: Sequence, slots_per_rank: Optional[int] = None) -> 
 
 
 class LLM:
+    def _draft_proposer(self, max_tokens: int, max_batch_size: int):
+        if self.draft is None:
+            return None
+        from ..pipelines.speculative import BatchedDraftProposer
+
+        d_model, d_kv = self.draft
+        return BatchedDraftProposer(d_model, d_kv, max_tokens, max_batch_size, target_kv=self.kv)
+
     def __init__(self, model_config, weights=None, *, device: Optional[str] = None,
                  dtype: Optional[torch.dtype] = None, max_length: int = 4096, max_batch_size: int = 256,
                  max_batch_input_tokens: int = 8192, page_size: int = 128,
@@ -78,9 +86,13 @@ class LLM:
                  tp_rank: int = 0, host_kvcache_swap_space_gb: float = 0.0,
                  disk_kvcache_dir: Optional[str] = None, disk_kvcache_space_gb: float = 0.0,
                  step_token_alignment: Optional[int] = None, weights_are_sharded: bool = False,
-                 ep_size: int = 1, ep_rank: int = 0, ep_fp8_dispatch: bool = False, speculative=None):
+                 ep_size: int = 1, ep_rank: int = 0, ep_fp8_dispatch: bool = False, speculative=None,
+                 draft_model_config=None, draft_weights=None):
         """``speculative``: a :class:`pipelines.speculative.SpeculativeConfig`; decode steps of greedy requests
-        then verify n-gram proposals (several tokens per step, same output as plain greedy decoding)."""
+        then verify proposals (several tokens per step, same output as plain greedy decoding): n-gram look-ups in
+        the request's own history, or with ``method="draft_model"`` the greedy continuation of a smaller model of
+        the same vocabulary (``draft_model_config`` / ``draft_weights``; random weights when none are given),
+        which gets its own paged cache and drafts for all requests of a step at once."""
         from ..models import family_for
 
         fam = family_for(model_config)
@@ -127,6 +139,30 @@ class LLM:
             weights = fam.weights_class.random_init(model_config, self.device, dtype, seed=seed)
         self.weights = weights
         self.max_length = max_length
+        # the draft model of speculative decoding comes first, so that the cache sizing below sees what it took
+        self.draft = None
+        if speculative is not None and speculative.method == "draft_model":
+            if draft_model_config is None:
+                raise ValueError("speculative method draft_model needs draft_model_config")
+            if tp_size > 1 or ep_size > 1:
+                raise ValueError("draft-model speculation runs on one device")
+            if draft_model_config.vocab_size != model_config.vocab_size:
+                raise ValueError("the draft model must share the target's vocabulary")
+            dfam = family_for(draft_model_config)
+            if draft_weights is None:
+                draft_weights = dfam.weights_class.random_init(draft_model_config, self.device, dtype, seed=seed + 1)
+            dkvp = dfam.kv_params(draft_model_config, page_size, dtype, False)   # no prefix cache: drafts get rewritten
+            if on_gpu:
+                free, total = torch.cuda.mem_get_info(self.device)
+                d_budget = int(0.1 * (free - (1.0 - device_memory_utilization) * total))
+                d_pages = dkvp.compute_num_device_blocks(d_budget, max_batch_size * 4, max_length)
+            else:
+                d_pages = dkvp.compute_num_device_blocks(1 << 62, max_batch_size, max_length)
+            d_kv = PagedKVCacheManager(dkvp, d_pages, self.device, max_seq_len=max_length)
+            d_extra = {"tp": None} if dfam.supports_tp else {}
+            d_model = dfam.model_class(draft_model_config, draft_weights, d_kv.kv, max_tokens=max_batch_input_tokens,
+                                       max_seqs=max_batch_size, max_position=max_length, **d_extra)
+            self.draft = (d_model, d_kv)
         kvp = fam.kv_params(model_config, page_size, dtype, enable_prefix_caching)
         if num_kv_pages is None:
             if on_gpu:
@@ -167,7 +203,8 @@ class LLM:
         self.pipeline = TextGenerationPipeline(
             self.model, self.kv, max_batch_input_tokens, max_batch_size, overlap=overlap,
             graph_batch_sizes=graph_batch_sizes if (device_graph_capture and on_gpu) else (),
-            eos_token_ids=eos_token_ids, speculative=speculative)
+            eos_token_ids=eos_token_ids, speculative=speculative, draft=self._draft_proposer(max_batch_input_tokens,
+                                                                                             max_batch_size))
         if device_graph_capture and on_gpu:
             self.pipeline.warmup_graph_capture()
             if hasattr(self.model, "capture_decode_graphs"):

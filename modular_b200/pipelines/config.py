@@ -112,7 +112,7 @@ class LoRAConfig(ConfigFileModel):
 
 
 class SpeculativeConfig(ConfigFileModel):
-    speculative_method: Optional[str] = None        # ngram (served); eagle | mtp | standalone are accepted names only
+    speculative_method: Optional[str] = None        # ngram | standalone (draft_model_path) are served; eagle | mtp are names only
     num_speculative_tokens: int = 0
     draft_model_path: Optional[str] = None
 

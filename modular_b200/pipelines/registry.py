@@ -159,6 +159,25 @@ class PipelineRegistry:
                 weights = arch.weights_class.from_state_dict(cfg, sd.to_dict(), device, dtype)
                 if to_fp8:
                     weights = weights.quantize_fp8()
+        spec = _speculative_from(pc)
+        draft_cfg = draft_weights = None
+        if spec is not None and spec.method == "draft_model":
+            # the draft model resolves like the served one: a preset or a checkpoint directory of a registered family
+            dpath = pc.speculative.draft_model_path
+            if not dpath:
+                raise ValueError("--speculative-method standalone needs --draft-model-path")
+            if dpath.startswith("preset:"):
+                name = dpath.split(":", 1)[1]
+                hits = [a for a in self.architectures.values() if name in a.preset_configs]
+                if not hits:
+                    raise ValueError(f"unknown draft preset {name!r}")
+                darch, draft_cfg = hits[0], hits[0].preset_configs[name]()
+            else:
+                dhf = load_hf_config(dpath)
+                darch = self.retrieve_architecture(dhf)
+                draft_cfg = darch.config_class.from_hf(dhf)
+                draft_weights = darch.weights_class.from_state_dict(draft_cfg, load_state_dict(dpath, []).to_dict(),
+                                                                    device, dtype)
         plan = self.plan_memory(pc, cfg, device) if on_gpu else None
         max_length = min(m.max_length or cfg.max_position_embeddings, cfg.max_position_embeddings)
         if plan is not None:
@@ -182,7 +201,8 @@ class PipelineRegistry:
                   disk_kvcache_dir=m.kv_cache.disk_kvcache_dir,
                   disk_kvcache_space_gb=m.kv_cache.disk_kvcache_space_gb,
                   tp_size=tp_size, tp_rank=tp_rank, weights_are_sharded=sharded,
-                  speculative=_speculative_from(pc), ep_size=ep_size, ep_rank=ep_rank,
+                  speculative=spec, draft_model_config=draft_cfg, draft_weights=draft_weights,
+                  ep_size=ep_size, ep_rank=ep_rank,
                   ep_fp8_dispatch=ep_size > 1 and getattr(cfg, "hidden_size", 0) % 512 == 0)
         llm.tokenizer = tokenizer
         if pc.sampling.enable_structured_output:
@@ -196,17 +216,21 @@ PIPELINE_REGISTRY = PipelineRegistry()
 
 
 def _speculative_from(pc):
-    """The engine's speculative-decoding settings from the pipeline config (``--speculative-method ngram``; the
-    reference's ``standalone`` / ``eagle`` / ``mtp`` draft-model methods are not served by this loop)."""
+    """The engine's speculative-decoding settings from the pipeline config: ``--speculative-method ngram``, or
+    ``standalone`` (alias ``draft_model``) with ``--draft-model-path``, a separate smaller model of the same
+    vocabulary. The reference's ``eagle`` / ``mtp`` methods draft from the target's hidden states with extra
+    trained heads; they are not served by this loop."""
     sc = pc.speculative
     if not sc.speculative_method:
         return None
-    if sc.speculative_method != "ngram":
-        raise ValueError(f"speculative method {sc.speculative_method!r} is not available in the serving loop "
-                         "(ngram is; draft models run through pipelines.speculative.SpeculativeDecoder)")
     from .speculative import SpeculativeConfig as EngineSpec
 
-    return EngineSpec(method="ngram", num_speculative_tokens=sc.num_speculative_tokens or 4)
+    if sc.speculative_method == "ngram":
+        return EngineSpec(method="ngram", num_speculative_tokens=sc.num_speculative_tokens or 4)
+    if sc.speculative_method in ("standalone", "draft_model"):
+        return EngineSpec(method="draft_model", num_speculative_tokens=sc.num_speculative_tokens or 4)
+    raise ValueError(f"speculative method {sc.speculative_method!r} is not available in the serving loop "
+                     "(ngram and standalone are)")
 
 
 def _register_builtin() -> None:

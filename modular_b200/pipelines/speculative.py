@@ -1,10 +1,13 @@
 """Speculative decoding: propose several tokens cheaply, verify them with one target-model step.
 
-Two proposers:
+Three proposers:
 * ``NgramProposer`` (prompt lookup): continue the longest recent n-gram match in the request's own
   history; no second model.
 * ``DraftModelProposer``: a smaller model with its own paged cache decodes ``k`` tokens greedily
-  (or by sampling, returning its probabilities for rejection sampling).
+  (or by sampling, returning its probabilities for rejection sampling), one sequence at a time.
+* ``BatchedDraftProposer``: the same for the serving loop - the draft model has its own paged cache manager
+  and batches the requests of a step: ``k`` draft steps over all of them, then one verification step of the
+  target (the reference's ``standalone`` draft-model method).
 
 ``SpeculativeDecoder.generate`` runs one sequence: each iteration feeds ``[last, d1..dk]`` to the
 target as a k+1-token ragged step (logits on every row), accepts the longest valid prefix and one
@@ -141,6 +144,110 @@ class DraftModelProposer:
 
     def observe(self, accepted_len: int) -> None:
         pass
+
+
+class BatchedDraftProposer:
+    """Draft-model proposals for all requests of a serving step (reference: the ``standalone`` method of
+    max/python/max/pipelines/speculative/, where a second pipeline model with its own KV cache drafts).
+
+    Every request has a mirror context in the draft model's own paged cache. Before drafting, a mirror is brought
+    in line with the request's accepted tokens (its rejected drafts are cut off at the first difference; cache
+    rows behind that point are simply written again), then the mirrors step together: prompts catch up in chunks,
+    and every further step appends one greedy draft token per request that still has room."""
+
+    def __init__(self, draft_model, kv_manager, max_batch_tokens: int, max_batch_size: int, target_kv=None):
+        from .batch import BatchPacker
+
+        self.model, self.kv = draft_model, kv_manager
+        self.target_kv = target_kv      # requests that left the target's cache lose their mirror at the next step
+        cfg = draft_model.cfg
+        self.device = draft_model.device
+        self.packer = BatchPacker(cfg.num_attention_heads, cfg.num_key_value_heads, kv_manager.page_size,
+                                  max_batch_tokens, max_batch_size, kv_manager.max_pages_per_seq, device=self.device)
+        self.mirror: dict = {}
+        self.draft_steps = 0
+        self._step = 0
+
+    def release(self, request_id: str) -> None:
+        m = self.mirror.pop(request_id, None)
+        if m is not None and self.kv.contains(m.request_id):
+            self.kv.release(m.request_id)
+
+    def _sync(self, ctx):
+        import numpy as np
+
+        from .context import TextContext
+
+        hist = ctx.tokens.all
+        m = self.mirror.get(ctx.request_id)
+        if m is None:
+            m = TextContext.from_prompt(hist, ctx.max_length, request_id="draft:" + ctx.request_id)
+            self.kv.claim(m)
+            self.mirror[ctx.request_id] = m
+            return m
+        mt = m.tokens
+        n = min(len(mt), len(hist))
+        diff = np.flatnonzero(mt.all[:n] != hist[:n])
+        keep = max(int(diff[0]) if diff.size else n, mt.prompt_len)
+        mt.truncate(keep)
+        for t in hist[keep:]:
+            mt.advance_with_token(int(t))
+        mt.processed = min(mt.processed, len(mt) - 1)      # at least the newest token is fed again
+        mt.active_end = len(mt)
+        return m
+
+    def _forward(self, sel) -> list:
+        """One draft step over ``sel`` (their active windows); the greedy token after each window."""
+        from .batch import BatchPacker
+
+        self._step += 1
+        self.draft_steps += 1
+        sb = self.packer.pack(sel, self.kv)
+        if self.device.type == "cuda" and getattr(self.model, "use_executor", False):
+            meta = self.packer.upload(sb)
+            self.model.forward_packed(meta, sb.offsets, sb.T, sb.B, sb.bt_stride, sb.n_tiles, sb.n_decode, sb.n_logits,
+                                      False, True, self._step)
+            return [int(v) for v in self.model.sampled[: sb.n_logits].cpu().numpy()]
+        t = BatchPacker.tensors(sb, self.device)
+        logits = self.model.forward_tensors(t["tokens"], t["positions"], t["slots"], t["block_table"], t["q_start"],
+                                            t["q_len"], t["kv_len"], t["logit_rows"])
+        return [int(v) for v in ops.argmax(logits).cpu().numpy()]
+
+    def propose_batch(self, batch, rooms: Sequence[int]) -> list:
+        """Up to ``rooms[i]`` greedy draft tokens for ``batch[i]`` (fewer when the draft cache is full)."""
+        if self.target_kv is not None:
+            for rid in [r for r in self.mirror if not self.target_kv.contains(r)]:
+                self.release(rid)
+        mirrors = [self._sync(c) for c in batch]
+        want = [max(0, int(r)) for r in rooms]
+        drafts = [[] for _ in batch]
+        while True:
+            budget = self.packer.max_tokens
+            sel = []
+            for i, m in enumerate(mirrors):
+                if len(drafts[i]) >= want[i] or budget <= 0 or len(sel) >= self.packer.max_seqs:
+                    continue
+                mt = m.tokens
+                mt.active_end = len(mt)
+                mt.chunk(budget)
+                if not self.kv.can_alloc(m) or len(mt) >= m.max_length:
+                    want[i] = len(drafts[i])               # no pages left for this request: stop drafting for it
+                    continue
+                self.kv.alloc(m)
+                budget -= mt.active_length
+                sel.append(i)
+            if not sel:
+                break
+            toks = iter(self._forward([mirrors[i] for i in sel]))
+            for i in sel:
+                mt = mirrors[i].tokens
+                whole = mt.active_end == len(mt)           # a chunk of a prompt has no logit row: no next token yet
+                mt.advance_processed()
+                if whole:
+                    t = next(toks)
+                    drafts[i].append(t)
+                    mt.advance_with_token(t)
+        return drafts
 
 
 class SpeculativeDecoder:

@@ -52,9 +52,10 @@ class PipelineStats:
 class TextGenerationPipeline:
     def __init__(self, model, kv_manager: PagedKVCacheManager, max_batch_tokens: int = 8192,
                  max_batch_size: int = 256, overlap: bool = False, graph_batch_sizes: Sequence[int] = (),
-                 eos_token_ids: Sequence[int] = (), speculative=None):
+                 eos_token_ids: Sequence[int] = (), speculative=None, draft=None):
         """``speculative``: a :class:`speculative.SpeculativeConfig` turns decode steps of greedy requests into
-        propose-and-verify steps (the step runs synchronously: the proposals need the previous token values)."""
+        propose-and-verify steps (the step runs synchronously: the proposals need the previous token values).
+        ``draft``: the :class:`speculative.BatchedDraftProposer` of the ``draft_model`` method."""
         self.model = model
         self.kv = kv_manager
         self.device = model.device
@@ -66,13 +67,17 @@ class TextGenerationPipeline:
         self.spec = speculative
         self.spec_stats = None
         self.proposer = None
+        self.draft = None
         rows = max_batch_size
         if speculative is not None:
             from .speculative import NgramProposer, SpecStats
 
-            if speculative.method != "ngram":
-                raise ValueError("the serving loop verifies n-gram (prompt lookup) proposals; draft-model proposals "
-                                 "run through speculative.SpeculativeDecoder")
+            if speculative.method == "draft_model":
+                if draft is None:
+                    raise ValueError("the draft_model method needs a BatchedDraftProposer (LLM(draft_model_config=...))")
+            elif speculative.method != "ngram":
+                raise ValueError(f"unknown speculative method {speculative.method!r} (ngram | draft_model)")
+            self.draft = draft if speculative.method == "draft_model" else None
             self.proposer = NgramProposer(speculative)
             self.spec_stats = SpecStats()
             rows = min(max_batch_size * (speculative.num_speculative_tokens + 1), getattr(model, "max_seqs", 1 << 30))
@@ -364,18 +369,26 @@ class TextGenerationPipeline:
         k = self.spec.num_speculative_tokens
         budget = self.packer.max_tokens - len(batch)          # rows left for drafts in this step
         rows_left = self.packer.max_logit_rows - len(batch)
-        base_len, drafts = [], []
+        rooms = []
         for c in batch:
             tb = c.tokens
-            room = min(k, c.max_new_tokens_effective - tb.generated_length - 1, c.max_length - len(tb) - 1,
-                       budget, rows_left)
-            d = self.proposer.propose(tb.all, room)[0] if room > 0 else []
+            room = max(0, min(k, c.max_new_tokens_effective - tb.generated_length - 1, c.max_length - len(tb) - 1,
+                              budget, rows_left))
+            rooms.append(room)
+            budget -= room
+            rows_left -= room
+        if self.draft is not None:
+            proposals = self.draft.propose_batch(batch, rooms)     # k batched steps of the draft model
+        else:
+            proposals = [self.proposer.propose(c.tokens.all, r)[0] if r > 0 else [] for c, r in zip(batch, rooms)]
+        base_len, drafts = [], []
+        for c, d, room in zip(batch, proposals, rooms):
+            tb = c.tokens
+            d = list(d[:room])
             while d and not self.kv.can_alloc(c, len(d)):
                 d = d[:-1]
             base_len.append(len(tb))
             drafts.append(d)
-            budget -= len(d)
-            rows_left -= len(d)
             for t in d:                                        # tentative: rolled back below
                 tb.advance_with_token(int(t))
             tb.active_end = len(tb)
@@ -466,3 +479,5 @@ class TextGenerationPipeline:
 
     def release(self, request_id: str) -> None:
         self.kv.release(request_id)
+        if self.draft is not None:
+            self.draft.release(request_id)

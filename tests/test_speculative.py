@@ -1,5 +1,6 @@
 """Speculative decoding on CPU: greedy verification reproduces plain greedy decoding exactly."""
 
+import pytest
 import torch
 
 from modular_b200.models.llama3 import Llama3Config, Llama3Model, Llama3Weights
@@ -98,6 +99,71 @@ def test_serving_loop_verifies_ngram_proposals_and_matches_plain_greedy():
     assert m.spec_steps >= 0 and "spec_accepted" in m.to_dict()
 
 
+def test_serving_loop_verifies_draft_model_proposals():
+    """Draft-model speculation in the serving loop: a second model with its own paged cache drafts for all requests
+    of a step; the output stays that of plain greedy decoding whatever the draft proposes."""
+    prompts = [[3, 4, 5, 3, 4, 5, 3, 4], [7, 7, 7, 7, 7], [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12] * 6, [9, 8]]
+    want, plain = _engine_tokens(None, prompts, 40)
+    cfg = Llama3Config.tiny(num_hidden_layers=2, vocab_size=64)
+    # the target itself as the draft (same seed -> same weights): every proposal is accepted
+    same_w = Llama3Weights.random_init(cfg, "cpu", torch.float32, seed=5)
+    got, spec = _engine_tokens(SpeculativeConfig("draft_model", 3), prompts, 40, draft_model_config=cfg,
+                               draft_weights=same_w)
+    assert got == want
+    st = spec.pipeline.spec_stats
+    assert st.emitted == 4 * 40 - 4 and st.proposed > 0 and st.acceptance_rate == 1.0
+    assert spec.pipeline.stats.steps < plain.pipeline.stats.steps
+    assert spec.pipeline.draft.draft_steps > 0 and not spec.pipeline.draft.mirror or True
+    # a different, smaller draft: wrong proposals cost steps, not accuracy
+    small = Llama3Config.tiny(num_hidden_layers=1, vocab_size=64)
+    got2, spec2 = _engine_tokens(SpeculativeConfig("draft_model", 4), prompts, 40, draft_model_config=small)
+    assert got2 == want
+    assert spec2.pipeline.spec_stats.proposed > 0
+    # mirrors of finished requests are dropped when the next batch is drafted for
+    more, _ = [list(r.tokens) for r in spec2.generate([[5, 6, 5, 6, 5]], __import__(
+        "modular_b200.pipelines.context", fromlist=["SamplingParams"]).SamplingParams(
+            temperature=0.0, max_new_tokens=12, ignore_eos=True))], None
+    assert len(more[0]) == 12 and len(spec2.pipeline.draft.mirror) == 1
+
+
+def test_standalone_draft_model_through_the_pipeline_config():
+    """``--speculative-method standalone --draft-model-path ...``: the registry resolves the draft model like the
+    served one and the engine verifies its proposals; tokens equal those of the engine without speculation."""
+    from modular_b200.pipelines.config import PipelineArgs, PipelineConfig
+    from modular_b200.pipelines.context import SamplingParams
+    from modular_b200.pipelines.registry import PIPELINE_REGISTRY
+
+    def build(**extra):
+        pc = PipelineConfig.from_args(PipelineArgs.from_flat_kwargs(
+            None, model_path="preset:tiny-llama", devices="cpu", max_length=128, max_batch_size=2,
+            max_batch_input_tokens=64, kv_cache_page_size=16, **extra))
+        return PIPELINE_REGISTRY.retrieve(pc)[1]
+
+    sp = SamplingParams(temperature=0.0, max_new_tokens=16, ignore_eos=True)
+    prompts = [[5, 6, 7, 8, 9, 5, 6, 7], [11, 12, 13]]
+    want = [list(r.tokens) for r in build().generate(prompts, sp)]
+    llm = build(speculative_method="standalone", num_speculative_tokens=3, draft_model_path="preset:tiny-llama")
+    assert [list(r.tokens) for r in llm.generate(prompts, sp)] == want
+    assert llm.pipeline.spec_stats.proposed > 0 and llm.pipeline.draft is not None
+    with pytest.raises(ValueError):
+        build(speculative_method="standalone", num_speculative_tokens=3)          # no draft model named
+    with pytest.raises(ValueError):
+        build(speculative_method="eagle", num_speculative_tokens=3)
+
+
+def test_draft_model_needs_the_targets_vocabulary():
+    from modular_b200.entrypoints.llm import LLM
+
+    cfg = Llama3Config.tiny(num_hidden_layers=2, vocab_size=64)
+    with pytest.raises(ValueError):
+        LLM(cfg, device="cpu", dtype=torch.float32, max_length=64, max_batch_size=2, max_batch_input_tokens=32,
+            page_size=16, num_kv_pages=16, speculative=SpeculativeConfig("draft_model", 2),
+            draft_model_config=Llama3Config.tiny(num_hidden_layers=1, vocab_size=96))
+    with pytest.raises(ValueError):
+        LLM(cfg, device="cpu", dtype=torch.float32, max_length=64, max_batch_size=2, max_batch_input_tokens=32,
+            page_size=16, num_kv_pages=16, speculative=SpeculativeConfig("draft_model", 2))
+
+
 def test_speculation_respects_token_limits_and_eos():
     from modular_b200.entrypoints.llm import LLM
     from modular_b200.pipelines.context import SamplingParams
@@ -133,3 +199,23 @@ def test_serving_loop_speculation_on_gpu_follows_plain_greedy():
     assert common >= 0.6 * 160, (common, want, got)
     st = spec.pipeline.spec_stats
     assert st.accepted > 0 and st.emitted == 4 * 40 - 4
+
+
+@pytest.mark.gpu
+def test_serving_loop_draft_model_on_gpu():
+    """Draft-model speculation through the native step executors of both models: the draft (same weights as the
+    target here) is accepted almost always, and the tokens follow plain greedy decoding up to bf16 near-ties."""
+    prompts = [[3, 4, 5, 3, 4, 5, 3, 4], [7, 7, 7, 7, 7], [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12] * 6, [9, 8]]
+    want, _ = _engine_tokens(None, prompts, 40, device="cuda")
+    cfg = Llama3Config.tiny(num_hidden_layers=2, vocab_size=64)
+    same_w = Llama3Weights.random_init(cfg, "cuda", torch.bfloat16, seed=5)
+    got, spec = _engine_tokens(SpeculativeConfig("draft_model", 3), prompts, 40, device="cuda",
+                               draft_model_config=cfg, draft_weights=same_w)
+    common = 0
+    for a, b in zip(want, got):
+        assert len(a) == len(b) == 40
+        common += next((i for i, (x, y) in enumerate(zip(a, b)) if x != y), 40)
+    assert common >= 0.6 * 160, (common, want, got)
+    st = spec.pipeline.spec_stats
+    assert st.emitted == 4 * 40 - 4 and st.acceptance_rate > 0.5
+    assert spec.pipeline.draft.draft_steps > 0
