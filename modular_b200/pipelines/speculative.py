@@ -181,7 +181,11 @@ class BatchedDraftProposer:
         hist = ctx.tokens.all
         m = self.mirror.get(ctx.request_id)
         if m is None:
-            m = TextContext.from_prompt(hist, ctx.max_length, request_id="draft:" + ctx.request_id)
+            from .context import SamplingParams
+
+            # greedy drafts: the device-side sampler reads the mirror's parameters
+            m = TextContext.from_prompt(hist, ctx.max_length, request_id="draft:" + ctx.request_id,
+                                        sampling_params=SamplingParams(temperature=0.0))
             self.kv.claim(m)
             self.mirror[ctx.request_id] = m
             return m
