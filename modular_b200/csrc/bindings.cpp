@@ -433,8 +433,14 @@ class PyDecoderExecutor {
   // scales: the four block-scale tensors of an fp8 layer (all or none)
   void add_layer(const Tensor& attn_norm, const Tensor& wqkv, const Tensor& wo,
                  const Tensor& mlp_norm, const Tensor& wgu, const Tensor& wd,
-                 const c10::optional<std::vector<Tensor>>& scales) {
+                 const c10::optional<std::vector<Tensor>>& scales, const c10::optional<Tensor>& qkv_bias) {
     mb::DecoderLayerWeights w;
+    if (qkv_bias.has_value() && qkv_bias->defined()) {
+      TORCH_CHECK(qkv_bias->scalar_type() == at::kBFloat16 && qkv_bias->dim() == 1 &&
+                      qkv_bias->size(0) == wqkv.size(0) && qkv_bias->is_contiguous(),
+                  "add_layer: qkv_bias must be a contiguous bf16 vector with one entry per row of wqkv");
+      w.qkv_bias = hold(*qkv_bias);
+    }
     w.attn_norm = hold(attn_norm); w.wqkv = hold(wqkv); w.wo = hold(wo);
     w.mlp_norm = hold(mlp_norm); w.wgu = hold(wgu); w.wd = hold(wd);
     if (scales.has_value()) {
@@ -1199,7 +1205,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def(py::init<py::dict>())
       .def("set_globals", &PyDecoderExecutor::set_globals)
       .def("add_layer", &PyDecoderExecutor::add_layer, py::arg("attn_norm"), py::arg("wqkv"), py::arg("wo"),
-           py::arg("mlp_norm"), py::arg("wgu"), py::arg("wd"), py::arg("scales") = py::none())
+           py::arg("mlp_norm"), py::arg("wgu"), py::arg("wd"), py::arg("scales") = py::none(),
+           py::arg("qkv_bias") = py::none())
       .def("set_fp8_buffers", &PyDecoderExecutor::set_fp8_buffers)
       .def("set_kv_cache", &PyDecoderExecutor::set_kv_cache)
       .def("set_buffers", &PyDecoderExecutor::set_buffers)

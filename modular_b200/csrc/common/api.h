@@ -94,6 +94,8 @@ int mb_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, int 
                float eps, float weight_offset, int multiply_before_cast, cudaStream_t stream);
 int mb_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int rows, int cols,
                    float eps, float weight_offset, int multiply_before_cast, cudaStream_t stream);
+// x[r, 0:cols] += bias (bf16; rows `ld` elements apart, cols and ld multiples of 8)
+int mb_add_bias(void* x, const void* bias, int rows, int cols, int ld, cudaStream_t stream);
 int mb_silu_mul(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream);
 int mb_silu_mul_quant_fp8(const void* gate_up, void* q_fp8, float* scales, int M, int inter, int ld_s,
                           const int32_t* n_rows_dev, cudaStream_t stream);

@@ -29,6 +29,7 @@ struct DecoderLayerWeights {
   const float* wo_s = nullptr;
   const float* wgu_s = nullptr;
   const float* wd_s = nullptr;
+  const void* qkv_bias = nullptr;   // [(n_q + 2 n_kv) * head_dim] added to the fused projection (Qwen2), or nullptr
 };
 
 struct DecoderConfig {

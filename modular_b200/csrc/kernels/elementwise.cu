@@ -96,6 +96,27 @@ rmsnorm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf
   }
 }
 
+// x[r, c] += bias[c] (bias of a fused projection; rows of `ld` elements, cols a multiple of 8)
+__global__ void add_bias_kernel(bf16* __restrict__ x, const bf16* __restrict__ bias, int rows, int cols, int ld) {
+  pdl_wait();
+  pdl_trigger();
+  const int per_row = cols >> 3;
+  const size_t vec = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (vec >= static_cast<size_t>(rows) * per_row) return;
+  const int r = static_cast<int>(vec / per_row), c = static_cast<int>(vec % per_row) * 8;
+  bf16* xp = x + static_cast<size_t>(r) * ld + c;
+  uint4 a = *reinterpret_cast<const uint4*>(xp);
+  const uint4 b = *reinterpret_cast<const uint4*>(bias + c);
+  bf162* ap = reinterpret_cast<bf162*>(&a);
+  const bf162* bp = reinterpret_cast<const bf162*>(&b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 fa = __bfloat1622float2(ap[i]), fb = __bfloat1622float2(bp[i]);
+    ap[i] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+  }
+  *reinterpret_cast<uint4*>(xp) = a;
+}
+
 // out[r, i] = silu(gu[r, i]) * gu[r, inter + i]
 __global__ void silu_mul_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int rows,
                                 int inter) {
@@ -290,6 +311,16 @@ extern "C" int mb_add_rmsnorm(const void* x, void* residual, const void* w, void
   launch_k(rmsnorm_kernel<true>, dim3(rows), dim3(256), cols * 2, stream, static_cast<const bf16*>(x),
            static_cast<bf16*>(residual), static_cast<const bf16*>(w), static_cast<bf16*>(out), cols, cols, cols,
            eps, weight_offset, mbc);
+  return MB_LAUNCH_OK();
+}
+
+extern "C" int mb_add_bias(void* x, const void* bias, int rows, int cols, int ld, cudaStream_t stream) {
+  if (rows <= 0) return MB_OK;
+  if (cols % 8 || ld % 8) return MB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(bias)) & 15) return MB_ERR_ALIGN;
+  const size_t n = static_cast<size_t>(rows) * (cols / 8);
+  launch_k(add_bias_kernel, dim3(blocks_for(n, 256)), dim3(256), 0, stream, static_cast<bf16*>(x),
+           static_cast<const bf16*>(bias), rows, cols, ld);
   return MB_LAUNCH_OK();
 }
 

@@ -21,6 +21,7 @@ model_config.py; HF ``DeepseekV3ForCausalLM`` naming for checkpoints.
 
 from __future__ import annotations
 
+import contextlib
 import math
 from dataclasses import dataclass, field
 from typing import Optional
@@ -31,6 +32,24 @@ from .. import ops
 from ..nn.moe import Fp8ExpertWeights, MoE, MoEConfig
 from ..nn.rotary_embedding import RopeScaling, cos_sin_table
 
+
+
+@contextlib.contextmanager
+def _no_gc_during_capture():
+    """Collect dead reference cycles now and keep the cyclic collector off while a CUDA graph is captured. The
+    step below runs as Python code that allocates many temporaries; a collection triggered in the middle of it
+    can destroy CUDA graphs of an engine that is no longer referenced, and destroying a graph is not permitted
+    while a stream captures (the capture is invalidated and the next launch fails)."""
+    import gc
+
+    gc.collect()
+    was_on = gc.isenabled()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was_on:
+            gc.enable()
 
 @dataclass
 class DeepseekV3Config:
@@ -449,8 +468,9 @@ class DeepseekV3Model:
 
             g = torch.cuda.CUDAGraph()
             n0 = native_calls()
-            with torch.cuda.graph(g):
-                logits = self._forward(*args)
+            with _no_gc_during_capture():
+                with torch.cuda.graph(g):
+                    logits = self._forward(*args)
             self._graph_calls[B] = native_calls() - n0
             self._graphs[B] = (g, st, logits)
         torch.cuda.synchronize()

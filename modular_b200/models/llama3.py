@@ -45,6 +45,7 @@ class Llama3Config:
     tie_word_embeddings: bool = False
     attention_multiplier: Optional[float] = None
     logits_scaling: float = 1.0
+    attention_bias: bool = False      # bias on the query / key / value projections (Qwen2)
     architectures: tuple = ("LlamaForCausalLM",)
 
     def __post_init__(self):
@@ -102,6 +103,58 @@ class Llama3Config:
 
 
 @dataclass
+class MistralConfig(Llama3Config):
+    """Mistral checkpoints (``MistralForCausalLM``) share the Llama layer structure and tensor names. Versions with
+    a sliding attention window shorter than the context are refused: every layer here attends to the whole prefix.
+    Reference: max/python/max/pipelines/architectures/mistral/."""
+
+    rope_theta: float = 1000000.0
+    max_position_embeddings: int = 32768
+    architectures: tuple = ("MistralForCausalLM",)
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "MistralConfig":
+        window = d.get("sliding_window")
+        if window is not None and window < d.get("max_position_embeddings", cls.max_position_embeddings):
+            raise ValueError(f"sliding-window attention (window {window}) is not implemented")
+        return super().from_hf(d)
+
+    def to_hf(self) -> dict:
+        d = super().to_hf()
+        d["model_type"] = "mistral"
+        d["sliding_window"] = None
+        return d
+
+
+@dataclass
+class Qwen2Config(Llama3Config):
+    """Qwen2 / Qwen2.5 (``Qwen2ForCausalLM``): the Llama layer with a bias on the query, key and value projections.
+    Checkpoints that switch sliding-window attention on are refused.
+    Reference: max/python/max/pipelines/architectures/qwen2/."""
+
+    rope_theta: float = 1000000.0
+    rms_norm_eps: float = 1e-6
+    max_position_embeddings: int = 32768
+    attention_bias: bool = True
+    architectures: tuple = ("Qwen2ForCausalLM",)
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "Qwen2Config":
+        if d.get("use_sliding_window"):
+            raise ValueError("sliding-window attention is not implemented")
+        cfg = super().from_hf(d)
+        cfg.attention_bias = True          # HF's Qwen2 layers always carry the bias; the key is not in its config
+        return cfg
+
+    def to_hf(self) -> dict:
+        d = super().to_hf()
+        d["model_type"] = "qwen2"
+        d["use_sliding_window"] = False
+        return d
+
+
+
+@dataclass
 class LayerWeights:
     attn_norm: torch.Tensor
     wqkv: torch.Tensor
@@ -115,6 +168,7 @@ class LayerWeights:
     wo_s: Optional[torch.Tensor] = None
     wgu_s: Optional[torch.Tensor] = None
     wd_s: Optional[torch.Tensor] = None
+    qkv_bias: Optional[torch.Tensor] = None      # [q; k; v] projection bias (Qwen2), in the activation dtype
 
     @property
     def is_fp8(self) -> bool:
@@ -153,7 +207,8 @@ class Llama3Weights:
                 wo=rnd(cfg.hidden_size, cfg.q_dim),
                 mlp_norm=torch.ones(cfg.hidden_size, dtype=dtype, device=dev),
                 wgu=rnd(2 * cfg.intermediate_size, cfg.hidden_size),
-                wd=rnd(cfg.hidden_size, cfg.intermediate_size)))
+                wd=rnd(cfg.hidden_size, cfg.intermediate_size),
+                qkv_bias=rnd(cfg.q_dim + 2 * cfg.kv_dim) if cfg.attention_bias else None))
         final_norm = torch.ones(cfg.hidden_size, dtype=dtype, device=dev)
         lm_head = embed if cfg.tie_word_embeddings else rnd(cfg.vocab_size, cfg.hidden_size)
         return cls(embed, layers, final_norm, lm_head)
@@ -180,7 +235,8 @@ class Llama3Weights:
             l = LayerWeights(ones(), rnd(g_rank, local.q_dim + 2 * local.kv_dim, cfg.hidden_size),
                              rnd(g_rank, cfg.hidden_size, local.q_dim), ones(),
                              rnd(g_rank, 2 * local.intermediate_size, cfg.hidden_size),
-                             rnd(g_rank, cfg.hidden_size, local.intermediate_size))
+                             rnd(g_rank, cfg.hidden_size, local.intermediate_size),
+                             qkv_bias=rnd(g_rank, local.q_dim + 2 * local.kv_dim) if cfg.attention_bias else None)
             if fp8:
                 l = cls(embed, [l], ones(), embed).quantize_fp8().layers[0]
             layers.append(l)
@@ -201,7 +257,7 @@ class Llama3Weights:
                 layers.append(l)
                 continue
             (a, a_s), (b, b_s), (c_, c_s), (d, d_s) = q(l.wqkv), q(l.wo), q(l.wgu), q(l.wd)
-            layers.append(LayerWeights(l.attn_norm, a, b, l.mlp_norm, c_, d, a_s, b_s, c_s, d_s))
+            layers.append(LayerWeights(l.attn_norm, a, b, l.mlp_norm, c_, d, a_s, b_s, c_s, d_s, l.qkv_bias))
         return Llama3Weights(self.embed, layers, self.final_norm, self.lm_head)
 
     def dequantize(self, dtype=torch.bfloat16) -> "Llama3Weights":
@@ -209,7 +265,7 @@ class Llama3Weights:
         activation quantisation)."""
         d = lambda w, s: ops.reference.dequant_fp8_weight_block128(w, s).to(dtype)
         layers = [LayerWeights(l.attn_norm, d(l.wqkv, l.wqkv_s), d(l.wo, l.wo_s), l.mlp_norm, d(l.wgu, l.wgu_s),
-                               d(l.wd, l.wd_s)) if l.is_fp8 else l for l in self.layers]
+                               d(l.wd, l.wd_s), qkv_bias=l.qkv_bias) if l.is_fp8 else l for l in self.layers]
         return Llama3Weights(self.embed, layers, self.final_norm, self.lm_head)
 
     @classmethod
@@ -246,6 +302,12 @@ class Llama3Weights:
         def get(name):
             return raw(name).to(device=dev, dtype=dtype).contiguous()
 
+        def bias(p):
+            names = [p + f"self_attn.{n}_proj.bias" for n in "qkv"]
+            if not all(n in sd for n in names):
+                return None
+            return torch.cat([sd[n].float() for n in names]).to(device=dev, dtype=dtype).contiguous()
+
         layers = []
         for i in range(cfg.num_hidden_layers):
             p = f"layers.{i}."
@@ -255,7 +317,8 @@ class Llama3Weights:
                 c_, c_s = fp8_cat(p, ("mlp.gate_proj", "mlp.up_proj"))
                 d, d_s = fp8_cat(p, ("mlp.down_proj",))
                 layers.append(LayerWeights(get(p + "input_layernorm.weight"), a, b,
-                                           get(p + "post_attention_layernorm.weight"), c_, d, a_s, b_s, c_s, d_s))
+                                           get(p + "post_attention_layernorm.weight"), c_, d, a_s, b_s, c_s, d_s,
+                                           bias(p)))
                 continue
             wqkv = torch.cat([raw(p + "self_attn.q_proj.weight"), raw(p + "self_attn.k_proj.weight"),
                               raw(p + "self_attn.v_proj.weight")], dim=0)
@@ -266,7 +329,7 @@ class Llama3Weights:
                 wo=get(p + "self_attn.o_proj.weight"),
                 mlp_norm=get(p + "post_attention_layernorm.weight"),
                 wgu=wgu.to(device=dev, dtype=dtype).contiguous(),
-                wd=get(p + "mlp.down_proj.weight")))
+                wd=get(p + "mlp.down_proj.weight"), qkv_bias=bias(p)))
         embed = get("embed_tokens.weight")
         lm_head = embed if (cfg.tie_word_embeddings or "lm_head.weight" not in sd) else get("lm_head.weight")
         return cls(embed, layers, get("norm.weight"), lm_head)
@@ -278,6 +341,10 @@ class Llama3Weights:
             sd["lm_head.weight"] = self.lm_head
         for i, l in enumerate(self.layers):
             p = f"model.layers.{i}."
+            if l.qkv_bias is not None:
+                bq, bk, bv = torch.split(l.qkv_bias, [cfg.q_dim, cfg.kv_dim, cfg.kv_dim])
+                sd.update({p + "self_attn.q_proj.bias": bq, p + "self_attn.k_proj.bias": bk,
+                           p + "self_attn.v_proj.bias": bv})
             if l.is_fp8:
                 # e4m3 tensors cannot be split by torch.split on every build: slice through the byte view
                 rows = lambda w, a, b: w.view(torch.uint8)[a:b].view(torch.float8_e4m3fn)
@@ -364,7 +431,7 @@ class Llama3Model:
         if self.is_fp8 and not all(l.is_fp8 for l in self.w.layers):
             raise ValueError("mixed fp8 / bf16 layers are not supported by the executor")
         for l in self.w.layers:
-            ex.add_layer(l.attn_norm, l.wqkv, l.wo, l.mlp_norm, l.wgu, l.wd, l.scales())
+            ex.add_layer(l.attn_norm, l.wqkv, l.wo, l.mlp_norm, l.wgu, l.wd, l.scales(), l.qkv_bias)
         ex.set_kv_cache(self.kv)
         T, B = self.max_tokens, self.max_seqs
         mk = lambda *s, dtype=dt: torch.empty(*s, dtype=dtype, device=dev)
@@ -473,6 +540,8 @@ class Llama3Model:
             if l.is_fp8:
                 # block-scaled fp8 projections: activations quantised per token group in front of every GEMM
                 qkv = ops.linear_fp8(x, l.wqkv, l.wqkv_s)
+                if l.qkv_bias is not None:
+                    qkv += l.qkv_bias
                 ops.rope_kv_store(qkv, positions, slots, self.cos_sin, kc, vc, c.num_attention_heads,
                                   c.num_key_value_heads, c.head_dim, False)
                 a = ops.paged_attention(qkv, kc, vc, block_table, q_start, q_len, kv_len, c.num_attention_heads,
@@ -483,6 +552,8 @@ class Llama3Model:
                 h = ops.linear_fp8(act, l.wd, l.wd_s, residual=h)
                 continue
             qkv = ops.linear(x, l.wqkv)
+            if l.qkv_bias is not None:
+                qkv += l.qkv_bias
             ops.rope_kv_store(qkv, positions, slots, self.cos_sin, kc, vc, c.num_attention_heads,
                               c.num_key_value_heads, c.head_dim, False)
             a = ops.paged_attention(qkv, kc, vc, block_table, q_start, q_len, kv_len,
@@ -516,6 +587,8 @@ class Llama3Model:
             kc, vc = kv[:, 0, li], kv[:, 1, li]
             x = ops.rms_norm(h, l.attn_norm, c.rms_norm_eps)
             qkv = ops.linear(x, l.wqkv)
+            if l.qkv_bias is not None:
+                qkv += l.qkv_bias
             add(qkv, lora.delta(li, "q_proj", x), 0, c.q_dim)
             add(qkv, lora.delta(li, "k_proj", x), c.q_dim, c.q_dim + c.kv_dim)
             add(qkv, lora.delta(li, "v_proj", x), c.q_dim + c.kv_dim, c.q_dim + 2 * c.kv_dim)

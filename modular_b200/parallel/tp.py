@@ -225,7 +225,18 @@ def _shard_fp8_layer(cfg, l, rank: int, world: int):
     wgu_s = torch.cat([p[1] for p in gu], 0).contiguous()
     wd, wd_s = cols(l.wd, l.wd_s, rank * Il, Il)
     return LayerWeights(l.attn_norm, wqkv, f8(wo), l.mlp_norm, wgu, f8(wd), wqkv_s, wo_s.contiguous(), wgu_s,
-                        wd_s.contiguous())
+                        wd_s.contiguous(), _shard_qkv_bias(cfg, l.qkv_bias, rank, world))
+
+
+def _shard_qkv_bias(cfg, bias, rank: int, world: int):
+    """This rank's entries of a [q; k; v] projection bias: the rows of its query and KV heads."""
+    if bias is None:
+        return None
+    hd = cfg.head_dim
+    nq, nkv = cfg.num_attention_heads // world, cfg.num_key_value_heads // world
+    q, k, v = torch.split(bias, [cfg.q_dim, cfg.kv_dim, cfg.kv_dim])
+    q0, k0 = rank * nq * hd, rank * nkv * hd
+    return torch.cat([q[q0:q0 + nq * hd], k[k0:k0 + nkv * hd], v[k0:k0 + nkv * hd]]).contiguous()
 
 
 def shard_llama_weights(cfg, weights, rank: int, world: int):
@@ -248,7 +259,8 @@ def shard_llama_weights(cfg, weights, rank: int, world: int):
         g, u = l.wgu[:I], l.wgu[I:]
         wgu = torch.cat([g[rank * Il:(rank + 1) * Il], u[rank * Il:(rank + 1) * Il]], dim=0).contiguous()
         wd = l.wd[:, rank * Il:(rank + 1) * Il].contiguous()
-        layers.append(LayerWeights(l.attn_norm, wqkv, wo, l.mlp_norm, wgu, wd))
+        layers.append(LayerWeights(l.attn_norm, wqkv, wo, l.mlp_norm, wgu, wd,
+                                   qkv_bias=_shard_qkv_bias(cfg, l.qkv_bias, rank, world)))
     Vl = cfg.vocab_size // world
     lm_head = weights.lm_head[rank * Vl:(rank + 1) * Vl].contiguous()
     return Llama3Weights(weights.embed, layers, weights.final_norm, lm_head)

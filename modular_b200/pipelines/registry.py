@@ -244,6 +244,28 @@ def _register_builtin() -> None:
         preset_configs={"llama3.1-8b": Llama3Config.llama31_8b, "llama3.3-70b": Llama3Config.llama33_70b,
                         "tiny-llama": Llama3Config.tiny})
     PIPELINE_REGISTRY.register(llama, allow_override=True)
+    from ..models.llama3 import MistralConfig
+
+    # same layers, tensor names and kernels as Llama; full attention only
+    mistral = SupportedArchitecture(
+        name="MistralForCausalLM", config_class=MistralConfig, weights_class=Llama3Weights,
+        model_class=Llama3Model, default_encoding="bfloat16",
+        supported_encodings=("bfloat16", "float32", "float8_e4m3fn"),
+        example_repo_ids=("mistralai/Mistral-7B-Instruct-v0.3", "mistralai/Mistral-Nemo-Instruct-2407"),
+        preset_configs={})
+    PIPELINE_REGISTRY.register(mistral, allow_override=True)
+    from ..models.llama3 import Qwen2Config
+
+    # the Llama layer with a bias on the fused query / key / value projection
+    qwen2 = SupportedArchitecture(
+        name="Qwen2ForCausalLM", config_class=Qwen2Config, weights_class=Llama3Weights,
+        model_class=Llama3Model, default_encoding="bfloat16",
+        supported_encodings=("bfloat16", "float32", "float8_e4m3fn"),
+        example_repo_ids=("Qwen/Qwen2.5-7B-Instruct", "Qwen/Qwen2.5-72B-Instruct"),
+        preset_configs={"tiny-qwen2": lambda: Qwen2Config(hidden_size=256, intermediate_size=688, num_hidden_layers=2,
+                                                          num_attention_heads=4, num_key_value_heads=2, vocab_size=4096,
+                                                          tie_word_embeddings=True, max_position_embeddings=2048)})
+    PIPELINE_REGISTRY.register(qwen2, allow_override=True)
 
     from ..models.deepseek_v3 import DeepseekV3Config, DeepseekV3Model, DeepseekV3Weights
 

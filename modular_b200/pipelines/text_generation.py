@@ -16,6 +16,8 @@ lands). Decode-only steps of a captured batch size replay as CUDA graphs.
 
 from __future__ import annotations
 
+import gc
+
 import time
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
@@ -158,8 +160,17 @@ class TextGenerationPipeline:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             n0 = self.model.executor.launches()
-            with torch.cuda.graph(g):
-                self.model.forward_packed(*args)
+            # dead cycles (an engine that is no longer referenced, with its CUDA graphs) go now, not while the
+            # stream captures: destroying a graph during a capture invalidates it
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g):
+                    self.model.forward_packed(*args)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self._graph_launches[B] = self.model.executor.launches() - n0
             self._graphs[B] = (g, fixed, off, words)
         torch.cuda.synchronize()

@@ -166,3 +166,45 @@ def test_logprobs_follow_the_sampled_tokens():
         assert e["top"][0][0] == e["token"] and abs(e["top"][0][1] - e["logprob"]) < 1e-6
         assert len(e["top"]) == 4 and all(a[1] >= b[1] for a, b in zip(e["top"], e["top"][1:]))
         assert e["logprob"] <= 0 and math.isfinite(e["logprob"])
+
+
+def test_mistral_checkpoint_is_served_by_the_llama_family(tmp_path):
+    """``MistralForCausalLM`` directories (same layers and tensor names as Llama) load through the registry and give
+    the tokens of the same weights served as a Llama model; a sliding window shorter than the context is refused."""
+    import json
+
+    import pytest
+    from safetensors.torch import save_file
+
+    from modular_b200.models.llama3 import Llama3Config, Llama3Weights, MistralConfig
+    from modular_b200.pipelines.config import PipelineArgs, PipelineConfig
+    from modular_b200.pipelines.context import SamplingParams
+    from modular_b200.pipelines.registry import PIPELINE_REGISTRY
+
+    cfg = MistralConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, vocab_size=300, max_position_embeddings=512)
+    w = Llama3Weights.random_init(cfg, "cpu", torch.float32, seed=3, std=0.08)
+    save_file({k: v.contiguous() for k, v in w.to_hf_state_dict(cfg).items()}, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_hf()))
+
+    def build(path):
+        pc = PipelineConfig.from_args(PipelineArgs.from_flat_kwargs(
+            None, model_path=str(path), devices="cpu", max_length=128, max_batch_size=2, max_batch_input_tokens=64,
+            kv_cache_page_size=16, quantization_encoding="float32"))
+        return PIPELINE_REGISTRY.retrieve(pc)[1]
+
+    sp = SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True)
+    llm = build(tmp_path)
+    assert type(llm.cfg).__name__ == "MistralConfig"
+    got = [list(r.tokens) for r in llm.generate([[5, 6, 7, 8], [9, 10]], sp)]
+    from modular_b200.entrypoints.llm import LLM
+
+    as_llama = Llama3Config(**{k: getattr(cfg, k) for k in Llama3Config.__dataclass_fields__ if k != "architectures"})
+    ref = LLM(as_llama, w, device="cpu", dtype=torch.float32, max_length=128, max_batch_size=2,
+              max_batch_input_tokens=64, page_size=16)
+    assert got == [list(r.tokens) for r in ref.generate([[5, 6, 7, 8], [9, 10]], sp)]
+    bad = tmp_path / "windowed"
+    bad.mkdir()
+    (bad / "config.json").write_text(json.dumps(dict(cfg.to_hf(), sliding_window=64)))
+    with pytest.raises(ValueError):
+        build(bad)

@@ -67,6 +67,42 @@ def test_executor_matches_op_by_op(small):
     assert [r.tokens for r in a] == [r.tokens for r in b]
 
 
+def test_qwen2_projection_bias_on_the_executor():
+    """Qwen2 layers (bias on the fused q / k / v projection): the native executor adds it after the GEMM on the
+    prefill path, the decode-step path and under CUDA graphs, like the op-by-op path does; the bias matters (the
+    tokens change without it)."""
+    from modular_b200.models.llama3 import Qwen2Config
+
+    cfg = Qwen2Config(hidden_size=512, intermediate_size=1408, num_hidden_layers=3, num_attention_heads=8,
+                      num_key_value_heads=2, vocab_size=2048, max_position_embeddings=2048)
+    w = Llama3Weights.random_init(cfg, "cuda", torch.bfloat16, seed=2, std=0.05)
+    assert w.layers[0].qkv_bias is not None
+    for l in w.layers:
+        l.qkv_bias.mul_(20.0)          # std 0.05 would drown in the projections
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (90, 33, 600)]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True)
+    kw = dict(enable_overlap_scheduler=False, device_graph_capture=False, max_batch_input_tokens=1024)
+    a = _mk(cfg, w, **kw).generate(prompts, sp)
+    llm_b = _mk(cfg, w, **kw)
+    llm_b.model.use_executor = False
+    b = llm_b.generate(prompts, sp)
+    assert [r.tokens for r in a] == [r.tokens for r in b]
+    g = _mk(cfg, w, enable_overlap_scheduler=True, device_graph_capture=True, graph_batch_sizes=[4],
+            max_batch_input_tokens=1024).generate(prompts, sp)
+    assert sum(x.tokens[:3] == y.tokens[:3] for x, y in zip(a, g)) >= 2
+    import copy
+
+    w0 = copy.copy(w)
+    w0.layers = [copy.copy(l) for l in w.layers]
+    for l in w0.layers:
+        l.qkv_bias = torch.zeros_like(l.qkv_bias)
+    z = _mk(cfg, w0, **kw).generate(prompts, sp)
+    assert [r.tokens for r in a] != [r.tokens for r in z]
+    torch.cuda.synchronize()
+    ops.check_device_error()
+
+
 @pytest.mark.parametrize("inflight", [False, True])
 def test_overlap_and_graphs_match_sync(small, inflight):
     cfg, w = small
