@@ -146,6 +146,13 @@ class Qwen2Config(Llama3Config):
         cfg.attention_bias = True          # HF's Qwen2 layers always carry the bias; the key is not in its config
         return cfg
 
+    @classmethod
+    def tiny(cls, **kw) -> "Qwen2Config":
+        base = dict(hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, vocab_size=4096, tie_word_embeddings=True, max_position_embeddings=2048)
+        base.update(kw)
+        return cls(**base)
+
     def to_hf(self) -> dict:
         d = super().to_hf()
         d["model_type"] = "qwen2"

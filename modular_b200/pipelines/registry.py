@@ -262,9 +262,7 @@ def _register_builtin() -> None:
         model_class=Llama3Model, default_encoding="bfloat16",
         supported_encodings=("bfloat16", "float32", "float8_e4m3fn"),
         example_repo_ids=("Qwen/Qwen2.5-7B-Instruct", "Qwen/Qwen2.5-72B-Instruct"),
-        preset_configs={"tiny-qwen2": lambda: Qwen2Config(hidden_size=256, intermediate_size=688, num_hidden_layers=2,
-                                                          num_attention_heads=4, num_key_value_heads=2, vocab_size=4096,
-                                                          tie_word_embeddings=True, max_position_embeddings=2048)})
+        preset_configs={"tiny-qwen2": Qwen2Config.tiny})
     PIPELINE_REGISTRY.register(qwen2, allow_override=True)
 
     from ..models.deepseek_v3 import DeepseekV3Config, DeepseekV3Model, DeepseekV3Weights
