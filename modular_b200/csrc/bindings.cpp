@@ -372,6 +372,16 @@ void sample(const Tensor& logits, Tensor& out, const c10::optional<Tensor>& temp
                                static_cast<uint64_t>(step), cur_stream()),
            "sample");
 }
+void qk_norm(Tensor& qkv, const Tensor& q_w, const Tensor& k_w, int n_q, int n_kv, int head_dim, double eps) {
+  need_cuda(qkv, "qkv");
+  TORCH_CHECK(qkv.scalar_type() == at::kBFloat16 && qkv.dim() == 2 && qkv.stride(1) == 1 &&
+                  qkv.size(1) >= static_cast<int64_t>(n_q + n_kv) * head_dim && q_w.numel() == head_dim &&
+                  k_w.numel() == head_dim && q_w.scalar_type() == at::kBFloat16 && k_w.scalar_type() == at::kBFloat16,
+              "qk_norm: bf16 [T, >= (n_q + n_kv) * head_dim] projection and two [head_dim] weights expected");
+  check_rc(mb_qk_norm(qkv.data_ptr(), q_w.data_ptr(), k_w.data_ptr(), qkv.size(0), n_q, n_kv, head_dim, qkv.stride(0),
+                      static_cast<float>(eps), cur_stream()),
+           "qk_norm");
+}
 void apply_penalties(Tensor& logits, const Tensor& tok, const Tensor& cnt, const Tensor& offsets,
                      const c10::optional<Tensor>& freq, const c10::optional<Tensor>& pres,
                      const c10::optional<Tensor>& rep) {
@@ -433,8 +443,18 @@ class PyDecoderExecutor {
   // scales: the four block-scale tensors of an fp8 layer (all or none)
   void add_layer(const Tensor& attn_norm, const Tensor& wqkv, const Tensor& wo,
                  const Tensor& mlp_norm, const Tensor& wgu, const Tensor& wd,
-                 const c10::optional<std::vector<Tensor>>& scales, const c10::optional<Tensor>& qkv_bias) {
+                 const c10::optional<std::vector<Tensor>>& scales, const c10::optional<Tensor>& qkv_bias,
+                 const c10::optional<Tensor>& q_norm, const c10::optional<Tensor>& k_norm) {
     mb::DecoderLayerWeights w;
+    if (q_norm.has_value() && q_norm->defined()) {
+      TORCH_CHECK(k_norm.has_value() && k_norm->defined() && q_norm->scalar_type() == at::kBFloat16 &&
+                      k_norm->scalar_type() == at::kBFloat16 && q_norm->dim() == 1 && k_norm->dim() == 1 &&
+                      q_norm->size(0) == ex.cfg.head_dim && k_norm->size(0) == ex.cfg.head_dim &&
+                      q_norm->is_contiguous() && k_norm->is_contiguous(),
+                  "add_layer: q_norm / k_norm must be contiguous bf16 vectors of head_dim entries");
+      w.q_norm = hold(*q_norm);
+      w.k_norm = hold(*k_norm);
+    }
     if (qkv_bias.has_value() && qkv_bias->defined()) {
       TORCH_CHECK(qkv_bias->scalar_type() == at::kBFloat16 && qkv_bias->dim() == 1 &&
                       qkv_bias->size(0) == wqkv.size(0) && qkv_bias->is_contiguous(),
@@ -838,6 +858,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_attn_split", [](int mode) { mb_set_attn_split(mode); });
   m.def("set_attn_tc", [](int min_tiles) { mb_set_attn_tc(min_tiles); });
   m.def("get_attn_tc", []() { return mb_get_attn_tc(); });
+  m.def("qk_norm", &qk_norm, py::arg("qkv"), py::arg("q_w"), py::arg("k_w"), py::arg("n_q"), py::arg("n_kv"),
+        py::arg("head_dim"), py::arg("eps"));
   m.def("set_gemm_pair_token_major", [](int mask) { mb_set_gemm_pair_token_major(mask); }, py::arg("mask"));
   m.def("set_gemm_pair_persistent", [](bool on) { mb_set_gemm_pair_persistent(on ? 1 : 0); }, py::arg("on"));
   m.def("set_gemm_pair", [](int min_m_plain, int min_m_dual) { mb_set_gemm_pair(min_m_plain, min_m_dual); },
@@ -1206,7 +1228,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_globals", &PyDecoderExecutor::set_globals)
       .def("add_layer", &PyDecoderExecutor::add_layer, py::arg("attn_norm"), py::arg("wqkv"), py::arg("wo"),
            py::arg("mlp_norm"), py::arg("wgu"), py::arg("wd"), py::arg("scales") = py::none(),
-           py::arg("qkv_bias") = py::none())
+           py::arg("qkv_bias") = py::none(), py::arg("q_norm") = py::none(), py::arg("k_norm") = py::none())
       .def("set_fp8_buffers", &PyDecoderExecutor::set_fp8_buffers)
       .def("set_kv_cache", &PyDecoderExecutor::set_kv_cache)
       .def("set_buffers", &PyDecoderExecutor::set_buffers)

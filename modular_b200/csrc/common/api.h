@@ -94,6 +94,9 @@ int mb_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, int 
                float eps, float weight_offset, int multiply_before_cast, cudaStream_t stream);
 int mb_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int rows, int cols,
                    float eps, float weight_offset, int multiply_before_cast, cudaStream_t stream);
+// RMSNorm over head_dim of every query and key head of a fused [T, (n_q + 2 n_kv) * head_dim] projection, in place
+int mb_qk_norm(void* qkv, const void* q_w, const void* k_w, int T, int n_q, int n_kv, int head_dim, int ld, float eps,
+               cudaStream_t stream);
 // x[r, 0:cols] += bias (bf16; rows `ld` elements apart, cols and ld multiples of 8)
 int mb_add_bias(void* x, const void* bias, int rows, int cols, int ld, cudaStream_t stream);
 int mb_silu_mul(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream);

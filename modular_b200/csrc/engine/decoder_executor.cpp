@@ -101,7 +101,7 @@ int DecoderExecutor::forward_dec(const StepInputs& in, cudaStream_t stream) {
     char* kbase = static_cast<char*>(kv.base) + 2 * (static_cast<int64_t>(l) * kv.layer_stride);
     // one launch for the projection, the rotation and the cache store where the kernel takes the shape
     int fused = MB_ERR_SHAPE;
-    if (!c.rope_interleaved && w.wqkv_s == nullptr && w.qkv_bias == nullptr)
+    if (!c.rope_interleaved && w.wqkv_s == nullptr && w.qkv_bias == nullptr && w.q_norm == nullptr)
       fused = mb_gemm_dec_qkv_rope(buf.xn, w.wqkv, T, c.hidden, c.hidden, c.hidden, buf.qkv, qkv_dim, in.positions,
                                    in.slots, cos_sin, kbase, kbase + 2 * kv.kv_stride, c.n_q, c.n_kv, c.head_dim,
                                    c.page_size, kv.page_stride, kv.head_stride, buf.dec_ws, buf.dec_ws_bytes,
@@ -115,6 +115,10 @@ int DecoderExecutor::forward_dec(const StepInputs& in, cudaStream_t stream) {
       MB_TRY(dec(buf.xn, w.wqkv, w.wqkv_s, qkv_dim, c.hidden, 0, buf.qkv, qkv_dim, nullptr));
       if (w.qkv_bias != nullptr) {
         MB_TRY(mb_add_bias(buf.qkv, w.qkv_bias, T, qkv_dim, qkv_dim, stream));
+        launches += 1;
+      }
+      if (w.q_norm != nullptr) {
+        MB_TRY(mb_qk_norm(buf.qkv, w.q_norm, w.k_norm, T, c.n_q, c.n_kv, c.head_dim, qkv_dim, c.eps, stream));
         launches += 1;
       }
       mark("gemm_qkv", stream);
@@ -258,6 +262,10 @@ int DecoderExecutor::forward(const StepInputs& in, cudaStream_t stream) {
     }
     if (w.qkv_bias != nullptr) {
       MB_TRY(mb_add_bias(buf.qkv, w.qkv_bias, T, qkv_dim, qkv_dim, stream));
+      launches += 1;
+    }
+    if (w.q_norm != nullptr) {
+      MB_TRY(mb_qk_norm(buf.qkv, w.q_norm, w.k_norm, T, c.n_q, c.n_kv, c.head_dim, qkv_dim, c.eps, stream));
       launches += 1;
     }
     mark("gemm_qkv", stream);
@@ -449,6 +457,10 @@ int DecoderExecutor::forward_tp(const StepInputs& in, cudaStream_t stream) {
     MB_TRY(gemm_gathered(w.wqkv, w.wqkv_s, buf.qkv, qkv_dim, qkv_dim, 0, gate_on && l > 0));
     if (w.qkv_bias != nullptr) {
       MB_TRY(mb_add_bias(buf.qkv, w.qkv_bias, T, qkv_dim, qkv_dim, stream));
+      launches += 1;
+    }
+    if (w.q_norm != nullptr) {
+      MB_TRY(mb_qk_norm(buf.qkv, w.q_norm, w.k_norm, T, c.n_q, c.n_kv, c.head_dim, qkv_dim, c.eps, stream));
       launches += 1;
     }
     mark("gemm_qkv", stream);

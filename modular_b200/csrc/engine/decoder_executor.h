@@ -30,6 +30,8 @@ struct DecoderLayerWeights {
   const float* wgu_s = nullptr;
   const float* wd_s = nullptr;
   const void* qkv_bias = nullptr;   // [(n_q + 2 n_kv) * head_dim] added to the fused projection (Qwen2), or nullptr
+  const void* q_norm = nullptr;     // [head_dim] weights of the RMSNorm on every query / key head (Qwen3), or nullptr
+  const void* k_norm = nullptr;
 };
 
 struct DecoderConfig {

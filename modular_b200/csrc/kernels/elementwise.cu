@@ -96,6 +96,46 @@ rmsnorm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf
   }
 }
 
+// RMSNorm over head_dim of every query and key head of a fused projection, in place: one warp per (token, head),
+// head_dim / 8 lanes hold 8 values each (head_dim <= 256). Llama rounding order: normalise, round to bf16, multiply
+// by the bf16 weight.
+__global__ void qk_norm_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
+                               int T, int n_q, int n_kv, int hd, int ld, float eps) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const long long unit = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int heads = n_q + n_kv;
+  if (unit >= static_cast<long long>(T) * heads) return;
+  const int t = static_cast<int>(unit / heads), h = static_cast<int>(unit % heads);
+  const bf16* w = h < n_q ? qw : kw;
+  bf16* p = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * hd;   // key heads follow the query heads
+  const bool on = lane * 8 < hd;
+  uint4 a = make_uint4(0u, 0u, 0u, 0u);
+  if (on) a = *reinterpret_cast<const uint4*>(p + lane * 8);
+  bf162* ap = reinterpret_cast<bf162*>(&a);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(ap[i]);
+    ss += f.x * f.x + f.y * f.y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (!on) return;
+  const float inv = rsqrtf(ss / static_cast<float>(hd) + eps);
+  const uint4 wv = *reinterpret_cast<const uint4*>(w + lane * 8);
+  const bf162* wp = reinterpret_cast<const bf162*>(&wv);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(ap[i]);
+    const float2 g = __bfloat1622float2(wp[i]);
+    const float2 n = __bfloat1622float2(__floats2bfloat162_rn(f.x * inv, f.y * inv));
+    ap[i] = __floats2bfloat162_rn(n.x * g.x, n.y * g.y);
+  }
+  *reinterpret_cast<uint4*>(p + lane * 8) = a;
+}
+
 // x[r, c] += bias[c] (bias of a fused projection; rows of `ld` elements, cols a multiple of 8)
 __global__ void add_bias_kernel(bf16* __restrict__ x, const bf16* __restrict__ bias, int rows, int cols, int ld) {
   pdl_wait();
@@ -311,6 +351,18 @@ extern "C" int mb_add_rmsnorm(const void* x, void* residual, const void* w, void
   launch_k(rmsnorm_kernel<true>, dim3(rows), dim3(256), cols * 2, stream, static_cast<const bf16*>(x),
            static_cast<bf16*>(residual), static_cast<const bf16*>(w), static_cast<bf16*>(out), cols, cols, cols,
            eps, weight_offset, mbc);
+  return MB_LAUNCH_OK();
+}
+
+extern "C" int mb_qk_norm(void* qkv, const void* q_w, const void* k_w, int T, int n_q, int n_kv, int head_dim, int ld,
+                          float eps, cudaStream_t stream) {
+  if (T <= 0) return MB_OK;
+  if (head_dim % 8 || head_dim > 256 || ld % 8) return MB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_w) | reinterpret_cast<uintptr_t>(k_w)) & 15)
+    return MB_ERR_ALIGN;
+  const size_t units = static_cast<size_t>(T) * (n_q + n_kv);
+  launch_k(qk_norm_kernel, dim3(blocks_for(units * 32, 256)), dim3(256), 0, stream, static_cast<bf16*>(qkv),
+           static_cast<const bf16*>(q_w), static_cast<const bf16*>(k_w), T, n_q, n_kv, head_dim, ld, eps);
   return MB_LAUNCH_OK();
 }
 

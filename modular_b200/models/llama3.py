@@ -46,6 +46,7 @@ class Llama3Config:
     attention_multiplier: Optional[float] = None
     logits_scaling: float = 1.0
     attention_bias: bool = False      # bias on the query / key / value projections (Qwen2)
+    qk_norm: bool = False             # RMSNorm over head_dim on every query and key head before the rotation (Qwen3)
     architectures: tuple = ("LlamaForCausalLM",)
 
     def __post_init__(self):
@@ -102,11 +103,19 @@ class Llama3Config:
         return cls(**base)
 
 
+def _cap_to_window(cfg, window):
+    """Sliding-window attention equals full attention while the sequence is no longer than the window: serve such
+    checkpoints with the context capped there instead of refusing them."""
+    if window is not None and int(window) > 0:
+        cfg.max_position_embeddings = min(cfg.max_position_embeddings, int(window))
+    return cfg
+
+
 @dataclass
 class MistralConfig(Llama3Config):
-    """Mistral checkpoints (``MistralForCausalLM``) share the Llama layer structure and tensor names. Versions with
-    a sliding attention window shorter than the context are refused: every layer here attends to the whole prefix.
-    Reference: max/python/max/pipelines/architectures/mistral/."""
+    """Mistral checkpoints (``MistralForCausalLM``) share the Llama layer structure and tensor names. Every layer
+    here attends to the whole prefix, so a checkpoint with a sliding attention window is served up to the window
+    length (where the two are the same function). Reference: max/python/max/pipelines/architectures/mistral/."""
 
     rope_theta: float = 1000000.0
     max_position_embeddings: int = 32768
@@ -114,10 +123,7 @@ class MistralConfig(Llama3Config):
 
     @classmethod
     def from_hf(cls, d: dict) -> "MistralConfig":
-        window = d.get("sliding_window")
-        if window is not None and window < d.get("max_position_embeddings", cls.max_position_embeddings):
-            raise ValueError(f"sliding-window attention (window {window}) is not implemented")
-        return super().from_hf(d)
+        return _cap_to_window(super().from_hf(d), d.get("sliding_window"))
 
     def to_hf(self) -> dict:
         d = super().to_hf()
@@ -160,6 +166,67 @@ class Qwen2Config(Llama3Config):
         return d
 
 
+@dataclass
+class Qwen3Config(Llama3Config):
+    """Qwen3 dense models (``Qwen3ForCausalLM``): the Llama layer with an RMSNorm over ``head_dim`` on every query
+    and key head between the projection and the rotary embedding, and an explicit ``head_dim``.
+    Reference: max/python/max/pipelines/architectures/qwen3/."""
+
+    rope_theta: float = 1000000.0
+    rms_norm_eps: float = 1e-6
+    max_position_embeddings: int = 40960
+    qk_norm: bool = True
+    architectures: tuple = ("Qwen3ForCausalLM",)
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "Qwen3Config":
+        if d.get("use_sliding_window"):
+            raise ValueError("sliding-window attention is not implemented")
+        cfg = super().from_hf(d)
+        cfg.qk_norm = True
+        cfg.attention_bias = bool(d.get("attention_bias", False))
+        return cfg
+
+    @classmethod
+    def tiny(cls, **kw) -> "Qwen3Config":
+        base = dict(hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, head_dim=64, vocab_size=4096, tie_word_embeddings=True,
+                    max_position_embeddings=2048)
+        base.update(kw)
+        return cls(**base)
+
+    def to_hf(self) -> dict:
+        d = super().to_hf()
+        d["model_type"] = "qwen3"
+        d["use_sliding_window"] = False
+        return d
+
+
+@dataclass
+class Phi3Config(Llama3Config):
+    """Phi-3 / Phi-3.5 mini (``Phi3ForCausalLM``): the Llama layer with the q / k / v and the gate / up projections
+    already fused in the checkpoint (``qkv_proj``, ``gate_up_proj``). Scaled rotary variants (``longrope``) and
+    partial rotary embeddings are refused. Reference: max/python/max/pipelines/architectures/phi3/."""
+
+    rope_theta: float = 10000.0
+    max_position_embeddings: int = 4096
+    architectures: tuple = ("Phi3ForCausalLM",)
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "Phi3Config":
+        if d.get("rope_scaling"):
+            raise ValueError(f"rotary scaling {d['rope_scaling'].get('type', d['rope_scaling'])!r} is not implemented")
+        if float(d.get("partial_rotary_factor", 1.0)) != 1.0:
+            raise ValueError("partial rotary embeddings are not implemented")
+        return _cap_to_window(super().from_hf(d), d.get("sliding_window"))
+
+    def to_hf(self) -> dict:
+        d = super().to_hf()
+        d["model_type"] = "phi3"
+        d["sliding_window"] = None
+        return d
+
+
 
 @dataclass
 class LayerWeights:
@@ -176,6 +243,8 @@ class LayerWeights:
     wgu_s: Optional[torch.Tensor] = None
     wd_s: Optional[torch.Tensor] = None
     qkv_bias: Optional[torch.Tensor] = None      # [q; k; v] projection bias (Qwen2), in the activation dtype
+    q_norm: Optional[torch.Tensor] = None        # [head_dim] weights of the per-head query / key RMSNorm (Qwen3)
+    k_norm: Optional[torch.Tensor] = None
 
     @property
     def is_fp8(self) -> bool:
@@ -215,7 +284,9 @@ class Llama3Weights:
                 mlp_norm=torch.ones(cfg.hidden_size, dtype=dtype, device=dev),
                 wgu=rnd(2 * cfg.intermediate_size, cfg.hidden_size),
                 wd=rnd(cfg.hidden_size, cfg.intermediate_size),
-                qkv_bias=rnd(cfg.q_dim + 2 * cfg.kv_dim) if cfg.attention_bias else None))
+                qkv_bias=rnd(cfg.q_dim + 2 * cfg.kv_dim) if cfg.attention_bias else None,
+                q_norm=torch.ones(cfg.head_dim, dtype=dtype, device=dev) if cfg.qk_norm else None,
+                k_norm=torch.ones(cfg.head_dim, dtype=dtype, device=dev) if cfg.qk_norm else None))
         final_norm = torch.ones(cfg.hidden_size, dtype=dtype, device=dev)
         lm_head = embed if cfg.tie_word_embeddings else rnd(cfg.vocab_size, cfg.hidden_size)
         return cls(embed, layers, final_norm, lm_head)
@@ -243,7 +314,9 @@ class Llama3Weights:
                              rnd(g_rank, cfg.hidden_size, local.q_dim), ones(),
                              rnd(g_rank, 2 * local.intermediate_size, cfg.hidden_size),
                              rnd(g_rank, cfg.hidden_size, local.intermediate_size),
-                             qkv_bias=rnd(g_rank, local.q_dim + 2 * local.kv_dim) if cfg.attention_bias else None)
+                             qkv_bias=rnd(g_rank, local.q_dim + 2 * local.kv_dim) if cfg.attention_bias else None,
+                             q_norm=torch.ones(cfg.head_dim, dtype=dtype, device=dev) if cfg.qk_norm else None,
+                             k_norm=torch.ones(cfg.head_dim, dtype=dtype, device=dev) if cfg.qk_norm else None)
             if fp8:
                 l = cls(embed, [l], ones(), embed).quantize_fp8().layers[0]
             layers.append(l)
@@ -264,7 +337,8 @@ class Llama3Weights:
                 layers.append(l)
                 continue
             (a, a_s), (b, b_s), (c_, c_s), (d, d_s) = q(l.wqkv), q(l.wo), q(l.wgu), q(l.wd)
-            layers.append(LayerWeights(l.attn_norm, a, b, l.mlp_norm, c_, d, a_s, b_s, c_s, d_s, l.qkv_bias))
+            layers.append(LayerWeights(l.attn_norm, a, b, l.mlp_norm, c_, d, a_s, b_s, c_s, d_s, l.qkv_bias,
+                                       l.q_norm, l.k_norm))
         return Llama3Weights(self.embed, layers, self.final_norm, self.lm_head)
 
     def dequantize(self, dtype=torch.bfloat16) -> "Llama3Weights":
@@ -272,14 +346,15 @@ class Llama3Weights:
         activation quantisation)."""
         d = lambda w, s: ops.reference.dequant_fp8_weight_block128(w, s).to(dtype)
         layers = [LayerWeights(l.attn_norm, d(l.wqkv, l.wqkv_s), d(l.wo, l.wo_s), l.mlp_norm, d(l.wgu, l.wgu_s),
-                               d(l.wd, l.wd_s), qkv_bias=l.qkv_bias) if l.is_fp8 else l for l in self.layers]
+                               d(l.wd, l.wd_s), qkv_bias=l.qkv_bias, q_norm=l.q_norm, k_norm=l.k_norm)
+                  if l.is_fp8 else l for l in self.layers]
         return Llama3Weights(self.embed, layers, self.final_norm, self.lm_head)
 
     @classmethod
     def from_state_dict(cls, cfg: Llama3Config, sd: dict, device="cpu", dtype=torch.bfloat16, keep_fp8: bool = True):
         """``keep_fp8``: block-scaled fp8 projections (``<name>`` e4m3 + ``<name>_scale_inv``) stay fp8 when the
         fused row blocks line up with the 128-row scale blocks; otherwise they are expanded to ``dtype``."""
-        sd = adapt_hf_state_dict(sd)
+        sd = _split_fused_projections(cfg, adapt_hf_state_dict(sd))
         dev = torch.device(device)
         fp8_names = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
                      "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")
@@ -315,6 +390,9 @@ class Llama3Weights:
                 return None
             return torch.cat([sd[n].float() for n in names]).to(device=dev, dtype=dtype).contiguous()
 
+        def opt(name):
+            return get(name) if name in sd else None
+
         layers = []
         for i in range(cfg.num_hidden_layers):
             p = f"layers.{i}."
@@ -325,7 +403,8 @@ class Llama3Weights:
                 d, d_s = fp8_cat(p, ("mlp.down_proj",))
                 layers.append(LayerWeights(get(p + "input_layernorm.weight"), a, b,
                                            get(p + "post_attention_layernorm.weight"), c_, d, a_s, b_s, c_s, d_s,
-                                           bias(p)))
+                                           bias(p), opt(p + "self_attn.q_norm.weight"),
+                                           opt(p + "self_attn.k_norm.weight")))
                 continue
             wqkv = torch.cat([raw(p + "self_attn.q_proj.weight"), raw(p + "self_attn.k_proj.weight"),
                               raw(p + "self_attn.v_proj.weight")], dim=0)
@@ -336,7 +415,8 @@ class Llama3Weights:
                 wo=get(p + "self_attn.o_proj.weight"),
                 mlp_norm=get(p + "post_attention_layernorm.weight"),
                 wgu=wgu.to(device=dev, dtype=dtype).contiguous(),
-                wd=get(p + "mlp.down_proj.weight"), qkv_bias=bias(p)))
+                wd=get(p + "mlp.down_proj.weight"), qkv_bias=bias(p),
+                q_norm=opt(p + "self_attn.q_norm.weight"), k_norm=opt(p + "self_attn.k_norm.weight")))
         embed = get("embed_tokens.weight")
         lm_head = embed if (cfg.tie_word_embeddings or "lm_head.weight" not in sd) else get("lm_head.weight")
         return cls(embed, layers, get("norm.weight"), lm_head)
@@ -348,6 +428,8 @@ class Llama3Weights:
             sd["lm_head.weight"] = self.lm_head
         for i, l in enumerate(self.layers):
             p = f"model.layers.{i}."
+            if l.q_norm is not None:
+                sd.update({p + "self_attn.q_norm.weight": l.q_norm, p + "self_attn.k_norm.weight": l.k_norm})
             if l.qkv_bias is not None:
                 bq, bk, bv = torch.split(l.qkv_bias, [cfg.q_dim, cfg.kv_dim, cfg.kv_dim])
                 sd.update({p + "self_attn.q_proj.bias": bq, p + "self_attn.k_proj.bias": bk,
@@ -376,6 +458,26 @@ class Llama3Weights:
                        p + "mlp.gate_proj.weight": g, p + "mlp.up_proj.weight": u,
                        p + "mlp.down_proj.weight": l.wd})
         return {k: v.contiguous() for k, v in sd.items()}
+
+
+def _split_fused_projections(cfg, sd: dict) -> dict:
+    """Checkpoints that store ``qkv_proj`` / ``gate_up_proj`` (Phi-3) -> the separate tensors the loader expects
+    (views, no copies)."""
+    if not any(k.endswith("self_attn.qkv_proj.weight") for k in sd):
+        return sd
+    out = {}
+    for k, v in sd.items():
+        if k.endswith("self_attn.qkv_proj.weight"):
+            p = k[: -len("qkv_proj.weight")]
+            q, kk, vv = torch.split(v, [cfg.q_dim, cfg.kv_dim, cfg.kv_dim], dim=0)
+            out[p + "q_proj.weight"], out[p + "k_proj.weight"], out[p + "v_proj.weight"] = q, kk, vv
+        elif k.endswith("mlp.gate_up_proj.weight"):
+            p = k[: -len("gate_up_proj.weight")]
+            g, u = torch.split(v, cfg.intermediate_size, dim=0)
+            out[p + "gate_proj.weight"], out[p + "up_proj.weight"] = g, u
+        else:
+            out[k] = v
+    return out
 
 
 def adapt_hf_state_dict(sd: dict) -> dict:
@@ -438,7 +540,7 @@ class Llama3Model:
         if self.is_fp8 and not all(l.is_fp8 for l in self.w.layers):
             raise ValueError("mixed fp8 / bf16 layers are not supported by the executor")
         for l in self.w.layers:
-            ex.add_layer(l.attn_norm, l.wqkv, l.wo, l.mlp_norm, l.wgu, l.wd, l.scales(), l.qkv_bias)
+            ex.add_layer(l.attn_norm, l.wqkv, l.wo, l.mlp_norm, l.wgu, l.wd, l.scales(), l.qkv_bias, l.q_norm, l.k_norm)
         ex.set_kv_cache(self.kv)
         T, B = self.max_tokens, self.max_seqs
         mk = lambda *s, dtype=dt: torch.empty(*s, dtype=dtype, device=dev)
@@ -549,6 +651,7 @@ class Llama3Model:
                 qkv = ops.linear_fp8(x, l.wqkv, l.wqkv_s)
                 if l.qkv_bias is not None:
                     qkv += l.qkv_bias
+                self._qk_norm(qkv, l)
                 ops.rope_kv_store(qkv, positions, slots, self.cos_sin, kc, vc, c.num_attention_heads,
                                   c.num_key_value_heads, c.head_dim, False)
                 a = ops.paged_attention(qkv, kc, vc, block_table, q_start, q_len, kv_len, c.num_attention_heads,
@@ -561,6 +664,7 @@ class Llama3Model:
             qkv = ops.linear(x, l.wqkv)
             if l.qkv_bias is not None:
                 qkv += l.qkv_bias
+            self._qk_norm(qkv, l)
             ops.rope_kv_store(qkv, positions, slots, self.cos_sin, kc, vc, c.num_attention_heads,
                               c.num_key_value_heads, c.head_dim, False)
             a = ops.paged_attention(qkv, kc, vc, block_table, q_start, q_len, kv_len,
@@ -574,6 +678,13 @@ class Llama3Model:
                 act = ops.silu_mul(ops.linear(x, l.wgu))
             h = ops.linear(act, l.wd, residual=h)
         return h
+
+    def _qk_norm(self, qkv: torch.Tensor, l) -> None:
+        """Per-head RMSNorm of the query and key heads of a fused projection, in place (Qwen3)."""
+        if l.q_norm is None:
+            return
+        c = self.cfg
+        ops.qk_norm(qkv, l.q_norm, l.k_norm, c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rms_norm_eps)
 
     def _forward_hidden_lora(self, tokens, positions, slots, block_table, q_start, q_len, kv_len, plan, kv, lora):
         """Same network with LoRA deltas on the seven projection modules (separate gate/up products so the
@@ -596,6 +707,7 @@ class Llama3Model:
             qkv = ops.linear(x, l.wqkv)
             if l.qkv_bias is not None:
                 qkv += l.qkv_bias
+            self._qk_norm(qkv, l)
             add(qkv, lora.delta(li, "q_proj", x), 0, c.q_dim)
             add(qkv, lora.delta(li, "k_proj", x), c.q_dim, c.q_dim + c.kv_dim)
             add(qkv, lora.delta(li, "v_proj", x), c.q_dim + c.kv_dim, c.q_dim + 2 * c.kv_dim)

@@ -216,6 +216,19 @@ def rms_norm(x, w, eps, weight_offset=0.0, multiply_before_cast=False, out=None)
     return out
 
 
+def qk_norm(qkv, q_w, k_w, n_q: int, n_kv: int, head_dim: int, eps: float):
+    """RMSNorm over ``head_dim`` of every query and key head of a fused [T, (n_q + 2 n_kv) * head_dim] projection,
+    in place (value heads untouched): normalise in fp32, round to the activation dtype, multiply by the weight."""
+    if not qkv.is_cuda or qkv.dtype != torch.bfloat16:
+        T = qkv.shape[0]
+        for w, lo, n in ((q_w, 0, n_q), (k_w, n_q * head_dim, n_kv)):
+            part = qkv[:, lo: lo + n * head_dim].reshape(T * n, head_dim)
+            qkv[:, lo: lo + n * head_dim] = ref.rms_norm(part, w, eps).reshape(T, n * head_dim)
+        return qkv
+    _lib().qk_norm(qkv, q_w, k_w, n_q, n_kv, head_dim, float(eps))
+    return qkv
+
+
 def add_rms_norm(x, residual, w, eps, weight_offset=0.0, multiply_before_cast=False, out=None):
     """residual <- x + residual (in place); returns (rms_norm(residual), residual)."""
     if not x.is_cuda or x.dtype != torch.bfloat16:

@@ -225,7 +225,7 @@ def _shard_fp8_layer(cfg, l, rank: int, world: int):
     wgu_s = torch.cat([p[1] for p in gu], 0).contiguous()
     wd, wd_s = cols(l.wd, l.wd_s, rank * Il, Il)
     return LayerWeights(l.attn_norm, wqkv, f8(wo), l.mlp_norm, wgu, f8(wd), wqkv_s, wo_s.contiguous(), wgu_s,
-                        wd_s.contiguous(), _shard_qkv_bias(cfg, l.qkv_bias, rank, world))
+                        wd_s.contiguous(), _shard_qkv_bias(cfg, l.qkv_bias, rank, world), l.q_norm, l.k_norm)
 
 
 def _shard_qkv_bias(cfg, bias, rank: int, world: int):
@@ -260,7 +260,8 @@ def shard_llama_weights(cfg, weights, rank: int, world: int):
         wgu = torch.cat([g[rank * Il:(rank + 1) * Il], u[rank * Il:(rank + 1) * Il]], dim=0).contiguous()
         wd = l.wd[:, rank * Il:(rank + 1) * Il].contiguous()
         layers.append(LayerWeights(l.attn_norm, wqkv, wo, l.mlp_norm, wgu, wd,
-                                   qkv_bias=_shard_qkv_bias(cfg, l.qkv_bias, rank, world)))
+                                   qkv_bias=_shard_qkv_bias(cfg, l.qkv_bias, rank, world), q_norm=l.q_norm,
+                                   k_norm=l.k_norm))
     Vl = cfg.vocab_size // world
     lm_head = weights.lm_head[rank * Vl:(rank + 1) * Vl].contiguous()
     return Llama3Weights(weights.embed, layers, weights.final_norm, lm_head)

@@ -264,6 +264,26 @@ def _register_builtin() -> None:
         example_repo_ids=("Qwen/Qwen2.5-7B-Instruct", "Qwen/Qwen2.5-72B-Instruct"),
         preset_configs={"tiny-qwen2": Qwen2Config.tiny})
     PIPELINE_REGISTRY.register(qwen2, allow_override=True)
+    from ..models.llama3 import Qwen3Config
+
+    # the Llama layer with an RMSNorm on every query and key head before the rotation
+    qwen3 = SupportedArchitecture(
+        name="Qwen3ForCausalLM", config_class=Qwen3Config, weights_class=Llama3Weights,
+        model_class=Llama3Model, default_encoding="bfloat16",
+        supported_encodings=("bfloat16", "float32", "float8_e4m3fn"),
+        example_repo_ids=("Qwen/Qwen3-8B", "Qwen/Qwen3-32B"),
+        preset_configs={"tiny-qwen3": Qwen3Config.tiny})
+    PIPELINE_REGISTRY.register(qwen3, allow_override=True)
+    from ..models.llama3 import Phi3Config
+
+    # the Llama layer with the projections already fused in the checkpoint
+    phi3 = SupportedArchitecture(
+        name="Phi3ForCausalLM", config_class=Phi3Config, weights_class=Llama3Weights,
+        model_class=Llama3Model, default_encoding="bfloat16",
+        supported_encodings=("bfloat16", "float32", "float8_e4m3fn"),
+        example_repo_ids=("microsoft/Phi-3-mini-4k-instruct", "microsoft/Phi-3.5-mini-instruct"),
+        preset_configs={})
+    PIPELINE_REGISTRY.register(phi3, allow_override=True)
 
     from ..models.deepseek_v3 import DeepseekV3Config, DeepseekV3Model, DeepseekV3Weights
 

@@ -103,6 +103,44 @@ def test_qwen2_projection_bias_on_the_executor():
     ops.check_device_error()
 
 
+def test_qwen3_query_key_norm_on_the_executor():
+    """Qwen3 layers (RMSNorm over head_dim on every query and key head before the rotation): the kernel equals the
+    fp32 reference, and the native executor (prefill path, decode-step path) gives the tokens of the op-by-op path."""
+    from modular_b200.models.llama3 import Qwen3Config
+    from modular_b200.ops import reference as ref
+
+    torch.manual_seed(3)
+    T, n_q, n_kv, hd = 37, 8, 2, 128
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, device="cuda", dtype=torch.bfloat16)
+    qw = (1 + 0.2 * torch.randn(hd, device="cuda")).to(torch.bfloat16)
+    kw_ = (1 + 0.2 * torch.randn(hd, device="cuda")).to(torch.bfloat16)
+    want = qkv.clone()
+    for w_, lo, n in ((qw, 0, n_q), (kw_, n_q * hd, n_kv)):
+        part = want[:, lo: lo + n * hd].reshape(T * n, hd)
+        want[:, lo: lo + n * hd] = ref.rms_norm(part, w_, 1e-6).reshape(T, n * hd)
+    got = ops.qk_norm(qkv.clone(), qw, kw_, n_q, n_kv, hd, 1e-6)
+    assert torch.equal(got[:, (n_q + n_kv) * hd:], qkv[:, (n_q + n_kv) * hd:])          # values untouched
+    assert (got.float() - want.float()).abs().max() <= 0.02 * want.float().abs().max()
+
+    cfg = Qwen3Config(hidden_size=512, intermediate_size=1408, num_hidden_layers=3, num_attention_heads=8,
+                      num_key_value_heads=2, head_dim=128, vocab_size=2048, max_position_embeddings=2048)
+    w = Llama3Weights.random_init(cfg, "cuda", torch.bfloat16, seed=4, std=0.05)
+    for l in w.layers:
+        l.q_norm.copy_((1 + 0.3 * torch.randn(128, device="cuda")).to(torch.bfloat16))
+        l.k_norm.copy_((1 + 0.3 * torch.randn(128, device="cuda")).to(torch.bfloat16))
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (90, 33, 600)]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True)
+    kw = dict(enable_overlap_scheduler=False, device_graph_capture=False, max_batch_input_tokens=1024)
+    a = _mk(cfg, w, **kw).generate(prompts, sp)
+    llm_b = _mk(cfg, w, **kw)
+    llm_b.model.use_executor = False
+    b = llm_b.generate(prompts, sp)
+    assert [r.tokens for r in a] == [r.tokens for r in b]
+    torch.cuda.synchronize()
+    ops.check_device_error()
+
+
 @pytest.mark.parametrize("inflight", [False, True])
 def test_overlap_and_graphs_match_sync(small, inflight):
     cfg, w = small

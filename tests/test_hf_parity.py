@@ -1,5 +1,7 @@
 """Golden check against Hugging Face transformers on CPU: a randomly initialised HF model is saved as a checkpoint
-directory, served by this engine through the registry, and both must produce the same greedy tokens. Covers the Llama layer and its variants: Mistral (same tensors), Qwen2 (projection bias)."""
+directory, served by this engine through the registry, and both must produce the same greedy tokens. Covers the Llama layer and its variants: Mistral (same tensors), Qwen2 (projection bias), Qwen3 (RMSNorm on
+every query and key head), Phi-3 (projections fused
+in the checkpoint)."""
 
 import json
 
@@ -33,6 +35,10 @@ CASES = {
     "llama": ("LlamaConfig", "LlamaForCausalLM", dict(rope_theta=500000.0, rms_norm_eps=1e-5)),
     "mistral": ("MistralConfig", "MistralForCausalLM", dict(rope_theta=1e6, rms_norm_eps=1e-5, sliding_window=None)),
     "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", dict(rope_theta=1e6, rms_norm_eps=1e-6, use_sliding_window=False)),
+    "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(rope_theta=1e6, rms_norm_eps=1e-6, use_sliding_window=False,
+                                                      head_dim=32)),
+    "phi3": ("Phi3Config", "Phi3ForCausalLM", dict(rope_theta=10000.0, rms_norm_eps=1e-5, sliding_window=None,
+                                                   pad_token_id=0)),
 }
 
 
