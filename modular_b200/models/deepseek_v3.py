@@ -152,6 +152,9 @@ class DeepseekV3Config:
 
     @classmethod
     def from_hf(cls, d: dict) -> "DeepseekV3Config":
+        from ..pipelines.weights import normalize_hf_rope
+
+        d = normalize_hf_rope(d)
         names = cls.__dataclass_fields__.keys()
         return cls(**{k: v for k, v in d.items() if k in names})
 
@@ -323,6 +326,11 @@ class DeepseekV3Weights:
                         return Fp8ExpertWeights(torch.stack([torch.cat([p.q for p in ps]) for ps in parts]),
                                                 torch.stack([torch.cat([p.scale for p in ps]) for ps in parts]))
                     gu, dn = stack8(("gate_proj", "up_proj")), stack8(("down_proj",))
+                elif m + "experts.gate_up_proj" in sd:
+                    # all experts of a layer in two tensors ([E, 2 I, H] gate rows then up rows, [E, H, I]): the
+                    # layout transformers >= 5 keeps in memory and writes back
+                    gu = sd[m + "experts.gate_up_proj"][e_begin:e_end].to(dtype).to(device).contiguous()
+                    dn = sd[m + "experts.down_proj"][e_begin:e_end].to(dtype).to(device).contiguous()
                 else:
                     gu = torch.stack([cat(W(f"{m}experts.{e}.gate_proj", False), W(f"{m}experts.{e}.up_proj", False))
                                       for e in range(e_begin, e_end)])

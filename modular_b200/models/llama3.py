@@ -55,6 +55,9 @@ class Llama3Config:
 
     @classmethod
     def from_hf(cls, d: dict) -> "Llama3Config":
+        from ..pipelines.weights import normalize_hf_rope
+
+        d = normalize_hf_rope(d)
         keys = set(cls.__dataclass_fields__)
         kw = {k: v for k, v in d.items() if k in keys}
         if "architectures" in kw:

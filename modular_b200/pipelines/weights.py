@@ -78,6 +78,22 @@ def parse_quant_config(hf_config: dict) -> Optional[QuantConfig]:
     raise ValueError(f"unsupported quantisation method {method!r}")
 
 
+def normalize_hf_rope(d: dict) -> dict:
+    """``config.json`` written by transformers >= 5 carries the rotary settings as ``rope_parameters``
+    (``{"rope_type": ..., "rope_theta": ..., <scaling keys>}``) instead of ``rope_theta`` + ``rope_scaling``: returns
+    a copy with the older pair filled in (``rope_scaling`` None for the default type)."""
+    rp = d.get("rope_parameters")
+    if not isinstance(rp, dict):
+        return d
+    d = dict(d)
+    if "rope_theta" in rp and d.get("rope_theta") is None:
+        d["rope_theta"] = rp["rope_theta"]
+    if "rope_scaling" not in d:
+        kind = rp.get("rope_type", rp.get("type", "default"))
+        d["rope_scaling"] = None if kind in (None, "default") else {k: v for k, v in rp.items() if k != "rope_theta"}
+    return d
+
+
 def load_hf_config(model_path: str) -> dict:
     g = _gguf_file(model_path)
     if g is not None and not (os.path.isdir(model_path) and (Path(model_path) / "config.json").exists()):

@@ -31,6 +31,17 @@ def _engine(path):
     return PIPELINE_REGISTRY.retrieve(pc)[1]
 
 
+def _assert_logits_close(llm, hf, prompt, tol=2e-3):
+    """Logits of every prompt position against transformers (the engine's model on a private cache)."""
+    from modular_b200.pipelines.speculative import _SeqCache
+
+    ours = _SeqCache(llm.model, 64).step(prompt, all_logits=True).float().cpu()
+    with torch.no_grad():
+        want = hf(torch.tensor([prompt])).logits[0].float()
+    err = (ours - want).abs().max().item()
+    assert err <= tol * max(1.0, want.abs().max().item()), err
+
+
 CASES = {
     "llama": ("LlamaConfig", "LlamaForCausalLM", dict(rope_theta=500000.0, rms_norm_eps=1e-5)),
     "mistral": ("MistralConfig", "MistralForCausalLM", dict(rope_theta=1e6, rms_norm_eps=1e-5, sliding_window=None)),
@@ -70,3 +81,44 @@ def test_greedy_tokens_match_transformers(tmp_path, family, tied):
             want = hf.generate(torch.tensor([prompt]), max_new_tokens=n_new, do_sample=False, pad_token_id=0,
                                eos_token_id=None)[0, len(prompt):].tolist()
         assert list(rec.tokens) == want, (family, tied)
+    _assert_logits_close(llm, hf, prompts[0])
+
+
+@pytest.mark.parametrize("q_lora,yarn", [(96, False), (None, False), (96, True)])
+def test_deepseek_v3_greedy_tokens_match_transformers(tmp_path, q_lora, yarn):
+    """DeepSeek-V3 (multi-head latent attention in the absorbed form over the latent cache, interleaved rotary
+    convention of the checkpoint, group-limited sigmoid routing with the correction bias, shared experts, a dense
+    first layer): same greedy tokens as ``DeepseekV3ForCausalLM``. The expert weights arrive in the two-tensor layout
+    transformers keeps in memory (``experts.gate_up_proj`` / ``experts.down_proj``)."""
+    from modular_b200.pipelines.context import SamplingParams
+
+    torch.manual_seed(11)
+    hf_cfg = transformers.DeepseekV3Config(
+        vocab_size=512, hidden_size=128, intermediate_size=256, moe_intermediate_size=64, num_hidden_layers=3,
+        num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1, n_routed_experts=8,
+        routed_scaling_factor=2.5, kv_lora_rank=64, q_lora_rank=q_lora, qk_rope_head_dim=16, v_head_dim=32,
+        qk_nope_head_dim=32, n_group=2, topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1,
+        norm_topk_prob=True, max_position_embeddings=512, rope_theta=10000.0,
+        rope_scaling={"rope_type": "yarn", "type": "yarn", "factor": 40.0, "beta_fast": 32, "beta_slow": 1,
+                      "mscale": 1.0, "mscale_all_dim": 1.0, "original_max_position_embeddings": 16} if yarn else None,
+        tie_word_embeddings=False)
+    hf = transformers.DeepseekV3ForCausalLM(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+        for n, b in hf.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.add_(torch.randn_like(b) * 0.1)
+    d = hf_cfg.to_dict()
+    d["architectures"] = ["DeepseekV3ForCausalLM"]
+    _save(hf, d, tmp_path)
+    llm = _engine(tmp_path)
+    prompts = [[5, 6, 7, 8, 9, 10, 11], [200, 3, 17], [41, 42, 43, 44, 45, 46, 47, 48, 49, 50, 51, 52]]
+    recs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=10, ignore_eos=True))
+    for prompt, rec in zip(prompts, recs):
+        with torch.no_grad():
+            want = hf.generate(torch.tensor([prompt]), max_new_tokens=10, do_sample=False, pad_token_id=0,
+                               eos_token_id=None)[0, len(prompt):].tolist()
+        assert list(rec.tokens) == want
+    _assert_logits_close(llm, hf, prompts[2] * 3)      # 36 positions: past the original context of the yarn case
