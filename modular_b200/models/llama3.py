@@ -47,6 +47,13 @@ class Llama3Config:
     logits_scaling: float = 1.0
     attention_bias: bool = False      # bias on the query / key / value projections (Qwen2)
     qk_norm: bool = False             # RMSNorm over head_dim on every query and key head before the rotation (Qwen3)
+    # mixture-of-experts feed-forward (Mixtral, Qwen3-MoE): 0 experts = dense SwiGLU MLP in every layer
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    decoder_sparse_step: int = 1
+    mlp_only_layers: tuple = ()
     architectures: tuple = ("LlamaForCausalLM",)
 
     def __post_init__(self):
@@ -62,11 +69,14 @@ class Llama3Config:
         kw = {k: v for k, v in d.items() if k in keys}
         if "architectures" in kw:
             kw["architectures"] = tuple(kw["architectures"])
+        if "mlp_only_layers" in kw:
+            kw["mlp_only_layers"] = tuple(kw["mlp_only_layers"] or ())
         return cls(**kw)
 
     def to_hf(self) -> dict:
         d = {k: getattr(self, k) for k in self.__dataclass_fields__}
         d["architectures"] = list(self.architectures)
+        d["mlp_only_layers"] = list(self.mlp_only_layers)
         d["model_type"] = "llama"
         return d
 
@@ -78,11 +88,25 @@ class Llama3Config:
     def kv_dim(self) -> int:
         return self.num_key_value_heads * self.head_dim
 
+    def is_moe_layer(self, i: int) -> bool:
+        return (self.num_experts > 0 and i not in self.mlp_only_layers
+                and (i + 1) % max(1, self.decoder_sparse_step) == 0)
+
+    def moe_config(self):
+        from ..nn.moe import MoEConfig
+
+        return MoEConfig(self.hidden_size, self.moe_intermediate_size or self.intermediate_size, self.num_experts,
+                         self.num_experts_per_tok, norm_topk_prob=self.norm_topk_prob, scoring_func="softmax")
+
     def param_count(self) -> int:
-        per_layer = (self.hidden_size * (self.q_dim + 2 * self.kv_dim) + self.q_dim * self.hidden_size
-                     + 3 * self.hidden_size * self.intermediate_size + 2 * self.hidden_size)
+        attn = self.hidden_size * (self.q_dim + 2 * self.kv_dim) + self.q_dim * self.hidden_size + 2 * self.hidden_size
+        dense = 3 * self.hidden_size * self.intermediate_size
+        moe = self.num_experts * (3 * self.hidden_size * (self.moe_intermediate_size or self.intermediate_size)
+                                  + self.hidden_size)
+        n_moe = sum(self.is_moe_layer(i) for i in range(self.num_hidden_layers))
         emb = self.vocab_size * self.hidden_size
-        return self.num_hidden_layers * per_layer + emb * (1 if self.tie_word_embeddings else 2) + self.hidden_size
+        return (self.num_hidden_layers * attn + n_moe * moe + (self.num_hidden_layers - n_moe) * dense
+                + emb * (1 if self.tie_word_embeddings else 2) + self.hidden_size)
 
     # named presets used by benchmarks and tests
     @classmethod
@@ -206,6 +230,74 @@ class Qwen3Config(Llama3Config):
 
 
 @dataclass
+class MixtralConfig(Llama3Config):
+    """Mixtral (``MixtralForCausalLM``): Llama attention with a mixture-of-experts feed-forward in every layer -
+    softmax over all experts, top-k, weights renormalised. ``intermediate_size`` is the size of one expert.
+    Reference: max/python/max/pipelines/architectures/mixtral/."""
+
+    rope_theta: float = 1000000.0
+    max_position_embeddings: int = 32768
+    num_experts: int = 8
+    num_experts_per_tok: int = 2
+    architectures: tuple = ("MixtralForCausalLM",)
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "MixtralConfig":
+        d = dict(d)
+        d["num_experts"] = d.get("num_local_experts", d.get("num_experts", 8))
+        cfg = _cap_to_window(super().from_hf(d), d.get("sliding_window"))
+        cfg.moe_intermediate_size = cfg.intermediate_size
+        cfg.norm_topk_prob = True
+        return cfg
+
+    def __post_init__(self):
+        super().__post_init__()
+        if not self.moe_intermediate_size:
+            self.moe_intermediate_size = self.intermediate_size
+
+    @classmethod
+    def tiny(cls, **kw) -> "MixtralConfig":
+        base = dict(hidden_size=256, intermediate_size=384, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, vocab_size=4096, num_experts=4, num_experts_per_tok=2,
+                    max_position_embeddings=2048)
+        base.update(kw)
+        return cls(**base)
+
+    def to_hf(self) -> dict:
+        d = super().to_hf()
+        d["model_type"] = "mixtral"
+        d["num_local_experts"] = self.num_experts
+        d["sliding_window"] = None
+        return d
+
+
+@dataclass
+class Qwen3MoeConfig(Qwen3Config):
+    """Qwen3 mixture-of-experts models (``Qwen3MoeForCausalLM``): Qwen3 attention; layers selected by
+    ``decoder_sparse_step`` / ``mlp_only_layers`` route to ``num_experts`` experts of ``moe_intermediate_size``
+    (softmax, top-k, optional renormalisation), the others keep the dense MLP.
+    Reference: max/python/max/pipelines/architectures/qwen3_moe/."""
+
+    num_experts: int = 128
+    num_experts_per_tok: int = 8
+    moe_intermediate_size: int = 768
+    architectures: tuple = ("Qwen3MoeForCausalLM",)
+
+    @classmethod
+    def tiny(cls, **kw) -> "Qwen3MoeConfig":
+        base = dict(hidden_size=256, intermediate_size=512, moe_intermediate_size=128, num_hidden_layers=2,
+                    num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=4096, num_experts=8,
+                    num_experts_per_tok=2, tie_word_embeddings=False, max_position_embeddings=2048)
+        base.update(kw)
+        return cls(**base)
+
+    def to_hf(self) -> dict:
+        d = super().to_hf()
+        d["model_type"] = "qwen3_moe"
+        return d
+
+
+@dataclass
 class Phi3Config(Llama3Config):
     """Phi-3 / Phi-3.5 mini (``Phi3ForCausalLM``): the Llama layer with the q / k / v and the gate / up projections
     already fused in the checkpoint (``qkv_proj``, ``gate_up_proj``). Scaled rotary variants (``longrope``) and
@@ -248,6 +340,7 @@ class LayerWeights:
     qkv_bias: Optional[torch.Tensor] = None      # [q; k; v] projection bias (Qwen2), in the activation dtype
     q_norm: Optional[torch.Tensor] = None        # [head_dim] weights of the per-head query / key RMSNorm (Qwen3)
     k_norm: Optional[torch.Tensor] = None
+    moe: Optional[object] = None                 # nn.moe.MoE of a mixture-of-experts layer (wgu / wd are None then)
 
     @property
     def is_fp8(self) -> bool:
@@ -279,14 +372,19 @@ class Llama3Weights:
 
         embed = rnd(cfg.vocab_size, cfg.hidden_size)
         layers = []
-        for _ in range(cfg.num_hidden_layers):
+        for li in range(cfg.num_hidden_layers):
+            moe = None
+            if cfg.is_moe_layer(li):
+                from ..nn.moe import MoE
+
+                moe = MoE.random_init(cfg.moe_config(), dev, dtype, seed=seed * 1009 + li + 1, std=std)
             layers.append(LayerWeights(
                 attn_norm=torch.ones(cfg.hidden_size, dtype=dtype, device=dev),
                 wqkv=rnd(cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden_size),
                 wo=rnd(cfg.hidden_size, cfg.q_dim),
                 mlp_norm=torch.ones(cfg.hidden_size, dtype=dtype, device=dev),
-                wgu=rnd(2 * cfg.intermediate_size, cfg.hidden_size),
-                wd=rnd(cfg.hidden_size, cfg.intermediate_size),
+                wgu=None if moe is not None else rnd(2 * cfg.intermediate_size, cfg.hidden_size),
+                wd=None if moe is not None else rnd(cfg.hidden_size, cfg.intermediate_size), moe=moe,
                 qkv_bias=rnd(cfg.q_dim + 2 * cfg.kv_dim) if cfg.attention_bias else None,
                 q_norm=torch.ones(cfg.head_dim, dtype=dtype, device=dev) if cfg.qk_norm else None,
                 k_norm=torch.ones(cfg.head_dim, dtype=dtype, device=dev) if cfg.qk_norm else None))
@@ -411,14 +509,18 @@ class Llama3Weights:
                 continue
             wqkv = torch.cat([raw(p + "self_attn.q_proj.weight"), raw(p + "self_attn.k_proj.weight"),
                               raw(p + "self_attn.v_proj.weight")], dim=0)
-            wgu = torch.cat([raw(p + "mlp.gate_proj.weight"), raw(p + "mlp.up_proj.weight")], dim=0)
+            moe = _moe_from_state_dict(cfg, sd, p, dev, dtype) if cfg.is_moe_layer(i) else None
+            wgu = None
+            if moe is None:
+                wgu = torch.cat([raw(p + "mlp.gate_proj.weight"), raw(p + "mlp.up_proj.weight")], dim=0)
+                wgu = wgu.to(device=dev, dtype=dtype).contiguous()
             layers.append(LayerWeights(
                 attn_norm=get(p + "input_layernorm.weight"),
                 wqkv=wqkv.to(device=dev, dtype=dtype).contiguous(),
                 wo=get(p + "self_attn.o_proj.weight"),
                 mlp_norm=get(p + "post_attention_layernorm.weight"),
-                wgu=wgu.to(device=dev, dtype=dtype).contiguous(),
-                wd=get(p + "mlp.down_proj.weight"), qkv_bias=bias(p),
+                wgu=wgu, wd=None if moe is not None else get(p + "mlp.down_proj.weight"), moe=moe,
+                qkv_bias=bias(p),
                 q_norm=opt(p + "self_attn.q_norm.weight"), k_norm=opt(p + "self_attn.k_norm.weight")))
         embed = get("embed_tokens.weight")
         lm_head = embed if (cfg.tie_word_embeddings or "lm_head.weight" not in sd) else get("lm_head.weight")
@@ -453,14 +555,44 @@ class Llama3Weights:
                 sd[p + "post_attention_layernorm.weight"] = l.mlp_norm
                 continue
             q, k, v = torch.split(l.wqkv, [cfg.q_dim, cfg.kv_dim, cfg.kv_dim], dim=0)
-            g, u = torch.split(l.wgu, cfg.intermediate_size, dim=0)
             sd.update({p + "input_layernorm.weight": l.attn_norm, p + "self_attn.q_proj.weight": q,
                        p + "self_attn.k_proj.weight": k, p + "self_attn.v_proj.weight": v,
                        p + "self_attn.o_proj.weight": l.wo,
-                       p + "post_attention_layernorm.weight": l.mlp_norm,
-                       p + "mlp.gate_proj.weight": g, p + "mlp.up_proj.weight": u,
+                       p + "post_attention_layernorm.weight": l.mlp_norm})
+            if l.moe is not None:
+                sd.update({p + "mlp.gate.weight": l.moe.gate.to(l.wo.dtype), p + "mlp.experts.gate_up_proj": l.moe.w_gate_up,
+                           p + "mlp.experts.down_proj": l.moe.w_down})
+                continue
+            g, u = torch.split(l.wgu, cfg.intermediate_size, dim=0)
+            sd.update({p + "mlp.gate_proj.weight": g, p + "mlp.up_proj.weight": u,
                        p + "mlp.down_proj.weight": l.wd})
         return {k: v.contiguous() for k, v in sd.items()}
+
+
+def _moe_from_state_dict(cfg, sd: dict, p: str, dev, dtype):
+    """The mixture-of-experts feed-forward of layer prefix ``p``. Three checkpoint layouts: all experts in two
+    tensors (``mlp.experts.gate_up_proj`` [E, 2 I, H] and ``mlp.experts.down_proj`` [E, H, I], what transformers >= 5
+    writes), one set per expert (``mlp.experts.N.{gate,up,down}_proj``, Qwen3-MoE on the hub), and Mixtral's
+    ``block_sparse_moe.experts.N.{w1,w3,w2}`` (gate, up, down)."""
+    from ..nn.moe import MoE
+
+    E = cfg.num_experts
+    to = lambda t: t.to(device=dev, dtype=dtype).contiguous()
+    if p + "mlp.experts.gate_up_proj" in sd:
+        gate = sd[p + "mlp.gate.weight"]
+        gu, dn = to(sd[p + "mlp.experts.gate_up_proj"]), to(sd[p + "mlp.experts.down_proj"])
+    elif p + "block_sparse_moe.gate.weight" in sd:
+        m = p + "block_sparse_moe."
+        gate = sd[m + "gate.weight"]
+        gu = to(torch.stack([torch.cat((sd[f"{m}experts.{e}.w1.weight"], sd[f"{m}experts.{e}.w3.weight"])) for e in range(E)]))
+        dn = to(torch.stack([sd[f"{m}experts.{e}.w2.weight"] for e in range(E)]))
+    else:
+        m = p + "mlp."
+        gate = sd[m + "gate.weight"]
+        gu = to(torch.stack([torch.cat((sd[f"{m}experts.{e}.gate_proj.weight"], sd[f"{m}experts.{e}.up_proj.weight"]))
+                             for e in range(E)]))
+        dn = to(torch.stack([sd[f"{m}experts.{e}.down_proj.weight"] for e in range(E)]))
+    return MoE(cfg.moe_config(), gate.float().to(dev), gu, dn)
 
 
 def _split_fused_projections(cfg, sd: dict) -> dict:
@@ -516,6 +648,12 @@ class Llama3Model:
                                      RopeScaling.from_hf(cfg.rope_scaling), self.device)
         on_gpu = self.device.type == "cuda"
         self.use_executor = on_gpu and self.dtype == torch.bfloat16 if use_executor is None else use_executor
+        if any(l.moe is not None for l in weights.layers):
+            # mixture-of-experts layers run op by op (router, grouped GEMMs of nn.moe); the native step executor
+            # knows dense layers only
+            self.use_executor = False
+            if tp is not None and tp.world > 1:
+                raise ValueError("tensor parallelism is not implemented for mixture-of-experts layers of this family")
         self.fuse_swiglu = fuse_swiglu
         self.executor = None
         self.logits_buf = None
@@ -675,6 +813,9 @@ class Llama3Model:
                                     self.scale, plan=plan)
             h = ops.linear(a, l.wo, residual=h)
             x = ops.rms_norm(h, l.mlp_norm, c.rms_norm_eps)
+            if l.moe is not None:
+                h = h + l.moe(x)
+                continue
             if self.fuse_swiglu:
                 act = ops.linear_swiglu(x, l.wgu)
             else:

@@ -274,6 +274,17 @@ def _register_builtin() -> None:
         example_repo_ids=("Qwen/Qwen3-8B", "Qwen/Qwen3-32B"),
         preset_configs={"tiny-qwen3": Qwen3Config.tiny})
     PIPELINE_REGISTRY.register(qwen3, allow_override=True)
+    from ..models.llama3 import MixtralConfig, Qwen3MoeConfig
+
+    # Llama / Qwen3 attention with a mixture-of-experts feed-forward (softmax top-k routing, grouped GEMMs); these
+    # layers run op by op, without the native step executor
+    for name, cc, repos, presets in (
+            ("MixtralForCausalLM", MixtralConfig, ("mistralai/Mixtral-8x7B-Instruct-v0.1",), {"tiny-mixtral": MixtralConfig.tiny}),
+            ("Qwen3MoeForCausalLM", Qwen3MoeConfig, ("Qwen/Qwen3-30B-A3B",), {"tiny-qwen3-moe": Qwen3MoeConfig.tiny})):
+        PIPELINE_REGISTRY.register(SupportedArchitecture(
+            name=name, config_class=cc, weights_class=Llama3Weights, model_class=Llama3Model,
+            default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"), example_repo_ids=repos,
+            preset_configs=presets), allow_override=True)
     from ..models.llama3 import Phi3Config
 
     # the Llama layer with the projections already fused in the checkpoint

@@ -1,7 +1,7 @@
 """Golden check against Hugging Face transformers on CPU: a randomly initialised HF model is saved as a checkpoint
 directory, served by this engine through the registry, and both must produce the same greedy tokens. Covers the Llama layer and its variants: Mistral (same tensors), Qwen2 (projection bias), Qwen3 (RMSNorm on
 every query and key head), Phi-3 (projections fused
-in the checkpoint)."""
+in the checkpoint), Mixtral and Qwen3-MoE (mixture-of-experts feed-forward)."""
 
 import json
 
@@ -48,6 +48,12 @@ CASES = {
     "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", dict(rope_theta=1e6, rms_norm_eps=1e-6, use_sliding_window=False)),
     "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(rope_theta=1e6, rms_norm_eps=1e-6, use_sliding_window=False,
                                                       head_dim=32)),
+    "mixtral": ("MixtralConfig", "MixtralForCausalLM", dict(rope_theta=1e6, rms_norm_eps=1e-5, sliding_window=None,
+                                                            num_local_experts=4, num_experts_per_tok=2)),
+    "qwen3_moe": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM", dict(rope_theta=1e6, rms_norm_eps=1e-6, head_dim=32,
+                                                                num_experts=8, num_experts_per_tok=2,
+                                                                moe_intermediate_size=48, norm_topk_prob=True,
+                                                                mlp_only_layers=[0])),
     "phi3": ("Phi3Config", "Phi3ForCausalLM", dict(rope_theta=10000.0, rms_norm_eps=1e-5, sliding_window=None,
                                                    pad_token_id=0)),
 }
@@ -73,6 +79,7 @@ def test_greedy_tokens_match_transformers(tmp_path, family, tied):
     _save(hf, d, tmp_path)
     llm = _engine(tmp_path)
     assert (llm.weights.layers[0].qkv_bias is not None) == (family == "qwen2")
+    assert (llm.weights.layers[-1].moe is not None) == (family in ("mixtral", "qwen3_moe"))
     prompts = [[5, 6, 7, 8, 9, 10, 11], [200, 3, 17]]
     n_new = 10
     recs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=n_new, ignore_eos=True))
