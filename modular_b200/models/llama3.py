@@ -44,7 +44,9 @@ class Llama3Config:
     max_position_embeddings: int = 131072
     tie_word_embeddings: bool = False
     attention_multiplier: Optional[float] = None
-    logits_scaling: float = 1.0
+    logits_scaling: float = 1.0       # Granite: logits are divided by it (folded into the LM head at load)
+    embedding_multiplier: float = 1.0 # Granite: folded into the embedding table at load
+    residual_multiplier: float = 1.0  # Granite: scale of every block output, folded into the o / down projections
     attention_bias: bool = False      # bias on the query / key / value projections (Qwen2)
     qk_norm: bool = False             # RMSNorm over head_dim on every query and key head before the rotation (Qwen3)
     # mixture-of-experts feed-forward (Mixtral, Qwen3-MoE): 0 experts = dense SwiGLU MLP in every layer
@@ -226,6 +228,24 @@ class Qwen3Config(Llama3Config):
         d = super().to_hf()
         d["model_type"] = "qwen3"
         d["use_sliding_window"] = False
+        return d
+
+
+@dataclass
+class GraniteConfig(Llama3Config):
+    """IBM Granite 3.x dense models (``GraniteForCausalLM``): the Llama layer with four scalars - the embedding,
+    every block output and the attention scores are multiplied by constants and the logits divided by one. The
+    first, second and last are folded into the embedding table, the o / down projections and the LM head when the
+    checkpoint is read, so the layers run unchanged; ``attention_multiplier`` is the softmax scale.
+    Reference: max/python/max/pipelines/architectures/granite/."""
+
+    rope_theta: float = 10000.0
+    max_position_embeddings: int = 4096
+    architectures: tuple = ("GraniteForCausalLM",)
+
+    def to_hf(self) -> dict:
+        d = super().to_hf()
+        d["model_type"] = "granite"
         return d
 
 
@@ -524,6 +544,16 @@ class Llama3Weights:
                 q_norm=opt(p + "self_attn.q_norm.weight"), k_norm=opt(p + "self_attn.k_norm.weight")))
         embed = get("embed_tokens.weight")
         lm_head = embed if (cfg.tie_word_embeddings or "lm_head.weight" not in sd) else get("lm_head.weight")
+        if cfg.embedding_multiplier != 1.0 or cfg.logits_scaling != 1.0 or cfg.residual_multiplier != 1.0:
+            # Granite's scalars go into the weights (computed in fp32, rounded once); a tied LM head becomes its own
+            # tensor because table and head are scaled differently
+            scaled = lambda w, f: (w.float() * f).to(dtype) if f != 1.0 else w
+            lm_head = scaled(lm_head, 1.0 / cfg.logits_scaling)
+            embed = scaled(embed, cfg.embedding_multiplier)
+            for l in layers:
+                if l.is_fp8 or l.moe is not None:
+                    raise ValueError("residual / embedding multipliers are folded into bf16 dense layers only")
+                l.wo, l.wd = scaled(l.wo, cfg.residual_multiplier), scaled(l.wd, cfg.residual_multiplier)
         return cls(embed, layers, get("norm.weight"), lm_head)
 
     def to_hf_state_dict(self, cfg: Llama3Config) -> dict:

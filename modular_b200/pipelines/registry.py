@@ -285,6 +285,12 @@ def _register_builtin() -> None:
             name=name, config_class=cc, weights_class=Llama3Weights, model_class=Llama3Model,
             default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"), example_repo_ids=repos,
             preset_configs=presets), allow_override=True)
+    from ..models.llama3 import GraniteConfig
+
+    PIPELINE_REGISTRY.register(SupportedArchitecture(
+        name="GraniteForCausalLM", config_class=GraniteConfig, weights_class=Llama3Weights, model_class=Llama3Model,
+        default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"),
+        example_repo_ids=("ibm-granite/granite-3.3-8b-instruct",), preset_configs={}), allow_override=True)
     from ..models.llama3 import Phi3Config
 
     # the Llama layer with the projections already fused in the checkpoint

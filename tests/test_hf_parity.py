@@ -1,7 +1,7 @@
 """Golden check against Hugging Face transformers on CPU: a randomly initialised HF model is saved as a checkpoint
 directory, served by this engine through the registry, and both must produce the same greedy tokens. Covers the Llama layer and its variants: Mistral (same tensors), Qwen2 (projection bias), Qwen3 (RMSNorm on
 every query and key head), Phi-3 (projections fused
-in the checkpoint), Mixtral and Qwen3-MoE (mixture-of-experts feed-forward)."""
+in the checkpoint), Mixtral and Qwen3-MoE (mixture-of-experts feed-forward), Granite (scalar multipliers folded into the weights)."""
 
 import json
 
@@ -54,6 +54,9 @@ CASES = {
                                                                 num_experts=8, num_experts_per_tok=2,
                                                                 moe_intermediate_size=48, norm_topk_prob=True,
                                                                 mlp_only_layers=[0])),
+    "granite": ("GraniteConfig", "GraniteForCausalLM", dict(rope_theta=10000.0, rms_norm_eps=1e-5,
+                                                            embedding_multiplier=12.0, residual_multiplier=0.22,
+                                                            attention_multiplier=0.0078125 * 16, logits_scaling=8.0)),
     "phi3": ("Phi3Config", "Phi3ForCausalLM", dict(rope_theta=10000.0, rms_norm_eps=1e-5, sliding_window=None,
                                                    pad_token_id=0)),
 }
