@@ -320,8 +320,8 @@ class Qwen3MoeConfig(Qwen3Config):
 @dataclass
 class Phi3Config(Llama3Config):
     """Phi-3 / Phi-3.5 mini (``Phi3ForCausalLM``): the Llama layer with the q / k / v and the gate / up projections
-    already fused in the checkpoint (``qkv_proj``, ``gate_up_proj``). Scaled rotary variants (``longrope``) and
-    partial rotary embeddings are refused. Reference: max/python/max/pipelines/architectures/phi3/."""
+    already fused in the checkpoint (``qkv_proj``, ``gate_up_proj``). The 128k variants scale the rotary
+    frequencies with LongRoPE; partial rotary embeddings (Phi-4-mini) are refused. Reference: max/python/max/pipelines/architectures/phi3/."""
 
     rope_theta: float = 10000.0
     max_position_embeddings: int = 4096
@@ -329,10 +329,23 @@ class Phi3Config(Llama3Config):
 
     @classmethod
     def from_hf(cls, d: dict) -> "Phi3Config":
-        if d.get("rope_scaling"):
-            raise ValueError(f"rotary scaling {d['rope_scaling'].get('type', d['rope_scaling'])!r} is not implemented")
-        if float(d.get("partial_rotary_factor", 1.0)) != 1.0:
+        from ..pipelines.weights import normalize_hf_rope
+
+        d = normalize_hf_rope(d)
+        if float(d.get("partial_rotary_factor", (d.get("rope_parameters") or {}).get("partial_rotary_factor", 1.0))) != 1.0:
             raise ValueError("partial rotary embeddings are not implemented")
+        rs = d.get("rope_scaling")
+        if rs:
+            kind = rs.get("rope_type", rs.get("type"))
+            if kind not in ("longrope", "su"):
+                raise ValueError(f"rotary scaling {kind!r} is not implemented for this family")
+            # LongRoPE (the 128k variants): per-frequency divisors for short and for long contexts and an attention
+            # factor from the ratio of the two context lengths, which live at the top level of the config. The
+            # table is built once: long divisors when the served context exceeds the original one, else short.
+            orig = int(d.get("original_max_position_embeddings") or rs.get("original_max_position_embeddings")
+                       or d["max_position_embeddings"])
+            d = dict(d, rope_scaling=dict(rs, rope_type="longrope", original_max_position_embeddings=orig,
+                                          factor=rs.get("factor") or d["max_position_embeddings"] / orig))
         return _cap_to_window(super().from_hf(d), d.get("sliding_window"))
 
     def to_hf(self) -> dict:

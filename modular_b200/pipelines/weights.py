@@ -88,7 +88,7 @@ def normalize_hf_rope(d: dict) -> dict:
     d = dict(d)
     if "rope_theta" in rp and d.get("rope_theta") is None:
         d["rope_theta"] = rp["rope_theta"]
-    if "rope_scaling" not in d:
+    if d.get("rope_scaling") is None:
         kind = rp.get("rope_type", rp.get("type", "default"))
         d["rope_scaling"] = None if kind in (None, "default") else {k: v for k, v in rp.items() if k != "rope_theta"}
     return d

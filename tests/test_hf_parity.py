@@ -132,3 +132,48 @@ def test_deepseek_v3_greedy_tokens_match_transformers(tmp_path, q_lora, yarn):
                                eos_token_id=None)[0, len(prompt):].tolist()
         assert list(rec.tokens) == want
     _assert_logits_close(llm, hf, prompts[2] * 3)      # 36 positions: past the original context of the yarn case
+
+
+def test_phi3_longrope_matches_transformers(tmp_path):
+    """Phi-3 128k variants: LongRoPE divides the rotary frequencies by per-frequency factors (short ones while the
+    context fits the original length, long ones beyond) and scales cos / sin by an attention factor from the ratio
+    of the two lengths. Both regimes against transformers, and the comparison is sensitive to the scaling."""
+    from modular_b200.models.llama3 import Llama3Model
+    from modular_b200.pipelines.speculative import _SeqCache
+
+    torch.manual_seed(3)
+    hd = 16
+    rs = {"rope_type": "longrope", "type": "longrope", "short_factor": [1.0 + 0.05 * i for i in range(hd // 2)],
+          "long_factor": [1.5 + 0.4 * i for i in range(hd // 2)]}
+    hf_cfg = transformers.Phi3Config(
+        hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+        vocab_size=320, max_position_embeddings=96, original_max_position_embeddings=16, rope_scaling=rs,
+        rope_theta=10000.0, sliding_window=None, pad_token_id=0, tie_word_embeddings=False)
+    hf = transformers.Phi3ForCausalLM(hf_cfg).eval()
+    d = hf_cfg.to_dict()
+    d["architectures"] = ["Phi3ForCausalLM"]
+    _save(hf, d, tmp_path)
+
+    def engine(max_len):
+        from modular_b200.pipelines.config import PipelineArgs, PipelineConfig
+        from modular_b200.pipelines.registry import PIPELINE_REGISTRY
+
+        pc = PipelineConfig.from_args(PipelineArgs.from_flat_kwargs(
+            None, model_path=str(tmp_path), devices="cpu", max_length=max_len, max_batch_size=2,
+            max_batch_input_tokens=64, kv_cache_page_size=16, quantization_encoding="float32"))
+        return PIPELINE_REGISTRY.retrieve(pc)[1]
+
+    for max_len, n in ((16, 12), (96, 40)):      # short factors / long factors
+        llm = engine(max_len)
+        assert llm.cfg.rope_scaling["rope_type"] == "longrope" and llm.cfg.rope_scaling["factor"] == 6.0
+        prompt = [(7 * i + 3) % 320 for i in range(n)]
+        ours = _SeqCache(llm.model, 64).step(prompt, all_logits=True).float()
+        with torch.no_grad():
+            want = hf(torch.tensor([prompt])).logits[0].float()
+        assert (ours - want).abs().max().item() < 1e-5
+    import copy
+
+    plain = copy.copy(llm.cfg)
+    plain.rope_scaling = None
+    other = _SeqCache(Llama3Model(plain, llm.weights, llm.model.kv), 64).step(prompt, all_logits=True).float()
+    assert (other - want).abs().max().item() > 1e-3
