@@ -177,3 +177,32 @@ def test_phi3_longrope_matches_transformers(tmp_path):
     plain.rope_scaling = None
     other = _SeqCache(Llama3Model(plain, llm.weights, llm.model.kv), 64).step(prompt, all_logits=True).float()
     assert (other - want).abs().max().item() > 1e-3
+
+
+@pytest.mark.parametrize("scaling", [
+    {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+     "original_max_position_embeddings": 32},
+    {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 24, "beta_fast": 32, "beta_slow": 1},
+    {"rope_type": "linear", "factor": 2.5},
+])
+def test_llama_rope_scaling_families_match_transformers(tmp_path, scaling):
+    """The rotary scaling rules of Llama-3.1 (``llama3``), YaRN and linear interpolation: logits of a prompt that
+    reaches past the original context, against transformers."""
+    from modular_b200.pipelines.speculative import _SeqCache
+
+    torch.manual_seed(5)
+    hf_cfg = transformers.LlamaConfig(
+        hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+        vocab_size=320, max_position_embeddings=128, rope_theta=10000.0, rope_scaling=dict(scaling),
+        tie_word_embeddings=False)
+    hf = transformers.LlamaForCausalLM(hf_cfg).eval()
+    d = hf_cfg.to_dict()
+    d["architectures"] = ["LlamaForCausalLM"]
+    _save(hf, d, tmp_path)
+    llm = _engine(tmp_path)
+    assert llm.cfg.rope_scaling["rope_type"] == scaling["rope_type"]
+    prompt = [(11 * i + 5) % 320 for i in range(60)]
+    ours = _SeqCache(llm.model, 64).step(prompt, all_logits=True).float()
+    with torch.no_grad():
+        want = hf(torch.tensor([prompt])).logits[0].float()
+    assert (ours - want).abs().max().item() < 1e-5
