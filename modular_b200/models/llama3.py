@@ -67,6 +67,11 @@ class Llama3Config:
         from ..pipelines.weights import normalize_hf_rope
 
         d = normalize_hf_rope(d)
+        act = d.get("hidden_act") or d.get("hidden_activation") or "silu"
+        if act not in ("silu", "swish"):
+            raise ValueError(f"activation {act!r} is not implemented by this family (SwiGLU layers only)")
+        if d.get("mlp_bias"):
+            raise ValueError("biases on the MLP projections are not implemented")
         keys = set(cls.__dataclass_fields__)
         kw = {k: v for k, v in d.items() if k in keys}
         if "architectures" in kw:
@@ -489,6 +494,11 @@ class Llama3Weights:
         """``keep_fp8``: block-scaled fp8 projections (``<name>`` e4m3 + ``<name>_scale_inv``) stay fp8 when the
         fused row blocks line up with the 128-row scale blocks; otherwise they are expanded to ``dtype``."""
         sd = _split_fused_projections(cfg, adapt_hf_state_dict(sd))
+        # parameters this family has no place for must not be dropped silently
+        extra = [k for k in sd if k.endswith((".o_proj.bias", ".gate_proj.bias", ".up_proj.bias", ".down_proj.bias"))
+                 and bool(torch.count_nonzero(sd[k]))]
+        if extra:
+            raise ValueError(f"checkpoint has biases that are not implemented: {extra[:3]}")
         dev = torch.device(device)
         fp8_names = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
                      "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")

@@ -205,3 +205,23 @@ def test_mistral_checkpoint_is_served_by_the_llama_family(tmp_path):
     assert got == [list(r.tokens) for r in ref.generate([[5, 6, 7, 8], [9, 10]], sp)]
     # a sliding window caps the served context at the window length (there the two attentions are the same)
     assert MistralConfig.from_hf(dict(cfg.to_hf(), sliding_window=64)).max_position_embeddings == 64
+
+
+def test_checkpoints_with_parts_this_family_lacks_are_refused():
+    """Nothing is dropped silently: another activation, MLP biases or an output-projection bias raise."""
+    import pytest
+
+    from modular_b200.models.llama3 import Llama3Config, Llama3Weights
+
+    base = Llama3Config.tiny(num_hidden_layers=1, vocab_size=64).to_hf()
+    with pytest.raises(ValueError):
+        Llama3Config.from_hf(dict(base, hidden_act="gelu_pytorch_tanh"))
+    with pytest.raises(ValueError):
+        Llama3Config.from_hf(dict(base, mlp_bias=True))
+    cfg = Llama3Config.tiny(num_hidden_layers=1, vocab_size=64)
+    sd = Llama3Weights.random_init(cfg, "cpu", torch.float32, seed=0).to_hf_state_dict(cfg)
+    Llama3Weights.from_state_dict(cfg, dict(sd, **{"model.layers.0.self_attn.o_proj.bias": torch.zeros(cfg.hidden_size)}),
+                                  "cpu", torch.float32)          # an all-zero bias changes nothing
+    with pytest.raises(ValueError):
+        Llama3Weights.from_state_dict(cfg, dict(sd, **{"model.layers.0.self_attn.o_proj.bias": torch.ones(cfg.hidden_size)}),
+                                      "cpu", torch.float32)
