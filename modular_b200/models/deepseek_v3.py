@@ -156,7 +156,19 @@ class DeepseekV3Config:
 
         d = normalize_hf_rope(d)
         names = cls.__dataclass_fields__.keys()
-        return cls(**{k: v for k, v in d.items() if k in names})
+        kw = {k: v for k, v in d.items() if k in names}
+        if "DeepseekV2ForCausalLM" in (d.get("architectures") or ()) or d.get("model_type") == "deepseek_v2":
+            # DeepSeek-V2 / V2-Lite: same attention and layer layout; the router is a softmax over the experts with a
+            # plain top-k ("greedy") - V2's group-limited variant of it is not implemented
+            method = d.get("topk_method", "greedy")
+            if method != "greedy":
+                raise ValueError(f"router method {method!r} of DeepSeek-V2 is not implemented (greedy is)")
+            kw.update(scoring_func="softmax", n_group=1, topk_group=1)
+            kw.setdefault("norm_topk_prob", False)
+            kw.setdefault("routed_scaling_factor", 1.0)
+            if "rope_scaling" not in kw:
+                kw["rope_scaling"] = None
+        return cls(**kw)
 
 
 class Fp8Weight:

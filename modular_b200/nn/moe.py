@@ -62,7 +62,7 @@ def route_softmax_ref(logits, cfg: MoEConfig):
     w, ids = p.topk(cfg.num_experts_per_tok, dim=-1)
     if cfg.norm_topk_prob:
         w = w / (w.sum(-1, keepdim=True) + 1e-20)
-    return ids.int(), w
+    return ids.int(), w * cfg.routed_scaling_factor
 
 
 def route(logits, bias, cfg: MoEConfig):
@@ -80,6 +80,8 @@ def route(logits, bias, cfg: MoEConfig):
                                         cfg.topk_group, cfg.norm_topk_prob, cfg.routed_scaling_factor)
     else:
         _lib().moe_router_softmax_topk(lg, ids, w, cfg.norm_topk_prob)
+        if cfg.routed_scaling_factor != 1.0:
+            w *= cfg.routed_scaling_factor
     return ids, w
 
 

@@ -311,6 +311,11 @@ def _register_builtin() -> None:
         example_repo_ids=("deepseek-ai/DeepSeek-V3", "deepseek-ai/DeepSeek-R1"),
         preset_configs={"deepseek-v3": DeepseekV3Config.deepseek_v3, "tiny-deepseek": DeepseekV3Config.tiny})
     PIPELINE_REGISTRY.register(deepseek, allow_override=True)
+    # DeepSeek-V2 / V2-Lite: the same model code with a softmax top-k router (config mapping in from_hf)
+    PIPELINE_REGISTRY.register(SupportedArchitecture(
+        name="DeepseekV2ForCausalLM", config_class=DeepseekV3Config, weights_class=DeepseekV3Weights,
+        model_class=DeepseekV3Model, default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"),
+        example_repo_ids=("deepseek-ai/DeepSeek-V2-Lite",), preset_configs={}), allow_override=True)
 
 
 PIPELINE_REGISTRY.register_lazy(_register_builtin)
