@@ -55,8 +55,17 @@ class SamplingParams:
     logprobs: int = 0
     # grammar spec for constrained decoding: {"type": "json_object" | "json_schema" | "regex" | "ebnf", ...}
     response_format: Optional[dict] = None
+    # additive bias on the logits of given token ids before sampling (OpenAI ``logit_bias``; -100 bans a token)
+    logit_bias: Optional[dict] = None
 
     def __post_init__(self):
+        if self.logit_bias:
+            try:
+                self.logit_bias = {int(k): float(v) for k, v in self.logit_bias.items()}
+            except (TypeError, ValueError) as e:
+                raise ValueError("logit_bias must map token ids to numbers") from e
+            if any(k < 0 for k in self.logit_bias) or any(not -100.0 <= v <= 100.0 for v in self.logit_bias.values()):
+                raise ValueError("logit_bias: token ids must be >= 0 and values in [-100, 100]")
         if self.temperature < 0:
             raise ValueError("temperature must be >= 0")
         if not (0.0 < self.top_p <= 1.0):
@@ -75,7 +84,7 @@ class SamplingParams:
     @property
     def needs_penalties(self) -> bool:
         return (self.frequency_penalty != 0.0 or self.presence_penalty != 0.0
-                or self.repetition_penalty != 1.0)
+                or self.repetition_penalty != 1.0 or bool(self.logit_bias))
 
 
 class TokenBuffer:

@@ -296,6 +296,7 @@ class TextGenerationPipeline:
         ops.apply_penalties(logits, mk(tok or [0], torch.int32), mk(cnt or [0], torch.int32),
                             mk(offs, torch.int32), mk(freq, torch.float32), mk(pres, torch.float32),
                             mk(rep, torch.float32))
+        self._add_logit_bias(sb, logits)
         f32 = lambda name: meta[off[name] : off[name] + n].view(torch.float32)
         ops.sample(logits, f32("temperature"), meta[off["top_k"] : off["top_k"] + n], f32("top_p"),
                    f32("min_p"), meta[off["seeds"] : off["seeds"] + 2 * n].view(torch.int64),
@@ -329,10 +330,28 @@ class TextGenerationPipeline:
                                 torch.tensor([s.frequency_penalty for s in sp]),
                                 torch.tensor([s.presence_penalty for s in sp]),
                                 torch.tensor([s.repetition_penalty for s in sp]))
+        self._add_logit_bias(sb, logits)
         if sb.all_greedy:
             return ops.argmax(logits)
         return ops.sample(logits, t["temperature"], t["top_k"], t["top_p"], t["min_p"],
                           generator=self._cpu_gen)
+
+    @staticmethod
+    def _add_logit_bias(sb: StepBatch, logits: torch.Tensor) -> None:
+        """Per-request additive biases (``SamplingParams.logit_bias``) on the rows that sample this step; ids
+        outside the vocabulary are ignored."""
+        rows, toks, vals = [], [], []
+        V = logits.shape[1]
+        for i, c in enumerate(sb.logit_ctx):
+            lb = c.sampling_params.logit_bias
+            if lb:
+                for t_, v in lb.items():
+                    if t_ < V:
+                        rows.append(i), toks.append(t_), vals.append(v)
+        if rows:
+            dev = logits.device
+            logits.index_put_((torch.tensor(rows, device=dev), torch.tensor(toks, device=dev)),
+                              torch.tensor(vals, dtype=logits.dtype, device=dev), accumulate=True)
 
     def _collect(self, inflight: Optional[_InFlight]) -> dict:
         """Wait for a launched step's tokens, fold them into the contexts, build outputs."""

@@ -56,7 +56,8 @@ def sampling_from_request(req, default_max_tokens: Optional[int]) -> SamplingPar
             repetition_penalty=req.repetition_penalty or 1.0,
             max_new_tokens=max_tokens if max_tokens is not None else default_max_tokens,
             min_new_tokens=req.min_tokens or 0, ignore_eos=req.ignore_eos, stop=stop,
-            stop_token_ids=req.stop_token_ids, seed=req.seed or 0, logprobs=_logprobs_requested(req))
+            stop_token_ids=req.stop_token_ids, seed=req.seed or 0, logprobs=_logprobs_requested(req),
+            logit_bias=getattr(req, "logit_bias", None))
     except ValueError as e:
         raise HTTPException(status_code=400, detail=str(e)) from e
 

@@ -40,6 +40,7 @@ class _SamplingMixin(_Req):
     seed: Optional[int] = None
     ignore_eos: bool = False
     min_tokens: Optional[int] = None
+    logit_bias: Optional[dict[str, float]] = None    # token id -> additive bias in [-100, 100]
     n: int = 1
     stream: bool = False
     stream_options: Optional[StreamOptions] = None

@@ -225,3 +225,34 @@ def test_checkpoints_with_parts_this_family_lacks_are_refused():
     with pytest.raises(ValueError):
         Llama3Weights.from_state_dict(cfg, dict(sd, **{"model.layers.0.self_attn.o_proj.bias": torch.ones(cfg.hidden_size)}),
                                       "cpu", torch.float32)
+
+
+def test_logit_bias_forces_and_bans_tokens():
+    """OpenAI ``logit_bias``: +100 on a token makes greedy decoding emit it, -100 on the greedy choice removes it;
+    other requests of the same batch are untouched, and the map survives the worker transport."""
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.models.llama3 import Llama3Config
+    from modular_b200.pipelines.context import SamplingParams
+
+    cfg = Llama3Config.tiny(num_hidden_layers=2, vocab_size=64)
+    llm = LLM(cfg, device="cpu", dtype=torch.float32, max_length=96, max_batch_size=4, max_batch_input_tokens=64,
+              page_size=16, num_kv_pages=32, seed=2)
+    prompt = [3, 4, 5, 6]
+    plain = SamplingParams(temperature=0.0, max_new_tokens=5, ignore_eos=True)
+    base = list(llm.generate([prompt], plain)[0].tokens)
+    forced = SamplingParams(temperature=0.0, max_new_tokens=5, ignore_eos=True, logit_bias={"17": 100})
+    banned = SamplingParams(temperature=0.0, max_new_tokens=5, ignore_eos=True, logit_bias={base[0]: -100.0})
+    recs = llm.generate([prompt, prompt, prompt], [forced, banned, plain])
+    assert list(recs[0].tokens) == [17] * 5
+    assert recs[1].tokens[0] != base[0]
+    assert list(recs[2].tokens) == base
+    with pytest.raises(ValueError):
+        SamplingParams(logit_bias={"x": 1.0})
+    with pytest.raises(ValueError):
+        SamplingParams(logit_bias={3: 1000.0})
+    from modular_b200.serve.worker_interface.codec import decode, encode
+    from modular_b200.pipelines.context import TextContext
+
+    ctx = TextContext.from_prompt(prompt, 64, sampling_params=forced)
+    back = decode(encode(ctx))
+    assert back.sampling_params.logit_bias == {17: 100.0}
