@@ -159,11 +159,14 @@ class DeepseekV3Config:
         kw = {k: v for k, v in d.items() if k in names}
         if "DeepseekV2ForCausalLM" in (d.get("architectures") or ()) or d.get("model_type") == "deepseek_v2":
             # DeepSeek-V2 / V2-Lite: same attention and layer layout; the router is a softmax over the experts with a
-            # plain top-k ("greedy") - V2's group-limited variant of it is not implemented
+            # plain top-k ("greedy", V2-Lite) or a top-k inside the groups with the largest single score
+            # ("group_limited_greedy", V2 / V2.5)
             method = d.get("topk_method", "greedy")
-            if method != "greedy":
-                raise ValueError(f"router method {method!r} of DeepSeek-V2 is not implemented (greedy is)")
-            kw.update(scoring_func="softmax", n_group=1, topk_group=1)
+            if method not in ("greedy", "group_limited_greedy"):
+                raise ValueError(f"router method {method!r} of DeepSeek-V2 is not implemented")
+            kw["scoring_func"] = "softmax"
+            if method == "greedy":
+                kw.update(n_group=1, topk_group=1)
             kw.setdefault("norm_topk_prob", False)
             kw.setdefault("routed_scaling_factor", 1.0)
             if "rope_scaling" not in kw:

@@ -65,8 +65,25 @@ def route_softmax_ref(logits, cfg: MoEConfig):
     return ids.int(), w * cfg.routed_scaling_factor
 
 
+def route_softmax_group_limited(logits, cfg: MoEConfig):
+    """DeepSeek-V2's ``group_limited_greedy``: softmax over all experts, the ``topk_group`` groups with the largest
+    single score stay, top-k among their experts (torch ops on either device: this router has no kernel of its own)."""
+    p = torch.softmax(logits.float(), dim=-1)
+    T, E = p.shape
+    g = p.view(T, cfg.n_group, E // cfg.n_group)
+    gidx = g.amax(dim=-1).topk(cfg.topk_group, dim=-1).indices
+    gmask = torch.zeros(T, cfg.n_group, dtype=torch.bool, device=p.device).scatter_(1, gidx, True)
+    masked = p.masked_fill(~gmask.unsqueeze(-1).expand_as(g).reshape(T, E), 0.0)
+    w, ids = masked.topk(cfg.num_experts_per_tok, dim=-1)
+    if cfg.norm_topk_prob:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return ids.int(), (w * cfg.routed_scaling_factor).contiguous()
+
+
 def route(logits, bias, cfg: MoEConfig):
     """Returns (topk_ids int32 [T, k], topk_weights fp32 [T, k])."""
+    if cfg.scoring_func != "sigmoid" and cfg.n_group > 1:
+        return route_softmax_group_limited(logits, cfg)
     if not logits.is_cuda:
         if cfg.scoring_func == "sigmoid":
             return route_group_limited_ref(logits, bias, cfg)

@@ -208,9 +208,11 @@ def test_llama_rope_scaling_families_match_transformers(tmp_path, scaling):
     assert (ours - want).abs().max().item() < 1e-5
 
 
-def test_deepseek_v2_lite_matches_transformers(tmp_path):
-    """DeepSeek-V2-Lite shapes (``DeepseekV2ForCausalLM``): the V3 model code with no query low-rank projection and
-    a plain softmax top-k router without renormalisation, two shared experts. V2's group-limited router is refused."""
+@pytest.mark.parametrize("method", ["greedy", "group_limited_greedy"])
+def test_deepseek_v2_matches_transformers(tmp_path, method):
+    """DeepSeek-V2 shapes (``DeepseekV2ForCausalLM``): the V3 model code with a softmax router - plain top-k without
+    renormalisation and no query low-rank projection (V2-Lite), or top-k inside the best groups with a scaling
+    factor (V2) - and two shared experts."""
     from modular_b200.models.deepseek_v3 import DeepseekV3Config
     from modular_b200.pipelines.speculative import _SeqCache
 
@@ -218,11 +220,16 @@ def test_deepseek_v2_lite_matches_transformers(tmp_path):
     hf_cfg = transformers.DeepseekV2Config(
         vocab_size=512, hidden_size=128, intermediate_size=256, moe_intermediate_size=64, num_hidden_layers=3,
         num_attention_heads=4, num_key_value_heads=4, n_shared_experts=2, n_routed_experts=8,
-        routed_scaling_factor=1.0, kv_lora_rank=64, q_lora_rank=None, qk_rope_head_dim=16, v_head_dim=32,
-        qk_nope_head_dim=32, topk_method="greedy", n_group=1, topk_group=1, num_experts_per_tok=3,
+        routed_scaling_factor=1.0 if method == "greedy" else 4.0, kv_lora_rank=64,
+        q_lora_rank=None if method == "greedy" else 96, qk_rope_head_dim=16, v_head_dim=32,
+        qk_nope_head_dim=32, topk_method=method, n_group=1 if method == "greedy" else 4,
+        topk_group=1 if method == "greedy" else 2, num_experts_per_tok=3,
         first_k_dense_replace=1, norm_topk_prob=False, max_position_embeddings=512, rope_theta=10000.0,
         tie_word_embeddings=False)
     hf = transformers.DeepseekV2ForCausalLM(hf_cfg).eval()
+    for mod in hf.modules():          # the group-limited branch of this transformers version reads an unset attribute
+        if type(mod).__name__ == "DeepseekV2Moe" and not hasattr(mod, "num_experts"):
+            mod.num_experts = hf_cfg.n_routed_experts
     with torch.no_grad():
         for n, p in hf.named_parameters():
             if "norm" in n:
@@ -231,11 +238,12 @@ def test_deepseek_v2_lite_matches_transformers(tmp_path):
     d["architectures"] = ["DeepseekV2ForCausalLM"]
     _save(hf, d, tmp_path)
     llm = _engine(tmp_path)
-    assert llm.cfg.scoring_func == "softmax" and llm.cfg.q_lora_rank is None and not llm.cfg.norm_topk_prob
+    assert llm.cfg.scoring_func == "softmax" and not llm.cfg.norm_topk_prob
+    assert llm.cfg.n_group == (1 if method == "greedy" else 4)
     prompt = [(7 * i + 3) % 512 for i in range(30)]
     ours = _SeqCache(llm.model, 64).step(prompt, all_logits=True).float()
     with torch.no_grad():
         want = hf(torch.tensor([prompt])).logits[0].float()
     assert (ours - want).abs().max().item() < 1e-5
     with pytest.raises(ValueError):
-        DeepseekV3Config.from_hf(dict(d, topk_method="group_limited_greedy"))
+        DeepseekV3Config.from_hf(dict(d, topk_method="something_else"))
