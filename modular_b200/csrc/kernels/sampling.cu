@@ -897,7 +897,7 @@ extern "C" int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, 
   if (rows <= 0) return MB_OK;
   // rows with a top-k / top-p / min-p filter go to the cluster kernel first; what it leaves (out = -1: greedy
   // and plain-temperature rows, kept sets too wide for its list) is drawn by the one-CTA kernel after it
-  const bool clustered = g_sample_cluster && (top_k || top_p || min_p) && rows <= 65535;
+  bool clustered = g_sample_cluster && (top_k || top_p || min_p) && rows <= 65535;
   if (clustered) {
     static PerDeviceOnce once;
     if (once.needed()) {
@@ -928,8 +928,12 @@ extern "C" int mb_sample_topk_topp(const float* logits, int64_t* out, int rows, 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, out, vocab, ld, temperature, top_k, top_p, min_p,
-                           seeds, step) != cudaSuccess)
-      return MB_ERR_LAUNCH;
+                           seeds, step) != cudaSuccess) {
+      // a device (or partition) that cannot place such clusters: every row goes to the one-CTA kernel from now on
+      cudaGetLastError();
+      g_sample_cluster = false;
+      clustered = false;
+    }
   }
   return launch_k(sample_kernel, dim3(rows), dim3(kSampThreads), 0, stream, logits, out, vocab, ld, temperature,
                   top_k, top_p, min_p, seeds, step, clustered ? 1 : 0) == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
