@@ -49,7 +49,10 @@ def test_moe_cpu_matches_dense_evaluation():
 @pytest.mark.parametrize("scoring", ["sigmoid", "softmax"])
 def test_router_kernels(scoring):
     torch.manual_seed(2)
-    cfg = MoEConfig(7168, 2048, 256, 8, 1, 8, 4, True, 2.5, scoring)
+    # softmax scoring with groups means DeepSeek-V2's group-limited router (torch ops); the softmax kernel under test
+    # here is the plain top-k one
+    groups = (8, 4) if scoring == "sigmoid" else (1, 1)
+    cfg = MoEConfig(7168, 2048, 256, 8, 1, groups[0], groups[1], True, 2.5, scoring)
     logits = torch.randn(77, 256, device="cuda")
     bias = (torch.randn(256, device="cuda") * 0.1) if scoring == "sigmoid" else None
     ids, w = route(logits, bias, cfg)
