@@ -10,6 +10,7 @@ follow the public API.
 from __future__ import annotations
 
 import json
+import logging
 import uuid
 from typing import AsyncIterator, Optional, Union
 
@@ -21,6 +22,8 @@ import asyncio
 import hashlib
 
 from ..parser import ReasoningSplitter, get_tool_parser, split_reasoning
+from ..parser.conformance import check_response_format, check_tool_calls, tool_schemas
+from ..parser.normalization import anchor_object_schemas, tool_call_arguments_as_mappings, tools_with_parameters
 from ..schemas.openai import (ChatChoice, ChatChoiceMessage, ChatChunkChoice, ChatCompletionChunk,
                               ChatCompletionRequest, ChatCompletionResponse, ChatDelta, CompletionChoice,
                               CompletionRequest, CompletionResponse, ErrorBody, ErrorResponse, ModelCard,
@@ -28,6 +31,8 @@ from ..schemas.openai import (ChatChoice, ChatChoiceMessage, ChatChunkChoice, Ch
                               LoadLoraRequest, UnloadLoraRequest)
 from ..telemetry.metrics import METRICS
 from ..worker_interface import RequestQueueFull
+
+logger = logging.getLogger("modular_b200.serve")
 
 router = APIRouter()
 
@@ -45,6 +50,12 @@ def sampling_from_request(req, default_max_tokens: Optional[int]) -> SamplingPar
     from ...pipelines.structured_output import response_format_to_spec
     try:
         spec = response_format_to_spec(getattr(req, "response_format", None))
+        if spec is not None and spec.get("type") == "json_schema":
+            # untyped nodes with object keywords would let the grammar accept a bare, never-ending string
+            try:
+                spec = dict(spec, schema=json.dumps(anchor_object_schemas(json.loads(spec["schema"]))))
+            except (TypeError, ValueError):
+                pass
         return SamplingParams(
             response_format=spec,
             top_k=req.top_k if req.top_k not in (None, 0) else -1,
@@ -288,7 +299,11 @@ def _chat_prompt(pipeline, req: ChatCompletionRequest) -> str:
     msgs = [m.model_dump(exclude_none=True) for m in req.messages]
     if not msgs:
         raise HTTPException(status_code=400, detail="messages must not be empty")
-    return pipeline.tokenizer.apply_chat_template(msgs, tools=req.tools, add_generation_prompt=True)
+    for m in msgs:      # templates walk the arguments of earlier tool calls as mappings; clients send JSON strings
+        if m.get("tool_calls"):
+            m["tool_calls"] = tool_call_arguments_as_mappings(m["tool_calls"])
+    tools = tools_with_parameters(req.tools) if req.tools else req.tools
+    return pipeline.tokenizer.apply_chat_template(msgs, tools=tools, add_generation_prompt=True)
 
 
 def _tool_parser_for(request: Request, req: ChatCompletionRequest):
@@ -298,7 +313,30 @@ def _tool_parser_for(request: Request, req: ChatCompletionRequest):
     return get_tool_parser(getattr(request.app.state, "tool_parser", None) or "llama")
 
 
-def _finish_message(text: str, parser, reasoning_on: bool):
+def _observe_conformance(req, tool_calls=None, content=None) -> None:
+    """Counts and logs (names and JSON paths only, no values) tool calls and JSON answers that do not match what the
+    request declared. Never changes the response and never raises."""
+    try:
+        if tool_calls:
+            schemas, names = tool_schemas(req.tools)
+            for r in check_tool_calls([(c["function"]["name"], c["function"].get("arguments", "")) for c in tool_calls],
+                                      schemas, names):
+                if r.outcome != "valid":
+                    METRICS.tool_call_nonconforming.inc()
+                    logger.info("tool call %s: %s %s (+%d)", r.function, r.outcome, r.errors, r.more_errors)
+        rf = getattr(req, "response_format", None)
+        if content is not None and rf is not None and rf.type in ("json_schema", "json_object"):
+            js = getattr(rf, "json_schema", None) or {}
+            schema = (js.get("schema", js) if isinstance(js, dict) else {}) if rf.type == "json_schema" else {"type": "object"}
+            r = check_response_format(content, schema if isinstance(schema, dict) else {})
+            if r.outcome != "valid":
+                METRICS.response_format_nonconforming.inc()
+                logger.info("response_format: %s %s (+%d)", r.outcome, r.errors, r.more_errors)
+    except Exception:      # noqa: BLE001 - observation must not fail a request
+        pass
+
+
+def _finish_message(text: str, parser, reasoning_on: bool, req=None):
     """(message, finish_reason override) of a complete answer."""
     reasoning = None
     if reasoning_on:
@@ -309,8 +347,12 @@ def _finish_message(text: str, parser, reasoning_on: bool):
         except ValueError:
             parsed = None
         if parsed is not None and parsed.tool_calls:
-            return ChatChoiceMessage(content=parsed.content, reasoning_content=reasoning,
-                                     tool_calls=[c.to_openai() for c in parsed.tool_calls]), "tool_calls"
+            calls = [c.to_openai() for c in parsed.tool_calls]
+            if req is not None:
+                _observe_conformance(req, tool_calls=calls)
+            return ChatChoiceMessage(content=parsed.content, reasoning_content=reasoning, tool_calls=calls), "tool_calls"
+    if req is not None:
+        _observe_conformance(req, content=text)
     return ChatChoiceMessage(content=text, reasoning_content=reasoning), None
 
 
@@ -388,7 +430,7 @@ async def create_chat_completion(req: ChatCompletionRequest, request: Request):
         usage.total_tokens = usage.prompt_tokens + usage.completion_tokens
         choices = []
         for i, ch in enumerate(results):
-            msg, reason = _finish_message(ch.text, _tool_parser_for(request, req), reasoning_on)
+            msg, reason = _finish_message(ch.text, _tool_parser_for(request, req), reasoning_on, req)
             choices.append(ChatChoice(index=i, message=msg, logprobs=_chat_logprobs(pipeline, ch),
                                       finish_reason=reason if (reason and ch.finish_reason == "stop") else ch.finish_reason))
         return ChatCompletionResponse(id=cid, model=req.model, usage=usage, choices=choices)

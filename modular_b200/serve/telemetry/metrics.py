@@ -85,6 +85,11 @@ class Metrics:
                                         (1, 1.5, 2, 2.5, 3, 4, 5, 6, 8))
         self.spec_acceptance_rate = mk_g("maxserve_spec_decode_acceptance_rate", "accepted / proposed draft tokens")
         self.grammar_rejections = mk_c("maxserve_structured_output_grammar_rejections", "sampled tokens a grammar refused")
+        # ---- did generated tool calls / JSON answers match the declared schemas (observation only)
+        self.tool_call_nonconforming = mk_c("maxserve_tool_call_nonconforming",
+                                            "tool calls with unknown names, unparsable or schema-violating arguments")
+        self.response_format_nonconforming = mk_c("maxserve_response_format_nonconforming",
+                                                  "JSON answers that did not parse or did not match the requested schema")
 
     def render(self) -> bytes:
         return generate_latest(self.registry)
