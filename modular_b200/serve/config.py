@@ -60,6 +60,8 @@ class Settings(BaseSettings):
     metrics_port: int = 8001
     detailed_buffer_factor: int = 20
     kernel_trace_level: int = 0
+    gc_debug: bool = False              # log slow garbage collections of the model worker (MAX_SERVE_GC_DEBUG)
+    gc_debug_top_objects: int = 0       # with gc_debug: also the N most common types of the collected generation
     # record / replay
     transaction_recording_file: Optional[str] = None
     transaction_recording_include_responses: bool = False

@@ -204,9 +204,17 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
                 return progress
 
             sched.run_iteration = run_traced
-        gc.collect()
-        gc.freeze()
-        logger.info("model worker ready in %.1f s", time.perf_counter() - t0)
+        # start-up objects go to the permanent generation (collections then only see what the loop allocates), free
+        # allocator pages of the start-up peak go back to the system, and collections are timed from here on
+        from .telemetry import gc_utils
+        from .telemetry.metrics import METRICS
+
+        frozen = gc_utils.freeze_startup_heap()
+        gc_utils.trim_host_heap()
+        gc_utils.install_gc_monitor(True, slow_ms=5.0 if settings.gc_debug else 50.0,
+                                    top_types=settings.gc_debug_top_objects if settings.gc_debug else 0,
+                                    observe=METRICS.gc_pause_ms.observe)
+        logger.info("model worker ready in %.1f s (%d objects frozen)", time.perf_counter() - t0, frozen)
         ready_event.set()
         idle = 0
         while not stop_event.is_set():

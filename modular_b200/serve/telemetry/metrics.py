@@ -85,6 +85,8 @@ class Metrics:
                                         (1, 1.5, 2, 2.5, 3, 4, 5, 6, 8))
         self.spec_acceptance_rate = mk_g("maxserve_spec_decode_acceptance_rate", "accepted / proposed draft tokens")
         self.grammar_rejections = mk_c("maxserve_structured_output_grammar_rejections", "sampled tokens a grammar refused")
+        self.gc_pause_ms = mk_h("maxserve_gc_pause_ms", "stop-the-world time of a Python garbage collection",
+                                (0.1, 0.5, 1, 2, 5, 10, 20, 50, 100, 500))
         # ---- did generated tool calls / JSON answers match the declared schemas (observation only)
         self.tool_call_nonconforming = mk_c("maxserve_tool_call_nonconforming",
                                             "tool calls with unknown names, unparsable or schema-violating arguments")

@@ -501,3 +501,28 @@ def test_benchmark_client_loads_datasets_and_sweeps(tmp_path):
     finally:
         server.should_exit = True
         th.join(timeout=10)
+
+
+def test_gc_pause_monitor_and_heap_freeze():
+    import gc
+
+    from modular_b200.serve.telemetry import gc_utils
+
+    seen = []
+    mon = gc_utils.install_gc_monitor(True, slow_ms=0.0, top_types=3, observe=seen.append)
+    try:
+        junk = [[] for _ in range(1000)]
+        for a in junk:
+            a.append(a)                 # cycles for the collector
+        del junk
+        gc.collect()
+    finally:
+        gc_utils.remove_gc_monitor(mon)
+    assert mon.collections >= 1 and len(seen) == mon.collections and mon.max_ms >= 0.0 and mon._census
+    assert gc_utils.install_gc_monitor(False) is None
+    n = gc_utils.freeze_startup_heap()
+    try:
+        assert n > 0 and gc.get_freeze_count() > 0
+    finally:
+        gc.unfreeze()
+    assert gc_utils.trim_host_heap() in (True, False)
