@@ -182,6 +182,10 @@ def fastapi_app(settings: Settings, pipeline_config=None, tokenizer=None, factor
 
     tracing.configure_tracing(settings)
 
+    from .debug import register_debug
+
+    register_debug(app, settings.profiling_enabled, settings.profile_dir)     # inside the request-id middleware
+
     @app.middleware("http")
     async def request_id_middleware(request: Request, call_next):
         rid = request.headers.get("x-request-id") or uuid.uuid4().hex

@@ -60,6 +60,8 @@ class Settings(BaseSettings):
     metrics_port: int = 8001
     detailed_buffer_factor: int = 20
     kernel_trace_level: int = 0
+    profiling_enabled: bool = False     # ?profile=1 on a request writes profile.<request id>.txt (serve/debug.py)
+    profile_dir: str = "."
     gc_debug: bool = False              # log slow garbage collections of the model worker (MAX_SERVE_GC_DEBUG)
     gc_debug_top_objects: int = 0       # with gc_debug: also the N most common types of the collected generation
     # record / replay

@@ -526,3 +526,23 @@ def test_gc_pause_monitor_and_heap_freeze():
     finally:
         gc.unfreeze()
     assert gc_utils.trim_host_heap() in (True, False)
+
+
+def test_request_profiling_is_opt_in(tmp_path):
+    settings = Settings(metric_recording="NOOP", profiling_enabled=True, profile_dir=str(tmp_path))
+    pc = _config(model_path="echo", devices="cpu")
+    app = fastapi_app(settings, pc, ByteTokenizer(), EchoPipeline, "echo", 4096)
+    with TestClient(app) as c:
+        body = {"model": "echo", "prompt": "hello", "max_tokens": 4}
+        plain = c.post("/v1/completions", json=body)
+        assert plain.status_code == 200 and "x-profile-file" not in plain.headers and not list(tmp_path.iterdir())
+        prof = c.post("/v1/completions?profile=1", json=body, headers={"x-request-id": "abc"})
+        assert prof.status_code == 200 and prof.json()["choices"][0]["text"] == plain.json()["choices"][0]["text"]
+        path = tmp_path / "profile.abc.txt"
+        assert prof.headers["x-profile-file"] == str(path) and "cumulative" in path.read_text()
+        c.post("/v1/completions?profile=1&profile_format=pstats", json=body, headers={"x-request-id": "bin"})
+        assert (tmp_path / "profile.bin.pstats").stat().st_size > 0
+    off = fastapi_app(Settings(metric_recording="NOOP"), pc, ByteTokenizer(), EchoPipeline, "echo", 4096)
+    with TestClient(off) as c:
+        r = c.post("/v1/completions?profile=1", json={"model": "echo", "prompt": "hi", "max_tokens": 2})
+        assert r.status_code == 200 and "x-profile-file" not in r.headers
