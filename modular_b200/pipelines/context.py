@@ -30,6 +30,7 @@ class GenerationStatus(str, enum.Enum):
     END_OF_SEQUENCE = "end_of_sequence"
     MAXIMUM_LENGTH = "maximum_length"
     CANCELLED = "cancelled"
+    ERROR = "error"              # the request could not be served (e.g. its grammar does not compile)
 
     @property
     def is_done(self) -> bool:
@@ -183,6 +184,7 @@ class TextGenerationOutput:
     tokens: list[int]
     final_status: GenerationStatus = GenerationStatus.ACTIVE
     log_probabilities: Optional[list[Any]] = None
+    error: Optional[str] = None          # with final_status ERROR: what to tell the client
 
     @property
     def is_done(self) -> bool:

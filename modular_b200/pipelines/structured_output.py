@@ -102,3 +102,69 @@ def apply_token_bitmask_reference(logits: torch.Tensor, bitmask: torch.Tensor) -
     V = logits.shape[1]
     bits = torch.from_numpy(np.unpackbits(bitmask.cpu().numpy().view(np.uint8), axis=1, bitorder="little")[:, :V])
     logits.masked_fill_(~bits.bool().to(logits.device), float("-inf"))
+
+
+class GrammarGate:
+    """Compiles the grammars of new requests on worker threads while the scheduler keeps serving.
+
+    Building a matcher for a large schema can take seconds; done inline it would stall every request that shares
+    the step loop. The scheduler hands a constrained request to :meth:`submit` and admits it to prefill only once
+    :meth:`ready`; :meth:`install` then puts the matcher on the context or returns the message for the client when
+    the grammar does not compile (the request fails, the server goes on). All methods are called from the
+    scheduler thread; only the compilation runs elsewhere (the grammar backend releases the GIL while it works).
+
+    Reference: max/python/max/serve/scheduler/batch_constructor/grammar_gate.py:41 (AsyncGrammarGate).
+    """
+
+    def __init__(self, backend, workers: Optional[int] = None):
+        import os
+
+        self.backend = backend
+        self.workers = workers or max(1, (os.cpu_count() or 2) // 2)
+        self._pool = None
+        self._jobs: dict = {}
+
+    def submit(self, ctx) -> bool:
+        """Starts the compilation for ``ctx`` if it needs one and none runs yet. True when the request now waits."""
+        spec = ctx.sampling_params.response_format
+        if spec is None or ctx.grammar_state is not None:
+            return False
+        if ctx.request_id not in self._jobs:
+            if self._pool is None:
+                from concurrent.futures import ThreadPoolExecutor
+
+                self._pool = ThreadPoolExecutor(max_workers=self.workers, thread_name_prefix="grammar-compile")
+            self._jobs[ctx.request_id] = self._pool.submit(self.backend.compile, spec)
+        return True
+
+    def ready(self, ctx) -> bool:
+        job = self._jobs.get(ctx.request_id)
+        return job is None or job.done()
+
+    def install(self, ctx) -> Optional[str]:
+        """After :meth:`ready`: the matcher goes onto the context (None), or the reason it could not be built."""
+        job = self._jobs.pop(ctx.request_id, None)
+        if job is None:
+            return None
+        try:
+            ctx.grammar_state = job.result()
+        except Exception as e:      # noqa: BLE001 - whatever the backend raises is the client's answer
+            import re
+
+            last = str(e).strip().splitlines()[-1] if str(e).strip() else type(e).__name__
+            last = re.sub(r"^\[[^\]]*\]\s*\S+:\d+:\s*", "", last)      # "[time] file.cc:123: " of native backends
+            return f"the grammar of this request cannot be compiled: {last}"
+        for t in ctx.tokens.generated:      # tokens from before a preemption are replayed into the fresh matcher
+            if t >= 0:
+                ctx.grammar_state.accept(int(t))
+        return None
+
+    def release(self, request_id: str) -> None:
+        job = self._jobs.pop(request_id, None)
+        if job is not None:
+            job.cancel()
+
+    def shutdown(self) -> None:
+        if self._pool is not None:
+            self._pool.shutdown(wait=False, cancel_futures=True)
+            self._pool = None

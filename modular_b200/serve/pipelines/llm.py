@@ -73,6 +73,9 @@ class TokenGeneratorPipeline:
         buf_lps: list = []
         buf_text = ""
         async for out in self.proxy.stream(ctx):
+            if out.final_status is GenerationStatus.ERROR:
+                METRICS.request_errors.inc()
+                raise ValueError(getattr(out, "error", None) or "the request could not be served")
             now = time.perf_counter()
             if out.tokens:
                 if t_last is None:

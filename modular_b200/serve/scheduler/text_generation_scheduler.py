@@ -86,6 +86,8 @@ class TokenGenerationScheduler:
         self.total_steps = 0
         self._cache_seen = (0, 0)        # (hit tokens, queried tokens) already reported
         self._spec_seen = (0, 0, 0, 0)   # speculative-decoding counters already reported
+        self._gate = None                # grammar compilations off the scheduler thread (created on first use)
+        self._compiling: dict[str, TextContext] = {}
         # requests with task == "embed" are answered by an embeddings scheduler when the model can encode
         self.embeddings = None
         model = getattr(pipeline, "model", None)
@@ -122,9 +124,43 @@ class TokenGenerationScheduler:
                     n += 1
                     continue
             self._contexts[ctx.request_id] = ctx
+            if ctx.sampling_params.response_format is not None and ctx.grammar_state is None:
+                # constrained request: its grammar is compiled off this thread and the request joins the prefill
+                # queue when that is done; a grammar that does not compile fails this request only
+                backend = getattr(self.pipeline, "structured", None)
+                if backend is None:
+                    self._fail(ctx, "this server was started without structured output (response_format)")
+                    n += 1
+                    continue
+                if self._gate is None:
+                    from ...pipelines.structured_output import GrammarGate
+
+                    self._gate = GrammarGate(backend)
+                self._gate.submit(ctx)
+                self._compiling[ctx.request_id] = ctx
+                n += 1
+                continue
             self.batch_constructor.enqueue_new_request(ctx)
             n += 1
         return n
+
+    def _fail(self, ctx: TextContext, message: str) -> None:
+        self._contexts.pop(ctx.request_id, None)
+        self.response_queue.put_nowait({ctx.request_id: TextGenerationOutput(
+            ctx.request_id, [], GenerationStatus.ERROR, None, message)})
+
+    def _admit_compiled(self) -> None:
+        """Requests whose grammar compilation has finished: into the prefill queue, or failed with the reason."""
+        for rid in [r for r, c in self._compiling.items() if self._gate.ready(c)]:
+            ctx = self._compiling.pop(rid)
+            if rid not in self._contexts:       # cancelled meanwhile
+                self._gate.release(rid)
+                continue
+            err = self._gate.install(ctx)
+            if err is not None:
+                self._fail(ctx, err)
+            else:
+                self.batch_constructor.enqueue_new_request(ctx)
 
     def _handle_cancels(self) -> None:
         while True:
@@ -138,6 +174,8 @@ class TokenGenerationScheduler:
                     self.embeddings.cancel(rid)
                 continue
             ctx.status = GenerationStatus.CANCELLED
+            if self._compiling.pop(rid, None) is not None and self._gate is not None:
+                self._gate.release(rid)
             self.batch_constructor.release_request(rid)
             self.response_queue.put_nowait({rid: TextGenerationOutput(rid, [], GenerationStatus.CANCELLED)})
 
@@ -146,7 +184,7 @@ class TokenGenerationScheduler:
 
     def has_work(self) -> bool:
         return (self.batch_constructor.num_requests() > 0 or bool(self.batch_constructor.draining)
-                or self.pipeline.has_pending() or bool(self.embeddings is not None and self.embeddings.pending))
+                or bool(self._compiling) or self.pipeline.has_pending() or bool(self.embeddings is not None and self.embeddings.pending))
 
     # ------------------------------------------------------------ one iteration
     def _finish(self, outputs: dict) -> None:
@@ -162,6 +200,8 @@ class TokenGenerationScheduler:
 
     def run_iteration(self) -> SchedulerProgress:
         self._drain_requests()
+        if self._compiling:
+            self._admit_compiled()
         t0 = time.perf_counter()
         embedded = self.embeddings.run_iteration() if self.embeddings is not None else 0
         batch = self.batch_constructor.construct_batch()

@@ -61,7 +61,8 @@ def _ctx_from_wire(m: dict) -> TextContext:
 def _out_to_wire(o) -> list:
     if isinstance(o, EmbeddingsOutput):
         return ["emb", o.request_id, [float(x) for x in o.embedding], o.prompt_tokens]
-    return ["gen", o.request_id, [int(t) for t in o.tokens], o.final_status.value, _plain(o.log_probabilities)]
+    return ["gen", o.request_id, [int(t) for t in o.tokens], o.final_status.value, _plain(o.log_probabilities),
+            getattr(o, "error", None)]
 
 
 def _out_from_wire(w: list):
@@ -70,7 +71,7 @@ def _out_from_wire(w: list):
     lps = w[4]
     if lps is not None:
         lps = [dict(e, top=[tuple(p) for p in e.get("top", [])]) if isinstance(e, dict) else e for e in lps]
-    return TextGenerationOutput(w[1], w[2], GenerationStatus(w[3]), lps)
+    return TextGenerationOutput(w[1], w[2], GenerationStatus(w[3]), lps, w[5] if len(w) > 5 else None)
 
 
 def encode(obj) -> bytes:

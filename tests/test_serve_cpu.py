@@ -546,3 +546,24 @@ def test_request_profiling_is_opt_in(tmp_path):
     with TestClient(off) as c:
         r = c.post("/v1/completions?profile=1", json={"model": "echo", "prompt": "hi", "max_tokens": 2})
         assert r.status_code == 200 and "x-profile-file" not in r.headers
+
+
+def test_uncompilable_grammar_fails_the_request_not_the_server():
+    pytest.importorskip("xgrammar")
+    pc = _config(model_path="preset:tiny-llama", devices="cpu", max_length=256, max_batch_size=4,
+                 max_batch_input_tokens=128, kv_cache_page_size=16, enable_structured_output=True)
+    tokenizer, factory = PIPELINE_REGISTRY.retrieve_factory(pc)
+    app = fastapi_app(Settings(), pc, tokenizer, factory, "tiny", 256)
+    bad_schema = {"type": "object", "properties": {"a": {"$ref": "#/nope"}}}
+    with TestClient(app) as c:
+        msgs = [{"role": "user", "content": "hi"}]
+        bad = c.post("/v1/chat/completions", json={"model": "tiny", "messages": msgs, "max_tokens": 8, "response_format": {
+            "type": "json_schema", "json_schema": {"name": "x", "schema": bad_schema}}})
+        assert bad.status_code == 400 and "cannot be compiled" in bad.json()["error"]["message"]
+        good = c.post("/v1/chat/completions", json={"model": "tiny", "messages": msgs, "max_tokens": 24, "temperature": 0,
+                                                    "response_format": {"type": "json_schema", "json_schema": {
+                                                        "name": "y", "schema": {"properties": {"ok": {"type": "boolean"}},
+                                                                                "required": ["ok"]}}}})
+        assert good.status_code == 200
+        plain = c.post("/v1/chat/completions", json={"model": "tiny", "messages": msgs, "max_tokens": 4, "temperature": 0})
+        assert plain.status_code == 200 and plain.json()["usage"]["completion_tokens"] == 4
