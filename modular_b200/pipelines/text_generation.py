@@ -507,6 +507,10 @@ class TextGenerationPipeline:
     def has_pending(self) -> bool:
         return self._pending is not None
 
+    def abort_pending(self) -> None:
+        """Forget a launched step whose results nobody will collect (its requests were failed by the caller)."""
+        self._pending = None
+
     def release(self, request_id: str) -> None:
         self.kv.release(request_id)
         if self.draft is not None:

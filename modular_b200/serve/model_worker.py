@@ -239,7 +239,17 @@ def model_worker_main(factory: Callable, pipeline_config, queue_specs: dict, set
                 if any(not p.is_alive() for p in followers):
                     raise RuntimeError("a tensor-parallel rank died")
                 feed.exchange(_drain(queues.request, cfg.max_pending_requests), _drain(queues.cancel, 0))
-            progress = sched.run_iteration()
+            try:
+                progress = sched.run_iteration()
+            except Exception as e:      # noqa: BLE001
+                # a single-process engine answers the requests it held with an error and goes on, as long as the
+                # device still responds; ranks that step in lock-step cannot (the others are mid-step): they end
+                if feed is not None or not hasattr(sched, "recover"):
+                    raise
+                logger.exception("a scheduler step failed; failing its requests and continuing")
+                if not sched.recover(f"internal error in the model worker: {type(e).__name__}"):
+                    raise
+                progress = SchedulerProgress.MADE_PROGRESS
             side.service(handlers)
             if progress is SchedulerProgress.NO_PROGRESS:
                 idle = min(idle + 1, 50)

@@ -149,6 +149,34 @@ class TokenGenerationScheduler:
         self.response_queue.put_nowait({ctx.request_id: TextGenerationOutput(
             ctx.request_id, [], GenerationStatus.ERROR, None, message)})
 
+    def recover(self, message: str) -> bool:
+        """After an exception inside a step: every request this scheduler knows fails with ``message``, pages and
+        queues are released and the in-flight step is forgotten, so the worker can serve what comes next. False
+        when the device no longer answers (the caller should then let the process end)."""
+        for rid, ctx in list(self._contexts.items()):
+            try:
+                self.batch_constructor.release_request(rid, ctx)
+            except Exception:      # noqa: BLE001 - the bookkeeping of a broken step may be half done
+                pass
+            self._fail(ctx, message)
+        self._contexts.clear()
+        if self._gate is not None:
+            for rid in list(self._compiling):
+                self._gate.release(rid)
+        self._compiling.clear()
+        bc = self.batch_constructor
+        bc.ce_reqs.clear(), bc.tg_reqs.clear(), bc.draining.clear()
+        if hasattr(self.pipeline, "abort_pending"):
+            self.pipeline.abort_pending()
+        try:
+            import torch
+
+            if torch.cuda.is_available() and getattr(self.pipeline, "on_gpu", False):
+                torch.cuda.synchronize()
+        except Exception:          # noqa: BLE001 - a sticky device error: nothing can run in this process any more
+            return False
+        return True
+
     def _admit_compiled(self) -> None:
         """Requests whose grammar compilation has finished: into the prefill queue, or failed with the reason."""
         for rid in [r for r, c in self._compiling.items() if self._gate.ready(c)]:

@@ -567,3 +567,43 @@ def test_uncompilable_grammar_fails_the_request_not_the_server():
         assert good.status_code == 200
         plain = c.post("/v1/chat/completions", json={"model": "tiny", "messages": msgs, "max_tokens": 4, "temperature": 0})
         assert plain.status_code == 200 and plain.json()["usage"]["completion_tokens"] == 4
+
+
+def test_a_failing_step_fails_its_requests_and_the_worker_goes_on():
+    """An exception inside a scheduler step answers the requests in flight with an error; later requests are served."""
+    import torch
+
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.models.llama3 import Llama3Config
+    from modular_b200.pipelines.context import GenerationStatus, SamplingParams, TextContext
+
+    cfg = Llama3Config.tiny(num_hidden_layers=1, vocab_size=64)
+    llm = LLM(cfg, device="cpu", dtype=torch.float32, max_length=64, max_batch_size=4, max_batch_input_tokens=32,
+              page_size=16, num_kv_pages=16)
+    sched = llm.scheduler
+    sp = SamplingParams(temperature=0.0, max_new_tokens=3, ignore_eos=True)
+    real = llm.pipeline.execute
+    calls = {"n": 0}
+
+    def flaky(batch):
+        calls["n"] += 1
+        if calls["n"] == 2:
+            raise RuntimeError("boom")
+        return real(batch)
+
+    llm.pipeline.execute = flaky
+    sched.add_request(TextContext.from_prompt([1, 2, 3], 32, "a", sp))
+    sched.run_iteration()
+    with pytest.raises(RuntimeError):
+        sched.run_iteration()
+    assert sched.recover("internal error: RuntimeError") is True
+    outs = {}
+    while True:
+        try:
+            outs.update(sched.response_queue.get_nowait())
+        except Exception:      # noqa: BLE001
+            break
+    assert outs["a"].final_status is GenerationStatus.ERROR and "internal error" in outs["a"].error
+    assert not sched.has_work() and llm.kv.pool.used_blocks == 0
+    rec = llm.generate([[4, 5, 6]], sp)[0]
+    assert len(rec.tokens) == 3
