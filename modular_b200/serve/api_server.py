@@ -133,6 +133,13 @@ def make_lifespan(settings: Settings, pipeline_config, tokenizer, factory: Calla
                 for t in done:
                     t.result()          # re-raises SubprocessExit of the replica that died
 
+            # a replica that dies answers what waits on it with an error (503) instead of leaving it hanging
+            def _on_exit(task, p):
+                if not task.cancelled() and task.exception() is not None:
+                    p.abort_all(f"the model worker is gone: {task.exception()}")
+
+            for w, p in zip(watchers, proxies):
+                w.add_done_callback(lambda t, p=p: _on_exit(t, p))
             app.state.worker_watcher = watchers[0] if n_rep == 1 else asyncio.ensure_future(first_failure())
             app.state.proxy = proxy
             METRICS.pipeline_load.inc(n_rep)

@@ -75,6 +75,10 @@ class TokenGeneratorPipeline:
         async for out in self.proxy.stream(ctx):
             if out.final_status is GenerationStatus.ERROR:
                 METRICS.request_errors.inc()
+                if getattr(self.proxy, "dead", None):
+                    from ..worker_interface.interface import WorkerGone
+
+                    raise WorkerGone(self.proxy.dead)
                 raise ValueError(getattr(out, "error", None) or "the request could not be served")
             now = time.perf_counter()
             if out.tokens:

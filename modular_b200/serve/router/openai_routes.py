@@ -30,7 +30,7 @@ from ..schemas.openai import (ChatChoice, ChatChoiceMessage, ChatChunkChoice, Ch
                               ModelList, Usage, EmbeddingData, EmbeddingsRequest, EmbeddingsResponse,
                               LoadLoraRequest, UnloadLoraRequest)
 from ..telemetry.metrics import METRICS
-from ..worker_interface import RequestQueueFull
+from ..worker_interface import RequestQueueFull, WorkerGone
 
 logger = logging.getLogger("modular_b200.serve")
 
@@ -290,6 +290,8 @@ async def create_completion(req: CompletionRequest, request: Request):
         return CompletionResponse(id=cid, model=req.model, choices=choices, usage=usage)
     except RequestQueueFull as e:
         return error_response(429, str(e), "rate_limit_error")
+    except WorkerGone as e:
+        return error_response(503, str(e), "service_unavailable")
     except ValueError as e:
         return error_response(400, str(e))
 
@@ -436,6 +438,8 @@ async def create_chat_completion(req: ChatCompletionRequest, request: Request):
         return ChatCompletionResponse(id=cid, model=req.model, usage=usage, choices=choices)
     except RequestQueueFull as e:
         return error_response(429, str(e), "rate_limit_error")
+    except WorkerGone as e:
+        return error_response(503, str(e), "service_unavailable")
     except ValueError as e:
         return error_response(400, str(e))
 
@@ -471,6 +475,8 @@ async def create_embeddings(req: EmbeddingsRequest, request: Request):
             data.append(EmbeddingData(index=i, embedding=emb))
     except RequestQueueFull as e:
         return error_response(429, str(e), "rate_limit_error")
+    except WorkerGone as e:
+        return error_response(503, str(e), "service_unavailable")
     except ValueError as e:
         return error_response(400, str(e))
     return EmbeddingsResponse(data=data, model=req.model, usage=Usage(prompt_tokens=n_tok, total_tokens=n_tok))

@@ -7,4 +7,4 @@ zmq_interface.py:50; _zmq_queue.py).
 """
 
 from .zmq_queue import ZmqPullSocket, ZmqPushSocket, ZmqQueueSpec, generate_ipc_path  # noqa: F401
-from .interface import ModelWorkerProxy, ReplicaRouter, RequestQueueFull, WorkerQueues  # noqa: F401
+from .interface import ModelWorkerProxy, ReplicaRouter, RequestQueueFull, WorkerGone, WorkerQueues  # noqa: F401

@@ -12,6 +12,10 @@ class RequestQueueFull(RuntimeError):
     """More requests are pending than ``max_queue_size`` allows (mapped to HTTP 429)."""
 
 
+class WorkerGone(RuntimeError):
+    """The model worker process behind a proxy has exited (mapped to HTTP 503)."""
+
+
 @dataclass
 class WorkerQueues:
     request: Any
@@ -28,6 +32,7 @@ class ModelWorkerProxy:
         self.poll_s = poll_s
         self._streams: dict[str, asyncio.Queue] = {}
         self._task: Optional[asyncio.Task] = None
+        self.dead: Optional[str] = None      # set by abort_all
 
     def start(self) -> None:
         if self._task is None:
@@ -67,6 +72,8 @@ class ModelWorkerProxy:
 
     async def stream(self, ctx) -> AsyncIterator:
         """Submit ``ctx`` and yield TextGenerationOutput chunks until the final one."""
+        if self.dead is not None:
+            raise WorkerGone(self.dead)
         if self.max_queue_size and len(self._streams) >= self.max_queue_size:
             raise RequestQueueFull(f"{len(self._streams)} requests pending (limit {self.max_queue_size})")
         q: asyncio.Queue = asyncio.Queue()
@@ -85,6 +92,15 @@ class ModelWorkerProxy:
                     self.queues.cancel.put_nowait(ctx.request_id)
                 except Exception:  # noqa: BLE001
                     pass
+
+    def abort_all(self, message: str) -> None:
+        """The worker behind this proxy is gone: every waiting request ends with an error, and requests that arrive
+        later are refused at once instead of waiting for an answer that cannot come."""
+        from ...pipelines.context import GenerationStatus, TextGenerationOutput
+
+        self.dead = message
+        for rid, q in list(self._streams.items()):
+            q.put_nowait(TextGenerationOutput(rid, [], GenerationStatus.ERROR, None, message))
 
     def cancel(self, request_id: str) -> None:
         self.queues.cancel.put_nowait(request_id)

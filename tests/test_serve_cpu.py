@@ -607,3 +607,36 @@ def test_a_failing_step_fails_its_requests_and_the_worker_goes_on():
     assert not sched.has_work() and llm.kv.pool.used_blocks == 0
     rec = llm.generate([[4, 5, 6]], sp)[0]
     assert len(rec.tokens) == 3
+
+
+def test_requests_get_503_when_the_model_worker_dies():
+    """Waiting requests and later ones are answered with an error when the worker process is gone."""
+    import asyncio
+
+    from modular_b200.pipelines.context import SamplingParams, TextContext
+    from modular_b200.serve.worker_interface.interface import ModelWorkerProxy, WorkerGone, WorkerQueues
+    import queue
+
+    async def run():
+        q = WorkerQueues(queue.SimpleQueue(), queue.SimpleQueue(), queue.SimpleQueue())
+        proxy = ModelWorkerProxy(q)
+        proxy.start()
+        ctx = TextContext.from_prompt([1, 2, 3], 16, "r1", SamplingParams(max_new_tokens=4))
+        got = []
+
+        async def consume():
+            async for out in proxy.stream(ctx):
+                got.append(out)
+
+        task = asyncio.create_task(consume())
+        await asyncio.sleep(0.05)                   # the request is waiting: nobody answers
+        assert proxy.pending == 1 and not task.done()
+        proxy.abort_all("the model worker is gone: exit code 1")
+        await asyncio.wait_for(task, 2.0)
+        assert got and got[-1].is_done and "gone" in got[-1].error
+        with pytest.raises(WorkerGone):
+            async for _ in proxy.stream(TextContext.from_prompt([1], 16, "r2", SamplingParams(max_new_tokens=1))):
+                pass
+        await proxy.stop()
+
+    asyncio.run(run())
