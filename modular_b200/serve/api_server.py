@@ -234,11 +234,27 @@ def fastapi_app(settings: Settings, pipeline_config=None, tokenizer=None, factor
         logger.exception("unhandled error")
         return error_response(500, f"{type(exc).__name__}: {exc}", "server_error")
 
-    @app.get("/health")
-    async def health():
+    def _readiness():
+        """200 while a model worker can take requests; 503 while it starts and after it has exited."""
         if app.state.pipeline is None:
             return JSONResponse(status_code=503, content={"status": "starting"})
+        proxy = getattr(app.state, "proxy", None)
+        gone = getattr(proxy, "dead", None) if proxy is not None else None      # a router: once all replicas are gone
+        if gone:
+            return JSONResponse(status_code=503, content={"status": "unavailable", "reason": gone})
         return {"status": "ok"}
+
+    @app.get("/health")
+    async def health():
+        return _readiness()
+
+    @app.get("/health/ready")
+    async def health_ready():
+        return _readiness()
+
+    @app.get("/health/live")
+    async def health_live():
+        return {"status": "ok"}      # the API process answers
 
     @app.get("/version")
     async def version():

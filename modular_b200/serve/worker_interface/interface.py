@@ -144,9 +144,16 @@ class ReplicaRouter:
     def pending(self) -> int:
         return sum(p.pending for p in self.proxies)
 
+    @property
+    def dead(self) -> Optional[str]:
+        """Set once every replica is gone (one dead replica only stops receiving requests)."""
+        gone = [p.dead for p in self.proxies]
+        return gone[0] if all(gone) else None
+
     def pick(self) -> int:
         n = len(self.proxies)
-        best = min(range(n), key=lambda i: (self.proxies[i].pending, (i - self._rr) % n))
+        alive = [i for i in range(n) if self.proxies[i].dead is None] or list(range(n))
+        best = min(alive, key=lambda i: (self.proxies[i].pending, (i - self._rr) % n))
         self._rr = (best + 1) % n
         return best
 

@@ -98,6 +98,8 @@ def test_worker_rpc(echo_client):
                  b"maxserve_batch_generation_throughput", b"maxserve_cache_preemption_count"):
         assert name in body
     assert echo_client.post("/reset_prefix_cache").json() == {"success": False}  # echo has no cache
+    assert echo_client.get("/health/live").json() == {"status": "ok"}
+    assert echo_client.get("/health/ready").status_code == 200
 
 
 def test_tiny_llama_server():
@@ -638,5 +640,15 @@ def test_requests_get_503_when_the_model_worker_dies():
             async for _ in proxy.stream(TextContext.from_prompt([1], 16, "r2", SamplingParams(max_new_tokens=1))):
                 pass
         await proxy.stop()
+        # replicas: a dead one stops receiving requests; the router is dead once all are
+        from modular_b200.serve.worker_interface.interface import ReplicaRouter
+
+        a = ModelWorkerProxy(WorkerQueues(queue.SimpleQueue(), queue.SimpleQueue(), queue.SimpleQueue()))
+        b = ModelWorkerProxy(WorkerQueues(queue.SimpleQueue(), queue.SimpleQueue(), queue.SimpleQueue()))
+        router = ReplicaRouter([a, b])
+        a.abort_all("gone")
+        assert router.dead is None and all(router.pick() == 1 for _ in range(4))
+        b.abort_all("gone too")
+        assert router.dead == "gone"
 
     asyncio.run(run())
