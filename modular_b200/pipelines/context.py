@@ -60,6 +60,10 @@ class SamplingParams:
     logit_bias: Optional[dict] = None
 
     def __post_init__(self):
+        # any integer is a seed; 40 bits of it are kept (it is multiplied by a 20-bit constant into an int64 stream id)
+        self.seed = int(self.seed or 0) & 0xFFFFFFFFFF
+        if self.max_new_tokens is not None and self.max_new_tokens < 0:
+            raise ValueError("max_new_tokens must not be negative")
         if self.logit_bias:
             try:
                 self.logit_bias = {int(k): float(v) for k, v in self.logit_bias.items()}

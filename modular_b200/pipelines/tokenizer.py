@@ -46,6 +46,12 @@ class PipelineTokenizer:
             raise ValueError("prompt encodes to zero tokens")
         if len(ids) >= max_length:
             raise ValueError(f"prompt has {len(ids)} tokens, max_length is {max_length}")
+        if not isinstance(prompt, str):
+            # ids a client sends directly index the embedding table: they must lie inside the vocabulary
+            vocab = int(getattr(self, "vocab_size", 0) or 0)
+            lo, hi = min(ids), max(ids)
+            if lo < 0 or (vocab and hi >= vocab):
+                raise ValueError(f"prompt token ids must be in [0, {vocab or 'vocab size'}); got {lo if lo < 0 else hi}")
         sp = sampling_params or SamplingParams()
         if sp.stop:
             # single-token stop strings become stop ids; longer ones are matched on text downstream

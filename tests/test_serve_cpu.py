@@ -652,3 +652,20 @@ def test_requests_get_503_when_the_model_worker_dies():
         assert router.dead == "gone"
 
     asyncio.run(run())
+
+
+def test_odd_requests_get_an_answer_and_leave_the_worker_alone():
+    """Ids outside the vocabulary, a negative token budget and an enormous seed are answered (400 or a normal
+    completion); none of them reaches the worker as something it cannot pack."""
+    pc = _config(model_path="preset:tiny-llama", devices="cpu", max_length=64, max_batch_size=4,
+                 max_batch_input_tokens=32, kv_cache_page_size=16)
+    tokenizer, factory = PIPELINE_REGISTRY.retrieve_factory(pc)
+    app = fastapi_app(Settings(), pc, tokenizer, factory, "tiny", 64)
+    with TestClient(app) as c:
+        post = lambda **kw: c.post("/v1/completions", json=dict(kw, model="tiny"))
+        assert post(prompt=[5, 99999999], max_tokens=2).status_code == 400
+        assert post(prompt=[5, -4], max_tokens=2).status_code == 400
+        assert post(prompt=[5, 6], max_tokens=-3).status_code == 400
+        big = post(prompt=[5, 6], max_tokens=2, seed=2 ** 62, temperature=1.0)
+        assert big.status_code == 200 and big.json()["usage"]["completion_tokens"] == 2
+        assert c.get("/health/ready").status_code == 200
