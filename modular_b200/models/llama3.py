@@ -49,6 +49,10 @@ class Llama3Config:
     residual_multiplier: float = 1.0  # Granite: scale of every block output, folded into the o / down projections
     attention_bias: bool = False      # bias on the query / key / value projections (Qwen2)
     qk_norm: bool = False             # RMSNorm over head_dim on every query and key head before the rotation (Qwen3)
+    qk_norm_full: bool = False        # with qk_norm: one RMSNorm over the whole query / key projection (OLMo 2)
+    norm_after: bool = False          # norms on the block outputs (before the residual add) instead of the inputs (OLMo 2)
+    plain_layer_norm: bool = False    # LayerNorm without weight or bias (eps 1e-5) in place of every RMSNorm (OLMo)
+    clip_qkv: Optional[float] = None  # queries, keys and values clamped to [-clip, clip] after the projection (OLMo)
     # mixture-of-experts feed-forward (Mixtral, Qwen3-MoE): 0 experts = dense SwiGLU MLP in every layer
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -255,6 +259,67 @@ class GraniteConfig(Llama3Config):
 
 
 @dataclass
+class OlmoConfig(Llama3Config):
+    """OLMo (``OlmoForCausalLM``): the Llama layer with a LayerNorm without weight or bias in place of every
+    RMSNorm, and the query / key / value projections clamped to ``[-clip_qkv, clip_qkv]`` where the checkpoint
+    asks for it. Reference: max/python/max/pipelines/architectures/olmo/."""
+
+    rope_theta: float = 10000.0
+    max_position_embeddings: int = 2048
+    plain_layer_norm: bool = True
+    architectures: tuple = ("OlmoForCausalLM",)
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "OlmoConfig":
+        cfg = super().from_hf(d)
+        cfg.plain_layer_norm = True
+        cfg.clip_qkv = float(d["clip_qkv"]) if d.get("clip_qkv") else None
+        return cfg
+
+    def to_hf(self) -> dict:
+        d = super().to_hf()
+        d["model_type"] = "olmo"
+        return d
+
+
+@dataclass
+class Olmo2Config(Llama3Config):
+    """OLMo 2 and OLMo 3 (``Olmo2ForCausalLM``, ``Olmo3ForCausalLM``): Llama projections in another order - no norm
+    on the block inputs, an RMSNorm on every block output before it joins the residual stream, and one RMSNorm over
+    the whole query and the whole key projection before the rotation. OLMo 3 adds a sliding window on three layers
+    out of four, which is served up to the window length.
+    Reference: max/python/max/pipelines/architectures/olmo2/, olmo3/."""
+
+    rope_theta: float = 500000.0
+    rms_norm_eps: float = 1e-6
+    max_position_embeddings: int = 4096
+    qk_norm: bool = True
+    qk_norm_full: bool = True
+    norm_after: bool = True
+    architectures: tuple = ("Olmo2ForCausalLM",)
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "Olmo2Config":
+        cfg = super().from_hf(d)
+        cfg.qk_norm = cfg.qk_norm_full = cfg.norm_after = True
+        if "sliding_attention" in (d.get("layer_types") or ()):
+            _cap_to_window(cfg, d.get("sliding_window"))
+        return cfg
+
+    @classmethod
+    def tiny(cls, **kw) -> "Olmo2Config":
+        base = dict(hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, vocab_size=4096, max_position_embeddings=2048)
+        base.update(kw)
+        return cls(**base)
+
+    def to_hf(self) -> dict:
+        d = super().to_hf()
+        d["model_type"] = "olmo2"
+        return d
+
+
+@dataclass
 class MixtralConfig(Llama3Config):
     """Mixtral (``MixtralForCausalLM``): Llama attention with a mixture-of-experts feed-forward in every layer -
     softmax over all experts, top-k, weights renormalised. ``intermediate_size`` is the size of one expert.
@@ -424,8 +489,10 @@ class Llama3Weights:
                 wgu=None if moe is not None else rnd(2 * cfg.intermediate_size, cfg.hidden_size),
                 wd=None if moe is not None else rnd(cfg.hidden_size, cfg.intermediate_size), moe=moe,
                 qkv_bias=rnd(cfg.q_dim + 2 * cfg.kv_dim) if cfg.attention_bias else None,
-                q_norm=torch.ones(cfg.head_dim, dtype=dtype, device=dev) if cfg.qk_norm else None,
-                k_norm=torch.ones(cfg.head_dim, dtype=dtype, device=dev) if cfg.qk_norm else None))
+                q_norm=torch.ones(cfg.q_dim if cfg.qk_norm_full else cfg.head_dim, dtype=dtype, device=dev)
+                if cfg.qk_norm else None,
+                k_norm=torch.ones(cfg.kv_dim if cfg.qk_norm_full else cfg.head_dim, dtype=dtype, device=dev)
+                if cfg.qk_norm else None))
         final_norm = torch.ones(cfg.hidden_size, dtype=dtype, device=dev)
         lm_head = embed if cfg.tie_word_embeddings else rnd(cfg.vocab_size, cfg.hidden_size)
         return cls(embed, layers, final_norm, lm_head)
@@ -494,6 +561,19 @@ class Llama3Weights:
         """``keep_fp8``: block-scaled fp8 projections (``<name>`` e4m3 + ``<name>_scale_inv``) stay fp8 when the
         fused row blocks line up with the 128-row scale blocks; otherwise they are expanded to ``dtype``."""
         sd = _split_fused_projections(cfg, adapt_hf_state_dict(sd))
+        if cfg.plain_layer_norm:
+            # norms without parameters: nothing in the checkpoint; the slots hold ones and are not read
+            one = torch.ones(cfg.hidden_size)
+            sd = dict(sd)
+            for i in range(cfg.num_hidden_layers):
+                sd.setdefault(f"layers.{i}.input_layernorm.weight", one)
+                sd.setdefault(f"layers.{i}.post_attention_layernorm.weight", one)
+            sd.setdefault("norm.weight", one)
+        if cfg.norm_after:
+            # the two norms of a layer sit on the block outputs: the attention one is kept where the input norm of
+            # the attention block is otherwise, the feed-forward one where the input norm of the MLP is
+            sd = {k.replace(".post_attention_layernorm.", ".input_layernorm.")
+                  .replace(".post_feedforward_layernorm.", ".post_attention_layernorm."): v for k, v in sd.items()}
         # parameters this family has no place for must not be dropped silently
         extra = [k for k in sd if k.endswith((".o_proj.bias", ".gate_proj.bias", ".up_proj.bias", ".down_proj.bias"))
                  and bool(torch.count_nonzero(sd[k]))]
@@ -619,6 +699,11 @@ class Llama3Weights:
             g, u = torch.split(l.wgu, cfg.intermediate_size, dim=0)
             sd.update({p + "mlp.gate_proj.weight": g, p + "mlp.up_proj.weight": u,
                        p + "mlp.down_proj.weight": l.wd})
+        if cfg.plain_layer_norm:
+            sd = {k: v for k, v in sd.items() if not k.endswith(("layernorm.weight", "model.norm.weight"))}
+        if cfg.norm_after:
+            sd = {k.replace(".post_attention_layernorm.", ".post_feedforward_layernorm.")
+                  .replace(".input_layernorm.", ".post_attention_layernorm."): v for k, v in sd.items()}
         return {k: v.contiguous() for k, v in sd.items()}
 
 
@@ -707,6 +792,11 @@ class Llama3Model:
             self.use_executor = False
             if tp is not None and tp.world > 1:
                 raise ValueError("tensor parallelism is not implemented for mixture-of-experts layers of this family")
+        if cfg.norm_after or cfg.qk_norm_full or cfg.plain_layer_norm or cfg.clip_qkv:
+            # another layer order than the native step executor runs
+            self.use_executor = False
+            if tp is not None and tp.world > 1:
+                raise ValueError("tensor parallelism is not implemented for the OLMo layer variants")
         self.fuse_swiglu = fuse_swiglu
         self.executor = None
         self.logits_buf = None
@@ -821,7 +911,7 @@ class Llama3Model:
         cross-check for the executor on GPU). Returns fp32 logits [len(logit_rows), vocab]."""
         h = self.forward_hidden(tokens, positions, slots, block_table, q_start, q_len, kv_len, plan=plan, lora=lora)
         last = h[logit_rows.long()]
-        xn = ops.rms_norm(last, self.w.final_norm, self.cfg.rms_norm_eps)
+        xn = self._norm(last, self.w.final_norm)
         logits = ops.linear(xn, self.w.lm_head, out_dtype=torch.float32)
         return logits.float()
 
@@ -833,9 +923,13 @@ class Llama3Model:
         if lora is not None and not lora.active:
             lora = None
         if lora is not None:
+            if c.norm_after or c.plain_layer_norm or c.clip_qkv:
+                raise ValueError("LoRA adapters are not implemented for the OLMo layer variants")
             return self._forward_hidden_lora(tokens, positions, slots, block_table, q_start, q_len, kv_len, plan,
                                              self.kv if kv is None else kv, lora)
         kv = self.kv if kv is None else kv
+        if c.norm_after or c.plain_layer_norm or c.clip_qkv:
+            return self._forward_hidden_olmo(tokens, positions, slots, block_table, q_start, q_len, kv_len, plan, kv)
         h = ops.embedding(tokens, self.w.embed)
         for li, l in enumerate(self.w.layers):
             kc, vc = kv[:, 0, li], kv[:, 1, li]
@@ -876,11 +970,55 @@ class Llama3Model:
             h = ops.linear(act, l.wd, residual=h)
         return h
 
+    def _norm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """The model's norm: RMSNorm with weight ``w``, or (OLMo) a LayerNorm without parameters, computed in fp32."""
+        if self.cfg.plain_layer_norm:
+            return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), None, None, 1e-5).to(x.dtype)
+        return ops.rms_norm(x, w, self.cfg.rms_norm_eps)
+
+    def _forward_hidden_olmo(self, tokens, positions, slots, block_table, q_start, q_len, kv_len, plan, kv):
+        """The OLMo layer variants, op by op. OLMo: input norms without parameters and clamped projections.
+        OLMo 2 / 3: no input norms, ``h += norm(attn(h)); h += norm(mlp(h))`` with the norms on the block outputs.
+        Reference: max/python/max/pipelines/architectures/olmo/, olmo2/."""
+        c = self.cfg
+        h = ops.embedding(tokens, self.w.embed)
+        for li, l in enumerate(self.w.layers):
+            if l.is_fp8 or l.moe is not None or l.qkv_bias is not None:
+                raise ValueError("the OLMo layer variants are implemented for dense bf16 / fp32 weights without bias")
+            kc, vc = kv[:, 0, li], kv[:, 1, li]
+            x = h if c.norm_after else self._norm(h, l.attn_norm)
+            qkv = ops.linear(x, l.wqkv)
+            if c.clip_qkv:
+                qkv.clamp_(-c.clip_qkv, c.clip_qkv)
+            self._qk_norm(qkv, l)
+            ops.rope_kv_store(qkv, positions, slots, self.cos_sin, kc, vc, c.num_attention_heads,
+                              c.num_key_value_heads, c.head_dim, False)
+            a = ops.paged_attention(qkv, kc, vc, block_table, q_start, q_len, kv_len, c.num_attention_heads,
+                                    c.num_key_value_heads, c.head_dim, self.scale, plan=plan)
+            if c.norm_after:
+                h = h + self._norm(ops.linear(a, l.wo), l.attn_norm)
+                x = h
+            else:
+                h = ops.linear(a, l.wo, residual=h)
+                x = self._norm(h, l.mlp_norm)
+            act = ops.linear_swiglu(x, l.wgu) if self.fuse_swiglu else ops.silu_mul(ops.linear(x, l.wgu))
+            if c.norm_after:
+                h = h + self._norm(ops.linear(act, l.wd), l.mlp_norm)
+            else:
+                h = ops.linear(act, l.wd, residual=h)
+        return h
+
     def _qk_norm(self, qkv: torch.Tensor, l) -> None:
-        """Per-head RMSNorm of the query and key heads of a fused projection, in place (Qwen3)."""
+        """RMSNorm of the queries and keys of a fused projection, in place: per head (Qwen3) or over the whole
+        projection (OLMo 2)."""
         if l.q_norm is None:
             return
         c = self.cfg
+        if c.qk_norm_full:
+            qd, kd = c.q_dim, c.kv_dim
+            qkv[:, :qd] = ops.rms_norm(qkv[:, :qd].contiguous(), l.q_norm, c.rms_norm_eps)
+            qkv[:, qd:qd + kd] = ops.rms_norm(qkv[:, qd:qd + kd].contiguous(), l.k_norm, c.rms_norm_eps)
+            return
         ops.qk_norm(qkv, l.q_norm, l.k_norm, c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rms_norm_eps)
 
     def _forward_hidden_lora(self, tokens, positions, slots, block_table, q_start, q_len, kv_len, plan, kv, lora):
@@ -944,7 +1082,7 @@ class Llama3Model:
         tokens = torch.tensor([t for tl in token_lists for t in tl], dtype=torch.long, device=dev)
         h = self.forward_hidden(tokens, torch.cat(positions).int().to(dev), torch.cat(slots).to(dev), bt.to(dev),
                                 q_start.to(dev), q_len.to(dev), q_len.to(dev), kv=kv)
-        hn = ops.rms_norm(h, self.w.final_norm, c.rms_norm_eps).float()
+        hn = self._norm(h, self.w.final_norm).float()
         out = torch.empty(len(lens), c.hidden_size, dtype=torch.float32, device=dev)
         for i, (s0, n) in enumerate(zip(q_start.tolist(), lens)):
             out[i] = hn[s0 + n - 1] if pooling == "last" else hn[s0:s0 + n].mean(0)

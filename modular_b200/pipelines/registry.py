@@ -291,6 +291,18 @@ def _register_builtin() -> None:
         name="GraniteForCausalLM", config_class=GraniteConfig, weights_class=Llama3Weights, model_class=Llama3Model,
         default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"),
         example_repo_ids=("ibm-granite/granite-3.3-8b-instruct",), preset_configs={}), allow_override=True)
+    from ..models.llama3 import Olmo2Config, OlmoConfig
+
+    # OLMo: parameter-free LayerNorms and clamped projections. OLMo 2 / 3: Llama projections with the norms on the
+    # block outputs and over the whole query / key projection. Both run op by op
+    for name, cc, repos in (("OlmoForCausalLM", OlmoConfig, ("allenai/OLMo-7B-0724-Instruct-hf",)),
+                            ("Olmo2ForCausalLM", Olmo2Config, ("allenai/OLMo-2-1124-7B-Instruct",)),
+                            ("Olmo3ForCausalLM", Olmo2Config, ("allenai/Olmo-3-7B-Instruct",))):
+        PIPELINE_REGISTRY.register(SupportedArchitecture(
+            name=name, config_class=cc, weights_class=Llama3Weights, model_class=Llama3Model,
+            default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"), example_repo_ids=repos,
+            preset_configs={"tiny-olmo2": Olmo2Config.tiny} if name == "Olmo2ForCausalLM" else {}),
+            allow_override=True)
     from ..models.llama3 import Phi3Config
 
     # the Llama layer with the projections already fused in the checkpoint

@@ -1,7 +1,7 @@
 """Golden check against Hugging Face transformers on CPU: a randomly initialised HF model is saved as a checkpoint
 directory, served by this engine through the registry, and both must produce the same greedy tokens. Covers the Llama layer and its variants: Mistral (same tensors), Qwen2 (projection bias), Qwen3 (RMSNorm on
 every query and key head), Phi-3 (projections fused
-in the checkpoint), Mixtral and Qwen3-MoE (mixture-of-experts feed-forward), Granite (scalar multipliers folded into the weights)."""
+in the checkpoint), Mixtral and Qwen3-MoE (mixture-of-experts feed-forward), Granite (scalar multipliers folded into the weights), OLMo (LayerNorm without parameters, clamped projections) and OLMo 2 / 3 (norms on the block outputs and over the whole query / key projection)."""
 
 import json
 
@@ -57,6 +57,10 @@ CASES = {
     "granite": ("GraniteConfig", "GraniteForCausalLM", dict(rope_theta=10000.0, rms_norm_eps=1e-5,
                                                             embedding_multiplier=12.0, residual_multiplier=0.22,
                                                             attention_multiplier=0.0078125 * 16, logits_scaling=8.0)),
+    "olmo": ("OlmoConfig", "OlmoForCausalLM", dict(rope_theta=10000.0, clip_qkv=0.05, pad_token_id=0)),
+    "olmo2": ("Olmo2Config", "Olmo2ForCausalLM", dict(rope_theta=500000.0, rms_norm_eps=1e-6, pad_token_id=0)),
+    "olmo3": ("Olmo3Config", "Olmo3ForCausalLM", dict(rope_theta=500000.0, rms_norm_eps=1e-6, pad_token_id=0,
+                                                      sliding_window=256)),
     "phi3": ("Phi3Config", "Phi3ForCausalLM", dict(rope_theta=10000.0, rms_norm_eps=1e-5, sliding_window=None,
                                                    pad_token_id=0)),
 }
@@ -247,3 +251,30 @@ def test_deepseek_v2_matches_transformers(tmp_path, method):
     assert (ours - want).abs().max().item() < 1e-5
     with pytest.raises(ValueError):
         DeepseekV3Config.from_hf(dict(d, topk_method="something_else"))
+
+
+@pytest.mark.parametrize("pooling", ["last", "mean"])
+def test_embeddings_match_transformers_hidden_states(tmp_path, pooling):
+    """The embeddings path pools the final-normed hidden states: the same vectors as pooling transformers'
+    ``last_hidden_state`` (prompts of different lengths in one ragged batch)."""
+    torch.manual_seed(11)
+    hf_cfg = transformers.Qwen2Config(
+        hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+        vocab_size=320, max_position_embeddings=512, rope_theta=1e6, rms_norm_eps=1e-6, use_sliding_window=False)
+    hf = transformers.Qwen2ForCausalLM(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith(".bias") or n.endswith("norm.weight"):
+                p.add_(torch.randn_like(p) * 0.1)
+    d = hf_cfg.to_dict()
+    d["architectures"] = ["Qwen2ForCausalLM"]
+    _save(hf, d, tmp_path)
+    llm = _engine(tmp_path)
+    prompts = [[5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22], [200, 3, 17], [9]]
+    ours = llm.encode(prompts, pooling=pooling).cpu()
+    for i, p in enumerate(prompts):
+        with torch.no_grad():
+            hs = hf.model(torch.tensor([p])).last_hidden_state[0].float()
+        want = hs[-1] if pooling == "last" else hs.mean(0)
+        want = want / want.norm()
+        assert (ours[i] - want).abs().max().item() < 2e-4, (pooling, i)
