@@ -137,6 +137,9 @@ class LLM:
                 weights = fam.weights_class.random_init_ep(model_config, ep_rank, ep_size, self.device, dtype, seed=seed)
         elif weights is None:
             weights = fam.weights_class.random_init(model_config, self.device, dtype, seed=seed)
+        if speculative is not None and fam.name == "mamba":
+            # verifying a draft runs the rejected tokens through the recurrence too, and a state cannot be rolled back
+            raise ValueError("speculative decoding is not implemented for state-space models")
         self.weights = weights
         self.max_length = max_length
         # the draft model of speculative decoding comes first, so that the cache sizing below sees what it took

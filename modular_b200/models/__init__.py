@@ -55,9 +55,25 @@ def _deepseek_family() -> ModelFamily:
     return ModelFamily("deepseek_v3", DeepseekV3Config, DeepseekV3Weights, DeepseekV3Model, kv, act, supports_ep=True)
 
 
+def _mamba_family() -> ModelFamily:
+    from ..kv_cache import KVCacheParams
+    from .mamba import STATE_PAGE_TOKENS, MambaConfig, MambaModel, MambaWeights
+
+    def kv(cfg, page, dtype, prefix):
+        # a bookkeeping cache only (one 8-element row per token): the recurrent state lives in the model, one slot
+        # per first page, so pages are large and never shared by prefix
+        return KVCacheParams(1, 1, 8, max(page, STATE_PAGE_TOKENS), dtype, True, False)
+
+    def act(cfg, T, B):
+        return (T * (2 * cfg.hidden_size + 6 * cfg.intermediate_size) * 4 + B * cfg.vocab_size * 4
+                + 4 * B * cfg.state_bytes_per_slot() + (256 << 20))
+
+    return ModelFamily("mamba", MambaConfig, MambaWeights, MambaModel, kv, act)
+
+
 def family_for(config) -> ModelFamily:
     """The family that serves `config` (matched on the config class)."""
-    for make in (_llama_family, _deepseek_family):
+    for make in (_llama_family, _deepseek_family, _mamba_family):
         fam = make()
         if isinstance(config, fam.config_class):
             return fam

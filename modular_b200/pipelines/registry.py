@@ -303,6 +303,15 @@ def _register_builtin() -> None:
             default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"), example_repo_ids=repos,
             preset_configs={"tiny-olmo2": Olmo2Config.tiny} if name == "Olmo2ForCausalLM" else {}),
             allow_override=True)
+    from ..models.mamba import MambaConfig, MambaModel, MambaWeights
+
+    # selective state-space layers: a fixed-size recurrent state per request instead of a KV cache
+    PIPELINE_REGISTRY.register(SupportedArchitecture(
+        name="MambaForCausalLM", config_class=MambaConfig, weights_class=MambaWeights, model_class=MambaModel,
+        default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"),
+        example_repo_ids=("state-spaces/mamba-130m-hf", "state-spaces/mamba-2.8b-hf"),
+        preset_configs={"tiny-mamba": MambaConfig.tiny, "mamba-130m": MambaConfig.mamba_130m,
+                        "mamba-2.8b": MambaConfig.mamba_2_8b}), allow_override=True)
     from ..models.llama3 import Phi3Config
 
     # the Llama layer with the projections already fused in the checkpoint
