@@ -284,10 +284,13 @@ class LLM:
     def has_unfinished(self) -> bool:
         return self.scheduler.has_work() or not self.scheduler.request_queue.empty()
 
-    def encode(self, prompts: Sequence[Sequence[int]], pooling: str = "last") -> torch.Tensor:
-        """Pooled, L2-normalised embeddings of token-id prompts: fp32 [n, hidden]."""
+    def encode(self, prompts: Sequence[Sequence[int]], pooling: str = "default") -> torch.Tensor:
+        """Pooled, L2-normalised embeddings of token-id prompts: fp32 [n, hidden]. ``default`` is the model's own
+        pooling (the last token for decoders, the mean for encoders)."""
         if not hasattr(self.model, "encode"):
             raise NotImplementedError(f"{type(self.model).__name__} does not produce embeddings")
+        if pooling in (None, "default"):
+            pooling = getattr(self.model, "default_pooling", "last")
         return self.model.encode([list(p) for p in prompts], pooling)
 
     # ------------------------------------------------------------ batch API

@@ -71,9 +71,23 @@ def _mamba_family() -> ModelFamily:
     return ModelFamily("mamba", MambaConfig, MambaWeights, MambaModel, kv, act)
 
 
+def _bert_family() -> ModelFamily:
+    from ..kv_cache import KVCacheParams
+    from .bert import BertConfig, BertModel, BertWeights
+
+    def kv(cfg, page, dtype, prefix):
+        # encoders keep nothing between requests: a token-sized dummy cache for the engine's bookkeeping
+        return KVCacheParams(1, 1, 8, page, dtype, True, False)
+
+    def act(cfg, T, B):
+        return T * (8 * cfg.hidden_size + 2 * cfg.intermediate_size) * 4 + (256 << 20)
+
+    return ModelFamily("bert", BertConfig, BertWeights, BertModel, kv, act)
+
+
 def family_for(config) -> ModelFamily:
     """The family that serves `config` (matched on the config class)."""
-    for make in (_llama_family, _deepseek_family, _mamba_family):
+    for make in (_llama_family, _deepseek_family, _mamba_family, _bert_family):
         fam = make()
         if isinstance(config, fam.config_class):
             return fam

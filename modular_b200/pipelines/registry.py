@@ -312,6 +312,17 @@ def _register_builtin() -> None:
         example_repo_ids=("state-spaces/mamba-130m-hf", "state-spaces/mamba-2.8b-hf"),
         preset_configs={"tiny-mamba": MambaConfig.tiny, "mamba-130m": MambaConfig.mamba_130m,
                         "mamba-2.8b": MambaConfig.mamba_2_8b}), allow_override=True)
+    from ..models.bert import BertConfig, BertModel, BertWeights
+
+    # encoder-only embedding models (bidirectional attention; MPNet adds relative-position biases); embeddings only
+    for name, repos, presets in (
+            ("BertModel", ("sentence-transformers/all-MiniLM-L6-v2", "BAAI/bge-base-en-v1.5"), {"tiny-bert": BertConfig.tiny}),
+            ("MPNetForMaskedLM", ("sentence-transformers/all-mpnet-base-v2",), {}),
+            ("MPNetModel", ("sentence-transformers/all-mpnet-base-v2",), {})):
+        PIPELINE_REGISTRY.register(SupportedArchitecture(
+            name=name, config_class=BertConfig, weights_class=BertWeights, model_class=BertModel,
+            default_encoding="float32", supported_encodings=("float32", "bfloat16"), example_repo_ids=repos,
+            preset_configs=presets), allow_override=True)
     from ..models.llama3 import Phi3Config
 
     # the Llama layer with the projections already fused in the checkpoint

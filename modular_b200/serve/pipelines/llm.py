@@ -125,7 +125,7 @@ class TokenGeneratorPipeline:
             n_prompt, n_out = ch.prompt_tokens, ch.completion_tokens
         return TokenChunk(text, ids, reason, n_prompt, n_out, lps or None)
 
-    async def embed(self, prompt: Union[str, Sequence[int]], pooling: str = "last",
+    async def embed(self, prompt: Union[str, Sequence[int]], pooling: str = "default",
                     request_id: Optional[str] = None):
         """One pooled embedding; returns (vector, prompt_tokens)."""
         rid = request_id or uuid.uuid4().hex

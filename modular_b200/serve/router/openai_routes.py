@@ -465,7 +465,7 @@ async def create_embeddings(req: EmbeddingsRequest, request: Request):
     data, n_tok = [], 0
     try:
         for i, item in enumerate(inputs):
-            vec, n = await pipeline.embed(item, req.pooling or "last", f"{rid}-{i}")
+            vec, n = await pipeline.embed(item, req.pooling or "default", f"{rid}-{i}")
             if req.dimensions:
                 vec = vec[: req.dimensions]
                 norm = sum(v * v for v in vec) ** 0.5 or 1.0

@@ -93,12 +93,15 @@ class TokenGenerationScheduler:
         model = getattr(pipeline, "model", None)
         if model is not None and hasattr(model, "encode"):
             from .embeddings_scheduler import EmbeddingsScheduler
-            self.embeddings = EmbeddingsScheduler(model.encode, self.response_queue,
+            own = getattr(model, "default_pooling", "last")    # what a request that names no pooling gets
+            encode = lambda toks, pooling: model.encode(toks, own if pooling in (None, "default") else pooling)
+            self.embeddings = EmbeddingsScheduler(encode, self.response_queue,
                                                   config.target_tokens_per_batch_ce, config.max_batch_size)
 
     # ------------------------------------------------------------ queue plumbing
     def _drain_requests(self) -> int:
         n, limit = 0, self.config.max_pending_requests
+        model_generates = getattr(getattr(self.pipeline, "model", None), "generates", True)   # False: encoders
         while limit <= 0 or n < limit:
             try:
                 ctx = self.request_queue.get_nowait()
@@ -112,6 +115,10 @@ class TokenGenerationScheduler:
                         ctx.request_id, [], GenerationStatus.CANCELLED)})
                 else:
                     self.embeddings.enqueue(ctx)
+                n += 1
+                continue
+            if model_generates is False:
+                self._fail(ctx, "this model serves embeddings (/v1/embeddings), not generation")
                 n += 1
                 continue
             if ctx.lora_name:

@@ -185,7 +185,7 @@ class EmbeddingsRequest(BaseModel):
     input: Union[str, list[str], list[int], list[list[int]]]
     encoding_format: str = "float"
     dimensions: Optional[int] = None
-    pooling: Optional[str] = None      # extension: "last" (default) | "mean"
+    pooling: Optional[str] = None      # extension: "last" | "mean" | "cls" (encoders); default: the model's own
     user: Optional[str] = None
 
 

@@ -341,3 +341,41 @@ def test_mamba_chunked_prefill_and_slot_reuse_keep_the_state_right(tmp_path):
     again = LLM(cfg, w2, device="cpu", dtype=torch.float32, max_length=256, max_batch_size=4,
                 max_batch_input_tokens=256)
     assert [list(r.tokens) for r in again.generate(prompts, sp)] == solo
+
+
+@pytest.mark.parametrize("kind", ["bert", "mpnet"])
+def test_encoder_embeddings_match_transformers(tmp_path, kind):
+    """Encoder-only embedding models: pooled final hidden states against transformers (MPNet: relative-position
+    biases over distances beyond the exact buckets, positions counted from the padding index)."""
+    torch.manual_seed(3)
+    common = dict(vocab_size=320, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+                  max_position_embeddings=128)
+    if kind == "bert":
+        hf_cfg = transformers.BertConfig(**common)
+        hf = transformers.BertModel(hf_cfg, add_pooling_layer=False).eval()
+        arch = "BertModel"
+    else:
+        hf_cfg = transformers.MPNetConfig(**common)
+        hf = transformers.MPNetModel(hf_cfg, add_pooling_layer=False).eval()
+        arch = "MPNetForMaskedLM"
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith(".bias") or "LayerNorm" in n or "relative_attention_bias" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = hf_cfg.to_dict()
+    d["architectures"] = [arch]
+    _save(hf, d, tmp_path)
+    llm = _engine(tmp_path)
+    assert type(llm.model).__name__ == "BertModel"
+    prompts = [list(range(5, 75)), [200, 3, 17], [9, 8]]
+    for pooling in ("default", "cls", "last"):
+        ours = llm.encode(prompts, pooling=pooling).cpu()
+        for i, p in enumerate(prompts):
+            with torch.no_grad():
+                hs = hf(torch.tensor([p])).last_hidden_state[0].float()
+            want = hs.mean(0) if pooling == "default" else hs[0] if pooling == "cls" else hs[-1]
+            want = want / want.norm()
+            assert (ours[i] - want).abs().max().item() < 2e-4, (kind, pooling, i)
+    with pytest.raises(NotImplementedError):
+        from modular_b200.pipelines.context import SamplingParams
+        llm.generate([[1, 2, 3]], SamplingParams(max_new_tokens=2))

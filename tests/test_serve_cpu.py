@@ -136,6 +136,32 @@ def test_tiny_llama_server():
         assert len(base64.b64decode(m["data"][0]["embedding"])) == 64
 
 
+def test_encoder_and_state_space_presets_behind_the_server():
+    """An encoder-only preset answers /v1/embeddings with its own default pooling and refuses generation with a
+    client error; a state-space preset generates through the same routes."""
+    pc = _config(model_path="preset:tiny-bert", devices="cpu", max_length=128, max_batch_size=4,
+                 max_batch_input_tokens=128, quantization_encoding="float32")
+    tokenizer, factory = PIPELINE_REGISTRY.retrieve_factory(pc)
+    with TestClient(fastapi_app(Settings(), pc, tokenizer, factory, "enc", 128)) as c:
+        e = c.post("/v1/embeddings", json={"model": "enc", "input": [[5, 6, 7], [9, 9]]}).json()
+        v = [d["embedding"] for d in e["data"]]
+        assert len(v) == 2 and abs(sum(x * x for x in v[0]) - 1.0) < 1e-4
+        cls = c.post("/v1/embeddings", json={"model": "enc", "input": [[5, 6, 7]], "pooling": "cls"}).json()
+        assert cls["data"][0]["embedding"] != v[0]
+        r = c.post("/v1/completions", json={"model": "enc", "prompt": [5, 6, 7], "max_tokens": 2})
+        assert r.status_code == 400 and "embeddings" in r.json()["error"]["message"], r.text
+        assert c.get("/health").status_code == 200
+    pc = _config(model_path="preset:tiny-mamba", devices="cpu", max_length=128, max_batch_size=4,
+                 max_batch_input_tokens=64, quantization_encoding="float32")
+    tokenizer, factory = PIPELINE_REGISTRY.retrieve_factory(pc)
+    with TestClient(fastapi_app(Settings(), pc, tokenizer, factory, "ssm", 128)) as c:
+        a = c.post("/v1/completions", json={"model": "ssm", "prompt": [5, 6, 7, 8], "max_tokens": 5, "temperature": 0,
+                                            "ignore_eos": True}).json()
+        b = c.post("/v1/completions", json={"model": "ssm", "prompt": [5, 6, 7, 8], "max_tokens": 5, "temperature": 0,
+                                            "ignore_eos": True}).json()
+        assert a["usage"]["completion_tokens"] == 5 and a["choices"][0]["text"] == b["choices"][0]["text"]
+
+
 def test_incremental_detokenizer_utf8_and_stop():
     tok = ByteTokenizer()
     d = IncrementalDetokenizer(tok, stop=["END"])
