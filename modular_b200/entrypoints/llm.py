@@ -242,6 +242,8 @@ class LLM:
 
     def add_request(self, prompt_ids, sampling_params: Optional[SamplingParams] = None,
                     request_id: Optional[str] = None, lora_name: Optional[str] = None) -> str:
+        if getattr(self.model, "generates", True) is False:
+            raise NotImplementedError(f"{type(self.model).__name__} serves embeddings (encode), not generation")
         self._n += 1
         rid = request_id or f"llm-{self._n}"
         ctx = TextContext.from_prompt(prompt_ids, self.max_length, rid, sampling_params,
