@@ -51,6 +51,9 @@ class Llama3Config:
     qk_norm: bool = False             # RMSNorm over head_dim on every query and key head before the rotation (Qwen3)
     qk_norm_full: bool = False        # with qk_norm: one RMSNorm over the whole query / key projection (OLMo 2)
     norm_after: bool = False          # norms on the block outputs (before the residual add) instead of the inputs (OLMo 2)
+    sandwich_norm: bool = False       # Gemma 3: norms on block inputs AND outputs, weights stored as (w - 1), gelu-tanh MLP
+    rope_local_theta: Optional[float] = None   # Gemma 3: rotary base of the sliding-window layers (no scaling there)
+    local_layers: tuple = ()          # Gemma 3: indices of the sliding-window layers
     plain_layer_norm: bool = False    # LayerNorm without weight or bias (eps 1e-5) in place of every RMSNorm (OLMo)
     clip_qkv: Optional[float] = None  # queries, keys and values clamped to [-clip, clip] after the projection (OLMo)
     # mixture-of-experts feed-forward (Mixtral, Qwen3-MoE): 0 experts = dense SwiGLU MLP in every layer
@@ -259,6 +262,67 @@ class GraniteConfig(Llama3Config):
 
 
 @dataclass
+class Gemma3Config(Llama3Config):
+    """Gemma 3 text models (``Gemma3ForCausalLM``): four RMSNorms per layer (block inputs and outputs) whose weights
+    the checkpoint stores minus one, per-head query / key norms, a tanh-GELU gated MLP, embeddings scaled by
+    ``sqrt(hidden)``, ``query_pre_attn_scalar ** -0.5`` as the softmax scale, and five sliding-window layers (rotary
+    base 10 000, no scaling) for every full-attention layer (base 1 000 000, linear scaling on the larger models). Every
+    layer here attends to the whole prefix, so the served context is capped at the window, where the two agree. The
+    attention kernels cover head sizes 64 and 128: checkpoints with ``head_dim`` 256 run on CPU only.
+    Reference: max/python/max/pipelines/architectures/gemma3/."""
+
+    rope_theta: float = 1000000.0
+    rms_norm_eps: float = 1e-6
+    max_position_embeddings: int = 131072
+    tie_word_embeddings: bool = True
+    qk_norm: bool = True
+    sandwich_norm: bool = True
+    architectures: tuple = ("Gemma3ForCausalLM",)
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "Gemma3Config":
+        # a vision-language checkpoint (Gemma3ForConditionalGeneration) nests the language model's settings
+        d = dict(d.get("text_config") or d, architectures=d.get("architectures", ["Gemma3ForCausalLM"]))
+        if d.get("attn_logit_softcapping") or d.get("final_logit_softcapping"):
+            raise ValueError("logit soft-capping is not implemented")
+        act = d.pop("hidden_activation", None) or d.pop("hidden_act", None) or "gelu_pytorch_tanh"
+        d.pop("hidden_act", None)
+        if act not in ("gelu_pytorch_tanh", "gelu_tanh"):
+            raise ValueError(f"activation {act!r} is not implemented for this family")
+        rp = d.pop("rope_parameters", None)
+        local_theta = d.get("rope_local_base_freq", 10000.0)
+        if isinstance(rp, dict) and "full_attention" in rp:
+            g, loc = rp["full_attention"], rp.get("sliding_attention") or {}
+            d["rope_theta"] = g.get("rope_theta", 1000000.0)
+            kind = g.get("rope_type", "default")
+            d["rope_scaling"] = None if kind in (None, "default") else {k: v for k, v in g.items() if k != "rope_theta"}
+            local_theta = loc.get("rope_theta", local_theta)
+        d.setdefault("tie_word_embeddings", True)
+        cfg = super().from_hf(d)
+        cfg.qk_norm = cfg.sandwich_norm = True
+        cfg.rope_local_theta = float(local_theta)
+        types = d.get("layer_types")
+        if types is None:
+            pat = int(d.get("sliding_window_pattern") or d.get("_sliding_window_pattern") or 6)
+            types = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention" for i in range(cfg.num_hidden_layers)]
+        cfg.local_layers = tuple(i for i, t in enumerate(types) if t == "sliding_attention")
+        cfg.attention_multiplier = float(d.get("query_pre_attn_scalar", cfg.head_dim)) ** -0.5
+        cfg.embedding_multiplier = float(cfg.hidden_size) ** 0.5
+        if cfg.local_layers:
+            _cap_to_window(cfg, d.get("sliding_window"))
+        return cfg
+
+    def to_hf(self) -> dict:
+        d = super().to_hf()
+        d.update(model_type="gemma3_text", hidden_activation="gelu_pytorch_tanh", rope_local_base_freq=self.rope_local_theta,
+                 query_pre_attn_scalar=(self.attention_multiplier or self.head_dim ** -0.5) ** -2,
+                 layer_types=["sliding_attention" if i in self.local_layers else "full_attention"
+                              for i in range(self.num_hidden_layers)])
+        d.pop("hidden_act", None)
+        return d
+
+
+@dataclass
 class OlmoConfig(Llama3Config):
     """OLMo (``OlmoForCausalLM``): the Llama layer with a LayerNorm without weight or bias in place of every
     RMSNorm, and the query / key / value projections clamped to ``[-clip_qkv, clip_qkv]`` where the checkpoint
@@ -444,6 +508,8 @@ class LayerWeights:
     q_norm: Optional[torch.Tensor] = None        # [head_dim] weights of the per-head query / key RMSNorm (Qwen3)
     k_norm: Optional[torch.Tensor] = None
     moe: Optional[object] = None                 # nn.moe.MoE of a mixture-of-experts layer (wgu / wd are None then)
+    attn_out_norm: Optional[torch.Tensor] = None  # Gemma 3: RMSNorm weights on the attention / MLP block outputs
+    mlp_out_norm: Optional[torch.Tensor] = None
 
     @property
     def is_fp8(self) -> bool:
@@ -492,7 +558,9 @@ class Llama3Weights:
                 q_norm=torch.ones(cfg.q_dim if cfg.qk_norm_full else cfg.head_dim, dtype=dtype, device=dev)
                 if cfg.qk_norm else None,
                 k_norm=torch.ones(cfg.kv_dim if cfg.qk_norm_full else cfg.head_dim, dtype=dtype, device=dev)
-                if cfg.qk_norm else None))
+                if cfg.qk_norm else None,
+                attn_out_norm=torch.ones(cfg.hidden_size, dtype=dtype, device=dev) if cfg.sandwich_norm else None,
+                mlp_out_norm=torch.ones(cfg.hidden_size, dtype=dtype, device=dev) if cfg.sandwich_norm else None))
         final_norm = torch.ones(cfg.hidden_size, dtype=dtype, device=dev)
         lm_head = embed if cfg.tie_word_embeddings else rnd(cfg.vocab_size, cfg.hidden_size)
         return cls(embed, layers, final_norm, lm_head)
@@ -561,6 +629,13 @@ class Llama3Weights:
         """``keep_fp8``: block-scaled fp8 projections (``<name>`` e4m3 + ``<name>_scale_inv``) stay fp8 when the
         fused row blocks line up with the 128-row scale blocks; otherwise they are expanded to ``dtype``."""
         sd = _split_fused_projections(cfg, adapt_hf_state_dict(sd))
+        if cfg.sandwich_norm:
+            # the checkpoint stores every norm weight minus one; the four norms of a layer: the two on the block
+            # inputs go where Llama's are, the two on the block outputs get slots of their own
+            ren = lambda k: (k.replace(".post_attention_layernorm.", ".attn_out_norm.")
+                             .replace(".pre_feedforward_layernorm.", ".post_attention_layernorm.")
+                             .replace(".post_feedforward_layernorm.", ".mlp_out_norm."))
+            sd = {ren(k): (v.float() + 1.0 if k.endswith("norm.weight") else v) for k, v in sd.items()}
         if cfg.plain_layer_norm:
             # norms without parameters: nothing in the checkpoint; the slots hold ones and are not read
             one = torch.ones(cfg.hidden_size)
@@ -644,7 +719,8 @@ class Llama3Weights:
                 mlp_norm=get(p + "post_attention_layernorm.weight"),
                 wgu=wgu, wd=None if moe is not None else get(p + "mlp.down_proj.weight"), moe=moe,
                 qkv_bias=bias(p),
-                q_norm=opt(p + "self_attn.q_norm.weight"), k_norm=opt(p + "self_attn.k_norm.weight")))
+                q_norm=opt(p + "self_attn.q_norm.weight"), k_norm=opt(p + "self_attn.k_norm.weight"),
+                attn_out_norm=opt(p + "attn_out_norm.weight"), mlp_out_norm=opt(p + "mlp_out_norm.weight")))
         embed = get("embed_tokens.weight")
         lm_head = embed if (cfg.tie_word_embeddings or "lm_head.weight" not in sd) else get("lm_head.weight")
         if cfg.embedding_multiplier != 1.0 or cfg.logits_scaling != 1.0 or cfg.residual_multiplier != 1.0:
@@ -699,6 +775,16 @@ class Llama3Weights:
             g, u = torch.split(l.wgu, cfg.intermediate_size, dim=0)
             sd.update({p + "mlp.gate_proj.weight": g, p + "mlp.up_proj.weight": u,
                        p + "mlp.down_proj.weight": l.wd})
+        if cfg.sandwich_norm:
+            for i, l in enumerate(self.layers):
+                sd[f"model.layers.{i}.attn_out_norm.weight"] = l.attn_out_norm
+                sd[f"model.layers.{i}.mlp_out_norm.weight"] = l.mlp_out_norm
+            ren = lambda k: (k.replace(".post_attention_layernorm.", ".pre_feedforward_layernorm.")
+                             .replace(".attn_out_norm.", ".post_attention_layernorm.")
+                             .replace(".mlp_out_norm.", ".post_feedforward_layernorm."))
+            sd = {ren(k): (v.float() - 1.0).to(v.dtype) if k.endswith("norm.weight") else v for k, v in sd.items()}
+            if cfg.embedding_multiplier != 1.0:
+                sd["model.embed_tokens.weight"] = (self.embed.float() / cfg.embedding_multiplier).to(self.embed.dtype)
         if cfg.plain_layer_norm:
             sd = {k: v for k, v in sd.items() if not k.endswith(("layernorm.weight", "model.norm.weight"))}
         if cfg.norm_after:
@@ -754,11 +840,17 @@ def _split_fused_projections(cfg, sd: dict) -> dict:
 
 
 def adapt_hf_state_dict(sd: dict) -> dict:
-    """HF checkpoint names -> internal names: strips the ``model.`` prefix, keeps ``lm_head``."""
+    """HF checkpoint names -> internal names: strips the ``model.`` prefix, keeps ``lm_head``. Of a vision-language
+    checkpoint the language model is kept (``language_model.`` wrappers stripped) and the vision tower and projector
+    are dropped: such checkpoints are served for text."""
     out = {}
     for k, v in sd.items():
-        if k.startswith("model."):
-            k = k[len("model."):]
+        if any(part in k for part in ("vision_tower.", "vision_model.", "multi_modal_projector.", "visual.")):
+            continue
+        for pre in ("model.language_model.", "language_model.model.", "language_model.", "model."):
+            if k.startswith(pre):
+                k = k[len(pre):]
+                break
         out[k] = v
     return out
 
@@ -784,6 +876,9 @@ class Llama3Model:
         max_position = max_position or cfg.max_position_embeddings
         self.cos_sin = cos_sin_table(cfg.head_dim, max_position, cfg.rope_theta,
                                      RopeScaling.from_hf(cfg.rope_scaling), self.device)
+        self.cos_sin_local = None
+        if cfg.rope_local_theta:
+            self.cos_sin_local = cos_sin_table(cfg.head_dim, max_position, cfg.rope_local_theta, None, self.device)
         on_gpu = self.device.type == "cuda"
         self.use_executor = on_gpu and self.dtype == torch.bfloat16 if use_executor is None else use_executor
         if any(l.moe is not None for l in weights.layers):
@@ -792,11 +887,11 @@ class Llama3Model:
             self.use_executor = False
             if tp is not None and tp.world > 1:
                 raise ValueError("tensor parallelism is not implemented for mixture-of-experts layers of this family")
-        if cfg.norm_after or cfg.qk_norm_full or cfg.plain_layer_norm or cfg.clip_qkv:
+        if cfg.norm_after or cfg.qk_norm_full or cfg.plain_layer_norm or cfg.clip_qkv or cfg.sandwich_norm:
             # another layer order than the native step executor runs
             self.use_executor = False
             if tp is not None and tp.world > 1:
-                raise ValueError("tensor parallelism is not implemented for the OLMo layer variants")
+                raise ValueError("tensor parallelism is not implemented for the OLMo and Gemma layer variants")
         self.fuse_swiglu = fuse_swiglu
         self.executor = None
         self.logits_buf = None
@@ -923,11 +1018,13 @@ class Llama3Model:
         if lora is not None and not lora.active:
             lora = None
         if lora is not None:
-            if c.norm_after or c.plain_layer_norm or c.clip_qkv:
-                raise ValueError("LoRA adapters are not implemented for the OLMo layer variants")
+            if c.norm_after or c.plain_layer_norm or c.clip_qkv or c.sandwich_norm:
+                raise ValueError("LoRA adapters are not implemented for the OLMo and Gemma layer variants")
             return self._forward_hidden_lora(tokens, positions, slots, block_table, q_start, q_len, kv_len, plan,
                                              self.kv if kv is None else kv, lora)
         kv = self.kv if kv is None else kv
+        if c.sandwich_norm:
+            return self._forward_hidden_gemma(tokens, positions, slots, block_table, q_start, q_len, kv_len, plan, kv)
         if c.norm_after or c.plain_layer_norm or c.clip_qkv:
             return self._forward_hidden_olmo(tokens, positions, slots, block_table, q_start, q_len, kv_len, plan, kv)
         h = ops.embedding(tokens, self.w.embed)
@@ -1006,6 +1103,31 @@ class Llama3Model:
                 h = h + self._norm(ops.linear(act, l.wd), l.mlp_norm)
             else:
                 h = ops.linear(act, l.wd, residual=h)
+        return h
+
+    def _forward_hidden_gemma(self, tokens, positions, slots, block_table, q_start, q_len, kv_len, plan, kv):
+        """Gemma 3 text layers, op by op: ``h += norm(attn(norm(h))); h += norm(mlp(norm(h)))`` with a tanh-GELU
+        gate in the MLP, per-head query / key norms, and a rotary base of their own on the sliding-window layers.
+        The checkpoint's ``w - 1`` norm weights and the ``sqrt(hidden)`` embedding scale were folded in at load.
+        Reference: max/python/max/pipelines/architectures/gemma3/."""
+        c = self.cfg
+        I = c.intermediate_size
+        h = ops.embedding(tokens, self.w.embed)
+        for li, l in enumerate(self.w.layers):
+            if l.is_fp8 or l.moe is not None or l.qkv_bias is not None:
+                raise ValueError("Gemma layers are implemented for dense bf16 / fp32 weights without bias")
+            kc, vc = kv[:, 0, li], kv[:, 1, li]
+            cos_sin = self.cos_sin_local if (li in c.local_layers and self.cos_sin_local is not None) else self.cos_sin
+            qkv = ops.linear(ops.rms_norm(h, l.attn_norm, c.rms_norm_eps), l.wqkv)
+            self._qk_norm(qkv, l)
+            ops.rope_kv_store(qkv, positions, slots, cos_sin, kc, vc, c.num_attention_heads, c.num_key_value_heads,
+                              c.head_dim, False)
+            a = ops.paged_attention(qkv, kc, vc, block_table, q_start, q_len, kv_len, c.num_attention_heads,
+                                    c.num_key_value_heads, c.head_dim, self.scale, plan=plan)
+            h = h + ops.rms_norm(ops.linear(a, l.wo), l.attn_out_norm, c.rms_norm_eps)
+            gu = ops.linear(ops.rms_norm(h, l.mlp_norm, c.rms_norm_eps), l.wgu)
+            act = torch.nn.functional.gelu(gu[:, :I], approximate="tanh") * gu[:, I:]
+            h = h + ops.rms_norm(ops.linear(act.contiguous(), l.wd), l.mlp_out_norm, c.rms_norm_eps)
         return h
 
     def _qk_norm(self, qkv: torch.Tensor, l) -> None:

@@ -291,6 +291,15 @@ def _register_builtin() -> None:
         name="GraniteForCausalLM", config_class=GraniteConfig, weights_class=Llama3Weights, model_class=Llama3Model,
         default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"),
         example_repo_ids=("ibm-granite/granite-3.3-8b-instruct",), preset_configs={}), allow_override=True)
+    from ..models.llama3 import Gemma3Config
+
+    # Gemma 3 text: norms on block inputs and outputs, tanh-GELU MLP, two rotary bases; op by op
+    # (Gemma3ForConditionalGeneration: the language model of the vision-language checkpoints, served for text)
+    for name, repo in (("Gemma3ForCausalLM", "google/gemma-3-1b-it"), ("Gemma3ForConditionalGeneration", "google/gemma-3-4b-it")):
+        PIPELINE_REGISTRY.register(SupportedArchitecture(
+            name=name, config_class=Gemma3Config, weights_class=Llama3Weights, model_class=Llama3Model,
+            default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"),
+            example_repo_ids=(repo,), preset_configs={}), allow_override=True)
     from ..models.llama3 import Olmo2Config, OlmoConfig
 
     # OLMo: parameter-free LayerNorms and clamped projections. OLMo 2 / 3: Llama projections with the norms on the

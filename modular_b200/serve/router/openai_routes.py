@@ -367,6 +367,12 @@ async def create_chat_completion(req: ChatCompletionRequest, request: Request):
     if req.response_format is not None and req.response_format.type != "text":
         if not request.app.state.structured_output:
             return error_response(400, "response_format requires the server to run with --enable-structured-output")
+    for m in req.messages:
+        # content parts other than text (images, audio, video, files) would otherwise vanish from the prompt
+        for part in (m.content if isinstance(m.content, list) else ()):
+            kind = part.get("type", "text") if isinstance(part, dict) else "text"
+            if kind != "text":
+                return error_response(400, f"content parts of type {kind!r} are not supported: this server takes text")
     sp = sampling_from_request(req, None)
     salt = _salt_of(req)
     prompt = _chat_prompt(pipeline, req)

@@ -57,6 +57,13 @@ CASES = {
     "granite": ("GraniteConfig", "GraniteForCausalLM", dict(rope_theta=10000.0, rms_norm_eps=1e-5,
                                                             embedding_multiplier=12.0, residual_multiplier=0.22,
                                                             attention_multiplier=0.0078125 * 16, logits_scaling=8.0)),
+    "gemma3": ("Gemma3TextConfig", "Gemma3ForCausalLM", dict(rms_norm_eps=1e-6, head_dim=32, query_pre_attn_scalar=24,
+                                                             sliding_window=256, num_hidden_layers=6, pad_token_id=0,
+                                                             rope_parameters={
+                                                                 "sliding_attention": {"rope_type": "default",
+                                                                                       "rope_theta": 10000.0},
+                                                                 "full_attention": {"rope_type": "linear", "factor": 4.0,
+                                                                                    "rope_theta": 1000000.0}})),
     "olmo": ("OlmoConfig", "OlmoForCausalLM", dict(rope_theta=10000.0, clip_qkv=0.05, pad_token_id=0)),
     "olmo2": ("Olmo2Config", "Olmo2ForCausalLM", dict(rope_theta=500000.0, rms_norm_eps=1e-6, pad_token_id=0)),
     "olmo3": ("Olmo3Config", "Olmo3ForCausalLM", dict(rope_theta=500000.0, rms_norm_eps=1e-6, pad_token_id=0,
@@ -73,9 +80,10 @@ def test_greedy_tokens_match_transformers(tmp_path, family, tied):
 
     cfg_name, model_name, extra = CASES[family]
     torch.manual_seed(7)
-    hf_cfg = getattr(transformers, cfg_name)(
-        hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
-        vocab_size=320, max_position_embeddings=512, tie_word_embeddings=tied, **extra)
+    kw = dict(hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              vocab_size=320, max_position_embeddings=512, tie_word_embeddings=tied)
+    kw.update(extra)
+    hf_cfg = getattr(transformers, cfg_name)(**kw)
     hf = getattr(transformers, model_name)(hf_cfg).eval()
     with torch.no_grad():       # the default initialisation leaves biases at zero and norms at one: move them
         for n, p in hf.named_parameters():
@@ -379,3 +387,31 @@ def test_encoder_embeddings_match_transformers(tmp_path, kind):
     with pytest.raises(NotImplementedError):
         from modular_b200.pipelines.context import SamplingParams
         llm.generate([[1, 2, 3]], SamplingParams(max_new_tokens=2))
+
+
+def test_gemma3_vision_language_checkpoint_serves_its_language_model(tmp_path):
+    """``Gemma3ForConditionalGeneration``: settings nested under ``text_config``, tensors under a ``language_model``
+    wrapper next to a vision tower; the language model is served for text and matches the text-only model."""
+    from modular_b200.pipelines.context import SamplingParams
+
+    torch.manual_seed(2)
+    text = transformers.Gemma3TextConfig(hidden_size=64, intermediate_size=176, num_hidden_layers=6, num_attention_heads=4,
+                                         num_key_value_heads=2, head_dim=32, vocab_size=320, sliding_window=256,
+                                         query_pre_attn_scalar=24, max_position_embeddings=512, pad_token_id=0)
+    hf = transformers.Gemma3ForCausalLM(text).eval()
+    sd = {k.replace("model.", "model.language_model.", 1): v.detach().clone() for k, v in hf.state_dict().items()
+          if k != "lm_head.weight"}
+    sd["model.vision_tower.vision_model.embeddings.position_embedding.weight"] = torch.zeros(4, 8)
+    sd["model.multi_modal_projector.mm_input_projection_weight"] = torch.zeros(8, 64)
+    from safetensors.torch import save_file
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps({
+        "architectures": ["Gemma3ForConditionalGeneration"], "model_type": "gemma3", "text_config": text.to_dict(),
+        "vision_config": {"model_type": "siglip_vision_model", "hidden_size": 8}}))
+    llm = _engine(tmp_path)
+    prompt = [5, 6, 7, 8, 9, 10, 11]
+    rec = llm.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True))[0]
+    with torch.no_grad():
+        want = hf.generate(torch.tensor([prompt]), max_new_tokens=8, do_sample=False, pad_token_id=0,
+                           eos_token_id=None)[0, len(prompt):].tolist()
+    assert list(rec.tokens) == want

@@ -694,4 +694,11 @@ def test_odd_requests_get_an_answer_and_leave_the_worker_alone():
         assert post(prompt=[5, 6], max_tokens=-3).status_code == 400
         big = post(prompt=[5, 6], max_tokens=2, seed=2 ** 62, temperature=1.0)
         assert big.status_code == 200 and big.json()["usage"]["completion_tokens"] == 2
+        # an image part must not silently drop out of the prompt: the server takes text
+        img = c.post("/v1/chat/completions", json={"model": "tiny", "max_tokens": 2, "messages": [{"role": "user", "content": [
+            {"type": "text", "text": "what is this?"}, {"type": "image_url", "image_url": {"url": "data:image/png;base64,AAAA"}}]}]})
+        assert img.status_code == 400 and "image_url" in img.json()["error"]["message"]
+        txt = c.post("/v1/chat/completions", json={"model": "tiny", "max_tokens": 2, "messages": [{"role": "user", "content": [
+            {"type": "text", "text": "hello"}]}]})
+        assert txt.status_code == 200
         assert c.get("/health/ready").status_code == 200
