@@ -73,6 +73,9 @@ class Llama3Config:
     def from_hf(cls, d: dict) -> "Llama3Config":
         from ..pipelines.weights import normalize_hf_rope
 
+        if isinstance(d.get("text_config"), dict) and "hidden_size" not in d:
+            # a vision-language checkpoint nests the language model's settings; that model is what is served
+            d = dict(d["text_config"], architectures=d.get("architectures", ()))
         d = normalize_hf_rope(d)
         act = d.get("hidden_act") or d.get("hidden_activation") or "silu"
         if act not in ("silu", "swish"):
@@ -164,7 +167,7 @@ class MistralConfig(Llama3Config):
 
     @classmethod
     def from_hf(cls, d: dict) -> "MistralConfig":
-        return _cap_to_window(super().from_hf(d), d.get("sliding_window"))
+        return _cap_to_window(super().from_hf(d), (d.get("text_config") or d).get("sliding_window"))
 
     def to_hf(self) -> dict:
         d = super().to_hf()
@@ -480,7 +483,7 @@ class Phi3Config(Llama3Config):
                        or d["max_position_embeddings"])
             d = dict(d, rope_scaling=dict(rs, rope_type="longrope", original_max_position_embeddings=orig,
                                           factor=rs.get("factor") or d["max_position_embeddings"] / orig))
-        return _cap_to_window(super().from_hf(d), d.get("sliding_window"))
+        return _cap_to_window(super().from_hf(d), (d.get("text_config") or d).get("sliding_window"))
 
     def to_hf(self) -> dict:
         d = super().to_hf()

@@ -254,6 +254,14 @@ def _register_builtin() -> None:
         example_repo_ids=("mistralai/Mistral-7B-Instruct-v0.3", "mistralai/Mistral-Nemo-Instruct-2407"),
         preset_configs={})
     PIPELINE_REGISTRY.register(mistral, allow_override=True)
+    # vision-language checkpoints around a Mistral or Llama language model: that model is served, for text (the
+    # vision tower and projector are dropped at load, requests with image parts are refused)
+    for name, repo in (("Mistral3ForConditionalGeneration", "mistralai/Mistral-Small-3.1-24B-Instruct-2503"),
+                       ("LlavaForConditionalGeneration", "mistral-community/pixtral-12b")):
+        PIPELINE_REGISTRY.register(SupportedArchitecture(
+            name=name, config_class=MistralConfig, weights_class=Llama3Weights, model_class=Llama3Model,
+            default_encoding="bfloat16", supported_encodings=("bfloat16", "float32", "float8_e4m3fn"),
+            example_repo_ids=(repo,), preset_configs={}), allow_override=True)
     from ..models.llama3 import Qwen2Config
 
     # the Llama layer with a bias on the fused query / key / value projection
@@ -331,7 +339,7 @@ def _register_builtin() -> None:
         PIPELINE_REGISTRY.register(SupportedArchitecture(
             name=name, config_class=BertConfig, weights_class=BertWeights, model_class=BertModel,
             default_encoding="float32", supported_encodings=("float32", "bfloat16"), example_repo_ids=repos,
-            preset_configs=presets), allow_override=True)
+            task="embeddings_generation", preset_configs=presets), allow_override=True)
     from ..models.llama3 import Phi3Config
 
     # the Llama layer with the projections already fused in the checkpoint

@@ -415,3 +415,31 @@ def test_gemma3_vision_language_checkpoint_serves_its_language_model(tmp_path):
         want = hf.generate(torch.tensor([prompt]), max_new_tokens=8, do_sample=False, pad_token_id=0,
                            eos_token_id=None)[0, len(prompt):].tolist()
     assert list(rec.tokens) == want
+
+
+def test_vision_language_checkpoint_around_mistral_serves_its_language_model(tmp_path):
+    """``Mistral3ForConditionalGeneration`` in the ``language_model.model.*`` layout with an untied head: the vision
+    tower and projector are dropped, the language model matches ``MistralForCausalLM``."""
+    from modular_b200.pipelines.context import SamplingParams
+    from safetensors.torch import save_file
+
+    torch.manual_seed(4)
+    text = transformers.MistralConfig(hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
+                                      num_key_value_heads=2, vocab_size=320, max_position_embeddings=512,
+                                      sliding_window=None, tie_word_embeddings=False)
+    hf = transformers.MistralForCausalLM(text).eval()
+    sd = {"language_model." + k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()}
+    sd["vision_tower.transformer.layers.0.attention.q_proj.weight"] = torch.zeros(8, 8)
+    sd["multi_modal_projector.linear_1.weight"] = torch.zeros(64, 8)
+    save_file(sd, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps({
+        "architectures": ["Mistral3ForConditionalGeneration"], "model_type": "mistral3", "text_config": text.to_dict(),
+        "vision_config": {"model_type": "pixtral", "hidden_size": 8}}))
+    llm = _engine(tmp_path)
+    prompt = [5, 6, 7, 8, 9, 10, 11]
+    rec = llm.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True))[0]
+    with torch.no_grad():
+        want = hf.generate(torch.tensor([prompt]), max_new_tokens=8, do_sample=False, pad_token_id=0,
+                           eos_token_id=None)[0, len(prompt):].tolist()
+    assert list(rec.tokens) == want
+    _assert_logits_close(llm, hf, prompt)
