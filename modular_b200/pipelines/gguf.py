@@ -158,12 +158,14 @@ class GGUFReader:
         return torch.from_numpy(dequantize(raw, info.ggml_type, n).reshape(info.shape)).to(dtype)
 
     def hf_config(self) -> dict:
-        """The HF-style config fields recoverable from llama-family metadata."""
+        """The HF-style config fields recoverable from the metadata of a llama, qwen2 or qwen3 file."""
         md, a = self.metadata, self.metadata.get("general.architecture", "llama")
+        if a not in _ARCH:
+            raise ValueError(f"GGUF architecture {a!r} is not supported (supported: {sorted(_ARCH)})")
         g = lambda k, d=None: md.get(f"{a}.{k}", d)
         heads = g("attention.head_count")
         emb = g("embedding_length")
-        cfg = {"architectures": ["LlamaForCausalLM"], "model_type": a, "hidden_size": emb,
+        cfg = {"architectures": [_ARCH[a][0]], "model_type": a, "hidden_size": emb,
                "num_hidden_layers": g("block_count"), "num_attention_heads": heads,
                "num_key_value_heads": g("attention.head_count_kv", heads),
                "intermediate_size": g("feed_forward_length"), "rms_norm_eps": g("attention.layer_norm_rms_epsilon", 1e-5),
@@ -175,16 +177,20 @@ class GGUFReader:
         return {k: v for k, v in cfg.items() if v is not None}
 
     def to_hf_state_dict(self, dtype: torch.dtype = torch.bfloat16) -> dict:
-        """Dequantised tensors under HF Llama names. llama.cpp stores Q and K projection rows permuted for
-        its interleaved RoPE; they are permuted back to the HF (rotate-half) order."""
+        """Dequantised tensors under HF names. For the llama architecture llama.cpp stores Q and K projection rows
+        permuted for its interleaved RoPE; they are permuted back to the HF (rotate-half) order. qwen2 / qwen3 files
+        keep the HF order (and carry projection biases / per-head norm weights under the same block names)."""
         cfg = self.hf_config()
+        permuted = _ARCH[self.metadata.get("general.architecture", "llama")][1]
         out = {}
         for name in self.tensors:
             hf = hf_name(name)
             if hf is None:
                 continue
             t = self.get(name, dtype)
-            if name.endswith("attn_q.weight"):
+            if not permuted:
+                pass
+            elif name.endswith("attn_q.weight"):
                 t = _unpermute_qk(t, cfg["num_attention_heads"])
             elif name.endswith("attn_k.weight"):
                 t = _unpermute_qk(t, cfg["num_key_value_heads"])
@@ -194,7 +200,9 @@ class GGUFReader:
 
 _TOP = {"token_embd.weight": "model.embed_tokens.weight", "output_norm.weight": "model.norm.weight",
         "output.weight": "lm_head.weight"}
-_LAYER = {"attn_norm": "input_layernorm", "ffn_norm": "post_attention_layernorm", "attn_q": "self_attn.q_proj",
+# general.architecture -> (HF architecture, Q / K rows stored in llama.cpp's interleaved-rotary order)
+_ARCH = {"llama": ("LlamaForCausalLM", True), "qwen2": ("Qwen2ForCausalLM", False), "qwen3": ("Qwen3ForCausalLM", False)}
+_LAYER = {"attn_q_norm": "self_attn.q_norm", "attn_k_norm": "self_attn.k_norm", "attn_norm": "input_layernorm", "ffn_norm": "post_attention_layernorm", "attn_q": "self_attn.q_proj",
           "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj", "attn_output": "self_attn.o_proj",
           "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj"}
 

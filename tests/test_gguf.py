@@ -2,6 +2,7 @@
 GGUF-stored tiny Llama that reproduces the original model's logits."""
 
 import numpy as np
+import pytest
 import torch
 
 from modular_b200.pipelines import gguf as G
@@ -112,3 +113,54 @@ def test_gguf_llama_checkpoint_reproduces_logits(tmp_path):
     a = Llama3Model(cfg, w, kv()).forward_tensors(*args)
     b = Llama3Model(cfg, w2, kv()).forward_tensors(*args)
     assert (a - b).abs().max() < 0.02 * a.abs().max()     # weights went through fp16
+
+
+@pytest.mark.parametrize("arch", ["qwen2", "qwen3"])
+def test_gguf_qwen_checkpoints_load_through_the_registry(tmp_path, arch):
+    """qwen2 / qwen3 files: projection biases and per-head norm weights under the block names, Q / K rows in HF
+    order; served through the registry from the .gguf alone, same greedy tokens as the source weights."""
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.models.llama3 import Llama3Weights, Qwen2Config, Qwen3Config
+    from modular_b200.pipelines.config import PipelineArgs, PipelineConfig
+    from modular_b200.pipelines.context import SamplingParams
+    from modular_b200.pipelines.registry import PIPELINE_REGISTRY
+
+    cfg = (Qwen2Config if arch == "qwen2" else Qwen3Config).tiny(tie_word_embeddings=False, vocab_size=512)
+    w = Llama3Weights.random_init(cfg, "cpu", torch.float32, seed=1, std=0.05)
+    for l in w.layers:
+        if l.q_norm is not None:
+            l.q_norm.add_(torch.randn(l.q_norm.shape, generator=torch.Generator().manual_seed(2)) * 0.1)
+            l.k_norm.add_(torch.randn(l.k_norm.shape, generator=torch.Generator().manual_seed(3)) * 0.1)
+    inv = {v: k for k, v in G._TOP.items()}
+    inv_layer = {v: k for k, v in G._LAYER.items()}
+    tensors = {}
+    for k, v in w.to_hf_state_dict(cfg).items():
+        parts = k.split(".")
+        name = inv[k] if k in inv else f"blk.{parts[2]}.{inv_layer['.'.join(parts[3:-1])]}.{parts[-1]}"
+        tensors[name] = (v.float().numpy(), G.GGML_F32)
+    md = {"general.architecture": arch, f"{arch}.block_count": cfg.num_hidden_layers,
+          f"{arch}.embedding_length": cfg.hidden_size, f"{arch}.attention.head_count": cfg.num_attention_heads,
+          f"{arch}.attention.head_count_kv": cfg.num_key_value_heads, f"{arch}.feed_forward_length": cfg.intermediate_size,
+          f"{arch}.attention.layer_norm_rms_epsilon": cfg.rms_norm_eps, f"{arch}.rope.freq_base": float(cfg.rope_theta),
+          f"{arch}.attention.key_length": cfg.head_dim, f"{arch}.context_length": 512}
+    path = tmp_path / "m"
+    path.mkdir()
+    G.write_gguf(str(path / "tiny.gguf"), md, tensors)
+    pc = PipelineConfig.from_args(PipelineArgs.from_flat_kwargs(
+        None, model_path=str(path), devices="cpu", max_length=128, max_batch_size=2, max_batch_input_tokens=64,
+        kv_cache_page_size=16, quantization_encoding="float32"))
+    llm = PIPELINE_REGISTRY.retrieve(pc)[1]
+    assert type(llm.cfg).__name__ == type(cfg).__name__
+    assert (llm.weights.layers[0].qkv_bias is not None) == (arch == "qwen2")
+    assert (llm.weights.layers[0].q_norm is not None) == (arch == "qwen3")
+    sp = SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True)
+    src = LLM(cfg, w, device="cpu", dtype=torch.float32, max_length=128, max_batch_size=2, max_batch_input_tokens=64,
+              page_size=16)
+    prompt = [5, 6, 7, 8, 9, 10]
+    assert list(llm.generate([prompt], sp)[0].tokens) == list(src.generate([prompt], sp)[0].tokens)
+
+
+def test_gguf_of_an_unknown_architecture_is_refused(tmp_path):
+    G.write_gguf(str(tmp_path / "x.gguf"), {"general.architecture": "falcon"}, {})
+    with pytest.raises(ValueError, match="falcon"):
+        G.GGUFReader(str(tmp_path / "x.gguf")).hf_config()
