@@ -137,7 +137,7 @@ class LLM:
                 weights = fam.weights_class.random_init_ep(model_config, ep_rank, ep_size, self.device, dtype, seed=seed)
         elif weights is None:
             weights = fam.weights_class.random_init(model_config, self.device, dtype, seed=seed)
-        if speculative is not None and fam.name == "mamba":
+        if speculative is not None and fam.name in ("mamba", "lfm2"):
             # verifying a draft runs the rejected tokens through the recurrence too, and a state cannot be rolled back
             raise ValueError("speculative decoding is not implemented for state-space models")
         self.weights = weights

@@ -71,6 +71,22 @@ def _mamba_family() -> ModelFamily:
     return ModelFamily("mamba", MambaConfig, MambaWeights, MambaModel, kv, act)
 
 
+def _lfm2_family() -> ModelFamily:
+    from ..kv_cache import KVCacheParams
+    from .lfm2 import Lfm2Config, Lfm2Model, Lfm2Weights
+
+    def kv(cfg, page, dtype, prefix):
+        # keys and values for the attention layers only; no prefix sharing (it cannot restore the convolution tails)
+        return KVCacheParams(max(len(cfg.attention_layers), 1), cfg.num_key_value_heads, cfg.head_dim, page, dtype,
+                             False, False)
+
+    def act(cfg, T, B):
+        return (T * (8 * cfg.hidden_size + 3 * cfg.intermediate_size) * 2 + B * cfg.vocab_size * 4
+                + 4 * B * cfg.state_bytes_per_slot() + (256 << 20))
+
+    return ModelFamily("lfm2", Lfm2Config, Lfm2Weights, Lfm2Model, kv, act)
+
+
 def _bert_family() -> ModelFamily:
     from ..kv_cache import KVCacheParams
     from .bert import BertConfig, BertModel, BertWeights
@@ -87,7 +103,7 @@ def _bert_family() -> ModelFamily:
 
 def family_for(config) -> ModelFamily:
     """The family that serves `config` (matched on the config class)."""
-    for make in (_llama_family, _deepseek_family, _mamba_family, _bert_family):
+    for make in (_llama_family, _deepseek_family, _mamba_family, _lfm2_family, _bert_family):
         fam = make()
         if isinstance(config, fam.config_class):
             return fam

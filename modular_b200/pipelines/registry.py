@@ -329,6 +329,13 @@ def _register_builtin() -> None:
         example_repo_ids=("state-spaces/mamba-130m-hf", "state-spaces/mamba-2.8b-hf"),
         preset_configs={"tiny-mamba": MambaConfig.tiny, "mamba-130m": MambaConfig.mamba_130m,
                         "mamba-2.8b": MambaConfig.mamba_2_8b}), allow_override=True)
+    from ..models.lfm2 import Lfm2Config, Lfm2Model, Lfm2Weights
+
+    # hybrid decoder: gated short-convolution layers (a convolution tail per request) between attention layers
+    PIPELINE_REGISTRY.register(SupportedArchitecture(
+        name="Lfm2ForCausalLM", config_class=Lfm2Config, weights_class=Lfm2Weights, model_class=Lfm2Model,
+        default_encoding="bfloat16", supported_encodings=("bfloat16", "float32"),
+        example_repo_ids=("LiquidAI/LFM2-1.2B",), preset_configs={"tiny-lfm2": Lfm2Config.tiny}), allow_override=True)
     from ..models.bert import BertConfig, BertModel, BertWeights
 
     # encoder-only embedding models (bidirectional attention; MPNet adds relative-position biases); embeddings only

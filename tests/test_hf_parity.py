@@ -443,3 +443,44 @@ def test_vision_language_checkpoint_around_mistral_serves_its_language_model(tmp
                            eos_token_id=None)[0, len(prompt):].tolist()
     assert list(rec.tokens) == want
     _assert_logits_close(llm, hf, prompt)
+
+
+def test_lfm2_hybrid_matches_transformers(tmp_path):
+    """Hybrid of gated short convolutions and attention layers: greedy tokens of two requests served together and
+    the logits of every prompt position; then a long prompt prefilled in chunks with few state slots."""
+    from modular_b200.entrypoints.llm import LLM
+    from modular_b200.pipelines.context import SamplingParams
+
+    torch.manual_seed(9)
+    hf_cfg = transformers.Lfm2Config(hidden_size=64, intermediate_size=176, num_hidden_layers=4, num_attention_heads=4,
+                                     num_key_value_heads=2, vocab_size=320, conv_L_cache=3, block_multiple_of=16,
+                                     block_auto_adjust_ff_dim=True, max_position_embeddings=512,
+                                     layer_types=["conv", "conv", "full_attention", "conv"], pad_token_id=0)
+    hf = transformers.Lfm2ForCausalLM(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("norm.weight"):
+                p.add_(torch.randn_like(p) * 0.1)
+    d = hf_cfg.to_dict()
+    d["architectures"] = ["Lfm2ForCausalLM"]
+    _save(hf, d, tmp_path)
+    llm = _engine(tmp_path)
+    assert type(llm.model).__name__ == "Lfm2Model" and llm.kv.kv.shape[2] == 1      # one KV plane: one attention layer
+    prompts = [[5, 6, 7, 8, 9, 10, 11, 12, 13], [200, 3, 17]]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=10, ignore_eos=True)
+    want = []
+    for prompt in prompts:
+        with torch.no_grad():
+            want.append(hf.generate(torch.tensor([prompt]), max_new_tokens=10, do_sample=False, pad_token_id=0,
+                                    eos_token_id=None)[0, len(prompt):].tolist())
+    assert [list(r.tokens) for r in llm.generate(prompts, sp)] == want
+    # chunked prefill (the convolution tail crosses step boundaries) and slot reuse
+    long = [(7 * i) % 300 + 1 for i in range(50)]
+    with torch.no_grad():
+        want_long = hf.generate(torch.tensor([long]), max_new_tokens=6, do_sample=False, pad_token_id=0,
+                                eos_token_id=None)[0, len(long):].tolist()
+    small = LLM(llm.cfg, llm.weights, device="cpu", dtype=torch.float32, max_length=128, max_batch_size=2,
+                max_batch_input_tokens=16, page_size=16, num_kv_pages=12)
+    sp6 = SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True)
+    got = small.generate([long, prompts[1], prompts[0]], sp6)
+    assert list(got[0].tokens) == want_long and list(got[1].tokens) == want[1][:6] and list(got[2].tokens) == want[0][:6]
