@@ -77,6 +77,11 @@ class Llama3Config:
             # a vision-language checkpoint nests the language model's settings; that model is what is served
             d = dict(d["text_config"], architectures=d.get("architectures", ()))
         d = normalize_hf_rope(d)
+        rs = d.get("rope_scaling")
+        if isinstance(rs, dict) and (rs.get("rope_type") or rs.get("type")) in ("mrope", "default"):
+            # multimodal rotary sections: with text alone the three position streams coincide and the rotation is
+            # the plain one
+            d = dict(d, rope_scaling=None)
         act = d.get("hidden_act") or d.get("hidden_activation") or "silu"
         if act not in ("silu", "swish"):
             raise ValueError(f"activation {act!r} is not implemented by this family (SwiGLU layers only)")

@@ -282,6 +282,15 @@ def _register_builtin() -> None:
         example_repo_ids=("Qwen/Qwen3-8B", "Qwen/Qwen3-32B"),
         preset_configs={"tiny-qwen3": Qwen3Config.tiny})
     PIPELINE_REGISTRY.register(qwen3, allow_override=True)
+    # Qwen vision-language checkpoints: the language model, served for text (multimodal rotary sections reduce to
+    # the plain rotation without images; the vision tower is dropped at load)
+    for name, cc, repo in (("Qwen2_5_VLForConditionalGeneration", Qwen2Config, "Qwen/Qwen2.5-VL-7B-Instruct"),
+                           ("Qwen2VLForConditionalGeneration", Qwen2Config, "Qwen/Qwen2-VL-7B-Instruct"),
+                           ("Qwen3VLForConditionalGeneration", Qwen3Config, "Qwen/Qwen3-VL-8B-Instruct")):
+        PIPELINE_REGISTRY.register(SupportedArchitecture(
+            name=name, config_class=cc, weights_class=Llama3Weights, model_class=Llama3Model,
+            default_encoding="bfloat16", supported_encodings=("bfloat16", "float32", "float8_e4m3fn"),
+            example_repo_ids=(repo,), preset_configs={}), allow_override=True)
     from ..models.llama3 import MixtralConfig, Qwen3MoeConfig
 
     # Llama / Qwen3 attention with a mixture-of-experts feed-forward (softmax top-k routing, grouped GEMMs); these

@@ -484,3 +484,64 @@ def test_lfm2_hybrid_matches_transformers(tmp_path):
     sp6 = SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True)
     got = small.generate([long, prompts[1], prompts[0]], sp6)
     assert list(got[0].tokens) == want_long and list(got[1].tokens) == want[1][:6] and list(got[2].tokens) == want[0][:6]
+
+
+def test_qwen2_5_vl_checkpoint_serves_text_like_transformers(tmp_path):
+    """A real (tiny) ``Qwen2_5_VLForConditionalGeneration``: vision tower beside the language model, multimodal
+    rotary sections in the config. Text-only requests give transformers' tokens."""
+    from modular_b200.pipelines.context import SamplingParams
+
+    torch.manual_seed(0)
+    cfg = transformers.Qwen2_5_VLConfig(
+        text_config=dict(hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, vocab_size=320, max_position_embeddings=512, rope_theta=1e6,
+                         rms_norm_eps=1e-6, use_sliding_window=False, tie_word_embeddings=False,
+                         rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}),
+        vision_config=dict(depth=1, hidden_size=32, intermediate_size=64, num_heads=2, out_hidden_size=64, patch_size=14,
+                           spatial_merge_size=2, temporal_patch_size=2, fullatt_block_indexes=[0], window_size=28),
+        image_token_id=300, video_token_id=301, vision_start_token_id=302, vision_end_token_id=303)
+    hf = transformers.Qwen2_5_VLForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "language_model" in n and (n.endswith(".bias") or n.endswith("norm.weight")):
+                p.add_(torch.randn_like(p) * 0.1)
+    d = cfg.to_dict()
+    d["architectures"] = ["Qwen2_5_VLForConditionalGeneration"]
+    _save(hf, d, tmp_path)
+    llm = _engine(tmp_path)
+    assert llm.weights.layers[0].qkv_bias is not None
+    for prompt in ([5, 6, 7, 8, 9, 10, 11], [200, 3, 17]):
+        rec = llm.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True))[0]
+        with torch.no_grad():
+            want = hf.generate(torch.tensor([prompt]), max_new_tokens=8, do_sample=False, pad_token_id=0,
+                               eos_token_id=None)[0, len(prompt):].tolist()
+        assert list(rec.tokens) == want
+
+
+def test_qwen3_vl_checkpoint_serves_text_like_transformers(tmp_path):
+    """A tiny ``Qwen3VLForConditionalGeneration`` (interleaved multimodal rotary sections, per-head q/k norms):
+    text-only requests give transformers' tokens."""
+    from modular_b200.pipelines.context import SamplingParams
+
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3VLConfig(
+        text_config=dict(hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, vocab_size=320, max_position_embeddings=512, rope_theta=1e6,
+                         rms_norm_eps=1e-6, tie_word_embeddings=False,
+                         rope_scaling={"rope_type": "default", "mrope_section": [4, 6, 6], "mrope_interleaved": True}),
+        vision_config=dict(depth=1, hidden_size=32, intermediate_size=64, num_heads=2, out_hidden_size=64, patch_size=16,
+                           spatial_merge_size=2, temporal_patch_size=2, deepstack_visual_indexes=[0],
+                           num_position_embeddings=16),
+        image_token_id=300, video_token_id=301, vision_start_token_id=302, vision_end_token_id=303)
+    hf = transformers.Qwen3VLForConditionalGeneration(cfg).eval()
+    d = cfg.to_dict()
+    d["architectures"] = ["Qwen3VLForConditionalGeneration"]
+    _save(hf, d, tmp_path)
+    llm = _engine(tmp_path)
+    assert llm.weights.layers[0].q_norm is not None
+    prompt = [5, 6, 7, 8, 9, 10, 11]
+    rec = llm.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True))[0]
+    with torch.no_grad():
+        want = hf.generate(torch.tensor([prompt]), max_new_tokens=8, do_sample=False, pad_token_id=0,
+                           eos_token_id=None)[0, len(prompt):].tolist()
+    assert list(rec.tokens) == want
