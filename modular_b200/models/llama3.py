@@ -853,9 +853,10 @@ def adapt_hf_state_dict(sd: dict) -> dict:
     are dropped: such checkpoints are served for text."""
     out = {}
     for k, v in sd.items():
-        if any(part in k for part in ("vision_tower.", "vision_model.", "multi_modal_projector.", "visual.")):
+        if any(part in k for part in ("vision_tower.", "vision_model.", "multi_modal_projector.", "visual.",
+                                      "model.connector.")):
             continue
-        for pre in ("model.language_model.", "language_model.model.", "language_model.", "model."):
+        for pre in ("model.language_model.", "language_model.model.", "language_model.", "model.text_model.", "model."):
             if k.startswith(pre):
                 k = k[len(pre):]
                 break

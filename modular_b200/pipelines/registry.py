@@ -257,7 +257,8 @@ def _register_builtin() -> None:
     # vision-language checkpoints around a Mistral or Llama language model: that model is served, for text (the
     # vision tower and projector are dropped at load, requests with image parts are refused)
     for name, repo in (("Mistral3ForConditionalGeneration", "mistralai/Mistral-Small-3.1-24B-Instruct-2503"),
-                       ("LlavaForConditionalGeneration", "mistral-community/pixtral-12b")):
+                       ("LlavaForConditionalGeneration", "mistral-community/pixtral-12b"),
+                       ("Idefics3ForConditionalGeneration", "HuggingFaceTB/SmolVLM-Instruct")):
         PIPELINE_REGISTRY.register(SupportedArchitecture(
             name=name, config_class=MistralConfig, weights_class=Llama3Weights, model_class=Llama3Model,
             default_encoding="bfloat16", supported_encodings=("bfloat16", "float32", "float8_e4m3fn"),

@@ -417,9 +417,11 @@ def test_gemma3_vision_language_checkpoint_serves_its_language_model(tmp_path):
     assert list(rec.tokens) == want
 
 
-def test_vision_language_checkpoint_around_mistral_serves_its_language_model(tmp_path):
-    """``Mistral3ForConditionalGeneration`` in the ``language_model.model.*`` layout with an untied head: the vision
-    tower and projector are dropped, the language model matches ``MistralForCausalLM``."""
+@pytest.mark.parametrize("layout", ["mistral3", "idefics3"])
+def test_vision_language_checkpoint_around_mistral_serves_its_language_model(tmp_path, layout):
+    """``Mistral3ForConditionalGeneration`` in the ``language_model.model.*`` layout with an untied head, and the
+    ``model.text_model.*`` layout of ``Idefics3ForConditionalGeneration``: the vision tower and projector are dropped,
+    the language model matches ``MistralForCausalLM``."""
     from modular_b200.pipelines.context import SamplingParams
     from safetensors.torch import save_file
 
@@ -428,12 +430,19 @@ def test_vision_language_checkpoint_around_mistral_serves_its_language_model(tmp
                                       num_key_value_heads=2, vocab_size=320, max_position_embeddings=512,
                                       sliding_window=None, tie_word_embeddings=False)
     hf = transformers.MistralForCausalLM(text).eval()
-    sd = {"language_model." + k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()}
-    sd["vision_tower.transformer.layers.0.attention.q_proj.weight"] = torch.zeros(8, 8)
-    sd["multi_modal_projector.linear_1.weight"] = torch.zeros(64, 8)
+    if layout == "mistral3":
+        sd = {"language_model." + k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()}
+        sd["vision_tower.transformer.layers.0.attention.q_proj.weight"] = torch.zeros(8, 8)
+        sd["multi_modal_projector.linear_1.weight"] = torch.zeros(64, 8)
+    else:
+        sd = {k.replace("model.", "model.text_model.", 1): v.detach().clone().contiguous()
+              for k, v in hf.state_dict().items()}
+        sd["model.vision_model.embeddings.patch_embedding.weight"] = torch.zeros(8, 8)
+        sd["model.connector.modality_projection.proj.weight"] = torch.zeros(64, 8)
     save_file(sd, str(tmp_path / "model.safetensors"))
+    arch = "Mistral3ForConditionalGeneration" if layout == "mistral3" else "Idefics3ForConditionalGeneration"
     (tmp_path / "config.json").write_text(json.dumps({
-        "architectures": ["Mistral3ForConditionalGeneration"], "model_type": "mistral3", "text_config": text.to_dict(),
+        "architectures": [arch], "model_type": layout, "text_config": text.to_dict(),
         "vision_config": {"model_type": "pixtral", "hidden_size": 8}}))
     llm = _engine(tmp_path)
     prompt = [5, 6, 7, 8, 9, 10, 11]
